@@ -1,0 +1,90 @@
+"""Mamba-2 mixer (in_proj -> causal depthwise conv + SiLU -> SSD -> gated RMSNorm -> out_proj).
+
+Parameter names, shapes and initialisation ranges follow the reference's
+``backbones/mamba2/mamba2_simple.py:24-122`` so its checkpoints load unchanged.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from ..norms import RMSNormGated
+from .ssd import ssd_chunk_scan
+
+
+class Mamba2Simple(nn.Module):
+    def __init__(
+        self,
+        d_model: int,
+        d_state: int = 64,
+        d_conv: int = 4,
+        expand: int = 2,
+        headdim: int = 128,
+        ngroups: int = 1,
+        A_init_range=(1, 16),
+        dt_min: float = 0.001,
+        dt_max: float = 0.1,
+        dt_init_floor: float = 1e-4,
+        dt_limit=(0.0, float("inf")),
+        bias: bool = False,
+        conv_bias: bool = True,
+        chunk_size: int = 256,
+        use_mem_eff_path: bool = True,
+        layer_idx=None,
+        device=None,
+        dtype=None,
+    ) -> None:
+        super().__init__()
+        fk = {"device": device, "dtype": dtype}
+        self.d_model, self.d_state, self.d_conv, self.expand = d_model, d_state, d_conv, expand
+        self.d_inner = expand * d_model
+        self.headdim, self.ngroups = headdim, ngroups
+        if self.d_inner % headdim != 0:
+            raise ValueError("expand * d_model must be divisible by headdim")
+        self.nheads = self.d_inner // headdim
+        self.dt_limit = dt_limit
+        self.chunk_size = chunk_size
+        self.use_mem_eff_path = use_mem_eff_path
+        self.layer_idx = layer_idx
+
+        # in_proj output order: [z, x, B, C, dt]
+        self.in_proj = nn.Linear(d_model, 2 * self.d_inner + 2 * ngroups * d_state + self.nheads, bias=bias, **fk)
+        conv_dim = self.d_inner + 2 * ngroups * d_state
+        self.conv1d = nn.Conv1d(conv_dim, conv_dim, kernel_size=d_conv, groups=conv_dim, padding=d_conv - 1, bias=conv_bias, **fk)
+
+        dt = torch.exp(torch.rand(self.nheads, **fk) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min))
+        dt = torch.clamp(dt, min=dt_init_floor)
+        self.dt_bias = nn.Parameter(dt + torch.log(-torch.expm1(-dt)))  # inverse softplus
+        self.dt_bias._no_weight_decay = True
+        A = torch.empty(self.nheads, dtype=torch.float32, device=device).uniform_(*A_init_range)
+        self.A_log = nn.Parameter(torch.log(A).to(dtype=dtype))
+        self.A_log._no_weight_decay = True
+        self.D = nn.Parameter(torch.ones(self.nheads, device=device))
+        self.D._no_weight_decay = True
+        self.norm = RMSNormGated(self.d_inner, eps=1e-5, norm_before_gate=False, **fk)
+        self.out_proj = nn.Linear(self.d_inner, d_model, bias=bias, **fk)
+
+    def forward(self, u: torch.Tensor, seq_idx=None) -> torch.Tensor:
+        bsz, seqlen, _ = u.shape
+        zxbcdt = self.in_proj(u)
+        gn = self.ngroups * self.d_state
+        z, xBC, dt = torch.split(zxbcdt, [self.d_inner, self.d_inner + 2 * gn, self.nheads], dim=-1)
+        dt = F.softplus(dt.float() + self.dt_bias.float())
+        if self.dt_limit != (0.0, float("inf")):
+            dt = dt.clamp(self.dt_limit[0], self.dt_limit[1])
+        xBC = F.silu(self.conv1d(xBC.transpose(1, 2))[..., :seqlen].transpose(1, 2))
+        x, B, C = torch.split(xBC, [self.d_inner, gn, gn], dim=-1)
+        y = ssd_chunk_scan(
+            x.reshape(bsz, seqlen, self.nheads, self.headdim),
+            dt,
+            -torch.exp(self.A_log.float()),
+            B.reshape(bsz, seqlen, self.ngroups, self.d_state),
+            C.reshape(bsz, seqlen, self.ngroups, self.d_state),
+            chunk_size=self.chunk_size,
+            D=self.D,
+        )
+        y = self.norm(y.reshape(bsz, seqlen, self.d_inner), z)
+        return self.out_proj(y.to(self.out_proj.weight.dtype))

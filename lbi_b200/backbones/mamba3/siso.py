@@ -1,0 +1,131 @@
+"""Mamba-3 single-input single-output (SISO) scan.
+
+Maths (reference Triton kernels backbones/mamba3/ops/triton/mamba3/
+mamba3_siso_fwd.py:256-424 and angle_dt.py:83-119; the reference ships no
+PyTorch restatement of them):
+
+    theta_t = (sum_{i<=t} pi * tanh(angle_i) * dt_i) mod 2pi           rotary phase, per head
+    gamma_t = dt_t * sigmoid(trap_t)                                   trapezoid weight of token t at time t
+    scale_t = gamma_t + dt_{t+1} * (1 - sigmoid(trap_{t+1}))           total weight with which token t enters the state
+    Qr_t = Rot_theta_t(Q_t + b_Q),  Kr_t = Rot_theta_t(K_t + b_K)      pairwise (2i, 2i+1) rotation of the first pairs
+    h_t  = exp(ADT_t) h_{t-1} + scale_t * V_t Kr_t^T
+    o_t  = Qr_t . (exp(ADT_t) h_{t-1}) + (D + gamma_t <Q_t + b_Q, K_t + b_K>) V_t
+    out_t = o_t * silu(Z_t)
+
+``mamba3_siso_chunked`` evaluates this chunk by chunk with differentiable tensor
+ops (CPU or CUDA); ``mamba3_siso_recurrent_reference`` is the fp64 token loop
+used as the oracle.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+
+TWO_PI = 2.0 * math.pi
+
+
+def angle_dt_cumsum(angles: torch.Tensor, dt: torch.Tensor) -> torch.Tensor:
+    """angles [b, l, h, s], dt [b, l, h] -> cumulative rotary phase [b, l, h, s] in [0, 2pi)."""
+    vals = torch.tanh(angles.float()) * math.pi * dt.float().unsqueeze(-1)
+    theta = torch.cumsum(vals, dim=1)
+    return theta - TWO_PI * torch.floor(theta / TWO_PI)
+
+
+def _rotate_pairs(x: torch.Tensor, theta: torch.Tensor) -> torch.Tensor:
+    """Rotate pairs (2i, 2i+1) of the last dim by theta[..., i]; pairs beyond theta's width stay fixed."""
+    n_angles = theta.shape[-1]
+    head, tail = x[..., : 2 * n_angles], x[..., 2 * n_angles :]
+    pairs = head.unflatten(-1, (n_angles, 2))
+    a, b = pairs[..., 0], pairs[..., 1]
+    cos, sin = torch.cos(theta), torch.sin(theta)
+    rotated = torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).flatten(-2)
+    return torch.cat((rotated, tail), dim=-1)
+
+
+def _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, compute_dtype):
+    """Shared preprocessing: per-head biased/rotated Q, K, trapezoid weights."""
+    bsz, seqlen, nheads, _ = V.shape
+    rep = nheads // Q.shape[2]
+    Qh = Q.to(compute_dtype).repeat_interleave(rep, dim=2) + Q_bias.to(compute_dtype)[None, None]
+    Kh = K.to(compute_dtype).repeat_interleave(rep, dim=2) + K_bias.to(compute_dtype)[None, None]
+    dt = DT.to(compute_dtype).transpose(1, 2)  # [b, l, h]
+    adt = ADT.to(compute_dtype).transpose(1, 2)
+    sig = torch.sigmoid(Trap.to(compute_dtype).transpose(1, 2))
+    gamma = dt * sig
+    carry = F.pad((dt * (1.0 - sig))[:, 1:], (0, 0, 0, 1))  # dt_{t+1} (1 - sigma_{t+1}), zero after the last token
+    scale = gamma + carry
+    theta = angle_dt_cumsum(Angles, dt).to(compute_dtype)
+    qk_dot = gamma * (Qh * Kh).sum(dim=-1)
+    Qr = _rotate_pairs(Qh, theta)
+    Kr = _rotate_pairs(Kh, theta) * scale.unsqueeze(-1)
+    return Qr, Kr, adt, qk_dot
+
+
+def mamba3_siso_recurrent_reference(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, Z=None):
+    """fp64 token-by-token evaluation.  Q, K [b, l, g, n]; V, Z [b, l, h, p]; ADT, DT, Trap [b, h, l];
+    Q_bias, K_bias [h, n]; Angles [b, l, h, s]; D [h]."""
+    bsz, seqlen, nheads, headdim = V.shape
+    Qr, Kr, adt, qk_dot = _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, torch.float64)
+    Vd = V.double()
+    state = torch.zeros(bsz, nheads, headdim, Qr.shape[-1], dtype=torch.float64, device=V.device)
+    outs = []
+    for t in range(seqlen):
+        state = state * torch.exp(adt[:, t])[..., None, None]
+        o = torch.einsum("bhpn,bhn->bhp", state, Qr[:, t])
+        skip = qk_dot[:, t] if D is None else qk_dot[:, t] + D.double()[None]
+        o = o + skip[..., None] * Vd[:, t]
+        state = state + Vd[:, t][..., None] * Kr[:, t][:, :, None, :]
+        outs.append(o)
+    out = torch.stack(outs, dim=1)
+    if Z is not None:
+        out = out * F.silu(Z.double())
+    return out
+
+
+def mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, Z=None, chunk_size: int = 64):
+    """Chunked evaluation in fp32 with the same argument layout as the recurrent reference."""
+    bsz, seqlen, nheads, headdim = V.shape
+    out_dtype = V.dtype
+    Qr, Kr, adt, qk_dot = _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, torch.float32)
+    Vf = V.float()
+    pad = (-seqlen) % chunk_size
+    if pad:
+        Qr = F.pad(Qr, (0, 0, 0, 0, 0, pad))
+        Kr = F.pad(Kr, (0, 0, 0, 0, 0, pad))
+        Vf = F.pad(Vf, (0, 0, 0, 0, 0, pad))
+        adt = F.pad(adt, (0, 0, 0, pad))
+        qk_dot = F.pad(qk_dot, (0, 0, 0, pad))
+    nchunks = (seqlen + pad) // chunk_size
+    dstate = Qr.shape[-1]
+    Qc = Qr.view(bsz, nchunks, chunk_size, nheads, dstate)
+    Kc = Kr.view(bsz, nchunks, chunk_size, nheads, dstate)
+    Vc = Vf.view(bsz, nchunks, chunk_size, nheads, headdim)
+    cum = torch.cumsum(adt.view(bsz, nchunks, chunk_size, nheads), dim=2)
+    total = cum[:, :, -1]
+
+    strict = torch.ones(chunk_size, chunk_size, dtype=torch.bool, device=V.device).tril(-1)
+    diff = cum[:, :, :, None, :] - cum[:, :, None, :, :]
+    decay = torch.exp(diff.masked_fill(~strict[None, None, :, :, None], float("-inf")))
+    scores = torch.einsum("bcihn,bcjhn->bcijh", Qc, Kc) * decay
+    y = torch.einsum("bcijh,bcjhp->bcihp", scores, Vc)
+
+    to_end = torch.exp(total[:, :, None, :] - cum)
+    chunk_states = torch.einsum("bcqhp,bcqh,bcqhn->bchpn", Vc, to_end, Kc)
+    state = torch.zeros(bsz, nheads, headdim, dstate, dtype=torch.float32, device=V.device)
+    incoming = []
+    for c in range(nchunks):
+        incoming.append(state)
+        state = state * torch.exp(total[:, c])[..., None, None] + chunk_states[:, c]
+    prev = torch.stack(incoming, dim=1)
+    y = y + torch.einsum("bcqhn,bchpn,bcqh->bcqhp", Qc, prev, torch.exp(cum))
+
+    skip = qk_dot.view(bsz, nchunks, chunk_size, nheads)
+    if D is not None:
+        skip = skip + D.float()[None, None, None, :]
+    y = y + skip.unsqueeze(-1) * Vc
+    y = y.reshape(bsz, nchunks * chunk_size, nheads, headdim)[:, :seqlen]
+    if Z is not None:
+        y = y * F.silu(Z.float())
+    return y.to(out_dtype)

@@ -1,0 +1,95 @@
+"""Normalisation layers shared by all backbones.
+
+The reference keeps a plain-PyTorch RMSNorm for the Transformer
+(backbones/transformer/block.py:12-22) and Triton-only RMSNorm / gated RMSNorm
+for the Mamba families (backbones/mamba2/ops/triton/layernorm_gated.py:384-437),
+which is why its Mamba models cannot run without a GPU.  Here one set of modules
+serves every backbone: on CUDA tensors they call the fused sm_100a kernels in
+``lbi_b200.ops``; on CPU they evaluate the same formula in fp32 PyTorch.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+
+def rms_norm_reference(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    *,
+    eps: float,
+    z: torch.Tensor | None = None,
+    norm_before_gate: bool = True,
+    group_size: int | None = None,
+) -> torch.Tensor:
+    """fp32 RMSNorm with optional SiLU gate; the oracle for the fused kernels."""
+    out_dtype = x.dtype
+    xf = x.float()
+    zf = z.float() if z is not None else None
+    if zf is not None and not norm_before_gate:
+        xf = xf * F.silu(zf)
+    if group_size is None or group_size == xf.shape[-1]:
+        rstd = torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + eps)
+        out = xf * rstd * weight.float()
+    else:
+        grouped = xf.unflatten(-1, (-1, group_size))
+        rstd = torch.rsqrt(grouped.square().mean(dim=-1, keepdim=True) + eps)
+        out = (grouped * rstd).flatten(-2) * weight.float()
+    if zf is not None and norm_before_gate:
+        out = out * F.silu(zf)
+    return out.to(out_dtype)
+
+
+class RMSNorm(nn.Module):
+    """``y = x / rms(x) * weight`` computed in fp32 and cast back to the input dtype."""
+
+    def __init__(self, dim: int, eps: float = 1e-5, device=None, dtype=None) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+        self.eps = float(eps)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+            from lbi_b200.ops import rmsnorm
+
+            return rmsnorm(x, self.weight, self.eps)
+        xf = x.float()
+        rstd = torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + self.eps)
+        return (xf * rstd).to(dtype=x.dtype) * self.weight.to(dtype=x.dtype)
+
+
+class RMSNormGated(nn.Module):
+    """RMSNorm with an optional SiLU gate ``z`` applied before or after normalisation.
+
+    ``norm_before_gate=False`` is the Mamba-2 setting ``norm(x * silu(z))``
+    (reference backbones/mamba2/mamba2_simple.py:119); without ``z`` it is a
+    plain RMSNorm as used for the Mamba-3 B/C projections
+    (reference backbones/mamba3/mamba3.py:116-117).
+    """
+
+    def __init__(
+        self,
+        dim: int,
+        eps: float = 1e-5,
+        norm_before_gate: bool = True,
+        group_size: int | None = None,
+        device=None,
+        dtype=None,
+    ) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, device=device, dtype=dtype))
+        self.register_parameter("bias", None)
+        self.eps = float(eps)
+        self.norm_before_gate = bool(norm_before_gate)
+        self.group_size = group_size
+
+    def forward(self, x: torch.Tensor, z: torch.Tensor | None = None) -> torch.Tensor:
+        return rms_norm_reference(
+            x,
+            self.weight,
+            eps=self.eps,
+            z=z,
+            norm_before_gate=self.norm_before_gate,
+            group_size=self.group_size,
+        )

@@ -1,0 +1,88 @@
+"""Causal self-attention with fused qkv projection, optional depthwise causal
+conv on qkv, RoPE and grouped-query heads.
+
+Parameter names (``in_proj``, ``conv1d``, ``out_proj``) and the op order match
+the reference's ``backbones/transformer/attention.py:19-112``.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .rope import apply_rope
+
+
+class CausalSelfAttention(nn.Module):
+    def __init__(
+        self,
+        dim: int,
+        *,
+        n_heads: int,
+        n_kv_heads: int,
+        head_dim: int,
+        rope_base: float = 10000.0,
+        rope_interleaved: bool = False,
+        softmax_scale: float | None = None,
+        d_conv: int = 0,
+        use_flash_attn: bool = True,
+        bias: bool = False,
+    ) -> None:
+        super().__init__()
+        if n_heads % n_kv_heads != 0:
+            raise ValueError("n_heads must be divisible by n_kv_heads")
+        self.dim = dim
+        self.n_heads = n_heads
+        self.n_kv_heads = n_kv_heads
+        self.head_dim = head_dim
+        self.rope_base = rope_base
+        self.rope_interleaved = rope_interleaved
+        self.softmax_scale = softmax_scale
+        self.d_conv = d_conv
+        self.use_flash_attn = use_flash_attn
+        self.qkv_dim = head_dim * (n_heads + 2 * n_kv_heads)
+        self.out_dim = head_dim * n_heads
+        self.in_proj = nn.Linear(dim, self.qkv_dim, bias=bias)
+        if d_conv > 0:
+            self.conv1d = nn.Conv1d(
+                self.qkv_dim, self.qkv_dim, kernel_size=d_conv, padding=d_conv - 1, groups=self.qkv_dim, bias=bias
+            )
+        self.out_proj = nn.Linear(self.out_dim, dim, bias=bias)
+
+    @property
+    def scale(self) -> float:
+        return self.softmax_scale if self.softmax_scale is not None else 1.0 / math.sqrt(self.head_dim)
+
+    def split_heads(self, qkv: torch.Tensor):
+        """[B, T, qkv_dim] -> q [B, H, T, Dh], k/v [B, Hkv, T, Dh] (views)."""
+        bsz, seqlen, _ = qkv.shape
+        q_dim, kv_dim = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        q, k, v = qkv.split((q_dim, kv_dim, kv_dim), dim=-1)
+        q = q.view(bsz, seqlen, self.n_heads, self.head_dim).transpose(1, 2)
+        k = k.view(bsz, seqlen, self.n_kv_heads, self.head_dim).transpose(1, 2)
+        v = v.view(bsz, seqlen, self.n_kv_heads, self.head_dim).transpose(1, 2)
+        return q, k, v
+
+    def expand_kv(self, x: torch.Tensor) -> torch.Tensor:
+        if self.n_kv_heads == self.n_heads:
+            return x
+        return x.repeat_interleave(self.n_heads // self.n_kv_heads, dim=1)
+
+    def causal_conv(self, qkv: torch.Tensor) -> torch.Tensor:
+        seqlen = qkv.shape[1]
+        return self.conv1d(qkv.transpose(1, 2))[..., :seqlen].transpose(1, 2).contiguous()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        bsz, seqlen, _ = x.shape
+        qkv = self.in_proj(x)
+        if self.d_conv > 0:
+            qkv = self.causal_conv(qkv)
+        q, k, v = self.split_heads(qkv)
+        q = apply_rope(q, base=self.rope_base, interleaved=self.rope_interleaved)
+        k = apply_rope(k, base=self.rope_base, interleaved=self.rope_interleaved)
+        k, v = self.expand_kv(k), self.expand_kv(v)
+        out = F.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=True, scale=self.scale)
+        out = out.transpose(1, 2).contiguous().view(bsz, seqlen, self.out_dim)
+        return self.out_proj(out)

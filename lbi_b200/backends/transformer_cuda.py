@@ -1,0 +1,23 @@
+"""CUDA lowering for Transformer regions.
+
+The reference's class of the same name exposes only the attention kernel and leaves the region-level
+methods as stubs (backends/transformer_cuda.py:23-83).  This one is the structured lowering plus the
+attention entry point with the reference's argument layout.
+"""
+from __future__ import annotations
+
+import torch
+
+from .transformer import StructuredTransformerLowering
+
+
+class CudaTransformerLowering(StructuredTransformerLowering):
+    def __init__(self, *, allow_reference_fallback: bool = False) -> None:
+        self.allow_reference_fallback = bool(allow_reference_fallback)
+
+    def attention_input_pullback_basis(self, q, k, v, output_cotangent_basis, *, scale=None, causal=True,
+                                       kernel_mode: str = "tcgen05_pblock"):
+        from ..ops.attention import attention_input_pullback_basis
+
+        return attention_input_pullback_basis(q, k, v, output_cotangent_basis, scale=scale, causal=causal,
+                                              use_cuda=q.is_cuda, kernel_mode=kernel_mode)

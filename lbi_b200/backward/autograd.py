@@ -1,0 +1,23 @@
+"""Dense autograd engine: ``loss.backward()`` and collect (reference backward/autograd.py:11-28)."""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+from torch import nn
+
+from .base import ADResult, collect_named_grads
+
+
+def autograd_backward_step(model: nn.Module, loss: torch.Tensor) -> dict:
+    model.zero_grad(set_to_none=True)
+    loss.backward()
+    return collect_named_grads(model)
+
+
+class AutogradEngine:
+    name = "autograd"
+    requires_detached_states = False
+
+    def backward(self, *, model: nn.Module, loss: torch.Tensor, cache: Any | None = None) -> ADResult:
+        return ADResult(grad_map=autograd_backward_step(model, loss), diagnostics={})

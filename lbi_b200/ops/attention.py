@@ -1,0 +1,121 @@
+"""Causal attention forward and the input pullback over a basis of output cotangents.
+
+``attention_input_pullback_basis`` keeps the reference's call signature and tensor layout
+(cuda/transformer/__init__.py:279-355: q, k, v [B, H, T, Dh]; dO_basis [B, P, H, T, Dh] ->
+dQ, dK, dV [B, P, H, T, Dh]).  Kernel modes:
+
+* ``"tcgen05_pblock"``  this package's sm_100a kernel: S and P = softmax(S) are recomputed once per
+  (query tile, key tile) and reused by every basis direction; all five products run on tcgen05 with
+  accumulators in TMEM (replaces the reference's WMMA kernels and host loop,
+  cuda/transformer/attention_pullback_mma.cu:60-515);
+* ``"fa2_loop"``        P library flash-attention backward passes (the reference's fallback and the
+  baseline the kernel is timed against);
+* ``"dense"``           the O(T^2) fp32 formula (oracle).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import reference as ref
+from .native import ext, native_available
+
+_LIB_STATE_KEYS = ("cum_q", "cum_k", "max_q", "max_k", "seed", "offset")
+
+
+def _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim):
+    q_dim, kv_dim = n_heads * head_dim, n_kv_heads * head_dim
+    x = qkv.view(batch, seq_len, q_dim + 2 * kv_dim)
+    q = x[..., :q_dim].unflatten(-1, (n_heads, head_dim)).transpose(1, 2)
+    k = x[..., q_dim : q_dim + kv_dim].unflatten(-1, (n_kv_heads, head_dim)).transpose(1, 2)
+    v = x[..., q_dim + kv_dim :].unflatten(-1, (n_kv_heads, head_dim)).transpose(1, 2)
+    return q, k, v
+
+
+def _expand(x, rep):
+    return x if rep == 1 else x.repeat_interleave(rep, dim=1)
+
+
+def flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale):
+    """Library flash-attention forward on the packed qkv buffer -> (out [n, H*Dh], lse [B, H, T])."""
+    q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
+    rep = n_heads // n_kv_heads
+    res = torch.ops.aten._scaled_dot_product_flash_attention(q, _expand(k, rep), _expand(v, rep), 0.0, True, False, scale=scale)
+    out, lse = res[0], res[1]
+    return out.transpose(1, 2).reshape(batch * seq_len, n_heads * head_dim), lse
+
+
+def _library_backward(do, q, k, v, out, lse, scale):
+    """One flash-attention backward; all tensors [B, H, T, Dh]."""
+    t = q.shape[2]
+    empty = torch.empty(0, dtype=torch.int64, device=q.device)
+    seed = torch.zeros((), dtype=torch.int64, device=q.device)
+    return torch.ops.aten._scaled_dot_product_flash_attention_backward(
+        do, q, k, v, out, lse, empty, empty, t, t, 0.0, True, seed, seed, scale=scale
+    )
+
+
+def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, kernel_mode=None):
+    """Packed layout: do_rows [P*n, H*Dh] -> d_qkv [P*n, (H+2Hkv)*Dh]."""
+    n = batch * seq_len
+    nbasis = do_rows.shape[0] // n
+    qkv_dim = (n_heads + 2 * n_kv_heads) * head_dim
+    mode = kernel_mode or default_kernel_mode(do_rows, head_dim, n_heads, n_kv_heads, seq_len)
+    if mode == "tcgen05_pblock":
+        return ext().attn_pullback_packed(do_rows.contiguous(), qkv, o, lse, batch, seq_len, n_heads, head_dim, float(scale))
+    q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
+    rep = n_heads // n_kv_heads
+    ke, ve = _expand(k, rep), _expand(v, rep)
+    out4 = o.view(batch, seq_len, n_heads, head_dim).transpose(1, 2)
+    d_qkv = torch.empty(nbasis * n, qkv_dim, dtype=do_rows.dtype, device=do_rows.device)
+    q_dim, kv_dim = n_heads * head_dim, n_kv_heads * head_dim
+    for p in range(nbasis):
+        do = do_rows[p * n : (p + 1) * n].view(batch, seq_len, n_heads, head_dim).transpose(1, 2)
+        dq, dk, dv = _library_backward(do, q, ke, ve, out4, lse, scale)
+        if rep > 1:
+            dk = dk.unflatten(1, (n_kv_heads, rep)).sum(dim=2)
+            dv = dv.unflatten(1, (n_kv_heads, rep)).sum(dim=2)
+        dst = d_qkv[p * n : (p + 1) * n].view(batch, seq_len, qkv_dim)
+        dst[..., :q_dim] = dq.transpose(1, 2).reshape(batch, seq_len, q_dim)
+        dst[..., q_dim : q_dim + kv_dim] = dk.transpose(1, 2).reshape(batch, seq_len, kv_dim)
+        dst[..., q_dim + kv_dim :] = dv.transpose(1, 2).reshape(batch, seq_len, kv_dim)
+    return d_qkv
+
+
+def tcgen05_pullback_supported(dtype, head_dim, n_heads, n_kv_heads, seq_len) -> bool:
+    return (
+        native_available()
+        and hasattr(ext(), "attn_pullback_packed")
+        and dtype == torch.bfloat16
+        and head_dim in (64, 128)
+        and n_heads == n_kv_heads
+        and seq_len % 128 == 0
+    )
+
+
+def default_kernel_mode(t, head_dim, n_heads, n_kv_heads, seq_len) -> str:
+    if t.is_cuda and tcgen05_pullback_supported(t.dtype, head_dim, n_heads, n_kv_heads, seq_len):
+        return "tcgen05_pblock"
+    return "fa2_loop"
+
+
+def attention_input_pullback_basis(q, k, v, dO_basis, *, scale=None, causal=True, use_cuda=True, kernel_mode=None):
+    """q, k, v [B, H, T, Dh]; dO_basis [B, P, H, T, Dh] -> (dQ, dK, dV) each [B, P, H, T, Dh]."""
+    if q.dim() != 4 or dO_basis.dim() != 5:
+        raise ValueError("expected q,k,v [B,H,T,Dh] and dO_basis [B,P,H,T,Dh]")
+    bsz, heads, seqlen, head_dim = q.shape
+    nbasis = dO_basis.shape[1]
+    scale = float(scale) if scale else 1.0 / math.sqrt(head_dim)
+    if not use_cuda or not q.is_cuda or kernel_mode == "dense" or not causal:
+        dq, dk, dv = ref.attention_input_pullback_dense(q, k, v, dO_basis, scale, causal)
+        return dq.to(q.dtype), dk.to(q.dtype), dv.to(q.dtype)
+    if k.shape[1] != heads:
+        raise ValueError("expand grouped kv heads before calling the basis pullback")
+    # pack to the token-major layout the kernels use
+    qkv = torch.cat([x.transpose(1, 2).reshape(bsz * seqlen, heads * head_dim) for x in (q, k, v)], dim=-1).contiguous()
+    o_rows, lse = flash_forward_packed(qkv, bsz, seqlen, heads, heads, head_dim, scale)
+    do_rows = dO_basis.permute(1, 0, 3, 2, 4).reshape(nbasis * bsz * seqlen, heads * head_dim).contiguous()
+    d_qkv = pullback_packed(do_rows, qkv, o_rows.contiguous(), lse, bsz, seqlen, heads, heads, head_dim, scale, kernel_mode)
+    parts = d_qkv.view(nbasis, bsz, seqlen, 3, heads, head_dim).permute(3, 1, 0, 4, 2, 5)
+    return parts[0], parts[1], parts[2]

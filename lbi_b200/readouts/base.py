@@ -1,0 +1,22 @@
+"""Readout protocol: region features -> vocabulary logits (reference readouts/base.py:12-28)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Protocol, runtime_checkable
+
+import torch
+from torch import nn
+
+
+@dataclass
+class ReadoutCache:
+    features: torch.Tensor
+    normed_features: torch.Tensor
+    logits: torch.Tensor
+
+
+@runtime_checkable
+class ReadoutModule(Protocol):
+    def forward(self, features: torch.Tensor, *, canvas) -> torch.Tensor: ...
+
+    def vjp_parameters(self) -> list[nn.Parameter]: ...
