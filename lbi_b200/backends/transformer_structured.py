@@ -47,7 +47,9 @@ class StructuredRegionCache:
     layer_range: tuple[int, int]
     region_input: torch.Tensor  # [n, D] in the activation dtype
     layers: list[LayerCache] = field(default_factory=list)
-    output: torch.Tensor | None = None  # fp32 [n, D]
+    output: torch.Tensor | None = None  # fp32 [n, D] = last_branch + last_stream
+    last_branch: torch.Tensor | None = None
+    last_stream: torch.Tensor | None = None
 
 
 class LayerWeights:
@@ -56,17 +58,24 @@ class LayerWeights:
     __slots__ = ("block", "norm1", "norm2", "w_qkv", "w_o", "w_fc1", "w_fc2", "w_qkv_t", "w_o_t", "w_fc1_t", "w_fc2_t",
                  "conv_w", "conv_b", "version")
 
-    def __init__(self, block, dtype: torch.dtype, want_transposes: bool) -> None:
+    def __init__(self, block, dtype: torch.dtype, want_transposes: bool, shadow_of=None) -> None:
         self.block = block
         self.version = None
-        self.refresh(dtype, want_transposes)
+        self.refresh(dtype, want_transposes, shadow_of)
 
-    def refresh(self, dtype: torch.dtype, want_transposes: bool) -> None:
+    def refresh(self, dtype: torch.dtype, want_transposes: bool, shadow_of=None) -> None:
         b = self.block
         for lin in (b.attn.in_proj, b.attn.out_proj, b.mlp.fc1, b.mlp.fc2):
             if lin.bias is not None:
                 raise NotImplementedError("the structured Transformer lowering supports bias-free projections only")
-        cast = (lambda w: w.detach().to(dtype).contiguous())
+
+        def cast(w):
+            if shadow_of is not None:
+                view = shadow_of(w)
+                if view is not None and view.dtype == dtype:
+                    return view  # lives in the optimizer's bf16 shadow buffer: refreshed by the AdamW kernel itself
+            return w.detach().to(dtype).contiguous()
+
         self.norm1 = b.norm.weight.detach()
         self.norm2 = b.norm2.weight.detach()
         self.w_qkv, self.w_o = cast(b.attn.in_proj.weight), cast(b.attn.out_proj.weight)
@@ -90,6 +99,8 @@ class StructuredTransformerRegion:
         self.blocks = blocks
         self.act_dtype = act_dtype
         self._weights: dict[tuple, list[LayerWeights]] = {}
+        self.shadow_of = None  # callable(param) -> compute-dtype view, set by the flat-buffer optimizer
+        self.want_transposes = False  # K-major copies of W^T; only needed when the GEMM's MN-major path is off
 
     # ------------------------------------------------------------------ weights
     def weights(self, dtype: torch.dtype) -> list[LayerWeights]:
@@ -97,7 +108,7 @@ class StructuredTransformerRegion:
         key = (dtype, str(device))
         cached = self._weights.get(key)
         if cached is None:
-            cached = [LayerWeights(b, dtype, want_transposes=device.type == "cuda") for b in self.blocks]
+            cached = [LayerWeights(b, dtype, self.want_transposes and device.type == "cuda", self.shadow_of) for b in self.blocks]
             self._weights[key] = cached
         return cached
 
@@ -105,7 +116,7 @@ class StructuredTransformerRegion:
         """Call after an optimizer step that did not update the compute-dtype copies in place."""
         for (dtype, dev), layers in self._weights.items():
             for lw in layers:
-                lw.refresh(dtype, want_transposes=dev.startswith("cuda"))
+                lw.refresh(dtype, self.want_transposes and dev.startswith("cuda"), self.shadow_of)
 
     def _dims(self, index: int):
         attn = self.blocks[index].attn
@@ -113,8 +124,11 @@ class StructuredTransformerRegion:
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
-    def forward(self, region_input: torch.Tensor, layer_range: tuple[int, int]) -> tuple[torch.Tensor, StructuredRegionCache]:
-        """region_input [B, T, D] -> (fp32 output [B, T, D], cache)."""
+    def forward(self, region_input: torch.Tensor, layer_range: tuple[int, int], materialize_output: bool = True):
+        """region_input [B, T, D] -> (fp32 output [B, T, D], cache).
+
+        With ``materialize_output=False`` the sum ``branch + stream`` is left to the consumer (the final-norm
+        kernel fuses it) and ``None`` is returned in place of the output."""
         bsz, seqlen, dim = region_input.shape
         dtype = self.act_dtype or region_input.dtype
         x = region_input.reshape(bsz * seqlen, dim).to(dtype).contiguous()
@@ -142,6 +156,9 @@ class StructuredTransformerRegion:
             cache.layers.append(
                 LayerCache(stream1, rstd1, normed1, qkv_pre, qkv, attn_out, lse, stream2, rstd2, normed2, fc1_out, act)
             )
+        cache.last_branch, cache.last_stream = branch, stream
+        if not materialize_output:
+            return None, cache
         out = branch.float() if stream is None else branch.float() + stream
         cache.output = out
         return out.reshape(bsz, seqlen, dim), cache
@@ -166,11 +183,11 @@ class StructuredTransformerRegion:
             prefix = f"blocks.{index}."
             # MLP branch
             if grads is not None:
-                _acc(grads, prefix + "mlp.fc2.weight", ops.linear_wgrad(d_branch, lc.act))
+                _wgrad(grads, prefix + "mlp.fc2.weight", d_branch, lc.act)
             d_act = ops.linear_dgrad(d_branch, lw.w_fc2, lw.w_fc2_t)
             d_fc1 = ops.swiglu_bwd(d_act, lc.fc1_out)
             if grads is not None:
-                _acc(grads, prefix + "mlp.fc1.weight", ops.linear_wgrad(d_fc1, lc.normed2))
+                _wgrad(grads, prefix + "mlp.fc1.weight", d_fc1, lc.normed2)
             d_normed2 = ops.linear_dgrad(d_fc1, lw.w_fc1, lw.w_fc1_t)
             if grads is not None:
                 _acc(grads, prefix + "norm2.weight", ops.rmsnorm_wgrad(d_normed2, lc.stream2, lc.rstd2))
@@ -178,7 +195,7 @@ class StructuredTransformerRegion:
             # attention branch
             d_branch = d_stream.to(dtype)
             if grads is not None:
-                _acc(grads, prefix + "attn.out_proj.weight", ops.linear_wgrad(d_branch, lc.attn_out))
+                _wgrad(grads, prefix + "attn.out_proj.weight", d_branch, lc.attn_out)
             d_attn = ops.linear_dgrad(d_branch, lw.w_o, lw.w_o_t)
             d_qkv = ops.attention_pullback_packed(d_attn, lc.qkv, lc.attn_out, lc.lse, bsz, seqlen, heads, kv_heads, head_dim, scale)
             d_qkv = ops.rope_qkv(d_qkv, cos, sin, heads, kv_heads, head_dim, seqlen, interleaved, inverse=True)
@@ -190,7 +207,7 @@ class StructuredTransformerRegion:
                         _acc(grads, prefix + "attn.conv1d.bias", db)
                 d_qkv = ops.causal_conv_dgrad(d_qkv, lw.conv_w, bsz, seqlen)
             if grads is not None:
-                _acc(grads, prefix + "attn.in_proj.weight", ops.linear_wgrad(d_qkv, lc.normed1))
+                _wgrad(grads, prefix + "attn.in_proj.weight", d_qkv, lc.normed1)
             d_normed1 = ops.linear_dgrad(d_qkv, lw.w_qkv, lw.w_qkv_t)
             if grads is not None:
                 _acc(grads, prefix + "norm.weight", ops.rmsnorm_wgrad(d_normed1, lc.stream1, lc.rstd1))
@@ -209,7 +226,20 @@ class StructuredTransformerRegion:
         return self._reverse(cache, d_out_rows, grads)
 
 
-def _acc(grads: dict, name: str, value: torch.Tensor) -> None:
+def _wgrad(grads, name: str, dy: torch.Tensor, x: torch.Tensor) -> None:
+    """dW = dy^T x, accumulated straight into the sink's fp32 buffer when it offers one."""
+    target = grads.target(name) if hasattr(grads, "target") else None
+    if target is not None:
+        ops.linear_wgrad(dy, x, accumulate_into=target)
+    else:
+        _acc(grads, name, ops.linear_wgrad(dy, x))
+
+
+def _acc(grads, name: str, value: torch.Tensor) -> None:
+    target = grads.target(name) if hasattr(grads, "target") else None
+    if target is not None:
+        target.add_(value.reshape(target.shape).to(target.dtype))
+        return
     prev = grads.get(name)
     if prev is None:
         grads[name] = value.float()

@@ -1,0 +1,63 @@
+// C entry points of the lbi_b200 CUDA kernels.  All pointers are device pointers unless noted; every
+// function enqueues work on `stream` and returns the cudaError_t of the launch as an int (0 = success).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- fused elementwise / normalisation (elementwise.cu) -------------------------------------------------
+// new_stream = branch (+ stream); rstd = rsqrt(mean(new_stream^2) + eps); normed = new_stream * rstd * weight.
+int lbi_add_rmsnorm_fwd(const void* branch_bf16, const float* stream_or_null, const float* weight, void* normed_bf16,
+                        float* new_stream, float* rstd, int64_t rows, int dim, float eps, cudaStream_t stream);
+// d_stream_out = d_stream_in (or 0) + J_rmsnorm^T d_normed; activation rows are indexed by row % act_rows.
+int lbi_rmsnorm_bwd(const void* d_normed_bf16, const float* x_stream, const float* rstd, const float* weight,
+                    const float* d_stream_in_or_null, float* d_stream_out, int64_t rows, int64_t act_rows, int dim,
+                    cudaStream_t stream);
+// dw[d] = sum_r d_normed[r, d] * x[r, d] * rstd[r]; `partials` holds nblocks * dim floats.
+int lbi_rmsnorm_wgrad(const void* d_normed_bf16, const float* x_stream, const float* rstd, float* partials, float* dw,
+                      int64_t rows, int dim, int nblocks, cudaStream_t stream);
+int lbi_rope_qkv(void* qkv_bf16, const float* cos_tab, const float* sin_tab, int64_t rows, int n_rot_heads, int qkv_dim,
+                 int head_dim, int seq_len, int interleaved, int inverse, cudaStream_t stream);
+int lbi_swiglu_fwd(const void* u_bf16, void* a_bf16, int64_t rows, int hidden, cudaStream_t stream);
+int lbi_swiglu_bwd(const void* da_bf16, const void* u_bf16, void* du_bf16, int64_t rows, int64_t act_rows, int hidden,
+                   cudaStream_t stream);
+int lbi_add_condition(const void* canvas_bf16, const float* cond, void* out_bf16, int64_t rows, int dim, int seq_len,
+                      cudaStream_t stream);
+// out[g, d] = scale * sum_t rows[g * seq_len + t, d]; out must be zeroed by the caller (accumulates with atomics).
+int lbi_pool_tokens(const void* rows, int is_bf16, float* out, int64_t groups, int seq_len, int dim, float scale,
+                    cudaStream_t stream);
+int lbi_embedding_fwd(const int64_t* ids, const void* table, int table_is_bf16, void* out_bf16, int64_t rows, int dim,
+                      cudaStream_t stream);
+int lbi_embedding_scatter_add(float* d_table, const int64_t* ids, const void* d_rows, int rows_is_bf16, int64_t rows,
+                              int dim, cudaStream_t stream);
+int lbi_transpose_bf16(const void* in, void* out, int64_t rows, int64_t cols, cudaStream_t stream);
+int lbi_causal_conv_fwd(const void* x_bf16, const float* w, const float* bias_or_null, void* y_bf16, int64_t seqs,
+                        int seq_len, int channels, int width, cudaStream_t stream);
+int lbi_causal_conv_dgrad(const void* dy_bf16, const float* w, void* dx_bf16, int64_t seqs, int seq_len, int channels,
+                          int width, cudaStream_t stream);
+// sumsq_out += sum(x^2) over a flat fp32 buffer (sumsq_out zeroed by the caller).
+int lbi_sumsq(const float* x, int64_t n, float* sumsq_out, cudaStream_t stream);
+// AdamW with decoupled weight decay on flat fp32 buffers.  The gradient is multiplied by grad_mul and, when
+// sumsq_or_null is given, by the clip coefficient min(1, clip_norm / (sqrt(*sumsq * grad_mul^2) + 1e-6)).
+// shadow_bf16_or_null receives the updated parameters rounded to bf16.
+int lbi_adamw_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, void* shadow_bf16_or_null,
+                   int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay, int step, float grad_mul,
+                   const float* sumsq_or_null, float clip_norm, cudaStream_t stream);
+// Per-row softmax cross-entropy over bf16 logits [rows, vocab]: loss_sum += scale * (lse - logit[target]) and
+// logits are overwritten by scale * (softmax - onehot).  Rows with a negative target get zero gradient.
+int lbi_ce_fwd_bwd(void* logits_bf16, const int64_t* targets, float* loss_sum, int64_t rows, int vocab, float scale,
+                   cudaStream_t stream);
+
+// ---- interface Jacobian scans (suffix_scan.cu) -----------------------------------------------------------
+// out[b, k] = mats[b, k] @ mats[b, k+1] @ ... @ mats[b, K-1], out[b, K] = I;  mats [B, K, R, R] fp32 row-major.
+int lbi_suffix_scan(const float* mats, float* out, int batch, int k, int r, cudaStream_t stream);
+// g[b, k] = offsets[b, k] + mats[b, k] @ g[b, k+1], g[b, K] = seed (or 0);  g [B, K+1, R].
+int lbi_affine_suffix_scan(const float* mats, const float* offsets, const float* seed_or_null, float* g, int batch, int k,
+                           int r, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,331 @@
+// Python bindings of the lbi_b200 CUDA kernels (module lbi_b200._C).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "api.h"
+#include "api_gemm.h"
+
+namespace {
+
+using torch::Tensor;
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check(int rc, const char* what) {
+  TORCH_CHECK(rc == 0, what, " failed with code ", rc, " (", rc < 1000 ? cudaGetErrorString((cudaError_t)rc) : "driver", ")");
+}
+
+#define CHECK_BF16(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kBFloat16 && (x).is_contiguous(), #x " must be a contiguous CUDA bf16 tensor")
+#define CHECK_F32(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kFloat && (x).is_contiguous(), #x " must be a contiguous CUDA fp32 tensor")
+
+Tensor status_word(const Tensor& like) {
+  static thread_local std::vector<Tensor> words(16);
+  int dev = like.get_device();
+  if (!words[dev].defined()) words[dev] = torch::zeros({1}, like.options().dtype(at::kInt));
+  return words[dev];
+}
+
+std::tuple<Tensor, Tensor, Tensor> add_rmsnorm_fwd(const Tensor& branch, const c10::optional<Tensor>& stream_in,
+                                                   const Tensor& weight, double eps) {
+  CHECK_BF16(branch);
+  c10::cuda::CUDAGuard guard(branch.device());
+  const int64_t rows = branch.size(0);
+  const int dim = (int)branch.size(1);
+  TORCH_CHECK(dim % 8 == 0, "feature dim must be a multiple of 8");
+  Tensor w = weight.to(at::kFloat).contiguous();
+  Tensor normed = torch::empty_like(branch);
+  Tensor new_stream = torch::empty({rows, dim}, branch.options().dtype(at::kFloat));
+  Tensor rstd = torch::empty({rows}, branch.options().dtype(at::kFloat));
+  const float* sp = nullptr;
+  if (stream_in.has_value() && stream_in->defined()) {
+    CHECK_F32(*stream_in);
+    sp = stream_in->data_ptr<float>();
+  }
+  check(lbi_add_rmsnorm_fwd(branch.data_ptr(), sp, w.data_ptr<float>(), normed.data_ptr(), new_stream.data_ptr<float>(),
+                            rstd.data_ptr<float>(), rows, dim, (float)eps, cur_stream()),
+        "add_rmsnorm_fwd");
+  return {normed, new_stream, rstd};
+}
+
+Tensor rmsnorm_bwd(const Tensor& d_normed, const Tensor& x_stream, const Tensor& rstd, const Tensor& weight,
+                   const c10::optional<Tensor>& d_stream) {
+  CHECK_BF16(d_normed);
+  CHECK_F32(x_stream);
+  CHECK_F32(rstd);
+  c10::cuda::CUDAGuard guard(d_normed.device());
+  const int64_t rows = d_normed.size(0), act_rows = x_stream.size(0);
+  const int dim = (int)d_normed.size(1);
+  TORCH_CHECK(rows % act_rows == 0, "cotangent rows must be a multiple of activation rows");
+  Tensor w = weight.to(at::kFloat).contiguous();
+  Tensor out;
+  const float* din = nullptr;
+  if (d_stream.has_value() && d_stream->defined()) {
+    CHECK_F32(*d_stream);
+    out = *d_stream;  // accumulate in place
+    din = out.data_ptr<float>();
+  } else {
+    out = torch::empty({rows, dim}, d_normed.options().dtype(at::kFloat));
+  }
+  check(lbi_rmsnorm_bwd(d_normed.data_ptr(), x_stream.data_ptr<float>(), rstd.data_ptr<float>(), w.data_ptr<float>(), din,
+                        out.data_ptr<float>(), rows, act_rows, dim, cur_stream()),
+        "rmsnorm_bwd");
+  return out;
+}
+
+Tensor rmsnorm_wgrad(const Tensor& d_normed, const Tensor& x_stream, const Tensor& rstd) {
+  CHECK_BF16(d_normed);
+  CHECK_F32(x_stream);
+  c10::cuda::CUDAGuard guard(d_normed.device());
+  const int64_t rows = d_normed.size(0);
+  const int dim = (int)d_normed.size(1);
+  TORCH_CHECK(x_stream.size(0) == rows, "rmsnorm_wgrad takes a single cotangent");
+  const int nblocks = (int)std::min<int64_t>(296, std::max<int64_t>(1, rows / 16));
+  Tensor partials = torch::empty({nblocks, dim}, x_stream.options());
+  Tensor dw = torch::empty({dim}, x_stream.options());
+  check(lbi_rmsnorm_wgrad(d_normed.data_ptr(), x_stream.data_ptr<float>(), rstd.data_ptr<float>(),
+                          partials.data_ptr<float>(), dw.data_ptr<float>(), rows, dim, nblocks, cur_stream()),
+        "rmsnorm_wgrad");
+  return dw;
+}
+
+Tensor rope_qkv_(Tensor qkv, const Tensor& cos_tab, const Tensor& sin_tab, int64_t n_heads, int64_t n_kv_heads,
+                 int64_t head_dim, int64_t seq_len, bool interleaved, bool inverse) {
+  CHECK_BF16(qkv);
+  CHECK_F32(cos_tab);
+  CHECK_F32(sin_tab);
+  c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(head_dim % 16 == 0, "head_dim must be a multiple of 16");
+  TORCH_CHECK(cos_tab.size(0) >= seq_len && cos_tab.size(1) == head_dim / 2, "rope table shape mismatch");
+  check(lbi_rope_qkv(qkv.data_ptr(), cos_tab.data_ptr<float>(), sin_tab.data_ptr<float>(), qkv.size(0),
+                     (int)(n_heads + n_kv_heads), (int)qkv.size(1), (int)head_dim, (int)seq_len, interleaved ? 1 : 0,
+                     inverse ? 1 : 0, cur_stream()),
+        "rope_qkv");
+  return qkv;
+}
+
+Tensor swiglu_fwd(const Tensor& u) {
+  CHECK_BF16(u);
+  c10::cuda::CUDAGuard guard(u.device());
+  const int hidden = (int)(u.size(1) / 2);
+  Tensor a = torch::empty({u.size(0), hidden}, u.options());
+  check(lbi_swiglu_fwd(u.data_ptr(), a.data_ptr(), u.size(0), hidden, cur_stream()), "swiglu_fwd");
+  return a;
+}
+
+Tensor swiglu_bwd(const Tensor& da, const Tensor& u) {
+  CHECK_BF16(da);
+  CHECK_BF16(u);
+  c10::cuda::CUDAGuard guard(u.device());
+  const int hidden = (int)da.size(1);
+  TORCH_CHECK(u.size(1) == 2 * hidden && da.size(0) % u.size(0) == 0, "swiglu_bwd shape mismatch");
+  Tensor du = torch::empty({da.size(0), 2 * hidden}, da.options());
+  check(lbi_swiglu_bwd(da.data_ptr(), u.data_ptr(), du.data_ptr(), da.size(0), u.size(0), hidden, cur_stream()),
+        "swiglu_bwd");
+  return du;
+}
+
+Tensor add_condition(const Tensor& canvas, const Tensor& cond, int64_t seq_len) {
+  CHECK_BF16(canvas);
+  CHECK_F32(cond);
+  c10::cuda::CUDAGuard guard(canvas.device());
+  Tensor out = torch::empty_like(canvas);
+  check(lbi_add_condition(canvas.data_ptr(), cond.data_ptr<float>(), out.data_ptr(), canvas.size(0), (int)canvas.size(1),
+                          (int)seq_len, cur_stream()),
+        "add_condition");
+  return out;
+}
+
+Tensor pool_tokens(const Tensor& rows, int64_t groups, int64_t seq_len, double scale) {
+  TORCH_CHECK(rows.is_cuda() && rows.is_contiguous(), "rows must be a contiguous CUDA tensor");
+  c10::cuda::CUDAGuard guard(rows.device());
+  const int dim = (int)rows.size(-1);
+  TORCH_CHECK(rows.numel() == groups * seq_len * dim, "pool_tokens shape mismatch");
+  Tensor out = torch::zeros({groups, dim}, rows.options().dtype(at::kFloat));
+  check(lbi_pool_tokens(rows.data_ptr(), rows.scalar_type() == at::kBFloat16 ? 1 : 0, out.data_ptr<float>(), groups,
+                        (int)seq_len, dim, (float)scale, cur_stream()),
+        "pool_tokens");
+  return out;
+}
+
+Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "ids must be contiguous int64");
+  TORCH_CHECK(table.is_cuda() && table.is_contiguous(), "table must be contiguous");
+  c10::cuda::CUDAGuard guard(table.device());
+  Tensor out = torch::empty({ids.numel(), table.size(1)}, table.options().dtype(at::kBFloat16));
+  check(lbi_embedding_fwd(ids.data_ptr<int64_t>(), table.data_ptr(), table.scalar_type() == at::kBFloat16 ? 1 : 0,
+                          out.data_ptr(), ids.numel(), (int)table.size(1), cur_stream()),
+        "embedding_fwd");
+  return out;
+}
+
+void embedding_scatter_add_(Tensor d_table, const Tensor& ids, const Tensor& d_rows) {
+  CHECK_F32(d_table);
+  c10::cuda::CUDAGuard guard(d_table.device());
+  check(lbi_embedding_scatter_add(d_table.data_ptr<float>(), ids.data_ptr<int64_t>(), d_rows.data_ptr(),
+                                  d_rows.scalar_type() == at::kBFloat16 ? 1 : 0, ids.numel(), (int)d_table.size(1),
+                                  cur_stream()),
+        "embedding_scatter_add");
+}
+
+Tensor transpose_bf16(const Tensor& x) {
+  CHECK_BF16(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(1), x.size(0)}, x.options());
+  check(lbi_transpose_bf16(x.data_ptr(), out.data_ptr(), x.size(0), x.size(1), cur_stream()), "transpose_bf16");
+  return out;
+}
+
+Tensor causal_conv_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t batch, int64_t seq_len) {
+  CHECK_BF16(x);
+  CHECK_F32(w);
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = torch::empty_like(x);
+  const float* bp = (bias.has_value() && bias->defined()) ? bias->data_ptr<float>() : nullptr;
+  check(lbi_causal_conv_fwd(x.data_ptr(), w.data_ptr<float>(), bp, y.data_ptr(), x.size(0) / seq_len, (int)seq_len,
+                            (int)x.size(1), (int)w.size(1), cur_stream()),
+        "causal_conv_fwd");
+  return y;
+}
+
+Tensor causal_conv_dgrad(const Tensor& dy, const Tensor& w, int64_t batch, int64_t seq_len) {
+  CHECK_BF16(dy);
+  CHECK_F32(w);
+  c10::cuda::CUDAGuard guard(dy.device());
+  Tensor dx = torch::empty_like(dy);
+  check(lbi_causal_conv_dgrad(dy.data_ptr(), w.data_ptr<float>(), dx.data_ptr(), dy.size(0) / seq_len, (int)seq_len,
+                              (int)dy.size(1), (int)w.size(1), cur_stream()),
+        "causal_conv_dgrad");
+  return dx;
+}
+
+void sumsq_(const Tensor& x, Tensor out) {
+  CHECK_F32(x);
+  CHECK_F32(out);
+  c10::cuda::CUDAGuard guard(x.device());
+  check(lbi_sumsq(x.data_ptr<float>(), x.numel(), out.data_ptr<float>(), cur_stream()), "sumsq");
+}
+
+void adamw_step_(Tensor param, const Tensor& grad, Tensor m, Tensor v, const c10::optional<Tensor>& shadow, double lr,
+                 double beta1, double beta2, double eps, double weight_decay, int64_t step, double grad_mul,
+                 const c10::optional<Tensor>& sumsq, double clip_norm) {
+  CHECK_F32(param);
+  CHECK_F32(grad);
+  CHECK_F32(m);
+  CHECK_F32(v);
+  c10::cuda::CUDAGuard guard(param.device());
+  void* sh = nullptr;
+  if (shadow.has_value() && shadow->defined()) {
+    CHECK_BF16(*shadow);
+    sh = shadow->data_ptr();
+  }
+  const float* sq = (sumsq.has_value() && sumsq->defined()) ? sumsq->data_ptr<float>() : nullptr;
+  check(lbi_adamw_step(param.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), sh,
+                       param.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)weight_decay, (int)step,
+                       (float)grad_mul, sq, (float)clip_norm, cur_stream()),
+        "adamw_step");
+}
+
+void ce_fwd_bwd_(Tensor logits, const Tensor& targets, Tensor loss_sum, double scale) {
+  CHECK_BF16(logits);
+  CHECK_F32(loss_sum);
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous(), "targets must be contiguous int64");
+  TORCH_CHECK(logits.size(1) % 8 == 0, "vocab must be a multiple of 8");
+  c10::cuda::CUDAGuard guard(logits.device());
+  check(lbi_ce_fwd_bwd(logits.data_ptr(), targets.data_ptr<int64_t>(), loss_sum.data_ptr<float>(), logits.size(0),
+                       (int)logits.size(1), (float)scale, cur_stream()),
+        "ce_fwd_bwd");
+}
+
+Tensor suffix_scan(const Tensor& mats) {
+  TORCH_CHECK(mats.is_cuda() && mats.dim() == 4 && mats.size(2) == mats.size(3), "mats must be [B, K, R, R] on CUDA");
+  c10::cuda::CUDAGuard guard(mats.device());
+  Tensor m = mats.to(at::kFloat).contiguous();
+  const int b = (int)m.size(0), k = (int)m.size(1), r = (int)m.size(2);
+  Tensor out = torch::empty({b, k + 1, r, r}, m.options());
+  check(lbi_suffix_scan(m.data_ptr<float>(), out.data_ptr<float>(), b, k, r, cur_stream()), "suffix_scan");
+  return out;
+}
+
+Tensor affine_suffix_scan(const Tensor& mats, const Tensor& offsets, const c10::optional<Tensor>& seed) {
+  CHECK_F32(mats);
+  CHECK_F32(offsets);
+  c10::cuda::CUDAGuard guard(mats.device());
+  const int b = (int)mats.size(0), k = (int)mats.size(1), r = (int)mats.size(2);
+  Tensor g = torch::empty({b, k + 1, r}, mats.options());
+  const float* sp = (seed.has_value() && seed->defined()) ? seed->data_ptr<float>() : nullptr;
+  check(lbi_affine_suffix_scan(mats.data_ptr<float>(), offsets.data_ptr<float>(), sp, g.data_ptr<float>(), b, k, r,
+                               cur_stream()),
+        "affine_suffix_scan");
+  return g;
+}
+
+// C = A @ B^T (both K-major by default).  a_t / b_t: the operand is given as its transpose ([K, rows] row-major).
+Tensor gemm(const Tensor& a, const Tensor& b, bool a_t, bool b_t, bool out_fp32, const c10::optional<Tensor>& accumulate_into,
+            int64_t splits) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16,
+              "gemm operands must be CUDA bf16");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "gemm operands must be 2-D row-major");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t M = a_t ? a.size(1) : a.size(0), K = a_t ? a.size(0) : a.size(1);
+  const int64_t N = b_t ? b.size(1) : b.size(0), Kb = b_t ? b.size(0) : b.size(1);
+  TORCH_CHECK(K == Kb, "gemm reduction extents differ: ", K, " vs ", Kb);
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0, "leading dimensions must be multiples of 8");
+  TORCH_CHECK(((uintptr_t)a.data_ptr()) % 16 == 0 && ((uintptr_t)b.data_ptr()) % 16 == 0, "operands must be 16-byte aligned");
+  TORCH_CHECK(!a_t || M % 64 == 0, "transposed A needs M % 64 == 0");
+  TORCH_CHECK(!b_t || N % 64 == 0, "transposed B needs N % 64 == 0");
+  Tensor c;
+  bool acc = false;
+  if (accumulate_into.has_value() && accumulate_into->defined()) {
+    c = *accumulate_into;
+    TORCH_CHECK(c.scalar_type() == at::kFloat && c.size(0) == M && c.size(1) == N && c.stride(1) == 1, "bad accumulator");
+    out_fp32 = true;
+    acc = true;
+  } else if (splits > 1) {
+    c = torch::zeros({M, N}, a.options().dtype(at::kFloat));
+    out_fp32 = true;
+  } else {
+    c = torch::empty({M, N}, a.options().dtype(out_fp32 ? at::kFloat : at::kBFloat16));
+  }
+  TORCH_CHECK((c.stride(0) * (out_fp32 ? 4 : 2)) % 16 == 0, "C leading dimension must keep rows 16-byte aligned");
+  Tensor st = status_word(a);
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  check(lbi_gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K, a.stride(0), b.stride(0),
+                      c.stride(0), a_t ? 1 : 0, b_t ? 1 : 0, out_fp32 ? 1 : 0, acc ? 1 : 0, (int)splits,
+                      st.data_ptr<int>(), sms, cur_stream()),
+        "gemm_bf16");
+  return c;
+}
+
+Tensor gemm_tn(const Tensor& a, const Tensor& b, bool out_fp32, const c10::optional<Tensor>& accumulate_into) {
+  return gemm(a, b, false, false, out_fp32, accumulate_into, 1);
+}
+
+int64_t kernel_status(const Tensor& like) { return status_word(like).item<int>(); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_wgrad", &rmsnorm_wgrad);
+  m.def("rope_qkv_", &rope_qkv_);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("add_condition", &add_condition);
+  m.def("pool_tokens", &pool_tokens);
+  m.def("embedding_fwd", &embedding_fwd);
+  m.def("embedding_scatter_add_", &embedding_scatter_add_);
+  m.def("transpose_bf16", &transpose_bf16);
+  m.def("causal_conv_fwd", &causal_conv_fwd);
+  m.def("causal_conv_dgrad", &causal_conv_dgrad);
+  m.def("sumsq_", &sumsq_);
+  m.def("adamw_step_", &adamw_step_);
+  m.def("ce_fwd_bwd_", &ce_fwd_bwd_);
+  m.def("suffix_scan", &suffix_scan);
+  m.def("affine_suffix_scan", &affine_suffix_scan);
+  m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("a_t") = false, py::arg("b_t") = false,
+        py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);
+  m.def("gemm_tn", &gemm_tn);
+  m.def("kernel_status", &kernel_status);
+}

@@ -111,16 +111,33 @@ def linear_fwd(x, w, bias=None):
     return ref.linear_fwd(x, w, bias)
 
 
+# MN-major operand support of the GEMM lets dgrad and wgrad read W, dY and X as stored (no transposed copies).
+GEMM_MN_MAJOR = {"enabled": True}
+
+
+def _mn_ok(t) -> bool:
+    return t.dim() == 2 and t.stride(1) == 1 and t.shape[1] % 64 == 0 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
 def linear_dgrad(dy, w, w_t=None):
-    """dx = dy @ w.  ``w_t`` is an optional contiguous copy of w^T ([in, out]) that makes the product K-major."""
+    """dx = dy @ w with w stored [out, in].  Uses the MN-major B path of the GEMM; ``w_t`` ([in, out]) is an
+    optional pre-transposed copy for the K-major path."""
+    if GEMM_MN_MAJOR["enabled"] and _gemm_ok(dy, dy) and _native(w) and w.dtype == torch.bfloat16 and _mn_ok(w):
+        _count()
+        return ext().gemm(dy, w, False, True, False, None, 1)
     if w_t is not None and _gemm_ok(dy, w_t):
         return gemm_tn(dy, w_t)
     return ref.linear_dgrad(dy, w)
 
 
 def linear_wgrad(dy, x, accumulate_into=None):
-    """dW[out, in] = dy^T @ x with fp32 accumulation."""
-    if _native(dy, x) and dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and hasattr(ext(), "gemm_tn"):
+    """dW[out, in] = dy^T @ x with fp32 accumulation (split-K over the token rows)."""
+    if _native(dy, x) and dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and hasattr(ext(), "gemm"):
+        if GEMM_MN_MAJOR["enabled"] and _mn_ok(dy) and _mn_ok(x):
+            tiles = max(1, (dy.shape[1] // 128) * max(1, x.shape[1] // 256))
+            splits = max(1, min(16, 148 // tiles, dy.shape[0] // 512))
+            _count()
+            return ext().gemm(dy, x, True, True, True, accumulate_into, splits)
         dy_t = transpose_2d(dy)
         x_t = transpose_2d(x)
         if _gemm_ok(dy_t, x_t):
@@ -204,12 +221,13 @@ def causal_conv_wgrad(dy, x, width, batch, seq_len):
 
 
 # ---------------------------------------------------------------- LM head + CE
-def lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight=True, weight_t=None):
-    if _native(normed, weight, targets) and normed.dtype == torch.bfloat16 and hasattr(ext(), "ce_fwd_bwd_"):
+def lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight=True, weight_t=None, dweight_into=None):
+    if (_native(normed, weight, targets) and normed.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+            and weight.shape[0] % 64 == 0 and normed.shape[1] % 64 == 0):
         from .cross_entropy import fused_lm_head_ce
 
-        return fused_lm_head_ce(normed, weight, targets, loss_scale, want_dweight, weight_t)
-    return ref.lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight)
+        return fused_lm_head_ce(normed, weight, targets, loss_scale, want_dweight, weight_t, dweight_into)
+    return ref.lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight, dweight_into)
 
 
 # ---------------------------------------------------------------- embedding

@@ -190,7 +190,7 @@ def causal_conv_wgrad(dy, x, width, batch, seq_len):
 
 
 # ---------------------------------------------------------------- LM head + cross-entropy
-def lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight=True):
+def lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight=True, dweight_into=None):
     """loss = loss_scale * sum_rows CE(normed @ W^T, target); returns (loss_sum fp32 scalar, d_normed, dW or None).
 
     Rows whose target is negative are ignored."""
@@ -205,6 +205,9 @@ def lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight=True
     dlogits = probs * (valid.unsqueeze(1) * loss_scale)
     d_normed = (dlogits @ weight.float()).to(normed.dtype)
     dW = dlogits.t() @ normed.float() if want_dweight else None
+    if dW is not None and dweight_into is not None:
+        dweight_into.add_(dW)
+        dW = dweight_into
     return loss, d_normed, dW
 
 

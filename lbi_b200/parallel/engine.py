@@ -1,0 +1,352 @@
+"""Region-parallel exact-backprop training engine (no autograd on the hot path).
+
+One step of ``FastLBIEngine.step(input_ids, targets)``:
+
+1. forward chain over this rank's regions: embedding gather, condition add, structured Transformer region
+   forward, token pooling, interface update; the boundary state is handed to the rank that owns the next region;
+2. for regions with loss terms: final norm, LM head fused with cross-entropy (forward and backward at once);
+3. one batched input pullback per region over the R interface basis directions plus (where the region has
+   loss) the loss cotangent as an extra direction: yields A_k^T and the offset b_k together;
+4. affine suffix scan g_k = b_k + A_k^T g_{k+1} over all regions (inputs exchanged across ranks);
+5. one full backward per region with cotangent (loss part + update-path part of g_{k+1}); weight gradients are
+   accumulated by the GEMMs straight into the flat fp32 gradient buffer;
+6. gradient reduce-scatter, clip + AdamW on this rank's shard (bf16 shadow refreshed by the same kernel),
+   all-gather of the updated weights.
+
+Regions are blocks of layers (depth axis, the reference's definition) or blocks of tokens (sequence axis).
+The reference performs steps 3-5 with autograd over a retained graph (backward/scan.py:18-97,
+backward/pullbacks.py:84-149, backward/local_vjp.py:137-185) and has no multi-device mode.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+from .. import ops
+from ..models.region_plan import RegionPlacement
+from .comm import LocalComm
+from .flat import FlatParams
+
+
+@dataclass
+class RegionRecord:
+    index: int
+    token_range: tuple[int, int]
+    state_in: torch.Tensor
+    pooled: torch.Tensor
+    diagnostics: dict
+    cache: Any
+    ids: torch.Tensor
+    out: torch.Tensor | None = None  # fp32 region output (only kept for regions with loss)
+    rstd: torch.Tensor | None = None
+    normed: torch.Tensor | None = None
+    d_out_loss: torch.Tensor | None = None
+    state_out: torch.Tensor | None = None
+
+
+@dataclass
+class StepResult:
+    loss: torch.Tensor
+    state_cotangents: torch.Tensor | None = None
+    jacobians: torch.Tensor | None = None
+    extras: dict = field(default_factory=dict)
+
+
+class FastLBIEngine:
+    def __init__(
+        self,
+        model,
+        *,
+        lr: float = 1e-3,
+        betas: tuple[float, float] = (0.9, 0.999),
+        eps: float = 1e-8,
+        weight_decay: float = 0.0,
+        grad_clip: float = 1.0,
+        basis_chunk: int = 16,
+        act_dtype: torch.dtype | None = None,
+        comm=None,
+    ) -> None:
+        backend = model.region_backend
+        if not hasattr(backend, "structured"):
+            raise NotImplementedError("FastLBIEngine needs a Transformer region backend; use ScanADEngine for other backbones")
+        self.model = model
+        self.comm = comm or LocalComm()
+        self.device = next(model.parameters()).device
+        on_cuda = self.device.type == "cuda"
+        self.act_dtype = act_dtype or (torch.bfloat16 if on_cuda else torch.float32)
+        self.lr, self.betas, self.eps, self.weight_decay, self.grad_clip = lr, betas, eps, weight_decay, grad_clip
+        self.basis_chunk = max(1, int(basis_chunk))
+        self.placement = RegionPlacement(model.num_regions, self.comm.world_size)
+        self.my_regions = list(self.placement.regions_of(self.comm.rank))
+        self.flat = FlatParams(model, world_size=self.comm.world_size,
+                               shadow_dtype=self.act_dtype if self.act_dtype != torch.float32 else None)
+        lo = self.comm.rank * self.flat.shard
+        self.flat.ensure_state(lo, lo + self.flat.shard)
+        self.structured = backend.structured
+        self.structured.act_dtype = self.act_dtype
+        self.structured.shadow_of = self._shadow_of
+        self.structured._weights.clear()
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.last: dict = {}
+
+    # ------------------------------------------------------------------ helpers
+    def _shadow_of(self, p):
+        try:
+            return self.flat.weight(self.flat.name_of(p))
+        except KeyError:
+            return None
+
+    def _w(self, p) -> torch.Tensor:
+        return self.flat.weight(self.flat.name_of(p))
+
+    def _g(self, p) -> torch.Tensor:
+        return self.flat.grad(self.flat.name_of(p))
+
+    def _acc_grads(self, params, grads) -> None:
+        for p, g in zip(params, grads):
+            if g is not None:
+                self._g(p).add_(g.float())
+
+    def target(self, name: str):
+        """Gradient sink protocol of the structured backward: backbone-relative name -> fp32 accumulator."""
+        return self.flat.grad("region_backend.backbone." + name)
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def _forward(self, ids: torch.Tensor, targets: torch.Tensor) -> tuple[list[RegionRecord], torch.Tensor]:
+        model, iface, comm = self.model, self.model.interface, self.comm
+        bsz, seqlen = ids.shape
+        sequence_axis = model.region_axis == "sequence"
+        token_ranges = model.plan.token_ranges(seqlen)
+        table = self._w(model.canvas.embedding.weight)
+        dim = model.hidden_dim
+        k_regions = model.num_regions
+        loss = torch.zeros((), dtype=torch.float32, device=self.device)
+        loss_scale = 1.0 / float(bsz * seqlen)
+        final_w = model.readout.norm.weight
+        final_eps = model.readout.norm.eps
+        head_w = table if model.tie_embeddings else self._w(model.readout.lm_head.weight)
+        head_grad = self._g(model.canvas.embedding.weight if model.tie_embeddings else model.readout.lm_head.weight)
+
+        full_canvas = None
+        if not sequence_axis:
+            full_canvas = ops.embedding_fwd(ids, table, self.act_dtype)
+
+        first = self.my_regions[0]
+        if first == 0:
+            if sequence_axis:
+                pooled0 = torch.zeros(bsz, dim, dtype=torch.float32, device=self.device)
+            else:
+                pooled0 = ops.mean_pool_tokens(full_canvas, bsz, seqlen)
+            state = iface.initial_encoder(pooled0).float()
+            self.last["pooled0"] = pooled0
+        else:
+            like = torch.empty(bsz, model.interface_width, dtype=torch.float32, device=self.device)
+            state = comm.handoff_recv(like, self.placement.owner(first - 1), slot=first)
+
+        records: list[RegionRecord] = []
+        for k in self.my_regions:
+            t0, t1 = token_ranges[k]
+            t_len = t1 - t0
+            region_ids = ids[:, t0:t1].contiguous() if sequence_axis else ids
+            canvas_rows = ops.embedding_fwd(region_ids, table, self.act_dtype) if sequence_axis else full_canvas
+            cond = iface.decode(state, k).float()
+            x_in = ops.add_condition(canvas_rows, cond, t_len)
+            _, cache = self.structured.forward(x_in.view(bsz, t_len, dim), model.region_ranges[k], materialize_output=False)
+            rec = RegionRecord(index=k, token_range=(t0, t1), state_in=state, pooled=None, diagnostics={}, cache=cache,
+                               ids=region_ids)
+            if model.plan.region_has_loss(k):
+                normed, out, rstd = ops.add_rmsnorm_fwd(cache.last_branch, cache.last_stream, final_w, final_eps, self.act_dtype)
+                pooled = ops.mean_pool_tokens(out, bsz, t_len)
+                region_targets = targets[:, t0:t1].reshape(-1) if sequence_axis else targets.reshape(-1)
+                loss_k, d_normed, _ = ops.lm_head_cross_entropy(normed, head_w, region_targets, loss_scale,
+                                                                want_dweight=True, dweight_into=head_grad)
+                loss = loss + loss_k
+                self._g(final_w).add_(ops.rmsnorm_wgrad(d_normed, out, rstd))
+                rec.d_out_loss = ops.rmsnorm_bwd(d_normed, out, rstd, final_w)
+                rec.out, rec.rstd = None, None  # not needed again
+            else:
+                pooled = ops.mean_pool_tokens(cache.last_branch, bsz, t_len)
+                if cache.last_stream is not None:
+                    pooled = pooled + ops.mean_pool_tokens(cache.last_stream, bsz, t_len)
+            step = iface.update_from_pooled(state, pooled, k)
+            rec.pooled, rec.diagnostics, rec.state_out = pooled, step.diagnostics, step.state.float()
+            records.append(rec)
+            state = rec.state_out
+            if k + 1 < k_regions and self.placement.owner(k + 1) != comm.rank:
+                comm.handoff_send(state, self.placement.owner(k + 1), slot=k + 1)
+        return records, loss
+
+    # ------------------------------------------------------------------ Jacobian + offset of one region
+    @torch.no_grad()
+    def _pullback_region(self, rec: RegionRecord, need_jacobian: bool):
+        """Returns (A^T [B, R, R] or None, b [B, R])."""
+        model, iface = self.model, self.model.interface
+        k = rec.index
+        bsz, r = rec.state_in.shape
+        t_len = rec.token_range[1] - rec.token_range[0]
+        n = bsz * t_len
+        dim = model.hidden_dim
+        dirs: list[torch.Tensor] = []  # each [B, D] fp32 (rank-one in time) for the basis directions
+        skip = None
+        if need_jacobian:
+            eye = torch.eye(r, device=self.device, dtype=torch.float32).unsqueeze(0).expand(bsz, r, r)
+            upd = iface.update_jacobian_t(k, rec.diagnostics, eye, t_len)
+            skip = upd["g_state_skip"]  # [B, R, R]
+            g_pooled = upd["g_pooled_features"] / float(t_len)  # [B, R, D]
+        n_basis = r if need_jacobian else 0
+        has_loss = rec.d_out_loss is not None
+        total = n_basis + (1 if has_loss else 0)
+        cond_cots = torch.empty(total, bsz, dim, dtype=torch.float32, device=self.device)
+        j = 0
+        while j < total:
+            c = min(self.basis_chunk, total - j)
+            rows = torch.empty(c, bsz, t_len, dim, dtype=self.act_dtype, device=self.device)
+            nb = max(0, min(c, n_basis - j))
+            if nb > 0:
+                rows[:nb] = g_pooled[:, j : j + nb].transpose(0, 1).unsqueeze(2).to(self.act_dtype)
+            if nb < c:  # the loss direction rides in the last chunk
+                rows[nb] = rec.d_out_loss.view(bsz, t_len, dim).to(self.act_dtype)
+            g_in = self.structured.input_pullback(rec.cache, rows.view(c * n, dim))
+            cond_cots[j : j + c] = ops.sum_tokens(g_in, c * bsz, t_len).view(c, bsz, dim)
+            j += c
+        g_state = iface.decode_jacobian_t(k, rec.state_in, cond_cots.transpose(0, 1))  # [B, total, R]
+        jac = None
+        if need_jacobian:
+            jac = (skip + g_state[:, :n_basis]).transpose(1, 2).contiguous()
+        offset = g_state[:, n_basis].contiguous() if has_loss else torch.zeros(bsz, r, dtype=torch.float32, device=self.device)
+        return jac, offset
+
+    # ------------------------------------------------------------------ scan over all regions
+    @torch.no_grad()
+    def _scan(self, jacobians: list, offsets: list[torch.Tensor]) -> torch.Tensor:
+        """Local lists (one entry per owned region; jacobian None for the global last region) -> g [B, K, R]."""
+        model, comm = self.model, self.comm
+        k_regions = model.num_regions
+        bsz, r = offsets[0].shape
+        mats = torch.stack(
+            [j if j is not None else torch.zeros(bsz, r, r, dtype=torch.float32, device=self.device) for j in jacobians], dim=1
+        )
+        offs = torch.stack(offsets, dim=1)
+        mats_all, offs_all = comm.gather_scan_inputs(mats, offs)  # [B, K, R, R], [B, K, R]
+        self.last["jacobians"] = mats_all
+        self.last["offsets"] = offs_all
+        if k_regions == 1:
+            return offs_all
+        g = ops.affine_suffix_scan(mats_all[:, : k_regions - 1].contiguous(), offs_all[:, : k_regions - 1].contiguous(),
+                                   seed=offs_all[:, k_regions - 1].contiguous())
+        return g[:, :k_regions]
+
+    # ------------------------------------------------------------------ local VJPs
+    def _backward_region(self, rec: RegionRecord, g_next: torch.Tensor | None) -> None:
+        model, iface = self.model, self.model.interface
+        k = rec.index
+        bsz = rec.state_in.shape[0]
+        t_len = rec.token_range[1] - rec.token_range[0]
+        dim = model.hidden_dim
+        cot = rec.d_out_loss
+        if g_next is not None:
+            enc_params = [*iface.encoders[k].parameters(), *iface.norms[k].parameters(), iface.update_scale]
+            with torch.enable_grad():
+                pooled_leaf = rec.pooled.detach().clone().requires_grad_(True)
+                step = iface.update_from_pooled(rec.state_in.detach(), pooled_leaf, k)
+                grads = torch.autograd.grad(step.state, [pooled_leaf, *enc_params], g_next.to(step.state.dtype), allow_unused=True)
+            self._acc_grads(enc_params, grads[1:])
+            spread = (grads[0].float() / float(t_len)).unsqueeze(1)  # [B, 1, D] broadcast over tokens
+            with torch.no_grad():
+                if cot is None:
+                    cot = spread.expand(bsz, t_len, dim).reshape(bsz * t_len, dim).contiguous()
+                else:
+                    cot.view(bsz, t_len, dim).add_(spread)
+        if cot is None:
+            return
+        with torch.no_grad():
+            d_in = self.structured.backward(rec.cache, cot, self)
+            d_cond = ops.sum_tokens(d_in, bsz, t_len)
+            ops.embedding_scatter_add(self._g(model.canvas.embedding.weight), rec.ids, d_in)
+        dec_params = list(iface.decoders[k].parameters())
+        with torch.enable_grad():
+            cond = iface.decode(rec.state_in.detach(), k)
+            grads = torch.autograd.grad(cond, dec_params, d_cond.to(cond.dtype), allow_unused=True)
+        self._acc_grads(dec_params, grads)
+
+    def _backward_initial(self, ids: torch.Tensor, g0: torch.Tensor) -> None:
+        model, iface = self.model, self.model.interface
+        params = list(iface.initial_encoder.parameters())
+        with torch.enable_grad():
+            pooled_leaf = self.last["pooled0"].detach().clone().requires_grad_(True)
+            s0 = iface.initial_encoder(pooled_leaf)
+            grads = torch.autograd.grad(s0, [pooled_leaf, *params], g0.to(s0.dtype), allow_unused=True)
+        self._acc_grads(params, grads[1:])
+        if model.region_axis == "depth" and grads[0] is not None:
+            bsz, seqlen = ids.shape
+            with torch.no_grad():
+                rows = (grads[0].float() / float(seqlen)).unsqueeze(1).expand(bsz, seqlen, -1).reshape(bsz * seqlen, -1).contiguous()
+                ops.embedding_scatter_add(self._g(model.canvas.embedding.weight), ids, rows)
+
+    # ------------------------------------------------------------------ optimizer
+    @torch.no_grad()
+    def _optimizer_step(self, lr: float) -> None:
+        flat, comm = self.flat, self.comm
+        shard = flat.shard
+        lo = comm.rank * shard
+        g_shard = comm.reduce_scatter_grads(flat.grads, shard) if comm.world_size > 1 else flat.grads
+        flat.step_count += 1
+        use_kernel = self.device.type == "cuda" and ops.native_available()
+        self.sumsq.zero_()
+        if self.grad_clip > 0:
+            if use_kernel:
+                ops.ext().sumsq_(g_shard, self.sumsq)
+                ops.dispatch.KERNEL_LAUNCHES["count"] += 1
+            else:
+                self.sumsq += g_shard.float().square().sum()
+            comm.all_reduce_sum(self.sumsq)
+        p_shard = flat.params[lo : lo + shard]
+        sh_shard = flat.shadow[lo : lo + shard] if flat.shadow is not None else None
+        if use_kernel:
+            ops.ext().adamw_step_(p_shard, g_shard, flat.exp_avg, flat.exp_avg_sq, sh_shard, lr, self.betas[0], self.betas[1],
+                                  self.eps, self.weight_decay, flat.step_count, 1.0,
+                                  self.sumsq if self.grad_clip > 0 else None, float(self.grad_clip))
+            ops.dispatch.KERNEL_LAUNCHES["count"] += 1
+        else:
+            scale = 1.0
+            if self.grad_clip > 0:
+                scale = torch.clamp(self.grad_clip / (self.sumsq.sqrt() + 1e-6), max=1.0)
+            ops.reference.adamw_step(p_shard, g_shard, flat.exp_avg, flat.exp_avg_sq, lr, self.betas[0], self.betas[1], self.eps,
+                                     self.weight_decay, flat.step_count, scale, sh_shard)
+        if comm.world_size > 1:
+            comm.all_gather_flat(flat.shadow if flat.shadow is not None else flat.params, shard)
+
+    # ------------------------------------------------------------------ public API
+    def backward(self, input_ids: torch.Tensor, targets: torch.Tensor) -> StepResult:
+        """Forward + exact region-local backward; gradients end up in ``self.flat.grads`` (not yet reduced)."""
+        model = self.model
+        self.flat.zero_grad()
+        records, loss = self._forward(input_ids, targets)
+        k_regions = model.num_regions
+        jacobians, offsets = [], []
+        for rec in records:
+            jac, off = self._pullback_region(rec, need_jacobian=rec.index < k_regions - 1)
+            jacobians.append(jac)
+            offsets.append(off)
+        g = self._scan(jacobians, offsets)  # [B, K, R]
+        for rec in records:
+            g_next = g[:, rec.index + 1] if rec.index + 1 < k_regions else None
+            self._backward_region(rec, g_next)
+            rec.cache = None
+        if self.my_regions[0] == 0:
+            self._backward_initial(input_ids, g[:, 0])
+        return StepResult(loss=loss, state_cotangents=g, jacobians=self.last.get("jacobians"))
+
+    def step(self, input_ids: torch.Tensor, targets: torch.Tensor, lr: float | None = None) -> torch.Tensor:
+        result = self.backward(input_ids, targets)
+        self._optimizer_step(self.lr if lr is None else lr)
+        loss = result.loss.detach().clone()
+        if self.comm.world_size > 1:
+            self.comm.all_reduce_sum(loss)
+        return loss
+
+    def named_grads(self) -> dict[str, torch.Tensor]:
+        return self.flat.grad_map()
