@@ -12,6 +12,7 @@ import os
 
 import torch
 
+from . import dispatch, reference
 from . import reference as ref
 from .native import ext, native_available, require_native
 
@@ -28,6 +29,7 @@ from .dispatch import (  # noqa: E402
     causal_conv_wgrad,
     embedding_fwd,
     embedding_scatter_add,
+    gemm_tn,
     linear_dgrad,
     linear_fwd,
     linear_wgrad,
@@ -41,6 +43,7 @@ from .dispatch import (  # noqa: E402
     sum_tokens,
     swiglu_bwd,
     swiglu_fwd,
+    transpose_2d,
 )
 
 __all__ = [name for name in dir() if not name.startswith("_")]

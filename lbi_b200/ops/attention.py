@@ -21,39 +21,29 @@ import torch
 from . import reference as ref
 from .native import ext, native_available
 
-_LIB_STATE_KEYS = ("cum_q", "cum_k", "max_q", "max_k", "seed", "offset")
 
 
 def _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim):
+    """Token-major views [B, T, h, Dh] of the q, k and v parts of a packed buffer (no copies)."""
     q_dim, kv_dim = n_heads * head_dim, n_kv_heads * head_dim
     x = qkv.view(batch, seq_len, q_dim + 2 * kv_dim)
-    q = x[..., :q_dim].unflatten(-1, (n_heads, head_dim)).transpose(1, 2)
-    k = x[..., q_dim : q_dim + kv_dim].unflatten(-1, (n_kv_heads, head_dim)).transpose(1, 2)
-    v = x[..., q_dim + kv_dim :].unflatten(-1, (n_kv_heads, head_dim)).transpose(1, 2)
+    q = x[..., :q_dim].unflatten(-1, (n_heads, head_dim))
+    k = x[..., q_dim : q_dim + kv_dim].unflatten(-1, (n_kv_heads, head_dim))
+    v = x[..., q_dim + kv_dim :].unflatten(-1, (n_kv_heads, head_dim))
     return q, k, v
 
 
-def _expand(x, rep):
-    return x if rep == 1 else x.repeat_interleave(rep, dim=1)
+def _flash():
+    from flash_attn import flash_attn_interface as fa
+
+    return fa
 
 
 def flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale):
-    """Library flash-attention forward on the packed qkv buffer -> (out [n, H*Dh], lse [B, H, T])."""
+    """Library flash-attention forward on the packed qkv buffer -> (out [n, H*Dh], lse [B, H, T] fp32)."""
     q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
-    rep = n_heads // n_kv_heads
-    res = torch.ops.aten._scaled_dot_product_flash_attention(q, _expand(k, rep), _expand(v, rep), 0.0, True, False, scale=scale)
-    out, lse = res[0], res[1]
-    return out.transpose(1, 2).reshape(batch * seq_len, n_heads * head_dim), lse
-
-
-def _library_backward(do, q, k, v, out, lse, scale):
-    """One flash-attention backward; all tensors [B, H, T, Dh]."""
-    t = q.shape[2]
-    empty = torch.empty(0, dtype=torch.int64, device=q.device)
-    seed = torch.zeros((), dtype=torch.int64, device=q.device)
-    return torch.ops.aten._scaled_dot_product_flash_attention_backward(
-        do, q, k, v, out, lse, empty, empty, t, t, 0.0, True, seed, seed, scale=scale
-    )
+    out, lse, _, _ = _flash()._flash_attn_forward(q, k, v, 0.0, float(scale), True, -1, -1, 0.0, None, False)
+    return out.reshape(batch * seq_len, n_heads * head_dim), lse
 
 
 def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, kernel_mode=None):
@@ -63,23 +53,18 @@ def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, h
     qkv_dim = (n_heads + 2 * n_kv_heads) * head_dim
     mode = kernel_mode or default_kernel_mode(do_rows, head_dim, n_heads, n_kv_heads, seq_len)
     if mode == "tcgen05_pblock":
+        from .dispatch import KERNEL_LAUNCHES
+
+        KERNEL_LAUNCHES["count"] += 2
         return ext().attn_pullback_packed(do_rows.contiguous(), qkv, o, lse, batch, seq_len, n_heads, head_dim, float(scale))
     q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
-    rep = n_heads // n_kv_heads
-    ke, ve = _expand(k, rep), _expand(v, rep)
-    out4 = o.view(batch, seq_len, n_heads, head_dim).transpose(1, 2)
+    out4 = o.view(batch, seq_len, n_heads, head_dim)
     d_qkv = torch.empty(nbasis * n, qkv_dim, dtype=do_rows.dtype, device=do_rows.device)
-    q_dim, kv_dim = n_heads * head_dim, n_kv_heads * head_dim
+    fa = _flash()
     for p in range(nbasis):
-        do = do_rows[p * n : (p + 1) * n].view(batch, seq_len, n_heads, head_dim).transpose(1, 2)
-        dq, dk, dv = _library_backward(do, q, ke, ve, out4, lse, scale)
-        if rep > 1:
-            dk = dk.unflatten(1, (n_kv_heads, rep)).sum(dim=2)
-            dv = dv.unflatten(1, (n_kv_heads, rep)).sum(dim=2)
-        dst = d_qkv[p * n : (p + 1) * n].view(batch, seq_len, qkv_dim)
-        dst[..., :q_dim] = dq.transpose(1, 2).reshape(batch, seq_len, q_dim)
-        dst[..., q_dim : q_dim + kv_dim] = dk.transpose(1, 2).reshape(batch, seq_len, kv_dim)
-        dst[..., q_dim + kv_dim :] = dv.transpose(1, 2).reshape(batch, seq_len, kv_dim)
+        do = do_rows[p * n : (p + 1) * n].view(batch, seq_len, n_heads, head_dim)
+        dq, dk, dv = _views(d_qkv[p * n : (p + 1) * n], batch, seq_len, n_heads, n_kv_heads, head_dim)
+        fa._flash_attn_backward(do, q, k, v, out4, lse, dq, dk, dv, 0.0, float(scale), True, -1, -1, 0.0, None, False, None)
     return d_qkv
 
 
@@ -117,5 +102,5 @@ def attention_input_pullback_basis(q, k, v, dO_basis, *, scale=None, causal=True
     o_rows, lse = flash_forward_packed(qkv, bsz, seqlen, heads, heads, head_dim, scale)
     do_rows = dO_basis.permute(1, 0, 3, 2, 4).reshape(nbasis * bsz * seqlen, heads * head_dim).contiguous()
     d_qkv = pullback_packed(do_rows, qkv, o_rows.contiguous(), lse, bsz, seqlen, heads, heads, head_dim, scale, kernel_mode)
-    parts = d_qkv.view(nbasis, bsz, seqlen, 3, heads, head_dim).permute(3, 1, 0, 4, 2, 5)
+    parts = d_qkv.view(nbasis, bsz, seqlen, 3, heads, head_dim).permute(3, 1, 0, 4, 2, 5)  # [3, B, P, H, T, Dh]
     return parts[0], parts[1], parts[2]

@@ -7,6 +7,8 @@ launches of this package's own kernels (bench.py reports it).
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import reference as ref
@@ -75,9 +77,13 @@ def rmsnorm(x, weight, eps):
 
 
 # ---------------------------------------------------------------- linear (tcgen05 GEMM)
+GEMM_NATIVE = {"enabled": os.environ.get("LBI_B200_LIBRARY_GEMM", "0") != "1"}
+
+
 def _gemm_ok(a, b) -> bool:
     return (
-        _native(a, b)
+        GEMM_NATIVE["enabled"]
+        and _native(a, b)
         and a.dtype == torch.bfloat16
         and b.dtype == torch.bfloat16
         and a.dim() == 2
@@ -132,7 +138,7 @@ def linear_dgrad(dy, w, w_t=None):
 
 def linear_wgrad(dy, x, accumulate_into=None):
     """dW[out, in] = dy^T @ x with fp32 accumulation (split-K over the token rows)."""
-    if _native(dy, x) and dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and hasattr(ext(), "gemm"):
+    if GEMM_NATIVE["enabled"] and _native(dy, x) and dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16:
         if GEMM_MN_MAJOR["enabled"] and _mn_ok(dy) and _mn_ok(x):
             tiles = max(1, (dy.shape[1] // 128) * max(1, x.shape[1] // 256))
             splits = max(1, min(16, 148 // tiles, dy.shape[0] // 512))
@@ -222,7 +228,7 @@ def causal_conv_wgrad(dy, x, width, batch, seq_len):
 
 # ---------------------------------------------------------------- LM head + CE
 def lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight=True, weight_t=None, dweight_into=None):
-    if (_native(normed, weight, targets) and normed.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
+    if (GEMM_NATIVE["enabled"] and _native(normed, weight, targets) and normed.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16
             and weight.shape[0] % 64 == 0 and normed.shape[1] % 64 == 0):
         from .cross_entropy import fused_lm_head_ce
 

@@ -1,0 +1,156 @@
+"""Numerics of every sm_100a kernel against its fp32 PyTorch statement (all tests need a GPU)."""
+import math
+
+import pytest
+import torch
+
+from lbi_b200 import ops
+from lbi_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    bound = atol + rtol * b.abs()
+    assert bool((err <= bound).all()), f"{what}: max err {err.max().item():.3e}, max ref {b.abs().max().item():.3e}"
+
+
+def test_extension_loaded():
+    assert ops.native_available(), "lbi_b200._C must be built in-tree and loadable on a GPU box"
+
+
+@pytest.mark.parametrize("rows,dim,with_stream", [(300, 256, True), (64, 1024, False), (17, 4096, True)])
+def test_add_rmsnorm_fwd_bwd(rows, dim, with_stream):
+    torch.manual_seed(0)
+    branch = torch.randn(rows, dim, device=DEV).bfloat16()
+    stream = torch.randn(rows, dim, device=DEV) if with_stream else None
+    w = torch.rand(dim, device=DEV) + 0.5
+    n1, s1, r1 = ops.add_rmsnorm_fwd(branch, stream, w, 1e-5, torch.bfloat16)
+    n0, s0, r0 = ref.add_rmsnorm_fwd(branch, stream, w, 1e-5, torch.bfloat16)
+    _close(s1, s0, 1e-6, 1e-6, "stream")
+    _close(r1, r0, 1e-5, 1e-5, "rstd")
+    _close(n1, n0, 2e-2, 1e-2, "normed")
+    for reps in (1, 3):
+        g = torch.randn(reps * rows, dim, device=DEV).bfloat16()
+        d_in = torch.randn(reps * rows, dim, device=DEV)
+        got = ops.rmsnorm_bwd(g, s0, r0, w, d_in.clone())
+        want = ref.rmsnorm_bwd(g, s0, r0, w, d_in)
+        _close(got, want, 1e-4, 1e-4, "rmsnorm_bwd")
+    g = torch.randn(rows, dim, device=DEV).bfloat16()
+    _close(ops.rmsnorm_wgrad(g, s0, r0), ref.rmsnorm_wgrad(g, s0, r0), 1e-3, 1e-4, "rmsnorm_wgrad")
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope(interleaved):
+    from lbi_b200.backbones.transformer.rope import rope_tables
+
+    torch.manual_seed(1)
+    heads, kv, hd, t, b = 4, 2, 64, 96, 3
+    qkv = torch.randn(b * t, (heads + 2 * kv) * hd, device=DEV).bfloat16()
+    cos, sin = rope_tables(t, hd, 10000.0, torch.device(DEV))
+    want = ref.rope_qkv(qkv, cos, sin, heads, kv, hd, t, interleaved, False)
+    got = ops.rope_qkv(qkv.clone(), cos, sin, heads, kv, hd, t, interleaved, False)
+    _close(got, want, 2e-2, 1e-2, "rope")
+    back = ops.rope_qkv(got.clone(), cos, sin, heads, kv, hd, t, interleaved, True)
+    _close(back, qkv, 5e-2, 2e-2, "rope inverse")
+
+
+def test_swiglu():
+    torch.manual_seed(2)
+    u = torch.randn(200, 2 * 384, device=DEV).bfloat16()
+    _close(ops.swiglu_fwd(u), ref.swiglu_fwd(u), 2e-2, 1e-2, "swiglu_fwd")
+    da = torch.randn(3 * 200, 384, device=DEV).bfloat16()
+    _close(ops.swiglu_bwd(da, u), ref.swiglu_bwd(da, u), 3e-2, 2e-2, "swiglu_bwd")
+
+
+def test_interface_glue_and_embedding():
+    torch.manual_seed(3)
+    b, t, d, v = 3, 200, 256, 500
+    canvas = torch.randn(b * t, d, device=DEV).bfloat16()
+    cond = torch.randn(b, d, device=DEV)
+    _close(ops.add_condition(canvas, cond, t), ref.add_condition(canvas, cond, t), 2e-2, 1e-2, "add_condition")
+    rows = torch.randn(b * t, d, device=DEV)
+    _close(ops.mean_pool_tokens(rows, b, t), ref.mean_pool_tokens(rows, b, t), 1e-5, 1e-5, "mean_pool")
+    _close(ops.sum_tokens(rows.bfloat16(), b, t), ref.sum_tokens(rows.bfloat16(), b, t), 1e-3, 1e-4, "sum_tokens")
+    table = torch.randn(v, d, device=DEV)
+    ids = torch.randint(0, v, (b, t), device=DEV)
+    _close(ops.embedding_fwd(ids, table, torch.bfloat16), ref.embedding_fwd(ids, table, torch.bfloat16), 0, 0, "embedding")
+    g = torch.randn(b * t, d, device=DEV)
+    got = ops.embedding_scatter_add(torch.zeros(v, d, device=DEV), ids, g)
+    want = ref.embedding_scatter_add(torch.zeros(v, d, device=DEV), ids, g)
+    _close(got, want, 1e-4, 1e-5, "embedding_scatter_add")
+    x = torch.randn(130, 70, device=DEV).bfloat16()
+    assert torch.equal(ops.transpose_2d(x), x.t().contiguous())
+
+
+def test_causal_conv():
+    torch.manual_seed(4)
+    b, t, c, w = 2, 50, 64, 4
+    x = torch.randn(b * t, c, device=DEV).bfloat16()
+    weight = torch.randn(c, w, device=DEV)
+    bias = torch.randn(c, device=DEV)
+    _close(ops.causal_conv_fwd(x, weight, bias, b, t), ref.causal_conv_fwd(x, weight, bias, b, t), 3e-2, 2e-2, "conv fwd")
+    dy = torch.randn(3 * b * t, c, device=DEV).bfloat16()
+    _close(ops.causal_conv_dgrad(dy, weight, b, t), ref.causal_conv_dgrad(dy, weight, b, t), 3e-2, 2e-2, "conv dgrad")
+
+
+@pytest.mark.parametrize("b,k,r", [(1, 1, 1), (2, 3, 8), (3, 8, 64), (2, 5, 100), (1, 16, 128), (2, 8, 256)])
+def test_suffix_scans(b, k, r):
+    torch.manual_seed(5)
+    mats = torch.randn(b, k, r, r, device=DEV) / math.sqrt(r)
+    got = ops.suffix_scan_pullbacks(mats)
+    want = ref.suffix_scan_pullbacks(mats)
+    _close(got, want, 2e-5, 1e-5, "suffix_scan")
+    offs = torch.randn(b, k, r, device=DEV)
+    seed = torch.randn(b, r, device=DEV)
+    _close(ops.affine_suffix_scan(mats, offs, seed), ref.affine_suffix_scan(mats, offs, seed), 2e-5, 1e-5, "affine scan")
+    _close(ops.affine_suffix_scan(mats, offs, None), ref.affine_suffix_scan(mats, offs, None), 2e-5, 1e-5, "affine scan")
+    # two identical launches must agree bit for bit (no atomics in the scans)
+    assert torch.equal(got, ops.suffix_scan_pullbacks(mats))
+
+
+def test_suffix_scan_low_precision_inputs_promote():
+    torch.manual_seed(6)
+    mats = (torch.randn(2, 4, 16, 16, device=DEV) / 4).bfloat16()
+    out = ops.suffix_scan_pullbacks(mats)
+    assert out.dtype == torch.float32
+    _close(out, ref.suffix_scan_pullbacks(mats), 1e-4, 1e-4)
+
+
+def test_adamw_and_sumsq():
+    torch.manual_seed(7)
+    n = 100_003
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    shadow = torch.zeros(n, device=DEV, dtype=torch.bfloat16)
+    p0, m0, v0 = p.clone(), m.clone(), v.clone()
+    sumsq = torch.zeros(1, device=DEV)
+    ops.ext().sumsq_(g, sumsq)
+    _close(sumsq, g.square().sum().reshape(1), 1e-1, 1e-5, "sumsq")
+    for step in (1, 2):
+        ops.ext().adamw_step_(p, g, m, v, shadow, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, 1.0, sumsq, 1.0)
+        scale = torch.clamp(1.0 / (sumsq.sqrt() + 1e-6), max=1.0)
+        ref.adamw_step(p0, g, m0, v0, 1e-2, 0.9, 0.999, 1e-8, 0.1, step, scale)
+    _close(p, p0, 1e-5, 1e-5, "adamw params")
+    _close(shadow, p0.bfloat16(), 1e-2, 1e-2, "adamw shadow")
+
+
+def test_ce_fwd_bwd():
+    torch.manual_seed(8)
+    rows, vocab = 37, 1024
+    logits = (torch.randn(rows, vocab, device=DEV) * 3).bfloat16()
+    targets = torch.randint(0, vocab, (rows,), device=DEV)
+    targets[5] = -1
+    want_loss = torch.nn.functional.cross_entropy(logits.float(), targets, ignore_index=-1, reduction="sum") * 0.25
+    lf = logits.float().requires_grad_(True)
+    (torch.nn.functional.cross_entropy(lf, targets, ignore_index=-1, reduction="sum") * 0.25).backward()
+    loss = torch.zeros(1, device=DEV)
+    work = logits.clone()
+    ops.ext().ce_fwd_bwd_(work, targets, loss, 0.25)
+    _close(loss, want_loss.reshape(1), 1e-2, 1e-4, "ce loss")
+    _close(work, lf.grad, 2e-3, 2e-2, "ce grad")
