@@ -46,6 +46,7 @@ def parse_args():
     p.add_argument("--basis-chunk", type=int, default=16)
     p.add_argument("--comm", type=str, default="auto", choices=["auto", "collective", "symm"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--profile-ops", action="store_true", help="after the timed run, time one more step op by op (stderr)")
     return p.parse_args()
 
 
@@ -218,6 +219,16 @@ def run_ours(args) -> dict:
         e2e = {"value": tokens * args.steps / dt, "unit": "tokens/s",
                "h2d_bytes_per_step": int(host[0][0].numel() * 8 + host[0][1].numel() * 8), "d2h_bytes_per_step": 4,
                "last_loss": loss_val}
+
+    if args.profile_ops and rank == 0 or (args.profile_ops and world > 1):
+        from lbi_b200.ops import profile
+
+        profile.enable()
+        profile.reset()
+        engine.step(*dev_batches[-1])
+        if rank == 0:
+            print(profile.report(), file=sys.stderr)
+        profile.disable()
 
     status = ops.ext().kernel_status(flush) if ops.native_available() else 0
     return {
