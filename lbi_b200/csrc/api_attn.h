@@ -1,0 +1,24 @@
+// C entry point of the tcgen05 attention input pullback (attn_pullback.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Causal attention, head_dim 64, seq_len a multiple of 128, equal numbers of query and key/value heads.
+//   qkv    bf16 [B*T, 3*H*64]      packed q | k | v (rotary already applied)
+//   d_o    bf16 [P*B*T, H*64]      P output cotangents, direction-major rows
+//   o      bf16 [B*T, H*64]        forward output,  lse fp32 [B, H, T] natural-log sum-exp of the scaled scores
+//   d_qkv  bf16 [P*B*T, 3*H*64]    result: dq | dk | dv per direction
+//   delta  fp32 [P, B, H, T]       scratch supplied by the caller
+//   status device int, set non-zero if a bounded wait inside the kernels ran out
+// Launches three kernels on `stream` (row dots, dK/dV, dQ).  Returns 0 or a cudaError_t / 1000 + CUresult.
+int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const float* lse, void* d_qkv, float* delta,
+                      int batch, int heads, int seq_len, int head_dim, int nbasis, float scale, int* status,
+                      cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

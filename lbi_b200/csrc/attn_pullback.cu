@@ -1,0 +1,561 @@
+// Causal-attention input pullback over a block of output-cotangent directions, on tcgen05 / TMEM / TMA.
+//
+// For q, k, v [T, Dh] of one (batch, head), P = softmax(mask(q k^T s)) and directions dO_p:
+//     dV_p = P^T dO_p,   dP_p = dO_p v^T,   dS_p = P o (dP_p - delta_p),   dQ_p = s dS_p k,   dK_p = s dS_p^T q
+// with delta_p = rowsum(dO_p o O).  Two kernels, both built from the same template:
+//
+//   DKDV = true   one CTA owns a 128-row key tile j and PB = 3 directions; it walks the query tiles i >= j.
+//                 Per (i, j): S = Q_i K_j^T and P are computed ONCE and P is parked in shared memory; then for every
+//                 direction: dP, dS, dV_p += P^T dO_p, dK_p += dS^T Q_i.  dK_p / dV_p accumulate in TMEM over all i.
+//   DKDV = false  one CTA owns a 128-row query tile i and PB = 4 directions; it walks the key tiles j <= i:
+//                 S and P once per (i, j), then per direction dP, dS, dQ_p += dS K_j.  dQ_p accumulates in TMEM.
+//
+// The reference recomputes S and P for every direction: its "pblock4" entry is a host loop over a P = 1 WMMA kernel
+// (cuda/transformer/attention_pullback_mma.cu:479-515), fp16 only, T <= 1024.
+//
+// Layout: all tensors are token-major and packed, rows = (p * B + b) * T + t:
+//   qkv [n, 3 * H * Dh] bf16 (q | k | v sections), dO [P * n, H * Dh] bf16, d_qkv [P * n, 3 * H * Dh] bf16 (output),
+//   lse [B, H, T] fp32 (natural log), delta [P, B, H, T] fp32.
+// Every tile is 128 rows x 64 columns of bf16 = 128-byte rows, loaded by TMA with 128-byte swizzle; such a tile can be
+// fed to the tensor core both as a K-major operand (rows = M/N index) and as an MN-major operand (rows = K index), so
+// Q, K, V and dO are each loaded once per use and never transposed.  P and dS are written by the compute warps into
+// shared memory in the same swizzled layout ([128 q rows] x two 64-wide key panels).
+//
+// TMEM (512 columns): [0, 128) holds S and is then reused for dP; the accumulators follow, 64 columns each.
+// Warp roles (288 threads): warps 0-7 compute (TMEM lane quarter = warp % 4, key-column half = warp / 4),
+// warp 8 lane 0 issues all TMA loads and all MMAs.  Every mbarrier wait is bounded (tcgen05.cuh).
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "api_attn.h"
+#include "tcgen05.cuh"
+
+namespace lbi {
+namespace attn {
+
+using namespace tc;
+
+constexpr int TILE = 128;       // query rows and key rows per tile
+constexpr int DH = 64;          // head dimension handled by this build
+constexpr int TILE_BYTES = TILE * DH * 2;   // 16 KB
+constexpr int PANEL_BYTES = TILE * 128;     // one 64-column panel of P / dS: 128 rows x 128 B
+constexpr int THREADS = 288;
+constexpr int PB_DKDV = 3;
+constexpr int PB_DQ = 4;
+constexpr int NDO = 3;          // dO stages in DKDV mode
+
+struct Params {
+  int batch, heads, seq_len, nbasis;
+  int n_tiles;                  // seq_len / TILE
+  int64_t n_rows;               // batch * seq_len
+  int64_t out_ld;               // 3 * H * Dh
+  float scale, scale_log2;      // softmax scale and scale * log2(e)
+  const float* lse;             // [B, H, T]
+  const float* delta;           // [P, B, H, T]
+  __nv_bfloat16* d_qkv;         // [P * n, 3 H Dh]
+  int* status;
+};
+
+template <bool DKDV>
+struct Smem {
+  // fixed tiles: DKDV: K_j, V_j ; DQ: Q_i, dO_0..3
+  alignas(1024) uint8_t fixed[(DKDV ? 2 : 1 + PB_DQ)][TILE_BYTES];
+  // streamed tiles: DKDV: Q_i (2 stages) then dO (NDO stages) ; DQ: K_j (2 stages) then V_j (2 stages)
+  alignas(1024) uint8_t stream[(DKDV ? 2 + NDO : 4)][TILE_BYTES];
+  alignas(1024) uint8_t p_tile[2][PANEL_BYTES];
+  alignas(1024) uint8_t ds_tile[2][PANEL_BYTES];
+  uint64_t bar_fixed;            // fixed tiles landed
+  uint64_t bar_stream_full[(DKDV ? 2 + NDO : 4)];
+  uint64_t bar_stream_empty[(DKDV ? 2 + NDO : 4)];
+  uint64_t bar_s_ready;          // S in TMEM (commit)
+  uint64_t bar_p_ready;          // P in shared memory (256 arrivals)
+  uint64_t bar_p_free;           // MMAs that read P have finished (commit)
+  uint64_t bar_dp_ready;         // dP in TMEM (commit)
+  uint64_t bar_ds_ready;         // dS in shared memory, dP consumed (256 arrivals)
+  uint64_t bar_ds_free;          // MMA that read dS has finished (commit)
+  uint64_t bar_acc_done;         // all accumulating MMAs finished (commit)
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct Phase {
+  uint32_t bits = 0;
+  __device__ __forceinline__ uint32_t get(int idx) const { return (bits >> idx) & 1u; }
+  __device__ __forceinline__ void flip(int idx) { bits ^= (1u << idx); }
+};
+
+// 16-byte chunk address of row r, chunk c (8 bf16) inside a 128-byte-swizzled panel of 128-byte rows.
+__device__ __forceinline__ uint32_t swz(uint32_t panel_base, int r, int c) {
+  return panel_base + r * 128 + ((c ^ (r & 7)) << 4);
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool DKDV>
+__global__ void __launch_bounds__(THREADS, 1)
+pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const Params p) {
+  constexpr int PB = DKDV ? PB_DKDV : PB_DQ;
+  constexpr int NSTREAM = DKDV ? 2 + NDO : 4;
+  extern __shared__ uint8_t raw_smem[];
+  Smem<DKDV>& s = *reinterpret_cast<Smem<DKDV>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // tile ownership: heavy tiles first (DKDV: small j walks more query tiles; DQ: large i walks more key tiles)
+  const int own = DKDV ? (int)blockIdx.x : p.n_tiles - 1 - (int)blockIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads, h = bh % p.heads;
+  const int p0 = blockIdx.z * PB;
+  const int np = min(PB, p.nbasis - p0);
+  const int n_iter = DKDV ? p.n_tiles - own : own + 1;
+  const int hd = p.heads * DH;
+  const int col_q = h * DH, col_k = hd + h * DH, col_v = 2 * hd + h * DH;
+  const int row_b = b * p.seq_len;  // first token row of this batch element (within one direction)
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.bar_fixed, 1);
+    for (int i = 0; i < NSTREAM; ++i) {
+      mbar_init(&s.bar_stream_full[i], 1);
+      mbar_init(&s.bar_stream_empty[i], 1);
+    }
+    mbar_init(&s.bar_s_ready, 1);
+    mbar_init(&s.bar_p_ready, 256);
+    mbar_init(&s.bar_p_free, 1);
+    mbar_init(&s.bar_dp_ready, 1);
+    mbar_init(&s.bar_ds_ready, 256);
+    mbar_init(&s.bar_ds_free, 1);
+    mbar_init(&s.bar_acc_done, 1);
+    fence_barrier_init();
+    prefetch_tmap(&map_qkv);
+    prefetch_tmap(&map_do);
+  }
+  if (warp == 8) tmem_alloc(&s.tmem_base, 512);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abortp = &s.abort_flag;
+
+  if (warp == 8) {
+    // ======================================================================== control: TMA + MMA issue
+    if (lane == 0) {
+      const uint32_t idesc_nn = make_idesc_bf16(128, 128, 0, 0);          // S, dP
+      const uint32_t idesc_acc = DKDV ? make_idesc_bf16(128, 64, 1, 1)     // dV, dK: both operands MN-major
+                                      : make_idesc_bf16(128, 64, 0, 1);    // dQ: dS K-major, K_j MN-major
+      Phase full, empty;
+      uint32_t ph_p_ready = 0, ph_ds_ready = 0;
+      bool ok = true;
+
+      auto load_tile = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int col, int64_t row) {
+        mbar_arrive_expect_tx(bar, TILE_BYTES);
+        tma_load_2d(dst, m, bar, col, (int)row);
+      };
+      // K-major 128 x 64 operand: four K = 16 slices, 32 bytes apart inside the swizzled row
+      auto kdesc = [&](const void* tile, int k) { return make_smem_desc(smem_u32(tile) + k * 32, 16, 1024); };
+      // MN-major operand read from a [128 k-rows] x 128 B panel: K = 16 is sixteen rows = 2048 bytes
+      auto mndesc = [&](const void* tile, int k) { return make_smem_desc(smem_u32(tile) + k * 2048, PANEL_BYTES, 1024); };
+
+      if (DKDV) {
+        // ---------------- fixed: K_j, V_j ; streamed: Q_i (stages 0, 1), dO_{p,i} (stages 2 .. 2 + NDO)
+        mbar_arrive_expect_tx(&s.bar_fixed, 2 * TILE_BYTES);
+        tma_load_2d(s.fixed[0], &map_qkv, &s.bar_fixed, col_k, row_b + own * TILE);
+        tma_load_2d(s.fixed[1], &map_qkv, &s.bar_fixed, col_v, row_b + own * TILE);
+        const int total_do = n_iter * np;
+        int next_do = 0, next_q = 0;
+        auto refill_do = [&](int upto) {  // load dO tiles with index < upto
+          while (ok && next_do < total_do && next_do < upto) {
+            const int st = 2 + next_do % NDO;
+            if (next_do >= NDO) {
+              ok = mbar_wait(&s.bar_stream_empty[st], empty.get(st), abortp, p.status, 11);
+              empty.flip(st);
+              if (!ok) break;
+            }
+            const int it = next_do / np, pp = next_do % np;
+            const int64_t row = (int64_t)(p0 + pp) * p.n_rows + row_b + (own + it) * TILE;
+            load_tile(s.stream[st], &map_do, &s.bar_stream_full[st], h * DH, row);
+            ++next_do;
+          }
+        };
+        auto refill_q = [&](int upto) {
+          while (ok && next_q < n_iter && next_q < upto) {
+            const int st = next_q & 1;
+            if (next_q >= 2) {
+              ok = mbar_wait(&s.bar_stream_empty[st], empty.get(st), abortp, p.status, 12);
+              empty.flip(st);
+              if (!ok) break;
+            }
+            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_q, row_b + (own + next_q) * TILE);
+            ++next_q;
+          }
+        };
+        refill_q(1);
+        refill_do(NDO - 1);
+        ok = ok && mbar_wait(&s.bar_fixed, 0, abortp, p.status, 13);
+        int c = 0;  // running index over (iteration, direction)
+        for (int it = 0; it < n_iter && ok; ++it) {
+          const int qs = it & 1;
+          ok = mbar_wait(&s.bar_stream_full[qs], full.get(qs), abortp, p.status, 14);
+          full.flip(qs);
+          if (!ok) break;
+          fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_bf16(tmem, kdesc(s.stream[qs], k), kdesc(s.fixed[0], k), idesc_nn, k);
+          mma_commit(&s.bar_s_ready);
+          refill_q(it + 2);
+          ok = ok && mbar_wait(&s.bar_p_ready, ph_p_ready, abortp, p.status, 15);
+          ph_p_ready ^= 1;
+          if (!ok) break;
+          fence_after_sync();
+          for (int pp = 0; pp < np && ok; ++pp, ++c) {
+            const int st = 2 + c % NDO;
+            ok = mbar_wait(&s.bar_stream_full[st], full.get(st), abortp, p.status, 16);
+            full.flip(st);
+            if (!ok) break;
+            fence_after_sync();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mma_bf16(tmem, kdesc(s.stream[st], k), kdesc(s.fixed[1], k), idesc_nn, k);
+            mma_commit(&s.bar_dp_ready);
+            const uint32_t acc_dk = tmem + 128 + pp * 128, acc_dv = acc_dk + 64;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              mma_bf16(acc_dv, mndesc(s.p_tile, k), mndesc(s.stream[st], k), idesc_acc, (it | k) != 0);
+            if (pp == np - 1) mma_commit(&s.bar_p_free);
+            refill_do(c + NDO - 1);
+            ok = ok && mbar_wait(&s.bar_ds_ready, ph_ds_ready, abortp, p.status, 17);
+            ph_ds_ready ^= 1;
+            if (!ok) break;
+            fence_after_sync();
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              mma_bf16(acc_dk, mndesc(s.ds_tile, k), mndesc(s.stream[qs], k), idesc_acc, (it | k) != 0);
+            mma_commit(&s.bar_ds_free);
+            mma_commit(&s.bar_stream_empty[st]);
+          }
+          mma_commit(&s.bar_stream_empty[qs]);
+        }
+        if (ok) mma_commit(&s.bar_acc_done);
+      } else {
+        // ---------------- fixed: Q_i, dO_0 .. dO_{np-1} ; streamed: K_j (stages 0, 1), V_j (stages 2, 3)
+        mbar_arrive_expect_tx(&s.bar_fixed, (1 + np) * TILE_BYTES);
+        tma_load_2d(s.fixed[0], &map_qkv, &s.bar_fixed, col_q, row_b + own * TILE);
+        for (int pp = 0; pp < np; ++pp)
+          tma_load_2d(s.fixed[1 + pp], &map_do, &s.bar_fixed, h * DH,
+                      (int)((int64_t)(p0 + pp) * p.n_rows + row_b + own * TILE));
+        int next_kv = 0;
+        auto refill_kv = [&](int upto) {
+          while (ok && next_kv < n_iter && next_kv < upto) {
+            const int st = next_kv & 1;
+            if (next_kv >= 2) {
+              ok = mbar_wait(&s.bar_stream_empty[st], empty.get(st), abortp, p.status, 21);
+              empty.flip(st);
+              if (!ok) break;
+            }
+            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_k, row_b + next_kv * TILE);
+            load_tile(s.stream[2 + st], &map_qkv, &s.bar_stream_full[2 + st], col_v, row_b + next_kv * TILE);
+            ++next_kv;
+          }
+        };
+        refill_kv(1);
+        ok = ok && mbar_wait(&s.bar_fixed, 0, abortp, p.status, 23);
+        for (int it = 0; it < n_iter && ok; ++it) {
+          const int ks = it & 1;
+          ok = mbar_wait(&s.bar_stream_full[ks], full.get(ks), abortp, p.status, 24);
+          full.flip(ks);
+          if (!ok) break;
+          fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mma_bf16(tmem, kdesc(s.fixed[0], k), kdesc(s.stream[ks], k), idesc_nn, k);
+          mma_commit(&s.bar_s_ready);
+          refill_kv(it + 2);
+          ok = ok && mbar_wait(&s.bar_p_ready, ph_p_ready, abortp, p.status, 25);
+          ph_p_ready ^= 1;
+          ok = ok && mbar_wait(&s.bar_stream_full[2 + ks], full.get(2 + ks), abortp, p.status, 26);
+          full.flip(2 + ks);
+          if (!ok) break;
+          fence_after_sync();
+          for (int pp = 0; pp < np && ok; ++pp) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_bf16(tmem, kdesc(s.fixed[1 + pp], k), kdesc(s.stream[2 + ks], k), idesc_nn, k);
+            mma_commit(&s.bar_dp_ready);
+            ok = mbar_wait(&s.bar_ds_ready, ph_ds_ready, abortp, p.status, 27);
+            ph_ds_ready ^= 1;
+            if (!ok) break;
+            fence_after_sync();
+            const uint32_t acc_dq = tmem + 128 + pp * 64;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              mma_bf16(acc_dq, make_smem_desc(smem_u32(s.ds_tile[k >> 2]) + (k & 3) * 32, 16, 1024),
+                       mndesc(s.stream[ks], k), idesc_acc, (it | k) != 0);
+            mma_commit(&s.bar_ds_free);
+          }
+          mma_commit(&s.bar_stream_empty[ks]);  // one commit covers K_j and V_j: both stages free together
+        }
+        if (ok) mma_commit(&s.bar_acc_done);
+      }
+    }
+  } else {
+    // ======================================================================== compute warps 0..7
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
+    const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t p_panel = smem_u32(s.p_tile[half]);
+    const uint32_t ds_panel = smem_u32(s.ds_tile[half]);
+    const float* lse_bh = p.lse + ((int64_t)b * p.heads + h) * p.seq_len;
+    constexpr float LOG2E = 1.4426950408889634f;
+    uint32_t ph_s = 0, ph_dp = 0, ph_pfree = 0, ph_dsfree = 0;
+    int c = 0;
+    bool ok = true;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int qi = DKDV ? own + it : own;   // query tile of this step
+      const int kj = DKDV ? own : it;         // key tile of this step
+      const float lse_r = lse_bh[qi * TILE + r] * LOG2E;
+      ok = mbar_wait(&s.bar_s_ready, ph_s, abortp, p.status, 31);
+      ph_s ^= 1;
+      if (DKDV && it > 0 && ok) {
+        ok = mbar_wait(&s.bar_p_free, ph_pfree, abortp, p.status, 32);
+        ph_pfree ^= 1;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      fence_after_sync();
+      const bool diagonal = (qi == kj);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_lane + half * 64 + cc * 32, v);
+        tmem_ld_wait();
+        const int col0 = half * 64 + cc * 32;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = col0 + g * 8 + e * 2;
+            float a = fast_exp2(__uint_as_float(v[g * 8 + e * 2]) * p.scale_log2 - lse_r);
+            float bb = fast_exp2(__uint_as_float(v[g * 8 + e * 2 + 1]) * p.scale_log2 - lse_r);
+            if (diagonal) {
+              if (col > r) a = 0.f;
+              if (col + 1 > r) bb = 0.f;
+            }
+            w[e] = pack_bf16(a, bb);
+          }
+          st_shared_v4(swz(p_panel, r, cc * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
+        }
+      }
+      fence_proxy_async();
+      fence_before_sync();
+      mbar_arrive(&s.bar_p_ready);
+
+      for (int pp = 0; pp < np && ok; ++pp, ++c) {
+        const float delta_r = p.delta[(((int64_t)(p0 + pp) * p.batch + b) * p.heads + h) * p.seq_len + qi * TILE + r];
+        ok = mbar_wait(&s.bar_dp_ready, ph_dp, abortp, p.status, 33);
+        ph_dp ^= 1;
+        if (c > 0 && ok) {
+          ok = mbar_wait(&s.bar_ds_free, ph_dsfree, abortp, p.status, 34);
+          ph_dsfree ^= 1;
+        }
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        fence_after_sync();
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_lane + half * 64 + cc * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const uint4 pv = ld_shared_v4(swz(p_panel, r, cc * 4 + g));
+            const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 pr = unpack_bf16(pw[e]);
+              const float d0 = pr.x * (__uint_as_float(v[g * 8 + e * 2]) - delta_r);
+              const float d1 = pr.y * (__uint_as_float(v[g * 8 + e * 2 + 1]) - delta_r);
+              w[e] = pack_bf16(d0, d1);
+            }
+            st_shared_v4(swz(ds_panel, r, cc * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
+          }
+        }
+        fence_proxy_async();
+        fence_before_sync();
+        mbar_arrive(&s.bar_ds_ready);
+      }
+    }
+    // ------------------------------------------------------------------ epilogue: accumulators -> global
+    if (ok) ok = mbar_wait(&s.bar_acc_done, 0, abortp, p.status, 35);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      fence_after_sync();
+      const int64_t tok = (int64_t)row_b + own * TILE + r;
+      for (int pp = 0; pp < np; ++pp) {
+        __nv_bfloat16* out_row = p.d_qkv + ((int64_t)(p0 + pp) * p.n_rows + tok) * p.out_ld;
+        const int n_acc = DKDV ? 2 : 1;
+        for (int a = 0; a < n_acc; ++a) {
+          // DKDV: a = 0 -> dK (scaled), a = 1 -> dV ; DQ: dQ (scaled)
+          const uint32_t acc = DKDV ? tmem + 128 + pp * 128 + a * 64 : tmem + 128 + pp * 64;
+          const int col = (DKDV ? (a == 0 ? col_k : col_v) : col_q) + half * 32;
+          const float mul = (DKDV && a == 1) ? 1.f : p.scale;
+          uint32_t v[32];
+          tmem_ld_32x32(acc + ((uint32_t)(quarter * 32) << 16) + half * 32, v);
+          tmem_ld_wait();
+          uint4* dst = reinterpret_cast<uint4*>(out_row + col);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * mul, __uint_as_float(v[g * 8 + 1]) * mul);
+            o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * mul, __uint_as_float(v[g * 8 + 3]) * mul);
+            o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * mul, __uint_as_float(v[g * 8 + 5]) * mul);
+            o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * mul, __uint_as_float(v[g * 8 + 7]) * mul);
+            dst[g] = o;
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  __syncwarp();
+  if (s.abort_flag) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);  // let copies in flight land before smem is released
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 8) {
+    fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// delta[p, b, h, t] = sum_d dO[(p, b, t), h * Dh + d] * O[(b, t), h * Dh + d]; one warp per (row, head).
+__global__ void delta_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o,
+                             float* __restrict__ delta, int64_t rows_total, int64_t n_rows, int batch, int heads,
+                             int seq_len) {
+  const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= rows_total * heads) return;
+  const int h = (int)(gw % heads);
+  const int64_t row = gw / heads;          // (p * B + b) * T + t
+  const int64_t arow = row % n_rows;       // b * T + t
+  const int hd = heads * DH;
+  const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(d_o + row * hd + h * DH)[lane];
+  const __nv_bfloat162 c = reinterpret_cast<const __nv_bfloat162*>(o + arow * hd + h * DH)[lane];
+  const float2 af = __bfloat1622float2(a), cf = __bfloat1622float2(c);
+  float acc = af.x * cf.x + af.y * cf.y;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    const int64_t pb = row / seq_len;      // p * B + b
+    const int t = (int)(row % seq_len);
+    delta[(pb * heads + h) * seq_len + t] = acc;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// [rows, width] bf16 row-major, tiles of 128 rows x 64 columns, 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t width) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return 801;
+  cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+  cuuint32_t box[2] = {DH, TILE};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
+}
+
+template <bool DKDV>
+static int launch(const CUtensorMap& mq, const CUtensorMap& md, const Params& p, cudaStream_t st) {
+  constexpr int PB = DKDV ? PB_DKDV : PB_DQ;
+  const size_t smem = sizeof(Smem<DKDV>) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(pullback_kernel<DKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(p.n_tiles, p.batch * p.heads, (p.nbasis + PB - 1) / PB);
+  pullback_kernel<DKDV><<<grid, THREADS, smem, st>>>(mq, md, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace attn
+}  // namespace lbi
+
+extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const float* lse, void* d_qkv,
+                                 float* delta, int batch, int heads, int seq_len, int head_dim, int nbasis, float scale,
+                                 int* status, cudaStream_t st) {
+  using namespace lbi::attn;
+  if (head_dim != DH || seq_len % TILE != 0 || batch <= 0 || heads <= 0 || nbasis <= 0) return (int)cudaErrorInvalidValue;
+  const int64_t n_rows = (int64_t)batch * seq_len;
+  const int64_t rows_total = n_rows * nbasis;
+  if (rows_total >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+  {
+    const int64_t warps = rows_total * heads;
+    const int threads = 256;
+    const int64_t blocks = (warps * 32 + threads - 1) / threads;
+    delta_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta,
+                                                       rows_total, n_rows, batch, heads, seq_len);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+  }
+  CUtensorMap mq, md;
+  int rc = make_map(&mq, qkv, n_rows, 3ll * heads * DH);
+  if (rc) return rc;
+  rc = make_map(&md, d_o, rows_total, (int64_t)heads * DH);
+  if (rc) return rc;
+  Params p;
+  p.batch = batch; p.heads = heads; p.seq_len = seq_len; p.nbasis = nbasis;
+  p.n_tiles = seq_len / TILE;
+  p.n_rows = n_rows;
+  p.out_ld = 3ll * heads * DH;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = lse; p.delta = delta;
+  p.d_qkv = (__nv_bfloat16*)d_qkv;
+  p.status = status;
+  rc = launch<true>(mq, md, p, st);
+  if (rc) return rc;
+  return launch<false>(mq, md, p, st);
+}

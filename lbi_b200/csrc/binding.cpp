@@ -4,6 +4,7 @@
 #include <torch/extension.h>
 
 #include "api.h"
+#include "api_attn.h"
 #include "api_gemm.h"
 
 namespace {
@@ -301,6 +302,29 @@ Tensor gemm_tn(const Tensor& a, const Tensor& b, bool out_fp32, const c10::optio
   return gemm(a, b, false, false, out_fp32, accumulate_into, 1);
 }
 
+Tensor attn_pullback_packed(const Tensor& d_o, const Tensor& qkv, const Tensor& o, const Tensor& lse, int64_t batch,
+                            int64_t seq_len, int64_t heads, int64_t head_dim, double scale) {
+  CHECK_BF16(d_o);
+  CHECK_BF16(qkv);
+  CHECK_BF16(o);
+  CHECK_F32(lse);
+  c10::cuda::CUDAGuard guard(d_o.device());
+  const int64_t n = batch * seq_len;
+  TORCH_CHECK(qkv.size(0) == n && qkv.size(1) == 3 * heads * head_dim, "qkv shape mismatch");
+  TORCH_CHECK(d_o.size(0) % n == 0 && d_o.size(1) == heads * head_dim, "d_o shape mismatch");
+  TORCH_CHECK(o.size(0) == n && o.size(1) == heads * head_dim, "o shape mismatch");
+  TORCH_CHECK(lse.numel() == batch * heads * seq_len, "lse shape mismatch");
+  const int64_t nbasis = d_o.size(0) / n;
+  Tensor d_qkv = torch::empty({d_o.size(0), qkv.size(1)}, d_o.options());
+  Tensor delta = torch::empty({nbasis, batch, heads, seq_len}, lse.options());
+  Tensor st = status_word(d_o);
+  check(lbi_attn_pullback(qkv.data_ptr(), d_o.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), d_qkv.data_ptr(),
+                          delta.data_ptr<float>(), (int)batch, (int)heads, (int)seq_len, (int)head_dim, (int)nbasis,
+                          (float)scale, st.data_ptr<int>(), cur_stream()),
+        "attn_pullback");
+  return d_qkv;
+}
+
 int64_t kernel_status(const Tensor& like) { return status_word(like).item<int>(); }
 
 }  // namespace
@@ -327,5 +351,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("a_t") = false, py::arg("b_t") = false,
         py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);
   m.def("gemm_tn", &gemm_tn);
+  m.def("attn_pullback_packed", &attn_pullback_packed);
   m.def("kernel_status", &kernel_status);
 }
