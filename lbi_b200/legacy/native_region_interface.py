@@ -60,7 +60,7 @@ class NativeRegionInterfaceModel(nn.Module):
         self.interface = LegacyVectorMLPInterfaceView(
             interface_width=message_dim, initial_encoder=self.input_to_message, decoders=self.message_to_hidden,
             encoders=self.hidden_to_message, norms=self.message_norm)
-        self.region_backend = self.backbone
+        object.__setattr__(self, "region_backend", self.backbone)  # engine hook only; must not add state-dict keys
         if backbone_spec.name in ("transformer", "hybrid"):
             init_transformer_module(self.embedding, n_layers=backbone_spec.layers)
             apply_backbone_init(self.backbone, backbone_spec, blocks=self.blocks)

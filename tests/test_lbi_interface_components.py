@@ -1,0 +1,193 @@
+"""Component-level checks: closed-form interface pullbacks vs autograd, Jacobian providers vs one-step VJPs,
+cache contents, state ablations, backbone smoke, Mamba scans vs token recurrences, structured Transformer lowering."""
+import pytest
+import torch
+
+from lbi_b200.backbones import BackboneSpec, build_backbone_stack
+from lbi_b200.backbones.mamba2.ssd import ssd_chunk_scan, ssd_recurrent_reference
+from lbi_b200.backbones.mamba3 import Mamba3Block
+from lbi_b200.backbones.mamba3.siso import mamba3_siso_chunked, mamba3_siso_recurrent_reference
+from lbi_b200.backends import TorchAutogradTransformerLowering
+from lbi_b200.backward import build_interface_pullback_provider
+from lbi_b200.interfaces import VectorMLPInterface
+from lbi_b200.interfaces.vector_mlp import (
+    VectorMLPHead, broadcast_condition_jacobian_t, head_input_jacobian, head_input_jacobian_t, layer_norm_input_jacobian,
+    layer_norm_input_jacobian_t, mean_pool_jacobian_t,
+)
+from lbi_b200.models import LBILanguageModel
+
+
+def lbi_model(backbone="transformer", axis="depth", k=2, **kw):
+    torch.manual_seed(0)
+    spec = BackboneSpec(name=backbone, dim=32, layers=4, n_heads=4, d_conv=4, d_state=16, headdim=16, chunk_size=8, **kw)
+    iface = VectorMLPInterface(feature_dim=32, num_regions=k, interface_width=8, interface_map_hidden_dim=16)
+    return LBILanguageModel(vocab_size=50, layers_per_region=4 // k, backbone_spec=spec, interface=iface, region_axis=axis,
+                            num_sequence_regions=k)
+
+
+@pytest.mark.parametrize("hidden,act", [(0, "silu"), (12, "silu"), (12, "gelu")])
+def test_head_pullbacks_match_autograd(hidden, act):
+    torch.manual_seed(1)
+    head = VectorMLPHead(10, 6, hidden_dim=hidden, activation=act)
+    x = torch.randn(3, 10, requires_grad=True)
+    g = torch.randn(3, 4, 6)
+    want = torch.stack([torch.autograd.grad(head(x), x, g[:, p], retain_graph=True)[0] for p in range(4)], dim=1)
+    assert torch.allclose(head_input_jacobian_t(head, x.detach(), g), want, atol=1e-6, rtol=1e-5)
+    t = torch.randn(3, 4, 10)
+    fwd = torch.stack([torch.autograd.functional.jvp(head, x.detach(), t[:, p])[1] for p in range(4)], dim=1)
+    assert torch.allclose(head_input_jacobian(head, x.detach(), t), fwd, atol=1e-6, rtol=1e-5)
+
+
+def test_layer_norm_pullbacks_match_autograd():
+    torch.manual_seed(2)
+    norm = torch.nn.LayerNorm(8)
+    with torch.no_grad():
+        norm.weight.uniform_(0.5, 1.5)
+        norm.bias.normal_()
+    x = torch.randn(3, 8, requires_grad=True)
+    g = torch.randn(3, 5, 8)
+    want = torch.stack([torch.autograd.grad(norm(x), x, g[:, p], retain_graph=True)[0] for p in range(5)], dim=1)
+    assert torch.allclose(layer_norm_input_jacobian_t(norm, x.detach(), g), want, atol=1e-6, rtol=1e-5)
+    fwd = torch.stack([torch.autograd.functional.jvp(norm, x.detach(), g[:, p])[1] for p in range(5)], dim=1)
+    assert torch.allclose(layer_norm_input_jacobian(norm, x.detach(), g), fwd, atol=1e-6, rtol=1e-5)
+
+
+def test_pool_and_broadcast_pullbacks():
+    g = torch.randn(2, 3, 7)
+    spread = mean_pool_jacobian_t(g, 5)
+    assert spread.shape == (2, 3, 5, 7) and torch.allclose(spread.sum(dim=2), g, atol=1e-6)
+    assert torch.allclose(broadcast_condition_jacobian_t(spread), g, atol=1e-6)
+    with pytest.raises(ValueError):
+        mean_pool_jacobian_t(g, 0)
+
+
+@pytest.mark.parametrize("axis,k", [("depth", 2), ("sequence", 4)])
+def test_providers_agree_with_one_step_vjp(axis, k):
+    model = lbi_model(axis=axis, k=k)
+    ids = torch.randint(0, 50, (2, 24))
+    _, cache = model.forward_with_cache(ids, detach_states=True)
+    jac = {m: build_interface_pullback_provider(m, basis_chunk=c).materialize_state_jacobian_t(model=model, cache=cache)
+           for m, c in (("graph", 1), ("recompute", 1), ("recompute", 3), ("recompute", 8), ("structured", 3), ("forward", 1))
+           for m in [m]}
+    for region in range(k):
+        base = jac["graph"][region]
+        for mode, mats in jac.items():
+            assert torch.allclose(mats[region], base, atol=1e-5, rtol=1e-4), mode
+        g = torch.randn(2, 8)
+        (vjp,) = torch.autograd.grad(cache["states"][region + 1], cache["state_inputs"][region], g, retain_graph=True)
+        assert torch.allclose(torch.einsum("bij,bj->bi", base, g), vjp, atol=1e-5)
+
+
+def test_structured_transition_hooks_match_materialised_jacobian():
+    model = lbi_model()
+    ids = torch.randint(0, 50, (2, 16))
+    _, cache = model.forward_with_cache(ids, detach_states=True)
+    rc = cache["region_caches"][0]
+    eye = torch.eye(8).unsqueeze(0).expand(2, 8, 8)
+    upd = model.interface.apply_update_jacobian_t_to_region_output(region_cache=rc, state_out_cotangent_basis=eye)
+    g_in = model.region_backend.input_pullback_basis(cache=rc.backend_cache, output_cotangent_basis=upd["g_region_output"])
+    out = model.interface.apply_region_transition_jacobian_t(region_cache=rc, state_out_cotangent_basis=eye,
+                                                             region_input_cotangent_basis=g_in)
+    want = build_interface_pullback_provider("graph").materialize_state_jacobian_t(model=model, cache=cache, regions=[0])[0]
+    assert torch.allclose(out["g_state_input_total"].transpose(1, 2), want, atol=1e-5, rtol=1e-4)
+
+
+def test_cache_contents_and_ablations():
+    model = lbi_model()
+    ids = torch.randint(0, 50, (2, 16))
+    logits, cache = model.forward_with_cache(ids)
+    assert logits.shape == (2, 16, 50) and len(cache["states"]) == 3 and len(cache["region_caches"]) == 2
+    rc = cache["region_caches"][1]
+    assert rc.layer_range == (2, 4) and rc.region_input.shape == (2, 16, 32) and rc.state_out is cache["states"][2]
+    for key in ("pooled_features", "delta_state", "update_scale", "pre_norm_state"):
+        assert key in rc.interface_step.diagnostics
+    model.eval()
+    with torch.no_grad():
+        base = model(ids)
+        zero, _ = model.forward_with_cache(ids, message_ablation="zero_all")
+        g = torch.Generator().manual_seed(0)
+        noisy, _ = model.forward_with_cache(ids, message_ablation="noise", message_noise_std=1.0, ablation_generator=g)
+        same, _ = model.forward_with_cache(ids, message_ablation="mask", message_mask_keep_prob=1.0)
+    assert not torch.allclose(zero, base) and not torch.allclose(noisy, base) and torch.allclose(same, base)
+    with pytest.raises(ValueError):
+        model.forward_with_cache(ids, message_ablation="shuffle")
+
+
+@pytest.mark.parametrize("name", ["transformer", "mamba2", "mamba3", "hybrid"])
+def test_backbone_smoke_and_range_composition(name):
+    torch.manual_seed(3)
+    lt = ("mamba2", "transformer", "mamba3", "transformer") if name == "hybrid" else ()
+    spec = BackboneSpec(name=name, dim=32, layers=4, n_heads=4, n_kv_heads=2, d_state=16, headdim=16, chunk_size=8, layer_types=lt)
+    stack = build_backbone_stack(spec)
+    x = torch.randn(2, 20, 32)
+    y = stack(x)
+    assert y.shape == x.shape and torch.isfinite(y).all()
+    y.sum().backward()
+    assert all(p.grad is not None for p in stack.parameters())
+
+
+def test_causality_of_every_backbone():
+    for name in ("transformer", "mamba2", "mamba3"):
+        torch.manual_seed(4)
+        stack = build_backbone_stack(BackboneSpec(name=name, dim=32, layers=2, n_heads=4, d_state=16, headdim=16, chunk_size=8))
+        x = torch.randn(1, 24, 32)
+        x2 = x.clone()
+        x2[:, 15:] += 1.0
+        with torch.no_grad():
+            assert torch.allclose(stack(x)[:, :15], stack(x2)[:, :15], atol=1e-5), name
+
+
+def test_ssd_chunk_scan_matches_recurrence():
+    torch.manual_seed(5)
+    b, l, h, p, g, n = 2, 37, 4, 8, 2, 16
+    x, dt, A = torch.randn(b, l, h, p), torch.rand(b, l, h) * 0.5 + 0.01, -torch.rand(h) - 0.1
+    B, C, D = torch.randn(b, l, g, n), torch.randn(b, l, g, n), torch.randn(h)
+    want, final = ssd_recurrent_reference(x, dt, A, B, C, D)
+    for chunk in (4, 8, 64):
+        got, state = ssd_chunk_scan(x, dt, A, B, C, chunk, D, return_final_state=True)
+        assert torch.allclose(got.double(), want, atol=1e-4, rtol=1e-4)
+        assert torch.allclose(state.double(), final, atol=1e-4, rtol=1e-4)
+
+
+def test_mamba3_siso_matches_recurrence_and_block_pullback():
+    torch.manual_seed(6)
+    b, l, h, p, n = 2, 29, 4, 8, 16
+    Q, K, V, Z = torch.randn(b, l, 1, n), torch.randn(b, l, 1, n), torch.randn(b, l, h, p), torch.randn(b, l, h, p)
+    DT = torch.rand(b, h, l) * 0.5 + 0.01
+    ADT, Trap = -DT * (torch.rand(b, h, l) + 0.1), torch.randn(b, h, l)
+    qb, kb, ang, D = torch.randn(h, n), torch.randn(h, n), torch.randn(b, l, h, n // 4), torch.randn(h)
+    want = mamba3_siso_recurrent_reference(Q, K, V, ADT, DT, Trap, qb, kb, ang, D, Z)
+    for chunk in (8, 16):
+        got = mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, qb, kb, ang, D, Z, chunk_size=chunk)
+        assert torch.allclose(got.double(), want, atol=2e-4, rtol=1e-4)
+    block = Mamba3Block(32, d_state=16, headdim=16, chunk_size=8)
+    x = torch.randn(2, 12, 32, requires_grad=True)
+    basis = torch.randn(2, 3, 12, 32)
+    got = block.input_pullback_matrix(x.detach(), basis)
+    branch, stream = block(x)
+    want = torch.stack([torch.autograd.grad(branch + stream, x, basis[:, i], retain_graph=True)[0] for i in range(3)], dim=1)
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+
+
+@pytest.mark.parametrize("d_conv,kv", [(0, 4), (4, 2)])
+def test_structured_transformer_lowering_matches_autograd_lowering(d_conv, kv):
+    torch.manual_seed(7)
+    spec = BackboneSpec(name="transformer", dim=32, layers=2, n_heads=4, n_kv_heads=kv, d_conv=d_conv)
+    iface = VectorMLPInterface(feature_dim=32, num_regions=1, interface_width=4)
+    model = LBILanguageModel(vocab_size=20, layers_per_region=2, backbone_spec=spec, interface=iface)
+    backend = model.region_backend
+    x = torch.randn(2, 10, 32)
+    with torch.no_grad():
+        out, cache = backend.forward_region(region_input=x, region_index=0)
+    with torch.enable_grad():
+        ref_out = backend.backbone.forward_range(x, 0, 2)
+    assert torch.allclose(out, ref_out, atol=1e-5, rtol=1e-4)
+    oracle = TorchAutogradTransformerLowering()
+    basis = torch.randn(2, 3, 10, 32)
+    assert torch.allclose(backend.input_pullback_basis(cache=cache, output_cotangent_basis=basis),
+                          oracle.input_pullback_basis(backend=backend, cache=cache, output_cotangent_basis=basis), atol=1e-5, rtol=1e-4)
+    ct = torch.randn(2, 10, 32)
+    got, want = backend.parameter_vjp(cache=cache, output_cotangent=ct), oracle.parameter_vjp(backend=backend, cache=cache, output_cotangent=ct)
+    assert set(got) == set(want)
+    for name in want:
+        assert torch.allclose(got[name].reshape(want[name].shape), want[name], atol=1e-5, rtol=1e-4), name
