@@ -1,0 +1,77 @@
+"""Small, self-terminating workloads for ``ncu`` captures of single kernels.
+
+    python -m lbi_b200.benchmarks.profile_case --case attn      # attention pullback: B 2, H 16, T 2048, Dh 64, P 12
+    python -m lbi_b200.benchmarks.profile_case --case gemm      # tcgen05 GEMM 32768 x 5632 x 1024 (fc1 forward)
+    python -m lbi_b200.benchmarks.profile_case --case dgrad     # tcgen05 GEMM with MN-major B (fc1 dgrad)
+    python -m lbi_b200.benchmarks.profile_case --case elementwise   # rmsnorm_bwd / swiglu_bwd / rope over 65536 rows
+    python -m lbi_b200.benchmarks.profile_case --case scan      # suffix scan B 8, K 32, R 256
+
+Each case holds well under 2 GB on the device, touches more than the 126 MB L2, launches the kernel of interest a
+handful of times and exits.  Typical capture:
+    ncu --set full --clock-control none -k regex:pullback_kernel -c 2 -o prof python -m lbi_b200.benchmarks.profile_case --case attn
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+from lbi_b200 import ops
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan"])
+    ap.add_argument("--repeats", type=int, default=2)
+    args = ap.parse_args()
+    dev = "cuda"
+    torch.manual_seed(0)
+    if args.case == "attn":
+        from lbi_b200.ops.attention import attention_input_pullback_basis
+
+        b, h, t, dh, p = 2, 16, 2048, 64, 12
+        q, k, v = (torch.randn(b, h, t, dh, device=dev).bfloat16() for _ in range(3))
+        do = torch.randn(b, p, h, t, dh, device=dev).bfloat16()
+        for _ in range(args.repeats):
+            attention_input_pullback_basis(q, k, v, do, scale=1.0 / math.sqrt(dh), causal=True, kernel_mode="tcgen05_pblock")
+    elif args.case in ("gemm", "dgrad"):
+        m, n, k = 32768, 5632, 1024
+        if args.case == "gemm":
+            a = torch.randn(m, k, device=dev).bfloat16()
+            w = torch.randn(n, k, device=dev).bfloat16()
+            for _ in range(args.repeats):
+                ops.ext().gemm(a, w)
+        else:
+            dy = torch.randn(m, n, device=dev).bfloat16()
+            w = torch.randn(n, k, device=dev).bfloat16()
+            for _ in range(args.repeats):
+                ops.ext().gemm(dy, w, False, True, False, None, 1)
+    elif args.case == "elementwise":
+        from lbi_b200.backbones.transformer.rope import rope_tables
+
+        rows, reps, dim, hidden = 8192, 8, 1024, 2816
+        stream = torch.randn(rows, dim, device=dev)
+        rstd = torch.rand(rows, device=dev) + 0.5
+        w = torch.ones(dim, device=dev)
+        g = torch.randn(rows * reps, dim, device=dev).bfloat16()
+        acc = torch.zeros(rows * reps, dim, device=dev)
+        u = torch.randn(rows, 2 * hidden, device=dev).bfloat16()
+        da = torch.randn(rows * reps, hidden, device=dev).bfloat16()
+        qkv = torch.randn(rows * reps, 3 * dim, device=dev).bfloat16()
+        cos, sin = rope_tables(2048, 64, 10000.0, torch.device(dev))
+        for _ in range(args.repeats):
+            ops.rmsnorm_bwd(g, stream, rstd, w, acc)
+            ops.swiglu_bwd(da, u)
+            ops.rope_qkv(qkv, cos, sin, 16, 16, 64, 2048, False, True)
+    else:
+        mats = torch.randn(8, 32, 256, 256, device=dev) / 16
+        for _ in range(args.repeats):
+            ops.suffix_scan_pullbacks(mats)
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(torch.zeros(1, device=dev)) == 0
+    print("done")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,121 @@
+"""Attention input-pullback microbenchmark (shape sweep).
+
+    python -m lbi_b200.benchmarks.time_attention_pullback [--quick] [--check] [--out-dir out/benchmarks/attention_pullback]
+
+Sweep (the workload of the reference's benchmarks/time_attention_pullback.py, extended to bf16 and head_dim 128):
+causal attention, batch 8, 16 heads, seq {128, 512, 2048}, head_dim {64, 128}, basis {4, 16}, fp16 and bf16, inputs
+N(0, 1) from seed 0.  Every kernel mode that supports the cell is timed with CUDA events on the launching stream
+(3 warm-ups, median of ``--iters``, a 256 MB write between launches to flush L2); peak bytes and, with ``--check``,
+the max abs error against the dense fp32 formula are recorded.  Writes ``attention_pullback_<timestamp>.csv``,
+``latest.csv`` and ``latest_summary.json`` (speed-ups of the tcgen05 kernel over the library loop).
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import math
+import time
+from pathlib import Path
+
+import torch
+
+from lbi_b200.ops import reference as ref
+from lbi_b200.ops.attention import attention_input_pullback_basis, tcgen05_pullback_supported
+
+FIELDS = ["dtype", "batch", "heads", "seq_len", "head_dim", "basis", "kernel_mode", "median_ms", "best_ms", "tflops",
+          "peak_bytes", "max_abs_err", "status"]
+
+
+def pullback_flops(b, h, t, dh, p):
+    """Useful work: per direction dV, dP, dQ, dK (4 causal matmuls of 2*T*T/2*Dh) plus S once."""
+    one = 2.0 * t * t / 2.0 * dh
+    return b * h * (p * 4 * one + one)
+
+
+def time_mode(mode, q, k, v, do, scale, iters, flush):
+    fn = lambda: attention_input_pullback_basis(q, k, v, do, scale=scale, causal=True, kernel_mode=mode)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        out = fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2], times[0], torch.cuda.max_memory_allocated(), out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--quick", action="store_true", help="seq 512 and 2048, head_dim 64, bf16 only")
+    ap.add_argument("--check", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--atol", type=float, default=3e-2)
+    ap.add_argument("--out-dir", type=str, default="out/benchmarks/attention_pullback")
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    batch, heads = 8, 16
+    seqs = (512, 2048) if args.quick else (128, 512, 2048)
+    dims = (64,) if args.quick else (64, 128)
+    dtypes = (torch.bfloat16,) if args.quick else (torch.float16, torch.bfloat16)
+    rows = []
+    for dtype in dtypes:
+        for t in seqs:
+            for dh in dims:
+                for p in (4, 16):
+                    g = torch.Generator(device=dev).manual_seed(0)
+                    q, k, v = (torch.randn(batch, heads, t, dh, device=dev, generator=g).to(dtype) for _ in range(3))
+                    do = torch.randn(batch, p, heads, t, dh, device=dev, generator=g).to(dtype)
+                    scale = 1.0 / math.sqrt(dh)
+                    want = None
+                    if args.check and t <= 512:
+                        want = ref.attention_input_pullback_dense(q, k, v, do, scale, True)
+                    modes = ["fa2_loop"]
+                    if tcgen05_pullback_supported(dtype, dh, heads, heads, t):
+                        modes.insert(0, "tcgen05_pblock")
+                    for mode in modes:
+                        row = dict(dtype=str(dtype).replace("torch.", ""), batch=batch, heads=heads, seq_len=t, head_dim=dh,
+                                   basis=p, kernel_mode=mode, max_abs_err="", status="ok")
+                        try:
+                            med, best, peak, out = time_mode(mode, q, k, v, do, scale, args.iters, flush)
+                            row.update(median_ms=med, best_ms=best, peak_bytes=peak,
+                                       tflops=pullback_flops(batch, heads, t, dh, p) / med / 1e9)
+                            if want is not None:
+                                err = max((a.float() - w).abs().max().item() for a, w in zip(out, want))
+                                row["max_abs_err"] = err
+                                if err > args.atol * max(w.abs().max().item() for w in want) + 1e-3:
+                                    row["status"] = "mismatch"
+                        except Exception as exc:  # noqa: BLE001 - recorded per cell
+                            row.update(median_ms="", best_ms="", peak_bytes="", tflops="", status=f"error: {exc!r}"[:120])
+                        rows.append(row)
+                        print(row, flush=True)
+                    del q, k, v, do, want
+    out_dir = Path(args.out_dir)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    stamp = time.strftime("%Y%m%d_%H%M%S")
+    for name in (f"attention_pullback_{stamp}.csv", "latest.csv"):
+        with (out_dir / name).open("w", newline="") as f:
+            w = csv.DictWriter(f, fieldnames=FIELDS)
+            w.writeheader()
+            w.writerows(rows)
+    speedups = {}
+    for r in rows:
+        if r["kernel_mode"] == "tcgen05_pblock" and r["status"] == "ok":
+            base = next((x for x in rows if x["kernel_mode"] == "fa2_loop" and all(x[k] == r[k] for k in ("dtype", "seq_len", "head_dim", "basis"))), None)
+            if base and base["status"] == "ok":
+                key = f"{r['dtype']}_T{r['seq_len']}_D{r['head_dim']}_P{r['basis']}"
+                speedups[key] = base["median_ms"] / r["median_ms"]
+    (out_dir / "latest_summary.json").write_text(json.dumps({"speedup_tcgen05_over_fa2_loop": speedups, "rows": len(rows)}, indent=2))
+    print(json.dumps({"speedup_tcgen05_over_fa2_loop": speedups}))
+
+
+if __name__ == "__main__":
+    main()
