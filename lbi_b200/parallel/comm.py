@@ -60,13 +60,23 @@ class CollectiveComm:
         dist.recv(buf, src=src, group=self.group, tag=slot)
         return buf
 
+    def _all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        """[*shape] on every rank -> [world, *shape]."""
+        w = self.world_size
+        flat = t.contiguous().reshape(-1)
+        if dist.get_backend(self.group) == "gloo":
+            parts = [torch.empty_like(flat) for _ in range(w)]
+            dist.all_gather(parts, flat, group=self.group)
+            return torch.stack(parts).reshape(w, *t.shape)
+        out = torch.empty(w * flat.numel(), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(out, flat, group=self.group)
+        return out.reshape(w, *t.shape)
+
     def gather_scan_inputs(self, mats: torch.Tensor, offsets: torch.Tensor):
         """mats [B, k_local, R, R], offsets [B, k_local, R] -> concatenated over ranks along dim 1."""
         w = self.world_size
-        m_all = torch.empty((w, *mats.shape), dtype=mats.dtype, device=mats.device)
-        o_all = torch.empty((w, *offsets.shape), dtype=offsets.dtype, device=offsets.device)
-        dist.all_gather_into_tensor(m_all, mats.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(o_all, offsets.contiguous(), group=self.group)
+        m_all = self._all_gather(mats)
+        o_all = self._all_gather(offsets)
         b = mats.shape[0]
         m_cat = m_all.permute(1, 0, 2, 3, 4).reshape(b, w * mats.shape[1], *mats.shape[2:])
         o_cat = o_all.permute(1, 0, 2, 3).reshape(b, w * offsets.shape[1], offsets.shape[2])

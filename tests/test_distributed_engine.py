@@ -1,0 +1,72 @@
+"""Region-parallel engine over several ranks (gloo on CPU): gradients and the optimizer step must equal the
+single-process run, for both region axes."""
+import copy
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from lbi_b200.backbones import BackboneSpec
+from lbi_b200.interfaces import VectorMLPInterface
+from lbi_b200.models import LBILanguageModel
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _model(axis, regions):
+    torch.manual_seed(0)
+    spec = BackboneSpec(name="transformer", dim=32, layers=4, n_heads=4, d_conv=0)
+    iface = VectorMLPInterface(feature_dim=32, num_regions=regions, interface_width=8, interface_map_hidden_dim=16)
+    return LBILanguageModel(vocab_size=64, layers_per_region=4 // regions if axis == "depth" else 1, backbone_spec=spec,
+                            interface=iface, region_axis=axis, num_sequence_regions=regions, tie_embeddings=True)
+
+
+def _worker(rank, world, port, axis, regions, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lbi_b200.parallel import CollectiveComm, FastLBIEngine
+
+        torch.set_num_threads(1)
+        model = _model(axis, regions)
+        engine = FastLBIEngine(model, lr=1e-2, grad_clip=1.0, basis_chunk=3, comm=CollectiveComm())
+        g = torch.Generator().manual_seed(5)
+        ids, tgt = torch.randint(0, 64, (2, 32), generator=g), torch.randint(0, 64, (2, 32), generator=g)
+        res = engine.backward(ids, tgt)
+        grads = engine.flat.grads.clone()
+        dist.all_reduce(grads)
+        loss = res.loss.clone()
+        dist.all_reduce(loss)
+        engine._optimizer_step(1e-2)
+        if rank == 0:
+            torch.save({"grads": grads, "loss": loss, "params": engine.flat.params.clone(), "g": res.state_cotangents},
+                       os.path.join(out_dir, "dist.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("axis,regions,world", [("sequence", 4, 2), ("depth", 4, 4), ("sequence", 4, 4)])
+def test_multi_rank_engine_matches_single_process(tmp_path, axis, regions, world):
+    from lbi_b200.parallel import FastLBIEngine
+
+    port = _free_port()
+    mp.spawn(_worker, args=(world, port, axis, regions, str(tmp_path)), nprocs=world, join=True)
+    got = torch.load(tmp_path / "dist.pt")
+    model = _model(axis, regions)
+    engine = FastLBIEngine(copy.deepcopy(model), lr=1e-2, grad_clip=1.0, basis_chunk=3)
+    g = torch.Generator().manual_seed(5)
+    ids, tgt = torch.randint(0, 64, (2, 32), generator=g), torch.randint(0, 64, (2, 32), generator=g)
+    res = engine.backward(ids, tgt)
+    n = min(engine.flat.total, got["grads"].numel())
+    assert torch.allclose(got["loss"], res.loss, atol=1e-6)
+    assert torch.allclose(got["g"], res.state_cotangents, atol=1e-6)
+    assert torch.allclose(got["grads"][:n], engine.flat.grads[:n], atol=1e-6, rtol=1e-5)
+    engine._optimizer_step(1e-2)
+    assert torch.allclose(got["params"][:n], engine.flat.params[:n], atol=1e-5, rtol=1e-5)
