@@ -4,7 +4,7 @@
 //     dV_p = P^T dO_p,   dP_p = dO_p v^T,   dS_p = P o (dP_p - delta_p),   dQ_p = s dS_p k,   dK_p = s dS_p^T q
 // with delta_p = rowsum(dO_p o O).  Two kernels, both built from the same template:
 //
-//   DKDV = true   one CTA owns a 128-row key tile j and PB = 3 directions; it walks the query tiles i >= j.
+//   DKDV = true   one CTA owns a 128-row key tile j and PB = 2 directions; it walks the query tiles i >= j.
 //                 Per (i, j): S = Q_i K_j^T and P are computed ONCE and P is parked in shared memory; then for every
 //                 direction: dP, dS, dV_p += P^T dO_p, dK_p += dS^T Q_i.  dK_p / dV_p accumulate in TMEM over all i.
 //   DKDV = false  one CTA owns a 128-row query tile i and PB = 4 directions; it walks the key tiles j <= i:
@@ -21,9 +21,17 @@
 // Q, K, V and dO are each loaded once per use and never transposed.  P and dS are written by the compute warps into
 // shared memory in the same swizzled layout ([128 q rows] x two 64-wide key panels).
 //
-// TMEM (512 columns): [0, 128) holds S and is then reused for dP; the accumulators follow, 64 columns each.
-// Warp roles (288 threads): warps 0-7 compute (TMEM lane quarter = warp % 4, key-column half = warp / 4),
-// warp 8 lane 0 issues all TMA loads and all MMAs.  Every mbarrier wait is bounded (tcgen05.cuh).
+// Pipeline.  The S and dP products of one CTA form a sequence of "jobs" (per step: S, dP_0, .., dP_{np-1}).  Job n
+// writes TMEM buffer n & 1 (columns [0,128) and [128,256)); the accumulators follow from column 256, 64 columns each.
+// The control thread issues job n as soon as the compute warps have consumed job n - 2, and issues the accumulating
+// MMAs of job n - 2 (which need the dS tile the compute warps wrote) at the same moment, so the tensor core always has
+// the next product queued while the compute warps turn the previous one into P or dS.  dS tiles are double-buffered
+// in shared memory; P stays in registers (and, for DKDV, in shared memory as an MMA operand).
+// Warp roles (320 threads): warps 0-7 compute (TMEM lane quarter = warp % 4, key-column half = warp / 4);
+// warp 8 lane 0 issues the TMA loads and the S / dP products; warp 9 lane 0 issues the accumulating products and
+// releases shared-memory stages.  Two issuing threads because a single thread's instruction stream (descriptor
+// arithmetic + about twenty tcgen05.mma per job) was measured to be the bottleneck.  Every mbarrier wait is bounded
+// (tcgen05.cuh); all barrier parities are derived from job / tile counters.
 #include <cuda_bf16.h>
 
 #include <mutex>
@@ -40,10 +48,10 @@ constexpr int TILE = 128;       // query rows and key rows per tile
 constexpr int DH = 64;          // head dimension handled by this build
 constexpr int TILE_BYTES = TILE * DH * 2;   // 16 KB
 constexpr int PANEL_BYTES = TILE * 128;     // one 64-column panel of P / dS: 128 rows x 128 B
-constexpr int THREADS = 288;
-constexpr int PB_DKDV = 3;
+constexpr int THREADS = 320;
+constexpr int PB_DKDV = 2;
 constexpr int PB_DQ = 4;
-constexpr int NDO = 3;          // dO stages in DKDV mode
+constexpr int NDO = 4;          // dO stages in DKDV mode
 
 struct Params {
   int batch, heads, seq_len, nbasis;
@@ -59,30 +67,23 @@ struct Params {
 
 template <bool DKDV>
 struct Smem {
-  // fixed tiles: DKDV: K_j, V_j ; DQ: Q_i, dO_0..3
-  alignas(1024) uint8_t fixed[(DKDV ? 2 : 1 + PB_DQ)][TILE_BYTES];
-  // streamed tiles: DKDV: Q_i (2 stages) then dO (NDO stages) ; DQ: K_j (2 stages) then V_j (2 stages)
-  alignas(1024) uint8_t stream[(DKDV ? 2 + NDO : 4)][TILE_BYTES];
-  alignas(1024) uint8_t p_tile[2][PANEL_BYTES];
-  alignas(1024) uint8_t ds_tile[2][PANEL_BYTES];
-  uint64_t bar_fixed;            // fixed tiles landed
-  uint64_t bar_stream_full[(DKDV ? 2 + NDO : 4)];
-  uint64_t bar_stream_empty[(DKDV ? 2 + NDO : 4)];
-  uint64_t bar_s_ready;          // S in TMEM (commit)
-  uint64_t bar_p_ready;          // P in shared memory (256 arrivals)
-  uint64_t bar_p_free;           // MMAs that read P have finished (commit)
-  uint64_t bar_dp_ready;         // dP in TMEM (commit)
-  uint64_t bar_ds_ready;         // dS in shared memory, dP consumed (256 arrivals)
-  uint64_t bar_ds_free;          // MMA that read dS has finished (commit)
-  uint64_t bar_acc_done;         // all accumulating MMAs finished (commit)
+  static constexpr int NFIXED = DKDV ? 2 : 1 + PB_DQ;   // DKDV: K_j, V_j ; DQ: Q_i, dO_0..3
+  static constexpr int NSTREAM = DKDV ? 2 + NDO : 4;    // DKDV: Q_i x2, dO x NDO ; DQ: K_j x2, V_j x2
+  alignas(1024) uint8_t fixed[NFIXED][TILE_BYTES];
+  alignas(1024) uint8_t stream[NSTREAM][TILE_BYTES];
+  alignas(1024) uint8_t ds_tile[2][2][PANEL_BYTES];      // [buffer][64-column panel]
+  alignas(1024) uint8_t p_tile[DKDV ? 2 : 1][DKDV ? PANEL_BYTES : 1024];
+  uint64_t bar_fixed;
+  uint64_t bar_stream_full[NSTREAM];
+  uint64_t bar_stream_empty[NSTREAM];
+  uint64_t bar_ready[2];          // job result in TMEM buffer (commit)
+  uint64_t bar_consumed[2];       // compute warps are done with the TMEM buffer: 256 arrivals (read by the S/dP issuer)
+  uint64_t bar_written[4];        // same event for the accumulate issuer (P / dS are in shared memory), 4 slots deep
+  uint64_t bar_ds_free[2];        // the MMA that read this dS buffer has finished (commit)
+  uint64_t bar_p_free;            // the MMAs that read P have finished (commit)
+  uint64_t bar_acc_done;          // all accumulating MMAs finished (commit)
   uint32_t tmem_base;
   volatile int abort_flag;
-};
-
-struct Phase {
-  uint32_t bits = 0;
-  __device__ __forceinline__ uint32_t get(int idx) const { return (bits >> idx) & 1u; }
-  __device__ __forceinline__ void flip(int idx) { bits ^= (1u << idx); }
 };
 
 // 16-byte chunk address of row r, chunk c (8 bf16) inside a 128-byte-swizzled panel of 128-byte rows.
@@ -111,11 +112,13 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+
+
 template <bool DKDV>
 __global__ void __launch_bounds__(THREADS, 1)
 pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const Params p) {
   constexpr int PB = DKDV ? PB_DKDV : PB_DQ;
-  constexpr int NSTREAM = DKDV ? 2 + NDO : 4;
+  constexpr int NSTREAM = Smem<DKDV>::NSTREAM;
   extern __shared__ uint8_t raw_smem[];
   Smem<DKDV>& s = *reinterpret_cast<Smem<DKDV>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -127,9 +130,13 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   const int p0 = blockIdx.z * PB;
   const int np = min(PB, p.nbasis - p0);
   const int n_iter = DKDV ? p.n_tiles - own : own + 1;
+  const int jobs_per_iter = np + 1;
+  const int total_jobs = n_iter * jobs_per_iter;
   const int hd = p.heads * DH;
   const int col_q = h * DH, col_k = hd + h * DH, col_v = 2 * hd + h * DH;
   const int row_b = b * p.seq_len;  // first token row of this batch element (within one direction)
+  // TMEM columns: job buffers [0,128) and [128,256); DKDV: dK_p at 256 + 64 p, dV_p at 384 + 64 p; DQ: dQ_p at 256 + 64 p
+  constexpr int ACC0 = 256, ACC_DV = 384;
 
   if (threadIdx.x == 0) {
     s.abort_flag = 0;
@@ -138,12 +145,13 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       mbar_init(&s.bar_stream_full[i], 1);
       mbar_init(&s.bar_stream_empty[i], 1);
     }
-    mbar_init(&s.bar_s_ready, 1);
-    mbar_init(&s.bar_p_ready, 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.bar_ready[i], 1);
+      mbar_init(&s.bar_consumed[i], 256);
+      mbar_init(&s.bar_ds_free[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(&s.bar_written[i], 256);
     mbar_init(&s.bar_p_free, 1);
-    mbar_init(&s.bar_dp_ready, 1);
-    mbar_init(&s.bar_ds_ready, 256);
-    mbar_init(&s.bar_ds_free, 1);
     mbar_init(&s.bar_acc_done, 1);
     fence_barrier_init();
     prefetch_tmap(&map_qkv);
@@ -156,241 +164,262 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   const uint32_t tmem = s.tmem_base;
   volatile int* abortp = &s.abort_flag;
 
-  if (warp == 8) {
-    // ======================================================================== control: TMA + MMA issue
-    if (lane == 0) {
-      const uint32_t idesc_nn = make_idesc_bf16(128, 128, 0, 0);          // S, dP
-      const uint32_t idesc_acc = DKDV ? make_idesc_bf16(128, 64, 1, 1)     // dV, dK: both operands MN-major
-                                      : make_idesc_bf16(128, 64, 0, 1);    // dQ: dS K-major, K_j MN-major
-      Phase full, empty;
-      uint32_t ph_p_ready = 0, ph_ds_ready = 0;
-      bool ok = true;
+  // Descriptors are a constant template plus (address >> 4); consecutive tiles are TILE_BYTES apart.
+  const uint64_t kmajor0 = make_smem_desc(0, 16, 1024);            // rows = M/N index, 64 K-elements per 128-byte row
+  const uint64_t mnmajor0 = make_smem_desc(0, PANEL_BYTES, 1024);  // rows = K index, 64-wide M/N panels PANEL_BYTES apart
+  const uint32_t stream0 = smem_u32(s.stream[0]) >> 4, fixed0 = smem_u32(s.fixed[0]) >> 4;
+  constexpr uint32_t TILE16 = TILE_BYTES >> 4;
 
+  if (warp == 8) {
+    // ======================================================================== issuer X: TMA loads, S and dP products
+    if (lane == 0) {
+      const uint32_t idesc_nn = make_idesc_bf16(128, 128, 0, 0);
+      bool ok = true;
+      int next_main = 0, main_waited = 0, next_do = 0, do_waited = 0, v_waited = 0;
+      const int total_do = DKDV ? n_iter * np : 0;
       auto load_tile = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int col, int64_t row) {
         mbar_arrive_expect_tx(bar, TILE_BYTES);
         tma_load_2d(dst, m, bar, col, (int)row);
       };
-      // K-major 128 x 64 operand: four K = 16 slices, 32 bytes apart inside the swizzled row
-      auto kdesc = [&](const void* tile, int k) { return make_smem_desc(smem_u32(tile) + k * 32, 16, 1024); };
-      // MN-major operand read from a [128 k-rows] x 128 B panel: K = 16 is sixteen rows = 2048 bytes
-      auto mndesc = [&](const void* tile, int k) { return make_smem_desc(smem_u32(tile) + k * 2048, PANEL_BYTES, 1024); };
-
+      // Load further streamed tiles while their stage is free.  Non-blocking unless a tile up to need_* is required.
+      auto refill = [&](int need_main, int need_do) {
+        while (ok && next_main < n_iter) {
+          const int st = next_main & 1;
+          if (next_main >= 2) {
+            const uint32_t par = ((next_main >> 1) - 1) & 1;
+            if (next_main <= need_main) ok = mbar_wait(&s.bar_stream_empty[st], par, abortp, p.status, 11);
+            else if (!mbar_try_wait(&s.bar_stream_empty[st], par)) break;
+            if (!ok) break;
+          }
+          if (DKDV) {
+            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_q, row_b + (own + next_main) * TILE);
+          } else {
+            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_k, row_b + next_main * TILE);
+            load_tile(s.stream[2 + st], &map_qkv, &s.bar_stream_full[2 + st], col_v, row_b + next_main * TILE);
+          }
+          ++next_main;
+        }
+        while (DKDV && ok && next_do < total_do) {
+          const int st = 2 + next_do % NDO;
+          if (next_do >= NDO) {
+            const uint32_t par = ((next_do / NDO) - 1) & 1;
+            if (next_do <= need_do) ok = mbar_wait(&s.bar_stream_empty[st], par, abortp, p.status, 12);
+            else if (!mbar_try_wait(&s.bar_stream_empty[st], par)) break;
+            if (!ok) break;
+          }
+          const int it = next_do / np, pp = next_do % np;
+          load_tile(s.stream[st], &map_do, &s.bar_stream_full[st], h * DH,
+                    (int64_t)(p0 + pp) * p.n_rows + row_b + (own + it) * TILE);
+          ++next_do;
+        }
+      };
       if (DKDV) {
-        // ---------------- fixed: K_j, V_j ; streamed: Q_i (stages 0, 1), dO_{p,i} (stages 2 .. 2 + NDO)
         mbar_arrive_expect_tx(&s.bar_fixed, 2 * TILE_BYTES);
         tma_load_2d(s.fixed[0], &map_qkv, &s.bar_fixed, col_k, row_b + own * TILE);
         tma_load_2d(s.fixed[1], &map_qkv, &s.bar_fixed, col_v, row_b + own * TILE);
-        const int total_do = n_iter * np;
-        int next_do = 0, next_q = 0;
-        auto refill_do = [&](int upto) {  // load dO tiles with index < upto
-          while (ok && next_do < total_do && next_do < upto) {
-            const int st = 2 + next_do % NDO;
-            if (next_do >= NDO) {
-              ok = mbar_wait(&s.bar_stream_empty[st], empty.get(st), abortp, p.status, 11);
-              empty.flip(st);
-              if (!ok) break;
-            }
-            const int it = next_do / np, pp = next_do % np;
-            const int64_t row = (int64_t)(p0 + pp) * p.n_rows + row_b + (own + it) * TILE;
-            load_tile(s.stream[st], &map_do, &s.bar_stream_full[st], h * DH, row);
-            ++next_do;
-          }
-        };
-        auto refill_q = [&](int upto) {
-          while (ok && next_q < n_iter && next_q < upto) {
-            const int st = next_q & 1;
-            if (next_q >= 2) {
-              ok = mbar_wait(&s.bar_stream_empty[st], empty.get(st), abortp, p.status, 12);
-              empty.flip(st);
-              if (!ok) break;
-            }
-            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_q, row_b + (own + next_q) * TILE);
-            ++next_q;
-          }
-        };
-        refill_q(1);
-        refill_do(NDO - 1);
-        ok = ok && mbar_wait(&s.bar_fixed, 0, abortp, p.status, 13);
-        int c = 0;  // running index over (iteration, direction)
-        for (int it = 0; it < n_iter && ok; ++it) {
-          const int qs = it & 1;
-          ok = mbar_wait(&s.bar_stream_full[qs], full.get(qs), abortp, p.status, 14);
-          full.flip(qs);
-          if (!ok) break;
-          fence_after_sync();
-#pragma unroll
-          for (int k = 0; k < 4; ++k) mma_bf16(tmem, kdesc(s.stream[qs], k), kdesc(s.fixed[0], k), idesc_nn, k);
-          mma_commit(&s.bar_s_ready);
-          refill_q(it + 2);
-          ok = ok && mbar_wait(&s.bar_p_ready, ph_p_ready, abortp, p.status, 15);
-          ph_p_ready ^= 1;
-          if (!ok) break;
-          fence_after_sync();
-          for (int pp = 0; pp < np && ok; ++pp, ++c) {
-            const int st = 2 + c % NDO;
-            ok = mbar_wait(&s.bar_stream_full[st], full.get(st), abortp, p.status, 16);
-            full.flip(st);
-            if (!ok) break;
-            fence_after_sync();
-#pragma unroll
-            for (int k = 0; k < 4; ++k) mma_bf16(tmem, kdesc(s.stream[st], k), kdesc(s.fixed[1], k), idesc_nn, k);
-            mma_commit(&s.bar_dp_ready);
-            const uint32_t acc_dk = tmem + 128 + pp * 128, acc_dv = acc_dk + 64;
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              mma_bf16(acc_dv, mndesc(s.p_tile, k), mndesc(s.stream[st], k), idesc_acc, (it | k) != 0);
-            if (pp == np - 1) mma_commit(&s.bar_p_free);
-            refill_do(c + NDO - 1);
-            ok = ok && mbar_wait(&s.bar_ds_ready, ph_ds_ready, abortp, p.status, 17);
-            ph_ds_ready ^= 1;
-            if (!ok) break;
-            fence_after_sync();
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              mma_bf16(acc_dk, mndesc(s.ds_tile, k), mndesc(s.stream[qs], k), idesc_acc, (it | k) != 0);
-            mma_commit(&s.bar_ds_free);
-            mma_commit(&s.bar_stream_empty[st]);
-          }
-          mma_commit(&s.bar_stream_empty[qs]);
-        }
-        if (ok) mma_commit(&s.bar_acc_done);
       } else {
-        // ---------------- fixed: Q_i, dO_0 .. dO_{np-1} ; streamed: K_j (stages 0, 1), V_j (stages 2, 3)
         mbar_arrive_expect_tx(&s.bar_fixed, (1 + np) * TILE_BYTES);
         tma_load_2d(s.fixed[0], &map_qkv, &s.bar_fixed, col_q, row_b + own * TILE);
         for (int pp = 0; pp < np; ++pp)
           tma_load_2d(s.fixed[1 + pp], &map_do, &s.bar_fixed, h * DH,
                       (int)((int64_t)(p0 + pp) * p.n_rows + row_b + own * TILE));
-        int next_kv = 0;
-        auto refill_kv = [&](int upto) {
-          while (ok && next_kv < n_iter && next_kv < upto) {
-            const int st = next_kv & 1;
-            if (next_kv >= 2) {
-              ok = mbar_wait(&s.bar_stream_empty[st], empty.get(st), abortp, p.status, 21);
-              empty.flip(st);
-              if (!ok) break;
-            }
-            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_k, row_b + next_kv * TILE);
-            load_tile(s.stream[2 + st], &map_qkv, &s.bar_stream_full[2 + st], col_v, row_b + next_kv * TILE);
-            ++next_kv;
-          }
-        };
-        refill_kv(1);
-        ok = ok && mbar_wait(&s.bar_fixed, 0, abortp, p.status, 23);
-        for (int it = 0; it < n_iter && ok; ++it) {
-          const int ks = it & 1;
-          ok = mbar_wait(&s.bar_stream_full[ks], full.get(ks), abortp, p.status, 24);
-          full.flip(ks);
-          if (!ok) break;
-          fence_after_sync();
-#pragma unroll
-          for (int k = 0; k < 4; ++k) mma_bf16(tmem, kdesc(s.fixed[0], k), kdesc(s.stream[ks], k), idesc_nn, k);
-          mma_commit(&s.bar_s_ready);
-          refill_kv(it + 2);
-          ok = ok && mbar_wait(&s.bar_p_ready, ph_p_ready, abortp, p.status, 25);
-          ph_p_ready ^= 1;
-          ok = ok && mbar_wait(&s.bar_stream_full[2 + ks], full.get(2 + ks), abortp, p.status, 26);
-          full.flip(2 + ks);
-          if (!ok) break;
-          fence_after_sync();
-          for (int pp = 0; pp < np && ok; ++pp) {
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              mma_bf16(tmem, kdesc(s.fixed[1 + pp], k), kdesc(s.stream[2 + ks], k), idesc_nn, k);
-            mma_commit(&s.bar_dp_ready);
-            ok = mbar_wait(&s.bar_ds_ready, ph_ds_ready, abortp, p.status, 27);
-            ph_ds_ready ^= 1;
-            if (!ok) break;
-            fence_after_sync();
-            const uint32_t acc_dq = tmem + 128 + pp * 64;
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              mma_bf16(acc_dq, make_smem_desc(smem_u32(s.ds_tile[k >> 2]) + (k & 3) * 32, 16, 1024),
-                       mndesc(s.stream[ks], k), idesc_acc, (it | k) != 0);
-            mma_commit(&s.bar_ds_free);
-          }
-          mma_commit(&s.bar_stream_empty[ks]);  // one commit covers K_j and V_j: both stages free together
-        }
-        if (ok) mma_commit(&s.bar_acc_done);
       }
+      refill(-1, -1);
+      ok = ok && mbar_wait(&s.bar_fixed, 0, abortp, p.status, 16);
+
+      for (int n = 0; n < total_jobs && ok; ++n) {
+        const int it = n / jobs_per_iter, r = n % jobs_per_iter;
+        if (n >= 2) {
+          ok = mbar_wait(&s.bar_consumed[n & 1], ((n - 2) >> 1) & 1, abortp, p.status, 17);
+          if (!ok) break;
+        }
+        uint32_t a16, b16;  // operand tile addresses >> 4
+        if (r == 0) {
+          refill(it, -1);
+          while (ok && main_waited <= it) {
+            ok = mbar_wait(&s.bar_stream_full[main_waited & 1], (main_waited >> 1) & 1, abortp, p.status, 13);
+            ++main_waited;
+          }
+          a16 = DKDV ? stream0 + (it & 1) * TILE16 : fixed0;
+          b16 = DKDV ? fixed0 : stream0 + (it & 1) * TILE16;
+        } else if (DKDV) {
+          const int c = it * np + (r - 1);
+          refill(-1, c);
+          while (ok && do_waited <= c) {
+            ok = mbar_wait(&s.bar_stream_full[2 + do_waited % NDO], (do_waited / NDO) & 1, abortp, p.status, 15);
+            ++do_waited;
+          }
+          a16 = stream0 + (2 + c % NDO) * TILE16;
+          b16 = fixed0 + TILE16;
+        } else {
+          while (ok && v_waited <= it) {
+            ok = mbar_wait(&s.bar_stream_full[2 + (v_waited & 1)], (v_waited >> 1) & 1, abortp, p.status, 14);
+            ++v_waited;
+          }
+          a16 = fixed0 + r * TILE16;
+          b16 = stream0 + (2 + (it & 1)) * TILE16;
+        }
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t d_tmem = tmem + (n & 1) * 128;
+        const uint64_t da = kmajor0 + a16, db = kmajor0 + b16;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc_nn, k);
+        mma_commit(&s.bar_ready[n & 1]);
+        refill(-1, -1);
+      }
+    }
+  } else if (warp == 9) {
+    // ======================================================================== issuer Y: accumulating products, releases
+    if (lane == 0) {
+      const uint32_t idesc_acc = DKDV ? make_idesc_bf16(128, 64, 1, 1) : make_idesc_bf16(128, 64, 0, 1);
+      const uint32_t idesc_dv2 = make_idesc_bf16(128, 128, 1, 1);  // dV of two directions in one instruction
+      const uint32_t ds0 = smem_u32(s.ds_tile[0][0]) >> 4, p16 = smem_u32(s.p_tile[0]) >> 4;
+      constexpr uint32_t DSBUF16 = (2 * PANEL_BYTES) >> 4, PANEL16 = PANEL_BYTES >> 4;
+      bool ok = true;
+      int do_waited = 0;
+      for (int m = 0; m < total_jobs && ok; ++m) {
+        const int it = m / jobs_per_iter, r = m % jobs_per_iter;
+        ok = mbar_wait(&s.bar_written[m & 3], (m >> 2) & 1, abortp, p.status, 18);
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t first = it != 0;  // accumulate onto earlier steps?
+        if (r == 0) {
+          if (DKDV) {  // P_it is in shared memory: dV_p += P^T dO_p for the directions of this step
+            const int c0 = it * np;
+            while (ok && do_waited <= c0 + np - 1) {
+              ok = mbar_wait(&s.bar_stream_full[2 + do_waited % NDO], (do_waited / NDO) & 1, abortp, p.status, 19);
+              ++do_waited;
+            }
+            if (!ok) break;
+            const uint64_t da = mnmajor0 + p16;
+            const uint64_t db = mnmajor0 + stream0 + (2 + c0 % NDO) * TILE16;
+            if (np == 2) {  // the two dO tiles are adjacent stages: one N = 128 operand with two 64-wide panels
+#pragma unroll
+              for (int k = 0; k < 8; ++k) mma_bf16(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
+            } else {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) mma_bf16(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
+            }
+            mma_commit(&s.bar_p_free);
+          }
+          continue;
+        }
+        const int pp = r - 1, d = it * np + pp, buf = d & 1;
+        const uint32_t acc = tmem + ACC0 + pp * 64;
+        if (DKDV) {
+          const uint64_t da = mnmajor0 + ds0 + buf * DSBUF16;
+          const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mma_bf16(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
+          mma_commit(&s.bar_ds_free[buf]);
+          mma_commit(&s.bar_stream_empty[2 + d % NDO]);  // dO tile d: its dV and this dK are behind the commit, dP was consumed
+        } else {
+          const uint64_t da = kmajor0 + ds0 + buf * DSBUF16;
+          const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_bf16(acc, da + (k >> 2) * PANEL16 + (k & 3) * 2, db + 128 * k, idesc_acc, first | (k != 0));
+          mma_commit(&s.bar_ds_free[buf]);
+        }
+        if (pp == np - 1) mma_commit(&s.bar_stream_empty[it & 1]);  // Q_it (DKDV) or K_it and V_it (DQ) may be overwritten
+      }
+      if (ok) mma_commit(&s.bar_acc_done);
     }
   } else {
     // ======================================================================== compute warps 0..7
     const int quarter = warp & 3, half = warp >> 2;
     const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
-    const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t p_panel = smem_u32(s.p_tile[half]);
-    const uint32_t ds_panel = smem_u32(s.ds_tile[half]);
+    const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16) + half * 64;
+    const uint32_t p_panel = smem_u32(s.p_tile[DKDV ? half : 0]);
     const float* lse_bh = p.lse + ((int64_t)b * p.heads + h) * p.seq_len;
     constexpr float LOG2E = 1.4426950408889634f;
-    uint32_t ph_s = 0, ph_dp = 0, ph_pfree = 0, ph_dsfree = 0;
-    int c = 0;
+    uint32_t preg[32];                                        // this thread's 64 probabilities as bf16 pairs
+    // Row statistics (log-sum-exp and the per-direction row dots) are fetched one step ahead: a load issued at the
+    // point of use would expose a full DRAM round trip on every job.
+    const float* delta_base = p.delta + (((int64_t)p0 * p.batch + b) * p.heads + h) * p.seq_len + r;
+    const int64_t delta_dir = (int64_t)p.batch * p.heads * p.seq_len;   // stride between directions
+    auto load_stats = [&](int q_tile, float& lse_out, float (&delta_out)[PB]) {
+      lse_out = lse_bh[q_tile * TILE + r] * LOG2E;
+#pragma unroll
+      for (int i = 0; i < PB; ++i) delta_out[i] = i < np ? delta_base[i * delta_dir + q_tile * TILE] : 0.f;
+    };
+    float lse_r, delta_cur[PB], lse_next = 0.f, delta_next[PB];
+    load_stats(own, lse_r, delta_cur);                       // DKDV: first query tile is `own`; DQ: the only one
+#pragma unroll
+    for (int i = 0; i < PB; ++i) delta_next[i] = 0.f;
     bool ok = true;
-    for (int it = 0; it < n_iter && ok; ++it) {
+    for (int n = 0; n < total_jobs && ok; ++n) {
+      const int it = n / jobs_per_iter, rr = n % jobs_per_iter, buf = n & 1;
       const int qi = DKDV ? own + it : own;   // query tile of this step
       const int kj = DKDV ? own : it;         // key tile of this step
-      const float lse_r = lse_bh[qi * TILE + r] * LOG2E;
-      ok = mbar_wait(&s.bar_s_ready, ph_s, abortp, p.status, 31);
-      ph_s ^= 1;
-      if (DKDV && it > 0 && ok) {
-        ok = mbar_wait(&s.bar_p_free, ph_pfree, abortp, p.status, 32);
-        ph_pfree ^= 1;
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      fence_after_sync();
-      const bool diagonal = (qi == kj);
+      const uint32_t t_buf = t_lane + buf * 128;
+      if (rr == 0) {
+        if (DKDV) {
+          if (it > 0) {
+            lse_r = lse_next;
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_lane + half * 64 + cc * 32, v);
-        tmem_ld_wait();
-        const int col0 = half * 64 + cc * 32;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = col0 + g * 8 + e * 2;
-            float a = fast_exp2(__uint_as_float(v[g * 8 + e * 2]) * p.scale_log2 - lse_r);
-            float bb = fast_exp2(__uint_as_float(v[g * 8 + e * 2 + 1]) * p.scale_log2 - lse_r);
-            if (diagonal) {
-              if (col > r) a = 0.f;
-              if (col + 1 > r) bb = 0.f;
-            }
-            w[e] = pack_bf16(a, bb);
+            for (int i = 0; i < PB; ++i) delta_cur[i] = delta_next[i];
           }
-          st_shared_v4(swz(p_panel, r, cc * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
+          if (it + 1 < n_iter) load_stats(qi + 1, lse_next, delta_next);
         }
-      }
-      fence_proxy_async();
-      fence_before_sync();
-      mbar_arrive(&s.bar_p_ready);
-
-      for (int pp = 0; pp < np && ok; ++pp, ++c) {
-        const float delta_r = p.delta[(((int64_t)(p0 + pp) * p.batch + b) * p.heads + h) * p.seq_len + qi * TILE + r];
-        ok = mbar_wait(&s.bar_dp_ready, ph_dp, abortp, p.status, 33);
-        ph_dp ^= 1;
-        if (c > 0 && ok) {
-          ok = mbar_wait(&s.bar_ds_free, ph_dsfree, abortp, p.status, 34);
-          ph_dsfree ^= 1;
+        ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 31);
+        if (DKDV && it > 0 && ok) ok = mbar_wait(&s.bar_p_free, (it - 1) & 1, abortp, p.status, 32);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        fence_after_sync();
+        const bool diagonal = (qi == kj);
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_buf + cc * 32, v);
+          tmem_ld_wait();
+          const int col0 = half * 64 + cc * 32;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int col = col0 + g * 8 + e * 2;
+              float a = fast_exp2(__uint_as_float(v[g * 8 + e * 2]) * p.scale_log2 - lse_r);
+              float bb = fast_exp2(__uint_as_float(v[g * 8 + e * 2 + 1]) * p.scale_log2 - lse_r);
+              if (diagonal) {
+                if (col > r) a = 0.f;
+                if (col + 1 > r) bb = 0.f;
+              }
+              preg[cc * 16 + g * 4 + e] = pack_bf16(a, bb);
+            }
+            if (DKDV)
+              st_shared_v4(swz(p_panel, r, cc * 4 + g),
+                           make_uint4(preg[cc * 16 + g * 4], preg[cc * 16 + g * 4 + 1], preg[cc * 16 + g * 4 + 2],
+                                      preg[cc * 16 + g * 4 + 3]));
+          }
         }
+        if (DKDV) fence_proxy_async();
+        fence_before_sync();
+        mbar_arrive(&s.bar_consumed[buf]);
+        mbar_arrive(&s.bar_written[n & 3]);
+      } else {
+        const int pp = rr - 1, d = it * np + pp, dbuf = d & 1;
+        float delta_r = delta_cur[0];
+#pragma unroll
+        for (int i = 1; i < PB; ++i) delta_r = (pp == i) ? delta_cur[i] : delta_r;
+        const uint32_t ds_panel = smem_u32(s.ds_tile[dbuf][half]);
+        ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 33);
+        if (d >= 2 && ok) ok = mbar_wait(&s.bar_ds_free[dbuf], ((d >> 1) - 1) & 1, abortp, p.status, 34);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after_sync();
 #pragma unroll
         for (int cc = 0; cc < 2; ++cc) {
           uint32_t v[32];
-          tmem_ld_32x32(t_lane + half * 64 + cc * 32, v);
+          tmem_ld_32x32(t_buf + cc * 32, v);
           tmem_ld_wait();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const uint4 pv = ld_shared_v4(swz(p_panel, r, cc * 4 + g));
-            const uint32_t pw[4] = {pv.x, pv.y, pv.z, pv.w};
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float2 pr = unpack_bf16(pw[e]);
+              const float2 pr = unpack_bf16(preg[cc * 16 + g * 4 + e]);
               const float d0 = pr.x * (__uint_as_float(v[g * 8 + e * 2]) - delta_r);
               const float d1 = pr.y * (__uint_as_float(v[g * 8 + e * 2 + 1]) - delta_r);
               w[e] = pack_bf16(d0, d1);
@@ -400,7 +429,8 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         }
         fence_proxy_async();
         fence_before_sync();
-        mbar_arrive(&s.bar_ds_ready);
+        mbar_arrive(&s.bar_consumed[buf]);
+        mbar_arrive(&s.bar_written[n & 3]);
       }
     }
     // ------------------------------------------------------------------ epilogue: accumulators -> global
@@ -414,7 +444,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         const int n_acc = DKDV ? 2 : 1;
         for (int a = 0; a < n_acc; ++a) {
           // DKDV: a = 0 -> dK (scaled), a = 1 -> dV ; DQ: dQ (scaled)
-          const uint32_t acc = DKDV ? tmem + 128 + pp * 128 + a * 64 : tmem + 128 + pp * 64;
+          const uint32_t acc = tmem + (a == 0 ? ACC0 : ACC_DV) + pp * 64;
           const int col = (DKDV ? (a == 0 ? col_k : col_v) : col_q) + half * 32;
           const float mul = (DKDV && a == 1) ? 1.f : p.scale;
           uint32_t v[32];

@@ -6,6 +6,7 @@
 #include "api.h"
 #include "api_attn.h"
 #include "api_gemm.h"
+#include "api_peer.h"
 
 namespace {
 
@@ -325,6 +326,118 @@ Tensor attn_pullback_packed(const Tensor& d_o, const Tensor& qkv, const Tensor& 
   return d_qkv;
 }
 
+// ---- peer-memory kernels.  `*_ptrs` are int64 CUDA tensors holding one device pointer per rank.
+template <typename T>
+T ptr_table(const Tensor& t) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), "pointer table must be a CUDA int64 tensor");
+  return reinterpret_cast<T>(t.data_ptr<int64_t>());
+}
+
+void peer_barrier(const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t slot_base, int64_t seq) {
+  c10::cuda::CUDAGuard guard(flag_ptrs.device());
+  Tensor st = status_word(flag_ptrs);
+  check(lbi_peer_barrier(ptr_table<uint32_t* const*>(flag_ptrs), (int)rank, (int)world, (int)slot_base, (uint32_t)seq,
+                         st.data_ptr<int>(), cur_stream()),
+        "peer_barrier");
+}
+
+void peer_signal_all(const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t slot_base, int64_t seq) {
+  c10::cuda::CUDAGuard guard(flag_ptrs.device());
+  check(lbi_peer_signal_all(ptr_table<uint32_t* const*>(flag_ptrs), (int)rank, (int)world, (int)slot_base, (uint32_t)seq,
+                            cur_stream()),
+        "peer_signal_all");
+}
+
+// Returns (delta, pre_norm, state_out).  peer_state_ptr / peer_flag_ptr are raw device addresses (0 = local only).
+std::tuple<Tensor, Tensor, Tensor> interface_update_handoff(
+    const Tensor& state_in, const Tensor& pooled, const Tensor& w1, const c10::optional<Tensor>& b1,
+    const c10::optional<Tensor>& w2, const c10::optional<Tensor>& b2, const Tensor& alpha, const Tensor& ln_w,
+    const Tensor& ln_b, double ln_eps, int64_t act, int64_t peer_state_ptr, int64_t peer_flag_ptr, int64_t seq,
+    const Tensor& done_counter) {
+  CHECK_F32(state_in);
+  CHECK_F32(pooled);
+  CHECK_F32(w1);
+  CHECK_F32(ln_w);
+  CHECK_F32(ln_b);
+  c10::cuda::CUDAGuard guard(state_in.device());
+  const int batch = (int)state_in.size(0), width = (int)state_in.size(1), dim = (int)pooled.size(1);
+  const bool two_layer = w2.has_value() && w2->defined();
+  const int hidden = two_layer ? (int)w1.size(0) : 0;
+  TORCH_CHECK(w1.size(1) == dim && (two_layer ? (w2->size(0) == width && w2->size(1) == hidden) : w1.size(0) == width),
+              "interface map shapes do not match");
+  Tensor delta = torch::empty_like(state_in), pre = torch::empty_like(state_in), out = torch::empty_like(state_in);
+  auto opt_ptr = [](const c10::optional<Tensor>& t) -> const float* {
+    return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr;
+  };
+  check(lbi_interface_update_handoff(state_in.data_ptr<float>(), pooled.data_ptr<float>(), w1.data_ptr<float>(), opt_ptr(b1),
+                                     opt_ptr(w2), opt_ptr(b2), alpha.data_ptr<float>(), ln_w.data_ptr<float>(),
+                                     ln_b.data_ptr<float>(), (float)ln_eps, (int)act, batch, dim, hidden, width,
+                                     delta.data_ptr<float>(), pre.data_ptr<float>(), out.data_ptr<float>(),
+                                     reinterpret_cast<float*>(peer_state_ptr), reinterpret_cast<uint32_t*>(peer_flag_ptr),
+                                     (uint32_t)seq, reinterpret_cast<uint32_t*>(done_counter.data_ptr<int>()), cur_stream()),
+        "interface_update_handoff");
+  return {delta, pre, out};
+}
+
+Tensor wait_state(const Tensor& mailbox, const Tensor& flags, int64_t flag_index, int64_t seq) {
+  CHECK_F32(mailbox);
+  c10::cuda::CUDAGuard guard(mailbox.device());
+  Tensor out = torch::empty_like(mailbox);
+  Tensor st = status_word(mailbox);
+  check(lbi_wait_state(mailbox.data_ptr<float>(), reinterpret_cast<const uint32_t*>(flags.data_ptr<int>()) + flag_index,
+                       (uint32_t)seq, out.data_ptr<float>(), (int)mailbox.numel(), st.data_ptr<int>(), cur_stream()),
+        "wait_state");
+  return out;
+}
+
+Tensor affine_scan_peer(const Tensor& mats_ptrs, const Tensor& offs_ptrs, const Tensor& flags, int64_t slot_base, int64_t seq,
+                        int64_t batch, int64_t world, int64_t k_local, int64_t r) {
+  c10::cuda::CUDAGuard guard(flags.device());
+  Tensor g = torch::empty({batch, world * k_local, r}, flags.options().dtype(at::kFloat));
+  Tensor st = status_word(flags);
+  check(lbi_affine_scan_peer(ptr_table<const float* const*>(mats_ptrs), ptr_table<const float* const*>(offs_ptrs),
+                             reinterpret_cast<const uint32_t*>(flags.data_ptr<int>()), (int)slot_base, (uint32_t)seq,
+                             g.data_ptr<float>(), (int)batch, (int)world, (int)k_local, (int)r, st.data_ptr<int>(),
+                             cur_stream()),
+        "affine_scan_peer");
+  return g;
+}
+
+void grad_reduce_scatter_(const Tensor& grad_ptrs, int64_t mc_ptr, int64_t rank, int64_t world, int64_t lo, int64_t n,
+                          Tensor sumsq) {
+  CHECK_F32(sumsq);
+  c10::cuda::CUDAGuard guard(sumsq.device());
+  check(lbi_grad_reduce_scatter(ptr_table<float* const*>(grad_ptrs), reinterpret_cast<const float*>(mc_ptr), (int)rank,
+                                (int)world, lo, n, sumsq.data_ptr<float>(), cur_stream()),
+        "grad_reduce_scatter");
+}
+
+void exchange_scalar(const Tensor& val_ptrs, const Tensor& flag_ptrs, const Tensor& mine, int64_t rank, int64_t world,
+                     int64_t slot_base, int64_t seq) {
+  CHECK_F32(mine);
+  c10::cuda::CUDAGuard guard(mine.device());
+  Tensor st = status_word(mine);
+  check(lbi_exchange_scalar(ptr_table<float* const*>(val_ptrs), ptr_table<uint32_t* const*>(flag_ptrs), mine.data_ptr<float>(),
+                            (int)rank, (int)world, (int)slot_base, (uint32_t)seq, st.data_ptr<int>(), cur_stream()),
+        "exchange_scalar");
+}
+
+void adamw_allgather_(Tensor param, const Tensor& reduced_grad, Tensor m, Tensor v, const Tensor& shadow_ptrs, int64_t world,
+                      int64_t lo, double lr, double beta1, double beta2, double eps, double weight_decay, int64_t step,
+                      const Tensor& sumsq_parts, double clip_norm) {
+  CHECK_F32(param);
+  CHECK_F32(reduced_grad);
+  CHECK_F32(m);
+  CHECK_F32(v);
+  CHECK_F32(sumsq_parts);
+  c10::cuda::CUDAGuard guard(param.device());
+  check(lbi_adamw_allgather(param.data_ptr<float>(), reduced_grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+                            ptr_table<void* const*>(shadow_ptrs), (int)world, lo, param.numel(), (float)lr, (float)beta1,
+                            (float)beta2, (float)eps, (float)weight_decay, (int)step, sumsq_parts.data_ptr<float>(),
+                            (float)clip_norm, cur_stream()),
+        "adamw_allgather");
+}
+
 int64_t kernel_status(const Tensor& like) { return status_word(like).item<int>(); }
 
 }  // namespace
@@ -353,4 +466,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_tn", &gemm_tn);
   m.def("attn_pullback_packed", &attn_pullback_packed);
   m.def("kernel_status", &kernel_status);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("peer_signal_all", &peer_signal_all);
+  m.def("interface_update_handoff", &interface_update_handoff);
+  m.def("wait_state", &wait_state);
+  m.def("affine_scan_peer", &affine_scan_peer);
+  m.def("grad_reduce_scatter_", &grad_reduce_scatter_);
+  m.def("exchange_scalar", &exchange_scalar);
+  m.def("adamw_allgather_", &adamw_allgather_);
 }

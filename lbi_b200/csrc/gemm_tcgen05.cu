@@ -4,8 +4,10 @@
 //   warp 0        TMA producer: 128 x 64 tile of A and BN x 64 tile of B per stage, 128-byte swizzle, 4-stage ring
 //   warp 1        allocates 512 TMEM columns (two BN-column accumulators) and issues tcgen05.mma (one elected lane):
 //                 four K = 16 instructions per stage, tcgen05.commit frees the stage, a last commit publishes the tile
-//   warps 2..5    epilogue: tcgen05.ld 32 lanes x 32 columns, convert, vector stores (bf16 / fp32 / fp32 atomic add);
-//                 runs one tile behind the MMA warp thanks to the double-buffered accumulator
+//   warps 2..5    epilogue: tcgen05.ld 32 lanes x 32 columns, convert, stage 128-byte rows in swizzled shared memory,
+//                 TMA store (or TMA reduce-add for fp32 accumulation / split-K) of 128 x 128-byte boxes; runs one tile
+//                 behind the MMA warp thanks to the double-buffered accumulator.  (Direct 16-byte stores from
+//                 registers made the epilogue, not the main loop, the limit for K <= 1024: about 10 us per tile.)
 // Each operand may be K-major (row-major [rows, K]) or MN-major (row-major [K, rows]); the latter is loaded as
 // 64-row panels through a 3-D tensor map, so dgrad (dY * W) and wgrad (dY^T * X) need no transposed copies.
 // Split-K (gridDim.y) spreads a long reduction over several CTAs that add into an fp32 C with vector atomics.
@@ -31,10 +33,8 @@ constexpr int UMMA_K = 16;
 
 struct Params {
   int M, N, K;
-  int64_t ldc;
-  void* C;
   int out_fp32;
-  int atomic_add;    // fp32 C: add with atomics instead of storing
+  int atomic_add;    // fp32 C: add to memory (TMA reduce) instead of storing
   int a_mn_major, b_mn_major;
   int k_blocks_per_split;
   int* status;
@@ -44,6 +44,7 @@ template <int BN>
 struct Smem {
   alignas(1024) uint8_t a[STAGES][BM * BK * 2];
   alignas(1024) uint8_t b[STAGES][BN * BK * 2];
+  alignas(1024) uint8_t cstage[2][BM * 128];   // epilogue staging: two boxes of 128 rows x 128 bytes
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
@@ -54,7 +55,8 @@ struct Smem {
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_c, const Params p) {
   extern __shared__ uint8_t raw_smem[];
   Smem<BN>& s = *reinterpret_cast<Smem<BN>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5;
@@ -81,6 +83,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     fence_barrier_init();
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
+    prefetch_tmap(&tmap_c);
   }
   if (warp == 1) tmem_alloc(&s.tmem_base, 512);
   fence_before_sync();
@@ -124,6 +127,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // K-major: one K = 16 slice is 32 bytes inside the 128-byte row; MN-major: 16 k-rows = two swizzle atoms
         const uint32_t a_lbo = p.a_mn_major ? 64 * BK * 2 : 16, a_kstep = p.a_mn_major ? 2048 : 32;
         const uint32_t b_lbo = p.b_mn_major ? 64 * BK * 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
+        const uint64_t a_desc0 = make_smem_desc(smem_u32(s.a[0]), a_lbo, 1024);
+        const uint64_t b_desc0 = make_smem_desc(smem_u32(s.b[0]), b_lbo, 1024);
         int stage = 0;
         uint32_t phase = 0;
         int local_tile = 0;
@@ -139,14 +144,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             ok = mbar_wait(&s.full[stage], phase, &s.abort_flag, p.status, 3);
             if (!ok) break;
             fence_after_sync();
-            const uint32_t a_addr = smem_u32(s.a[stage]);
-            const uint32_t b_addr = smem_u32(s.b[stage]);
+            // descriptor = constant template + (address >> 4); a K = 16 slice advances the address field only
+            const uint64_t da = a_desc0 + (uint64_t)(stage * ((BM * BK * 2) >> 4));
+            const uint64_t db = b_desc0 + (uint64_t)(stage * ((BN * BK * 2) >> 4));
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t da = make_smem_desc(a_addr + k * a_kstep, a_lbo, 1024);
-              const uint64_t db = make_smem_desc(b_addr + k * b_kstep, b_lbo, 1024);
-              mma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              mma_bf16(d_tmem, da + k * (a_kstep >> 4), db + k * (b_kstep >> 4), idesc, (kb | k) != 0 ? 1u : 0u);
             mma_commit(&s.empty[stage]);
             if (++stage == STAGES) {
               stage = 0;
@@ -159,7 +162,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     } else {
       // ------------------------------------------------------------------ epilogue (warps 2..5)
       const int quarter = warp & 3;  // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
-      int local_tile = 0;
+      const int row = quarter * 32 + lane;
+      const bool leader = (warp == 2 && lane == 0);
+      constexpr int COLS_PER_BOX_BF16 = 64, COLS_PER_BOX_F32 = 32;
+      const int cols_per_box = p.out_fp32 ? COLS_PER_BOX_F32 : COLS_PER_BOX_BF16;
+      const int boxes = BN / cols_per_box;
+      int local_tile = 0, box_count = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
         const int buf = local_tile & 1;
@@ -170,64 +178,61 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after_sync();
-        const int row = m0 + quarter * 32 + lane;
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c0, r);
-          tmem_ld_wait();
-          const int col = n0 + c0;
-          if (row < p.M && col < p.N) {
-            const int ncols = min(32, p.N - col);
-            if (p.out_fp32) {
-              float* dst = reinterpret_cast<float*>(p.C) + (int64_t)row * p.ldc + col;
-              if (ncols == 32 && p.atomic_add) {
+        for (int bx = 0; bx < boxes; ++bx, ++box_count) {
+          const int half = box_count & 1;
+          const uint32_t stage_row = smem_u32(s.cstage[half]) + row * 128;
+          // the TMA store issued two boxes ago must have finished reading this staging half
+          if (leader) tma_store_wait_read<1>();
+          named_barrier_sync(1, 128);
+          if (p.out_fp32) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + bx * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  atomicAdd(reinterpret_cast<float4*>(dst) + i,
-                            make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                        __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3])));
-              } else if (ncols == 32) {
+            for (int j = 0; j < 8; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((j ^ (row & 7)) << 4)), "r"(r[4 * j]),
+                           "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
+                           : "memory");
+          } else {
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  reinterpret_cast<float4*>(dst)[i] =
-                      make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                  __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-              } else {
-                for (int i = 0; i < ncols; ++i) {
-                  if (p.atomic_add)
-                    atomicAdd(dst + i, __uint_as_float(r[i]));
-                  else
-                    dst[i] = __uint_as_float(r[i]);
+            for (int hh = 0; hh < 2; ++hh) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_row + bx * 64 + hh * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+                  w[e] = *reinterpret_cast<uint32_t*>(&t2);
                 }
-              }
-            } else {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (int64_t)row * p.ldc + col;
-              if (ncols == 32) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  uint4 v;
-                  __nv_bfloat162 t0 = __floats2bfloat162_rn(__uint_as_float(r[8 * i]), __uint_as_float(r[8 * i + 1]));
-                  __nv_bfloat162 t1 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-                  __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-                  __nv_bfloat162 t3 = __floats2bfloat162_rn(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-                  v.x = *reinterpret_cast<uint32_t*>(&t0);
-                  v.y = *reinterpret_cast<uint32_t*>(&t1);
-                  v.z = *reinterpret_cast<uint32_t*>(&t2);
-                  v.w = *reinterpret_cast<uint32_t*>(&t3);
-                  reinterpret_cast<uint4*>(dst)[i] = v;
-                }
-              } else {
-                for (int i = 0; i < ncols; ++i) dst[i] = __float2bfloat16(__uint_as_float(r[i]));
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((hh * 4 + j) ^ (row & 7)) << 4)),
+                             "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                             : "memory");
               }
             }
           }
+          if (bx == boxes - 1) {  // accumulator fully read: hand the TMEM buffer back to the MMA warp
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s.tmem_empty[buf]);
+          }
+          fence_proxy_async();
+          named_barrier_sync(1, 128);
+          if (leader) {
+            const int x = n0 + bx * cols_per_box;
+            if (x < p.N && m0 < p.M) {
+              if (p.atomic_add) tma_reduce_add_2d(&tmap_c, s.cstage[half], x, m0);
+              else tma_store_2d(&tmap_c, s.cstage[half], x, m0);
+            }
+            tma_store_commit();
+          }
         }
-        fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&s.tmem_empty[buf]);
       }
+      if (leader) tma_store_wait_all<0>();
     }
   }
 
@@ -292,20 +297,37 @@ static int make_operand_map(CUtensorMap* map, const void* ptr, int64_t rows, int
   return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
 }
 
+// Output map: boxes of 128 rows x 128 bytes (64 bf16 or 32 fp32 columns), 128-byte swizzle like the staging buffer.
+static int make_output_map(CUtensorMap* map, void* ptr, int64_t rows, int64_t cols, int64_t ld, int out_fp32) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return 801;
+  const int esize = out_fp32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esize};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esize), (cuuint32_t)BM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = fn(map, out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
+}
+
 template <int BN>
 static int launch(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                   int a_mn, int b_mn, int out_fp32, int accumulate, int splits, int* status, int max_ctas,
                   cudaStream_t st) {
-  CUtensorMap ma, mb;
+  CUtensorMap ma, mb, mc;
   int rc = make_operand_map(&ma, A, M, K, lda, a_mn, BM);
   if (rc) return rc;
   rc = make_operand_map(&mb, B, N, K, ldb, b_mn, BN);
+  if (rc) return rc;
+  rc = make_output_map(&mc, C, M, N, ldc, out_fp32);
   if (rc) return rc;
   const int k_blocks = (K + BK - 1) / BK;
   if (splits < 1) splits = 1;
   if (splits > k_blocks) splits = k_blocks > 0 ? k_blocks : 1;
   Params p;
-  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C; p.out_fp32 = out_fp32;
+  p.M = M; p.N = N; p.K = K; p.out_fp32 = out_fp32;
   p.atomic_add = (accumulate || splits > 1) ? 1 : 0;
   p.a_mn_major = a_mn; p.b_mn_major = b_mn;
   p.k_blocks_per_split = (k_blocks + splits - 1) / splits;
@@ -322,7 +344,7 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
     configured = true;
   }
   dim3 grid(ctas, splits);
-  gemm_kernel<BN><<<grid, THREADS, smem, st>>>(ma, mb, p);
+  gemm_kernel<BN><<<grid, THREADS, smem, st>>>(ma, mb, mc, p);
   return (int)cudaGetLastError();
 }
 

@@ -82,6 +82,8 @@ class FastLBIEngine:
         self.my_regions = list(self.placement.regions_of(self.comm.rank))
         self.flat = FlatParams(model, world_size=self.comm.world_size,
                                shadow_dtype=self.act_dtype if self.act_dtype != torch.float32 else None)
+        if hasattr(self.comm, "attach_flat"):
+            self.comm.attach_flat(self.flat)  # gradients and bf16 weights move into symmetric (peer-mapped) memory
         lo = self.comm.rank * self.flat.shard
         self.flat.ensure_state(lo, lo + self.flat.shard)
         self.structured = backend.structured
@@ -134,6 +136,9 @@ class FastLBIEngine:
         if not sequence_axis:
             full_canvas = ops.embedding_fwd(ids, table, self.act_dtype)
 
+        fused_iface = hasattr(comm, "interface_update_handoff") and self.device.type == "cuda"
+        if hasattr(comm, "prepare"):
+            comm.prepare(bsz, model.interface_width)
         first = self.my_regions[0]
         if first == 0:
             if sequence_axis:
@@ -171,12 +176,19 @@ class FastLBIEngine:
                 pooled = ops.mean_pool_tokens(cache.last_branch, bsz, t_len)
                 if cache.last_stream is not None:
                     pooled = pooled + ops.mean_pool_tokens(cache.last_stream, bsz, t_len)
-            step = iface.update_from_pooled(state, pooled, k)
-            rec.pooled, rec.diagnostics, rec.state_out = pooled, step.diagnostics, step.state.float()
+            remote = k + 1 < k_regions and self.placement.owner(k + 1) != comm.rank
+            if fused_iface:
+                # interface MLP + LayerNorm in one kernel whose epilogue stores the state into the next owner's mailbox
+                new_state, diagnostics = comm.interface_update_handoff(
+                    iface, k, state, pooled, self.placement.owner(k + 1) if remote else None)
+                rec.pooled, rec.diagnostics, rec.state_out = pooled, diagnostics, new_state
+            else:
+                step = iface.update_from_pooled(state, pooled, k)
+                rec.pooled, rec.diagnostics, rec.state_out = pooled, step.diagnostics, step.state.float()
+                if remote:
+                    comm.handoff_send(rec.state_out, self.placement.owner(k + 1), slot=k + 1)
             records.append(rec)
             state = rec.state_out
-            if k + 1 < k_regions and self.placement.owner(k + 1) != comm.rank:
-                comm.handoff_send(state, self.placement.owner(k + 1), slot=k + 1)
         return records, loss
 
     # ------------------------------------------------------------------ Jacobian + offset of one region
@@ -230,6 +242,9 @@ class FastLBIEngine:
             [j if j is not None else torch.zeros(bsz, r, r, dtype=torch.float32, device=self.device) for j in jacobians], dim=1
         )
         offs = torch.stack(offsets, dim=1)
+        if hasattr(comm, "scan") and self.device.type == "cuda":
+            self.last["jacobians"] = None
+            return comm.scan(mats, offs)  # peer-loaded matrices, recursion on every rank
         mats_all, offs_all = comm.gather_scan_inputs(mats, offs)  # [B, K, R, R], [B, K, R]
         self.last["jacobians"] = mats_all
         self.last["offsets"] = offs_all
@@ -290,6 +305,10 @@ class FastLBIEngine:
     @torch.no_grad()
     def _optimizer_step(self, lr: float) -> None:
         flat, comm = self.flat, self.comm
+        if hasattr(comm, "optimizer_step") and self.device.type == "cuda":
+            comm.optimizer_step(flat, lr=lr, betas=self.betas, eps=self.eps, weight_decay=self.weight_decay,
+                                grad_clip=self.grad_clip)
+            return
         shard = flat.shard
         lo = comm.rank * shard
         g_shard = comm.reduce_scatter_grads(flat.grads, shard) if comm.world_size > 1 else flat.grads
