@@ -175,7 +175,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int m0 = (tile / tiles_n) * BM;
         const int n0 = (tile % tiles_n) * BN;
         ok = mbar_wait(&s.tmem_full[buf], acc_phase, &s.abort_flag, p.status, 4);
-        ok = __all_sync(0xffffffffu, ok);
+        // all four warps take the same decision (they share named barrier 1 below): a raised abort flag wins
+        named_barrier_sync(1, 128);
+        ok = (s.abort_flag == 0);
         if (!ok) break;
         fence_after_sync();
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
@@ -196,17 +198,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                            "r"(r[4 * j + 1]), "r"(r[4 * j + 2]), "r"(r[4 * j + 3])
                            : "memory");
           } else {
+            uint32_t r[2][32];
+            tmem_ld_32x32(t_row + bx * 64, r[0]);
+            tmem_ld_32x32(t_row + bx * 64 + 32, r[1]);
+            tmem_ld_wait();
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-              uint32_t r[32];
-              tmem_ld_32x32(t_row + bx * 64 + hh * 32, r);
-              tmem_ld_wait();
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                  __nv_bfloat162 t2 = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * e]), __uint_as_float(r[8 * j + 2 * e + 1]));
+                  __nv_bfloat162 t2 =
+                      __floats2bfloat162_rn(__uint_as_float(r[hh][8 * j + 2 * e]), __uint_as_float(r[hh][8 * j + 2 * e + 1]));
                   w[e] = *reinterpret_cast<uint32_t*>(&t2);
                 }
                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((hh * 4 + j) ^ (row & 7)) << 4)),

@@ -1,0 +1,78 @@
+"""Interface-Jacobian diagnostics: spectral norm of the local region Jacobians over training, per state width.
+
+Reads runs logged with ``--log-interface-jacobian-every`` (columns ``jac_local_spec_mean/max``, ``jac_local_frob_*``,
+``jac_suffix_spec_*`` of ``metrics.csv``), groups them by ``message_dim``, averages over seeds and writes
+``jacobian_spec_mean_vs_tokens.{png,pdf}`` plus ``jacobian_final_summary.{csv,tex}``
+(reference scripts/plot_jacobian_diagnostics.py:271-287).
+"""
+from __future__ import annotations
+
+import argparse
+import re
+from collections import defaultdict
+from pathlib import Path
+from typing import Any
+
+from ._charts import Chart, mean_std, write_csv
+from .plot_training_curves import aggregate, discover_runs, read_metrics
+
+_FIELDS = ("jac_local_spec_mean", "jac_local_spec_max", "jac_local_frob_mean", "jac_local_frob_normed_mean",
+           "jac_suffix_spec_mean", "jac_suffix_spec_max")
+
+
+def _tex_number(v: float) -> str:
+    return "--" if v != v else f"{v:.3g}"
+
+
+def main(argv: list[str] | None = None) -> dict[str, Any]:
+    import json
+
+    p = argparse.ArgumentParser(description="Plot interface Jacobian diagnostics of one run family.")
+    p.add_argument("run_root", type=Path, help="Jacobian diagnostic family directory.")
+    p.add_argument("--output-dir", type=Path, default=None, help="default: <run_root>/jacobian_plots")
+    p.add_argument("--min-step", type=int, default=200, help="Minimum step to include in plots/tables.")
+    p.add_argument("--dpi", type=int, default=150, help="Output DPI for PNG figures.")
+    p.add_argument("--font-scale", type=float, default=1.0, help="Multiplier for paper font sizes.")
+    p.add_argument("--include-rank-regex", type=str, default="", help="Optional regex over rank strings, e.g. '^(16|32)$'.")
+    ns = p.parse_args(argv)
+    out_dir = ns.output_dir or (ns.run_root / "jacobian_plots")
+    by_rank: dict[int, list[dict]] = defaultdict(list)
+    for run in discover_runs([ns.run_root]):
+        cfg = json.loads((run / "config.json").read_text(encoding="utf-8"))
+        rank = int(cfg.get("message_dim", 0))
+        if ns.include_rank_regex and not re.search(ns.include_rank_regex, str(rank)):
+            continue
+        rows = [r for r in read_metrics(run) if (r.get("step") or 0) >= ns.min_step]
+        if any(r.get("jac_local_spec_mean") is not None for r in rows):
+            by_rank[rank].append({"dir": run, "cfg": cfg, "rows": rows})
+    if not by_rank:
+        raise SystemExit(f"no Jacobian diagnostic metrics found under {ns.run_root}")
+    chart = Chart("Local interface Jacobian spectral norm", "tokens seen", "mean spectral norm")
+    table: list[dict[str, Any]] = []
+    for rank, runs in sorted(by_rank.items()):
+        s = aggregate(runs, "train", "tokens_seen", "jac_local_spec_mean")
+        if s is not None:
+            s.label = f"R = {rank}"
+            chart.series.append(s)
+        row: dict[str, Any] = {"message_dim": rank, "num_runs": len(runs)}
+        for f in _FIELDS:
+            finals = []
+            for run in runs:
+                vals = [r[f] for r in run["rows"] if r["split"] == "train" and r.get(f) is not None]
+                if vals:
+                    finals.append(vals[-1])
+            row[f + "_mean"], row[f + "_std"] = mean_std(finals)
+        table.append(row)
+    files = chart.save(out_dir / "jacobian_spec_mean_vs_tokens", dpi=ns.dpi, font_scale=ns.font_scale, also_pdf=True)
+    write_csv(out_dir / "jacobian_final_summary.csv", table)
+    lines = [r"\begin{tabular}{r|c|c|c}", r"$R$ & local $\|J\|_2$ mean & local $\|J\|_2$ max & suffix $\|J\|_2$ max \\", r"\hline"]
+    for row in table:
+        lines.append(f"{row['message_dim']} & {_tex_number(row['jac_local_spec_mean_mean'])} & "
+                     f"{_tex_number(row['jac_local_spec_max_mean'])} & {_tex_number(row['jac_suffix_spec_max_mean'])} \\\\")
+    lines += [r"\end{tabular}", ""]
+    (out_dir / "jacobian_final_summary.tex").write_text("\n".join(lines), encoding="utf-8")
+    return {"output_dir": str(out_dir), "figures": [str(f) for f in files], "table": table}
+
+
+if __name__ == "__main__":
+    main()

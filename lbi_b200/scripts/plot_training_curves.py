@@ -1,0 +1,173 @@
+"""Training-curve figures and per-group summary tables from ``metrics.csv`` files.
+
+Runs are discovered below the given roots (any directory with ``metrics.csv`` + ``config.json``), grouped by label
+(``dense``, ``lbi r<R>`` ... with the seed stripped), averaged over seeds on the union of logged steps, and drawn as
+mean +- one standard deviation.  Outputs follow reference scripts/plot_training_curves.py:672-753:
+``ce_vs_tokens``, ``ce_vs_step``, ``paper_val_ce_vs_tokens``, ``paper_val_ce_vs_step``, ``paper_ce_vs_tokens``,
+``tokens_per_s_vs_step``, ``message_diagnostics``, ``val_summary_bar`` figures and ``group_summary.{csv,json}``.
+"""
+from __future__ import annotations
+
+import argparse
+import csv
+import json
+import math
+import re
+from collections import defaultdict
+from pathlib import Path
+from typing import Any
+
+from ._charts import Chart, Series, mean_std, moving_average, write_csv, write_json
+
+
+def discover_runs(roots: list[Path]) -> list[Path]:
+    found: list[Path] = []
+    for root in roots:
+        if (root / "metrics.csv").exists():
+            found.append(root)
+        found.extend(p.parent for p in sorted(root.rglob("metrics.csv")) if p.parent != root)
+    seen, out = set(), []
+    for p in found:
+        if p.resolve() not in seen and (p / "config.json").exists():
+            seen.add(p.resolve())
+            out.append(p)
+    return out
+
+
+def read_metrics(run_dir: Path) -> list[dict[str, Any]]:
+    rows = []
+    with (run_dir / "metrics.csv").open(newline="", encoding="utf-8") as fh:
+        for row in csv.DictReader(fh):
+            parsed: dict[str, Any] = {"split": row.get("split", "")}
+            for key, value in row.items():
+                if key == "split":
+                    continue
+                try:
+                    parsed[key] = float(value) if value not in ("", None) else None
+                except ValueError:
+                    parsed[key] = None
+            rows.append(parsed)
+    return rows
+
+
+def run_label(run_dir: Path, cfg: dict[str, Any], mode: str = "auto") -> str:
+    variant = run_dir.name
+    is_dense = variant in {"dense", "backprop_ref"}
+    if mode == "variant":
+        return re.sub(r"_seed\d+$", "", run_dir.parent.name) or variant
+    if is_dense:
+        return "dense"
+    label = f"lbi r{cfg.get('message_dim', '?')}"
+    if mode == "full":
+        label += f" rs{cfg.get('region_size', '?')}"
+    return label
+
+
+def load_groups(roots: list[Path], *, include: str = "", exclude: str = "", label_mode: str = "auto") -> dict[str, list[dict]]:
+    groups: dict[str, list[dict]] = defaultdict(list)
+    for run in discover_runs(roots):
+        name = run.parent.name + "/" + run.name
+        if include and not re.search(include, name):
+            continue
+        if exclude and re.search(exclude, name):
+            continue
+        cfg = json.loads((run / "config.json").read_text(encoding="utf-8"))
+        groups[run_label(run, cfg, label_mode)].append({"dir": run, "cfg": cfg, "rows": read_metrics(run)})
+    return dict(groups)
+
+
+def _curve(rows: list[dict], split: str, xkey: str, ykey: str) -> dict[float, float]:
+    return {r[xkey]: r[ykey] for r in rows if r["split"] == split and r.get(xkey) is not None and r.get(ykey) is not None}
+
+
+def aggregate(runs: list[dict], split: str, xkey: str, ykey: str, smooth: int = 1) -> Series | None:
+    curves = [_curve(r["rows"], split, xkey, ykey) for r in runs]
+    curves = [c for c in curves if c]
+    if not curves:
+        return None
+    xs = sorted(set().union(*[set(c) for c in curves]))
+    mean, band = [], []
+    for x in xs:
+        m, s = mean_std([c[x] for c in curves if x in c])
+        mean.append(m)
+        band.append(s if math.isfinite(s) else 0.0)
+    return Series("", xs, moving_average(mean, smooth), band if len(curves) > 1 else None)
+
+
+def summarize(groups: dict[str, list[dict]]) -> list[dict[str, Any]]:
+    out = []
+    for label, runs in sorted(groups.items()):
+        finals, bests, tps = [], [], []
+        for r in runs:
+            val = [x for x in r["rows"] if x["split"] == "val" and x.get("ce_loss") is not None]
+            train = [x for x in r["rows"] if x["split"] == "train" and x.get("tokens_per_s")]
+            if val:
+                finals.append(val[-1]["ce_loss"])
+                bests.append(min(x["ce_loss"] for x in val))
+            if train:
+                tps.append(sum(x["tokens_per_s"] for x in train) / len(train))
+        fm, fs = mean_std(finals)
+        bm, bs = mean_std(bests)
+        tm, _ = mean_std(tps)
+        out.append({"label": label, "num_runs": len(runs), "seeds": ",".join(str(r["cfg"].get("seed", "")) for r in runs),
+                    "final_val_ce_mean": fm, "final_val_ce_std": fs, "best_val_ce_mean": bm, "best_val_ce_std": bs,
+                    "mean_tokens_per_s": tm})
+    return out
+
+
+def make_figures(groups: dict[str, list[dict]], out_dir: Path, *, dpi: int, font_scale: float, smooth: int) -> list[Path]:
+    written: list[Path] = []
+
+    def figure(stem: str, title: str, xlabel: str, ylabel: str, parts: list[tuple[str, str, str, str, str]], logy=False) -> None:
+        chart = Chart(title, xlabel, ylabel, logy=logy)
+        for label, runs in sorted(groups.items()):
+            for split, xkey, ykey, suffix, style in parts:
+                s = aggregate(runs, split, xkey, ykey, smooth if split == "train" else 1)
+                if s is not None:
+                    s.label, s.style = f"{label}{suffix}", style
+                    chart.series.append(s)
+        if chart.series:
+            written.extend(chart.save(out_dir / stem, dpi=dpi, font_scale=font_scale))
+
+    both = lambda x: [("train", x, "ce_loss", " train", "--"), ("val", x, "ce_loss", " val", "-")]  # noqa: E731
+    figure("ce_vs_tokens", "Cross-entropy vs tokens", "tokens seen", "CE loss", both("tokens_seen"))
+    figure("ce_vs_step", "Cross-entropy vs step", "step", "CE loss", both("step"))
+    figure("paper_val_ce_vs_tokens", "Validation cross-entropy", "tokens seen", "val CE", [("val", "tokens_seen", "ce_loss", "", "-")])
+    figure("paper_val_ce_vs_step", "Validation cross-entropy", "step", "val CE", [("val", "step", "ce_loss", "", "-")])
+    figure("paper_ce_vs_tokens", "Training cross-entropy", "tokens seen", "train CE", [("train", "tokens_seen", "ce_loss", "", "-")])
+    figure("tokens_per_s_vs_step", "Throughput", "step", "tokens / s", [("train", "step", "tokens_per_s", "", "-")])
+    figure("message_diagnostics", "Interface state norm and scan alignment", "step", "value",
+           [("train", "step", "message_norm", " |s|", "-"), ("train", "step", "scan_align", " scan align", "--")])
+    summary = summarize(groups)
+    bars = [(r["label"], r["final_val_ce_mean"], 0.0 if not math.isfinite(r["final_val_ce_std"]) else r["final_val_ce_std"])
+            for r in summary if math.isfinite(r["final_val_ce_mean"])]
+    if bars:
+        written.extend(Chart("Final validation cross-entropy", "", "val CE", bars=bars).save(out_dir / "val_summary_bar", dpi=dpi,
+                                                                                              font_scale=font_scale))
+    return written
+
+
+def main(argv: list[str] | None = None) -> dict[str, Any]:
+    p = argparse.ArgumentParser(description="Plot training curves of one or more run roots.")
+    p.add_argument("run_roots", nargs="+", type=Path, help="Run roots or per-regime run directories.")
+    p.add_argument("--output-dir", type=Path, default=None, help="default: <first root>/plots")
+    p.add_argument("--include-variant-regex", type=str, default="")
+    p.add_argument("--exclude-variant-regex", type=str, default="")
+    p.add_argument("--label-mode", choices=("auto", "full", "variant"), default="auto")
+    p.add_argument("--smooth-window", type=int, default=1, help="moving-average window for training curves")
+    p.add_argument("--dpi", type=int, default=150)
+    p.add_argument("--font-scale", type=float, default=1.0)
+    ns = p.parse_args(argv)
+    out_dir = ns.output_dir or (ns.run_roots[0] / "plots")
+    groups = load_groups(ns.run_roots, include=ns.include_variant_regex, exclude=ns.exclude_variant_regex, label_mode=ns.label_mode)
+    if not groups:
+        raise SystemExit("no runs with metrics.csv found")
+    summary = summarize(groups)
+    write_csv(out_dir / "group_summary.csv", summary)
+    write_json(out_dir / "group_summary.json", summary)
+    files = make_figures(groups, out_dir, dpi=ns.dpi, font_scale=ns.font_scale, smooth=ns.smooth_window)
+    return {"output_dir": str(out_dir), "figures": [str(f) for f in files], "groups": summary}
+
+
+if __name__ == "__main__":
+    main()

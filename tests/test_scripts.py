@@ -1,0 +1,97 @@
+"""Paper tooling on the CPU: launcher presets, post-hoc evaluation, figures/tables from metrics, grad-parity report."""
+import csv
+import json
+from pathlib import Path
+
+import pytest
+
+from lbi_b200.scripts import (evaluate_paper_checkpoints, generate_grad_parity_report, paper_presets, plot_jacobian_diagnostics,
+                              plot_message_ablations, plot_training_curves)
+from lbi_b200.train.config import LBITrainingConfig, build_arg_parser, config_from_args
+from lbi_b200.train.lbi import run_lbi_experiment
+
+
+def _train(family: Path, run_name: str, variants: str, seed: int, message_dim: int = 4, **kw):
+    cfg = LBITrainingConfig(
+        variants=variants, backbone="transformer", device="cpu", dtype="float32", output_dir=str(family), run_name=run_name,
+        task="copy", vocab_size=32, seq_len=16, train_sequences=32, val_sequences=8, batch_size=2, steps=3, eval_every=1,
+        eval_batches=1, log_every=1, save_every=1, layers=2, dim=16, n_heads=2, region_size=1, message_dim=message_dim,
+        message_hidden_dim=8, seed=seed, **kw)
+    return run_lbi_experiment(cfg)
+
+
+@pytest.fixture(scope="module")
+def family(tmp_path_factory):
+    root = tmp_path_factory.mktemp("family")
+    _train(root, "dense_seed7", "dense", 7)
+    for seed in (7, 8):
+        _train(root, f"lbi_r4_seed{seed}", "lbi", seed, eval_all_message_ablations=True, log_interface_jacobian_every=1,
+               log_interface_jacobian_suffix=True)
+    return root
+
+
+@pytest.mark.parametrize("kind,backbone,dim", [("lbi", "transformer", 64), ("lbi", "hybrid", 32), ("dense", "mamba2", 16),
+                                               ("lbi", "mamba3", 16)])
+def test_launcher_commands_parse_with_the_training_cli(monkeypatch, kind, backbone, dim):
+    monkeypatch.setenv("BACKBONE", backbone)
+    monkeypatch.setenv("MESSAGE_DIM", str(dim))
+    monkeypatch.setenv("TOKENIZER_PATH", "/tmp/tok")
+    cmd = paper_presets.build_command(kind)
+    assert cmd[1:3] == ["-m", "lbi_b200.train.lbi"]
+    cfg = config_from_args(build_arg_parser().parse_args(cmd[3:]))
+    arch = paper_presets.ARCHITECTURES[("canonical", backbone)]
+    assert (cfg.layers, cfg.dim, cfg.backbone) == (arch.layers, arch.dim, backbone)
+    assert cfg.seq_len == 1024 and cfg.batch_size == 1 and cfg.steps == 20000 and cfg.tie_embeddings
+    if kind == "lbi":
+        assert cfg.message_dim == dim and cfg.region_size == 2 and cfg.interface_jacobian_mode == "recompute"
+        assert cfg.jacobian_basis_chunk == 32 and cfg.message_hidden_dim == arch.dim
+        assert cfg.lr_model == paper_presets.lbi_learning_rate(backbone, dim)
+    else:
+        assert cfg.lr_model == paper_presets.DENSE_RECIPE[backbone][0]
+
+
+def test_posthoc_evaluation_writes_summary(family, tmp_path):
+    rows = evaluate_paper_checkpoints.main([str(family), "--output-dir", str(tmp_path / "ev"), "--eval-batches", "2",
+                                            "--checkpoint", "latest", "--device", "cpu"])
+    assert [r["label"] for r in rows] == ["dense_seed7", "lbi_r4_seed7", "lbi_r4_seed8"]
+    stored = json.loads((tmp_path / "ev" / "lm_eval_summary.json").read_text())
+    assert len(stored) == 3 and all(r["posthoc_val_ce_loss"] > 0 and r["eval_tokens"] == 2 * 2 * 16 for r in stored)
+    assert all(r["posthoc_val_ppl"] == pytest.approx(2.718281828 ** r["posthoc_val_ce_loss"], rel=1e-4) for r in stored)
+    with (tmp_path / "ev" / "lm_eval_summary.csv").open() as fh:
+        assert len(list(csv.DictReader(fh))) == 3
+
+
+def test_training_curve_outputs(family, tmp_path):
+    out = plot_training_curves.main([str(family), "--output-dir", str(tmp_path / "plots")])
+    names = {Path(f).stem for f in out["figures"]}
+    assert {"ce_vs_tokens", "ce_vs_step", "paper_val_ce_vs_tokens", "paper_val_ce_vs_step", "paper_ce_vs_tokens",
+            "tokens_per_s_vs_step", "message_diagnostics", "val_summary_bar"} <= names
+    groups = {g["label"]: g for g in json.loads((tmp_path / "plots" / "group_summary.json").read_text())}
+    assert groups["lbi r4"]["num_runs"] == 2 and groups["dense"]["num_runs"] == 1
+    assert (tmp_path / "plots" / "group_summary.csv").exists()
+
+
+def test_ablation_and_jacobian_outputs(family, tmp_path):
+    out = plot_message_ablations.main([str(family), "--output-dir", str(tmp_path / "abl")])
+    stems = {Path(f).stem for f in out["figures"]}
+    assert {"transformer_ablation_ce_vs_tokens", "transformer_ablation_final_ce"} <= stems
+    with (tmp_path / "abl" / "ablation_summary.csv").open() as fh:
+        splits = {r["split"] for r in csv.DictReader(fh)}
+    assert {"val", "val_zero_all", "val_noise", "val_mask"} <= splits
+    out = plot_jacobian_diagnostics.main([str(family), "--output-dir", str(tmp_path / "jac"), "--min-step", "1"])
+    assert out["table"][0]["message_dim"] == 4 and out["table"][0]["num_runs"] == 2
+    assert (tmp_path / "jac" / "jacobian_final_summary.csv").exists() and (tmp_path / "jac" / "jacobian_final_summary.tex").exists()
+    assert any(Path(f).stem == "jacobian_spec_mean_vs_tokens" for f in out["figures"])
+
+
+def test_grad_parity_report(tmp_path):
+    rows = generate_grad_parity_report.generate_report(
+        output_dir=tmp_path, case_names=["transformer_multi_region", "mamba2_multi_region", "transformer_multi_region_cuda_bf16"],
+        preset="test", plot=True, interface_jacobian_mode="recompute", jacobian_basis_chunk=3)
+    by_name = {r["case_name"]: r for r in rows}
+    assert by_name["transformer_multi_region"]["status"] == "ok" and by_name["transformer_multi_region"]["num_trials_passed"] == 1
+    for name in ("case_summary.csv", "case_summary.json", "case_summary.md", "trial_summary.csv", "per_parameter.csv",
+                 "report_config.json", "summary.csv", "summary.json", "summary.md", "paper_table.csv", "paper_table.tex"):
+        assert (tmp_path / name).exists(), name
+    assert "Transformer" in (tmp_path / "paper_table.tex").read_text()
+    assert generate_grad_parity_report.latex_number(1.5e-9) == r"$1.50\times 10^{-9}$"
