@@ -19,6 +19,11 @@ int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const flo
                       int batch, int heads, int seq_len, int head_dim, int nbasis, float scale, int* status,
                       cudaStream_t stream);
 
+// Causal flash-attention forward (attn_fwd.cu), same layout and limits as above:
+//   out bf16 [B*T, H*64], lse fp32 [B, H, T].  One kernel on `stream`.
+int lbi_attn_fwd(const void* qkv, void* out, float* lse, int batch, int heads, int seq_len, int head_dim, float scale,
+                 int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

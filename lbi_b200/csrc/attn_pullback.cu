@@ -27,9 +27,11 @@
 // MMAs of job n - 2 (which need the dS tile the compute warps wrote) at the same moment, so the tensor core always has
 // the next product queued while the compute warps turn the previous one into P or dS.  dS tiles are double-buffered
 // in shared memory; P stays in registers (and, for DKDV, in shared memory as an MMA operand).
-// Warp roles (320 threads): warps 0-7 compute (TMEM lane quarter = warp % 4, key-column half = warp / 4);
-// warp 8 lane 0 issues the TMA loads and the S / dP products; warp 9 lane 0 issues the accumulating products and
-// releases shared-memory stages.  Two issuing threads because a single thread's instruction stream (descriptor
+// Warp roles (608 threads): warps 0-15 compute (TMEM lane quarter = warp % 4, 32-column slice = warp / 4); warp 16
+// lane 0 issues the S / dP products; warp 17 lane 0 issues the accumulating products and releases shared-memory
+// stages; warp 18 lane 0 is the TMA producer.  A job is only four (S, dP) or eight (accumulate) tcgen05.mma, about 256
+// tensor-core cycles, so the issuing threads' own instruction streams set the pace: they carry no integer division,
+// no polling and no TMA issue (phase timing showed one thread doing all three spent half its time in them).  Two issuing threads because a single thread's instruction stream (descriptor
 // arithmetic + about twenty tcgen05.mma per job) was measured to be the bottleneck.  Every mbarrier wait is bounded
 // (tcgen05.cuh); all barrier parities are derived from job / tile counters.
 #include <cuda_bf16.h>
@@ -48,7 +50,9 @@ constexpr int TILE = 128;       // query rows and key rows per tile
 constexpr int DH = 64;          // head dimension handled by this build
 constexpr int TILE_BYTES = TILE * DH * 2;   // 16 KB
 constexpr int PANEL_BYTES = TILE * 128;     // one 64-column panel of P / dS: 128 rows x 128 B
-constexpr int THREADS = 320;
+constexpr int THREADS = 608;          // 16 compute warps + 2 MMA-issuing warps + 1 TMA warp
+constexpr int NCOMPUTE_WARPS = 16;     // barrier arrivals are per warp: 512 same-address arrivals per job congested the
+                                      // shared-memory pipe that the MMA issue also goes through
 constexpr int PB_DKDV = 2;
 constexpr int PB_DQ = 4;
 constexpr int NDO = 4;          // dO stages in DKDV mode
@@ -77,7 +81,7 @@ struct Smem {
   uint64_t bar_stream_full[NSTREAM];
   uint64_t bar_stream_empty[NSTREAM];
   uint64_t bar_ready[2];          // job result in TMEM buffer (commit)
-  uint64_t bar_consumed[2];       // compute warps are done with the TMEM buffer: 256 arrivals (read by the S/dP issuer)
+  uint64_t bar_consumed[2];       // compute warps are done with the TMEM buffer: one arrival per warp (read by the S/dP issuer)
   uint64_t bar_written[4];        // same event for the accumulate issuer (P / dS are in shared memory), 4 slots deep
   uint64_t bar_ds_free[2];        // the MMA that read this dS buffer has finished (commit)
   uint64_t bar_p_free;            // the MMAs that read P have finished (commit)
@@ -114,6 +118,28 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 
 
+// Optional phase timing (build with -DLBI_ATTN_TIMING): cycles spent per role and phase, summed over CTAs.
+//   [kernel: 0 = dQ, 1 = dK/dV][role: 0 = TMA producer, 1 = issuer X, 2 = issuer Y, 3 = compute thread 0][slot]; slot 7 = total.
+#ifdef LBI_ATTN_TIMING
+__device__ unsigned long long g_attn_timing[2][4][8];
+#define TIMED(slot, ...)              \
+  {                                   \
+    const long long _t0 = clock64();  \
+    __VA_ARGS__;                      \
+    tacc[slot] += clock64() - _t0;    \
+  }
+#define TIMING_BEGIN() long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long _tstart = clock64();
+#define TIMING_END(role)                                                                                   \
+  {                                                                                                        \
+    tacc[7] = clock64() - _tstart;                                                                         \
+    for (int _i = 0; _i < 8; ++_i) atomicAdd(&g_attn_timing[DKDV ? 1 : 0][role][_i], (unsigned long long)tacc[_i]); \
+  }
+#else
+#define TIMED(slot, ...) __VA_ARGS__;
+#define TIMING_BEGIN()
+#define TIMING_END(role)
+#endif
+
 template <bool DKDV>
 __global__ void __launch_bounds__(THREADS, 1)
 pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const Params p) {
@@ -147,17 +173,17 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s.bar_ready[i], 1);
-      mbar_init(&s.bar_consumed[i], 256);
+      mbar_init(&s.bar_consumed[i], NCOMPUTE_WARPS);
       mbar_init(&s.bar_ds_free[i], 1);
     }
-    for (int i = 0; i < 4; ++i) mbar_init(&s.bar_written[i], 256);
+    for (int i = 0; i < 4; ++i) mbar_init(&s.bar_written[i], NCOMPUTE_WARPS);
     mbar_init(&s.bar_p_free, 1);
     mbar_init(&s.bar_acc_done, 1);
     fence_barrier_init();
     prefetch_tmap(&map_qkv);
     prefetch_tmap(&map_do);
   }
-  if (warp == 8) tmem_alloc(&s.tmem_base, 512);
+  if (warp == 16) tmem_alloc(&s.tmem_base, 512);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
@@ -170,48 +196,16 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   const uint32_t stream0 = smem_u32(s.stream[0]) >> 4, fixed0 = smem_u32(s.fixed[0]) >> 4;
   constexpr uint32_t TILE16 = TILE_BYTES >> 4;
 
-  if (warp == 8) {
-    // ======================================================================== issuer X: TMA loads, S and dP products
+  if (warp == 18) {
+    // ======================================================================== TMA producer
+    // Streams the tiles of up to two steps ahead.  All waits are blocking here: this thread has nothing else to do,
+    // and everything a stage release depends on was loaded earlier in this same order, so the waits cannot cycle.
     if (lane == 0) {
-      const uint32_t idesc_nn = make_idesc_bf16(128, 128, 0, 0);
+      TIMING_BEGIN();
       bool ok = true;
-      int next_main = 0, main_waited = 0, next_do = 0, do_waited = 0, v_waited = 0;
-      const int total_do = DKDV ? n_iter * np : 0;
       auto load_tile = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int col, int64_t row) {
         mbar_arrive_expect_tx(bar, TILE_BYTES);
         tma_load_2d(dst, m, bar, col, (int)row);
-      };
-      // Load further streamed tiles while their stage is free.  Non-blocking unless a tile up to need_* is required.
-      auto refill = [&](int need_main, int need_do) {
-        while (ok && next_main < n_iter) {
-          const int st = next_main & 1;
-          if (next_main >= 2) {
-            const uint32_t par = ((next_main >> 1) - 1) & 1;
-            if (next_main <= need_main) ok = mbar_wait(&s.bar_stream_empty[st], par, abortp, p.status, 11);
-            else if (!mbar_try_wait(&s.bar_stream_empty[st], par)) break;
-            if (!ok) break;
-          }
-          if (DKDV) {
-            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_q, row_b + (own + next_main) * TILE);
-          } else {
-            load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_k, row_b + next_main * TILE);
-            load_tile(s.stream[2 + st], &map_qkv, &s.bar_stream_full[2 + st], col_v, row_b + next_main * TILE);
-          }
-          ++next_main;
-        }
-        while (DKDV && ok && next_do < total_do) {
-          const int st = 2 + next_do % NDO;
-          if (next_do >= NDO) {
-            const uint32_t par = ((next_do / NDO) - 1) & 1;
-            if (next_do <= need_do) ok = mbar_wait(&s.bar_stream_empty[st], par, abortp, p.status, 12);
-            else if (!mbar_try_wait(&s.bar_stream_empty[st], par)) break;
-            if (!ok) break;
-          }
-          const int it = next_do / np, pp = next_do % np;
-          load_tile(s.stream[st], &map_do, &s.bar_stream_full[st], h * DH,
-                    (int64_t)(p0 + pp) * p.n_rows + row_b + (own + it) * TILE);
-          ++next_do;
-        }
       };
       if (DKDV) {
         mbar_arrive_expect_tx(&s.bar_fixed, 2 * TILE_BYTES);
@@ -224,38 +218,56 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           tma_load_2d(s.fixed[1 + pp], &map_do, &s.bar_fixed, h * DH,
                       (int)((int64_t)(p0 + pp) * p.n_rows + row_b + own * TILE));
       }
-      refill(-1, -1);
-      ok = ok && mbar_wait(&s.bar_fixed, 0, abortp, p.status, 16);
-
+      int c = 0;  // running index of dO tiles (DKDV)
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it & 1;
+        if (it >= 2) {
+          TIMED(0, ok = mbar_wait(&s.bar_stream_empty[st], ((it >> 1) - 1) & 1, abortp, p.status, 11));
+          if (!ok) break;
+        }
+        if (DKDV) {
+          load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_q, row_b + (own + it) * TILE);
+          for (int pp = 0; pp < np && ok; ++pp, ++c) {
+            const int ds = 2 + (c & (NDO - 1));
+            if (c >= NDO) {
+              TIMED(1, ok = mbar_wait(&s.bar_stream_empty[ds], ((c / NDO) - 1) & 1, abortp, p.status, 12));
+              if (!ok) break;
+            }
+            load_tile(s.stream[ds], &map_do, &s.bar_stream_full[ds], h * DH,
+                      (int64_t)(p0 + pp) * p.n_rows + row_b + (own + it) * TILE);
+          }
+        } else {
+          load_tile(s.stream[st], &map_qkv, &s.bar_stream_full[st], col_k, row_b + it * TILE);
+          load_tile(s.stream[2 + st], &map_qkv, &s.bar_stream_full[2 + st], col_v, row_b + it * TILE);
+        }
+      }
+      TIMING_END(0);
+    }
+  } else if (warp == 16) {
+    // ======================================================================== issuer X: S and dP products
+    if (lane == 0) {
+      const uint32_t idesc_nn = make_idesc_bf16(128, 128, 0, 0);
+      TIMING_BEGIN();
+      bool ok = true;
+      TIMED(2, ok = mbar_wait(&s.bar_fixed, 0, abortp, p.status, 16));
+      int it = 0, r = 0, c = 0;   // step, job within the step (0 = S, 1.. = dP of direction r - 1), dO tile index
       for (int n = 0; n < total_jobs && ok; ++n) {
-        const int it = n / jobs_per_iter, r = n % jobs_per_iter;
         if (n >= 2) {
-          ok = mbar_wait(&s.bar_consumed[n & 1], ((n - 2) >> 1) & 1, abortp, p.status, 17);
+          TIMED(0, ok = mbar_wait(&s.bar_consumed[n & 1], ((n - 2) >> 1) & 1, abortp, p.status, 17));
           if (!ok) break;
         }
         uint32_t a16, b16;  // operand tile addresses >> 4
         if (r == 0) {
-          refill(it, -1);
-          while (ok && main_waited <= it) {
-            ok = mbar_wait(&s.bar_stream_full[main_waited & 1], (main_waited >> 1) & 1, abortp, p.status, 13);
-            ++main_waited;
-          }
+          TIMED(1, ok = mbar_wait(&s.bar_stream_full[it & 1], (it >> 1) & 1, abortp, p.status, 13));
           a16 = DKDV ? stream0 + (it & 1) * TILE16 : fixed0;
           b16 = DKDV ? fixed0 : stream0 + (it & 1) * TILE16;
         } else if (DKDV) {
-          const int c = it * np + (r - 1);
-          refill(-1, c);
-          while (ok && do_waited <= c) {
-            ok = mbar_wait(&s.bar_stream_full[2 + do_waited % NDO], (do_waited / NDO) & 1, abortp, p.status, 15);
-            ++do_waited;
-          }
-          a16 = stream0 + (2 + c % NDO) * TILE16;
+          TIMED(1, ok = mbar_wait(&s.bar_stream_full[2 + (c & (NDO - 1))], (c / NDO) & 1, abortp, p.status, 15));
+          a16 = stream0 + (2 + (c & (NDO - 1))) * TILE16;
           b16 = fixed0 + TILE16;
+          ++c;
         } else {
-          while (ok && v_waited <= it) {
-            ok = mbar_wait(&s.bar_stream_full[2 + (v_waited & 1)], (v_waited >> 1) & 1, abortp, p.status, 14);
-            ++v_waited;
-          }
+          if (r == 1) TIMED(1, ok = mbar_wait(&s.bar_stream_full[2 + (it & 1)], (it >> 1) & 1, abortp, p.status, 14))
           a16 = fixed0 + r * TILE16;
           b16 = stream0 + (2 + (it & 1)) * TILE16;
         }
@@ -263,37 +275,45 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         fence_after_sync();
         const uint32_t d_tmem = tmem + (n & 1) * 128;
         const uint64_t da = kmajor0 + a16, db = kmajor0 + b16;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc_nn, k);
-        mma_commit(&s.bar_ready[n & 1]);
-        refill(-1, -1);
+        TIMED(4, _Pragma("unroll") for (int k = 0; k < 4; ++k) mma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc_nn, k));
+        TIMED(5, mma_commit(&s.bar_ready[n & 1]));
+        if (++r == jobs_per_iter) {
+          r = 0;
+          ++it;
+        }
       }
+      TIMING_END(1);
     }
-  } else if (warp == 9) {
+  } else if (warp == 17) {
     // ======================================================================== issuer Y: accumulating products, releases
     if (lane == 0) {
       const uint32_t idesc_acc = DKDV ? make_idesc_bf16(128, 64, 1, 1) : make_idesc_bf16(128, 64, 0, 1);
       const uint32_t idesc_dv2 = make_idesc_bf16(128, 128, 1, 1);  // dV of two directions in one instruction
       const uint32_t ds0 = smem_u32(s.ds_tile[0][0]) >> 4, p16 = smem_u32(s.p_tile[0]) >> 4;
       constexpr uint32_t DSBUF16 = (2 * PANEL_BYTES) >> 4, PANEL16 = PANEL_BYTES >> 4;
+      TIMING_BEGIN();
       bool ok = true;
       int do_waited = 0;
+      int it = 0, r = -1, c0 = 0;   // step, job within the step, index of the step's first dO tile
       for (int m = 0; m < total_jobs && ok; ++m) {
-        const int it = m / jobs_per_iter, r = m % jobs_per_iter;
-        ok = mbar_wait(&s.bar_written[m & 3], (m >> 2) & 1, abortp, p.status, 18);
+        if (++r == jobs_per_iter) {
+          r = 0;
+          ++it;
+          c0 += np;
+        }
+        TIMED(0, ok = mbar_wait(&s.bar_written[m & 3], (m >> 2) & 1, abortp, p.status, 18));
         if (!ok) break;
         fence_after_sync();
         const uint32_t first = it != 0;  // accumulate onto earlier steps?
         if (r == 0) {
           if (DKDV) {  // P_it is in shared memory: dV_p += P^T dO_p for the directions of this step
-            const int c0 = it * np;
             while (ok && do_waited <= c0 + np - 1) {
-              ok = mbar_wait(&s.bar_stream_full[2 + do_waited % NDO], (do_waited / NDO) & 1, abortp, p.status, 19);
+              TIMED(1, ok = mbar_wait(&s.bar_stream_full[2 + (do_waited & (NDO - 1))], (do_waited / NDO) & 1, abortp, p.status, 19));
               ++do_waited;
             }
             if (!ok) break;
             const uint64_t da = mnmajor0 + p16;
-            const uint64_t db = mnmajor0 + stream0 + (2 + c0 % NDO) * TILE16;
+            const uint64_t db = mnmajor0 + stream0 + (2 + (c0 & (NDO - 1))) * TILE16;
             if (np == 2) {  // the two dO tiles are adjacent stages: one N = 128 operand with two 64-wide panels
 #pragma unroll
               for (int k = 0; k < 8; ++k) mma_bf16(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
@@ -305,7 +325,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           }
           continue;
         }
-        const int pp = r - 1, d = it * np + pp, buf = d & 1;
+        const int pp = r - 1, d = c0 + pp, buf = d & 1;
         const uint32_t acc = tmem + ACC0 + pp * 64;
         if (DKDV) {
           const uint64_t da = mnmajor0 + ds0 + buf * DSBUF16;
@@ -313,7 +333,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 #pragma unroll
           for (int k = 0; k < 8; ++k) mma_bf16(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
           mma_commit(&s.bar_ds_free[buf]);
-          mma_commit(&s.bar_stream_empty[2 + d % NDO]);  // dO tile d: its dV and this dK are behind the commit, dP was consumed
+          mma_commit(&s.bar_stream_empty[2 + (d & (NDO - 1))]);  // dO tile d: its dV and this dK are behind the commit, dP was consumed
         } else {
           const uint64_t da = kmajor0 + ds0 + buf * DSBUF16;
           const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
@@ -325,16 +345,17 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         if (pp == np - 1) mma_commit(&s.bar_stream_empty[it & 1]);  // Q_it (DKDV) or K_it and V_it (DQ) may be overwritten
       }
       if (ok) mma_commit(&s.bar_acc_done);
+      TIMING_END(2);
     }
   } else {
-    // ======================================================================== compute warps 0..7
-    const int quarter = warp & 3, half = warp >> 2;
+    // ======================================================================== compute warps 0..15
+    const int quarter = warp & 3, slice = warp >> 2, half = slice >> 1;   // slice: 32 key columns, half: 64-column panel
     const int r = quarter * 32 + lane;                       // row of the tile = TMEM lane
-    const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16) + half * 64;
+    const uint32_t t_lane = tmem + ((uint32_t)(quarter * 32) << 16) + slice * 32;
     const uint32_t p_panel = smem_u32(s.p_tile[DKDV ? half : 0]);
     const float* lse_bh = p.lse + ((int64_t)b * p.heads + h) * p.seq_len;
     constexpr float LOG2E = 1.4426950408889634f;
-    uint32_t preg[32];                                        // this thread's 64 probabilities as bf16 pairs
+    uint32_t preg[16];                                        // this thread's 32 probabilities as bf16 pairs
     // Row statistics (log-sum-exp and the per-direction row dots) are fetched one step ahead: a load issued at the
     // point of use would expose a full DRAM round trip on every job.
     const float* delta_base = p.delta + (((int64_t)p0 * p.batch + b) * p.heads + h) * p.seq_len + r;
@@ -348,9 +369,19 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     load_stats(own, lse_r, delta_cur);                       // DKDV: first query tile is `own`; DQ: the only one
 #pragma unroll
     for (int i = 0; i < PB; ++i) delta_next[i] = 0.f;
+    TIMING_BEGIN();
+#ifdef LBI_ATTN_TIMING
+    long long _tm2 = 0;
+#endif
     bool ok = true;
+    int it = 0, rr = -1, d0 = 0;   // step, job within the step, index of the step's first dS tile
     for (int n = 0; n < total_jobs && ok; ++n) {
-      const int it = n / jobs_per_iter, rr = n % jobs_per_iter, buf = n & 1;
+      if (++rr == jobs_per_iter) {
+        rr = 0;
+        ++it;
+        d0 += np;
+      }
+      const int buf = n & 1;
       const int qi = DKDV ? own + it : own;   // query tile of this step
       const int kj = DKDV ? own : it;         // key tile of this step
       const uint32_t t_buf = t_lane + buf * 128;
@@ -363,18 +394,22 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           }
           if (it + 1 < n_iter) load_stats(qi + 1, lse_next, delta_next);
         }
-        ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 31);
-        if (DKDV && it > 0 && ok) ok = mbar_wait(&s.bar_p_free, (it - 1) & 1, abortp, p.status, 32);
+        TIMED(0, ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 31));
+        if (DKDV && it > 0 && ok) TIMED(1, ok = mbar_wait(&s.bar_p_free, (it - 1) & 1, abortp, p.status, 32))
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after_sync();
         const bool diagonal = (qi == kj);
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        {
           uint32_t v[32];
-          tmem_ld_32x32(t_buf + cc * 32, v);
-          tmem_ld_wait();
-          const int col0 = half * 64 + cc * 32;
+          TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
+          fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.bar_consumed[buf]);   // the TMEM buffer may be refilled while the tile is turned into P
+#ifdef LBI_ATTN_TIMING
+          _tm2 = clock64();
+#endif
+          const int col0 = slice * 32;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
 #pragma unroll
@@ -386,57 +421,63 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
                 if (col > r) a = 0.f;
                 if (col + 1 > r) bb = 0.f;
               }
-              preg[cc * 16 + g * 4 + e] = pack_bf16(a, bb);
+              preg[g * 4 + e] = pack_bf16(a, bb);
             }
             if (DKDV)
-              st_shared_v4(swz(p_panel, r, cc * 4 + g),
-                           make_uint4(preg[cc * 16 + g * 4], preg[cc * 16 + g * 4 + 1], preg[cc * 16 + g * 4 + 2],
-                                      preg[cc * 16 + g * 4 + 3]));
+              st_shared_v4(swz(p_panel, r, (slice & 1) * 4 + g),
+                           make_uint4(preg[g * 4], preg[g * 4 + 1], preg[g * 4 + 2], preg[g * 4 + 3]));
           }
         }
-        if (DKDV) fence_proxy_async();
-        fence_before_sync();
-        mbar_arrive(&s.bar_consumed[buf]);
-        mbar_arrive(&s.bar_written[n & 3]);
+#ifdef LBI_ATTN_TIMING
+        tacc[4] += clock64() - _tm2;
+#endif
+        TIMED(5, if (DKDV) fence_proxy_async(); __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_written[n & 3]));
       } else {
-        const int pp = rr - 1, d = it * np + pp, dbuf = d & 1;
+        const int pp = rr - 1, d = d0 + pp, dbuf = d & 1;
         float delta_r = delta_cur[0];
 #pragma unroll
         for (int i = 1; i < PB; ++i) delta_r = (pp == i) ? delta_cur[i] : delta_r;
         const uint32_t ds_panel = smem_u32(s.ds_tile[dbuf][half]);
-        ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 33);
-        if (d >= 2 && ok) ok = mbar_wait(&s.bar_ds_free[dbuf], ((d >> 1) - 1) & 1, abortp, p.status, 34);
+        TIMED(0, ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 33));
+        if (d >= 2 && ok) TIMED(2, ok = mbar_wait(&s.bar_ds_free[dbuf], ((d >> 1) - 1) & 1, abortp, p.status, 34))
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         fence_after_sync();
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
+        {
           uint32_t v[32];
-          tmem_ld_32x32(t_buf + cc * 32, v);
-          tmem_ld_wait();
+          TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
+          fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.bar_consumed[buf]);
+#ifdef LBI_ATTN_TIMING
+          _tm2 = clock64();
+#endif
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const float2 pr = unpack_bf16(preg[cc * 16 + g * 4 + e]);
+              const float2 pr = unpack_bf16(preg[g * 4 + e]);
               const float d0 = pr.x * (__uint_as_float(v[g * 8 + e * 2]) - delta_r);
               const float d1 = pr.y * (__uint_as_float(v[g * 8 + e * 2 + 1]) - delta_r);
               w[e] = pack_bf16(d0, d1);
             }
-            st_shared_v4(swz(ds_panel, r, cc * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
+            st_shared_v4(swz(ds_panel, r, (slice & 1) * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
           }
         }
-        fence_proxy_async();
-        fence_before_sync();
-        mbar_arrive(&s.bar_consumed[buf]);
-        mbar_arrive(&s.bar_written[n & 3]);
+#ifdef LBI_ATTN_TIMING
+        tacc[4] += clock64() - _tm2;
+#endif
+        TIMED(5, fence_proxy_async(); __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_written[n & 3]));
       }
     }
     // ------------------------------------------------------------------ epilogue: accumulators -> global
+#ifdef LBI_ATTN_TIMING
+    _tm2 = clock64();
+#endif
     if (ok) ok = mbar_wait(&s.bar_acc_done, 0, abortp, p.status, 35);
     ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    if (ok && slice < 2) {
       fence_after_sync();
       const int64_t tok = (int64_t)row_b + own * TILE + r;
       for (int pp = 0; pp < np; ++pp) {
@@ -445,10 +486,10 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         for (int a = 0; a < n_acc; ++a) {
           // DKDV: a = 0 -> dK (scaled), a = 1 -> dV ; DQ: dQ (scaled)
           const uint32_t acc = tmem + (a == 0 ? ACC0 : ACC_DV) + pp * 64;
-          const int col = (DKDV ? (a == 0 ? col_k : col_v) : col_q) + half * 32;
+          const int col = (DKDV ? (a == 0 ? col_k : col_v) : col_q) + slice * 32;
           const float mul = (DKDV && a == 1) ? 1.f : p.scale;
           uint32_t v[32];
-          tmem_ld_32x32(acc + ((uint32_t)(quarter * 32) << 16) + half * 32, v);
+          tmem_ld_32x32(acc + ((uint32_t)(quarter * 32) << 16) + slice * 32, v);
           tmem_ld_wait();
           uint4* dst = reinterpret_cast<uint4*>(out_row + col);
 #pragma unroll
@@ -463,6 +504,10 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         }
       }
     }
+#ifdef LBI_ATTN_TIMING
+    tacc[6] += clock64() - _tm2;
+    if (threadIdx.x == 0) TIMING_END(3);
+#endif
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -473,7 +518,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 16) {
     fence_after_sync();
     tmem_dealloc(tmem, 512);
   }
@@ -552,6 +597,16 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& md, const Params& p,
 
 }  // namespace attn
 }  // namespace lbi
+
+#ifdef LBI_ATTN_TIMING
+// Copies the 2 x 4 x 8 cycle counters to `out` and clears them.
+extern "C" int lbi_attn_timing_read(unsigned long long* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_timing, sizeof(unsigned long long) * 64);
+  if (e != cudaSuccess) return (int)e;
+  unsigned long long zeros[64] = {0};
+  return (int)cudaMemcpyToSymbol(lbi::attn::g_attn_timing, zeros, sizeof(zeros));
+}
+#endif
 
 extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const float* lse, void* d_qkv,
                                  float* delta, int batch, int heads, int seq_len, int head_dim, int nbasis, float scale,

@@ -326,6 +326,21 @@ Tensor attn_pullback_packed(const Tensor& d_o, const Tensor& qkv, const Tensor& 
   return d_qkv;
 }
 
+std::tuple<Tensor, Tensor> attn_fwd_packed(const Tensor& qkv, int64_t batch, int64_t seq_len, int64_t heads, int64_t head_dim,
+                                           double scale) {
+  CHECK_BF16(qkv);
+  c10::cuda::CUDAGuard guard(qkv.device());
+  const int64_t n = batch * seq_len;
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(0) == n && qkv.size(1) == 3 * heads * head_dim, "qkv shape mismatch");
+  Tensor out = torch::empty({n, heads * head_dim}, qkv.options());
+  Tensor lse = torch::empty({batch, heads, seq_len}, qkv.options().dtype(at::kFloat));
+  Tensor st = status_word(qkv);
+  check(lbi_attn_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), (int)batch, (int)heads, (int)seq_len, (int)head_dim,
+                     (float)scale, st.data_ptr<int>(), cur_stream()),
+        "attn_fwd");
+  return {out, lse};
+}
+
 // ---- peer-memory kernels.  `*_ptrs` are int64 CUDA tensors holding one device pointer per rank.
 template <typename T>
 T ptr_table(const Tensor& t) {
@@ -438,7 +453,13 @@ void adamw_allgather_(Tensor param, const Tensor& reduced_grad, Tensor m, Tensor
         "adamw_allgather");
 }
 
-int64_t kernel_status(const Tensor& like) { return status_word(like).item<int>(); }
+// Reads the device status word (non-zero: a bounded wait in some kernel ran out; the value names the site) and clears it.
+int64_t kernel_status(const Tensor& like) {
+  Tensor st = status_word(like);
+  const int v = st.item<int>();
+  if (v != 0) st.zero_();
+  return v;
+}
 
 }  // namespace
 
@@ -465,6 +486,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);
   m.def("gemm_tn", &gemm_tn);
   m.def("attn_pullback_packed", &attn_pullback_packed);
+  m.def("attn_fwd_packed", &attn_fwd_packed);
   m.def("kernel_status", &kernel_status);
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_signal_all", &peer_signal_all);

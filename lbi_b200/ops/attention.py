@@ -15,6 +15,7 @@ dQ, dK, dV [B, P, H, T, Dh]).  Kernel modes:
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -39,8 +40,22 @@ def _flash():
     return fa
 
 
-def flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale):
-    """Library flash-attention forward on the packed qkv buffer -> (out [n, H*Dh], lse [B, H, T] fp32)."""
+FORWARD_NATIVE = os.environ.get("LBI_B200_LIBRARY_ATTENTION", "0") != "1"
+
+
+def flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, kernel_mode=None):
+    """Causal attention forward on the packed qkv buffer -> (out [n, H*Dh], lse [B, H, T] fp32).
+
+    ``tcgen05``: the extension's own kernel (bf16, head_dim 64, T % 128 == 0, no grouped kv heads);
+    ``fa2``: the flash_attn library kernel, kept as the baseline and for every other shape."""
+    mode = kernel_mode or ("tcgen05" if FORWARD_NATIVE and qkv.is_cuda and qkv.is_contiguous() and hasattr(ext(), "attn_fwd_packed")
+                           and tcgen05_pullback_supported(qkv.dtype, head_dim, n_heads, n_kv_heads, seq_len) else "fa2")
+    if mode == "tcgen05":
+        from .dispatch import KERNEL_LAUNCHES
+
+        KERNEL_LAUNCHES["count"] += 1
+        out, lse = ext().attn_fwd_packed(qkv, batch, seq_len, n_heads, head_dim, float(scale))
+        return out, lse
     q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
     out, lse, _, _ = _flash()._flash_attn_forward(q, k, v, 0.0, float(scale), True, -1, -1, 0.0, None, False)
     return out.reshape(batch * seq_len, n_heads * head_dim), lse
@@ -73,7 +88,7 @@ def tcgen05_pullback_supported(dtype, head_dim, n_heads, n_kv_heads, seq_len) ->
         native_available()
         and hasattr(ext(), "attn_pullback_packed")
         and dtype == torch.bfloat16
-        and head_dim in (64, 128)
+        and head_dim == 64
         and n_heads == n_kv_heads
         and seq_len % 128 == 0
     )

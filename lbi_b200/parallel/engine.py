@@ -26,6 +26,7 @@ import torch
 
 from .. import ops
 from ..models.region_plan import RegionPlacement
+from ..utils import nvtx
 from .comm import LocalComm
 from .flat import FlatParams
 
@@ -343,29 +344,41 @@ class FastLBIEngine:
         """Forward + exact region-local backward; gradients end up in ``self.flat.grads`` (not yet reduced)."""
         model = self.model
         self.flat.zero_grad()
-        records, loss = self._forward(input_ids, targets)
+        with nvtx.range("lbi/forward"):
+            records, loss = self._forward(input_ids, targets)
         k_regions = model.num_regions
         jacobians, offsets = [], []
         for rec in records:
-            jac, off = self._pullback_region(rec, need_jacobian=rec.index < k_regions - 1)
+            with nvtx.range(f"lbi/pullback/region{rec.index}"):
+                jac, off = self._pullback_region(rec, need_jacobian=rec.index < k_regions - 1)
             jacobians.append(jac)
             offsets.append(off)
-        g = self._scan(jacobians, offsets)  # [B, K, R]
+        with nvtx.range("lbi/scan"):
+            g = self._scan(jacobians, offsets)  # [B, K, R]
         for rec in records:
             g_next = g[:, rec.index + 1] if rec.index + 1 < k_regions else None
-            self._backward_region(rec, g_next)
+            with nvtx.range(f"lbi/local_vjp/region{rec.index}"):
+                self._backward_region(rec, g_next)
             rec.cache = None
         if self.my_regions[0] == 0:
-            self._backward_initial(input_ids, g[:, 0])
+            with nvtx.range("lbi/local_vjp/initial"):
+                self._backward_initial(input_ids, g[:, 0])
         return StepResult(loss=loss, state_cotangents=g, jacobians=self.last.get("jacobians"))
 
     def step(self, input_ids: torch.Tensor, targets: torch.Tensor, lr: float | None = None) -> torch.Tensor:
         result = self.backward(input_ids, targets)
-        self._optimizer_step(self.lr if lr is None else lr)
+        with nvtx.range("lbi/optimizer"):
+            self._optimizer_step(self.lr if lr is None else lr)
         loss = result.loss.detach().clone()
         if self.comm.world_size > 1:
             self.comm.all_reduce_sum(loss)
         return loss
+
+    def sync_master_params(self) -> None:
+        """Collective: complete the fp32 master copy on every rank (a rank's optimizer updates only its own shard; the
+        other shards reach it as bf16 weights).  Needed before evaluating or saving the module's parameters."""
+        if self.comm.world_size > 1 and self.flat.shadow is not None:
+            self.comm.all_gather_flat(self.flat.params, self.flat.shard)
 
     def named_grads(self) -> dict[str, torch.Tensor]:
         return self.flat.grad_map()

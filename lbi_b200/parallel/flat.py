@@ -92,33 +92,41 @@ class FlatParams:
             self.exp_avg = torch.zeros(hi - lo, dtype=torch.float32, device=self.device)
             self.exp_avg_sq = torch.zeros(hi - lo, dtype=torch.float32, device=self.device)
 
-    def state_dict_like_torch(self, param_order: list[str], hyper: dict) -> dict:
-        """Optimizer state in ``torch.optim.AdamW.state_dict()`` layout (needs the full moments on this rank)."""
+    def gathered_moments(self, comm=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Full-length AdamW moments.  With sharded state every rank must call this (it is an all-gather)."""
         lo, hi = self.state_range
-        if (lo, hi) != (0, self.total):
-            raise RuntimeError("gather the moment shards before exporting the optimizer state")
+        if (lo, hi) == (0, self.total):
+            return self.exp_avg, self.exp_avg_sq
+        if comm is None or comm.world_size != self.world_size:
+            raise RuntimeError("gather the moment shards before exporting the optimizer state: pass the communicator")
+        return comm._all_gather(self.exp_avg).reshape(-1), comm._all_gather(self.exp_avg_sq).reshape(-1)
+
+    def state_dict_like_torch(self, param_order: list[str], hyper: dict, comm=None) -> dict:
+        """Optimizer state in ``torch.optim.AdamW.state_dict()`` layout (consolidated over ranks when sharded)."""
+        exp_avg, exp_avg_sq = self.gathered_moments(comm)
         state = {}
         for idx, name in enumerate(param_order):
             s = self.slots[name]
             state[idx] = {
                 "step": torch.tensor(float(self.step_count)),
-                "exp_avg": self.exp_avg[s.offset : s.offset + s.numel].view(s.shape).clone(),
-                "exp_avg_sq": self.exp_avg_sq[s.offset : s.offset + s.numel].view(s.shape).clone(),
+                "exp_avg": exp_avg[s.offset : s.offset + s.numel].view(s.shape).clone(),
+                "exp_avg_sq": exp_avg_sq[s.offset : s.offset + s.numel].view(s.shape).clone(),
             }
         group = dict(hyper)
         group["params"] = list(range(len(param_order)))
         return {"state": state, "param_groups": [group]}
 
     def load_state_dict_like_torch(self, sd: dict, param_order: list[str]) -> None:
+        """Load a consolidated state; a rank with sharded moments keeps only the part inside its range."""
         self.ensure_state()
         lo, hi = self.state_range
-        if (lo, hi) != (0, self.total):
-            raise RuntimeError("loading a consolidated optimizer state needs the full moments on this rank")
         for idx, name in enumerate(param_order):
             st = sd["state"].get(idx)
             if st is None:
                 continue
             s = self.slots[name]
-            self.exp_avg[s.offset : s.offset + s.numel].copy_(st["exp_avg"].reshape(-1))
-            self.exp_avg_sq[s.offset : s.offset + s.numel].copy_(st["exp_avg_sq"].reshape(-1))
+            a, b = max(lo, s.offset), min(hi, s.offset + s.numel)
+            if a < b:
+                self.exp_avg[a - lo : b - lo].copy_(st["exp_avg"].reshape(-1)[a - s.offset : b - s.offset])
+                self.exp_avg_sq[a - lo : b - lo].copy_(st["exp_avg_sq"].reshape(-1)[a - s.offset : b - s.offset])
             self.step_count = int(float(st["step"]))

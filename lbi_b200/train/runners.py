@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import json
 import math
+import os
 import time
 from contextlib import nullcontext
 from pathlib import Path
@@ -31,6 +32,7 @@ from .data import build_corpora, sample_batch_any
 from .eval import evaluate_native, evaluate_reference, next_token_loss, resolve_eval_message_ablation_modes
 from .metrics import log_row, write_run_metadata
 from .model_builders import build_dense_model, build_lbi_model
+from ..utils.failure import FaultInjector, Heartbeat, check_kernel_status
 
 _EVAL_MESSAGE_ABLATION_MODES = ("zero_all", "noise", "mask")
 
@@ -45,11 +47,36 @@ def _lbi_cache_state_norm(cache: dict[str, Any]) -> float:
 def _resolve_device(cfg: LBITrainingConfig) -> torch.device:
     if cfg.device == "cpu":
         return torch.device("cpu")
+    local_rank = int(os.environ.get("LOCAL_RANK", "0")) if _world_size() > 1 else None
     if cfg.device == "cuda":
         if not torch.cuda.is_available():
             raise RuntimeError("CUDA requested but not available.")
-        return torch.device("cuda")
-    return torch.device("cuda" if torch.cuda.is_available() else "cpu")
+        return torch.device("cuda") if local_rank is None else torch.device("cuda", local_rank)
+    if torch.cuda.is_available():
+        return torch.device("cuda") if local_rank is None else torch.device("cuda", local_rank)
+    return torch.device("cpu")
+
+
+def _world_size() -> int:
+    return int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def _make_comm(device: torch.device):
+    """Communicator of a multi-process launch (torchrun environment): peer-memory kernels on GPUs unless
+    LBI_B200_COMM=collective, library collectives otherwise and on CPU ranks; None for a single process."""
+    if _world_size() <= 1:
+        return None
+    from ..parallel.comm import CollectiveComm, init_distributed_from_env
+
+    init_distributed_from_env(device.type)
+    if device.type == "cuda" and os.environ.get("LBI_B200_COMM", "symm") != "collective":
+        try:
+            from ..parallel.symm import SymmComm
+
+            return SymmComm()
+        except Exception as exc:  # no peer access between the GPUs of this job
+            print(f"[lbi_b200] peer-memory plane unavailable ({exc}); using library collectives", flush=True)
+    return CollectiveComm()
 
 
 def _autocast_context(cfg: LBITrainingConfig, device: torch.device):
@@ -129,14 +156,25 @@ class _FlatOptimizerView:
         return [name for name, p in self.engine.model.named_parameters() if p.requires_grad]
 
     def state_dict(self) -> dict:
+        """Consolidated over ranks: every rank must call this (the moment shards are all-gathered)."""
         e = self.engine
         hyper = {"lr": self.param_groups[0]["lr"], "betas": tuple(e.betas), "eps": e.eps, "weight_decay": e.weight_decay,
                  "amsgrad": False, "maximize": False, "foreach": None, "capturable": False, "differentiable": False,
                  "fused": None}
-        return e.flat.state_dict_like_torch(self._order(), hyper)
+        return e.flat.state_dict_like_torch(self._order(), hyper, comm=e.comm)
 
     def load_state_dict(self, sd: dict) -> None:
         self.engine.flat.load_state_dict_like_torch(sd, self._order())
+
+
+class _FrozenState:
+    """An optimizer state dict that was already consolidated (checkpoint writer of multi-process runs)."""
+
+    def __init__(self, sd: dict) -> None:
+        self._sd = sd
+
+    def state_dict(self) -> dict:
+        return self._sd
 
 
 class _FastStepper:
@@ -145,7 +183,7 @@ class _FastStepper:
 
         act = torch.bfloat16 if cfg.dtype == "bfloat16" else torch.float32
         self.engine = FastLBIEngine(model, lr=cfg.lr_model, weight_decay=cfg.weight_decay, grad_clip=cfg.grad_clip,
-                                    basis_chunk=max(1, cfg.jacobian_basis_chunk), act_dtype=act)
+                                    basis_chunk=max(1, cfg.jacobian_basis_chunk), act_dtype=act, comm=_make_comm(device))
         self.optimizer = _FlatOptimizerView(self.engine, cfg)
         self.diagnostics: dict[str, Any] = {"interface_scan_rms": 0.0}
         self.cfg = cfg
@@ -168,6 +206,8 @@ class _FastStepper:
 
 
 def _build_stepper(cfg, model, device, variant: str):
+    if _world_size() > 1 and (variant == DENSE_VARIANT or cfg.backward_engine != "fast"):
+        raise ValueError("multi-process training is region-parallel: it needs the lbi variant with --backward-engine fast")
     if variant == DENSE_VARIANT:
         return _AutogradStepper(cfg, model, device, AutogradEngine(), lbi=False)
     if cfg.backward_engine == "fast":
@@ -188,8 +228,12 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
     if is_lbi and not isinstance(model, LBILanguageModel):
         raise TypeError("LBI training requires LBILanguageModel")
     stepper = _build_stepper(cfg, model, device, variant)
+    is_main = int(os.environ.get("RANK", "0")) == 0 or _world_size() <= 1   # rank 0 owns every file of the run
+    distributed = _world_size() > 1
     train_corpus, val_corpus = build_corpora(cfg, device=device)
-    write_run_metadata(cfg=cfg, run_dir=run_dir, model=model, train_corpus=train_corpus, val_corpus=val_corpus)
+    if is_main:
+        write_run_metadata(cfg=cfg, run_dir=run_dir, model=model, train_corpus=train_corpus, val_corpus=val_corpus)
+    log_row_main = log_row if is_main else (lambda *a, **k: None)
 
     gen_device = device if cfg.data_mode == "synthetic" else torch.device("cpu")
     train_gen = torch.Generator(device=gen_device)
@@ -223,13 +267,27 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
         return extra
 
     def save(filename: str, step: int, **more) -> str:
+        if distributed:  # all ranks: complete the fp32 master copy and consolidate the optimizer shards
+            stepper.engine.sync_master_params()
+            optimizer = _FrozenState(stepper.optimizer.state_dict())
+            if not is_main:
+                return ""
+        else:
+            optimizer = stepper.optimizer
         return str(save_checkpoint(
-            run_dir=run_dir, filename=filename, model=model, optimizer=stepper.optimizer, cfg=cfg, device=device,
+            run_dir=run_dir, filename=filename, model=model, optimizer=optimizer, cfg=cfg, device=device,
             train_generator=train_gen, eval_generator=eval_gen, step=step, tokens_seen=total_tokens,
             best_val_ce_loss=best_val, best_val_step=best_val_step, extra=checkpoint_extra(**more)))
 
+    injector = FaultInjector(rank=int(os.environ.get("RANK", "0")))
+    heartbeat = Heartbeat.from_process_group() if (torch.distributed.is_available() and torch.distributed.is_initialized()) else None
     window_t0, window_steps = time.perf_counter(), 0
     for step in range(start_step + 1, cfg.steps + 1):
+        # between steps: nothing of this rank is in flight, so faults are injected and peers are checked here
+        injector.at_step(step, heartbeat=heartbeat, checkpoint_path=Path(latest_path) if latest_path else None)
+        if heartbeat is not None:
+            heartbeat.beat(step)
+            heartbeat.check_peers()
         model.train()
         xb, yb = sample_batch_any(cfg=cfg, corpus=train_corpus, batch_size=cfg.batch_size, generator=train_gen, device=device)
         want_stats = is_lbi and cfg.log_interface_jacobian_every > 0 and (
@@ -243,6 +301,8 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
         logging = (step % cfg.log_every) == 0 or step == 1 or want_stats or step == cfg.steps
         if logging:
             final_train = float(loss.item())  # the only device read of a training step
+            if device.type == "cuda":
+                check_kernel_status(loss)
             elapsed = max(1e-9, time.perf_counter() - window_t0)
             scan_rms = float(stepper.diagnostics.get("interface_scan_rms", 0.0)) if is_lbi else 0.0
             row = {"step": step, "tokens_seen": total_tokens, "split": "train", "ce_loss": final_train,
@@ -251,10 +311,12 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
             if jac_stats is not None:
                 row.update(jac_stats)
             if (step % cfg.log_every) == 0 or step == 1 or want_stats:
-                log_row(run_dir, row)
+                log_row_main(run_dir, row)
             window_t0, window_steps = time.perf_counter(), 0
 
         if (step % cfg.eval_every) == 0 or step == cfg.steps:
+            if distributed:
+                stepper.engine.sync_master_params()  # evaluation runs replicated on the fp32 master weights
             if is_lbi:
                 step_gen = torch.Generator(device=gen_device)
                 step_gen.manual_seed(cfg.seed + 202 + step * 11)
@@ -269,7 +331,7 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
                 if cfg.save_checkpoints:
                     best_path = save("best.pt", step, val_ce_loss=final_val, is_best=True)
             blank = {"step": step, "tokens_seen": total_tokens, "message_norm": "", "scan_align": "", "tokens_per_s": 0.0, "wall_time_s": 0.0}
-            log_row(run_dir, {**blank, "split": "val", "ce_loss": final_val})
+            log_row_main(run_dir, {**blank, "split": "val", "ce_loss": final_val})
             if is_lbi:
                 modes = resolve_eval_message_ablation_modes(cfg, ablation_modes=_EVAL_MESSAGE_ABLATION_MODES)
                 for idx, mode in enumerate(modes):
@@ -282,7 +344,7 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
                                               autocast_context_fn=_autocast_context, message_ablation=mode,
                                               ablation_generator=noise_gen)
                     final_ablations[f"val_{mode}"] = float(ablated["ce_loss"])
-                    log_row(run_dir, {**blank, "split": f"val_{mode}", "ce_loss": float(ablated["ce_loss"])})
+                    log_row_main(run_dir, {**blank, "split": f"val_{mode}", "ce_loss": float(ablated["ce_loss"])})
             window_t0, window_steps = time.perf_counter(), 0
 
         if cfg.save_checkpoints and ((step % cfg.save_every) == 0 or step == cfg.steps):
@@ -305,7 +367,8 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
             final_interface_jacobian_stats=final_jac_stats, final_eval_message_ablations=final_ablations,
             owned_lbi_model=True, region_axis=cfg.region_axis, backward_engine=cfg.backward_engine,
         )
-    (run_dir / "summary.json").write_text(json.dumps(summary, indent=2, sort_keys=True), encoding="utf-8")
+    if is_main:
+        (run_dir / "summary.json").write_text(json.dumps(summary, indent=2, sort_keys=True), encoding="utf-8")
     return summary
 
 

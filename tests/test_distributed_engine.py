@@ -70,3 +70,56 @@ def test_multi_rank_engine_matches_single_process(tmp_path, axis, regions, world
     assert torch.allclose(got["grads"][:n], engine.flat.grads[:n], atol=1e-6, rtol=1e-5)
     engine._optimizer_step(1e-2)
     assert torch.allclose(got["params"][:n], engine.flat.params[:n], atol=1e-5, rtol=1e-5)
+
+
+def _train_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    from lbi_b200.train.lbi import run_lbi_experiment
+
+    torch.set_num_threads(1)
+    try:
+        run_lbi_experiment(_train_cfg(out_dir))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def _train_cfg(out_dir, **kw):
+    from lbi_b200.train.config import LBITrainingConfig
+
+    base = dict(variants="lbi", backbone="transformer", device="cpu", dtype="float32", output_dir=str(out_dir), run_name="run",
+                task="copy", vocab_size=32, seq_len=32, train_sequences=32, val_sequences=8, batch_size=2, steps=3, eval_every=3,
+                eval_batches=1, log_every=1, save_every=3, layers=2, dim=16, n_heads=2, d_conv=0, region_axis="sequence",
+                sequence_regions=4, region_size=2, message_dim=4, message_hidden_dim=8, backward_engine="fast", jacobian_basis_chunk=2)
+    base.update(kw)
+    return LBITrainingConfig(**base)
+
+
+def test_training_program_on_two_ranks_matches_one_process(tmp_path, monkeypatch):
+    """The training CLI path under a torchrun-style environment: rank 0 writes the run, the checkpoint holds the
+    consolidated optimizer state, and losses / weights equal the single-process run."""
+    import json
+
+    from lbi_b200.train.lbi import run_lbi_experiment
+
+    for key in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(key, raising=False)
+    mp.spawn(_train_worker, args=(2, _free_port(), str(tmp_path / "dist")), nprocs=2, join=True)
+    single = run_lbi_experiment(_train_cfg(tmp_path / "single"))
+    rows = {}
+    for tag in ("dist", "single"):
+        path = tmp_path / tag / "run" / "lbi" / "metrics.jsonl"
+        rows[tag] = [json.loads(line) for line in path.read_text().splitlines()]
+    assert [r["split"] for r in rows["dist"]] == [r["split"] for r in rows["single"]]
+    for a, b in zip(rows["dist"], rows["single"]):
+        assert a["ce_loss"] == pytest.approx(b["ce_loss"], rel=1e-5, abs=1e-6), (a, b)
+    ck_d = torch.load(tmp_path / "dist" / "run" / "lbi" / "checkpoints" / "latest.pt", weights_only=False)
+    ck_s = torch.load(tmp_path / "single" / "run" / "lbi" / "checkpoints" / "latest.pt", weights_only=False)
+    for name, w in ck_s["model_state_dict"].items():
+        assert torch.allclose(ck_d["model_state_dict"][name], w, atol=1e-5, rtol=1e-5), name
+    for idx, st in ck_s["optimizer_state_dict"]["state"].items():
+        for key in ("exp_avg", "exp_avg_sq"):
+            assert torch.allclose(ck_d["optimizer_state_dict"]["state"][idx][key], st[key], atol=1e-6, rtol=1e-4), (idx, key)
+    # a single process resumes from the checkpoint the two ranks wrote
+    resumed = run_lbi_experiment(_train_cfg(tmp_path / "dist", steps=4, resume_from=str(tmp_path / "dist" / "run")))
+    assert resumed["runs"][0]["start_step"] == 3

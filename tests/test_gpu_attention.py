@@ -59,3 +59,25 @@ def test_tcgen05_pullback_is_deterministic():
     b = attention_input_pullback_basis(q, k, v, do, causal=True, kernel_mode="tcgen05_pblock")
     for x, y in zip(a, b):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize("b,h,t", [(1, 1, 128), (2, 2, 256), (1, 3, 384), (2, 1, 640), (1, 2, 2048)])
+def test_tcgen05_forward_matches_fp32_attention(b, h, t):
+    from lbi_b200.ops.attention import flash_forward_packed
+
+    g = torch.Generator(device=DEV).manual_seed(t)
+    qkv = torch.randn(b * t, 3 * h * 64, device=DEV, generator=g).bfloat16()
+    scale = 1.0 / math.sqrt(64)
+    out, lse = flash_forward_packed(qkv, b, t, h, h, 64, scale, kernel_mode="tcgen05")
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(qkv) == 0, "a bounded wait inside the attention forward kernel ran out"
+    q, k, v = (x.reshape(b, t, h, 64).permute(0, 2, 1, 3).float() for x in qkv.split(h * 64, dim=1))
+    s = torch.einsum("bhqd,bhkd->bhqk", q, k) * scale
+    s = s.masked_fill(torch.ones(t, t, device=DEV, dtype=torch.bool).triu(1), float("-inf"))
+    want_lse = torch.logsumexp(s, dim=-1)
+    want = torch.einsum("bhqk,bhkd->bhqd", torch.softmax(s, dim=-1), v).permute(0, 2, 1, 3).reshape(b * t, h * 64)
+    assert (lse - want_lse).abs().max().item() < 2e-3
+    assert (out.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
+    lib_out, lib_lse = flash_forward_packed(qkv, b, t, h, h, 64, scale, kernel_mode="fa2")
+    assert (lib_out.float() - out.float()).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
+    assert (lib_lse - lse).abs().max().item() < 2e-3
