@@ -11,6 +11,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ...ops import ssd as ops_ssd
 from ..norms import RMSNormGated
 from .ssd import ssd_chunk_scan
 
@@ -77,14 +78,14 @@ class Mamba2Simple(nn.Module):
             dt = dt.clamp(self.dt_limit[0], self.dt_limit[1])
         xBC = F.silu(self.conv1d(xBC.transpose(1, 2))[..., :seqlen].transpose(1, 2))
         x, B, C = torch.split(xBC, [self.d_inner, gn, gn], dim=-1)
-        y = ssd_chunk_scan(
-            x.reshape(bsz, seqlen, self.nheads, self.headdim),
-            dt,
-            -torch.exp(self.A_log.float()),
-            B.reshape(bsz, seqlen, self.ngroups, self.d_state),
-            C.reshape(bsz, seqlen, self.ngroups, self.d_state),
-            chunk_size=self.chunk_size,
-            D=self.D,
-        )
+        x4 = x.reshape(bsz, seqlen, self.nheads, self.headdim)
+        B4 = B.reshape(bsz, seqlen, self.ngroups, self.d_state)
+        C4 = C.reshape(bsz, seqlen, self.ngroups, self.d_state)
+        A = -torch.exp(self.A_log.float())
+        if ops_ssd.ssd_cuda_supported(x4, B4) and x4.dtype == torch.bfloat16:
+            # sm_100a kernels (chunk 128 inside); the chunk size does not change the result, only the blocking
+            y = ops_ssd.ssd_chunk_scan_cuda(x4, dt, A, B4, C4, D=self.D)
+        else:
+            y = ssd_chunk_scan(x4, dt, A, B4, C4, chunk_size=self.chunk_size, D=self.D)
         y = self.norm(y.reshape(bsz, seqlen, self.d_inner), z)
         return self.out_proj(y.to(self.out_proj.weight.dtype))

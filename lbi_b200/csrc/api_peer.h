@@ -1,7 +1,8 @@
 // C entry points of the peer-memory kernels (peer.cu): compute fused with the transfer over NVLink / NVSwitch.
 // Every rank runs one process with one GPU; `*_ptrs` arguments are DEVICE arrays of `world` pointers into the peers'
 // symmetric buffers (entry `rank` is this GPU's own buffer).  Cross-GPU ordering uses 32-bit sequence flags written
-// with st.release.sys and polled with ld.acquire.sys; every poll is bounded (2 s) and reports through `status`.
+// with st.release.sys and polled with ld.acquire.sys; every poll is bounded (lbi_peer_set_wait_limit_ms) and reports
+// through `status`.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -9,6 +10,9 @@
 #ifdef __cplusplus
 extern "C" {
 #endif
+
+// Time limit (milliseconds, default 20000) of every flag wait of the kernels below, for the current device.
+int lbi_peer_set_wait_limit_ms(int ms);
 
 // All ranks write `seq` into slot [slot_base + rank] of every peer's flag array and wait until every peer's write has
 // arrived in their own array.  Flags only ever grow, so no reset is needed.

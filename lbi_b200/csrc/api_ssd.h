@@ -1,0 +1,26 @@
+// C entry points of the Mamba-2 SSD chunk-scan forward (ssd.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// dt_raw [B, L, H] fp32 -> dt_out, cum [B, H, L] fp32: dt = clamp(softplus(dt_raw + bias)) when `softplus`, else dt_raw;
+// cum = inclusive cumulative sum of dt * a[h] inside every 128-token chunk.  L must be a multiple of 128.
+int lbi_ssd_cumsum(const float* dt_raw, const float* dt_bias, const float* a, float* dt_out, float* cum, int batch, int seq_len,
+                   int heads, int softplus, float dt_min, float dt_max, cudaStream_t stream);
+
+// Chunked scan.  x [B*L, H*64] bf16, bm / cm [B*L, G*N] bf16, dt / cum from lbi_ssd_cumsum, d_skip [H] fp32 or null,
+// init_state [B, H, 64, N] fp32 or null.  Scratch supplied by the caller: states [B, L/128, H, 64, N] fp32 and
+// prev (same shape, bf16).  Outputs: final_state [B, H, 64, N] fp32, y [B*L, H*64] bf16.
+// head_dim must be 64, d_state 64 or 128, heads / groups even.  Three kernels on `stream`.
+int lbi_ssd_chunk_scan_fwd(const void* x, const void* bm, const void* cm, const float* dt, const float* cum,
+                           const float* d_skip, const float* init_state, float* states, void* prev, float* final_state,
+                           void* y, int batch, int seq_len, int heads, int groups, int head_dim, int d_state, int* status,
+                           cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -235,8 +235,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const Params p) {
         }
         l_run = l_run * alpha + sum;
         m_run = m_new;
-        fence_before_sync();
-        fence_proxy_async();
+        fence_proxy_async();   // S was read with tcgen05.wait::ld above, so the TMEM reads are complete
         __syncwarp();
         if (lane == 0) mbar_arrive(&s.bar_p_ready[g]);
 #pragma unroll
@@ -255,7 +254,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const Params p) {
             acc[32 + e] += __uint_as_float(r1[e]);
           }
         }
-        fence_before_sync();
       }
       if (ok) {
         const float inv = 1.f / l_run;

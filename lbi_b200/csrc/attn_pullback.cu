@@ -110,6 +110,43 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 __device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
   return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
+// Packed pairs: two fp32 in one 64-bit register (add / sub / fma .f32x2) and two bf16 in one 32-bit register.  The
+// compute warps are bound by instruction issue, so the per-element instruction count is what matters here.
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ float2 unpack_f32x2(uint64_t v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+__device__ __forceinline__ uint64_t sub_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("sub.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t cvt_bf16x2(uint64_t v) {   // {lo, hi} fp32 -> bf16 pair, lo in the low half
+  uint32_t d;
+  asm("{\n.reg .f32 lo, hi;\nmov.b64 {lo, hi}, %1;\ncvt.rn.bf16x2.f32 %0, hi, lo;\n}" : "=r"(d) : "l"(v));
+  return d;
+}
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -121,18 +158,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Optional phase timing (build with -DLBI_ATTN_TIMING): cycles spent per role and phase, summed over CTAs.
 //   [kernel: 0 = dQ, 1 = dK/dV][role: 0 = TMA producer, 1 = issuer X, 2 = issuer Y, 3 = compute thread 0][slot]; slot 7 = total.
 #ifdef LBI_ATTN_TIMING
-__device__ unsigned long long g_attn_timing[2][4][8];
+__device__ unsigned long long g_attn_timing[2][4][12];
 #define TIMED(slot, ...)              \
   {                                   \
     const long long _t0 = clock64();  \
     __VA_ARGS__;                      \
     tacc[slot] += clock64() - _t0;    \
   }
-#define TIMING_BEGIN() long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long _tstart = clock64();
+#define TIMING_BEGIN() long long tacc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; const long long _tstart = clock64();
 #define TIMING_END(role)                                                                                   \
   {                                                                                                        \
     tacc[7] = clock64() - _tstart;                                                                         \
-    for (int _i = 0; _i < 8; ++_i) atomicAdd(&g_attn_timing[DKDV ? 1 : 0][role][_i], (unsigned long long)tacc[_i]); \
+    for (int _i = 0; _i < 12; ++_i) atomicAdd(&g_attn_timing[DKDV ? 1 : 0][role][_i], (unsigned long long)tacc[_i]); \
   }
 #else
 #define TIMED(slot, ...) __VA_ARGS__;
@@ -386,6 +423,9 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       const int kj = DKDV ? own : it;         // key tile of this step
       const uint32_t t_buf = t_lane + buf * 128;
       if (rr == 0) {
+#ifdef LBI_ATTN_TIMING
+        const long long _ts = clock64();
+#endif
         if (DKDV) {
           if (it > 0) {
             lse_r = lse_next;
@@ -394,29 +434,31 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           }
           if (it + 1 < n_iter) load_stats(qi + 1, lse_next, delta_next);
         }
+#ifdef LBI_ATTN_TIMING
+        tacc[10] += clock64() - _ts;
+#endif
         TIMED(0, ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 31));
         if (DKDV && it > 0 && ok) TIMED(1, ok = mbar_wait(&s.bar_p_free, (it - 1) & 1, abortp, p.status, 32))
-        ok = __all_sync(0xffffffffu, ok);
+        TIMED(8, ok = __all_sync(0xffffffffu, ok); fence_after_sync());
         if (!ok) break;
-        fence_after_sync();
         const bool diagonal = (qi == kj);
         {
           uint32_t v[32];
           TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
-          fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s.bar_consumed[buf]);   // the TMEM buffer may be refilled while the tile is turned into P
+          TIMED(9, __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]));  // tcgen05.wait::ld above: the loads are complete  // TMEM buffer free
 #ifdef LBI_ATTN_TIMING
           _tm2 = clock64();
 #endif
           const int col0 = slice * 32;
+          const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse_r, -lse_r);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const int col = col0 + g * 8 + e * 2;
-              float a = fast_exp2(__uint_as_float(v[g * 8 + e * 2]) * p.scale_log2 - lse_r);
-              float bb = fast_exp2(__uint_as_float(v[g * 8 + e * 2 + 1]) * p.scale_log2 - lse_r);
+              const float2 t = unpack_f32x2(fma_f32x2(pack_u32x2(v[g * 8 + e * 2], v[g * 8 + e * 2 + 1]), sc2, nl2));
+              float a = fast_exp2(t.x);
+              float bb = fast_exp2(t.y);
               if (diagonal) {
                 if (col > r) a = 0.f;
                 if (col + 1 > r) bb = 0.f;
@@ -440,28 +482,24 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         const uint32_t ds_panel = smem_u32(s.ds_tile[dbuf][half]);
         TIMED(0, ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 33));
         if (d >= 2 && ok) TIMED(2, ok = mbar_wait(&s.bar_ds_free[dbuf], ((d >> 1) - 1) & 1, abortp, p.status, 34))
-        ok = __all_sync(0xffffffffu, ok);
+        TIMED(8, ok = __all_sync(0xffffffffu, ok); fence_after_sync());
         if (!ok) break;
-        fence_after_sync();
         {
           uint32_t v[32];
           TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
-          fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s.bar_consumed[buf]);
+          TIMED(9, __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]));  // tcgen05.wait::ld above: the loads are complete
 #ifdef LBI_ATTN_TIMING
           _tm2 = clock64();
 #endif
+          // dS = P o (dP - delta): the difference in fp32 (it cancels), the product of two bf16 values in bf16
+          const uint64_t delta2 = pack_f32x2(delta_r, delta_r);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 pr = unpack_bf16(preg[g * 4 + e]);
-              const float d0 = pr.x * (__uint_as_float(v[g * 8 + e * 2]) - delta_r);
-              const float d1 = pr.y * (__uint_as_float(v[g * 8 + e * 2 + 1]) - delta_r);
-              w[e] = pack_bf16(d0, d1);
-            }
+            for (int e = 0; e < 4; ++e)
+              w[e] = mul_bf16x2(preg[g * 4 + e],
+                                cvt_bf16x2(sub_f32x2(pack_u32x2(v[g * 8 + e * 2], v[g * 8 + e * 2 + 1]), delta2)));
             st_shared_v4(swz(ds_panel, r, (slice & 1) * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
           }
         }
@@ -601,9 +639,9 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& md, const Params& p,
 #ifdef LBI_ATTN_TIMING
 // Copies the 2 x 4 x 8 cycle counters to `out` and clears them.
 extern "C" int lbi_attn_timing_read(unsigned long long* out) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_timing, sizeof(unsigned long long) * 64);
+  cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_timing, sizeof(unsigned long long) * 96);
   if (e != cudaSuccess) return (int)e;
-  unsigned long long zeros[64] = {0};
+  unsigned long long zeros[96] = {0};
   return (int)cudaMemcpyToSymbol(lbi::attn::g_attn_timing, zeros, sizeof(zeros));
 }
 #endif

@@ -5,6 +5,7 @@
 
 #include "api.h"
 #include "api_attn.h"
+#include "api_ssd.h"
 #include "api_gemm.h"
 #include "api_peer.h"
 
@@ -341,12 +342,48 @@ std::tuple<Tensor, Tensor> attn_fwd_packed(const Tensor& qkv, int64_t batch, int
   return {out, lse};
 }
 
+// Mamba-2 SSD chunk scan forward.  x [B, L, H, 64] bf16, dt_raw [B, L, H] fp32, a [H] fp32, bm / cm [B, L, G, N] bf16.
+// Returns (y [B, L, H, 64] bf16, final_state [B, H, 64, N] fp32).
+std::tuple<Tensor, Tensor> ssd_chunk_scan_fwd(const Tensor& x, const Tensor& dt_raw, const Tensor& a, const Tensor& bm, const Tensor& cm,
+                                              const c10::optional<Tensor>& d_skip, const c10::optional<Tensor>& dt_bias,
+                                              const c10::optional<Tensor>& init_state, bool softplus, double dt_min, double dt_max) {
+  CHECK_BF16(x);
+  CHECK_BF16(bm);
+  CHECK_BF16(cm);
+  CHECK_F32(dt_raw);
+  CHECK_F32(a);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 4 && bm.dim() == 4 && cm.dim() == 4 && dt_raw.dim() == 3, "ssd: expected x [B,L,H,P], B/C [B,L,G,N], dt [B,L,H]");
+  const int64_t batch = x.size(0), seq = x.size(1), heads = x.size(2), hd = x.size(3), groups = bm.size(2), n = bm.size(3);
+  TORCH_CHECK(cm.sizes() == bm.sizes() && dt_raw.size(0) == batch && dt_raw.size(1) == seq && dt_raw.size(2) == heads, "ssd: shape mismatch");
+  const int64_t chunks = seq / 128;
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor dt = torch::empty({batch, heads, seq}, f32), cum = torch::empty({batch, heads, seq}, f32);
+  Tensor states = torch::empty({batch, chunks, heads, hd, n}, f32);
+  Tensor prev = torch::empty({batch, chunks, heads, hd, n}, x.options());
+  Tensor final_state = torch::empty({batch, heads, hd, n}, f32);
+  Tensor y = torch::empty_like(x);
+  Tensor st = status_word(x);
+  check(lbi_ssd_cumsum(dt_raw.data_ptr<float>(), dt_bias ? dt_bias->data_ptr<float>() : nullptr, a.data_ptr<float>(),
+                       dt.data_ptr<float>(), cum.data_ptr<float>(), (int)batch, (int)seq, (int)heads, softplus ? 1 : 0, (float)dt_min,
+                       (float)dt_max, cur_stream()),
+        "ssd_cumsum");
+  check(lbi_ssd_chunk_scan_fwd(x.data_ptr(), bm.data_ptr(), cm.data_ptr(), dt.data_ptr<float>(), cum.data_ptr<float>(),
+                               d_skip ? d_skip->data_ptr<float>() : nullptr, init_state ? init_state->data_ptr<float>() : nullptr,
+                               states.data_ptr<float>(), prev.data_ptr(), final_state.data_ptr<float>(), y.data_ptr(), (int)batch,
+                               (int)seq, (int)heads, (int)groups, (int)hd, (int)n, st.data_ptr<int>(), cur_stream()),
+        "ssd_chunk_scan_fwd");
+  return {y, final_state};
+}
+
 // ---- peer-memory kernels.  `*_ptrs` are int64 CUDA tensors holding one device pointer per rank.
 template <typename T>
 T ptr_table(const Tensor& t) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kLong && t.is_contiguous(), "pointer table must be a CUDA int64 tensor");
   return reinterpret_cast<T>(t.data_ptr<int64_t>());
 }
+
+void set_peer_wait_limit_ms(int64_t ms) { check(lbi_peer_set_wait_limit_ms((int)ms), "set_peer_wait_limit_ms"); }
 
 void peer_barrier(const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t slot_base, int64_t seq) {
   c10::cuda::CUDAGuard guard(flag_ptrs.device());
@@ -487,7 +524,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_tn", &gemm_tn);
   m.def("attn_pullback_packed", &attn_pullback_packed);
   m.def("attn_fwd_packed", &attn_fwd_packed);
+  m.def("ssd_chunk_scan_fwd", &ssd_chunk_scan_fwd);
   m.def("kernel_status", &kernel_status);
+  m.def("set_peer_wait_limit_ms", &set_peer_wait_limit_ms);
   m.def("peer_barrier", &peer_barrier);
   m.def("peer_signal_all", &peer_signal_all);
   m.def("interface_update_handoff", &interface_update_handoff);

@@ -15,7 +15,9 @@
 namespace lbi {
 namespace peer {
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+// Time limit of every flag wait.  Ranks of one step may legitimately be seconds apart (a rank's forward starts when the
+// previous owner's regions are done), so the default is generous; tests of the failure path set it to about a second.
+__device__ unsigned long long g_wait_limit_ns = 20000000000ull;
 
 __device__ __forceinline__ unsigned long long now_ns() {
   unsigned long long t;
@@ -36,7 +38,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, i
   const unsigned long long t0 = now_ns();
   uint32_t spins = 0;
   while ((int32_t)(ld_acquire_sys(flag) - want) < 0) {
-    if ((++spins & 0xff) == 0 && now_ns() - t0 > WAIT_LIMIT_NS) {
+    if ((++spins & 0xff) == 0 && now_ns() - t0 > g_wait_limit_ns) {
       if (status) atomicCAS(status, 0, site);
       return false;
     }
@@ -287,6 +289,12 @@ __global__ void adamw_allgather_kernel(float* __restrict__ param, const float* _
 using namespace lbi::peer;
 
 extern "C" {
+
+int lbi_peer_set_wait_limit_ms(int ms) {
+  if (ms < 1) return (int)cudaErrorInvalidValue;
+  const unsigned long long ns = (unsigned long long)ms * 1000000ull;
+  return (int)cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns));
+}
 
 int lbi_peer_barrier(uint32_t* const* flag_ptrs, int rank, int world, int slot_base, uint32_t seq, int* status,
                      cudaStream_t st) {

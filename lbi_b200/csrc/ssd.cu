@@ -1,0 +1,513 @@
+// Mamba-2 state-space-duality (SSD) chunk scan, forward, on tcgen05 / TMEM / TMA.
+//
+//   h_t = exp(dt_t A) h_{t-1} + dt_t x_t B_t^T ,   y_t = h_t C_t + D x_t          (per head; B, C shared per group)
+//
+// evaluated chunk-wise (chunk L = 128 tokens) in four kernels:
+//   1. cumsum        dt = softplus(dt_raw + bias) (optional), dA = dt A, inclusive in-chunk cumulative sum
+//   2. chunk state   S_c[(h,p), n] = sum_l x[l,(h,p)] exp(total - cum_l) dt_l B[l, n]        one tcgen05 GEMM per
+//                    (batch, chunk, pair of heads): M = 2 heads x 64, N = d_state, K = 128; x is scaled in place in
+//                    shared memory by the compute warps after TMA delivered it
+//   3. state passing sequential over chunks (elementwise): incoming state of every chunk (bf16) and the final state
+//   4. chunk scan    per (batch, chunk, head):  G = C B^T (128 x 128, K = d_state) -> TMEM;  W = G o decay o dt (causal)
+//                    written as bf16 into shared memory;  Y = W X (K = 128) and Y += (C o exp(cum)) H_in^T (K = d_state)
+//                    accumulate in TMEM;  epilogue adds D x and stores y.
+// This replaces the reference's Triton kernels _chunk_cumsum_fwd, _chunk_state_fwd, _state_passing_fwd, _bmm_chunk_fwd
+// and _chunk_scan_fwd (backbones/mamba2/ops/triton/ssd_combined.py:343-393), fusing the last two.
+//
+// Shapes: head_dim 64, d_state 64 or 128, seq_len a multiple of 128, an even number of heads per group.
+// x [B*L, H*64] bf16, Bm / Cm [B*L, G*N] bf16, dt / cum [B, H, L] fp32, states [B, C, H, 64, N] fp32,
+// prev [B, C, H, 64, N] bf16, y [B*L, H*64] bf16.  Every mbarrier wait is bounded (tcgen05.cuh).
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "api_ssd.h"
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace lbi {
+namespace ssd {
+
+using namespace tc;
+
+constexpr int L = 128;            // chunk length
+constexpr int P = 64;             // head dimension
+constexpr int PANEL = L * 128;    // 128 rows x 128 bytes
+constexpr int THREADS = 160;      // 4 compute warps + 1 control warp
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ float2 unpack2(uint32_t v) { return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v)); }
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// Multiply the 64 bf16 of row `row` of a 128-byte-row panel by f, in place (the swizzle only permutes the chunks).
+__device__ __forceinline__ void scale_row(uint32_t panel, int row, float f) {
+  const uint32_t base = panel + row * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    uint4 v = lds128(base + c * 16);
+    float2 a = unpack2(v.x), b = unpack2(v.y), cc = unpack2(v.z), d = unpack2(v.w);
+    v.x = pack2(a.x * f, a.y * f);
+    v.y = pack2(b.x * f, b.y * f);
+    v.z = pack2(cc.x * f, cc.y * f);
+    v.w = pack2(d.x * f, d.y * f);
+    sts128(base + c * 16, v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ 1. cumsum
+// grid (C, H, B), 128 threads.  dt_raw [B, L_total, H] fp32; outputs dt_out, cum [B, H, L_total] fp32.
+__global__ void __launch_bounds__(128) cumsum_kernel(const float* __restrict__ dt_raw, const float* __restrict__ dt_bias,
+                                                     const float* __restrict__ a_log_neg, float* __restrict__ dt_out,
+                                                     float* __restrict__ cum, int seq_len, int heads, int softplus,
+                                                     float dt_min, float dt_max) {
+  __shared__ float warp_tot[4];
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z, t = threadIdx.x;
+  const int64_t tok = (int64_t)b * seq_len + c * L + t;
+  float v = dt_raw[tok * heads + h];
+  if (softplus) {
+    v += dt_bias ? dt_bias[h] : 0.f;
+    v = v > 20.f ? v : log1pf(__expf(v));
+    v = fminf(fmaxf(v, dt_min), dt_max);
+  }
+  float acc = v * a_log_neg[h];
+  const int lane = t & 31, w = t >> 5;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float o = __shfl_up_sync(0xffffffffu, acc, off);
+    if (lane >= off) acc += o;
+  }
+  if (lane == 31) warp_tot[w] = acc;
+  __syncthreads();
+  float pre = 0.f;
+  for (int i = 0; i < w; ++i) pre += warp_tot[i];
+  const int64_t o = ((int64_t)b * heads + h) * seq_len + c * L + t;
+  dt_out[o] = v;
+  cum[o] = acc + pre;
+}
+
+// ------------------------------------------------------------------------------------------------ 2. chunk state
+template <int N>
+struct SmemState {
+  alignas(1024) uint8_t xs[2][PANEL];          // x of two heads: [l][64 p] per panel
+  alignas(1024) uint8_t bt[N / 64][PANEL];     // B: [l][64 n] per panel
+  uint64_t bar_full, bar_scaled, bar_done;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct StateParams {
+  int seq_len, heads, groups, chunks;
+  const float* dt;      // [B, H, L_total]
+  const float* cum;     // [B, H, L_total]
+  float* states;        // [B, C, H, 64, N]
+  int* status;
+};
+
+template <int N>
+__global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                              const __grid_constant__ CUtensorMap map_b, const StateParams p) {
+  extern __shared__ uint8_t raw_smem[];
+  SmemState<N>& s = *reinterpret_cast<SmemState<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
+  const int h0 = 2 * hp;
+  const int g = h0 / (p.heads / p.groups);
+  const int row0 = b * p.seq_len + c * L;
+  constexpr uint32_t TMEM_COLS = N;   // 64 or 128: a power of two >= 32
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.bar_full, 1);
+    mbar_init(&s.bar_scaled, 4);
+    mbar_init(&s.bar_done, 1);
+    fence_barrier_init();
+    prefetch_tmap(&map_x);
+    prefetch_tmap(&map_b);
+  }
+  if (warp == 4) tmem_alloc(&s.tmem_base, TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abortp = &s.abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&s.bar_full, (2 + N / 64) * PANEL);
+      tma_load_2d(s.xs[0], &map_x, &s.bar_full, h0 * P, row0);
+      tma_load_2d(s.xs[1], &map_x, &s.bar_full, (h0 + 1) * P, row0);
+      for (int q = 0; q < N / 64; ++q) tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, row0);
+      bool ok = mbar_wait(&s.bar_scaled, 0, abortp, p.status, 51);
+      if (ok) {
+        fence_after_sync();
+        // D[(h, p), n] = sum_l xs[l, (h, p)] * bt[l, n]: both operands have the reduction index as their row
+        const uint32_t idesc = make_idesc_bf16(128, N, 1, 1);
+        const uint64_t da = make_smem_desc(smem_u32(s.xs[0]), PANEL, 1024);
+        const uint64_t db = make_smem_desc(smem_u32(s.bt[0]), PANEL, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_bf16(tmem, da + 128 * kk, db + 128 * kk, idesc, kk);
+        mma_commit(&s.bar_done);
+      }
+    }
+  } else {
+    const int l = warp * 32 + lane;   // token of the chunk handled in the scaling pass; row (h, p) in the epilogue
+    const int64_t base0 = ((int64_t)b * p.heads + h0) * p.seq_len + c * L;
+    const int64_t base1 = base0 + p.seq_len;
+    const float f0 = ex2((p.cum[base0 + L - 1] - p.cum[base0 + l]) * LOG2E) * p.dt[base0 + l];
+    const float f1 = ex2((p.cum[base1 + L - 1] - p.cum[base1 + l]) * LOG2E) * p.dt[base1 + l];
+    bool ok = mbar_wait(&s.bar_full, 0, abortp, p.status, 52);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      scale_row(smem_u32(s.xs[0]), l, f0);
+      scale_row(smem_u32(s.xs[1]), l, f1);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.bar_scaled);
+      ok = mbar_wait(&s.bar_done, 0, abortp, p.status, 53);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      fence_after_sync();
+      const int h = h0 + (l >> 6), pp = l & 63;
+      float* dst = p.states + ((((int64_t)b * p.chunks + c) * p.heads + h) * P + pp) * N;
+#pragma unroll
+      for (int q = 0; q < N / 32; ++q) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + q * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          reinterpret_cast<float4*>(dst + q * 32)[e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                                                  __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
+      }
+    }
+  }
+  __syncwarp();
+  if (s.abort_flag) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    fence_after_sync();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ 3. state passing
+// One thread per state element (b, h, e), e in [0, 64 * N); walks the chunks.
+__global__ void state_passing_kernel(const float* __restrict__ states, const float* __restrict__ cum,
+                                     const float* __restrict__ init, __nv_bfloat16* __restrict__ prev,
+                                     float* __restrict__ final_state, int batch, int heads, int chunks, int seq_len,
+                                     int elems) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)batch * heads * elems) return;
+  const int e = (int)(idx % elems);
+  const int h = (int)((idx / elems) % heads);
+  const int b = (int)(idx / ((int64_t)elems * heads));
+  float st = init ? init[idx] : 0.f;
+  const float* cum_bh = cum + ((int64_t)b * heads + h) * seq_len;
+  for (int c = 0; c < chunks; ++c) {
+    const int64_t o = (((int64_t)b * chunks + c) * heads + h) * elems + e;
+    prev[o] = __float2bfloat16(st);
+    st = st * ex2(cum_bh[c * L + L - 1] * LOG2E) + states[o];
+  }
+  final_state[idx] = st;
+}
+
+// ------------------------------------------------------------------------------------------------ 4. chunk scan
+template <int N>
+struct SmemScan {
+  alignas(1024) uint8_t ct[N / 64][PANEL];     // C: [l][64 n] per panel (K-major A of G and of the state term)
+  alignas(1024) uint8_t bw[2][PANEL];          // first B ([l'][64 n] per panel, N / 64 panels), then W ([l][64 l'] x 2)
+  alignas(1024) uint8_t xt[PANEL];             // x: [l'][64 p]
+  alignas(1024) uint8_t pv[N / 64][P * 128];   // incoming state: [p][64 n] per panel
+  float cum2[L];                               // cum * log2(e)
+  float dtv[L];
+  uint64_t bar_full, bar_g, bar_w, bar_y;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct ScanParams {
+  int seq_len, heads, groups, chunks;
+  const float* dt;
+  const float* cum;
+  const float* d_skip;    // [H] or null
+  __nv_bfloat16* y;       // [B*L, H*64]
+  int* status;
+};
+
+template <int N>
+__global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                             const __grid_constant__ CUtensorMap map_b,
+                                                             const __grid_constant__ CUtensorMap map_c,
+                                                             const __grid_constant__ CUtensorMap map_prev, const ScanParams p) {
+  extern __shared__ uint8_t raw_smem[];
+  SmemScan<N>& s = *reinterpret_cast<SmemScan<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int g = h / (p.heads / p.groups);
+  const int row0 = b * p.seq_len + c * L;
+  constexpr int KS = N / 16;           // K = 16 slices over d_state
+  constexpr uint32_t PANEL16 = PANEL >> 4, PV16 = (P * 128) >> 4;
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.bar_full, 1);
+    mbar_init(&s.bar_g, 1);
+    mbar_init(&s.bar_w, 4);
+    mbar_init(&s.bar_y, 1);
+    fence_barrier_init();
+    prefetch_tmap(&map_x);
+    prefetch_tmap(&map_b);
+    prefetch_tmap(&map_c);
+    prefetch_tmap(&map_prev);
+  }
+  if (warp == 4) tmem_alloc(&s.tmem_base, 256);   // G: columns [0, 128), Y: [128, 192)
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abortp = &s.abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&s.bar_full, (2 * (N / 64) + 1) * PANEL + (N / 64) * P * 128);
+      for (int q = 0; q < N / 64; ++q) {
+        tma_load_2d(s.ct[q], &map_c, &s.bar_full, g * N + q * 64, row0);
+        tma_load_2d(s.bw[q], &map_b, &s.bar_full, g * N + q * 64, row0);
+        tma_load_2d(s.pv[q], &map_prev, &s.bar_full, q * 64, (int)((((int64_t)b * p.chunks + c) * p.heads + h) * P));
+      }
+      tma_load_2d(s.xt, &map_x, &s.bar_full, h * P, row0);
+      const uint64_t kmajor0 = make_smem_desc(0, 16, 1024), mnmajor0 = make_smem_desc(0, PANEL, 1024);
+      const uint32_t ct16 = smem_u32(s.ct[0]) >> 4, bw16 = smem_u32(s.bw[0]) >> 4, xt16 = smem_u32(s.xt) >> 4,
+                     pv16 = smem_u32(s.pv[0]) >> 4;
+      bool ok = mbar_wait(&s.bar_full, 0, abortp, p.status, 54);
+      if (ok) {
+        fence_after_sync();
+        const uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, kmajor0 + bw16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   idesc_g, kk);
+        mma_commit(&s.bar_g);
+        ok = mbar_wait(&s.bar_w, 0, abortp, p.status, 55);
+      }
+      if (ok) {
+        fence_after_sync();
+        const uint32_t idesc_y = make_idesc_bf16(128, 64, 0, 1);   // W (K-major) x X (rows are the reduction index)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          mma_bf16(tmem + 128, kmajor0 + bw16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, mnmajor0 + xt16 + 128 * kk, idesc_y, kk);
+        const uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);   // scaled C (K-major) x incoming state [p][n] (K-major)
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem + 128, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, kmajor0 + pv16 + (kk >> 2) * PV16 + (kk & 3) * 2,
+                   idesc_s, 1);
+        mma_commit(&s.bar_y);
+      }
+    }
+  } else {
+    const int l = warp * 32 + lane;
+    const int64_t base = ((int64_t)b * p.heads + h) * p.seq_len + c * L;
+    const float my_cum2 = p.cum[base + l] * LOG2E;
+    s.cum2[l] = my_cum2;
+    s.dtv[l] = p.dt[base + l];
+    named_barrier_sync(1, 128);
+    bool ok = mbar_wait(&s.bar_g, 0, abortp, p.status, 56);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      fence_after_sync();
+      // W[l, j] = G[l, j] exp(cum_l - cum_j) dt_j for j <= l, else 0; bf16, K-major, two 64-column panels
+      const uint32_t w_base = smem_u32(s.bw[0]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + q * 32, r);
+        tmem_ld_wait();
+        const uint32_t panel = w_base + (q >> 1) * PANEL + l * 128;
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e2 = 0; e2 < 4; ++e2) {
+            const int j = q * 32 + c8 * 8 + e2 * 2;
+            float a = __uint_as_float(r[c8 * 8 + e2 * 2]) * ex2(my_cum2 - s.cum2[j]) * s.dtv[j];
+            float bb = __uint_as_float(r[c8 * 8 + e2 * 2 + 1]) * ex2(my_cum2 - s.cum2[j + 1]) * s.dtv[j + 1];
+            if (j > l) a = 0.f;
+            if (j + 1 > l) bb = 0.f;
+            w[e2] = pack2(a, bb);
+          }
+          const int chunk = (q & 1) * 4 + c8;
+          sts128(panel + ((chunk ^ (l & 7)) << 4), make_uint4(w[0], w[1], w[2], w[3]));
+        }
+      }
+      // C row l scaled by exp(cum_l) for the incoming-state term
+      const float fc = ex2(my_cum2);
+#pragma unroll
+      for (int q = 0; q < N / 64; ++q) scale_row(smem_u32(s.ct[q]), l, fc);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.bar_w);
+      ok = mbar_wait(&s.bar_y, 0, abortp, p.status, 57);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      fence_after_sync();
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + 128, r0);
+      tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + 160, r1);
+      tmem_ld_wait();
+      const float dsk = p.d_skip ? p.d_skip[h] : 0.f;
+      const uint32_t xrow = smem_u32(s.xt) + l * 128;
+      uint4* dst = reinterpret_cast<uint4*>(p.y + ((int64_t)row0 + l) * (p.heads * P) + h * P);
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) {
+        const uint4 xv = lds128(xrow + ((ch ^ (l & 7)) << 4));
+        const uint32_t* rr = ch < 4 ? r0 + ch * 8 : r1 + (ch - 4) * 8;
+        const float2 x0 = unpack2(xv.x), x1 = unpack2(xv.y), x2 = unpack2(xv.z), x3 = unpack2(xv.w);
+        uint4 o;
+        o.x = pack2(__uint_as_float(rr[0]) + dsk * x0.x, __uint_as_float(rr[1]) + dsk * x0.y);
+        o.y = pack2(__uint_as_float(rr[2]) + dsk * x1.x, __uint_as_float(rr[3]) + dsk * x1.y);
+        o.z = pack2(__uint_as_float(rr[4]) + dsk * x2.x, __uint_as_float(rr[5]) + dsk * x2.y);
+        o.w = pack2(__uint_as_float(rr[6]) + dsk * x3.x, __uint_as_float(rr[7]) + dsk * x3.y);
+        dst[ch] = o;
+      }
+    }
+  }
+  __syncwarp();
+  if (s.abort_flag) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    fence_after_sync();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+        res == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// [rows, width] bf16 row-major, boxes of box_rows x 64 columns, 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t width, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return 801;
+  cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
+}
+
+template <typename K>
+static int set_smem(K kernel, size_t bytes) {
+  return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+template <int N>
+static int run(const void* x, const void* bm, const void* cm, const float* dt, const float* cum, const float* d_skip,
+               const float* init_state, float* states, void* prev, float* final_state, void* y, int batch, int seq_len,
+               int heads, int groups, int* status, cudaStream_t st) {
+  const int chunks = seq_len / L;
+  const int64_t rows = (int64_t)batch * seq_len;
+  CUtensorMap mx, mb, mc, mp;
+  int rc = make_map(&mx, x, rows, (int64_t)heads * P, L);
+  if (rc) return rc;
+  rc = make_map(&mb, bm, rows, (int64_t)groups * N, L);
+  if (rc) return rc;
+  rc = make_map(&mc, cm, rows, (int64_t)groups * N, L);
+  if (rc) return rc;
+  rc = make_map(&mp, prev, (int64_t)batch * chunks * heads * P, N, P);
+  if (rc) return rc;
+  {
+    StateParams p{seq_len, heads, groups, chunks, dt, cum, states, status};
+    const size_t smem = sizeof(SmemState<N>) + 1024;
+    rc = set_smem(chunk_state_kernel<N>, smem);
+    if (rc) return rc;
+    chunk_state_kernel<N><<<dim3(chunks, heads / 2, batch), THREADS, smem, st>>>(mx, mb, p);
+    rc = (int)cudaGetLastError();
+    if (rc) return rc;
+  }
+  {
+    const int elems = P * N;
+    const int64_t total = (int64_t)batch * heads * elems;
+    state_passing_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(states, cum, init_state, (__nv_bfloat16*)prev,
+                                                                         final_state, batch, heads, chunks, seq_len, elems);
+    rc = (int)cudaGetLastError();
+    if (rc) return rc;
+  }
+  {
+    ScanParams p{seq_len, heads, groups, chunks, dt, cum, d_skip, (__nv_bfloat16*)y, status};
+    const size_t smem = sizeof(SmemScan<N>) + 1024;
+    rc = set_smem(chunk_scan_kernel<N>, smem);
+    if (rc) return rc;
+    chunk_scan_kernel<N><<<dim3(chunks, heads, batch), THREADS, smem, st>>>(mx, mb, mc, mp, p);
+    rc = (int)cudaGetLastError();
+  }
+  return rc;
+}
+
+}  // namespace ssd
+}  // namespace lbi
+
+extern "C" int lbi_ssd_cumsum(const float* dt_raw, const float* dt_bias, const float* a, float* dt_out, float* cum, int batch,
+                              int seq_len, int heads, int softplus, float dt_min, float dt_max, cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (seq_len % L != 0 || batch <= 0 || heads <= 0) return (int)cudaErrorInvalidValue;
+  cumsum_kernel<<<dim3(seq_len / L, heads, batch), 128, 0, st>>>(dt_raw, dt_bias, a, dt_out, cum, seq_len, heads, softplus,
+                                                                 dt_min, dt_max);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_ssd_chunk_scan_fwd(const void* x, const void* bm, const void* cm, const float* dt, const float* cum,
+                                      const float* d_skip, const float* init_state, float* states, void* prev,
+                                      float* final_state, void* y, int batch, int seq_len, int heads, int groups, int head_dim,
+                                      int d_state, int* status, cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (head_dim != P || seq_len % L != 0 || batch <= 0 || heads <= 0 || groups <= 0 || heads % groups != 0 ||
+      (heads / groups) % 2 != 0 || (int64_t)batch * seq_len >= (1ll << 31))
+    return (int)cudaErrorInvalidValue;
+  if (d_state == 64)
+    return run<64>(x, bm, cm, dt, cum, d_skip, init_state, states, prev, final_state, y, batch, seq_len, heads, groups, status, st);
+  if (d_state == 128)
+    return run<128>(x, bm, cm, dt, cum, d_skip, init_state, states, prev, final_state, y, batch, seq_len, heads, groups, status, st);
+  return (int)cudaErrorInvalidValue;
+}

@@ -57,7 +57,7 @@ class SymmComm(CollectiveComm):
         self.use_multimem = os.environ.get("LBI_B200_MULTIMEM", "0") == "1"
         self._flat_state = None
         self._handle_keepalive = []
-        self.barrier()
+        self._setup_barrier()
 
     # ------------------------------------------------------------------ symmetric allocation
     def _alloc(self, numel: int, dtype: torch.dtype):
@@ -77,6 +77,11 @@ class SymmComm(CollectiveComm):
         return t, self._table(handle), mc
 
     # ------------------------------------------------------------------ barrier
+    def _setup_barrier(self) -> None:
+        """Barrier for set-up points, where ranks may be far apart (imports, allocation): meet on the host first."""
+        dist.barrier(group=self.group)
+        self.barrier()
+
     def barrier(self) -> None:
         self.seq += 1
         ops.ext().peer_barrier(self.flag_ptrs, self.rank, self.world_size, _SLOT_BARRIER * self.world_size, self.seq)
@@ -92,7 +97,7 @@ class SymmComm(CollectiveComm):
             t, handle = self._alloc(numel, torch.float32)
             hit = (t.view(*shape), [int(p) for p in handle.buffer_ptrs], handle)
             self._mailboxes[key] = hit
-            self.barrier()
+            self._setup_barrier()
         return hit
 
     def prepare(self, batch: int, width: int) -> None:
@@ -142,7 +147,7 @@ class SymmComm(CollectiveComm):
             o_buf, oh = self._alloc(offsets.numel(), torch.float32)
             hit = (m_buf, o_buf, self._table(mh), self._table(oh), mh, oh)
             self._scan_bufs[key] = hit
-            self.barrier()
+            self._setup_barrier()
         m_buf, o_buf, m_ptrs, o_ptrs, _, _ = hit
         # peers may still be reading last step's matrices: the barrier at the end of the optimizer step orders that
         m_buf.copy_(mats.reshape(-1))
@@ -166,7 +171,7 @@ class SymmComm(CollectiveComm):
             shadow.copy_(flat.shadow)
             flat.shadow = shadow
         self._flat_state = (g_ptrs, g_mc if self.use_multimem else 0, shadow_ptrs)
-        self.barrier()
+        self._setup_barrier()
 
     def optimizer_step(self, flat, *, lr, betas, eps, weight_decay, grad_clip) -> None:
         g_ptrs, g_mc, shadow_ptrs = self._flat_state

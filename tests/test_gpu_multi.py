@@ -38,7 +38,10 @@ def _worker(rank, world, port, axis, plane, out_dir):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    import datetime
+
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
     try:
         from lbi_b200 import ops
         from lbi_b200.parallel import CollectiveComm, FastLBIEngine
