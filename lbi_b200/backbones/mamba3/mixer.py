@@ -11,11 +11,13 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
+from functools import partial
 
 import torch
 import torch.nn.functional as F
 from torch import nn
 
+from ...ops import ssd as ops_ssd
 from ..norms import RMSNormGated
 from .siso import mamba3_siso_chunked
 
@@ -119,7 +121,9 @@ class Mamba3(nn.Module):
         DT = DT.transpose(1, 2)
         trap_t = trap.transpose(1, 2)
         angles_h = angles.unsqueeze(-2).expand(-1, -1, self.nheads, -1)
-        y = mamba3_siso_chunked(
+        use_kernels = ops_ssd.siso_cuda_supported(x, C) and x.dtype == torch.bfloat16 and self.D is not None
+        siso = ops_ssd.mamba3_siso_cuda if use_kernels else partial(mamba3_siso_chunked, chunk_size=self.chunk_size)
+        y = siso(
             Q=C,
             K=B,
             V=x,
@@ -131,7 +135,6 @@ class Mamba3(nn.Module):
             Angles=angles_h,
             D=self.D,
             Z=None if self.is_outproj_norm else z,
-            chunk_size=self.chunk_size,
         )
         y = y.reshape(bsz, seqlen, self.d_inner)
         if self.is_outproj_norm:

@@ -70,14 +70,22 @@ def propagate_state_adjoint_by_chain(state_jacobian_t: Sequence[torch.Tensor], o
     return out
 
 
+def _matrix_norms(mats: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """(spectral, Frobenius) norms of [..., R, R]; on CUDA one kernel (power iteration), else torch.linalg."""
+    from .. import ops
+
+    if mats.is_cuda and ops.native_available() and hasattr(ops.ext(), "matrix_norms"):
+        return ops.ext().matrix_norms(mats.float().contiguous(), 96)
+    return torch.linalg.matrix_norm(mats, ord=2), torch.linalg.matrix_norm(mats, ord="fro")
+
+
 def interface_state_jacobian_t_stats(state_jacobian_t: Sequence[torch.Tensor], *, include_suffix: bool = False) -> dict[str, float]:
     """Frobenius / spectral norms of the local Jacobians (and optionally of the suffix products)."""
     if len(state_jacobian_t) == 0:
         return {}
     mats = torch.stack([m.float() for m in state_jacobian_t], dim=1)  # [B, K, R, R]
     r = mats.shape[-1]
-    spec = torch.linalg.matrix_norm(mats, ord=2)
-    frob = torch.linalg.matrix_norm(mats, ord="fro")
+    spec, frob = _matrix_norms(mats)
     stats = {
         "jac_local_spec_mean": float(spec.mean()),
         "jac_local_spec_max": float(spec.max()),
@@ -87,7 +95,7 @@ def interface_state_jacobian_t_stats(state_jacobian_t: Sequence[torch.Tensor], *
     }
     if include_suffix:
         suffix = torch.stack(compose_suffix_jacobian_t(list(state_jacobian_t))[:-1], dim=1)
-        sspec = torch.linalg.matrix_norm(suffix, ord=2)
+        sspec = _matrix_norms(suffix)[0]
         stats["jac_suffix_spec_mean"] = float(sspec.mean())
         stats["jac_suffix_spec_max"] = float(sspec.max())
     return stats

@@ -55,6 +55,8 @@ int lbi_ce_fwd_bwd(void* logits_bf16, const int64_t* targets, float* loss_sum, i
 // out[b, k] = mats[b, k] @ mats[b, k+1] @ ... @ mats[b, K-1], out[b, K] = I;  mats [B, K, R, R] fp32 row-major.
 int lbi_suffix_scan(const float* mats, float* out, int batch, int k, int r, cudaStream_t stream);
 // g[b, k] = offsets[b, k] + mats[b, k] @ g[b, k+1], g[b, K] = seed (or 0);  g [B, K+1, R].
+// Frobenius and spectral norms (power iteration, `iters` rounds) of `count` fp32 R x R matrices.
+int lbi_matrix_norms(const float* mats, float* spec, float* frob, int count, int r, int iters, cudaStream_t stream);
 int lbi_affine_suffix_scan(const float* mats, const float* offsets, const float* seed_or_null, float* g, int batch, int k,
                            int r, cudaStream_t stream);
 

@@ -21,6 +21,16 @@ int lbi_ssd_chunk_scan_fwd(const void* x, const void* bm, const void* cm, const 
                            void* y, int batch, int seq_len, int heads, int groups, int head_dim, int d_state, int* status,
                            cudaStream_t stream);
 
+// Mamba-3 SISO chunk scan on preprocessed operands (per-head rotated / biased / scaled):
+//   h_t = exp(adt_t) h_{t-1} + v_t kr_t^T ,   y_t = qr_t . (exp(adt_t) h_{t-1}) + (d_skip[h] + skip_tok[t]) v_t
+// v [B*L, H*64] bf16, kr / qr [B*L, H*128] bf16, cum [B, H, L] fp32 = in-chunk cumulative sum of adt (lbi_ssd_cumsum
+// with a = 1), skip_tok [B, H, L] fp32.  States are kept [n][p]: states / prev [B, L/128, H, 128, 64], init / final
+// [B, H, 128, 64].  head_dim 64, d_state 128.
+int lbi_siso_chunk_scan_fwd(const void* v, const void* kr, const void* qr, const float* cum, const float* d_skip,
+                            const float* skip_tok, const float* init_state, float* states, void* prev, float* final_state,
+                            void* y, int batch, int seq_len, int heads, int head_dim, int d_state, int* status,
+                            cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -452,20 +452,20 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           const int col0 = slice * 32;
           const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse_r, -lse_r);
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
+          for (int i = 0; i < 16; ++i) {
+            const float2 t = unpack_f32x2(fma_f32x2(pack_u32x2(v[2 * i], v[2 * i + 1]), sc2, nl2));
+            preg[i] = cvt_bf16x2(pack_f32x2(fast_exp2(t.x), fast_exp2(t.y)));
+          }
+          if (diagonal) {   // warp-uniform: only the tile on the diagonal pays for the causal mask
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int col = col0 + g * 8 + e * 2;
-              const float2 t = unpack_f32x2(fma_f32x2(pack_u32x2(v[g * 8 + e * 2], v[g * 8 + e * 2 + 1]), sc2, nl2));
-              float a = fast_exp2(t.x);
-              float bb = fast_exp2(t.y);
-              if (diagonal) {
-                if (col > r) a = 0.f;
-                if (col + 1 > r) bb = 0.f;
-              }
-              preg[g * 4 + e] = pack_bf16(a, bb);
+            for (int i = 0; i < 16; ++i) {
+              const int col = col0 + 2 * i;
+              preg[i] &= (col <= r ? 0x0000ffffu : 0u) | (col + 1 <= r ? 0xffff0000u : 0u);
             }
-            if (DKDV)
+          }
+          if (DKDV) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
               st_shared_v4(swz(p_panel, r, (slice & 1) * 4 + g),
                            make_uint4(preg[g * 4], preg[g * 4 + 1], preg[g * 4 + 2], preg[g * 4 + 3]));
           }

@@ -250,6 +250,22 @@ Tensor suffix_scan(const Tensor& mats) {
   return out;
 }
 
+// mats [..., R, R] fp32 -> (spectral norms, Frobenius norms), each shaped like the leading dimensions.
+std::tuple<Tensor, Tensor> matrix_norms(const Tensor& mats, int64_t iters) {
+  CHECK_F32(mats);
+  c10::cuda::CUDAGuard guard(mats.device());
+  TORCH_CHECK(mats.dim() >= 2 && mats.size(-1) == mats.size(-2), "matrix_norms: expected [..., R, R]");
+  const int64_t r = mats.size(-1);
+  const int64_t count = mats.numel() / (r * r);
+  auto lead = mats.sizes().vec();
+  lead.resize(lead.size() - 2);
+  Tensor spec = torch::empty(lead, mats.options()), frob = torch::empty(lead, mats.options());
+  check(lbi_matrix_norms(mats.data_ptr<float>(), spec.data_ptr<float>(), frob.data_ptr<float>(), (int)count, (int)r, (int)iters,
+                         cur_stream()),
+        "matrix_norms");
+  return {spec, frob};
+}
+
 Tensor affine_suffix_scan(const Tensor& mats, const Tensor& offsets, const c10::optional<Tensor>& seed) {
   CHECK_F32(mats);
   CHECK_F32(offsets);
@@ -373,6 +389,40 @@ std::tuple<Tensor, Tensor> ssd_chunk_scan_fwd(const Tensor& x, const Tensor& dt_
                                states.data_ptr<float>(), prev.data_ptr(), final_state.data_ptr<float>(), y.data_ptr(), (int)batch,
                                (int)seq, (int)heads, (int)groups, (int)hd, (int)n, st.data_ptr<int>(), cur_stream()),
         "ssd_chunk_scan_fwd");
+  return {y, final_state};
+}
+
+// Mamba-3 SISO chunk scan forward on preprocessed operands.  v [B, L, H, 64] bf16, kr / qr [B, L, H, 128] bf16,
+// adt [B, L, H] fp32, skip_tok [B, H, L] fp32, d_skip [H] fp32.  Returns (y [B, L, H, 64] bf16, final_state [B, H, 128, 64]).
+std::tuple<Tensor, Tensor> siso_chunk_scan_fwd(const Tensor& v, const Tensor& kr, const Tensor& qr, const Tensor& adt,
+                                               const c10::optional<Tensor>& d_skip, const c10::optional<Tensor>& skip_tok,
+                                               const c10::optional<Tensor>& init_state) {
+  CHECK_BF16(v);
+  CHECK_BF16(kr);
+  CHECK_BF16(qr);
+  CHECK_F32(adt);
+  c10::cuda::CUDAGuard guard(v.device());
+  TORCH_CHECK(v.dim() == 4 && kr.dim() == 4 && qr.sizes() == kr.sizes() && adt.dim() == 3, "siso: expected v [B,L,H,P], kr/qr [B,L,H,N], adt [B,L,H]");
+  const int64_t batch = v.size(0), seq = v.size(1), heads = v.size(2), hd = v.size(3), n = kr.size(3);
+  TORCH_CHECK(kr.size(2) == heads && adt.size(1) == seq && adt.size(2) == heads, "siso: shape mismatch");
+  const int64_t chunks = seq / 128;
+  auto f32 = v.options().dtype(at::kFloat);
+  Tensor ones = torch::ones({heads}, f32);
+  Tensor dt = torch::empty({batch, heads, seq}, f32), cum = torch::empty({batch, heads, seq}, f32);
+  Tensor states = torch::empty({batch, chunks, heads, n, hd}, f32);
+  Tensor prev = torch::empty({batch, chunks, heads, n, hd}, v.options());
+  Tensor final_state = torch::empty({batch, heads, n, hd}, f32);
+  Tensor y = torch::empty_like(v);
+  Tensor st = status_word(v);
+  check(lbi_ssd_cumsum(adt.data_ptr<float>(), nullptr, ones.data_ptr<float>(), dt.data_ptr<float>(), cum.data_ptr<float>(), (int)batch,
+                       (int)seq, (int)heads, 0, 0.f, 0.f, cur_stream()),
+        "siso_cumsum");
+  check(lbi_siso_chunk_scan_fwd(v.data_ptr(), kr.data_ptr(), qr.data_ptr(), cum.data_ptr<float>(),
+                                d_skip ? d_skip->data_ptr<float>() : nullptr, skip_tok ? skip_tok->data_ptr<float>() : nullptr,
+                                init_state ? init_state->data_ptr<float>() : nullptr, states.data_ptr<float>(), prev.data_ptr(),
+                                final_state.data_ptr<float>(), y.data_ptr(), (int)batch, (int)seq, (int)heads, (int)hd, (int)n,
+                                st.data_ptr<int>(), cur_stream()),
+        "siso_chunk_scan_fwd");
   return {y, final_state};
 }
 
@@ -519,12 +569,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ce_fwd_bwd_", &ce_fwd_bwd_);
   m.def("suffix_scan", &suffix_scan);
   m.def("affine_suffix_scan", &affine_suffix_scan);
+  m.def("matrix_norms", &matrix_norms);
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("a_t") = false, py::arg("b_t") = false,
         py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);
   m.def("gemm_tn", &gemm_tn);
   m.def("attn_pullback_packed", &attn_pullback_packed);
   m.def("attn_fwd_packed", &attn_fwd_packed);
   m.def("ssd_chunk_scan_fwd", &ssd_chunk_scan_fwd);
+  m.def("siso_chunk_scan_fwd", &siso_chunk_scan_fwd);
   m.def("kernel_status", &kernel_status);
   m.def("set_peer_wait_limit_ms", &set_peer_wait_limit_ms);
   m.def("peer_barrier", &peer_barrier);

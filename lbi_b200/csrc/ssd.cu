@@ -101,9 +101,11 @@ __global__ void __launch_bounds__(128) cumsum_kernel(const float* __restrict__ d
 }
 
 // ------------------------------------------------------------------------------------------------ 2. chunk state
+// PH ("per head"): B and C are given per head (Mamba-3 after its rotary / bias preprocessing) instead of per group.  Then
+// one CTA owns one head, the product is taken as S^T[n, p] (M = d_state = 128) and states are stored [n][p].
 template <int N>
 struct SmemState {
-  alignas(1024) uint8_t xs[2][PANEL];          // x of two heads: [l][64 p] per panel
+  alignas(1024) uint8_t xs[2][PANEL];          // x of two heads (PH: of one head): [l][64 p] per panel
   alignas(1024) uint8_t bt[N / 64][PANEL];     // B: [l][64 n] per panel
   uint64_t bar_full, bar_scaled, bar_done;
   uint32_t tmem_base;
@@ -118,17 +120,17 @@ struct StateParams {
   int* status;
 };
 
-template <int N>
+template <int N, bool PH>
 __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_constant__ CUtensorMap map_x,
                                                               const __grid_constant__ CUtensorMap map_b, const StateParams p) {
   extern __shared__ uint8_t raw_smem[];
   SmemState<N>& s = *reinterpret_cast<SmemState<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x, hp = blockIdx.y, b = blockIdx.z;
-  const int h0 = 2 * hp;
-  const int g = h0 / (p.heads / p.groups);
+  const int h0 = PH ? hp : 2 * hp;
+  const int g = PH ? h0 : h0 / (p.heads / p.groups);
   const int row0 = b * p.seq_len + c * L;
-  constexpr uint32_t TMEM_COLS = N;   // 64 or 128: a power of two >= 32
+  constexpr uint32_t TMEM_COLS = PH ? 64 : N;   // a power of two >= 32
 
   if (threadIdx.x == 0) {
     s.abort_flag = 0;
@@ -148,17 +150,18 @@ __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_const
 
   if (warp == 4) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(&s.bar_full, (2 + N / 64) * PANEL);
+      mbar_arrive_expect_tx(&s.bar_full, ((PH ? 1 : 2) + N / 64) * PANEL);
       tma_load_2d(s.xs[0], &map_x, &s.bar_full, h0 * P, row0);
-      tma_load_2d(s.xs[1], &map_x, &s.bar_full, (h0 + 1) * P, row0);
+      if (!PH) tma_load_2d(s.xs[1], &map_x, &s.bar_full, (h0 + 1) * P, row0);
       for (int q = 0; q < N / 64; ++q) tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, row0);
       bool ok = mbar_wait(&s.bar_scaled, 0, abortp, p.status, 51);
       if (ok) {
         fence_after_sync();
         // D[(h, p), n] = sum_l xs[l, (h, p)] * bt[l, n]: both operands have the reduction index as their row
-        const uint32_t idesc = make_idesc_bf16(128, N, 1, 1);
-        const uint64_t da = make_smem_desc(smem_u32(s.xs[0]), PANEL, 1024);
-        const uint64_t db = make_smem_desc(smem_u32(s.bt[0]), PANEL, 1024);
+        // (PH: D[n, p] = sum_l bt[l, n] * xs[l, p], the roles of the two tiles swapped)
+        const uint32_t idesc = make_idesc_bf16(128, PH ? 64 : N, 1, 1);
+        const uint64_t da = make_smem_desc(smem_u32(PH ? s.bt[0] : s.xs[0]), PANEL, 1024);
+        const uint64_t db = make_smem_desc(smem_u32(PH ? s.xs[0] : s.bt[0]), PANEL, 1024);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) mma_bf16(tmem, da + 128 * kk, db + 128 * kk, idesc, kk);
         mma_commit(&s.bar_done);
@@ -168,13 +171,13 @@ __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_const
     const int l = warp * 32 + lane;   // token of the chunk handled in the scaling pass; row (h, p) in the epilogue
     const int64_t base0 = ((int64_t)b * p.heads + h0) * p.seq_len + c * L;
     const int64_t base1 = base0 + p.seq_len;
-    const float f0 = ex2((p.cum[base0 + L - 1] - p.cum[base0 + l]) * LOG2E) * p.dt[base0 + l];
-    const float f1 = ex2((p.cum[base1 + L - 1] - p.cum[base1 + l]) * LOG2E) * p.dt[base1 + l];
+    const float f0 = ex2((p.cum[base0 + L - 1] - p.cum[base0 + l]) * LOG2E) * (p.dt ? p.dt[base0 + l] : 1.f);
+    const float f1 = PH ? 0.f : ex2((p.cum[base1 + L - 1] - p.cum[base1 + l]) * LOG2E) * (p.dt ? p.dt[base1 + l] : 1.f);
     bool ok = mbar_wait(&s.bar_full, 0, abortp, p.status, 52);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       scale_row(smem_u32(s.xs[0]), l, f0);
-      scale_row(smem_u32(s.xs[1]), l, f1);
+      if (!PH) scale_row(smem_u32(s.xs[1]), l, f1);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.bar_scaled);
@@ -183,10 +186,12 @@ __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_const
     }
     if (ok) {
       fence_after_sync();
-      const int h = h0 + (l >> 6), pp = l & 63;
-      float* dst = p.states + ((((int64_t)b * p.chunks + c) * p.heads + h) * P + pp) * N;
+      // rows of D: (head, p) with N columns, or (PH) n with 64 columns
+      const int h = PH ? h0 : h0 + (l >> 6), pp = l & 63;
+      float* dst = PH ? p.states + ((((int64_t)b * p.chunks + c) * p.heads + h) * N + l) * P
+                      : p.states + ((((int64_t)b * p.chunks + c) * p.heads + h) * P + pp) * N;
 #pragma unroll
-      for (int q = 0; q < N / 32; ++q) {
+      for (int q = 0; q < (PH ? P : N) / 32; ++q) {
         uint32_t r[32];
         tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + q * 32, r);
         tmem_ld_wait();
@@ -247,14 +252,16 @@ struct SmemScan {
 
 struct ScanParams {
   int seq_len, heads, groups, chunks;
-  const float* dt;
+  const float* dt;        // null: weight 1 (already folded into B)
   const float* cum;
   const float* d_skip;    // [H] or null
+  const float* skip_tok;  // [B, H, L] per-token skip coefficient added to d_skip, or null
+  int strict;             // 1: token l sees tokens j < l through the scores (its own term comes with the skip)
   __nv_bfloat16* y;       // [B*L, H*64]
   int* status;
 };
 
-template <int N>
+template <int N, bool PH>
 __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_constant__ CUtensorMap map_x,
                                                              const __grid_constant__ CUtensorMap map_b,
                                                              const __grid_constant__ CUtensorMap map_c,
@@ -263,7 +270,7 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
   SmemScan<N>& s = *reinterpret_cast<SmemScan<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int g = h / (p.heads / p.groups);
+  const int g = PH ? h : h / (p.heads / p.groups);
   const int row0 = b * p.seq_len + c * L;
   constexpr int KS = N / 16;           // K = 16 slices over d_state
   constexpr uint32_t PANEL16 = PANEL >> 4, PV16 = (P * 128) >> 4;
@@ -293,8 +300,10 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
       for (int q = 0; q < N / 64; ++q) {
         tma_load_2d(s.ct[q], &map_c, &s.bar_full, g * N + q * 64, row0);
         tma_load_2d(s.bw[q], &map_b, &s.bar_full, g * N + q * 64, row0);
-        tma_load_2d(s.pv[q], &map_prev, &s.bar_full, q * 64, (int)((((int64_t)b * p.chunks + c) * p.heads + h) * P));
+        if (!PH) tma_load_2d(s.pv[q], &map_prev, &s.bar_full, q * 64, (int)((((int64_t)b * p.chunks + c) * p.heads + h) * P));
       }
+      if (PH)  // incoming state stored [n][p]: one 128-row tile
+        tma_load_2d(s.pv[0], &map_prev, &s.bar_full, 0, (int)((((int64_t)b * p.chunks + c) * p.heads + h) * N));
       tma_load_2d(s.xt, &map_x, &s.bar_full, h * P, row0);
       const uint64_t kmajor0 = make_smem_desc(0, 16, 1024), mnmajor0 = make_smem_desc(0, PANEL, 1024);
       const uint32_t ct16 = smem_u32(s.ct[0]) >> 4, bw16 = smem_u32(s.bw[0]) >> 4, xt16 = smem_u32(s.xt) >> 4,
@@ -316,11 +325,12 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           mma_bf16(tmem + 128, kmajor0 + bw16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, mnmajor0 + xt16 + 128 * kk, idesc_y, kk);
-        const uint32_t idesc_s = make_idesc_bf16(128, 64, 0, 0);   // scaled C (K-major) x incoming state [p][n] (K-major)
+        // scaled C (K-major) x incoming state: [p][n] K-major, or (PH) [n][p] with the reduction index as the row
+        const uint32_t idesc_s = make_idesc_bf16(128, 64, 0, PH ? 1 : 0);
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk)
-          mma_bf16(tmem + 128, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, kmajor0 + pv16 + (kk >> 2) * PV16 + (kk & 3) * 2,
-                   idesc_s, 1);
+          mma_bf16(tmem + 128, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   PH ? mnmajor0 + pv16 + 128 * kk : kmajor0 + pv16 + (kk >> 2) * PV16 + (kk & 3) * 2, idesc_s, 1);
         mma_commit(&s.bar_y);
       }
     }
@@ -329,7 +339,7 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
     const int64_t base = ((int64_t)b * p.heads + h) * p.seq_len + c * L;
     const float my_cum2 = p.cum[base + l] * LOG2E;
     s.cum2[l] = my_cum2;
-    s.dtv[l] = p.dt[base + l];
+    s.dtv[l] = p.dt ? p.dt[base + l] : 1.f;
     named_barrier_sync(1, 128);
     bool ok = mbar_wait(&s.bar_g, 0, abortp, p.status, 56);
     ok = __all_sync(0xffffffffu, ok);
@@ -351,8 +361,8 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
             const int j = q * 32 + c8 * 8 + e2 * 2;
             float a = __uint_as_float(r[c8 * 8 + e2 * 2]) * ex2(my_cum2 - s.cum2[j]) * s.dtv[j];
             float bb = __uint_as_float(r[c8 * 8 + e2 * 2 + 1]) * ex2(my_cum2 - s.cum2[j + 1]) * s.dtv[j + 1];
-            if (j > l) a = 0.f;
-            if (j + 1 > l) bb = 0.f;
+            if (j + p.strict > l) a = 0.f;
+            if (j + 1 + p.strict > l) bb = 0.f;
             w[e2] = pack2(a, bb);
           }
           const int chunk = (q & 1) * 4 + c8;
@@ -375,7 +385,7 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
       tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + 128, r0);
       tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + 160, r1);
       tmem_ld_wait();
-      const float dsk = p.d_skip ? p.d_skip[h] : 0.f;
+      const float dsk = (p.d_skip ? p.d_skip[h] : 0.f) + (p.skip_tok ? p.skip_tok[base + l] : 0.f);
       const uint32_t xrow = smem_u32(s.xt) + l * 128;
       uint4* dst = reinterpret_cast<uint4*>(p.y + ((int64_t)row0 + l) * (p.heads * P) + h * P);
 #pragma unroll
@@ -442,27 +452,28 @@ static int set_smem(K kernel, size_t bytes) {
   return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-template <int N>
+template <int N, bool PH>
 static int run(const void* x, const void* bm, const void* cm, const float* dt, const float* cum, const float* d_skip,
-               const float* init_state, float* states, void* prev, float* final_state, void* y, int batch, int seq_len,
-               int heads, int groups, int* status, cudaStream_t st) {
+               const float* skip_tok, int strict, const float* init_state, float* states, void* prev, float* final_state,
+               void* y, int batch, int seq_len, int heads, int groups, int* status, cudaStream_t st) {
   const int chunks = seq_len / L;
   const int64_t rows = (int64_t)batch * seq_len;
   CUtensorMap mx, mb, mc, mp;
   int rc = make_map(&mx, x, rows, (int64_t)heads * P, L);
   if (rc) return rc;
-  rc = make_map(&mb, bm, rows, (int64_t)groups * N, L);
+  rc = make_map(&mb, bm, rows, (int64_t)(PH ? heads : groups) * N, L);
   if (rc) return rc;
-  rc = make_map(&mc, cm, rows, (int64_t)groups * N, L);
+  rc = make_map(&mc, cm, rows, (int64_t)(PH ? heads : groups) * N, L);
   if (rc) return rc;
-  rc = make_map(&mp, prev, (int64_t)batch * chunks * heads * P, N, P);
+  rc = PH ? make_map(&mp, prev, (int64_t)batch * chunks * heads * N, P, N)
+          : make_map(&mp, prev, (int64_t)batch * chunks * heads * P, N, P);
   if (rc) return rc;
   {
     StateParams p{seq_len, heads, groups, chunks, dt, cum, states, status};
     const size_t smem = sizeof(SmemState<N>) + 1024;
-    rc = set_smem(chunk_state_kernel<N>, smem);
+    rc = set_smem(chunk_state_kernel<N, PH>, smem);
     if (rc) return rc;
-    chunk_state_kernel<N><<<dim3(chunks, heads / 2, batch), THREADS, smem, st>>>(mx, mb, p);
+    chunk_state_kernel<N, PH><<<dim3(chunks, PH ? heads : heads / 2, batch), THREADS, smem, st>>>(mx, mb, p);
     rc = (int)cudaGetLastError();
     if (rc) return rc;
   }
@@ -475,11 +486,11 @@ static int run(const void* x, const void* bm, const void* cm, const float* dt, c
     if (rc) return rc;
   }
   {
-    ScanParams p{seq_len, heads, groups, chunks, dt, cum, d_skip, (__nv_bfloat16*)y, status};
+    ScanParams p{seq_len, heads, groups, chunks, dt, cum, d_skip, skip_tok, strict, (__nv_bfloat16*)y, status};
     const size_t smem = sizeof(SmemScan<N>) + 1024;
-    rc = set_smem(chunk_scan_kernel<N>, smem);
+    rc = set_smem(chunk_scan_kernel<N, PH>, smem);
     if (rc) return rc;
-    chunk_scan_kernel<N><<<dim3(chunks, heads, batch), THREADS, smem, st>>>(mx, mb, mc, mp, p);
+    chunk_scan_kernel<N, PH><<<dim3(chunks, heads, batch), THREADS, smem, st>>>(mx, mb, mc, mp, p);
     rc = (int)cudaGetLastError();
   }
   return rc;
@@ -506,8 +517,21 @@ extern "C" int lbi_ssd_chunk_scan_fwd(const void* x, const void* bm, const void*
       (heads / groups) % 2 != 0 || (int64_t)batch * seq_len >= (1ll << 31))
     return (int)cudaErrorInvalidValue;
   if (d_state == 64)
-    return run<64>(x, bm, cm, dt, cum, d_skip, init_state, states, prev, final_state, y, batch, seq_len, heads, groups, status, st);
+    return run<64, false>(x, bm, cm, dt, cum, d_skip, nullptr, 0, init_state, states, prev, final_state, y, batch, seq_len, heads,
+                          groups, status, st);
   if (d_state == 128)
-    return run<128>(x, bm, cm, dt, cum, d_skip, init_state, states, prev, final_state, y, batch, seq_len, heads, groups, status, st);
+    return run<128, false>(x, bm, cm, dt, cum, d_skip, nullptr, 0, init_state, states, prev, final_state, y, batch, seq_len, heads,
+                           groups, status, st);
   return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int lbi_siso_chunk_scan_fwd(const void* v, const void* kr, const void* qr, const float* cum, const float* d_skip,
+                                       const float* skip_tok, const float* init_state, float* states, void* prev,
+                                       float* final_state, void* y, int batch, int seq_len, int heads, int head_dim,
+                                       int d_state, int* status, cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (head_dim != P || d_state != 128 || seq_len % L != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * seq_len >= (1ll << 31))
+    return (int)cudaErrorInvalidValue;
+  return run<128, true>(v, kr, qr, nullptr, cum, d_skip, skip_tok, 1, init_state, states, prev, final_state, y, batch, seq_len,
+                        heads, heads, status, st);
 }

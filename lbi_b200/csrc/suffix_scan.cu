@@ -119,9 +119,64 @@ __global__ void __launch_bounds__(256) affine_suffix_scan_kernel(const float* __
   }
 }
 
+// Frobenius and spectral norm of each R x R matrix (interface-Jacobian diagnostics).  One CTA per matrix; the spectral
+// norm is the square root of the top eigenvalue of A^T A found by power iteration from a fixed non-degenerate start
+// vector, with the Rayleigh quotient of the last iterate as the estimate.  Dynamic smem: 2 * r floats.
+__global__ void __launch_bounds__(256) matrix_norms_kernel(const float* __restrict__ mats, float* __restrict__ spec,
+                                                           float* __restrict__ frob, int r, int iters) {
+  extern __shared__ float sm[];
+  __shared__ float scratch[33];
+  float* v = sm;        // current iterate (unit norm)
+  float* w = sm + r;    // A v
+  const float* a = mats + (size_t)blockIdx.x * r * r;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float part = 0.f;
+  for (int i = threadIdx.x; i < r * r; i += blockDim.x) part += a[i] * a[i];
+  const float f2 = block_sum(part, scratch);
+  if (threadIdx.x == 0) frob[blockIdx.x] = sqrtf(f2);
+  for (int i = threadIdx.x; i < r; i += blockDim.x) v[i] = rsqrtf((float)r) * (1.f + 0.37f * __sinf(1.7f * (float)i + 0.3f));
+  __syncthreads();
+  float sigma2 = 0.f;
+  for (int it = 0; it < iters; ++it) {
+    for (int row = warp; row < r; row += nwarps) {   // w = A v
+      float acc = 0.f;
+      for (int j = lane; j < r; j += 32) acc += a[(size_t)row * r + j] * v[j];
+      acc = warp_sum(acc);
+      if (lane == 0) w[row] = acc;
+    }
+    __syncthreads();
+    part = 0.f;
+    for (int i = threadIdx.x; i < r; i += blockDim.x) part += w[i] * w[i];
+    const float vv = block_sum(part, scratch);     // |A v|^2 with |v| = 1: Rayleigh quotient of A^T A
+    sigma2 = vv;
+    __syncthreads();
+    for (int col = threadIdx.x; col < r; col += blockDim.x) {   // v = A^T w (column access: coalesced over threads)
+      float acc = 0.f;
+      for (int i = 0; i < r; ++i) acc += a[(size_t)i * r + col] * w[i];
+      v[col] = acc;
+    }
+    __syncthreads();
+    part = 0.f;
+    for (int i = threadIdx.x; i < r; i += blockDim.x) part += v[i] * v[i];
+    const float n2 = block_sum(part, scratch);
+    const float inv = n2 > 0.f ? rsqrtf(n2) : 0.f;
+    for (int i = threadIdx.x; i < r; i += blockDim.x) v[i] *= inv;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) spec[blockIdx.x] = sqrtf(sigma2);
+}
+
 }  // namespace lbi
 
 extern "C" {
+
+int lbi_matrix_norms(const float* mats, float* spec, float* frob, int count, int r, int iters, cudaStream_t st) {
+  using namespace lbi;
+  if (count == 0) return 0;
+  if (r <= 0 || r > 4096 || iters <= 0) return (int)cudaErrorInvalidValue;
+  matrix_norms_kernel<<<count, 256, 2 * r * sizeof(float), st>>>(mats, spec, frob, r, iters);
+  return (int)cudaGetLastError();
+}
 
 int lbi_suffix_scan(const float* mats, float* out, int batch, int k, int r, cudaStream_t st) {
   using namespace lbi;

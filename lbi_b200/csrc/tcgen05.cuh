@@ -75,21 +75,33 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or the hint (nanoseconds)
+// runs out, instead of spinning through the instruction stream and taking issue slots from the warps that do the math.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Returns false after WAIT_LIMIT_NS; *status (global) receives `site` and *abort_flag (shared) is raised.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int site) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
-  uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3ff) == 0) {
-      if (*abort_flag) return false;
-      if (global_ns() - t0 > WAIT_LIMIT_NS) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, site);
-        return false;
-      }
+    if (mbar_try_wait_hint(bar, parity, 200000u)) return true;   // up to 0.2 ms asleep per attempt
+    if (*abort_flag) return false;
+    if (global_ns() - t0 > WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, site);
+      return false;
     }
   }
 }

@@ -81,3 +81,63 @@ def ssd_chunk_scan_cuda(x, dt, A, B, C, D=None, initial_state=None, return_final
         y, final = _forward_kernels(x, dt, A, B, C, D, initial_state)
         y = y.to(x.dtype)
     return (y, final) if return_final_state else y
+
+
+# ------------------------------------------------------------------------------------------------ Mamba-3 SISO
+def siso_cuda_supported(V: torch.Tensor, Q: torch.Tensor) -> bool:
+    """CUDA inputs with head_dim 64 and d_state 128 (the paper's Mamba-3 shape)."""
+    return bool(V.is_cuda and native_available() and hasattr(ext(), "siso_chunk_scan_fwd") and V.shape[3] == 64 and Q.shape[3] == 128)
+
+
+def _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
+    """The rotary / bias / trapezoid preprocessing (elementwise, PyTorch) followed by the chunk-scan kernels.
+
+    After the preprocessing the recurrence is the SSD one with per-head operands, a strictly causal score mask and a
+    per-token skip coefficient, which is how ``csrc/ssd.cu`` evaluates it (the reference runs one Triton program per
+    (head, batch) that walks all chunks serially, mamba3_siso_fwd.py:360-424)."""
+    from ..backbones.mamba3.siso import _prepare
+    from .dispatch import KERNEL_LAUNCHES
+
+    seqlen = V.shape[1]
+    Qr, Kr, adt, qk_dot = _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, torch.float32)
+    pad = (-seqlen) % CHUNK
+    vb, qb, kb = V.to(torch.bfloat16), Qr.to(torch.bfloat16), Kr.to(torch.bfloat16)
+    skip = qk_dot
+    if pad:  # adt = 0 and k = 0 on the padding: the state is carried unchanged
+        vb, qb, kb = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (vb, qb, kb))
+        adt, skip = F.pad(adt, (0, 0, 0, pad)), F.pad(skip, (0, 0, 0, pad))
+    y, final = ext().siso_chunk_scan_fwd(vb.contiguous(), kb.contiguous(), qb.contiguous(), adt.float().contiguous(),
+                                         None if D is None else D.float().contiguous(),
+                                         skip.float().transpose(1, 2).contiguous(), None)
+    KERNEL_LAUNCHES["count"] += 4
+    return y[:, :seqlen], final
+
+
+class _SISOFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
+        y, _ = _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D)
+        ctx.save_for_backward(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D)
+        return y.to(V.dtype)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from ..backbones.mamba3.siso import mamba3_siso_chunked
+
+        leaves = [t.detach().requires_grad_(True) for t in ctx.saved_tensors]
+        with torch.enable_grad():
+            y = mamba3_siso_chunked(*leaves[:9], D=leaves[9], Z=None, chunk_size=CHUNK)
+            grads = torch.autograd.grad(y, leaves, gy.to(y.dtype), allow_unused=True)
+        return tuple(grads)
+
+
+def mamba3_siso_cuda(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D, Z=None):
+    """Same arguments and result as ``mamba3_siso_chunked``; forward on the sm_100a kernels, backward by recompute."""
+    tensors = (Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D)
+    if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
+        y = _SISOFunction.apply(*tensors)
+    else:
+        y = _siso_forward_kernels(*tensors)[0].to(V.dtype)
+    if Z is not None:
+        y = (y.float() * F.silu(Z.float())).to(V.dtype)
+    return y

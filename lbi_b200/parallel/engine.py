@@ -68,6 +68,7 @@ class FastLBIEngine:
         basis_chunk: int = 16,
         act_dtype: torch.dtype | None = None,
         comm=None,
+        basis_parallel: bool | None = None,
     ) -> None:
         backend = model.region_backend
         if not hasattr(backend, "structured"):
@@ -93,6 +94,14 @@ class FastLBIEngine:
         self.structured._weights.clear()
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.last: dict = {}
+        # Basis-parallel pullback: the (region, block of basis directions) work items are spread evenly over the ranks;
+        # a rank that takes items of a region it does not own recomputes that region's forward (1 / R of the pullback).
+        # Needs every region's input to be recomputable from tokens and state, i.e. the sequence axis.
+        if basis_parallel is None:
+            basis_parallel = self.comm.world_size > 1 and model.region_axis == "sequence"
+        if basis_parallel and model.region_axis != "sequence":
+            raise ValueError("basis_parallel needs sequence-axis regions")
+        self.basis_parallel = bool(basis_parallel) and self.comm.world_size > 1
 
     # ------------------------------------------------------------------ helpers
     def _shadow_of(self, p):
@@ -194,24 +203,26 @@ class FastLBIEngine:
 
     # ------------------------------------------------------------------ Jacobian + offset of one region
     @torch.no_grad()
-    def _pullback_region(self, rec: RegionRecord, need_jacobian: bool):
-        """Returns (A^T [B, R, R] or None, b [B, R])."""
+    def _pullback_directions(self, rec: RegionRecord, lo: int, hi: int, include_loss: bool):
+        """Pull basis directions [lo, hi) of the outgoing state (and, if asked, the region's loss cotangent) back to the
+        incoming state.  Returns (rows [B, hi - lo, R] with rows[b, i] = d s_out[lo + i] / d s_in, or None; b [B, R] or None)."""
         model, iface = self.model, self.model.interface
         k = rec.index
         bsz, r = rec.state_in.shape
         t_len = rec.token_range[1] - rec.token_range[0]
         n = bsz * t_len
         dim = model.hidden_dim
-        dirs: list[torch.Tensor] = []  # each [B, D] fp32 (rank-one in time) for the basis directions
+        n_basis = hi - lo
         skip = None
-        if need_jacobian:
-            eye = torch.eye(r, device=self.device, dtype=torch.float32).unsqueeze(0).expand(bsz, r, r)
+        if n_basis > 0:
+            eye = torch.eye(r, device=self.device, dtype=torch.float32)[lo:hi].unsqueeze(0).expand(bsz, n_basis, r)
             upd = iface.update_jacobian_t(k, rec.diagnostics, eye, t_len)
-            skip = upd["g_state_skip"]  # [B, R, R]
-            g_pooled = upd["g_pooled_features"] / float(t_len)  # [B, R, D]
-        n_basis = r if need_jacobian else 0
-        has_loss = rec.d_out_loss is not None
+            skip = upd["g_state_skip"]  # [B, n_basis, R]
+            g_pooled = upd["g_pooled_features"] / float(t_len)  # [B, n_basis, D]
+        has_loss = include_loss and rec.d_out_loss is not None
         total = n_basis + (1 if has_loss else 0)
+        if total == 0:
+            return None, None
         cond_cots = torch.empty(total, bsz, dim, dtype=torch.float32, device=self.device)
         j = 0
         while j < total:
@@ -226,11 +237,108 @@ class FastLBIEngine:
             cond_cots[j : j + c] = ops.sum_tokens(g_in, c * bsz, t_len).view(c, bsz, dim)
             j += c
         g_state = iface.decode_jacobian_t(k, rec.state_in, cond_cots.transpose(0, 1))  # [B, total, R]
-        jac = None
-        if need_jacobian:
-            jac = (skip + g_state[:, :n_basis]).transpose(1, 2).contiguous()
-        offset = g_state[:, n_basis].contiguous() if has_loss else torch.zeros(bsz, r, dtype=torch.float32, device=self.device)
+        jac_rows = (skip + g_state[:, :n_basis]) if n_basis > 0 else None
+        offset = g_state[:, n_basis].contiguous() if has_loss else None
+        return jac_rows, offset
+
+    def _pullback_region(self, rec: RegionRecord, need_jacobian: bool):
+        """Returns (A^T [B, R, R] or None, b [B, R])."""
+        bsz, r = rec.state_in.shape
+        rows, offset = self._pullback_directions(rec, 0, r if need_jacobian else 0, include_loss=True)
+        jac = rows.transpose(1, 2).contiguous() if rows is not None else None
+        if offset is None:
+            offset = torch.zeros(bsz, r, dtype=torch.float32, device=self.device)
         return jac, offset
+
+    # ------------------------------------------------------------------ basis-parallel plan
+    def basis_plan(self) -> list[list[tuple[int, int, int]]]:
+        """Per rank, the (region, lo, hi) blocks of basis directions it pulls back.  Owners keep blocks of their own
+        regions up to an equal share; the surplus goes to the ranks with the least work, lowest rank first.  The plan
+        is a pure function of (regions, width, block size, world), so every rank computes the same one."""
+        k_regions, r, bc, world = self.model.num_regions, self.model.interface_width, self.basis_chunk, self.comm.world_size
+        blocks = {k: [(k, lo, min(r, lo + bc)) for lo in range(0, r, bc)] for k in range(k_regions - 1)}
+        total = sum(len(v) for v in blocks.values())
+        quota = -(-total // world)
+        plan: list[list[tuple[int, int, int]]] = [[] for _ in range(world)]
+        surplus: list[tuple[int, int, int]] = []
+        for k in range(k_regions - 1):
+            owner = self.placement.owner(k)
+            for blk in blocks[k]:
+                (plan[owner] if len(plan[owner]) < quota else surplus).append(blk)
+        for blk in surplus:
+            target = min(range(world), key=lambda rr: (len(plan[rr]), rr))
+            plan[target].append(blk)
+        return plan
+
+    @torch.no_grad()
+    def _adopt_region(self, k: int, state: torch.Tensor, ids: torch.Tensor) -> RegionRecord:
+        """Forward of a region owned by another rank, recomputed here from its tokens and incoming state."""
+        model, iface = self.model, self.model.interface
+        bsz, seqlen = ids.shape
+        t0, t1 = model.plan.token_ranges(seqlen)[k]
+        t_len, dim = t1 - t0, model.hidden_dim
+        region_ids = ids[:, t0:t1].contiguous()
+        table = self._w(model.canvas.embedding.weight)
+        canvas_rows = ops.embedding_fwd(region_ids, table, self.act_dtype)
+        x_in = ops.add_condition(canvas_rows, iface.decode(state, k).float(), t_len)
+        _, cache = self.structured.forward(x_in.view(bsz, t_len, dim), model.region_ranges[k], materialize_output=False)
+        if model.plan.region_has_loss(k):
+            _, out, _ = ops.add_rmsnorm_fwd(cache.last_branch, cache.last_stream, model.readout.norm.weight, model.readout.norm.eps,
+                                            self.act_dtype)
+            pooled = ops.mean_pool_tokens(out, bsz, t_len)
+        else:
+            pooled = ops.mean_pool_tokens(cache.last_branch, bsz, t_len)
+            if cache.last_stream is not None:
+                pooled = pooled + ops.mean_pool_tokens(cache.last_stream, bsz, t_len)
+        step = iface.update_from_pooled(state, pooled, k)
+        return RegionRecord(index=k, token_range=(t0, t1), state_in=state, pooled=pooled, diagnostics=step.diagnostics, cache=cache,
+                            ids=region_ids)
+
+    @torch.no_grad()
+    def _pullback_basis_parallel(self, records: list[RegionRecord], ids: torch.Tensor) -> torch.Tensor:
+        """All regions' Jacobians and offsets with the work spread over the ranks -> g [B, K, R]."""
+        model, comm = self.model, self.comm
+        k_regions, r = model.num_regions, model.interface_width
+        bsz = ids.shape[0]
+        own = {rec.index: rec for rec in records}
+        states = torch.zeros(k_regions, bsz, r, dtype=torch.float32, device=self.device)
+        for rec in records:
+            states[rec.index] = rec.state_in
+        comm.all_reduce_sum(states)   # every rank learns every region's incoming state (K x B x R floats)
+        rows_all = torch.zeros(k_regions, bsz, r, r, dtype=torch.float32, device=self.device)   # [k, b, direction, R]
+        offs_all = torch.zeros(k_regions, bsz, r, dtype=torch.float32, device=self.device)
+        mine = self.basis_plan()[comm.rank]
+        by_region: dict[int, list[tuple[int, int]]] = {}
+        for k, lo, hi in mine:
+            by_region.setdefault(k, []).append((lo, hi))
+        loss_done = set()
+        for k in sorted(by_region):
+            rec = own.get(k) or self._adopt_region(k, states[k], ids)
+            blocks = by_region[k]
+            for i, (lo, hi) in enumerate(blocks):
+                # the owner's loss direction rides with its last block when that block has room
+                ride = k in own and i == len(blocks) - 1 and (hi - lo) < self.basis_chunk
+                rows, off = self._pullback_directions(rec, lo, hi, include_loss=ride)
+                rows_all[k, :, lo:hi] = rows
+                if off is not None:
+                    offs_all[k] = off
+                    loss_done.add(k)
+            if k not in own:
+                rec.cache = None
+        for rec in records:   # loss directions that found no block to ride with
+            if rec.index not in loss_done and rec.d_out_loss is not None:
+                _, off = self._pullback_directions(rec, 0, 0, include_loss=True)
+                offs_all[rec.index] = off
+        comm.all_reduce_sum(rows_all)
+        comm.all_reduce_sum(offs_all)
+        mats_all = rows_all.permute(1, 0, 3, 2).contiguous()   # [B, K, R, R] with A_k^T[b, i, j] = d s_out[j] / d s_in[i]
+        offs = offs_all.transpose(0, 1).contiguous()           # [B, K, R]
+        self.last["jacobians"], self.last["offsets"] = mats_all, offs
+        if k_regions == 1:
+            return offs
+        g = ops.affine_suffix_scan(mats_all[:, : k_regions - 1].contiguous(), offs[:, : k_regions - 1].contiguous(),
+                                   seed=offs[:, k_regions - 1].contiguous())
+        return g[:, :k_regions]
 
     # ------------------------------------------------------------------ scan over all regions
     @torch.no_grad()
@@ -347,14 +455,18 @@ class FastLBIEngine:
         with nvtx.range("lbi/forward"):
             records, loss = self._forward(input_ids, targets)
         k_regions = model.num_regions
-        jacobians, offsets = [], []
-        for rec in records:
-            with nvtx.range(f"lbi/pullback/region{rec.index}"):
-                jac, off = self._pullback_region(rec, need_jacobian=rec.index < k_regions - 1)
-            jacobians.append(jac)
-            offsets.append(off)
-        with nvtx.range("lbi/scan"):
-            g = self._scan(jacobians, offsets)  # [B, K, R]
+        if self.basis_parallel:
+            with nvtx.range("lbi/pullback/basis_parallel"):
+                g = self._pullback_basis_parallel(records, input_ids)  # [B, K, R]
+        else:
+            jacobians, offsets = [], []
+            for rec in records:
+                with nvtx.range(f"lbi/pullback/region{rec.index}"):
+                    jac, off = self._pullback_region(rec, need_jacobian=rec.index < k_regions - 1)
+                jacobians.append(jac)
+                offsets.append(off)
+            with nvtx.range("lbi/scan"):
+                g = self._scan(jacobians, offsets)  # [B, K, R]
         for rec in records:
             g_next = g[:, rec.index + 1] if rec.index + 1 < k_regions else None
             with nvtx.range(f"lbi/local_vjp/region{rec.index}"):

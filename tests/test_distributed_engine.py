@@ -123,3 +123,26 @@ def test_training_program_on_two_ranks_matches_one_process(tmp_path, monkeypatch
     # a single process resumes from the checkpoint the two ranks wrote
     resumed = run_lbi_experiment(_train_cfg(tmp_path / "dist", steps=4, resume_from=str(tmp_path / "dist" / "run")))
     assert resumed["runs"][0]["start_step"] == 3
+
+
+def test_basis_plan_is_balanced_and_complete():
+    """Every (region, block) of basis directions is assigned exactly once and no rank gets more than its share."""
+    from types import SimpleNamespace
+
+    from lbi_b200.models.region_plan import RegionPlacement
+    from lbi_b200.parallel import FastLBIEngine
+
+    for k_regions, width, chunk, world in [(8, 128, 16, 8), (8, 128, 16, 2), (8, 128, 16, 4), (4, 8, 3, 2), (4, 8, 3, 4), (2, 16, 16, 2)]:
+        fake = SimpleNamespace(model=SimpleNamespace(num_regions=k_regions, interface_width=width), basis_chunk=chunk,
+                               comm=SimpleNamespace(world_size=world), placement=RegionPlacement(k_regions, world))
+        plan = FastLBIEngine.basis_plan(fake)
+        blocks = [b for per_rank in plan for b in per_rank]
+        want = [(k, lo, min(width, lo + chunk)) for k in range(k_regions - 1) for lo in range(0, width, chunk)]
+        assert sorted(blocks) == sorted(want)
+        quota = -(-len(want) // world)
+        assert max(len(p) for p in plan) <= quota
+    # 8 regions on 8 ranks: the last rank, whose own region needs no Jacobian, takes one block from each of the others
+    fake = SimpleNamespace(model=SimpleNamespace(num_regions=8, interface_width=128), basis_chunk=16,
+                           comm=SimpleNamespace(world_size=8), placement=RegionPlacement(8, 8))
+    plan = FastLBIEngine.basis_plan(fake)
+    assert [len(p) for p in plan] == [7] * 8 and sorted({k for k, _, _ in plan[7]}) == list(range(7))

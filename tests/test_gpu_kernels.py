@@ -154,3 +154,16 @@ def test_ce_fwd_bwd():
     ops.ext().ce_fwd_bwd_(work, targets, loss, 0.25)
     _close(loss, want_loss.reshape(1), 1e-2, 1e-4, "ce loss")
     _close(work, lf.grad, 2e-3, 2e-2, "ce grad")
+
+
+def test_matrix_norms_kernel_matches_linalg():
+    g = torch.Generator(device="cuda").manual_seed(11)
+    mats = torch.randn(3, 5, 96, 96, device="cuda", generator=g) / 96 ** 0.5
+    mats[0, 0] = torch.eye(96, device="cuda") * 0.5          # degenerate spectrum
+    mats[0, 1] = 0.0                                         # zero matrix
+    spec, frob = ops.ext().matrix_norms(mats, 128)
+    want_spec = torch.linalg.matrix_norm(mats, ord=2)
+    want_frob = torch.linalg.matrix_norm(mats, ord="fro")
+    assert torch.allclose(frob, want_frob, rtol=1e-4, atol=1e-6)
+    assert torch.allclose(spec, want_spec, rtol=2e-2, atol=1e-6)
+    assert (spec <= want_spec * (1 + 1e-4) + 1e-6).all()     # power iteration never overshoots

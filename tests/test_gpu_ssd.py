@@ -50,3 +50,32 @@ def test_ssd_initial_state_and_gradients():
     ssd_chunk_scan(xr, dtr, A, B.float(), C.float(), chunk_size=128, D=D).float().square().sum().backward()
     assert torch.allclose(xs.grad, xr.grad, rtol=5e-2, atol=5e-2 * xr.grad.abs().max().item())
     assert torch.allclose(dts.grad, dtr.grad, rtol=5e-2, atol=5e-2 * dtr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("b,l,h,g", [(1, 128, 2, 1), (2, 320, 4, 2), (1, 1024, 4, 1)])
+def test_siso_kernels_match_recurrence(b, l, h, g):
+    from lbi_b200.backbones.mamba3.siso import mamba3_siso_chunked, mamba3_siso_recurrent_reference
+    from lbi_b200.ops.ssd import mamba3_siso_cuda, siso_cuda_supported
+
+    gen = torch.Generator(device=DEV).manual_seed(l + h)
+    n, s = 128, 32
+    Q = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3).bfloat16()
+    K = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3).bfloat16()
+    V = torch.randn(b, l, h, 64, device=DEV, generator=gen).bfloat16()
+    DT = torch.rand(b, h, l, device=DEV, generator=gen) * 0.1 + 0.005
+    ADT = -DT * (torch.rand(b, h, l, device=DEV, generator=gen) * 4 + 0.5)
+    Trap = torch.randn(b, h, l, device=DEV, generator=gen)
+    Qb = torch.randn(h, n, device=DEV, generator=gen) * 0.2
+    Kb = torch.randn(h, n, device=DEV, generator=gen) * 0.2
+    Angles = torch.randn(b, l, h, s, device=DEV, generator=gen)
+    D = torch.randn(h, device=DEV, generator=gen)
+    Z = torch.randn(b, l, h, 64, device=DEV, generator=gen).bfloat16()
+    assert siso_cuda_supported(V, Q)
+    y = mamba3_siso_cuda(Q, K, V, ADT, DT, Trap, Qb, Kb, Angles, D, Z=Z)
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(V) == 0, "a bounded wait inside the SISO kernels ran out"
+    want = mamba3_siso_recurrent_reference(Q, K, V, ADT, DT, Trap, Qb, Kb, Angles, D=D, Z=Z)
+    scale = want.abs().max().item()
+    assert (y.double() - want).abs().max().item() <= 3e-2 * scale + 1e-3
+    torch_y = mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Qb, Kb, Angles, D=D, Z=Z, chunk_size=64)
+    assert (y.float() - torch_y.float()).abs().max().item() <= 3e-2 * scale + 1e-3
