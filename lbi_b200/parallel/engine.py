@@ -227,6 +227,8 @@ class FastLBIEngine:
         j = 0
         while j < total:
             c = min(self.basis_chunk, total - j)
+            if total - (j + c) == 1:
+                c += 1  # a lone trailing direction (the loss cotangent) joins this pass instead of costing one of its own
             rows = torch.empty(c, bsz, t_len, dim, dtype=self.act_dtype, device=self.device)
             nb = max(0, min(c, n_basis - j))
             if nb > 0:
@@ -316,8 +318,8 @@ class FastLBIEngine:
             rec = own.get(k) or self._adopt_region(k, states[k], ids)
             blocks = by_region[k]
             for i, (lo, hi) in enumerate(blocks):
-                # the owner's loss direction rides with its last block when that block has room
-                ride = k in own and i == len(blocks) - 1 and (hi - lo) < self.basis_chunk
+                # the owner's loss direction rides with its last block (one direction more in that pass)
+                ride = k in own and i == len(blocks) - 1
                 rows, off = self._pullback_directions(rec, lo, hi, include_loss=ride)
                 rows_all[k, :, lo:hi] = rows
                 if off is not None:
