@@ -191,14 +191,13 @@ class StructuredTransformerRegion:
             d_normed2 = ops.linear_dgrad(d_fc1, lw.w_fc1, lw.w_fc1_t)
             if grads is not None:
                 _acc(grads, prefix + "norm2.weight", ops.rmsnorm_wgrad(d_normed2, lc.stream2, lc.rstd2))
-            d_stream = ops.rmsnorm_bwd(d_normed2, lc.stream2, lc.rstd2, lw.norm2, d_stream)
+            d_stream, d_branch = ops.rmsnorm_bwd(d_normed2, lc.stream2, lc.rstd2, lw.norm2, d_stream, lowp_dtype=dtype)
             # attention branch
-            d_branch = d_stream.to(dtype)
             if grads is not None:
                 _wgrad(grads, prefix + "attn.out_proj.weight", d_branch, lc.attn_out)
             d_attn = ops.linear_dgrad(d_branch, lw.w_o, lw.w_o_t)
-            d_qkv = ops.attention_pullback_packed(d_attn, lc.qkv, lc.attn_out, lc.lse, bsz, seqlen, heads, kv_heads, head_dim, scale)
-            d_qkv = ops.rope_qkv(d_qkv, cos, sin, heads, kv_heads, head_dim, seqlen, interleaved, inverse=True)
+            d_qkv = ops.attention_pullback_packed(d_attn, lc.qkv, lc.attn_out, lc.lse, bsz, seqlen, heads, kv_heads, head_dim, scale,
+                                                  rope=(cos, sin, interleaved))
             if lw.conv_w is not None:
                 if grads is not None:
                     dw, db = ops.causal_conv_wgrad(d_qkv, lc.qkv_pre, lw.conv_w.shape[1], bsz, seqlen)
@@ -211,8 +210,7 @@ class StructuredTransformerRegion:
             d_normed1 = ops.linear_dgrad(d_qkv, lw.w_qkv, lw.w_qkv_t)
             if grads is not None:
                 _acc(grads, prefix + "norm.weight", ops.rmsnorm_wgrad(d_normed1, lc.stream1, lc.rstd1))
-            d_stream = ops.rmsnorm_bwd(d_normed1, lc.stream1, lc.rstd1, lw.norm1, d_stream)
-            d_branch = d_stream.to(dtype)
+            d_stream, d_branch = ops.rmsnorm_bwd(d_normed1, lc.stream1, lc.rstd1, lw.norm1, d_stream, lowp_dtype=dtype)
         return d_stream
 
     def input_pullback(self, cache: StructuredRegionCache, d_out_basis_rows: torch.Tensor) -> torch.Tensor:

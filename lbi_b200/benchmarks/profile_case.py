@@ -5,6 +5,8 @@
     python -m lbi_b200.benchmarks.profile_case --case dgrad     # tcgen05 GEMM with MN-major B (fc1 dgrad)
     python -m lbi_b200.benchmarks.profile_case --case elementwise   # rmsnorm_bwd / swiglu_bwd / rope over 65536 rows
     python -m lbi_b200.benchmarks.profile_case --case scan      # suffix scan B 8, K 32, R 256
+    python -m lbi_b200.benchmarks.profile_case --case attn_fwd  # causal attention forward B 4, H 16, T 4096
+    python -m lbi_b200.benchmarks.profile_case --case ssd       # Mamba-2 SSD forward B 2, L 8192, 24 heads, d_state 64
 
 Each case holds well under 2 GB on the device, touches more than the 126 MB L2, launches the kernel of interest a
 handful of times and exits.  Typical capture:
@@ -22,7 +24,7 @@ from lbi_b200 import ops
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan"])
+    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd"])
     ap.add_argument("--repeats", type=int, default=2)
     args = ap.parse_args()
     dev = "cuda"
@@ -61,9 +63,28 @@ def main() -> None:
         qkv = torch.randn(rows * reps, 3 * dim, device=dev).bfloat16()
         cos, sin = rope_tables(2048, 64, 10000.0, torch.device(dev))
         for _ in range(args.repeats):
-            ops.rmsnorm_bwd(g, stream, rstd, w, acc)
+            ops.rmsnorm_bwd(g, stream, rstd, w, acc, lowp_dtype=torch.bfloat16)
             ops.swiglu_bwd(da, u)
             ops.rope_qkv(qkv, cos, sin, 16, 16, 64, 2048, False, True)
+    elif args.case == "attn_fwd":
+        from lbi_b200.ops.attention import flash_forward_packed
+
+        b, h, t = 4, 16, 4096
+        qkv = torch.randn(b * t, 3 * h * 64, device=dev).bfloat16()
+        for _ in range(args.repeats):
+            flash_forward_packed(qkv, b, t, h, h, 64, 0.125, kernel_mode="tcgen05")
+    elif args.case == "ssd":
+        from lbi_b200.ops.ssd import ssd_chunk_scan_cuda
+
+        b, l, h, n = 2, 8192, 24, 64
+        x = torch.randn(b, l, h, 64, device=dev).bfloat16()
+        dt = torch.rand(b, l, h, device=dev) * 0.1 + 0.001
+        a = -(torch.rand(h, device=dev) * 8 + 1)
+        bm = (torch.randn(b, l, 1, n, device=dev) * 0.5).bfloat16()
+        cm = (torch.randn(b, l, 1, n, device=dev) * 0.5).bfloat16()
+        with torch.no_grad():
+            for _ in range(args.repeats):
+                ssd_chunk_scan_cuda(x, dt, a, bm, cm, D=torch.ones(h, device=dev))
     else:
         mats = torch.randn(8, 32, 256, 256, device=dev) / 16
         for _ in range(args.repeats):

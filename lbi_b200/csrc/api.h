@@ -13,9 +13,10 @@ extern "C" {
 int lbi_add_rmsnorm_fwd(const void* branch_bf16, const float* stream_or_null, const float* weight, void* normed_bf16,
                         float* new_stream, float* rstd, int64_t rows, int dim, float eps, cudaStream_t stream);
 // d_stream_out = d_stream_in (or 0) + J_rmsnorm^T d_normed; activation rows are indexed by row % act_rows.
+// d_stream_out_bf16 (optional) receives a bf16 copy of the result in the same pass.
 int lbi_rmsnorm_bwd(const void* d_normed_bf16, const float* x_stream, const float* rstd, const float* weight,
-                    const float* d_stream_in_or_null, float* d_stream_out, int64_t rows, int64_t act_rows, int dim,
-                    cudaStream_t stream);
+                    const float* d_stream_in_or_null, float* d_stream_out, void* d_stream_out_bf16_or_null, int64_t rows,
+                    int64_t act_rows, int dim, cudaStream_t stream);
 // dw[d] = sum_r d_normed[r, d] * x[r, d] * rstd[r]; `partials` holds nblocks * dim floats.
 int lbi_rmsnorm_wgrad(const void* d_normed_bf16, const float* x_stream, const float* rstd, float* partials, float* dw,
                       int64_t rows, int dim, int nblocks, cudaStream_t stream);

@@ -66,6 +66,9 @@ struct Params {
   const float* lse;             // [B, H, T]
   const float* delta;           // [P, B, H, T]
   __nv_bfloat16* d_qkv;         // [P * n, 3 H Dh]
+  const float* rope_cos;        // [T, Dh / 2] fp32 or null: rotate dQ and dK back before they are stored
+  const float* rope_sin;
+  int rope_interleaved;
   int* status;
 };
 
@@ -159,6 +162,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 //   [kernel: 0 = dQ, 1 = dK/dV][role: 0 = TMA producer, 1 = issuer X, 2 = issuer Y, 3 = compute thread 0][slot]; slot 7 = total.
 #ifdef LBI_ATTN_TIMING
 __device__ unsigned long long g_attn_timing[2][4][12];
+__device__ unsigned long long g_attn_phase[2][8];   // thread 0: wall-clock phases of the CTA, summed over CTAs
 #define TIMED(slot, ...)              \
   {                                   \
     const long long _t0 = clock64();  \
@@ -185,6 +189,10 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   extern __shared__ uint8_t raw_smem[];
   Smem<DKDV>& s = *reinterpret_cast<Smem<DKDV>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef LBI_ATTN_TIMING
+  const long long _t_entry = clock64();
+  long long _t_setup = 0, _t_first = 0, _t_loop = 0, _t_acc = 0, _t_store = 0;
+#endif
 
   // tile ownership: heavy tiles first (DKDV: small j walks more query tiles; DQ: large i walks more key tiles)
   const int own = DKDV ? (int)blockIdx.x : p.n_tiles - 1 - (int)blockIdx.x;
@@ -409,6 +417,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     TIMING_BEGIN();
 #ifdef LBI_ATTN_TIMING
     long long _tm2 = 0;
+    _t_setup = _tstart;
 #endif
     bool ok = true;
     int it = 0, rr = -1, d0 = 0;   // step, job within the step, index of the step's first dS tile
@@ -438,6 +447,9 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         tacc[10] += clock64() - _ts;
 #endif
         TIMED(0, ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 31));
+#ifdef LBI_ATTN_TIMING
+        if (n == 0) _t_first = clock64();
+#endif
         if (DKDV && it > 0 && ok) TIMED(1, ok = mbar_wait(&s.bar_p_free, (it - 1) & 1, abortp, p.status, 32))
         TIMED(8, ok = __all_sync(0xffffffffu, ok); fence_after_sync());
         if (!ok) break;
@@ -512,38 +524,95 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     // ------------------------------------------------------------------ epilogue: accumulators -> global
 #ifdef LBI_ATTN_TIMING
     _tm2 = clock64();
+    _t_loop = _tm2;
 #endif
     if (ok) ok = mbar_wait(&s.bar_acc_done, 0, abortp, p.status, 35);
+#ifdef LBI_ATTN_TIMING
+    _t_acc = clock64();
+#endif
     ok = __all_sync(0xffffffffu, ok);
-    if (ok && slice < 2) {
+    if (ok) {
+      // One (direction, accumulator) item per 32-row quarter and pass: the four column slices take items round-robin and
+      // each thread writes a whole 64-element head row (128 contiguous bytes).  With rotary tables given, dQ and dK are
+      // rotated back here (the transpose of the forward rotation), which saves a separate pass over d_qkv.
       fence_after_sync();
-      const int64_t tok = (int64_t)row_b + own * TILE + r;
-      for (int pp = 0; pp < np; ++pp) {
-        __nv_bfloat16* out_row = p.d_qkv + ((int64_t)(p0 + pp) * p.n_rows + tok) * p.out_ld;
-        const int n_acc = DKDV ? 2 : 1;
-        for (int a = 0; a < n_acc; ++a) {
-          // DKDV: a = 0 -> dK (scaled), a = 1 -> dV ; DQ: dQ (scaled)
-          const uint32_t acc = tmem + (a == 0 ? ACC0 : ACC_DV) + pp * 64;
-          const int col = (DKDV ? (a == 0 ? col_k : col_v) : col_q) + slice * 32;
-          const float mul = (DKDV && a == 1) ? 1.f : p.scale;
-          uint32_t v[32];
-          tmem_ld_32x32(acc + ((uint32_t)(quarter * 32) << 16) + slice * 32, v);
-          tmem_ld_wait();
-          uint4* dst = reinterpret_cast<uint4*>(out_row + col);
+      const int pos = own * TILE + r;
+      const int64_t tok = (int64_t)row_b + pos;
+      constexpr int n_acc = DKDV ? 2 : 1;
+      const int items = np * n_acc;
+      for (int item = slice; item < items; item += 4) {
+        const int pp = item / n_acc, a = item % n_acc;
+        // DKDV: a = 0 -> dK (scaled), a = 1 -> dV ; DQ: dQ (scaled)
+        const uint32_t acc = tmem + (a == 0 ? ACC0 : ACC_DV) + pp * 64 + ((uint32_t)(quarter * 32) << 16);
+        const int col = DKDV ? (a == 0 ? col_k : col_v) : col_q;
+        const float mul = (DKDV && a == 1) ? 1.f : p.scale;
+        const bool rotate = p.rope_cos != nullptr && !(DKDV && a == 1);
+        uint32_t lo[32], hi[32];
+        tmem_ld_32x32(acc, lo);
+        tmem_ld_32x32(acc + 32, hi);
+        tmem_ld_wait();
+        uint4* dst = reinterpret_cast<uint4*>(p.d_qkv + ((int64_t)(p0 + pp) * p.n_rows + tok) * p.out_ld + col);
+        if (!rotate) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * mul, __uint_as_float(v[g * 8 + 1]) * mul);
-            o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * mul, __uint_as_float(v[g * 8 + 3]) * mul);
-            o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * mul, __uint_as_float(v[g * 8 + 5]) * mul);
-            o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * mul, __uint_as_float(v[g * 8 + 7]) * mul);
+            uint4 o, o2;
+            o.x = pack_bf16(__uint_as_float(lo[g * 8 + 0]) * mul, __uint_as_float(lo[g * 8 + 1]) * mul);
+            o.y = pack_bf16(__uint_as_float(lo[g * 8 + 2]) * mul, __uint_as_float(lo[g * 8 + 3]) * mul);
+            o.z = pack_bf16(__uint_as_float(lo[g * 8 + 4]) * mul, __uint_as_float(lo[g * 8 + 5]) * mul);
+            o.w = pack_bf16(__uint_as_float(lo[g * 8 + 6]) * mul, __uint_as_float(lo[g * 8 + 7]) * mul);
+            o2.x = pack_bf16(__uint_as_float(hi[g * 8 + 0]) * mul, __uint_as_float(hi[g * 8 + 1]) * mul);
+            o2.y = pack_bf16(__uint_as_float(hi[g * 8 + 2]) * mul, __uint_as_float(hi[g * 8 + 3]) * mul);
+            o2.z = pack_bf16(__uint_as_float(hi[g * 8 + 4]) * mul, __uint_as_float(hi[g * 8 + 5]) * mul);
+            o2.w = pack_bf16(__uint_as_float(hi[g * 8 + 6]) * mul, __uint_as_float(hi[g * 8 + 7]) * mul);
             dst[g] = o;
+            dst[4 + g] = o2;
+          }
+        } else {
+          const float4* c4 = reinterpret_cast<const float4*>(p.rope_cos + (int64_t)pos * (DH / 2));
+          const float4* s4 = reinterpret_cast<const float4*>(p.rope_sin + (int64_t)pos * (DH / 2));
+          if (!p.rope_interleaved) {   // pairs (i, i + 32): x_i <- x_i c + x_{i+32} s ,  x_{i+32} <- -x_i s + x_{i+32} c
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float oa[8], ob[8];
+#pragma unroll
+              for (int q = 0; q < 2; ++q) {
+                const float4 c = c4[g * 2 + q], sn = s4[g * 2 + q];
+                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float xa = __uint_as_float(lo[g * 8 + q * 4 + e]) * mul, xb = __uint_as_float(hi[g * 8 + q * 4 + e]) * mul;
+                  oa[q * 4 + e] = xa * cc[e] + xb * ss[e];
+                  ob[q * 4 + e] = xb * cc[e] - xa * ss[e];
+                }
+              }
+              dst[g] = make_uint4(pack_bf16(oa[0], oa[1]), pack_bf16(oa[2], oa[3]), pack_bf16(oa[4], oa[5]), pack_bf16(oa[6], oa[7]));
+              dst[4 + g] = make_uint4(pack_bf16(ob[0], ob[1]), pack_bf16(ob[2], ob[3]), pack_bf16(ob[4], ob[5]), pack_bf16(ob[6], ob[7]));
+            }
+          } else {                     // pairs (2 i, 2 i + 1), angle index i
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              const uint32_t* x = hh == 0 ? lo : hi;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {   // 8 elements = 4 pairs, angles hh * 16 + g * 4 .. + 3
+                const float4 c = c4[hh * 4 + g], sn = s4[hh * 4 + g];
+                const float cc[4] = {c.x, c.y, c.z, c.w}, ss[4] = {sn.x, sn.y, sn.z, sn.w};
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float xa = __uint_as_float(x[g * 8 + 2 * e]) * mul, xb = __uint_as_float(x[g * 8 + 2 * e + 1]) * mul;
+                  o[2 * e] = xa * cc[e] + xb * ss[e];
+                  o[2 * e + 1] = xb * cc[e] - xa * ss[e];
+                }
+                dst[hh * 4 + g] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+              }
+            }
           }
         }
       }
     }
 #ifdef LBI_ATTN_TIMING
     tacc[6] += clock64() - _tm2;
+    _t_store = clock64();
     if (threadIdx.x == 0) TIMING_END(3);
 #endif
   }
@@ -560,6 +629,18 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     fence_after_sync();
     tmem_dealloc(tmem, 512);
   }
+#ifdef LBI_ATTN_TIMING
+  if (threadIdx.x == 0) {
+    const long long t_exit = clock64();
+    unsigned long long* ph = g_attn_phase[DKDV ? 1 : 0];
+    atomicAdd(&ph[0], (unsigned long long)(_t_setup - _t_entry));   // entry -> set-up done
+    atomicAdd(&ph[1], (unsigned long long)(_t_first - _t_setup));   // -> first S tile in TMEM
+    atomicAdd(&ph[2], (unsigned long long)(_t_loop - _t_first));   // -> all jobs processed
+    atomicAdd(&ph[3], (unsigned long long)(_t_acc - _t_loop));     // -> last accumulating product finished
+    atomicAdd(&ph[4], (unsigned long long)(_t_store - _t_acc));    // -> outputs stored
+    atomicAdd(&ph[5], (unsigned long long)(t_exit - _t_store));    // -> exit
+  }
+#endif
 }
 
 // delta[p, b, h, t] = sum_d dO[(p, b, t), h * Dh + d] * O[(b, t), h * Dh + d]; one warp per (row, head).
@@ -638,6 +719,12 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& md, const Params& p,
 
 #ifdef LBI_ATTN_TIMING
 // Copies the 2 x 4 x 8 cycle counters to `out` and clears them.
+extern "C" int lbi_attn_phase_read(unsigned long long* out) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_phase, sizeof(unsigned long long) * 16);
+  if (e != cudaSuccess) return (int)e;
+  unsigned long long zeros[16] = {0};
+  return (int)cudaMemcpyToSymbol(lbi::attn::g_attn_phase, zeros, sizeof(zeros));
+}
 extern "C" int lbi_attn_timing_read(unsigned long long* out) {
   cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_timing, sizeof(unsigned long long) * 96);
   if (e != cudaSuccess) return (int)e;
@@ -648,7 +735,8 @@ extern "C" int lbi_attn_timing_read(unsigned long long* out) {
 
 extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const float* lse, void* d_qkv,
                                  float* delta, int batch, int heads, int seq_len, int head_dim, int nbasis, float scale,
-                                 int* status, cudaStream_t st) {
+                                 const float* rope_cos, const float* rope_sin, int rope_interleaved, int* status,
+                                 cudaStream_t st) {
   using namespace lbi::attn;
   if (head_dim != DH || seq_len % TILE != 0 || batch <= 0 || heads <= 0 || nbasis <= 0) return (int)cudaErrorInvalidValue;
   const int64_t n_rows = (int64_t)batch * seq_len;
@@ -677,6 +765,7 @@ extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o
   p.scale_log2 = scale * 1.4426950408889634f;
   p.lse = lse; p.delta = delta;
   p.d_qkv = (__nv_bfloat16*)d_qkv;
+  p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_interleaved = rope_interleaved;
   p.status = status;
   rc = launch<true>(mq, md, p, st);
   if (rc) return rc;

@@ -51,8 +51,8 @@ std::tuple<Tensor, Tensor, Tensor> add_rmsnorm_fwd(const Tensor& branch, const c
   return {normed, new_stream, rstd};
 }
 
-Tensor rmsnorm_bwd(const Tensor& d_normed, const Tensor& x_stream, const Tensor& rstd, const Tensor& weight,
-                   const c10::optional<Tensor>& d_stream) {
+static std::tuple<Tensor, Tensor> rmsnorm_bwd_impl(const Tensor& d_normed, const Tensor& x_stream, const Tensor& rstd,
+                                                   const Tensor& weight, const c10::optional<Tensor>& d_stream, bool want_lowp) {
   CHECK_BF16(d_normed);
   CHECK_F32(x_stream);
   CHECK_F32(rstd);
@@ -61,7 +61,7 @@ Tensor rmsnorm_bwd(const Tensor& d_normed, const Tensor& x_stream, const Tensor&
   const int dim = (int)d_normed.size(1);
   TORCH_CHECK(rows % act_rows == 0, "cotangent rows must be a multiple of activation rows");
   Tensor w = weight.to(at::kFloat).contiguous();
-  Tensor out;
+  Tensor out, lowp;
   const float* din = nullptr;
   if (d_stream.has_value() && d_stream->defined()) {
     CHECK_F32(*d_stream);
@@ -70,10 +70,22 @@ Tensor rmsnorm_bwd(const Tensor& d_normed, const Tensor& x_stream, const Tensor&
   } else {
     out = torch::empty({rows, dim}, d_normed.options().dtype(at::kFloat));
   }
+  if (want_lowp) lowp = torch::empty({rows, dim}, d_normed.options());
   check(lbi_rmsnorm_bwd(d_normed.data_ptr(), x_stream.data_ptr<float>(), rstd.data_ptr<float>(), w.data_ptr<float>(), din,
-                        out.data_ptr<float>(), rows, act_rows, dim, cur_stream()),
+                        out.data_ptr<float>(), want_lowp ? lowp.data_ptr() : nullptr, rows, act_rows, dim, cur_stream()),
         "rmsnorm_bwd");
-  return out;
+  return {out, lowp};
+}
+
+Tensor rmsnorm_bwd(const Tensor& d_normed, const Tensor& x_stream, const Tensor& rstd, const Tensor& weight,
+                   const c10::optional<Tensor>& d_stream) {
+  return std::get<0>(rmsnorm_bwd_impl(d_normed, x_stream, rstd, weight, d_stream, false));
+}
+
+// Same, and also returns the bf16 copy of the new cotangent stream (what the next GEMM reads).
+std::tuple<Tensor, Tensor> rmsnorm_bwd_lowp(const Tensor& d_normed, const Tensor& x_stream, const Tensor& rstd, const Tensor& weight,
+                                            const c10::optional<Tensor>& d_stream) {
+  return rmsnorm_bwd_impl(d_normed, x_stream, rstd, weight, d_stream, true);
 }
 
 Tensor rmsnorm_wgrad(const Tensor& d_normed, const Tensor& x_stream, const Tensor& rstd) {
@@ -321,7 +333,8 @@ Tensor gemm_tn(const Tensor& a, const Tensor& b, bool out_fp32, const c10::optio
 }
 
 Tensor attn_pullback_packed(const Tensor& d_o, const Tensor& qkv, const Tensor& o, const Tensor& lse, int64_t batch,
-                            int64_t seq_len, int64_t heads, int64_t head_dim, double scale) {
+                            int64_t seq_len, int64_t heads, int64_t head_dim, double scale,
+                            const c10::optional<Tensor>& rope_cos, const c10::optional<Tensor>& rope_sin, bool rope_interleaved) {
   CHECK_BF16(d_o);
   CHECK_BF16(qkv);
   CHECK_BF16(o);
@@ -333,12 +346,22 @@ Tensor attn_pullback_packed(const Tensor& d_o, const Tensor& qkv, const Tensor& 
   TORCH_CHECK(o.size(0) == n && o.size(1) == heads * head_dim, "o shape mismatch");
   TORCH_CHECK(lse.numel() == batch * heads * seq_len, "lse shape mismatch");
   const int64_t nbasis = d_o.size(0) / n;
+  const float *cos_p = nullptr, *sin_p = nullptr;
+  if (rope_cos.has_value()) {
+    TORCH_CHECK(rope_sin.has_value(), "rope_sin missing");
+    CHECK_F32(*rope_cos);
+    CHECK_F32(*rope_sin);
+    TORCH_CHECK(rope_cos->size(0) >= seq_len && rope_cos->size(1) == head_dim / 2 && rope_sin->sizes() == rope_cos->sizes(),
+                "rope tables must be [seq_len, head_dim / 2]");
+    cos_p = rope_cos->data_ptr<float>();
+    sin_p = rope_sin->data_ptr<float>();
+  }
   Tensor d_qkv = torch::empty({d_o.size(0), qkv.size(1)}, d_o.options());
   Tensor delta = torch::empty({nbasis, batch, heads, seq_len}, lse.options());
   Tensor st = status_word(d_o);
   check(lbi_attn_pullback(qkv.data_ptr(), d_o.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), d_qkv.data_ptr(),
                           delta.data_ptr<float>(), (int)batch, (int)heads, (int)seq_len, (int)head_dim, (int)nbasis,
-                          (float)scale, st.data_ptr<int>(), cur_stream()),
+                          (float)scale, cos_p, sin_p, rope_interleaved ? 1 : 0, st.data_ptr<int>(), cur_stream()),
         "attn_pullback");
   return d_qkv;
 }
@@ -553,6 +576,7 @@ int64_t kernel_status(const Tensor& like) {
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_rmsnorm_fwd", &add_rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd_lowp", &rmsnorm_bwd_lowp);
   m.def("rmsnorm_wgrad", &rmsnorm_wgrad);
   m.def("rope_qkv_", &rope_qkv_);
   m.def("swiglu_fwd", &swiglu_fwd);
@@ -573,7 +597,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("a_t") = false, py::arg("b_t") = false,
         py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);
   m.def("gemm_tn", &gemm_tn);
-  m.def("attn_pullback_packed", &attn_pullback_packed);
+  m.def("attn_pullback_packed", &attn_pullback_packed, py::arg("d_o"), py::arg("qkv"), py::arg("o"), py::arg("lse"), py::arg("batch"),
+        py::arg("seq_len"), py::arg("heads"), py::arg("head_dim"), py::arg("scale"), py::arg("rope_cos") = py::none(),
+        py::arg("rope_sin") = py::none(), py::arg("rope_interleaved") = false);
   m.def("attn_fwd_packed", &attn_fwd_packed);
   m.def("ssd_chunk_scan_fwd", &ssd_chunk_scan_fwd);
   m.def("siso_chunk_scan_fwd", &siso_chunk_scan_fwd);

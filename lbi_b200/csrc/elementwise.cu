@@ -53,52 +53,81 @@ __global__ void __launch_bounds__(THREADS) add_rmsnorm_fwd_kernel(const bf16x8* 
 }
 
 // ------------------------------------------------------------------------------------------------ RMSNorm bwd (dx)
+// One CTA per activation row; it walks all cotangent rows that share the row (row = p * act_rows + arow), so the
+// normalised activations and the weight are staged once in shared memory (2 * dim floats) instead of being re-read per
+// direction, and each thread keeps its part of the cotangent in registers between the two passes (dim <= 8 * 4 * THREADS).
 template <int THREADS>
 __global__ void __launch_bounds__(THREADS) rmsnorm_bwd_kernel(const bf16x8* __restrict__ d_normed,
                                                                const float4* __restrict__ x_stream,
                                                                const float* __restrict__ rstd,
                                                                const float4* __restrict__ weight,
                                                                const float4* d_stream_in, float4* d_stream_out,
-                                                               int64_t act_rows, int dim) {
+                                                               bf16x8* lowp_out, int64_t rows, int64_t act_rows, int dim) {
+  extern __shared__ float4 sm4[];
   __shared__ float scratch[33];
-  const int64_t row = blockIdx.x;
-  const int64_t arow = row % act_rows;
+  const int64_t arow = blockIdx.x;
   const int nvec = dim >> 3;
-  const bf16x8* g = d_normed + row * nvec;
-  const float4* x = x_stream + arow * nvec * 2;
+  float4* xh = sm4;             // xhat = x * rstd, 2 float4 per vector
+  float4* wv = sm4 + 2 * nvec;  // weight
   const float r = rstd[arow];
-  float dot = 0.f;
-  for (int i = threadIdx.x; i < nvec; i += THREADS) {
-    float gv[8];
-    unpack8(g[i], gv);
-    float4 x0 = x[2 * i], x1 = x[2 * i + 1], w0 = weight[2 * i], w1 = weight[2 * i + 1];
-    dot += gv[0] * w0.x * x0.x + gv[1] * w0.y * x0.y + gv[2] * w0.z * x0.z + gv[3] * w0.w * x0.w +
-           gv[4] * w1.x * x1.x + gv[5] * w1.y * x1.y + gv[6] * w1.z * x1.z + gv[7] * w1.w * x1.w;
+  for (int i = threadIdx.x; i < 2 * nvec; i += THREADS) {
+    float4 v = x_stream[arow * nvec * 2 + i];
+    v.x *= r; v.y *= r; v.z *= r; v.w *= r;
+    xh[i] = v;
+    wv[i] = weight[i];
   }
-  // mean over the row of (g*w) * xhat with xhat = x * r
-  const float c = block_sum(dot, scratch) * r / (float)dim;
-  const float4* din = d_stream_in ? d_stream_in + row * nvec * 2 : nullptr;
-  float4* dout = d_stream_out + row * nvec * 2;
-  for (int i = threadIdx.x; i < nvec; i += THREADS) {
-    float gv[8];
-    unpack8(g[i], gv);
-    float4 x0 = x[2 * i], x1 = x[2 * i + 1], w0 = weight[2 * i], w1 = weight[2 * i + 1];
-    float4 o0, o1;
-    o0.x = r * (gv[0] * w0.x - x0.x * r * c);
-    o0.y = r * (gv[1] * w0.y - x0.y * r * c);
-    o0.z = r * (gv[2] * w0.z - x0.z * r * c);
-    o0.w = r * (gv[3] * w0.w - x0.w * r * c);
-    o1.x = r * (gv[4] * w1.x - x1.x * r * c);
-    o1.y = r * (gv[5] * w1.y - x1.y * r * c);
-    o1.z = r * (gv[6] * w1.z - x1.z * r * c);
-    o1.w = r * (gv[7] * w1.w - x1.w * r * c);
-    if (din) {
-      float4 p0 = din[2 * i], p1 = din[2 * i + 1];
-      o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
-      o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
+  __syncthreads();
+  const int reps = (int)(rows / act_rows);
+  constexpr int MAXV = 4;   // vectors of 8 elements per thread kept in registers
+  for (int p = 0; p < reps; ++p) {
+    const int64_t row = (int64_t)p * act_rows + arow;
+    const bf16x8* g = d_normed + row * nvec;
+    float gw[MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = threadIdx.x + k * THREADS;
+      if (i < nvec) {
+        float gv[8];
+        unpack8(g[i], gv);
+        const float4 w0 = wv[2 * i], w1 = wv[2 * i + 1], x0 = xh[2 * i], x1 = xh[2 * i + 1];
+        gw[k][0] = gv[0] * w0.x; gw[k][1] = gv[1] * w0.y; gw[k][2] = gv[2] * w0.z; gw[k][3] = gv[3] * w0.w;
+        gw[k][4] = gv[4] * w1.x; gw[k][5] = gv[5] * w1.y; gw[k][6] = gv[6] * w1.z; gw[k][7] = gv[7] * w1.w;
+        dot += gw[k][0] * x0.x + gw[k][1] * x0.y + gw[k][2] * x0.z + gw[k][3] * x0.w + gw[k][4] * x1.x + gw[k][5] * x1.y +
+               gw[k][6] * x1.z + gw[k][7] * x1.w;
+      }
     }
-    dout[2 * i] = o0;
-    dout[2 * i + 1] = o1;
+    // c = mean over the row of (g * w) * xhat
+    const float c = block_sum(dot, scratch) / (float)dim;
+    const float4* din = d_stream_in ? d_stream_in + row * nvec * 2 : nullptr;
+    float4* dout = d_stream_out + row * nvec * 2;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = threadIdx.x + k * THREADS;
+      if (i < nvec) {
+        const float4 x0 = xh[2 * i], x1 = xh[2 * i + 1];
+        float4 o0, o1;
+        o0.x = r * (gw[k][0] - x0.x * c);
+        o0.y = r * (gw[k][1] - x0.y * c);
+        o0.z = r * (gw[k][2] - x0.z * c);
+        o0.w = r * (gw[k][3] - x0.w * c);
+        o1.x = r * (gw[k][4] - x1.x * c);
+        o1.y = r * (gw[k][5] - x1.y * c);
+        o1.z = r * (gw[k][6] - x1.z * c);
+        o1.w = r * (gw[k][7] - x1.w * c);
+        if (din) {
+          const float4 p0 = din[2 * i], p1 = din[2 * i + 1];
+          o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
+          o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
+        }
+        dout[2 * i] = o0;
+        dout[2 * i + 1] = o1;
+        if (lowp_out) {  // the bf16 copy the next GEMM reads, written here instead of by a separate cast pass
+          const float ov[8] = {o0.x, o0.y, o0.z, o0.w, o1.x, o1.y, o1.z, o1.w};
+          lowp_out[row * nvec + i] = pack8(ov);
+        }
+      }
+    }
   }
 }
 
@@ -194,25 +223,38 @@ __global__ void swiglu_fwd_kernel(const bf16x8* __restrict__ u, bf16x8* __restri
   a[idx] = pack8(o);
 }
 
+// One thread owns 8 columns of one activation row and walks all cotangent rows that share it (row = p * act_rows +
+// arow): the activations are read once and the two derivative factors computed once, instead of once per direction
+// (with 16 directions the 92 MB activation matrix was otherwise re-read from DRAM 16 times: it does not stay in L2).
 __global__ void swiglu_bwd_kernel(const bf16x8* __restrict__ da, const bf16x8* __restrict__ u, bf16x8* __restrict__ du,
                                   int64_t rows, int64_t act_rows, int hvec) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= rows * hvec) return;
-  const int64_t row = idx / hvec;
-  const int64_t arow = row % act_rows;
+  if (idx >= act_rows * hvec) return;
+  const int64_t arow = idx / hvec;
   const int col = (int)(idx % hvec);
-  float up[8], gate[8], g[8], dup[8], dgate[8];
+  float up[8], gate[8], f_up[8], f_gate[8];
   unpack8(u[arow * 2 * hvec + col], up);
   unpack8(u[arow * 2 * hvec + hvec + col], gate);
-  unpack8(da[idx], g);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const float sg = sigmoidf_(gate[i]);
-    dup[i] = g[i] * gate[i] * sg;
-    dgate[i] = g[i] * up[i] * sg * (1.f + gate[i] * (1.f - sg));
+    f_up[i] = gate[i] * sg;
+    f_gate[i] = up[i] * sg * (1.f + gate[i] * (1.f - sg));
   }
-  du[row * 2 * hvec + col] = pack8(dup);
-  du[row * 2 * hvec + hvec + col] = pack8(dgate);
+  const int reps = (int)(rows / act_rows);
+#pragma unroll 4
+  for (int p = 0; p < reps; ++p) {
+    const int64_t row = (int64_t)p * act_rows + arow;
+    float g[8], dup[8], dgate[8];
+    unpack8(da[row * hvec + col], g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      dup[i] = g[i] * f_up[i];
+      dgate[i] = g[i] * f_gate[i];
+    }
+    du[row * 2 * hvec + col] = pack8(dup);
+    du[row * 2 * hvec + hvec + col] = pack8(dgate);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------ interface glue
@@ -422,11 +464,26 @@ int lbi_add_rmsnorm_fwd(const void* branch, const float* stream_in, const float*
 }
 
 int lbi_rmsnorm_bwd(const void* d_normed, const float* x_stream, const float* rstd, const float* weight,
-                    const float* d_in, float* d_out, int64_t rows, int64_t act_rows, int dim, cudaStream_t st) {
+                    const float* d_in, float* d_out, void* d_out_lowp, int64_t rows, int64_t act_rows, int dim,
+                    cudaStream_t st) {
   if (rows == 0) return 0;
-  rmsnorm_bwd_kernel<128><<<(unsigned)rows, 128, 0, st>>>((const bf16x8*)d_normed, (const float4*)x_stream, rstd,
-                                                          (const float4*)weight, (const float4*)d_in, (float4*)d_out,
-                                                          act_rows, dim);
+  if (act_rows <= 0 || rows % act_rows != 0 || dim % 8 != 0 || dim > 8 * 4 * 256) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)dim * 2 * sizeof(float);
+  if (dim <= 8 * 4 * 128) {
+    rmsnorm_bwd_kernel<128><<<(unsigned)act_rows, 128, smem, st>>>((const bf16x8*)d_normed, (const float4*)x_stream, rstd,
+                                                                   (const float4*)weight, (const float4*)d_in, (float4*)d_out,
+                                                                   (bf16x8*)d_out_lowp, rows, act_rows, dim);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(rmsnorm_bwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    rmsnorm_bwd_kernel<256><<<(unsigned)act_rows, 256, smem, st>>>((const bf16x8*)d_normed, (const float4*)x_stream, rstd,
+                                                                   (const float4*)weight, (const float4*)d_in, (float4*)d_out,
+                                                                   (bf16x8*)d_out_lowp, rows, act_rows, dim);
+  }
   return launch_status();
 }
 
@@ -458,8 +515,9 @@ int lbi_swiglu_fwd(const void* u, void* a, int64_t rows, int hidden, cudaStream_
 int lbi_swiglu_bwd(const void* da, const void* u, void* du, int64_t rows, int64_t act_rows, int hidden,
                    cudaStream_t st) {
   const int hvec = hidden / 8;
-  const int64_t total = rows * hvec;
-  if (total == 0) return 0;
+  const int64_t total = act_rows * hvec;
+  if (total == 0 || rows == 0) return 0;
+  if (rows % act_rows != 0) return (int)cudaErrorInvalidValue;
   swiglu_bwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const bf16x8*)da, (const bf16x8*)u, (bf16x8*)du,
                                                                      rows, act_rows, hvec);
   return launch_status();

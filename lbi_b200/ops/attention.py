@@ -61,8 +61,11 @@ def flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, sca
     return out.reshape(batch * seq_len, n_heads * head_dim), lse
 
 
-def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, kernel_mode=None):
-    """Packed layout: do_rows [P*n, H*Dh] -> d_qkv [P*n, (H+2Hkv)*Dh]."""
+def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, kernel_mode=None, rope=None):
+    """Packed layout: do_rows [P*n, H*Dh] -> d_qkv [P*n, (H+2Hkv)*Dh].
+
+    ``rope = (cos, sin, interleaved)`` asks for dq and dk rotated back through the rotary embedding (its VJP); the
+    tcgen05 kernel does that in its epilogue, the other modes in a separate pass."""
     n = batch * seq_len
     nbasis = do_rows.shape[0] // n
     qkv_dim = (n_heads + 2 * n_kv_heads) * head_dim
@@ -70,8 +73,11 @@ def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, h
     if mode == "tcgen05_pblock":
         from .dispatch import KERNEL_LAUNCHES
 
-        KERNEL_LAUNCHES["count"] += 2
-        return ext().attn_pullback_packed(do_rows.contiguous(), qkv, o, lse, batch, seq_len, n_heads, head_dim, float(scale))
+        KERNEL_LAUNCHES["count"] += 3
+        if rope is None:
+            return ext().attn_pullback_packed(do_rows.contiguous(), qkv, o, lse, batch, seq_len, n_heads, head_dim, float(scale))
+        return ext().attn_pullback_packed(do_rows.contiguous(), qkv, o, lse, batch, seq_len, n_heads, head_dim, float(scale),
+                                          rope[0], rope[1], bool(rope[2]))
     q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
     out4 = o.view(batch, seq_len, n_heads, head_dim)
     d_qkv = torch.empty(nbasis * n, qkv_dim, dtype=do_rows.dtype, device=do_rows.device)
@@ -80,6 +86,10 @@ def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, h
         do = do_rows[p * n : (p + 1) * n].view(batch, seq_len, n_heads, head_dim)
         dq, dk, dv = _views(d_qkv[p * n : (p + 1) * n], batch, seq_len, n_heads, n_kv_heads, head_dim)
         fa._flash_attn_backward(do, q, k, v, out4, lse, dq, dk, dv, 0.0, float(scale), True, -1, -1, 0.0, None, False, None)
+    if rope is not None:
+        from .dispatch import rope_qkv
+
+        d_qkv = rope_qkv(d_qkv, rope[0], rope[1], n_heads, n_kv_heads, head_dim, seq_len, rope[2], inverse=True)
     return d_qkv
 
 

@@ -34,11 +34,18 @@ def add_rmsnorm_fwd(branch, stream, weight, eps, out_dtype):
     return ref.add_rmsnorm_fwd(branch, stream, weight, eps, out_dtype)
 
 
-def rmsnorm_bwd(d_normed, stream, rstd, weight, d_stream=None):
-    if _native(d_normed, stream, rstd, weight, d_stream) and d_normed.dtype == torch.bfloat16 and d_normed.shape[-1] % 8 == 0:
+def rmsnorm_bwd(d_normed, stream, rstd, weight, d_stream=None, lowp_dtype=None):
+    """d_stream (+)= J^T d_normed.  With ``lowp_dtype`` also returns the result cast to that dtype (one pass on CUDA)."""
+    native = _native(d_normed, stream, rstd, weight, d_stream) and d_normed.dtype == torch.bfloat16 and d_normed.shape[-1] % 8 == 0
+    if native and lowp_dtype == torch.bfloat16 and hasattr(ext(), "rmsnorm_bwd_lowp"):
         _count()
-        return ext().rmsnorm_bwd(d_normed.contiguous(), stream, rstd, weight.contiguous(), d_stream)
-    return ref.rmsnorm_bwd(d_normed, stream, rstd, weight, d_stream)
+        return ext().rmsnorm_bwd_lowp(d_normed.contiguous(), stream, rstd, weight.contiguous(), d_stream)
+    if native:
+        _count()
+        out = ext().rmsnorm_bwd(d_normed.contiguous(), stream, rstd, weight.contiguous(), d_stream)
+    else:
+        out = ref.rmsnorm_bwd(d_normed, stream, rstd, weight, d_stream)
+    return out if lowp_dtype is None else (out, out.to(lowp_dtype))
 
 
 def rmsnorm_wgrad(d_normed, stream, rstd):
@@ -179,12 +186,16 @@ def attention_fwd(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale):
     return ref.attention_fwd(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
 
 
-def attention_pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale):
+def attention_pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, rope=None):
+    """``rope = (cos, sin, interleaved)``: also rotate dq and dk back (fused into the kernel epilogue where possible)."""
     if do_rows.is_cuda and do_rows.dtype in _LOWP:
         from .attention import pullback_packed
 
-        return pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
-    return ref.attention_pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
+        return pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, rope=rope)
+    d_qkv = ref.attention_pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
+    if rope is not None:
+        d_qkv = rope_qkv(d_qkv, rope[0], rope[1], n_heads, n_kv_heads, head_dim, seq_len, rope[2], inverse=True)
+    return d_qkv
 
 
 def attention_bwd_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale):

@@ -7,17 +7,20 @@ Triton pipeline ``mamba_chunk_scan_combined`` (backbones/mamba2/ops/triton/ssd_c
 """
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
 from .native import ext, native_available
 
 CHUNK = 128
+ENABLED = os.environ.get("LBI_B200_TORCH_SSD", "0") != "1"   # set to use the chunked PyTorch scans everywhere
 
 
 def ssd_cuda_supported(x: torch.Tensor, B: torch.Tensor) -> bool:
     """bf16 or fp32 CUDA inputs with head_dim 64, d_state 64 / 128 and an even number of heads per group."""
-    if not (x.is_cuda and native_available() and hasattr(ext(), "ssd_chunk_scan_fwd")):
+    if not (ENABLED and x.is_cuda and native_available() and hasattr(ext(), "ssd_chunk_scan_fwd")):
         return False
     nheads, headdim = x.shape[2], x.shape[3]
     ngroups, dstate = B.shape[2], B.shape[3]
@@ -86,7 +89,8 @@ def ssd_chunk_scan_cuda(x, dt, A, B, C, D=None, initial_state=None, return_final
 # ------------------------------------------------------------------------------------------------ Mamba-3 SISO
 def siso_cuda_supported(V: torch.Tensor, Q: torch.Tensor) -> bool:
     """CUDA inputs with head_dim 64 and d_state 128 (the paper's Mamba-3 shape)."""
-    return bool(V.is_cuda and native_available() and hasattr(ext(), "siso_chunk_scan_fwd") and V.shape[3] == 64 and Q.shape[3] == 128)
+    return bool(ENABLED and V.is_cuda and native_available() and hasattr(ext(), "siso_chunk_scan_fwd") and V.shape[3] == 64
+                and Q.shape[3] == 128)
 
 
 def _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):

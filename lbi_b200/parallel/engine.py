@@ -254,23 +254,14 @@ class FastLBIEngine:
 
     # ------------------------------------------------------------------ basis-parallel plan
     def basis_plan(self) -> list[list[tuple[int, int, int]]]:
-        """Per rank, the (region, lo, hi) blocks of basis directions it pulls back.  Owners keep blocks of their own
-        regions up to an equal share; the surplus goes to the ranks with the least work, lowest rank first.  The plan
-        is a pure function of (regions, width, block size, world), so every rank computes the same one."""
+        """Per rank, the (region, lo, hi) blocks of basis directions it pulls back: the blocks of all regions that need a
+        Jacobian, in region order, cut into `world` contiguous runs of equal length.  A rank's run then covers part of
+        at most two neighbouring regions beyond whole ones, so it recomputes the forward of at most a few foreign
+        regions, and every rank computes the same plan from (regions, width, block size, world) alone."""
         k_regions, r, bc, world = self.model.num_regions, self.model.interface_width, self.basis_chunk, self.comm.world_size
-        blocks = {k: [(k, lo, min(r, lo + bc)) for lo in range(0, r, bc)] for k in range(k_regions - 1)}
-        total = sum(len(v) for v in blocks.values())
-        quota = -(-total // world)
-        plan: list[list[tuple[int, int, int]]] = [[] for _ in range(world)]
-        surplus: list[tuple[int, int, int]] = []
-        for k in range(k_regions - 1):
-            owner = self.placement.owner(k)
-            for blk in blocks[k]:
-                (plan[owner] if len(plan[owner]) < quota else surplus).append(blk)
-        for blk in surplus:
-            target = min(range(world), key=lambda rr: (len(plan[rr]), rr))
-            plan[target].append(blk)
-        return plan
+        blocks = [(k, lo, min(r, lo + bc)) for k in range(k_regions - 1) for lo in range(0, r, bc)]
+        quota = -(-len(blocks) // world) if blocks else 0
+        return [blocks[rank * quota : (rank + 1) * quota] for rank in range(world)]
 
     @torch.no_grad()
     def _adopt_region(self, k: int, state: torch.Tensor, ids: torch.Tensor) -> RegionRecord:

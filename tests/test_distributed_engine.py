@@ -141,8 +141,9 @@ def test_basis_plan_is_balanced_and_complete():
         assert sorted(blocks) == sorted(want)
         quota = -(-len(want) // world)
         assert max(len(p) for p in plan) <= quota
-    # 8 regions on 8 ranks: the last rank, whose own region needs no Jacobian, takes one block from each of the others
+    # 8 regions on 8 ranks: 56 blocks, 7 each; no rank touches more than two regions, so at most one foreign forward each
     fake = SimpleNamespace(model=SimpleNamespace(num_regions=8, interface_width=128), basis_chunk=16,
                            comm=SimpleNamespace(world_size=8), placement=RegionPlacement(8, 8))
     plan = FastLBIEngine.basis_plan(fake)
-    assert [len(p) for p in plan] == [7] * 8 and sorted({k for k, _, _ in plan[7]}) == list(range(7))
+    assert [len(p) for p in plan] == [7] * 8
+    assert all(len({k for k, _, _ in per_rank}) <= 2 for per_rank in plan) and {k for k, _, _ in plan[7]} == {6}

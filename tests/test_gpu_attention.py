@@ -81,3 +81,26 @@ def test_tcgen05_forward_matches_fp32_attention(b, h, t):
     lib_out, lib_lse = flash_forward_packed(qkv, b, t, h, h, 64, scale, kernel_mode="fa2")
     assert (lib_out.float() - out.float()).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
     assert (lib_lse - lse).abs().max().item() < 2e-3
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_pullback_epilogue_rotates_dq_dk_back(interleaved):
+    from lbi_b200.backbones.transformer.rope import rope_tables
+    from lbi_b200.ops.attention import flash_forward_packed, pullback_packed
+
+    b, h, t, p = 2, 3, 384, 5
+    g = torch.Generator(device=DEV).manual_seed(9)
+    qkv = torch.randn(b * t, 3 * h * 64, device=DEV, generator=g).bfloat16()
+    do = torch.randn(p * b * t, h * 64, device=DEV, generator=g).bfloat16()
+    scale = 0.125
+    o, lse = flash_forward_packed(qkv, b, t, h, h, 64, scale)
+    cos, sin = rope_tables(t, 64, 10000.0, torch.device(DEV))
+    plain = pullback_packed(do, qkv, o, lse, b, t, h, h, 64, scale, kernel_mode="tcgen05_pblock")
+    want = ops.rope_qkv(plain.clone(), cos, sin, h, h, 64, t, interleaved, inverse=True)
+    got = pullback_packed(do, qkv, o, lse, b, t, h, h, 64, scale, kernel_mode="tcgen05_pblock", rope=(cos, sin, interleaved))
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(qkv) == 0
+    tol = 2e-2 * want.float().abs().max().item()
+    assert (got.float() - want.float()).abs().max().item() <= tol
+    # dv is not rotated
+    assert torch.equal(got[:, 2 * h * 64 :], plain[:, 2 * h * 64 :])

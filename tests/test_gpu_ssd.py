@@ -79,3 +79,45 @@ def test_siso_kernels_match_recurrence(b, l, h, g):
     assert (y.double() - want).abs().max().item() <= 3e-2 * scale + 1e-3
     torch_y = mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Qb, Kb, Angles, D=D, Z=Z, chunk_size=64)
     assert (y.float() - torch_y.float()).abs().max().item() <= 3e-2 * scale + 1e-3
+
+
+@pytest.mark.parametrize("backbone,d_state", [("mamba2", 64), ("mamba3", 128)])
+def test_mamba_lbi_model_trains_through_the_kernels(backbone, d_state, monkeypatch):
+    """An LBI model with a Mamba backbone on the GPU under bf16 autocast: the kernel path and the PyTorch path give the
+    same loss and the same scan-engine gradients (the backward of the kernels recomputes the PyTorch form)."""
+    import torch.nn.functional as F
+
+    from lbi_b200.backbones import BackboneSpec
+    from lbi_b200.backward import ScanADEngine
+    from lbi_b200.interfaces import VectorMLPInterface
+    from lbi_b200.models import LBILanguageModel
+    from lbi_b200.ops import ssd as ops_ssd
+
+    torch.manual_seed(0)
+    spec = BackboneSpec(name=backbone, dim=128, layers=2, d_state=d_state, headdim=64, expand=2, d_conv=4, chunk_size=64)
+    iface = VectorMLPInterface(feature_dim=128, num_regions=2, interface_width=8, interface_map_hidden_dim=32)
+    model = LBILanguageModel(vocab_size=256, layers_per_region=1, backbone_spec=spec, interface=iface).to(DEV)
+    g = torch.Generator().manual_seed(1)
+    ids, tgt = torch.randint(0, 256, (2, 256), generator=g).to(DEV), torch.randint(0, 256, (2, 256), generator=g).to(DEV)
+
+    def run(enabled):
+        monkeypatch.setattr(ops_ssd, "ENABLED", enabled)
+        model.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits, cache = model.forward_with_cache(ids, detach_states=True)
+        loss = F.cross_entropy(logits.float().reshape(-1, 256), tgt.reshape(-1))
+        res = ScanADEngine(state_jacobian_mode="recompute", state_jacobian_basis_chunk=4).backward(model=model, loss=loss, cache=cache)
+        return loss.detach(), {k: (None if v is None else v.detach().clone()) for k, v in res.grad_map.items()}
+
+    launches0 = ops.dispatch.KERNEL_LAUNCHES["count"]
+    loss_k, grads_k = run(True)
+    assert ops.dispatch.KERNEL_LAUNCHES["count"] > launches0, "the Mamba mixer did not reach the CUDA kernels"
+    assert ops.ext().kernel_status(ids.float()) == 0
+    loss_t, grads_t = run(False)
+    assert abs(float(loss_k) - float(loss_t)) < 2e-2
+    for name, gt in grads_t.items():
+        if gt is None:
+            continue
+        gk = grads_k[name]
+        denom = gt.float().norm().item() + 1e-6
+        assert (gk.float() - gt.float()).norm().item() / denom < 0.15, name
