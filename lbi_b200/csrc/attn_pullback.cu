@@ -183,7 +183,8 @@ __device__ unsigned long long g_attn_phase[2][8];   // thread 0: wall-clock phas
 
 template <bool DKDV>
 __global__ void __launch_bounds__(THREADS, 1)
-pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do, const Params p) {
+pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
+                const __grid_constant__ CUtensorMap map_out, const Params p) {
   constexpr int PB = DKDV ? PB_DKDV : PB_DQ;
   constexpr int NSTREAM = Smem<DKDV>::NSTREAM;
   extern __shared__ uint8_t raw_smem[];
@@ -227,6 +228,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     fence_barrier_init();
     prefetch_tmap(&map_qkv);
     prefetch_tmap(&map_do);
+    prefetch_tmap(&map_out);
   }
   if (warp == 16) tmem_alloc(&s.tmem_base, 512);
   fence_before_sync();
@@ -530,14 +532,16 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 #ifdef LBI_ATTN_TIMING
     _t_acc = clock64();
 #endif
-    ok = __all_sync(0xffffffffu, ok);
+    // the four warps of a column slice share named barrier 1 + slice below: they take one decision (a raised abort flag wins)
+    named_barrier_sync(1 + slice, 128);
+    ok = (s.abort_flag == 0);
     if (ok) {
-      // One (direction, accumulator) item per 32-row quarter and pass: the four column slices take items round-robin and
-      // each thread writes a whole 64-element head row (128 contiguous bytes).  With rotary tables given, dQ and dK are
-      // rotated back here (the transpose of the forward rotation), which saves a separate pass over d_qkv.
+      // The (direction, accumulator) items (at most four) go one to each column slice; every thread turns one 64-element
+      // head row into bf16, the slice stages its 128 x 64 tile in the (now idle) dS buffers and one TMA store writes it:
+      // 16-byte stores from registers, 32 different lines per instruction, made this epilogue 12 % of the kernel.  With
+      // rotary tables given, dQ and dK are rotated back here (the transpose of the forward rotation).
       fence_after_sync();
       const int pos = own * TILE + r;
-      const int64_t tok = (int64_t)row_b + pos;
       constexpr int n_acc = DKDV ? 2 : 1;
       const int items = np * n_acc;
       for (int item = slice; item < items; item += 4) {
@@ -551,7 +555,8 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         tmem_ld_32x32(acc, lo);
         tmem_ld_32x32(acc + 32, hi);
         tmem_ld_wait();
-        uint4* dst = reinterpret_cast<uint4*>(p.d_qkv + ((int64_t)(p0 + pp) * p.n_rows + tok) * p.out_ld + col);
+        const uint32_t stage = smem_u32(s.ds_tile[0][0]) + item * PANEL_BYTES;   // 4 panels of 128 rows x 128 bytes
+        auto put = [&](int chunk, uint4 val) { st_shared_v4(swz(stage, r, chunk), val); };
         if (!rotate) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -564,8 +569,8 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
             o2.y = pack_bf16(__uint_as_float(hi[g * 8 + 2]) * mul, __uint_as_float(hi[g * 8 + 3]) * mul);
             o2.z = pack_bf16(__uint_as_float(hi[g * 8 + 4]) * mul, __uint_as_float(hi[g * 8 + 5]) * mul);
             o2.w = pack_bf16(__uint_as_float(hi[g * 8 + 6]) * mul, __uint_as_float(hi[g * 8 + 7]) * mul);
-            dst[g] = o;
-            dst[4 + g] = o2;
+            put(g, o);
+            put(4 + g, o2);
           }
         } else {
           const float4* c4 = reinterpret_cast<const float4*>(p.rope_cos + (int64_t)pos * (DH / 2));
@@ -585,8 +590,8 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
                   ob[q * 4 + e] = xb * cc[e] - xa * ss[e];
                 }
               }
-              dst[g] = make_uint4(pack_bf16(oa[0], oa[1]), pack_bf16(oa[2], oa[3]), pack_bf16(oa[4], oa[5]), pack_bf16(oa[6], oa[7]));
-              dst[4 + g] = make_uint4(pack_bf16(ob[0], ob[1]), pack_bf16(ob[2], ob[3]), pack_bf16(ob[4], ob[5]), pack_bf16(ob[6], ob[7]));
+              put(g, make_uint4(pack_bf16(oa[0], oa[1]), pack_bf16(oa[2], oa[3]), pack_bf16(oa[4], oa[5]), pack_bf16(oa[6], oa[7])));
+              put(4 + g, make_uint4(pack_bf16(ob[0], ob[1]), pack_bf16(ob[2], ob[3]), pack_bf16(ob[4], ob[5]), pack_bf16(ob[6], ob[7])));
             }
           } else {                     // pairs (2 i, 2 i + 1), angle index i
 #pragma unroll
@@ -603,10 +608,18 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
                   o[2 * e] = xa * cc[e] + xb * ss[e];
                   o[2 * e + 1] = xb * cc[e] - xa * ss[e];
                 }
-                dst[hh * 4 + g] = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+                put(hh * 4 + g, make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7])));
               }
             }
           }
+        }
+        fence_proxy_async();
+        named_barrier_sync(1 + slice, 128);
+        if (quarter == 0 && lane == 0) {
+          tma_store_2d(&map_out, &s.ds_tile[0][0][0] + item * PANEL_BYTES, col,
+                       (int)((int64_t)(p0 + pp) * p.n_rows + row_b + own * TILE));
+          tma_store_commit();
+          tma_store_wait_read<0>();   // the staging tile must stay intact until the copy engine has read it
         }
       }
     }
@@ -700,7 +713,7 @@ static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t wid
 }
 
 template <bool DKDV>
-static int launch(const CUtensorMap& mq, const CUtensorMap& md, const Params& p, cudaStream_t st) {
+static int launch(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMap& mo, const Params& p, cudaStream_t st) {
   constexpr int PB = DKDV ? PB_DKDV : PB_DQ;
   const size_t smem = sizeof(Smem<DKDV>) + 1024;
   static bool configured = false;
@@ -710,7 +723,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& md, const Params& p,
     configured = true;
   }
   dim3 grid(p.n_tiles, p.batch * p.heads, (p.nbasis + PB - 1) / PB);
-  pullback_kernel<DKDV><<<grid, THREADS, smem, st>>>(mq, md, p);
+  pullback_kernel<DKDV><<<grid, THREADS, smem, st>>>(mq, md, mo, p);
   return (int)cudaGetLastError();
 }
 
@@ -751,10 +764,12 @@ extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
   }
-  CUtensorMap mq, md;
+  CUtensorMap mq, md, mo;
   int rc = make_map(&mq, qkv, n_rows, 3ll * heads * DH);
   if (rc) return rc;
   rc = make_map(&md, d_o, rows_total, (int64_t)heads * DH);
+  if (rc) return rc;
+  rc = make_map(&mo, d_qkv, rows_total, 3ll * heads * DH);
   if (rc) return rc;
   Params p;
   p.batch = batch; p.heads = heads; p.seq_len = seq_len; p.nbasis = nbasis;
@@ -767,7 +782,7 @@ extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o
   p.d_qkv = (__nv_bfloat16*)d_qkv;
   p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_interleaved = rope_interleaved;
   p.status = status;
-  rc = launch<true>(mq, md, p, st);
+  rc = launch<true>(mq, md, mo, p, st);
   if (rc) return rc;
-  return launch<false>(mq, md, p, st);
+  return launch<false>(mq, md, mo, p, st);
 }
