@@ -272,66 +272,80 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": f"reference import failed: {exc!r}"[:300]}
 
     device = torch.device("cuda", 0)
-    torch.manual_seed(0)
     layers_per_region = max(1, cfg["layers"] // cfg["regions"])
-    chunk = int(os.environ.get("LBI_REF_BASIS_CHUNK", "8"))
-    rcfg = LBITrainingConfig(
-        variants="lbi", regime="lbi", backbone="transformer", device="cuda", dtype="bfloat16", vocab_size=cfg["vocab"],
-        tie_embeddings=True, seq_len=cfg["seq_len"], batch_size=cfg["batch"], layers=cfg["layers"], dim=cfg["dim"],
-        n_heads=cfg["n_heads"], d_intermediate=cfg["d_intermediate"], d_conv=1, region_size=layers_per_region,
-        message_dim=cfg["message_dim"], message_hidden_dim=cfg["message_hidden"], interface_jacobian_mode="recompute",
-        jacobian_basis_chunk=chunk, lr_model=3e-4, weight_decay=0.01, grad_clip=1.0, steps=max(1, args.steps + args.warmup),
-    )
-    try:
-        model = build_lbi_model(rcfg).to(device=device, dtype=torch.float32)
-        optimizer = torch.optim.AdamW(model.parameters(), lr=rcfg.lr_model, weight_decay=rcfg.weight_decay)
-    except Exception as exc:  # noqa: BLE001
-        return {"impl": "reference", "unavailable": f"reference model build failed: {exc!r}"[:300]}
-    n_params = sum(p.numel() for p in model.parameters())
+    # The reference's recompute Jacobian mode replicates the batch `chunk` times per pass; the launcher default (32) and
+    # 8 do not fit 180 GB at this configuration, so the largest chunk that fits is used and reported.
+    env_chunk = os.environ.get("LBI_REF_BASIS_CHUNK")
+    chunks = [int(env_chunk)] if env_chunk else [8, 4, 2, 1]
     total = args.warmup + args.steps
     host = make_batches(cfg, total, seed=1234)
-    dev_batches = [(x.to(device), y.to(device)) for x, y in host]
     path = {"engine": "ScanADEngine.backward"}
-
-    def step(xb, yb):
-        model.train()
-        with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
-            logits, cache = model.forward_with_cache(xb)
-        loss = next_token_loss(logits, yb)
-        engine = ScanADEngine.from_config(rcfg)
+    last_oom = ""
+    for chunk in chunks:
+        torch.manual_seed(0)
+        rcfg = LBITrainingConfig(
+            variants="lbi", regime="lbi", backbone="transformer", device="cuda", dtype="bfloat16", vocab_size=cfg["vocab"],
+            tie_embeddings=True, seq_len=cfg["seq_len"], batch_size=cfg["batch"], layers=cfg["layers"], dim=cfg["dim"],
+            n_heads=cfg["n_heads"], d_intermediate=cfg["d_intermediate"], d_conv=1, region_size=layers_per_region,
+            message_dim=cfg["message_dim"], message_hidden_dim=cfg["message_hidden"], interface_jacobian_mode="recompute",
+            jacobian_basis_chunk=chunk, lr_model=3e-4, weight_decay=0.01, grad_clip=1.0, steps=max(1, args.steps + args.warmup),
+        )
         try:
-            engine.backward(model=model, loss=loss, cache=cache)
-        except TypeError:
-            # Python >= 3.12: the reference's isinstance check against its runtime-checkable Protocol raises;
-            # call the function the engine wraps (same arguments, same providers).
-            path["engine"] = "lbi_scan_backward_step (ScanADEngine.backward raises TypeError on Python 3.12)"
-            model.zero_grad(set_to_none=True)
-            result = lbi_scan_backward_step(model, ce_loss=loss, cache=cache, pullback_provider=engine.pullback_provider,
-                                            local_vjp_provider=engine.local_vjp_provider)
-            assign_grad_map(model, result.grad_map)
-        torch.nn.utils.clip_grad_norm_(model.parameters(), rcfg.grad_clip)
-        optimizer.step()
-        return loss
+            model = build_lbi_model(rcfg).to(device=device, dtype=torch.float32)
+            optimizer = torch.optim.AdamW(model.parameters(), lr=rcfg.lr_model, weight_decay=rcfg.weight_decay)
+        except Exception as exc:  # noqa: BLE001
+            return {"impl": "reference", "unavailable": f"reference model build failed: {exc!r}"[:300]}
+        n_params = sum(p.numel() for p in model.parameters())
+        dev_batches = [(x.to(device), y.to(device)) for x, y in host]
 
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
-    try:
-        for i in range(args.warmup):
-            step(*dev_batches[i])
-        torch.cuda.synchronize()
-        sampler = ClockSampler(physical_gpu_index(0))
-        sampler.start()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        for i in range(args.warmup, total):
-            flush.zero_()
-            loss = step(*dev_batches[i])
-        stop.record()
-        torch.cuda.synchronize()
-        clocks = sampler.stop()
-    except torch.OutOfMemoryError as exc:
-        return {"impl": "reference", "unavailable": f"reference ran out of GPU memory at the named config (recompute chunk {chunk}): {str(exc)[:120]}"}
-    except Exception as exc:  # noqa: BLE001
-        return {"impl": "reference", "unavailable": f"reference step failed: {exc!r}"[:300]}
+        def step(xb, yb):
+            model.train()
+            with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+                logits, cache = model.forward_with_cache(xb)
+            loss = next_token_loss(logits, yb)
+            engine = ScanADEngine.from_config(rcfg)
+            try:
+                engine.backward(model=model, loss=loss, cache=cache)
+            except TypeError:
+                # Python >= 3.12: the reference's isinstance check against its runtime-checkable Protocol raises;
+                # call the function the engine wraps (same arguments, same providers).
+                path["engine"] = "lbi_scan_backward_step (ScanADEngine.backward raises TypeError on Python 3.12)"
+                model.zero_grad(set_to_none=True)
+                result = lbi_scan_backward_step(model, ce_loss=loss, cache=cache, pullback_provider=engine.pullback_provider,
+                                                local_vjp_provider=engine.local_vjp_provider)
+                assign_grad_map(model, result.grad_map)
+            torch.nn.utils.clip_grad_norm_(model.parameters(), rcfg.grad_clip)
+            optimizer.step()
+            return loss
+
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+        try:
+            for i in range(args.warmup):
+                step(*dev_batches[i])
+            torch.cuda.synchronize()
+            sampler = ClockSampler(physical_gpu_index(0))
+            sampler.start()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for i in range(args.warmup, total):
+                flush.zero_()
+                loss = step(*dev_batches[i])
+            stop.record()
+            torch.cuda.synchronize()
+            clocks = sampler.stop()
+            break
+        except torch.OutOfMemoryError as exc:
+            last_oom = str(exc)[:120]
+            del model, optimizer, dev_batches, flush, step
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+            continue
+        except Exception as exc:  # noqa: BLE001
+            return {"impl": "reference", "unavailable": f"reference step failed: {exc!r}"[:300]}
+    else:
+        return {"impl": "reference", "unavailable": f"reference ran out of GPU memory at the named config for every recompute chunk in {chunks}: {last_oom}"}
     ms = start.elapsed_time(stop) / max(1, args.steps)
     tokens = cfg["batch"] * cfg["seq_len"]
     e2e = None
