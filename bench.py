@@ -319,19 +319,43 @@ def run_reference(args) -> dict:
             return loss
 
         flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+        # One reference step at the headline configuration takes about 13 minutes on a B200 (recompute chunk 1 is the only
+        # one that fits), so the requested warm-up / step counts are cut to what fits LBI_REF_TIME_BUDGET_S (default 1500 s,
+        # never below one warm-up and one timed step); the counts actually run are the ones reported.
+        budget_s = float(os.environ.get("LBI_REF_TIME_BUDGET_S", "1500"))
+        n_warm, n_steps = args.warmup, args.steps
         try:
-            for i in range(args.warmup):
+            t_first = None
+            i = 0
+            while i < n_warm:
+                t0 = time.perf_counter()
                 step(*dev_batches[i])
+                torch.cuda.synchronize()
+                if t_first is None:
+                    t_first = time.perf_counter() - t0
+                    if t_first * (args.warmup + args.steps) > budget_s:
+                        n_warm = 1
+                        n_steps = max(1, min(args.steps, int((budget_s - t_first) // t_first)))
+                i += 1
+            total = n_warm + n_steps
             torch.cuda.synchronize()
             sampler = ClockSampler(physical_gpu_index(0))
             sampler.start()
+            # A reference step takes minutes at this configuration, so the device-timed and the end-to-end figure come
+            # from the same K steps: every step copies its batch from pinned host memory and reads its loss back (as the
+            # reference's own training loop does); CUDA events give the device time, the wall clock the end-to-end time.
             start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            wall0 = time.perf_counter()
             start.record()
-            for i in range(args.warmup, total):
+            for i in range(n_warm, total):
                 flush.zero_()
-                loss = step(*dev_batches[i])
+                x, y = host[i]
+                loss = step(x.to(device, non_blocking=True), y.to(device, non_blocking=True))
+                loss_val = float(loss.item())
             stop.record()
             torch.cuda.synchronize()
+            wall = time.perf_counter() - wall0
             clocks = sampler.stop()
             break
         except torch.OutOfMemoryError as exc:
@@ -346,29 +370,21 @@ def run_reference(args) -> dict:
             return {"impl": "reference", "unavailable": f"reference step failed: {exc!r}"[:300]}
     else:
         return {"impl": "reference", "unavailable": f"reference ran out of GPU memory at the named config for every recompute chunk in {chunks}: {last_oom}"}
-    ms = start.elapsed_time(stop) / max(1, args.steps)
+    ms = start.elapsed_time(stop) / max(1, n_steps)
     tokens = cfg["batch"] * cfg["seq_len"]
-    e2e = None
-    if not args.no_e2e:
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for i in range(args.steps):
-            x, y = host[args.warmup + i]
-            loss_val = float(step(x.to(device, non_blocking=True), y.to(device, non_blocking=True)).item())
-        torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
-        e2e = {"value": tokens * args.steps / dt, "unit": "tokens/s", "h2d_bytes_per_step": int(host[0][0].numel() * 16),
-               "d2h_bytes_per_step": 4, "last_loss": loss_val}
+    e2e = {"value": tokens * n_steps / wall, "unit": "tokens/s", "h2d_bytes_per_step": int(host[0][0].numel() * 16),
+           "d2h_bytes_per_step": 4, "last_loss": loss_val, "note": "same steps as the device-timed figure (wall clock)"}
     return {
         "metric": "train tokens/s (device-timed, max over ranks)", "value": tokens / (ms / 1e3), "unit": "tokens/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "n_gpus": 1, "steps": n_steps, "warmup": n_warm, "ms_per_step": ms, "higher_is_better": True,
+        "requested": {"steps": args.steps, "warmup": args.warmup, "time_budget_s": budget_s},
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16 autocast (fp32 weights)",
         "data": "synthetic uniform-random tokens, random-init weights", "impl": "reference",
         "config": {"model": cfg["model"], "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": cfg["regions"],
                    "region_axis": "depth (the reference has no sequence-axis regions)", "interface_width": cfg["message_dim"],
                    "params": n_params, "parallelism": "single", "jacobian_mode": "recompute", "basis_chunk": chunk,
                    "d_conv": "1 (the reference's Transformer requires d_conv >= 1)", "path": path["engine"]},
-        "clocks": clocks, "e2e": e2e, "gpu_launches": 0, "final_loss": float(loss),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 0, "final_loss": float(loss.detach()),
     }
 
 

@@ -47,6 +47,13 @@ int lbi_affine_scan_peer(const float* const* mats_ptrs, const float* const* offs
                          int slot_base, uint32_t seq, float* g, int batch, int world, int k_local, int r, int* status,
                          cudaStream_t stream);
 
+// Basis-parallel form of the cross-GPU scan: every rank publishes partial rows [K, B, R, R] (rows[k][b][j][a] =
+// d s_out[j] / d s_in[a], zero where another rank did the work) and partial offsets [K, B, R]; the kernel sums them over
+// the ranks as it loads them and writes all g_k ([B, K, R]) on every rank.
+int lbi_affine_scan_peer_sum(const float* const* rows_ptrs, const float* const* offs_ptrs, const uint32_t* flags, int slot_base,
+                             uint32_t seq, float* g, int batch, int world, int k_total, int r, int* status,
+                             cudaStream_t stream);
+
 // Gradient reduce-scatter by peer loads: reduced[i] = sum_w grad_ptrs[w][lo + i] for this rank's shard, written back
 // into this rank's own buffer at [lo, lo + n), with sum of squares of the reduced shard added to *sumsq.
 // mc_grads: optional NVLS multicast address of the gradient buffer (multimem.ld_reduce); null selects peer loads.

@@ -162,7 +162,8 @@ __device__ __forceinline__ float fast_exp2(float x) {
 //   [kernel: 0 = dQ, 1 = dK/dV][role: 0 = TMA producer, 1 = issuer X, 2 = issuer Y, 3 = compute thread 0][slot]; slot 7 = total.
 #ifdef LBI_ATTN_TIMING
 __device__ unsigned long long g_attn_timing[2][4][12];
-__device__ unsigned long long g_attn_phase[2][8];   // thread 0: wall-clock phases of the CTA, summed over CTAs
+__device__ unsigned long long g_attn_phase[2][8];
+__device__ int g_attn_debug;   // bit 0: no exp in S jobs, 1: no dS math, 2: no shared-memory stores of P / dS, 3: no TMEM loads   // thread 0: wall-clock phases of the CTA, summed over CTAs
 #define TIMED(slot, ...)              \
   {                                   \
     const long long _t0 = clock64();  \
@@ -458,6 +459,12 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         const bool diagonal = (qi == kj);
         {
           uint32_t v[32];
+#ifdef LBI_ATTN_TIMING
+          if (g_attn_debug & 8) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0x3c003c00u + i + n;
+          } else
+#endif
           TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
           TIMED(9, __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]));  // tcgen05.wait::ld above: the loads are complete  // TMEM buffer free
 #ifdef LBI_ATTN_TIMING
@@ -465,6 +472,12 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 #endif
           const int col0 = slice * 32;
           const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse_r, -lse_r);
+#ifdef LBI_ATTN_TIMING
+          if (g_attn_debug & 1) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) preg[i] = v[2 * i] ^ v[2 * i + 1];
+          } else
+#endif
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 t = unpack_f32x2(fma_f32x2(pack_u32x2(v[2 * i], v[2 * i + 1]), sc2, nl2));
@@ -477,7 +490,11 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
               preg[i] &= (col <= r ? 0x0000ffffu : 0u) | (col + 1 <= r ? 0xffff0000u : 0u);
             }
           }
+#ifdef LBI_ATTN_TIMING
+          if (DKDV && !(g_attn_debug & 4)) {
+#else
           if (DKDV) {
+#endif
 #pragma unroll
             for (int g = 0; g < 4; ++g)
               st_shared_v4(swz(p_panel, r, (slice & 1) * 4 + g),
@@ -500,6 +517,12 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         if (!ok) break;
         {
           uint32_t v[32];
+#ifdef LBI_ATTN_TIMING
+          if (g_attn_debug & 8) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0x3c003c00u + i + n;
+          } else
+#endif
           TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
           TIMED(9, __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]));  // tcgen05.wait::ld above: the loads are complete
 #ifdef LBI_ATTN_TIMING
@@ -511,9 +534,22 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           for (int g = 0; g < 4; ++g) {
             uint32_t w[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
+            for (int e = 0; e < 4; ++e) {
+#ifdef LBI_ATTN_TIMING
+              if (g_attn_debug & 2) {
+                w[e] = preg[g * 4 + e] ^ v[g * 8 + e * 2] ^ v[g * 8 + e * 2 + 1];
+                continue;
+              }
+#endif
               w[e] = mul_bf16x2(preg[g * 4 + e],
                                 cvt_bf16x2(sub_f32x2(pack_u32x2(v[g * 8 + e * 2], v[g * 8 + e * 2 + 1]), delta2)));
+            }
+#ifdef LBI_ATTN_TIMING
+            if (g_attn_debug & 4) {
+              if (w[0] == 0x12345u && w[3] == 0x54321u) st_shared_v4(swz(ds_panel, r, 0), make_uint4(w[0], w[1], w[2], w[3]));
+              continue;
+            }
+#endif
             st_shared_v4(swz(ds_panel, r, (slice & 1) * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
           }
         }
@@ -732,6 +768,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMa
 
 #ifdef LBI_ATTN_TIMING
 // Copies the 2 x 4 x 8 cycle counters to `out` and clears them.
+extern "C" int lbi_attn_set_debug(int flags) { return (int)cudaMemcpyToSymbol(lbi::attn::g_attn_debug, &flags, sizeof(int)); }
 extern "C" int lbi_attn_phase_read(unsigned long long* out) {
   cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_phase, sizeof(unsigned long long) * 16);
   if (e != cudaSuccess) return (int)e;

@@ -528,6 +528,18 @@ Tensor affine_scan_peer(const Tensor& mats_ptrs, const Tensor& offs_ptrs, const 
   return g;
 }
 
+Tensor affine_scan_peer_sum(const Tensor& rows_ptrs, const Tensor& offs_ptrs, const Tensor& flags, int64_t slot_base, int64_t seq,
+                            int64_t batch, int64_t world, int64_t k_total, int64_t r) {
+  c10::cuda::CUDAGuard guard(flags.device());
+  Tensor g = torch::empty({batch, k_total, r}, flags.options().dtype(at::kFloat));
+  Tensor st = status_word(flags);
+  check(lbi_affine_scan_peer_sum(ptr_table<const float* const*>(rows_ptrs), ptr_table<const float* const*>(offs_ptrs),
+                                 reinterpret_cast<const uint32_t*>(flags.data_ptr<int>()), (int)slot_base, (uint32_t)seq,
+                                 g.data_ptr<float>(), (int)batch, (int)world, (int)k_total, (int)r, st.data_ptr<int>(), cur_stream()),
+        "affine_scan_peer_sum");
+  return g;
+}
+
 void grad_reduce_scatter_(const Tensor& grad_ptrs, int64_t mc_ptr, int64_t rank, int64_t world, int64_t lo, int64_t n,
                           Tensor sumsq) {
   CHECK_F32(sumsq);
@@ -610,6 +622,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("interface_update_handoff", &interface_update_handoff);
   m.def("wait_state", &wait_state);
   m.def("affine_scan_peer", &affine_scan_peer);
+  m.def("affine_scan_peer_sum", &affine_scan_peer_sum);
   m.def("grad_reduce_scatter_", &grad_reduce_scatter_);
   m.def("exchange_scalar", &exchange_scalar);
   m.def("adamw_allgather_", &adamw_allgather_);

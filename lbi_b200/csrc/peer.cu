@@ -206,6 +206,62 @@ __global__ void __launch_bounds__(256) affine_scan_peer_kernel(const float* cons
   }
 }
 
+// Basis-parallel variant: every rank holds PARTIAL Jacobian rows for all regions (zeros where another rank did the work),
+// rows[k][b][j][a] = d s_out[j] / d s_in[a], and partial offsets offs[k][b][a].  The kernel sums the partials over the
+// ranks while it loads them (plain peer loads) and runs g_k[a] = b_k[a] + sum_j rows_k[j][a] g_{k+1}[j] on every rank.
+// One CTA per batch element; component a of the result is shared by blockDim.x / r thread groups that split the j range
+// (the loads are peer loads with microseconds of latency, so many must be in flight).  Dynamic smem: (2 + groups) * r floats.
+__global__ void __launch_bounds__(1024) affine_scan_peer_sum_kernel(const float* const* rows_ptrs, const float* const* offs_ptrs,
+                                                                     const uint32_t* flags, int slot_base, uint32_t seq,
+                                                                     float* __restrict__ g, int world, int batch, int k_total, int r,
+                                                                     int* status) {
+  extern __shared__ float vec[];
+  __shared__ int ok_all;
+  const int b = blockIdx.x;
+  if (threadIdx.x == 0) ok_all = 1;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    if (!wait_flag(flags + slot_base + threadIdx.x, seq, status, 45)) ok_all = 0;
+  }
+  __syncthreads();
+  if (!ok_all) return;
+  const int groups = max(1, (int)blockDim.x / r);
+  const int a = threadIdx.x % r, grp = threadIdx.x / r;
+  const bool active = grp < groups;
+  float* cur = vec;
+  float* nxt = vec + r;
+  float* part = vec + 2 * r;   // [groups][r]
+  float* g_b = g + (size_t)b * k_total * r;
+  for (int k = k_total - 1; k >= 0; --k) {
+    const size_t off_base = ((size_t)k * batch + b) * r;
+    const size_t row_base = off_base * r;
+    if (active) {
+      float acc = 0.f;
+      if (grp == 0)
+        for (int w = 0; w < world; ++w) acc += __ldcv(offs_ptrs[w] + off_base + a);
+      if (k < k_total - 1) {
+        for (int j = grp; j < r; j += groups) {
+          float m = 0.f;
+          for (int w = 0; w < world; ++w) m += __ldcv(rows_ptrs[w] + row_base + (size_t)j * r + a);
+          acc += m * cur[j];
+        }
+      }
+      part[grp * r + a] = acc;
+    }
+    __syncthreads();
+    if (threadIdx.x < r) {
+      float acc = 0.f;
+      for (int q = 0; q < groups; ++q) acc += part[q * r + threadIdx.x];
+      nxt[threadIdx.x] = acc;
+      g_b[(size_t)k * r + threadIdx.x] = acc;
+    }
+    __syncthreads();
+    float* t = cur;
+    cur = nxt;
+    nxt = t;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ gradient path
 __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
   float4 v;
@@ -337,6 +393,17 @@ int lbi_affine_scan_peer(const float* const* mats_ptrs, const float* const* offs
   if (batch <= 0) return 0;
   affine_scan_peer_kernel<<<batch, 256, 2 * r * sizeof(float), st>>>(mats_ptrs, offs_ptrs, flags, slot_base, seq, g, world,
                                                                      k_local, r, status);
+  return (int)cudaGetLastError();
+}
+
+int lbi_affine_scan_peer_sum(const float* const* rows_ptrs, const float* const* offs_ptrs, const uint32_t* flags, int slot_base,
+                             uint32_t seq, float* g, int batch, int world, int k_total, int r, int* status, cudaStream_t st) {
+  if (batch <= 0) return 0;
+  if (r <= 0 || r > 1024) return (int)cudaErrorInvalidValue;
+  const int threads = 1024 / r * r >= 32 ? (1024 / r) * r : r;   // a whole number of groups of r threads
+  const int groups = threads / r;
+  affine_scan_peer_sum_kernel<<<batch, threads, (size_t)(2 + groups) * r * sizeof(float), st>>>(rows_ptrs, offs_ptrs, flags, slot_base,
+                                                                                                seq, g, world, batch, k_total, r, status);
   return (int)cudaGetLastError();
 }
 
