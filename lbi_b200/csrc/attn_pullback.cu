@@ -182,6 +182,14 @@ __device__ int g_attn_debug;   // bit 0: no exp in S jobs, 1: no dS math, 2: no 
 #define TIMING_END(role)
 #endif
 
+#ifdef LBI_ATTN_TIMING
+#define MMA_X(...) do { if (!(g_attn_debug & 32)) mma_bf16(__VA_ARGS__); } while (0)
+#define MMA_Y(...) do { if (!(g_attn_debug & 16)) mma_bf16(__VA_ARGS__); } while (0)
+#else
+#define MMA_X(...) mma_bf16(__VA_ARGS__)
+#define MMA_Y(...) mma_bf16(__VA_ARGS__)
+#endif
+
 template <bool DKDV>
 __global__ void __launch_bounds__(THREADS, 1)
 pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
@@ -323,7 +331,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         fence_after_sync();
         const uint32_t d_tmem = tmem + (n & 1) * 128;
         const uint64_t da = kmajor0 + a16, db = kmajor0 + b16;
-        TIMED(4, _Pragma("unroll") for (int k = 0; k < 4; ++k) mma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc_nn, k));
+        TIMED(4, _Pragma("unroll") for (int k = 0; k < 4; ++k) MMA_X(d_tmem, da + 2 * k, db + 2 * k, idesc_nn, k));
         TIMED(5, mma_commit(&s.bar_ready[n & 1]));
         if (++r == jobs_per_iter) {
           r = 0;
@@ -364,10 +372,10 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
             const uint64_t db = mnmajor0 + stream0 + (2 + (c0 & (NDO - 1))) * TILE16;
             if (np == 2) {  // the two dO tiles are adjacent stages: one N = 128 operand with two 64-wide panels
 #pragma unroll
-              for (int k = 0; k < 8; ++k) mma_bf16(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
+              for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
             } else {
 #pragma unroll
-              for (int k = 0; k < 8; ++k) mma_bf16(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
+              for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
             }
             mma_commit(&s.bar_p_free);
           }
@@ -379,7 +387,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           const uint64_t da = mnmajor0 + ds0 + buf * DSBUF16;
           const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) mma_bf16(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
+          for (int k = 0; k < 8; ++k) MMA_Y(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
           mma_commit(&s.bar_ds_free[buf]);
           mma_commit(&s.bar_stream_empty[2 + (d & (NDO - 1))]);  // dO tile d: its dV and this dK are behind the commit, dP was consumed
         } else {
@@ -387,7 +395,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            mma_bf16(acc, da + (k >> 2) * PANEL16 + (k & 3) * 2, db + 128 * k, idesc_acc, first | (k != 0));
+            MMA_Y(acc, da + (k >> 2) * PANEL16 + (k & 3) * 2, db + 128 * k, idesc_acc, first | (k != 0));
           mma_commit(&s.bar_ds_free[buf]);
         }
         if (pp == np - 1) mma_commit(&s.bar_stream_empty[it & 1]);  // Q_it (DKDV) or K_it and V_it (DQ) may be overwritten

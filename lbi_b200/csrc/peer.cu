@@ -34,7 +34,10 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 }
 // Wait until *flag >= want (sequence numbers, wrap-safe for differences < 2^31).  False on timeout.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t want, int* status, int site) {
-  if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+  // the clock is read only after a few thousand polls: %globaltimer is slow to read and most waits are short
+  for (int i = 0; i < 4096; ++i) {
+    if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+  }
   const unsigned long long t0 = now_ns();
   uint32_t spins = 0;
   while ((int32_t)(ld_acquire_sys(flag) - want) < 0) {

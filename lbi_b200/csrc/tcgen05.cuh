@@ -91,9 +91,12 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
   return ok != 0;
 }
 // Returns false after WAIT_LIMIT_NS; *status (global) receives `site` and *abort_flag (shared) is raised.
+// The clock is only consulted by waits that have already slept 20 us: reading %globaltimer costs far more than a
+// barrier hand-over (about 200 cycles), and nearly every wait in these pipelines ends within microseconds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int site) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
   const unsigned long long t0 = global_ns();
   while (true) {
     if (mbar_try_wait_hint(bar, parity, 200000u)) return true;   // up to 0.2 ms asleep per attempt
