@@ -274,9 +274,25 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           tma_load_2d(s.fixed[1 + pp], &map_do, &s.bar_fixed, h * DH,
                       (int)((int64_t)(p0 + pp) * p.n_rows + row_b + own * TILE));
       }
+      // The shared-memory ring holds the tiles of two steps, less than the DRAM latency of a dO tile is worth in steps:
+      // tiles are therefore requested into L2 PF steps ahead, so that the ring refills at L2 latency.
+      constexpr int PF = 4;
+      auto prefetch_step = [&](int it2) {
+        if (it2 >= n_iter) return;
+        if (DKDV) {
+          tma_prefetch_l2_2d(&map_qkv, col_q, row_b + (own + it2) * TILE);
+          for (int pp = 0; pp < np; ++pp)
+            tma_prefetch_l2_2d(&map_do, h * DH, (int)((int64_t)(p0 + pp) * p.n_rows + row_b + (own + it2) * TILE));
+        } else {
+          tma_prefetch_l2_2d(&map_qkv, col_k, row_b + it2 * TILE);
+          tma_prefetch_l2_2d(&map_qkv, col_v, row_b + it2 * TILE);
+        }
+      };
+      for (int it2 = 2; it2 < 2 + PF; ++it2) prefetch_step(it2);
       int c = 0;  // running index of dO tiles (DKDV)
       for (int it = 0; it < n_iter && ok; ++it) {
         const int st = it & 1;
+        prefetch_step(it + 2 + PF);
         if (it >= 2) {
           TIMED(0, ok = mbar_wait(&s.bar_stream_empty[st], ((it >> 1) - 1) & 1, abortp, p.status, 11));
           if (!ok) break;
@@ -370,14 +386,12 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
             if (!ok) break;
             const uint64_t da = mnmajor0 + p16;
             const uint64_t db = mnmajor0 + stream0 + (2 + (c0 & (NDO - 1))) * TILE16;
-            if (np == 2) {  // the two dO tiles are adjacent stages: one N = 128 operand with two 64-wide panels
-#pragma unroll
-              for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
+            TIMED(2, if (np == 2) {  // the two dO tiles are adjacent stages: one N = 128 operand with two 64-wide panels
+              _Pragma("unroll") for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
             } else {
-#pragma unroll
-              for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
-            }
-            mma_commit(&s.bar_p_free);
+              _Pragma("unroll") for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
+            });
+            TIMED(3, mma_commit(&s.bar_p_free));
           }
           continue;
         }
@@ -386,19 +400,17 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         if (DKDV) {
           const uint64_t da = mnmajor0 + ds0 + buf * DSBUF16;
           const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
-#pragma unroll
-          for (int k = 0; k < 8; ++k) MMA_Y(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
-          mma_commit(&s.bar_ds_free[buf]);
-          mma_commit(&s.bar_stream_empty[2 + (d & (NDO - 1))]);  // dO tile d: its dV and this dK are behind the commit, dP was consumed
+          TIMED(2, _Pragma("unroll") for (int k = 0; k < 8; ++k) MMA_Y(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0)));
+          TIMED(3, mma_commit(&s.bar_ds_free[buf]);
+                mma_commit(&s.bar_stream_empty[2 + (d & (NDO - 1))]));  // dO tile d: its dV and this dK are behind the commit, dP was consumed
         } else {
           const uint64_t da = kmajor0 + ds0 + buf * DSBUF16;
           const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            MMA_Y(acc, da + (k >> 2) * PANEL16 + (k & 3) * 2, db + 128 * k, idesc_acc, first | (k != 0));
-          mma_commit(&s.bar_ds_free[buf]);
+          TIMED(2, _Pragma("unroll") for (int k = 0; k < 8; ++k)
+            MMA_Y(acc, da + (k >> 2) * PANEL16 + (k & 3) * 2, db + 128 * k, idesc_acc, first | (k != 0)));
+          TIMED(3, mma_commit(&s.bar_ds_free[buf]));
         }
-        if (pp == np - 1) mma_commit(&s.bar_stream_empty[it & 1]);  // Q_it (DKDV) or K_it and V_it (DQ) may be overwritten
+        if (pp == np - 1) TIMED(3, mma_commit(&s.bar_stream_empty[it & 1]))  // Q_it (DKDV) or K_it and V_it (DQ) may be overwritten
       }
       if (ok) mma_commit(&s.bar_acc_done);
       TIMING_END(2);
