@@ -61,6 +61,17 @@ int lbi_matrix_norms(const float* mats, float* spec, float* frob, int count, int
 int lbi_affine_suffix_scan(const float* mats, const float* offsets, const float* seed_or_null, float* g, int batch, int k,
                            int r, cudaStream_t stream);
 
+
+// ---- interface Jacobian products over a basis (interface_jac.cu) -----------------------------------------
+// out[b, p, :] = (((in_scale * g[b, p, :]) @ wa) o d[b, :]) @ wb;  g [B, P, din], wa [din, hidden], d [B, hidden] or null,
+// wb [hidden, dout] or null (then out [B, P, hidden] = (g @ wa) o d).  All fp32 row-major.
+int lbi_interface_mlp_jac(const float* g, const float* wa, const float* d, const float* wb, float* out, int batch, int p_total,
+                          int din, int hidden, int dout, float in_scale, cudaStream_t stream);
+// LayerNorm Jacobian at x [B, R] applied to g [B, P, R]: transpose = 1 gives J^T g (weight on the input side),
+// transpose = 0 gives J g (weight on the output side); the result is multiplied by out_scale.
+int lbi_layernorm_jac(const float* x, const float* weight, const float* g, float* out, int batch, int p_total, int r, float eps,
+                      int transpose, float out_scale, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,6 +31,17 @@ int lbi_siso_chunk_scan_fwd(const void* v, const void* kr, const void* qr, const
                             void* y, int batch, int seq_len, int heads, int head_dim, int d_state, int* status,
                             cudaStream_t stream);
 
+// The chunk scan with free operand roles (the backward passes are this operator with the roles permuted):
+//   y_t = sum_{s <= t} exp(c_t - c_s) (cq_t . bk_s) w_s v_s + exp(c_t) cq_t . init      (s < t when `strict`)
+//   final = sum_s exp(c_end - c_s) w_s v_s bk_s^T + exp(c_end) init
+// v [B*L, H*64] bf16; bk / cq [B*L, G*N] bf16 (or [B*L, H*128] when `per_head`); weight [B, H, L] fp32 or null (w = 1);
+// cum [B, H, L] fp32 in-chunk cumulative sums.  The result goes to `y32` (fp32) when it is set, else to `y` (bf16).
+// States are [p][n] (per_head: [n][p]).  N = 64 or 128 (per_head: 128); heads / groups even unless per_head.
+int lbi_ssd_scan_generic(const void* v, const void* bk, const void* cq, const float* weight, const float* cum,
+                         const float* d_skip, const float* skip_tok, int strict, const float* init_state, float* states,
+                         void* prev, float* final_state, void* y, float* y32, int batch, int seq_len, int heads, int groups,
+                         int d_state, int per_head, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

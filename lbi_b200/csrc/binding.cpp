@@ -278,6 +278,48 @@ std::tuple<Tensor, Tensor> matrix_norms(const Tensor& mats, int64_t iters) {
   return {spec, frob};
 }
 
+// (((in_scale g) @ wa) o d) @ wb over a basis: g [B, P, din] fp32, wa [din, hidden], d [B, hidden] or none, wb [hidden, dout] or none.
+Tensor interface_mlp_jac(const Tensor& g, const Tensor& wa, const c10::optional<Tensor>& d, const c10::optional<Tensor>& wb,
+                         double in_scale) {
+  CHECK_F32(g);
+  CHECK_F32(wa);
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.dim() == 3 && wa.dim() == 2 && wa.size(0) == g.size(2), "interface_mlp_jac: g [B, P, din], wa [din, hidden]");
+  const int64_t batch = g.size(0), p = g.size(1), din = g.size(2), hidden = wa.size(1);
+  int64_t dout = hidden;
+  if (d) {
+    CHECK_F32((*d));
+    TORCH_CHECK(d->dim() == 2 && d->size(0) == batch && d->size(1) == hidden, "interface_mlp_jac: d must be [B, hidden]");
+  }
+  if (wb) {
+    CHECK_F32((*wb));
+    TORCH_CHECK(wb->dim() == 2 && wb->size(0) == hidden, "interface_mlp_jac: wb must be [hidden, dout]");
+    dout = wb->size(1);
+  }
+  Tensor out = torch::empty({batch, p, dout}, g.options());
+  check(lbi_interface_mlp_jac(g.data_ptr<float>(), wa.data_ptr<float>(), d ? d->data_ptr<float>() : nullptr,
+                              wb ? wb->data_ptr<float>() : nullptr, out.data_ptr<float>(), (int)batch, (int)p, (int)din, (int)hidden,
+                              (int)dout, (float)in_scale, cur_stream()),
+        "interface_mlp_jac");
+  return out;
+}
+
+Tensor layernorm_jac(const Tensor& x, const c10::optional<Tensor>& weight, const Tensor& g, double eps, bool transpose, double out_scale) {
+  CHECK_F32(x);
+  CHECK_F32(g);
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(x.dim() == 2 && g.dim() == 3 && g.size(0) == x.size(0) && g.size(2) == x.size(1), "layernorm_jac: x [B, R], g [B, P, R]");
+  if (weight) {
+    CHECK_F32((*weight));
+    TORCH_CHECK(weight->numel() == x.size(1), "layernorm_jac: weight must be [R]");
+  }
+  Tensor out = torch::empty_like(g);
+  check(lbi_layernorm_jac(x.data_ptr<float>(), weight ? weight->data_ptr<float>() : nullptr, g.data_ptr<float>(), out.data_ptr<float>(),
+                          (int)g.size(0), (int)g.size(1), (int)g.size(2), (float)eps, transpose ? 1 : 0, (float)out_scale, cur_stream()),
+        "layernorm_jac");
+  return out;
+}
+
 Tensor affine_suffix_scan(const Tensor& mats, const Tensor& offsets, const c10::optional<Tensor>& seed) {
   CHECK_F32(mats);
   CHECK_F32(offsets);
@@ -449,6 +491,51 @@ std::tuple<Tensor, Tensor> siso_chunk_scan_fwd(const Tensor& v, const Tensor& kr
   return {y, final_state};
 }
 
+// The chunk scan with free operand roles.  v [B, L, H, 64] bf16; bk / cq [B, L, G, N] bf16 (per_head: G = H, N = 128);
+// a [B, L, H] fp32 log-decay per token; weight [B, L, H] fp32 or none; skip_tok [B, H, L]; init [B, H, 64, N] (per_head:
+// [B, H, N, 64]).  Returns (y [B, L, H, 64] in bf16 or fp32, final_state).
+std::tuple<Tensor, Tensor> ssd_scan_generic(const Tensor& v, const Tensor& bk, const Tensor& cq, const Tensor& a,
+                                            const c10::optional<Tensor>& weight, const c10::optional<Tensor>& d_skip,
+                                            const c10::optional<Tensor>& skip_tok, const c10::optional<Tensor>& init_state,
+                                            bool strict, bool per_head, bool out_f32) {
+  CHECK_BF16(v);
+  CHECK_BF16(bk);
+  CHECK_BF16(cq);
+  CHECK_F32(a);
+  c10::cuda::CUDAGuard guard(v.device());
+  TORCH_CHECK(v.dim() == 4 && bk.dim() == 4 && cq.sizes() == bk.sizes() && a.dim() == 3, "scan: expected v [B,L,H,64], bk/cq [B,L,G,N], a [B,L,H]");
+  const int64_t batch = v.size(0), seq = v.size(1), heads = v.size(2), hd = v.size(3), groups = bk.size(2), n = bk.size(3);
+  TORCH_CHECK(hd == 64 && a.size(0) == batch && a.size(1) == seq && a.size(2) == heads && bk.size(1) == seq, "scan: shape mismatch");
+  TORCH_CHECK(!per_head || groups == heads, "scan: per_head wants one bk / cq per head");
+  const int64_t chunks = seq / 128;
+  auto f32 = v.options().dtype(at::kFloat);
+  Tensor ones = torch::ones({heads}, f32);
+  Tensor a_t = torch::empty({batch, heads, seq}, f32), cum = torch::empty({batch, heads, seq}, f32);
+  Tensor w_t;
+  if (weight) {
+    CHECK_F32((*weight));
+    TORCH_CHECK(weight->sizes() == a.sizes(), "scan: weight must match a");
+    w_t = weight->transpose(1, 2).contiguous();
+  }
+  Tensor states = torch::empty({batch, chunks, heads, hd, n}, f32);
+  Tensor prev = torch::empty({batch, chunks, heads, hd, n}, v.options());
+  Tensor final_state = per_head ? torch::empty({batch, heads, n, hd}, f32) : torch::empty({batch, heads, hd, n}, f32);
+  Tensor y = torch::empty(v.sizes(), out_f32 ? f32 : v.options());
+  Tensor st = status_word(v);
+  check(lbi_ssd_cumsum(a.data_ptr<float>(), nullptr, ones.data_ptr<float>(), a_t.data_ptr<float>(), cum.data_ptr<float>(), (int)batch,
+                       (int)seq, (int)heads, 0, 0.f, 0.f, cur_stream()),
+        "scan_cumsum");
+  check(lbi_ssd_scan_generic(v.data_ptr(), bk.data_ptr(), cq.data_ptr(), weight ? w_t.data_ptr<float>() : nullptr,
+                             cum.data_ptr<float>(), d_skip ? d_skip->data_ptr<float>() : nullptr,
+                             skip_tok ? skip_tok->data_ptr<float>() : nullptr, strict ? 1 : 0,
+                             init_state ? init_state->data_ptr<float>() : nullptr, states.data_ptr<float>(), prev.data_ptr(),
+                             final_state.data_ptr<float>(), out_f32 ? nullptr : y.data_ptr(),
+                             out_f32 ? y.data_ptr<float>() : nullptr, (int)batch, (int)seq, (int)heads, (int)groups, (int)n,
+                             per_head ? 1 : 0, st.data_ptr<int>(), cur_stream()),
+        "ssd_scan_generic");
+  return {y, final_state};
+}
+
 // ---- peer-memory kernels.  `*_ptrs` are int64 CUDA tensors holding one device pointer per rank.
 template <typename T>
 T ptr_table(const Tensor& t) {
@@ -606,6 +693,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("suffix_scan", &suffix_scan);
   m.def("affine_suffix_scan", &affine_suffix_scan);
   m.def("matrix_norms", &matrix_norms);
+  m.def("interface_mlp_jac", &interface_mlp_jac);
+  m.def("layernorm_jac", &layernorm_jac);
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("a_t") = false, py::arg("b_t") = false,
         py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);
   m.def("gemm_tn", &gemm_tn);
@@ -615,6 +704,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_fwd_packed", &attn_fwd_packed);
   m.def("ssd_chunk_scan_fwd", &ssd_chunk_scan_fwd);
   m.def("siso_chunk_scan_fwd", &siso_chunk_scan_fwd);
+  m.def("ssd_scan_generic", &ssd_scan_generic);
   m.def("kernel_status", &kernel_status);
   m.def("set_peer_wait_limit_ms", &set_peer_wait_limit_ms);
   m.def("peer_barrier", &peer_barrier);

@@ -258,6 +258,7 @@ struct ScanParams {
   const float* skip_tok;  // [B, H, L] per-token skip coefficient added to d_skip, or null
   int strict;             // 1: token l sees tokens j < l through the scores (its own term comes with the skip)
   __nv_bfloat16* y;       // [B*L, H*64]
+  float* y32;             // when set, the result is written here in fp32 instead of `y`
   int* status;
 };
 
@@ -387,18 +388,24 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
       tmem_ld_wait();
       const float dsk = (p.d_skip ? p.d_skip[h] : 0.f) + (p.skip_tok ? p.skip_tok[base + l] : 0.f);
       const uint32_t xrow = smem_u32(s.xt) + l * 128;
-      uint4* dst = reinterpret_cast<uint4*>(p.y + ((int64_t)row0 + l) * (p.heads * P) + h * P);
+      const int64_t out_off = ((int64_t)row0 + l) * (p.heads * P) + h * P;
+      uint4* dst = reinterpret_cast<uint4*>(p.y + out_off);
+      float4* dst32 = reinterpret_cast<float4*>(p.y32 + out_off);
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         const uint4 xv = lds128(xrow + ((ch ^ (l & 7)) << 4));
         const uint32_t* rr = ch < 4 ? r0 + ch * 8 : r1 + (ch - 4) * 8;
         const float2 x0 = unpack2(xv.x), x1 = unpack2(xv.y), x2 = unpack2(xv.z), x3 = unpack2(xv.w);
-        uint4 o;
-        o.x = pack2(__uint_as_float(rr[0]) + dsk * x0.x, __uint_as_float(rr[1]) + dsk * x0.y);
-        o.y = pack2(__uint_as_float(rr[2]) + dsk * x1.x, __uint_as_float(rr[3]) + dsk * x1.y);
-        o.z = pack2(__uint_as_float(rr[4]) + dsk * x2.x, __uint_as_float(rr[5]) + dsk * x2.y);
-        o.w = pack2(__uint_as_float(rr[6]) + dsk * x3.x, __uint_as_float(rr[7]) + dsk * x3.y);
-        dst[ch] = o;
+        const float o0 = __uint_as_float(rr[0]) + dsk * x0.x, o1 = __uint_as_float(rr[1]) + dsk * x0.y,
+                    o2 = __uint_as_float(rr[2]) + dsk * x1.x, o3 = __uint_as_float(rr[3]) + dsk * x1.y,
+                    o4 = __uint_as_float(rr[4]) + dsk * x2.x, o5 = __uint_as_float(rr[5]) + dsk * x2.y,
+                    o6 = __uint_as_float(rr[6]) + dsk * x3.x, o7 = __uint_as_float(rr[7]) + dsk * x3.y;
+        if (p.y32) {
+          dst32[2 * ch] = make_float4(o0, o1, o2, o3);
+          dst32[2 * ch + 1] = make_float4(o4, o5, o6, o7);
+        } else {
+          dst[ch] = make_uint4(pack2(o0, o1), pack2(o2, o3), pack2(o4, o5), pack2(o6, o7));
+        }
       }
     }
   }
@@ -455,7 +462,7 @@ static int set_smem(K kernel, size_t bytes) {
 template <int N, bool PH>
 static int run(const void* x, const void* bm, const void* cm, const float* dt, const float* cum, const float* d_skip,
                const float* skip_tok, int strict, const float* init_state, float* states, void* prev, float* final_state,
-               void* y, int batch, int seq_len, int heads, int groups, int* status, cudaStream_t st) {
+               void* y, float* y32, int batch, int seq_len, int heads, int groups, int* status, cudaStream_t st) {
   const int chunks = seq_len / L;
   const int64_t rows = (int64_t)batch * seq_len;
   CUtensorMap mx, mb, mc, mp;
@@ -486,7 +493,7 @@ static int run(const void* x, const void* bm, const void* cm, const float* dt, c
     if (rc) return rc;
   }
   {
-    ScanParams p{seq_len, heads, groups, chunks, dt, cum, d_skip, skip_tok, strict, (__nv_bfloat16*)y, status};
+    ScanParams p{seq_len, heads, groups, chunks, dt, cum, d_skip, skip_tok, strict, (__nv_bfloat16*)y, y32, status};
     const size_t smem = sizeof(SmemScan<N>) + 1024;
     rc = set_smem(chunk_scan_kernel<N, PH>, smem);
     if (rc) return rc;
@@ -517,11 +524,11 @@ extern "C" int lbi_ssd_chunk_scan_fwd(const void* x, const void* bm, const void*
       (heads / groups) % 2 != 0 || (int64_t)batch * seq_len >= (1ll << 31))
     return (int)cudaErrorInvalidValue;
   if (d_state == 64)
-    return run<64, false>(x, bm, cm, dt, cum, d_skip, nullptr, 0, init_state, states, prev, final_state, y, batch, seq_len, heads,
-                          groups, status, st);
+    return run<64, false>(x, bm, cm, dt, cum, d_skip, nullptr, 0, init_state, states, prev, final_state, y, nullptr, batch, seq_len,
+                          heads, groups, status, st);
   if (d_state == 128)
-    return run<128, false>(x, bm, cm, dt, cum, d_skip, nullptr, 0, init_state, states, prev, final_state, y, batch, seq_len, heads,
-                           groups, status, st);
+    return run<128, false>(x, bm, cm, dt, cum, d_skip, nullptr, 0, init_state, states, prev, final_state, y, nullptr, batch, seq_len,
+                           heads, groups, status, st);
   return (int)cudaErrorInvalidValue;
 }
 
@@ -532,6 +539,27 @@ extern "C" int lbi_siso_chunk_scan_fwd(const void* v, const void* kr, const void
   using namespace lbi::ssd;
   if (head_dim != P || d_state != 128 || seq_len % L != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * seq_len >= (1ll << 31))
     return (int)cudaErrorInvalidValue;
-  return run<128, true>(v, kr, qr, nullptr, cum, d_skip, skip_tok, 1, init_state, states, prev, final_state, y, batch, seq_len,
+  return run<128, true>(v, kr, qr, nullptr, cum, d_skip, skip_tok, 1, init_state, states, prev, final_state, y, nullptr, batch, seq_len,
                         heads, heads, status, st);
+}
+
+extern "C" int lbi_ssd_scan_generic(const void* v, const void* bk, const void* cq, const float* weight, const float* cum,
+                                    const float* d_skip, const float* skip_tok, int strict, const float* init_state,
+                                    float* states, void* prev, float* final_state, void* y, float* y32, int batch, int seq_len,
+                                    int heads, int groups, int d_state, int per_head, int* status, cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (seq_len % L != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * seq_len >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+  if (per_head) {
+    if (d_state != 128) return (int)cudaErrorInvalidValue;
+    return run<128, true>(v, bk, cq, weight, cum, d_skip, skip_tok, strict, init_state, states, prev, final_state, y, y32, batch,
+                          seq_len, heads, heads, status, st);
+  }
+  if (groups <= 0 || heads % groups != 0 || (heads / groups) % 2 != 0) return (int)cudaErrorInvalidValue;
+  if (d_state == 64)
+    return run<64, false>(v, bk, cq, weight, cum, d_skip, skip_tok, strict, init_state, states, prev, final_state, y, y32, batch,
+                          seq_len, heads, groups, status, st);
+  if (d_state == 128)
+    return run<128, false>(v, bk, cq, weight, cum, d_skip, skip_tok, strict, init_state, states, prev, final_state, y, y32, batch,
+                           seq_len, heads, groups, status, st);
+  return (int)cudaErrorInvalidValue;
 }

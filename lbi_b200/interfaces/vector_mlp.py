@@ -61,9 +61,33 @@ def activation_derivative(pre: torch.Tensor, activation: str) -> torch.Tensor:
     raise ValueError(activation)
 
 
+def _jac_kernels(*tensors: torch.Tensor) -> bool:
+    """The basis-Jacobian kernels (csrc/interface_jac.cu) serve fp32 CUDA tensors outside of autograd graphs."""
+    from .. import ops
+
+    if not (tensors[0].is_cuda and ops.native_available() and hasattr(ops.ext(), "interface_mlp_jac")):
+        return False
+    if torch.is_grad_enabled() and any(t.requires_grad for t in tensors):
+        return False
+    return all(t.dtype == torch.float32 for t in tensors)
+
+
+def _activation_diagonal(head: VectorMLPHead, first: nn.Linear, x: torch.Tensor) -> torch.Tensor:
+    pre = F.linear(x.float(), first.weight, first.bias)
+    return activation_derivative(pre, head.activation).contiguous()
+
+
 def head_input_jacobian_t(head: VectorMLPHead, x: torch.Tensor, g_out: torch.Tensor) -> torch.Tensor:
     """J^T of an interface map at input x [B, Din], applied to cotangents g_out [B, P, Dout] -> [B, P, Din]."""
     first, second = head.layers()
+    if g_out.dim() == 3 and _jac_kernels(g_out, first.weight, *(() if second is None else (second.weight,))):
+        from .. import ops
+
+        ops.dispatch.KERNEL_LAUNCHES["count"] += 1
+        if second is None:   # g @ W
+            return ops.ext().interface_mlp_jac(g_out.contiguous(), first.weight.detach().contiguous(), None, None, 1.0)
+        return ops.ext().interface_mlp_jac(g_out.contiguous(), second.weight.detach().contiguous(), _activation_diagonal(head, first, x),
+                                           first.weight.detach().contiguous(), 1.0)
     dtype = torch.promote_types(g_out.dtype, first.weight.dtype)
     g = g_out.to(dtype)
     if second is None:
@@ -76,6 +100,15 @@ def head_input_jacobian_t(head: VectorMLPHead, x: torch.Tensor, g_out: torch.Ten
 def head_input_jacobian(head: VectorMLPHead, x: torch.Tensor, t_in: torch.Tensor) -> torch.Tensor:
     """Forward-mode counterpart: J applied to tangents t_in [B, P, Din] -> [B, P, Dout]."""
     first, second = head.layers()
+    if t_in.dim() == 3 and _jac_kernels(t_in, first.weight, *(() if second is None else (second.weight,))):
+        from .. import ops
+
+        ops.dispatch.KERNEL_LAUNCHES["count"] += 1
+        w1_t = first.weight.detach().t().contiguous()
+        if second is None:
+            return ops.ext().interface_mlp_jac(t_in.contiguous(), w1_t, None, None, 1.0)
+        return ops.ext().interface_mlp_jac(t_in.contiguous(), w1_t, _activation_diagonal(head, first, x),
+                                           second.weight.detach().t().contiguous(), 1.0)
     dtype = torch.promote_types(t_in.dtype, first.weight.dtype)
     t = t_in.to(dtype) @ first.weight.to(dtype).t()
     if second is None:
@@ -87,6 +120,12 @@ def head_input_jacobian(head: VectorMLPHead, x: torch.Tensor, t_in: torch.Tensor
 
 def layer_norm_input_jacobian_t(norm: nn.LayerNorm, x: torch.Tensor, g_out: torch.Tensor) -> torch.Tensor:
     """Closed-form LayerNorm J^T at x [B, R] applied to g_out [B, P, R]."""
+    if g_out.dim() == 3 and x.dim() == 2 and _jac_kernels(g_out, x, *(() if norm.weight is None else (norm.weight,))):
+        from .. import ops
+
+        ops.dispatch.KERNEL_LAUNCHES["count"] += 1
+        return ops.ext().layernorm_jac(x.contiguous(), None if norm.weight is None else norm.weight.detach().contiguous(),
+                                       g_out.contiguous(), float(norm.eps), True, 1.0)
     dtype = torch.promote_types(g_out.dtype, torch.float32)
     xf = x.to(dtype)
     mu = xf.mean(dim=-1, keepdim=True)
@@ -102,6 +141,12 @@ def layer_norm_input_jacobian_t(norm: nn.LayerNorm, x: torch.Tensor, g_out: torc
 
 def layer_norm_input_jacobian(norm: nn.LayerNorm, x: torch.Tensor, t_in: torch.Tensor) -> torch.Tensor:
     """Forward-mode LayerNorm Jacobian (the un-weighted core is symmetric, so only the weight moves sides)."""
+    if t_in.dim() == 3 and x.dim() == 2 and _jac_kernels(t_in, x, *(() if norm.weight is None else (norm.weight,))):
+        from .. import ops
+
+        ops.dispatch.KERNEL_LAUNCHES["count"] += 1
+        return ops.ext().layernorm_jac(x.contiguous(), None if norm.weight is None else norm.weight.detach().contiguous(),
+                                       t_in.contiguous(), float(norm.eps), False, 1.0)
     dtype = torch.promote_types(t_in.dtype, torch.float32)
     xf = x.to(dtype)
     mu = xf.mean(dim=-1, keepdim=True)

@@ -1,9 +1,14 @@
-"""Mamba-2 SSD chunk scan: CUDA forward (csrc/ssd.cu) behind a differentiable wrapper.
+"""Mamba-2 SSD chunk scan: CUDA forward and backward (csrc/ssd.cu) behind a differentiable wrapper.
 
-``ssd_chunk_scan_cuda`` runs the four sm_100a kernels (cumsum, chunk state, state passing, fused chunk scan) and, when a
-gradient is needed, differentiates by recomputing the chunked PyTorch form (``backbones/mamba2/ssd.py``) under
-autograd: the forward is the kernel's, the backward is exact for the same math.  The reference's counterpart is the
-Triton pipeline ``mamba_chunk_scan_combined`` (backbones/mamba2/ops/triton/ssd_combined.py:343-513).
+``ssd_chunk_scan_cuda`` runs the four sm_100a kernels (cumsum, chunk state, state passing, fused chunk scan).  The
+backward runs the same kernels three more times with the operand roles permuted (``ssd_backward``): the scan
+
+    y_t = sum_{s <= t} exp(c_t - c_s) (cq_t . bk_s) w_s v_s + exp(c_t) cq_t . init
+
+is linear in v, in bk and in cq, and each of the three pullbacks is again a scan of this form, in forward or reversed
+time, so that no separate backward kernels exist.  The gradient of the decay follows from the per-head gradients of B
+and C (``dc_t = C_t . dC_t - B_t . dB_t``).  The reference's counterpart is the Triton pipeline
+``mamba_chunk_scan_combined`` with its ten backward kernels (backbones/mamba2/ops/triton/ssd_combined.py:343-513).
 """
 from __future__ import annotations
 
@@ -16,6 +21,7 @@ from .native import ext, native_available
 
 CHUNK = 128
 ENABLED = os.environ.get("LBI_B200_TORCH_SSD", "0") != "1"   # set to use the chunked PyTorch scans everywhere
+BACKWARD_KERNELS = os.environ.get("LBI_B200_SSD_RECOMPUTE_BACKWARD", "0") != "1"   # set to differentiate the PyTorch form
 
 
 def ssd_cuda_supported(x: torch.Tensor, B: torch.Tensor) -> bool:
@@ -44,20 +50,140 @@ def _forward_kernels(x, dt, A, B, C, D, initial_state):
     return y[:, :seqlen], final
 
 
+def scan_generic_torch(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False):
+    """fp32 PyTorch statement of the kernels' scan operator (token-by-token), the oracle of ``scan_generic``.
+
+    v [b, l, h, p]; bk, cq [b, l, g, n]; a, weight [b, l, h]; init [b, h, p, n] ([b, h, n, p] when ``per_head``).
+    Returns (y [b, l, h, p] fp32, final state in the layout of ``init``)."""
+    b, l, h, p = v.shape
+    g, n = bk.shape[2], bk.shape[3]
+    vf, af = v.float(), a.float()
+    bkf = bk.float().repeat_interleave(h // g, dim=2)
+    cqf = cq.float().repeat_interleave(h // g, dim=2)
+    wf = torch.ones_like(af) if weight is None else weight.float()
+    state = vf.new_zeros(b, h, p, n) if init is None else (init.float().transpose(2, 3) if per_head else init.float()).clone()
+    ys = []
+    for t in range(l):
+        decayed = state * torch.exp(af[:, t])[..., None, None]
+        new = decayed + (wf[:, t, :, None] * vf[:, t])[..., None] * bkf[:, t, :, None, :]
+        ys.append(torch.einsum("bhpn,bhn->bhp", decayed if strict else new, cqf[:, t]))
+        state = new
+    return torch.stack(ys, dim=1), (state.transpose(2, 3) if per_head else state)
+
+
+def scan_generic(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False):
+    """The kernels' scan operator with free operand roles; bf16 operands, fp32 result.  ``seq_len % 128 == 0``."""
+    from .dispatch import KERNEL_LAUNCHES
+
+    bf = torch.bfloat16
+    y, final = ext().ssd_scan_generic(v.to(bf).contiguous(), bk.to(bf).contiguous(), cq.to(bf).contiguous(), a.float().contiguous(),
+                                      None if weight is None else weight.float().contiguous(), None, None,
+                                      None if init is None else init.float().contiguous(), bool(strict), bool(per_head), True)
+    KERNEL_LAUNCHES["count"] += 4
+    return y, final
+
+
+def _shift_reverse(a):
+    """Log-decays of the time-reversed recurrence: position tau takes a[T - tau], position 0 takes 0."""
+    return torch.cat([torch.zeros_like(a[:, :1]), a.flip(1)[:, :-1]], dim=1)
+
+
+def _blocks(t, dup):
+    """[b, l, h, n] -> [b, l, h * max(n // 64, dup), 64]: the state axis as virtual heads of width 64."""
+    b, l, h, n = t.shape
+    if n == 64 and dup > 1:
+        return t.unsqueeze(3).expand(b, l, h, dup, 64).reshape(b, l, h * dup, 64)
+    return t.reshape(b, l, h * (n // 64), 64)
+
+
+def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, scan=scan_generic):
+    """Gradients of (y, final) = SSD(x, dt, A, B, C, D, init) from three role-permuted scans.
+
+    With X = dt x, c the cumulative log-decay and per-head copies of B, C:
+      dX_s   = sum_{t >= s} e^{c_t - c_s} (B_s . C_t) gy_t        reversed time: v = gy, bk = C, cq = B, init = gfinal
+      dC_t   = sum_{s <= t} e^{c_t - c_s} (gy_t . X_s) B_s        forward time:  v = B,  bk = x (w = dt), cq = gy, init = init^T
+      dB_s/dt_s = sum_{t >= s} e^{c_t - c_s} (x_s . gy_t) C_t     reversed time: v = C,  bk = gy, cq = x, init = gfinal^T
+    The state axis (64 or 128 wide) of B and C is cut into virtual heads of width 64 for the last two.  Then
+      dc_t = C_t . dC_t - B_t . dB_t  (+ gfinal . final at the last token),  da = reversed cumulative sum of dc,
+      ddt = da A + dX . x,  dA = sum da dt,  dx = dt dX + D gy,  dD = sum gy . x.
+    All arguments are un-padded; ``scan`` is ``scan_generic`` (kernels) or ``scan_generic_torch`` (oracle)."""
+    bsz, seqlen, h, p = x.shape
+    g, n = B.shape[2], B.shape[3]
+    rep = h // g
+    pad = (-seqlen) % CHUNK
+    xf, dtf, Bf, Cf, gyf = x.float(), dt.float(), B.float(), C.float(), gy.float()
+    if pad:
+        xf, Bf, Cf, gyf = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (xf, Bf, Cf, gyf))
+        dtf = F.pad(dtf, (0, 0, 0, pad))
+    Af = A.float()
+    a = dtf * Af
+    a_rev = _shift_reverse(a)
+    Bh, Ch = Bf.repeat_interleave(rep, dim=2), Cf.repeat_interleave(rep, dim=2)       # [b, l, h, n]
+    nv = max(n // 64, 2)                                                               # virtual heads per head (even)
+    gfin = None if gfinal is None else gfinal.float()
+
+    # 1. dX (before the dt factor) and the gradient of the initial state
+    y1, fin1 = scan(gyf.flip(1), Cf.flip(1), Bf.flip(1), a_rev, None, gfin)
+    dX = y1.flip(1)
+    d_init = fin1 * torch.exp(a[:, 0])[..., None, None] if init is not None else None
+
+    def state_blocks(st):   # [b, h, p, n] -> [b, h * nv, 64 (n in block), 64 (p)]
+        t = st.float().transpose(2, 3)                                                 # [b, h, n, p]
+        if n == 64:
+            return t.unsqueeze(2).expand(bsz, h, nv, 64, p).reshape(bsz, h * nv, 64, p)
+        return t.reshape(bsz, h * nv, 64, p)
+
+    rep_v = lambda t: t.repeat_interleave(nv, dim=2)  # noqa: E731
+    # 2. dC per head
+    y2, _ = scan(_blocks(Bh, nv), xf, gyf, rep_v(a), rep_v(dtf), None if init is None else state_blocks(init))
+    dCh = y2.reshape(bsz, seqlen + pad, h, nv * 64)[..., :n]
+    # 3. dB per head
+    y3, _ = scan(_blocks(Ch, nv).flip(1), gyf.flip(1), xf.flip(1), rep_v(a_rev), None, None if gfin is None else state_blocks(gfin))
+    dBh = y3.flip(1).reshape(bsz, seqlen + pad, h, nv * 64)[..., :n] * dtf[..., None]
+
+    dc = (Ch * dCh).sum(-1) - (Bh * dBh).sum(-1)                                       # [b, l, h]
+    if gfin is not None:
+        dc[:, -1] += (gfin * final.float()).sum((2, 3))
+    da = dc.flip(1).cumsum(1).flip(1)
+    ddt = da * Af + (dX * xf).sum(-1)
+    dA = (da * dtf).sum((0, 1))
+    dx = dtf[..., None] * dX
+    dD = None
+    if D is not None:
+        dx = dx + D.float()[None, None, :, None] * gyf
+        dD = (gyf * xf).sum((0, 1, 3))
+    dB = dBh.reshape(bsz, seqlen + pad, g, rep, n).sum(3)
+    dC = dCh.reshape(bsz, seqlen + pad, g, rep, n).sum(3)
+    cut = slice(0, seqlen)
+    return dx[:, cut], ddt[:, cut], dA, dB[:, cut], dC[:, cut], dD, d_init
+
+
 class _SSDFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dt, A, B, C, D, initial_state):
         y, final = _forward_kernels(x, dt, A, B, C, D, initial_state)
         ctx.save_for_backward(x, dt, A, B, C, D if D is not None else x.new_empty(0),
-                              initial_state if initial_state is not None else x.new_empty(0))
+                              initial_state if initial_state is not None else x.new_empty(0), final)
         ctx.has_d, ctx.has_init = D is not None, initial_state is not None
         return y.to(x.dtype), final
 
     @staticmethod
     def backward(ctx, gy, gfinal):
+        x, dt, A, B, C, D, init, final = ctx.saved_tensors
+        if BACKWARD_KERNELS and hasattr(ext(), "ssd_scan_generic"):
+            if gy is None:
+                gy = torch.zeros_like(x)
+            dx, ddt, dA, dB, dC, dD, d_init = ssd_backward(x, dt, A, B, C, D if ctx.has_d else None, init if ctx.has_init else None,
+                                                           final, gy, gfinal)
+            return (dx.to(x.dtype), ddt.to(dt.dtype), dA.to(A.dtype), dB.to(B.dtype), dC.to(C.dtype),
+                    None if dD is None else dD.to(D.dtype), None if d_init is None else d_init.to(init.dtype))
+        return _SSDFunction._backward_recompute(ctx, gy, gfinal)
+
+    @staticmethod
+    def _backward_recompute(ctx, gy, gfinal):
         from ..backbones.mamba2.ssd import ssd_chunk_scan
 
-        x, dt, A, B, C, D, init = ctx.saved_tensors
+        x, dt, A, B, C, D, init, _ = ctx.saved_tensors
         leaves = [t.detach().requires_grad_(t.is_floating_point()) for t in (x, dt, A, B, C)]
         d_leaf = D.detach().requires_grad_(True) if ctx.has_d else None
         i_leaf = init.detach().requires_grad_(True) if ctx.has_init else None
@@ -117,6 +243,36 @@ def _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
     return y[:, :seqlen], final
 
 
+def siso_core_backward(Qr, Kr, adt, skip, V, gy, scan=scan_generic):
+    """Gradients of y_t = sum_{s < t} e^{c_t - c_s} (Qr_t . Kr_s) V_s + skip_t V_t with respect to the preprocessed operands.
+
+    Qr, Kr [b, l, h, 128]; adt, skip [b, l, h]; V, gy [b, l, h, 64].  Three strict scans with permuted roles:
+      dV_s  = sum_{t > s} e^{c_t - c_s} (Kr_s . Qr_t) gy_t + skip_s gy_s    reversed, per head:  v = gy, bk = Qr, cq = Kr
+      dQr_t = sum_{s < t} e^{c_t - c_s} (gy_t . V_s) Kr_s                   forward:  v = Kr (two halves), bk = V,  cq = gy
+      dKr_s = sum_{t > s} e^{c_t - c_s} (V_s . gy_t) Qr_t                   reversed: v = Qr (two halves), bk = gy, cq = V
+    and dadt = reversed cumulative sum of (Qr . dQr - Kr . dKr), dskip = gy . V.  Returns (dQr, dKr, dadt, dskip, dV)."""
+    bsz, seqlen, h, _ = V.shape
+    n = Qr.shape[-1]
+    pad = (-seqlen) % CHUNK
+    Qf, Kf, Vf, gyf, af = Qr.float(), Kr.float(), V.float(), gy.float(), adt.float()
+    if pad:
+        Qf, Kf, Vf, gyf = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (Qf, Kf, Vf, gyf))
+        af = F.pad(af, (0, 0, 0, pad))
+    a_rev = _shift_reverse(af)
+    nv = n // 64
+    rep_v = lambda t: t.repeat_interleave(nv, dim=2)  # noqa: E731
+    y1, _ = scan(gyf.flip(1), Qf.flip(1), Kf.flip(1), a_rev, None, None, strict=True, per_head=True)
+    dV = y1.flip(1)[:, :seqlen] + skip.float()[..., None] * gy.float()
+    y2, _ = scan(_blocks(Kf, nv), Vf, gyf, rep_v(af), None, None, strict=True)
+    dQr = y2.reshape(bsz, seqlen + pad, h, n)
+    y3, _ = scan(_blocks(Qf, nv).flip(1), gyf.flip(1), Vf.flip(1), rep_v(a_rev), None, None, strict=True)
+    dKr = y3.flip(1).reshape(bsz, seqlen + pad, h, n)
+    dc = (Qf * dQr).sum(-1) - (Kf * dKr).sum(-1)
+    dadt = dc.flip(1).cumsum(1).flip(1)[:, :seqlen]
+    dskip = (gy.float() * V.float()).sum(-1)
+    return dQr[:, :seqlen], dKr[:, :seqlen], dadt, dskip, dV
+
+
 class _SISOFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
@@ -126,6 +282,27 @@ class _SISOFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
+        if BACKWARD_KERNELS and hasattr(ext(), "ssd_scan_generic"):
+            return _SISOFunction._backward_kernels(ctx, gy)
+        return _SISOFunction._backward_recompute(ctx, gy)
+
+    @staticmethod
+    def _backward_kernels(ctx, gy):
+        """Kernel scans for the recurrence, autograd for the elementwise preprocessing in front of it."""
+        from ..backbones.mamba3.siso import _prepare
+
+        Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D = ctx.saved_tensors
+        pre = [t.detach().requires_grad_(True) for t in (Q, K, ADT, DT, Trap, Q_bias, K_bias, Angles)]
+        with torch.enable_grad():
+            Qr, Kr, adt, qk_dot = _prepare(pre[0], pre[1], V, pre[2], pre[3], pre[4], pre[5], pre[6], pre[7], torch.float32)
+        skip = qk_dot.detach() + D.float()[None, None]
+        dQr, dKr, dadt, dskip, dV = siso_core_backward(Qr.detach(), Kr.detach(), adt.detach(), skip, V, gy)
+        grads = torch.autograd.grad([Qr, Kr, adt, qk_dot], pre, [dQr, dKr, dadt, dskip], allow_unused=True)
+        gQ, gK, gADT, gDT, gTrap, gQb, gKb, gAng = grads
+        return gQ, gK, dV.to(V.dtype), gADT, gDT, gTrap, gQb, gKb, gAng, dskip.sum((0, 1)).to(D.dtype)
+
+    @staticmethod
+    def _backward_recompute(ctx, gy):
         from ..backbones.mamba3.siso import mamba3_siso_chunked
 
         leaves = [t.detach().requires_grad_(True) for t in ctx.saved_tensors]

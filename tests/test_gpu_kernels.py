@@ -167,3 +167,33 @@ def test_matrix_norms_kernel_matches_linalg():
     assert torch.allclose(frob, want_frob, rtol=1e-4, atol=1e-6)
     assert torch.allclose(spec, want_spec, rtol=2e-2, atol=1e-6)
     assert (spec <= want_spec * (1 + 1e-4) + 1e-6).all()     # power iteration never overshoots
+
+
+@pytest.mark.parametrize("hidden,activation", [(0, "silu"), (192, "silu"), (256, "gelu")])
+def test_interface_jacobian_kernels_match_the_einsum_forms(hidden, activation):
+    """J^T and J of an interface head and of LayerNorm over a basis: kernels (no graph) against the PyTorch forms
+    (taken with a graph attached, which routes around the kernels) and against each other by <g, J t> = <J^T g, t>."""
+    from lbi_b200.interfaces import vector_mlp as vm
+
+    torch.manual_seed(hidden + 3)
+    bsz, p, din, dout = 3, 37, 160, 96
+    head = vm.VectorMLPHead(din, dout, hidden_dim=hidden, activation=activation).to(DEV)
+    norm = torch.nn.LayerNorm(dout).to(DEV)
+    with torch.no_grad():
+        norm.weight.uniform_(0.5, 1.5)
+    x = torch.randn(bsz, din, device=DEV)
+    s = torch.randn(bsz, dout, device=DEV)
+    g = torch.randn(bsz, p, dout, device=DEV)
+    t = torch.randn(bsz, p, din, device=DEV)
+    before = ops.dispatch.KERNEL_LAUNCHES["count"]
+    with torch.no_grad():
+        jt_g, j_t = vm.head_input_jacobian_t(head, x, g), vm.head_input_jacobian(head, x, t)
+        ln_t, ln_f = vm.layer_norm_input_jacobian_t(norm, s, g), vm.layer_norm_input_jacobian(norm, s, g)
+    assert ops.dispatch.KERNEL_LAUNCHES["count"] == before + 4, "the Jacobian kernels did not run"
+    gg, tt = g.clone().requires_grad_(True), t.clone().requires_grad_(True)      # graph attached -> PyTorch forms
+    _close(jt_g, vm.head_input_jacobian_t(head, x, gg).detach(), 1e-4, 1e-4, "head J^T")
+    _close(j_t, vm.head_input_jacobian(head, x, tt).detach(), 1e-4, 1e-4, "head J")
+    _close(ln_t, vm.layer_norm_input_jacobian_t(norm, s, gg).detach(), 1e-4, 1e-4, "layernorm J^T")
+    _close(ln_f, vm.layer_norm_input_jacobian(norm, s, gg).detach(), 1e-4, 1e-4, "layernorm J")
+    lhs, rhs = (g * j_t).sum(-1), (jt_g * t).sum(-1)
+    _close(lhs, rhs, 1e-3, 1e-3, "adjoint identity")

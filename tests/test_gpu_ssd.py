@@ -43,13 +43,56 @@ def test_ssd_initial_state_and_gradients():
     want, want_final = ssd_recurrent_reference(x, dt, A, B, C, D=D, initial_state=init)
     assert (y.double() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 1e-3
     assert (final.double() - want_final).abs().max().item() <= 2e-2 * want_final.abs().max().item() + 1e-3
-    # gradients flow through the recompute backward and agree with the pure PyTorch path
+    # gradients through the kernel backward agree with the pure PyTorch path
     xs, dts = x.float().requires_grad_(True), dt.clone().requires_grad_(True)
     ssd_chunk_scan_cuda(xs, dts, A, B.float(), C.float(), D=D).float().square().sum().backward()
     xr, dtr = x.float().requires_grad_(True), dt.clone().requires_grad_(True)
     ssd_chunk_scan(xr, dtr, A, B.float(), C.float(), chunk_size=128, D=D).float().square().sum().backward()
     assert torch.allclose(xs.grad, xr.grad, rtol=5e-2, atol=5e-2 * xr.grad.abs().max().item())
     assert torch.allclose(dts.grad, dtr.grad, rtol=5e-2, atol=5e-2 * dtr.grad.abs().max().item())
+
+
+@pytest.mark.parametrize("strict,per_head,n", [(False, False, 64), (True, False, 128), (True, True, 128), (False, True, 128)])
+def test_generic_scan_matches_its_oracle(strict, per_head, n):
+    from lbi_b200.ops.ssd import scan_generic, scan_generic_torch
+
+    b, l, h = 2, 384, 4
+    g = h if per_head else 2
+    gen = torch.Generator(device=DEV).manual_seed(11)
+    v = torch.randn(b, l, h, 64, device=DEV, generator=gen).bfloat16()
+    bk = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3).bfloat16()
+    cq = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3).bfloat16()
+    a = -(torch.rand(b, l, h, device=DEV, generator=gen) * 0.2)
+    w = torch.rand(b, l, h, device=DEV, generator=gen) + 0.5
+    init = torch.randn(b, h, n, 64, device=DEV, generator=gen) if per_head else torch.randn(b, h, 64, n, device=DEV, generator=gen)
+    y, fin = scan_generic(v, bk, cq, a, w, init, strict=strict, per_head=per_head)
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(v) == 0
+    assert y.dtype == torch.float32
+    want, want_fin = scan_generic_torch(v, bk, cq, a, w, init, strict=strict, per_head=per_head)
+    assert (y - want).norm().item() <= 1e-2 * want.norm().item()
+    assert (fin - want_fin).norm().item() <= 1e-2 * want_fin.norm().item()
+
+
+@pytest.mark.parametrize("b,l,h,g,n,with_state", [(2, 256, 4, 1, 128, True), (1, 200, 4, 2, 64, False), (1, 512, 8, 2, 128, False),
+                                                   (2, 128, 2, 1, 64, True)])
+def test_ssd_backward_kernels_match_autograd_of_the_recurrence(b, l, h, g, n, with_state):
+    """Every gradient of the role-permuted kernel backward against fp64 autograd through the token recurrence."""
+    x, dt, A, B, C, D = _inputs(b, l, h, g, n, seed=3 * l + n)
+    init = torch.randn(b, h, 64, n, device=DEV) * 0.2 if with_state else None
+    leaves = [t.detach().clone().requires_grad_(True) for t in (x, dt, A, B, C, D)] + ([init.clone().requires_grad_(True)] if with_state else [])
+    y, final = ssd_chunk_scan_cuda(*leaves[:5], D=leaves[5], initial_state=leaves[6] if with_state else None, return_final_state=True)
+    gy = torch.randn_like(y)
+    gfin = torch.randn_like(final) * (1.0 if with_state else 0.0)
+    got = torch.autograd.grad([y, final], leaves, [gy, gfin])
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(x) == 0
+    ref_leaves = [t.detach().double().requires_grad_(True) for t in leaves]
+    ry, rfin = ssd_recurrent_reference(*ref_leaves[:5], D=ref_leaves[5], initial_state=ref_leaves[6] if with_state else None)
+    want = torch.autograd.grad([ry, rfin], ref_leaves, [gy.double(), gfin.double()])
+    for name, a_, w_ in zip(("dx", "ddt", "dA", "dB", "dC", "dD", "dinit"), got, want):
+        err = (a_.double() - w_).norm().item() / max(w_.norm().item(), 1e-12)
+        assert err <= 2.5e-2, f"{name}: relative error {err:.3e}"
 
 
 @pytest.mark.parametrize("b,l,h,g", [(1, 128, 2, 1), (2, 320, 4, 2), (1, 1024, 4, 1)])
@@ -81,10 +124,40 @@ def test_siso_kernels_match_recurrence(b, l, h, g):
     assert (y.float() - torch_y.float()).abs().max().item() <= 3e-2 * scale + 1e-3
 
 
+@pytest.mark.parametrize("b,l,h,g", [(1, 256, 2, 1), (2, 200, 4, 2)])
+def test_siso_backward_kernels_match_autograd_of_the_recurrence(b, l, h, g):
+    from lbi_b200.backbones.mamba3.siso import mamba3_siso_recurrent_reference
+    from lbi_b200.ops.ssd import mamba3_siso_cuda
+
+    gen = torch.Generator(device=DEV).manual_seed(5 * l + h)
+    n, s = 128, 32
+    Q = torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3
+    K = torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3
+    V = torch.randn(b, l, h, 64, device=DEV, generator=gen)
+    DT = torch.rand(b, h, l, device=DEV, generator=gen) * 0.1 + 0.005
+    ADT = -DT * (torch.rand(b, h, l, device=DEV, generator=gen) * 4 + 0.5)
+    Trap = torch.randn(b, h, l, device=DEV, generator=gen)
+    Qb = torch.randn(h, n, device=DEV, generator=gen) * 0.2
+    Kb = torch.randn(h, n, device=DEV, generator=gen) * 0.2
+    Angles = torch.randn(b, l, h, s, device=DEV, generator=gen)
+    D = torch.randn(h, device=DEV, generator=gen)
+    leaves = [t.requires_grad_(True) for t in (Q, K, V, ADT, DT, Trap, Qb, Kb, Angles, D)]
+    y = mamba3_siso_cuda(*leaves)
+    gy = torch.randn_like(y)
+    got = torch.autograd.grad(y, leaves, gy)
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(V) == 0
+    ref = [t.detach().double().requires_grad_(True) for t in leaves]
+    want = torch.autograd.grad(mamba3_siso_recurrent_reference(*ref[:9], D=ref[9]), ref, gy.double())
+    for name, a_, w_ in zip("Q K V ADT DT Trap Q_bias K_bias Angles D".split(), got, want):
+        err = (a_.double() - w_).norm().item() / max(w_.norm().item(), 1e-12)
+        assert err <= 3e-2, f"{name}: relative error {err:.3e}"
+
+
 @pytest.mark.parametrize("backbone,d_state", [("mamba2", 64), ("mamba3", 128)])
 def test_mamba_lbi_model_trains_through_the_kernels(backbone, d_state, monkeypatch):
     """An LBI model with a Mamba backbone on the GPU under bf16 autocast: the kernel path and the PyTorch path give the
-    same loss and the same scan-engine gradients (the backward of the kernels recomputes the PyTorch form)."""
+    same loss and the same scan-engine gradients (the backward of the kernels is the role-permuted scans)."""
     import torch.nn.functional as F
 
     from lbi_b200.backbones import BackboneSpec
