@@ -41,6 +41,50 @@ def rms_norm_reference(
     return out.to(out_dtype)
 
 
+class _GatedRMSNormFunction(torch.autograd.Function):
+    """Forward and backward on the gated / grouped RMSNorm kernels (csrc/gated_norm.cu)."""
+
+    @staticmethod
+    def forward(ctx, x, z, weight, eps, group_size, gate_first):
+        from lbi_b200.ops import dispatch, ext
+
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).contiguous()
+        z2 = None if z is None else z.to(x.dtype).reshape(-1, shape[-1]).contiguous()
+        w = weight.float().contiguous()
+        y, rstd = ext().gated_rmsnorm_fwd(x2, z2, w, float(eps), int(group_size), bool(gate_first))
+        dispatch.KERNEL_LAUNCHES["count"] += 1
+        ctx.save_for_backward(x2, z2 if z2 is not None else x2.new_empty(0), w, rstd)
+        ctx.meta = (shape, z is not None, int(group_size), bool(gate_first), weight.dtype, None if z is None else z.dtype)
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx, gy):
+        from lbi_b200.ops import dispatch, ext
+
+        x2, z2, w, rstd = ctx.saved_tensors
+        shape, has_z, group_size, gate_first, w_dtype, z_dtype = ctx.meta
+        dy = gy.to(x2.dtype).reshape(-1, shape[-1]).contiguous()
+        dx, dz, dw = ext().gated_rmsnorm_bwd(dy, x2, z2 if has_z else None, w, rstd, group_size, gate_first)
+        dispatch.KERNEL_LAUNCHES["count"] += 1
+        return dx.view(shape), (dz.view(shape).to(z_dtype) if has_z else None), dw.to(w_dtype), None, None, None
+
+
+def gated_rms_norm(x, weight, *, eps, z=None, norm_before_gate=True, group_size=None):
+    """Kernel path for bf16 / fp32 CUDA tensors (``LBI_B200_TORCH_NORMS=1`` keeps the PyTorch form), else the oracle."""
+    import os
+
+    in_transform = torch._C._functorch.maybe_current_level() is not None     # jvp / vmap: the PyTorch form has the rules
+    if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float32) and not in_transform
+            and os.environ.get("LBI_B200_TORCH_NORMS", "0") != "1"):
+        from lbi_b200.ops import ext, native_available
+
+        gs = x.shape[-1] if group_size is None else int(group_size)
+        if native_available() and hasattr(ext(), "gated_rmsnorm_fwd") and gs <= 6144 and x.shape[-1] % gs == 0:
+            return _GatedRMSNormFunction.apply(x, z, weight, eps, gs, not norm_before_gate)
+    return rms_norm_reference(x, weight, eps=eps, z=z, norm_before_gate=norm_before_gate, group_size=group_size)
+
+
 class RMSNorm(nn.Module):
     """``y = x / rms(x) * weight`` computed in fp32 and cast back to the input dtype."""
 
@@ -85,7 +129,7 @@ class RMSNormGated(nn.Module):
         self.group_size = group_size
 
     def forward(self, x: torch.Tensor, z: torch.Tensor | None = None) -> torch.Tensor:
-        return rms_norm_reference(
+        return gated_rms_norm(
             x,
             self.weight,
             eps=self.eps,

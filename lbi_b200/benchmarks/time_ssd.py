@@ -1,4 +1,4 @@
-"""Mamba-2 SSD chunk-scan forward: this package's sm_100a kernels against the chunked PyTorch form and, when the
+"""Mamba-2 SSD chunk scan (forward, or forward + backward with --backward): this package's sm_100a kernels against the chunked PyTorch form and, when the
 reference tree is present under baseline/_ref, its Triton pipeline (``mamba_chunk_scan_combined``).
 
     python -m lbi_b200.benchmarks.time_ssd [--batch 4 --seq-len 8192 --heads 24 --d-state 64 128]
@@ -62,6 +62,8 @@ def main() -> None:
     ap.add_argument("--d-state", type=int, nargs="+", default=[64, 128])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skip-torch", action="store_true")
+    ap.add_argument("--kernel-table", action="store_true", help="with --backward: print the device-time table of one forward + backward")
+    ap.add_argument("--backward", action="store_true", help="time forward + backward (all input gradients) instead of the forward")
     args = ap.parse_args()
     dev = "cuda"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -82,6 +84,40 @@ def main() -> None:
         D = torch.randn(h, device=dev)
         nbytes = 2 * x.numel() * 2 + 2 * B.numel() * 2 + dt.numel() * 4
         rows = {}
+        if args.backward:
+            from lbi_b200.ops import ssd as ops_ssd
+
+            leaves = [t.clone().requires_grad_(True) for t in (x, dt, A, B, C, D)]
+            gy = torch.randn_like(x)
+
+            def fwd_bwd(fn):
+                def run():
+                    y = fn(*leaves[:5], D=leaves[5])
+                    torch.autograd.grad(y, leaves, gy)
+                return run
+
+            rows["tcgen05_fwd_bwd"] = time_ms(fwd_bwd(ssd_chunk_scan_cuda), args.iters, flush)
+            if args.kernel_table:
+                from torch.profiler import ProfilerActivity, profile
+
+                with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                    fwd_bwd(ssd_chunk_scan_cuda)()
+                    torch.cuda.synchronize()
+                print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25, max_name_column_width=70), file=sys.stderr)
+            ops_ssd.BACKWARD_KERNELS = False
+            if not args.skip_torch:
+                rows["tcgen05_fwd_torch_recompute_bwd"] = time_ms(fwd_bwd(ssd_chunk_scan_cuda), max(2, args.iters // 3), flush)
+            ops_ssd.BACKWARD_KERNELS = True
+            if triton_fn is not None:
+                try:
+                    rows["reference_triton_fwd_bwd"] = time_ms(fwd_bwd(lambda *a, D=None: triton_fn(*a, 128, D=D)), args.iters, flush)
+                except Exception as exc:  # noqa: BLE001
+                    print(f"[time_ssd] reference Triton backward failed: {exc!r}", file=sys.stderr)
+            for name, ms in rows.items():
+                print(json.dumps({"d_state": n, "batch": b, "seq_len": l, "heads": h, "kernel": name, "median_ms": ms}))
+            if "reference_triton_fwd_bwd" in rows:
+                print(json.dumps({"d_state": n, "fwd_bwd_speedup_over_reference_triton": rows["reference_triton_fwd_bwd"] / rows["tcgen05_fwd_bwd"]}))
+            continue
         with torch.no_grad():
             rows["tcgen05"] = time_ms(lambda: ssd_chunk_scan_cuda(x, dt, A, B, C, D=D), args.iters, flush)
             if triton_fn is not None:

@@ -62,6 +62,17 @@ int lbi_affine_suffix_scan(const float* mats, const float* offsets, const float*
                            int r, cudaStream_t stream);
 
 
+// ---- gated / grouped RMSNorm (gated_norm.cu) --------------------------------------------------------------
+// y = rmsnorm_group(x * silu(z)) * w (gate_first) or rmsnorm_group(x) * w * silu(z); z may be null.  x, z, y are bf16
+// (is_bf16) or fp32 [rows, dim]; weight fp32 [dim]; rstd [rows, dim / group_size] fp32.
+int lbi_gated_rmsnorm_fwd(const void* x, const void* z_or_null, const float* weight, void* y, float* rstd, int64_t rows, int dim,
+                          int group_size, float eps, int gate_first, int is_bf16, cudaStream_t stream);
+// dw_partials holds lbi_gated_rmsnorm_slots(rows, dim, group_size) rows of dim floats; the caller sums them.
+int lbi_gated_rmsnorm_slots(int64_t rows, int dim, int group_size);
+int lbi_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z_or_null, const float* weight, const float* rstd, void* dx,
+                          void* dz_or_null, float* dw_partials, int64_t rows, int dim, int group_size, int gate_first,
+                          int is_bf16, cudaStream_t stream);
+
 // ---- interface Jacobian products over a basis (interface_jac.cu) -----------------------------------------
 // out[b, p, :] = (((in_scale * g[b, p, :]) @ wa) o d[b, :]) @ wb;  g [B, P, din], wa [din, hidden], d [B, hidden] or null,
 // wb [hidden, dout] or null (then out [B, P, hidden] = (g @ wa) o d).  All fp32 row-major.

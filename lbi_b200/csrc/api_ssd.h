@@ -42,6 +42,14 @@ int lbi_ssd_scan_generic(const void* v, const void* bk, const void* cq, const fl
                          void* prev, float* final_state, void* y, float* y32, int batch, int seq_len, int heads, int groups,
                          int d_state, int per_head, int* status, cudaStream_t stream);
 
+// Gradient of the log-decays of that scan: da_u = sum over pairs s < u <= t of e^{c_t - c_s} (cq_t . bk_s) w_s (gy_t . v_s),
+// pairs that reach before the first or past the last token included through `state_in` (the bf16 incoming states of the
+// forward scan, [B, L/128, H, 64, N]; per_head: [.., N, 64]) and `state_cot_rev` (the incoming states of the
+// time-reversed scan that pulled gy back, same layout, chunk axis reversed).  gy like v; da [B, H, L] fp32.
+int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk, const void* cq, const float* weight, const float* cum,
+                       const void* state_in, const void* state_cot_rev, float* da, int batch, int seq_len, int heads,
+                       int groups, int d_state, int per_head, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -278,6 +278,47 @@ std::tuple<Tensor, Tensor> matrix_norms(const Tensor& mats, int64_t iters) {
   return {spec, frob};
 }
 
+// Gated / grouped RMSNorm.  x, z [rows, dim] bf16 or fp32 (same dtype), weight fp32 [dim] -> (y, rstd [rows, dim / group]).
+std::tuple<Tensor, Tensor> gated_rmsnorm_fwd(const Tensor& x, const c10::optional<Tensor>& z, const Tensor& weight, double eps,
+                                             int64_t group_size, bool gate_first) {
+  CHECK_F32(weight);
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && x.dim() == 2 && (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat),
+              "gated_rmsnorm: x must be a contiguous CUDA [rows, dim] bf16 / fp32 tensor");
+  TORCH_CHECK(!z || (z->is_contiguous() && z->sizes() == x.sizes() && z->scalar_type() == x.scalar_type()), "gated_rmsnorm: z must match x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0), dim = x.size(1);
+  TORCH_CHECK(weight.numel() == dim && group_size > 0 && dim % group_size == 0, "gated_rmsnorm: bad weight / group size");
+  Tensor y = torch::empty_like(x);
+  Tensor rstd = torch::empty({rows, dim / group_size}, x.options().dtype(at::kFloat));
+  check(lbi_gated_rmsnorm_fwd(x.data_ptr(), z ? z->data_ptr() : nullptr, weight.data_ptr<float>(), y.data_ptr(), rstd.data_ptr<float>(),
+                              rows, (int)dim, (int)group_size, (float)eps, gate_first ? 1 : 0, x.scalar_type() == at::kBFloat16 ? 1 : 0,
+                              cur_stream()),
+        "gated_rmsnorm_fwd");
+  return {y, rstd};
+}
+
+// -> (dx, dz (empty when z is none), dw [dim] fp32)
+std::tuple<Tensor, Tensor, Tensor> gated_rmsnorm_bwd(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>& z, const Tensor& weight,
+                                                     const Tensor& rstd, int64_t group_size, bool gate_first) {
+  CHECK_F32(weight);
+  CHECK_F32(rstd);
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dy.is_contiguous() && dy.sizes() == x.sizes() && dy.scalar_type() == x.scalar_type(),
+              "gated_rmsnorm_bwd: dy must match x");
+  TORCH_CHECK(!z || (z->is_contiguous() && z->sizes() == x.sizes() && z->scalar_type() == x.scalar_type()), "gated_rmsnorm_bwd: z must match x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0), dim = x.size(1);
+  const int slots = lbi_gated_rmsnorm_slots(rows, (int)dim, (int)group_size);
+  TORCH_CHECK(slots > 0, "gated_rmsnorm_bwd: bad shape");
+  Tensor dx = torch::empty_like(x);
+  Tensor dz = z ? torch::empty_like(x) : torch::empty({0}, x.options());
+  Tensor partials = torch::empty({slots, dim}, x.options().dtype(at::kFloat));
+  check(lbi_gated_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), z ? z->data_ptr() : nullptr, weight.data_ptr<float>(), rstd.data_ptr<float>(),
+                              dx.data_ptr(), z ? dz.data_ptr() : nullptr, partials.data_ptr<float>(), rows, (int)dim, (int)group_size,
+                              gate_first ? 1 : 0, x.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+        "gated_rmsnorm_bwd");
+  return {dx, dz, partials.sum(0)};
+}
+
 // (((in_scale g) @ wa) o d) @ wb over a basis: g [B, P, din] fp32, wa [din, hidden], d [B, hidden] or none, wb [hidden, dout] or none.
 Tensor interface_mlp_jac(const Tensor& g, const Tensor& wa, const c10::optional<Tensor>& d, const c10::optional<Tensor>& wb,
                          double in_scale) {
@@ -425,7 +466,7 @@ std::tuple<Tensor, Tensor> attn_fwd_packed(const Tensor& qkv, int64_t batch, int
 
 // Mamba-2 SSD chunk scan forward.  x [B, L, H, 64] bf16, dt_raw [B, L, H] fp32, a [H] fp32, bm / cm [B, L, G, N] bf16.
 // Returns (y [B, L, H, 64] bf16, final_state [B, H, 64, N] fp32).
-std::tuple<Tensor, Tensor> ssd_chunk_scan_fwd(const Tensor& x, const Tensor& dt_raw, const Tensor& a, const Tensor& bm, const Tensor& cm,
+std::tuple<Tensor, Tensor, Tensor> ssd_chunk_scan_fwd(const Tensor& x, const Tensor& dt_raw, const Tensor& a, const Tensor& bm, const Tensor& cm,
                                               const c10::optional<Tensor>& d_skip, const c10::optional<Tensor>& dt_bias,
                                               const c10::optional<Tensor>& init_state, bool softplus, double dt_min, double dt_max) {
   CHECK_BF16(x);
@@ -454,12 +495,12 @@ std::tuple<Tensor, Tensor> ssd_chunk_scan_fwd(const Tensor& x, const Tensor& dt_
                                states.data_ptr<float>(), prev.data_ptr(), final_state.data_ptr<float>(), y.data_ptr(), (int)batch,
                                (int)seq, (int)heads, (int)groups, (int)hd, (int)n, st.data_ptr<int>(), cur_stream()),
         "ssd_chunk_scan_fwd");
-  return {y, final_state};
+  return {y, final_state, prev};
 }
 
 // Mamba-3 SISO chunk scan forward on preprocessed operands.  v [B, L, H, 64] bf16, kr / qr [B, L, H, 128] bf16,
 // adt [B, L, H] fp32, skip_tok [B, H, L] fp32, d_skip [H] fp32.  Returns (y [B, L, H, 64] bf16, final_state [B, H, 128, 64]).
-std::tuple<Tensor, Tensor> siso_chunk_scan_fwd(const Tensor& v, const Tensor& kr, const Tensor& qr, const Tensor& adt,
+std::tuple<Tensor, Tensor, Tensor> siso_chunk_scan_fwd(const Tensor& v, const Tensor& kr, const Tensor& qr, const Tensor& adt,
                                                const c10::optional<Tensor>& d_skip, const c10::optional<Tensor>& skip_tok,
                                                const c10::optional<Tensor>& init_state) {
   CHECK_BF16(v);
@@ -488,13 +529,13 @@ std::tuple<Tensor, Tensor> siso_chunk_scan_fwd(const Tensor& v, const Tensor& kr
                                 final_state.data_ptr<float>(), y.data_ptr(), (int)batch, (int)seq, (int)heads, (int)hd, (int)n,
                                 st.data_ptr<int>(), cur_stream()),
         "siso_chunk_scan_fwd");
-  return {y, final_state};
+  return {y, final_state, prev};
 }
 
 // The chunk scan with free operand roles.  v [B, L, H, 64] bf16; bk / cq [B, L, G, N] bf16 (per_head: G = H, N = 128);
 // a [B, L, H] fp32 log-decay per token; weight [B, L, H] fp32 or none; skip_tok [B, H, L]; init [B, H, 64, N] (per_head:
 // [B, H, N, 64]).  Returns (y [B, L, H, 64] in bf16 or fp32, final_state).
-std::tuple<Tensor, Tensor> ssd_scan_generic(const Tensor& v, const Tensor& bk, const Tensor& cq, const Tensor& a,
+std::tuple<Tensor, Tensor, Tensor> ssd_scan_generic(const Tensor& v, const Tensor& bk, const Tensor& cq, const Tensor& a,
                                             const c10::optional<Tensor>& weight, const c10::optional<Tensor>& d_skip,
                                             const c10::optional<Tensor>& skip_tok, const c10::optional<Tensor>& init_state,
                                             bool strict, bool per_head, bool out_f32) {
@@ -533,7 +574,46 @@ std::tuple<Tensor, Tensor> ssd_scan_generic(const Tensor& v, const Tensor& bk, c
                              out_f32 ? y.data_ptr<float>() : nullptr, (int)batch, (int)seq, (int)heads, (int)groups, (int)n,
                              per_head ? 1 : 0, st.data_ptr<int>(), cur_stream()),
         "ssd_scan_generic");
-  return {y, final_state};
+  return {y, final_state, prev};
+}
+
+// Log-decay gradient of the scan (see lbi_ssd_decay_grad).  v, gy [B, L, H, 64] bf16; bk / cq [B, L, G, N] bf16; a, weight
+// [B, L, H] fp32; state_in / state_cot_rev: the third result of the forward and of the reversed scan.  Returns da [B, L, H].
+Tensor ssd_decay_grad(const Tensor& v, const Tensor& gy, const Tensor& bk, const Tensor& cq, const Tensor& a,
+                      const c10::optional<Tensor>& weight, const Tensor& state_in, const Tensor& state_cot_rev, bool per_head) {
+  CHECK_BF16(v);
+  CHECK_BF16(gy);
+  CHECK_BF16(bk);
+  CHECK_BF16(cq);
+  CHECK_BF16(state_in);
+  CHECK_BF16(state_cot_rev);
+  CHECK_F32(a);
+  c10::cuda::CUDAGuard guard(v.device());
+  TORCH_CHECK(v.dim() == 4 && gy.sizes() == v.sizes() && bk.dim() == 4 && cq.sizes() == bk.sizes() && a.dim() == 3, "decay_grad: bad shapes");
+  const int64_t batch = v.size(0), seq = v.size(1), heads = v.size(2), hd = v.size(3), groups = bk.size(2), n = bk.size(3);
+  TORCH_CHECK(hd == 64 && a.size(0) == batch && a.size(1) == seq && a.size(2) == heads && bk.size(1) == seq, "decay_grad: shape mismatch");
+  TORCH_CHECK(!per_head || groups == heads, "decay_grad: per_head wants one bk / cq per head");
+  TORCH_CHECK(state_in.numel() == batch * (seq / 128) * heads * hd * n && state_cot_rev.numel() == state_in.numel(),
+              "decay_grad: states must be [B, L/128, H, 64, N]");
+  auto f32 = v.options().dtype(at::kFloat);
+  Tensor ones = torch::ones({heads}, f32);
+  Tensor a_t = torch::empty({batch, heads, seq}, f32), cum = torch::empty({batch, heads, seq}, f32);
+  Tensor w_t;
+  if (weight) {
+    CHECK_F32((*weight));
+    TORCH_CHECK(weight->sizes() == a.sizes(), "decay_grad: weight must match a");
+    w_t = weight->transpose(1, 2).contiguous();
+  }
+  Tensor da = torch::empty({batch, heads, seq}, f32);
+  Tensor st = status_word(v);
+  check(lbi_ssd_cumsum(a.data_ptr<float>(), nullptr, ones.data_ptr<float>(), a_t.data_ptr<float>(), cum.data_ptr<float>(), (int)batch,
+                       (int)seq, (int)heads, 0, 0.f, 0.f, cur_stream()),
+        "decay_grad_cumsum");
+  check(lbi_ssd_decay_grad(v.data_ptr(), gy.data_ptr(), bk.data_ptr(), cq.data_ptr(), weight ? w_t.data_ptr<float>() : nullptr,
+                           cum.data_ptr<float>(), state_in.data_ptr(), state_cot_rev.data_ptr(), da.data_ptr<float>(), (int)batch,
+                           (int)seq, (int)heads, (int)groups, (int)n, per_head ? 1 : 0, st.data_ptr<int>(), cur_stream()),
+        "ssd_decay_grad");
+  return da.transpose(1, 2);
 }
 
 // ---- peer-memory kernels.  `*_ptrs` are int64 CUDA tensors holding one device pointer per rank.
@@ -694,6 +774,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("affine_suffix_scan", &affine_suffix_scan);
   m.def("matrix_norms", &matrix_norms);
   m.def("interface_mlp_jac", &interface_mlp_jac);
+  m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);
+  m.def("gated_rmsnorm_bwd", &gated_rmsnorm_bwd);
   m.def("layernorm_jac", &layernorm_jac);
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("a_t") = false, py::arg("b_t") = false,
         py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);
@@ -705,6 +787,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ssd_chunk_scan_fwd", &ssd_chunk_scan_fwd);
   m.def("siso_chunk_scan_fwd", &siso_chunk_scan_fwd);
   m.def("ssd_scan_generic", &ssd_scan_generic);
+  m.def("ssd_decay_grad", &ssd_decay_grad);
   m.def("kernel_status", &kernel_status);
   m.def("set_peer_wait_limit_ms", &set_peer_wait_limit_ms);
   m.def("peer_barrier", &peer_barrier);

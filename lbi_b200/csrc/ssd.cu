@@ -422,6 +422,218 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------ 5. decay gradient
+// da_u = d loss / d a_u for the log-decay a_u of token u, given the output cotangent gy: the sum of
+//   E_ts = e^{c_t - c_s} (cq_t . bk_s) w_s (gy_t . v_s)      over all pairs s < u <= t.
+// Taken as differences of row sums (cq . dcq - bk . dbk) the pairs on one side of u cancel only in exact arithmetic;
+// here every pair is counted once.  Per (batch, chunk, head), with H_in the state entering the chunk and dH_out the
+// cotangent of the state leaving it (the incoming state of the time-reversed pass at the mirrored chunk):
+//   pairs inside the chunk     G1 = cq bk^T, G2 = gy v^T in TMEM; row prefixes of G1 o G2 o decay o w, summed over t >= u
+//   s before, t inside         sum_{t >= u} e^{c_t} gy_t . (cq_t H_in^T)
+//   s inside, t after          sum_{s < u}  w_s e^{c_end - c_s} v_s . (bk_s dH_out^T)
+//   s before, t after          e^{c_end} <H_in, dH_out>
+// Replaces the reference's _chunk_scan_bwd_ddAcs_stable_kernel and the ddA parts of its dc / db / dstates kernels
+// (backbones/mamba2/ops/triton/ssd_chunk_scan.py:1098, ssd_chunk_state.py:398, ssd_state_passing.py:102).
+template <int N>
+struct SmemDda {
+  alignas(1024) uint8_t ct[N / 64][PANEL];
+  alignas(1024) uint8_t bt[N / 64][PANEL];
+  alignas(1024) uint8_t gyt[PANEL];
+  alignas(1024) uint8_t xt[PANEL];
+  alignas(1024) uint8_t hin[N / 64][P * 128];
+  alignas(1024) uint8_t dho[N / 64][P * 128];
+  float cum2[L];
+  float wv[L];
+  float r2[L];
+  float r3[L];
+  float da_in[L];
+  float red[4];
+  uint64_t bar_full, bar_mma;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct DdaParams {
+  int seq_len, heads, groups, chunks;
+  const float* weight;   // [B, H, L] or null
+  const float* cum;      // [B, H, L]
+  float* da;             // [B, H, L]
+  int* status;
+};
+
+__device__ __forceinline__ float dot_row64(uint32_t row_addr, int l, const uint32_t* r0, const uint32_t* r1) {
+  float acc = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    const uint4 v = lds128(row_addr + ((ch ^ (l & 7)) << 4));
+    const uint32_t* rr = ch < 4 ? r0 + ch * 8 : r1 + (ch - 4) * 8;
+    const float2 a = unpack2(v.x), b = unpack2(v.y), c = unpack2(v.z), d = unpack2(v.w);
+    acc = fmaf(a.x, __uint_as_float(rr[0]), acc);
+    acc = fmaf(a.y, __uint_as_float(rr[1]), acc);
+    acc = fmaf(b.x, __uint_as_float(rr[2]), acc);
+    acc = fmaf(b.y, __uint_as_float(rr[3]), acc);
+    acc = fmaf(c.x, __uint_as_float(rr[4]), acc);
+    acc = fmaf(c.y, __uint_as_float(rr[5]), acc);
+    acc = fmaf(d.x, __uint_as_float(rr[6]), acc);
+    acc = fmaf(d.y, __uint_as_float(rr[7]), acc);
+  }
+  return acc;
+}
+
+template <int N, bool PH>
+__global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                      const __grid_constant__ CUtensorMap map_gy,
+                                                      const __grid_constant__ CUtensorMap map_b,
+                                                      const __grid_constant__ CUtensorMap map_c,
+                                                      const __grid_constant__ CUtensorMap map_hin,
+                                                      const __grid_constant__ CUtensorMap map_dho, const DdaParams p) {
+  extern __shared__ uint8_t raw_smem[];
+  SmemDda<N>& s = *reinterpret_cast<SmemDda<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int g = PH ? h : h / (p.heads / p.groups);
+  const int row0 = b * p.seq_len + c * L;
+  constexpr int KS = N / 16;
+  constexpr uint32_t PANEL16 = PANEL >> 4, PV16 = (P * 128) >> 4;
+  constexpr uint32_t TMEM_COLS = 512;   // G1 [0, 128), G2 [128, 256), cq H_in^T [256, 320), bk dH_out^T [320, 384)
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.bar_full, 1);
+    mbar_init(&s.bar_mma, 1);
+    fence_barrier_init();
+    prefetch_tmap(&map_x);
+    prefetch_tmap(&map_gy);
+    prefetch_tmap(&map_b);
+    prefetch_tmap(&map_c);
+    prefetch_tmap(&map_hin);
+    prefetch_tmap(&map_dho);
+  }
+  if (warp == 4) tmem_alloc(&s.tmem_base, TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abortp = &s.abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&s.bar_full, (2 * (N / 64) + 2) * PANEL + 2 * (N / 64) * P * 128);
+      const int st_in = (int)((((int64_t)b * p.chunks + c) * p.heads + h) * (PH ? N : P));
+      const int st_out = (int)((((int64_t)b * p.chunks + (p.chunks - 1 - c)) * p.heads + h) * (PH ? N : P));
+      for (int q = 0; q < N / 64; ++q) {
+        tma_load_2d(s.ct[q], &map_c, &s.bar_full, g * N + q * 64, row0);
+        tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, row0);
+        if (!PH) {
+          tma_load_2d(s.hin[q], &map_hin, &s.bar_full, q * 64, st_in);
+          tma_load_2d(s.dho[q], &map_dho, &s.bar_full, q * 64, st_out);
+        }
+      }
+      if (PH) {
+        tma_load_2d(s.hin[0], &map_hin, &s.bar_full, 0, st_in);
+        tma_load_2d(s.dho[0], &map_dho, &s.bar_full, 0, st_out);
+      }
+      tma_load_2d(s.gyt, &map_gy, &s.bar_full, h * P, row0);
+      tma_load_2d(s.xt, &map_x, &s.bar_full, h * P, row0);
+      const uint64_t kmajor0 = make_smem_desc(0, 16, 1024), mnmajor0 = make_smem_desc(0, PANEL, 1024);
+      const uint32_t ct16 = smem_u32(s.ct[0]) >> 4, bt16 = smem_u32(s.bt[0]) >> 4, gy16 = smem_u32(s.gyt) >> 4,
+                     xt16 = smem_u32(s.xt) >> 4, hin16 = smem_u32(s.hin[0]) >> 4, dho16 = smem_u32(s.dho[0]) >> 4;
+      const bool ok = mbar_wait(&s.bar_full, 0, abortp, p.status, 61);
+      if (ok) {
+        fence_after_sync();
+        const uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, kmajor0 + bt16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   idesc_g, kk);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_bf16(tmem + 128, kmajor0 + gy16 + kk * 2, kmajor0 + xt16 + kk * 2, idesc_g, kk);
+        const uint32_t idesc_s = make_idesc_bf16(128, 64, 0, PH ? 1 : 0);
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem + 256, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   PH ? mnmajor0 + hin16 + 128 * kk : kmajor0 + hin16 + (kk >> 2) * PV16 + (kk & 3) * 2, idesc_s, kk);
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem + 320, kmajor0 + bt16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   PH ? mnmajor0 + dho16 + 128 * kk : kmajor0 + dho16 + (kk >> 2) * PV16 + (kk & 3) * 2, idesc_s, kk);
+        mma_commit(&s.bar_mma);
+      }
+    }
+  } else {
+    const int l = warp * 32 + lane;
+    const int64_t base = ((int64_t)b * p.heads + h) * p.seq_len + c * L;
+    const float my_cum2 = p.cum[base + l] * LOG2E;
+    s.cum2[l] = my_cum2;
+    s.wv[l] = p.weight ? p.weight[base + l] : 1.f;
+    s.da_in[l] = 0.f;
+    named_barrier_sync(1, 128);
+    bool ok = mbar_wait(&s.bar_mma, 0, abortp, p.status, 62);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      fence_after_sync();
+      const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+      // pairs inside the chunk: running row prefix, column u = s + 1 collects it from every row t >= u
+      float prefix = 0.f;
+      for (int q = 0; q <= warp; ++q) {
+        uint32_t g1[32], g2[32];
+        tmem_ld_32x32(trow + q * 32, g1);
+        tmem_ld_32x32(trow + 128 + q * 32, g2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int sidx = q * 32 + j;
+          const bool live = sidx < l;
+          const float e = live ? __uint_as_float(g1[j]) * __uint_as_float(g2[j]) * ex2(my_cum2 - s.cum2[sidx]) * s.wv[sidx] : 0.f;
+          prefix += e;
+          const float col = warp_sum(live ? prefix : 0.f);
+          if (lane == 0 && sidx < L - 1) atomicAdd(&s.da_in[sidx + 1], col);
+        }
+      }
+      // state terms
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(trow + 256, r0);
+      tmem_ld_32x32(trow + 288, r1);
+      tmem_ld_wait();
+      s.r2[l] = ex2(my_cum2) * dot_row64(smem_u32(s.gyt) + l * 128, l, r0, r1);
+      tmem_ld_32x32(trow + 320, r0);
+      tmem_ld_32x32(trow + 352, r1);
+      tmem_ld_wait();
+      const float cum_end2 = s.cum2[L - 1];
+      s.r3[l] = s.wv[l] * ex2(cum_end2 - my_cum2) * dot_row64(smem_u32(s.xt) + l * 128, l, r0, r1);
+      // <H_in, dH_out>: both tiles have the same layout, so the product runs over raw 16-byte pieces
+      float hd = 0.f;
+      const uint32_t hin_a = smem_u32(s.hin[0]), dho_a = smem_u32(s.dho[0]);
+      for (int off = l * 16; off < (N / 64) * P * 128; off += 128 * 16) {
+        const uint4 a = lds128(hin_a + off), d = lds128(dho_a + off);
+        const float2 a0 = unpack2(a.x), a1 = unpack2(a.y), a2 = unpack2(a.z), a3 = unpack2(a.w);
+        const float2 d0 = unpack2(d.x), d1 = unpack2(d.y), d2 = unpack2(d.z), d3 = unpack2(d.w);
+        hd += a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y + a2.x * d2.x + a2.y * d2.y + a3.x * d3.x + a3.y * d3.y;
+      }
+      hd = warp_sum(hd);
+      if (lane == 0) s.red[warp] = hd;
+      named_barrier_sync(1, 128);
+      float tail2 = 0.f, head3 = 0.f;
+      for (int t = l; t < L; ++t) tail2 += s.r2[t];
+      for (int t = 0; t < l; ++t) head3 += s.r3[t];
+      const float through = ex2(cum_end2) * (s.red[0] + s.red[1] + s.red[2] + s.red[3]);
+      p.da[base + l] = s.da_in[l] + tail2 + head3 + through;
+    }
+  }
+  __syncwarp();
+  if (s.abort_flag) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    fence_after_sync();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -503,6 +715,33 @@ static int run(const void* x, const void* bm, const void* cm, const float* dt, c
   return rc;
 }
 
+template <int N, bool PH>
+static int run_dda(const void* x, const void* gy, const void* bm, const void* cm, const float* weight, const float* cum,
+                   const void* hin, const void* dho, float* da, int batch, int seq_len, int heads, int groups, int* status,
+                   cudaStream_t st) {
+  const int chunks = seq_len / L;
+  const int64_t rows = (int64_t)batch * seq_len;
+  CUtensorMap mx, mg, mb, mc, mh, md;
+  int rc = make_map(&mx, x, rows, (int64_t)heads * P, L);
+  if (rc) return rc;
+  rc = make_map(&mg, gy, rows, (int64_t)heads * P, L);
+  if (rc) return rc;
+  rc = make_map(&mb, bm, rows, (int64_t)(PH ? heads : groups) * N, L);
+  if (rc) return rc;
+  rc = make_map(&mc, cm, rows, (int64_t)(PH ? heads : groups) * N, L);
+  if (rc) return rc;
+  rc = PH ? make_map(&mh, hin, (int64_t)batch * chunks * heads * N, P, N) : make_map(&mh, hin, (int64_t)batch * chunks * heads * P, N, P);
+  if (rc) return rc;
+  rc = PH ? make_map(&md, dho, (int64_t)batch * chunks * heads * N, P, N) : make_map(&md, dho, (int64_t)batch * chunks * heads * P, N, P);
+  if (rc) return rc;
+  DdaParams p{seq_len, heads, groups, chunks, weight, cum, da, status};
+  const size_t smem = sizeof(SmemDda<N>) + 1024;
+  rc = set_smem(dda_kernel<N, PH>, smem);
+  if (rc) return rc;
+  dda_kernel<N, PH><<<dim3(chunks, heads, batch), THREADS, smem, st>>>(mx, mg, mb, mc, mh, md, p);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace ssd
 }  // namespace lbi
 
@@ -561,5 +800,22 @@ extern "C" int lbi_ssd_scan_generic(const void* v, const void* bk, const void* c
   if (d_state == 128)
     return run<128, false>(v, bk, cq, weight, cum, d_skip, skip_tok, strict, init_state, states, prev, final_state, y, y32, batch,
                            seq_len, heads, groups, status, st);
+  return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk, const void* cq, const float* weight,
+                                  const float* cum, const void* state_in, const void* state_cot_rev, float* da, int batch,
+                                  int seq_len, int heads, int groups, int d_state, int per_head, int* status, cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (seq_len % L != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * seq_len >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+  if (per_head) {
+    if (d_state != 128) return (int)cudaErrorInvalidValue;
+    return run_dda<128, true>(v, gy, bk, cq, weight, cum, state_in, state_cot_rev, da, batch, seq_len, heads, heads, status, st);
+  }
+  if (groups <= 0 || heads % groups != 0) return (int)cudaErrorInvalidValue;
+  if (d_state == 64)
+    return run_dda<64, false>(v, gy, bk, cq, weight, cum, state_in, state_cot_rev, da, batch, seq_len, heads, groups, status, st);
+  if (d_state == 128)
+    return run_dda<128, false>(v, gy, bk, cq, weight, cum, state_in, state_cot_rev, da, batch, seq_len, heads, groups, status, st);
   return (int)cudaErrorInvalidValue;
 }

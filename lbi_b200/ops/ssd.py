@@ -42,12 +42,12 @@ def _forward_kernels(x, dt, A, B, C, D, initial_state):
     if pad:  # dt = 0 on the padding: no decay, no contribution
         xb, Bb, Cb = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (xb, Bb, Cb))
         dtf = F.pad(dtf, (0, 0, 0, pad))
-    y, final = ext().ssd_chunk_scan_fwd(
+    y, final, states = ext().ssd_chunk_scan_fwd(
         xb.contiguous(), dtf.contiguous(), A.float().contiguous(), Bb.contiguous(), Cb.contiguous(),
         None if D is None else D.float().contiguous(), None, None if initial_state is None else initial_state.float().contiguous(),
         False, 0.0, float("inf"))
     KERNEL_LAUNCHES["count"] += 4
-    return y[:, :seqlen], final
+    return y[:, :seqlen], final, states
 
 
 def scan_generic_torch(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False):
@@ -71,16 +71,78 @@ def scan_generic_torch(v, bk, cq, a, weight=None, init=None, strict=False, per_h
     return torch.stack(ys, dim=1), (state.transpose(2, 3) if per_head else state)
 
 
-def scan_generic(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False):
-    """The kernels' scan operator with free operand roles; bf16 operands, fp32 result.  ``seq_len % 128 == 0``."""
+def scan_generic(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False, out_f32=True):
+    """The kernels' scan operator with free operand roles; bf16 operands.  ``seq_len % 128 == 0``.
+
+    Returns (y in fp32 or bf16, final state, bf16 incoming state of every chunk [b, l / 128, h, 64, n])."""
     from .dispatch import KERNEL_LAUNCHES
 
     bf = torch.bfloat16
-    y, final = ext().ssd_scan_generic(v.to(bf).contiguous(), bk.to(bf).contiguous(), cq.to(bf).contiguous(), a.float().contiguous(),
-                                      None if weight is None else weight.float().contiguous(), None, None,
-                                      None if init is None else init.float().contiguous(), bool(strict), bool(per_head), True)
+    out = ext().ssd_scan_generic(v.to(bf).contiguous(), bk.to(bf).contiguous(), cq.to(bf).contiguous(), a.float().contiguous(),
+                                 None if weight is None else weight.float().contiguous(), None, None,
+                                 None if init is None else init.float().contiguous(), bool(strict), bool(per_head), bool(out_f32))
     KERNEL_LAUNCHES["count"] += 4
-    return y, final
+    return out
+
+
+def decay_grad(v, gy, bk, cq, a, weight, *, states_in, states_cot_rev, per_head=False, init=None, gfinal=None):
+    """da_u = sum over pairs s < u <= t of e^{c_t - c_s} (cq_t . bk_s) w_s (gy_t . v_s) on the kernel (csrc/ssd.cu, part 5).
+
+    ``states_in`` / ``states_cot_rev`` are the third results of the forward scan and of the reversed scan that pulled gy
+    back; they carry the pairs that reach before the first token (``init``) or past the last one (``gfinal``)."""
+    from .dispatch import KERNEL_LAUNCHES
+
+    bf = torch.bfloat16
+    KERNEL_LAUNCHES["count"] += 2
+    return ext().ssd_decay_grad(v.to(bf).contiguous(), gy.to(bf).contiguous(), bk.to(bf).contiguous(), cq.to(bf).contiguous(),
+                                a.float().contiguous(), None if weight is None else weight.float().contiguous(),
+                                states_in, states_cot_rev, bool(per_head))
+
+
+def decay_grad_torch(v, gy, bk, cq, a, weight, *, states_in=None, states_cot_rev=None, per_head=False, init=None, gfinal=None):
+    """The same sum taken from its definition in fp32 (O(l^2) memory), the oracle of ``decay_grad``."""
+    b, l, h, _ = v.shape
+    g = bk.shape[2]
+    vf, gyf, af = v.float(), gy.float(), a.float()
+    bkf = bk.float().repeat_interleave(h // g, dim=2)
+    cqf = cq.float().repeat_interleave(h // g, dim=2)
+    wf = torch.ones_like(af) if weight is None else weight.float()
+    c = af.cumsum(1)                                                                      # [b, l, h]
+    diff = (c[:, :, None] - c[:, None, :]).permute(0, 3, 1, 2)                            # [b, h, t, s]
+    strict = torch.ones(l, l, dtype=torch.bool, device=v.device).tril(-1)
+    e = (torch.einsum("bthn,bshn->bhts", cqf, bkf) * torch.einsum("bthp,bshp->bhts", gyf, vf)
+         * torch.exp(diff.masked_fill(~strict, float("-inf"))) * wf.permute(0, 2, 1)[:, :, None, :])
+    # pairs s < u <= t: prefix over s up to u - 1, suffix over t from u
+    pre = F.pad(e.cumsum(-1), (1, 0))[..., :l]                                            # [b, h, t, u] = sum_{s < u} e[t, s]
+    da = pre.flip(2).cumsum(2).flip(2).diagonal(dim1=2, dim2=3)                           # [b, h, u] = sum_{t >= u} pre[t, u]
+    da = da.permute(0, 2, 1).clone()
+    ini = None if init is None else (init.float().transpose(2, 3) if per_head else init.float())      # [b, h, p, n]
+    gfi = None if gfinal is None else (gfinal.float().transpose(2, 3) if per_head else gfinal.float())
+    if ini is not None:    # s before the first token, t inside: every u <= t
+        r = torch.exp(c) * torch.einsum("bthp,bhpn,bthn->bth", gyf, ini, cqf)
+        da += r.flip(1).cumsum(1).flip(1)
+    if gfi is not None:    # s inside, t past the last token: every u > s
+        r = wf * torch.exp(c[:, -1:] - c) * torch.einsum("bshp,bhpn,bshn->bsh", vf, gfi, bkf)
+        da += r.cumsum(1) - r
+        if ini is not None:
+            da += (torch.exp(c[:, -1]) * (ini * gfi).sum((2, 3)))[:, None, :]
+    return da
+
+
+class KernelScans:
+    """The sm_100a kernels as the backend of ``ssd_backward`` / ``siso_core_backward``."""
+    scan = staticmethod(scan_generic)
+    decay_grad = staticmethod(decay_grad)
+
+
+class TorchScans:
+    """fp32 PyTorch statements of the same operators (CPU-runnable oracle)."""
+
+    @staticmethod
+    def scan(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False, out_f32=True):
+        return (*scan_generic_torch(v, bk, cq, a, weight, init, strict=strict, per_head=per_head), None)
+
+    decay_grad = staticmethod(decay_grad_torch)
 
 
 def _shift_reverse(a):
@@ -96,22 +158,24 @@ def _blocks(t, dup):
     return t.reshape(b, l, h * (n // 64), 64)
 
 
-def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, scan=scan_generic):
-    """Gradients of (y, final) = SSD(x, dt, A, B, C, D, init) from three role-permuted scans.
+def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, ops=KernelScans, fwd_states=None):
+    """Gradients of (y, final) = SSD(x, dt, A, B, C, D, init) from three role-permuted scans and the decay-gradient kernel.
 
     With X = dt x, c the cumulative log-decay and per-head copies of B, C:
       dX_s   = sum_{t >= s} e^{c_t - c_s} (B_s . C_t) gy_t        reversed time: v = gy, bk = C, cq = B, init = gfinal
       dC_t   = sum_{s <= t} e^{c_t - c_s} (gy_t . X_s) B_s        forward time:  v = B,  bk = x (w = dt), cq = gy, init = init^T
       dB_s/dt_s = sum_{t >= s} e^{c_t - c_s} (x_s . gy_t) C_t     reversed time: v = C,  bk = gy, cq = x, init = gfinal^T
-    The state axis (64 or 128 wide) of B and C is cut into virtual heads of width 64 for the last two.  Then
-      dc_t = C_t . dC_t - B_t . dB_t  (+ gfinal . final at the last token),  da = reversed cumulative sum of dc,
+    The state axis (64 or 128 wide) of B and C is cut into virtual heads of width 64 for the last two.  The gradient of
+    the log-decays a = dt A comes from ``ops.decay_grad`` (every pair counted once; the identity
+    ``dc_t = C_t . dC_t - B_t . dB_t`` is exact but cancels badly in bf16).  Then
       ddt = da A + dX . x,  dA = sum da dt,  dx = dt dX + D gy,  dD = sum gy . x.
-    All arguments are un-padded; ``scan`` is ``scan_generic`` (kernels) or ``scan_generic_torch`` (oracle)."""
+    All arguments are un-padded; ``ops`` is ``KernelScans`` or ``TorchScans``; ``fwd_states`` are the incoming chunk states
+    of the forward kernels (third result of ``_forward_kernels``)."""
     bsz, seqlen, h, p = x.shape
     g, n = B.shape[2], B.shape[3]
     rep = h // g
     pad = (-seqlen) % CHUNK
-    xf, dtf, Bf, Cf, gyf = x.float(), dt.float(), B.float(), C.float(), gy.float()
+    xf, dtf, Bf, Cf, gyf = x, dt.float(), B, C, gy            # operands keep their dtype: the scans take bf16, the glue promotes
     if pad:
         xf, Bf, Cf, gyf = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (xf, Bf, Cf, gyf))
         dtf = F.pad(dtf, (0, 0, 0, pad))
@@ -122,10 +186,11 @@ def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, scan=scan_generic):
     nv = max(n // 64, 2)                                                               # virtual heads per head (even)
     gfin = None if gfinal is None else gfinal.float()
 
-    # 1. dX (before the dt factor) and the gradient of the initial state
-    y1, fin1 = scan(gyf.flip(1), Cf.flip(1), Bf.flip(1), a_rev, None, gfin)
+    # 1. dX (before the dt factor), the gradient of the initial state, the state cotangents at the chunk boundaries
+    y1, fin1, rev_states = ops.scan(gyf.flip(1), Cf.flip(1), Bf.flip(1), a_rev, None, gfin)
     dX = y1.flip(1)
     d_init = fin1 * torch.exp(a[:, 0])[..., None, None] if init is not None else None
+    da = ops.decay_grad(xf, gyf, Bf, Cf, a, dtf, states_in=fwd_states, states_cot_rev=rev_states, init=init, gfinal=gfin)
 
     def state_blocks(st):   # [b, h, p, n] -> [b, h * nv, 64 (n in block), 64 (p)]
         t = st.float().transpose(2, 3)                                                 # [b, h, n, p]
@@ -135,25 +200,22 @@ def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, scan=scan_generic):
 
     rep_v = lambda t: t.repeat_interleave(nv, dim=2)  # noqa: E731
     # 2. dC per head
-    y2, _ = scan(_blocks(Bh, nv), xf, gyf, rep_v(a), rep_v(dtf), None if init is None else state_blocks(init))
+    y2 = ops.scan(_blocks(Bh, nv), xf, gyf, rep_v(a), rep_v(dtf), None if init is None else state_blocks(init), out_f32=False)[0]
     dCh = y2.reshape(bsz, seqlen + pad, h, nv * 64)[..., :n]
     # 3. dB per head
-    y3, _ = scan(_blocks(Ch, nv).flip(1), gyf.flip(1), xf.flip(1), rep_v(a_rev), None, None if gfin is None else state_blocks(gfin))
-    dBh = y3.flip(1).reshape(bsz, seqlen + pad, h, nv * 64)[..., :n] * dtf[..., None]
+    y3 = ops.scan(_blocks(Ch, nv).flip(1), gyf.flip(1), xf.flip(1), rep_v(a_rev), None, None if gfin is None else state_blocks(gfin),
+                  out_f32=False)[0]
+    dBh = y3.flip(1).reshape(bsz, seqlen + pad, h, nv * 64)[..., :n]
 
-    dc = (Ch * dCh).sum(-1) - (Bh * dBh).sum(-1)                                       # [b, l, h]
-    if gfin is not None:
-        dc[:, -1] += (gfin * final.float()).sum((2, 3))
-    da = dc.flip(1).cumsum(1).flip(1)
     ddt = da * Af + (dX * xf).sum(-1)
     dA = (da * dtf).sum((0, 1))
     dx = dtf[..., None] * dX
     dD = None
     if D is not None:
         dx = dx + D.float()[None, None, :, None] * gyf
-        dD = (gyf * xf).sum((0, 1, 3))
-    dB = dBh.reshape(bsz, seqlen + pad, g, rep, n).sum(3)
-    dC = dCh.reshape(bsz, seqlen + pad, g, rep, n).sum(3)
+        dD = (gyf.float() * xf).sum((0, 1, 3))
+    dB = (dBh.reshape(bsz, seqlen + pad, g, rep, n) * dtf.reshape(bsz, seqlen + pad, g, rep, 1)).sum(3)
+    dC = dCh.reshape(bsz, seqlen + pad, g, rep, n).sum(3, dtype=torch.float32)
     cut = slice(0, seqlen)
     return dx[:, cut], ddt[:, cut], dA, dB[:, cut], dC[:, cut], dD, d_init
 
@@ -161,20 +223,20 @@ def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, scan=scan_generic):
 class _SSDFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, dt, A, B, C, D, initial_state):
-        y, final = _forward_kernels(x, dt, A, B, C, D, initial_state)
+        y, final, states = _forward_kernels(x, dt, A, B, C, D, initial_state)
         ctx.save_for_backward(x, dt, A, B, C, D if D is not None else x.new_empty(0),
-                              initial_state if initial_state is not None else x.new_empty(0), final)
+                              initial_state if initial_state is not None else x.new_empty(0), final, states)
         ctx.has_d, ctx.has_init = D is not None, initial_state is not None
         return y.to(x.dtype), final
 
     @staticmethod
     def backward(ctx, gy, gfinal):
-        x, dt, A, B, C, D, init, final = ctx.saved_tensors
-        if BACKWARD_KERNELS and hasattr(ext(), "ssd_scan_generic"):
+        x, dt, A, B, C, D, init, final, states = ctx.saved_tensors
+        if BACKWARD_KERNELS and hasattr(ext(), "ssd_decay_grad"):
             if gy is None:
                 gy = torch.zeros_like(x)
             dx, ddt, dA, dB, dC, dD, d_init = ssd_backward(x, dt, A, B, C, D if ctx.has_d else None, init if ctx.has_init else None,
-                                                           final, gy, gfinal)
+                                                           final, gy, gfinal, fwd_states=states)
             return (dx.to(x.dtype), ddt.to(dt.dtype), dA.to(A.dtype), dB.to(B.dtype), dC.to(C.dtype),
                     None if dD is None else dD.to(D.dtype), None if d_init is None else d_init.to(init.dtype))
         return _SSDFunction._backward_recompute(ctx, gy, gfinal)
@@ -183,7 +245,7 @@ class _SSDFunction(torch.autograd.Function):
     def _backward_recompute(ctx, gy, gfinal):
         from ..backbones.mamba2.ssd import ssd_chunk_scan
 
-        x, dt, A, B, C, D, init, _ = ctx.saved_tensors
+        x, dt, A, B, C, D, init, _, _ = ctx.saved_tensors
         leaves = [t.detach().requires_grad_(t.is_floating_point()) for t in (x, dt, A, B, C)]
         d_leaf = D.detach().requires_grad_(True) if ctx.has_d else None
         i_leaf = init.detach().requires_grad_(True) if ctx.has_init else None
@@ -207,7 +269,7 @@ def ssd_chunk_scan_cuda(x, dt, A, B, C, D=None, initial_state=None, return_final
     if torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (x, dt, A, B, C, D, initial_state)):
         y, final = _SSDFunction.apply(x, dt, A, B, C, D, initial_state)
     else:
-        y, final = _forward_kernels(x, dt, A, B, C, D, initial_state)
+        y, final, _ = _forward_kernels(x, dt, A, B, C, D, initial_state)
         y = y.to(x.dtype)
     return (y, final) if return_final_state else y
 
@@ -236,39 +298,38 @@ def _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
     if pad:  # adt = 0 and k = 0 on the padding: the state is carried unchanged
         vb, qb, kb = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (vb, qb, kb))
         adt, skip = F.pad(adt, (0, 0, 0, pad)), F.pad(skip, (0, 0, 0, pad))
-    y, final = ext().siso_chunk_scan_fwd(vb.contiguous(), kb.contiguous(), qb.contiguous(), adt.float().contiguous(),
-                                         None if D is None else D.float().contiguous(),
-                                         skip.float().transpose(1, 2).contiguous(), None)
+    y, final, states = ext().siso_chunk_scan_fwd(vb.contiguous(), kb.contiguous(), qb.contiguous(), adt.float().contiguous(),
+                                                 None if D is None else D.float().contiguous(),
+                                                 skip.float().transpose(1, 2).contiguous(), None)
     KERNEL_LAUNCHES["count"] += 4
-    return y[:, :seqlen], final
+    return y[:, :seqlen], final, states
 
 
-def siso_core_backward(Qr, Kr, adt, skip, V, gy, scan=scan_generic):
+def siso_core_backward(Qr, Kr, adt, skip, V, gy, ops=KernelScans, fwd_states=None):
     """Gradients of y_t = sum_{s < t} e^{c_t - c_s} (Qr_t . Kr_s) V_s + skip_t V_t with respect to the preprocessed operands.
 
     Qr, Kr [b, l, h, 128]; adt, skip [b, l, h]; V, gy [b, l, h, 64].  Three strict scans with permuted roles:
       dV_s  = sum_{t > s} e^{c_t - c_s} (Kr_s . Qr_t) gy_t + skip_s gy_s    reversed, per head:  v = gy, bk = Qr, cq = Kr
       dQr_t = sum_{s < t} e^{c_t - c_s} (gy_t . V_s) Kr_s                   forward:  v = Kr (two halves), bk = V,  cq = gy
       dKr_s = sum_{t > s} e^{c_t - c_s} (V_s . gy_t) Qr_t                   reversed: v = Qr (two halves), bk = gy, cq = V
-    and dadt = reversed cumulative sum of (Qr . dQr - Kr . dKr), dskip = gy . V.  Returns (dQr, dKr, dadt, dskip, dV)."""
+    dadt from ``ops.decay_grad`` (pairs s < u <= t counted once), dskip = gy . V.  Returns (dQr, dKr, dadt, dskip, dV)."""
     bsz, seqlen, h, _ = V.shape
     n = Qr.shape[-1]
     pad = (-seqlen) % CHUNK
-    Qf, Kf, Vf, gyf, af = Qr.float(), Kr.float(), V.float(), gy.float(), adt.float()
+    Qf, Kf, Vf, gyf, af = Qr, Kr, V, gy, adt.float()
     if pad:
         Qf, Kf, Vf, gyf = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (Qf, Kf, Vf, gyf))
         af = F.pad(af, (0, 0, 0, pad))
     a_rev = _shift_reverse(af)
     nv = n // 64
     rep_v = lambda t: t.repeat_interleave(nv, dim=2)  # noqa: E731
-    y1, _ = scan(gyf.flip(1), Qf.flip(1), Kf.flip(1), a_rev, None, None, strict=True, per_head=True)
+    y1, _, rev_states = ops.scan(gyf.flip(1), Qf.flip(1), Kf.flip(1), a_rev, None, None, strict=True, per_head=True)
     dV = y1.flip(1)[:, :seqlen] + skip.float()[..., None] * gy.float()
-    y2, _ = scan(_blocks(Kf, nv), Vf, gyf, rep_v(af), None, None, strict=True)
+    dadt = ops.decay_grad(Vf, gyf, Kf, Qf, af, None, states_in=fwd_states, states_cot_rev=rev_states, per_head=True)[:, :seqlen]
+    y2 = ops.scan(_blocks(Kf, nv), Vf, gyf, rep_v(af), None, None, strict=True)[0]
     dQr = y2.reshape(bsz, seqlen + pad, h, n)
-    y3, _ = scan(_blocks(Qf, nv).flip(1), gyf.flip(1), Vf.flip(1), rep_v(a_rev), None, None, strict=True)
+    y3 = ops.scan(_blocks(Qf, nv).flip(1), gyf.flip(1), Vf.flip(1), rep_v(a_rev), None, None, strict=True)[0]
     dKr = y3.flip(1).reshape(bsz, seqlen + pad, h, n)
-    dc = (Qf * dQr).sum(-1) - (Kf * dKr).sum(-1)
-    dadt = dc.flip(1).cumsum(1).flip(1)[:, :seqlen]
     dskip = (gy.float() * V.float()).sum(-1)
     return dQr[:, :seqlen], dKr[:, :seqlen], dadt, dskip, dV
 
@@ -276,13 +337,13 @@ def siso_core_backward(Qr, Kr, adt, skip, V, gy, scan=scan_generic):
 class _SISOFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
-        y, _ = _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D)
-        ctx.save_for_backward(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D)
+        y, _, states = _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D)
+        ctx.save_for_backward(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D, states)
         return y.to(V.dtype)
 
     @staticmethod
     def backward(ctx, gy):
-        if BACKWARD_KERNELS and hasattr(ext(), "ssd_scan_generic"):
+        if BACKWARD_KERNELS and hasattr(ext(), "ssd_decay_grad"):
             return _SISOFunction._backward_kernels(ctx, gy)
         return _SISOFunction._backward_recompute(ctx, gy)
 
@@ -291,12 +352,12 @@ class _SISOFunction(torch.autograd.Function):
         """Kernel scans for the recurrence, autograd for the elementwise preprocessing in front of it."""
         from ..backbones.mamba3.siso import _prepare
 
-        Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D = ctx.saved_tensors
+        Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D, states = ctx.saved_tensors
         pre = [t.detach().requires_grad_(True) for t in (Q, K, ADT, DT, Trap, Q_bias, K_bias, Angles)]
         with torch.enable_grad():
             Qr, Kr, adt, qk_dot = _prepare(pre[0], pre[1], V, pre[2], pre[3], pre[4], pre[5], pre[6], pre[7], torch.float32)
         skip = qk_dot.detach() + D.float()[None, None]
-        dQr, dKr, dadt, dskip, dV = siso_core_backward(Qr.detach(), Kr.detach(), adt.detach(), skip, V, gy)
+        dQr, dKr, dadt, dskip, dV = siso_core_backward(Qr.detach(), Kr.detach(), adt.detach(), skip, V, gy, fwd_states=states)
         grads = torch.autograd.grad([Qr, Kr, adt, qk_dot], pre, [dQr, dKr, dadt, dskip], allow_unused=True)
         gQ, gK, gADT, gDT, gTrap, gQb, gKb, gAng = grads
         return gQ, gK, dV.to(V.dtype), gADT, gDT, gTrap, gQb, gKb, gAng, dskip.sum((0, 1)).to(D.dtype)
@@ -305,7 +366,7 @@ class _SISOFunction(torch.autograd.Function):
     def _backward_recompute(ctx, gy):
         from ..backbones.mamba3.siso import mamba3_siso_chunked
 
-        leaves = [t.detach().requires_grad_(True) for t in ctx.saved_tensors]
+        leaves = [t.detach().requires_grad_(True) for t in ctx.saved_tensors[:10]]
         with torch.enable_grad():
             y = mamba3_siso_chunked(*leaves[:9], D=leaves[9], Z=None, chunk_size=CHUNK)
             grads = torch.autograd.grad(y, leaves, gy.to(y.dtype), allow_unused=True)

@@ -197,3 +197,30 @@ def test_interface_jacobian_kernels_match_the_einsum_forms(hidden, activation):
     _close(ln_f, vm.layer_norm_input_jacobian(norm, s, gg).detach(), 1e-4, 1e-4, "layernorm J")
     lhs, rhs = (g * j_t).sum(-1), (jt_g * t).sum(-1)
     _close(lhs, rhs, 1e-3, 1e-3, "adjoint identity")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("gated,norm_before_gate,group", [(True, False, None), (True, True, 64), (False, True, None), (True, True, None)])
+def test_gated_rmsnorm_kernels_match_the_pytorch_form(dtype, gated, norm_before_gate, group):
+    """Forward and every gradient (x, gate, weight) of the gated / grouped RMSNorm kernels against fp32 autograd."""
+    from lbi_b200.backbones.norms import gated_rms_norm, rms_norm_reference
+
+    torch.manual_seed(5)
+    rows, dim = 3 * 67, 256
+    x = torch.randn(3, 67, dim, device=DEV).to(dtype)
+    z = torch.randn(3, 67, dim, device=DEV).to(dtype) if gated else None
+    w = (torch.rand(dim, device=DEV) + 0.5)
+    gy = torch.randn(3, 67, dim, device=DEV).to(dtype)
+    leaves = [t.clone().requires_grad_(True) for t in ([x, z, w] if gated else [x, w])]
+    before = ops.dispatch.KERNEL_LAUNCHES["count"]
+    y = gated_rms_norm(leaves[0], leaves[-1], eps=1e-5, z=leaves[1] if gated else None, norm_before_gate=norm_before_gate, group_size=group)
+    got = torch.autograd.grad(y, leaves, gy)
+    assert ops.dispatch.KERNEL_LAUNCHES["count"] == before + 2, "the gated RMSNorm kernels did not run"
+    ref = [t.detach().float().requires_grad_(True) for t in leaves]
+    ry = rms_norm_reference(ref[0], ref[-1], eps=1e-5, z=ref[1] if gated else None, norm_before_gate=norm_before_gate, group_size=group)
+    want = torch.autograd.grad(ry, ref, gy.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    _close(y, ry.detach(), tol, tol, "gated rmsnorm y")
+    for name, a_, w_ in zip(("dx", "dz", "dw") if gated else ("dx", "dw"), got, want):
+        err = (a_.float() - w_).norm().item() / w_.norm().item()
+        assert err <= (1e-2 if dtype == torch.bfloat16 else 1e-5), f"{name}: {err:.2e}"

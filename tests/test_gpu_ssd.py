@@ -74,6 +74,34 @@ def test_generic_scan_matches_its_oracle(strict, per_head, n):
     assert (fin - want_fin).norm().item() <= 1e-2 * want_fin.norm().item()
 
 
+@pytest.mark.parametrize("per_head,n,with_states", [(False, 64, True), (False, 128, False), (True, 128, True)])
+def test_decay_gradient_kernel_matches_its_definition(per_head, n, with_states):
+    from lbi_b200.ops.ssd import _shift_reverse, decay_grad, decay_grad_torch, scan_generic
+
+    b, l, h = 2, 384, 4
+    g = h if per_head else 2
+    gen = torch.Generator(device=DEV).manual_seed(23 + n)
+    v = torch.randn(b, l, h, 64, device=DEV, generator=gen).bfloat16()
+    gy = torch.randn(b, l, h, 64, device=DEV, generator=gen).bfloat16()
+    bk = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3).bfloat16()
+    cq = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.3).bfloat16()
+    a = -(torch.rand(b, l, h, device=DEV, generator=gen) * 0.2)
+    w = None if per_head else torch.rand(b, l, h, device=DEV, generator=gen) + 0.5
+    shape = (b, h, n, 64) if per_head else (b, h, 64, n)
+    init = torch.randn(shape, device=DEV, generator=gen).bfloat16().float() if with_states else None
+    gfin = torch.randn(shape, device=DEV, generator=gen).bfloat16().float() if with_states else None
+    fwd_states = scan_generic(v, bk, cq, a, w, init, strict=per_head, per_head=per_head)[2]
+    rev_states = scan_generic(gy.flip(1), cq.flip(1), bk.flip(1), _shift_reverse(a), None, gfin, strict=per_head, per_head=per_head)[2]
+    da = decay_grad(v, gy, bk, cq, a, w, states_in=fwd_states, states_cot_rev=rev_states, per_head=per_head)
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(v) == 0
+    want = decay_grad_torch(v, gy, bk, cq, a, w, per_head=per_head, init=init, gfinal=gfin)
+    assert da.shape == want.shape
+    assert (da - want).norm().item() <= 1e-2 * want.norm().item()
+    # sums that weight every token alike (what dA is made of) keep the accuracy: no accumulated cancellation
+    assert abs((da.sum() - want.sum()).item()) <= 1e-2 * want.abs().sum().item() / l ** 0.5 + 1e-3 * abs(want.sum().item())
+
+
 @pytest.mark.parametrize("b,l,h,g,n,with_state", [(2, 256, 4, 1, 128, True), (1, 200, 4, 2, 64, False), (1, 512, 8, 2, 128, False),
                                                    (2, 128, 2, 1, 64, True)])
 def test_ssd_backward_kernels_match_autograd_of_the_recurrence(b, l, h, g, n, with_state):

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from lbi_b200.backbones.mamba2.ssd import ssd_recurrent_reference
-from lbi_b200.ops.ssd import scan_generic_torch, ssd_backward
+from lbi_b200.ops.ssd import TorchScans, scan_generic_torch, ssd_backward
 
 
 @pytest.mark.parametrize("n,g,with_state,seqlen", [(128, 1, True, 40), (64, 2, False, 33), (128, 2, True, 130)])
@@ -27,7 +27,7 @@ def test_role_permuted_backward_matches_autograd(n, g, with_state, seqlen):
     leaves = [x, dt, A, B, C, D] + ([init] if with_state else [])
     want = torch.autograd.grad([y, fin], leaves, [gy, gfin])
     f = lambda t: None if t is None else t.detach().float()  # noqa: E731
-    got = ssd_backward(f(x), f(dt), f(A), f(B), f(C), f(D), f(init), f(fin), f(gy), f(gfin), scan=scan_generic_torch)
+    got = ssd_backward(f(x), f(dt), f(A), f(B), f(C), f(D), f(init), f(fin), f(gy), f(gfin), ops=TorchScans)
     for name, a_, w_ in zip(("dx", "ddt", "dA", "dB", "dC", "dD", "dinit"), got, want):
         assert a_.shape == w_.shape, name
         err = (a_.double() - w_).norm().item() / w_.norm().item()
@@ -72,7 +72,7 @@ def test_siso_backward_from_permuted_strict_scans_matches_autograd():
     pre = [t.requires_grad_(True) for t in (f[0], f[1], f[3], f[4], f[5], f[6], f[7], f[8])]
     Qr, Kr, adt, qk = _prepare(pre[0], pre[1], f[2], pre[2], pre[3], pre[4], pre[5], pre[6], pre[7], torch.float32)
     skip = qk.detach() + f[9][None, None]
-    dQr, dKr, dadt, dskip, dV = siso_core_backward(Qr.detach(), Kr.detach(), adt.detach(), skip, f[2], gy.float(), scan=scan_generic_torch)
+    dQr, dKr, dadt, dskip, dV = siso_core_backward(Qr.detach(), Kr.detach(), adt.detach(), skip, f[2], gy.float(), ops=TorchScans)
     gr = torch.autograd.grad([Qr, Kr, adt, qk], pre, [dQr, dKr, dadt, dskip])
     got = [gr[0], gr[1], dV, gr[2], gr[3], gr[4], gr[5], gr[6], gr[7], dskip.sum((0, 1))]
     for name, a_, w_ in zip("Q K V ADT DT Trap Q_bias K_bias Angles D".split(), got, want):
