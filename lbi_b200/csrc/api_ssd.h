@@ -50,6 +50,17 @@ int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk, const void
                        const void* state_in, const void* state_cot_rev, float* da, int batch, int seq_len, int heads,
                        int groups, int d_state, int per_head, int* status, cudaStream_t stream);
 
+// Elementwise tail of the SSD backward.  dx_rev [B, seq_pad, H, 64] fp32 is the reversed-time scan result; x, gy, dx
+// [B, L, H, 64] bf16 or fp32; dt, ddt [B, L, H]; da [B, H, seq_pad]; a_param, d_skip (or null), dd (or null, accumulated) [H].
+//   dx = dt * dX + d_skip * gy,  ddt = da * a_param + dX . x,  dd[h] += sum gy . x
+int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void* gy, const float* dt, const float* da,
+                       const float* a_param, const float* d_skip, void* dx, float* ddt, float* dd, int batch, int seq_len,
+                       int seq_pad, int heads, int is_bf16, cudaStream_t stream);
+// out[b, l, g, :n] = sum over the heads h of group g of w[b, l, h] * y[b, l or seq_pad - 1 - l, h, :n]; y bf16 with rows of
+// `width` columns, w [B, L, H] or null, out bf16 or fp32.
+int lbi_ssd_group_sum(const void* y_bf16, const float* w, void* out, int batch, int seq_len, int seq_pad, int heads, int groups,
+                      int n, int width, int reversed, int out_is_bf16, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -616,6 +616,55 @@ Tensor ssd_decay_grad(const Tensor& v, const Tensor& gy, const Tensor& bk, const
   return da.transpose(1, 2);
 }
 
+// dx_rev [B, Lp, H, 64] fp32 (reversed time), x / gy [B, L, H, 64], dt [B, L, H], da [B, Lp, H] (a transposed view of the
+// decay-gradient result), a_param [H], d_skip [H] or none -> (dx like x, ddt [B, L, H], dD [H] or empty).
+std::tuple<Tensor, Tensor, Tensor> ssd_bwd_finish(const Tensor& dx_rev, const Tensor& x, const Tensor& gy, const Tensor& dt, const Tensor& da,
+                                                  const Tensor& a_param, const c10::optional<Tensor>& d_skip) {
+  CHECK_F32(dx_rev);
+  CHECK_F32(dt);
+  CHECK_F32(a_param);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && gy.is_contiguous() && gy.sizes() == x.sizes() && gy.scalar_type() == x.scalar_type() &&
+                  (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat) && x.dim() == 4 && x.size(3) == 64,
+              "ssd_bwd_finish: x, gy must be contiguous [B, L, H, 64] bf16 / fp32");
+  const int64_t batch = x.size(0), seq = x.size(1), heads = x.size(2), seq_pad = dx_rev.size(1);
+  TORCH_CHECK(dx_rev.dim() == 4 && dx_rev.size(0) == batch && dx_rev.size(2) == heads && dx_rev.size(3) == 64 && seq_pad >= seq,
+              "ssd_bwd_finish: dx_rev must be [B, Lp, H, 64]");
+  TORCH_CHECK(dt.sizes() == at::IntArrayRef({batch, seq, heads}), "ssd_bwd_finish: dt must be [B, L, H]");
+  Tensor da_t = da.transpose(1, 2).contiguous();   // [B, H, Lp]; free when da is the transposed view the kernel returned
+  TORCH_CHECK(da_t.scalar_type() == at::kFloat && da_t.size(0) == batch && da_t.size(1) == heads && da_t.size(2) == seq_pad,
+              "ssd_bwd_finish: da must be [B, Lp, H] fp32");
+  Tensor dx = torch::empty_like(x);
+  Tensor ddt = torch::empty({batch, seq, heads}, dt.options());
+  Tensor dd = d_skip ? torch::zeros({heads}, dt.options()) : torch::empty({0}, dt.options());
+  if (d_skip) CHECK_F32((*d_skip));
+  check(lbi_ssd_bwd_finish(dx_rev.data_ptr<float>(), x.data_ptr(), gy.data_ptr(), dt.data_ptr<float>(), da_t.data_ptr<float>(),
+                           a_param.data_ptr<float>(), d_skip ? d_skip->data_ptr<float>() : nullptr, dx.data_ptr(), ddt.data_ptr<float>(),
+                           d_skip ? dd.data_ptr<float>() : nullptr, (int)batch, (int)seq, (int)seq_pad, (int)heads,
+                           x.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+        "ssd_bwd_finish");
+  return {dx, ddt, dd};
+}
+
+// y [B, Lp, H, width] bf16 -> out [B, L, G, n] (bf16 or fp32): sum over the heads of each group, optional per-head weight
+// w [B, L, H], optional time reversal of y.
+Tensor ssd_group_sum(const Tensor& y, const c10::optional<Tensor>& w, int64_t seq_len, int64_t groups, int64_t n, bool reversed,
+                     bool out_bf16) {
+  CHECK_BF16(y);
+  c10::cuda::CUDAGuard guard(y.device());
+  TORCH_CHECK(y.dim() == 4, "ssd_group_sum: y must be [B, Lp, H, width]");
+  const int64_t batch = y.size(0), seq_pad = y.size(1), heads = y.size(2), width = y.size(3);
+  if (w) {
+    CHECK_F32((*w));
+    TORCH_CHECK(w->sizes() == at::IntArrayRef({batch, seq_len, heads}), "ssd_group_sum: w must be [B, L, H]");
+  }
+  Tensor out = torch::empty({batch, seq_len, groups, n}, y.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+  check(lbi_ssd_group_sum(y.data_ptr(), w ? w->data_ptr<float>() : nullptr, out.data_ptr(), (int)batch, (int)seq_len, (int)seq_pad,
+                          (int)heads, (int)groups, (int)n, (int)width, reversed ? 1 : 0, out_bf16 ? 1 : 0, cur_stream()),
+        "ssd_group_sum");
+  return out;
+}
+
 // ---- peer-memory kernels.  `*_ptrs` are int64 CUDA tensors holding one device pointer per rank.
 template <typename T>
 T ptr_table(const Tensor& t) {
@@ -788,6 +837,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("siso_chunk_scan_fwd", &siso_chunk_scan_fwd);
   m.def("ssd_scan_generic", &ssd_scan_generic);
   m.def("ssd_decay_grad", &ssd_decay_grad);
+  m.def("ssd_bwd_finish", &ssd_bwd_finish);
+  m.def("ssd_group_sum", &ssd_group_sum);
   m.def("kernel_status", &kernel_status);
   m.def("set_peer_wait_limit_ms", &set_peer_wait_limit_ms);
   m.def("peer_barrier", &peer_barrier);

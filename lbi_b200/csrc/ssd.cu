@@ -428,8 +428,11 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
 //   E_ts = e^{c_t - c_s} (cq_t . bk_s) w_s (gy_t . v_s)      over all pairs s < u <= t.
 // Taken as differences of row sums (cq . dcq - bk . dbk) the pairs on one side of u cancel only in exact arithmetic;
 // here every pair is counted once.  Per (batch, chunk, head), with H_in the state entering the chunk and dH_out the
-// cotangent of the state leaving it (the incoming state of the time-reversed pass at the mirrored chunk):
-//   pairs inside the chunk     G1 = cq bk^T, G2 = gy v^T in TMEM; row prefixes of G1 o G2 o decay o w, summed over t >= u
+// cotangent of the state leaving it (the incoming state of the time-reversed pass at the mirrored chunk, times the
+// decay of the first token after the chunk, which that pass applies inside its chunk):
+//   pairs inside the chunk     G1 = cq bk^T, G2 = gy v^T in TMEM; e = G1 o G2 o decay o w is formed once in fp32, its row
+//                              sums R_t and (through a shared-memory transpose) column sums K_s give the block sums as
+//                              sum_{u' >= u} (R_u' - K_u'): exact cancellation, since both sums see the same e
 //   s before, t inside         sum_{t >= u} e^{c_t} gy_t . (cq_t H_in^T)
 //   s inside, t after          sum_{s < u}  w_s e^{c_end - c_s} v_s . (bk_s dH_out^T)
 //   s before, t after          e^{c_end} <H_in, dH_out>
@@ -447,9 +450,9 @@ struct SmemDda {
   float wv[L];
   float r2[L];
   float r3[L];
-  float da_in[L];
   float red[4];
-  uint64_t bar_full, bar_mma;
+  float et[L][L + 1];   // e[t][s], padded rows: conflict-free row writes and column reads
+  uint64_t bar_full, bar_mma, bar_rows;
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -502,6 +505,7 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
     s.abort_flag = 0;
     mbar_init(&s.bar_full, 1);
     mbar_init(&s.bar_mma, 1);
+    mbar_init(&s.bar_rows, 4);
     fence_barrier_init();
     prefetch_tmap(&map_x);
     prefetch_tmap(&map_gy);
@@ -567,15 +571,16 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
     const float my_cum2 = p.cum[base + l] * LOG2E;
     s.cum2[l] = my_cum2;
     s.wv[l] = p.weight ? p.weight[base + l] : 1.f;
-    s.da_in[l] = 0.f;
+    // decay of the first token of the next chunk (its first in-chunk cumulative value); 1 past the last chunk
+    const float next_decay = c + 1 < p.chunks ? ex2(p.cum[base + L] * LOG2E) : 1.f;
     named_barrier_sync(1, 128);
     bool ok = mbar_wait(&s.bar_mma, 0, abortp, p.status, 62);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       fence_after_sync();
       const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-      // pairs inside the chunk: running row prefix, column u = s + 1 collects it from every row t >= u
-      float prefix = 0.f;
+      // pairs inside the chunk: e[t][s] for s < t, row sum kept, the tile stored for the column sums
+      float row_sum = 0.f;
       for (int q = 0; q <= warp; ++q) {
         uint32_t g1[32], g2[32];
         tmem_ld_32x32(trow + q * 32, g1);
@@ -584,11 +589,9 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int sidx = q * 32 + j;
-          const bool live = sidx < l;
-          const float e = live ? __uint_as_float(g1[j]) * __uint_as_float(g2[j]) * ex2(my_cum2 - s.cum2[sidx]) * s.wv[sidx] : 0.f;
-          prefix += e;
-          const float col = warp_sum(live ? prefix : 0.f);
-          if (lane == 0 && sidx < L - 1) atomicAdd(&s.da_in[sidx + 1], col);
+          const float e = sidx < l ? __uint_as_float(g1[j]) * __uint_as_float(g2[j]) * ex2(my_cum2 - s.cum2[sidx]) * s.wv[sidx] : 0.f;
+          row_sum += e;
+          s.et[l][sidx] = e;
         }
       }
       // state terms
@@ -596,12 +599,12 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
       tmem_ld_32x32(trow + 256, r0);
       tmem_ld_32x32(trow + 288, r1);
       tmem_ld_wait();
-      s.r2[l] = ex2(my_cum2) * dot_row64(smem_u32(s.gyt) + l * 128, l, r0, r1);
+      const float r2 = ex2(my_cum2) * dot_row64(smem_u32(s.gyt) + l * 128, l, r0, r1);
       tmem_ld_32x32(trow + 320, r0);
       tmem_ld_32x32(trow + 352, r1);
       tmem_ld_wait();
       const float cum_end2 = s.cum2[L - 1];
-      s.r3[l] = s.wv[l] * ex2(cum_end2 - my_cum2) * dot_row64(smem_u32(s.xt) + l * 128, l, r0, r1);
+      s.r3[l] = next_decay * s.wv[l] * ex2(cum_end2 - my_cum2) * dot_row64(smem_u32(s.xt) + l * 128, l, r0, r1);
       // <H_in, dH_out>: both tiles have the same layout, so the product runs over raw 16-byte pieces
       float hd = 0.f;
       const uint32_t hin_a = smem_u32(s.hin[0]), dho_a = smem_u32(s.dho[0]);
@@ -613,12 +616,29 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
       }
       hd = warp_sum(hd);
       if (lane == 0) s.red[warp] = hd;
-      named_barrier_sync(1, 128);
+      // every warp's tile rows must be in shared memory before the column sums: bounded waits, not bar.sync, so that a
+      // warp that gave up above cannot strand the others
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.bar_rows);
+      ok = mbar_wait(&s.bar_rows, 0, abortp, p.status, 63);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        float col_sum = 0.f;   // K_l = sum_{t > l} e[t][l]
+        for (int t = l + 1; t < L; ++t) col_sum += s.et[t][l];
+        s.r2[l] = r2 + row_sum - col_sum;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s.bar_rows);
+        ok = mbar_wait(&s.bar_rows, 1, abortp, p.status, 64);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+    }
+    if (ok) {
+      const float cum_end2 = s.cum2[L - 1];
       float tail2 = 0.f, head3 = 0.f;
       for (int t = l; t < L; ++t) tail2 += s.r2[t];
       for (int t = 0; t < l; ++t) head3 += s.r3[t];
-      const float through = ex2(cum_end2) * (s.red[0] + s.red[1] + s.red[2] + s.red[3]);
-      p.da[base + l] = s.da_in[l] + tail2 + head3 + through;
+      const float through = next_decay * ex2(cum_end2) * (s.red[0] + s.red[1] + s.red[2] + s.red[3]);
+      p.da[base + l] = tail2 + head3 + through;
     }
   }
   __syncwarp();
@@ -632,6 +652,87 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
     fence_after_sync();
     tmem_dealloc(tmem, TMEM_COLS);
   }
+}
+
+
+// ------------------------------------------------------------------------------------------------ 6. backward glue
+// dx = dt * dX + D * gy,  ddt = da * A + dX . x,  dD[h] += sum gy . x        with dX read in reversed time order.
+// One warp per (batch, token, head) row of 64; dD through one atomic per warp.
+template <typename T>
+__device__ __forceinline__ float2 ld2(const T* p);
+template <>
+__device__ __forceinline__ float2 ld2<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <>
+__device__ __forceinline__ float2 ld2<float>(const float* p) {
+  return *reinterpret_cast<const float2*>(p);
+}
+template <typename T>
+__device__ __forceinline__ void st2(T* p, float a, float b);
+template <>
+__device__ __forceinline__ void st2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+template <>
+__device__ __forceinline__ void st2<float>(float* p, float a, float b) {
+  *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bwd_finish_kernel(const float* __restrict__ dx_rev, const T* __restrict__ x,
+                                                         const T* __restrict__ gy, const float* __restrict__ dt,
+                                                         const float* __restrict__ da, const float* __restrict__ a_param,
+                                                         const float* __restrict__ d_skip, T* __restrict__ dx,
+                                                         float* __restrict__ ddt, float* __restrict__ dd, int64_t rows,
+                                                         int seq_len, int seq_pad, int heads) {
+  // rows = batch * seq_len * heads; dx_rev is [batch, seq_pad, heads, 64] in reversed time; dt [b, l, h]; da [b, h, seq_pad]
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int h = (int)(row % heads);
+  const int64_t bl = row / heads;
+  const int l = (int)(bl % seq_len);
+  const int64_t b = bl / seq_len;
+  const int64_t rrow = (b * seq_pad + (seq_pad - 1 - l)) * heads + h;
+  const float2 g = *reinterpret_cast<const float2*>(dx_rev + rrow * P + lane * 2);
+  const float2 xv = ld2<T>(x + row * P + lane * 2);
+  const float2 gv = ld2<T>(gy + row * P + lane * 2);
+  const float dtv = dt[row], dsk = d_skip ? d_skip[h] : 0.f;
+  st2<T>(dx + row * P + lane * 2, dtv * g.x + dsk * gv.x, dtv * g.y + dsk * gv.y);
+  const float dot = warp_sum(g.x * xv.x + g.y * xv.y);
+  const float gx = warp_sum(gv.x * xv.x + gv.y * xv.y);
+  if (lane == 0) {
+    ddt[row] = da[(b * heads + h) * seq_pad + l] * a_param[h] + dot;
+    if (dd) atomicAdd(dd + h, gx);
+  }
+}
+
+// out[b, l, g, n] = sum over the heads of group g of w[b, l, h] * y[b, l', h, n]   (l' = seq_pad - 1 - l when reversed; w = 1
+// when null); y is [batch, seq_pad, heads, width] bf16 with the first n of every `width` columns used.
+template <typename T>
+__global__ void __launch_bounds__(256) group_sum_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
+                                                        T* __restrict__ out, int64_t total, int seq_len, int seq_pad, int heads,
+                                                        int groups, int n, int width, int reversed) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // one thread per two outputs
+  if (idx >= total) return;
+  const int half_n = n / 2;
+  const int c2 = (int)(idx % half_n);
+  const int g = (int)((idx / half_n) % groups);
+  const int64_t bl = idx / ((int64_t)half_n * groups);
+  const int l = (int)(bl % seq_len);
+  const int64_t b = bl / seq_len;
+  const int rep = heads / groups;
+  const int64_t src_tok = b * seq_pad + (reversed ? seq_pad - 1 - l : l);
+  float a0 = 0.f, a1 = 0.f;
+  for (int r = 0; r < rep; ++r) {
+    const int h = g * rep + r;
+    const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(y + (src_tok * heads + h) * width + c2 * 2));
+    const float ww = w ? w[(b * seq_len + l) * heads + h] : 1.f;
+    a0 = fmaf(ww, v.x, a0);
+    a1 = fmaf(ww, v.y, a1);
+  }
+  st2<T>(out + ((b * seq_len + l) * groups + g) * n + c2 * 2, a0, a1);
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -818,4 +919,37 @@ extern "C" int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk,
   if (d_state == 128)
     return run_dda<128, false>(v, gy, bk, cq, weight, cum, state_in, state_cot_rev, da, batch, seq_len, heads, groups, status, st);
   return (int)cudaErrorInvalidValue;
+}
+
+extern "C" int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void* gy, const float* dt, const float* da,
+                                  const float* a_param, const float* d_skip, void* dx, float* ddt, float* dd, int batch,
+                                  int seq_len, int seq_pad, int heads, int is_bf16, cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (batch <= 0 || seq_len <= 0 || seq_pad < seq_len || heads <= 0) return (int)cudaErrorInvalidValue;
+  const int64_t rows = (int64_t)batch * seq_len * heads;
+  const unsigned blocks = (unsigned)((rows + 7) / 8);
+  if (is_bf16)
+    bwd_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(dx_rev, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gy, dt, da, a_param,
+                                                            d_skip, (__nv_bfloat16*)dx, ddt, dd, rows, seq_len, seq_pad, heads);
+  else
+    bwd_finish_kernel<float><<<blocks, 256, 0, st>>>(dx_rev, (const float*)x, (const float*)gy, dt, da, a_param, d_skip, (float*)dx, ddt,
+                                                    dd, rows, seq_len, seq_pad, heads);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_ssd_group_sum(const void* y_bf16, const float* w, void* out, int batch, int seq_len, int seq_pad, int heads,
+                                 int groups, int n, int width, int reversed, int out_is_bf16, cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (batch <= 0 || seq_len <= 0 || seq_pad < seq_len || heads <= 0 || groups <= 0 || heads % groups != 0 || n <= 0 || n % 2 != 0 ||
+      width < n)
+    return (int)cudaErrorInvalidValue;
+  const int64_t total = (int64_t)batch * seq_len * groups * (n / 2);
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (out_is_bf16)
+    group_sum_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)y_bf16, w, (__nv_bfloat16*)out, total, seq_len, seq_pad,
+                                                           heads, groups, n, width, reversed);
+  else
+    group_sum_kernel<float><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)y_bf16, w, (float*)out, total, seq_len, seq_pad, heads, groups,
+                                                   n, width, reversed);
+  return (int)cudaGetLastError();
 }

@@ -129,10 +129,52 @@ def decay_grad_torch(v, gy, bk, cq, a, weight, *, states_in=None, states_cot_rev
     return da
 
 
+def _finish_torch(dx_rev, x, gy, dt, da, A, D):
+    """dx = dt dX + D gy, ddt = da A + dX . x, dD = sum gy . x with dX = dx_rev flipped back in time (PyTorch form)."""
+    seqlen = x.shape[1]
+    dX = dx_rev.flip(1)[:, :seqlen].float()
+    dx = dt[..., None] * dX
+    ddt = da[:, :seqlen] * A + (dX * x).sum(-1)
+    dD = None
+    if D is not None:
+        dx = dx + D.float()[None, None, :, None] * gy
+        dD = (gy.float() * x).sum((0, 1, 3))
+    return dx, ddt, dD
+
+
+def _group_sum_torch(y, w, seqlen, groups, n, reversed_time):
+    """[b, lp, h, width] -> [b, l, g, n]: sum over the heads of a group of w[b, l, h] * y[..., :n] (PyTorch form)."""
+    b, _, h, width = y.shape
+    yy = (y.flip(1) if reversed_time else y)[:, :seqlen].reshape(b, seqlen, groups, h // groups, width)[..., :n]
+    if w is not None:
+        yy = yy * w.reshape(b, seqlen, groups, h // groups, 1)
+    return yy.sum(3, dtype=torch.float32)
+
+
 class KernelScans:
     """The sm_100a kernels as the backend of ``ssd_backward`` / ``siso_core_backward``."""
     scan = staticmethod(scan_generic)
     decay_grad = staticmethod(decay_grad)
+
+    @staticmethod
+    def finish(dx_rev, x, gy, dt, da, A, D):
+        from .dispatch import KERNEL_LAUNCHES
+
+        if x.dtype not in (torch.bfloat16, torch.float32) or not hasattr(ext(), "ssd_bwd_finish"):
+            return _finish_torch(dx_rev, x, gy, dt, da, A, D)
+        KERNEL_LAUNCHES["count"] += 1
+        dx, ddt, dD = ext().ssd_bwd_finish(dx_rev.contiguous(), x.contiguous(), gy.to(x.dtype).contiguous(), dt.contiguous(), da,
+                                           A.contiguous(), None if D is None else D.float().contiguous())
+        return dx, ddt, (dD if D is not None else None)
+
+    @staticmethod
+    def group_sum(y, w, seqlen, groups, n, reversed_time):
+        from .dispatch import KERNEL_LAUNCHES
+
+        if y.dtype != torch.bfloat16 or n % 2 or not hasattr(ext(), "ssd_group_sum"):
+            return _group_sum_torch(y, w, seqlen, groups, n, reversed_time)
+        KERNEL_LAUNCHES["count"] += 1
+        return ext().ssd_group_sum(y.contiguous(), None if w is None else w.contiguous(), seqlen, groups, n, bool(reversed_time), False)
 
 
 class TorchScans:
@@ -143,6 +185,8 @@ class TorchScans:
         return (*scan_generic_torch(v, bk, cq, a, weight, init, strict=strict, per_head=per_head), None)
 
     decay_grad = staticmethod(decay_grad_torch)
+    finish = staticmethod(_finish_torch)
+    group_sum = staticmethod(_group_sum_torch)
 
 
 def _shift_reverse(a):
@@ -182,13 +226,12 @@ def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, ops=KernelScans, fw
     Af = A.float()
     a = dtf * Af
     a_rev = _shift_reverse(a)
-    Bh, Ch = Bf.repeat_interleave(rep, dim=2), Cf.repeat_interleave(rep, dim=2)       # [b, l, h, n]
     nv = max(n // 64, 2)                                                               # virtual heads per head (even)
     gfin = None if gfinal is None else gfinal.float()
+    gy_r, x_r, B_r, C_r = gyf.flip(1), xf.flip(1), Bf.flip(1), Cf.flip(1)              # time-reversed operands, flipped once
 
     # 1. dX (before the dt factor), the gradient of the initial state, the state cotangents at the chunk boundaries
-    y1, fin1, rev_states = ops.scan(gyf.flip(1), Cf.flip(1), Bf.flip(1), a_rev, None, gfin)
-    dX = y1.flip(1)
+    y1, fin1, rev_states = ops.scan(gy_r, C_r, B_r, a_rev, None, gfin)
     d_init = fin1 * torch.exp(a[:, 0])[..., None, None] if init is not None else None
     da = ops.decay_grad(xf, gyf, Bf, Cf, a, dtf, states_in=fwd_states, states_cot_rev=rev_states, init=init, gfinal=gfin)
 
@@ -199,25 +242,18 @@ def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, ops=KernelScans, fw
         return t.reshape(bsz, h * nv, 64, p)
 
     rep_v = lambda t: t.repeat_interleave(nv, dim=2)  # noqa: E731
-    # 2. dC per head
-    y2 = ops.scan(_blocks(Bh, nv), xf, gyf, rep_v(a), rep_v(dtf), None if init is None else state_blocks(init), out_f32=False)[0]
-    dCh = y2.reshape(bsz, seqlen + pad, h, nv * 64)[..., :n]
-    # 3. dB per head
-    y3 = ops.scan(_blocks(Ch, nv).flip(1), gyf.flip(1), xf.flip(1), rep_v(a_rev), None, None if gfin is None else state_blocks(gfin),
-                  out_f32=False)[0]
-    dBh = y3.flip(1).reshape(bsz, seqlen + pad, h, nv * 64)[..., :n]
+    # 2. dC per head (forward time), 3. dB / dt per head (reversed time); the state axis as nv virtual heads of width 64
+    y2 = ops.scan(_blocks(Bf.repeat_interleave(rep, dim=2), nv), xf, gyf, rep_v(a), rep_v(dtf),
+                  None if init is None else state_blocks(init), out_f32=False)[0]
+    y3 = ops.scan(_blocks(C_r.repeat_interleave(rep, dim=2), nv), gy_r, x_r, rep_v(a_rev), None,
+                  None if gfin is None else state_blocks(gfin), out_f32=False)[0]
 
-    ddt = da * Af + (dX * xf).sum(-1)
-    dA = (da * dtf).sum((0, 1))
-    dx = dtf[..., None] * dX
-    dD = None
-    if D is not None:
-        dx = dx + D.float()[None, None, :, None] * gyf
-        dD = (gyf.float() * xf).sum((0, 1, 3))
-    dB = (dBh.reshape(bsz, seqlen + pad, g, rep, n) * dtf.reshape(bsz, seqlen + pad, g, rep, 1)).sum(3)
-    dC = dCh.reshape(bsz, seqlen + pad, g, rep, n).sum(3, dtype=torch.float32)
-    cut = slice(0, seqlen)
-    return dx[:, cut], ddt[:, cut], dA, dB[:, cut], dC[:, cut], dD, d_init
+    dt_real = dt.float()
+    dx, ddt, dD = ops.finish(y1, x, gy, dt_real, da, Af, D)
+    dC = ops.group_sum(y2.reshape(bsz, seqlen + pad, h, nv * 64), None, seqlen, g, n, False)
+    dB = ops.group_sum(y3.reshape(bsz, seqlen + pad, h, nv * 64), dt_real, seqlen, g, n, True)
+    dA = (da[:, :seqlen] * dt_real).sum((0, 1))
+    return dx, ddt, dA, dB, dC, dD, d_init
 
 
 class _SSDFunction(torch.autograd.Function):

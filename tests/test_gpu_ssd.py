@@ -65,7 +65,7 @@ def test_generic_scan_matches_its_oracle(strict, per_head, n):
     a = -(torch.rand(b, l, h, device=DEV, generator=gen) * 0.2)
     w = torch.rand(b, l, h, device=DEV, generator=gen) + 0.5
     init = torch.randn(b, h, n, 64, device=DEV, generator=gen) if per_head else torch.randn(b, h, 64, n, device=DEV, generator=gen)
-    y, fin = scan_generic(v, bk, cq, a, w, init, strict=strict, per_head=per_head)
+    y, fin, _ = scan_generic(v, bk, cq, a, w, init, strict=strict, per_head=per_head)
     torch.cuda.synchronize()
     assert ops.ext().kernel_status(v) == 0
     assert y.dtype == torch.float32
