@@ -37,10 +37,12 @@ int lbi_siso_chunk_scan_fwd(const void* v, const void* kr, const void* qr, const
 // v [B*L, H*64] bf16; bk / cq [B*L, G*N] bf16 (or [B*L, H*128] when `per_head`); weight [B, H, L] fp32 or null (w = 1);
 // cum [B, H, L] fp32 in-chunk cumulative sums.  The result goes to `y32` (fp32) when it is set, else to `y` (bf16).
 // States are [p][n] (per_head: [n][p]).  N = 64 or 128 (per_head: 128); heads / groups even unless per_head.
+// Head h reads the 64-column block (h / v_div) * v_mod + h % v_mod of v (1, 1: its own block), so that several heads can
+// share columns of a narrower v matrix without a materialised copy.
 int lbi_ssd_scan_generic(const void* v, const void* bk, const void* cq, const float* weight, const float* cum,
                          const float* d_skip, const float* skip_tok, int strict, const float* init_state, float* states,
                          void* prev, float* final_state, void* y, float* y32, int batch, int seq_len, int heads, int groups,
-                         int d_state, int per_head, int* status, cudaStream_t stream);
+                         int d_state, int per_head, int v_div, int v_mod, int* status, cudaStream_t stream);
 
 // Gradient of the log-decays of that scan: da_u = sum over pairs s < u <= t of e^{c_t - c_s} (cq_t . bk_s) w_s (gy_t . v_s),
 // pairs that reach before the first or past the last token included through `state_in` (the bf16 incoming states of the

@@ -538,15 +538,16 @@ std::tuple<Tensor, Tensor, Tensor> siso_chunk_scan_fwd(const Tensor& v, const Te
 std::tuple<Tensor, Tensor, Tensor> ssd_scan_generic(const Tensor& v, const Tensor& bk, const Tensor& cq, const Tensor& a,
                                             const c10::optional<Tensor>& weight, const c10::optional<Tensor>& d_skip,
                                             const c10::optional<Tensor>& skip_tok, const c10::optional<Tensor>& init_state,
-                                            bool strict, bool per_head, bool out_f32) {
+                                            bool strict, bool per_head, bool out_f32, int64_t v_div, int64_t v_mod) {
   CHECK_BF16(v);
   CHECK_BF16(bk);
   CHECK_BF16(cq);
   CHECK_F32(a);
   c10::cuda::CUDAGuard guard(v.device());
   TORCH_CHECK(v.dim() == 4 && bk.dim() == 4 && cq.sizes() == bk.sizes() && a.dim() == 3, "scan: expected v [B,L,H,64], bk/cq [B,L,G,N], a [B,L,H]");
-  const int64_t batch = v.size(0), seq = v.size(1), heads = v.size(2), hd = v.size(3), groups = bk.size(2), n = bk.size(3);
-  TORCH_CHECK(hd == 64 && a.size(0) == batch && a.size(1) == seq && a.size(2) == heads && bk.size(1) == seq, "scan: shape mismatch");
+  const int64_t batch = v.size(0), seq = v.size(1), heads = a.size(2), hd = v.size(3), groups = bk.size(2), n = bk.size(3);
+  TORCH_CHECK(hd == 64 && a.size(0) == batch && a.size(1) == seq && bk.size(1) == seq, "scan: shape mismatch");
+  TORCH_CHECK(v_div > 0 && v_mod > 0 && v.size(2) == ((heads - 1) / v_div) * v_mod + v_mod, "scan: v has the wrong number of 64-column blocks");
   TORCH_CHECK(!per_head || groups == heads, "scan: per_head wants one bk / cq per head");
   const int64_t chunks = seq / 128;
   auto f32 = v.options().dtype(at::kFloat);
@@ -561,7 +562,7 @@ std::tuple<Tensor, Tensor, Tensor> ssd_scan_generic(const Tensor& v, const Tenso
   Tensor states = torch::empty({batch, chunks, heads, hd, n}, f32);
   Tensor prev = torch::empty({batch, chunks, heads, hd, n}, v.options());
   Tensor final_state = per_head ? torch::empty({batch, heads, n, hd}, f32) : torch::empty({batch, heads, hd, n}, f32);
-  Tensor y = torch::empty(v.sizes(), out_f32 ? f32 : v.options());
+  Tensor y = torch::empty({batch, seq, heads, hd}, out_f32 ? f32 : v.options());
   Tensor st = status_word(v);
   check(lbi_ssd_cumsum(a.data_ptr<float>(), nullptr, ones.data_ptr<float>(), a_t.data_ptr<float>(), cum.data_ptr<float>(), (int)batch,
                        (int)seq, (int)heads, 0, 0.f, 0.f, cur_stream()),
@@ -572,7 +573,7 @@ std::tuple<Tensor, Tensor, Tensor> ssd_scan_generic(const Tensor& v, const Tenso
                              init_state ? init_state->data_ptr<float>() : nullptr, states.data_ptr<float>(), prev.data_ptr(),
                              final_state.data_ptr<float>(), out_f32 ? nullptr : y.data_ptr(),
                              out_f32 ? y.data_ptr<float>() : nullptr, (int)batch, (int)seq, (int)heads, (int)groups, (int)n,
-                             per_head ? 1 : 0, st.data_ptr<int>(), cur_stream()),
+                             per_head ? 1 : 0, (int)v_div, (int)v_mod, st.data_ptr<int>(), cur_stream()),
         "ssd_scan_generic");
   return {y, final_state, prev};
 }

@@ -114,6 +114,7 @@ struct SmemState {
 
 struct StateParams {
   int seq_len, heads, groups, chunks;
+  int v_div, v_mod;     // head h reads the 64-column block (h / v_div) * v_mod + h % v_mod of the v matrix (1, 1: block h)
   const float* dt;      // [B, H, L_total]
   const float* cum;     // [B, H, L_total]
   float* states;        // [B, C, H, 64, N]
@@ -151,8 +152,8 @@ __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_const
   if (warp == 4) {
     if (lane == 0) {
       mbar_arrive_expect_tx(&s.bar_full, ((PH ? 1 : 2) + N / 64) * PANEL);
-      tma_load_2d(s.xs[0], &map_x, &s.bar_full, h0 * P, row0);
-      if (!PH) tma_load_2d(s.xs[1], &map_x, &s.bar_full, (h0 + 1) * P, row0);
+      tma_load_2d(s.xs[0], &map_x, &s.bar_full, ((h0 / p.v_div) * p.v_mod + h0 % p.v_mod) * P, row0);
+      if (!PH) tma_load_2d(s.xs[1], &map_x, &s.bar_full, (((h0 + 1) / p.v_div) * p.v_mod + (h0 + 1) % p.v_mod) * P, row0);
       for (int q = 0; q < N / 64; ++q) tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, row0);
       bool ok = mbar_wait(&s.bar_scaled, 0, abortp, p.status, 51);
       if (ok) {
@@ -252,6 +253,7 @@ struct SmemScan {
 
 struct ScanParams {
   int seq_len, heads, groups, chunks;
+  int v_div, v_mod;       // as in StateParams
   const float* dt;        // null: weight 1 (already folded into B)
   const float* cum;
   const float* d_skip;    // [H] or null
@@ -305,7 +307,7 @@ __global__ void __launch_bounds__(THREADS) chunk_scan_kernel(const __grid_consta
       }
       if (PH)  // incoming state stored [n][p]: one 128-row tile
         tma_load_2d(s.pv[0], &map_prev, &s.bar_full, 0, (int)((((int64_t)b * p.chunks + c) * p.heads + h) * N));
-      tma_load_2d(s.xt, &map_x, &s.bar_full, h * P, row0);
+      tma_load_2d(s.xt, &map_x, &s.bar_full, ((h / p.v_div) * p.v_mod + h % p.v_mod) * P, row0);
       const uint64_t kmajor0 = make_smem_desc(0, 16, 1024), mnmajor0 = make_smem_desc(0, PANEL, 1024);
       const uint32_t ct16 = smem_u32(s.ct[0]) >> 4, bw16 = smem_u32(s.bw[0]) >> 4, xt16 = smem_u32(s.xt) >> 4,
                      pv16 = smem_u32(s.pv[0]) >> 4;
@@ -775,11 +777,13 @@ static int set_smem(K kernel, size_t bytes) {
 template <int N, bool PH>
 static int run(const void* x, const void* bm, const void* cm, const float* dt, const float* cum, const float* d_skip,
                const float* skip_tok, int strict, const float* init_state, float* states, void* prev, float* final_state,
-               void* y, float* y32, int batch, int seq_len, int heads, int groups, int* status, cudaStream_t st) {
+               void* y, float* y32, int batch, int seq_len, int heads, int groups, int* status, cudaStream_t st, int v_div = 1,
+               int v_mod = 1) {
   const int chunks = seq_len / L;
   const int64_t rows = (int64_t)batch * seq_len;
   CUtensorMap mx, mb, mc, mp;
-  int rc = make_map(&mx, x, rows, (int64_t)heads * P, L);
+  const int v_blocks = ((heads - 1) / v_div) * v_mod + v_mod;   // 64-column blocks of the v matrix
+  int rc = make_map(&mx, x, rows, (int64_t)v_blocks * P, L);
   if (rc) return rc;
   rc = make_map(&mb, bm, rows, (int64_t)(PH ? heads : groups) * N, L);
   if (rc) return rc;
@@ -789,7 +793,7 @@ static int run(const void* x, const void* bm, const void* cm, const float* dt, c
           : make_map(&mp, prev, (int64_t)batch * chunks * heads * P, N, P);
   if (rc) return rc;
   {
-    StateParams p{seq_len, heads, groups, chunks, dt, cum, states, status};
+    StateParams p{seq_len, heads, groups, chunks, v_div, v_mod, dt, cum, states, status};
     const size_t smem = sizeof(SmemState<N>) + 1024;
     rc = set_smem(chunk_state_kernel<N, PH>, smem);
     if (rc) return rc;
@@ -806,7 +810,7 @@ static int run(const void* x, const void* bm, const void* cm, const float* dt, c
     if (rc) return rc;
   }
   {
-    ScanParams p{seq_len, heads, groups, chunks, dt, cum, d_skip, skip_tok, strict, (__nv_bfloat16*)y, y32, status};
+    ScanParams p{seq_len, heads, groups, chunks, v_div, v_mod, dt, cum, d_skip, skip_tok, strict, (__nv_bfloat16*)y, y32, status};
     const size_t smem = sizeof(SmemScan<N>) + 1024;
     rc = set_smem(chunk_scan_kernel<N, PH>, smem);
     if (rc) return rc;
@@ -886,21 +890,23 @@ extern "C" int lbi_siso_chunk_scan_fwd(const void* v, const void* kr, const void
 extern "C" int lbi_ssd_scan_generic(const void* v, const void* bk, const void* cq, const float* weight, const float* cum,
                                     const float* d_skip, const float* skip_tok, int strict, const float* init_state,
                                     float* states, void* prev, float* final_state, void* y, float* y32, int batch, int seq_len,
-                                    int heads, int groups, int d_state, int per_head, int* status, cudaStream_t st) {
+                                    int heads, int groups, int d_state, int per_head, int v_div, int v_mod, int* status,
+                                    cudaStream_t st) {
   using namespace lbi::ssd;
-  if (seq_len % L != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * seq_len >= (1ll << 31)) return (int)cudaErrorInvalidValue;
+  if (seq_len % L != 0 || batch <= 0 || heads <= 0 || (int64_t)batch * seq_len >= (1ll << 31) || v_div <= 0 || v_mod <= 0)
+    return (int)cudaErrorInvalidValue;
   if (per_head) {
     if (d_state != 128) return (int)cudaErrorInvalidValue;
     return run<128, true>(v, bk, cq, weight, cum, d_skip, skip_tok, strict, init_state, states, prev, final_state, y, y32, batch,
-                          seq_len, heads, heads, status, st);
+                          seq_len, heads, heads, status, st, v_div, v_mod);
   }
   if (groups <= 0 || heads % groups != 0 || (heads / groups) % 2 != 0) return (int)cudaErrorInvalidValue;
   if (d_state == 64)
     return run<64, false>(v, bk, cq, weight, cum, d_skip, skip_tok, strict, init_state, states, prev, final_state, y, y32, batch,
-                          seq_len, heads, groups, status, st);
+                          seq_len, heads, groups, status, st, v_div, v_mod);
   if (d_state == 128)
     return run<128, false>(v, bk, cq, weight, cum, d_skip, skip_tok, strict, init_state, states, prev, final_state, y, y32, batch,
-                           seq_len, heads, groups, status, st);
+                           seq_len, heads, groups, status, st, v_div, v_mod);
   return (int)cudaErrorInvalidValue;
 }
 

@@ -71,16 +71,19 @@ def scan_generic_torch(v, bk, cq, a, weight=None, init=None, strict=False, per_h
     return torch.stack(ys, dim=1), (state.transpose(2, 3) if per_head else state)
 
 
-def scan_generic(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False, out_f32=True):
+def scan_generic(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False, out_f32=True, v_div=1, v_mod=1):
     """The kernels' scan operator with free operand roles; bf16 operands.  ``seq_len % 128 == 0``.
 
-    Returns (y in fp32 or bf16, final state, bf16 incoming state of every chunk [b, l / 128, h, 64, n])."""
+    The number of heads is that of ``a``; head h reads the 64-column block ``(h // v_div) * v_mod + h % v_mod`` of ``v``
+    (several heads can share columns of a narrower v).  Returns (y in fp32 or bf16, final state, bf16 incoming state of
+    every chunk [b, l / 128, h, 64, n])."""
     from .dispatch import KERNEL_LAUNCHES
 
     bf = torch.bfloat16
     out = ext().ssd_scan_generic(v.to(bf).contiguous(), bk.to(bf).contiguous(), cq.to(bf).contiguous(), a.float().contiguous(),
                                  None if weight is None else weight.float().contiguous(), None, None,
-                                 None if init is None else init.float().contiguous(), bool(strict), bool(per_head), bool(out_f32))
+                                 None if init is None else init.float().contiguous(), bool(strict), bool(per_head), bool(out_f32),
+                                 int(v_div), int(v_mod))
     KERNEL_LAUNCHES["count"] += 4
     return out
 
@@ -181,7 +184,10 @@ class TorchScans:
     """fp32 PyTorch statements of the same operators (CPU-runnable oracle)."""
 
     @staticmethod
-    def scan(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False, out_f32=True):
+    def scan(v, bk, cq, a, weight=None, init=None, strict=False, per_head=False, out_f32=True, v_div=1, v_mod=1):
+        if (v_div, v_mod) != (1, 1):
+            heads = torch.arange(a.shape[2], device=v.device)
+            v = v[:, :, (heads // v_div) * v_mod + heads % v_mod]
         return (*scan_generic_torch(v, bk, cq, a, weight, init, strict=strict, per_head=per_head), None)
 
     decay_grad = staticmethod(decay_grad_torch)
@@ -243,10 +249,12 @@ def ssd_backward(x, dt, A, B, C, D, init, final, gy, gfinal, ops=KernelScans, fw
 
     rep_v = lambda t: t.repeat_interleave(nv, dim=2)  # noqa: E731
     # 2. dC per head (forward time), 3. dB / dt per head (reversed time); the state axis as nv virtual heads of width 64
-    y2 = ops.scan(_blocks(Bf.repeat_interleave(rep, dim=2), nv), xf, gyf, rep_v(a), rep_v(dtf),
-                  None if init is None else state_blocks(init), out_f32=False)[0]
-    y3 = ops.scan(_blocks(C_r.repeat_interleave(rep, dim=2), nv), gy_r, x_r, rep_v(a_rev), None,
-                  None if gfin is None else state_blocks(gfin), out_f32=False)[0]
+    # (virtual head h * nv + j reads block j of its group's B / C: no per-head copies of B and C are made)
+    as_blocks = lambda t: t.reshape(bsz, seqlen + pad, g * (n // 64), 64)  # noqa: E731
+    y2 = ops.scan(as_blocks(Bf), xf, gyf, rep_v(a), rep_v(dtf), None if init is None else state_blocks(init), out_f32=False,
+                  v_div=nv * rep, v_mod=n // 64)[0]
+    y3 = ops.scan(as_blocks(C_r), gy_r, x_r, rep_v(a_rev), None, None if gfin is None else state_blocks(gfin), out_f32=False,
+                  v_div=nv * rep, v_mod=n // 64)[0]
 
     dt_real = dt.float()
     dx, ddt, dD = ops.finish(y1, x, gy, dt_real, da, Af, D)
