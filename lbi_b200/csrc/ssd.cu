@@ -686,27 +686,41 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const float* __restrict
                                                          const T* __restrict__ gy, const float* __restrict__ dt,
                                                          const float* __restrict__ da, const float* __restrict__ a_param,
                                                          const float* __restrict__ d_skip, T* __restrict__ dx,
-                                                         float* __restrict__ ddt, float* __restrict__ dd, int64_t rows,
+                                                         float* __restrict__ ddt, float* __restrict__ dd, int64_t tokens,
                                                          int seq_len, int seq_pad, int heads) {
-  // rows = batch * seq_len * heads; dx_rev is [batch, seq_pad, heads, 64] in reversed time; dt [b, l, h]; da [b, h, seq_pad]
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const int h = (int)(row % heads);
-  const int64_t bl = row / heads;
-  const int l = (int)(bl % seq_len);
-  const int64_t b = bl / seq_len;
-  const int64_t rrow = (b * seq_pad + (seq_pad - 1 - l)) * heads + h;
-  const float2 g = *reinterpret_cast<const float2*>(dx_rev + rrow * P + lane * 2);
-  const float2 xv = ld2<T>(x + row * P + lane * 2);
-  const float2 gv = ld2<T>(gy + row * P + lane * 2);
-  const float dtv = dt[row], dsk = d_skip ? d_skip[h] : 0.f;
-  st2<T>(dx + row * P + lane * 2, dtv * g.x + dsk * gv.x, dtv * g.y + dsk * gv.y);
-  const float dot = warp_sum(g.x * xv.x + g.y * xv.y);
-  const float gx = warp_sum(gv.x * xv.x + gv.y * xv.y);
-  if (lane == 0) {
-    ddt[row] = da[(b * heads + h) * seq_pad + l] * a_param[h] + dot;
-    if (dd) atomicAdd(dd + h, gx);
+  // grid (ceil(tokens / 128), heads): a block owns one head and 128 tokens (16 per warp), so that the dD sum leaves as one
+  // atomic per block.  dx_rev is [batch, seq_pad, heads, 64] in reversed time; dt [b, l, h]; da [b, h, seq_pad].
+  __shared__ float warp_dd[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = blockIdx.y;
+  const float a_h = a_param[h], dsk = d_skip ? d_skip[h] : 0.f;
+  float dd_acc = 0.f;
+  for (int i = 0; i < 16; ++i) {
+    const int64_t bl = (int64_t)blockIdx.x * 128 + warp * 16 + i;
+    if (bl >= tokens) break;
+    const int l = (int)(bl % seq_len);
+    const int64_t b = bl / seq_len;
+    const int64_t row = bl * heads + h;
+    const int64_t rrow = (b * seq_pad + (seq_pad - 1 - l)) * heads + h;
+    const float2 g = *reinterpret_cast<const float2*>(dx_rev + rrow * P + lane * 2);
+    const float2 xv = ld2<T>(x + row * P + lane * 2);
+    const float2 gv = ld2<T>(gy + row * P + lane * 2);
+    const float dtv = dt[row];
+    st2<T>(dx + row * P + lane * 2, dtv * g.x + dsk * gv.x, dtv * g.y + dsk * gv.y);
+    const float dot = warp_sum(g.x * xv.x + g.y * xv.y);
+    dd_acc += gv.x * xv.x + gv.y * xv.y;
+    if (lane == 0) ddt[row] = da[(b * heads + h) * seq_pad + l] * a_h + dot;
+  }
+  if (dd) {
+    dd_acc = warp_sum(dd_acc);
+    if (lane == 0) warp_dd[warp] = dd_acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += warp_dd[w];
+      atomicAdd(dd + h, t);
+    }
   }
 }
 
@@ -932,14 +946,14 @@ extern "C" int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void
                                   int seq_len, int seq_pad, int heads, int is_bf16, cudaStream_t st) {
   using namespace lbi::ssd;
   if (batch <= 0 || seq_len <= 0 || seq_pad < seq_len || heads <= 0) return (int)cudaErrorInvalidValue;
-  const int64_t rows = (int64_t)batch * seq_len * heads;
-  const unsigned blocks = (unsigned)((rows + 7) / 8);
+  const int64_t tokens = (int64_t)batch * seq_len;
+  const dim3 blocks((unsigned)((tokens + 127) / 128), (unsigned)heads);
   if (is_bf16)
     bwd_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(dx_rev, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gy, dt, da, a_param,
-                                                            d_skip, (__nv_bfloat16*)dx, ddt, dd, rows, seq_len, seq_pad, heads);
+                                                            d_skip, (__nv_bfloat16*)dx, ddt, dd, tokens, seq_len, seq_pad, heads);
   else
     bwd_finish_kernel<float><<<blocks, 256, 0, st>>>(dx_rev, (const float*)x, (const float*)gy, dt, da, a_param, d_skip, (float*)dx, ddt,
-                                                    dd, rows, seq_len, seq_pad, heads);
+                                                    dd, tokens, seq_len, seq_pad, heads);
   return (int)cudaGetLastError();
 }
 

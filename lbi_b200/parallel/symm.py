@@ -29,6 +29,20 @@ from .comm import CollectiveComm
 _SLOT_BARRIER, _SLOT_SCAN, _SLOT_NORM, _SLOT_HANDOFF = 0, 1, 2, 3
 
 
+_GUARD_BYTES = 256          # canary region before and after every symmetric buffer (keeps 256-byte alignment)
+_GUARD_BYTE = 0xA5
+
+
+class _GuardedHandle:
+    """A rendezvous handle seen through the guard offset: peers address the payload, not the canary in front of it."""
+
+    def __init__(self, handle, offset: int) -> None:
+        self._handle = handle
+        self.buffer_ptrs = [int(p) + offset for p in handle.buffer_ptrs]
+        mc = getattr(handle, "multicast_ptr", 0)
+        self.multicast_ptr = int(mc) + offset if mc else 0
+
+
 class SymmComm(CollectiveComm):
     name = "symm"
 
@@ -61,9 +75,29 @@ class SymmComm(CollectiveComm):
 
     # ------------------------------------------------------------------ symmetric allocation
     def _alloc(self, numel: int, dtype: torch.dtype):
-        t = self._symm.empty(int(numel), dtype=dtype, device=self.device)
-        handle = self._symm.rendezvous(t, self._group)
-        return t, handle
+        """Symmetric buffer of ``numel`` elements with a canary region on both sides (peers write into these buffers with
+        plain stores; a store that runs past an end lands in a canary and ``check_canaries`` reports it)."""
+        item = torch.empty((), dtype=dtype).element_size()
+        guard = _GUARD_BYTES // item
+        payload = -(-int(numel) * item // _GUARD_BYTES) * _GUARD_BYTES // item     # rounded up: the rear canary stays aligned
+        full = self._symm.empty(payload + 2 * guard, dtype=dtype, device=self.device)
+        handle = self._symm.rendezvous(full, self._group)
+        raw = full.view(torch.uint8)
+        raw[:_GUARD_BYTES] = _GUARD_BYTE
+        raw[_GUARD_BYTES + payload * item:] = _GUARD_BYTE
+        if not hasattr(self, "_guarded"):
+            self._guarded = []
+        self._guarded.append((raw, payload * item))
+        return full[guard : guard + int(numel)], _GuardedHandle(handle, _GUARD_BYTES)
+
+    def check_canaries(self) -> list[int]:
+        """Indices (allocation order) of the symmetric buffers whose front or rear canary was overwritten."""
+        bad = []
+        for i, (raw, nbytes) in enumerate(getattr(self, "_guarded", [])):
+            front, rear = raw[:_GUARD_BYTES], raw[_GUARD_BYTES + nbytes:]
+            if not (bool((front == _GUARD_BYTE).all()) and bool((rear == _GUARD_BYTE).all())):
+                bad.append(i)
+        return bad
 
     def _table(self, handle, byte_offset: int = 0) -> torch.Tensor:
         return torch.tensor([int(p) + byte_offset for p in handle.buffer_ptrs], dtype=torch.int64, device=self.device)
@@ -73,8 +107,7 @@ class SymmComm(CollectiveComm):
         t, handle = self._alloc(numel, dtype)
         t.zero_()
         self._handle_keepalive.append(handle)
-        mc = int(handle.multicast_ptr) if getattr(handle, "multicast_ptr", 0) else 0
-        return t, self._table(handle), mc
+        return t, self._table(handle), handle.multicast_ptr
 
     # ------------------------------------------------------------------ barrier
     def _setup_barrier(self) -> None:

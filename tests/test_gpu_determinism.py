@@ -1,0 +1,86 @@
+"""Run-to-run bitwise equality of the kernels that use no floating-point atomics.
+
+With no race detector available on the build machines, a kernel that reads a tile before its barrier completed, or
+that lets two warps write one word, shows up here as a result that changes between two runs on the same inputs.
+(The dD reduction of the SSD backward tail and split-K GEMM accumulate with atomics / TMA reduce-adds and are left out.)
+"""
+import pytest
+import torch
+
+from lbi_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _twice(fn):
+    a = fn()
+    torch.cuda.synchronize()
+    b = fn()
+    torch.cuda.synchronize()
+    a = a if isinstance(a, (tuple, list)) else (a,)
+    b = b if isinstance(b, (tuple, list)) else (b,)
+    for i, (x, y) in enumerate(zip(a, b)):
+        if x is None:
+            continue
+        assert torch.equal(x, y), f"result {i} differs between two runs: max diff {(x.float() - y.float()).abs().max().item():.3e}"
+
+
+def test_gemm_and_elementwise_kernels_repeat_bitwise():
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn(1024, 512, device=DEV, generator=g).bfloat16()
+    w = torch.randn(768, 512, device=DEV, generator=g).bfloat16()
+    dy = torch.randn(1024, 768, device=DEV, generator=g).bfloat16()
+    _twice(lambda: ops.linear_fwd(x, w))
+    _twice(lambda: ops.linear_dgrad(dy, w))
+    weight = torch.rand(512, device=DEV, generator=g) + 0.5
+    normed, stream, rstd = ops.add_rmsnorm_fwd(x, None, weight, 1e-5, torch.bfloat16)
+    _twice(lambda: ops.rmsnorm_bwd(x, stream, rstd, weight))
+    u = torch.randn(1024, 1024, device=DEV, generator=g).bfloat16()
+    _twice(lambda: ops.swiglu_fwd(u))
+    _twice(lambda: ops.swiglu_bwd(x, u))
+
+
+def test_scan_kernels_repeat_bitwise():
+    from lbi_b200.ops.ssd import _shift_reverse, decay_grad, scan_generic, ssd_chunk_scan_cuda
+
+    g = torch.Generator(device=DEV).manual_seed(1)
+    b, l, h, n = 2, 512, 4, 128
+    x = torch.randn(b, l, h, 64, device=DEV, generator=g).bfloat16()
+    gy = torch.randn(b, l, h, 64, device=DEV, generator=g).bfloat16()
+    B = (torch.randn(b, l, 2, n, device=DEV, generator=g) * 0.3).bfloat16()
+    C = (torch.randn(b, l, 2, n, device=DEV, generator=g) * 0.3).bfloat16()
+    dt = torch.rand(b, l, h, device=DEV, generator=g) * 0.1 + 0.01
+    A = -(torch.rand(h, device=DEV, generator=g) + 0.5)
+    _twice(lambda: ssd_chunk_scan_cuda(x, dt, A, B, C, return_final_state=True))
+    a = dt * A
+    _twice(lambda: scan_generic(x, B, C, a, dt, None))
+    fwd = scan_generic(x, B, C, a, dt, None)[2]
+    rev = scan_generic(gy.flip(1), C.flip(1), B.flip(1), _shift_reverse(a), None, None)[2]
+    _twice(lambda: decay_grad(x, gy, B, C, a, dt, states_in=fwd, states_cot_rev=rev).contiguous())
+
+    mats = torch.randn(2, 6, 64, 64, device=DEV, generator=g) / 8
+    offs = torch.randn(2, 6, 64, device=DEV, generator=g)
+    _twice(lambda: ops.affine_suffix_scan(mats, offs))
+    _twice(lambda: ops.suffix_scan_pullbacks(mats))
+
+
+def test_norm_and_interface_kernels_repeat_bitwise():
+    from lbi_b200.backbones.norms import gated_rms_norm
+    from lbi_b200.interfaces import vector_mlp as vm
+
+    torch.manual_seed(2)
+    x = torch.randn(4, 130, 256, device=DEV).bfloat16().requires_grad_(True)
+    z = torch.randn(4, 130, 256, device=DEV).bfloat16().requires_grad_(True)
+    w = (torch.rand(256, device=DEV) + 0.5).requires_grad_(True)
+    gy = torch.randn(4, 130, 256, device=DEV).bfloat16()
+
+    def fwd_bwd():
+        y = gated_rms_norm(x, w, eps=1e-5, z=z, norm_before_gate=False, group_size=64)
+        return (y.detach(), *torch.autograd.grad(y, (x, z, w), gy))
+
+    _twice(fwd_bwd)
+    head = vm.VectorMLPHead(160, 96, hidden_dim=128).to(DEV)
+    s, g = torch.randn(3, 160, device=DEV), torch.randn(3, 40, 96, device=DEV)
+    with torch.no_grad():
+        _twice(lambda: vm.head_input_jacobian_t(head, s, g))

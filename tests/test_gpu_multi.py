@@ -54,8 +54,10 @@ def _worker(rank, world, port, axis, plane, out_dir):
         losses = [engine.step(ids.cuda(), tgt.cuda()) for _ in range(2)]
         torch.cuda.synchronize()
         status = ops.ext().kernel_status(losses[0])
+        canaries = comm.check_canaries() if plane == "symm" else []
         if rank == 0:
-            torch.save({"params": engine.flat.shadow.float().cpu(), "losses": [float(x) for x in losses], "status": int(status)},
+            torch.save({"params": engine.flat.shadow.float().cpu(), "losses": [float(x) for x in losses], "status": int(status),
+                        "canaries": canaries},
                        os.path.join(out_dir, f"{plane}.pt"))
     finally:
         dist.barrier()
@@ -72,6 +74,7 @@ def test_peer_memory_plane_matches_collectives(tmp_path, axis):
         mp.spawn(_worker, args=(2, _free_port(), axis, plane, str(tmp_path)), nprocs=2, join=True)
     a, b = torch.load(tmp_path / "collective.pt"), torch.load(tmp_path / "symm.pt")
     assert b["status"] == 0, "a bounded wait in a peer-memory kernel ran out"
+    assert b["canaries"] == [], f"a peer store ran past the end of symmetric buffer(s) {b['canaries']}"
     for x, y in zip(a["losses"], b["losses"]):
         assert abs(x - y) < 2e-2 * max(1.0, abs(x))
     n = min(a["params"].numel(), b["params"].numel())
