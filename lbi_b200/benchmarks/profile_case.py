@@ -7,6 +7,7 @@
     python -m lbi_b200.benchmarks.profile_case --case scan      # suffix scan B 8, K 32, R 256
     python -m lbi_b200.benchmarks.profile_case --case attn_fwd  # causal attention forward B 4, H 16, T 4096
     python -m lbi_b200.benchmarks.profile_case --case ssd       # Mamba-2 SSD forward B 2, L 8192, 24 heads, d_state 64
+    python -m lbi_b200.benchmarks.profile_case --case ssd_bwd   # SSD forward + backward (permuted scans, decay gradient, tails)
 
 Each case holds well under 2 GB on the device, touches more than the 126 MB L2, launches the kernel of interest a
 handful of times and exits.  Typical capture:
@@ -24,7 +25,7 @@ from lbi_b200 import ops
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd"])
+    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd", "ssd_bwd"])
     ap.add_argument("--repeats", type=int, default=2)
     args = ap.parse_args()
     dev = "cuda"
@@ -85,6 +86,20 @@ def main() -> None:
         with torch.no_grad():
             for _ in range(args.repeats):
                 ssd_chunk_scan_cuda(x, dt, a, bm, cm, D=torch.ones(h, device=dev))
+    elif args.case == "ssd_bwd":
+        from lbi_b200.ops.ssd import ssd_chunk_scan_cuda
+
+        b, l, h, n = 2, 8192, 24, 128
+        x = torch.randn(b, l, h, 64, device=dev).bfloat16().requires_grad_(True)
+        dt = (torch.rand(b, l, h, device=dev) * 0.1 + 0.001).requires_grad_(True)
+        a = (-(torch.rand(h, device=dev) * 8 + 1)).requires_grad_(True)
+        bm = (torch.randn(b, l, 1, n, device=dev) * 0.5).bfloat16().requires_grad_(True)
+        cm = (torch.randn(b, l, 1, n, device=dev) * 0.5).bfloat16().requires_grad_(True)
+        d = torch.ones(h, device=dev, requires_grad=True)
+        gy = torch.randn(b, l, h, 64, device=dev).bfloat16()
+        for _ in range(args.repeats):
+            y = ssd_chunk_scan_cuda(x, dt, a, bm, cm, D=d)
+            torch.autograd.grad(y, (x, dt, a, bm, cm, d), gy)
     else:
         mats = torch.randn(8, 32, 256, 256, device=dev) / 16
         for _ in range(args.repeats):
