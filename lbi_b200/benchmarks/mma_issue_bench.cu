@@ -18,6 +18,7 @@ __device__ __forceinline__ void mma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem
       : "memory");
 }
 
+template <bool A_TMEM>
 __global__ void __launch_bounds__(128, 1) k(Cfg c, int iters, long long* out, int* status) {
   extern __shared__ uint8_t raw[];
   uint8_t* sm = (uint8_t*)(((uintptr_t)raw + 1023) & ~uintptr_t(1023));
@@ -43,7 +44,7 @@ __global__ void __launch_bounds__(128, 1) k(Cfg c, int iters, long long* out, in
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
       for (int kk = 0; kk < 4; ++kk) {
-        if (c.a_tmem) mma_bf16_a_tmem(tmem + warp * 256, tmem + 480 + kk * 8, db0 + bstep * kk, idesc, 1);
+        if (A_TMEM) mma_bf16_a_tmem(tmem + warp * 256, tmem + 480 + kk * 8, db0 + bstep * kk, idesc, 1);
         else mma_bf16(tmem + warp * 256, da0 + astep * kk, db0 + bstep * kk, idesc, 1);
       }
     }
@@ -61,13 +62,15 @@ __global__ void __launch_bounds__(128, 1) k(Cfg c, int iters, long long* out, in
 int main() {
   long long* out; int* status;
   cudaMalloc(&out, 64); cudaMalloc(&status, 4); cudaMemset(status, 0, 4);
-  cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  cudaFuncSetAttribute(k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+  cudaFuncSetAttribute(k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
   Cfg cfgs[] = {{256,0,0,0,0},{128,0,0,0,0},{64,0,0,0,0},{64,0,1,0,0},{64,1,1,0,0},{128,1,1,0,0},{128,0,0,1,0},{64,0,1,1,0},{32,0,0,0,0},{16,0,0,0,0},
                 {64,0,0,0,1},{64,0,1,0,1},{128,0,0,0,1},{32,0,0,0,1}};
   const int iters = 500;
   for (auto c : cfgs) {
     cudaMemset(out, 0, 64);
-    k<<<148, 128, 100 * 1024>>>(c, iters, out, status);
+    if (c.a_tmem) k<true><<<148, 128, 100 * 1024>>>(c, iters, out, status);
+    else k<false><<<148, 128, 100 * 1024>>>(c, iters, out, status);
     cudaError_t e = cudaDeviceSynchronize();
     long long h[4]; int st; cudaMemcpy(h, out, 32, cudaMemcpyDeviceToHost); cudaMemcpy(&st, status, 4, cudaMemcpyDeviceToHost);
     const double n = iters * 4.0;
