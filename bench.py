@@ -4,6 +4,7 @@
     python bench.py --gpus N --steps K --warmup W            # this framework
     python bench.py --impl reference --gpus N ...            # the unmodified reference from baseline/_ref
 
+Configs "cfg3" / "cfg5" (--config): LBI Mamba-3 130M / LBI Mamba-2 780M through the scan engine on one GPU.
 Config "cfg4" (default): LBI Transformer, 24 layers, d_model 1024, 16 heads x 64, RoPE, RMSNorm, SwiGLU 2816,
 vocab 32768, sequence 16384 split into 8 regions of 2048 tokens, interface width 128, batch 4, bf16, AdamW,
 uniform-random tokens, random-init weights.  Regions are placed on the GPUs in contiguous blocks (8 regions on N
@@ -31,6 +32,14 @@ CONFIGS = {
                        vocab=32768, seq_len=16384, regions=8, batch=4, message_dim=128, message_hidden=1024, axis="depth"),
     "small": dict(model="lbi-transformer-small", layers=4, dim=512, n_heads=8, d_intermediate=1408, vocab=8192,
                   seq_len=4096, regions=8, batch=2, message_dim=32, message_hidden=512),
+    # Mamba backbones run through the autograd-based scan engine (one GPU): the region-parallel fast engine is the
+    # Transformer's.  cfg3 / cfg5 are the LBI Mamba-3 (~130M) and LBI Mamba-2 (~780M) shapes.
+    "cfg3": dict(model="lbi-mamba3-130m", backbone="mamba3", layers=24, dim=768, d_state=128, headdim=64, expand=2, chunk=128,
+                 vocab=32768, seq_len=8192, regions=8, batch=8, message_dim=64, message_hidden=768),
+    "cfg5": dict(model="lbi-mamba2-780m", backbone="mamba2", layers=48, dim=1536, d_state=128, headdim=64, expand=2, chunk=256,
+                 vocab=32768, seq_len=32768, regions=32, batch=2, message_dim=256, message_hidden=1536),
+    "mamba-tiny": dict(model="lbi-mamba3-tiny", backbone="mamba3", layers=2, dim=256, d_state=128, headdim=64, expand=2, chunk=128,
+                       vocab=1024, seq_len=1024, regions=4, batch=2, message_dim=16, message_hidden=64),
     "tiny": dict(model="lbi-transformer-tiny", layers=2, dim=256, n_heads=4, d_intermediate=512, vocab=1024,
                  seq_len=1024, regions=8, batch=2, message_dim=16, message_hidden=64),
 }
@@ -247,6 +256,90 @@ def run_ours(args) -> dict:
     }
 
 
+def run_ours_scan_engine(args) -> dict:
+    """Mamba configs: LBILanguageModel + ScanADEngine (recompute Jacobian provider over blocks of basis directions, the
+    state mixers on the tcgen05 scan kernels forward and backward) + AdamW with clipping, one GPU."""
+    import torch.nn.functional as F
+
+    from lbi_b200 import ops
+    from lbi_b200.backbones import BackboneSpec
+    from lbi_b200.backward import ScanADEngine
+    from lbi_b200.interfaces import VectorMLPInterface
+    from lbi_b200.models import LBILanguageModel
+
+    cfg = CONFIGS[args.config]
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("the Mamba configs run on one GPU (the region-parallel engine covers the Transformer backend)")
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.manual_seed(0)
+    spec = BackboneSpec(name=cfg["backbone"], dim=cfg["dim"], layers=cfg["layers"], d_state=cfg["d_state"], headdim=cfg["headdim"],
+                        expand=cfg["expand"], d_conv=4, chunk_size=cfg["chunk"])
+    iface = VectorMLPInterface(feature_dim=cfg["dim"], num_regions=cfg["regions"], interface_width=cfg["message_dim"],
+                               interface_map_hidden_dim=cfg["message_hidden"])
+    model = LBILanguageModel(vocab_size=cfg["vocab"], layers_per_region=max(1, cfg["layers"] // cfg["regions"]), backbone_spec=spec,
+                             interface=iface, tie_embeddings=True, region_axis="sequence",
+                             num_sequence_regions=cfg["regions"]).to(device)
+    n_params = sum(p.numel() for p in model.parameters())
+    engine = ScanADEngine(state_jacobian_mode="recompute", state_jacobian_basis_chunk=args.basis_chunk)
+    optimizer = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.01)
+
+    def step(x, y):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            logits, cache = model.forward_with_cache(x, detach_states=True)
+        loss = F.cross_entropy(logits.float().reshape(-1, cfg["vocab"]), y.reshape(-1))
+        engine.backward(model=model, loss=loss, cache=cache)
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        optimizer.step()
+        return loss.detach()
+
+    total = args.warmup + args.steps
+    host = make_batches(cfg, total, seed=1234)
+    dev_batches = [(x.to(device, non_blocking=True), y.to(device, non_blocking=True)) for x, y in host]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    for i in range(args.warmup):
+        step(*dev_batches[i])
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    launches0 = ops.dispatch.KERNEL_LAUNCHES["count"]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    loss = None
+    for i in range(args.warmup, total):
+        flush.zero_()
+        loss = step(*dev_batches[i])
+    stop.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    launches = ops.dispatch.KERNEL_LAUNCHES["count"] - launches0
+    ms = start.elapsed_time(stop) / max(1, args.steps)
+    tokens = cfg["batch"] * cfg["seq_len"]
+    e2e = None
+    if not args.no_e2e:
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            x, y = host[args.warmup + i]
+            loss_val = float(step(x.to(device, non_blocking=True), y.to(device, non_blocking=True)).item())
+        torch.cuda.synchronize()
+        e2e = {"value": tokens * args.steps / (time.perf_counter() - t0), "unit": "tokens/s",
+               "h2d_bytes_per_step": int(host[0][0].numel() * 8 + host[0][1].numel() * 8), "d2h_bytes_per_step": 4,
+               "last_loss": loss_val}
+    status = ops.ext().kernel_status(flush) if ops.native_available() else 0
+    return {
+        "metric": "train tokens/s (device-timed, max over ranks)", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
+        "config": {"model": cfg["model"], "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": cfg["regions"],
+                   "region_axis": "sequence", "interface_width": cfg["message_dim"], "params": n_params, "parallelism": "single",
+                   "backward": "suffix-scan exact (scan engine, recompute Jacobian provider, kernel scans forward and backward)",
+                   "basis_chunk": args.basis_chunk, "optimizer": "AdamW + global-norm clip in the timed region",
+                   "cache": "L2 flushed (256 MB write) before every timed step; per-step working set is GBs"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": float(loss) if loss is not None else None,
+        "kernel_status": int(status),
+    }
+
+
 # --------------------------------------------------------------------------------------------------- reference arm
 def run_reference(args) -> dict:
     """The unmodified reference tree under baseline/_ref, driven through its own classes on one GPU."""
@@ -393,7 +486,11 @@ def main() -> None:
     if not torch.cuda.is_available():
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}))
         return
-    result = run_reference(args) if args.impl == "reference" else run_ours(args)
+    mamba = "backbone" in CONFIGS[args.config]
+    if args.impl == "reference" and mamba:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm is wired for the Transformer configuration (cfg4) only"}))
+        return
+    result = run_reference(args) if args.impl == "reference" else (run_ours_scan_engine(args) if mamba else run_ours(args))
     if int(os.environ.get("RANK", "0")) == 0 and result:
         print(json.dumps(result))
     import torch.distributed as dist
