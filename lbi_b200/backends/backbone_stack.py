@@ -10,7 +10,7 @@ import torch
 from torch import nn
 
 from ..backbones.general import BackboneSpec, apply_backbone_init, build_backbone_stack
-from .base import RegionForwardCache
+from .base import RegionForwardCache, autocast_as, current_autocast
 
 
 class BackboneStackRegionBackend(nn.Module):
@@ -27,7 +27,8 @@ class BackboneStackRegionBackend(nn.Module):
     def forward_region(self, *, region_input: torch.Tensor, region_index: int):
         start, end = self.region_ranges[region_index]
         out = self.backbone.forward_range(region_input, start, end)
-        return out, RegionForwardCache(region_index=region_index, layer_range=(start, end), region_input=region_input)
+        return out, RegionForwardCache(region_index=region_index, layer_range=(start, end), region_input=region_input,
+                                       autocast=current_autocast(region_input.device))
 
     def parameters_for_region(self, region_index: int) -> list[nn.Parameter]:
         start, end = self.region_ranges[region_index]
@@ -54,7 +55,7 @@ class BackboneStackRegionBackend(nn.Module):
         x = cache.region_input.detach()
         rep = x.unsqueeze(1).expand(bsz, nbasis, *x.shape[1:]).reshape(bsz * nbasis, *x.shape[1:]).clone().requires_grad_(True)
         start, end = cache.layer_range
-        with torch.enable_grad():
+        with torch.enable_grad(), autocast_as(cache.autocast):
             out = self.backbone.forward_range(rep, start, end)
         (g,) = torch.autograd.grad(out, rep, output_cotangent_basis.reshape(bsz * nbasis, *x.shape[1:]).to(out.dtype))
         return g.reshape(bsz, nbasis, *x.shape[1:])
@@ -64,7 +65,7 @@ class BackboneStackRegionBackend(nn.Module):
             raise ValueError("cache has no region_input to recompute from")
         named = self.named_parameters_for_region(cache.region_index)
         start, end = cache.layer_range
-        with torch.enable_grad():
+        with torch.enable_grad(), autocast_as(cache.autocast):
             out = self.backbone.forward_range(cache.region_input.detach(), start, end)
         grads = torch.autograd.grad(out, [p for _, p in named], output_cotangent.to(out.dtype), allow_unused=True)
         return {name: g for (name, _), g in zip(named, grads) if g is not None}

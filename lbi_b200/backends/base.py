@@ -8,6 +8,23 @@ import torch
 from torch import nn
 
 
+def current_autocast(device: torch.device) -> tuple[str, torch.dtype] | None:
+    """(device type, dtype) of the autocast region the caller runs in, or None: recorded at forward time so that every
+    later recompute of the same computation (Jacobian providers, pullbacks, parameter VJPs) runs at the same precision
+    and reaches the same kernels."""
+    kind = device.type
+    if torch.is_autocast_enabled(kind):
+        return kind, torch.get_autocast_dtype(kind)
+    return None
+
+
+def autocast_as(state: tuple[str, torch.dtype] | None):
+    """Context manager that restores a state recorded by ``current_autocast`` (a no-op context for None)."""
+    import contextlib
+
+    return torch.autocast(state[0], dtype=state[1]) if state else contextlib.nullcontext()
+
+
 @dataclass
 class RegionForwardCache:
     region_index: int
@@ -15,6 +32,7 @@ class RegionForwardCache:
     region_input: torch.Tensor | None = None
     structured: Any | None = None
     extras: dict = field(default_factory=dict)
+    autocast: tuple | None = None
 
 
 class RegionBackend(Protocol):

@@ -13,7 +13,7 @@ import torch
 from torch import nn
 
 from ..backbones.general import BackboneSpec, build_backbone_stack, init_transformer_module
-from .base import RegionForwardCache
+from .base import RegionForwardCache, autocast_as, current_autocast
 from .transformer_structured import StructuredTransformerRegion
 
 
@@ -32,14 +32,14 @@ class TorchAutogradTransformerLowering:
         bsz, nbasis = output_cotangent_basis.shape[:2]
         x = cache.region_input.detach()
         rep = x.unsqueeze(1).expand(bsz, nbasis, *x.shape[1:]).reshape(bsz * nbasis, *x.shape[1:]).clone().requires_grad_(True)
-        with torch.enable_grad():
+        with torch.enable_grad(), autocast_as(cache.autocast):
             out = backend.backbone.forward_range(rep, *cache.layer_range)
         (g,) = torch.autograd.grad(out, rep, output_cotangent_basis.reshape(bsz * nbasis, *x.shape[1:]).to(out.dtype))
         return g.reshape(bsz, nbasis, *x.shape[1:])
 
     def parameter_vjp(self, *, backend, cache, output_cotangent):
         named = backend.named_parameters_for_region(cache.region_index)
-        with torch.enable_grad():
+        with torch.enable_grad(), autocast_as(cache.autocast):
             out = backend.backbone.forward_range(cache.region_input.detach(), *cache.layer_range)
         grads = torch.autograd.grad(out, [p for _, p in named], output_cotangent.to(out.dtype), allow_unused=True)
         return {name: g for (name, _), g in zip(named, grads) if g is not None}
@@ -85,7 +85,8 @@ class TransformerRegionBackend(nn.Module):
 
     def forward_region(self, *, region_input: torch.Tensor, region_index: int):
         start, end = self.region_ranges[region_index]
-        cache = RegionForwardCache(region_index=region_index, layer_range=(start, end), region_input=region_input)
+        cache = RegionForwardCache(region_index=region_index, layer_range=(start, end), region_input=region_input,
+                                   autocast=current_autocast(region_input.device))
         if torch.is_grad_enabled():
             return self.backbone.forward_range(region_input, start, end), cache
         out, cache.structured = self.structured.forward(region_input, (start, end))

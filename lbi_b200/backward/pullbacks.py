@@ -16,6 +16,8 @@ from typing import Any, Protocol, Sequence
 
 import torch
 
+from ..backends.base import autocast_as
+
 
 class InterfacePullbackProvider(Protocol):
     name: str
@@ -71,7 +73,7 @@ class TorchRecomputeInterfacePullbackProvider:
                 c = min(self.basis_chunk, r - j0)
                 s_rep = s_in.repeat_interleave(c, dim=0).requires_grad_(True)
                 canvas_rep = canvas.repeat_interleave(c, dim=0)
-                with torch.enable_grad():
+                with torch.enable_grad(), autocast_as(cache.get("autocast")):
                     cond = model.interface.decode(s_rep, k)
                     region_out, _ = model.region_backend.forward_region(region_input=canvas_rep + cond.unsqueeze(1), region_index=k)
                     s_next = model.interface.update(s_rep, region_out, k).state

@@ -15,6 +15,7 @@ from torch import nn
 
 from ..backbones.general import BackboneSpec, init_transformer_module, make_final_norm
 from ..backends import BackboneStackRegionBackend, RegionForwardCache, TransformerRegionBackend
+from ..backends.base import current_autocast
 from ..canvas import TokenEmbeddingCanvas
 from ..interfaces import InterfaceModule, InterfaceStep
 from ..readouts import NormLMHeadReadout
@@ -188,6 +189,7 @@ class LBILanguageModel(nn.Module):
             "region_caches": region_caches,
             "detached_states": bool(detach_states and torch.is_grad_enabled()),
             "region_axis": self.region_axis,
+            "autocast": current_autocast(canvas_features.device),
         }
 
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:

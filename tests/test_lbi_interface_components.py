@@ -191,3 +191,35 @@ def test_structured_transformer_lowering_matches_autograd_lowering(d_conv, kv):
     assert set(got) == set(want)
     for name in want:
         assert torch.allclose(got[name].reshape(want[name].shape), want[name], atol=1e-5, rtol=1e-4), name
+
+
+@pytest.mark.parametrize("backbone", ["transformer", "mamba2"])
+def test_recomputes_run_under_the_autocast_state_of_the_forward(backbone):
+    """A forward under autocast records that state; the Jacobian provider's recompute and the backend's pullback /
+    parameter VJP restore it (a recompute at another precision would take other code paths than the forward did)."""
+    model = lbi_model(backbone=backbone, axis="sequence", k=2)
+    ids = torch.randint(0, 50, (2, 16))
+    with torch.autocast("cpu", dtype=torch.bfloat16):
+        _, cache = model.forward_with_cache(ids, detach_states=True)
+    assert cache["autocast"] == ("cpu", torch.bfloat16)
+    assert all(rc.backend_cache.autocast == ("cpu", torch.bfloat16) for rc in cache["region_caches"])
+    seen = []
+    inner = model.region_backend.backbone.forward_range
+
+    def spy(*a, **kw):
+        seen.append(torch.is_autocast_enabled("cpu") and torch.get_autocast_dtype("cpu") == torch.bfloat16)
+        return inner(*a, **kw)
+
+    model.region_backend.backbone.forward_range = spy
+    try:
+        assert not torch.is_autocast_enabled("cpu")
+        build_interface_pullback_provider("recompute", basis_chunk=4).materialize_state_jacobian_t(model=model, cache=cache)
+        rc = cache["region_caches"][0].backend_cache
+        model.region_backend.parameter_vjp(cache=rc, output_cotangent=torch.randn(2, 8, 32))
+        if backbone != "transformer":
+            model.region_backend.input_pullback_basis(cache=rc, output_cotangent_basis=torch.randn(2, 3, 8, 32))
+    finally:
+        model.region_backend.backbone.forward_range = inner
+    assert seen and all(seen)
+    _, plain = model.forward_with_cache(ids, detach_states=True)
+    assert plain["autocast"] is None
