@@ -55,6 +55,8 @@ def parse_args():
     p.add_argument("--basis-chunk", type=int, default=16)
     p.add_argument("--comm", type=str, default="auto", choices=["auto", "collective", "symm"])
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--jacobian-mode", type=str, default="recompute", choices=["recompute", "graph", "structured"],
+                   help="scan-engine configs: how the interface Jacobians are materialised")
     p.add_argument("--profile-ops", action="store_true", help="after the timed run, time one more step op by op (stderr)")
     return p.parse_args()
 
@@ -281,7 +283,7 @@ def run_ours_scan_engine(args) -> dict:
                              interface=iface, tie_embeddings=True, region_axis="sequence",
                              num_sequence_regions=cfg["regions"]).to(device)
     n_params = sum(p.numel() for p in model.parameters())
-    engine = ScanADEngine(state_jacobian_mode="recompute", state_jacobian_basis_chunk=args.basis_chunk)
+    engine = ScanADEngine(state_jacobian_mode=args.jacobian_mode, state_jacobian_basis_chunk=args.basis_chunk)
     optimizer = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.01)
 
     def step(x, y):
@@ -332,7 +334,7 @@ def run_ours_scan_engine(args) -> dict:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights", "impl": "ours",
         "config": {"model": cfg["model"], "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": cfg["regions"],
                    "region_axis": "sequence", "interface_width": cfg["message_dim"], "params": n_params, "parallelism": "single",
-                   "backward": "suffix-scan exact (scan engine, recompute Jacobian provider, kernel scans forward and backward)",
+                   "backward": f"suffix-scan exact (scan engine, {args.jacobian_mode} Jacobian provider, kernel scans forward and backward)",
                    "basis_chunk": args.basis_chunk, "optimizer": "AdamW + global-norm clip in the timed region",
                    "cache": "L2 flushed (256 MB write) before every timed step; per-step working set is GBs"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": float(loss) if loss is not None else None,
