@@ -44,12 +44,48 @@ def _rotate_pairs(x: torch.Tensor, theta: torch.Tensor) -> torch.Tensor:
     return torch.cat((rotated, tail), dim=-1)
 
 
-def _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, compute_dtype):
-    """Shared preprocessing: per-head biased/rotated Q, K, trapezoid weights."""
-    bsz, seqlen, nheads, _ = V.shape
-    rep = nheads // Q.shape[2]
-    Qh = Q.to(compute_dtype).repeat_interleave(rep, dim=2) + Q_bias.to(compute_dtype)[None, None]
-    Kh = K.to(compute_dtype).repeat_interleave(rep, dim=2) + K_bias.to(compute_dtype)[None, None]
+class _WidePrepFunction(torch.autograd.Function):
+    """Bias, qk dot, rotary turn and trapezoid scale on the [b, l, h, 128] tensors: csrc/siso_prep.cu, both directions."""
+
+    @staticmethod
+    def forward(ctx, Q, K, Q_bias, K_bias, theta, gamma, scale):
+        from lbi_b200.ops import dispatch, ext
+
+        q, k = Q.contiguous(), K.to(Q.dtype).contiguous()
+        qb, kb = Q_bias.float().contiguous(), K_bias.float().contiguous()
+        th, gm, sc = theta.float().contiguous(), gamma.float().contiguous(), scale.float().contiguous()
+        qr, kr, qk = ext().siso_prep_fwd(q, k, qb, kb, th, gm, sc)
+        dispatch.KERNEL_LAUNCHES["count"] += 1
+        ctx.save_for_backward(q, k, qb, kb, th, gm, sc)
+        ctx.dtypes = (Q.dtype, K.dtype, Q_bias.dtype, K_bias.dtype, theta.dtype, gamma.dtype, scale.dtype)
+        return qr, kr, qk
+
+    @staticmethod
+    def backward(ctx, dqr, dkr, dqk):
+        from lbi_b200.ops import dispatch, ext
+
+        q, k, qb, kb, th, gm, sc = ctx.saved_tensors
+        zeros = lambda like, shape: torch.zeros(shape, dtype=torch.float32, device=like.device)  # noqa: E731
+        dqr = zeros(q, (*th.shape[:3], 128)) if dqr is None else dqr.float().contiguous()
+        dkr = zeros(q, (*th.shape[:3], 128)) if dkr is None else dkr.float().contiguous()
+        dqk = zeros(q, th.shape[:3]) if dqk is None else dqk.float().contiguous()
+        grads = ext().siso_prep_bwd(q, k, qb, kb, th, gm, sc, dqr, dkr, dqk)
+        dispatch.KERNEL_LAUNCHES["count"] += 1
+        return tuple(g.to(dt) for g, dt in zip(grads, ctx.dtypes))
+
+
+def _wide_kernels_ok(Q: torch.Tensor) -> bool:
+    if not (Q.is_cuda and Q.shape[-1] == 128 and Q.dtype in (torch.bfloat16, torch.float32)):
+        return False
+    if torch._C._functorch.maybe_current_level() is not None:
+        return False
+    from lbi_b200.ops import ext, native_available
+
+    return native_available() and hasattr(ext(), "siso_prep_fwd")
+
+
+def _prepare_small(ADT, DT, Trap, Angles, compute_dtype):
+    """The [b, l, h]-sized part: log-decay, trapezoid weights gamma / scale, cumulative rotary phase theta [b, l, h, s]."""
     dt = DT.to(compute_dtype).transpose(1, 2)  # [b, l, h]
     adt = ADT.to(compute_dtype).transpose(1, 2)
     sig = torch.sigmoid(Trap.to(compute_dtype).transpose(1, 2))
@@ -57,6 +93,23 @@ def _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, compute_dtype):
     carry = F.pad((dt * (1.0 - sig))[:, 1:], (0, 0, 0, 1))  # dt_{t+1} (1 - sigma_{t+1}), zero after the last token
     scale = gamma + carry
     theta = angle_dt_cumsum(Angles, dt).to(compute_dtype)
+    return adt, gamma, scale, theta
+
+
+def _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, compute_dtype, fused: bool = False):
+    """Shared preprocessing: per-head biased/rotated Q, K, trapezoid weights.
+
+    The small tensors ([b, l, h] and [b, l, h, angles]: trapezoid weights, cumulative rotary phase) are PyTorch ops.  With
+    ``fused`` (the kernel path of ``ops/ssd.py``) everything on the [b, l, h, d_state] tensors runs in one kernel per
+    direction and Qr, Kr come back in bf16, the dtype the scan kernels take."""
+    bsz, seqlen, nheads, _ = V.shape
+    rep = nheads // Q.shape[2]
+    adt, gamma, scale, theta = _prepare_small(ADT, DT, Trap, Angles, compute_dtype)
+    if fused and compute_dtype == torch.float32 and _wide_kernels_ok(Q):
+        Qr, Kr, qk_dot = _WidePrepFunction.apply(Q, K, Q_bias, K_bias, theta, gamma, scale)
+        return Qr, Kr, adt, qk_dot
+    Qh = Q.to(compute_dtype).repeat_interleave(rep, dim=2) + Q_bias.to(compute_dtype)[None, None]
+    Kh = K.to(compute_dtype).repeat_interleave(rep, dim=2) + K_bias.to(compute_dtype)[None, None]
     qk_dot = gamma * (Qh * Kh).sum(dim=-1)
     Qr = _rotate_pairs(Qh, theta)
     Kr = _rotate_pairs(Kh, theta) * scale.unsqueeze(-1)

@@ -73,6 +73,20 @@ int lbi_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z_or_null, 
                           void* dz_or_null, float* dw_partials, int64_t rows, int dim, int group_size, int gate_first,
                           int is_bf16, cudaStream_t stream);
 
+// ---- Mamba-3 SISO preprocessing on the wide tensors (siso_prep.cu) ---------------------------------------
+// q, k [tokens, groups, 128] bf16 (is_bf16) or fp32; biases [heads, 128]; theta [tokens, heads, n_angles]; gamma, scale
+// [tokens, heads]  ->  qr, kr [tokens, heads, 128] bf16, qk_dot [tokens, heads].
+int lbi_siso_prep_fwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
+                      const float* gamma, const float* scale, void* qr_bf16, void* kr_bf16, float* qk_dot, int64_t tokens,
+                      int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
+// Backward from dqr, dkr [tokens, heads, 128] fp32 and dqk [tokens, heads]: dq, dk [tokens, groups, 128] fp32, dtheta, dgamma,
+// dscale, and bias_partials [lbi_siso_prep_blocks(tokens * groups)][2][heads][128] (summed by the caller: dq_bias, dk_bias).
+int lbi_siso_prep_blocks(int64_t rows);
+int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
+                      const float* gamma, const float* scale, const float* dqr, const float* dkr, const float* dqk, float* dq,
+                      float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials, int64_t tokens, int groups,
+                      int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
+
 // ---- interface Jacobian products over a basis (interface_jac.cu) -----------------------------------------
 // out[b, p, :] = (((in_scale * g[b, p, :]) @ wa) o d[b, :]) @ wb;  g [B, P, din], wa [din, hidden], d [B, hidden] or null,
 // wb [hidden, dout] or null (then out [B, P, hidden] = (g @ wa) o d).  All fp32 row-major.

@@ -319,6 +319,67 @@ std::tuple<Tensor, Tensor, Tensor> gated_rmsnorm_bwd(const Tensor& dy, const Ten
   return {dx, dz, partials.sum(0)};
 }
 
+// SISO preprocessing.  q, k [B, L, G, 128] bf16 / fp32; biases [H, 128]; theta [B, L, H, S]; gamma, scale [B, L, H] (all fp32)
+// -> (qr, kr [B, L, H, 128] bf16, qk_dot [B, L, H] fp32).
+std::tuple<Tensor, Tensor, Tensor> siso_prep_fwd(const Tensor& q, const Tensor& k, const Tensor& q_bias, const Tensor& k_bias,
+                                                 const Tensor& theta, const Tensor& gamma, const Tensor& scale) {
+  CHECK_F32(q_bias);
+  CHECK_F32(k_bias);
+  CHECK_F32(theta);
+  CHECK_F32(gamma);
+  CHECK_F32(scale);
+  TORCH_CHECK(q.is_cuda() && q.is_contiguous() && k.is_contiguous() && k.sizes() == q.sizes() && k.scalar_type() == q.scalar_type() &&
+                  (q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kFloat) && q.dim() == 4 && q.size(3) == 128,
+              "siso_prep: q, k must be contiguous [B, L, G, 128] bf16 / fp32");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t batch = q.size(0), seq = q.size(1), groups = q.size(2), heads = q_bias.size(0), na = theta.size(3);
+  TORCH_CHECK(theta.dim() == 4 && theta.size(0) == batch && theta.size(1) == seq && theta.size(2) == heads && gamma.numel() == batch * seq * heads &&
+                  scale.numel() == gamma.numel() && k_bias.sizes() == q_bias.sizes() && q_bias.size(1) == 128,
+              "siso_prep: shape mismatch");
+  Tensor qr = torch::empty({batch, seq, heads, 128}, q.options().dtype(at::kBFloat16)), kr = torch::empty_like(qr);
+  Tensor qk = torch::empty({batch, seq, heads}, gamma.options());
+  check(lbi_siso_prep_fwd(q.data_ptr(), k.data_ptr(), q_bias.data_ptr<float>(), k_bias.data_ptr<float>(), theta.data_ptr<float>(),
+                          gamma.data_ptr<float>(), scale.data_ptr<float>(), qr.data_ptr(), kr.data_ptr(), qk.data_ptr<float>(), batch * seq,
+                          (int)groups, (int)heads, 128, (int)na, q.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+        "siso_prep_fwd");
+  return {qr, kr, qk};
+}
+
+// -> (dq, dk [B, L, G, 128] fp32, dq_bias, dk_bias [H, 128], dtheta [B, L, H, S], dgamma, dscale [B, L, H])
+std::vector<Tensor> siso_prep_bwd(const Tensor& q, const Tensor& k, const Tensor& q_bias, const Tensor& k_bias, const Tensor& theta,
+                                  const Tensor& gamma, const Tensor& scale, const Tensor& dqr, const Tensor& dkr, const Tensor& dqk) {
+  CHECK_F32(q_bias);
+  CHECK_F32(k_bias);
+  CHECK_F32(theta);
+  CHECK_F32(gamma);
+  CHECK_F32(scale);
+  CHECK_F32(dqr);
+  CHECK_F32(dkr);
+  CHECK_F32(dqk);
+  TORCH_CHECK(q.is_cuda() && q.is_contiguous() && k.is_contiguous() && k.sizes() == q.sizes() && k.scalar_type() == q.scalar_type() &&
+                  (q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kFloat) && q.dim() == 4 && q.size(3) == 128,
+              "siso_prep_bwd: q, k must be contiguous [B, L, G, 128] bf16 / fp32");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t batch = q.size(0), seq = q.size(1), groups = q.size(2), heads = q_bias.size(0), na = theta.size(3);
+  TORCH_CHECK(dqr.numel() == batch * seq * heads * 128 && dkr.numel() == dqr.numel() && dqk.numel() == batch * seq * heads &&
+                  theta.numel() == batch * seq * heads * na,
+              "siso_prep_bwd: shape mismatch");
+  auto f32 = gamma.options();
+  Tensor dq = torch::empty({batch, seq, groups, 128}, f32), dk = torch::empty_like(dq);
+  Tensor dtheta = torch::empty({batch, seq, heads, na}, f32);
+  Tensor dgamma = torch::empty({batch, seq, heads}, f32), dscale = torch::empty_like(dgamma);
+  const int blocks = lbi_siso_prep_blocks(batch * seq * groups);
+  Tensor partials = torch::empty({blocks, 2, heads, 128}, f32);
+  check(lbi_siso_prep_bwd(q.data_ptr(), k.data_ptr(), q_bias.data_ptr<float>(), k_bias.data_ptr<float>(), theta.data_ptr<float>(),
+                          gamma.data_ptr<float>(), scale.data_ptr<float>(), dqr.data_ptr<float>(), dkr.data_ptr<float>(),
+                          dqk.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dtheta.data_ptr<float>(),
+                          dgamma.data_ptr<float>(), dscale.data_ptr<float>(), partials.data_ptr<float>(), batch * seq, (int)groups,
+                          (int)heads, 128, (int)na, q.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+        "siso_prep_bwd");
+  Tensor bias = partials.sum(0);
+  return {dq, dk, bias.select(0, 0), bias.select(0, 1), dtheta, dgamma, dscale};
+}
+
 // (((in_scale g) @ wa) o d) @ wb over a basis: g [B, P, din] fp32, wa [din, hidden], d [B, hidden] or none, wb [hidden, dout] or none.
 Tensor interface_mlp_jac(const Tensor& g, const Tensor& wa, const c10::optional<Tensor>& d, const c10::optional<Tensor>& wb,
                          double in_scale) {
@@ -824,6 +885,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("affine_suffix_scan", &affine_suffix_scan);
   m.def("matrix_norms", &matrix_norms);
   m.def("interface_mlp_jac", &interface_mlp_jac);
+  m.def("siso_prep_fwd", &siso_prep_fwd);
+  m.def("siso_prep_bwd", &siso_prep_bwd);
   m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);
   m.def("gated_rmsnorm_bwd", &gated_rmsnorm_bwd);
   m.def("layernorm_jac", &layernorm_jac);

@@ -1,0 +1,214 @@
+// Mamba-3 SISO preprocessing of the state-mixer operands, forward and backward, on the wide tensors.
+//
+// Per (batch, token, head) with Qh = Q[group] + Q_bias[head], Kh = K[group] + K_bias[head] (d_state = 128 wide):
+//     qk_dot = gamma * (Qh . Kh)
+//     Qr     = rot(Qh, theta)                 pairs (2i, 2i + 1), i < n_angles, turn by theta_i; the rest stays
+//     Kr     = rot(Kh, theta) * scale
+// gamma, scale (trapezoid weights) and theta (cumulative rotary phase) are [batch, token, head(, angle)] tensors that
+// the caller forms with small PyTorch ops; what runs here is everything that touches [batch, token, head, 128].
+// Backward, from dQr, dKr (fp32) and dqk:
+//     dQh = rot^-1(dQr) + dqk gamma Kh         dKh = scale rot^-1(dKr) + dqk gamma Qh
+//     dQ[group] = sum over heads dQh,  dQ_bias[head] = sum over (batch, token) dQh        (same for K)
+//     dtheta_i = <dQr_pair, J rot(Qh)_pair> + scale <dKr_pair, J rot(Kh)_pair>,  J (a, b) = (-b, a)
+//     dgamma = dqk (Qh . Kh),   dscale = dKr . rot(Kh)
+// One warp owns one (batch, token, group) and walks the heads of the group: four state elements (two pairs) per lane.
+// The bias gradients accumulate in shared memory per block and leave as one row of a partials buffer.
+// Replaces phase 1 of the reference's mamba3_siso_fwd_kernel and its mamba3_siso_bwd_kernel_rotary_bias_angles
+// (backbones/mamba3/ops/triton/mamba3/mamba3_siso_fwd.py:29, mamba3_siso_bwd.py:811) for d_state 128.
+#include "api.h"
+#include "common.cuh"
+
+namespace lbi {
+namespace sisoprep {
+
+constexpr int N = 128;
+constexpr int THREADS = 256;
+constexpr int WARPS = THREADS / 32;
+
+template <typename T>
+__device__ __forceinline__ float4 ld4(const T* p);
+template <>
+__device__ __forceinline__ float4 ld4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4_bf16(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&a);
+  o.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+struct Rot {
+  float c0, s0, c1, s1;   // cos / sin of the lane's two pairs (1, 0 where the pair is not rotated)
+};
+
+__device__ __forceinline__ Rot load_rot(const float* theta_row, int lane, int n_angles) {
+  Rot r{1.f, 0.f, 1.f, 0.f};
+  const int i0 = 2 * lane, i1 = 2 * lane + 1;
+  if (i0 < n_angles) __sincosf(theta_row[i0], &r.s0, &r.c0);
+  if (i1 < n_angles) __sincosf(theta_row[i1], &r.s1, &r.c1);
+  return r;
+}
+__device__ __forceinline__ float4 rotate(float4 v, const Rot& r) {
+  return make_float4(v.x * r.c0 - v.y * r.s0, v.x * r.s0 + v.y * r.c0, v.z * r.c1 - v.w * r.s1, v.z * r.s1 + v.w * r.c1);
+}
+__device__ __forceinline__ float4 rotate_back(float4 v, const Rot& r) {
+  return make_float4(v.x * r.c0 + v.y * r.s0, -v.x * r.s0 + v.y * r.c0, v.z * r.c1 + v.w * r.s1, -v.z * r.s1 + v.w * r.c1);
+}
+
+// grid-stride over (batch * token * group) rows, one warp per row
+template <typename T>
+__global__ void __launch_bounds__(THREADS) fwd_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                      const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                                                      const float* __restrict__ theta, const float* __restrict__ gamma,
+                                                      const float* __restrict__ scale, __nv_bfloat16* __restrict__ qr,
+                                                      __nv_bfloat16* __restrict__ kr, float* __restrict__ qk_dot, int64_t rows,
+                                                      int groups, int heads, int n_angles) {
+  const int lane = threadIdx.x & 31;
+  const int rep = heads / groups;
+  for (int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * WARPS) {
+    const int g = (int)(row % groups);
+    const int64_t tok = row / groups;
+    const float4 qg = ld4<T>(q + row * N + lane * 4), kg = ld4<T>(k + row * N + lane * 4);
+    for (int r = 0; r < rep; ++r) {
+      const int h = g * rep + r;
+      const int64_t hrow = tok * heads + h;
+      const float4 qb = ld4<float>(q_bias + h * N + lane * 4), kb = ld4<float>(k_bias + h * N + lane * 4);
+      const float4 qh = make_float4(qg.x + qb.x, qg.y + qb.y, qg.z + qb.z, qg.w + qb.w);
+      const float4 kh = make_float4(kg.x + kb.x, kg.y + kb.y, kg.z + kb.z, kg.w + kb.w);
+      const Rot rot = load_rot(theta + hrow * n_angles, lane, n_angles);
+      const float sc = scale[hrow];
+      const float4 qo = rotate(qh, rot);
+      float4 ko = rotate(kh, rot);
+      ko = make_float4(ko.x * sc, ko.y * sc, ko.z * sc, ko.w * sc);
+      st4_bf16(qr + hrow * N + lane * 4, qo);
+      st4_bf16(kr + hrow * N + lane * 4, ko);
+      const float dot = warp_sum(qh.x * kh.x + qh.y * kh.y + qh.z * kh.z + qh.w * kh.w);
+      if (lane == 0) qk_dot[hrow] = gamma[hrow] * dot;
+    }
+  }
+}
+
+// bias_partials [gridDim.x][2][heads][N]
+template <typename T>
+__global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                      const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                                                      const float* __restrict__ theta, const float* __restrict__ gamma,
+                                                      const float* __restrict__ scale, const float* __restrict__ dqr,
+                                                      const float* __restrict__ dkr, const float* __restrict__ dqk,
+                                                      float* __restrict__ dq, float* __restrict__ dk, float* __restrict__ dtheta,
+                                                      float* __restrict__ dgamma, float* __restrict__ dscale,
+                                                      float* __restrict__ bias_partials, int64_t rows, int groups, int heads,
+                                                      int n_angles) {
+  extern __shared__ float bias_acc[];   // [2][heads][N]
+  const int lane = threadIdx.x & 31;
+  const int rep = heads / groups;
+  for (int i = threadIdx.x; i < 2 * heads * N; i += THREADS) bias_acc[i] = 0.f;
+  __syncthreads();
+  for (int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * WARPS) {
+    const int g = (int)(row % groups);
+    const int64_t tok = row / groups;
+    const float4 qg = ld4<T>(q + row * N + lane * 4), kg = ld4<T>(k + row * N + lane * 4);
+    float4 dq_sum = make_float4(0.f, 0.f, 0.f, 0.f), dk_sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < rep; ++r) {
+      const int h = g * rep + r;
+      const int64_t hrow = tok * heads + h;
+      const float4 qb = ld4<float>(q_bias + h * N + lane * 4), kb = ld4<float>(k_bias + h * N + lane * 4);
+      const float4 qh = make_float4(qg.x + qb.x, qg.y + qb.y, qg.z + qb.z, qg.w + qb.w);
+      const float4 kh = make_float4(kg.x + kb.x, kg.y + kb.y, kg.z + kb.z, kg.w + kb.w);
+      const Rot rot = load_rot(theta + hrow * n_angles, lane, n_angles);
+      const float sc = scale[hrow], gm = gamma[hrow], dd = dqk[hrow];
+      const float4 gq = ld4<float>(dqr + hrow * N + lane * 4), gk = ld4<float>(dkr + hrow * N + lane * 4);
+      const float4 qo = rotate(qh, rot), ko = rotate(kh, rot);   // ko without the scale
+      // angle gradients: J (a, b) = (-b, a) applied to the rotated pair
+      const float dth0 = (-gq.x * qo.y + gq.y * qo.x) + sc * (-gk.x * ko.y + gk.y * ko.x);
+      const float dth1 = (-gq.z * qo.w + gq.w * qo.z) + sc * (-gk.z * ko.w + gk.w * ko.z);
+      if (2 * lane < n_angles) dtheta[hrow * n_angles + 2 * lane] = dth0;
+      if (2 * lane + 1 < n_angles) dtheta[hrow * n_angles + 2 * lane + 1] = dth1;
+      const float dsc = warp_sum(gk.x * ko.x + gk.y * ko.y + gk.z * ko.z + gk.w * ko.w);
+      const float qk = warp_sum(qh.x * kh.x + qh.y * kh.y + qh.z * kh.z + qh.w * kh.w);
+      if (lane == 0) {
+        dscale[hrow] = dsc;
+        dgamma[hrow] = dd * qk;
+      }
+      float4 dqh = rotate_back(gq, rot);
+      float4 dkh = rotate_back(make_float4(gk.x * sc, gk.y * sc, gk.z * sc, gk.w * sc), rot);
+      const float w = dd * gm;
+      dqh = make_float4(dqh.x + w * kh.x, dqh.y + w * kh.y, dqh.z + w * kh.z, dqh.w + w * kh.w);
+      dkh = make_float4(dkh.x + w * qh.x, dkh.y + w * qh.y, dkh.z + w * qh.z, dkh.w + w * qh.w);
+      dq_sum = make_float4(dq_sum.x + dqh.x, dq_sum.y + dqh.y, dq_sum.z + dqh.z, dq_sum.w + dqh.w);
+      dk_sum = make_float4(dk_sum.x + dkh.x, dk_sum.y + dkh.y, dk_sum.z + dkh.z, dk_sum.w + dkh.w);
+      float* bq = bias_acc + (int64_t)h * N + lane * 4;
+      float* bk = bias_acc + (int64_t)(heads + h) * N + lane * 4;
+      atomicAdd(bq, dqh.x); atomicAdd(bq + 1, dqh.y); atomicAdd(bq + 2, dqh.z); atomicAdd(bq + 3, dqh.w);
+      atomicAdd(bk, dkh.x); atomicAdd(bk + 1, dkh.y); atomicAdd(bk + 2, dkh.z); atomicAdd(bk + 3, dkh.w);
+    }
+    *reinterpret_cast<float4*>(dq + row * N + lane * 4) = dq_sum;
+    *reinterpret_cast<float4*>(dk + row * N + lane * 4) = dk_sum;
+  }
+  __syncthreads();
+  float* out = bias_partials + (int64_t)blockIdx.x * 2 * heads * N;
+  for (int i = threadIdx.x; i < 2 * heads * N; i += THREADS) out[i] = bias_acc[i];
+}
+
+static int grid_for(int64_t rows) {
+  int64_t blocks = (rows + WARPS - 1) / WARPS;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  return (int)(blocks < 1 ? 1 : blocks);
+}
+
+}  // namespace sisoprep
+}  // namespace lbi
+
+extern "C" int lbi_siso_prep_blocks(int64_t rows) { return lbi::sisoprep::grid_for(rows); }
+
+extern "C" int lbi_siso_prep_fwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
+                                 const float* gamma, const float* scale, void* qr_bf16, void* kr_bf16, float* qk_dot,
+                                 int64_t tokens, int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t st) {
+  using namespace lbi::sisoprep;
+  if (d_state != N || tokens <= 0 || groups <= 0 || heads % groups != 0 || n_angles < 0 || 2 * n_angles > N) return (int)cudaErrorInvalidValue;
+  const int64_t rows = tokens * groups;
+  const int blocks = grid_for(rows);
+  if (is_bf16)
+    fwd_kernel<__nv_bfloat16><<<blocks, THREADS, 0, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, q_bias, k_bias, theta, gamma,
+                                                         scale, (__nv_bfloat16*)qr_bf16, (__nv_bfloat16*)kr_bf16, qk_dot, rows, groups,
+                                                         heads, n_angles);
+  else
+    fwd_kernel<float><<<blocks, THREADS, 0, st>>>((const float*)q, (const float*)k, q_bias, k_bias, theta, gamma, scale,
+                                                 (__nv_bfloat16*)qr_bf16, (__nv_bfloat16*)kr_bf16, qk_dot, rows, groups, heads, n_angles);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
+                                 const float* gamma, const float* scale, const float* dqr, const float* dkr, const float* dqk,
+                                 float* dq, float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials,
+                                 int64_t tokens, int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t st) {
+  using namespace lbi::sisoprep;
+  if (d_state != N || tokens <= 0 || groups <= 0 || heads % groups != 0 || n_angles < 0 || 2 * n_angles > N) return (int)cudaErrorInvalidValue;
+  const int64_t rows = tokens * groups;
+  const int blocks = grid_for(rows);
+  const size_t smem = (size_t)2 * heads * N * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  int rc;
+  if (is_bf16) {
+    rc = (int)cudaFuncSetAttribute(bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (rc) return rc;
+    bwd_kernel<__nv_bfloat16><<<blocks, THREADS, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, q_bias, k_bias, theta, gamma,
+                                                            scale, dqr, dkr, dqk, dq, dk, dtheta, dgamma, dscale, bias_partials, rows,
+                                                            groups, heads, n_angles);
+  } else {
+    rc = (int)cudaFuncSetAttribute(bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (rc) return rc;
+    bwd_kernel<float><<<blocks, THREADS, smem, st>>>((const float*)q, (const float*)k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk,
+                                                    dq, dk, dtheta, dgamma, dscale, bias_partials, rows, groups, heads, n_angles);
+  }
+  return (int)cudaGetLastError();
+}

@@ -335,7 +335,7 @@ def _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
     from .dispatch import KERNEL_LAUNCHES
 
     seqlen = V.shape[1]
-    Qr, Kr, adt, qk_dot = _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, torch.float32)
+    Qr, Kr, adt, qk_dot = _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, torch.float32, fused=True)
     pad = (-seqlen) % CHUNK
     vb, qb, kb = V.to(torch.bfloat16), Qr.to(torch.bfloat16), Kr.to(torch.bfloat16)
     skip = qk_dot
@@ -393,10 +393,29 @@ class _SISOFunction(torch.autograd.Function):
 
     @staticmethod
     def _backward_kernels(ctx, gy):
-        """Kernel scans for the recurrence, autograd for the elementwise preprocessing in front of it."""
-        from ..backbones.mamba3.siso import _prepare
+        """Kernel scans for the recurrence; the preprocessing in front of it is differentiated by its own kernel on the
+        wide tensors (csrc/siso_prep.cu) and by autograd on the [b, l, h]-sized ones (trapezoid weights, rotary phase)."""
+        from ..backbones.mamba3.siso import _prepare, _prepare_small, _wide_kernels_ok
 
         Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D, states = ctx.saved_tensors
+        if _wide_kernels_ok(Q) and hasattr(ext(), "siso_prep_bwd"):
+            from .dispatch import KERNEL_LAUNCHES
+
+            small = [t.detach().requires_grad_(True) for t in (ADT, DT, Trap, Angles)]
+            with torch.enable_grad():
+                adt, gamma, scale, theta = _prepare_small(*small, torch.float32)
+            wide = (Q.contiguous(), K.to(Q.dtype).contiguous(), Q_bias.float().contiguous(), K_bias.float().contiguous(),
+                    theta.detach().contiguous(), gamma.detach().contiguous(), scale.detach().contiguous())
+            Qr, Kr, qk_dot = ext().siso_prep_fwd(*wide)
+            skip = qk_dot + D.float()[None, None]
+            dQr, dKr, dadt, dskip, dV = siso_core_backward(Qr, Kr, adt.detach(), skip, V, gy, fwd_states=states)
+            gQ, gK, gQb, gKb, dtheta, dgamma, dscale = ext().siso_prep_bwd(*wide, dQr.float().contiguous(), dKr.float().contiguous(),
+                                                                            dskip.float().contiguous())
+            KERNEL_LAUNCHES["count"] += 2
+            gADT, gDT, gTrap, gAng = torch.autograd.grad([adt, theta, gamma, scale], small, [dadt, dtheta, dgamma, dscale],
+                                                         allow_unused=True)
+            return (gQ.to(Q.dtype), gK.to(K.dtype), dV.to(V.dtype), gADT, gDT, gTrap, gQb.to(Q_bias.dtype), gKb.to(K_bias.dtype), gAng,
+                    dskip.sum((0, 1)).to(D.dtype))
         pre = [t.detach().requires_grad_(True) for t in (Q, K, ADT, DT, Trap, Q_bias, K_bias, Angles)]
         with torch.enable_grad():
             Qr, Kr, adt, qk_dot = _prepare(pre[0], pre[1], V, pre[2], pre[3], pre[4], pre[5], pre[6], pre[7], torch.float32)

@@ -182,6 +182,42 @@ def test_siso_backward_kernels_match_autograd_of_the_recurrence(b, l, h, g):
         assert err <= 3e-2, f"{name}: relative error {err:.3e}"
 
 
+@pytest.mark.parametrize("dtype,g,n_angles", [(torch.float32, 2, 32), (torch.bfloat16, 1, 64), (torch.float32, 4, 5)])
+def test_siso_preprocessing_kernels_match_the_pytorch_form(dtype, g, n_angles):
+    """Forward and every gradient of the wide preprocessing (bias, qk dot, rotary turn, trapezoid scale) against autograd
+    through the PyTorch form in fp64."""
+    from lbi_b200.backbones.mamba3.siso import _WidePrepFunction, _rotate_pairs
+
+    b, l, h, n = 2, 77, 4, 128
+    gen = torch.Generator(device=DEV).manual_seed(17 + n_angles)
+    Q = torch.randn(b, l, g, n, device=DEV, generator=gen).to(dtype)
+    K = torch.randn(b, l, g, n, device=DEV, generator=gen).to(dtype)
+    Qb, Kb = torch.randn(h, n, device=DEV, generator=gen) * 0.3, torch.randn(h, n, device=DEV, generator=gen) * 0.3
+    theta = torch.rand(b, l, h, n_angles, device=DEV, generator=gen) * 6.28
+    gamma = torch.rand(b, l, h, device=DEV, generator=gen) + 0.1
+    scale = torch.rand(b, l, h, device=DEV, generator=gen) + 0.1
+    leaves = [t.clone().requires_grad_(True) for t in (Q, K, Qb, Kb, theta, gamma, scale)]
+    qr, kr, qk = _WidePrepFunction.apply(*leaves)
+    gq, gk, gd = torch.randn(b, l, h, n, device=DEV, generator=gen), torch.randn(b, l, h, n, device=DEV, generator=gen), \
+        torch.randn(b, l, h, device=DEV, generator=gen)
+    # cotangents go in as fp32 through the kernel entry point (autograd would round them to the bf16 outputs' dtype)
+    got = ops.ext().siso_prep_bwd(Q.contiguous(), K.contiguous(), Qb, Kb, theta, gamma, scale, gq, gk, gd)
+    ref = [t.detach().double().requires_grad_(True) for t in (Q, K, Qb, Kb, theta, gamma, scale)]
+    rep = h // g
+    Qh = ref[0].repeat_interleave(rep, dim=2) + ref[2][None, None]
+    Kh = ref[1].repeat_interleave(rep, dim=2) + ref[3][None, None]
+    want_qk = ref[5] * (Qh * Kh).sum(-1)
+    want_qr = _rotate_pairs(Qh, ref[4])
+    want_kr = _rotate_pairs(Kh, ref[4]) * ref[6].unsqueeze(-1)
+    want = torch.autograd.grad([want_qr, want_kr, want_qk], ref, [gq.double(), gk.double(), gd.double()])
+    assert qr.dtype == torch.bfloat16 and (qr.double() - want_qr).abs().max().item() <= 2e-2 * want_qr.abs().max().item()
+    assert (kr.double() - want_kr).abs().max().item() <= 2e-2 * want_kr.abs().max().item()
+    assert (qk.double() - want_qk).abs().max().item() <= 1e-4 * want_qk.abs().max().item()
+    for name, a_, w_ in zip("dQ dK dQ_bias dK_bias dtheta dgamma dscale".split(), got, want):
+        err = (a_.double() - w_).norm().item() / w_.norm().item()
+        assert err <= 2e-4, f"{name}: {err:.2e}"
+
+
 @pytest.mark.parametrize("backbone,d_state", [("mamba2", 64), ("mamba3", 128)])
 def test_mamba_lbi_model_trains_through_the_kernels(backbone, d_state, monkeypatch):
     """An LBI model with a Mamba backbone on the GPU under bf16 autocast: the kernel path and the PyTorch path give the
