@@ -132,7 +132,7 @@ class Mamba3(nn.Module):
             Trap=trap_t,
             Q_bias=self.C_bias.squeeze(1),
             K_bias=self.B_bias.squeeze(1),
-            Angles=angles_h,
+            Angles=angles.unsqueeze(-2),   # [b, l, 1, s]: the same angles for every head, broadcast against dt
             D=self.D,
             Z=None if self.is_outproj_norm else z,
         )

@@ -81,11 +81,12 @@ int lbi_siso_prep_fwd(const void* q, const void* k, const float* q_bias, const f
                       int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
 // Backward from dqr, dkr [tokens, heads, 128] fp32 and dqk [tokens, heads]: dq, dk [tokens, groups, 128] fp32, dtheta, dgamma,
 // dscale, and bias_partials [lbi_siso_prep_blocks(tokens * groups)][2][heads][128] (summed by the caller: dq_bias, dk_bias).
+// tokens = batch * seq_len.  dkr_pad > 0: dkr is [batch, dkr_pad, heads, 128] in reversed time, as the reversed scan left it.
 int lbi_siso_prep_blocks(int64_t rows);
 int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
                       const float* gamma, const float* scale, const float* dqr, const float* dkr, const float* dqk, float* dq,
-                      float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials, int64_t tokens, int groups,
-                      int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
+                      float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials, int64_t tokens, int seq_len,
+                      int dkr_pad, int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
 
 // ---- interface Jacobian products over a basis (interface_jac.cu) -----------------------------------------
 // out[b, p, :] = (((in_scale * g[b, p, :]) @ wa) o d[b, :]) @ wb;  g [B, P, din], wa [din, hidden], d [B, hidden] or null,

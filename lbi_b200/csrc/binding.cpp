@@ -347,7 +347,8 @@ std::tuple<Tensor, Tensor, Tensor> siso_prep_fwd(const Tensor& q, const Tensor& 
 
 // -> (dq, dk [B, L, G, 128] fp32, dq_bias, dk_bias [H, 128], dtheta [B, L, H, S], dgamma, dscale [B, L, H])
 std::vector<Tensor> siso_prep_bwd(const Tensor& q, const Tensor& k, const Tensor& q_bias, const Tensor& k_bias, const Tensor& theta,
-                                  const Tensor& gamma, const Tensor& scale, const Tensor& dqr, const Tensor& dkr, const Tensor& dqk) {
+                                  const Tensor& gamma, const Tensor& scale, const Tensor& dqr, const Tensor& dkr, const Tensor& dqk,
+                                  bool dkr_reversed) {
   CHECK_F32(q_bias);
   CHECK_F32(k_bias);
   CHECK_F32(theta);
@@ -361,9 +362,16 @@ std::vector<Tensor> siso_prep_bwd(const Tensor& q, const Tensor& k, const Tensor
               "siso_prep_bwd: q, k must be contiguous [B, L, G, 128] bf16 / fp32");
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t batch = q.size(0), seq = q.size(1), groups = q.size(2), heads = q_bias.size(0), na = theta.size(3);
-  TORCH_CHECK(dqr.numel() == batch * seq * heads * 128 && dkr.numel() == dqr.numel() && dqk.numel() == batch * seq * heads &&
-                  theta.numel() == batch * seq * heads * na,
+  TORCH_CHECK(dqr.numel() == batch * seq * heads * 128 && dqk.numel() == batch * seq * heads && theta.numel() == batch * seq * heads * na,
               "siso_prep_bwd: shape mismatch");
+  int64_t dkr_pad = 0;
+  if (dkr_reversed) {
+    TORCH_CHECK(dkr.dim() == 4 && dkr.size(0) == batch && dkr.size(1) >= seq && dkr.size(2) == heads && dkr.size(3) == 128,
+                "siso_prep_bwd: reversed dkr must be [B, Lp >= L, H, 128]");
+    dkr_pad = dkr.size(1);
+  } else {
+    TORCH_CHECK(dkr.numel() == dqr.numel(), "siso_prep_bwd: dkr must match dqr");
+  }
   auto f32 = gamma.options();
   Tensor dq = torch::empty({batch, seq, groups, 128}, f32), dk = torch::empty_like(dq);
   Tensor dtheta = torch::empty({batch, seq, heads, na}, f32);
@@ -373,8 +381,8 @@ std::vector<Tensor> siso_prep_bwd(const Tensor& q, const Tensor& k, const Tensor
   check(lbi_siso_prep_bwd(q.data_ptr(), k.data_ptr(), q_bias.data_ptr<float>(), k_bias.data_ptr<float>(), theta.data_ptr<float>(),
                           gamma.data_ptr<float>(), scale.data_ptr<float>(), dqr.data_ptr<float>(), dkr.data_ptr<float>(),
                           dqk.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dtheta.data_ptr<float>(),
-                          dgamma.data_ptr<float>(), dscale.data_ptr<float>(), partials.data_ptr<float>(), batch * seq, (int)groups,
-                          (int)heads, 128, (int)na, q.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+                          dgamma.data_ptr<float>(), dscale.data_ptr<float>(), partials.data_ptr<float>(), batch * seq, (int)seq,
+                          (int)dkr_pad, (int)groups, (int)heads, 128, (int)na, q.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
         "siso_prep_bwd");
   Tensor bias = partials.sum(0);
   return {dq, dk, bias.select(0, 0), bias.select(0, 1), dtheta, dgamma, dscale};
@@ -886,7 +894,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("matrix_norms", &matrix_norms);
   m.def("interface_mlp_jac", &interface_mlp_jac);
   m.def("siso_prep_fwd", &siso_prep_fwd);
-  m.def("siso_prep_bwd", &siso_prep_bwd);
+  m.def("siso_prep_bwd", &siso_prep_bwd, py::arg("q"), py::arg("k"), py::arg("q_bias"), py::arg("k_bias"), py::arg("theta"),
+        py::arg("gamma"), py::arg("scale"), py::arg("dqr"), py::arg("dkr"), py::arg("dqk"), py::arg("dkr_reversed") = false);
   m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);
   m.def("gated_rmsnorm_bwd", &gated_rmsnorm_bwd);
   m.def("layernorm_jac", &layernorm_jac);

@@ -107,7 +107,8 @@ __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, c
                                                       float* __restrict__ dq, float* __restrict__ dk, float* __restrict__ dtheta,
                                                       float* __restrict__ dgamma, float* __restrict__ dscale,
                                                       float* __restrict__ bias_partials, int64_t rows, int groups, int heads,
-                                                      int n_angles) {
+                                                      int n_angles, int seq_len, int dkr_pad) {
+  // dkr_pad > 0: dkr is [batch, dkr_pad, heads, N] in reversed time (token l of a sequence sits in row dkr_pad - 1 - l)
   extern __shared__ float bias_acc[];   // [2][heads][N]
   const int lane = threadIdx.x & 31;
   const int rep = heads / groups;
@@ -126,7 +127,8 @@ __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, c
       const float4 kh = make_float4(kg.x + kb.x, kg.y + kb.y, kg.z + kb.z, kg.w + kb.w);
       const Rot rot = load_rot(theta + hrow * n_angles, lane, n_angles);
       const float sc = scale[hrow], gm = gamma[hrow], dd = dqk[hrow];
-      const float4 gq = ld4<float>(dqr + hrow * N + lane * 4), gk = ld4<float>(dkr + hrow * N + lane * 4);
+      const int64_t krow = dkr_pad > 0 ? ((tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len)) * heads + h : hrow;
+      const float4 gq = ld4<float>(dqr + hrow * N + lane * 4), gk = ld4<float>(dkr + krow * N + lane * 4);
       const float4 qo = rotate(qh, rot), ko = rotate(kh, rot);   // ko without the scale
       // angle gradients: J (a, b) = (-b, a) applied to the rotated pair
       const float dth0 = (-gq.x * qo.y + gq.y * qo.x) + sc * (-gk.x * ko.y + gk.y * ko.x);
@@ -190,8 +192,10 @@ extern "C" int lbi_siso_prep_fwd(const void* q, const void* k, const float* q_bi
 extern "C" int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
                                  const float* gamma, const float* scale, const float* dqr, const float* dkr, const float* dqk,
                                  float* dq, float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials,
-                                 int64_t tokens, int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t st) {
+                                 int64_t tokens, int seq_len, int dkr_pad, int groups, int heads, int d_state, int n_angles, int is_bf16,
+                                 cudaStream_t st) {
   using namespace lbi::sisoprep;
+  if (seq_len <= 0 || tokens % seq_len != 0 || (dkr_pad > 0 && dkr_pad < seq_len)) return (int)cudaErrorInvalidValue;
   if (d_state != N || tokens <= 0 || groups <= 0 || heads % groups != 0 || n_angles < 0 || 2 * n_angles > N) return (int)cudaErrorInvalidValue;
   const int64_t rows = tokens * groups;
   const int blocks = grid_for(rows);
@@ -203,12 +207,13 @@ extern "C" int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bi
     if (rc) return rc;
     bwd_kernel<__nv_bfloat16><<<blocks, THREADS, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, q_bias, k_bias, theta, gamma,
                                                             scale, dqr, dkr, dqk, dq, dk, dtheta, dgamma, dscale, bias_partials, rows,
-                                                            groups, heads, n_angles);
+                                                            groups, heads, n_angles, seq_len, dkr_pad);
   } else {
     rc = (int)cudaFuncSetAttribute(bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (rc) return rc;
     bwd_kernel<float><<<blocks, THREADS, smem, st>>>((const float*)q, (const float*)k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk,
-                                                    dq, dk, dtheta, dgamma, dscale, bias_partials, rows, groups, heads, n_angles);
+                                                    dq, dk, dtheta, dgamma, dscale, bias_partials, rows, groups, heads, n_angles, seq_len,
+                                                    dkr_pad);
   }
   return (int)cudaGetLastError();
 }

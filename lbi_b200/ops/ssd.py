@@ -349,7 +349,7 @@ def _siso_forward_kernels(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D):
     return y[:, :seqlen], final, states
 
 
-def siso_core_backward(Qr, Kr, adt, skip, V, gy, ops=KernelScans, fwd_states=None):
+def siso_core_backward(Qr, Kr, adt, skip, V, gy, ops=KernelScans, fwd_states=None, keep_dkr_reversed=False):
     """Gradients of y_t = sum_{s < t} e^{c_t - c_s} (Qr_t . Kr_s) V_s + skip_t V_t with respect to the preprocessed operands.
 
     Qr, Kr [b, l, h, 128]; adt, skip [b, l, h]; V, gy [b, l, h, 64].  Three strict scans with permuted roles:
@@ -367,14 +367,17 @@ def siso_core_backward(Qr, Kr, adt, skip, V, gy, ops=KernelScans, fwd_states=Non
     a_rev = _shift_reverse(af)
     nv = n // 64
     rep_v = lambda t: t.repeat_interleave(nv, dim=2)  # noqa: E731
-    y1, _, rev_states = ops.scan(gyf.flip(1), Qf.flip(1), Kf.flip(1), a_rev, None, None, strict=True, per_head=True)
+    gy_r, Q_r, K_r, V_r = gyf.flip(1), Qf.flip(1), Kf.flip(1), Vf.flip(1)                # time-reversed operands, flipped once
+    y1, _, rev_states = ops.scan(gy_r, Q_r, K_r, a_rev, None, None, strict=True, per_head=True)
     dV = y1.flip(1)[:, :seqlen] + skip.float()[..., None] * gy.float()
     dadt = ops.decay_grad(Vf, gyf, Kf, Qf, af, None, states_in=fwd_states, states_cot_rev=rev_states, per_head=True)[:, :seqlen]
     y2 = ops.scan(_blocks(Kf, nv), Vf, gyf, rep_v(af), None, None, strict=True)[0]
     dQr = y2.reshape(bsz, seqlen + pad, h, n)
-    y3 = ops.scan(_blocks(Qf, nv).flip(1), gyf.flip(1), Vf.flip(1), rep_v(a_rev), None, None, strict=True)[0]
-    dKr = y3.flip(1).reshape(bsz, seqlen + pad, h, n)
+    y3 = ops.scan(_blocks(Q_r, nv), gy_r, V_r, rep_v(a_rev), None, None, strict=True)[0]
     dskip = (gy.float() * V.float()).sum(-1)
+    if keep_dkr_reversed:   # the caller reads it backwards (token l of the result is row seqlen + pad - 1 - l)
+        return dQr[:, :seqlen], y3.reshape(bsz, seqlen + pad, h, n), dadt, dskip, dV
+    dKr = y3.flip(1).reshape(bsz, seqlen + pad, h, n)
     return dQr[:, :seqlen], dKr[:, :seqlen], dadt, dskip, dV
 
 
@@ -408,9 +411,10 @@ class _SISOFunction(torch.autograd.Function):
                     theta.detach().contiguous(), gamma.detach().contiguous(), scale.detach().contiguous())
             Qr, Kr, qk_dot = ext().siso_prep_fwd(*wide)
             skip = qk_dot + D.float()[None, None]
-            dQr, dKr, dadt, dskip, dV = siso_core_backward(Qr, Kr, adt.detach(), skip, V, gy, fwd_states=states)
-            gQ, gK, gQb, gKb, dtheta, dgamma, dscale = ext().siso_prep_bwd(*wide, dQr.float().contiguous(), dKr.float().contiguous(),
-                                                                            dskip.float().contiguous())
+            dQr, dKr_rev, dadt, dskip, dV = siso_core_backward(Qr, Kr, adt.detach(), skip, V, gy, fwd_states=states,
+                                                               keep_dkr_reversed=True)
+            gQ, gK, gQb, gKb, dtheta, dgamma, dscale = ext().siso_prep_bwd(*wide, dQr.float().contiguous(), dKr_rev.float().contiguous(),
+                                                                            dskip.float().contiguous(), True)
             KERNEL_LAUNCHES["count"] += 2
             gADT, gDT, gTrap, gAng = torch.autograd.grad([adt, theta, gamma, scale], small, [dadt, dtheta, dgamma, dscale],
                                                          allow_unused=True)

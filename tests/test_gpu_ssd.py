@@ -216,6 +216,12 @@ def test_siso_preprocessing_kernels_match_the_pytorch_form(dtype, g, n_angles):
     for name, a_, w_ in zip("dQ dK dQ_bias dK_bias dtheta dgamma dscale".split(), got, want):
         err = (a_.double() - w_).norm().item() / w_.norm().item()
         assert err <= 2e-4, f"{name}: {err:.2e}"
+    # dKr handed over as the reversed scan leaves it: time-reversed and padded to a multiple of the chunk
+    pad = 128 - l % 128
+    gk_rev = torch.nn.functional.pad(gk, (0, 0, 0, 0, 0, pad)).flip(1).contiguous()
+    again = ops.ext().siso_prep_bwd(Q.contiguous(), K.contiguous(), Qb, Kb, theta, gamma, scale, gq, gk_rev, gd, True)
+    for a_, b_ in zip(got, again):
+        assert torch.allclose(a_, b_, rtol=1e-5, atol=1e-5)
 
 
 @pytest.mark.parametrize("backbone,d_state", [("mamba2", 64), ("mamba3", 128)])
