@@ -8,6 +8,7 @@
     python -m lbi_b200.benchmarks.profile_case --case attn_fwd  # causal attention forward B 4, H 16, T 4096
     python -m lbi_b200.benchmarks.profile_case --case ssd       # Mamba-2 SSD forward B 2, L 8192, 24 heads, d_state 64
     python -m lbi_b200.benchmarks.profile_case --case ssd_bwd   # SSD forward + backward (permuted scans, decay gradient, tails)
+    python -m lbi_b200.benchmarks.profile_case --case mamba_elementwise   # gated RMSNorm and SISO preprocessing, both directions
 
 Each case holds well under 2 GB on the device, touches more than the 126 MB L2, launches the kernel of interest a
 handful of times and exits.  Typical capture:
@@ -25,7 +26,7 @@ from lbi_b200 import ops
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd", "ssd_bwd"])
+    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd", "ssd_bwd", "mamba_elementwise"])
     ap.add_argument("--repeats", type=int, default=2)
     args = ap.parse_args()
     dev = "cuda"
@@ -100,6 +101,26 @@ def main() -> None:
         for _ in range(args.repeats):
             y = ssd_chunk_scan_cuda(x, dt, a, bm, cm, D=d)
             torch.autograd.grad(y, (x, dt, a, bm, cm, d), gy)
+    elif args.case == "mamba_elementwise":
+        from lbi_b200.backbones.mamba3.siso import _WidePrepFunction
+        from lbi_b200.backbones.norms import gated_rms_norm
+
+        b, l, h, n = 8, 4096, 24, 128
+        x = torch.randn(b, l, h * 64, device=dev).bfloat16().requires_grad_(True)
+        z = torch.randn(b, l, h * 64, device=dev).bfloat16().requires_grad_(True)
+        w = torch.ones(h * 64, device=dev, requires_grad=True)
+        gy = torch.randn(b, l, h * 64, device=dev).bfloat16()
+        q = torch.randn(b, l, 1, n, device=dev).bfloat16()
+        k = torch.randn(b, l, 1, n, device=dev).bfloat16()
+        qb, kb = torch.randn(h, n, device=dev), torch.randn(h, n, device=dev)
+        theta = torch.rand(b, l, h, 32, device=dev) * 6.28
+        gamma, scale = torch.rand(b, l, h, device=dev), torch.rand(b, l, h, device=dev)
+        dqr, dkr, dqk = torch.randn(b, l, h, n, device=dev), torch.randn(b, l, h, n, device=dev), torch.randn(b, l, h, device=dev)
+        for _ in range(args.repeats):
+            y = gated_rms_norm(x, w, eps=1e-5, z=z, norm_before_gate=True, group_size=64)
+            torch.autograd.grad(y, (x, z, w), gy)
+            _WidePrepFunction.apply(q, k, qb, kb, theta, gamma, scale)
+            ops.ext().siso_prep_bwd(q, k, qb, kb, theta, gamma, scale, dqr, dkr, dqk)
     else:
         mats = torch.randn(8, 32, 256, 256, device=dev) / 16
         for _ in range(args.repeats):
