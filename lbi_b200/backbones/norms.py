@@ -80,7 +80,7 @@ def gated_rms_norm(x, weight, *, eps, z=None, norm_before_gate=True, group_size=
         from lbi_b200.ops import ext, native_available
 
         gs = x.shape[-1] if group_size is None else int(group_size)
-        if native_available() and hasattr(ext(), "gated_rmsnorm_fwd") and gs <= 6144 and x.shape[-1] % gs == 0:
+        if native_available() and hasattr(ext(), "gated_rmsnorm_fwd") and x.shape[-1] <= 12288 and x.shape[-1] % gs == 0 and gs % 8 == 0:
             return _GatedRMSNormFunction.apply(x, z, weight, eps, gs, not norm_before_gate)
     return rms_norm_reference(x, weight, eps=eps, z=z, norm_before_gate=norm_before_gate, group_size=group_size)
 

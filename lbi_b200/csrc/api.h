@@ -67,8 +67,9 @@ int lbi_affine_suffix_scan(const float* mats, const float* offsets, const float*
 // (is_bf16) or fp32 [rows, dim]; weight fp32 [dim]; rstd [rows, dim / group_size] fp32.
 int lbi_gated_rmsnorm_fwd(const void* x, const void* z_or_null, const float* weight, void* y, float* rstd, int64_t rows, int dim,
                           int group_size, float eps, int gate_first, int is_bf16, cudaStream_t stream);
-// dw_partials holds lbi_gated_rmsnorm_slots(rows, dim, group_size) rows of dim floats; the caller sums them.
-int lbi_gated_rmsnorm_slots(int64_t rows, int dim, int group_size);
+// dw_partials holds lbi_gated_rmsnorm_slots(rows, dim, group_size, is_bf16) rows of dim floats; the caller sums them.
+// group_size must be a multiple of 8 (bf16) or 4 (fp32): every lane moves 16 bytes per access.
+int lbi_gated_rmsnorm_slots(int64_t rows, int dim, int group_size, int is_bf16);
 int lbi_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z_or_null, const float* weight, const float* rstd, void* dx,
                           void* dz_or_null, float* dw_partials, int64_t rows, int dim, int group_size, int gate_first,
                           int is_bf16, cudaStream_t stream);

@@ -307,7 +307,7 @@ std::tuple<Tensor, Tensor, Tensor> gated_rmsnorm_bwd(const Tensor& dy, const Ten
   TORCH_CHECK(!z || (z->is_contiguous() && z->sizes() == x.sizes() && z->scalar_type() == x.scalar_type()), "gated_rmsnorm_bwd: z must match x");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t rows = x.size(0), dim = x.size(1);
-  const int slots = lbi_gated_rmsnorm_slots(rows, (int)dim, (int)group_size);
+  const int slots = lbi_gated_rmsnorm_slots(rows, (int)dim, (int)group_size, x.scalar_type() == at::kBFloat16 ? 1 : 0);
   TORCH_CHECK(slots > 0, "gated_rmsnorm_bwd: bad shape");
   Tensor dx = torch::empty_like(x);
   Tensor dz = z ? torch::empty_like(x) : torch::empty({0}, x.options());

@@ -3,9 +3,11 @@
 //   u = x * silu(z)   (gate first, Mamba-2)      or   u = x                (gate last, Mamba-3; or no gate)
 //   y = u * rstd * w  with rstd = rsqrt(mean_group(u^2) + eps)             then  y *= silu(z)  when the gate comes last
 //
-// One warp owns one (row, group) at a time and walks rows with a fixed group, so that the weight gradient of its
-// columns accumulates privately (shared memory, one slice per warp) and leaves as one row of a partials buffer that
-// the caller sums: no atomics, deterministic.  Inputs and outputs are bf16 or fp32 (template), statistics fp32.
+// Every lane moves 16 bytes per access (8 bf16 or 4 fp32).  A group of `gs` elements is shared by LPG lanes (a power of
+// two, at most 32) that each walk IT vectors, so a warp holds 32 / LPG groups at a time and group statistics are
+// sub-warp shuffle reductions: a 64-wide group of the Mamba-3 norm takes 8 lanes and one access per lane and operand.
+// The weight gradient accumulates in shared memory per block and leaves as one row of a partials buffer that the
+// caller sums.  Statistics and arithmetic are fp32.
 // Replaces the reference's Triton pair _layer_norm_fwd_1pass_kernel / _layer_norm_bwd_kernel
 // (backbones/mamba2/ops/triton/layernorm_gated.py:45-271) for the RMS case without bias.
 #include "api.h"
@@ -18,160 +20,216 @@ constexpr int THREADS = 256;
 constexpr int WARPS = THREADS / 32;
 
 template <typename T>
-__device__ __forceinline__ float ldf(const T* p, int64_t i) {
-  return static_cast<float>(p[i]);
-}
+struct Vec;
 template <>
-__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) {
-  return __bfloat162float(p[i]);
-}
-template <typename T>
-__device__ __forceinline__ void stf(T* p, int64_t i, float v) {
-  p[i] = static_cast<T>(v);
-}
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+    const bf16x8 v = *reinterpret_cast<const bf16x8*>(p);
+    unpack8(v, f);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* f) { *reinterpret_cast<bf16x8*>(p) = pack8(f); }
+};
 template <>
-__device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, int64_t i, float v) {
-  p[i] = __float2bfloat16(v);
-}
+struct Vec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+};
 
 __device__ __forceinline__ float sigmoidf(float v) { return 1.f / (1.f + __expf(-v)); }
+
+__device__ __forceinline__ float group_sum(float v, int lpg) {
+  for (int off = lpg >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS) gated_rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ z,
                                                                     const float* __restrict__ w, T* __restrict__ y,
-                                                                    float* __restrict__ rstd_out, int64_t rows, int dim, int gs,
-                                                                    float eps, int gate_first) {
-  const int ngroups = dim / gs;
-  const int64_t vrows = rows * ngroups;
-  const int lane = threadIdx.x & 31;
-  for (int64_t vr = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); vr < vrows; vr += (int64_t)gridDim.x * WARPS) {
-    const int64_t base = (vr / ngroups) * dim + (vr % ngroups) * gs;
-    const int col0 = (int)(vr % ngroups) * gs;
+                                                                    float* __restrict__ rstd_out, int64_t vrows, int dim, int gs,
+                                                                    float eps, int gate_first, int lpg, int iters) {
+  constexpr int V = Vec<T>::N;
+  const int ngroups = dim / gs, gpw = 32 / lpg;
+  const int lane = threadIdx.x & 31, sub = lane / lpg, li = lane % lpg;
+  for (int64_t v0 = ((int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5)) * gpw; v0 < vrows; v0 += (int64_t)gridDim.x * WARPS * gpw) {
+    const int64_t vr = v0 + sub;
+    const bool live = vr < vrows;
+    const int g = live ? (int)(vr % ngroups) : 0;
+    const int64_t base = live ? (vr / ngroups) * dim + (int64_t)g * gs : 0;
     float ss = 0.f;
-    for (int c = lane; c < gs; c += 32) {
-      float u = ldf(x, base + c);
-      if (z && gate_first) {
-        const float zz = ldf(z, base + c);
-        u *= zz * sigmoidf(zz);
+    for (int it = 0; it < iters; ++it) {
+      const int c = (it * lpg + li) * V;
+      float xv[V], zv[V];
+      if (live) {
+        Vec<T>::load(x + base + c, xv);
+        if (z && gate_first) Vec<T>::load(z + base + c, zv);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const float u = (z && gate_first) ? xv[e] * zv[e] * sigmoidf(zv[e]) : xv[e];
+          ss = fmaf(u, u, ss);
+        }
       }
-      ss = fmaf(u, u, ss);
     }
-    const float rstd = rsqrtf(warp_sum(ss) / gs + eps);
-    if (lane == 0) rstd_out[vr] = rstd;
-    for (int c = lane; c < gs; c += 32) {
-      float u = ldf(x, base + c);
-      float gate = 1.f;
-      if (z) {
-        const float zz = ldf(z, base + c);
-        gate = zz * sigmoidf(zz);
+    const float rstd = rsqrtf(group_sum(ss, lpg) / gs + eps);
+    if (live && li == 0) rstd_out[vr] = rstd;
+    if (!live) continue;
+    for (int it = 0; it < iters; ++it) {
+      const int c = (it * lpg + li) * V;
+      float xv[V], zv[V], wv[V], o[V];
+      Vec<T>::load(x + base + c, xv);
+      if (z) Vec<T>::load(z + base + c, zv);
+#pragma unroll
+      for (int e = 0; e < V; e += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(w + g * gs + c + e);
+        wv[e] = t.x; wv[e + 1] = t.y; wv[e + 2] = t.z; wv[e + 3] = t.w;
       }
-      if (z && gate_first) u *= gate;
-      float o = u * rstd * w[col0 + c];
-      if (z && !gate_first) o *= gate;
-      stf(y, base + c, o);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float gate = z ? zv[e] * sigmoidf(zv[e]) : 1.f;
+        const float u = (z && gate_first) ? xv[e] * gate : xv[e];
+        o[e] = u * rstd * wv[e] * ((z && !gate_first) ? gate : 1.f);
+      }
+      Vec<T>::store(y + base + c, o);
     }
   }
 }
 
-// dw_partials [gridDim.x * WARPS / ngroups, dim]: slot s of group g holds the sum over the rows walked by that warp.
+// dw_partials [gridDim.x][dim]
 template <typename T>
 __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                                                     const T* __restrict__ z, const float* __restrict__ w,
                                                                     const float* __restrict__ rstd_in, T* __restrict__ dx,
                                                                     T* __restrict__ dz, float* __restrict__ dw_partials,
-                                                                    int64_t rows, int dim, int gs, int gate_first) {
-  extern __shared__ float dw_acc[];   // [WARPS][gs]
-  const int ngroups = dim / gs;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float* acc = dw_acc + (int64_t)warp * gs;
-  for (int c = lane; c < gs; c += 32) acc[c] = 0.f;
-  const int64_t gw = (int64_t)blockIdx.x * WARPS + warp;          // the launch makes the warp count a multiple of ngroups
-  const int g = (int)(gw % ngroups);
-  const int64_t slot = gw / ngroups, nslots = (int64_t)gridDim.x * WARPS / ngroups;
-  const int col0 = g * gs;
-  for (int64_t row = slot; row < rows; row += nslots) {
-    const int64_t base = row * dim + col0;
-    const float rstd = rstd_in[row * ngroups + g];
+                                                                    int64_t vrows, int dim, int gs, int gate_first, int lpg,
+                                                                    int iters) {
+  constexpr int V = Vec<T>::N;
+  extern __shared__ float dw_acc[];   // [dim]
+  for (int i = threadIdx.x; i < dim; i += THREADS) dw_acc[i] = 0.f;
+  __syncthreads();
+  const int ngroups = dim / gs, gpw = 32 / lpg;
+  const int lane = threadIdx.x & 31, sub = lane / lpg, li = lane % lpg;
+  for (int64_t v0 = ((int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5)) * gpw; v0 < vrows; v0 += (int64_t)gridDim.x * WARPS * gpw) {
+    const int64_t vr = v0 + sub;
+    const bool live = vr < vrows;
+    const int g = live ? (int)(vr % ngroups) : 0;
+    const int64_t base = live ? (vr / ngroups) * dim + (int64_t)g * gs : 0;
+    const float rstd = live ? rstd_in[vr] : 0.f;
     float dot = 0.f;
-    for (int c = lane; c < gs; c += 32) {
-      float u = ldf(x, base + c), dyn = ldf(dy, base + c);
-      if (z) {
-        const float zz = ldf(z, base + c);
-        const float gate = zz * sigmoidf(zz);
-        if (gate_first) u *= gate; else dyn *= gate;
+    for (int it = 0; it < iters; ++it) {
+      const int c = (it * lpg + li) * V;
+      if (live) {
+        float xv[V], zv[V], gv[V];
+        Vec<T>::load(x + base + c, xv);
+        Vec<T>::load(dy + base + c, gv);
+        if (z) Vec<T>::load(z + base + c, zv);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          float u = xv[e], dyn = gv[e];
+          if (z) {
+            const float gate = zv[e] * sigmoidf(zv[e]);
+            if (gate_first) u *= gate; else dyn *= gate;
+          }
+          dot = fmaf(dyn * w[g * gs + c + e], u * rstd, dot);
+        }
       }
-      dot = fmaf(dyn * w[col0 + c], u * rstd, dot);
     }
-    const float mean_gu = warp_sum(dot) / gs;
-    for (int c = lane; c < gs; c += 32) {
-      const float xv = ldf(x, base + c), dyv = ldf(dy, base + c), wv = w[col0 + c];
-      float u = xv, dyn = dyv, gate = 1.f, dgate = 0.f;
-      if (z) {
-        const float zz = ldf(z, base + c);
-        const float sg = sigmoidf(zz);
-        gate = zz * sg;
-        dgate = sg * (1.f + zz * (1.f - sg));
-        if (gate_first) u *= gate; else dyn *= gate;
+    const float mean_gu = group_sum(dot, lpg) / gs;
+    if (!live) continue;
+    for (int it = 0; it < iters; ++it) {
+      const int c = (it * lpg + li) * V;
+      float xv[V], zv[V], gv[V], ox[V], oz[V];
+      Vec<T>::load(x + base + c, xv);
+      Vec<T>::load(dy + base + c, gv);
+      if (z) Vec<T>::load(z + base + c, zv);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        const float wv = w[g * gs + c + e];
+        float u = xv[e], dyn = gv[e], gate = 1.f, dgate = 0.f;
+        if (z) {
+          const float sg = sigmoidf(zv[e]);
+          gate = zv[e] * sg;
+          dgate = sg * (1.f + zv[e] * (1.f - sg));
+          if (gate_first) u *= gate; else dyn *= gate;
+        }
+        const float uhat = u * rstd;
+        atomicAdd(dw_acc + g * gs + c + e, dyn * uhat);
+        const float du = rstd * (dyn * wv - uhat * mean_gu);
+        if (z && gate_first) {
+          ox[e] = du * gate;
+          oz[e] = du * xv[e] * dgate;
+        } else {
+          ox[e] = du;
+          oz[e] = gv[e] * uhat * wv * dgate;
+        }
       }
-      const float uhat = u * rstd;
-      acc[c] = fmaf(dyn, uhat, acc[c]);
-      const float du = rstd * (dyn * wv - uhat * mean_gu);
-      if (z && gate_first) {
-        stf(dx, base + c, du * gate);
-        stf(dz, base + c, du * xv * dgate);
-      } else {
-        stf(dx, base + c, du);
-        if (z) stf(dz, base + c, dyv * uhat * wv * dgate);
-      }
+      Vec<T>::store(dx + base + c, ox);
+      if (z) Vec<T>::store(dz + base + c, oz);
     }
   }
-  __syncwarp();
-  for (int c = lane; c < gs; c += 32) dw_partials[slot * dim + col0 + c] = acc[c];
+  __syncthreads();
+  float* out = dw_partials + (int64_t)blockIdx.x * dim;
+  for (int i = threadIdx.x; i < dim; i += THREADS) out[i] = dw_acc[i];
 }
 
-static int grid_for(int64_t rows, int ngroups, int* nslots) {
-  // warps per grid: a multiple of ngroups and of WARPS, about two CTAs per SM, never more slots than rows
-  int64_t slots = (2 * 148 * WARPS + ngroups - 1) / ngroups;
-  if (slots > rows) slots = rows;
-  if (slots < 1) slots = 1;
-  int64_t warps = slots * ngroups;
-  while (warps % WARPS != 0) warps += ngroups, ++slots;
-  *nslots = (int)slots;
-  return (int)(warps / WARPS);
+// lanes per group: the largest power of two <= 32 that divides the number of 16-byte vectors of a group
+static bool plan(int gs, int vec, int* lpg, int* iters) {
+  if (gs % vec != 0) return false;
+  const int nvec = gs / vec;
+  int l = 32;
+  while (l > 1 && nvec % l != 0) l >>= 1;
+  *lpg = l;
+  *iters = nvec / l;
+  return true;
+}
+
+static int grid_for(int64_t vrows, int lpg) {
+  const int64_t per_block = (int64_t)WARPS * (32 / lpg);
+  int64_t blocks = (vrows + per_block - 1) / per_block;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  return (int)(blocks < 1 ? 1 : blocks);
 }
 
 template <typename T>
 static int fwd(const void* x, const void* z, const float* w, void* y, float* rstd, int64_t rows, int dim, int gs, float eps,
                int gate_first, cudaStream_t st) {
-  const int ngroups = dim / gs;
-  int64_t blocks = (rows * ngroups + WARPS - 1) / WARPS;
-  if (blocks > 148 * 8) blocks = 148 * 8;
-  gated_rmsnorm_fwd_kernel<T><<<(unsigned)blocks, THREADS, 0, st>>>((const T*)x, (const T*)z, w, (T*)y, rstd, rows, dim, gs, eps,
-                                                                   gate_first);
+  int lpg, iters;
+  if (!plan(gs, Vec<T>::N, &lpg, &iters)) return (int)cudaErrorInvalidValue;
+  const int64_t vrows = rows * (dim / gs);
+  gated_rmsnorm_fwd_kernel<T><<<grid_for(vrows, lpg), THREADS, 0, st>>>((const T*)x, (const T*)z, w, (T*)y, rstd, vrows, dim, gs, eps,
+                                                                        gate_first, lpg, iters);
   return (int)cudaGetLastError();
 }
 
 template <typename T>
 static int bwd(const void* dy, const void* x, const void* z, const float* w, const float* rstd, void* dx, void* dz,
                float* dw_partials, int64_t rows, int dim, int gs, int gate_first, cudaStream_t st) {
-  int nslots = 0;
-  const int blocks = grid_for(rows, dim / gs, &nslots);
-  const size_t smem = (size_t)WARPS * gs * sizeof(float);
+  int lpg, iters;
+  if (!plan(gs, Vec<T>::N, &lpg, &iters)) return (int)cudaErrorInvalidValue;
+  const int64_t vrows = rows * (dim / gs);
+  const size_t smem = (size_t)dim * sizeof(float);
   int rc = (int)cudaFuncSetAttribute(gated_rmsnorm_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (rc) return rc;
-  gated_rmsnorm_bwd_kernel<T><<<blocks, THREADS, smem, st>>>((const T*)dy, (const T*)x, (const T*)z, w, rstd, (T*)dx, (T*)dz,
-                                                            dw_partials, rows, dim, gs, gate_first);
+  gated_rmsnorm_bwd_kernel<T><<<grid_for(vrows, lpg), THREADS, smem, st>>>((const T*)dy, (const T*)x, (const T*)z, w, rstd, (T*)dx, (T*)dz,
+                                                                           dw_partials, vrows, dim, gs, gate_first, lpg, iters);
   return (int)cudaGetLastError();
 }
 
 }  // namespace gnorm
 }  // namespace lbi
 
-extern "C" int lbi_gated_rmsnorm_slots(int64_t rows, int dim, int group_size) {
-  int nslots = 0;
-  if (rows <= 0 || dim <= 0 || group_size <= 0 || dim % group_size != 0) return 0;
-  lbi::gnorm::grid_for(rows, dim / group_size, &nslots);
-  return nslots;
+// Rows of the weight-gradient partials buffer for this shape (0: shape not supported).  The element size decides the
+// vector width, so the bf16 / fp32 answer can differ.
+extern "C" int lbi_gated_rmsnorm_slots(int64_t rows, int dim, int group_size, int is_bf16) {
+  using namespace lbi::gnorm;
+  int lpg, iters;
+  if (rows <= 0 || dim <= 0 || group_size <= 0 || dim % group_size != 0 || !plan(group_size, is_bf16 ? 8 : 4, &lpg, &iters)) return 0;
+  return grid_for(rows * (dim / group_size), lpg);
 }
 
 extern "C" int lbi_gated_rmsnorm_fwd(const void* x, const void* z_or_null, const float* weight, void* y, float* rstd, int64_t rows,
@@ -184,7 +242,7 @@ extern "C" int lbi_gated_rmsnorm_fwd(const void* x, const void* z_or_null, const
 extern "C" int lbi_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z_or_null, const float* weight, const float* rstd,
                                      void* dx, void* dz_or_null, float* dw_partials, int64_t rows, int dim, int group_size,
                                      int gate_first, int is_bf16, cudaStream_t st) {
-  if (rows <= 0 || dim <= 0 || group_size <= 0 || dim % group_size != 0 || group_size > 6144) return (int)cudaErrorInvalidValue;
+  if (rows <= 0 || dim <= 0 || group_size <= 0 || dim % group_size != 0 || dim > 12288) return (int)cudaErrorInvalidValue;
   return is_bf16 ? lbi::gnorm::bwd<__nv_bfloat16>(dy, x, z_or_null, weight, rstd, dx, dz_or_null, dw_partials, rows, dim, group_size,
                                                   gate_first, st)
                  : lbi::gnorm::bwd<float>(dy, x, z_or_null, weight, rstd, dx, dz_or_null, dw_partials, rows, dim, group_size,

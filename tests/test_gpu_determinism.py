@@ -2,7 +2,8 @@
 
 With no race detector available on the build machines, a kernel that reads a tile before its barrier completed, or
 that lets two warps write one word, shows up here as a result that changes between two runs on the same inputs.
-(The dD reduction of the SSD backward tail and split-K GEMM accumulate with atomics / TMA reduce-adds and are left out.)
+(The dD reduction of the SSD backward tail, the weight gradient of the gated norm and split-K GEMM accumulate with atomics /
+TMA reduce-adds and are left out.)
 """
 import pytest
 import torch
@@ -75,9 +76,9 @@ def test_norm_and_interface_kernels_repeat_bitwise():
     w = (torch.rand(256, device=DEV) + 0.5).requires_grad_(True)
     gy = torch.randn(4, 130, 256, device=DEV).bfloat16()
 
-    def fwd_bwd():
+    def fwd_bwd():   # the weight gradient is summed with shared-memory atomics (order not fixed) and is left out
         y = gated_rms_norm(x, w, eps=1e-5, z=z, norm_before_gate=False, group_size=64)
-        return (y.detach(), *torch.autograd.grad(y, (x, z, w), gy))
+        return (y.detach(), *torch.autograd.grad(y, (x, z, w), gy)[:2])
 
     _twice(fwd_bwd)
     head = vm.VectorMLPHead(160, 96, hidden_dim=128).to(DEV)
