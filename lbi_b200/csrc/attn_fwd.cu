@@ -18,6 +18,7 @@
 #include <mutex>
 
 #include "api_attn.h"
+#include "common.cuh"
 #include "tcgen05.cuh"
 
 namespace lbi {
@@ -331,11 +332,10 @@ extern "C" int lbi_attn_fwd(const void* qkv, void* out, float* lse, int batch, i
   p.scale_log2 = scale * 1.4426950408889634f;
   p.out = (__nv_bfloat16*)out; p.lse = lse; p.status = status;
   const size_t smem = sizeof(Smem) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static lbi::PerDeviceOnce configured;
+  {
+    cudaError_t e = configured.max_dynamic_smem(attn_fwd_kernel, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
   }
   dim3 grid((p.n_tiles + 1) / 2, batch * heads);
   attn_fwd_kernel<<<grid, THREADS, smem, st>>>(map, p);

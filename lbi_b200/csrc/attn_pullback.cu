@@ -39,6 +39,7 @@
 #include <mutex>
 
 #include "api_attn.h"
+#include "common.cuh"
 #include "tcgen05.cuh"
 
 namespace lbi {
@@ -772,11 +773,10 @@ template <bool DKDV>
 static int launch(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMap& mo, const Params& p, cudaStream_t st) {
   constexpr int PB = DKDV ? PB_DKDV : PB_DQ;
   const size_t smem = sizeof(Smem<DKDV>) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(pullback_kernel<DKDV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static lbi::PerDeviceOnce configured;
+  {
+    cudaError_t e = configured.max_dynamic_smem(pullback_kernel<DKDV>, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
   }
   dim3 grid(p.n_tiles, p.batch * p.heads, (p.nbasis + PB - 1) / PB);
   pullback_kernel<DKDV><<<grid, THREADS, smem, st>>>(mq, md, mo, p);

@@ -4,7 +4,27 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace lbi {
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (kernel, device) pair, so a process that drives several
+// GPUs has to set it once on each.  One static instance per kernel remembers which devices are done (bit per ordinal).
+struct PerDeviceOnce {
+  std::atomic<unsigned long long> done[4] = {};
+  template <typename Kernel>
+  cudaError_t max_dynamic_smem(Kernel kernel, int bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const bool tracked = dev >= 0 && dev < 256;
+    const unsigned long long bit = 1ull << (dev & 63);
+    if (tracked && (done[dev >> 6].load(std::memory_order_acquire) & bit)) return cudaSuccess;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && tracked) done[dev >> 6].fetch_or(bit, std::memory_order_release);
+    return e;
+  }
+};
 
 struct alignas(16) bf16x8 {
   __nv_bfloat162 v[4];

@@ -474,11 +474,10 @@ int lbi_rmsnorm_bwd(const void* d_normed, const float* x_stream, const float* rs
                                                                    (const float4*)weight, (const float4*)d_in, (float4*)d_out,
                                                                    (bf16x8*)d_out_lowp, rows, act_rows, dim);
   } else {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(rmsnorm_bwd_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);
+    static PerDeviceOnce configured;
+    {
+      cudaError_t e = configured.max_dynamic_smem(rmsnorm_bwd_kernel<256>, 64 * 1024);
       if (e != cudaSuccess) return (int)e;
-      configured = true;
     }
     rmsnorm_bwd_kernel<256><<<(unsigned)act_rows, 256, smem, st>>>((const bf16x8*)d_normed, (const float4*)x_stream, rstd,
                                                                    (const float4*)weight, (const float4*)d_in, (float4*)d_out,

@@ -18,6 +18,7 @@
 #include <mutex>
 
 #include "api_gemm.h"
+#include "common.cuh"
 #include "tcgen05.cuh"
 
 namespace lbi {
@@ -341,11 +342,10 @@ static int launch(const void* A, const void* B, void* C, int M, int N, int K, in
   if (ctas < 1) ctas = 1;
   if (ctas > tiles) ctas = tiles;
   const size_t smem = sizeof(Smem<BN>) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static lbi::PerDeviceOnce configured;
+  {
+    cudaError_t e = configured.max_dynamic_smem(gemm_kernel<BN>, (int)smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
   }
   dim3 grid(ctas, splits);
   gemm_kernel<BN><<<grid, THREADS, smem, st>>>(ma, mb, mc, p);
@@ -360,7 +360,14 @@ extern "C" int lbi_gemm_bf16(const void* A, const void* B, void* C, int M, int N
                              int* status, int sm_count, cudaStream_t st) {
   using namespace lbi::gemm;
   if (M <= 0 || N <= 0) return 0;
-  if (K <= 0) return 0;
+  if (K <= 0) {   // an empty sum: C = 0 unless the caller accumulates
+    if (!accumulate) {
+      const size_t esize = out_fp32 ? 4 : 2;
+      cudaError_t e = cudaMemset2DAsync(C, (size_t)ldc * esize, 0, (size_t)N * esize, (size_t)M, st);
+      if (e != cudaSuccess) return (int)e;
+    }
+    return 0;
+  }
   if (N > 128)
     return launch<256>(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_fp32, accumulate, splits, status,
                        sm_count, st);

@@ -410,7 +410,7 @@ class FastLBIEngine:
     @torch.no_grad()
     def _optimizer_step(self, lr: float) -> None:
         flat, comm = self.flat, self.comm
-        if hasattr(comm, "optimizer_step") and self.device.type == "cuda":
+        if hasattr(comm, "optimizer_step") and self.device.type == "cuda" and comm.fused_optimizer_ready(flat):
             comm.optimizer_step(flat, lr=lr, betas=self.betas, eps=self.eps, weight_decay=self.weight_decay,
                                 grad_clip=self.grad_clip)
             return
@@ -442,6 +442,49 @@ class FastLBIEngine:
                                      self.weight_decay, flat.step_count, scale, sh_shard)
         if comm.world_size > 1:
             comm.all_gather_flat(flat.shadow if flat.shadow is not None else flat.params, shard)
+
+    def _plan_master_sync(self) -> None:
+        """Runs of the flat layout that the engine reads from the fp32 master rather than from the compute-dtype shadow:
+        every interface parameter, every norm weight, bias and per-head scalar (all but the 2-D projection / embedding
+        matrices).  Adjacent slots are merged so that a step moves a few dozen contiguous pieces."""
+        runs: list[list[int]] = []
+        for name, slot in self.flat.slots.items():
+            matrix = len(slot.shape) == 2 and not name.startswith("interface.")
+            if matrix:
+                continue
+            lo, hi = slot.offset, slot.offset + slot.numel
+            if runs and lo - runs[-1][1] < 64:
+                runs[-1][1] = hi
+            else:
+                runs.append([lo, hi])
+        self._master_runs = [(a, b) for a, b in runs]
+        total = sum(b - a for a, b in self._master_runs)
+        self._master_buf = torch.zeros(total, dtype=torch.float32, device=self.device)
+
+    @torch.no_grad()
+    def _sync_fp32_read_params(self) -> None:
+        """Collective, after every optimizer step of a multi-rank run that keeps a low-precision shadow: a rank's AdamW
+        updates the fp32 master of its own shard only and the other shards arrive as shadow weights, so the parameters
+        that the engine reads in fp32 would otherwise go stale (and differ between ranks).  Their owners' fp32 values are
+        exchanged here through one compact buffer (zeros outside the owned part, summed over ranks)."""
+        if self.comm.world_size == 1 or self.flat.shadow is None:
+            return
+        if not hasattr(self, "_master_runs"):
+            self._plan_master_sync()
+        flat, buf = self.flat, self._master_buf
+        lo, hi = self.comm.rank * flat.shard, (self.comm.rank + 1) * flat.shard
+        buf.zero_()
+        pos = 0
+        for a, b in self._master_runs:
+            x, y = max(a, lo), min(b, hi)
+            if x < y:
+                buf[pos + x - a : pos + y - a].copy_(flat.params[x:y])
+            pos += b - a
+        self.comm.all_reduce_sum(buf)
+        pos = 0
+        for a, b in self._master_runs:
+            flat.params[a:b].copy_(buf[pos : pos + b - a])
+            pos += b - a
 
     # ------------------------------------------------------------------ public API
     def backward(self, input_ids: torch.Tensor, targets: torch.Tensor) -> StepResult:
@@ -477,6 +520,7 @@ class FastLBIEngine:
         result = self.backward(input_ids, targets)
         with nvtx.range("lbi/optimizer"):
             self._optimizer_step(self.lr if lr is None else lr)
+            self._sync_fp32_read_params()
         loss = result.loss.detach().clone()
         if self.comm.world_size > 1:
             self.comm.all_reduce_sum(loss)

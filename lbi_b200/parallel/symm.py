@@ -228,6 +228,12 @@ class SymmComm(CollectiveComm):
         self._flat_state = (g_ptrs, g_mc if self.use_multimem else 0, shadow_ptrs)
         self._setup_barrier()
 
+    def fused_optimizer_ready(self, flat) -> bool:
+        """The fused reduce-scatter + AdamW + all-gather kernels move the updated weights as the low-precision shadow.  A
+        run without one (fp32 activations) keeps its gradients in symmetric memory but takes the library-collective
+        optimizer step, which gathers the fp32 master itself."""
+        return self._flat_state is not None and self._flat_state[2] is not None
+
     def optimizer_step(self, flat, *, lr, betas, eps, weight_decay, grad_clip) -> None:
         g_ptrs, g_mc, shadow_ptrs = self._flat_state
         w, shard = self.world_size, flat.shard

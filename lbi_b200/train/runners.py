@@ -218,6 +218,22 @@ def _build_stepper(cfg, model, device, variant: str):
 
 # ----------------------------------------------------------------------------------------------------- the loop
 def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dict[str, Any]:
+    """Runs the loop with this rank's liveness published from a background thread (multi-process runs), so that a long
+    evaluation, a consolidated checkpoint save on rank 0 or a slow step never looks like a dead rank to the peers.  A rank
+    that hangs inside a step is caught by its own step watchdog; one that raises reports through ``fail/<rank>``."""
+    heartbeat, progress = None, {"step": -1}
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        heartbeat = Heartbeat.from_process_group(stale_after_s=float(os.environ.get("LBI_B200_HEARTBEAT_STALE_S", "120")))
+        heartbeat.start_background(interval_s=float(os.environ.get("LBI_B200_HEARTBEAT_EVERY_S", "1.0")),
+                                   step_fn=lambda: progress["step"])
+    try:
+        return _run_training_loop(cfg, run_dir=run_dir, variant=variant, heartbeat=heartbeat, progress=progress)
+    finally:
+        if heartbeat is not None:
+            heartbeat.stop()
+
+
+def _run_training_loop(cfg: LBITrainingConfig, *, run_dir: Path, variant: str, heartbeat, progress: dict) -> Dict[str, Any]:
     is_lbi = variant == LBI_VARIANT
     legacy_regime = LEGACY_LBI_REGIME if is_lbi else LEGACY_DENSE_REGIME
     device = _resolve_device(cfg)
@@ -280,11 +296,11 @@ def _run_training(cfg: LBITrainingConfig, *, run_dir: Path, variant: str) -> Dic
             best_val_ce_loss=best_val, best_val_step=best_val_step, extra=checkpoint_extra(**more)))
 
     injector = FaultInjector(rank=int(os.environ.get("RANK", "0")))
-    heartbeat = Heartbeat.from_process_group() if (torch.distributed.is_available() and torch.distributed.is_initialized()) else None
     window_t0, window_steps = time.perf_counter(), 0
     for step in range(start_step + 1, cfg.steps + 1):
         # between steps: nothing of this rank is in flight, so faults are injected and peers are checked here
         injector.at_step(step, heartbeat=heartbeat, checkpoint_path=Path(latest_path) if latest_path else None)
+        progress["step"] = step
         if heartbeat is not None:
             heartbeat.beat(step)
             heartbeat.check_peers()

@@ -218,11 +218,28 @@ def newest_loadable_checkpoint(run_dir: Path) -> Path | None:
     return None
 
 
+def _is_device_error(exc: BaseException) -> bool:
+    """True for errors raised by the accelerator runtime (never retried in-process)."""
+    accel = getattr(torch, "AcceleratorError", None)
+    if accel is not None and isinstance(exc, accel):
+        return True
+    if isinstance(exc, (KernelWaitTimeout, PeerFailure, StepTimeout, InjectedFault)):
+        return False
+    text = str(exc)
+    return isinstance(exc, RuntimeError) and ("CUDA error" in text or "cudaError" in text or "CUBLAS_STATUS" in text
+                                              or "NCCL error" in text)
+
+
 def run_with_recovery(train_fn: Callable[[Any], dict], cfg: Any, *, max_restarts: int = 2,
-                      retry_on: tuple[type[BaseException], ...] = (KernelWaitTimeout, PeerFailure, StepTimeout, InjectedFault,
-                                                                    RuntimeError)) -> dict:
+                      retry_on: tuple[type[BaseException], ...] = (KernelWaitTimeout, PeerFailure, StepTimeout,
+                                                                    InjectedFault)) -> dict:
     """Run ``train_fn(cfg)``; after a failure restart it with ``resume_from`` set to the newest loadable checkpoint of
-    the run (or from scratch when there is none).  The run directory must be stable (``cfg.run_name`` set)."""
+    the run (or from scratch when there is none).  The run directory must be stable (``cfg.run_name`` set).
+
+    Only the failures this module defines are retried by default.  A CUDA error (``torch.AcceleratorError``, a
+    ``RuntimeError`` from a launch, a sticky context error after a device fault) is never retried in-process, whatever
+    ``retry_on`` says: re-running the same kernels in the same context repeats the fault and hides shape or state-dict
+    bugs behind restarts, so it propagates and the launcher or an operator decides."""
     if not getattr(cfg, "run_name", ""):
         raise ValueError("run_with_recovery needs cfg.run_name so that restarts find the same run directory")
     attempt, failures = 0, []
@@ -232,6 +249,8 @@ def run_with_recovery(train_fn: Callable[[Any], dict], cfg: Any, *, max_restarts
             result["restarts"], result["failures"] = attempt, failures
             return result
         except retry_on as exc:  # noqa: PERF203
+            if _is_device_error(exc):
+                raise
             failures.append(f"{type(exc).__name__}: {exc}")
             attempt += 1
             if attempt > max_restarts:

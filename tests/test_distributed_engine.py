@@ -147,3 +147,50 @@ def test_basis_plan_is_balanced_and_complete():
     plan = FastLBIEngine.basis_plan(fake)
     assert [len(p) for p in plan] == [7] * 8
     assert all(len({k for k, _, _ in per_rank}) <= 2 for per_rank in plan) and {k for k, _, _ in plan[7]} == {6}
+
+
+def _bf16_worker(rank, world, port, out_dir, steps):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lbi_b200.parallel import CollectiveComm, FastLBIEngine
+
+        torch.set_num_threads(1)
+        engine = FastLBIEngine(_model("sequence", 4), lr=3e-2, grad_clip=1.0, basis_chunk=3, comm=CollectiveComm(),
+                               act_dtype=torch.bfloat16)
+        g = torch.Generator().manual_seed(5)
+        ids, tgt = torch.randint(0, 64, (2, 32), generator=g), torch.randint(0, 64, (2, 32), generator=g)
+        losses = [float(engine.step(ids, tgt)) for _ in range(steps)]
+        torch.save({"losses": losses, "params": engine.flat.params.clone(), "shadow": engine.flat.shadow.clone()},
+                   os.path.join(out_dir, f"bf16_rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_low_precision_shadow_run_keeps_every_rank_on_current_weights(tmp_path):
+    """With a bf16 shadow a rank's optimizer updates the fp32 master of its own shard only.  The parameters the engine
+    reads in fp32 (interface maps, norm weights) must still be current and identical on every rank after each step:
+    losses and fp32-read weights of a 2-rank run equal the single-process run over several steps."""
+    from lbi_b200.parallel import FastLBIEngine
+
+    steps = 4
+    mp.spawn(_bf16_worker, args=(2, _free_port(), str(tmp_path), steps), nprocs=2, join=True)
+    ranks = [torch.load(tmp_path / f"bf16_rank{r}.pt") for r in range(2)]
+    engine = FastLBIEngine(_model("sequence", 4), lr=3e-2, grad_clip=1.0, basis_chunk=3, act_dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(5)
+    ids, tgt = torch.randint(0, 64, (2, 32), generator=g), torch.randint(0, 64, (2, 32), generator=g)
+    single = [float(engine.step(ids, tgt)) for _ in range(steps)]
+    for r in range(2):
+        for a, b in zip(ranks[r]["losses"], single):
+            assert a == pytest.approx(b, rel=2e-3, abs=2e-3), (r, ranks[r]["losses"], single)
+    # both ranks hold the same fp32 values for every parameter the engine reads from the master copy
+    flat = engine.flat
+    for name, slot in flat.slots.items():
+        if len(slot.shape) == 2 and not name.startswith("interface."):
+            continue
+        a = ranks[0]["params"][slot.offset : slot.offset + slot.numel]
+        b = ranks[1]["params"][slot.offset : slot.offset + slot.numel]
+        ref = flat.params[slot.offset : slot.offset + slot.numel]
+        assert torch.equal(a, b), f"{name}: ranks disagree on an fp32-read parameter"
+        assert torch.allclose(a, ref, atol=2e-3, rtol=2e-2), f"{name}: drifted from the single-process run"
+    assert torch.equal(ranks[0]["shadow"], ranks[1]["shadow"])

@@ -128,3 +128,52 @@ def test_peer_failure_is_seen_on_the_host_before_the_next_launch(mode):
         assert results[1] == "injected" and "injected fault at step 2" in results[0]
     else:
         assert "silent" in results[0]
+
+
+def test_device_errors_and_plain_runtime_errors_are_not_retried(tmp_path):
+    calls = []
+
+    def cuda_fault(cfg):
+        calls.append("cuda")
+        raise F.KernelWaitTimeout("CUDA error: an illegal memory access was encountered")   # even a retryable class ...
+
+    def shape_bug(cfg):
+        calls.append("shape")
+        raise RuntimeError("size mismatch for blocks.0.weight")
+
+    # ... is retried only when it does not come from the device runtime; this one is one of ours, so it is retried
+    with pytest.raises(F.KernelWaitTimeout):
+        F.run_with_recovery(cuda_fault, _cfg(tmp_path), max_restarts=1)
+    assert calls == ["cuda", "cuda"]
+    calls.clear()
+    with pytest.raises(RuntimeError):
+        F.run_with_recovery(shape_bug, _cfg(tmp_path), max_restarts=2)
+    assert calls == ["shape"]          # a plain RuntimeError is not in the default retry set
+    calls.clear()
+
+    def launch_failure(cfg):
+        calls.append("launch")
+        raise RuntimeError("CUDA error: unspecified launch failure")
+
+    with pytest.raises(RuntimeError):
+        F.run_with_recovery(launch_failure, _cfg(tmp_path), max_restarts=2, retry_on=(RuntimeError,))
+    assert calls == ["launch"]         # never retried in-process, even when the caller widens retry_on
+
+
+def test_background_heartbeat_keeps_a_slow_rank_alive():
+    """A rank whose loop iteration takes longer than the staleness limit (evaluation, checkpoint save) still publishes
+    through its background thread, so the peer check of another rank does not raise."""
+    store = dist.HashStore()
+    slow = F.Heartbeat(store, rank=0, world_size=2, stale_after_s=0.4)
+    other = F.Heartbeat(store, rank=1, world_size=2, stale_after_s=0.4)
+    progress = {"step": 7}
+    slow.start_background(interval_s=0.05, step_fn=lambda: progress["step"])
+    try:
+        time.sleep(0.9)                # rank 0's main thread is "busy" for more than twice the limit
+        other.check_peers()            # must not raise
+        assert other.peer_states()[0]["step"] == 7
+    finally:
+        slow.stop()
+    time.sleep(0.6)                    # thread stopped: now the silence is real
+    with pytest.raises(F.PeerFailure):
+        other.check_peers()
