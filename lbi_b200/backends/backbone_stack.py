@@ -19,6 +19,17 @@ class BackboneStackRegionBackend(nn.Module):
         self.backbone_spec = backbone_spec
         self.region_ranges = [tuple(r) for r in region_ranges]
         self.backbone = build_backbone_stack(backbone_spec)
+        self._structured = None
+
+    @property
+    def structured(self):
+        """Closed-form lowering of the stack (forward with caches, basis pullback, parameter VJP without autograd); built
+        on first use.  Raises NotImplementedError for a block type that has none."""
+        if self._structured is None:
+            from .mamba_structured import StructuredMambaRegion
+
+            object.__setattr__(self, "_structured", StructuredMambaRegion(self.backbone.blocks))
+        return self._structured
 
     @property
     def blocks(self) -> nn.ModuleList:

@@ -108,19 +108,42 @@ class StructuredTransformerRegion:
         key = (dtype, str(device))
         cached = self._weights.get(key)
         if cached is None:
-            cached = [LayerWeights(b, dtype, self.want_transposes and device.type == "cuda", self.shadow_of) for b in self.blocks]
+            cached = [LayerWeights(b, dtype, self.want_transposes and device.type == "cuda", self.shadow_of) if hasattr(b, "attn") else None
+                      for b in self.blocks]   # None for the non-Transformer blocks of a hybrid stack
             self._weights[key] = cached
         return cached
 
     def refresh_weights(self) -> None:
         """Call after an optimizer step that did not update the compute-dtype copies in place."""
         for (dtype, dev), layers in self._weights.items():
-            for lw in layers:
+            for lw in filter(None, layers):
                 lw.refresh(dtype, self.want_transposes and dev.startswith("cuda"), self.shadow_of)
 
     def _dims(self, index: int):
         attn = self.blocks[index].attn
         return attn.n_heads, attn.n_kv_heads, attn.head_dim, attn.scale, attn.rope_base, attn.rope_interleaved
+
+    # ------------------------------------------------------------------ one block, forward
+    @torch.no_grad()
+    def layer_forward(self, index: int, branch: torch.Tensor, stream: torch.Tensor | None, bsz: int, seqlen: int, dtype: torch.dtype):
+        """(branch, fp32 stream or None) entering block ``index`` -> (branch, stream, LayerCache) leaving it."""
+        lw = self.weights(dtype)[index]
+        heads, kv_heads, head_dim, scale, rope_base, interleaved = self._dims(index)
+        cos, sin = rope_tables(seqlen, head_dim, rope_base, branch.device)
+        normed1, stream1, rstd1 = ops.add_rmsnorm_fwd(branch, stream, lw.norm1, self.blocks[index].norm.eps, dtype)
+        qkv = ops.linear_fwd(normed1, lw.w_qkv)
+        qkv_pre = None
+        if lw.conv_w is not None:
+            qkv_pre = qkv
+            qkv = ops.causal_conv_fwd(qkv_pre, lw.conv_w, lw.conv_b, bsz, seqlen)
+        qkv = ops.rope_qkv(qkv, cos, sin, heads, kv_heads, head_dim, seqlen, interleaved, inverse=False)
+        attn_out, lse = ops.attention_fwd(qkv, bsz, seqlen, heads, kv_heads, head_dim, scale)
+        branch = ops.linear_fwd(attn_out, lw.w_o)
+        normed2, stream2, rstd2 = ops.add_rmsnorm_fwd(branch, stream1, lw.norm2, self.blocks[index].norm2.eps, dtype)
+        fc1_out = ops.linear_fwd(normed2, lw.w_fc1)
+        act = ops.swiglu_fwd(fc1_out)
+        branch = ops.linear_fwd(act, lw.w_fc2)
+        return branch, stream2, LayerCache(stream1, rstd1, normed1, qkv_pre, qkv, attn_out, lse, stream2, rstd2, normed2, fc1_out, act)
 
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
@@ -133,35 +156,57 @@ class StructuredTransformerRegion:
         dtype = self.act_dtype or region_input.dtype
         x = region_input.reshape(bsz * seqlen, dim).to(dtype).contiguous()
         cache = StructuredRegionCache(batch=bsz, seq_len=seqlen, layer_range=tuple(layer_range), region_input=x)
-        weights = self.weights(dtype)
         branch, stream = x, None
         for index in range(*layer_range):
-            lw = weights[index]
-            heads, kv_heads, head_dim, scale, rope_base, interleaved = self._dims(index)
-            cos, sin = rope_tables(seqlen, head_dim, rope_base, x.device)
-            normed1, stream1, rstd1 = ops.add_rmsnorm_fwd(branch, stream, lw.norm1, self.blocks[index].norm.eps, dtype)
-            qkv = ops.linear_fwd(normed1, lw.w_qkv)
-            qkv_pre = None
-            if lw.conv_w is not None:
-                qkv_pre = qkv
-                qkv = ops.causal_conv_fwd(qkv_pre, lw.conv_w, lw.conv_b, bsz, seqlen)
-            qkv = ops.rope_qkv(qkv, cos, sin, heads, kv_heads, head_dim, seqlen, interleaved, inverse=False)
-            attn_out, lse = ops.attention_fwd(qkv, bsz, seqlen, heads, kv_heads, head_dim, scale)
-            branch = ops.linear_fwd(attn_out, lw.w_o)
-            normed2, stream2, rstd2 = ops.add_rmsnorm_fwd(branch, stream1, lw.norm2, self.blocks[index].norm2.eps, dtype)
-            fc1_out = ops.linear_fwd(normed2, lw.w_fc1)
-            act = ops.swiglu_fwd(fc1_out)
-            branch = ops.linear_fwd(act, lw.w_fc2)
-            stream = stream2
-            cache.layers.append(
-                LayerCache(stream1, rstd1, normed1, qkv_pre, qkv, attn_out, lse, stream2, rstd2, normed2, fc1_out, act)
-            )
+            branch, stream, lc = self.layer_forward(index, branch, stream, bsz, seqlen, dtype)
+            cache.layers.append(lc)
         cache.last_branch, cache.last_stream = branch, stream
         if not materialize_output:
             return None, cache
         out = branch.float() if stream is None else branch.float() + stream
         cache.output = out
         return out.reshape(bsz, seqlen, dim), cache
+
+    # ------------------------------------------------------------------ one block, reverse
+    @torch.no_grad()
+    def layer_reverse(self, index: int, lc: LayerCache, d_stream: torch.Tensor, d_branch: torch.Tensor, grads, bsz: int, seqlen: int,
+                      dtype: torch.dtype):
+        """Cotangents (fp32 stream, low-precision branch) [P * n, D] leaving block ``index`` -> the pair entering it."""
+        lw = self.weights(dtype)[index]
+        heads, kv_heads, head_dim, scale, rope_base, interleaved = self._dims(index)
+        cos, sin = rope_tables(seqlen, head_dim, rope_base, d_stream.device)
+        prefix = f"blocks.{index}."
+        # MLP branch
+        if grads is not None:
+            _wgrad(grads, prefix + "mlp.fc2.weight", d_branch, lc.act)
+        d_act = ops.linear_dgrad(d_branch, lw.w_fc2, lw.w_fc2_t)
+        d_fc1 = ops.swiglu_bwd(d_act, lc.fc1_out)
+        if grads is not None:
+            _wgrad(grads, prefix + "mlp.fc1.weight", d_fc1, lc.normed2)
+        d_normed2 = ops.linear_dgrad(d_fc1, lw.w_fc1, lw.w_fc1_t)
+        if grads is not None:
+            _acc(grads, prefix + "norm2.weight", ops.rmsnorm_wgrad(d_normed2, lc.stream2, lc.rstd2))
+        d_stream, d_branch = ops.rmsnorm_bwd(d_normed2, lc.stream2, lc.rstd2, lw.norm2, d_stream, lowp_dtype=dtype)
+        # attention branch
+        if grads is not None:
+            _wgrad(grads, prefix + "attn.out_proj.weight", d_branch, lc.attn_out)
+        d_attn = ops.linear_dgrad(d_branch, lw.w_o, lw.w_o_t)
+        d_qkv = ops.attention_pullback_packed(d_attn, lc.qkv, lc.attn_out, lc.lse, bsz, seqlen, heads, kv_heads, head_dim, scale,
+                                              rope=(cos, sin, interleaved))
+        if lw.conv_w is not None:
+            if grads is not None:
+                dw, db = ops.causal_conv_wgrad(d_qkv, lc.qkv_pre, lw.conv_w.shape[1], bsz, seqlen)
+                _acc(grads, prefix + "attn.conv1d.weight", dw.unsqueeze(1))
+                if lw.conv_b is not None:
+                    _acc(grads, prefix + "attn.conv1d.bias", db)
+            d_qkv = ops.causal_conv_dgrad(d_qkv, lw.conv_w, bsz, seqlen)
+        if grads is not None:
+            _wgrad(grads, prefix + "attn.in_proj.weight", d_qkv, lc.normed1)
+        d_normed1 = ops.linear_dgrad(d_qkv, lw.w_qkv, lw.w_qkv_t)
+        if grads is not None:
+            _acc(grads, prefix + "norm.weight", ops.rmsnorm_wgrad(d_normed1, lc.stream1, lc.rstd1))
+        d_stream, d_branch = ops.rmsnorm_bwd(d_normed1, lc.stream1, lc.rstd1, lw.norm1, d_stream, lowp_dtype=dtype)
+        return d_stream, d_branch
 
     # ------------------------------------------------------------------ reverse chain
     @torch.no_grad()
@@ -171,46 +216,11 @@ class StructuredTransformerRegion:
         With ``grads`` (a dict name -> fp32 tensor, P must be 1) parameter gradients are accumulated into it."""
         bsz, seqlen = cache.batch, cache.seq_len
         dtype = cache.region_input.dtype
-        weights = self.weights(dtype)
         d_stream = d_out_rows.float()
         d_branch = d_out_rows.to(dtype)
         start, end = cache.layer_range
         for index in range(end - 1, start - 1, -1):
-            lc = cache.layers[index - start]
-            lw = weights[index]
-            heads, kv_heads, head_dim, scale, rope_base, interleaved = self._dims(index)
-            cos, sin = rope_tables(seqlen, head_dim, rope_base, d_stream.device)
-            prefix = f"blocks.{index}."
-            # MLP branch
-            if grads is not None:
-                _wgrad(grads, prefix + "mlp.fc2.weight", d_branch, lc.act)
-            d_act = ops.linear_dgrad(d_branch, lw.w_fc2, lw.w_fc2_t)
-            d_fc1 = ops.swiglu_bwd(d_act, lc.fc1_out)
-            if grads is not None:
-                _wgrad(grads, prefix + "mlp.fc1.weight", d_fc1, lc.normed2)
-            d_normed2 = ops.linear_dgrad(d_fc1, lw.w_fc1, lw.w_fc1_t)
-            if grads is not None:
-                _acc(grads, prefix + "norm2.weight", ops.rmsnorm_wgrad(d_normed2, lc.stream2, lc.rstd2))
-            d_stream, d_branch = ops.rmsnorm_bwd(d_normed2, lc.stream2, lc.rstd2, lw.norm2, d_stream, lowp_dtype=dtype)
-            # attention branch
-            if grads is not None:
-                _wgrad(grads, prefix + "attn.out_proj.weight", d_branch, lc.attn_out)
-            d_attn = ops.linear_dgrad(d_branch, lw.w_o, lw.w_o_t)
-            d_qkv = ops.attention_pullback_packed(d_attn, lc.qkv, lc.attn_out, lc.lse, bsz, seqlen, heads, kv_heads, head_dim, scale,
-                                                  rope=(cos, sin, interleaved))
-            if lw.conv_w is not None:
-                if grads is not None:
-                    dw, db = ops.causal_conv_wgrad(d_qkv, lc.qkv_pre, lw.conv_w.shape[1], bsz, seqlen)
-                    _acc(grads, prefix + "attn.conv1d.weight", dw.unsqueeze(1))
-                    if lw.conv_b is not None:
-                        _acc(grads, prefix + "attn.conv1d.bias", db)
-                d_qkv = ops.causal_conv_dgrad(d_qkv, lw.conv_w, bsz, seqlen)
-            if grads is not None:
-                _wgrad(grads, prefix + "attn.in_proj.weight", d_qkv, lc.normed1)
-            d_normed1 = ops.linear_dgrad(d_qkv, lw.w_qkv, lw.w_qkv_t)
-            if grads is not None:
-                _acc(grads, prefix + "norm.weight", ops.rmsnorm_wgrad(d_normed1, lc.stream1, lc.rstd1))
-            d_stream, d_branch = ops.rmsnorm_bwd(d_normed1, lc.stream1, lc.rstd1, lw.norm1, d_stream, lowp_dtype=dtype)
+            d_stream, d_branch = self.layer_reverse(index, cache.layers[index - start], d_stream, d_branch, grads, bsz, seqlen, dtype)
         return d_stream
 
     def input_pullback(self, cache: StructuredRegionCache, d_out_basis_rows: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,318 @@
+"""Ops of the closed-form Mamba-2 / Mamba-3 block chains (``backends/mamba_structured.py``).
+
+Every function has a PyTorch statement (fp32, any device, no autograd needed: forward values and explicit
+cotangent formulas) and, for bf16 CUDA tensors, a route to the sm_100a kernels.  Functions that pull cotangents
+back accept ``P`` stacked directions: the cotangent rows are ``[P * n, ...]`` (direction-major) while the cached
+forward operands keep their ``n`` rows and are shared by all directions.
+
+Reference counterparts: the gated RMSNorm Triton kernels (backbones/mamba2/ops/triton/layernorm_gated.py:45-268),
+the angle / dt kernels of Mamba-3 (backbones/mamba3/ops/triton/mamba3/angle_dt.py:26-330) and the dd_dt / trap /
+rotary part of its backward (mamba3_siso_bwd.py:811-1418).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from .native import ext, native_available
+
+TWO_PI = 2.0 * math.pi
+
+
+def _count(n: int = 1) -> None:
+    from .dispatch import KERNEL_LAUNCHES
+
+    KERNEL_LAUNCHES["count"] += n
+
+
+def _kernel_ok(*tensors, name: str | None = None) -> bool:
+    if not native_available() or (name is not None and not hasattr(ext(), name)):
+        return False
+    return all(t is None or t.is_cuda for t in tensors)
+
+
+def _tile_rows(t: torch.Tensor, reps: int) -> torch.Tensor:
+    """[n, ...] -> [reps * n, ...] with the n rows repeated (direction-major stacking)."""
+    if reps == 1:
+        return t
+    return t.unsqueeze(0).expand(reps, *t.shape).reshape(reps * t.shape[0], *t.shape[1:])
+
+
+# ---------------------------------------------------------------- SiLU gate  yg = y * silu(z)
+def gate_silu_fwd(y: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
+    if _kernel_ok(y, z, name="gate_silu_fwd") and y.dtype == torch.bfloat16 and z.dtype == torch.bfloat16 and y.shape[-1] % 8 == 0:
+        _count()
+        return ext().gate_silu_fwd(y.contiguous(), z.contiguous())
+    return (y.float() * F.silu(z.float())).to(y.dtype)
+
+
+def gate_silu_bwd(dyg: torch.Tensor, y: torch.Tensor, z: torch.Tensor):
+    """dyg [P * n, d]; y, z [n, d] -> (dy, dz) [P * n, d] in the dtype of dyg."""
+    if (_kernel_ok(dyg, y, z, name="gate_silu_bwd") and dyg.dtype == torch.bfloat16 and y.dtype == torch.bfloat16
+            and z.dtype == torch.bfloat16 and y.shape[-1] % 8 == 0):
+        _count()
+        return ext().gate_silu_bwd(dyg.contiguous(), y.contiguous(), z.contiguous())
+    reps = dyg.shape[0] // y.shape[0]
+    g = dyg.float().view(reps, *y.shape)
+    zf, yf = z.float(), y.float()
+    sig = torch.sigmoid(zf)
+    dy = g * (zf * sig)
+    dz = g * yf * (sig * (1.0 + zf * (1.0 - sig)))
+    return dy.reshape(dyg.shape).to(dyg.dtype), dz.reshape(dyg.shape).to(dyg.dtype)
+
+
+# ---------------------------------------------------------------- RMSNorm over groups of the last axis, optional SiLU gate
+def gated_rmsnorm_fwd(x, z, weight, eps: float, group: int, gate_first: bool):
+    """x, z [n, d] -> (y [n, d], rstd [n, d / group] fp32).  ``gate_first``: norm(x * silu(z)) (Mamba-2), else
+    norm(x) * silu(z); without z a plain grouped RMSNorm (the B / C norms of Mamba-3)."""
+    if (_kernel_ok(x, z, weight, name="gated_rmsnorm_fwd") and x.dtype in (torch.bfloat16, torch.float32) and group % 8 == 0
+            and x.shape[-1] <= 12288 and x.shape[-1] % group == 0):
+        _count()
+        return ext().gated_rmsnorm_fwd(x.contiguous(), None if z is None else z.to(x.dtype).contiguous(), weight.float().contiguous(),
+                                       float(eps), int(group), bool(gate_first))
+    xf = x.float()
+    if z is not None and gate_first:
+        xf = xf * F.silu(z.float())
+    grouped = xf.unflatten(-1, (-1, group))
+    rstd = torch.rsqrt(grouped.square().mean(dim=-1) + eps)
+    y = (grouped * rstd.unsqueeze(-1)).flatten(-2) * weight.float()
+    if z is not None and not gate_first:
+        y = y * F.silu(z.float())
+    return y.to(x.dtype), rstd
+
+
+def gated_rmsnorm_bwd(dy, x, z, weight, rstd, group: int, gate_first: bool, want_dweight: bool = False):
+    """dy [P * n, d]; x, z [n, d]; rstd [n, d / group] -> (dx, dz or None, dweight or None)."""
+    reps = dy.shape[0] // x.shape[0]
+    if (_kernel_ok(dy, x, z, weight, rstd, name="gated_rmsnorm_bwd") and x.dtype in (torch.bfloat16, torch.float32)
+            and group % 8 == 0 and x.shape[-1] <= 12288):
+        _count()
+        xr = _tile_rows(x, reps).contiguous()
+        zr = None if z is None else _tile_rows(z.to(x.dtype), reps).contiguous()
+        rr = _tile_rows(rstd, reps).contiguous()
+        dx, dz, dw = ext().gated_rmsnorm_bwd(dy.to(x.dtype).contiguous(), xr, zr, weight.float().contiguous(), rr, int(group), bool(gate_first))
+        return dx, (dz if z is not None else None), (dw if want_dweight else None)
+    w = weight.float()
+    g = dy.float().view(reps, *x.shape)
+    xf = x.float()
+    dz = None
+    if z is not None:
+        zf = z.float()
+        sig = torch.sigmoid(zf)
+        silu, dsilu = zf * sig, sig * (1.0 + zf * (1.0 - sig))
+    u = xf * silu if (z is not None and gate_first) else xf
+    uh = (u.unflatten(-1, (-1, group)) * rstd.unsqueeze(-1)).flatten(-2)          # normalised input
+    if z is not None and not gate_first:
+        dz = g * (uh * w) * dsilu
+        g = g * silu
+    dw = (g * uh).sum(dim=(0, 1)) if want_dweight else None
+    wg = (g * w).unflatten(-1, (-1, group))
+    uhg = uh.unflatten(-1, (-1, group))
+    du = ((wg - uhg * (wg * uhg).mean(dim=-1, keepdim=True)) * rstd.unsqueeze(-1)).flatten(-2)
+    if z is not None and gate_first:
+        dz = du * xf * dsilu
+        du = du * silu
+    out_dtype = x.dtype
+    return du.reshape(dy.shape).to(out_dtype), (None if dz is None else dz.reshape(dy.shape).to(out_dtype)), dw
+
+
+# ---------------------------------------------------------------- Mamba-3: the [b, l, h]-sized preprocessing
+@dataclass
+class SisoSmall:
+    """Per-token, per-head scalars of the SISO mixer (all fp32).  dt, a, sig, adt, gamma, scale [b, l, h];
+    tanh_angle [b, l, s]; theta [b, l, h, s] in [0, 2 pi); sp_dt, sp_a: the sigmoids of the softplus arguments;
+    a_live: 1 where A is not clamped at -A_floor."""
+    dt: torch.Tensor
+    a: torch.Tensor
+    sig: torch.Tensor
+    adt: torch.Tensor
+    gamma: torch.Tensor
+    scale: torch.Tensor
+    tanh_angle: torch.Tensor
+    theta: torch.Tensor
+    sp_dt: torch.Tensor
+    sp_a: torch.Tensor
+    a_live: torch.Tensor
+
+
+def siso_small_fwd(dd_dt, dd_a, trap, angles, dt_bias, a_floor: float, batch: int, seq_len: int) -> SisoSmall:
+    """dd_dt, dd_a, trap [n, h]; angles [n, s]; dt_bias [h].  DT = softplus(dd_dt + bias), A = min(-softplus(dd_a), -floor),
+    gamma = DT sigmoid(trap), scale_t = gamma_t + DT_{t+1} (1 - sigmoid(trap_{t+1})) (0 past the last token of a sequence),
+    theta_t = (sum_{i <= t} pi tanh(angle_i) DT_i) mod 2 pi."""
+    h, s = dd_dt.shape[-1], angles.shape[-1]
+    if _kernel_ok(dd_dt, dd_a, trap, angles, dt_bias, name="siso_small_fwd"):
+        _count()
+        out = ext().siso_small_fwd(dd_dt.float().contiguous(), dd_a.float().contiguous(), trap.float().contiguous(),
+                                   angles.float().contiguous(), dt_bias.float().contiguous(), float(a_floor), int(batch), int(seq_len))
+        return SisoSmall(*out)
+    pre = dd_dt.float().view(batch, seq_len, h) + dt_bias.float()
+    dt = F.softplus(pre)
+    raw_a = -F.softplus(dd_a.float().view(batch, seq_len, h))
+    a = torch.clamp(raw_a, max=-a_floor)
+    sig = torch.sigmoid(trap.float().view(batch, seq_len, h))
+    gamma = dt * sig
+    carry = F.pad((dt * (1.0 - sig))[:, 1:], (0, 0, 0, 1))
+    tanh_angle = torch.tanh(angles.float().view(batch, seq_len, s))
+    vals = (math.pi * tanh_angle).unsqueeze(2) * dt.unsqueeze(-1)                       # [b, l, h, s]
+    theta = torch.cumsum(vals, dim=1)
+    theta = theta - TWO_PI * torch.floor(theta / TWO_PI)
+    return SisoSmall(dt=dt, a=a, sig=sig, adt=a * dt, gamma=gamma, scale=gamma + carry, tanh_angle=tanh_angle, theta=theta,
+                     sp_dt=torch.sigmoid(pre), sp_a=torch.sigmoid(dd_a.float().view(batch, seq_len, h)),
+                     a_live=(raw_a < -a_floor).float())
+
+
+def siso_small_bwd(small: SisoSmall, dadt, dtheta, dgamma, dscale, out_dtype=torch.float32):
+    """Cotangents [P * b, l, h(, s)] of (adt, theta, gamma, scale) -> cotangents of (dd_dt, dd_a, trap) [P * b * l, h] and of
+    the angles [P * b * l, s]."""
+    b, l, h = small.dt.shape
+    s = small.tanh_angle.shape[-1]
+    reps = dadt.shape[0] // b
+    if _kernel_ok(dadt, dtheta, dgamma, dscale, small.dt, name="siso_small_bwd"):
+        _count()
+        return ext().siso_small_bwd(small.dt, small.a, small.sig, small.tanh_angle, small.sp_dt, small.sp_a, small.a_live,
+                                    dadt.float().contiguous(), dtheta.float().contiguous(), dgamma.float().contiguous(),
+                                    dscale.float().contiguous(), out_dtype == torch.bfloat16)
+    dadt, dgamma, dscale = (t.float().reshape(reps, b, l, h) for t in (dadt, dgamma, dscale))
+    dvals = dtheta.float().reshape(reps, b, l, h, s).flip(2).cumsum(2).flip(2)              # reversed cumulative sum over tokens
+    d_tanh = math.pi * (dvals * small.dt.unsqueeze(-1)).sum(3)                             # [P, b, l, s]
+    d_angles = d_tanh * (1.0 - small.tanh_angle.square())
+    d_scale_prev = F.pad(dscale[:, :, :-1], (0, 0, 1, 0))                                  # token t receives dscale_{t-1}
+    d_gamma_all = dgamma + dscale
+    d_dt = (dadt * small.a + math.pi * (dvals * small.tanh_angle.unsqueeze(2)).sum(-1) + d_gamma_all * small.sig
+            + d_scale_prev * (1.0 - small.sig))
+    d_sig = small.dt * (d_gamma_all - d_scale_prev)
+    d_trap = d_sig * small.sig * (1.0 - small.sig)
+    d_dd_a = -(dadt * small.dt) * small.sp_a * small.a_live
+    d_dd_dt = d_dt * small.sp_dt
+    n = reps * b * l
+    return (d_dd_dt.reshape(n, h).to(out_dtype), d_dd_a.reshape(n, h).to(out_dtype), d_trap.reshape(n, h).to(out_dtype),
+            d_angles.reshape(n, s).to(out_dtype))
+
+
+# ---------------------------------------------------------------- Mamba-3: bias, rotary turn, trapezoid scale on [b, l, h, n]
+def _rotate_pairs(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    n_angles = cos.shape[-1]
+    head, tail = x[..., : 2 * n_angles], x[..., 2 * n_angles:]
+    a, b = head.unflatten(-1, (n_angles, 2)).unbind(-1)
+    rotated = torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).flatten(-2)
+    return torch.cat((rotated, tail), dim=-1)
+
+
+def siso_wide_fwd(q, k, q_bias, k_bias, theta, gamma, scale):
+    """q, k [b, l, g, n]; biases [h, n]; theta [b, l, h, s]; gamma, scale [b, l, h] -> (Qr, Kr [b, l, h, n], qk [b, l, h] fp32):
+    Qr = Rot(q + bq), Kr = scale Rot(k + bk), qk = gamma <q + bq, k + bk>."""
+    if _kernel_ok(q, k, theta, name="siso_prep_fwd") and q.shape[-1] == 128 and q.dtype in (torch.bfloat16, torch.float32):
+        _count()
+        return ext().siso_prep_fwd(q.contiguous(), k.to(q.dtype).contiguous(), q_bias.float().contiguous(), k_bias.float().contiguous(),
+                                   theta.float().contiguous(), gamma.float().contiguous(), scale.float().contiguous())
+    h = q_bias.shape[0]
+    rep = h // q.shape[2]
+    qh = q.float().repeat_interleave(rep, dim=2) + q_bias.float()
+    kh = k.float().repeat_interleave(rep, dim=2) + k_bias.float()
+    cos, sin = torch.cos(theta.float()), torch.sin(theta.float())
+    return (_rotate_pairs(qh, cos, sin).to(q.dtype), (_rotate_pairs(kh, cos, sin) * scale.float().unsqueeze(-1)).to(q.dtype),
+            gamma.float() * (qh * kh).sum(-1))
+
+
+def siso_wide_bwd(q, k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, dkr_reversed: bool = False):
+    """Cotangents dqr, dkr [P * b, l(p), h, n] (dkr optionally in reversed token order over a padded length), dqk [P * b, l, h]
+    -> (dq, dk [P * b, l, g, n] fp32, dq_bias, dk_bias [h, n], dtheta [P * b, l, h, s], dgamma, dscale [P * b, l, h])."""
+    b, l = q.shape[:2]
+    reps = dqr.shape[0] // b
+    if _kernel_ok(q, k, theta, dqr, dkr, dqk, name="siso_prep_bwd") and q.shape[-1] == 128 and q.dtype in (torch.bfloat16, torch.float32):
+        _count()
+        return tuple(ext().siso_prep_bwd(
+            _tile_rows(q, reps).contiguous(), _tile_rows(k.to(q.dtype), reps).contiguous(), q_bias.float().contiguous(),
+            k_bias.float().contiguous(), _tile_rows(theta.float(), reps).contiguous(), _tile_rows(gamma.float(), reps).contiguous(),
+            _tile_rows(scale.float(), reps).contiguous(), dqr.float().contiguous(), dkr.float().contiguous(), dqk.float().contiguous(),
+            bool(dkr_reversed)))
+    if dkr_reversed:
+        dkr = dkr.flip(1)[:, :l]
+    h, n = q_bias.shape
+    g = q.shape[2]
+    rep = h // g
+    qh = q.float().repeat_interleave(rep, dim=2) + q_bias.float()
+    kh = k.float().repeat_interleave(rep, dim=2) + k_bias.float()
+    cos, sin = torch.cos(theta.float()), torch.sin(theta.float())
+    dqr_, dkr_, dqk_ = dqr.float().view(reps, b, l, h, n), dkr.float().view(reps, b, l, h, n), dqk.float().view(reps, b, l, h)
+    sc, gm = scale.float().unsqueeze(-1), gamma.float()
+    dqh = _rotate_pairs(dqr_, cos, -sin) + (dqk_ * gm).unsqueeze(-1) * kh
+    dkh = sc * _rotate_pairs(dkr_, cos, -sin) + (dqk_ * gm).unsqueeze(-1) * qh
+    na = theta.shape[-1]
+    rq, rk = _rotate_pairs(qh, cos, sin), _rotate_pairs(kh, cos, sin)
+
+    def turn_grad(d, r):   # <d_pair, J r_pair> with J (a, b) = (-b, a)
+        da, db = d[..., : 2 * na].unflatten(-1, (na, 2)).unbind(-1)
+        ra, rb = r[..., : 2 * na].unflatten(-1, (na, 2)).unbind(-1)
+        return -da * rb + db * ra
+
+    dtheta = turn_grad(dqr_, rq) + scale.float().unsqueeze(-1) * turn_grad(dkr_, rk)
+    dgamma = dqk_ * (qh * kh).sum(-1)
+    dscale = (dkr_ * rk).sum(-1)
+    dq = dqh.view(reps, b, l, g, rep, n).sum(4).reshape(reps * b, l, g, n)
+    dk = dkh.view(reps, b, l, g, rep, n).sum(4).reshape(reps * b, l, g, n)
+    return (dq, dk, dqh.sum((0, 1, 2)), dkh.sum((0, 1, 2)), dtheta.reshape(reps * b, l, h, na), dgamma.reshape(reps * b, l, h),
+            dscale.reshape(reps * b, l, h))
+
+
+# ---------------------------------------------------------------- Mamba-3: the recurrence itself
+def siso_scan_fwd(v, kr, qr, adt, skip, d_skip):
+    """v [b, l, h, p]; kr, qr [b, l, h, n]; adt, skip [b, l, h]; d_skip [h] ->
+    (y_t = sum_{s < t} e^{c_t - c_s} (qr_t . kr_s) v_s + (skip_t + D) v_t, incoming chunk states or None)."""
+    from . import ssd
+
+    b, l, h, p = v.shape
+    if ssd.siso_cuda_supported(v, qr) and v.dtype == torch.bfloat16:
+        pad = (-l) % ssd.CHUNK
+        vb, qb, kb, a, sk = v, qr.to(torch.bfloat16), kr.to(torch.bfloat16), adt.float(), skip.float()
+        if pad:
+            vb, qb, kb = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (vb, qb, kb))
+            a, sk = F.pad(a, (0, 0, 0, pad)), F.pad(sk, (0, 0, 0, pad))
+        y, _, states = ext().siso_chunk_scan_fwd(vb.contiguous(), kb.contiguous(), qb.contiguous(), a.contiguous(),
+                                                 None if d_skip is None else d_skip.float().contiguous(),
+                                                 sk.transpose(1, 2).contiguous(), None)
+        _count(4)
+        return y[:, :l], states
+    y, _ = ssd.scan_generic_torch(v, kr, qr, adt, None, None, strict=True, per_head=True)
+    total_skip = skip.float() if d_skip is None else skip.float() + d_skip.float()
+    return (y + total_skip.unsqueeze(-1) * v.float()).to(v.dtype), None
+
+
+def siso_scan_bwd(qr, kr, adt, skip_total, v, gy, states, keep_dkr_reversed: bool = False):
+    """gy [P * b, l, h, p] with the forward operands shared by the P directions -> (dQr, dKr, dadt, dskip, dV)."""
+    from . import ssd
+
+    reps = gy.shape[0] // v.shape[0]
+    if ssd.siso_cuda_supported(v, qr) and gy.dtype == torch.bfloat16 and hasattr(ext(), "ssd_decay_grad"):
+        tile = lambda t: None if t is None else _tile_rows(t, reps)  # noqa: E731
+        return ssd.siso_core_backward(tile(qr), tile(kr), tile(adt), tile(skip_total), tile(v), gy, ops=ssd.KernelScans,
+                                      fwd_states=tile(states), keep_dkr_reversed=keep_dkr_reversed)
+    return ssd.siso_core_backward_dense(qr, kr, adt, skip_total, v, gy)
+
+
+# ---------------------------------------------------------------- Mamba-2: softplus of dt, SiLU of the conv output
+def softplus_dt_fwd(dt_raw, dt_bias, lo: float, hi: float):
+    """-> (dt [n, h] fp32, d dt / d dt_raw [n, h] fp32)."""
+    pre = dt_raw.float() + dt_bias.float()
+    dt = F.softplus(pre)
+    slope = torch.sigmoid(pre)
+    if (lo, hi) != (0.0, float("inf")):
+        inside = (dt >= lo) & (dt <= hi)
+        dt, slope = dt.clamp(lo, hi), slope * inside
+    return dt, slope
+
+
+def silu_fwd(x):
+    return F.silu(x.float()).to(x.dtype)
+
+
+def silu_bwd(dy, x):
+    """dy [P * n, c]; x [n, c] (the pre-activation)."""
+    reps = dy.shape[0] // x.shape[0]
+    xf = x.float()
+    sig = torch.sigmoid(xf)
+    slope = sig * (1.0 + xf * (1.0 - sig))
+    return (dy.float().view(reps, *x.shape) * slope).reshape(dy.shape).to(dy.dtype)

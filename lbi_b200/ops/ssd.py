@@ -450,3 +450,75 @@ def mamba3_siso_cuda(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D, Z=None):
     if Z is not None:
         y = (y.float() * F.silu(Z.float())).to(V.dtype)
     return y
+
+
+# ------------------------------------------------------------------------------------------------ dense statements
+def _pair_weights(a):
+    """a [b, l, h] log-decays -> (c [b, h, l] cumulative, diff [b, h, t, s] = c_t - c_s)."""
+    c = a.float().cumsum(1).permute(0, 2, 1)
+    return c, c[:, :, :, None] - c[:, :, None, :]
+
+
+def _decay_cotangent(e):
+    """e [b, h, t, s] = dW o W for W[t, s] = exp(c_t - c_s) -> cotangent of the per-token log-decays [b, l, h]."""
+    dc = e.sum(3) - e.sum(2)                                    # [b, h, l]
+    return dc.flip(2).cumsum(2).flip(2).permute(0, 2, 1)
+
+
+def siso_core_backward_dense(Qr, Kr, adt, skip, V, gy):
+    """The gradients of ``siso_core_backward`` from the O(l^2) definition, in fp32, for any head_dim / d_state / length and
+    with the forward operands shared by P stacked directions (gy [P * b, ...], the rest [b, ...])."""
+    b, l, h, p = V.shape
+    reps = gy.shape[0] // b
+    g = gy.float().view(reps, b, l, h, p)
+    q, k, v = Qr.float(), Kr.float(), V.float()
+    _, diff = _pair_weights(adt)
+    strict = torch.ones(l, l, dtype=torch.bool, device=V.device).tril(-1)
+    w = torch.exp(diff.masked_fill(~strict, float("-inf")))                      # [b, h, t, s]
+    gram = torch.einsum("bthn,bshn->bhts", q, k)
+    m = w * gram
+    dV = torch.einsum("bhts,rbthp->rbshp", m, g) + skip.float()[None, ..., None] * g
+    dM = torch.einsum("rbthp,bshp->rbhts", g, v)
+    dG = dM * w
+    dQr = torch.einsum("rbhts,bshn->rbthn", dG, k)
+    dKr = torch.einsum("rbhts,bthn->rbshn", dG, q)
+    dadt = _decay_cotangent((dM * m).reshape(reps * b, h, l, l))
+    dskip = (g * v).sum(-1)
+    n = q.shape[-1]
+    return (dQr.reshape(reps * b, l, h, n), dKr.reshape(reps * b, l, h, n), dadt, dskip.reshape(reps * b, l, h),
+            dV.reshape(reps * b, l, h, p))
+
+
+def ssd_backward_dense(x, dt, A, B, C, D, gy):
+    """Gradients of y_t = sum_{s <= t} e^{c_t - c_s} (C_t . B_s) dt_s x_s + D x_t from the O(l^2) definition, in fp32, for any
+    shape, with the forward operands shared by P stacked directions.  Returns (dx, ddt, dA, dB, dC, dD)."""
+    b, l, h, p = x.shape
+    grp, n = B.shape[2], B.shape[3]
+    rep = h // grp
+    reps = gy.shape[0] // b
+    g = gy.float().view(reps, b, l, h, p)
+    xf, dtf, Af = x.float(), dt.float(), A.float()
+    Bh, Ch = B.float().repeat_interleave(rep, dim=2), C.float().repeat_interleave(rep, dim=2)
+    _, diff = _pair_weights(dtf * Af)
+    causal = torch.ones(l, l, dtype=torch.bool, device=x.device).tril(0)
+    w = torch.exp(diff.masked_fill(~causal, float("-inf")))
+    gram = torch.einsum("bthn,bshn->bhts", Ch, Bh)
+    nmat = w * gram
+    X = dtf.unsqueeze(-1) * xf
+    dX = torch.einsum("bhts,rbthp->rbshp", nmat, g)
+    dx = dtf[None, ..., None] * dX
+    ddt = (dX * xf).sum(-1)
+    dN = torch.einsum("rbthp,bshp->rbhts", g, X)
+    dG = dN * w
+    dCh = torch.einsum("rbhts,bshn->rbthn", dG, Bh)
+    dBh = torch.einsum("rbhts,bthn->rbshn", dG, Ch)
+    da = _decay_cotangent((dN * nmat).reshape(reps * b, h, l, l)).view(reps, b, l, h)
+    ddt = ddt + da * Af
+    dA = (da * dtf).sum((0, 1, 2))
+    dD = None
+    if D is not None:
+        dx = dx + D.float()[None, None, None, :, None] * g
+        dD = (g * xf).sum((0, 1, 2, 4))
+    dB = dBh.view(reps, b, l, grp, rep, n).sum(4).reshape(reps * b, l, grp, n)
+    dC = dCh.view(reps, b, l, grp, rep, n).sum(4).reshape(reps * b, l, grp, n)
+    return dx.reshape(reps * b, l, h, p), ddt.reshape(reps * b, l, h), dA, dB, dC, dD

@@ -71,8 +71,9 @@ class FastLBIEngine:
         basis_parallel: bool | None = None,
     ) -> None:
         backend = model.region_backend
-        if not hasattr(backend, "structured"):
-            raise NotImplementedError("FastLBIEngine needs a Transformer region backend; use ScanADEngine for other backbones")
+        if getattr(backend, "structured", None) is None:
+            raise NotImplementedError("FastLBIEngine needs a region backend with a closed-form lowering (`structured`: forward with "
+                                      "caches, input_pullback, backward); use ScanADEngine otherwise")
         self.model = model
         self.comm = comm or LocalComm()
         self.device = next(model.parameters()).device
