@@ -190,9 +190,8 @@ class StructuredMambaRegion:
                 _acc(grads, prefix + "mixer.norm.weight", dw)
         else:
             d_y, d_z = mops.gate_silu_bwd(d_yin, lc.y, lc.z)
-        d_qr, d_kr, d_adt, d_skip, d_v = mops.siso_scan_bwd(lc.qr, lc.kr, lc.small.adt, lc.skip, lc.x.view(bsz, seqlen, h, p),
-                                                            d_y.view(pb, seqlen, h, p), lc.states, keep_dkr_reversed=True)
-        reversed_dkr = lc.states is not None   # the kernel path leaves dKr in reversed token order over the padded length
+        d_qr, d_kr, d_adt, d_skip, d_v, reversed_dkr = mops.siso_scan_bwd(lc.qr, lc.kr, lc.small.adt, lc.skip, lc.x.view(bsz, seqlen, h, p),
+                                                                          d_y.view(pb, seqlen, h, p), lc.states)
         d_c, d_b, d_cb, d_bb, d_theta, d_gamma, d_scale = mops.siso_wide_bwd(
             lc.c_normed, lc.b_normed, mx.C_bias.detach().squeeze(1), mx.B_bias.detach().squeeze(1), lc.small.theta, lc.small.gamma,
             lc.small.scale, d_qr, d_kr, d_skip, dkr_reversed=reversed_dkr)
@@ -362,6 +361,8 @@ def _ssd_backward(x, dt, a_neg, b, c, d_skip, gy, states, final):
     """x, dt, b, c, states, final: forward operands [b, ...]; gy [P * b, l, h, p] -> (dx, ddt, dA [h], dB, dC, dD [h]) for the
     P stacked directions."""
     reps = gy.shape[0] // x.shape[0]
+    if ops_ssd.ssd_cuda_supported(x, b) and x.dtype == torch.bfloat16 and states is not None and ops_ssd.chunk_backward_supported(x):
+        return ops_ssd.ssd_backward_fused(x, dt, a_neg, b, c, d_skip, gy.to(x.dtype), states)
     if ops_ssd.ssd_cuda_supported(x, b) and x.dtype == torch.bfloat16 and hasattr(ops.ext(), "ssd_decay_grad"):
         tile = lambda t: None if t is None else mops._tile_rows(t, reps)  # noqa: E731
         dx, ddt, d_a, d_b, d_c, d_d, _ = ops_ssd.ssd_backward(tile(x), tile(dt), a_neg, tile(b), tile(c), d_skip, None, tile(final),

@@ -18,7 +18,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 BUILD = PKG / "build"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-CUDA_SOURCES = ["elementwise.cu", "suffix_scan.cu", "interface_jac.cu", "gated_norm.cu", "siso_prep.cu", "gemm_tcgen05.cu", "attn_pullback.cu", "attn_fwd.cu", "ssd.cu", "peer.cu", "noalloc.cu"]
+CUDA_SOURCES = ["elementwise.cu", "suffix_scan.cu", "interface_jac.cu", "gated_norm.cu", "siso_prep.cu", "mamba_small.cu", "gemm_tcgen05.cu", "attn_pullback.cu", "attn_fwd.cu", "ssd.cu", "peer.cu", "noalloc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

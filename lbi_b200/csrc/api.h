@@ -89,6 +89,26 @@ int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const f
                       float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials, int64_t tokens, int seq_len,
                       int dkr_pad, int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
 
+// ---- Mamba block glue on the small tensors (mamba_small.cu) ------------------------------------------------
+// out = y * silu(z); bf16, numel a multiple of 8.
+int lbi_gate_silu_fwd(const void* y, const void* z, void* out, int64_t numel, cudaStream_t stream);
+// dyg, dy, dz [reps * numel] bf16; y, z [numel] shared by the reps stacked directions.
+int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, void* dy, void* dz, int64_t numel, int reps,
+                      cudaStream_t stream);
+// Mamba-3 per-token, per-head scalars.  dd_dt, dd_a, trap [B * L, H], angles [B * L, S], dt_bias [H] (fp32) ->
+// dt, a, sig, adt, gamma, scale, sp_dt, sp_a, live [B, L, H]; tanh_a [B, L, S]; theta [B, L, H, S] in [0, 2 pi).  S <= 64.
+int lbi_siso_small_fwd(const float* dd_dt, const float* dd_a, const float* trap, const float* angles, const float* dt_bias,
+                       float a_floor, float* dt, float* a, float* sig, float* adt, float* gamma, float* scale, float* tanh_a,
+                       float* theta, float* sp_dt, float* sp_a, float* live, int batch, int seq_len, int heads, int n_angles,
+                       cudaStream_t stream);
+// Cotangents dadt, dgamma, dscale [reps * B, L, H] and dtheta [reps * B, L, H, S] -> d_dd_dt, d_dd_a, d_trap [reps * B * L, H]
+// and d_angles [reps * B * L, S] (fp32 or bf16); the forward tensors [B, ...] are shared by the reps directions.
+// H <= 32, S <= 32.
+int lbi_siso_small_bwd(const float* dt, const float* a, const float* sig, const float* tanh_a, const float* sp_dt,
+                       const float* sp_a, const float* live, const float* dadt, const float* dtheta, const float* dgamma,
+                       const float* dscale, void* d_dd_dt, void* d_dd_a, void* d_trap, void* d_angles, int batch, int reps,
+                       int seq_len, int heads, int n_angles, int out_bf16, cudaStream_t stream);
+
 // ---- interface Jacobian products over a basis (interface_jac.cu) -----------------------------------------
 // out[b, p, :] = (((in_scale * g[b, p, :]) @ wa) o d[b, :]) @ wb;  g [B, P, din], wa [din, hidden], d [B, hidden] or null,
 // wb [hidden, dout] or null (then out [B, P, hidden] = (g @ wa) o d).  All fp32 row-major.

@@ -55,9 +55,24 @@ int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk, const void
 // Elementwise tail of the SSD backward.  dx_rev [B, seq_pad, H, 64] fp32 is the reversed-time scan result; x, gy, dx
 // [B, L, H, 64] bf16 or fp32; dt, ddt [B, L, H]; da [B, H, seq_pad]; a_param, d_skip (or null), dd (or null, accumulated) [H].
 //   dx = dt * dX + d_skip * gy,  ddt = da * a_param + dX . x,  dd[h] += sum gy . x
+// `reversed`: dx_rev is in reversed time (else natural order); x and dt hold `fbatch` sequences shared by batch / fbatch
+// stacked directions of gy.
 int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void* gy, const float* dt, const float* da,
                        const float* a_param, const float* d_skip, void* dx, float* ddt, float* dd, int batch, int seq_len,
-                       int seq_pad, int heads, int is_bf16, cudaStream_t stream);
+                       int seq_pad, int heads, int is_bf16, int reversed, int fbatch, cudaStream_t stream);
+
+// Fused chunk backward of lbi_ssd_scan_generic: every input cotangent from one pass (see bwd_chunk_kernel in ssd.cu).
+// Forward operands v [Bf*L, H*64], bk / cq [Bf*L, G*N] (per_head: [Bf*L, H*128]) bf16, weight / cum / skip_tok [Bf, H, L] fp32 and
+// state_in (bf16 incoming chunk states of the forward, [Bf, L/128, H, 64, N]; per_head [.., N, 64]) belong to `bmod` = Bf
+// sequences and are shared by batch / bmod stacked directions of gy [B*L, H*64] bf16.  d_final (cotangent of the final state,
+// fp32, layout of the states) may be null.  Scratch: chunk_cot [B, L/128, H, 64*N] fp32, d_out (same shape, bf16).
+// Results: d_init (or null), da, dskip (or null) [B, H, L]; dv [B*L, H*64] in dv32 or dv16 (cotangent of w_s v_s, plus
+// (d_skip[h] + skip_tok) * gy when given); dcq, dbk [B*L, H*N] per head in fp32 or bf16.  Three kernels on `stream`.
+int lbi_ssd_chunk_bwd(const void* v, const void* gy, const void* bk, const void* cq, const float* weight, const float* cum,
+                      const float* skip_tok, const float* d_skip, const void* state_in, const float* d_final, float* chunk_cot,
+                      void* d_out, float* d_init, float* da, float* dskip, float* dv32, void* dv16, float* dcq32, float* dbk32,
+                      void* dcq16, void* dbk16, int batch, int bmod, int seq_len, int heads, int groups, int d_state, int per_head,
+                      int strict, int* status, cudaStream_t stream);
 // out[b, l, g, :n] = sum over the heads h of group g of w[b, l, h] * y[b, l or seq_pad - 1 - l, h, :n]; y bf16 with rows of
 // `width` columns, w [B, L, H] or null, out bf16 or fp32.
 int lbi_ssd_group_sum(const void* y_bf16, const float* w, void* out, int batch, int seq_len, int seq_pad, int heads, int groups,

@@ -388,6 +388,95 @@ std::vector<Tensor> siso_prep_bwd(const Tensor& q, const Tensor& k, const Tensor
   return {dq, dk, bias.select(0, 0), bias.select(0, 1), dtheta, dgamma, dscale};
 }
 
+// ---- Mamba block glue (mamba_small.cu)
+Tensor gate_silu_fwd(const Tensor& y, const Tensor& z) {
+  CHECK_BF16(y);
+  CHECK_BF16(z);
+  TORCH_CHECK(z.sizes() == y.sizes() && y.numel() % 8 == 0, "gate_silu_fwd: y, z must have the same shape, numel % 8 == 0");
+  c10::cuda::CUDAGuard guard(y.device());
+  Tensor out = torch::empty_like(y);
+  check(lbi_gate_silu_fwd(y.data_ptr(), z.data_ptr(), out.data_ptr(), y.numel(), cur_stream()), "gate_silu_fwd");
+  return out;
+}
+
+std::tuple<Tensor, Tensor> gate_silu_bwd(const Tensor& dyg, const Tensor& y, const Tensor& z) {
+  CHECK_BF16(dyg);
+  CHECK_BF16(y);
+  CHECK_BF16(z);
+  TORCH_CHECK(z.sizes() == y.sizes() && y.numel() % 8 == 0 && y.numel() > 0 && dyg.numel() % y.numel() == 0,
+              "gate_silu_bwd: dyg must hold a whole number of copies of y's shape");
+  c10::cuda::CUDAGuard guard(y.device());
+  Tensor dy = torch::empty_like(dyg), dz = torch::empty_like(dyg);
+  check(lbi_gate_silu_bwd(dyg.data_ptr(), y.data_ptr(), z.data_ptr(), dy.data_ptr(), dz.data_ptr(), y.numel(),
+                          (int)(dyg.numel() / y.numel()), cur_stream()),
+        "gate_silu_bwd");
+  return {dy, dz};
+}
+
+// -> (dt, a, sig, adt, gamma, scale, tanh_angle, theta, sp_dt, sp_a, a_live)
+std::vector<Tensor> siso_small_fwd(const Tensor& dd_dt, const Tensor& dd_a, const Tensor& trap, const Tensor& angles,
+                                   const Tensor& dt_bias, double a_floor, int64_t batch, int64_t seq_len) {
+  CHECK_F32(dd_dt);
+  CHECK_F32(dd_a);
+  CHECK_F32(trap);
+  CHECK_F32(angles);
+  CHECK_F32(dt_bias);
+  c10::cuda::CUDAGuard guard(dd_dt.device());
+  const int64_t heads = dt_bias.numel(), na = angles.size(-1);
+  TORCH_CHECK(dd_dt.numel() == batch * seq_len * heads && dd_a.numel() == dd_dt.numel() && trap.numel() == dd_dt.numel() &&
+                  angles.numel() == batch * seq_len * na && na <= 64,
+              "siso_small_fwd: shape mismatch");
+  auto f32 = dd_dt.options();
+  std::vector<Tensor> out;
+  for (int i = 0; i < 6; ++i) out.push_back(torch::empty({batch, seq_len, heads}, f32));
+  out.push_back(torch::empty({batch, seq_len, na}, f32));
+  out.push_back(torch::empty({batch, seq_len, heads, na}, f32));
+  for (int i = 0; i < 3; ++i) out.push_back(torch::empty({batch, seq_len, heads}, f32));
+  check(lbi_siso_small_fwd(dd_dt.data_ptr<float>(), dd_a.data_ptr<float>(), trap.data_ptr<float>(), angles.data_ptr<float>(),
+                           dt_bias.data_ptr<float>(), (float)a_floor, out[0].data_ptr<float>(), out[1].data_ptr<float>(),
+                           out[2].data_ptr<float>(), out[3].data_ptr<float>(), out[4].data_ptr<float>(), out[5].data_ptr<float>(),
+                           out[6].data_ptr<float>(), out[7].data_ptr<float>(), out[8].data_ptr<float>(), out[9].data_ptr<float>(),
+                           out[10].data_ptr<float>(), (int)batch, (int)seq_len, (int)heads, (int)na, cur_stream()),
+        "siso_small_fwd");
+  return out;
+}
+
+// -> (d_dd_dt, d_dd_a, d_trap [P * B * L, H], d_angles [P * B * L, S]) in fp32 or bf16
+std::vector<Tensor> siso_small_bwd(const Tensor& dt, const Tensor& a, const Tensor& sig, const Tensor& tanh_a, const Tensor& sp_dt,
+                                   const Tensor& sp_a, const Tensor& live, const Tensor& dadt, const Tensor& dtheta,
+                                   const Tensor& dgamma, const Tensor& dscale, bool out_bf16) {
+  CHECK_F32(dt);
+  CHECK_F32(a);
+  CHECK_F32(sig);
+  CHECK_F32(tanh_a);
+  CHECK_F32(sp_dt);
+  CHECK_F32(sp_a);
+  CHECK_F32(live);
+  CHECK_F32(dadt);
+  CHECK_F32(dtheta);
+  CHECK_F32(dgamma);
+  CHECK_F32(dscale);
+  c10::cuda::CUDAGuard guard(dt.device());
+  TORCH_CHECK(dt.dim() == 3 && tanh_a.dim() == 3, "siso_small_bwd: dt [B, L, H], tanh_angle [B, L, S]");
+  const int64_t batch = dt.size(0), seq = dt.size(1), heads = dt.size(2), na = tanh_a.size(2);
+  TORCH_CHECK(heads <= 32 && na <= 32, "siso_small_bwd: at most 32 heads and 32 angles");
+  TORCH_CHECK(dadt.numel() % dt.numel() == 0 && dgamma.numel() == dadt.numel() && dscale.numel() == dadt.numel() &&
+                  dtheta.numel() == dadt.numel() * na,
+              "siso_small_bwd: cotangent shapes");
+  const int64_t reps = dadt.numel() / dt.numel();
+  auto opt = dt.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat);
+  const int64_t rows = reps * batch * seq;
+  Tensor d1 = torch::empty({rows, heads}, opt), d2 = torch::empty({rows, heads}, opt), d3 = torch::empty({rows, heads}, opt);
+  Tensor d4 = torch::empty({rows, na}, opt);
+  check(lbi_siso_small_bwd(dt.data_ptr<float>(), a.data_ptr<float>(), sig.data_ptr<float>(), tanh_a.data_ptr<float>(),
+                           sp_dt.data_ptr<float>(), sp_a.data_ptr<float>(), live.data_ptr<float>(), dadt.data_ptr<float>(),
+                           dtheta.data_ptr<float>(), dgamma.data_ptr<float>(), dscale.data_ptr<float>(), d1.data_ptr(), d2.data_ptr(),
+                           d3.data_ptr(), d4.data_ptr(), (int)batch, (int)reps, (int)seq, (int)heads, (int)na, out_bf16 ? 1 : 0,
+                           cur_stream()),
+        "siso_small_bwd");
+  return {d1, d2, d3, d4};
+}
+
 // (((in_scale g) @ wa) o d) @ wb over a basis: g [B, P, din] fp32, wa [din, hidden], d [B, hidden] or none, wb [hidden, dout] or none.
 Tensor interface_mlp_jac(const Tensor& g, const Tensor& wa, const c10::optional<Tensor>& d, const c10::optional<Tensor>& wb,
                          double in_scale) {
@@ -686,32 +775,91 @@ Tensor ssd_decay_grad(const Tensor& v, const Tensor& gy, const Tensor& bk, const
   return da.transpose(1, 2);
 }
 
+// Fused chunk backward (lbi_ssd_chunk_bwd).  v [Bf, L, H, 64], bk / cq [Bf, L, G, N], a / weight / skip_tok [Bf, L, H], state_in: the
+// third result of the forward scan; gy [P * Bf, L, H, 64].  Returns (dv [B, L, H, 64], dcq, dbk [B, L, H, N] per head, da, dskip
+// [B, L, H]); dv in bf16 when `dv_bf16`, dcq and dbk in bf16 when `dn_bf16`, else fp32.
+std::vector<Tensor> ssd_chunk_bwd(const Tensor& v, const Tensor& gy, const Tensor& bk, const Tensor& cq, const Tensor& a,
+                                  const c10::optional<Tensor>& weight, const c10::optional<Tensor>& skip_tok,
+                                  const c10::optional<Tensor>& d_skip, const Tensor& state_in, bool per_head, bool strict,
+                                  bool dv_bf16, bool dn_bf16) {
+  CHECK_BF16(v);
+  CHECK_BF16(gy);
+  CHECK_BF16(bk);
+  CHECK_BF16(cq);
+  CHECK_BF16(state_in);
+  CHECK_F32(a);
+  c10::cuda::CUDAGuard guard(v.device());
+  TORCH_CHECK(v.dim() == 4 && gy.dim() == 4 && bk.dim() == 4 && cq.sizes() == bk.sizes() && a.dim() == 3, "chunk_bwd: bad shapes");
+  const int64_t fbatch = v.size(0), batch = gy.size(0), seq = v.size(1), heads = v.size(2), hd = v.size(3), groups = bk.size(2), n = bk.size(3);
+  TORCH_CHECK(hd == 64 && batch % fbatch == 0 && gy.size(1) == seq && gy.size(2) == heads && gy.size(3) == 64 && seq % 128 == 0 &&
+                  bk.size(0) == fbatch && bk.size(1) == seq && a.size(0) == fbatch && a.size(1) == seq && a.size(2) == heads,
+              "chunk_bwd: shape mismatch");
+  TORCH_CHECK(!per_head || groups == heads, "chunk_bwd: per_head wants one bk / cq per head");
+  const int64_t chunks = seq / 128;
+  TORCH_CHECK(state_in.numel() == fbatch * chunks * heads * hd * n, "chunk_bwd: state_in must be [Bf, L/128, H, 64, N]");
+  auto f32 = v.options().dtype(at::kFloat);
+  Tensor ones = torch::ones({heads}, f32);
+  Tensor a_t = torch::empty({fbatch, heads, seq}, f32), cum = torch::empty({fbatch, heads, seq}, f32);
+  Tensor w_t, s_t;
+  if (weight) {
+    CHECK_F32((*weight));
+    TORCH_CHECK(weight->sizes() == a.sizes(), "chunk_bwd: weight must match a");
+    w_t = weight->transpose(1, 2).contiguous();
+  }
+  if (skip_tok) {
+    CHECK_F32((*skip_tok));
+    TORCH_CHECK(skip_tok->sizes() == a.sizes(), "chunk_bwd: skip_tok must match a");
+    s_t = skip_tok->transpose(1, 2).contiguous();
+  }
+  if (d_skip) CHECK_F32((*d_skip));
+  Tensor chunk_cot = torch::empty({batch, chunks, heads, hd * n}, f32);
+  Tensor d_out = torch::empty({batch, chunks, heads, hd * n}, v.options());
+  Tensor da = torch::empty({batch, heads, seq}, f32), dskip = torch::empty({batch, heads, seq}, f32);
+  Tensor dv = torch::empty({batch, seq, heads, hd}, dv_bf16 ? v.options() : f32);
+  Tensor dcq = torch::empty({batch, seq, heads, n}, dn_bf16 ? v.options() : f32), dbk = torch::empty_like(dcq);
+  Tensor st = status_word(v);
+  check(lbi_ssd_cumsum(a.data_ptr<float>(), nullptr, ones.data_ptr<float>(), a_t.data_ptr<float>(), cum.data_ptr<float>(), (int)fbatch,
+                       (int)seq, (int)heads, 0, 0.f, 0.f, cur_stream()),
+        "chunk_bwd_cumsum");
+  check(lbi_ssd_chunk_bwd(v.data_ptr(), gy.data_ptr(), bk.data_ptr(), cq.data_ptr(), weight ? w_t.data_ptr<float>() : nullptr,
+                          cum.data_ptr<float>(), skip_tok ? s_t.data_ptr<float>() : nullptr,
+                          d_skip ? d_skip->data_ptr<float>() : nullptr, state_in.data_ptr(), nullptr, chunk_cot.data_ptr<float>(),
+                          d_out.data_ptr(), nullptr, da.data_ptr<float>(), dskip.data_ptr<float>(),
+                          dv_bf16 ? nullptr : dv.data_ptr<float>(), dv_bf16 ? dv.data_ptr() : nullptr,
+                          dn_bf16 ? nullptr : dcq.data_ptr<float>(), dn_bf16 ? nullptr : dbk.data_ptr<float>(),
+                          dn_bf16 ? dcq.data_ptr() : nullptr, dn_bf16 ? dbk.data_ptr() : nullptr, (int)batch, (int)fbatch, (int)seq,
+                          (int)heads, (int)groups, (int)n, per_head ? 1 : 0, strict ? 1 : 0, st.data_ptr<int>(), cur_stream()),
+        "ssd_chunk_bwd");
+  return {dv, dcq, dbk, da.transpose(1, 2), dskip.transpose(1, 2)};
+}
+
 // dx_rev [B, Lp, H, 64] fp32 (reversed time), x / gy [B, L, H, 64], dt [B, L, H], da [B, Lp, H] (a transposed view of the
 // decay-gradient result), a_param [H], d_skip [H] or none -> (dx like x, ddt [B, L, H], dD [H] or empty).
 std::tuple<Tensor, Tensor, Tensor> ssd_bwd_finish(const Tensor& dx_rev, const Tensor& x, const Tensor& gy, const Tensor& dt, const Tensor& da,
-                                                  const Tensor& a_param, const c10::optional<Tensor>& d_skip) {
+                                                  const Tensor& a_param, const c10::optional<Tensor>& d_skip, bool reversed) {
   CHECK_F32(dx_rev);
   CHECK_F32(dt);
   CHECK_F32(a_param);
   c10::cuda::CUDAGuard guard(x.device());
-  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && gy.is_contiguous() && gy.sizes() == x.sizes() && gy.scalar_type() == x.scalar_type() &&
-                  (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat) && x.dim() == 4 && x.size(3) == 64,
-              "ssd_bwd_finish: x, gy must be contiguous [B, L, H, 64] bf16 / fp32");
-  const int64_t batch = x.size(0), seq = x.size(1), heads = x.size(2), seq_pad = dx_rev.size(1);
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && gy.is_contiguous() && gy.dim() == 4 && gy.scalar_type() == x.scalar_type() &&
+                  (x.scalar_type() == at::kBFloat16 || x.scalar_type() == at::kFloat) && x.dim() == 4 && x.size(3) == 64 &&
+                  gy.size(1) == x.size(1) && gy.size(2) == x.size(2) && gy.size(3) == 64 && gy.size(0) % x.size(0) == 0,
+              "ssd_bwd_finish: x [Bf, L, H, 64], gy [P * Bf, L, H, 64], contiguous bf16 / fp32");
+  const int64_t batch = gy.size(0), fbatch = x.size(0), seq = x.size(1), heads = x.size(2), seq_pad = dx_rev.size(1);
   TORCH_CHECK(dx_rev.dim() == 4 && dx_rev.size(0) == batch && dx_rev.size(2) == heads && dx_rev.size(3) == 64 && seq_pad >= seq,
               "ssd_bwd_finish: dx_rev must be [B, Lp, H, 64]");
-  TORCH_CHECK(dt.sizes() == at::IntArrayRef({batch, seq, heads}), "ssd_bwd_finish: dt must be [B, L, H]");
+  TORCH_CHECK(dt.sizes() == at::IntArrayRef({fbatch, seq, heads}), "ssd_bwd_finish: dt must be [Bf, L, H]");
   Tensor da_t = da.transpose(1, 2).contiguous();   // [B, H, Lp]; free when da is the transposed view the kernel returned
   TORCH_CHECK(da_t.scalar_type() == at::kFloat && da_t.size(0) == batch && da_t.size(1) == heads && da_t.size(2) == seq_pad,
               "ssd_bwd_finish: da must be [B, Lp, H] fp32");
-  Tensor dx = torch::empty_like(x);
+  Tensor dx = torch::empty_like(gy);
   Tensor ddt = torch::empty({batch, seq, heads}, dt.options());
   Tensor dd = d_skip ? torch::zeros({heads}, dt.options()) : torch::empty({0}, dt.options());
   if (d_skip) CHECK_F32((*d_skip));
   check(lbi_ssd_bwd_finish(dx_rev.data_ptr<float>(), x.data_ptr(), gy.data_ptr(), dt.data_ptr<float>(), da_t.data_ptr<float>(),
                            a_param.data_ptr<float>(), d_skip ? d_skip->data_ptr<float>() : nullptr, dx.data_ptr(), ddt.data_ptr<float>(),
                            d_skip ? dd.data_ptr<float>() : nullptr, (int)batch, (int)seq, (int)seq_pad, (int)heads,
-                           x.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+                           x.scalar_type() == at::kBFloat16 ? 1 : 0, reversed ? 1 : 0, (int)fbatch, cur_stream()),
         "ssd_bwd_finish");
   return {dx, ddt, dd};
 }
@@ -896,6 +1044,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("siso_prep_fwd", &siso_prep_fwd);
   m.def("siso_prep_bwd", &siso_prep_bwd, py::arg("q"), py::arg("k"), py::arg("q_bias"), py::arg("k_bias"), py::arg("theta"),
         py::arg("gamma"), py::arg("scale"), py::arg("dqr"), py::arg("dkr"), py::arg("dqk"), py::arg("dkr_reversed") = false);
+  m.def("gate_silu_fwd", &gate_silu_fwd);
+  m.def("gate_silu_bwd", &gate_silu_bwd);
+  m.def("siso_small_fwd", &siso_small_fwd);
+  m.def("siso_small_bwd", &siso_small_bwd);
   m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);
   m.def("gated_rmsnorm_bwd", &gated_rmsnorm_bwd);
   m.def("layernorm_jac", &layernorm_jac);
@@ -910,7 +1062,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("siso_chunk_scan_fwd", &siso_chunk_scan_fwd);
   m.def("ssd_scan_generic", &ssd_scan_generic);
   m.def("ssd_decay_grad", &ssd_decay_grad);
-  m.def("ssd_bwd_finish", &ssd_bwd_finish);
+  m.def("ssd_bwd_finish", &ssd_bwd_finish, py::arg("dx_rev"), py::arg("x"), py::arg("gy"), py::arg("dt"), py::arg("da"),
+        py::arg("a_param"), py::arg("d_skip"), py::arg("reversed") = true);
+  m.def("ssd_chunk_bwd", &ssd_chunk_bwd);
   m.def("ssd_group_sum", &ssd_group_sum);
   m.def("kernel_status", &kernel_status);
   m.def("set_peer_wait_limit_ms", &set_peer_wait_limit_ms);

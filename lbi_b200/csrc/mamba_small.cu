@@ -1,0 +1,266 @@
+// Mamba block glue on the small tensors: the SiLU gate and the per-token, per-head scalars of the Mamba-3 SISO mixer.
+//
+// 1. gate            yg = y * silu(z), and its pullback for P stacked directions that share y and z.
+// 2. siso small fwd  DT = softplus(dd_dt + bias), A = min(-softplus(dd_A), -floor), ADT = A DT, the trapezoid weights
+//                    gamma_t = DT_t sigmoid(trap_t), scale_t = gamma_t + DT_{t+1} (1 - sigmoid(trap_{t+1})), and the rotary phase
+//                    theta_t = (sum_{i <= t} pi tanh(angle_i) DT_i) mod 2 pi  (a running sum over the tokens of a sequence).
+// 3. siso small bwd  cotangents of (ADT, theta, gamma, scale) -> cotangents of the four in_proj slices (dd_dt, dd_A, trap,
+//                    angles); the running sum turns into a reversed running sum of dtheta.
+// One warp owns one head, its lanes the rotary angles; a block walks the tokens of one sequence.  They replace the
+// reference's Triton kernels angle_dt_fwd / angle_dt_bwd (backbones/mamba3/ops/triton/mamba3/angle_dt.py:26, 234) and
+// the dd_dt / trap part of its backward (mamba3_siso_bwd.py:1418).
+#include "api.h"
+#include "common.cuh"
+
+namespace lbi {
+namespace msmall {
+
+constexpr float PI_F = 3.14159265358979323846f;
+constexpr float TWO_PI_F = 6.28318530717958647692f;
+
+__device__ __forceinline__ float softplus_(float v) { return v > 20.f ? v : log1pf(__expf(v)); }
+
+// ------------------------------------------------------------------------------------------------ gate
+__global__ void gate_silu_fwd_kernel(const bf16x8* __restrict__ y, const bf16x8* __restrict__ z, bf16x8* __restrict__ out, int64_t n8) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    float a[8], b[8];
+    unpack8(y[i], a);
+    unpack8(z[i], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] *= b[j] * sigmoidf_(b[j]);
+    out[i] = pack8(a);
+  }
+}
+
+// dyg [reps * n8]; y, z [n8] shared by the reps directions.
+__global__ void gate_silu_bwd_kernel(const bf16x8* __restrict__ dyg, const bf16x8* __restrict__ y, const bf16x8* __restrict__ z,
+                                     bf16x8* __restrict__ dy, bf16x8* __restrict__ dz, int64_t n8, int reps) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    float yv[8], zv[8], silu[8], slope[8];
+    unpack8(y[i], yv);
+    unpack8(z[i], zv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = sigmoidf_(zv[j]);
+      silu[j] = zv[j] * s;
+      slope[j] = yv[j] * s * (1.f + zv[j] * (1.f - s));
+    }
+    for (int r = 0; r < reps; ++r) {
+      float g[8], a[8], b[8];
+      unpack8(dyg[(int64_t)r * n8 + i], g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        a[j] = g[j] * silu[j];
+        b[j] = g[j] * slope[j];
+      }
+      dy[(int64_t)r * n8 + i] = pack8(a);
+      dz[(int64_t)r * n8 + i] = pack8(b);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ siso small, forward
+// grid (batch, ceil(heads / warps)), block = warps * 32.  Inputs dd_dt, dd_a, trap [B * L, H], angles [B * L, S] fp32.
+__global__ void siso_small_fwd_kernel(const float* __restrict__ dd_dt, const float* __restrict__ dd_a, const float* __restrict__ trap,
+                                      const float* __restrict__ angles, const float* __restrict__ dt_bias, float a_floor,
+                                      float* __restrict__ dt_o, float* __restrict__ a_o, float* __restrict__ sig_o,
+                                      float* __restrict__ adt_o, float* __restrict__ gamma_o, float* __restrict__ scale_o,
+                                      float* __restrict__ tanh_o, float* __restrict__ theta_o, float* __restrict__ spdt_o,
+                                      float* __restrict__ spa_o, float* __restrict__ live_o, int seq_len, int heads, int n_angles) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (h >= heads) return;
+  const float bias = dt_bias[h];
+  const int64_t row0 = (int64_t)b * seq_len;
+  const bool writes_tanh = h == 0;
+  float acc0 = 0.f, acc1 = 0.f;   // running phase of angles lane and lane + 32
+  float carry_next = 0.f;         // DT_{t+1} (1 - sig_{t+1}) seen from token t: filled by walking the elementwise part backwards
+  // elementwise part, tokens spread over the lanes (independent of the running sum)
+  for (int t0 = seq_len - 32; t0 > -32; t0 -= 32) {
+    const int t = t0 + lane;
+    float dt = 0.f, sg = 0.f;
+    if (t >= 0) {
+      const int64_t i = (row0 + t) * heads + h;
+      const float pre = dd_dt[i] + bias;
+      dt = softplus_(pre);
+      const float raw_a = -softplus_(dd_a[i]);
+      const float a = fminf(raw_a, -a_floor);
+      sg = sigmoidf_(trap[i]);
+      dt_o[i] = dt;
+      a_o[i] = a;
+      sig_o[i] = sg;
+      adt_o[i] = a * dt;
+      gamma_o[i] = dt * sg;
+      spdt_o[i] = sigmoidf_(pre);
+      spa_o[i] = sigmoidf_(dd_a[i]);
+      live_o[i] = raw_a < -a_floor ? 1.f : 0.f;
+    }
+    const float mine = dt * (1.f - sg);
+    float next = __shfl_down_sync(0xffffffffu, mine, 1);
+    if (lane == 31) next = carry_next;
+    carry_next = __shfl_sync(0xffffffffu, mine, 0);
+    if (t >= 0) scale_o[(row0 + t) * heads + h] = dt * sg + next;
+  }
+  __syncwarp();
+  // rotary phase: sequential over the tokens, lanes = angles
+  const bool has0 = lane < n_angles, has1 = lane + 32 < n_angles;
+  for (int t0 = 0; t0 < seq_len; t0 += 8) {
+    float dts[8], t0v[8], t1v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int t = t0 + j;
+      dts[j] = t < seq_len ? dt_o[(row0 + t) * heads + h] : 0.f;
+      t0v[j] = (t < seq_len && has0) ? tanhf(angles[(row0 + t) * n_angles + lane]) : 0.f;
+      t1v[j] = (t < seq_len && has1) ? tanhf(angles[(row0 + t) * n_angles + lane + 32]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int t = t0 + j;
+      if (t >= seq_len) break;
+      acc0 += PI_F * t0v[j] * dts[j];
+      acc1 += PI_F * t1v[j] * dts[j];
+      acc0 -= TWO_PI_F * floorf(acc0 * (1.f / TWO_PI_F));
+      acc1 -= TWO_PI_F * floorf(acc1 * (1.f / TWO_PI_F));
+      const int64_t o = ((row0 + t) * heads + h) * n_angles;
+      if (has0) theta_o[o + lane] = acc0;
+      if (has1) theta_o[o + lane + 32] = acc1;
+      if (writes_tanh) {
+        if (has0) tanh_o[(row0 + t) * n_angles + lane] = t0v[j];
+        if (has1) tanh_o[(row0 + t) * n_angles + lane + 32] = t1v[j];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ siso small, backward
+// grid (P * B), block = heads * 32 (heads <= 32, n_angles <= 32).  Forward tensors are indexed by b = blockIdx.x % batch.
+constexpr int TL = 8;   // tokens per tile
+
+template <typename OutT>
+__device__ __forceinline__ void put(OutT* p, float v);
+template <>
+__device__ __forceinline__ void put<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void put<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
+
+template <typename OutT>
+__global__ void __launch_bounds__(1024) siso_small_bwd_kernel(
+    const float* __restrict__ dt, const float* __restrict__ a, const float* __restrict__ sig, const float* __restrict__ tanh_a,
+    const float* __restrict__ sp_dt, const float* __restrict__ sp_a, const float* __restrict__ live,
+    const float* __restrict__ dadt, const float* __restrict__ dtheta, const float* __restrict__ dgamma,
+    const float* __restrict__ dscale, OutT* __restrict__ d_dd_dt, OutT* __restrict__ d_dd_a, OutT* __restrict__ d_trap,
+    OutT* __restrict__ d_angles, int batch, int seq_len, int heads, int n_angles) {
+  extern __shared__ float contrib[];   // [TL][heads][32]: pi * (reversed running sum of dtheta) * DT per token, head, angle
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = warp;
+  const int pb = blockIdx.x, b = pb % batch;
+  const int64_t frow0 = (int64_t)b * seq_len, crow0 = (int64_t)pb * seq_len;
+  const bool has = lane < n_angles;
+  float acc = 0.f;
+  for (int t_hi = seq_len - 1; t_hi >= 0; t_hi -= TL) {
+    float dth[TL], tn[TL], dts[TL];
+#pragma unroll
+    for (int j = 0; j < TL; ++j) {
+      const int t = t_hi - j;
+      const bool ok = t >= 0;
+      dth[j] = (ok && has) ? dtheta[((crow0 + t) * heads + h) * n_angles + lane] : 0.f;
+      tn[j] = (ok && has) ? tanh_a[(frow0 + t) * n_angles + lane] : 0.f;
+      dts[j] = ok ? dt[(frow0 + t) * heads + h] : 0.f;
+    }
+    float mine = 0.f;   // lane j keeps the rotary part of d DT of token t_hi - j
+#pragma unroll
+    for (int j = 0; j < TL; ++j) {
+      acc += dth[j];
+      const float part = PI_F * warp_sum(acc * tn[j]);
+      if (lane == j) mine = part;
+      contrib[(j * heads + h) * 32 + lane] = PI_F * acc * dts[j];
+    }
+    if (lane < TL) {
+      const int t = t_hi - lane;
+      if (t >= 0) {
+        const int64_t fi = (frow0 + t) * heads + h, ci = (crow0 + t) * heads + h;
+        const float dsc = dscale[ci];
+        const float dsc_prev = t > 0 ? dscale[ci - heads] : 0.f;
+        const float dg_all = dgamma[ci] + dsc;
+        const float sg = sig[fi], dtv = dt[fi], da = dadt[ci];
+        const float d_dt = da * a[fi] + mine + dg_all * sg + dsc_prev * (1.f - sg);
+        const float d_sig = dtv * (dg_all - dsc_prev);
+        put(d_dd_dt + ci, d_dt * sp_dt[fi]);
+        put(d_dd_a + ci, -(da * dtv) * sp_a[fi] * live[fi]);
+        put(d_trap + ci, d_sig * sg * (1.f - sg));
+      }
+    }
+    __syncthreads();
+    // sum the heads: TL * n_angles outputs
+    for (int o = threadIdx.x; o < TL * 32; o += blockDim.x) {
+      const int j = o >> 5, s = o & 31;
+      const int t = t_hi - j;
+      if (t >= 0 && s < n_angles) {
+        float sum = 0.f;
+        for (int hh = 0; hh < heads; ++hh) sum += contrib[(j * heads + hh) * 32 + s];
+        const float tv = tanh_a[(frow0 + t) * n_angles + s];
+        put(d_angles + (crow0 + t) * n_angles + s, sum * (1.f - tv * tv));
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace msmall
+}  // namespace lbi
+
+extern "C" int lbi_gate_silu_fwd(const void* y, const void* z, void* out, int64_t numel, cudaStream_t st) {
+  using namespace lbi;
+  if (numel <= 0) return 0;
+  if (numel % 8) return (int)cudaErrorInvalidValue;
+  const int64_t n8 = numel / 8;
+  const int blocks = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
+  msmall::gate_silu_fwd_kernel<<<blocks, 256, 0, st>>>((const bf16x8*)y, (const bf16x8*)z, (bf16x8*)out, n8);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, void* dy, void* dz, int64_t numel, int reps,
+                                 cudaStream_t st) {
+  using namespace lbi;
+  if (numel <= 0 || reps <= 0) return 0;
+  if (numel % 8) return (int)cudaErrorInvalidValue;
+  const int64_t n8 = numel / 8;
+  const int blocks = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
+  msmall::gate_silu_bwd_kernel<<<blocks, 256, 0, st>>>((const bf16x8*)dyg, (const bf16x8*)y, (const bf16x8*)z, (bf16x8*)dy,
+                                                       (bf16x8*)dz, n8, reps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_siso_small_fwd(const float* dd_dt, const float* dd_a, const float* trap, const float* angles,
+                                  const float* dt_bias, float a_floor, float* dt, float* a, float* sig, float* adt, float* gamma,
+                                  float* scale, float* tanh_a, float* theta, float* sp_dt, float* sp_a, float* live, int batch,
+                                  int seq_len, int heads, int n_angles, cudaStream_t st) {
+  using namespace lbi;
+  if (batch <= 0 || seq_len <= 0) return 0;
+  if (n_angles > 64 || n_angles <= 0) return (int)cudaErrorInvalidValue;
+  const int warps = heads < 8 ? heads : 8;
+  dim3 grid(batch, (heads + warps - 1) / warps);
+  msmall::siso_small_fwd_kernel<<<grid, warps * 32, 0, st>>>(dd_dt, dd_a, trap, angles, dt_bias, a_floor, dt, a, sig, adt, gamma,
+                                                             scale, tanh_a, theta, sp_dt, sp_a, live, seq_len, heads, n_angles);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_siso_small_bwd(const float* dt, const float* a, const float* sig, const float* tanh_a, const float* sp_dt,
+                                  const float* sp_a, const float* live, const float* dadt, const float* dtheta,
+                                  const float* dgamma, const float* dscale, void* d_dd_dt, void* d_dd_a, void* d_trap,
+                                  void* d_angles, int batch, int reps, int seq_len, int heads, int n_angles, int out_bf16,
+                                  cudaStream_t st) {
+  using namespace lbi;
+  if (batch <= 0 || reps <= 0 || seq_len <= 0) return 0;
+  if (heads > 32 || heads <= 0 || n_angles > 32 || n_angles <= 0) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)msmall::TL * heads * 32 * sizeof(float);
+  if (out_bf16)
+    msmall::siso_small_bwd_kernel<__nv_bfloat16><<<batch * reps, heads * 32, smem, st>>>(
+        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, (__nv_bfloat16*)d_dd_dt, (__nv_bfloat16*)d_dd_a,
+        (__nv_bfloat16*)d_trap, (__nv_bfloat16*)d_angles, batch, seq_len, heads, n_angles);
+  else
+    msmall::siso_small_bwd_kernel<float><<<batch * reps, heads * 32, smem, st>>>(
+        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, (float*)d_dd_dt, (float*)d_dd_a, (float*)d_trap,
+        (float*)d_angles, batch, seq_len, heads, n_angles);
+  return (int)cudaGetLastError();
+}

@@ -119,6 +119,8 @@ struct StateParams {
   const float* cum;     // [B, H, L_total]
   float* states;        // [B, C, H, 64, N]
   int* status;
+  int rev;              // 1: cotangent form, rows scaled by exp(cum_l) (no weight) instead of exp(total - cum_l) dt_l
+  int bmod;             // the B operand, dt and cum belong to batch b % bmod (forward tensors shared by stacked directions)
 };
 
 template <int N, bool PH>
@@ -131,6 +133,8 @@ __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_const
   const int h0 = PH ? hp : 2 * hp;
   const int g = PH ? h0 : h0 / (p.heads / p.groups);
   const int row0 = b * p.seq_len + c * L;
+  const int fb = b % p.bmod;
+  const int frow0 = fb * p.seq_len + c * L;
   constexpr uint32_t TMEM_COLS = PH ? 64 : N;   // a power of two >= 32
 
   if (threadIdx.x == 0) {
@@ -154,7 +158,7 @@ __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_const
       mbar_arrive_expect_tx(&s.bar_full, ((PH ? 1 : 2) + N / 64) * PANEL);
       tma_load_2d(s.xs[0], &map_x, &s.bar_full, ((h0 / p.v_div) * p.v_mod + h0 % p.v_mod) * P, row0);
       if (!PH) tma_load_2d(s.xs[1], &map_x, &s.bar_full, (((h0 + 1) / p.v_div) * p.v_mod + (h0 + 1) % p.v_mod) * P, row0);
-      for (int q = 0; q < N / 64; ++q) tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, row0);
+      for (int q = 0; q < N / 64; ++q) tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, frow0);
       bool ok = mbar_wait(&s.bar_scaled, 0, abortp, p.status, 51);
       if (ok) {
         fence_after_sync();
@@ -170,10 +174,13 @@ __global__ void __launch_bounds__(THREADS) chunk_state_kernel(const __grid_const
     }
   } else {
     const int l = warp * 32 + lane;   // token of the chunk handled in the scaling pass; row (h, p) in the epilogue
-    const int64_t base0 = ((int64_t)b * p.heads + h0) * p.seq_len + c * L;
+    const int64_t base0 = ((int64_t)fb * p.heads + h0) * p.seq_len + c * L;
     const int64_t base1 = base0 + p.seq_len;
-    const float f0 = ex2((p.cum[base0 + L - 1] - p.cum[base0 + l]) * LOG2E) * (p.dt ? p.dt[base0 + l] : 1.f);
-    const float f1 = PH ? 0.f : ex2((p.cum[base1 + L - 1] - p.cum[base1 + l]) * LOG2E) * (p.dt ? p.dt[base1 + l] : 1.f);
+    const float f0 = p.rev ? ex2(p.cum[base0 + l] * LOG2E)
+                           : ex2((p.cum[base0 + L - 1] - p.cum[base0 + l]) * LOG2E) * (p.dt ? p.dt[base0 + l] : 1.f);
+    const float f1 = PH ? 0.f
+                        : (p.rev ? ex2(p.cum[base1 + l] * LOG2E)
+                                 : ex2((p.cum[base1 + L - 1] - p.cum[base1 + l]) * LOG2E) * (p.dt ? p.dt[base1 + l] : 1.f));
     bool ok = mbar_wait(&s.bar_full, 0, abortp, p.status, 52);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
@@ -657,6 +664,405 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
 }
 
 
+// ------------------------------------------------------------------------------------------------ 5b. fused chunk backward
+// All input cotangents of the scan
+//   y_t = sum_{s <= t} e^{c_t - c_s} (cq_t . bk_s) w_s v_s + e^{c_t} cq_t . S_in        (s < t when `strict`)
+// for one (direction, chunk, head) per CTA, from one pass over the tiles.  With W[t, s] = e^{c_t - c_s} on the causal
+// mask, G1 = cq bk^T, G2 = gy v^T (both in TMEM, as in the decay-gradient kernel above):
+//   M   = W o G1                  bf16 tile [t][s] in shared memory
+//   dGw = W o G2 o w_s            bf16 tile [t][s] in shared memory
+//   dX_s   = sum_t M[t, s] gy_t + e^{c_end - c_s} bk_s . D_out                         (cotangent of w_s v_s)
+//   dcq_t  = sum_s dGw[t, s] bk_s + e^{c_t} gy_t . S_in
+//   dbk_s  = sum_t dGw[t, s] cq_t + w_s e^{c_end - c_s} v_s . D_out
+//   da_u   = the decay gradient (pairs s < u <= t; E = G1 o dGw, row and column sums; state terms through S_in, D_out)
+//   dskip_t = gy_t . v_t = G2[t, t]
+// S_in is the state entering the chunk (cached by the forward), D_out the cotangent of the state leaving it, produced by
+// the reversed state passing below from the per-chunk sums sum_t e^{c_t} gy_t cq_t^T (chunk_state_kernel with `rev`).
+// Forward operands (cq, bk, v, S_in, cum, w, skip) are indexed by batch b % bmod, so P stacked cotangent directions read one
+// copy of them (from L2 after the first direction).  TMEM: G1 -> dcq [0, 128), G2 -> dbk [128, 256), cq S_in^T [256, 320),
+// bk D_out^T [320, 384), dX [384, 448).  Replaces the reference's _chunk_scan_chunk_state_bwd_dx, _chunk_state_bwd_db,
+// _chunk_scan_bwd_dc, _chunk_scan_bwd_dcb, _bmm_chunk_bwd and ddAcs kernels (backbones/mamba2/ops/triton/ssd_combined.py:396-513)
+// and the Mamba-3 dqkv kernel (backbones/mamba3/ops/triton/mamba3/mamba3_siso_bwd.py:202-594).
+template <int N>
+struct SmemBwd {
+  alignas(1024) uint8_t ct[N / 64][PANEL];      // cq [t][64 n] per panel
+  alignas(1024) uint8_t bt[N / 64][PANEL];      // bk [s][64 n] per panel
+  alignas(1024) uint8_t gyt[PANEL];             // gy [t][64 p]; rows scaled by e^{c_t} once dX has been taken
+  alignas(1024) uint8_t xt[PANEL];              // v  [s][64 p]; rows scaled by w_s e^{c_end - c_s}
+  alignas(1024) uint8_t hin[N / 64][P * 128];   // S_in
+  alignas(1024) uint8_t dho[N / 64][P * 128];   // D_out
+  alignas(1024) uint8_t mt[2][PANEL];           // M   [t][64 s] per panel
+  alignas(1024) uint8_t gt[2][PANEL];           // dGw [t][64 s] per panel
+  float tr[4][32][33];                          // per-warp transpose scratch for the column sums of E
+  float colpart[4][L];
+  float cum2[L];
+  float wv[L];
+  float r2[L];
+  float r3[L];
+  float red[4];
+  uint64_t bar_full, bar_mma, bar_w, bar_x, bar_x2, bar_y, bar_rows;
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct BwdParams {
+  int seq_len, heads, groups, chunks, bmod, strict;
+  const float* weight;     // [Bf, H, L] or null
+  const float* cum;        // [Bf, H, L]
+  const float* skip_tok;   // [Bf, H, L] or null: dv += skip * gy
+  const float* d_skip;     // [H] or null: dv += d_skip[h] * gy
+  float* da;               // [B, H, L]
+  float* dskip;            // [B, H, L] or null
+  float* dv32;             // [B * L, H * 64], one of dv32 / dv16
+  __nv_bfloat16* dv16;
+  float* dcq32;            // [B * L, H * N], one of the fp32 / bf16 pairs
+  float* dbk32;
+  __nv_bfloat16* dcq16;
+  __nv_bfloat16* dbk16;
+  int* status;
+};
+
+__device__ __forceinline__ void store_row(float* dst32, __nv_bfloat16* dst16, const uint32_t* r, int n) {
+  if (dst32) {
+    for (int e = 0; e < n / 4; ++e)
+      reinterpret_cast<float4*>(dst32)[e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                                        __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
+  } else {
+    for (int e = 0; e < n / 8; ++e)
+      reinterpret_cast<uint4*>(dst16)[e] =
+          make_uint4(pack2(__uint_as_float(r[8 * e]), __uint_as_float(r[8 * e + 1])),
+                     pack2(__uint_as_float(r[8 * e + 2]), __uint_as_float(r[8 * e + 3])),
+                     pack2(__uint_as_float(r[8 * e + 4]), __uint_as_float(r[8 * e + 5])),
+                     pack2(__uint_as_float(r[8 * e + 6]), __uint_as_float(r[8 * e + 7])));
+  }
+}
+
+template <int N, bool PH>
+__global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                            const __grid_constant__ CUtensorMap map_gy,
+                                                            const __grid_constant__ CUtensorMap map_b,
+                                                            const __grid_constant__ CUtensorMap map_c,
+                                                            const __grid_constant__ CUtensorMap map_hin,
+                                                            const __grid_constant__ CUtensorMap map_dho, const BwdParams p) {
+  extern __shared__ uint8_t raw_smem[];
+  SmemBwd<N>& s = *reinterpret_cast<SmemBwd<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int fb = b % p.bmod;
+  const int g = PH ? h : h / (p.heads / p.groups);
+  const int row0 = b * p.seq_len + c * L, frow0 = fb * p.seq_len + c * L;
+  constexpr int KS = N / 16;
+  constexpr uint32_t PANEL16 = PANEL >> 4, PV16 = (P * 128) >> 4;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    mbar_init(&s.bar_full, 1);
+    mbar_init(&s.bar_mma, 1);
+    mbar_init(&s.bar_w, 4);
+    mbar_init(&s.bar_x, 1);
+    mbar_init(&s.bar_x2, 4);
+    mbar_init(&s.bar_y, 1);
+    mbar_init(&s.bar_rows, 4);
+    fence_barrier_init();
+    prefetch_tmap(&map_x);
+    prefetch_tmap(&map_gy);
+    prefetch_tmap(&map_b);
+    prefetch_tmap(&map_c);
+    prefetch_tmap(&map_hin);
+    prefetch_tmap(&map_dho);
+  }
+  if (warp == 4) tmem_alloc(&s.tmem_base, TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abortp = &s.abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&s.bar_full, (2 * (N / 64) + 2) * PANEL + 2 * (N / 64) * P * 128);
+      const int st_in = (int)((((int64_t)fb * p.chunks + c) * p.heads + h) * (PH ? N : P));
+      const int st_out = (int)((((int64_t)b * p.chunks + c) * p.heads + h) * (PH ? N : P));
+      for (int q = 0; q < N / 64; ++q) {
+        tma_load_2d(s.ct[q], &map_c, &s.bar_full, g * N + q * 64, frow0);
+        tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, frow0);
+        if (!PH) {
+          tma_load_2d(s.hin[q], &map_hin, &s.bar_full, q * 64, st_in);
+          tma_load_2d(s.dho[q], &map_dho, &s.bar_full, q * 64, st_out);
+        }
+      }
+      if (PH) {
+        tma_load_2d(s.hin[0], &map_hin, &s.bar_full, 0, st_in);
+        tma_load_2d(s.dho[0], &map_dho, &s.bar_full, 0, st_out);
+      }
+      tma_load_2d(s.gyt, &map_gy, &s.bar_full, h * P, row0);
+      tma_load_2d(s.xt, &map_x, &s.bar_full, h * P, frow0);
+      const uint64_t kmajor0 = make_smem_desc(0, 16, 1024), mnmajor0 = make_smem_desc(0, PANEL, 1024),
+                     mnstate0 = make_smem_desc(0, P * 128, 1024);
+      const uint32_t ct16 = smem_u32(s.ct[0]) >> 4, bt16 = smem_u32(s.bt[0]) >> 4, gy16 = smem_u32(s.gyt) >> 4,
+                     xt16 = smem_u32(s.xt) >> 4, hin16 = smem_u32(s.hin[0]) >> 4, dho16 = smem_u32(s.dho[0]) >> 4,
+                     mt16 = smem_u32(s.mt[0]) >> 4, gt16 = smem_u32(s.gt[0]) >> 4;
+      bool ok = mbar_wait(&s.bar_full, 0, abortp, p.status, 71);
+      if (ok) {
+        fence_after_sync();
+        const uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 0);
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, kmajor0 + bt16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   idesc_g, kk);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) mma_bf16(tmem + 128, kmajor0 + gy16 + kk * 2, kmajor0 + xt16 + kk * 2, idesc_g, kk);
+        const uint32_t idesc_s = make_idesc_bf16(128, 64, 0, PH ? 1 : 0);
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem + 256, kmajor0 + ct16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   PH ? mnmajor0 + hin16 + 128 * kk : kmajor0 + hin16 + (kk >> 2) * PV16 + (kk & 3) * 2, idesc_s, kk);
+#pragma unroll
+        for (int kk = 0; kk < KS; ++kk)
+          mma_bf16(tmem + 320, kmajor0 + bt16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
+                   PH ? mnmajor0 + dho16 + 128 * kk : kmajor0 + dho16 + (kk >> 2) * PV16 + (kk & 3) * 2, idesc_s, kk);
+        mma_commit(&s.bar_mma);
+        ok = mbar_wait(&s.bar_w, 0, abortp, p.status, 72);
+      }
+      if (ok) {
+        fence_after_sync();
+        // dX[s, p] = sum_t M[t, s] gy[t, p]: both operands have the reduction index t as their row
+        const uint32_t idesc_x = make_idesc_bf16(128, 64, 1, 1);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_bf16(tmem + 384, mnmajor0 + mt16 + 128 * kk, mnmajor0 + gy16 + 128 * kk, idesc_x, kk);
+        mma_commit(&s.bar_x);
+        // dcq[t, n] = sum_s dGw[t, s] bk[s, n]
+        const uint32_t idesc_q = make_idesc_bf16(128, N, 0, 1);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          mma_bf16(tmem, kmajor0 + gt16 + (kk >> 2) * PANEL16 + (kk & 3) * 2, mnmajor0 + bt16 + 128 * kk, idesc_q, kk);
+        // dbk[s, n] = sum_t dGw[t, s] cq[t, n] + sum_p v'[s, p] D_out[p, n]
+        const uint32_t idesc_k = make_idesc_bf16(128, N, 1, 1);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_bf16(tmem + 128, mnmajor0 + gt16 + 128 * kk, mnmajor0 + ct16 + 128 * kk, idesc_k, kk);
+        const uint32_t idesc_st = make_idesc_bf16(128, N, 0, PH ? 0 : 1);   // state [n][p]: K-major B; [p][n]: rows are the reduction index
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_bf16(tmem + 128, kmajor0 + xt16 + kk * 2, PH ? kmajor0 + dho16 + kk * 2 : mnstate0 + dho16 + 128 * kk, idesc_st, 1);
+        ok = mbar_wait(&s.bar_x2, 0, abortp, p.status, 73);
+        if (ok) {
+          fence_after_sync();
+          // dcq[t, n] += sum_p gy'[t, p] S_in[p, n]
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16(tmem, kmajor0 + gy16 + kk * 2, PH ? kmajor0 + hin16 + kk * 2 : mnstate0 + hin16 + 128 * kk, idesc_st, 1);
+          mma_commit(&s.bar_y);
+        }
+      }
+    }
+  } else {
+    const int l = warp * 32 + lane;
+    const int64_t base = ((int64_t)b * p.heads + h) * p.seq_len + c * L;
+    const int64_t fbase = ((int64_t)fb * p.heads + h) * p.seq_len + c * L;
+    const float my_cum2 = p.cum[fbase + l] * LOG2E;
+    s.cum2[l] = my_cum2;
+    s.wv[l] = p.weight ? p.weight[fbase + l] : 1.f;
+    named_barrier_sync(1, 128);
+    const float cum_end2 = s.cum2[L - 1];
+    const float my_w = s.wv[l];
+    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
+    float row_sum = 0.f, diag_g2 = 0.f, r2 = 0.f;
+    bool ok = mbar_wait(&s.bar_mma, 0, abortp, p.status, 74);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      fence_after_sync();
+      const uint32_t m_base = smem_u32(s.mt[0]), g_base = smem_u32(s.gt[0]);
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t m_row = m_base + (q >> 1) * PANEL + l * 128, g_row = g_base + (q >> 1) * PANEL + l * 128;
+        if (q > warp) {   // above the diagonal for every row of this warp
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            const int chunk = (q & 1) * 4 + c8;
+            sts128(m_row + ((chunk ^ (l & 7)) << 4), make_uint4(0, 0, 0, 0));
+            sts128(g_row + ((chunk ^ (l & 7)) << 4), make_uint4(0, 0, 0, 0));
+          }
+          s.colpart[warp][q * 32 + lane] = 0.f;
+          continue;
+        }
+        uint32_t g1[32], g2[32];
+        tmem_ld_32x32(trow + q * 32, g1);
+        tmem_ld_32x32(trow + 128 + q * 32, g2);
+        tmem_ld_wait();
+        float ev[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int sidx = q * 32 + j;
+          const bool in_mask = sidx + p.strict <= l;
+          const float wdec = in_mask ? ex2(my_cum2 - s.cum2[sidx]) : 0.f;
+          const float m = __uint_as_float(g1[j]) * wdec;
+          const float dg = __uint_as_float(g2[j]) * wdec * s.wv[sidx];
+          const float e = sidx < l ? __uint_as_float(g1[j]) * dg : 0.f;
+          if (sidx == l) diag_g2 = __uint_as_float(g2[j]);
+          row_sum += e;
+          ev[j] = e;
+          g1[j] = __float_as_uint(m);
+          g2[j] = __float_as_uint(dg);
+        }
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          const int chunk = (q & 1) * 4 + c8;
+          const uint32_t* a = g1 + c8 * 8;
+          const uint32_t* d = g2 + c8 * 8;
+          sts128(m_row + ((chunk ^ (l & 7)) << 4),
+                 make_uint4(pack2(__uint_as_float(a[0]), __uint_as_float(a[1])), pack2(__uint_as_float(a[2]), __uint_as_float(a[3])),
+                            pack2(__uint_as_float(a[4]), __uint_as_float(a[5])), pack2(__uint_as_float(a[6]), __uint_as_float(a[7]))));
+          sts128(g_row + ((chunk ^ (l & 7)) << 4),
+                 make_uint4(pack2(__uint_as_float(d[0]), __uint_as_float(d[1])), pack2(__uint_as_float(d[2]), __uint_as_float(d[3])),
+                            pack2(__uint_as_float(d[4]), __uint_as_float(d[5])), pack2(__uint_as_float(d[6]), __uint_as_float(d[7]))));
+        }
+        // column sums of this 32 x 32 block of E through the warp's transpose scratch
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s.tr[warp][lane][j] = ev[j];
+        __syncwarp();
+        float cp = 0.f;
+#pragma unroll
+        for (int r = 0; r < 32; ++r) cp += s.tr[warp][r][lane];
+        s.colpart[warp][q * 32 + lane] = cp;
+        __syncwarp();
+      }
+      // state terms of the decay gradient (unscaled gy and v rows)
+      uint32_t r0[32], r1[32];
+      tmem_ld_32x32(trow + 256, r0);
+      tmem_ld_32x32(trow + 288, r1);
+      tmem_ld_wait();
+      r2 = ex2(my_cum2) * dot_row64(smem_u32(s.gyt) + l * 128, l, r0, r1);
+      tmem_ld_32x32(trow + 320, r0);
+      tmem_ld_32x32(trow + 352, r1);
+      tmem_ld_wait();
+      const float f_end = ex2(cum_end2 - my_cum2);
+      s.r3[l] = my_w * f_end * dot_row64(smem_u32(s.xt) + l * 128, l, r0, r1);
+      float hd = 0.f;
+      const uint32_t hin_a = smem_u32(s.hin[0]), dho_a = smem_u32(s.dho[0]);
+      for (int off = l * 16; off < (N / 64) * P * 128; off += 128 * 16) {
+        const uint4 a = lds128(hin_a + off), d = lds128(dho_a + off);
+        const float2 a0 = unpack2(a.x), a1 = unpack2(a.y), a2 = unpack2(a.z), a3 = unpack2(a.w);
+        const float2 d0 = unpack2(d.x), d1 = unpack2(d.y), d2 = unpack2(d.z), d3 = unpack2(d.w);
+        hd += a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y + a2.x * d2.x + a2.y * d2.y + a3.x * d3.x + a3.y * d3.y;
+      }
+      hd = warp_sum(hd);
+      if (lane == 0) s.red[warp] = hd;
+      // v row scaled for the state term of dbk
+      scale_row(smem_u32(s.xt), l, my_w * f_end);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s.bar_w);
+        mbar_arrive(&s.bar_rows);
+      }
+      ok = mbar_wait(&s.bar_rows, 0, abortp, p.status, 75);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      const float col_sum = s.colpart[0][l] + s.colpart[1][l] + s.colpart[2][l] + s.colpart[3][l];
+      s.r2[l] = r2 + row_sum - col_sum;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.bar_rows);
+      ok = mbar_wait(&s.bar_rows, 1, abortp, p.status, 76);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    uint4 gy_saved[8];
+    if (ok) {
+      float tail2 = 0.f, head3 = 0.f;
+      for (int t = l; t < L; ++t) tail2 += s.r2[t];
+      for (int t = 0; t < l; ++t) head3 += s.r3[t];
+      const float through = ex2(cum_end2) * (s.red[0] + s.red[1] + s.red[2] + s.red[3]);
+      p.da[base + l] = tail2 + head3 + through;
+      if (p.dskip) p.dskip[base + l] = diag_g2;
+      // once dX has been taken, gy rows are scaled by e^{c_t} for the state term of dcq (the unscaled row is kept)
+      ok = mbar_wait(&s.bar_x, 0, abortp, p.status, 77);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      const uint32_t gy_row = smem_u32(s.gyt) + l * 128;
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch) gy_saved[ch] = lds128(gy_row + ((ch ^ (l & 7)) << 4));
+      scale_row(smem_u32(s.gyt), l, ex2(my_cum2));
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.bar_x2);
+      ok = mbar_wait(&s.bar_y, 0, abortp, p.status, 78);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      fence_after_sync();
+      const int64_t tok = (int64_t)row0 + l;
+      // dX row (+ state term, + skip * gy)
+      {
+        uint32_t x0[32], x1[32], t0[32], t1[32];
+        tmem_ld_32x32(trow + 384, x0);
+        tmem_ld_32x32(trow + 416, x1);
+        tmem_ld_32x32(trow + 320, t0);
+        tmem_ld_32x32(trow + 352, t1);
+        tmem_ld_wait();
+        const float f_end = ex2(cum_end2 - my_cum2);
+        const float sk = (p.d_skip ? p.d_skip[h] : 0.f) + (p.skip_tok ? p.skip_tok[fbase + l] : 0.f);
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          const uint4 gv = gy_saved[ch];
+          const float2 g0 = unpack2(gv.x), g1v = unpack2(gv.y), g2v = unpack2(gv.z), g3 = unpack2(gv.w);
+          const float gyv[8] = {g0.x, g0.y, g1v.x, g1v.y, g2v.x, g2v.y, g3.x, g3.y};
+          uint32_t* xx = ch < 4 ? x0 + ch * 8 : x1 + (ch - 4) * 8;
+          const uint32_t* tt = ch < 4 ? t0 + ch * 8 : t1 + (ch - 4) * 8;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) xx[e] = __float_as_uint(__uint_as_float(xx[e]) + f_end * __uint_as_float(tt[e]) + sk * gyv[e]);
+        }
+        const int64_t off = (tok * p.heads + h) * P;
+        store_row(p.dv32 ? p.dv32 + off : nullptr, p.dv16 ? p.dv16 + off : nullptr, x0, 32);
+        store_row(p.dv32 ? p.dv32 + off + 32 : nullptr, p.dv16 ? p.dv16 + off + 32 : nullptr, x1, 32);
+      }
+      const int64_t off_n = (tok * p.heads + h) * N;
+#pragma unroll
+      for (int q = 0; q < N / 32; ++q) {
+        uint32_t r[32];
+        tmem_ld_32x32(trow + q * 32, r);
+        tmem_ld_wait();
+        store_row(p.dcq32 ? p.dcq32 + off_n + q * 32 : nullptr, p.dcq16 ? p.dcq16 + off_n + q * 32 : nullptr, r, 32);
+        tmem_ld_32x32(trow + 128 + q * 32, r);
+        tmem_ld_wait();
+        store_row(p.dbk32 ? p.dbk32 + off_n + q * 32 : nullptr, p.dbk16 ? p.dbk16 + off_n + q * 32 : nullptr, r, 32);
+      }
+    }
+  }
+  __syncwarp();
+  if (s.abort_flag) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    fence_after_sync();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// Reversed state passing: chunk_cot [B, C, H, elems] fp32 holds sum_t e^{c_t} gy_t cq_t^T per chunk; d_out[c] (bf16) is the
+// cotangent of the state leaving chunk c, d_init the cotangent of the state entering the first chunk.
+__global__ void rev_state_passing_kernel(const float* __restrict__ chunk_cot, const float* __restrict__ cum,
+                                         const float* __restrict__ d_final, __nv_bfloat16* __restrict__ d_out,
+                                         float* __restrict__ d_init, int batch, int bmod, int heads, int chunks, int seq_len,
+                                         int elems) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)batch * heads * elems) return;
+  const int e = (int)(idx % elems);
+  const int h = (int)((idx / elems) % heads);
+  const int b = (int)(idx / ((int64_t)elems * heads));
+  float st = d_final ? d_final[idx] : 0.f;
+  const float* cum_bh = cum + ((int64_t)(b % bmod) * heads + h) * seq_len;
+  for (int c = chunks - 1; c >= 0; --c) {
+    const int64_t o = (((int64_t)b * chunks + c) * heads + h) * elems + e;
+    d_out[o] = __float2bfloat16(st);
+    st = st * ex2(cum_bh[c * L + L - 1] * LOG2E) + chunk_cot[o];
+  }
+  if (d_init) d_init[idx] = st;
+}
+
 // ------------------------------------------------------------------------------------------------ 6. backward glue
 // dx = dt * dX + D * gy,  ddt = da * A + dX . x,  dD[h] += sum gy . x        with dX read in reversed time order.
 // One warp per (batch, token, head) row of 64; dD through one atomic per warp.
@@ -687,9 +1093,10 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const float* __restrict
                                                          const float* __restrict__ da, const float* __restrict__ a_param,
                                                          const float* __restrict__ d_skip, T* __restrict__ dx,
                                                          float* __restrict__ ddt, float* __restrict__ dd, int64_t tokens,
-                                                         int seq_len, int seq_pad, int heads) {
+                                                         int seq_len, int seq_pad, int heads, int reversed, int64_t ftokens) {
   // grid (ceil(tokens / 128), heads): a block owns one head and 128 tokens (16 per warp), so that the dD sum leaves as one
-  // atomic per block.  dx_rev is [batch, seq_pad, heads, 64] in reversed time; dt [b, l, h]; da [b, h, seq_pad].
+  // atomic per block.  dx_rev is [batch, seq_pad, heads, 64] (in reversed time when `reversed`); dt [b, l, h]; da [b, h, seq_pad].
+  // x and dt hold `ftokens` tokens and are shared by the tokens / ftokens stacked directions of gy.
   __shared__ float warp_dd[8];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int h = blockIdx.y;
@@ -701,11 +1108,12 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const float* __restrict
     const int l = (int)(bl % seq_len);
     const int64_t b = bl / seq_len;
     const int64_t row = bl * heads + h;
-    const int64_t rrow = (b * seq_pad + (seq_pad - 1 - l)) * heads + h;
+    const int64_t frow = (bl % ftokens) * heads + h;
+    const int64_t rrow = (b * seq_pad + (reversed ? seq_pad - 1 - l : l)) * heads + h;
     const float2 g = *reinterpret_cast<const float2*>(dx_rev + rrow * P + lane * 2);
-    const float2 xv = ld2<T>(x + row * P + lane * 2);
+    const float2 xv = ld2<T>(x + frow * P + lane * 2);
     const float2 gv = ld2<T>(gy + row * P + lane * 2);
-    const float dtv = dt[row];
+    const float dtv = dt[frow];
     st2<T>(dx + row * P + lane * 2, dtv * g.x + dsk * gv.x, dtv * g.y + dsk * gv.y);
     const float dot = warp_sum(g.x * xv.x + g.y * xv.y);
     dd_acc += gv.x * xv.x + gv.y * xv.y;
@@ -807,7 +1215,7 @@ static int run(const void* x, const void* bm, const void* cm, const float* dt, c
           : make_map(&mp, prev, (int64_t)batch * chunks * heads * P, N, P);
   if (rc) return rc;
   {
-    StateParams p{seq_len, heads, groups, chunks, v_div, v_mod, dt, cum, states, status};
+    StateParams p{seq_len, heads, groups, chunks, v_div, v_mod, dt, cum, states, status, 0, batch};
     const size_t smem = sizeof(SmemState<N>) + 1024;
     rc = set_smem(chunk_state_kernel<N, PH>, smem);
     if (rc) return rc;
@@ -861,6 +1269,84 @@ static int run_dda(const void* x, const void* gy, const void* bm, const void* cm
   return (int)cudaGetLastError();
 }
 
+
+template <int N, bool PH>
+static int run_bwd(const void* v, const void* gy, const void* bk, const void* cq, const float* weight, const float* cum,
+                   const float* skip_tok, const float* d_skip, const void* state_in, const float* d_final, float* chunk_cot,
+                   void* d_out, float* d_init, float* da, float* dskip, float* dv32, void* dv16, float* dcq32, float* dbk32,
+                   void* dcq16, void* dbk16, int batch, int bmod, int seq_len, int heads, int groups, int strict, int* status,
+                   cudaStream_t st) {
+  const int chunks = seq_len / L;
+  const int64_t rows = (int64_t)batch * seq_len, frows = (int64_t)bmod * seq_len;
+  CUtensorMap mx, mg, mb, mc, mh, md;
+  int rc = make_map(&mx, v, frows, (int64_t)heads * P, L);
+  if (rc) return rc;
+  rc = make_map(&mg, gy, rows, (int64_t)heads * P, L);
+  if (rc) return rc;
+  rc = make_map(&mb, bk, frows, (int64_t)(PH ? heads : groups) * N, L);
+  if (rc) return rc;
+  rc = make_map(&mc, cq, frows, (int64_t)(PH ? heads : groups) * N, L);
+  if (rc) return rc;
+  rc = PH ? make_map(&mh, state_in, (int64_t)bmod * chunks * heads * N, P, N)
+          : make_map(&mh, state_in, (int64_t)bmod * chunks * heads * P, N, P);
+  if (rc) return rc;
+  rc = PH ? make_map(&md, d_out, (int64_t)batch * chunks * heads * N, P, N) : make_map(&md, d_out, (int64_t)batch * chunks * heads * P, N, P);
+  if (rc) return rc;
+  {   // per-chunk state cotangents: (gy o e^{c})^T cq, the chunk-state product with gy as the v operand and cq as the B operand
+    StateParams p{seq_len, heads, groups, chunks, 1, 1, nullptr, cum, chunk_cot, status, 1, bmod};
+    const size_t smem = sizeof(SmemState<N>) + 1024;
+    rc = set_smem(chunk_state_kernel<N, PH>, smem);
+    if (rc) return rc;
+    chunk_state_kernel<N, PH><<<dim3(chunks, PH ? heads : heads / 2, batch), THREADS, smem, st>>>(mg, mc, p);
+    rc = (int)cudaGetLastError();
+    if (rc) return rc;
+  }
+  {
+    const int elems = P * N;
+    const int64_t total = (int64_t)batch * heads * elems;
+    rev_state_passing_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(chunk_cot, cum, d_final, (__nv_bfloat16*)d_out, d_init,
+                                                                             batch, bmod, heads, chunks, seq_len, elems);
+    rc = (int)cudaGetLastError();
+    if (rc) return rc;
+  }
+  BwdParams p{seq_len, heads, groups, chunks, bmod, strict, weight, cum, skip_tok, d_skip, da, dskip, dv32, (__nv_bfloat16*)dv16,
+              dcq32, dbk32, (__nv_bfloat16*)dcq16, (__nv_bfloat16*)dbk16, status};
+  const size_t smem = sizeof(SmemBwd<N>) + 1024;
+  rc = set_smem(bwd_chunk_kernel<N, PH>, smem);
+  if (rc) return rc;
+  bwd_chunk_kernel<N, PH><<<dim3(chunks, heads, batch), THREADS, smem, st>>>(mx, mg, mb, mc, mh, md, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace ssd
+}  // namespace lbi
+
+extern "C" int lbi_ssd_chunk_bwd(const void* v, const void* gy, const void* bk, const void* cq, const float* weight,
+                                 const float* cum, const float* skip_tok, const float* d_skip, const void* state_in,
+                                 const float* d_final, float* chunk_cot, void* d_out, float* d_init, float* da, float* dskip,
+                                 float* dv32, void* dv16, float* dcq32, float* dbk32, void* dcq16, void* dbk16, int batch, int bmod,
+                                 int seq_len, int heads, int groups, int d_state, int per_head, int strict, int* status,
+                                 cudaStream_t st) {
+  using namespace lbi::ssd;
+  if (seq_len % L != 0 || batch <= 0 || bmod <= 0 || batch % bmod != 0) return (int)cudaErrorInvalidValue;
+  if (!!dv32 == !!dv16 || !!dcq32 == !!dcq16 || !!dbk32 == !!dbk16) return (int)cudaErrorInvalidValue;
+  if (per_head) {
+    if (d_state != 128) return (int)cudaErrorInvalidValue;
+    return run_bwd<128, true>(v, gy, bk, cq, weight, cum, skip_tok, d_skip, state_in, d_final, chunk_cot, d_out, d_init, da, dskip,
+                              dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st);
+  }
+  if (groups <= 0 || heads % groups != 0 || (heads / groups) % 2 != 0) return (int)cudaErrorInvalidValue;
+  if (d_state == 128)
+    return run_bwd<128, false>(v, gy, bk, cq, weight, cum, skip_tok, d_skip, state_in, d_final, chunk_cot, d_out, d_init, da, dskip,
+                               dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st);
+  if (d_state == 64)
+    return run_bwd<64, false>(v, gy, bk, cq, weight, cum, skip_tok, d_skip, state_in, d_final, chunk_cot, d_out, d_init, da, dskip,
+                              dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st);
+  return (int)cudaErrorInvalidValue;
+}
+
+namespace lbi {
+namespace ssd {
 }  // namespace ssd
 }  // namespace lbi
 
@@ -943,17 +1429,17 @@ extern "C" int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk,
 
 extern "C" int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void* gy, const float* dt, const float* da,
                                   const float* a_param, const float* d_skip, void* dx, float* ddt, float* dd, int batch,
-                                  int seq_len, int seq_pad, int heads, int is_bf16, cudaStream_t st) {
+                                  int seq_len, int seq_pad, int heads, int is_bf16, int reversed, int fbatch, cudaStream_t st) {
   using namespace lbi::ssd;
-  if (batch <= 0 || seq_len <= 0 || seq_pad < seq_len || heads <= 0) return (int)cudaErrorInvalidValue;
-  const int64_t tokens = (int64_t)batch * seq_len;
+  if (batch <= 0 || seq_len <= 0 || seq_pad < seq_len || heads <= 0 || fbatch <= 0 || batch % fbatch != 0) return (int)cudaErrorInvalidValue;
+  const int64_t tokens = (int64_t)batch * seq_len, ftokens = (int64_t)fbatch * seq_len;
   const dim3 blocks((unsigned)((tokens + 127) / 128), (unsigned)heads);
   if (is_bf16)
     bwd_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(dx_rev, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gy, dt, da, a_param,
-                                                            d_skip, (__nv_bfloat16*)dx, ddt, dd, tokens, seq_len, seq_pad, heads);
+                                                            d_skip, (__nv_bfloat16*)dx, ddt, dd, tokens, seq_len, seq_pad, heads, reversed, ftokens);
   else
     bwd_finish_kernel<float><<<blocks, 256, 0, st>>>(dx_rev, (const float*)x, (const float*)gy, dt, da, a_param, d_skip, (float*)dx, ddt,
-                                                    dd, tokens, seq_len, seq_pad, heads);
+                                                    dd, tokens, seq_len, seq_pad, heads, reversed, ftokens);
   return (int)cudaGetLastError();
 }
 

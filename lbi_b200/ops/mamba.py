@@ -281,16 +281,23 @@ def siso_scan_fwd(v, kr, qr, adt, skip, d_skip):
     return (y + total_skip.unsqueeze(-1) * v.float()).to(v.dtype), None
 
 
-def siso_scan_bwd(qr, kr, adt, skip_total, v, gy, states, keep_dkr_reversed: bool = False):
-    """gy [P * b, l, h, p] with the forward operands shared by the P directions -> (dQr, dKr, dadt, dskip, dV)."""
+def siso_scan_bwd(qr, kr, adt, skip_total, v, gy, states):
+    """gy [P * b, l, h, p] with the forward operands shared by the P directions ->
+    (dQr, dKr, dadt, dskip, dV, dkr_is_time_reversed)."""
     from . import ssd
 
     reps = gy.shape[0] // v.shape[0]
-    if ssd.siso_cuda_supported(v, qr) and gy.dtype == torch.bfloat16 and hasattr(ext(), "ssd_decay_grad"):
-        tile = lambda t: None if t is None else _tile_rows(t, reps)  # noqa: E731
-        return ssd.siso_core_backward(tile(qr), tile(kr), tile(adt), tile(skip_total), tile(v), gy, ops=ssd.KernelScans,
-                                      fwd_states=tile(states), keep_dkr_reversed=keep_dkr_reversed)
-    return ssd.siso_core_backward_dense(qr, kr, adt, skip_total, v, gy)
+    if ssd.siso_cuda_supported(v, qr) and gy.dtype == torch.bfloat16 and states is not None:
+        if ssd.chunk_backward_supported(v):
+            dv, dqr, dkr, dadt, dskip = ssd.chunk_backward(v, gy, kr, qr, adt, None, skip_total, states, per_head=True, strict=True,
+                                                           dv_bf16=True, dn_bf16=False)
+            return dqr, dkr, dadt, dskip, dv, False
+        if hasattr(ext(), "ssd_decay_grad"):
+            tile = lambda t: None if t is None else _tile_rows(t, reps)  # noqa: E731
+            out = ssd.siso_core_backward(tile(qr), tile(kr), tile(adt), tile(skip_total), tile(v), gy, ops=ssd.KernelScans,
+                                         fwd_states=tile(states), keep_dkr_reversed=True)
+            return (*out, True)
+    return (*ssd.siso_core_backward_dense(qr, kr, adt, skip_total, v, gy), False)
 
 
 # ---------------------------------------------------------------- Mamba-2: softplus of dt, SiLU of the conv output

@@ -452,6 +452,60 @@ def mamba3_siso_cuda(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D, Z=None):
     return y
 
 
+# ------------------------------------------------------------------------------------------------ fused chunk backward
+def chunk_backward_supported(v: torch.Tensor) -> bool:
+    return bool(ENABLED and v.is_cuda and native_available() and hasattr(ext(), "ssd_chunk_bwd")
+                and os.environ.get("LBI_B200_SSD_PERMUTED_BACKWARD", "0") != "1")
+
+
+def chunk_backward(v, gy, bk, cq, a, weight, skip, states_in, *, per_head: bool, strict: bool, dv_bf16: bool, dn_bf16: bool):
+    """Every input cotangent of the scan ``y_t = sum_{s <= t} e^{c_t - c_s} (cq_t . bk_s) w_s v_s (+ skip_t v_t)`` from one fused
+    kernel per (direction, chunk, head) (csrc/ssd.cu, ``bwd_chunk_kernel``).  The forward operands v [b, l, h, 64], bk, cq
+    [b, l, g, n], a, weight, skip [b, l, h] and the forward's incoming chunk states are shared by the P = gy.shape[0] / b stacked
+    directions of gy.  Returns (d(w v) [+ skip gy], dcq, dbk per head [P b, l, h, n], da, gy . v [P b, l, h])."""
+    from .dispatch import KERNEL_LAUNCHES
+
+    bf = torch.bfloat16
+    seqlen = v.shape[1]
+    pad = (-seqlen) % CHUNK
+    vb, gyb, bkb, cqb, af = v.to(bf), gy.to(bf), bk.to(bf), cq.to(bf), a.float()
+    wf = None if weight is None else weight.float()
+    sf = None if skip is None else skip.float()
+    if pad:   # a = 0, operands 0 on the padding: the state is carried unchanged and nothing is added
+        vb, gyb, bkb, cqb = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (vb, gyb, bkb, cqb))
+        af = F.pad(af, (0, 0, 0, pad))
+        wf = None if wf is None else F.pad(wf, (0, 0, 0, pad))
+        sf = None if sf is None else F.pad(sf, (0, 0, 0, pad))
+    KERNEL_LAUNCHES["count"] += 4
+    dv, dcq, dbk, da, dskip = ext().ssd_chunk_bwd(vb.contiguous(), gyb.contiguous(), bkb.contiguous(), cqb.contiguous(), af.contiguous(),
+                                                  None if wf is None else wf.contiguous(), None if sf is None else sf.contiguous(),
+                                                  None, states_in, bool(per_head), bool(strict), bool(dv_bf16), bool(dn_bf16))
+    if pad:
+        dv, dcq, dbk, da, dskip = (t[:, :seqlen] for t in (dv, dcq, dbk, da, dskip))
+    return dv, dcq, dbk, da, dskip
+
+
+def ssd_backward_fused(x, dt, A, B, C, D, gy, fwd_states):
+    """SSD input cotangents through the fused chunk backward; x, dt, B, C and the forward's chunk states [b, ...] are shared by
+    the P stacked directions of gy [P b, l, h, 64].  Returns (dx, ddt, dA, dB, dC, dD)."""
+    bsz, seqlen, h, p = x.shape
+    g, n = B.shape[2], B.shape[3]
+    reps = gy.shape[0] // bsz
+    dtf, Af = dt.float(), A.float()
+    dX, dC_h, dB_h, da, _ = chunk_backward(x, gy, B, C, dtf * Af, dtf, None, fwd_states, per_head=False, strict=False,
+                                           dv_bf16=False, dn_bf16=True)
+    xk = x if x.dtype in (torch.bfloat16, torch.float32) else x.float()
+    dx, ddt, dD = ext().ssd_bwd_finish(dX.contiguous(), xk.contiguous(), gy.to(xk.dtype).contiguous(), dtf.contiguous(), da,
+                                       Af.contiguous(), None if D is None else D.float().contiguous(), False)
+    dC = KernelScans.group_sum(dC_h.contiguous(), None, seqlen, g, n, False)
+    dB = KernelScans.group_sum(dB_h.contiguous(), None, seqlen, g, n, False)
+    dA = (da.reshape(reps, bsz, seqlen, h) * dtf).sum((0, 1, 2))
+    from .dispatch import KERNEL_LAUNCHES
+
+    KERNEL_LAUNCHES["count"] += 1
+    return dx, ddt, dA, dB, dC, (dD if D is not None else None)
+
+
 # ------------------------------------------------------------------------------------------------ dense statements
 def _pair_weights(a):
     """a [b, l, h] log-decays -> (c [b, h, l] cumulative, diff [b, h, t, s] = c_t - c_s)."""

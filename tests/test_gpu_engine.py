@@ -54,10 +54,51 @@ def test_engine_grad_parity_bf16(axis, tie):
     assert any(not torch.equal(a, b) for a, b in zip(before, gpu_model.parameters()))
 
 
+def _mamba_model(kind, k=2):
+    torch.manual_seed(0)
+    kw = dict(dim=256, layers=2, d_state=128, headdim=64, expand=2, d_conv=4, chunk_size=128)
+    if kind == "hybrid":
+        spec = BackboneSpec(name="hybrid", layer_types=("mamba3", "transformer"), n_heads=4, d_intermediate=512, **{**kw, "d_conv": 0})
+    else:
+        spec = BackboneSpec(name=kind, **kw)
+    iface = VectorMLPInterface(feature_dim=256, num_regions=k, interface_width=16, interface_map_hidden_dim=64)
+    return LBILanguageModel(vocab_size=1024, layers_per_region=1, backbone_spec=spec, interface=iface, region_axis="sequence",
+                            num_sequence_regions=k, tie_embeddings=True)
+
+
+@pytest.mark.parametrize("kind", ["mamba3", "mamba2", "hybrid"])
+def test_mamba_engine_grad_parity_bf16(kind):
+    """The closed-form Mamba lowering on the sm_100a kernels (bf16) against dense autograd in fp32 on the CPU, at the
+    reference's bf16 parity bar for Mamba-3 / hybrid models (atol = rtol = 5e-2, loss 5e-3)."""
+    cpu_model = _mamba_model(kind)
+    gpu_model = copy.deepcopy(cpu_model).cuda()
+    torch.manual_seed(1)
+    ids, tgt = torch.randint(0, 1024, (2, 512)), torch.randint(0, 1024, (2, 512))
+    logits = cpu_model(ids)
+    loss = F.cross_entropy(logits.float().reshape(-1, 1024), tgt.reshape(-1))
+    want = AutogradEngine().backward(model=cpu_model, loss=loss).grad_map
+    engine = FastLBIEngine(gpu_model, lr=1e-3, basis_chunk=8)
+    res = engine.backward(ids.cuda(), tgt.cuda())
+    from lbi_b200 import ops
+
+    assert ops.ext().kernel_status(res.loss) == 0
+    assert abs(float(res.loss) - float(loss.detach())) < 5e-3 * max(1.0, abs(float(loss.detach())))
+    got = engine.named_grads()
+    for name, ref in want.items():
+        if ref is None:
+            continue
+        g = got[name].float().cpu()
+        rel = float((g - ref).norm() / (ref.norm() + 1e-12))
+        assert torch.allclose(g, ref, atol=5e-2, rtol=5e-2), f"{name}: max abs err {float((g - ref).abs().max()):.3e}"
+        assert rel < 1.5e-1, f"{name}: rel-L2 {rel:.3e}"
+    out = engine.step(ids.cuda(), tgt.cuda())
+    assert torch.isfinite(out)
+
+
 @pytest.mark.parametrize("config", ["tiny", "mamba-tiny"])
 def test_bench_paths_run_on_tiny_configs(config):
-    """The two training paths of bench.py (region-parallel engine; scan engine for the Mamba backbones) on tiny shapes:
-    finite loss, kernels launched, no bounded wait ran out, end-to-end figure present."""
+    """bench.py's training path (the region-parallel engine, every backbone) on tiny shapes: finite loss, kernels
+    launched, no bounded wait ran out, end-to-end figure present."""
     import argparse
     import math
     import os
@@ -67,8 +108,8 @@ def test_bench_paths_run_on_tiny_configs(config):
     import bench
 
     args = argparse.Namespace(config=config, gpus=1, steps=1, warmup=1, basis_chunk=8, no_e2e=False, profile_ops=False, comm="auto",
-                              impl="ours", jacobian_mode="recompute")
-    out = bench.run_ours_scan_engine(args) if "backbone" in bench.CONFIGS[config] else bench.run_ours(args)
+                              impl="ours", jacobian_mode="recompute", engine="fast")
+    out = bench.run_ours(args)
     assert math.isfinite(out["final_loss"]) and out["value"] > 0
     assert out["gpu_launches"] > 0 and out["kernel_status"] == 0
     assert out["e2e"]["value"] > 0 and out["e2e"]["h2d_bytes_per_step"] > 0

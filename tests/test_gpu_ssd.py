@@ -264,3 +264,89 @@ def test_mamba_lbi_model_trains_through_the_kernels(backbone, d_state, monkeypat
         gk = grads_k[name]
         denom = gt.float().norm().item() + 1e-6
         assert (gk.float() - gt.float()).norm().item() / denom < 0.15, name
+
+
+def _rel(a, b):
+    return float((a.double() - b.double()).abs().max() / (b.double().abs().max() + 1e-9))
+
+
+@pytest.mark.parametrize("per_head,n,g,l", [(True, 128, 4, 384), (False, 128, 2, 256), (False, 64, 1, 384), (True, 128, 4, 200)])
+def test_fused_chunk_backward_matches_the_dense_definition(per_head, n, g, l):
+    """One fused kernel per (direction, chunk, head) against the O(l^2) fp32 definition, with the forward operands shared by
+    two stacked cotangent directions (the forward tensors are read with batch index b % 2)."""
+    from lbi_b200.ops import ssd
+
+    b, h, reps = 2, 4, 2
+    gen = torch.Generator(device=DEV).manual_seed(11 + l)
+    v = torch.randn(b, l, h, 64, device=DEV, generator=gen).bfloat16()
+    bk = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.4).bfloat16()
+    cq = (torch.randn(b, l, g, n, device=DEV, generator=gen) * 0.4).bfloat16()
+    a = -(torch.rand(b, l, h, device=DEV, generator=gen) * 0.08 + 0.002)
+    gy = torch.randn(reps * b, l, h, 64, device=DEV, generator=gen).bfloat16()
+    if per_head:   # the Mamba-3 form: strict mask, per-head operands, per-token skip, no weight
+        skip = torch.randn(b, l, h, device=DEV, generator=gen)
+        _, _, states = ssd.scan_generic(torch.nn.functional.pad(v, (0, 0, 0, 0, 0, (-l) % 128)),
+                                        torch.nn.functional.pad(bk, (0, 0, 0, 0, 0, (-l) % 128)),
+                                        torch.nn.functional.pad(cq, (0, 0, 0, 0, 0, (-l) % 128)),
+                                        torch.nn.functional.pad(a, (0, 0, 0, (-l) % 128)), None, None, strict=True, per_head=True)
+        dv, dcq, dbk, da, dskip = ssd.chunk_backward(v, gy, bk, cq, a, None, skip, states, per_head=True, strict=True, dv_bf16=True,
+                                                     dn_bf16=False)
+        want = ssd.siso_core_backward_dense(cq, bk, a, skip, v, gy)   # (dQr, dKr, dadt, dskip, dV)
+        got = (dcq, dbk, da, dskip, dv)
+        names = ("dcq", "dbk", "da", "dskip", "dv")
+    else:          # the Mamba-2 form: inclusive mask, grouped operands, weight dt
+        dt = torch.rand(b, l, h, device=DEV, generator=gen) * 0.1 + 0.01
+        A = -(torch.rand(h, device=DEV, generator=gen) * 2 + 0.3)
+        a = dt * A
+        pad = (-l) % 128
+        P = torch.nn.functional.pad
+        _, _, states = ssd.scan_generic(P(v, (0, 0, 0, 0, 0, pad)), P(bk, (0, 0, 0, 0, 0, pad)), P(cq, (0, 0, 0, 0, 0, pad)),
+                                        P(a, (0, 0, 0, pad)), P(dt, (0, 0, 0, pad)), None)
+        dx, ddt, dA, dB, dC, dD = ssd.ssd_backward_fused(v, dt, A, bk, cq, None, gy, states)
+        want = ssd.ssd_backward_dense(v, dt, A, bk, cq, None, gy)[:5]
+        got = (dx, ddt, dA, dB, dC)
+        names = ("dx", "ddt", "dA", "dB", "dC")
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(v) == 0, "a bounded wait inside the fused backward ran out"
+    for name, x, y in zip(names, got, want):
+        assert x.shape == y.shape, (name, x.shape, y.shape)
+        assert _rel(x.float(), y) < 3e-2, f"{name}: relative error {_rel(x.float(), y):.3e}"
+
+
+def test_mamba3_small_tensor_kernels_match_pytorch():
+    """Softplus / trapezoid weights / rotary phase (forward) and their pullback for stacked directions, kernel vs the
+    PyTorch statement evaluated on the CPU."""
+    from lbi_b200.ops import mamba as mops
+
+    b, l, h, s, reps = 2, 300, 6, 32, 3
+    gen = torch.Generator().manual_seed(5)
+    dd_dt, dd_a, trap = (torch.randn(b * l, h, generator=gen) for _ in range(3))
+    angles = torch.randn(b * l, s, generator=gen)
+    bias = torch.randn(h, generator=gen) * 0.5 - 2.0
+    want = mops.siso_small_fwd(dd_dt, dd_a, trap, angles, bias, 1e-4, b, l)
+    got = mops.siso_small_fwd(dd_dt.cuda(), dd_a.cuda(), trap.cuda(), angles.cuda(), bias.cuda(), 1e-4, b, l)
+    for name in ("dt", "a", "sig", "adt", "gamma", "scale", "tanh_angle", "sp_dt", "sp_a", "a_live"):
+        assert torch.allclose(getattr(got, name).cpu(), getattr(want, name), atol=1e-5, rtol=1e-4), name
+    # the phase is compared on the circle (a value just below 2 pi and one just above 0 are the same angle)
+    diff = (got.theta.cpu() - want.theta + torch.pi) % (2 * torch.pi) - torch.pi
+    assert diff.abs().max() < 2e-3
+    cots = [torch.randn(reps * b, l, h, generator=gen) for _ in range(3)]
+    dtheta = torch.randn(reps * b, l, h, s, generator=gen)
+    want_b = mops.siso_small_bwd(want, cots[0], dtheta, cots[1], cots[2])
+    got_b = mops.siso_small_bwd(got, cots[0].cuda(), dtheta.cuda(), cots[1].cuda(), cots[2].cuda())
+    for name, x, y in zip(("d_dd_dt", "d_dd_a", "d_trap", "d_angles"), got_b, want_b):
+        assert _rel(x.float().cpu(), y) < 1e-3, f"{name}: {_rel(x.float().cpu(), y):.3e}"
+    got_bf = mops.siso_small_bwd(got, cots[0].cuda(), dtheta.cuda(), cots[1].cuda(), cots[2].cuda(), out_dtype=torch.bfloat16)
+    assert got_bf[0].dtype == torch.bfloat16 and _rel(got_bf[3].float().cpu(), want_b[3]) < 2e-2
+
+
+def test_gate_kernels_match_pytorch():
+    from lbi_b200.ops import mamba as mops
+
+    gen = torch.Generator().manual_seed(9)
+    y, z = torch.randn(70, 192, generator=gen).bfloat16(), torch.randn(70, 192, generator=gen).bfloat16()
+    dyg = torch.randn(3 * 70, 192, generator=gen).bfloat16()
+    assert _rel(mops.gate_silu_fwd(y.cuda(), z.cuda()).float().cpu(), mops.gate_silu_fwd(y, z).float()) < 1e-2
+    dy, dz = mops.gate_silu_bwd(dyg.cuda(), y.cuda(), z.cuda())
+    wy, wz = mops.gate_silu_bwd(dyg, y, z)
+    assert _rel(dy.float().cpu(), wy.float()) < 1e-2 and _rel(dz.float().cpu(), wz.float()) < 1e-2
