@@ -37,7 +37,7 @@ CONFIGS = {
     "cfg3": dict(model="lbi-mamba3-130m", backbone="mamba3", layers=24, dim=768, d_state=128, headdim=64, expand=2, chunk=128,
                  vocab=32768, seq_len=8192, regions=8, batch=8, message_dim=64, message_hidden=768),
     "cfg5": dict(model="lbi-mamba2-780m", backbone="mamba2", layers=48, dim=1536, d_state=128, headdim=64, expand=2, chunk=256,
-                 vocab=32768, seq_len=32768, regions=32, batch=2, message_dim=256, message_hidden=1536),
+                 vocab=32768, seq_len=32768, regions=32, batch=2, message_dim=256, message_hidden=1536, basis_chunk=64, recompute=True),
     "mamba-tiny": dict(model="lbi-mamba3-tiny", backbone="mamba3", layers=2, dim=256, d_state=128, headdim=64, expand=2, chunk=128,
                        vocab=1024, seq_len=1024, regions=4, batch=2, message_dim=16, message_hidden=64),
     "tiny": dict(model="lbi-transformer-tiny", layers=2, dim=256, n_heads=4, d_intermediate=512, vocab=1024,
@@ -52,13 +52,17 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
     p.add_argument("--config", type=str, default="cfg4", choices=sorted(CONFIGS))
-    p.add_argument("--basis-chunk", type=int, default=16)
+    p.add_argument("--basis-chunk", type=int, default=0, help="basis directions per pullback pass (0: the config's default, 16 if none)")
+    p.add_argument("--recompute-forward", type=str, default="auto", choices=["auto", "on", "off"],
+                   help="drop each region's cached activations after its forward and rebuild them before its pullback / local VJP")
     p.add_argument("--comm", type=str, default="auto", choices=["auto", "collective", "symm"])
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--jacobian-mode", type=str, default="recompute", choices=["recompute", "graph", "structured"],
                    help="scan-engine configs: how the interface Jacobians are materialised")
     p.add_argument("--engine", type=str, default="fast", choices=["fast", "scan"],
                    help="fast: the autograd-free region-parallel engine (every backbone); scan: ScanADEngine over autograd (Mamba configs)")
+    p.add_argument("--variant", type=str, default="lbi", choices=["lbi", "dense"],
+                   help="dense: the dense model of the same size (no regions, plain autograd + AdamW), for either --impl")
     p.add_argument("--profile-ops", action="store_true", help="after the timed run, time one more step op by op (stderr)")
     return p.parse_args()
 
@@ -196,7 +200,10 @@ def run_ours(args) -> dict:
                              backbone_spec=spec, interface=iface, tie_embeddings=True, region_axis=axis,
                              num_sequence_regions=cfg["regions"]).to(device)
     n_params = sum(p.numel() for p in model.parameters())
-    engine = FastLBIEngine(model, lr=3e-4, weight_decay=0.01, grad_clip=1.0, basis_chunk=args.basis_chunk, comm=comm)
+    basis_chunk = args.basis_chunk or cfg.get("basis_chunk", 16)
+    recompute = {"on": True, "off": False, "auto": bool(cfg.get("recompute", False)) and axis == "sequence"}[args.recompute_forward]
+    engine = FastLBIEngine(model, lr=3e-4, weight_decay=0.01, grad_clip=1.0, basis_chunk=basis_chunk, comm=comm,
+                           recompute_forward=recompute)
 
     total = args.warmup + args.steps
     host = make_batches(cfg, total, seed=1234)
@@ -254,9 +261,11 @@ def run_ours(args) -> dict:
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random tokens, random-init weights",
         "impl": "ours",
         "config": {"model": cfg["model"], "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": cfg["regions"],
-                   "region_axis": axis, "interface_width": cfg["message_dim"], "params": n_params,
+                   "region_axis": axis, "same_decomposition": axis == "depth",
+                   "interface_width": cfg["message_dim"], "params": n_params,
                    "parallelism": f"rp{world}" if world > 1 else "single", "comm": comm_name,
-                   "backward": "suffix-scan exact (structured pullback over basis)", "basis_chunk": args.basis_chunk,
+                   "backward": "suffix-scan exact (structured pullback over basis)", "basis_chunk": basis_chunk,
+                   "recompute_forward": recompute,
                    **({"kernel_chunk": 128, "chunk_note": f"the scan kernels block time in chunks of 128 tokens whatever the model's "
                        f"chunk_size ({cfg['chunk']}); the result does not depend on the blocking"} if "backbone" in cfg else {}),
                    "optimizer": "AdamW + global-norm clip in the timed region",
@@ -291,7 +300,7 @@ def run_ours_scan_engine(args) -> dict:
                              interface=iface, tie_embeddings=True, region_axis="sequence",
                              num_sequence_regions=cfg["regions"]).to(device)
     n_params = sum(p.numel() for p in model.parameters())
-    engine = ScanADEngine(state_jacobian_mode=args.jacobian_mode, state_jacobian_basis_chunk=args.basis_chunk)
+    engine = ScanADEngine(state_jacobian_mode=args.jacobian_mode, state_jacobian_basis_chunk=args.basis_chunk or 16)
     optimizer = torch.optim.AdamW(model.parameters(), lr=3e-4, weight_decay=0.01)
 
     def step(x, y):
@@ -343,7 +352,7 @@ def run_ours_scan_engine(args) -> dict:
         "config": {"model": cfg["model"], "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": cfg["regions"],
                    "region_axis": "sequence", "interface_width": cfg["message_dim"], "params": n_params, "parallelism": "single",
                    "backward": f"suffix-scan exact (scan engine, {args.jacobian_mode} Jacobian provider, kernel scans forward and backward)",
-                   "basis_chunk": args.basis_chunk, "optimizer": "AdamW + global-norm clip in the timed region",
+                   "basis_chunk": args.basis_chunk or 16, "optimizer": "AdamW + global-norm clip in the timed region",
                    "cache": "L2 flushed (256 MB write) before every timed step; per-step working set is GBs"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": float(loss) if loss is not None else None,
         "kernel_status": int(status),
@@ -351,21 +360,146 @@ def run_ours_scan_engine(args) -> dict:
 
 
 # --------------------------------------------------------------------------------------------------- reference arm
-def run_reference(args) -> dict:
-    """The unmodified reference tree under baseline/_ref, driven through its own classes on one GPU."""
+def reference_backbone_fields(cfg: dict) -> dict:
+    """Backbone fields of the reference's LBITrainingConfig for one of CONFIGS.  Its Transformer requires d_conv >= 1; its
+    Mamba-2 runs the unfused path (use_mem_eff_path=False: the fused one needs the causal_conv1d package, which this image
+    does not have); Mamba-3 is its Triton SISO path."""
+    if "backbone" not in cfg:
+        return dict(backbone="transformer", n_heads=cfg["n_heads"], d_intermediate=cfg["d_intermediate"], d_conv=1)
+    return dict(backbone=cfg["backbone"], d_state=cfg["d_state"], headdim=cfg["headdim"], expand=cfg["expand"], d_conv=4,
+                chunk_size=cfg["chunk"], use_mem_eff_path=False)
+
+
+def import_reference():
+    """Put the unmodified reference tree (baseline/_ref) first on sys.path.  Returns an error string or None."""
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "train")):
-        return {"impl": "reference", "unavailable": "baseline/_ref does not hold the reference tree (it has no setup.py/pyproject, pip cannot install it; copy it with baseline/install_reference.sh)"}
-    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
-        if int(os.environ.get("RANK", "0")) == 0:
-            return {"impl": "reference", "unavailable": "reference is single-device: it has no torch.distributed code path, so there is no N>1 run"}
-        return {}
-    cfg = CONFIGS[args.config]
+        return ("baseline/_ref does not hold the reference tree (it has no setup.py/pyproject, pip cannot install it; copy it with "
+                "baseline/install_reference.sh)")
     # The image pre-registers an unrelated namespace package called `cuda` (cuda-python); the reference's own
     # top-level `cuda` package must win, so drop the cached entry before putting the reference first on sys.path.
     for name in [m for m in sys.modules if m == "cuda" or m.startswith("cuda.")]:
         del sys.modules[name]
-    sys.path.insert(0, ref_root)
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    return None
+
+
+def run_dense(args) -> dict:
+    """The dense model of the same size (no regions): forward under bf16 autocast, next-token loss, autograd backward, global-norm
+    clip and torch AdamW, for this framework (its modules run the sm_100a kernels through autograd Functions) or for the
+    reference (models/dense_language_model.py:11-47 with backward/autograd.py:11-28 there).  One GPU."""
+    cfg = CONFIGS[args.config]
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            return {"impl": args.impl, "variant": "dense", "unavailable": "the dense arms are single-device (no region decomposition to spread)"}
+        return {}
+    if args.impl == "reference":
+        err = import_reference()
+        if err:
+            return {"impl": "reference", "unavailable": err}
+        try:
+            from train.config import LBITrainingConfig
+            from train.eval import next_token_loss
+            from train.model_builders import build_dense_model
+        except Exception as exc:  # noqa: BLE001
+            return {"impl": "reference", "unavailable": f"reference import failed: {exc!r}"[:300]}
+        fields = reference_backbone_fields(cfg)
+    else:
+        from lbi_b200.train.config import LBITrainingConfig
+        from lbi_b200.train.eval import next_token_loss
+        from lbi_b200.train.model_builders import build_dense_model
+
+        fields = reference_backbone_fields(cfg)
+        if "backbone" not in cfg:
+            fields["d_conv"] = 0
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.manual_seed(0)
+    rcfg = LBITrainingConfig(variants="dense", regime="dense", device="cuda", dtype="bfloat16", vocab_size=cfg["vocab"], tie_embeddings=True,
+                             seq_len=cfg["seq_len"], batch_size=cfg["batch"], layers=cfg["layers"], dim=cfg["dim"], lr_model=3e-4,
+                             weight_decay=0.01, grad_clip=1.0, steps=max(1, args.steps + args.warmup), **fields)
+    try:
+        model = build_dense_model(rcfg).to(device=device, dtype=torch.float32)
+    except Exception as exc:  # noqa: BLE001
+        return {"impl": args.impl, "variant": "dense", "unavailable": f"dense model build failed: {exc!r}"[:300]}
+    optimizer = torch.optim.AdamW(model.parameters(), lr=rcfg.lr_model, weight_decay=rcfg.weight_decay)
+    n_params = sum(p.numel() for p in model.parameters())
+
+    def step(xb, yb):
+        model.train()
+        optimizer.zero_grad(set_to_none=True)
+        with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
+            logits = model(xb)
+        loss = next_token_loss(logits, yb)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), rcfg.grad_clip)
+        optimizer.step()
+        return loss.detach()
+
+    total = args.warmup + args.steps
+    host = make_batches(cfg, total, seed=1234)
+    dev_batches = [(x.to(device, non_blocking=True), y.to(device, non_blocking=True)) for x, y in host]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=device)
+    launches0 = 0
+    if args.impl == "ours":
+        from lbi_b200 import ops
+
+        launches0 = ops.dispatch.KERNEL_LAUNCHES["count"]
+    try:
+        for i in range(args.warmup):
+            step(*dev_batches[i])
+        torch.cuda.synchronize()
+        sampler = ClockSampler(physical_gpu_index(0))
+        sampler.start()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        loss = None
+        for i in range(args.warmup, total):
+            flush.zero_()
+            loss = step(*dev_batches[i])
+        stop.record()
+        torch.cuda.synchronize()
+        clocks = sampler.stop()
+        ms = start.elapsed_time(stop) / max(1, args.steps)
+        tokens = cfg["batch"] * cfg["seq_len"]
+        e2e = None
+        if not args.no_e2e:
+            t0 = time.perf_counter()
+            for i in range(args.steps):
+                x, y = host[args.warmup + i]
+                loss_val = float(step(x.to(device, non_blocking=True), y.to(device, non_blocking=True)).item())
+            torch.cuda.synchronize()
+            e2e = {"value": tokens * args.steps / (time.perf_counter() - t0), "unit": "tokens/s",
+                   "h2d_bytes_per_step": int(host[0][0].numel() * 16), "d2h_bytes_per_step": 4, "last_loss": loss_val}
+    except Exception as exc:  # noqa: BLE001
+        return {"impl": args.impl, "variant": "dense", "unavailable": f"dense step failed: {exc!r}"[:300]}
+    launches = 0
+    if args.impl == "ours":
+        launches = ops.dispatch.KERNEL_LAUNCHES["count"] - launches0
+    return {
+        "metric": "train tokens/s (device-timed, max over ranks)", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16 autocast (fp32 weights)", "data": "synthetic uniform-random tokens, random-init weights",
+        "impl": args.impl, "variant": "dense",
+        "config": {"model": cfg["model"] + "-dense", "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": 1,
+                   "params": n_params, "parallelism": "single", "backward": "dense autograd (no regions)",
+                   "optimizer": "torch AdamW + global-norm clip in the timed region",
+                   "cache": "L2 flushed (256 MB write) before every timed step; per-step working set is GBs"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": float(loss) if loss is not None else None,
+    }
+
+
+def run_reference(args) -> dict:
+    """The unmodified reference tree under baseline/_ref, driven through its own classes on one GPU."""
+    if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            return {"impl": "reference", "unavailable": "reference is single-device: it has no torch.distributed code path, so there is no N>1 run"}
+        return {}
+    err = import_reference()
+    if err:
+        return {"impl": "reference", "unavailable": err}
+    cfg = CONFIGS[args.config]
     try:
         from backward import ScanADEngine, assign_grad_map, build_interface_pullback_provider, lbi_scan_backward_step
         from train.config import LBITrainingConfig
@@ -375,7 +509,9 @@ def run_reference(args) -> dict:
         return {"impl": "reference", "unavailable": f"reference import failed: {exc!r}"[:300]}
 
     device = torch.device("cuda", 0)
-    layers_per_region = max(1, cfg["layers"] // cfg["regions"])
+    # the reference's regions are layer ranges of equal size: 48 layers cannot give 32 regions, so the nearest split is reported
+    layers_per_region = max(1, -(-cfg["layers"] // cfg["regions"]))
+    ref_regions = -(-cfg["layers"] // layers_per_region)
     # The reference's recompute Jacobian mode replicates the batch `chunk` times per pass; the launcher default (32) and
     # 8 do not fit 180 GB at this configuration, so the largest chunk that fits is used and reported.
     env_chunk = os.environ.get("LBI_REF_BASIS_CHUNK")
@@ -387,11 +523,11 @@ def run_reference(args) -> dict:
     for chunk in chunks:
         torch.manual_seed(0)
         rcfg = LBITrainingConfig(
-            variants="lbi", regime="lbi", backbone="transformer", device="cuda", dtype="bfloat16", vocab_size=cfg["vocab"],
+            variants="lbi", regime="lbi", device="cuda", dtype="bfloat16", vocab_size=cfg["vocab"],
             tie_embeddings=True, seq_len=cfg["seq_len"], batch_size=cfg["batch"], layers=cfg["layers"], dim=cfg["dim"],
-            n_heads=cfg["n_heads"], d_intermediate=cfg["d_intermediate"], d_conv=1, region_size=layers_per_region,
-            message_dim=cfg["message_dim"], message_hidden_dim=cfg["message_hidden"], interface_jacobian_mode="recompute",
-            jacobian_basis_chunk=chunk, lr_model=3e-4, weight_decay=0.01, grad_clip=1.0, steps=max(1, args.steps + args.warmup),
+            region_size=layers_per_region, message_dim=cfg["message_dim"], message_hidden_dim=cfg["message_hidden"],
+            interface_jacobian_mode="recompute", jacobian_basis_chunk=chunk, lr_model=3e-4, weight_decay=0.01, grad_clip=1.0,
+            steps=max(1, args.steps + args.warmup), **reference_backbone_fields(cfg),
         )
         try:
             model = build_lbi_model(rcfg).to(device=device, dtype=torch.float32)
@@ -483,10 +619,13 @@ def run_reference(args) -> dict:
         "requested": {"steps": args.steps, "warmup": args.warmup, "time_budget_s": budget_s},
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16 autocast (fp32 weights)",
         "data": "synthetic uniform-random tokens, random-init weights", "impl": "reference",
-        "config": {"model": cfg["model"], "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": cfg["regions"],
-                   "region_axis": "depth (the reference has no sequence-axis regions)", "interface_width": cfg["message_dim"],
-                   "params": n_params, "parallelism": "single", "jacobian_mode": "recompute", "basis_chunk": chunk,
-                   "d_conv": "1 (the reference's Transformer requires d_conv >= 1)", "path": path["engine"]},
+        "config": {"model": cfg["model"], "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": ref_regions,
+                   "region_axis": "depth (the reference has no sequence-axis regions)", "same_decomposition": False,
+                   "same_decomposition_note": "the reference cuts depth (layer ranges over the full sequence); this framework's default "
+                                              "arm cuts the sequence; `--config cfg4-depth` is this framework on the reference's cut",
+                   "interface_width": cfg["message_dim"], "params": n_params, "parallelism": "single", "jacobian_mode": "recompute",
+                   "basis_chunk": chunk, "backbone_fields": {k: v for k, v in reference_backbone_fields(cfg).items()},
+                   "path": path["engine"]},
         "clocks": clocks, "e2e": e2e, "gpu_launches": 0, "final_loss": float(loss.detach()),
     }
 
@@ -497,11 +636,12 @@ def main() -> None:
         print(json.dumps({"impl": args.impl, "unavailable": "no CUDA device visible"}))
         return
     mamba = "backbone" in CONFIGS[args.config]
-    if args.impl == "reference" and mamba:
-        print(json.dumps({"impl": "reference", "unavailable": "the reference arm is wired for the Transformer configuration (cfg4) only"}))
-        return
-    result = run_reference(args) if args.impl == "reference" else (
-        run_ours_scan_engine(args) if (mamba and args.engine == "scan") else run_ours(args))
+    if args.variant == "dense":
+        result = run_dense(args)
+    elif args.impl == "reference":
+        result = run_reference(args)
+    else:
+        result = run_ours_scan_engine(args) if (mamba and args.engine == "scan") else run_ours(args)
     if int(os.environ.get("RANK", "0")) == 0 and result:
         print(json.dumps(result))
     import torch.distributed as dist

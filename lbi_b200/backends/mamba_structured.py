@@ -194,7 +194,7 @@ class StructuredMambaRegion:
                                                                           d_y.view(pb, seqlen, h, p), lc.states)
         d_c, d_b, d_cb, d_bb, d_theta, d_gamma, d_scale = mops.siso_wide_bwd(
             lc.c_normed, lc.b_normed, mx.C_bias.detach().squeeze(1), mx.B_bias.detach().squeeze(1), lc.small.theta, lc.small.gamma,
-            lc.small.scale, d_qr, d_kr, d_skip, dkr_reversed=reversed_dkr)
+            lc.small.scale, d_qr, d_kr, d_skip, dkr_reversed=reversed_dkr, want_bias=grads is not None)
         d_dd_dt, d_dd_a, d_trap, d_angles = mops.siso_small_bwd(lc.small, d_adt, d_theta, d_gamma, d_scale, out_dtype=dtype)
         want_dw = grads is not None
         d_braw, _, dw_b = mops.gated_rmsnorm_bwd(d_b.reshape(rows * g, ns), lc.b_raw, None, mx.B_norm.weight.detach(), lc.b_rstd, ns, False,

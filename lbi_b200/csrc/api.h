@@ -70,9 +70,10 @@ int lbi_gated_rmsnorm_fwd(const void* x, const void* z_or_null, const float* wei
 // dw_partials holds lbi_gated_rmsnorm_slots(rows, dim, group_size, is_bf16) rows of dim floats; the caller sums them.
 // group_size must be a multiple of 8 (bf16) or 4 (fp32): every lane moves 16 bytes per access.
 int lbi_gated_rmsnorm_slots(int64_t rows, int dim, int group_size, int is_bf16);
+// x, z, rstd hold `frows` rows shared by rows / frows stacked directions of dy, dx, dz; dw_partials may be null (not wanted).
 int lbi_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z_or_null, const float* weight, const float* rstd, void* dx,
-                          void* dz_or_null, float* dw_partials, int64_t rows, int dim, int group_size, int gate_first,
-                          int is_bf16, cudaStream_t stream);
+                          void* dz_or_null, float* dw_partials, int64_t rows, int64_t frows, int dim, int group_size,
+                          int gate_first, int is_bf16, cudaStream_t stream);
 
 // ---- Mamba-3 SISO preprocessing on the wide tensors (siso_prep.cu) ---------------------------------------
 // q, k [tokens, groups, 128] bf16 (is_bf16) or fp32; biases [heads, 128]; theta [tokens, heads, n_angles]; gamma, scale
@@ -80,14 +81,16 @@ int lbi_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z_or_null, 
 int lbi_siso_prep_fwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
                       const float* gamma, const float* scale, void* qr_bf16, void* kr_bf16, float* qk_dot, int64_t tokens,
                       int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
-// Backward from dqr, dkr [tokens, heads, 128] fp32 and dqk [tokens, heads]: dq, dk [tokens, groups, 128] fp32, dtheta, dgamma,
-// dscale, and bias_partials [lbi_siso_prep_blocks(tokens * groups)][2][heads][128] (summed by the caller: dq_bias, dk_bias).
-// tokens = batch * seq_len.  dkr_pad > 0: dkr is [batch, dkr_pad, heads, 128] in reversed time, as the reversed scan left it.
+// Backward from dqr, dkr [tokens, heads, 128] (fp32, or bf16 when cot_bf16) and dqk [tokens, heads]: dq, dk [tokens, groups, 128]
+// fp32, dtheta, dgamma, dscale, and bias_partials [lbi_siso_prep_blocks(tokens * groups)][2][heads][128] (summed by the caller:
+// dq_bias, dk_bias; null: not wanted).  tokens = batch * seq_len; the forward tensors q, k, theta, gamma, scale hold `ftokens`
+// tokens shared by tokens / ftokens stacked directions.  dkr_pad > 0: dkr is [batch, dkr_pad, heads, 128] in reversed time.
 int lbi_siso_prep_blocks(int64_t rows);
 int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
-                      const float* gamma, const float* scale, const float* dqr, const float* dkr, const float* dqk, float* dq,
-                      float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials, int64_t tokens, int seq_len,
-                      int dkr_pad, int groups, int heads, int d_state, int n_angles, int is_bf16, cudaStream_t stream);
+                      const float* gamma, const float* scale, const void* dqr, const void* dkr, const float* dqk, float* dq,
+                      float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials, int64_t tokens, int64_t ftokens,
+                      int seq_len, int dkr_pad, int groups, int heads, int d_state, int n_angles, int is_bf16, int cot_bf16,
+                      cudaStream_t stream);
 
 // ---- Mamba block glue on the small tensors (mamba_small.cu) ------------------------------------------------
 // out = y * silu(z); bf16, numel a multiple of 8.

@@ -298,25 +298,27 @@ std::tuple<Tensor, Tensor> gated_rmsnorm_fwd(const Tensor& x, const c10::optiona
 }
 
 // -> (dx, dz (empty when z is none), dw [dim] fp32)
+// dy [P * rows, dim]; x, z [rows, dim] and rstd shared by the P stacked directions -> (dx, dz [P * rows, dim], dweight [dim] or empty).
 std::tuple<Tensor, Tensor, Tensor> gated_rmsnorm_bwd(const Tensor& dy, const Tensor& x, const c10::optional<Tensor>& z, const Tensor& weight,
-                                                     const Tensor& rstd, int64_t group_size, bool gate_first) {
+                                                     const Tensor& rstd, int64_t group_size, bool gate_first, bool want_dweight) {
   CHECK_F32(weight);
   CHECK_F32(rstd);
-  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dy.is_contiguous() && dy.sizes() == x.sizes() && dy.scalar_type() == x.scalar_type(),
-              "gated_rmsnorm_bwd: dy must match x");
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dy.is_contiguous() && dy.dim() == 2 && x.dim() == 2 && dy.size(1) == x.size(1) &&
+                  x.size(0) > 0 && dy.size(0) % x.size(0) == 0 && dy.scalar_type() == x.scalar_type(),
+              "gated_rmsnorm_bwd: dy must hold a whole number of copies of x's rows");
   TORCH_CHECK(!z || (z->is_contiguous() && z->sizes() == x.sizes() && z->scalar_type() == x.scalar_type()), "gated_rmsnorm_bwd: z must match x");
   c10::cuda::CUDAGuard guard(x.device());
-  const int64_t rows = x.size(0), dim = x.size(1);
+  const int64_t rows = dy.size(0), frows = x.size(0), dim = x.size(1);
   const int slots = lbi_gated_rmsnorm_slots(rows, (int)dim, (int)group_size, x.scalar_type() == at::kBFloat16 ? 1 : 0);
   TORCH_CHECK(slots > 0, "gated_rmsnorm_bwd: bad shape");
-  Tensor dx = torch::empty_like(x);
-  Tensor dz = z ? torch::empty_like(x) : torch::empty({0}, x.options());
-  Tensor partials = torch::empty({slots, dim}, x.options().dtype(at::kFloat));
+  Tensor dx = torch::empty_like(dy);
+  Tensor dz = z ? torch::empty_like(dy) : torch::empty({0}, x.options());
+  Tensor partials = want_dweight ? torch::empty({slots, dim}, x.options().dtype(at::kFloat)) : torch::empty({0}, x.options().dtype(at::kFloat));
   check(lbi_gated_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), z ? z->data_ptr() : nullptr, weight.data_ptr<float>(), rstd.data_ptr<float>(),
-                              dx.data_ptr(), z ? dz.data_ptr() : nullptr, partials.data_ptr<float>(), rows, (int)dim, (int)group_size,
-                              gate_first ? 1 : 0, x.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+                              dx.data_ptr(), z ? dz.data_ptr() : nullptr, want_dweight ? partials.data_ptr<float>() : nullptr, rows, frows,
+                              (int)dim, (int)group_size, gate_first ? 1 : 0, x.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
         "gated_rmsnorm_bwd");
-  return {dx, dz, partials.sum(0)};
+  return {dx, dz, want_dweight ? partials.sum(0) : partials};
 }
 
 // SISO preprocessing.  q, k [B, L, G, 128] bf16 / fp32; biases [H, 128]; theta [B, L, H, S]; gamma, scale [B, L, H] (all fp32)
@@ -345,24 +347,27 @@ std::tuple<Tensor, Tensor, Tensor> siso_prep_fwd(const Tensor& q, const Tensor& 
   return {qr, kr, qk};
 }
 
-// -> (dq, dk [B, L, G, 128] fp32, dq_bias, dk_bias [H, 128], dtheta [B, L, H, S], dgamma, dscale [B, L, H])
+// q, k, theta, gamma, scale: forward tensors of Bf sequences; dqr, dkr (fp32 or bf16), dqk: cotangents of B = P * Bf sequences.
+// -> (dq, dk [B, L, G, 128] fp32, dq_bias, dk_bias [H, 128] (empty when !want_bias), dtheta [B, L, H, S], dgamma, dscale [B, L, H])
 std::vector<Tensor> siso_prep_bwd(const Tensor& q, const Tensor& k, const Tensor& q_bias, const Tensor& k_bias, const Tensor& theta,
                                   const Tensor& gamma, const Tensor& scale, const Tensor& dqr, const Tensor& dkr, const Tensor& dqk,
-                                  bool dkr_reversed) {
+                                  bool dkr_reversed, bool want_bias) {
   CHECK_F32(q_bias);
   CHECK_F32(k_bias);
   CHECK_F32(theta);
   CHECK_F32(gamma);
   CHECK_F32(scale);
-  CHECK_F32(dqr);
-  CHECK_F32(dkr);
   CHECK_F32(dqk);
   TORCH_CHECK(q.is_cuda() && q.is_contiguous() && k.is_contiguous() && k.sizes() == q.sizes() && k.scalar_type() == q.scalar_type() &&
                   (q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kFloat) && q.dim() == 4 && q.size(3) == 128,
               "siso_prep_bwd: q, k must be contiguous [B, L, G, 128] bf16 / fp32");
+  TORCH_CHECK(dqr.is_cuda() && dqr.is_contiguous() && dkr.is_contiguous() && dkr.scalar_type() == dqr.scalar_type() &&
+                  (dqr.scalar_type() == at::kBFloat16 || dqr.scalar_type() == at::kFloat) && dqr.dim() == 4,
+              "siso_prep_bwd: dqr, dkr must be contiguous [B, L, H, 128] fp32 / bf16");
   c10::cuda::CUDAGuard guard(q.device());
-  const int64_t batch = q.size(0), seq = q.size(1), groups = q.size(2), heads = q_bias.size(0), na = theta.size(3);
-  TORCH_CHECK(dqr.numel() == batch * seq * heads * 128 && dqk.numel() == batch * seq * heads && theta.numel() == batch * seq * heads * na,
+  const int64_t fbatch = q.size(0), batch = dqr.size(0), seq = q.size(1), groups = q.size(2), heads = q_bias.size(0), na = theta.size(3);
+  TORCH_CHECK(batch % fbatch == 0 && dqr.numel() == batch * seq * heads * 128 && dqk.numel() == batch * seq * heads &&
+                  theta.numel() == fbatch * seq * heads * na && gamma.numel() == fbatch * seq * heads && scale.numel() == gamma.numel(),
               "siso_prep_bwd: shape mismatch");
   int64_t dkr_pad = 0;
   if (dkr_reversed) {
@@ -377,13 +382,15 @@ std::vector<Tensor> siso_prep_bwd(const Tensor& q, const Tensor& k, const Tensor
   Tensor dtheta = torch::empty({batch, seq, heads, na}, f32);
   Tensor dgamma = torch::empty({batch, seq, heads}, f32), dscale = torch::empty_like(dgamma);
   const int blocks = lbi_siso_prep_blocks(batch * seq * groups);
-  Tensor partials = torch::empty({blocks, 2, heads, 128}, f32);
+  Tensor partials = want_bias ? torch::empty({blocks, 2, heads, 128}, f32) : torch::empty({0}, f32);
   check(lbi_siso_prep_bwd(q.data_ptr(), k.data_ptr(), q_bias.data_ptr<float>(), k_bias.data_ptr<float>(), theta.data_ptr<float>(),
-                          gamma.data_ptr<float>(), scale.data_ptr<float>(), dqr.data_ptr<float>(), dkr.data_ptr<float>(),
-                          dqk.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dtheta.data_ptr<float>(),
-                          dgamma.data_ptr<float>(), dscale.data_ptr<float>(), partials.data_ptr<float>(), batch * seq, (int)seq,
-                          (int)dkr_pad, (int)groups, (int)heads, 128, (int)na, q.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
+                          gamma.data_ptr<float>(), scale.data_ptr<float>(), dqr.data_ptr(), dkr.data_ptr(), dqk.data_ptr<float>(),
+                          dq.data_ptr<float>(), dk.data_ptr<float>(), dtheta.data_ptr<float>(), dgamma.data_ptr<float>(),
+                          dscale.data_ptr<float>(), want_bias ? partials.data_ptr<float>() : nullptr, batch * seq, fbatch * seq, (int)seq,
+                          (int)dkr_pad, (int)groups, (int)heads, 128, (int)na, q.scalar_type() == at::kBFloat16 ? 1 : 0,
+                          dqr.scalar_type() == at::kBFloat16 ? 1 : 0, cur_stream()),
         "siso_prep_bwd");
+  if (!want_bias) return {dq, dk, partials, partials, dtheta, dgamma, dscale};
   Tensor bias = partials.sum(0);
   return {dq, dk, bias.select(0, 0), bias.select(0, 1), dtheta, dgamma, dscale};
 }
@@ -1043,13 +1050,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("interface_mlp_jac", &interface_mlp_jac);
   m.def("siso_prep_fwd", &siso_prep_fwd);
   m.def("siso_prep_bwd", &siso_prep_bwd, py::arg("q"), py::arg("k"), py::arg("q_bias"), py::arg("k_bias"), py::arg("theta"),
-        py::arg("gamma"), py::arg("scale"), py::arg("dqr"), py::arg("dkr"), py::arg("dqk"), py::arg("dkr_reversed") = false);
+        py::arg("gamma"), py::arg("scale"), py::arg("dqr"), py::arg("dkr"), py::arg("dqk"), py::arg("dkr_reversed") = false,
+        py::arg("want_bias") = true);
   m.def("gate_silu_fwd", &gate_silu_fwd);
   m.def("gate_silu_bwd", &gate_silu_bwd);
   m.def("siso_small_fwd", &siso_small_fwd);
   m.def("siso_small_bwd", &siso_small_bwd);
   m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);
-  m.def("gated_rmsnorm_bwd", &gated_rmsnorm_bwd);
+  m.def("gated_rmsnorm_bwd", &gated_rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("z"), py::arg("weight"), py::arg("rstd"),
+        py::arg("group_size"), py::arg("gate_first"), py::arg("want_dweight") = true);
   m.def("layernorm_jac", &layernorm_jac);
   m.def("gemm", &gemm, "bf16 tcgen05 GEMM", py::arg("a"), py::arg("b"), py::arg("a_t") = false, py::arg("b_t") = false,
         py::arg("out_fp32") = false, py::arg("accumulate_into") = py::none(), py::arg("splits") = 1);

@@ -106,12 +106,17 @@ __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __r
                                                                     const T* __restrict__ z, const float* __restrict__ w,
                                                                     const float* __restrict__ rstd_in, T* __restrict__ dx,
                                                                     T* __restrict__ dz, float* __restrict__ dw_partials,
-                                                                    int64_t vrows, int dim, int gs, int gate_first, int lpg,
-                                                                    int iters) {
+                                                                    int64_t vrows, int64_t fvrows, int dim, int gs, int gate_first,
+                                                                    int lpg, int iters) {
+  // x, z, rstd hold fvrows (row, group) pairs shared by vrows / fvrows stacked directions of dy; dw_partials may be null
+  // (a pullback pass wants no weight gradient: nothing is accumulated for it)
   constexpr int V = Vec<T>::N;
   extern __shared__ float dw_acc[];   // [dim]
-  for (int i = threadIdx.x; i < dim; i += THREADS) dw_acc[i] = 0.f;
-  __syncthreads();
+  const bool want_dw = dw_partials != nullptr;
+  if (want_dw) {
+    for (int i = threadIdx.x; i < dim; i += THREADS) dw_acc[i] = 0.f;
+    __syncthreads();
+  }
   const int ngroups = dim / gs, gpw = 32 / lpg;
   const int lane = threadIdx.x & 31, sub = lane / lpg, li = lane % lpg;
   for (int64_t v0 = ((int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5)) * gpw; v0 < vrows; v0 += (int64_t)gridDim.x * WARPS * gpw) {
@@ -119,15 +124,17 @@ __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __r
     const bool live = vr < vrows;
     const int g = live ? (int)(vr % ngroups) : 0;
     const int64_t base = live ? (vr / ngroups) * dim + (int64_t)g * gs : 0;
-    const float rstd = live ? rstd_in[vr] : 0.f;
+    const int64_t fvr = live ? vr % fvrows : 0;
+    const int64_t fbase = (fvr / ngroups) * dim + (int64_t)g * gs;
+    const float rstd = live ? rstd_in[fvr] : 0.f;
     float dot = 0.f;
     for (int it = 0; it < iters; ++it) {
       const int c = (it * lpg + li) * V;
       if (live) {
         float xv[V], zv[V], gv[V];
-        Vec<T>::load(x + base + c, xv);
+        Vec<T>::load(x + fbase + c, xv);
         Vec<T>::load(dy + base + c, gv);
-        if (z) Vec<T>::load(z + base + c, zv);
+        if (z) Vec<T>::load(z + fbase + c, zv);
 #pragma unroll
         for (int e = 0; e < V; ++e) {
           float u = xv[e], dyn = gv[e];
@@ -144,9 +151,9 @@ __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __r
     for (int it = 0; it < iters; ++it) {
       const int c = (it * lpg + li) * V;
       float xv[V], zv[V], gv[V], ox[V], oz[V];
-      Vec<T>::load(x + base + c, xv);
+      Vec<T>::load(x + fbase + c, xv);
       Vec<T>::load(dy + base + c, gv);
-      if (z) Vec<T>::load(z + base + c, zv);
+      if (z) Vec<T>::load(z + fbase + c, zv);
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         const float wv = w[g * gs + c + e];
@@ -158,7 +165,7 @@ __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __r
           if (gate_first) u *= gate; else dyn *= gate;
         }
         const float uhat = u * rstd;
-        atomicAdd(dw_acc + g * gs + c + e, dyn * uhat);
+        if (want_dw) atomicAdd(dw_acc + g * gs + c + e, dyn * uhat);
         const float du = rstd * (dyn * wv - uhat * mean_gu);
         if (z && gate_first) {
           ox[e] = du * gate;
@@ -172,9 +179,11 @@ __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __r
       if (z) Vec<T>::store(dz + base + c, oz);
     }
   }
-  __syncthreads();
-  float* out = dw_partials + (int64_t)blockIdx.x * dim;
-  for (int i = threadIdx.x; i < dim; i += THREADS) out[i] = dw_acc[i];
+  if (want_dw) {
+    __syncthreads();
+    float* out = dw_partials + (int64_t)blockIdx.x * dim;
+    for (int i = threadIdx.x; i < dim; i += THREADS) out[i] = dw_acc[i];
+  }
 }
 
 // lanes per group: the largest power of two <= 32 that divides the number of 16-byte vectors of a group
@@ -208,15 +217,16 @@ static int fwd(const void* x, const void* z, const float* w, void* y, float* rst
 
 template <typename T>
 static int bwd(const void* dy, const void* x, const void* z, const float* w, const float* rstd, void* dx, void* dz,
-               float* dw_partials, int64_t rows, int dim, int gs, int gate_first, cudaStream_t st) {
+               float* dw_partials, int64_t rows, int64_t frows, int dim, int gs, int gate_first, cudaStream_t st) {
   int lpg, iters;
   if (!plan(gs, Vec<T>::N, &lpg, &iters)) return (int)cudaErrorInvalidValue;
-  const int64_t vrows = rows * (dim / gs);
+  if (frows <= 0 || rows % frows != 0) return (int)cudaErrorInvalidValue;
+  const int64_t vrows = rows * (dim / gs), fvrows = frows * (dim / gs);
   const size_t smem = (size_t)dim * sizeof(float);
   int rc = (int)cudaFuncSetAttribute(gated_rmsnorm_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (rc) return rc;
   gated_rmsnorm_bwd_kernel<T><<<grid_for(vrows, lpg), THREADS, smem, st>>>((const T*)dy, (const T*)x, (const T*)z, w, rstd, (T*)dx, (T*)dz,
-                                                                           dw_partials, vrows, dim, gs, gate_first, lpg, iters);
+                                                                           dw_partials, vrows, fvrows, dim, gs, gate_first, lpg, iters);
   return (int)cudaGetLastError();
 }
 
@@ -240,11 +250,11 @@ extern "C" int lbi_gated_rmsnorm_fwd(const void* x, const void* z_or_null, const
 }
 
 extern "C" int lbi_gated_rmsnorm_bwd(const void* dy, const void* x, const void* z_or_null, const float* weight, const float* rstd,
-                                     void* dx, void* dz_or_null, float* dw_partials, int64_t rows, int dim, int group_size,
-                                     int gate_first, int is_bf16, cudaStream_t st) {
+                                     void* dx, void* dz_or_null, float* dw_partials, int64_t rows, int64_t frows, int dim,
+                                     int group_size, int gate_first, int is_bf16, cudaStream_t st) {
   if (rows <= 0 || dim <= 0 || group_size <= 0 || dim % group_size != 0 || dim > 12288) return (int)cudaErrorInvalidValue;
-  return is_bf16 ? lbi::gnorm::bwd<__nv_bfloat16>(dy, x, z_or_null, weight, rstd, dx, dz_or_null, dw_partials, rows, dim, group_size,
-                                                  gate_first, st)
-                 : lbi::gnorm::bwd<float>(dy, x, z_or_null, weight, rstd, dx, dz_or_null, dw_partials, rows, dim, group_size,
+  return is_bf16 ? lbi::gnorm::bwd<__nv_bfloat16>(dy, x, z_or_null, weight, rstd, dx, dz_or_null, dw_partials, rows, frows, dim,
+                                                  group_size, gate_first, st)
+                 : lbi::gnorm::bwd<float>(dy, x, z_or_null, weight, rstd, dx, dz_or_null, dw_partials, rows, frows, dim, group_size,
                                           gate_first, st);
 }

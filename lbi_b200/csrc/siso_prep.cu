@@ -98,37 +98,44 @@ __global__ void __launch_bounds__(THREADS) fwd_kernel(const T* __restrict__ q, c
 }
 
 // bias_partials [gridDim.x][2][heads][N]
-template <typename T>
+// T: dtype of q, k; C: dtype of the cotangents dqr, dkr.  The forward tensors (q, k, theta, gamma, scale) hold `frows` rows
+// (tokens x groups) and are shared by rows / frows stacked directions of the cotangents.
+template <typename T, typename C>
 __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, const T* __restrict__ k,
                                                       const float* __restrict__ q_bias, const float* __restrict__ k_bias,
                                                       const float* __restrict__ theta, const float* __restrict__ gamma,
-                                                      const float* __restrict__ scale, const float* __restrict__ dqr,
-                                                      const float* __restrict__ dkr, const float* __restrict__ dqk,
+                                                      const float* __restrict__ scale, const C* __restrict__ dqr,
+                                                      const C* __restrict__ dkr, const float* __restrict__ dqk,
                                                       float* __restrict__ dq, float* __restrict__ dk, float* __restrict__ dtheta,
                                                       float* __restrict__ dgamma, float* __restrict__ dscale,
-                                                      float* __restrict__ bias_partials, int64_t rows, int groups, int heads,
-                                                      int n_angles, int seq_len, int dkr_pad) {
+                                                      float* __restrict__ bias_partials, int64_t rows, int64_t frows, int groups,
+                                                      int heads, int n_angles, int seq_len, int dkr_pad) {
   // dkr_pad > 0: dkr is [batch, dkr_pad, heads, N] in reversed time (token l of a sequence sits in row dkr_pad - 1 - l)
+  // bias_partials == nullptr: the bias gradients are not wanted (a pullback pass) and nothing is accumulated for them
   extern __shared__ float bias_acc[];   // [2][heads][N]
   const int lane = threadIdx.x & 31;
   const int rep = heads / groups;
-  for (int i = threadIdx.x; i < 2 * heads * N; i += THREADS) bias_acc[i] = 0.f;
-  __syncthreads();
+  const bool want_bias = bias_partials != nullptr;
+  if (want_bias) {
+    for (int i = threadIdx.x; i < 2 * heads * N; i += THREADS) bias_acc[i] = 0.f;
+    __syncthreads();
+  }
   for (int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * WARPS) {
     const int g = (int)(row % groups);
     const int64_t tok = row / groups;
-    const float4 qg = ld4<T>(q + row * N + lane * 4), kg = ld4<T>(k + row * N + lane * 4);
+    const int64_t frow = row % frows, ftok = frow / groups;
+    const float4 qg = ld4<T>(q + frow * N + lane * 4), kg = ld4<T>(k + frow * N + lane * 4);
     float4 dq_sum = make_float4(0.f, 0.f, 0.f, 0.f), dk_sum = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int r = 0; r < rep; ++r) {
       const int h = g * rep + r;
-      const int64_t hrow = tok * heads + h;
+      const int64_t hrow = tok * heads + h, fhrow = ftok * heads + h;
       const float4 qb = ld4<float>(q_bias + h * N + lane * 4), kb = ld4<float>(k_bias + h * N + lane * 4);
       const float4 qh = make_float4(qg.x + qb.x, qg.y + qb.y, qg.z + qb.z, qg.w + qb.w);
       const float4 kh = make_float4(kg.x + kb.x, kg.y + kb.y, kg.z + kb.z, kg.w + kb.w);
-      const Rot rot = load_rot(theta + hrow * n_angles, lane, n_angles);
-      const float sc = scale[hrow], gm = gamma[hrow], dd = dqk[hrow];
+      const Rot rot = load_rot(theta + fhrow * n_angles, lane, n_angles);
+      const float sc = scale[fhrow], gm = gamma[fhrow], dd = dqk[hrow];
       const int64_t krow = dkr_pad > 0 ? ((tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len)) * heads + h : hrow;
-      const float4 gq = ld4<float>(dqr + hrow * N + lane * 4), gk = ld4<float>(dkr + krow * N + lane * 4);
+      const float4 gq = ld4<C>(dqr + hrow * N + lane * 4), gk = ld4<C>(dkr + krow * N + lane * 4);
       const float4 qo = rotate(qh, rot), ko = rotate(kh, rot);   // ko without the scale
       // angle gradients: J (a, b) = (-b, a) applied to the rotated pair
       const float dth0 = (-gq.x * qo.y + gq.y * qo.x) + sc * (-gk.x * ko.y + gk.y * ko.x);
@@ -148,17 +155,21 @@ __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, c
       dkh = make_float4(dkh.x + w * qh.x, dkh.y + w * qh.y, dkh.z + w * qh.z, dkh.w + w * qh.w);
       dq_sum = make_float4(dq_sum.x + dqh.x, dq_sum.y + dqh.y, dq_sum.z + dqh.z, dq_sum.w + dqh.w);
       dk_sum = make_float4(dk_sum.x + dkh.x, dk_sum.y + dkh.y, dk_sum.z + dkh.z, dk_sum.w + dkh.w);
-      float* bq = bias_acc + (int64_t)h * N + lane * 4;
-      float* bk = bias_acc + (int64_t)(heads + h) * N + lane * 4;
-      atomicAdd(bq, dqh.x); atomicAdd(bq + 1, dqh.y); atomicAdd(bq + 2, dqh.z); atomicAdd(bq + 3, dqh.w);
-      atomicAdd(bk, dkh.x); atomicAdd(bk + 1, dkh.y); atomicAdd(bk + 2, dkh.z); atomicAdd(bk + 3, dkh.w);
+      if (want_bias) {
+        float* bq = bias_acc + (int64_t)h * N + lane * 4;
+        float* bk = bias_acc + (int64_t)(heads + h) * N + lane * 4;
+        atomicAdd(bq, dqh.x); atomicAdd(bq + 1, dqh.y); atomicAdd(bq + 2, dqh.z); atomicAdd(bq + 3, dqh.w);
+        atomicAdd(bk, dkh.x); atomicAdd(bk + 1, dkh.y); atomicAdd(bk + 2, dkh.z); atomicAdd(bk + 3, dkh.w);
+      }
     }
     *reinterpret_cast<float4*>(dq + row * N + lane * 4) = dq_sum;
     *reinterpret_cast<float4*>(dk + row * N + lane * 4) = dk_sum;
   }
-  __syncthreads();
-  float* out = bias_partials + (int64_t)blockIdx.x * 2 * heads * N;
-  for (int i = threadIdx.x; i < 2 * heads * N; i += THREADS) out[i] = bias_acc[i];
+  if (want_bias) {
+    __syncthreads();
+    float* out = bias_partials + (int64_t)blockIdx.x * 2 * heads * N;
+    for (int i = threadIdx.x; i < 2 * heads * N; i += THREADS) out[i] = bias_acc[i];
+  }
 }
 
 static int grid_for(int64_t rows) {
@@ -189,31 +200,43 @@ extern "C" int lbi_siso_prep_fwd(const void* q, const void* k, const float* q_bi
   return (int)cudaGetLastError();
 }
 
-extern "C" int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
-                                 const float* gamma, const float* scale, const float* dqr, const float* dkr, const float* dqk,
-                                 float* dq, float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials,
-                                 int64_t tokens, int seq_len, int dkr_pad, int groups, int heads, int d_state, int n_angles, int is_bf16,
-                                 cudaStream_t st) {
-  using namespace lbi::sisoprep;
-  if (seq_len <= 0 || tokens % seq_len != 0 || (dkr_pad > 0 && dkr_pad < seq_len)) return (int)cudaErrorInvalidValue;
-  if (d_state != N || tokens <= 0 || groups <= 0 || heads % groups != 0 || n_angles < 0 || 2 * n_angles > N) return (int)cudaErrorInvalidValue;
-  const int64_t rows = tokens * groups;
+namespace lbi {
+namespace sisoprep {
+template <typename T, typename C>
+static int launch_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta, const float* gamma,
+                      const float* scale, const void* dqr, const void* dkr, const float* dqk, float* dq, float* dk, float* dtheta,
+                      float* dgamma, float* dscale, float* bias_partials, int64_t rows, int64_t frows, int groups, int heads,
+                      int n_angles, int seq_len, int dkr_pad, cudaStream_t st) {
   const int blocks = grid_for(rows);
   const size_t smem = (size_t)2 * heads * N * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-  int rc;
-  if (is_bf16) {
-    rc = (int)cudaFuncSetAttribute(bwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (rc) return rc;
-    bwd_kernel<__nv_bfloat16><<<blocks, THREADS, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k, q_bias, k_bias, theta, gamma,
-                                                            scale, dqr, dkr, dqk, dq, dk, dtheta, dgamma, dscale, bias_partials, rows,
-                                                            groups, heads, n_angles, seq_len, dkr_pad);
-  } else {
-    rc = (int)cudaFuncSetAttribute(bwd_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (rc) return rc;
-    bwd_kernel<float><<<blocks, THREADS, smem, st>>>((const float*)q, (const float*)k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk,
-                                                    dq, dk, dtheta, dgamma, dscale, bias_partials, rows, groups, heads, n_angles, seq_len,
-                                                    dkr_pad);
-  }
+  static PerDeviceOnce configured;
+  cudaError_t e = configured.max_dynamic_smem(bwd_kernel<T, C>, (int)(200 * 1024));
+  if (e != cudaSuccess) return (int)e;
+  bwd_kernel<T, C><<<blocks, THREADS, smem, st>>>((const T*)q, (const T*)k, q_bias, k_bias, theta, gamma, scale, (const C*)dqr,
+                                                  (const C*)dkr, dqk, dq, dk, dtheta, dgamma, dscale, bias_partials, rows, frows, groups,
+                                                  heads, n_angles, seq_len, dkr_pad);
   return (int)cudaGetLastError();
+}
+}  // namespace sisoprep
+}  // namespace lbi
+
+extern "C" int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const float* k_bias, const float* theta,
+                                 const float* gamma, const float* scale, const void* dqr, const void* dkr, const float* dqk,
+                                 float* dq, float* dk, float* dtheta, float* dgamma, float* dscale, float* bias_partials,
+                                 int64_t tokens, int64_t ftokens, int seq_len, int dkr_pad, int groups, int heads, int d_state,
+                                 int n_angles, int is_bf16, int cot_bf16, cudaStream_t st) {
+  using namespace lbi::sisoprep;
+  if (seq_len <= 0 || tokens % seq_len != 0 || (dkr_pad > 0 && dkr_pad < seq_len)) return (int)cudaErrorInvalidValue;
+  if (ftokens <= 0 || tokens % ftokens != 0 || ftokens % seq_len != 0) return (int)cudaErrorInvalidValue;
+  if (d_state != N || tokens <= 0 || groups <= 0 || heads % groups != 0 || n_angles < 0 || 2 * n_angles > N) return (int)cudaErrorInvalidValue;
+  const int64_t rows = tokens * groups, frows = ftokens * groups;
+#define LBI_PREP_BWD(T, C)                                                                                                      \
+  return launch_bwd<T, C>(q, k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, dq, dk, dtheta, dgamma, dscale, bias_partials, \
+                          rows, frows, groups, heads, n_angles, seq_len, dkr_pad, st)
+  if (is_bf16 && cot_bf16) LBI_PREP_BWD(__nv_bfloat16, __nv_bfloat16);
+  if (is_bf16) LBI_PREP_BWD(__nv_bfloat16, float);
+  if (cot_bf16) LBI_PREP_BWD(float, __nv_bfloat16);
+  LBI_PREP_BWD(float, float);
+#undef LBI_PREP_BWD
 }

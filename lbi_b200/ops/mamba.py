@@ -90,10 +90,9 @@ def gated_rmsnorm_bwd(dy, x, z, weight, rstd, group: int, gate_first: bool, want
     if (_kernel_ok(dy, x, z, weight, rstd, name="gated_rmsnorm_bwd") and x.dtype in (torch.bfloat16, torch.float32)
             and group % 8 == 0 and x.shape[-1] <= 12288):
         _count()
-        xr = _tile_rows(x, reps).contiguous()
-        zr = None if z is None else _tile_rows(z.to(x.dtype), reps).contiguous()
-        rr = _tile_rows(rstd, reps).contiguous()
-        dx, dz, dw = ext().gated_rmsnorm_bwd(dy.to(x.dtype).contiguous(), xr, zr, weight.float().contiguous(), rr, int(group), bool(gate_first))
+        dx, dz, dw = ext().gated_rmsnorm_bwd(dy.to(x.dtype).contiguous(), x.contiguous(), None if z is None else z.to(x.dtype).contiguous(),
+                                             weight.float().contiguous(), rstd.contiguous(), int(group), bool(gate_first),
+                                             bool(want_dweight))
         return dx, (dz if z is not None else None), (dw if want_dweight else None)
     w = weight.float()
     g = dy.float().view(reps, *x.shape)
@@ -217,18 +216,22 @@ def siso_wide_fwd(q, k, q_bias, k_bias, theta, gamma, scale):
             gamma.float() * (qh * kh).sum(-1))
 
 
-def siso_wide_bwd(q, k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, dkr_reversed: bool = False):
+def siso_wide_bwd(q, k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, dkr_reversed: bool = False, want_bias: bool = True):
     """Cotangents dqr, dkr [P * b, l(p), h, n] (dkr optionally in reversed token order over a padded length), dqk [P * b, l, h]
-    -> (dq, dk [P * b, l, g, n] fp32, dq_bias, dk_bias [h, n], dtheta [P * b, l, h, s], dgamma, dscale [P * b, l, h])."""
+    -> (dq, dk [P * b, l, g, n] fp32, dq_bias, dk_bias [h, n] or None, dtheta [P * b, l, h, s], dgamma, dscale [P * b, l, h]).
+    The forward tensors q, k, theta, gamma, scale [b, ...] are shared by the P directions."""
     b, l = q.shape[:2]
     reps = dqr.shape[0] // b
     if _kernel_ok(q, k, theta, dqr, dkr, dqk, name="siso_prep_bwd") and q.shape[-1] == 128 and q.dtype in (torch.bfloat16, torch.float32):
         _count()
-        return tuple(ext().siso_prep_bwd(
-            _tile_rows(q, reps).contiguous(), _tile_rows(k.to(q.dtype), reps).contiguous(), q_bias.float().contiguous(),
-            k_bias.float().contiguous(), _tile_rows(theta.float(), reps).contiguous(), _tile_rows(gamma.float(), reps).contiguous(),
-            _tile_rows(scale.float(), reps).contiguous(), dqr.float().contiguous(), dkr.float().contiguous(), dqk.float().contiguous(),
-            bool(dkr_reversed)))
+        cot = dqr.dtype if (dqr.dtype == dkr.dtype and dqr.dtype in (torch.bfloat16, torch.float32)) else torch.float32
+        out = ext().siso_prep_bwd(q.contiguous(), k.to(q.dtype).contiguous(), q_bias.float().contiguous(), k_bias.float().contiguous(),
+                                  theta.float().contiguous(), gamma.float().contiguous(), scale.float().contiguous(),
+                                  dqr.to(cot).contiguous(), dkr.to(cot).contiguous(), dqk.float().contiguous(), bool(dkr_reversed),
+                                  bool(want_bias))
+        if not want_bias:
+            out[2] = out[3] = None
+        return tuple(out)
     if dkr_reversed:
         dkr = dkr.flip(1)[:, :l]
     h, n = q_bias.shape
@@ -254,8 +257,8 @@ def siso_wide_bwd(q, k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, dkr_
     dscale = (dkr_ * rk).sum(-1)
     dq = dqh.view(reps, b, l, g, rep, n).sum(4).reshape(reps * b, l, g, n)
     dk = dkh.view(reps, b, l, g, rep, n).sum(4).reshape(reps * b, l, g, n)
-    return (dq, dk, dqh.sum((0, 1, 2)), dkh.sum((0, 1, 2)), dtheta.reshape(reps * b, l, h, na), dgamma.reshape(reps * b, l, h),
-            dscale.reshape(reps * b, l, h))
+    return (dq, dk, dqh.sum((0, 1, 2)) if want_bias else None, dkh.sum((0, 1, 2)) if want_bias else None,
+            dtheta.reshape(reps * b, l, h, na), dgamma.reshape(reps * b, l, h), dscale.reshape(reps * b, l, h))
 
 
 # ---------------------------------------------------------------- Mamba-3: the recurrence itself
@@ -290,7 +293,7 @@ def siso_scan_bwd(qr, kr, adt, skip_total, v, gy, states):
     if ssd.siso_cuda_supported(v, qr) and gy.dtype == torch.bfloat16 and states is not None:
         if ssd.chunk_backward_supported(v):
             dv, dqr, dkr, dadt, dskip = ssd.chunk_backward(v, gy, kr, qr, adt, None, skip_total, states, per_head=True, strict=True,
-                                                           dv_bf16=True, dn_bf16=False)
+                                                           dv_bf16=True, dn_bf16=True)
             return dqr, dkr, dadt, dskip, dv, False
         if hasattr(ext(), "ssd_decay_grad"):
             tile = lambda t: None if t is None else _tile_rows(t, reps)  # noqa: E731

@@ -23,6 +23,13 @@ _NAMES = [
 ]
 
 
+# functions of lbi_b200.ops.mamba (called as ``mops.<name>`` by the Mamba lowering)
+_MAMBA_NAMES = [
+    "gate_silu_fwd", "gate_silu_bwd", "gated_rmsnorm_fwd", "gated_rmsnorm_bwd", "siso_small_fwd", "siso_small_bwd", "siso_wide_fwd",
+    "siso_wide_bwd", "siso_scan_fwd", "siso_scan_bwd", "softplus_dt_fwd", "silu_fwd", "silu_bwd",
+]
+
+
 def _wrap(name, fn):
     @functools.wraps(fn)
     def timed(*args, **kwargs):
@@ -49,13 +56,24 @@ def enable() -> None:
             continue
         _ORIGINALS[name] = fn
         setattr(ops_pkg, name, _wrap(name, fn))
+    import lbi_b200.ops.mamba as mamba_ops
+
+    for name in _MAMBA_NAMES:
+        fn = getattr(mamba_ops, name, None)
+        if fn is not None:
+            _ORIGINALS["mamba." + name] = fn
+            setattr(mamba_ops, name, _wrap("mamba." + name, fn))
 
 
 def disable() -> None:
     import lbi_b200.ops as ops_pkg
+    import lbi_b200.ops.mamba as mamba_ops
 
     for name, fn in _ORIGINALS.items():
-        setattr(ops_pkg, name, fn)
+        if name.startswith("mamba."):
+            setattr(mamba_ops, name[len("mamba."):], fn)
+        else:
+            setattr(ops_pkg, name, fn)
     _ORIGINALS.clear()
 
 

@@ -69,6 +69,7 @@ class FastLBIEngine:
         act_dtype: torch.dtype | None = None,
         comm=None,
         basis_parallel: bool | None = None,
+        recompute_forward: bool = False,
     ) -> None:
         backend = model.region_backend
         if getattr(backend, "structured", None) is None:
@@ -103,6 +104,13 @@ class FastLBIEngine:
         if basis_parallel and model.region_axis != "sequence":
             raise ValueError("basis_parallel needs sequence-axis regions")
         self.basis_parallel = bool(basis_parallel) and self.comm.world_size > 1
+        # Activation recomputation: a region's cached activations are dropped as soon as its forward has produced the outgoing
+        # state and the loss cotangent, and rebuilt from its tokens and incoming state right before its pullback and again
+        # before its local VJP (two extra region forwards against R + 1 pullback directions).  Sequence axis only.
+        if recompute_forward and model.region_axis != "sequence":
+            raise ValueError("recompute_forward needs sequence-axis regions (a depth-axis region's input is not recomputable from tokens)")
+        self.recompute_forward = bool(recompute_forward)
+        self._step_ids: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ helpers
     def _shadow_of(self, p):
@@ -198,9 +206,17 @@ class FastLBIEngine:
                 rec.pooled, rec.diagnostics, rec.state_out = pooled, step.diagnostics, step.state.float()
                 if remote:
                     comm.handoff_send(rec.state_out, self.placement.owner(k + 1), slot=k + 1)
+            if self.recompute_forward:
+                rec.cache = None
             records.append(rec)
             state = rec.state_out
         return records, loss
+
+    def _cache_of(self, rec: RegionRecord):
+        """The region's cached activations; rebuilt from its tokens and incoming state when they were dropped."""
+        if rec.cache is None:
+            rec.cache = self._adopt_region(rec.index, rec.state_in, self._step_ids).cache
+        return rec.cache
 
     # ------------------------------------------------------------------ Jacobian + offset of one region
     @torch.no_grad()
@@ -236,7 +252,7 @@ class FastLBIEngine:
                 rows[:nb] = g_pooled[:, j : j + nb].transpose(0, 1).unsqueeze(2).to(self.act_dtype)
             if nb < c:  # the loss direction rides in the last chunk
                 rows[nb] = rec.d_out_loss.view(bsz, t_len, dim).to(self.act_dtype)
-            g_in = self.structured.input_pullback(rec.cache, rows.view(c * n, dim))
+            g_in = self.structured.input_pullback(self._cache_of(rec), rows.view(c * n, dim))
             cond_cots[j : j + c] = ops.sum_tokens(g_in, c * bsz, t_len).view(c, bsz, dim)
             j += c
         g_state = iface.decode_jacobian_t(k, rec.state_in, cond_cots.transpose(0, 1))  # [B, total, R]
@@ -249,6 +265,8 @@ class FastLBIEngine:
         bsz, r = rec.state_in.shape
         rows, offset = self._pullback_directions(rec, 0, r if need_jacobian else 0, include_loss=True)
         jac = rows.transpose(1, 2).contiguous() if rows is not None else None
+        if self.recompute_forward:
+            rec.cache = None
         if offset is None:
             offset = torch.zeros(bsz, r, dtype=torch.float32, device=self.device)
         return jac, offset
@@ -317,7 +335,7 @@ class FastLBIEngine:
                 if off is not None:
                     offs_all[k] = off
                     loss_done.add(k)
-            if k not in own:
+            if k not in own or self.recompute_forward:
                 rec.cache = None
         for rec in records:   # loss directions that found no block to ride with
             if rec.index not in loss_done and rec.d_out_loss is not None:
@@ -384,7 +402,7 @@ class FastLBIEngine:
         if cot is None:
             return
         with torch.no_grad():
-            d_in = self.structured.backward(rec.cache, cot, self)
+            d_in = self.structured.backward(self._cache_of(rec), cot, self)
             d_cond = ops.sum_tokens(d_in, bsz, t_len)
             ops.embedding_scatter_add(self._g(model.canvas.embedding.weight), rec.ids, d_in)
         dec_params = list(iface.decoders[k].parameters())
@@ -492,6 +510,7 @@ class FastLBIEngine:
         """Forward + exact region-local backward; gradients end up in ``self.flat.grads`` (not yet reduced)."""
         model = self.model
         self.flat.zero_grad()
+        self._step_ids = input_ids
         with nvtx.range("lbi/forward"):
             records, loss = self._forward(input_ids, targets)
         k_regions = model.num_regions

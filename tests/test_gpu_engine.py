@@ -108,7 +108,7 @@ def test_bench_paths_run_on_tiny_configs(config):
     import bench
 
     args = argparse.Namespace(config=config, gpus=1, steps=1, warmup=1, basis_chunk=8, no_e2e=False, profile_ops=False, comm="auto",
-                              impl="ours", jacobian_mode="recompute", engine="fast")
+                              impl="ours", jacobian_mode="recompute", engine="fast", recompute_forward="auto", variant="lbi")
     out = bench.run_ours(args)
     assert math.isfinite(out["final_loss"]) and out["value"] > 0
     assert out["gpu_launches"] > 0 and out["kernel_status"] == 0

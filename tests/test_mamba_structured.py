@@ -128,3 +128,17 @@ def test_two_ranks_with_basis_parallel_pullback_match_one_process(tmp_path, kind
     n = min(engine.flat.total, got["grads"].numel())
     assert torch.allclose(got["loss"], res.loss, atol=1e-6)
     assert torch.allclose(got["grads"][:n], engine.flat.grads[:n], atol=1e-6, rtol=1e-5)
+
+
+def test_activation_recomputation_gives_the_same_gradients():
+    """Dropping every region's cached activations after its forward and rebuilding them before the pullback and the local
+    VJP must not change anything."""
+    model = _model("mamba2", regions=4)
+    ids, tgt = _batch(32)
+    a = FastLBIEngine(copy.deepcopy(model), lr=1e-3, basis_chunk=4)
+    b = FastLBIEngine(copy.deepcopy(model), lr=1e-3, basis_chunk=4, recompute_forward=True)
+    ra, rb = a.backward(ids, tgt), b.backward(ids, tgt)
+    assert torch.equal(ra.loss, rb.loss)
+    assert torch.allclose(a.flat.grads, b.flat.grads, atol=1e-7, rtol=1e-6)
+    with pytest.raises(ValueError):
+        FastLBIEngine(_model("mamba2", axis="depth", regions=2), recompute_forward=True)
