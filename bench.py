@@ -164,6 +164,8 @@ def run_ours(args) -> dict:
     from lbi_b200.parallel import CollectiveComm, FastLBIEngine, LocalComm, init_distributed_from_env
 
     cfg = CONFIGS[args.config]
+    # strict mode: a route from a CUDA bf16 tensor to PyTorch / cuBLAS / flash_attn raises instead of running silently
+    ops.dispatch.set_strict(os.environ.get("LBI_B200_STRICT", "1") != "0")
     rank, local_rank, world = init_distributed_from_env("cuda")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N > 1")
@@ -271,7 +273,7 @@ def run_ours(args) -> dict:
                    "optimizer": "AdamW + global-norm clip in the timed region",
                    "cache": "L2 flushed (256 MB write) before every timed step; per-step working set is GBs"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": float(loss) if loss is not None else None,
-        "kernel_status": int(status),
+        "kernel_status": int(status), "strict": bool(ops.dispatch.STRICT["enabled"]), "fallbacks": dict(ops.dispatch.FALLBACKS),
     }
 
 
@@ -423,10 +425,19 @@ def run_dense(args) -> dict:
         model = build_dense_model(rcfg).to(device=device, dtype=torch.float32)
     except Exception as exc:  # noqa: BLE001
         return {"impl": args.impl, "variant": "dense", "unavailable": f"dense model build failed: {exc!r}"[:300]}
-    optimizer = torch.optim.AdamW(model.parameters(), lr=rcfg.lr_model, weight_decay=rcfg.weight_decay)
     n_params = sum(p.numel() for p in model.parameters())
+    fast = None
+    if args.impl == "ours":
+        # this framework's dense arm: the closed-form chain on the sm_100a kernels, flat-buffer AdamW (no autograd, no library GEMM)
+        from lbi_b200.parallel import DenseFastEngine
+
+        fast = DenseFastEngine(model, lr=rcfg.lr_model, weight_decay=rcfg.weight_decay, grad_clip=rcfg.grad_clip)
+    else:
+        optimizer = torch.optim.AdamW(model.parameters(), lr=rcfg.lr_model, weight_decay=rcfg.weight_decay)
 
     def step(xb, yb):
+        if fast is not None:
+            return fast.step(xb, yb)
         model.train()
         optimizer.zero_grad(set_to_none=True)
         with torch.autocast(device_type="cuda", dtype=torch.bfloat16):
@@ -480,11 +491,14 @@ def run_dense(args) -> dict:
     return {
         "metric": "train tokens/s (device-timed, max over ranks)", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16 autocast (fp32 weights)", "data": "synthetic uniform-random tokens, random-init weights",
-        "impl": args.impl, "variant": "dense",
+        "vs_baseline": None, "dtype": "bf16" if fast is not None else "bf16 autocast (fp32 weights)",
+        "data": "synthetic uniform-random tokens, random-init weights", "impl": args.impl, "variant": "dense",
         "config": {"model": cfg["model"] + "-dense", "global_batch": cfg["batch"], "seq_len": cfg["seq_len"], "regions": 1,
-                   "params": n_params, "parallelism": "single", "backward": "dense autograd (no regions)",
-                   "optimizer": "torch AdamW + global-norm clip in the timed region",
+                   "params": n_params, "parallelism": "single",
+                   "backward": "dense closed-form chain on the sm_100a kernels (no regions, no autograd)" if fast is not None
+                   else "dense autograd (no regions)",
+                   "optimizer": ("fused clip + AdamW on flat buffers" if fast is not None else "torch AdamW + global-norm clip")
+                   + " in the timed region",
                    "cache": "L2 flushed (256 MB write) before every timed step; per-step working set is GBs"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "final_loss": float(loss) if loss is not None else None,
     }

@@ -232,11 +232,9 @@ class StructuredMambaRegion:
         dt, dt_slope = mops.softplus_dt_fwd(dt_raw.reshape(bsz, seqlen, h), mx.dt_bias.detach(), *mx.dt_limit)
         conv_w = mx.conv1d.weight.detach().squeeze(1).float().contiguous()
         conv_b = None if mx.conv1d.bias is None else mx.conv1d.bias.detach().float()
-        xbc_conv = ops.causal_conv_fwd(xbc_pre, conv_w, conv_b, bsz, seqlen)
-        xbc = mops.silu_fwd(xbc_conv)
-        x, b_, c_ = torch.split(xbc, [mx.d_inner, gn, gn], dim=-1)
-        x4 = x.reshape(bsz, seqlen, h, p).contiguous()
-        b4, c4 = b_.reshape(bsz, seqlen, g, ns).contiguous(), c_.reshape(bsz, seqlen, g, ns).contiguous()
+        xbc_conv, (x, b_, c_) = mops.conv_silu_fwd(xbc_pre, conv_w, conv_b, bsz, seqlen, (mx.d_inner, gn, gn))
+        x4 = x.view(bsz, seqlen, h, p)
+        b4, c4 = b_.view(bsz, seqlen, g, ns), c_.view(bsz, seqlen, g, ns)
         a_neg = -torch.exp(mx.A_log.detach().float())
         y, final, states = _ssd_forward(x4, dt, a_neg, b4, c4, mx.D.detach(), mx.chunk_size)
         y = y.reshape(n, mx.d_inner).contiguous()
@@ -265,21 +263,23 @@ class StructuredMambaRegion:
         a_neg = -torch.exp(mx.A_log.detach().float())
         dx, ddt, d_a, d_b, d_c, d_dskip = _ssd_backward(lc.x, lc.dt, a_neg, lc.b, lc.c, mx.D.detach(), d_y.view(pb, seqlen, h, p),
                                                         lc.states, lc.final)
-        d_xbc = torch.cat([dx.reshape(rows, mx.d_inner).to(dtype), d_b.reshape(rows, gn).to(dtype), d_c.reshape(rows, gn).to(dtype)], dim=-1)
-        d_conv = mops.silu_bwd(d_xbc, lc.xbc_conv)
+        d_parts = (dx.reshape(rows, mx.d_inner), d_b.reshape(rows, gn), d_c.reshape(rows, gn))
         conv_w = mx.conv1d.weight.detach().squeeze(1).float().contiguous()
+        conv_dim = mx.d_inner + 2 * gn
         if grads is not None:
-            dw_conv, db_conv = ops.causal_conv_wgrad(d_conv, lc.xbc_pre, conv_w.shape[1], bsz, seqlen)
+            dw_conv, db_conv = mops.conv_silu_wgrad(d_parts, lc.xbc_conv, lc.xbc_pre, conv_w.shape[1], bsz, seqlen)
             _acc(grads, prefix + "mixer.conv1d.weight", dw_conv.unsqueeze(1))
             if mx.conv1d.bias is not None:
                 _acc(grads, prefix + "mixer.conv1d.bias", db_conv)
-        d_xbc_pre = ops.causal_conv_dgrad(d_conv, conv_w, pb, seqlen)
         d_dt_raw = (ddt.float().view(reps, bsz, seqlen, h) * lc.dt_slope).reshape(rows, h)
         if grads is not None:
             _acc(grads, prefix + "mixer.A_log", d_a.float() * a_neg)          # d/dA_log of A = -exp(A_log)
             _acc(grads, prefix + "mixer.D", d_dskip.float())
             _acc(grads, prefix + "mixer.dt_bias", d_dt_raw.float().sum(0))
-        d_proj = torch.cat([d_z.to(dtype), d_xbc_pre.to(dtype), d_dt_raw.to(dtype)], dim=-1)
+        d_proj = torch.empty(rows, mx.d_inner + conv_dim + h, dtype=dtype, device=d_branch.device)
+        d_proj[:, : mx.d_inner] = d_z
+        mops.conv_silu_bwd(d_parts, lc.xbc_conv, conv_w, bsz, seqlen, d_proj, mx.d_inner)   # fills the xBC columns
+        d_proj[:, mx.d_inner + conv_dim :] = d_dt_raw
         if grads is not None:
             _wgrad(grads, prefix + "mixer.in_proj.weight", d_proj, lc.normed)
         d_normed = ops.linear_dgrad(d_proj, lw.w_in)

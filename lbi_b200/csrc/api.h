@@ -112,6 +112,20 @@ int lbi_siso_small_bwd(const float* dt, const float* a, const float* sig, const 
                        const float* dscale, void* d_dd_dt, void* d_dd_a, void* d_trap, void* d_angles, int batch, int reps,
                        int seq_len, int heads, int n_angles, int out_bf16, cudaStream_t stream);
 
+// Mamba-2 depthwise causal conv + SiLU over the xBC slice (channels = c0 + c1 + c2, each a multiple of 8; width <= 8).
+// x [tokens, channels] bf16, w [channels, width], bias [channels] or null (fp32) -> pre [tokens, channels] bf16 (conv output) and
+// the activation split into o0 [tokens, c0], o1 [tokens, c1], o2 [tokens, c2] bf16.
+int lbi_conv_silu_fwd(const void* x, const float* w, const float* bias, void* pre, void* o0, void* o1, void* o2, int c0, int c1,
+                      int c2, int64_t tokens, int seq_len, int width, cudaStream_t stream);
+// Cotangents of the three activation parts d0 [tokens, c0] (bf16 or fp32), d1, d2 [tokens, c1 / c2] (bf16 or fp32) -> cotangent of
+// the conv input, written with row stride ld_in (elements) at din.  pre holds ftokens tokens shared by tokens / ftokens directions.
+int lbi_conv_silu_bwd(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre, const float* w,
+                      void* din, int64_t ld_in, int c0, int c1, int c2, int64_t tokens, int64_t ftokens, int seq_len, int width,
+                      cudaStream_t stream);
+// dw [channels, width] += , db [channels] += (fp32; zeroed by the caller).  One direction (tokens = ftokens).
+int lbi_conv_silu_wgrad(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre, const void* x,
+                        float* dw, float* db, int c0, int c1, int c2, int64_t tokens, int seq_len, int width, cudaStream_t stream);
+
 // ---- interface Jacobian products over a basis (interface_jac.cu) -----------------------------------------
 // out[b, p, :] = (((in_scale * g[b, p, :]) @ wa) o d[b, :]) @ wb;  g [B, P, din], wa [din, hidden], d [B, hidden] or null,
 // wb [hidden, dout] or null (then out [B, P, hidden] = (g @ wa) o d).  All fp32 row-major.
@@ -121,6 +135,13 @@ int lbi_interface_mlp_jac(const float* g, const float* wa, const float* d, const
 // transpose = 0 gives J g (weight on the output side); the result is multiplied by out_scale.
 int lbi_layernorm_jac(const float* x, const float* weight, const float* g, float* out, int batch, int p_total, int r, float eps,
                       int transpose, float out_scale, cudaStream_t stream);
+
+// Skinny fp32 linear maps of the interface (a few rows): y = act(x w^T + bias) with act 0 none / 1 SiLU / 2 GELU, `pre` (or null)
+// receives the value before the activation; gx = g w; dw += g^T x, db += sum_b g (db may be null).  x [B, din], w [dout, din].
+int lbi_small_linear_fwd(const float* x, const float* w, const float* bias, float* y, float* pre, int batch, int din, int dout,
+                         int act, cudaStream_t stream);
+int lbi_small_linear_dgrad(const float* g, const float* w, float* gx, int batch, int din, int dout, cudaStream_t stream);
+int lbi_small_linear_wgrad(const float* g, const float* x, float* dw, float* db, int batch, int din, int dout, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

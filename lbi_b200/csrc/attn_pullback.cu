@@ -157,40 +157,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-
-
-// Optional phase timing (build with -DLBI_ATTN_TIMING): cycles spent per role and phase, summed over CTAs.
-//   [kernel: 0 = dQ, 1 = dK/dV][role: 0 = TMA producer, 1 = issuer X, 2 = issuer Y, 3 = compute thread 0][slot]; slot 7 = total.
-#ifdef LBI_ATTN_TIMING
-__device__ unsigned long long g_attn_timing[2][4][12];
-__device__ unsigned long long g_attn_phase[2][8];
-__device__ int g_attn_debug;   // bit 0: no exp in S jobs, 1: no dS math, 2: no shared-memory stores of P / dS, 3: no TMEM loads   // thread 0: wall-clock phases of the CTA, summed over CTAs
-#define TIMED(slot, ...)              \
-  {                                   \
-    const long long _t0 = clock64();  \
-    __VA_ARGS__;                      \
-    tacc[slot] += clock64() - _t0;    \
-  }
-#define TIMING_BEGIN() long long tacc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; const long long _tstart = clock64();
-#define TIMING_END(role)                                                                                   \
-  {                                                                                                        \
-    tacc[7] = clock64() - _tstart;                                                                         \
-    for (int _i = 0; _i < 12; ++_i) atomicAdd(&g_attn_timing[DKDV ? 1 : 0][role][_i], (unsigned long long)tacc[_i]); \
-  }
-#else
-#define TIMED(slot, ...) __VA_ARGS__;
-#define TIMING_BEGIN()
-#define TIMING_END(role)
-#endif
-
-#ifdef LBI_ATTN_TIMING
-#define MMA_X(...) do { if (!(g_attn_debug & 32)) mma_bf16(__VA_ARGS__); } while (0)
-#define MMA_Y(...) do { if (!(g_attn_debug & 16)) mma_bf16(__VA_ARGS__); } while (0)
-#else
-#define MMA_X(...) mma_bf16(__VA_ARGS__)
-#define MMA_Y(...) mma_bf16(__VA_ARGS__)
-#endif
-
 template <bool DKDV>
 __global__ void __launch_bounds__(THREADS, 1)
 pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
@@ -200,10 +166,6 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   extern __shared__ uint8_t raw_smem[];
   Smem<DKDV>& s = *reinterpret_cast<Smem<DKDV>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef LBI_ATTN_TIMING
-  const long long _t_entry = clock64();
-  long long _t_setup = 0, _t_first = 0, _t_loop = 0, _t_acc = 0, _t_store = 0;
-#endif
 
   // tile ownership: heavy tiles first (DKDV: small j walks more query tiles; DQ: large i walks more key tiles)
   const int own = DKDV ? (int)blockIdx.x : p.n_tiles - 1 - (int)blockIdx.x;
@@ -258,7 +220,6 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     // Streams the tiles of up to two steps ahead.  All waits are blocking here: this thread has nothing else to do,
     // and everything a stage release depends on was loaded earlier in this same order, so the waits cannot cycle.
     if (lane == 0) {
-      TIMING_BEGIN();
       bool ok = true;
       auto load_tile = [&](void* dst, const CUtensorMap* m, uint64_t* bar, int col, int64_t row) {
         mbar_arrive_expect_tx(bar, TILE_BYTES);
@@ -295,7 +256,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         const int st = it & 1;
         prefetch_step(it + 2 + PF);
         if (it >= 2) {
-          TIMED(0, ok = mbar_wait(&s.bar_stream_empty[st], ((it >> 1) - 1) & 1, abortp, p.status, 11));
+          ok = mbar_wait(&s.bar_stream_empty[st], ((it >> 1) - 1) & 1, abortp, p.status, 11);
           if (!ok) break;
         }
         if (DKDV) {
@@ -303,7 +264,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           for (int pp = 0; pp < np && ok; ++pp, ++c) {
             const int ds = 2 + (c & (NDO - 1));
             if (c >= NDO) {
-              TIMED(1, ok = mbar_wait(&s.bar_stream_empty[ds], ((c / NDO) - 1) & 1, abortp, p.status, 12));
+              ok = mbar_wait(&s.bar_stream_empty[ds], ((c / NDO) - 1) & 1, abortp, p.status, 12);
               if (!ok) break;
             }
             load_tile(s.stream[ds], &map_do, &s.bar_stream_full[ds], h * DH,
@@ -314,33 +275,31 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           load_tile(s.stream[2 + st], &map_qkv, &s.bar_stream_full[2 + st], col_v, row_b + it * TILE);
         }
       }
-      TIMING_END(0);
     }
   } else if (warp == 16) {
     // ======================================================================== issuer X: S and dP products
     if (lane == 0) {
       const uint32_t idesc_nn = make_idesc_bf16(128, 128, 0, 0);
-      TIMING_BEGIN();
       bool ok = true;
-      TIMED(2, ok = mbar_wait(&s.bar_fixed, 0, abortp, p.status, 16));
+      ok = mbar_wait(&s.bar_fixed, 0, abortp, p.status, 16);
       int it = 0, r = 0, c = 0;   // step, job within the step (0 = S, 1.. = dP of direction r - 1), dO tile index
       for (int n = 0; n < total_jobs && ok; ++n) {
         if (n >= 2) {
-          TIMED(0, ok = mbar_wait(&s.bar_consumed[n & 1], ((n - 2) >> 1) & 1, abortp, p.status, 17));
+          ok = mbar_wait(&s.bar_consumed[n & 1], ((n - 2) >> 1) & 1, abortp, p.status, 17);
           if (!ok) break;
         }
         uint32_t a16, b16;  // operand tile addresses >> 4
         if (r == 0) {
-          TIMED(1, ok = mbar_wait(&s.bar_stream_full[it & 1], (it >> 1) & 1, abortp, p.status, 13));
+          ok = mbar_wait(&s.bar_stream_full[it & 1], (it >> 1) & 1, abortp, p.status, 13);
           a16 = DKDV ? stream0 + (it & 1) * TILE16 : fixed0;
           b16 = DKDV ? fixed0 : stream0 + (it & 1) * TILE16;
         } else if (DKDV) {
-          TIMED(1, ok = mbar_wait(&s.bar_stream_full[2 + (c & (NDO - 1))], (c / NDO) & 1, abortp, p.status, 15));
+          ok = mbar_wait(&s.bar_stream_full[2 + (c & (NDO - 1))], (c / NDO) & 1, abortp, p.status, 15);
           a16 = stream0 + (2 + (c & (NDO - 1))) * TILE16;
           b16 = fixed0 + TILE16;
           ++c;
         } else {
-          if (r == 1) TIMED(1, ok = mbar_wait(&s.bar_stream_full[2 + (it & 1)], (it >> 1) & 1, abortp, p.status, 14))
+          if (r == 1) ok = mbar_wait(&s.bar_stream_full[2 + (it & 1)], (it >> 1) & 1, abortp, p.status, 14);
           a16 = fixed0 + r * TILE16;
           b16 = stream0 + (2 + (it & 1)) * TILE16;
         }
@@ -348,14 +307,13 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         fence_after_sync();
         const uint32_t d_tmem = tmem + (n & 1) * 128;
         const uint64_t da = kmajor0 + a16, db = kmajor0 + b16;
-        TIMED(4, _Pragma("unroll") for (int k = 0; k < 4; ++k) MMA_X(d_tmem, da + 2 * k, db + 2 * k, idesc_nn, k));
-        TIMED(5, mma_commit(&s.bar_ready[n & 1]));
+        _Pragma("unroll") for (int k = 0; k < 4; ++k) mma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc_nn, k);
+        mma_commit(&s.bar_ready[n & 1]);
         if (++r == jobs_per_iter) {
           r = 0;
           ++it;
         }
       }
-      TIMING_END(1);
     }
   } else if (warp == 17) {
     // ======================================================================== issuer Y: accumulating products, releases
@@ -364,7 +322,6 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       const uint32_t idesc_dv2 = make_idesc_bf16(128, 128, 1, 1);  // dV of two directions in one instruction
       const uint32_t ds0 = smem_u32(s.ds_tile[0][0]) >> 4, p16 = smem_u32(s.p_tile[0]) >> 4;
       constexpr uint32_t DSBUF16 = (2 * PANEL_BYTES) >> 4, PANEL16 = PANEL_BYTES >> 4;
-      TIMING_BEGIN();
       bool ok = true;
       int do_waited = 0;
       int it = 0, r = -1, c0 = 0;   // step, job within the step, index of the step's first dO tile
@@ -374,25 +331,25 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           ++it;
           c0 += np;
         }
-        TIMED(0, ok = mbar_wait(&s.bar_written[m & 3], (m >> 2) & 1, abortp, p.status, 18));
+        ok = mbar_wait(&s.bar_written[m & 3], (m >> 2) & 1, abortp, p.status, 18);
         if (!ok) break;
         fence_after_sync();
         const uint32_t first = it != 0;  // accumulate onto earlier steps?
         if (r == 0) {
           if (DKDV) {  // P_it is in shared memory: dV_p += P^T dO_p for the directions of this step
             while (ok && do_waited <= c0 + np - 1) {
-              TIMED(1, ok = mbar_wait(&s.bar_stream_full[2 + (do_waited & (NDO - 1))], (do_waited / NDO) & 1, abortp, p.status, 19));
+              ok = mbar_wait(&s.bar_stream_full[2 + (do_waited & (NDO - 1))], (do_waited / NDO) & 1, abortp, p.status, 19);
               ++do_waited;
             }
             if (!ok) break;
             const uint64_t da = mnmajor0 + p16;
             const uint64_t db = mnmajor0 + stream0 + (2 + (c0 & (NDO - 1))) * TILE16;
-            TIMED(2, if (np == 2) {  // the two dO tiles are adjacent stages: one N = 128 operand with two 64-wide panels
-              _Pragma("unroll") for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
+            if (np == 2) {  // the two dO tiles are adjacent stages: one N = 128 operand with two 64-wide panels
+              _Pragma("unroll") for (int k = 0; k < 8; ++k) mma_bf16(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_dv2, first | (k != 0));
             } else {
-              _Pragma("unroll") for (int k = 0; k < 8; ++k) MMA_Y(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
-            });
-            TIMED(3, mma_commit(&s.bar_p_free));
+              _Pragma("unroll") for (int k = 0; k < 8; ++k) mma_bf16(tmem + ACC_DV, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
+            }
+            mma_commit(&s.bar_p_free);
           }
           continue;
         }
@@ -401,20 +358,19 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         if (DKDV) {
           const uint64_t da = mnmajor0 + ds0 + buf * DSBUF16;
           const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
-          TIMED(2, _Pragma("unroll") for (int k = 0; k < 8; ++k) MMA_Y(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0)));
-          TIMED(3, mma_commit(&s.bar_ds_free[buf]);
-                mma_commit(&s.bar_stream_empty[2 + (d & (NDO - 1))]));  // dO tile d: its dV and this dK are behind the commit, dP was consumed
+          _Pragma("unroll") for (int k = 0; k < 8; ++k) mma_bf16(acc, da + 128 * k, db + 128 * k, idesc_acc, first | (k != 0));
+          mma_commit(&s.bar_ds_free[buf]);
+                mma_commit(&s.bar_stream_empty[2 + (d & (NDO - 1))]);  // dO tile d: its dV and this dK are behind the commit, dP was consumed
         } else {
           const uint64_t da = kmajor0 + ds0 + buf * DSBUF16;
           const uint64_t db = mnmajor0 + stream0 + (it & 1) * TILE16;
-          TIMED(2, _Pragma("unroll") for (int k = 0; k < 8; ++k)
-            MMA_Y(acc, da + (k >> 2) * PANEL16 + (k & 3) * 2, db + 128 * k, idesc_acc, first | (k != 0)));
-          TIMED(3, mma_commit(&s.bar_ds_free[buf]));
+          _Pragma("unroll") for (int k = 0; k < 8; ++k)
+            mma_bf16(acc, da + (k >> 2) * PANEL16 + (k & 3) * 2, db + 128 * k, idesc_acc, first | (k != 0));
+          mma_commit(&s.bar_ds_free[buf]);
         }
-        if (pp == np - 1) TIMED(3, mma_commit(&s.bar_stream_empty[it & 1]))  // Q_it (DKDV) or K_it and V_it (DQ) may be overwritten
+        if (pp == np - 1) mma_commit(&s.bar_stream_empty[it & 1]);  // Q_it (DKDV) or K_it and V_it (DQ) may be overwritten
       }
       if (ok) mma_commit(&s.bar_acc_done);
-      TIMING_END(2);
     }
   } else {
     // ======================================================================== compute warps 0..15
@@ -438,11 +394,6 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     load_stats(own, lse_r, delta_cur);                       // DKDV: first query tile is `own`; DQ: the only one
 #pragma unroll
     for (int i = 0; i < PB; ++i) delta_next[i] = 0.f;
-    TIMING_BEGIN();
-#ifdef LBI_ATTN_TIMING
-    long long _tm2 = 0;
-    _t_setup = _tstart;
-#endif
     bool ok = true;
     int it = 0, rr = -1, d0 = 0;   // step, job within the step, index of the step's first dS tile
     for (int n = 0; n < total_jobs && ok; ++n) {
@@ -456,9 +407,6 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
       const int kj = DKDV ? own : it;         // key tile of this step
       const uint32_t t_buf = t_lane + buf * 128;
       if (rr == 0) {
-#ifdef LBI_ATTN_TIMING
-        const long long _ts = clock64();
-#endif
         if (DKDV) {
           if (it > 0) {
             lse_r = lse_next;
@@ -467,38 +415,17 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
           }
           if (it + 1 < n_iter) load_stats(qi + 1, lse_next, delta_next);
         }
-#ifdef LBI_ATTN_TIMING
-        tacc[10] += clock64() - _ts;
-#endif
-        TIMED(0, ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 31));
-#ifdef LBI_ATTN_TIMING
-        if (n == 0) _t_first = clock64();
-#endif
-        if (DKDV && it > 0 && ok) TIMED(1, ok = mbar_wait(&s.bar_p_free, (it - 1) & 1, abortp, p.status, 32))
-        TIMED(8, ok = __all_sync(0xffffffffu, ok); fence_after_sync());
+        ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 31);
+        if (DKDV && it > 0 && ok) ok = mbar_wait(&s.bar_p_free, (it - 1) & 1, abortp, p.status, 32);
+        ok = __all_sync(0xffffffffu, ok); fence_after_sync();
         if (!ok) break;
         const bool diagonal = (qi == kj);
         {
           uint32_t v[32];
-#ifdef LBI_ATTN_TIMING
-          if (g_attn_debug & 8) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0x3c003c00u + i + n;
-          } else
-#endif
-          TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
-          TIMED(9, __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]));  // tcgen05.wait::ld above: the loads are complete  // TMEM buffer free
-#ifdef LBI_ATTN_TIMING
-          _tm2 = clock64();
-#endif
+          tmem_ld_32x32(t_buf, v); tmem_ld_wait();
+          __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]);  // tcgen05.wait::ld above: the loads are complete  // TMEM buffer free
           const int col0 = slice * 32;
           const uint64_t sc2 = pack_f32x2(p.scale_log2, p.scale_log2), nl2 = pack_f32x2(-lse_r, -lse_r);
-#ifdef LBI_ATTN_TIMING
-          if (g_attn_debug & 1) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) preg[i] = v[2 * i] ^ v[2 * i + 1];
-          } else
-#endif
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 t = unpack_f32x2(fma_f32x2(pack_u32x2(v[2 * i], v[2 * i + 1]), sc2, nl2));
@@ -511,44 +438,28 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
               preg[i] &= (col <= r ? 0x0000ffffu : 0u) | (col + 1 <= r ? 0xffff0000u : 0u);
             }
           }
-#ifdef LBI_ATTN_TIMING
-          if (DKDV && !(g_attn_debug & 4)) {
-#else
           if (DKDV) {
-#endif
 #pragma unroll
             for (int g = 0; g < 4; ++g)
               st_shared_v4(swz(p_panel, r, (slice & 1) * 4 + g),
                            make_uint4(preg[g * 4], preg[g * 4 + 1], preg[g * 4 + 2], preg[g * 4 + 3]));
           }
         }
-#ifdef LBI_ATTN_TIMING
-        tacc[4] += clock64() - _tm2;
-#endif
-        TIMED(5, if (DKDV) fence_proxy_async(); __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_written[n & 3]));
+        if (DKDV) fence_proxy_async(); __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_written[n & 3]);
       } else {
         const int pp = rr - 1, d = d0 + pp, dbuf = d & 1;
         float delta_r = delta_cur[0];
 #pragma unroll
         for (int i = 1; i < PB; ++i) delta_r = (pp == i) ? delta_cur[i] : delta_r;
         const uint32_t ds_panel = smem_u32(s.ds_tile[dbuf][half]);
-        TIMED(0, ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 33));
-        if (d >= 2 && ok) TIMED(2, ok = mbar_wait(&s.bar_ds_free[dbuf], ((d >> 1) - 1) & 1, abortp, p.status, 34))
-        TIMED(8, ok = __all_sync(0xffffffffu, ok); fence_after_sync());
+        ok = mbar_wait(&s.bar_ready[buf], (n >> 1) & 1, abortp, p.status, 33);
+        if (d >= 2 && ok) ok = mbar_wait(&s.bar_ds_free[dbuf], ((d >> 1) - 1) & 1, abortp, p.status, 34);
+        ok = __all_sync(0xffffffffu, ok); fence_after_sync();
         if (!ok) break;
         {
           uint32_t v[32];
-#ifdef LBI_ATTN_TIMING
-          if (g_attn_debug & 8) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = 0x3c003c00u + i + n;
-          } else
-#endif
-          TIMED(3, tmem_ld_32x32(t_buf, v); tmem_ld_wait());
-          TIMED(9, __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]));  // tcgen05.wait::ld above: the loads are complete
-#ifdef LBI_ATTN_TIMING
-          _tm2 = clock64();
-#endif
+          tmem_ld_32x32(t_buf, v); tmem_ld_wait();
+          __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_consumed[buf]);  // tcgen05.wait::ld above: the loads are complete
           // dS = P o (dP - delta): the difference in fp32 (it cancels), the product of two bf16 values in bf16
           const uint64_t delta2 = pack_f32x2(delta_r, delta_r);
 #pragma unroll
@@ -556,39 +467,17 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-#ifdef LBI_ATTN_TIMING
-              if (g_attn_debug & 2) {
-                w[e] = preg[g * 4 + e] ^ v[g * 8 + e * 2] ^ v[g * 8 + e * 2 + 1];
-                continue;
-              }
-#endif
               w[e] = mul_bf16x2(preg[g * 4 + e],
                                 cvt_bf16x2(sub_f32x2(pack_u32x2(v[g * 8 + e * 2], v[g * 8 + e * 2 + 1]), delta2)));
             }
-#ifdef LBI_ATTN_TIMING
-            if (g_attn_debug & 4) {
-              if (w[0] == 0x12345u && w[3] == 0x54321u) st_shared_v4(swz(ds_panel, r, 0), make_uint4(w[0], w[1], w[2], w[3]));
-              continue;
-            }
-#endif
             st_shared_v4(swz(ds_panel, r, (slice & 1) * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
           }
         }
-#ifdef LBI_ATTN_TIMING
-        tacc[4] += clock64() - _tm2;
-#endif
-        TIMED(5, fence_proxy_async(); __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_written[n & 3]));
+        fence_proxy_async(); __syncwarp(); if (lane == 0) mbar_arrive(&s.bar_written[n & 3]);
       }
     }
     // ------------------------------------------------------------------ epilogue: accumulators -> global
-#ifdef LBI_ATTN_TIMING
-    _tm2 = clock64();
-    _t_loop = _tm2;
-#endif
     if (ok) ok = mbar_wait(&s.bar_acc_done, 0, abortp, p.status, 35);
-#ifdef LBI_ATTN_TIMING
-    _t_acc = clock64();
-#endif
     // the four warps of a column slice share named barrier 1 + slice below: they take one decision (a raised abort flag wins)
     named_barrier_sync(1 + slice, 128);
     ok = (s.abort_flag == 0);
@@ -680,11 +569,6 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
         }
       }
     }
-#ifdef LBI_ATTN_TIMING
-    tacc[6] += clock64() - _tm2;
-    _t_store = clock64();
-    if (threadIdx.x == 0) TIMING_END(3);
-#endif
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -699,18 +583,6 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
     fence_after_sync();
     tmem_dealloc(tmem, 512);
   }
-#ifdef LBI_ATTN_TIMING
-  if (threadIdx.x == 0) {
-    const long long t_exit = clock64();
-    unsigned long long* ph = g_attn_phase[DKDV ? 1 : 0];
-    atomicAdd(&ph[0], (unsigned long long)(_t_setup - _t_entry));   // entry -> set-up done
-    atomicAdd(&ph[1], (unsigned long long)(_t_first - _t_setup));   // -> first S tile in TMEM
-    atomicAdd(&ph[2], (unsigned long long)(_t_loop - _t_first));   // -> all jobs processed
-    atomicAdd(&ph[3], (unsigned long long)(_t_acc - _t_loop));     // -> last accumulating product finished
-    atomicAdd(&ph[4], (unsigned long long)(_t_store - _t_acc));    // -> outputs stored
-    atomicAdd(&ph[5], (unsigned long long)(t_exit - _t_store));    // -> exit
-  }
-#endif
 }
 
 // delta[p, b, h, t] = sum_d dO[(p, b, t), h * Dh + d] * O[(b, t), h * Dh + d]; one warp per (row, head).
@@ -785,23 +657,6 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMa
 
 }  // namespace attn
 }  // namespace lbi
-
-#ifdef LBI_ATTN_TIMING
-// Copies the 2 x 4 x 8 cycle counters to `out` and clears them.
-extern "C" int lbi_attn_set_debug(int flags) { return (int)cudaMemcpyToSymbol(lbi::attn::g_attn_debug, &flags, sizeof(int)); }
-extern "C" int lbi_attn_phase_read(unsigned long long* out) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_phase, sizeof(unsigned long long) * 16);
-  if (e != cudaSuccess) return (int)e;
-  unsigned long long zeros[16] = {0};
-  return (int)cudaMemcpyToSymbol(lbi::attn::g_attn_phase, zeros, sizeof(zeros));
-}
-extern "C" int lbi_attn_timing_read(unsigned long long* out) {
-  cudaError_t e = cudaMemcpyFromSymbol(out, lbi::attn::g_attn_timing, sizeof(unsigned long long) * 96);
-  if (e != cudaSuccess) return (int)e;
-  unsigned long long zeros[96] = {0};
-  return (int)cudaMemcpyToSymbol(lbi::attn::g_attn_timing, zeros, sizeof(zeros));
-}
-#endif
 
 extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const float* lse, void* d_qkv,
                                  float* delta, int batch, int heads, int seq_len, int head_dim, int nbasis, float scale,

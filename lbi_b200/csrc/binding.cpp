@@ -484,6 +484,110 @@ std::vector<Tensor> siso_small_bwd(const Tensor& dt, const Tensor& a, const Tens
   return {d1, d2, d3, d4};
 }
 
+// Skinny fp32 linear maps (interface_jac.cu).  -> (y, pre) with pre empty unless want_pre
+std::tuple<Tensor, Tensor> small_linear_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t act, bool want_pre) {
+  CHECK_F32(x);
+  CHECK_F32(w);
+  if (bias) CHECK_F32((*bias));
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && w.size(1) == x.size(1), "small_linear_fwd: x [B, din], w [dout, din]");
+  Tensor y = torch::empty({x.size(0), w.size(0)}, x.options());
+  Tensor pre = want_pre ? torch::empty_like(y) : torch::empty({0}, x.options());
+  check(lbi_small_linear_fwd(x.data_ptr<float>(), w.data_ptr<float>(), bias ? bias->data_ptr<float>() : nullptr, y.data_ptr<float>(),
+                             want_pre ? pre.data_ptr<float>() : nullptr, (int)x.size(0), (int)x.size(1), (int)w.size(0), (int)act,
+                             cur_stream()),
+        "small_linear_fwd");
+  return {y, pre};
+}
+
+Tensor small_linear_dgrad(const Tensor& g, const Tensor& w) {
+  CHECK_F32(g);
+  CHECK_F32(w);
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.dim() == 2 && w.dim() == 2 && w.size(0) == g.size(1), "small_linear_dgrad: g [B, dout], w [dout, din]");
+  Tensor gx = torch::empty({g.size(0), w.size(1)}, g.options());
+  check(lbi_small_linear_dgrad(g.data_ptr<float>(), w.data_ptr<float>(), gx.data_ptr<float>(), (int)g.size(0), (int)w.size(1),
+                               (int)w.size(0), cur_stream()),
+        "small_linear_dgrad");
+  return gx;
+}
+
+void small_linear_wgrad_(const Tensor& g, const Tensor& x, Tensor dw, c10::optional<Tensor> db) {
+  CHECK_F32(g);
+  CHECK_F32(x);
+  CHECK_F32(dw);
+  if (db) CHECK_F32((*db));
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.dim() == 2 && x.dim() == 2 && g.size(0) == x.size(0) && dw.numel() == g.size(1) * x.size(1) &&
+                  (!db || db->numel() == g.size(1)),
+              "small_linear_wgrad: g [B, dout], x [B, din], dw [dout, din], db [dout]");
+  check(lbi_small_linear_wgrad(g.data_ptr<float>(), x.data_ptr<float>(), dw.data_ptr<float>(), db ? db->data_ptr<float>() : nullptr,
+                               (int)g.size(0), (int)x.size(1), (int)g.size(1), cur_stream()),
+        "small_linear_wgrad");
+}
+
+// Mamba-2 conv + SiLU.  x [n, C] bf16 -> (pre [n, C], act0 [n, c0], act1 [n, c1], act2 [n, c2]) bf16.
+std::vector<Tensor> conv_silu_fwd(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& bias, int64_t seq_len, int64_t c0,
+                                  int64_t c1, int64_t c2) {
+  CHECK_BF16(x);
+  CHECK_F32(w);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.size(1) == c0 + c1 + c2 && w.dim() == 2 && w.size(0) == x.size(1), "conv_silu_fwd: shapes");
+  if (bias) CHECK_F32((*bias));
+  const int64_t n = x.size(0);
+  Tensor pre = torch::empty_like(x);
+  Tensor o0 = torch::empty({n, c0}, x.options()), o1 = torch::empty({n, c1}, x.options()), o2 = torch::empty({n, c2}, x.options());
+  check(lbi_conv_silu_fwd(x.data_ptr(), w.data_ptr<float>(), bias ? bias->data_ptr<float>() : nullptr, pre.data_ptr(), o0.data_ptr(),
+                          o1.data_ptr(), o2.data_ptr(), (int)c0, (int)c1, (int)c2, n, (int)seq_len, (int)w.size(1), cur_stream()),
+        "conv_silu_fwd");
+  return {pre, o0, o1, o2};
+}
+
+static int is_f32_or_bf16(const Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_cuda() && t.is_contiguous() && (t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16), what,
+              " must be a contiguous CUDA fp32 / bf16 tensor");
+  return t.scalar_type() == at::kFloat ? 1 : 0;
+}
+
+// d0 [P n, c0], d1 [P n, c1], d2 [P n, c2]; pre [n, C] -> writes the conv-input cotangent into out[:, col0 : col0 + C] (bf16,
+// out [P n, width_total]).
+void conv_silu_bwd_(const Tensor& d0, const Tensor& d1, const Tensor& d2, const Tensor& pre, const Tensor& w, Tensor out, int64_t col0,
+                    int64_t seq_len) {
+  CHECK_BF16(pre);
+  CHECK_BF16(out);
+  CHECK_F32(w);
+  c10::cuda::CUDAGuard guard(pre.device());
+  const int f0 = is_f32_or_bf16(d0, "d0"), f1 = is_f32_or_bf16(d1, "d1"), f2 = is_f32_or_bf16(d2, "d2");
+  TORCH_CHECK(f1 == f2, "conv_silu_bwd: d1, d2 must share a dtype");
+  const int64_t tokens = d0.size(0), ftokens = pre.size(0), c0 = d0.size(1), c1 = d1.size(1), c2 = d2.size(1);
+  TORCH_CHECK(pre.size(1) == c0 + c1 + c2 && d1.size(0) == tokens && d2.size(0) == tokens && out.dim() == 2 && out.size(0) == tokens &&
+                  col0 % 8 == 0 && col0 + c0 + c1 + c2 <= out.size(1),
+              "conv_silu_bwd: shapes");
+  check(lbi_conv_silu_bwd(d0.data_ptr(), f0, d1.data_ptr(), d2.data_ptr(), f1, pre.data_ptr(), w.data_ptr<float>(),
+                          static_cast<at::BFloat16*>(out.data_ptr()) + col0, out.size(1), (int)c0, (int)c1, (int)c2, tokens, ftokens,
+                          (int)seq_len, (int)w.size(1), cur_stream()),
+        "conv_silu_bwd");
+}
+
+// -> (dw [C, W], db [C]) fp32
+std::tuple<Tensor, Tensor> conv_silu_wgrad(const Tensor& d0, const Tensor& d1, const Tensor& d2, const Tensor& pre, const Tensor& x,
+                                           int64_t width, int64_t seq_len) {
+  CHECK_BF16(pre);
+  CHECK_BF16(x);
+  c10::cuda::CUDAGuard guard(pre.device());
+  const int f0 = is_f32_or_bf16(d0, "d0"), f1 = is_f32_or_bf16(d1, "d1"), f2 = is_f32_or_bf16(d2, "d2");
+  TORCH_CHECK(f1 == f2, "conv_silu_wgrad: d1, d2 must share a dtype");
+  const int64_t tokens = pre.size(0), c0 = d0.size(1), c1 = d1.size(1), c2 = d2.size(1), ch = pre.size(1);
+  TORCH_CHECK(d0.size(0) == tokens && d1.size(0) == tokens && d2.size(0) == tokens && x.sizes() == pre.sizes() && ch == c0 + c1 + c2,
+              "conv_silu_wgrad: one direction, shapes must match");
+  auto f32 = pre.options().dtype(at::kFloat);
+  Tensor dw = torch::zeros({ch, width}, f32), db = torch::zeros({ch}, f32);
+  check(lbi_conv_silu_wgrad(d0.data_ptr(), f0, d1.data_ptr(), d2.data_ptr(), f1, pre.data_ptr(), x.data_ptr(), dw.data_ptr<float>(),
+                            db.data_ptr<float>(), (int)c0, (int)c1, (int)c2, tokens, (int)seq_len, (int)width, cur_stream()),
+        "conv_silu_wgrad");
+  return {dw, db};
+}
+
 // (((in_scale g) @ wa) o d) @ wb over a basis: g [B, P, din] fp32, wa [din, hidden], d [B, hidden] or none, wb [hidden, dout] or none.
 Tensor interface_mlp_jac(const Tensor& g, const Tensor& wa, const c10::optional<Tensor>& d, const c10::optional<Tensor>& wb,
                          double in_scale) {
@@ -1052,6 +1156,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("siso_prep_bwd", &siso_prep_bwd, py::arg("q"), py::arg("k"), py::arg("q_bias"), py::arg("k_bias"), py::arg("theta"),
         py::arg("gamma"), py::arg("scale"), py::arg("dqr"), py::arg("dkr"), py::arg("dqk"), py::arg("dkr_reversed") = false,
         py::arg("want_bias") = true);
+  m.def("small_linear_fwd", &small_linear_fwd);
+  m.def("small_linear_dgrad", &small_linear_dgrad);
+  m.def("small_linear_wgrad_", &small_linear_wgrad_);
+  m.def("conv_silu_fwd", &conv_silu_fwd);
+  m.def("conv_silu_bwd_", &conv_silu_bwd_);
+  m.def("conv_silu_wgrad", &conv_silu_wgrad);
   m.def("gate_silu_fwd", &gate_silu_fwd);
   m.def("gate_silu_bwd", &gate_silu_bwd);
   m.def("siso_small_fwd", &siso_small_fwd);

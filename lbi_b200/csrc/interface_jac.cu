@@ -130,3 +130,95 @@ extern "C" int lbi_layernorm_jac(const float* x, const float* weight, const floa
                                                                               out_scale);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------ skinny linear maps
+// The interface maps themselves act on a handful of rows (one per batch element): y = act(x W^T + b), its input
+// cotangent and its parameter gradients.  Three fp32 kernels cover them, so that neither the forward of the region chain
+// nor the local VJPs call a library GEMM or autograd for these maps (reference: nn.Linear inside
+// interfaces/vector_mlp.py:125-161 and torch.autograd.grad in backward/local_vjp.py:137-168).
+namespace lbi {
+namespace iface {
+
+__device__ __forceinline__ float act_apply(float v, int act) {
+  if (act == 1) return v * sigmoidf_(v);                                            // SiLU
+  if (act == 2) return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));            // GELU (erf form)
+  return v;
+}
+
+// y[b, o] = act(sum_i x[b, i] w[o, i] + bias[o]); pre (optional) keeps the value before the activation.  One warp per output.
+__global__ void __launch_bounds__(256) small_linear_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                               const float* __restrict__ bias, float* __restrict__ y,
+                                                               float* __restrict__ pre, int batch, int din, int dout, int act) {
+  const int lane = threadIdx.x & 31;
+  const int64_t widx = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (widx >= (int64_t)batch * dout) return;
+  const int o = (int)(widx % dout), b = (int)(widx / dout);
+  const float* xr = x + (int64_t)b * din;
+  const float* wr = w + (int64_t)o * din;
+  float acc = 0.f;
+  for (int i = lane; i < din; i += 32) acc = fmaf(xr[i], wr[i], acc);
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    acc += bias ? bias[o] : 0.f;
+    if (pre) pre[widx] = acc;
+    y[widx] = act_apply(acc, act);
+  }
+}
+
+// gx[b, i] = sum_o g[b, o] w[o, i]
+__global__ void __launch_bounds__(256) small_linear_dgrad_kernel(const float* __restrict__ g, const float* __restrict__ w,
+                                                                 float* __restrict__ gx, int batch, int din, int dout) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)batch * din) return;
+  const int i = (int)(idx % din), b = (int)(idx / din);
+  const float* gr = g + (int64_t)b * dout;
+  float acc = 0.f;
+  for (int o = 0; o < dout; ++o) acc = fmaf(gr[o], w[(int64_t)o * din + i], acc);
+  gx[idx] = acc;
+}
+
+// dw[o, i] += sum_b g[b, o] x[b, i];  db[o] += sum_b g[b, o]   (db may be null)
+__global__ void __launch_bounds__(256) small_linear_wgrad_kernel(const float* __restrict__ g, const float* __restrict__ x,
+                                                                 float* __restrict__ dw, float* __restrict__ db, int batch, int din,
+                                                                 int dout) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)dout * din) return;
+  const int i = (int)(idx % din), o = (int)(idx / din);
+  float acc = 0.f, accb = 0.f;
+  for (int b = 0; b < batch; ++b) {
+    const float gv = g[(int64_t)b * dout + o];
+    acc = fmaf(gv, x[(int64_t)b * din + i], acc);
+    accb += gv;
+  }
+  dw[idx] += acc;
+  if (db && i == 0) db[o] += accb;
+}
+
+}  // namespace iface
+}  // namespace lbi
+
+extern "C" int lbi_small_linear_fwd(const float* x, const float* w, const float* bias, float* y, float* pre, int batch, int din,
+                                    int dout, int act, cudaStream_t st) {
+  using namespace lbi::iface;
+  if (batch <= 0 || din <= 0 || dout <= 0 || act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+  const int64_t warps = (int64_t)batch * dout;
+  small_linear_fwd_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(x, w, bias, y, pre, batch, din, dout, act);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_small_linear_dgrad(const float* g, const float* w, float* gx, int batch, int din, int dout, cudaStream_t st) {
+  using namespace lbi::iface;
+  if (batch <= 0 || din <= 0 || dout <= 0) return (int)cudaErrorInvalidValue;
+  const int64_t total = (int64_t)batch * din;
+  small_linear_dgrad_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(g, w, gx, batch, din, dout);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_small_linear_wgrad(const float* g, const float* x, float* dw, float* db, int batch, int din, int dout,
+                                      cudaStream_t st) {
+  using namespace lbi::iface;
+  if (batch <= 0 || din <= 0 || dout <= 0) return (int)cudaErrorInvalidValue;
+  const int64_t total = (int64_t)dout * din;
+  small_linear_wgrad_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(g, x, dw, db, batch, din, dout);
+  return (int)cudaGetLastError();
+}

@@ -264,3 +264,214 @@ extern "C" int lbi_siso_small_bwd(const float* dt, const float* a, const float* 
         (float*)d_angles, batch, seq_len, heads, n_angles);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------ Mamba-2 conv + SiLU
+// Depthwise causal conv over the xBC slice of in_proj followed by SiLU, eight channels per thread (16-byte accesses).
+//   pre[t, c] = bias[c] + sum_w w[c, w] x[t - (W - 1) + w, c],   act = silu(pre)
+// The activation leaves as three contiguous tensors (x | B | C: what the scan kernels take), the pre-activation is kept
+// for the backward.  Backward for P stacked directions: the cotangents of x, B, C arrive as three tensors,
+//   dpre[t', c] = dact[t', c] silu'(pre[t', c]),   din[t, c] = sum_w w[c, w] dpre[t + (W - 1) - w, c]
+// and din is written with a row stride, i.e. straight into its column range of the in_proj cotangent.  The weight
+// gradient dw[c, w] = sum_t dpre[t, c] x[t - (W - 1) + w, c], db[c] = sum_t dpre[t, c] accumulates per thread over a run
+// of tokens and leaves with one atomic per (thread, tap).  Replaces causal_conv1d_fn / its backward in the reference's fused
+// Mamba-2 path (backbones/mamba2/ops/triton/ssd_combined.py:847, 921, 970) and nn.Conv1d + SiLU in its unfused path.
+namespace lbi {
+namespace mconv {
+
+constexpr int MAXW = 8;
+
+struct Seg {          // channel c belongs to segment 0 [0, c0), 1 [c0, c0 + c1) or 2 [c0 + c1, c0 + c1 + c2)
+  int c0, c1, c2;
+};
+
+__device__ __forceinline__ float silu_(float v) { return v * sigmoidf_(v); }
+__device__ __forceinline__ float dsilu_(float v) {
+  const float s = sigmoidf_(v);
+  return s * (1.f + v * (1.f - s));
+}
+
+__global__ void __launch_bounds__(256) conv_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                                                            const float* __restrict__ bias, __nv_bfloat16* __restrict__ pre,
+                                                            __nv_bfloat16* __restrict__ o0, __nv_bfloat16* __restrict__ o1,
+                                                            __nv_bfloat16* __restrict__ o2, Seg seg, int64_t tokens, int seq_len,
+                                                            int width) {
+  const int channels = seg.c0 + seg.c1 + seg.c2, cvecs = channels / 8;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * cvecs) return;
+  const int cv = (int)(idx % cvecs), c = cv * 8;
+  const int64_t tok = idx / cvecs;
+  const int t = (int)(tok % seq_len);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+  for (int k = 0; k < width; ++k) {
+    const int tt = t - (width - 1) + k;
+    if (tt < 0) continue;
+    float xv[8];
+    unpack8(*reinterpret_cast<const bf16x8*>(x + (tok + (tt - t)) * channels + c), xv);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], xv[e], acc[e]);
+  }
+  *reinterpret_cast<bf16x8*>(pre + tok * channels + c) = pack8(acc);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = silu_(acc[e]);
+  __nv_bfloat16* dst = c < seg.c0 ? o0 + tok * seg.c0 + c
+                                  : (c < seg.c0 + seg.c1 ? o1 + tok * seg.c1 + (c - seg.c0) : o2 + tok * seg.c2 + (c - seg.c0 - seg.c1));
+  *reinterpret_cast<bf16x8*>(dst) = pack8(acc);
+}
+
+template <typename D0>
+__device__ __forceinline__ void load_cot(const D0* p, float* out);
+template <>
+__device__ __forceinline__ void load_cot<__nv_bfloat16>(const __nv_bfloat16* p, float* out) {
+  unpack8(*reinterpret_cast<const bf16x8*>(p), out);
+}
+template <>
+__device__ __forceinline__ void load_cot<float>(const float* p, float* out) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w; out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+
+// dpre of eight channels at token `tok` (cotangent row) / `ftok` (forward row)
+template <typename D0, typename D12>
+__device__ __forceinline__ void dpre8(const D0* d0, const D12* d1, const D12* d2, const __nv_bfloat16* pre, Seg seg, int channels,
+                                      int64_t tok, int64_t ftok, int c, float* out) {
+  float g[8], pv[8];
+  if (c < seg.c0) load_cot<D0>(d0 + tok * seg.c0 + c, g);
+  else if (c < seg.c0 + seg.c1) load_cot<D12>(d1 + tok * seg.c1 + (c - seg.c0), g);
+  else load_cot<D12>(d2 + tok * seg.c2 + (c - seg.c0 - seg.c1), g);
+  unpack8(*reinterpret_cast<const bf16x8*>(pre + ftok * channels + c), pv);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) out[e] = g[e] * dsilu_(pv[e]);
+}
+
+template <typename D0, typename D12>
+__global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const D0* __restrict__ d0, const D12* __restrict__ d1,
+                                                            const D12* __restrict__ d2, const __nv_bfloat16* __restrict__ pre,
+                                                            const float* __restrict__ w, __nv_bfloat16* __restrict__ din, int64_t ld_in,
+                                                            Seg seg, int64_t tokens, int64_t ftokens, int seq_len, int width) {
+  const int channels = seg.c0 + seg.c1 + seg.c2, cvecs = channels / 8;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= tokens * cvecs) return;
+  const int cv = (int)(idx % cvecs), c = cv * 8;
+  const int64_t tok = idx / cvecs;
+  const int t = (int)(tok % seq_len);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int k = 0; k < width; ++k) {
+    const int tt = t + (width - 1) - k;
+    if (tt >= seq_len) continue;
+    float dp[8];
+    const int64_t tk = tok + (tt - t);
+    dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tk, tk % ftokens, c, dp);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], dp[e], acc[e]);
+  }
+  *reinterpret_cast<bf16x8*>(din + tok * ld_in + c) = pack8(acc);
+}
+
+// grid (cvecs blocks of 32 lanes x 8 token runs per block, runs); every thread walks RUN tokens of its eight channels
+constexpr int RUN = 64;
+template <typename D0, typename D12>
+__global__ void __launch_bounds__(256) conv_silu_wgrad_kernel(const D0* __restrict__ d0, const D12* __restrict__ d1,
+                                                              const D12* __restrict__ d2, const __nv_bfloat16* __restrict__ pre,
+                                                              const __nv_bfloat16* __restrict__ x, float* __restrict__ dw,
+                                                              float* __restrict__ db, Seg seg, int64_t tokens, int seq_len, int width) {
+  const int channels = seg.c0 + seg.c1 + seg.c2, cvecs = channels / 8;
+  const int cv = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int64_t run = (int64_t)blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (cv >= cvecs) return;
+  const int c = cv * 8;
+  float accw[MAXW][8], accb[8];
+#pragma unroll
+  for (int k = 0; k < MAXW; ++k)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) accw[k][e] = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) accb[e] = 0.f;
+  const int64_t t_lo = run * RUN, t_hi = t_lo + RUN < tokens ? t_lo + RUN : tokens;
+  for (int64_t tok = t_lo; tok < t_hi; ++tok) {
+    const int t = (int)(tok % seq_len);
+    float dp[8];
+    dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tok, tok, c, dp);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) accb[e] += dp[e];
+#pragma unroll
+    for (int k = 0; k < MAXW; ++k) {
+      if (k >= width) break;
+      const int tt = t - (width - 1) + k;
+      if (tt < 0) continue;
+      float xv[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(x + (tok + (tt - t)) * channels + c), xv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) accw[k][e] = fmaf(dp[e], xv[e], accw[k][e]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    atomicAdd(db + c + e, accb[e]);
+#pragma unroll
+    for (int k = 0; k < MAXW; ++k)
+      if (k < width) atomicAdd(dw + (c + e) * width + k, accw[k][e]);
+  }
+}
+
+}  // namespace mconv
+}  // namespace lbi
+
+extern "C" int lbi_conv_silu_fwd(const void* x, const float* w, const float* bias, void* pre, void* o0, void* o1, void* o2, int c0,
+                                 int c1, int c2, int64_t tokens, int seq_len, int width, cudaStream_t st) {
+  using namespace lbi::mconv;
+  if (tokens <= 0) return 0;
+  if (c0 % 8 || c1 % 8 || c2 % 8 || c0 + c1 + c2 <= 0 || width <= 0 || width > MAXW || seq_len <= 0 || tokens % seq_len)
+    return (int)cudaErrorInvalidValue;
+  const int64_t total = tokens * ((c0 + c1 + c2) / 8);
+  conv_silu_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, w, bias, (__nv_bfloat16*)pre,
+                                                                        (__nv_bfloat16*)o0, (__nv_bfloat16*)o1, (__nv_bfloat16*)o2,
+                                                                        Seg{c0, c1, c2}, tokens, seq_len, width);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_conv_silu_bwd(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre,
+                                 const float* w, void* din, int64_t ld_in, int c0, int c1, int c2, int64_t tokens, int64_t ftokens,
+                                 int seq_len, int width, cudaStream_t st) {
+  using namespace lbi::mconv;
+  if (tokens <= 0) return 0;
+  if (c0 % 8 || c1 % 8 || c2 % 8 || c0 + c1 + c2 <= 0 || width <= 0 || width > MAXW || seq_len <= 0 || ftokens <= 0 ||
+      tokens % ftokens || ftokens % seq_len || ld_in % 8 || ld_in < c0 + c1 + c2)
+    return (int)cudaErrorInvalidValue;
+  const int64_t total = tokens * ((c0 + c1 + c2) / 8);
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  const Seg seg{c0, c1, c2};
+#define LBI_CONV_BWD(A, B)                                                                                                   \
+  conv_silu_bwd_kernel<A, B><<<blocks, 256, 0, st>>>((const A*)d0, (const B*)d1, (const B*)d2, (const __nv_bfloat16*)pre, w, \
+                                                     (__nv_bfloat16*)din, ld_in, seg, tokens, ftokens, seq_len, width)
+  if (d0_fp32 && d12_fp32) LBI_CONV_BWD(float, float);
+  else if (d0_fp32) LBI_CONV_BWD(float, __nv_bfloat16);
+  else if (d12_fp32) LBI_CONV_BWD(__nv_bfloat16, float);
+  else LBI_CONV_BWD(__nv_bfloat16, __nv_bfloat16);
+#undef LBI_CONV_BWD
+  return (int)cudaGetLastError();
+}
+
+// dw [C, W] and db [C] must be zeroed by the caller (the kernel adds).
+extern "C" int lbi_conv_silu_wgrad(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre,
+                                   const void* x, float* dw, float* db, int c0, int c1, int c2, int64_t tokens, int seq_len, int width,
+                                   cudaStream_t st) {
+  using namespace lbi::mconv;
+  if (tokens <= 0) return 0;
+  if (c0 % 8 || c1 % 8 || c2 % 8 || c0 + c1 + c2 <= 0 || width <= 0 || width > MAXW || seq_len <= 0 || tokens % seq_len)
+    return (int)cudaErrorInvalidValue;
+  const int cvecs = (c0 + c1 + c2) / 8;
+  const int64_t runs = (tokens + RUN - 1) / RUN;
+  const dim3 grid((unsigned)((cvecs + 31) / 32), (unsigned)((runs + 7) / 8));
+  const Seg seg{c0, c1, c2};
+#define LBI_CONV_WG(A, B)                                                                                                      \
+  conv_silu_wgrad_kernel<A, B><<<grid, 256, 0, st>>>((const A*)d0, (const B*)d1, (const B*)d2, (const __nv_bfloat16*)pre,      \
+                                                     (const __nv_bfloat16*)x, dw, db, seg, tokens, seq_len, width)
+  if (d0_fp32 && d12_fp32) LBI_CONV_WG(float, float);
+  else if (d0_fp32) LBI_CONV_WG(float, __nv_bfloat16);
+  else if (d12_fp32) LBI_CONV_WG(__nv_bfloat16, float);
+  else LBI_CONV_WG(__nv_bfloat16, __nv_bfloat16);
+#undef LBI_CONV_WG
+  return (int)cudaGetLastError();
+}

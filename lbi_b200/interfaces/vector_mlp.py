@@ -160,6 +160,87 @@ def layer_norm_input_jacobian(norm: nn.LayerNorm, x: torch.Tensor, t_in: torch.T
     return out.to(t_in.dtype)
 
 
+# ---- forward with caches and parameter VJPs in closed form (no autograd, no library GEMM on CUDA) ----------------------
+_ACT_CODE = {"silu": 1, "gelu": 2}
+
+
+def _skinny_kernels(*tensors) -> bool:
+    from .. import ops
+
+    return (tensors[0].is_cuda and ops.native_available() and hasattr(ops.ext(), "small_linear_fwd") and not torch.is_grad_enabled()
+            and all(t is None or t.dtype == torch.float32 for t in tensors))
+
+
+def _linear_forward(x: torch.Tensor, lin: nn.Linear, act: str | None, want_pre: bool):
+    """y = act(x W^T + b) for a few rows -> (y, pre-activation or None)."""
+    if _skinny_kernels(x, lin.weight, lin.bias):
+        from .. import ops
+
+        ops.dispatch.KERNEL_LAUNCHES["count"] += 1
+        y, pre = ops.ext().small_linear_fwd(x.contiguous(), lin.weight.detach().contiguous(), None if lin.bias is None else lin.bias.detach(),
+                                            _ACT_CODE[act] if act else 0, bool(want_pre))
+        return y, (pre if want_pre else None)
+    pre = F.linear(x.float(), lin.weight.float(), None if lin.bias is None else lin.bias.float())
+    if act is None:
+        return pre, (pre if want_pre else None)
+    return (F.silu(pre) if act == "silu" else F.gelu(pre)), (pre if want_pre else None)
+
+
+def _linear_vjp(g: torch.Tensor, x: torch.Tensor, lin: nn.Linear, target, want_input: bool):
+    """Adds g^T x and sum_b g into the gradient accumulators ``target(param)`` and returns g W (or None)."""
+    dw = target(lin.weight)
+    db = None if lin.bias is None else target(lin.bias)
+    if _skinny_kernels(g, x, lin.weight) and dw.is_contiguous() and (db is None or db.is_contiguous()):
+        from .. import ops
+
+        ops.dispatch.KERNEL_LAUNCHES["count"] += 1 + int(want_input)
+        ops.ext().small_linear_wgrad_(g.contiguous(), x.contiguous(), dw, db)
+        return ops.ext().small_linear_dgrad(g.contiguous(), lin.weight.detach().contiguous()) if want_input else None
+    gf, xf = g.float(), x.float()
+    dw.add_((gf.t() @ xf).to(dw.dtype))
+    if db is not None:
+        db.add_(gf.sum(0).to(db.dtype))
+    return gf @ lin.weight.detach().float() if want_input else None
+
+
+def head_forward_cached(head: VectorMLPHead, x: torch.Tensor):
+    """-> (y [B, Dout] fp32, cache for ``head_parameter_vjp``)."""
+    first, second = head.layers()
+    xf = x.float()
+    if second is None:
+        y, _ = _linear_forward(xf, first, None, False)
+        return y, (xf, None, None)
+    hid, pre = _linear_forward(xf, first, head.activation, True)
+    y, _ = _linear_forward(hid, second, None, False)
+    return y, (xf, pre, hid)
+
+
+def head_parameter_vjp(head: VectorMLPHead, cache, g_out: torch.Tensor, target, want_input: bool = True):
+    """Cotangent g_out [B, Dout] of a head evaluated by ``head_forward_cached``: parameter gradients are added into
+    ``target(param)``; returns the input cotangent [B, Din] (or None)."""
+    first, second = head.layers()
+    x, pre, hid = cache
+    g = g_out.float()
+    if second is None:
+        return _linear_vjp(g, x, first, target, want_input)
+    g_hid = _linear_vjp(g, hid, second, target, True)
+    g_pre = g_hid * activation_derivative(pre, head.activation)
+    return _linear_vjp(g_pre, x, first, target, want_input)
+
+
+def layer_norm_parameter_vjp(norm: nn.LayerNorm, x: torch.Tensor, g_out: torch.Tensor, target) -> torch.Tensor:
+    """LayerNorm at x [B, R] with cotangent g_out [B, R]: adds the weight / bias gradients, returns the input cotangent."""
+    xf, g = x.float(), g_out.float()
+    mu = xf.mean(dim=-1, keepdim=True)
+    rstd = torch.rsqrt(xf.var(dim=-1, unbiased=False, keepdim=True) + norm.eps)
+    xhat = (xf - mu) * rstd
+    if norm.weight is not None:
+        target(norm.weight).add_((g * xhat).sum(0))
+    if norm.bias is not None:
+        target(norm.bias).add_(g.sum(0))
+    return layer_norm_input_jacobian_t(norm, x, g.unsqueeze(1)).squeeze(1)
+
+
 def mean_pool_jacobian_t(g_pooled: torch.Tensor, seq_len: int) -> torch.Tensor:
     """[B, P, D] -> [B, P, L, D]: every token receives g / L (expanded view, no copy)."""
     if seq_len <= 0:
@@ -245,6 +326,44 @@ class VectorMLPInterface(InterfaceModule):
 
     def shared_vjp_parameters(self) -> list[nn.Parameter]:
         return [self.update_scale] if self.update_scale.requires_grad else []
+
+    # ---- forward with caches / parameter VJPs without autograd ---------------------------
+    def decode_cached(self, state: torch.Tensor, region_index: int):
+        """-> (condition [B, D] fp32, cache for ``decode_parameter_vjp``)."""
+        return head_forward_cached(self.decoders[region_index], state)
+
+    def decode_parameter_vjp(self, region_index: int, cache, g_condition: torch.Tensor, target) -> None:
+        head_parameter_vjp(self.decoders[region_index], cache, g_condition, target, want_input=False)
+
+    def initial_cached(self, pooled: torch.Tensor):
+        return head_forward_cached(self.initial_encoder, pooled)
+
+    def initial_parameter_vjp(self, cache, g_state: torch.Tensor, target, want_input: bool = False):
+        return head_parameter_vjp(self.initial_encoder, cache, g_state, target, want_input=want_input)
+
+    def update_cached(self, state: torch.Tensor, pooled: torch.Tensor, region_index: int):
+        """``update_from_pooled`` without autograd -> (InterfaceStep, encoder cache)."""
+        delta, enc_cache = head_forward_cached(self.encoders[region_index], pooled)
+        scale = torch.tanh(self.update_scale.detach()[region_index])
+        pre_norm = state.float() + scale * delta
+        norm = self.norms[region_index]
+        out = F.layer_norm(pre_norm, (pre_norm.shape[-1],), None if norm.weight is None else norm.weight.detach().float(),
+                           None if norm.bias is None else norm.bias.detach().float(), norm.eps)
+        step = InterfaceStep(state=out, diagnostics={"pooled_features": pooled, "delta_state": delta, "update_scale": scale,
+                                                     "pre_norm_state": pre_norm})
+        return step, enc_cache
+
+    def update_parameter_vjp(self, region_index: int, diagnostics: dict, enc_cache, g_state_out: torch.Tensor, target) -> torch.Tensor:
+        """Cotangent of the outgoing state [B, R] -> cotangent of the pooled region output [B, D]; the gradients of the
+        encoder, the LayerNorm and ``update_scale[region_index]`` are added into ``target(param)``.  ``enc_cache`` may be
+        None (a fused forward kept no pre-activations): the encoder is then re-evaluated at the pooled features."""
+        if enc_cache is None:
+            _, enc_cache = head_forward_cached(self.encoders[region_index], diagnostics["pooled_features"])
+        g_pre = layer_norm_parameter_vjp(self.norms[region_index], diagnostics["pre_norm_state"], g_state_out, target)
+        scale = diagnostics["update_scale"].float()
+        g_scale = (g_pre * diagnostics["delta_state"].float()).sum()
+        target(self.update_scale)[region_index] += g_scale * (1.0 - scale * scale)
+        return head_parameter_vjp(self.encoders[region_index], enc_cache, g_pre * scale, target, want_input=True)
 
     # ---- structured reverse-mode pieces -------------------------------------------------
     def update_jacobian_t(self, region_index: int, diagnostics: dict, g_state_out: torch.Tensor, seq_len: int) -> dict:

@@ -12,7 +12,13 @@ import torch
 from torch import nn
 
 from ..backbones.general import BackboneSpec, apply_backbone_init, build_backbone_stack, init_transformer_module, make_final_norm
-from ..interfaces.vector_mlp import LegacyVectorMLPInterfaceView, VectorMLPHead
+from ..interfaces.vector_mlp import (
+    LegacyVectorMLPInterfaceView,
+    VectorMLPHead,
+    head_input_jacobian_t,
+    layer_norm_input_jacobian_t,
+    mean_pool_jacobian_t,
+)
 from ..models.region_plan import RegionPlan, build_region_ranges
 
 RegionMessageHead = VectorMLPHead
@@ -136,3 +142,120 @@ class NativeRegionInterfaceModel(nn.Module):
 
     def forward(self, input_ids: torch.Tensor, **kwargs) -> torch.Tensor:
         return self.forward_with_cache(input_ids, **kwargs)[0]
+
+    # ---- closed-form pieces of the region-local pullback (reference legacy/native_region_interface.py:399-457; there the
+    # LayerNorm factor is an autograd call on a replicated batch, here every factor is closed-form)
+    def region_message_output_pullback_to_hidden_output(self, region_cache: RegionForwardCache, g_message_out: torch.Tensor) -> dict:
+        """Cotangents of the outgoing message [B, P, R] -> the skip path to the incoming message and the cotangents of the
+        region's hidden output [B, P, L, D] (through LayerNorm, the update scale, the encoder head and the token mean)."""
+        if g_message_out.dim() != 3:
+            raise ValueError("g_message_out must have shape [B, P, R]")
+        ridx = region_cache.region_idx
+        g_pre = layer_norm_input_jacobian_t(self.message_norm[ridx], region_cache.pre_norm_message.detach(), g_message_out)
+        g_delta = g_pre * region_cache.alpha.detach().to(g_pre.dtype)
+        g_pooled = head_input_jacobian_t(self.hidden_to_message[ridx], region_cache.pooled_hidden.detach(), g_delta)
+        return {"g_pre_norm_message": g_pre, "g_message_skip": g_pre, "g_delta_message": g_delta, "g_pooled_hidden": g_pooled,
+                "g_hidden_output": mean_pool_jacobian_t(g_pooled, region_cache.hidden_output.shape[1])}
+
+    def region_hidden_input_pullback_to_message_input(self, region_cache: RegionForwardCache, g_hidden_input: torch.Tensor) -> dict:
+        """Cotangents of the region's hidden input [B, P, L, D] -> cotangents of the incoming message (token sum, decoder head)."""
+        if g_hidden_input.dim() != 4:
+            raise ValueError("g_hidden_input must have shape [B, P, L, D]")
+        g_bias = g_hidden_input.sum(dim=2)
+        g_message = head_input_jacobian_t(self.message_to_hidden[region_cache.region_idx], region_cache.message_in.detach(), g_bias)
+        return {"g_hidden_bias": g_bias, "g_message_input": g_message}
+
+    def region_outer_message_input_pullback(self, region_cache: RegionForwardCache, g_message_out: torch.Tensor,
+                                            g_hidden_input: torch.Tensor) -> dict:
+        tail = self.region_message_output_pullback_to_hidden_output(region_cache, g_message_out)
+        head = self.region_hidden_input_pullback_to_message_input(region_cache, g_hidden_input)
+        return {**tail, **head, "g_message_input_total": tail["g_message_skip"] + head["g_message_input"]}
+
+    # ---- message-chain VJPs: sequential reference, Jacobian materialisers, suffix scan (reference :459-694)
+    def interface_vjp_chain(self, cache: dict[str, Any], g_top_message: torch.Tensor) -> list[torch.Tensor]:
+        """Sequential pullback of the top message cotangent through the retained graph, one region at a time."""
+        messages = cache["region_messages"]
+        if len(messages) != self.n_regions + 1:
+            raise ValueError("cache has an invalid region_messages length")
+        if cache.get("detached_states"):
+            raise ValueError("interface_vjp_chain needs a connected graph (forward_with_cache without detach_states)")
+        g = [torch.zeros_like(messages[0]) for _ in range(self.n_regions + 1)]
+        g[-1] = g_top_message
+        for ridx in reversed(range(self.n_regions)):
+            (g[ridx],) = torch.autograd.grad(messages[ridx + 1], messages[ridx], g[ridx + 1], retain_graph=True)
+        return g
+
+    def materialize_interface_pullback_mats(self, cache: dict[str, Any], *, mode: str = "graph", basis_chunk: int = 1) -> list[torch.Tensor]:
+        """A_k^T [B, R, R] for every region (g_k = A_k^T g_{k+1}); ``graph`` differentiates the retained forward graph,
+        ``recompute`` re-runs each region's message map on a basis-replicated batch, ``basis_chunk`` directions at a time."""
+        from ..backward.pullbacks import build_interface_pullback_provider
+
+        if mode not in ("graph", "recompute"):
+            raise ValueError("interface Jacobian mode must be one of: graph, recompute")
+        if mode == "recompute":
+            return self._materialize_recompute(cache, int(basis_chunk))
+        return build_interface_pullback_provider("graph").materialize_state_jacobian_t(model=self, cache=cache)
+
+    def _materialize_recompute(self, cache: dict[str, Any], basis_chunk: int) -> list[torch.Tensor]:
+        if basis_chunk <= 0:
+            raise ValueError("basis_chunk must be > 0")
+        out = []
+        for ridx, rc in enumerate(cache["region_caches"]):
+            m_in, x_static = rc.message_in.detach(), rc.x_static.detach()
+            bsz, r = m_in.shape
+            cols = []
+            for j0 in range(0, r, basis_chunk):
+                c = min(basis_chunk, r - j0)
+                m_rep = m_in.repeat_interleave(c, dim=0).requires_grad_(True)
+                with torch.enable_grad():
+                    m_next = self._forward_region_message_map(ridx, x_static.repeat_interleave(c, dim=0), m_rep)
+                basis = torch.zeros(bsz, c, r, device=m_in.device, dtype=m_next.dtype)
+                basis[:, torch.arange(c), j0 + torch.arange(c)] = 1.0
+                (g,) = torch.autograd.grad(m_next, m_rep, basis.reshape(bsz * c, r))
+                cols.append(g.reshape(bsz, c, r))
+            out.append(torch.cat(cols, dim=1).transpose(1, 2).contiguous())
+        return out
+
+    def compose_pullback_suffix(self, interface_pullback_mats) -> list[torch.Tensor]:
+        """Suffix products S_k = A_k^T A_{k+1}^T ... (S_K = I), one [B, R, R] per message index."""
+        from ..ops import suffix_scan_pullbacks
+
+        mats = list(interface_pullback_mats)
+        if not mats:
+            return []
+        if any(m.dim() != 3 or m.shape[-1] != m.shape[-2] for m in mats):
+            raise ValueError("interface pullback matrices must be square [B, R, R]")
+        suffix = suffix_scan_pullbacks(torch.stack(mats, dim=1))
+        if suffix.shape[1] != len(mats) + 1:
+            raise ValueError("suffix scan returned an unexpected shape")
+        return [suffix[:, k].contiguous() for k in range(len(mats) + 1)]
+
+    @staticmethod
+    def _apply_pullback_mat(mat: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+        dtype = torch.promote_types(mat.dtype, vec.dtype)
+        return torch.einsum("bij,bj->bi", mat.to(dtype), vec.to(dtype)).to(vec.dtype)
+
+    def interface_vjp_scan_from_mats(self, interface_pullback_mats, g_top_message: torch.Tensor) -> list[torch.Tensor]:
+        """Every message cotangent g_k = S_k g_K from the materialised A_k^T and the cotangent of the last message."""
+        suffix = self.compose_pullback_suffix(interface_pullback_mats)
+        if len(suffix) != self.n_regions + 1:
+            raise ValueError("suffix length mismatch")
+        return [self._apply_pullback_mat(s, g_top_message) for s in suffix]
+
+    def interface_vjp_scan(self, cache: dict[str, Any], g_top_message: torch.Tensor, *, mode: str = "graph",
+                           basis_chunk: int = 1) -> list[torch.Tensor]:
+        return self.interface_vjp_scan_from_mats(self.materialize_interface_pullback_mats(cache, mode=mode, basis_chunk=basis_chunk),
+                                                 g_top_message)
+
+    def interface_vjp_scan_from_last_input_seed(self, interface_pullback_mats, g_last_input_message: torch.Tensor) -> list[torch.Tensor]:
+        """The loss reads only the last region, so its cotangent enters at the last region's *incoming* message: cotangents
+        of messages 0 .. K - 1 from A_0^T .. A_{K-2}^T seeded there."""
+        mats = list(interface_pullback_mats)
+        if len(mats) != self.n_regions:
+            raise ValueError("interface_pullback_mats length mismatch")
+        if self.n_regions == 0:
+            return []
+        if self.n_regions == 1:
+            return [g_last_input_message]
+        suffix = self.compose_pullback_suffix(mats[:-1])
+        return [self._apply_pullback_mat(s, g_last_input_message) for s in suffix]

@@ -56,6 +56,9 @@ def flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, sca
         KERNEL_LAUNCHES["count"] += 1
         out, lse = ext().attn_fwd_packed(qkv, batch, seq_len, n_heads, head_dim, float(scale))
         return out, lse
+    from .dispatch import fell_back
+
+    fell_back("attention_fwd (flash_attn library)", qkv, why=f"head_dim {head_dim}, heads {n_heads}/{n_kv_heads}, seq_len {seq_len}")
     q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
     out, lse, _, _ = _flash()._flash_attn_forward(q, k, v, 0.0, float(scale), True, -1, -1, 0.0, None, False)
     return out.reshape(batch * seq_len, n_heads * head_dim), lse
@@ -78,6 +81,10 @@ def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, h
             return ext().attn_pullback_packed(do_rows.contiguous(), qkv, o, lse, batch, seq_len, n_heads, head_dim, float(scale))
         return ext().attn_pullback_packed(do_rows.contiguous(), qkv, o, lse, batch, seq_len, n_heads, head_dim, float(scale),
                                           rope[0], rope[1], bool(rope[2]))
+    from .dispatch import fell_back
+
+    fell_back("attention_pullback (flash_attn library loop)", do_rows,
+              why=f"head_dim {head_dim}, heads {n_heads}/{n_kv_heads}, seq_len {seq_len}, dtype {do_rows.dtype}")
     q, k, v = _views(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim)
     out4 = o.view(batch, seq_len, n_heads, head_dim)
     d_qkv = torch.empty(nbasis * n, qkv_dim, dtype=do_rows.dtype, device=do_rows.device)

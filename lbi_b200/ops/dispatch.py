@@ -17,6 +17,30 @@ from .native import ext, native_available
 KERNEL_LAUNCHES = {"count": 0}
 _LOWP = (torch.bfloat16, torch.float16)
 
+# Routes that leave the sm_100a kernels for CUDA bf16 tensors (an odd shape, a missing entry point, an environment
+# switch) are counted per op, so that a run cannot lose its kernels unnoticed; with LBI_B200_STRICT=1 (or
+# ``set_strict(True)``) such a route raises instead.  CPU tensors and fp32 activations are not fallbacks: the PyTorch
+# statements are their intended path.
+FALLBACKS: dict[str, int] = {}
+STRICT = {"enabled": os.environ.get("LBI_B200_STRICT", "0") == "1"}
+
+
+def set_strict(enabled: bool) -> bool:
+    """Turn strict mode on or off; returns the previous setting."""
+    prev = STRICT["enabled"]
+    STRICT["enabled"] = bool(enabled)
+    return prev
+
+
+def fell_back(op: str, *values, why: str = "") -> None:
+    """Record that ``op`` is about to run library / PyTorch code; counts (and in strict mode refuses) CUDA bf16 operands."""
+    if not any(isinstance(t, torch.Tensor) and t.is_cuda and t.dtype == torch.bfloat16 for t in values):
+        return
+    FALLBACKS[op] = FALLBACKS.get(op, 0) + 1
+    if STRICT["enabled"]:
+        shapes = [tuple(t.shape) for t in values if isinstance(t, torch.Tensor)]
+        raise RuntimeError(f"strict mode: {op} would leave the sm_100a kernels for CUDA bf16 operands {shapes}" + (f" ({why})" if why else ""))
+
 
 def _count(n: int = 1) -> None:
     KERNEL_LAUNCHES["count"] += n
@@ -31,6 +55,7 @@ def add_rmsnorm_fwd(branch, stream, weight, eps, out_dtype):
     if _native(branch, stream, weight) and out_dtype == torch.bfloat16 and branch.shape[-1] % 8 == 0:
         _count()
         return ext().add_rmsnorm_fwd(branch.contiguous(), stream, weight.contiguous(), float(eps))
+    fell_back("add_rmsnorm_fwd", branch, stream, weight, eps, out_dtype)
     return ref.add_rmsnorm_fwd(branch, stream, weight, eps, out_dtype)
 
 
@@ -44,6 +69,7 @@ def rmsnorm_bwd(d_normed, stream, rstd, weight, d_stream=None, lowp_dtype=None):
         _count()
         out = ext().rmsnorm_bwd(d_normed.contiguous(), stream, rstd, weight.contiguous(), d_stream)
     else:
+        fell_back("rmsnorm_bwd", d_normed)
         out = ref.rmsnorm_bwd(d_normed, stream, rstd, weight, d_stream)
     return out if lowp_dtype is None else (out, out.to(lowp_dtype))
 
@@ -52,6 +78,7 @@ def rmsnorm_wgrad(d_normed, stream, rstd):
     if _native(d_normed, stream, rstd) and d_normed.dtype == torch.bfloat16 and d_normed.shape[-1] % 8 == 0:
         _count(2)
         return ext().rmsnorm_wgrad(d_normed.contiguous(), stream, rstd)
+    fell_back("rmsnorm_wgrad", d_normed, stream, rstd)
     return ref.rmsnorm_wgrad(d_normed, stream, rstd)
 
 
@@ -111,6 +138,7 @@ def gemm_tn(a, b, out_dtype=torch.bfloat16, accumulate_into=None):
     if _gemm_ok(a, b) and (out_dtype in (torch.bfloat16, torch.float32)):
         _count()
         return ext().gemm_tn(a, b, out_dtype == torch.float32, accumulate_into)
+    fell_back("gemm_tn", a, b)
     c = (a.float() @ b.float().t()) if out_dtype == torch.float32 else (a @ b.t().to(a.dtype))
     if accumulate_into is not None:
         accumulate_into.add_(c.to(accumulate_into.dtype))
@@ -121,6 +149,7 @@ def gemm_tn(a, b, out_dtype=torch.bfloat16, accumulate_into=None):
 def linear_fwd(x, w, bias=None):
     if bias is None and _gemm_ok(x, w):
         return gemm_tn(x, w)
+    fell_back("linear_fwd", x, w, bias)
     return ref.linear_fwd(x, w, bias)
 
 
@@ -140,6 +169,7 @@ def linear_dgrad(dy, w, w_t=None):
         return ext().gemm(dy, w, False, True, False, None, 1)
     if w_t is not None and _gemm_ok(dy, w_t):
         return gemm_tn(dy, w_t)
+    fell_back("linear_dgrad", dy, w)
     return ref.linear_dgrad(dy, w)
 
 
@@ -155,6 +185,7 @@ def linear_wgrad(dy, x, accumulate_into=None):
         x_t = transpose_2d(x)
         if _gemm_ok(dy_t, x_t):
             return gemm_tn(dy_t, x_t, out_dtype=torch.float32, accumulate_into=accumulate_into)
+    fell_back("linear_wgrad", dy, x)
     dw = ref.linear_wgrad(dy, x)
     if accumulate_into is not None:
         accumulate_into.add_(dw)
@@ -166,6 +197,7 @@ def transpose_2d(x):
     if _native(x) and x.dtype == torch.bfloat16 and x.is_contiguous() and hasattr(ext(), "transpose_bf16"):
         _count()
         return ext().transpose_bf16(x)
+    fell_back("transpose_2d", x)
     return x.t().contiguous()
 
 
@@ -174,6 +206,7 @@ def rope_qkv(qkv, cos, sin, n_heads, n_kv_heads, head_dim, seq_len, interleaved=
     if _native(qkv, cos, sin) and qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and head_dim % 2 == 0:
         _count()
         return ext().rope_qkv_(qkv, cos, sin, n_heads, n_kv_heads, head_dim, seq_len, bool(interleaved), bool(inverse))
+    fell_back("rope_qkv", qkv, cos, sin, n_heads, n_kv_heads, head_dim, seq_len, interleaved, inverse)
     return ref.rope_qkv(qkv, cos, sin, n_heads, n_kv_heads, head_dim, seq_len, interleaved, inverse)
 
 
@@ -183,6 +216,7 @@ def attention_fwd(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale):
         from .attention import flash_forward_packed
 
         return flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
+    fell_back("attention_fwd", qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
     return ref.attention_fwd(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
 
 
@@ -192,6 +226,7 @@ def attention_pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_k
         from .attention import pullback_packed
 
         return pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, rope=rope)
+    fell_back("attention_pullback_packed", do_rows)
     d_qkv = ref.attention_pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, head_dim, scale)
     if rope is not None:
         d_qkv = rope_qkv(d_qkv, rope[0], rope[1], n_heads, n_kv_heads, head_dim, seq_len, rope[2], inverse=True)
@@ -208,6 +243,7 @@ def swiglu_fwd(u):
     if _native(u) and u.dtype == torch.bfloat16 and u.is_contiguous() and (u.shape[-1] // 2) % 8 == 0:
         _count()
         return ext().swiglu_fwd(u)
+    fell_back("swiglu_fwd", u)
     return ref.swiglu_fwd(u)
 
 
@@ -215,6 +251,7 @@ def swiglu_bwd(da, u):
     if _native(da, u) and da.dtype == torch.bfloat16 and u.dtype == torch.bfloat16 and da.is_contiguous() and da.shape[-1] % 8 == 0:
         _count()
         return ext().swiglu_bwd(da, u)
+    fell_back("swiglu_bwd", da, u)
     return ref.swiglu_bwd(da, u)
 
 
@@ -223,6 +260,7 @@ def causal_conv_fwd(x, weight, bias, batch, seq_len):
     if _native(x, weight, bias) and x.dtype == torch.bfloat16 and hasattr(ext(), "causal_conv_fwd"):
         _count()
         return ext().causal_conv_fwd(x.contiguous(), weight.float().contiguous(), bias, batch, seq_len)
+    fell_back("causal_conv_fwd", x, weight, bias, batch, seq_len)
     return ref.causal_conv_fwd(x, weight, bias, batch, seq_len)
 
 
@@ -230,10 +268,12 @@ def causal_conv_dgrad(dy, weight, batch, seq_len):
     if _native(dy, weight) and dy.dtype == torch.bfloat16 and hasattr(ext(), "causal_conv_dgrad"):
         _count()
         return ext().causal_conv_dgrad(dy.contiguous(), weight.float().contiguous(), batch, seq_len)
+    fell_back("causal_conv_dgrad", dy, weight, batch, seq_len)
     return ref.causal_conv_dgrad(dy, weight, batch, seq_len)
 
 
 def causal_conv_wgrad(dy, x, width, batch, seq_len):
+    fell_back("causal_conv_wgrad", dy, x, width, batch, seq_len)
     return ref.causal_conv_wgrad(dy, x, width, batch, seq_len)
 
 
@@ -244,6 +284,7 @@ def lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight=True
         from .cross_entropy import fused_lm_head_ce
 
         return fused_lm_head_ce(normed, weight, targets, loss_scale, want_dweight, weight_t, dweight_into)
+    fell_back("lm_head_cross_entropy", normed, weight, targets, loss_scale, want_dweight, dweight_into)
     return ref.lm_head_cross_entropy(normed, weight, targets, loss_scale, want_dweight, dweight_into)
 
 
@@ -252,6 +293,7 @@ def embedding_fwd(ids, table, out_dtype):
     if _native(ids, table) and out_dtype == torch.bfloat16 and table.dtype in (torch.bfloat16, torch.float32) and table.shape[1] % 8 == 0:
         _count()
         return ext().embedding_fwd(ids.reshape(-1).contiguous(), table)
+    fell_back("embedding_fwd", ids, table, out_dtype)
     return ref.embedding_fwd(ids, table, out_dtype)
 
 
@@ -260,6 +302,7 @@ def embedding_scatter_add(d_table, ids, d_rows):
         _count()
         ext().embedding_scatter_add_(d_table, ids.reshape(-1).contiguous(), d_rows.contiguous())
         return d_table
+    fell_back("embedding_scatter_add", d_table, ids, d_rows)
     return ref.embedding_scatter_add(d_table, ids, d_rows)
 
 
@@ -268,6 +311,7 @@ def add_condition(canvas_rows, cond, seq_len):
     if _native(canvas_rows, cond) and canvas_rows.dtype == torch.bfloat16 and canvas_rows.shape[-1] % 8 == 0:
         _count()
         return ext().add_condition(canvas_rows.contiguous(), cond.float().contiguous(), seq_len)
+    fell_back("add_condition", canvas_rows, cond, seq_len)
     return ref.add_condition(canvas_rows, cond, seq_len)
 
 
@@ -275,6 +319,7 @@ def mean_pool_tokens(rows, batch, seq_len):
     if _native(rows) and rows.dtype in (torch.float32, torch.bfloat16) and rows.is_contiguous():
         _count()
         return ext().pool_tokens(rows, batch, seq_len, 1.0 / float(seq_len))
+    fell_back("mean_pool_tokens", rows, batch, seq_len)
     return ref.mean_pool_tokens(rows, batch, seq_len)
 
 
@@ -282,6 +327,7 @@ def sum_tokens(rows, groups, seq_len):
     if _native(rows) and rows.dtype in (torch.float32, torch.bfloat16) and rows.is_contiguous():
         _count()
         return ext().pool_tokens(rows, groups, seq_len, 1.0)
+    fell_back("sum_tokens", rows, groups, seq_len)
     return ref.sum_tokens(rows, groups, seq_len)
 
 
@@ -290,6 +336,7 @@ def suffix_scan_pullbacks(mats):
     if _native(mats) and mats.dim() == 4 and mats.shape[1] > 0 and mats.shape[-1] <= 256:
         _count()
         return ext().suffix_scan(mats.contiguous())
+    fell_back("suffix_scan_pullbacks", mats)
     return ref.suffix_scan_pullbacks(mats)
 
 
@@ -297,6 +344,7 @@ def affine_suffix_scan(mats, offsets, seed=None):
     if _native(mats, offsets, seed) and mats.shape[1] > 0 and mats.shape[-1] <= 1024:
         _count()
         return ext().affine_suffix_scan(mats.float().contiguous(), offsets.float().contiguous(), None if seed is None else seed.float().contiguous())
+    fell_back("affine_suffix_scan", mats, offsets, seed)
     return ref.affine_suffix_scan(mats, offsets, seed)
 
 
@@ -308,4 +356,5 @@ def adamw_step(param, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_d
                           float(weight_decay), int(step), grad_scale)
         return param
     gs = float(grad_scale) if not torch.is_tensor(grad_scale) else grad_scale
+    fell_back("adamw_step", param, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, gs, shadow)
     return ref.adamw_step(param, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, gs, shadow)

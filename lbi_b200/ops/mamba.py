@@ -315,8 +315,64 @@ def softplus_dt_fwd(dt_raw, dt_bias, lo: float, hi: float):
     return dt, slope
 
 
-def silu_fwd(x):
-    return F.silu(x.float()).to(x.dtype)
+def conv_silu_fwd(x, weight, bias, batch: int, seq_len: int, parts: tuple[int, int, int]):
+    """Depthwise causal conv + SiLU over x [n, C]; weight [C, W] fp32 -> (pre-activation [n, C], the three parts of the
+    activation as contiguous tensors [n, parts[i]])."""
+    from . import reference as ref
+
+    if (_kernel_ok(x, weight, bias, name="conv_silu_fwd") and x.dtype == torch.bfloat16 and all(p % 8 == 0 for p in parts)
+            and weight.shape[1] <= 8):
+        _count()
+        pre, o0, o1, o2 = ext().conv_silu_fwd(x.contiguous(), weight.float().contiguous(), None if bias is None else bias.float().contiguous(),
+                                              int(seq_len), *map(int, parts))
+        return pre, (o0, o1, o2)
+    from .dispatch import fell_back
+
+    fell_back("conv_silu_fwd", x)
+    pre = ref.causal_conv_fwd(x, weight, bias, batch, seq_len)
+    act = F.silu(pre.float()).to(x.dtype)
+    return pre, tuple(t.contiguous() for t in torch.split(act, list(parts), dim=-1))
+
+
+def conv_silu_bwd(d_parts, pre, weight, batch: int, seq_len: int, out: torch.Tensor, col0: int) -> None:
+    """Cotangents of the three activation parts ([P * n, parts[i]]) -> cotangent of the conv input, written into
+    ``out[:, col0 : col0 + C]``; pre [n, C] is shared by the P directions."""
+    from . import reference as ref
+
+    channels = pre.shape[1]
+    if (_kernel_ok(*d_parts, pre, out, name="conv_silu_bwd_") and pre.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+            and all(d.shape[1] % 8 == 0 for d in d_parts) and col0 % 8 == 0 and weight.shape[1] <= 8 and out.is_contiguous()):
+        _count()
+        d0 = d_parts[0].contiguous()
+        d12 = torch.float32 if (d_parts[1].dtype == torch.float32 or d_parts[2].dtype == torch.float32) else torch.bfloat16
+        ext().conv_silu_bwd_(d0 if d0.dtype in (torch.float32, torch.bfloat16) else d0.float(), d_parts[1].to(d12).contiguous(),
+                             d_parts[2].to(d12).contiguous(), pre.contiguous(), weight.float().contiguous(), out, int(col0), int(seq_len))
+        return
+    from .dispatch import fell_back
+
+    fell_back("conv_silu_bwd", pre)
+    reps = d_parts[0].shape[0] // pre.shape[0]
+    d_act = torch.cat([d.float() for d in d_parts], dim=-1)
+    d_pre = silu_bwd(d_act, pre)
+    out[:, col0 : col0 + channels] = ref.causal_conv_dgrad(d_pre, weight, reps * batch, seq_len).to(out.dtype)
+
+
+def conv_silu_wgrad(d_parts, pre, x, width: int, batch: int, seq_len: int):
+    """-> (dweight [C, W], dbias [C]) fp32 for one direction."""
+    from . import reference as ref
+
+    if (_kernel_ok(*d_parts, pre, x, name="conv_silu_wgrad") and pre.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+            and all(d.shape[1] % 8 == 0 for d in d_parts) and width <= 8):
+        _count()
+        d12 = torch.float32 if (d_parts[1].dtype == torch.float32 or d_parts[2].dtype == torch.float32) else torch.bfloat16
+        d0 = d_parts[0].contiguous()
+        return ext().conv_silu_wgrad(d0 if d0.dtype in (torch.float32, torch.bfloat16) else d0.float(), d_parts[1].to(d12).contiguous(),
+                                     d_parts[2].to(d12).contiguous(), pre.contiguous(), x.contiguous(), int(width), int(seq_len))
+    from .dispatch import fell_back
+
+    fell_back("conv_silu_wgrad", pre)
+    d_pre = silu_bwd(torch.cat([d.float() for d in d_parts], dim=-1), pre)
+    return ref.causal_conv_wgrad(d_pre, x, width, batch, seq_len)
 
 
 def silu_bwd(dy, x):

@@ -45,6 +45,8 @@ class RegionRecord:
     normed: torch.Tensor | None = None
     d_out_loss: torch.Tensor | None = None
     state_out: torch.Tensor | None = None
+    dec_cache: Any = None   # decoder pre-activations (interface parameter VJP)
+    enc_cache: Any = None   # encoder pre-activations; None after the fused update kernel (re-evaluated in the VJP)
 
 
 @dataclass
@@ -164,7 +166,7 @@ class FastLBIEngine:
                 pooled0 = torch.zeros(bsz, dim, dtype=torch.float32, device=self.device)
             else:
                 pooled0 = ops.mean_pool_tokens(full_canvas, bsz, seqlen)
-            state = iface.initial_encoder(pooled0).float()
+            state, self.last["init_cache"] = iface.initial_cached(pooled0)
             self.last["pooled0"] = pooled0
         else:
             like = torch.empty(bsz, model.interface_width, dtype=torch.float32, device=self.device)
@@ -176,11 +178,11 @@ class FastLBIEngine:
             t_len = t1 - t0
             region_ids = ids[:, t0:t1].contiguous() if sequence_axis else ids
             canvas_rows = ops.embedding_fwd(region_ids, table, self.act_dtype) if sequence_axis else full_canvas
-            cond = iface.decode(state, k).float()
+            cond, dec_cache = iface.decode_cached(state, k)
             x_in = ops.add_condition(canvas_rows, cond, t_len)
             _, cache = self.structured.forward(x_in.view(bsz, t_len, dim), model.region_ranges[k], materialize_output=False)
             rec = RegionRecord(index=k, token_range=(t0, t1), state_in=state, pooled=None, diagnostics={}, cache=cache,
-                               ids=region_ids)
+                               ids=region_ids, dec_cache=dec_cache)
             if model.plan.region_has_loss(k):
                 normed, out, rstd = ops.add_rmsnorm_fwd(cache.last_branch, cache.last_stream, final_w, final_eps, self.act_dtype)
                 pooled = ops.mean_pool_tokens(out, bsz, t_len)
@@ -202,7 +204,7 @@ class FastLBIEngine:
                     iface, k, state, pooled, self.placement.owner(k + 1) if remote else None)
                 rec.pooled, rec.diagnostics, rec.state_out = pooled, diagnostics, new_state
             else:
-                step = iface.update_from_pooled(state, pooled, k)
+                step, rec.enc_cache = iface.update_cached(state, pooled, k)
                 rec.pooled, rec.diagnostics, rec.state_out = pooled, step.diagnostics, step.state.float()
                 if remote:
                     comm.handoff_send(rec.state_out, self.placement.owner(k + 1), slot=k + 1)
@@ -292,7 +294,7 @@ class FastLBIEngine:
         region_ids = ids[:, t0:t1].contiguous()
         table = self._w(model.canvas.embedding.weight)
         canvas_rows = ops.embedding_fwd(region_ids, table, self.act_dtype)
-        x_in = ops.add_condition(canvas_rows, iface.decode(state, k).float(), t_len)
+        x_in = ops.add_condition(canvas_rows, iface.decode_cached(state, k)[0], t_len)
         _, cache = self.structured.forward(x_in.view(bsz, t_len, dim), model.region_ranges[k], materialize_output=False)
         if model.plan.region_has_loss(k):
             _, out, _ = ops.add_rmsnorm_fwd(cache.last_branch, cache.last_stream, model.readout.norm.weight, model.readout.norm.eps,
@@ -302,7 +304,7 @@ class FastLBIEngine:
             pooled = ops.mean_pool_tokens(cache.last_branch, bsz, t_len)
             if cache.last_stream is not None:
                 pooled = pooled + ops.mean_pool_tokens(cache.last_stream, bsz, t_len)
-        step = iface.update_from_pooled(state, pooled, k)
+        step, _ = iface.update_cached(state, pooled, k)
         return RegionRecord(index=k, token_range=(t0, t1), state_in=state, pooled=pooled, diagnostics=step.diagnostics, cache=cache,
                             ids=region_ids)
 
@@ -379,6 +381,7 @@ class FastLBIEngine:
         return g[:, :k_regions]
 
     # ------------------------------------------------------------------ local VJPs
+    @torch.no_grad()
     def _backward_region(self, rec: RegionRecord, g_next: torch.Tensor | None) -> None:
         model, iface = self.model, self.model.interface
         k = rec.index
@@ -387,43 +390,28 @@ class FastLBIEngine:
         dim = model.hidden_dim
         cot = rec.d_out_loss
         if g_next is not None:
-            enc_params = [*iface.encoders[k].parameters(), *iface.norms[k].parameters(), iface.update_scale]
-            with torch.enable_grad():
-                pooled_leaf = rec.pooled.detach().clone().requires_grad_(True)
-                step = iface.update_from_pooled(rec.state_in.detach(), pooled_leaf, k)
-                grads = torch.autograd.grad(step.state, [pooled_leaf, *enc_params], g_next.to(step.state.dtype), allow_unused=True)
-            self._acc_grads(enc_params, grads[1:])
-            spread = (grads[0].float() / float(t_len)).unsqueeze(1)  # [B, 1, D] broadcast over tokens
-            with torch.no_grad():
-                if cot is None:
-                    cot = spread.expand(bsz, t_len, dim).reshape(bsz * t_len, dim).contiguous()
-                else:
-                    cot.view(bsz, t_len, dim).add_(spread)
+            g_pooled = iface.update_parameter_vjp(k, rec.diagnostics, rec.enc_cache, g_next, self._g)
+            spread = (g_pooled.float() / float(t_len)).unsqueeze(1)  # [B, 1, D] broadcast over tokens
+            if cot is None:
+                cot = spread.expand(bsz, t_len, dim).reshape(bsz * t_len, dim).contiguous()
+            else:
+                cot.view(bsz, t_len, dim).add_(spread)
         if cot is None:
             return
-        with torch.no_grad():
-            d_in = self.structured.backward(self._cache_of(rec), cot, self)
-            d_cond = ops.sum_tokens(d_in, bsz, t_len)
-            ops.embedding_scatter_add(self._g(model.canvas.embedding.weight), rec.ids, d_in)
-        dec_params = list(iface.decoders[k].parameters())
-        with torch.enable_grad():
-            cond = iface.decode(rec.state_in.detach(), k)
-            grads = torch.autograd.grad(cond, dec_params, d_cond.to(cond.dtype), allow_unused=True)
-        self._acc_grads(dec_params, grads)
+        d_in = self.structured.backward(self._cache_of(rec), cot, self)
+        d_cond = ops.sum_tokens(d_in, bsz, t_len)
+        ops.embedding_scatter_add(self._g(model.canvas.embedding.weight), rec.ids, d_in)
+        iface.decode_parameter_vjp(k, rec.dec_cache, d_cond, self._g)
 
+    @torch.no_grad()
     def _backward_initial(self, ids: torch.Tensor, g0: torch.Tensor) -> None:
         model, iface = self.model, self.model.interface
-        params = list(iface.initial_encoder.parameters())
-        with torch.enable_grad():
-            pooled_leaf = self.last["pooled0"].detach().clone().requires_grad_(True)
-            s0 = iface.initial_encoder(pooled_leaf)
-            grads = torch.autograd.grad(s0, [pooled_leaf, *params], g0.to(s0.dtype), allow_unused=True)
-        self._acc_grads(params, grads[1:])
-        if model.region_axis == "depth" and grads[0] is not None:
+        depth = model.region_axis == "depth"
+        g_pooled = iface.initial_parameter_vjp(self.last["init_cache"], g0, self._g, want_input=depth)
+        if depth and g_pooled is not None:
             bsz, seqlen = ids.shape
-            with torch.no_grad():
-                rows = (grads[0].float() / float(seqlen)).unsqueeze(1).expand(bsz, seqlen, -1).reshape(bsz * seqlen, -1).contiguous()
-                ops.embedding_scatter_add(self._g(model.canvas.embedding.weight), ids, rows)
+            rows = (g_pooled.float() / float(seqlen)).unsqueeze(1).expand(bsz, seqlen, -1).reshape(bsz * seqlen, -1).contiguous()
+            ops.embedding_scatter_add(self._g(model.canvas.embedding.weight), ids, rows)
 
     # ------------------------------------------------------------------ optimizer
     @torch.no_grad()

@@ -113,3 +113,38 @@ def test_bench_paths_run_on_tiny_configs(config):
     assert math.isfinite(out["final_loss"]) and out["value"] > 0
     assert out["gpu_launches"] > 0 and out["kernel_status"] == 0
     assert out["e2e"]["value"] > 0 and out["e2e"]["h2d_bytes_per_step"] > 0
+
+
+@pytest.mark.parametrize("kind", ["transformer", "mamba3", "mamba2", "hybrid"])
+def test_engine_step_never_leaves_the_kernels_in_strict_mode(kind):
+    """With strict mode on, any route to PyTorch / cuBLAS / flash_attn for a CUDA bf16 tensor raises: a full training step
+    of every backbone must pass, and the fallback counters must stay empty."""
+    from lbi_b200 import ops
+
+    model = (_model("sequence", 2, True) if kind == "transformer" else _mamba_model(kind)).cuda()
+    prev = ops.dispatch.set_strict(True)
+    ops.dispatch.FALLBACKS.clear()
+    try:
+        engine = FastLBIEngine(model, lr=1e-3, basis_chunk=8)
+        ids, tgt = torch.randint(0, 1024, (2, 512), device="cuda"), torch.randint(0, 1024, (2, 512), device="cuda")
+        loss = engine.step(ids, tgt)
+        assert torch.isfinite(loss)
+    finally:
+        ops.dispatch.set_strict(prev)
+    assert ops.dispatch.FALLBACKS == {}
+
+
+def test_strict_mode_refuses_a_library_route():
+    from lbi_b200 import ops
+
+    x = torch.randn(64, 100, device="cuda").bfloat16()      # K = 100 is not a multiple of 8: no kernel route
+    w = torch.randn(32, 100, device="cuda").bfloat16()
+    prev = ops.dispatch.set_strict(True)
+    try:
+        with pytest.raises(RuntimeError, match="strict mode"):
+            ops.linear_fwd(x, w)
+    finally:
+        ops.dispatch.set_strict(prev)
+    ops.dispatch.FALLBACKS.clear()
+    ops.linear_fwd(x, w)
+    assert ops.dispatch.FALLBACKS.get("linear_fwd") == 1

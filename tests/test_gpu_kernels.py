@@ -224,3 +224,60 @@ def test_gated_rmsnorm_kernels_match_the_pytorch_form(dtype, gated, norm_before_
     for name, a_, w_ in zip(("dx", "dz", "dw") if gated else ("dx", "dw"), got, want):
         err = (a_.float() - w_).norm().item() / w_.norm().item()
         assert err <= (1e-2 if dtype == torch.bfloat16 else 1e-5), f"{name}: {err:.2e}"
+
+
+def test_mamba2_conv_silu_kernels_match_pytorch():
+    """Depthwise causal conv + SiLU over the x | B | C slice: forward (split outputs), input cotangent for stacked directions
+    written into a column range of a wider buffer, and the weight / bias gradient."""
+    from lbi_b200.ops import mamba as mops
+
+    b, l, parts, width, reps = 2, 200, (128, 64, 64), 4, 3
+    ch = sum(parts)
+    gen = torch.Generator().manual_seed(3)
+    x = torch.randn(b * l, ch, generator=gen).bfloat16()
+    w = torch.randn(ch, width, generator=gen) * 0.5
+    bias = torch.randn(ch, generator=gen) * 0.1
+    pre_c, parts_c = mops.conv_silu_fwd(x, w, bias, b, l, parts)
+    pre_g, parts_g = mops.conv_silu_fwd(x.cuda(), w.cuda(), bias.cuda(), b, l, parts)
+    assert torch.allclose(pre_g.float().cpu(), pre_c.float(), atol=3e-2, rtol=3e-2)
+    for a, c in zip(parts_g, parts_c):
+        assert a.is_contiguous() and torch.allclose(a.float().cpu(), c.float(), atol=3e-2, rtol=3e-2)
+    d_parts = [torch.randn(reps * b * l, p, generator=gen) for p in parts]
+    d_parts[0] = d_parts[0].bfloat16()                       # dx arrives in bf16, dB / dC in fp32
+    out_c = torch.zeros(reps * b * l, 64 + ch + 8).bfloat16()
+    out_g = torch.zeros_like(out_c).cuda()
+    mops.conv_silu_bwd(d_parts, pre_c, w, b, l, out_c, 64)
+    mops.conv_silu_bwd([d.cuda() for d in d_parts], pre_g, w.cuda(), b, l, out_g, 64)
+    assert torch.equal(out_g[:, :64].cpu(), out_c[:, :64]) and torch.equal(out_g[:, 64 + ch:].cpu(), out_c[:, 64 + ch:])
+    err = (out_g.float().cpu() - out_c.float()).abs().max().item()
+    assert err <= 3e-2 * out_c.float().abs().max().item() + 1e-2
+    one = [d[: b * l] for d in d_parts]
+    dw_c, db_c = mops.conv_silu_wgrad(one, pre_c, x, width, b, l)
+    dw_g, db_g = mops.conv_silu_wgrad([d.cuda() for d in one], pre_g, x.cuda(), width, b, l)
+    assert torch.allclose(dw_g.cpu(), dw_c, atol=3e-2 * dw_c.abs().max().item(), rtol=3e-2)
+    assert torch.allclose(db_g.cpu(), db_c, atol=3e-2 * db_c.abs().max().item(), rtol=3e-2)
+
+
+@pytest.mark.parametrize("hidden,act", [(0, "silu"), (48, "silu"), (48, "gelu")])
+def test_interface_head_forward_and_parameter_vjp_kernels(hidden, act):
+    """The skinny fp32 linear kernels behind the interface maps: forward with cached pre-activations and the closed-form
+    parameter VJP against autograd on the same head."""
+    from lbi_b200.interfaces.vector_mlp import VectorMLPHead, head_forward_cached, head_parameter_vjp
+
+    torch.manual_seed(0)
+    head = VectorMLPHead(40, 24, hidden, act).cuda()
+    x = torch.randn(3, 40, device="cuda")
+    g = torch.randn(3, 24, device="cuda")
+    xr = x.clone().requires_grad_(True)
+    y_ref = head(xr)
+    grads_ref = torch.autograd.grad(y_ref, [xr, *head.parameters()], g)
+    sink = {id(p): torch.zeros_like(p) for p in head.parameters()}
+    with torch.no_grad():
+        before = ops.dispatch.KERNEL_LAUNCHES["count"]
+        y, cache = head_forward_cached(head, x)
+        gx = head_parameter_vjp(head, cache, g, lambda p: sink[id(p)], want_input=True)
+        assert ops.dispatch.KERNEL_LAUNCHES["count"] > before, "the skinny linear kernels did not run"
+    assert torch.allclose(y, y_ref.detach(), atol=1e-5, rtol=1e-5)
+    assert torch.allclose(gx, grads_ref[0], atol=1e-5, rtol=1e-4)
+    for p, want in zip(head.parameters(), grads_ref[1:]):
+        assert torch.allclose(sink[id(p)], want, atol=1e-5, rtol=1e-4)

@@ -142,3 +142,28 @@ def test_activation_recomputation_gives_the_same_gradients():
     assert torch.allclose(a.flat.grads, b.flat.grads, atol=1e-7, rtol=1e-6)
     with pytest.raises(ValueError):
         FastLBIEngine(_model("mamba2", axis="depth", regions=2), recompute_forward=True)
+
+
+@pytest.mark.parametrize("kind", ["transformer", "mamba3"])
+def test_dense_fast_engine_matches_autograd(kind):
+    """The dense (no regions) step on the closed-form chain against loss.backward() of the same dense model."""
+    from lbi_b200.models import DenseLanguageModel
+    from lbi_b200.parallel import DenseFastEngine
+
+    torch.manual_seed(0)
+    kw = dict(dim=32, layers=2, d_state=16, headdim=8, expand=2, chunk_size=8, ngroups=1)
+    spec = BackboneSpec(name=kind, n_heads=4, d_conv=0 if kind == "transformer" else 4, **kw)
+    model = DenseLanguageModel(vocab_size=VOCAB, backbone_spec=spec, tie_embeddings=True)
+    ids, tgt = _batch()
+    ref = copy.deepcopy(model)
+    loss = F.cross_entropy(ref(ids).float().reshape(-1, VOCAB), tgt.reshape(-1))
+    loss.backward()
+    engine = DenseFastEngine(model, lr=1e-3)
+    got = engine.backward(ids, tgt)
+    assert torch.allclose(got, loss.detach(), atol=1e-6, rtol=1e-6)
+    for name, p in ref.named_parameters():
+        if p.grad is not None and name in engine.flat.slots:
+            assert torch.allclose(engine.flat.grad(name), p.grad, atol=1e-5, rtol=1e-4), name
+    before = engine.flat.params.clone()
+    engine.step(ids, tgt)
+    assert not torch.equal(before, engine.flat.params)

@@ -96,3 +96,57 @@ def test_dense_state_dict_has_both_block_prefixes():
     model = DenseLanguageModel(vocab_size=30, backbone_spec=BackboneSpec(name="transformer", dim=16, layers=1, n_heads=2))
     keys = set(model.state_dict())
     assert "blocks.0.norm.weight" in keys and "backbone.blocks.0.norm.weight" in keys and "canvas.embedding.weight" in keys
+
+
+def _legacy_model(regions=3):
+    from lbi_b200.backbones import BackboneSpec
+
+    torch.manual_seed(0)
+    spec = BackboneSpec(name="transformer", dim=16, layers=regions * 1, n_heads=2, d_conv=0)
+    return NativeRegionInterfaceModel(vocab_size=40, region_size=1, message_dim=6, backbone_spec=spec, message_hidden_dim=8)
+
+
+def test_legacy_model_recompute_mode_and_scan_helpers():
+    """The LBI-1 model's own Jacobian materialisers (graph and recompute), suffix composition and message-cotangent scans
+    agree with the sequential autograd chain, and its backward step runs in both modes with the same gradients."""
+    model = _legacy_model()
+    ids = torch.randint(0, 40, (2, 12))
+    logits, cache = model.forward_with_cache(ids)
+    g_top = torch.randn_like(cache["region_messages"][-1])
+    chain = model.interface_vjp_chain(cache, g_top)
+    for mode, chunk in (("graph", 1), ("recompute", 4)):
+        mats = model.materialize_interface_pullback_mats(cache, mode=mode, basis_chunk=chunk)
+        assert len(mats) == model.n_regions and mats[0].shape == (2, 6, 6)
+        scan = model.interface_vjp_scan_from_mats(mats, g_top)
+        for a, b in zip(scan, chain):
+            assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+    seeded = model.interface_vjp_scan_from_last_input_seed(mats, chain[-2])
+    for a, b in zip(seeded, chain[:-1]):
+        assert torch.allclose(a, b, atol=1e-5, rtol=1e-4)
+    assert len(model.compose_pullback_suffix(mats)) == model.n_regions + 1
+    grads = {}
+    tgt = torch.randint(0, 40, (2, 12))
+    for mode in ("graph", "recompute"):
+        logits, cache = model.forward_with_cache(ids, detach_states=True)
+        loss = torch.nn.functional.cross_entropy(logits.reshape(-1, 40), tgt.reshape(-1))
+        native_backward_step(model, loss, cache, interface_jacobian_mode=mode, jacobian_basis_chunk=3)
+        grads[mode] = {n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None}
+    assert grads["graph"].keys() == grads["recompute"].keys()
+    for n in grads["graph"]:
+        assert torch.allclose(grads["graph"][n], grads["recompute"][n], atol=1e-5, rtol=1e-4), n
+
+
+def test_legacy_model_closed_form_region_pullback_matches_autograd():
+    """The closed-form outer pieces of a region's message pullback (LayerNorm, update scale, encoder, token mean on one side;
+    token sum, decoder on the other) combined with autograd through the backbone give the graph-mode A_k^T."""
+    model = _legacy_model()
+    ids = torch.randint(0, 40, (2, 12))
+    _, cache = model.forward_with_cache(ids)
+    mats = model.materialize_interface_pullback_mats(cache, mode="graph")
+    for ridx, rc in enumerate(cache["region_caches"]):
+        eye = torch.eye(6).unsqueeze(0).expand(2, 6, 6)
+        tail = model.region_message_output_pullback_to_hidden_output(rc, eye)
+        g_hidden_in = torch.stack([torch.autograd.grad(rc.hidden_output, rc.hidden_input, tail["g_hidden_output"][:, j].contiguous(),
+                                                       retain_graph=True)[0] for j in range(6)], dim=1)
+        total = model.region_outer_message_input_pullback(rc, eye, g_hidden_in)["g_message_input_total"]   # [B, j, i]
+        assert torch.allclose(total.transpose(1, 2), mats[ridx], atol=1e-5, rtol=1e-4)
