@@ -38,6 +38,9 @@ CONFIGS = {
                  vocab=32768, seq_len=8192, regions=8, batch=8, message_dim=64, message_hidden=768),
     "cfg5": dict(model="lbi-mamba2-780m", backbone="mamba2", layers=48, dim=1536, d_state=128, headdim=64, expand=2, chunk=256,
                  vocab=32768, seq_len=32768, regions=32, batch=2, message_dim=256, message_hidden=1536, basis_chunk=64, recompute=True),
+    # a slice of cfg5 (same widths, 4 layers, 4 regions of 1024 tokens) for per-op profiles that finish in seconds
+    "cfg5-slice": dict(model="lbi-mamba2-780m-slice", backbone="mamba2", layers=4, dim=1536, d_state=128, headdim=64, expand=2, chunk=256,
+                       vocab=32768, seq_len=4096, regions=4, batch=2, message_dim=256, message_hidden=1536, basis_chunk=64),
     "mamba-tiny": dict(model="lbi-mamba3-tiny", backbone="mamba3", layers=2, dim=256, d_state=128, headdim=64, expand=2, chunk=128,
                        vocab=1024, seq_len=1024, regions=4, batch=2, message_dim=16, message_hidden=64),
     "tiny": dict(model="lbi-transformer-tiny", layers=2, dim=256, n_heads=4, d_intermediate=512, vocab=1024,

@@ -25,8 +25,8 @@ NVCC_FLAGS = [
 ]
 
 
-def _ext_path() -> Path:
-    return PKG / f"_C{sysconfig.get_config_var('EXT_SUFFIX')}"
+def _ext_path(name: str = "_C") -> Path:
+    return PKG / f"{name}{sysconfig.get_config_var('EXT_SUFFIX')}"
 
 
 def _digest(paths) -> str:
@@ -45,17 +45,22 @@ def _run(cmd: list[str]) -> None:
         print(proc.stdout, proc.stderr, file=sys.stderr)
 
 
-def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
+def build(force: bool = False, verbose_ptxas: bool = False, bounds_check: bool = False) -> Path:
+    """``bounds_check``: the debug extension ``lbi_b200/_Cdbg*.so`` compiled with -DLBI_BOUNDS_CHECK (index checks that record a
+    site code and skip the access; ``LBI_B200_DEBUG_EXT=1`` makes ``lbi_b200.ops`` load it instead of ``_C``)."""
     import torch
     from torch.utils import cpp_extension
 
+    name = "_Cdbg" if bounds_check else "_C"
+    BUILD = PKG / ("build_dbg" if bounds_check else "build")
+    extra = ["-DLBI_BOUNDS_CHECK"] if bounds_check else []
     BUILD.mkdir(exist_ok=True)
     sources = [CSRC / s for s in CUDA_SOURCES if (CSRC / s).exists()]
     headers = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh"))
     binding = CSRC / "binding.cpp"
     stamp = BUILD / "stamp.txt"
     digest = _digest([*sources, *headers, binding]) + torch.__version__
-    out = _ext_path()
+    out = _ext_path(name)
     if not force and out.exists() and stamp.exists() and stamp.read_text() == digest:
         return out
 
@@ -66,13 +71,13 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
     for src in sources:
         obj = BUILD / (src.stem + ".o")
         objects.append(obj)
-        flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if verbose_ptxas else [])
+        flags = list(NVCC_FLAGS) + extra + (["-Xptxas", "-v"] if verbose_ptxas else [])
         jobs.append([NVCC, *flags, f"-I{CSRC}", "-I/usr/local/cuda/include", "-c", str(src), "-o", str(obj)])
     bind_obj = BUILD / "binding.o"
     objects.append(bind_obj)
     cxx11_abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     jobs.append([
-        "g++", "-O2", "-std=c++17", "-fPIC", "-DTORCH_EXTENSION_NAME=_C", "-DTORCH_API_INCLUDE_EXTENSION_H",
+        "g++", "-O2", "-std=c++17", "-fPIC", f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H", *extra,
         f"-D_GLIBCXX_USE_CXX11_ABI={cxx11_abi}", *inc, "-c", str(binding), "-o", str(bind_obj),
     ])
     with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
@@ -88,5 +93,5 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose_ptxas="--ptxas" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose_ptxas="--ptxas" in sys.argv, bounds_check="--bounds-check" in sys.argv)
     print(path)

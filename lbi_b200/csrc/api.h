@@ -30,10 +30,11 @@ int lbi_add_condition(const void* canvas_bf16, const float* cond, void* out_bf16
 // out[g, d] = scale * sum_t rows[g * seq_len + t, d]; out must be zeroed by the caller (accumulates with atomics).
 int lbi_pool_tokens(const void* rows, int is_bf16, float* out, int64_t groups, int seq_len, int dim, float scale,
                     cudaStream_t stream);
+// A token id outside [0, vocab) sets the status word (81 gather, 82 scatter) and is skipped (the gathered row is zeros).
 int lbi_embedding_fwd(const int64_t* ids, const void* table, int table_is_bf16, void* out_bf16, int64_t rows, int dim,
-                      cudaStream_t stream);
+                      int64_t vocab, int* status, cudaStream_t stream);
 int lbi_embedding_scatter_add(float* d_table, const int64_t* ids, const void* d_rows, int rows_is_bf16, int64_t rows,
-                              int dim, cudaStream_t stream);
+                              int dim, int64_t vocab, int* status, cudaStream_t stream);
 int lbi_transpose_bf16(const void* in, void* out, int64_t rows, int64_t cols, cudaStream_t stream);
 int lbi_causal_conv_fwd(const void* x_bf16, const float* w, const float* bias_or_null, void* y_bf16, int64_t seqs,
                         int seq_len, int channels, int width, cudaStream_t stream);
@@ -142,6 +143,11 @@ int lbi_small_linear_fwd(const float* x, const float* w, const float* bias, floa
                          int act, cudaStream_t stream);
 int lbi_small_linear_dgrad(const float* g, const float* w, float* gx, int batch, int din, int dout, cudaStream_t stream);
 int lbi_small_linear_wgrad(const float* g, const float* x, float* dw, float* db, int batch, int din, int dout, cudaStream_t stream);
+
+// Debug build only (-DLBI_BOUNDS_CHECK): the first index-check violation (site code) of a translation unit, read and cleared;
+// 0 = none.  The normal build returns 0.
+int lbi_bounds_site_elementwise();
+int lbi_bounds_site_mamba_small();
 
 #ifdef __cplusplus
 }

@@ -51,8 +51,14 @@ int lbi_affine_scan_peer(const float* const* mats_ptrs, const float* const* offs
 // d s_out[j] / d s_in[a], zero where another rank did the work) and partial offsets [K, B, R]; the kernel sums them over
 // the ranks as it loads them and writes all g_k ([B, K, R]) on every rank.
 int lbi_affine_scan_peer_sum(const float* const* rows_ptrs, const float* const* offs_ptrs, const uint32_t* flags, int slot_base,
-                             uint32_t seq, float* g, int batch, int world, int k_total, int r, int* status,
+                             uint32_t seq, float* g, int batch, int world, int k_total, int r, int flag_world, int* status,
                              cudaStream_t stream);
+// Copy segments (offset, length in floats, multiples of 4) of src_a / src_b into the same offsets of every rank's buffer
+// (dst_a[w], dst_b[w]: peer pointers, w < world, this rank included), then raise flag slot_base + rank on every peer to seq.
+// done_counter: one zero-initialised uint32 owned by the caller (left at zero).
+int lbi_peer_publish(const float* src_a, float* const* dst_a, const int64_t* segs_a, int n_a, const float* src_b,
+                     float* const* dst_b, const int64_t* segs_b, int n_b, uint32_t* const* flag_ptrs, int rank, int world,
+                     int slot_base, uint32_t seq, uint32_t* done_counter, cudaStream_t stream);
 
 // Gradient reduce-scatter by peer loads: reduced[i] = sum_w grad_ptrs[w][lo + i] for this rank's shard, written back
 // into this rank's own buffer at [lo, lo + n), with sum of squares of the reduced shard added to *sumsq.

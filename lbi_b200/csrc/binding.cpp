@@ -169,7 +169,7 @@ Tensor embedding_fwd(const Tensor& ids, const Tensor& table) {
   c10::cuda::CUDAGuard guard(table.device());
   Tensor out = torch::empty({ids.numel(), table.size(1)}, table.options().dtype(at::kBFloat16));
   check(lbi_embedding_fwd(ids.data_ptr<int64_t>(), table.data_ptr(), table.scalar_type() == at::kBFloat16 ? 1 : 0,
-                          out.data_ptr(), ids.numel(), (int)table.size(1), cur_stream()),
+                          out.data_ptr(), ids.numel(), (int)table.size(1), table.size(0), status_word(table).data_ptr<int>(), cur_stream()),
         "embedding_fwd");
   return out;
 }
@@ -178,8 +178,8 @@ void embedding_scatter_add_(Tensor d_table, const Tensor& ids, const Tensor& d_r
   CHECK_F32(d_table);
   c10::cuda::CUDAGuard guard(d_table.device());
   check(lbi_embedding_scatter_add(d_table.data_ptr<float>(), ids.data_ptr<int64_t>(), d_rows.data_ptr(),
-                                  d_rows.scalar_type() == at::kBFloat16 ? 1 : 0, ids.numel(), (int)d_table.size(1),
-                                  cur_stream()),
+                                  d_rows.scalar_type() == at::kBFloat16 ? 1 : 0, ids.numel(), (int)d_table.size(1), d_table.size(0),
+                                  status_word(d_table).data_ptr<int>(), cur_stream()),
         "embedding_scatter_add");
 }
 
@@ -1073,14 +1073,31 @@ Tensor affine_scan_peer(const Tensor& mats_ptrs, const Tensor& offs_ptrs, const 
   return g;
 }
 
+void peer_publish(const Tensor& src_a, const Tensor& dst_a_ptrs, const Tensor& segs_a, const Tensor& src_b, const Tensor& dst_b_ptrs,
+                  const Tensor& segs_b, const Tensor& flag_ptrs, int64_t rank, int64_t world, int64_t slot_base, int64_t seq,
+                  Tensor done_counter) {
+  CHECK_F32(src_a);
+  CHECK_F32(src_b);
+  c10::cuda::CUDAGuard guard(src_a.device());
+  TORCH_CHECK(segs_a.scalar_type() == at::kLong && segs_b.scalar_type() == at::kLong && segs_a.is_cuda() && segs_b.is_cuda() &&
+                  segs_a.is_contiguous() && segs_b.is_contiguous() && done_counter.scalar_type() == at::kInt,
+              "peer_publish: segment tables must be contiguous CUDA int64 [n, 2], the counter int32");
+  check(lbi_peer_publish(src_a.data_ptr<float>(), ptr_table<float* const*>(dst_a_ptrs), segs_a.data_ptr<int64_t>(), (int)(segs_a.numel() / 2),
+                         src_b.data_ptr<float>(), ptr_table<float* const*>(dst_b_ptrs), segs_b.data_ptr<int64_t>(), (int)(segs_b.numel() / 2),
+                         ptr_table<uint32_t* const*>(flag_ptrs), (int)rank, (int)world, (int)slot_base, (uint32_t)seq,
+                         reinterpret_cast<uint32_t*>(done_counter.data_ptr<int>()), cur_stream()),
+        "peer_publish");
+}
+
 Tensor affine_scan_peer_sum(const Tensor& rows_ptrs, const Tensor& offs_ptrs, const Tensor& flags, int64_t slot_base, int64_t seq,
-                            int64_t batch, int64_t world, int64_t k_total, int64_t r) {
+                            int64_t batch, int64_t world, int64_t k_total, int64_t r, int64_t flag_world) {
   c10::cuda::CUDAGuard guard(flags.device());
   Tensor g = torch::empty({batch, k_total, r}, flags.options().dtype(at::kFloat));
   Tensor st = status_word(flags);
   check(lbi_affine_scan_peer_sum(ptr_table<const float* const*>(rows_ptrs), ptr_table<const float* const*>(offs_ptrs),
                                  reinterpret_cast<const uint32_t*>(flags.data_ptr<int>()), (int)slot_base, (uint32_t)seq,
-                                 g.data_ptr<float>(), (int)batch, (int)world, (int)k_total, (int)r, st.data_ptr<int>(), cur_stream()),
+                                 g.data_ptr<float>(), (int)batch, (int)world, (int)k_total, (int)r, (int)(flag_world > 0 ? flag_world : world),
+                                 st.data_ptr<int>(), cur_stream()),
         "affine_scan_peer_sum");
   return g;
 }
@@ -1156,6 +1173,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("siso_prep_bwd", &siso_prep_bwd, py::arg("q"), py::arg("k"), py::arg("q_bias"), py::arg("k_bias"), py::arg("theta"),
         py::arg("gamma"), py::arg("scale"), py::arg("dqr"), py::arg("dkr"), py::arg("dqk"), py::arg("dkr_reversed") = false,
         py::arg("want_bias") = true);
+  m.def("bounds_violations", []() {
+    return std::vector<int>{lbi_bounds_site_elementwise(), lbi_bounds_site_mamba_small()};
+  });
+#ifdef LBI_BOUNDS_CHECK
+  m.attr("BOUNDS_CHECK") = true;
+#else
+  m.attr("BOUNDS_CHECK") = false;
+#endif
   m.def("small_linear_fwd", &small_linear_fwd);
   m.def("small_linear_dgrad", &small_linear_dgrad);
   m.def("small_linear_wgrad_", &small_linear_wgrad_);
@@ -1192,7 +1217,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("interface_update_handoff", &interface_update_handoff);
   m.def("wait_state", &wait_state);
   m.def("affine_scan_peer", &affine_scan_peer);
-  m.def("affine_scan_peer_sum", &affine_scan_peer_sum);
+  m.def("affine_scan_peer_sum", &affine_scan_peer_sum, py::arg("rows_ptrs"), py::arg("offs_ptrs"), py::arg("flags"), py::arg("slot_base"),
+        py::arg("seq"), py::arg("batch"), py::arg("world"), py::arg("k_total"), py::arg("r"), py::arg("flag_world") = 0);
+  m.def("peer_publish", &peer_publish);
   m.def("grad_reduce_scatter_", &grad_reduce_scatter_);
   m.def("exchange_scalar", &exchange_scalar);
   m.def("adamw_allgather_", &adamw_allgather_);

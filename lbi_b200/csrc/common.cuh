@@ -26,6 +26,31 @@ struct PerDeviceOnce {
   }
 };
 
+// Debug build (python -m lbi_b200.build --bounds-check, extension lbi_b200._Cdbg): index checks that record the first violation
+// (a site code) in a word of their translation unit and skip the access; nothing ever traps.  In the normal build the
+// macro is the constant true and costs nothing.  LBI_DEFINE_BOUNDS_GETTER(fn) defines the host function that reads and
+// clears the word of the translation unit it is placed in.
+#ifdef LBI_BOUNDS_CHECK
+static __device__ int g_bounds_site = 0;
+__device__ __forceinline__ bool bounds_ok(int64_t i, int64_t n, int site) {
+  if (i >= 0 && i < n) return true;
+  atomicCAS(&g_bounds_site, 0, site);
+  return false;
+}
+#define LBI_IN_RANGE(i, n, site) lbi::bounds_ok((int64_t)(i), (int64_t)(n), (site))
+#define LBI_DEFINE_BOUNDS_GETTER(fn)                                                                   \
+  extern "C" int fn() {                                                                                \
+    int v = 0, zero = 0;                                                                               \
+    if (cudaMemcpyFromSymbol(&v, lbi::g_bounds_site, sizeof(int)) != cudaSuccess) return -1;           \
+    if (cudaMemcpyToSymbol(lbi::g_bounds_site, &zero, sizeof(int)) != cudaSuccess) return -1;          \
+    return v;                                                                                          \
+  }
+#else
+#define LBI_IN_RANGE(i, n, site) (true)
+#define LBI_DEFINE_BOUNDS_GETTER(fn) \
+  extern "C" int fn() { return 0; }
+#endif
+
 struct alignas(16) bf16x8 {
   __nv_bfloat162 v[4];
 };

@@ -292,18 +292,31 @@ __global__ void pool_tokens_kernel(const T* __restrict__ rows, float* __restrict
 // ------------------------------------------------------------------------------------------------ embedding
 template <typename T>
 __global__ void embedding_fwd_kernel(const int64_t* __restrict__ ids, const T* __restrict__ table,
-                                     __nv_bfloat16* __restrict__ out, int64_t rows, int dim) {
+                                     __nv_bfloat16* __restrict__ out, int64_t rows, int dim, int64_t vocab, int* status) {
+  // a token id outside [0, vocab) is recorded in the status word (site 81) and its row is written as zeros: bad data must
+  // not become an illegal address
   const int64_t row = blockIdx.x;
-  const T* src = table + ids[row] * (int64_t)dim;
+  const int64_t id = ids[row];
   __nv_bfloat16* dst = out + row * dim;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, 81);
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = __float2bfloat16(0.f);
+    return;
+  }
+  const T* src = table + id * (int64_t)dim;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) dst[d] = __float2bfloat16((float)src[d]);
 }
 
 template <typename T>
 __global__ void embedding_scatter_add_kernel(float* __restrict__ d_table, const int64_t* __restrict__ ids,
-                                             const T* __restrict__ d_rows, int64_t rows, int dim) {
+                                             const T* __restrict__ d_rows, int64_t rows, int dim, int64_t vocab, int* status) {
   const int64_t row = blockIdx.x;
-  float* dst = d_table + ids[row] * (int64_t)dim;
+  const int64_t id = ids[row];
+  if (id < 0 || id >= vocab) {   // recorded (site 82) and skipped
+    if (threadIdx.x == 0 && status) atomicCAS(status, 0, 82);
+    return;
+  }
+  float* dst = d_table + id * (int64_t)dim;
   const T* src = d_rows + row * dim;
   for (int d = threadIdx.x; d < dim; d += blockDim.x) atomicAdd(dst + d, (float)src[d]);
 }
@@ -343,7 +356,8 @@ __global__ void causal_conv_fwd_kernel(const __nv_bfloat16* __restrict__ x, cons
   float acc = bias ? bias[c] : 0.f;
   for (int k = 0; k < width; ++k) {
     const int tt = t - (width - 1) + k;
-    if (tt >= 0) acc += w[c * width + k] * __bfloat162float(x[idx + (int64_t)(tt - t) * channels]);
+    if (tt >= 0 && LBI_IN_RANGE(idx + (int64_t)(tt - t) * channels, total, 95))
+      acc += w[c * width + k] * __bfloat162float(x[idx + (int64_t)(tt - t) * channels]);
   }
   y[idx] = __float2bfloat16(acc);
 }
@@ -360,7 +374,8 @@ __global__ void causal_conv_dgrad_kernel(const __nv_bfloat16* __restrict__ dy, c
   float acc = 0.f;
   for (int k = 0; k < width; ++k) {
     const int tt = t + (width - 1) - k;
-    if (tt < seq_len) acc += w[c * width + k] * __bfloat162float(dy[idx + (int64_t)(tt - t) * channels]);
+    if (tt < seq_len && LBI_IN_RANGE(idx + (int64_t)(tt - t) * channels, total, 96))
+      acc += w[c * width + k] * __bfloat162float(dy[idx + (int64_t)(tt - t) * channels]);
   }
   dx[idx] = __float2bfloat16(acc);
 }
@@ -547,24 +562,24 @@ int lbi_pool_tokens(const void* rows, int is_bf16, float* out, int64_t groups, i
 }
 
 int lbi_embedding_fwd(const int64_t* ids, const void* table, int table_is_bf16, void* out, int64_t rows, int dim,
-                      cudaStream_t st) {
+                      int64_t vocab, int* status, cudaStream_t st) {
   if (rows == 0) return 0;
   if (table_is_bf16)
     embedding_fwd_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, st>>>(ids, (const __nv_bfloat16*)table,
-                                                                         (__nv_bfloat16*)out, rows, dim);
+                                                                         (__nv_bfloat16*)out, rows, dim, vocab, status);
   else
-    embedding_fwd_kernel<float><<<(unsigned)rows, 128, 0, st>>>(ids, (const float*)table, (__nv_bfloat16*)out, rows, dim);
+    embedding_fwd_kernel<float><<<(unsigned)rows, 128, 0, st>>>(ids, (const float*)table, (__nv_bfloat16*)out, rows, dim, vocab, status);
   return launch_status();
 }
 
 int lbi_embedding_scatter_add(float* d_table, const int64_t* ids, const void* d_rows, int rows_is_bf16, int64_t rows,
-                              int dim, cudaStream_t st) {
+                              int dim, int64_t vocab, int* status, cudaStream_t st) {
   if (rows == 0) return 0;
   if (rows_is_bf16)
     embedding_scatter_add_kernel<__nv_bfloat16><<<(unsigned)rows, 128, 0, st>>>(d_table, ids,
-                                                                                 (const __nv_bfloat16*)d_rows, rows, dim);
+                                                                                 (const __nv_bfloat16*)d_rows, rows, dim, vocab, status);
   else
-    embedding_scatter_add_kernel<float><<<(unsigned)rows, 128, 0, st>>>(d_table, ids, (const float*)d_rows, rows, dim);
+    embedding_scatter_add_kernel<float><<<(unsigned)rows, 128, 0, st>>>(d_table, ids, (const float*)d_rows, rows, dim, vocab, status);
   return launch_status();
 }
 
@@ -624,3 +639,5 @@ int lbi_ce_fwd_bwd(void* logits, const int64_t* targets, float* loss_sum, int64_
 }
 
 }  // extern "C"
+
+LBI_DEFINE_BOUNDS_GETTER(lbi_bounds_site_elementwise)

@@ -180,7 +180,7 @@ __global__ void __launch_bounds__(1024) siso_small_bwd_kernel(
       if (t >= 0) {
         const int64_t fi = (frow0 + t) * heads + h, ci = (crow0 + t) * heads + h;
         const float dsc = dscale[ci];
-        const float dsc_prev = t > 0 ? dscale[ci - heads] : 0.f;
+        const float dsc_prev = (t > 0 && LBI_IN_RANGE(ci - heads, (int64_t)gridDim.x * seq_len * heads, 94)) ? dscale[ci - heads] : 0.f;
         const float dg_all = dgamma[ci] + dsc;
         const float sg = sig[fi], dtv = dt[fi], da = dadt[ci];
         const float d_dt = da * a[fi] + mine + dg_all * sg + dsc_prev * (1.f - sg);
@@ -307,6 +307,7 @@ __global__ void __launch_bounds__(256) conv_silu_fwd_kernel(const __nv_bfloat16*
   for (int k = 0; k < width; ++k) {
     const int tt = t - (width - 1) + k;
     if (tt < 0) continue;
+    if (!LBI_IN_RANGE(tok + (tt - t), tokens, 91)) continue;
     float xv[8];
     unpack8(*reinterpret_cast<const bf16x8*>(x + (tok + (tt - t)) * channels + c), xv);
 #pragma unroll
@@ -362,6 +363,7 @@ __global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const D0* __restrict
     if (tt >= seq_len) continue;
     float dp[8];
     const int64_t tk = tok + (tt - t);
+    if (!LBI_IN_RANGE(tk, tokens, 92)) continue;
     dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tk, tk % ftokens, c, dp);
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], dp[e], acc[e]);
@@ -400,6 +402,7 @@ __global__ void __launch_bounds__(256) conv_silu_wgrad_kernel(const D0* __restri
       if (k >= width) break;
       const int tt = t - (width - 1) + k;
       if (tt < 0) continue;
+      if (!LBI_IN_RANGE(tok + (tt - t), tokens, 93)) continue;
       float xv[8];
       unpack8(*reinterpret_cast<const bf16x8*>(x + (tok + (tt - t)) * channels + c), xv);
 #pragma unroll
@@ -475,3 +478,5 @@ extern "C" int lbi_conv_silu_wgrad(const void* d0, int d0_fp32, const void* d1, 
 #undef LBI_CONV_WG
   return (int)cudaGetLastError();
 }
+
+LBI_DEFINE_BOUNDS_GETTER(lbi_bounds_site_mamba_small)

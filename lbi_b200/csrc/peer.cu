@@ -217,13 +217,15 @@ __global__ void __launch_bounds__(256) affine_scan_peer_kernel(const float* cons
 __global__ void __launch_bounds__(1024) affine_scan_peer_sum_kernel(const float* const* rows_ptrs, const float* const* offs_ptrs,
                                                                      const uint32_t* flags, int slot_base, uint32_t seq,
                                                                      float* __restrict__ g, int world, int batch, int k_total, int r,
-                                                                     int* status) {
+                                                                     int* status, int flag_world) {
+  // `world` buffers are summed while they are loaded; `flag_world` >= world ranks are waited for (with published rows the
+  // whole matrix set already sits in this rank's own buffer: world = 1, flag_world = all ranks)
   extern __shared__ float vec[];
   __shared__ int ok_all;
   const int b = blockIdx.x;
   if (threadIdx.x == 0) ok_all = 1;
   __syncthreads();
-  if (threadIdx.x < world) {
+  if (threadIdx.x < flag_world) {
     if (!wait_flag(flags + slot_base + threadIdx.x, seq, status, 45)) ok_all = 0;
   }
   __syncthreads();
@@ -262,6 +264,40 @@ __global__ void __launch_bounds__(1024) affine_scan_peer_sum_kernel(const float*
     float* t = cur;
     cur = nxt;
     nxt = t;
+  }
+}
+
+// Publish: copy segments of two local buffers (Jacobian rows, offsets) into the same place of every rank's symmetric buffer by
+// peer stores, then raise this rank's flag on every peer.  Each (region, block of basis directions) was produced by exactly
+// one rank, so after all ranks have published, every rank holds the complete set and scans it from local memory: no rank
+// reads a matrix over NVLink more than once and nothing is summed.  segs[i] = (offset, length) in floats, multiples of 4.
+// grid (chunks, n_seg_a + n_seg_b).  The flags go out from the last CTA to finish (ticket counter), after a system fence.
+__global__ void __launch_bounds__(256) publish_segments_kernel(const float* __restrict__ src_a, float* const* dst_a,
+                                                               const int64_t* __restrict__ segs_a, int n_a,
+                                                               const float* __restrict__ src_b, float* const* dst_b,
+                                                               const int64_t* __restrict__ segs_b, uint32_t* const* flag_ptrs,
+                                                               int rank, int world, int slot_base, uint32_t seq,
+                                                               uint32_t* done_counter) {
+  const int sidx = blockIdx.y;
+  const bool first = sidx < n_a;
+  const float* src = first ? src_a : src_b;
+  float* const* dst = first ? dst_a : dst_b;
+  const int64_t* seg = first ? segs_a + 2 * sidx : segs_b + 2 * (sidx - n_a);
+  const int64_t off = seg[0], nvec = seg[1] >> 2;
+  const float4* s4 = reinterpret_cast<const float4*>(src + off);
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 v = s4[i];
+    for (int w = 0; w < world; ++w) reinterpret_cast<float4*>(dst[w] + off)[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ uint32_t ticket;
+  if (threadIdx.x == 0) ticket = atomicAdd(done_counter, 1u);
+  __syncthreads();
+  if (ticket == gridDim.x * gridDim.y - 1) {
+    if (threadIdx.x == 0) *done_counter = 0;
+    __threadfence_system();
+    if (threadIdx.x < world) st_release_sys(flag_ptrs[threadIdx.x] + slot_base + rank, seq);
   }
 }
 
@@ -399,14 +435,25 @@ int lbi_affine_scan_peer(const float* const* mats_ptrs, const float* const* offs
   return (int)cudaGetLastError();
 }
 
+int lbi_peer_publish(const float* src_a, float* const* dst_a, const int64_t* segs_a, int n_a, const float* src_b,
+                     float* const* dst_b, const int64_t* segs_b, int n_b, uint32_t* const* flag_ptrs, int rank, int world,
+                     int slot_base, uint32_t seq, uint32_t* done_counter, cudaStream_t st) {
+  if (n_a < 0 || n_b < 0 || n_a + n_b <= 0 || world <= 0 || world > 256) return (int)cudaErrorInvalidValue;
+  publish_segments_kernel<<<dim3(8, n_a + n_b), 256, 0, st>>>(src_a, dst_a, segs_a, n_a, src_b, dst_b, segs_b, flag_ptrs, rank, world,
+                                                              slot_base, seq, done_counter);
+  return (int)cudaGetLastError();
+}
+
 int lbi_affine_scan_peer_sum(const float* const* rows_ptrs, const float* const* offs_ptrs, const uint32_t* flags, int slot_base,
-                             uint32_t seq, float* g, int batch, int world, int k_total, int r, int* status, cudaStream_t st) {
+                             uint32_t seq, float* g, int batch, int world, int k_total, int r, int flag_world, int* status,
+                             cudaStream_t st) {
   if (batch <= 0) return 0;
-  if (r <= 0 || r > 1024) return (int)cudaErrorInvalidValue;
+  if (r <= 0 || r > 1024 || flag_world < world || flag_world > 1024) return (int)cudaErrorInvalidValue;
   const int threads = 1024 / r * r >= 32 ? (1024 / r) * r : r;   // a whole number of groups of r threads
   const int groups = threads / r;
   affine_scan_peer_sum_kernel<<<batch, threads, (size_t)(2 + groups) * r * sizeof(float), st>>>(rows_ptrs, offs_ptrs, flags, slot_base,
-                                                                                                seq, g, world, batch, k_total, r, status);
+                                                                                                seq, g, world, batch, k_total, r, status,
+                                                                                                flag_world);
   return (int)cudaGetLastError();
 }
 

@@ -15,7 +15,8 @@ def _load():
     if _EXT is not None or _ERR is not None:
         return
     try:
-        _EXT = importlib.import_module("lbi_b200._C")
+        # LBI_B200_DEBUG_EXT=1: the bounds-checking debug build (python -m lbi_b200.build --bounds-check)
+        _EXT = importlib.import_module("lbi_b200._Cdbg" if os.environ.get("LBI_B200_DEBUG_EXT", "0") == "1" else "lbi_b200._C")
     except Exception as exc:  # noqa: BLE001 - reported by require_native
         _ERR = exc
 

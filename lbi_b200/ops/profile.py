@@ -30,6 +30,13 @@ _MAMBA_NAMES = [
 ]
 
 
+# (module, attribute) pairs outside the two op modules: the SSD entry points of the Mamba-2 lowering
+_EXTRA = [
+    ("lbi_b200.backends.mamba_structured", "_ssd_forward"), ("lbi_b200.backends.mamba_structured", "_ssd_backward"),
+]
+_MAMBA_NAMES += ["conv_silu_fwd", "conv_silu_bwd", "conv_silu_wgrad"]
+
+
 def _wrap(name, fn):
     @functools.wraps(fn)
     def timed(*args, **kwargs):
@@ -63,14 +70,25 @@ def enable() -> None:
         if fn is not None:
             _ORIGINALS["mamba." + name] = fn
             setattr(mamba_ops, name, _wrap("mamba." + name, fn))
+    import importlib
+
+    for mod_name, attr in _EXTRA:
+        mod = importlib.import_module(mod_name)
+        _ORIGINALS[f"extra:{mod_name}:{attr}"] = getattr(mod, attr)
+        setattr(mod, attr, _wrap(attr.lstrip("_"), getattr(mod, attr)))
 
 
 def disable() -> None:
     import lbi_b200.ops as ops_pkg
     import lbi_b200.ops.mamba as mamba_ops
 
+    import importlib
+
     for name, fn in _ORIGINALS.items():
-        if name.startswith("mamba."):
+        if name.startswith("extra:"):
+            _, mod_name, attr = name.split(":")
+            setattr(importlib.import_module(mod_name), attr, fn)
+        elif name.startswith("mamba."):
             setattr(mamba_ops, name[len("mamba."):], fn)
         else:
             setattr(ops_pkg, name, fn)

@@ -343,9 +343,12 @@ class FastLBIEngine:
             if rec.index not in loss_done and rec.d_out_loss is not None:
                 _, off = self._pullback_directions(rec, 0, 0, include_loss=True)
                 offs_all[rec.index] = off
-        if hasattr(comm, "scan_partial_sums") and self.device.type == "cuda":
-            self.last["jacobians"] = None
-            return comm.scan_partial_sums(rows_all, offs_all)   # summed over ranks inside the scan kernel's peer loads
+        if hasattr(comm, "scan_published") and self.device.type == "cuda":
+            g, rows_full = comm.scan_published(rows_all, offs_all, mine, sorted(loss_done | {rec.index for rec in records
+                                                                                              if rec.d_out_loss is not None}))
+            # A_k^T[b, i, j] = d s_out[j] / d s_in[i]: a view of the gathered rows (valid until the next step publishes)
+            self.last["jacobians"], self.last["offsets"] = rows_full.permute(1, 0, 3, 2), None
+            return g
         comm.all_reduce_sum(rows_all)
         comm.all_reduce_sum(offs_all)
         mats_all = rows_all.permute(1, 0, 3, 2).contiguous()   # [B, K, R, R] with A_k^T[b, i, j] = d s_out[j] / d s_in[i]

@@ -215,6 +215,45 @@ class SymmComm(CollectiveComm):
         ops.dispatch.KERNEL_LAUNCHES["count"] += 2
         return g
 
+    def scan_published(self, rows_all: torch.Tensor, offs_all: torch.Tensor, row_blocks, off_regions):
+        """Basis-parallel scan, gather form.  rows_all [K, B, R, R] / offs_all [K, B, R] hold this rank's results in the
+        blocks ``row_blocks`` = [(region, lo, hi)] of basis directions and the offsets of ``off_regions``; one kernel stores
+        exactly those pieces into every rank's symmetric buffer (peer stores) and raises this rank's flag, then the scan
+        kernel waits for every rank's flag and recurses over its own, now complete, copy.  Each matrix element crosses
+        NVLink once per destination and nothing is summed.  Returns (g [B, K, R], complete rows [K, B, R, R] view)."""
+        key = ("published", tuple(rows_all.shape))
+        hit = self._scan_bufs.get(key)
+        if hit is None:
+            m_buf, mh = self._alloc(rows_all.numel(), torch.float32)
+            o_buf, oh = self._alloc(offs_all.numel(), torch.float32)
+            m_buf.zero_()
+            o_buf.zero_()
+            hit = (m_buf, o_buf, self._table(mh), self._table(oh), mh, oh, {})
+            self._scan_bufs[key] = hit
+            self._setup_barrier()
+        m_buf, o_buf, m_ptrs, o_ptrs, _, _, seg_cache = hit
+        k_total, bsz, r = rows_all.shape[0], rows_all.shape[1], rows_all.shape[-1]
+        plan_key = (tuple(row_blocks), tuple(off_regions))
+        segs = seg_cache.get(plan_key)
+        if segs is None:
+            seg_m = [(((k * bsz + b) * r + lo) * r, (hi - lo) * r) for (k, lo, hi) in row_blocks for b in range(bsz)]
+            seg_o = [(k * bsz * r, bsz * r) for k in off_regions]
+            if r % 4:
+                raise ValueError("the published scan moves 16-byte pieces: the interface width must be a multiple of 4")
+            as_tensor = lambda seg: torch.tensor(seg or [(0, 0)], dtype=torch.int64, device=self.device).reshape(-1, 2).contiguous()  # noqa: E731
+            segs = (as_tensor(seg_m), as_tensor(seg_o))
+            seg_cache[plan_key] = segs
+        self.seq += 1
+        w = self.world_size
+        ext = ops.ext()
+        # peers may still be reading last step's matrices: the barrier at the end of the optimizer step orders that
+        ext.peer_publish(rows_all.contiguous(), m_ptrs, segs[0], offs_all.contiguous(), o_ptrs, segs[1], self.flag_ptrs, self.rank, w,
+                         _SLOT_SCAN * w, self.seq, self.done_counter)
+        own_m, own_o = m_ptrs[self.rank : self.rank + 1], o_ptrs[self.rank : self.rank + 1]
+        g = ext.affine_scan_peer_sum(own_m, own_o, self.flags, _SLOT_SCAN * w, self.seq, bsz, 1, k_total, r, w)
+        ops.dispatch.KERNEL_LAUNCHES["count"] += 2
+        return g, m_buf.view(rows_all.shape)
+
     # ------------------------------------------------------------------ (3) gradients + optimizer + weight all-gather
     def attach_flat(self, flat) -> None:
         """Move the gradient and bf16-weight buffers of ``flat`` into symmetric memory (views are re-pointed)."""

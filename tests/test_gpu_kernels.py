@@ -281,3 +281,52 @@ def test_interface_head_forward_and_parameter_vjp_kernels(hidden, act):
     assert torch.allclose(gx, grads_ref[0], atol=1e-5, rtol=1e-4)
     for p, want in zip(head.parameters(), grads_ref[1:]):
         assert torch.allclose(sink[id(p)], want, atol=1e-5, rtol=1e-4)
+
+
+def test_tail_shapes_under_the_bounds_checking_debug_build():
+    """The debug extension (-DLBI_BOUNDS_CHECK: index checks that record a site code and skip the access, never trap) on
+    shapes that reach the tail paths of the conv / scan-glue kernels: no violation may be recorded.  Runs in a child process
+    because the extension is chosen at import time."""
+    import os
+    import subprocess
+    import sys
+
+    from lbi_b200.build import _ext_path
+
+    if not _ext_path("_Cdbg").exists():
+        pytest.skip("debug extension not built (python -m lbi_b200.build --bounds-check)")
+    code = r"""
+import torch
+from lbi_b200 import ops
+from lbi_b200.ops import mamba as mops
+assert ops.ext().BOUNDS_CHECK
+g = torch.Generator(device="cuda").manual_seed(0)
+for b, l, width in ((1, 37, 4), (3, 129, 2), (2, 200, 4)):
+    parts = (64, 24, 24)
+    ch = sum(parts)
+    x = torch.randn(b * l, ch, device="cuda", generator=g).bfloat16()
+    w = torch.randn(ch, width, device="cuda", generator=g)
+    pre, acts = mops.conv_silu_fwd(x, w, None, b, l, parts)
+    d = [torch.randn(2 * b * l, p, device="cuda", generator=g).bfloat16() for p in parts]
+    out = torch.zeros(2 * b * l, ch + 8, device="cuda").bfloat16()
+    mops.conv_silu_bwd(d, pre, w, b, l, out, 8)
+    mops.conv_silu_wgrad([t[: b * l] for t in d], pre, x, width, b, l)
+    y = ops.causal_conv_fwd(x, w, None, b, l)
+    ops.causal_conv_dgrad(y, w, b, l)
+    small = mops.siso_small_fwd(*(torch.randn(b * l, 5, device="cuda", generator=g) for _ in range(3)),
+                                torch.randn(b * l, 7, device="cuda", generator=g), torch.randn(5, device="cuda", generator=g), 1e-4, b, l)
+    mops.siso_small_bwd(small, *(torch.randn(2 * b, l, 5, device="cuda", generator=g) for _ in range(1)),
+                        torch.randn(2 * b, l, 5, 7, device="cuda", generator=g),
+                        *(torch.randn(2 * b, l, 5, device="cuda", generator=g) for _ in range(2)))
+ids = torch.tensor([3, 99999, 5], device="cuda")
+table = torch.randn(16, 8, device="cuda")
+rows = ops.embedding_fwd(ids, table, torch.bfloat16)
+torch.cuda.synchronize()
+assert float(rows[1].abs().sum()) == 0.0 and ops.ext().kernel_status(table) == 81   # bad id: recorded, row zeroed
+print("violations", ops.ext().bounds_violations())
+"""
+    env = dict(os.environ, LBI_B200_DEBUG_EXT="1")
+    proc = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600,
+                          cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert "violations [0, 0]" in proc.stdout, proc.stdout
