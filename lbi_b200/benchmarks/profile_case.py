@@ -9,6 +9,10 @@
     python -m lbi_b200.benchmarks.profile_case --case ssd       # Mamba-2 SSD forward B 2, L 8192, 24 heads, d_state 64
     python -m lbi_b200.benchmarks.profile_case --case ssd_bwd   # SSD forward + backward (permuted scans, decay gradient, tails)
     python -m lbi_b200.benchmarks.profile_case --case mamba_elementwise   # gated RMSNorm and SISO preprocessing, both directions
+    python -m lbi_b200.benchmarks.profile_case --case chunk_bwd          # fused chunk backward, Mamba-3 form: 16 directions x B 1, L 1024, 24 heads
+    python -m lbi_b200.benchmarks.profile_case --case chunk_bwd_ssd      # fused chunk backward, Mamba-2 form (grouped B / C, weight dt)
+    python -m lbi_b200.benchmarks.profile_case --case mamba_glue         # gate, small-tensor fwd / bwd, conv + SiLU fwd / bwd / wgrad
+    python -m lbi_b200.benchmarks.profile_case --case small              # interface / scan / optimizer / embedding / CE kernels
 
 Each case holds well under 2 GB on the device, touches more than the 126 MB L2, launches the kernel of interest a
 handful of times and exits.  Typical capture:
@@ -26,7 +30,8 @@ from lbi_b200 import ops
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd", "ssd_bwd", "mamba_elementwise"])
+    ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd", "ssd_bwd", "mamba_elementwise", "chunk_bwd",
+                             "chunk_bwd_ssd", "mamba_glue", "small"])
     ap.add_argument("--repeats", type=int, default=2)
     args = ap.parse_args()
     dev = "cuda"
@@ -121,6 +126,76 @@ def main() -> None:
             torch.autograd.grad(y, (x, z, w), gy)
             _WidePrepFunction.apply(q, k, qb, kb, theta, gamma, scale)
             ops.ext().siso_prep_bwd(q, k, qb, kb, theta, gamma, scale, dqr, dkr, dqk)
+    elif args.case in ("chunk_bwd", "chunk_bwd_ssd"):
+        from lbi_b200.ops import ssd
+
+        per_head = args.case == "chunk_bwd"
+        b, reps, l, h, n = 1, 16, 1024, 24, 128
+        g = h if per_head else 1
+        v = torch.randn(b, l, h, 64, device=dev).bfloat16()
+        bk = (torch.randn(b, l, g, n, device=dev) * 0.4).bfloat16()
+        cq = (torch.randn(b, l, g, n, device=dev) * 0.4).bfloat16()
+        a = -(torch.rand(b, l, h, device=dev) * 0.08 + 0.002)
+        w = None if per_head else torch.rand(b, l, h, device=dev) * 0.1 + 0.01
+        skip = torch.randn(b, l, h, device=dev) if per_head else None
+        gy = torch.randn(reps * b, l, h, 64, device=dev).bfloat16()
+        _, _, states = ssd.scan_generic(v, bk, cq, a, w, None, strict=per_head, per_head=per_head)
+        for _ in range(args.repeats):
+            ssd.chunk_backward(v, gy, bk, cq, a, w, skip, states, per_head=per_head, strict=per_head, dv_bf16=per_head, dn_bf16=True)
+    elif args.case == "mamba_glue":
+        from lbi_b200.ops import mamba as mops
+
+        b, reps, l, h, s = 2, 8, 1024, 24, 32
+        n = b * l
+        y, z = torch.randn(n, 1536, device=dev).bfloat16(), torch.randn(n, 1536, device=dev).bfloat16()
+        dyg = torch.randn(reps * n, 1536, device=dev).bfloat16()
+        small = mops.siso_small_fwd(*(torch.randn(n, h, device=dev) for _ in range(3)), torch.randn(n, s, device=dev),
+                                    torch.randn(h, device=dev) - 2.0, 1e-4, b, l)
+        cots = [torch.randn(reps * b, l, h, device=dev) for _ in range(3)]
+        dtheta = torch.randn(reps * b, l, h, s, device=dev)
+        parts = (3072, 128, 128)
+        xc = torch.randn(n, sum(parts), device=dev).bfloat16()
+        wc, bc = torch.randn(sum(parts), 4, device=dev) * 0.5, torch.zeros(sum(parts), device=dev)
+        for _ in range(args.repeats):
+            mops.gate_silu_fwd(y, z)
+            mops.gate_silu_bwd(dyg, y, z)
+            mops.siso_small_fwd(*(torch.randn(n, h, device=dev) for _ in range(3)), torch.randn(n, s, device=dev),
+                                torch.randn(h, device=dev) - 2.0, 1e-4, b, l)
+            mops.siso_small_bwd(small, cots[0], dtheta, cots[1], cots[2], out_dtype=torch.bfloat16)
+            pre, acts = mops.conv_silu_fwd(xc, wc, bc, b, l, parts)
+            d = [torch.randn(reps * n, pp, device=dev).bfloat16() for pp in parts]
+            out = torch.empty(reps * n, sum(parts) + 64, device=dev).bfloat16()
+            mops.conv_silu_bwd(d, pre, wc, b, l, out, 64)
+            mops.conv_silu_wgrad([t[:n] for t in d], pre, xc, 4, b, l)
+    elif args.case == "small":
+        from lbi_b200.interfaces.vector_mlp import VectorMLPHead, head_forward_cached, head_input_jacobian_t, head_parameter_vjp
+
+        head = VectorMLPHead(1024, 128, 1024).cuda()
+        x = torch.randn(4, 1024, device=dev)
+        gbasis = torch.randn(4, 128, 128, device=dev)
+        sink = {id(p): torch.zeros_like(p) for p in head.parameters()}
+        mats = torch.randn(4, 7, 128, 128, device=dev) / 16
+        offs = torch.randn(4, 7, 128, device=dev)
+        table = torch.randn(32768, 1024, device=dev).bfloat16()
+        ids = torch.randint(0, 32768, (32768,), device=dev)
+        flat = torch.randn(64 * 1024 * 1024, device=dev)
+        m1, m2, sh = torch.zeros_like(flat), torch.zeros_like(flat), torch.zeros(flat.numel(), device=dev, dtype=torch.bfloat16)
+        sq = torch.zeros(1, device=dev)
+        normed = torch.randn(8192, 1024, device=dev).bfloat16()
+        tgt = torch.randint(0, 32768, (8192,), device=dev)
+        with torch.no_grad():
+            for _ in range(args.repeats):
+                yv, cache = head_forward_cached(head, x)
+                head_parameter_vjp(head, cache, torch.randn_like(yv), lambda p: sink[id(p)])
+                head_input_jacobian_t(head, x, gbasis)
+                ops.affine_suffix_scan(mats, offs, seed=offs[:, 0].contiguous())
+                ops.ext().matrix_norms(mats.reshape(-1, 128, 128), 8) if hasattr(ops.ext(), "matrix_norms") else None
+                rows = ops.embedding_fwd(ids, table, torch.bfloat16)
+                ops.embedding_scatter_add(torch.zeros(32768, 1024, device=dev), ids, rows)
+                ops.ext().sumsq_(flat, sq)
+                ops.ext().adamw_step_(flat, flat * 1e-3, m1, m2, sh, 1e-4, 0.9, 0.999, 1e-8, 0.01, 1, 1.0, sq, 1.0)
+                ops.lm_head_cross_entropy(normed, table, tgt, 1.0 / 8192)
+                ops.mean_pool_tokens(rows, 16, 2048)
     else:
         mats = torch.randn(8, 32, 256, 256, device=dev) / 16
         for _ in range(args.repeats):

@@ -22,6 +22,10 @@ int lbi_rmsnorm_wgrad(const void* d_normed_bf16, const float* x_stream, const fl
                       int64_t rows, int dim, int nblocks, cudaStream_t stream);
 int lbi_rope_qkv(void* qkv_bf16, const float* cos_tab, const float* sin_tab, int64_t rows, int n_rot_heads, int qkv_dim,
                  int head_dim, int seq_len, int interleaved, int inverse, cudaStream_t stream);
+// Grouped kv heads: packed rows [q (H heads) | k (Hkv) | v (Hkv)] -> [q | k | v] with H heads each (expand), and the sum of the
+// cotangents of a group's copies back to the packed layout (reduce).  bf16, head_dim a multiple of 8.
+int lbi_gqa_expand(const void* in_bf16, void* out_bf16, int64_t rows, int heads, int kv_heads, int head_dim, cudaStream_t stream);
+int lbi_gqa_reduce(const void* in_bf16, void* out_bf16, int64_t rows, int heads, int kv_heads, int head_dim, cudaStream_t stream);
 int lbi_swiglu_fwd(const void* u_bf16, void* a_bf16, int64_t rows, int hidden, cudaStream_t stream);
 int lbi_swiglu_bwd(const void* da_bf16, const void* u_bf16, void* du_bf16, int64_t rows, int64_t act_rows, int hidden,
                    cudaStream_t stream);

@@ -19,12 +19,13 @@ extern "C" {
 // Launches three kernels on `stream` (row dots, dK/dV, dQ).  Returns 0 or a cudaError_t / 1000 + CUresult.
 int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const float* lse, void* d_qkv, float* delta,
                       int batch, int heads, int seq_len, int head_dim, int nbasis, float scale, const float* rope_cos,
-                      const float* rope_sin, int rope_interleaved, int* status, cudaStream_t stream);
+                      const float* rope_sin, int rope_interleaved, int is_fp16, int* status, cudaStream_t stream);
 
 // Causal flash-attention forward (attn_fwd.cu), same layout and limits as above:
 //   out bf16 [B*T, H*64], lse fp32 [B, H, T].  One kernel on `stream`.
+// is_fp16 (both entry points): the 16-bit tensors are fp16 instead of bf16 (the reference kernel's only dtype).
 int lbi_attn_fwd(const void* qkv, void* out, float* lse, int batch, int heads, int seq_len, int head_dim, float scale,
-                 int* status, cudaStream_t stream);
+                 int is_fp16, int* status, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

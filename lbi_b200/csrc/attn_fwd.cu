@@ -61,11 +61,23 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// F16 = false: bf16 operands and output; true: fp16.  Accumulation is fp32 either way.
+template <bool F16>
+__device__ __forceinline__ uint32_t pack_lp(float a, float b) {
+  uint32_t d;
+  if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  return d;
+}
+__host__ __device__ constexpr uint32_t make_idesc_lp(int m, int n, int a_mn_major, int b_mn_major, bool f16) {
+  return f16 ? (make_idesc_bf16(m, n, a_mn_major, b_mn_major) & ~((1u << 7) | (1u << 10))) : make_idesc_bf16(m, n, a_mn_major, b_mn_major);
+}
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
 }
 
+template <bool F16>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const Params p) {
   extern __shared__ uint8_t raw_smem[];
@@ -127,8 +139,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const Params p) {
   } else if (warp == 9) {
     // ======================================================================== MMA issuer
     if (lane == 0) {
-      const uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);   // Q (K-major) x K (K-major)
-      const uint32_t idesc_o = make_idesc_bf16(128, 64, 0, 1);    // P (K-major) x V (MN-major: rows are the key index)
+      const uint32_t idesc_s = make_idesc_lp(128, 128, 0, 0, F16);   // Q (K-major) x K (K-major)
+      const uint32_t idesc_o = make_idesc_lp(128, 64, 0, 1, F16);    // P (K-major) x V (MN-major: rows are the key index)
       const uint64_t kmajor0 = make_smem_desc(0, 16, 1024);
       const uint64_t mnmajor0 = make_smem_desc(0, PANEL_BYTES, 1024);
       const uint32_t q16 = smem_u32(s.q[0]) >> 4, k16 = smem_u32(s.k[0]) >> 4, v16 = smem_u32(s.v[0]) >> 4;
@@ -226,7 +238,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const Params p) {
                 if (c * 32 + e + 1 > row) bb = 0.f;
               }
               sum += a + bb;
-              w[e2] = pack2(a, bb);
+              w[e2] = pack_lp<F16>(a, bb);
             }
             const int chunk = (c & 1) * 4 + q4;
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(panel + ((chunk ^ (row & 7)) << 4)), "r"(w[0]),
@@ -263,10 +275,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_qkv, const Params p) {
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
           uint4 vv;
-          vv.x = pack2(acc[8 * c] * inv, acc[8 * c + 1] * inv);
-          vv.y = pack2(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
-          vv.z = pack2(acc[8 * c + 4] * inv, acc[8 * c + 5] * inv);
-          vv.w = pack2(acc[8 * c + 6] * inv, acc[8 * c + 7] * inv);
+          vv.x = pack_lp<F16>(acc[8 * c] * inv, acc[8 * c + 1] * inv);
+          vv.y = pack_lp<F16>(acc[8 * c + 2] * inv, acc[8 * c + 3] * inv);
+          vv.z = pack_lp<F16>(acc[8 * c + 4] * inv, acc[8 * c + 5] * inv);
+          vv.w = pack_lp<F16>(acc[8 * c + 6] * inv, acc[8 * c + 7] * inv);
           dst[c] = vv;
         }
         p.lse[((int64_t)b * p.heads + h) * p.seq_len + i_g * TILE + row] = (m_run + log2f(l_run)) * 0.6931471805599453f;
@@ -310,7 +322,7 @@ static EncodeTiledFn encode_fn() {
 }  // namespace lbi
 
 extern "C" int lbi_attn_fwd(const void* qkv, void* out, float* lse, int batch, int heads, int seq_len, int head_dim,
-                            float scale, int* status, cudaStream_t st) {
+                            float scale, int is_fp16, int* status, cudaStream_t st) {
   using namespace lbi::attn_fwd;
   if (head_dim != DH || seq_len % TILE != 0 || batch <= 0 || heads <= 0) return (int)cudaErrorInvalidValue;
   const int64_t n_rows = (int64_t)batch * seq_len;
@@ -323,7 +335,7 @@ extern "C" int lbi_attn_fwd(const void* qkv, void* out, float* lse, int batch, i
   cuuint64_t strides[1] = {(cuuint64_t)width * 2};
   cuuint32_t box[2] = {DH, TILE};
   cuuint32_t estr[2] = {1, 1};
-  CUresult rc = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides, box, estr,
+  CUresult rc = fn(&map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return 1000 + (int)rc;
@@ -332,12 +344,14 @@ extern "C" int lbi_attn_fwd(const void* qkv, void* out, float* lse, int batch, i
   p.scale_log2 = scale * 1.4426950408889634f;
   p.out = (__nv_bfloat16*)out; p.lse = lse; p.status = status;
   const size_t smem = sizeof(Smem) + 1024;
-  static lbi::PerDeviceOnce configured;
+  static lbi::PerDeviceOnce configured, configured_bf16;
   {
-    cudaError_t e = configured.max_dynamic_smem(attn_fwd_kernel, (int)smem);
+    cudaError_t e = is_fp16 ? configured.max_dynamic_smem(attn_fwd_kernel<true>, (int)smem)
+                            : configured_bf16.max_dynamic_smem(attn_fwd_kernel<false>, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid((p.n_tiles + 1) / 2, batch * heads);
-  attn_fwd_kernel<<<grid, THREADS, smem, st>>>(map, p);
+  if (is_fp16) attn_fwd_kernel<true><<<grid, THREADS, smem, st>>>(map, p);
+  else attn_fwd_kernel<false><<<grid, THREADS, smem, st>>>(map, p);
   return (int)cudaGetLastError();
 }

@@ -35,6 +35,7 @@
 // arithmetic + about twenty tcgen05.mma per job) was measured to be the bottleneck.  Every mbarrier wait is bounded
 // (tcgen05.cuh); all barrier parities are derived from job / tile counters.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include <mutex>
 
@@ -107,6 +108,14 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
   return v;
 }
+// F16 = false: bf16 operands and results; true: fp16 (the reference kernel's only dtype).  Accumulation is fp32 either way.
+template <bool F16>
+__device__ __forceinline__ uint32_t pack_lp(float a, float b) {
+  uint32_t d;
+  if (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&t);
@@ -141,15 +150,23 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
-__device__ __forceinline__ uint32_t cvt_bf16x2(uint64_t v) {   // {lo, hi} fp32 -> bf16 pair, lo in the low half
+template <bool F16>
+__device__ __forceinline__ uint32_t cvt_lp_x2(uint64_t v) {   // {lo, hi} fp32 -> 16-bit pair, lo in the low half
   uint32_t d;
-  asm("{\n.reg .f32 lo, hi;\nmov.b64 {lo, hi}, %1;\ncvt.rn.bf16x2.f32 %0, hi, lo;\n}" : "=r"(d) : "l"(v));
+  if (F16) asm("{\n.reg .f32 lo, hi;\nmov.b64 {lo, hi}, %1;\ncvt.rn.f16x2.f32 %0, hi, lo;\n}" : "=r"(d) : "l"(v));
+  else asm("{\n.reg .f32 lo, hi;\nmov.b64 {lo, hi}, %1;\ncvt.rn.bf16x2.f32 %0, hi, lo;\n}" : "=r"(d) : "l"(v));
   return d;
 }
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+template <bool F16>
+__device__ __forceinline__ uint32_t mul_lp_x2(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  if (F16) asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  else asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
+}
+// kind::f16 instruction descriptor with fp32 D and bf16 or fp16 A / B
+__host__ __device__ constexpr uint32_t make_idesc_lp(int m, int n, int a_mn_major, int b_mn_major, bool f16) {
+  return f16 ? (make_idesc_bf16(m, n, a_mn_major, b_mn_major) & ~((1u << 7) | (1u << 10))) : make_idesc_bf16(m, n, a_mn_major, b_mn_major);
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -157,7 +174,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-template <bool DKDV>
+template <bool DKDV, bool F16>
 __global__ void __launch_bounds__(THREADS, 1)
 pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_constant__ CUtensorMap map_do,
                 const __grid_constant__ CUtensorMap map_out, const Params p) {
@@ -279,7 +296,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   } else if (warp == 16) {
     // ======================================================================== issuer X: S and dP products
     if (lane == 0) {
-      const uint32_t idesc_nn = make_idesc_bf16(128, 128, 0, 0);
+      const uint32_t idesc_nn = make_idesc_lp(128, 128, 0, 0, F16);
       bool ok = true;
       ok = mbar_wait(&s.bar_fixed, 0, abortp, p.status, 16);
       int it = 0, r = 0, c = 0;   // step, job within the step (0 = S, 1.. = dP of direction r - 1), dO tile index
@@ -318,8 +335,8 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
   } else if (warp == 17) {
     // ======================================================================== issuer Y: accumulating products, releases
     if (lane == 0) {
-      const uint32_t idesc_acc = DKDV ? make_idesc_bf16(128, 64, 1, 1) : make_idesc_bf16(128, 64, 0, 1);
-      const uint32_t idesc_dv2 = make_idesc_bf16(128, 128, 1, 1);  // dV of two directions in one instruction
+      const uint32_t idesc_acc = DKDV ? make_idesc_lp(128, 64, 1, 1, F16) : make_idesc_lp(128, 64, 0, 1, F16);
+      const uint32_t idesc_dv2 = make_idesc_lp(128, 128, 1, 1, F16);  // dV of two directions in one instruction
       const uint32_t ds0 = smem_u32(s.ds_tile[0][0]) >> 4, p16 = smem_u32(s.p_tile[0]) >> 4;
       constexpr uint32_t DSBUF16 = (2 * PANEL_BYTES) >> 4, PANEL16 = PANEL_BYTES >> 4;
       bool ok = true;
@@ -429,7 +446,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float2 t = unpack_f32x2(fma_f32x2(pack_u32x2(v[2 * i], v[2 * i + 1]), sc2, nl2));
-            preg[i] = cvt_bf16x2(pack_f32x2(fast_exp2(t.x), fast_exp2(t.y)));
+            preg[i] = cvt_lp_x2<F16>(pack_f32x2(fast_exp2(t.x), fast_exp2(t.y)));
           }
           if (diagonal) {   // warp-uniform: only the tile on the diagonal pays for the causal mask
 #pragma unroll
@@ -467,8 +484,8 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
             uint32_t w[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              w[e] = mul_bf16x2(preg[g * 4 + e],
-                                cvt_bf16x2(sub_f32x2(pack_u32x2(v[g * 8 + e * 2], v[g * 8 + e * 2 + 1]), delta2)));
+              w[e] = mul_lp_x2<F16>(preg[g * 4 + e],
+                                    cvt_lp_x2<F16>(sub_f32x2(pack_u32x2(v[g * 8 + e * 2], v[g * 8 + e * 2 + 1]), delta2)));
             }
             st_shared_v4(swz(ds_panel, r, (slice & 1) * 4 + g), make_uint4(w[0], w[1], w[2], w[3]));
           }
@@ -507,14 +524,14 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 o, o2;
-            o.x = pack_bf16(__uint_as_float(lo[g * 8 + 0]) * mul, __uint_as_float(lo[g * 8 + 1]) * mul);
-            o.y = pack_bf16(__uint_as_float(lo[g * 8 + 2]) * mul, __uint_as_float(lo[g * 8 + 3]) * mul);
-            o.z = pack_bf16(__uint_as_float(lo[g * 8 + 4]) * mul, __uint_as_float(lo[g * 8 + 5]) * mul);
-            o.w = pack_bf16(__uint_as_float(lo[g * 8 + 6]) * mul, __uint_as_float(lo[g * 8 + 7]) * mul);
-            o2.x = pack_bf16(__uint_as_float(hi[g * 8 + 0]) * mul, __uint_as_float(hi[g * 8 + 1]) * mul);
-            o2.y = pack_bf16(__uint_as_float(hi[g * 8 + 2]) * mul, __uint_as_float(hi[g * 8 + 3]) * mul);
-            o2.z = pack_bf16(__uint_as_float(hi[g * 8 + 4]) * mul, __uint_as_float(hi[g * 8 + 5]) * mul);
-            o2.w = pack_bf16(__uint_as_float(hi[g * 8 + 6]) * mul, __uint_as_float(hi[g * 8 + 7]) * mul);
+            o.x = pack_lp<F16>(__uint_as_float(lo[g * 8 + 0]) * mul, __uint_as_float(lo[g * 8 + 1]) * mul);
+            o.y = pack_lp<F16>(__uint_as_float(lo[g * 8 + 2]) * mul, __uint_as_float(lo[g * 8 + 3]) * mul);
+            o.z = pack_lp<F16>(__uint_as_float(lo[g * 8 + 4]) * mul, __uint_as_float(lo[g * 8 + 5]) * mul);
+            o.w = pack_lp<F16>(__uint_as_float(lo[g * 8 + 6]) * mul, __uint_as_float(lo[g * 8 + 7]) * mul);
+            o2.x = pack_lp<F16>(__uint_as_float(hi[g * 8 + 0]) * mul, __uint_as_float(hi[g * 8 + 1]) * mul);
+            o2.y = pack_lp<F16>(__uint_as_float(hi[g * 8 + 2]) * mul, __uint_as_float(hi[g * 8 + 3]) * mul);
+            o2.z = pack_lp<F16>(__uint_as_float(hi[g * 8 + 4]) * mul, __uint_as_float(hi[g * 8 + 5]) * mul);
+            o2.w = pack_lp<F16>(__uint_as_float(hi[g * 8 + 6]) * mul, __uint_as_float(hi[g * 8 + 7]) * mul);
             put(g, o);
             put(4 + g, o2);
           }
@@ -536,8 +553,8 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
                   ob[q * 4 + e] = xb * cc[e] - xa * ss[e];
                 }
               }
-              put(g, make_uint4(pack_bf16(oa[0], oa[1]), pack_bf16(oa[2], oa[3]), pack_bf16(oa[4], oa[5]), pack_bf16(oa[6], oa[7])));
-              put(4 + g, make_uint4(pack_bf16(ob[0], ob[1]), pack_bf16(ob[2], ob[3]), pack_bf16(ob[4], ob[5]), pack_bf16(ob[6], ob[7])));
+              put(g, make_uint4(pack_lp<F16>(oa[0], oa[1]), pack_lp<F16>(oa[2], oa[3]), pack_lp<F16>(oa[4], oa[5]), pack_lp<F16>(oa[6], oa[7])));
+              put(4 + g, make_uint4(pack_lp<F16>(ob[0], ob[1]), pack_lp<F16>(ob[2], ob[3]), pack_lp<F16>(ob[4], ob[5]), pack_lp<F16>(ob[6], ob[7])));
             }
           } else {                     // pairs (2 i, 2 i + 1), angle index i
 #pragma unroll
@@ -554,7 +571,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
                   o[2 * e] = xa * cc[e] + xb * ss[e];
                   o[2 * e + 1] = xb * cc[e] - xa * ss[e];
                 }
-                put(hh * 4 + g, make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7])));
+                put(hh * 4 + g, make_uint4(pack_lp<F16>(o[0], o[1]), pack_lp<F16>(o[2], o[3]), pack_lp<F16>(o[4], o[5]), pack_lp<F16>(o[6], o[7])));
               }
             }
           }
@@ -586,6 +603,7 @@ pullback_kernel(const __grid_constant__ CUtensorMap map_qkv, const __grid_consta
 }
 
 // delta[p, b, h, t] = sum_d dO[(p, b, t), h * Dh + d] * O[(b, t), h * Dh + d]; one warp per (row, head).
+template <bool F16>
 __global__ void delta_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_bfloat16* __restrict__ o,
                              float* __restrict__ delta, int64_t rows_total, int64_t n_rows, int batch, int heads,
                              int seq_len) {
@@ -596,9 +614,14 @@ __global__ void delta_kernel(const __nv_bfloat16* __restrict__ d_o, const __nv_b
   const int64_t row = gw / heads;          // (p * B + b) * T + t
   const int64_t arow = row % n_rows;       // b * T + t
   const int hd = heads * DH;
-  const __nv_bfloat162 a = reinterpret_cast<const __nv_bfloat162*>(d_o + row * hd + h * DH)[lane];
-  const __nv_bfloat162 c = reinterpret_cast<const __nv_bfloat162*>(o + arow * hd + h * DH)[lane];
-  const float2 af = __bfloat1622float2(a), cf = __bfloat1622float2(c);
+  float2 af, cf;
+  if (F16) {
+    af = __half22float2(reinterpret_cast<const __half2*>(d_o + row * hd + h * DH)[lane]);
+    cf = __half22float2(reinterpret_cast<const __half2*>(o + arow * hd + h * DH)[lane]);
+  } else {
+    af = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(d_o + row * hd + h * DH)[lane]);
+    cf = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(o + arow * hd + h * DH)[lane]);
+  }
   float acc = af.x * cf.x + af.y * cf.y;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
@@ -628,30 +651,30 @@ static EncodeTiledFn encode_fn() {
 }
 
 // [rows, width] bf16 row-major, tiles of 128 rows x 64 columns, 128-byte swizzle
-static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t width) {
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t width, int f16 = 0) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return 801;
   cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)width * 2};
   cuuint32_t box[2] = {DH, TILE};
   cuuint32_t estr[2] = {1, 1};
-  CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult rc = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
 }
 
-template <bool DKDV>
+template <bool DKDV, bool F16>
 static int launch(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMap& mo, const Params& p, cudaStream_t st) {
   constexpr int PB = DKDV ? PB_DKDV : PB_DQ;
   const size_t smem = sizeof(Smem<DKDV>) + 1024;
   static lbi::PerDeviceOnce configured;
   {
-    cudaError_t e = configured.max_dynamic_smem(pullback_kernel<DKDV>, (int)smem);
+    cudaError_t e = configured.max_dynamic_smem(pullback_kernel<DKDV, F16>, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(p.n_tiles, p.batch * p.heads, (p.nbasis + PB - 1) / PB);
-  pullback_kernel<DKDV><<<grid, THREADS, smem, st>>>(mq, md, mo, p);
+  pullback_kernel<DKDV, F16><<<grid, THREADS, smem, st>>>(mq, md, mo, p);
   return (int)cudaGetLastError();
 }
 
@@ -660,7 +683,7 @@ static int launch(const CUtensorMap& mq, const CUtensorMap& md, const CUtensorMa
 
 extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o, const float* lse, void* d_qkv,
                                  float* delta, int batch, int heads, int seq_len, int head_dim, int nbasis, float scale,
-                                 const float* rope_cos, const float* rope_sin, int rope_interleaved, int* status,
+                                 const float* rope_cos, const float* rope_sin, int rope_interleaved, int is_fp16, int* status,
                                  cudaStream_t st) {
   using namespace lbi::attn;
   if (head_dim != DH || seq_len % TILE != 0 || batch <= 0 || heads <= 0 || nbasis <= 0) return (int)cudaErrorInvalidValue;
@@ -671,17 +694,21 @@ extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o
     const int64_t warps = rows_total * heads;
     const int threads = 256;
     const int64_t blocks = (warps * 32 + threads - 1) / threads;
-    delta_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta,
-                                                       rows_total, n_rows, batch, heads, seq_len);
+    if (is_fp16)
+      delta_kernel<true><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta, rows_total,
+                                                               n_rows, batch, heads, seq_len);
+    else
+      delta_kernel<false><<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)d_o, (const __nv_bfloat16*)o, delta, rows_total,
+                                                                n_rows, batch, heads, seq_len);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
   }
   CUtensorMap mq, md, mo;
-  int rc = make_map(&mq, qkv, n_rows, 3ll * heads * DH);
+  int rc = make_map(&mq, qkv, n_rows, 3ll * heads * DH, is_fp16);
   if (rc) return rc;
-  rc = make_map(&md, d_o, rows_total, (int64_t)heads * DH);
+  rc = make_map(&md, d_o, rows_total, (int64_t)heads * DH, is_fp16);
   if (rc) return rc;
-  rc = make_map(&mo, d_qkv, rows_total, 3ll * heads * DH);
+  rc = make_map(&mo, d_qkv, rows_total, 3ll * heads * DH, is_fp16);
   if (rc) return rc;
   Params p;
   p.batch = batch; p.heads = heads; p.seq_len = seq_len; p.nbasis = nbasis;
@@ -694,7 +721,12 @@ extern "C" int lbi_attn_pullback(const void* qkv, const void* d_o, const void* o
   p.d_qkv = (__nv_bfloat16*)d_qkv;
   p.rope_cos = rope_cos; p.rope_sin = rope_sin; p.rope_interleaved = rope_interleaved;
   p.status = status;
-  rc = launch<true>(mq, md, mo, p, st);
+  if (is_fp16) {
+    rc = launch<true, true>(mq, md, mo, p, st);
+    if (rc) return rc;
+    return launch<false, true>(mq, md, mo, p, st);
+  }
+  rc = launch<true, false>(mq, md, mo, p, st);
   if (rc) return rc;
-  return launch<false>(mq, md, mo, p, st);
+  return launch<false, false>(mq, md, mo, p, st);
 }

@@ -20,6 +20,7 @@ void check(int rc, const char* what) {
 }
 
 #define CHECK_BF16(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kBFloat16 && (x).is_contiguous(), #x " must be a contiguous CUDA bf16 tensor")
+#define CHECK_LP16(x) TORCH_CHECK((x).is_cuda() && ((x).scalar_type() == at::kBFloat16 || (x).scalar_type() == at::kHalf) && (x).is_contiguous(), #x " must be a contiguous CUDA bf16 / fp16 tensor")
 #define CHECK_F32(x) TORCH_CHECK((x).is_cuda() && (x).scalar_type() == at::kFloat && (x).is_contiguous(), #x " must be a contiguous CUDA fp32 tensor")
 
 Tensor status_word(const Tensor& like) {
@@ -117,6 +118,24 @@ Tensor rope_qkv_(Tensor qkv, const Tensor& cos_tab, const Tensor& sin_tab, int64
                      inverse ? 1 : 0, cur_stream()),
         "rope_qkv");
   return qkv;
+}
+
+Tensor gqa_expand(const Tensor& qkv, int64_t heads, int64_t kv_heads, int64_t head_dim) {
+  CHECK_BF16(qkv);
+  c10::cuda::CUDAGuard guard(qkv.device());
+  TORCH_CHECK(qkv.dim() == 2 && qkv.size(1) == (heads + 2 * kv_heads) * head_dim, "gqa_expand: packed rows [q | k | v]");
+  Tensor out = torch::empty({qkv.size(0), 3 * heads * head_dim}, qkv.options());
+  check(lbi_gqa_expand(qkv.data_ptr(), out.data_ptr(), qkv.size(0), (int)heads, (int)kv_heads, (int)head_dim, cur_stream()), "gqa_expand");
+  return out;
+}
+
+Tensor gqa_reduce(const Tensor& d_qkv, int64_t heads, int64_t kv_heads, int64_t head_dim) {
+  CHECK_BF16(d_qkv);
+  c10::cuda::CUDAGuard guard(d_qkv.device());
+  TORCH_CHECK(d_qkv.dim() == 2 && d_qkv.size(1) == 3 * heads * head_dim, "gqa_reduce: rows [q | k | v] with H heads each");
+  Tensor out = torch::empty({d_qkv.size(0), (heads + 2 * kv_heads) * head_dim}, d_qkv.options());
+  check(lbi_gqa_reduce(d_qkv.data_ptr(), out.data_ptr(), d_qkv.size(0), (int)heads, (int)kv_heads, (int)head_dim, cur_stream()), "gqa_reduce");
+  return out;
 }
 
 Tensor swiglu_fwd(const Tensor& u) {
@@ -687,10 +706,11 @@ Tensor gemm_tn(const Tensor& a, const Tensor& b, bool out_fp32, const c10::optio
 Tensor attn_pullback_packed(const Tensor& d_o, const Tensor& qkv, const Tensor& o, const Tensor& lse, int64_t batch,
                             int64_t seq_len, int64_t heads, int64_t head_dim, double scale,
                             const c10::optional<Tensor>& rope_cos, const c10::optional<Tensor>& rope_sin, bool rope_interleaved) {
-  CHECK_BF16(d_o);
-  CHECK_BF16(qkv);
-  CHECK_BF16(o);
+  CHECK_LP16(d_o);
+  CHECK_LP16(qkv);
+  CHECK_LP16(o);
   CHECK_F32(lse);
+  TORCH_CHECK(d_o.scalar_type() == qkv.scalar_type() && o.scalar_type() == qkv.scalar_type(), "attn_pullback: d_o, qkv, o must share a dtype");
   c10::cuda::CUDAGuard guard(d_o.device());
   const int64_t n = batch * seq_len;
   TORCH_CHECK(qkv.size(0) == n && qkv.size(1) == 3 * heads * head_dim, "qkv shape mismatch");
@@ -713,14 +733,15 @@ Tensor attn_pullback_packed(const Tensor& d_o, const Tensor& qkv, const Tensor& 
   Tensor st = status_word(d_o);
   check(lbi_attn_pullback(qkv.data_ptr(), d_o.data_ptr(), o.data_ptr(), lse.data_ptr<float>(), d_qkv.data_ptr(),
                           delta.data_ptr<float>(), (int)batch, (int)heads, (int)seq_len, (int)head_dim, (int)nbasis,
-                          (float)scale, cos_p, sin_p, rope_interleaved ? 1 : 0, st.data_ptr<int>(), cur_stream()),
+                          (float)scale, cos_p, sin_p, rope_interleaved ? 1 : 0, qkv.scalar_type() == at::kHalf ? 1 : 0, st.data_ptr<int>(),
+                          cur_stream()),
         "attn_pullback");
   return d_qkv;
 }
 
 std::tuple<Tensor, Tensor> attn_fwd_packed(const Tensor& qkv, int64_t batch, int64_t seq_len, int64_t heads, int64_t head_dim,
                                            double scale) {
-  CHECK_BF16(qkv);
+  CHECK_LP16(qkv);
   c10::cuda::CUDAGuard guard(qkv.device());
   const int64_t n = batch * seq_len;
   TORCH_CHECK(qkv.dim() == 2 && qkv.size(0) == n && qkv.size(1) == 3 * heads * head_dim, "qkv shape mismatch");
@@ -728,7 +749,7 @@ std::tuple<Tensor, Tensor> attn_fwd_packed(const Tensor& qkv, int64_t batch, int
   Tensor lse = torch::empty({batch, heads, seq_len}, qkv.options().dtype(at::kFloat));
   Tensor st = status_word(qkv);
   check(lbi_attn_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr<float>(), (int)batch, (int)heads, (int)seq_len, (int)head_dim,
-                     (float)scale, st.data_ptr<int>(), cur_stream()),
+                     (float)scale, qkv.scalar_type() == at::kHalf ? 1 : 0, st.data_ptr<int>(), cur_stream()),
         "attn_fwd");
   return {out, lse};
 }
@@ -1153,6 +1174,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd_lowp", &rmsnorm_bwd_lowp);
   m.def("rmsnorm_wgrad", &rmsnorm_wgrad);
   m.def("rope_qkv_", &rope_qkv_);
+  m.def("gqa_expand", &gqa_expand);
+  m.def("gqa_reduce", &gqa_reduce);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("add_condition", &add_condition);

@@ -343,6 +343,49 @@ __global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, __nv
   }
 }
 
+// ------------------------------------------------------------------------------------------------ grouped kv heads
+// Grouped-query attention on kernels that take one k / v head per q head: expand copies kv head h / group for q head h
+// (packed rows [q | k | v] with H, Hkv, Hkv heads -> H, H, H heads); reduce sums the cotangents of the group's copies back
+// (and copies the q part through).  16-byte pieces, head_dim a multiple of 8.
+__global__ void gqa_expand_kernel(const bf16x8* __restrict__ in, bf16x8* __restrict__ out, int64_t rows, int heads, int kv_heads,
+                                  int dvec) {
+  const int group = heads / kv_heads;
+  const int out_w = 3 * heads * dvec, in_w = (heads + 2 * kv_heads) * dvec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * out_w; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / out_w;
+    const int c = (int)(i - row * out_w);
+    const int part = c / (heads * dvec), within = c - part * heads * dvec;
+    const int h = within / dvec, d = within - h * dvec;
+    const int src = part == 0 ? within : heads * dvec + (part - 1) * kv_heads * dvec + (h / group) * dvec + d;
+    out[i] = in[row * in_w + src];
+  }
+}
+
+__global__ void gqa_reduce_kernel(const bf16x8* __restrict__ in, bf16x8* __restrict__ out, int64_t rows, int heads, int kv_heads,
+                                  int dvec) {
+  const int group = heads / kv_heads;
+  const int in_w = 3 * heads * dvec, out_w = (heads + 2 * kv_heads) * dvec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < rows * out_w; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / out_w;
+    const int c = (int)(i - row * out_w);
+    if (c < heads * dvec) {
+      out[i] = in[row * in_w + c];
+      continue;
+    }
+    const int rest = c - heads * dvec;
+    const int part = rest / (kv_heads * dvec), within = rest - part * kv_heads * dvec;
+    const int kh = within / dvec, d = within - kh * dvec;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int g = 0; g < group; ++g) {
+      float v[8];
+      unpack8(in[row * in_w + (1 + part) * heads * dvec + (kh * group + g) * dvec + d], v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += v[e];
+    }
+    out[i] = pack8(acc);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ causal conv
 // y[s, t, c] = bias[c] + sum_w w[c, w] * x[s, t - (W-1) + w, c]
 __global__ void causal_conv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
@@ -587,6 +630,24 @@ int lbi_transpose_bf16(const void* in, void* out, int64_t rows, int64_t cols, cu
   if (rows == 0 || cols == 0) return 0;
   dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
   transpose_bf16_kernel<<<grid, dim3(32, 8), 0, st>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, cols);
+  return launch_status();
+}
+
+int lbi_gqa_expand(const void* in, void* out, int64_t rows, int heads, int kv_heads, int head_dim, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || head_dim % 8 != 0) return (int)cudaErrorInvalidValue;
+  const int64_t total = rows * 3 * heads * (head_dim / 8);
+  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  gqa_expand_kernel<<<blocks, 256, 0, st>>>((const bf16x8*)in, (bf16x8*)out, rows, heads, kv_heads, head_dim / 8);
+  return launch_status();
+}
+
+int lbi_gqa_reduce(const void* in, void* out, int64_t rows, int heads, int kv_heads, int head_dim, cudaStream_t st) {
+  if (rows == 0) return 0;
+  if (heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || head_dim % 8 != 0) return (int)cudaErrorInvalidValue;
+  const int64_t total = rows * (heads + 2 * kv_heads) * (head_dim / 8);
+  int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  gqa_reduce_kernel<<<blocks, 256, 0, st>>>((const bf16x8*)in, (bf16x8*)out, rows, heads, kv_heads, head_dim / 8);
   return launch_status();
 }
 

@@ -290,35 +290,36 @@ __device__ __forceinline__ float dsilu_(float v) {
   return s * (1.f + v * (1.f - s));
 }
 
-__global__ void __launch_bounds__(256) conv_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+// grid (tokens), block 128: a block owns one token, its threads walk the 8-channel vectors (no 64-bit divisions per element).
+__global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                                                             const float* __restrict__ bias, __nv_bfloat16* __restrict__ pre,
                                                             __nv_bfloat16* __restrict__ o0, __nv_bfloat16* __restrict__ o1,
                                                             __nv_bfloat16* __restrict__ o2, Seg seg, int64_t tokens, int seq_len,
                                                             int width) {
   const int channels = seg.c0 + seg.c1 + seg.c2, cvecs = channels / 8;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= tokens * cvecs) return;
-  const int cv = (int)(idx % cvecs), c = cv * 8;
-  const int64_t tok = idx / cvecs;
+  const int64_t tok = blockIdx.x;
   const int t = (int)(tok % seq_len);
-  float acc[8];
+  const int k_lo = max(0, (width - 1) - t);   // taps that reach before the first token of the sequence are skipped
+  for (int cv = threadIdx.x; cv < cvecs; cv += blockDim.x) {
+    const int c = cv * 8;
+    float acc[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
-  for (int k = 0; k < width; ++k) {
-    const int tt = t - (width - 1) + k;
-    if (tt < 0) continue;
-    if (!LBI_IN_RANGE(tok + (tt - t), tokens, 91)) continue;
-    float xv[8];
-    unpack8(*reinterpret_cast<const bf16x8*>(x + (tok + (tt - t)) * channels + c), xv);
+    for (int e = 0; e < 8; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+    for (int k = k_lo; k < width; ++k) {
+      const int64_t src = tok - (width - 1) + k;
+      if (!LBI_IN_RANGE(src, tokens, 91)) continue;
+      float xv[8];
+      unpack8(*reinterpret_cast<const bf16x8*>(x + src * channels + c), xv);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], xv[e], acc[e]);
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], xv[e], acc[e]);
+    }
+    *reinterpret_cast<bf16x8*>(pre + tok * channels + c) = pack8(acc);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = silu_(acc[e]);
+    __nv_bfloat16* dst = c < seg.c0 ? o0 + tok * seg.c0 + c
+                                    : (c < seg.c0 + seg.c1 ? o1 + tok * seg.c1 + (c - seg.c0) : o2 + tok * seg.c2 + (c - seg.c0 - seg.c1));
+    *reinterpret_cast<bf16x8*>(dst) = pack8(acc);
   }
-  *reinterpret_cast<bf16x8*>(pre + tok * channels + c) = pack8(acc);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = silu_(acc[e]);
-  __nv_bfloat16* dst = c < seg.c0 ? o0 + tok * seg.c0 + c
-                                  : (c < seg.c0 + seg.c1 ? o1 + tok * seg.c1 + (c - seg.c0) : o2 + tok * seg.c2 + (c - seg.c0 - seg.c1));
-  *reinterpret_cast<bf16x8*>(dst) = pack8(acc);
 }
 
 template <typename D0>
@@ -347,28 +348,28 @@ __device__ __forceinline__ void dpre8(const D0* d0, const D12* d1, const D12* d2
 }
 
 template <typename D0, typename D12>
-__global__ void __launch_bounds__(256) conv_silu_bwd_kernel(const D0* __restrict__ d0, const D12* __restrict__ d1,
+__global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const D0* __restrict__ d0, const D12* __restrict__ d1,
                                                             const D12* __restrict__ d2, const __nv_bfloat16* __restrict__ pre,
                                                             const float* __restrict__ w, __nv_bfloat16* __restrict__ din, int64_t ld_in,
                                                             Seg seg, int64_t tokens, int64_t ftokens, int seq_len, int width) {
   const int channels = seg.c0 + seg.c1 + seg.c2, cvecs = channels / 8;
-  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= tokens * cvecs) return;
-  const int cv = (int)(idx % cvecs), c = cv * 8;
-  const int64_t tok = idx / cvecs;
-  const int t = (int)(tok % seq_len);
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  for (int k = 0; k < width; ++k) {
-    const int tt = t + (width - 1) - k;
-    if (tt >= seq_len) continue;
-    float dp[8];
-    const int64_t tk = tok + (tt - t);
-    if (!LBI_IN_RANGE(tk, tokens, 92)) continue;
-    dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tk, tk % ftokens, c, dp);
+  const int64_t tok = blockIdx.x;
+  const int64_t ftok = tok % ftokens;         // once per block
+  const int t = (int)(ftok % seq_len);
+  const int k_lo = max(0, (width - 1) - (seq_len - 1 - t));   // taps that reach past the last token of the sequence are skipped
+  for (int cv = threadIdx.x; cv < cvecs; cv += blockDim.x) {
+    const int c = cv * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = k_lo; k < width; ++k) {
+      const int shift = (width - 1) - k;
+      if (!LBI_IN_RANGE(tok + shift, tokens, 92)) continue;
+      float dp[8];
+      dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tok + shift, ftok + shift, c, dp);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], dp[e], acc[e]);
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], dp[e], acc[e]);
+    }
+    *reinterpret_cast<bf16x8*>(din + tok * ld_in + c) = pack8(acc);
   }
-  *reinterpret_cast<bf16x8*>(din + tok * ld_in + c) = pack8(acc);
 }
 
 // grid (cvecs blocks of 32 lanes x 8 token runs per block, runs); every thread walks RUN tokens of its eight channels
@@ -427,8 +428,8 @@ extern "C" int lbi_conv_silu_fwd(const void* x, const float* w, const float* bia
   if (tokens <= 0) return 0;
   if (c0 % 8 || c1 % 8 || c2 % 8 || c0 + c1 + c2 <= 0 || width <= 0 || width > MAXW || seq_len <= 0 || tokens % seq_len)
     return (int)cudaErrorInvalidValue;
-  const int64_t total = tokens * ((c0 + c1 + c2) / 8);
-  conv_silu_fwd_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, w, bias, (__nv_bfloat16*)pre,
+  if (tokens > 2147483647ll) return (int)cudaErrorInvalidValue;
+  conv_silu_fwd_kernel<<<(unsigned)tokens, 128, 0, st>>>((const __nv_bfloat16*)x, w, bias, (__nv_bfloat16*)pre,
                                                                         (__nv_bfloat16*)o0, (__nv_bfloat16*)o1, (__nv_bfloat16*)o2,
                                                                         Seg{c0, c1, c2}, tokens, seq_len, width);
   return (int)cudaGetLastError();
@@ -442,11 +443,11 @@ extern "C" int lbi_conv_silu_bwd(const void* d0, int d0_fp32, const void* d1, co
   if (c0 % 8 || c1 % 8 || c2 % 8 || c0 + c1 + c2 <= 0 || width <= 0 || width > MAXW || seq_len <= 0 || ftokens <= 0 ||
       tokens % ftokens || ftokens % seq_len || ld_in % 8 || ld_in < c0 + c1 + c2)
     return (int)cudaErrorInvalidValue;
-  const int64_t total = tokens * ((c0 + c1 + c2) / 8);
-  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (tokens > 2147483647ll) return (int)cudaErrorInvalidValue;
+  const unsigned blocks = (unsigned)tokens;
   const Seg seg{c0, c1, c2};
 #define LBI_CONV_BWD(A, B)                                                                                                   \
-  conv_silu_bwd_kernel<A, B><<<blocks, 256, 0, st>>>((const A*)d0, (const B*)d1, (const B*)d2, (const __nv_bfloat16*)pre, w, \
+  conv_silu_bwd_kernel<A, B><<<blocks, 128, 0, st>>>((const A*)d0, (const B*)d1, (const B*)d2, (const __nv_bfloat16*)pre, w, \
                                                      (__nv_bfloat16*)din, ld_in, seg, tokens, ftokens, seq_len, width)
   if (d0_fp32 && d12_fp32) LBI_CONV_BWD(float, float);
   else if (d0_fp32) LBI_CONV_BWD(float, __nv_bfloat16);

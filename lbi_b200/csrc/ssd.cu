@@ -683,6 +683,9 @@ __global__ void __launch_bounds__(THREADS) dda_kernel(const __grid_constant__ CU
 // bk D_out^T [320, 384), dX [384, 448).  Replaces the reference's _chunk_scan_chunk_state_bwd_dx, _chunk_state_bwd_db,
 // _chunk_scan_bwd_dc, _chunk_scan_bwd_dcb, _bmm_chunk_bwd and ddAcs kernels (backbones/mamba2/ops/triton/ssd_combined.py:396-513)
 // and the Mamba-3 dqkv kernel (backbones/mamba3/ops/triton/mamba3/mamba3_siso_bwd.py:202-594).
+constexpr int BWD_WARPS = 16;                       // compute warps: TMEM lane quarter = warp % 4, 32-column slice = warp / 4
+constexpr int BWD_THREADS = (BWD_WARPS + 1) * 32;   // + one control warp (TMA, MMA issue)
+
 template <int N>
 struct SmemBwd {
   alignas(1024) uint8_t ct[N / 64][PANEL];      // cq [t][64 n] per panel
@@ -693,13 +696,13 @@ struct SmemBwd {
   alignas(1024) uint8_t dho[N / 64][P * 128];   // D_out
   alignas(1024) uint8_t mt[2][PANEL];           // M   [t][64 s] per panel
   alignas(1024) uint8_t gt[2][PANEL];           // dGw [t][64 s] per panel
-  float tr[4][32][33];                          // per-warp transpose scratch for the column sums of E
-  float colpart[4][L];
+  float colpart[4][L];                          // column sums of E per row quarter
+  float rowpart[4][L];                          // row sums of E per column slice
   float cum2[L];
   float wv[L];
   float r2[L];
   float r3[L];
-  float red[4];
+  float red[BWD_WARPS];
   uint64_t bar_full, bar_mma, bar_w, bar_x, bar_x2, bar_y, bar_rows;
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -737,13 +740,66 @@ __device__ __forceinline__ void store_row(float* dst32, __nv_bfloat16* dst16, co
   }
 }
 
+// Lane j of the warp ends with sum over the 32 lanes of their v[j] (a transposing butterfly: 31 shuffles, no shared memory).
+__device__ __forceinline__ float warp_column_sums(float* v, int lane) {
+#pragma unroll
+  for (int step = 16, n = 32; step >= 1; step >>= 1, n >>= 1) {
+    const bool upper = (lane & step) != 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if (i < n / 2) {
+        const float send = upper ? v[i] : v[i + n / 2];
+        const float keep = upper ? v[i + n / 2] : v[i];
+        v[i] = keep + __shfl_xor_sync(0xffffffffu, send, step);
+      }
+    }
+  }
+  return v[0];
+}
+
+// Partial dot product of a 64-column bf16 row (128-byte swizzled) with 32 fp32 values: columns [32 * half, 32 * half + 32).
+__device__ __forceinline__ float dot_row32(uint32_t row_addr, int l, int half, const uint32_t* r) {
+  float acc = 0.f;
+#pragma unroll
+  for (int ch = 0; ch < 4; ++ch) {
+    const uint4 v = lds128(row_addr + (((half * 4 + ch) ^ (l & 7)) << 4));
+    const uint32_t* rr = r + ch * 8;
+    const float2 a = unpack2(v.x), b = unpack2(v.y), c = unpack2(v.z), d = unpack2(v.w);
+    acc = fmaf(a.x, __uint_as_float(rr[0]), acc);
+    acc = fmaf(a.y, __uint_as_float(rr[1]), acc);
+    acc = fmaf(b.x, __uint_as_float(rr[2]), acc);
+    acc = fmaf(b.y, __uint_as_float(rr[3]), acc);
+    acc = fmaf(c.x, __uint_as_float(rr[4]), acc);
+    acc = fmaf(c.y, __uint_as_float(rr[5]), acc);
+    acc = fmaf(d.x, __uint_as_float(rr[6]), acc);
+    acc = fmaf(d.y, __uint_as_float(rr[7]), acc);
+  }
+  return acc;
+}
+
+// Multiply columns [32 * half, 32 * half + 32) of row `row` of a 128-byte-row panel by f, in place.
+__device__ __forceinline__ void scale_half_row(uint32_t panel, int row, int half, float f) {
+  const uint32_t base = panel + row * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t addr = base + (((half * 4 + c) ^ (row & 7)) << 4);
+    uint4 v = lds128(addr);
+    float2 a = unpack2(v.x), b = unpack2(v.y), cc = unpack2(v.z), d = unpack2(v.w);
+    v.x = pack2(a.x * f, a.y * f);
+    v.y = pack2(b.x * f, b.y * f);
+    v.z = pack2(cc.x * f, cc.y * f);
+    v.w = pack2(d.x * f, d.y * f);
+    sts128(addr, v);
+  }
+}
+
 template <int N, bool PH>
-__global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_x,
-                                                            const __grid_constant__ CUtensorMap map_gy,
-                                                            const __grid_constant__ CUtensorMap map_b,
-                                                            const __grid_constant__ CUtensorMap map_c,
-                                                            const __grid_constant__ CUtensorMap map_hin,
-                                                            const __grid_constant__ CUtensorMap map_dho, const BwdParams p) {
+__global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                                   const __grid_constant__ CUtensorMap map_gy,
+                                                                   const __grid_constant__ CUtensorMap map_b,
+                                                                   const __grid_constant__ CUtensorMap map_c,
+                                                                   const __grid_constant__ CUtensorMap map_hin,
+                                                                   const __grid_constant__ CUtensorMap map_dho, const BwdParams p) {
   extern __shared__ uint8_t raw_smem[];
   SmemBwd<N>& s = *reinterpret_cast<SmemBwd<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -759,11 +815,11 @@ __global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constan
     s.abort_flag = 0;
     mbar_init(&s.bar_full, 1);
     mbar_init(&s.bar_mma, 1);
-    mbar_init(&s.bar_w, 4);
+    mbar_init(&s.bar_w, BWD_WARPS);
     mbar_init(&s.bar_x, 1);
-    mbar_init(&s.bar_x2, 4);
+    mbar_init(&s.bar_x2, BWD_WARPS / 2);
     mbar_init(&s.bar_y, 1);
-    mbar_init(&s.bar_rows, 4);
+    mbar_init(&s.bar_rows, BWD_WARPS);
     fence_barrier_init();
     prefetch_tmap(&map_x);
     prefetch_tmap(&map_gy);
@@ -772,14 +828,14 @@ __global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constan
     prefetch_tmap(&map_hin);
     prefetch_tmap(&map_dho);
   }
-  if (warp == 4) tmem_alloc(&s.tmem_base, TMEM_COLS);
+  if (warp == BWD_WARPS) tmem_alloc(&s.tmem_base, TMEM_COLS);
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem = s.tmem_base;
   volatile int* abortp = &s.abort_flag;
 
-  if (warp == 4) {
+  if (warp == BWD_WARPS) {
     if (lane == 0) {
       mbar_arrive_expect_tx(&s.bar_full, (2 * (N / 64) + 2) * PANEL + 2 * (N / 64) * P * 128);
       const int st_in = (int)((((int64_t)fb * p.chunks + c) * p.heads + h) * (PH ? N : P));
@@ -857,39 +913,43 @@ __global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constan
       }
     }
   } else {
-    const int l = warp * 32 + lane;
+    // 16 compute warps: row l of the tile (TMEM lane) and the 32-column slice q of it
+    const int rg = warp & 3, q = warp >> 2;
+    const int l = rg * 32 + lane;
     const int64_t base = ((int64_t)b * p.heads + h) * p.seq_len + c * L;
     const int64_t fbase = ((int64_t)fb * p.heads + h) * p.seq_len + c * L;
     const float my_cum2 = p.cum[fbase + l] * LOG2E;
-    s.cum2[l] = my_cum2;
-    s.wv[l] = p.weight ? p.weight[fbase + l] : 1.f;
-    named_barrier_sync(1, 128);
+    const float my_w = p.weight ? p.weight[fbase + l] : 1.f;
+    if (q == 0) {
+      s.cum2[l] = my_cum2;
+      s.wv[l] = my_w;
+    }
+    named_barrier_sync(1, BWD_WARPS * 32);
     const float cum_end2 = s.cum2[L - 1];
-    const float my_w = s.wv[l];
-    const uint32_t trow = tmem + ((uint32_t)(warp * 32) << 16);
-    float row_sum = 0.f, diag_g2 = 0.f, r2 = 0.f;
+    const float f_end = ex2(cum_end2 - my_cum2);
+    const uint32_t trow = tmem + ((uint32_t)(rg * 32) << 16);
+    float diag_g2 = 0.f, state_part = 0.f;
     bool ok = mbar_wait(&s.bar_mma, 0, abortp, p.status, 74);
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       fence_after_sync();
-      const uint32_t m_base = smem_u32(s.mt[0]), g_base = smem_u32(s.gt[0]);
-      for (int q = 0; q < 4; ++q) {
-        const uint32_t m_row = m_base + (q >> 1) * PANEL + l * 128, g_row = g_base + (q >> 1) * PANEL + l * 128;
-        if (q > warp) {   // above the diagonal for every row of this warp
+      const uint32_t m_row = smem_u32(s.mt[0]) + (q >> 1) * PANEL + l * 128, g_row = smem_u32(s.gt[0]) + (q >> 1) * PANEL + l * 128;
+      if (q > rg) {   // this 32 x 32 block lies above the diagonal for every row of the warp
 #pragma unroll
-          for (int c8 = 0; c8 < 4; ++c8) {
-            const int chunk = (q & 1) * 4 + c8;
-            sts128(m_row + ((chunk ^ (l & 7)) << 4), make_uint4(0, 0, 0, 0));
-            sts128(g_row + ((chunk ^ (l & 7)) << 4), make_uint4(0, 0, 0, 0));
-          }
-          s.colpart[warp][q * 32 + lane] = 0.f;
-          continue;
+        for (int c8 = 0; c8 < 4; ++c8) {
+          const int chunk = (q & 1) * 4 + c8;
+          sts128(m_row + ((chunk ^ (l & 7)) << 4), make_uint4(0, 0, 0, 0));
+          sts128(g_row + ((chunk ^ (l & 7)) << 4), make_uint4(0, 0, 0, 0));
         }
+        s.colpart[rg][q * 32 + lane] = 0.f;
+        s.rowpart[q][l] = 0.f;
+      } else {
         uint32_t g1[32], g2[32];
         tmem_ld_32x32(trow + q * 32, g1);
         tmem_ld_32x32(trow + 128 + q * 32, g2);
         tmem_ld_wait();
         float ev[32];
+        float row_sum = 0.f;
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           const int sidx = q * 32 + j;
@@ -916,39 +976,40 @@ __global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constan
                  make_uint4(pack2(__uint_as_float(d[0]), __uint_as_float(d[1])), pack2(__uint_as_float(d[2]), __uint_as_float(d[3])),
                             pack2(__uint_as_float(d[4]), __uint_as_float(d[5])), pack2(__uint_as_float(d[6]), __uint_as_float(d[7]))));
         }
-        // column sums of this 32 x 32 block of E through the warp's transpose scratch
-#pragma unroll
-        for (int j = 0; j < 32; ++j) s.tr[warp][lane][j] = ev[j];
-        __syncwarp();
-        float cp = 0.f;
-#pragma unroll
-        for (int r = 0; r < 32; ++r) cp += s.tr[warp][r][lane];
-        s.colpart[warp][q * 32 + lane] = cp;
-        __syncwarp();
+        s.rowpart[q][l] = row_sum;
+        s.colpart[rg][q * 32 + lane] = warp_column_sums(ev, lane);
+        if (q == rg && p.dskip) p.dskip[base + l] = diag_g2;   // gy_t . v_t sits on the diagonal of G2
       }
-      // state terms of the decay gradient (unscaled gy and v rows)
-      uint32_t r0[32], r1[32];
-      tmem_ld_32x32(trow + 256, r0);
-      tmem_ld_32x32(trow + 288, r1);
-      tmem_ld_wait();
-      r2 = ex2(my_cum2) * dot_row64(smem_u32(s.gyt) + l * 128, l, r0, r1);
-      tmem_ld_32x32(trow + 320, r0);
-      tmem_ld_32x32(trow + 352, r1);
-      tmem_ld_wait();
-      const float f_end = ex2(cum_end2 - my_cum2);
-      s.r3[l] = my_w * f_end * dot_row64(smem_u32(s.xt) + l * 128, l, r0, r1);
-      float hd = 0.f;
-      const uint32_t hin_a = smem_u32(s.hin[0]), dho_a = smem_u32(s.dho[0]);
-      for (int off = l * 16; off < (N / 64) * P * 128; off += 128 * 16) {
-        const uint4 a = lds128(hin_a + off), d = lds128(dho_a + off);
-        const float2 a0 = unpack2(a.x), a1 = unpack2(a.y), a2 = unpack2(a.z), a3 = unpack2(a.w);
-        const float2 d0 = unpack2(d.x), d1 = unpack2(d.y), d2 = unpack2(d.z), d3 = unpack2(d.w);
-        hd += a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y + a2.x * d2.x + a2.y * d2.y + a3.x * d3.x + a3.y * d3.y;
+      // state terms of the decay gradient (unscaled gy and v rows), split over the column slices:
+      //   q = 0, 1: halves of e^{c_t} gy_t . (cq_t S_in^T);  q = 2, 3: halves of w_s e^{c_end - c_s} v_s . (bk_s D_out^T)
+      {
+        uint32_t r[32];
+        tmem_ld_32x32(trow + (q < 2 ? 256 : 320) + (q & 1) * 32, r);
+        tmem_ld_wait();
+        state_part = (q < 2 ? ex2(my_cum2) : my_w * f_end) * dot_row32(smem_u32(q < 2 ? s.gyt : s.xt) + l * 128, l, q & 1, r);
       }
-      hd = warp_sum(hd);
-      if (lane == 0) s.red[warp] = hd;
-      // v row scaled for the state term of dbk
-      scale_row(smem_u32(s.xt), l, my_w * f_end);
+      // <S_in, D_out>: both tiles have the same layout, so the product runs over raw 16-byte pieces
+      {
+        float hd = 0.f;
+        const uint32_t hin_a = smem_u32(s.hin[0]), dho_a = smem_u32(s.dho[0]);
+        for (int off = (warp * 32 + lane) * 16; off < (N / 64) * P * 128; off += BWD_WARPS * 32 * 16) {
+          const uint4 a = lds128(hin_a + off), d = lds128(dho_a + off);
+          const float2 a0 = unpack2(a.x), a1 = unpack2(a.y), a2 = unpack2(a.z), a3 = unpack2(a.w);
+          const float2 d0 = unpack2(d.x), d1 = unpack2(d.y), d2 = unpack2(d.z), d3 = unpack2(d.w);
+          hd += a0.x * d0.x + a0.y * d0.y + a1.x * d1.x + a1.y * d1.y + a2.x * d2.x + a2.y * d2.y + a3.x * d3.x + a3.y * d3.y;
+        }
+        hd = warp_sum(hd);
+        if (lane == 0) s.red[warp] = hd;
+      }
+      // v rows scaled for the state term of dbk (slices 2 and 3 own the halves they just read)
+      if (q >= 2) scale_half_row(smem_u32(s.xt), l, q & 1, my_w * f_end);
+    }
+    // the two halves of each state term meet in r2 / r3 (shared-memory adds); the barrier is taken by every compute warp,
+    // whether or not its waits succeeded, so that a warp that gave up cannot strand the others at it
+    if ((q & 1) == 0) (q < 2 ? s.r2 : s.r3)[l] = 0.f;
+    named_barrier_sync(2, BWD_WARPS * 32);
+    if (ok) {
+      atomicAdd((q < 2 ? s.r2 : s.r3) + l, state_part);
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
@@ -959,73 +1020,75 @@ __global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constan
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
-      const float col_sum = s.colpart[0][l] + s.colpart[1][l] + s.colpart[2][l] + s.colpart[3][l];
-      s.r2[l] = r2 + row_sum - col_sum;
+      if (q == 0) {
+        const float col_sum = s.colpart[0][l] + s.colpart[1][l] + s.colpart[2][l] + s.colpart[3][l];
+        const float row_sum = s.rowpart[0][l] + s.rowpart[1][l] + s.rowpart[2][l] + s.rowpart[3][l];
+        s.r2[l] += row_sum - col_sum;
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(&s.bar_rows);
       ok = mbar_wait(&s.bar_rows, 1, abortp, p.status, 76);
       ok = __all_sync(0xffffffffu, ok);
     }
-    uint4 gy_saved[8];
+    uint4 gy_saved[4];
     if (ok) {
-      float tail2 = 0.f, head3 = 0.f;
-      for (int t = l; t < L; ++t) tail2 += s.r2[t];
-      for (int t = 0; t < l; ++t) head3 += s.r3[t];
-      const float through = ex2(cum_end2) * (s.red[0] + s.red[1] + s.red[2] + s.red[3]);
-      p.da[base + l] = tail2 + head3 + through;
-      if (p.dskip) p.dskip[base + l] = diag_g2;
-      // once dX has been taken, gy rows are scaled by e^{c_t} for the state term of dcq (the unscaled row is kept)
-      ok = mbar_wait(&s.bar_x, 0, abortp, p.status, 77);
-      ok = __all_sync(0xffffffffu, ok);
-    }
-    if (ok) {
-      const uint32_t gy_row = smem_u32(s.gyt) + l * 128;
+      if (q == 3) {   // one slice finishes the decay gradient of its row
+        float tail2 = 0.f, head3 = 0.f;
+        for (int t = l; t < L; ++t) tail2 += s.r2[t];
+        for (int t = 0; t < l; ++t) head3 += s.r3[t];
+        float through = 0.f;
 #pragma unroll
-      for (int ch = 0; ch < 8; ++ch) gy_saved[ch] = lds128(gy_row + ((ch ^ (l & 7)) << 4));
-      scale_row(smem_u32(s.gyt), l, ex2(my_cum2));
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s.bar_x2);
-      ok = mbar_wait(&s.bar_y, 0, abortp, p.status, 78);
+        for (int w = 0; w < BWD_WARPS; ++w) through += s.red[w];
+        p.da[base + l] = tail2 + head3 + ex2(cum_end2) * through;
+      }
+      // once dX has been taken, gy rows are scaled by e^{c_t} for the state term of dcq (slices 0, 1 own the halves and keep
+      // the unscaled values for the skip term of dX)
+      if (q < 2) {
+        ok = mbar_wait(&s.bar_x, 0, abortp, p.status, 77);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) {
+          const uint32_t gy_row = smem_u32(s.gyt) + l * 128;
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) gy_saved[ch] = lds128(gy_row + (((q * 4 + ch) ^ (l & 7)) << 4));
+          scale_half_row(smem_u32(s.gyt), l, q, ex2(my_cum2));
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s.bar_x2);
+        }
+      }
+      if (ok) ok = mbar_wait(&s.bar_y, 0, abortp, p.status, 78);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       fence_after_sync();
       const int64_t tok = (int64_t)row0 + l;
-      // dX row (+ state term, + skip * gy)
-      {
-        uint32_t x0[32], x1[32], t0[32], t1[32];
-        tmem_ld_32x32(trow + 384, x0);
-        tmem_ld_32x32(trow + 416, x1);
-        tmem_ld_32x32(trow + 320, t0);
-        tmem_ld_32x32(trow + 352, t1);
+      if (q < 2) {   // dX columns [32 q, 32 q + 32): intra-chunk part + state term + skip * gy
+        uint32_t x0[32], t0[32];
+        tmem_ld_32x32(trow + 384 + q * 32, x0);
+        tmem_ld_32x32(trow + 320 + q * 32, t0);
         tmem_ld_wait();
-        const float f_end = ex2(cum_end2 - my_cum2);
         const float sk = (p.d_skip ? p.d_skip[h] : 0.f) + (p.skip_tok ? p.skip_tok[fbase + l] : 0.f);
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
+        for (int ch = 0; ch < 4; ++ch) {
           const uint4 gv = gy_saved[ch];
           const float2 g0 = unpack2(gv.x), g1v = unpack2(gv.y), g2v = unpack2(gv.z), g3 = unpack2(gv.w);
           const float gyv[8] = {g0.x, g0.y, g1v.x, g1v.y, g2v.x, g2v.y, g3.x, g3.y};
-          uint32_t* xx = ch < 4 ? x0 + ch * 8 : x1 + (ch - 4) * 8;
-          const uint32_t* tt = ch < 4 ? t0 + ch * 8 : t1 + (ch - 4) * 8;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) xx[e] = __float_as_uint(__uint_as_float(xx[e]) + f_end * __uint_as_float(tt[e]) + sk * gyv[e]);
+          for (int e = 0; e < 8; ++e)
+            x0[ch * 8 + e] = __float_as_uint(__uint_as_float(x0[ch * 8 + e]) + f_end * __uint_as_float(t0[ch * 8 + e]) + sk * gyv[e]);
         }
-        const int64_t off = (tok * p.heads + h) * P;
+        const int64_t off = (tok * p.heads + h) * P + q * 32;
         store_row(p.dv32 ? p.dv32 + off : nullptr, p.dv16 ? p.dv16 + off : nullptr, x0, 32);
-        store_row(p.dv32 ? p.dv32 + off + 32 : nullptr, p.dv16 ? p.dv16 + off + 32 : nullptr, x1, 32);
       }
-      const int64_t off_n = (tok * p.heads + h) * N;
-#pragma unroll
-      for (int q = 0; q < N / 32; ++q) {
+      const int64_t off_n = (tok * p.heads + h) * N + q * 32;
+      if (q < N / 32) {
         uint32_t r[32];
         tmem_ld_32x32(trow + q * 32, r);
         tmem_ld_wait();
-        store_row(p.dcq32 ? p.dcq32 + off_n + q * 32 : nullptr, p.dcq16 ? p.dcq16 + off_n + q * 32 : nullptr, r, 32);
+        store_row(p.dcq32 ? p.dcq32 + off_n : nullptr, p.dcq16 ? p.dcq16 + off_n : nullptr, r, 32);
         tmem_ld_32x32(trow + 128 + q * 32, r);
         tmem_ld_wait();
-        store_row(p.dbk32 ? p.dbk32 + off_n + q * 32 : nullptr, p.dbk16 ? p.dbk16 + off_n + q * 32 : nullptr, r, 32);
+        store_row(p.dbk32 ? p.dbk32 + off_n : nullptr, p.dbk16 ? p.dbk16 + off_n : nullptr, r, 32);
       }
     }
   }
@@ -1036,7 +1099,7 @@ __global__ void __launch_bounds__(THREADS) bwd_chunk_kernel(const __grid_constan
   }
   fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == BWD_WARPS) {
     fence_after_sync();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -1314,7 +1377,7 @@ static int run_bwd(const void* v, const void* gy, const void* bk, const void* cq
   const size_t smem = sizeof(SmemBwd<N>) + 1024;
   rc = set_smem(bwd_chunk_kernel<N, PH>, smem);
   if (rc) return rc;
-  bwd_chunk_kernel<N, PH><<<dim3(chunks, heads, batch), THREADS, smem, st>>>(mx, mg, mb, mc, mh, md, p);
+  bwd_chunk_kernel<N, PH><<<dim3(chunks, heads, batch), BWD_THREADS, smem, st>>>(mx, mg, mb, mc, mh, md, p);
   return (int)cudaGetLastError();
 }
 

@@ -43,11 +43,27 @@ def _flash():
 FORWARD_NATIVE = os.environ.get("LBI_B200_LIBRARY_ATTENTION", "0") != "1"
 
 
+def _gqa_native(qkv, head_dim, n_heads, n_kv_heads, seq_len) -> bool:
+    """Grouped kv heads run on the tcgen05 kernels through an expanded copy of k and v (one head per q head)."""
+    return (n_kv_heads < n_heads and n_heads % n_kv_heads == 0 and qkv.is_cuda and hasattr(ext(), "gqa_expand")
+            and tcgen05_pullback_supported(qkv.dtype, head_dim, n_heads, n_heads, seq_len))
+
+
+def _gqa_expand(qkv, n_heads, n_kv_heads, head_dim):
+    from .dispatch import KERNEL_LAUNCHES
+
+    KERNEL_LAUNCHES["count"] += 1
+    return ext().gqa_expand(qkv.contiguous(), n_heads, n_kv_heads, head_dim)
+
+
 def flash_forward_packed(qkv, batch, seq_len, n_heads, n_kv_heads, head_dim, scale, kernel_mode=None):
     """Causal attention forward on the packed qkv buffer -> (out [n, H*Dh], lse [B, H, T] fp32).
 
-    ``tcgen05``: the extension's own kernel (bf16, head_dim 64, T % 128 == 0, no grouped kv heads);
+    ``tcgen05``: the extension's own kernel (bf16 or fp16, head_dim 64, T % 128 == 0; grouped kv heads through an expanded copy);
     ``fa2``: the flash_attn library kernel, kept as the baseline and for every other shape."""
+    if kernel_mode in (None, "tcgen05") and FORWARD_NATIVE and _gqa_native(qkv, head_dim, n_heads, n_kv_heads, seq_len):
+        return flash_forward_packed(_gqa_expand(qkv, n_heads, n_kv_heads, head_dim), batch, seq_len, n_heads, n_heads, head_dim, scale,
+                                    kernel_mode="tcgen05")
     mode = kernel_mode or ("tcgen05" if FORWARD_NATIVE and qkv.is_cuda and qkv.is_contiguous() and hasattr(ext(), "attn_fwd_packed")
                            and tcgen05_pullback_supported(qkv.dtype, head_dim, n_heads, n_kv_heads, seq_len) else "fa2")
     if mode == "tcgen05":
@@ -72,6 +88,15 @@ def pullback_packed(do_rows, qkv, o, lse, batch, seq_len, n_heads, n_kv_heads, h
     n = batch * seq_len
     nbasis = do_rows.shape[0] // n
     qkv_dim = (n_heads + 2 * n_kv_heads) * head_dim
+    if kernel_mode in (None, "tcgen05_pblock") and _gqa_native(qkv, head_dim, n_heads, n_kv_heads, seq_len):
+        # every q head gets its own copy of its group's k / v; the cotangents of the copies are summed afterwards (the
+        # inverse rotary turn of the epilogue is the same for all heads of a position, so it commutes with the sum)
+        from .dispatch import KERNEL_LAUNCHES
+
+        d_full = pullback_packed(do_rows, _gqa_expand(qkv, n_heads, n_kv_heads, head_dim), o, lse, batch, seq_len, n_heads, n_heads,
+                                 head_dim, scale, kernel_mode="tcgen05_pblock", rope=rope)
+        KERNEL_LAUNCHES["count"] += 1
+        return ext().gqa_reduce(d_full.contiguous(), n_heads, n_kv_heads, head_dim)
     mode = kernel_mode or default_kernel_mode(do_rows, head_dim, n_heads, n_kv_heads, seq_len)
     if mode == "tcgen05_pblock":
         from .dispatch import KERNEL_LAUNCHES
@@ -104,7 +129,7 @@ def tcgen05_pullback_supported(dtype, head_dim, n_heads, n_kv_heads, seq_len) ->
     return (
         native_available()
         and hasattr(ext(), "attn_pullback_packed")
-        and dtype == torch.bfloat16
+        and dtype in (torch.bfloat16, torch.float16)
         and head_dim == 64
         and n_heads == n_kv_heads
         and seq_len % 128 == 0

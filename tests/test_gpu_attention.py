@@ -104,3 +104,55 @@ def test_pullback_epilogue_rotates_dq_dk_back(interleaved):
     assert (got.float() - want.float()).abs().max().item() <= tol
     # dv is not rotated
     assert torch.equal(got[:, 2 * h * 64 :], plain[:, 2 * h * 64 :])
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(8, 4), (4, 1)])
+def test_grouped_kv_heads_run_on_the_tcgen05_kernels(heads, kv_heads):
+    """Grouped-query attention (the paper's canonical Transformer is 8 heads / 4 kv heads): forward and the basis pullback
+    go through the expand / reduce kernels around the tcgen05 kernels and match the library path on the packed layout."""
+    from lbi_b200.ops.attention import flash_forward_packed, pullback_packed
+
+    b, t, p = 2, 256, 3
+    g = torch.Generator(device=DEV).manual_seed(heads)
+    qkv = torch.randn(b * t, (heads + 2 * kv_heads) * 64, device=DEV, generator=g).bfloat16()
+    do = torch.randn(p * b * t, heads * 64, device=DEV, generator=g).bfloat16()
+    scale = 0.125
+    prev = ops.dispatch.set_strict(True)
+    try:
+        before = ops.dispatch.KERNEL_LAUNCHES["count"]
+        o, lse = flash_forward_packed(qkv, b, t, heads, kv_heads, 64, scale)
+        got = pullback_packed(do, qkv, o, lse, b, t, heads, kv_heads, 64, scale)
+        assert ops.dispatch.KERNEL_LAUNCHES["count"] - before >= 6
+    finally:
+        ops.dispatch.set_strict(prev)
+    o_lib, lse_lib = flash_forward_packed(qkv, b, t, heads, kv_heads, 64, scale, kernel_mode="fa2")
+    want = pullback_packed(do, qkv, o_lib, lse_lib, b, t, heads, kv_heads, 64, scale, kernel_mode="fa2_loop")
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(qkv) == 0
+    assert got.shape == want.shape == (p * b * t, (heads + 2 * kv_heads) * 64)
+    assert (o.float() - o_lib.float()).abs().max().item() <= 2e-2 * o_lib.float().abs().max().item() + 1e-3
+    assert (got.float() - want.float()).abs().max().item() <= 3e-2 * want.float().abs().max().item() + 1e-3
+
+
+@pytest.mark.parametrize("t,p", [(256, 4), (512, 3)])
+def test_fp16_runs_on_the_tcgen05_kernels(t, p):
+    """fp16 (the reference kernel's only dtype, tolerance 2e-2 for its fused fp16 path) through the public basis-pullback entry
+    point against the O(T^2) fp32 formula."""
+    from lbi_b200.ops.attention import attention_input_pullback_basis
+
+    b, h = 2, 2
+    g = torch.Generator(device=DEV).manual_seed(t + p)
+    q, k, v = (torch.randn(b, h, t, 64, device=DEV, generator=g).half() for _ in range(3))
+    do = torch.randn(b, p, h, t, 64, device=DEV, generator=g).half()
+    prev = ops.dispatch.set_strict(True)
+    try:
+        got = attention_input_pullback_basis(q, k, v, do, causal=True, kernel_mode="tcgen05_pblock")
+    finally:
+        ops.dispatch.set_strict(prev)
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(q) == 0
+    want = attention_input_pullback_basis(q.float(), k.float(), v.float(), do.float(), causal=True, kernel_mode="dense")
+    for name, a, w in zip(("dQ", "dK", "dV"), got, want):
+        assert a.dtype == torch.float16
+        err = (a.float() - w).abs().max().item()
+        assert err <= 2e-2 * w.abs().max().item() + 2e-3, f"{name}: {err:.3e}"

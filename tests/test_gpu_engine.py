@@ -150,3 +150,36 @@ def test_strict_mode_refuses_a_library_route():
     finally:
         ops.dispatch.set_strict(prev)
         ops.dispatch.FALLBACKS.clear()
+
+
+@pytest.mark.parametrize("kind", ["transformer", "mamba2"])
+def test_engine_grad_parity_at_headline_interface_width(kind):
+    """A 2-layer slice with the headline interface shape: 8 sequence regions, interface width 128, basis blocks of 16 (so the
+    loss cotangent rides as the lone 17th direction of the last block) against dense autograd in fp32 on the CPU."""
+    torch.manual_seed(0)
+    if kind == "transformer":
+        spec = BackboneSpec(name="transformer", dim=256, layers=2, n_heads=4, d_conv=0, d_intermediate=512)
+    else:
+        spec = BackboneSpec(name="mamba2", dim=256, layers=2, d_state=128, headdim=64, expand=2, d_conv=4, chunk_size=128)
+    iface = VectorMLPInterface(feature_dim=256, num_regions=8, interface_width=128, interface_map_hidden_dim=256)
+    cpu_model = LBILanguageModel(vocab_size=1024, layers_per_region=1, backbone_spec=spec, interface=iface, region_axis="sequence",
+                                 num_sequence_regions=8, tie_embeddings=True)
+    gpu_model = copy.deepcopy(cpu_model).cuda()
+    torch.manual_seed(1)
+    ids, tgt = torch.randint(0, 1024, (2, 1024)), torch.randint(0, 1024, (2, 1024))
+    loss = F.cross_entropy(cpu_model(ids).float().reshape(-1, 1024), tgt.reshape(-1))
+    want = AutogradEngine().backward(model=cpu_model, loss=loss).grad_map
+    engine = FastLBIEngine(gpu_model, lr=1e-3, basis_chunk=16)
+    res = engine.backward(ids.cuda(), tgt.cuda())
+    from lbi_b200 import ops
+
+    assert ops.ext().kernel_status(res.loss) == 0
+    assert abs(float(res.loss) - float(loss.detach())) < 5e-3 * max(1.0, abs(float(loss.detach())))
+    got = engine.named_grads()
+    for name, ref in want.items():
+        if ref is None:
+            continue
+        g = got[name].float().cpu()
+        rel = float((g - ref).norm() / (ref.norm() + 1e-12))
+        assert torch.allclose(g, ref, atol=5e-2, rtol=5e-2), f"{name}: max abs err {float((g - ref).abs().max()):.3e}"
+        assert rel < 1.5e-1, f"{name}: rel-L2 {rel:.3e}"
