@@ -8,6 +8,12 @@ N(0, 1) from seed 0.  Every kernel mode that supports the cell is timed with CUD
 (3 warm-ups, median of ``--iters``, a 256 MB write between launches to flush L2); peak bytes and, with ``--check``,
 the max abs error against the dense fp32 formula are recorded.  Writes ``attention_pullback_<timestamp>.csv``,
 ``latest.csv`` and ``latest_summary.json`` (speed-ups of the tcgen05 kernel over the library loop).
+
+``--reference-dir DIR`` adds the reference's own CUDA kernel as a third arm where it applies (its WMMA "pblock4" kernel,
+cuda/transformer/attention_pullback_mma.cu: fp16, head_dim 64, T <= 1024, at most four directions per launch; more
+directions are timed as consecutive launches of four, the way its engine blocks them).  DIR is an unmodified install of
+the reference whose ``cuda/transformer`` extension has been built for sm_100a; the arm calls
+``cuda.transformer.attention_input_pullback_basis(kernel_mode="fa2_mma_pblock4")``, the reference's public entry.
 """
 from __future__ import annotations
 
@@ -33,8 +39,43 @@ def pullback_flops(b, h, t, dh, p):
     return b * h * (p * 4 * one + one)
 
 
-def time_mode(mode, q, k, v, do, scale, iters, flush):
-    fn = lambda: attention_input_pullback_basis(q, k, v, do, scale=scale, causal=True, kernel_mode=mode)
+def load_reference_pullback(ref_dir: str):
+    """The reference's attention_input_pullback_basis, or None with the reason."""
+    import importlib
+    import sys
+
+    root = Path(ref_dir).resolve()
+    ext_dir = root / "cuda" / "transformer"
+    if not ext_dir.is_dir():
+        return None, f"{ext_dir} not found"
+    # an unrelated namespace package called `cuda` (cuda-python) may be registered already; the reference's own top-level
+    # `cuda` package has to win for `cuda.transformer` to resolve
+    for name in [m for m in sys.modules if m == "cuda" or m.startswith("cuda.")]:
+        del sys.modules[name]
+    for entry in (str(ext_dir), str(root)):
+        if entry not in sys.path:
+            sys.path.insert(0, entry)
+    try:
+        mod = importlib.import_module("cuda.transformer")
+    except Exception as exc:  # noqa: BLE001
+        return None, f"import failed: {exc!r}"
+    if getattr(mod, "transformer_lbi_cuda", None) is None:
+        return None, "transformer_lbi_cuda extension not built"
+    return mod.attention_input_pullback_basis, ""
+
+
+def reference_mode(ref_fn, q, k, v, do, scale):
+    """The reference's WMMA kernel over P directions: launches of at most four directions each."""
+    outs = [ref_fn(q, k, v, do[:, lo : lo + 4], softmax_scale=scale, causal=True, kernel_mode="fa2_mma_pblock4")
+            for lo in range(0, do.shape[1], 4)]
+    return tuple(torch.cat([o[i] for o in outs], dim=1) for i in range(3)) if len(outs) > 1 else outs[0]
+
+
+def time_mode(mode, q, k, v, do, scale, iters, flush, ref_fn=None):
+    if mode == "reference_wmma_pblock4":
+        fn = lambda: reference_mode(ref_fn, q, k, v, do, scale)
+    else:
+        fn = lambda: attention_input_pullback_basis(q, k, v, do, scale=scale, causal=True, kernel_mode=mode)
     for _ in range(3):
         fn()
     torch.cuda.synchronize()
@@ -59,11 +100,20 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--atol", type=float, default=3e-2)
     ap.add_argument("--out-dir", type=str, default="out/benchmarks/attention_pullback")
+    ap.add_argument("--reference-dir", type=str, default="", help="install of the reference with its CUDA extension built")
+    ap.add_argument("--seqs", type=str, default="", help="comma-separated sequence lengths (default: the sweep above)")
     args = ap.parse_args()
+    ref_fn = None
+    if args.reference_dir:
+        ref_fn, why = load_reference_pullback(args.reference_dir)
+        if ref_fn is None:
+            print(json.dumps({"reference_arm": "unavailable", "why": why}), flush=True)
     dev = torch.device("cuda")
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     batch, heads = 8, 16
     seqs = (512, 2048) if args.quick else (128, 512, 2048)
+    if args.seqs:
+        seqs = tuple(int(x) for x in args.seqs.split(","))
     dims = (64,) if args.quick else (64, 128)
     dtypes = (torch.bfloat16,) if args.quick else (torch.float16, torch.bfloat16)
     rows = []
@@ -81,11 +131,13 @@ def main() -> None:
                     modes = ["fa2_loop"]
                     if tcgen05_pullback_supported(dtype, dh, heads, heads, t):
                         modes.insert(0, "tcgen05_pblock")
+                    if ref_fn is not None and dtype == torch.float16 and dh == 64 and t <= 1024 and t % 16 == 0:
+                        modes.append("reference_wmma_pblock4")
                     for mode in modes:
                         row = dict(dtype=str(dtype).replace("torch.", ""), batch=batch, heads=heads, seq_len=t, head_dim=dh,
                                    basis=p, kernel_mode=mode, max_abs_err="", status="ok")
                         try:
-                            med, best, peak, out = time_mode(mode, q, k, v, do, scale, args.iters, flush)
+                            med, best, peak, out = time_mode(mode, q, k, v, do, scale, args.iters, flush, ref_fn)
                             row.update(median_ms=med, best_ms=best, peak_bytes=peak,
                                        tflops=pullback_flops(batch, heads, t, dh, p) / med / 1e9)
                             if want is not None:
@@ -113,8 +165,15 @@ def main() -> None:
             if base and base["status"] == "ok":
                 key = f"{r['dtype']}_T{r['seq_len']}_D{r['head_dim']}_P{r['basis']}"
                 speedups[key] = base["median_ms"] / r["median_ms"]
-    (out_dir / "latest_summary.json").write_text(json.dumps({"speedup_tcgen05_over_fa2_loop": speedups, "rows": len(rows)}, indent=2))
-    print(json.dumps({"speedup_tcgen05_over_fa2_loop": speedups}))
+    over_ref = {}
+    for r in rows:
+        if r["kernel_mode"] == "tcgen05_pblock" and r["status"] == "ok":
+            base = next((x for x in rows if x["kernel_mode"] == "reference_wmma_pblock4" and all(x[k] == r[k] for k in ("dtype", "seq_len", "head_dim", "basis"))), None)
+            if base and base["status"] == "ok":
+                over_ref[f"{r['dtype']}_T{r['seq_len']}_D{r['head_dim']}_P{r['basis']}"] = base["median_ms"] / r["median_ms"]
+    summary = {"speedup_tcgen05_over_fa2_loop": speedups, "speedup_tcgen05_over_reference_wmma": over_ref, "rows": len(rows)}
+    (out_dir / "latest_summary.json").write_text(json.dumps(summary, indent=2))
+    print(json.dumps(summary))
 
 
 if __name__ == "__main__":

@@ -118,13 +118,13 @@ int lbi_siso_small_bwd(const float* dt, const float* a, const float* sig, const 
                        int seq_len, int heads, int n_angles, int out_bf16, cudaStream_t stream);
 
 // Mamba-2 depthwise causal conv + SiLU over the xBC slice (channels = c0 + c1 + c2, each a multiple of 8; width <= 8).
-// x [tokens, channels] bf16, w [channels, width], bias [channels] or null (fp32) -> pre [tokens, channels] bf16 (conv output) and
+// x [tokens, channels] bf16, wt [width, channels] (the weights TRANSPOSED), bias [channels] or null (fp32) -> pre [tokens, channels] bf16 (conv output) and
 // the activation split into o0 [tokens, c0], o1 [tokens, c1], o2 [tokens, c2] bf16.
-int lbi_conv_silu_fwd(const void* x, const float* w, const float* bias, void* pre, void* o0, void* o1, void* o2, int c0, int c1,
+int lbi_conv_silu_fwd(const void* x, const float* wt, const float* bias, void* pre, void* o0, void* o1, void* o2, int c0, int c1,
                       int c2, int64_t tokens, int seq_len, int width, cudaStream_t stream);
 // Cotangents of the three activation parts d0 [tokens, c0] (bf16 or fp32), d1, d2 [tokens, c1 / c2] (bf16 or fp32) -> cotangent of
 // the conv input, written with row stride ld_in (elements) at din.  pre holds ftokens tokens shared by tokens / ftokens directions.
-int lbi_conv_silu_bwd(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre, const float* w,
+int lbi_conv_silu_bwd(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre, const float* wt,
                       void* din, int64_t ld_in, int c0, int c1, int c2, int64_t tokens, int64_t ftokens, int seq_len, int width,
                       cudaStream_t stream);
 // dw [channels, width] += , db [channels] += (fp32; zeroed by the caller).  One direction (tokens = ftokens).

@@ -65,9 +65,10 @@ int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void* gy, const
 // Forward operands v [Bf*L, H*64], bk / cq [Bf*L, G*N] (per_head: [Bf*L, H*128]) bf16, weight / cum / skip_tok [Bf, H, L] fp32 and
 // state_in (bf16 incoming chunk states of the forward, [Bf, L/128, H, 64, N]; per_head [.., N, 64]) belong to `bmod` = Bf
 // sequences and are shared by batch / bmod stacked directions of gy [B*L, H*64] bf16.  d_final (cotangent of the final state,
-// fp32, layout of the states) may be null.  Scratch: chunk_cot [B, L/128, H, 64*N] fp32, d_out (same shape, bf16).
+// fp32, layout of the states) may be null.  Scratch: d_out [B, L/128, H, 64*N] bf16 (cotangents of the chunk-boundary states);
+// chunk_cot is unused (kept for callers of the earlier three-kernel form) and may be null.
 // Results: d_init (or null), da, dskip (or null) [B, H, L]; dv [B*L, H*64] in dv32 or dv16 (cotangent of w_s v_s, plus
-// (d_skip[h] + skip_tok) * gy when given); dcq, dbk [B*L, H*N] per head in fp32 or bf16.  Three kernels on `stream`.
+// (d_skip[h] + skip_tok) * gy when given); dcq, dbk [B*L, H*N] per head in fp32 or bf16.  Two kernels on `stream`.
 int lbi_ssd_chunk_bwd(const void* v, const void* gy, const void* bk, const void* cq, const float* weight, const float* cum,
                       const float* skip_tok, const float* d_skip, const void* state_in, const float* d_final, float* chunk_cot,
                       void* d_out, float* d_init, float* da, float* dskip, float* dv32, void* dv16, float* dcq32, float* dbk32,

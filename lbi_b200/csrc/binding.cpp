@@ -556,7 +556,8 @@ std::vector<Tensor> conv_silu_fwd(const Tensor& x, const Tensor& w, const c10::o
   const int64_t n = x.size(0);
   Tensor pre = torch::empty_like(x);
   Tensor o0 = torch::empty({n, c0}, x.options()), o1 = torch::empty({n, c1}, x.options()), o2 = torch::empty({n, c2}, x.options());
-  check(lbi_conv_silu_fwd(x.data_ptr(), w.data_ptr<float>(), bias ? bias->data_ptr<float>() : nullptr, pre.data_ptr(), o0.data_ptr(),
+  Tensor wt = w.t().contiguous();   // [W, C]: the kernels read a tap's weights of neighbouring channels with one load
+  check(lbi_conv_silu_fwd(x.data_ptr(), wt.data_ptr<float>(), bias ? bias->data_ptr<float>() : nullptr, pre.data_ptr(), o0.data_ptr(),
                           o1.data_ptr(), o2.data_ptr(), (int)c0, (int)c1, (int)c2, n, (int)seq_len, (int)w.size(1), cur_stream()),
         "conv_silu_fwd");
   return {pre, o0, o1, o2};
@@ -582,7 +583,8 @@ void conv_silu_bwd_(const Tensor& d0, const Tensor& d1, const Tensor& d2, const 
   TORCH_CHECK(pre.size(1) == c0 + c1 + c2 && d1.size(0) == tokens && d2.size(0) == tokens && out.dim() == 2 && out.size(0) == tokens &&
                   col0 % 8 == 0 && col0 + c0 + c1 + c2 <= out.size(1),
               "conv_silu_bwd: shapes");
-  check(lbi_conv_silu_bwd(d0.data_ptr(), f0, d1.data_ptr(), d2.data_ptr(), f1, pre.data_ptr(), w.data_ptr<float>(),
+  Tensor wt = w.t().contiguous();
+  check(lbi_conv_silu_bwd(d0.data_ptr(), f0, d1.data_ptr(), d2.data_ptr(), f1, pre.data_ptr(), wt.data_ptr<float>(),
                           static_cast<at::BFloat16*>(out.data_ptr()) + col0, out.size(1), (int)c0, (int)c1, (int)c2, tokens, ftokens,
                           (int)seq_len, (int)w.size(1), cur_stream()),
         "conv_silu_bwd");
@@ -944,7 +946,6 @@ std::vector<Tensor> ssd_chunk_bwd(const Tensor& v, const Tensor& gy, const Tenso
     s_t = skip_tok->transpose(1, 2).contiguous();
   }
   if (d_skip) CHECK_F32((*d_skip));
-  Tensor chunk_cot = torch::empty({batch, chunks, heads, hd * n}, f32);
   Tensor d_out = torch::empty({batch, chunks, heads, hd * n}, v.options());
   Tensor da = torch::empty({batch, heads, seq}, f32), dskip = torch::empty({batch, heads, seq}, f32);
   Tensor dv = torch::empty({batch, seq, heads, hd}, dv_bf16 ? v.options() : f32);
@@ -955,7 +956,7 @@ std::vector<Tensor> ssd_chunk_bwd(const Tensor& v, const Tensor& gy, const Tenso
         "chunk_bwd_cumsum");
   check(lbi_ssd_chunk_bwd(v.data_ptr(), gy.data_ptr(), bk.data_ptr(), cq.data_ptr(), weight ? w_t.data_ptr<float>() : nullptr,
                           cum.data_ptr<float>(), skip_tok ? s_t.data_ptr<float>() : nullptr,
-                          d_skip ? d_skip->data_ptr<float>() : nullptr, state_in.data_ptr(), nullptr, chunk_cot.data_ptr<float>(),
+                          d_skip ? d_skip->data_ptr<float>() : nullptr, state_in.data_ptr(), nullptr, nullptr,
                           d_out.data_ptr(), nullptr, da.data_ptr<float>(), dskip.data_ptr<float>(),
                           dv_bf16 ? nullptr : dv.data_ptr<float>(), dv_bf16 ? dv.data_ptr() : nullptr,
                           dn_bf16 ? nullptr : dcq.data_ptr<float>(), dn_bf16 ? nullptr : dbk.data_ptr<float>(),

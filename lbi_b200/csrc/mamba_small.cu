@@ -268,6 +268,8 @@ extern "C" int lbi_siso_small_bwd(const float* dt, const float* a, const float* 
 // ------------------------------------------------------------------------------------------------ Mamba-2 conv + SiLU
 // Depthwise causal conv over the xBC slice of in_proj followed by SiLU, eight channels per thread (16-byte accesses).
 //   pre[t, c] = bias[c] + sum_w w[c, w] x[t - (W - 1) + w, c],   act = silu(pre)
+// The kernels take the weights transposed, wt [W][C] (a tap's weights of neighbouring channels are neighbours in memory: one
+// coalesced 32-byte load per thread and tap instead of eight scattered ones); the weight gradient is produced as [C][W].
 // The activation leaves as three contiguous tensors (x | B | C: what the scan kernels take), the pre-activation is kept
 // for the backward.  Backward for P stacked directions: the cotangents of x, B, C arrive as three tensors,
 //   dpre[t', c] = dact[t', c] silu'(pre[t', c]),   din[t, c] = sum_w w[c, w] dpre[t + (W - 1) - w, c]
@@ -310,8 +312,13 @@ __global__ void __launch_bounds__(128) conv_silu_fwd_kernel(const __nv_bfloat16*
       if (!LBI_IN_RANGE(src, tokens, 91)) continue;
       float xv[8];
       unpack8(*reinterpret_cast<const bf16x8*>(x + src * channels + c), xv);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], xv[e], acc[e]);
+      {
+        const float4 w0 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c + 4);
+        acc[0] = fmaf(w0.x, xv[0], acc[0]); acc[1] = fmaf(w0.y, xv[1], acc[1]); acc[2] = fmaf(w0.z, xv[2], acc[2]);
+        acc[3] = fmaf(w0.w, xv[3], acc[3]); acc[4] = fmaf(w1.x, xv[4], acc[4]); acc[5] = fmaf(w1.y, xv[5], acc[5]);
+        acc[6] = fmaf(w1.z, xv[6], acc[6]); acc[7] = fmaf(w1.w, xv[7], acc[7]);
+      }
     }
     *reinterpret_cast<bf16x8*>(pre + tok * channels + c) = pack8(acc);
 #pragma unroll
@@ -365,8 +372,13 @@ __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const D0* __restrict
       if (!LBI_IN_RANGE(tok + shift, tokens, 92)) continue;
       float dp[8];
       dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tok + shift, ftok + shift, c, dp);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[(c + e) * width + k], dp[e], acc[e]);
+      {
+        const float4 w0 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c);
+        const float4 w1 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c + 4);
+        acc[0] = fmaf(w0.x, dp[0], acc[0]); acc[1] = fmaf(w0.y, dp[1], acc[1]); acc[2] = fmaf(w0.z, dp[2], acc[2]);
+        acc[3] = fmaf(w0.w, dp[3], acc[3]); acc[4] = fmaf(w1.x, dp[4], acc[4]); acc[5] = fmaf(w1.y, dp[5], acc[5]);
+        acc[6] = fmaf(w1.z, dp[6], acc[6]); acc[7] = fmaf(w1.w, dp[7], acc[7]);
+      }
     }
     *reinterpret_cast<bf16x8*>(din + tok * ld_in + c) = pack8(acc);
   }

@@ -100,6 +100,34 @@ __global__ void __launch_bounds__(THREADS) fwd_kernel(const T* __restrict__ q, c
 // bias_partials [gridDim.x][2][heads][N]
 // T: dtype of q, k; C: dtype of the cotangents dqr, dkr.  The forward tensors (q, k, theta, gamma, scale) hold `frows` rows
 // (tokens x groups) and are shared by rows / frows stacked directions of the cotangents.
+// What one head of one (token, group) row reads: loaded one head ahead of its use, so that the loads of head r + 1 are in
+// flight while the shuffles and stores of head r run (the stores in the loop body keep the compiler from hoisting them itself).
+struct HeadIn {
+  float4 gq, gk, qb, kb;
+  float th0, th1, sc, gm, dd;
+};
+
+template <typename C>
+__device__ __forceinline__ HeadIn load_head(const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                                            const float* __restrict__ theta, const float* __restrict__ gamma,
+                                            const float* __restrict__ scale, const C* __restrict__ dqr, const C* __restrict__ dkr,
+                                            const float* __restrict__ dqk, int64_t tok, int64_t ftok, int h, int heads, int n_angles,
+                                            int seq_len, int dkr_pad, int lane) {
+  HeadIn in;
+  const int64_t hrow = tok * heads + h, fhrow = ftok * heads + h;
+  const int64_t krow = dkr_pad > 0 ? ((tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len)) * heads + h : hrow;
+  in.gq = ld4<C>(dqr + hrow * N + lane * 4);
+  in.gk = ld4<C>(dkr + krow * N + lane * 4);
+  in.qb = ld4<float>(q_bias + h * N + lane * 4);
+  in.kb = ld4<float>(k_bias + h * N + lane * 4);
+  in.th0 = 2 * lane < n_angles ? theta[fhrow * n_angles + 2 * lane] : 0.f;
+  in.th1 = 2 * lane + 1 < n_angles ? theta[fhrow * n_angles + 2 * lane + 1] : 0.f;
+  in.sc = scale[fhrow];
+  in.gm = gamma[fhrow];
+  in.dd = dqk[hrow];
+  return in;
+}
+
 template <typename T, typename C>
 __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, const T* __restrict__ k,
                                                       const float* __restrict__ q_bias, const float* __restrict__ k_bias,
@@ -126,24 +154,39 @@ __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, c
     const int64_t frow = row % frows, ftok = frow / groups;
     const float4 qg = ld4<T>(q + frow * N + lane * 4), kg = ld4<T>(k + frow * N + lane * 4);
     float4 dq_sum = make_float4(0.f, 0.f, 0.f, 0.f), dk_sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    HeadIn cur = load_head<C>(q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, tok, ftok, g * rep, heads, n_angles, seq_len,
+                              dkr_pad, lane);
     for (int r = 0; r < rep; ++r) {
       const int h = g * rep + r;
-      const int64_t hrow = tok * heads + h, fhrow = ftok * heads + h;
-      const float4 qb = ld4<float>(q_bias + h * N + lane * 4), kb = ld4<float>(k_bias + h * N + lane * 4);
-      const float4 qh = make_float4(qg.x + qb.x, qg.y + qb.y, qg.z + qb.z, qg.w + qb.w);
-      const float4 kh = make_float4(kg.x + kb.x, kg.y + kb.y, kg.z + kb.z, kg.w + kb.w);
-      const Rot rot = load_rot(theta + fhrow * n_angles, lane, n_angles);
-      const float sc = scale[fhrow], gm = gamma[fhrow], dd = dqk[hrow];
-      const int64_t krow = dkr_pad > 0 ? ((tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len)) * heads + h : hrow;
-      const float4 gq = ld4<C>(dqr + hrow * N + lane * 4), gk = ld4<C>(dkr + krow * N + lane * 4);
+      const int64_t hrow = tok * heads + h;
+      HeadIn nxt = cur;
+      if (r + 1 < rep)
+        nxt = load_head<C>(q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, tok, ftok, h + 1, heads, n_angles, seq_len, dkr_pad,
+                           lane);
+      const float4 qh = make_float4(qg.x + cur.qb.x, qg.y + cur.qb.y, qg.z + cur.qb.z, qg.w + cur.qb.w);
+      const float4 kh = make_float4(kg.x + cur.kb.x, kg.y + cur.kb.y, kg.z + cur.kb.z, kg.w + cur.kb.w);
+      Rot rot{1.f, 0.f, 1.f, 0.f};
+      if (2 * lane < n_angles) __sincosf(cur.th0, &rot.s0, &rot.c0);
+      if (2 * lane + 1 < n_angles) __sincosf(cur.th1, &rot.s1, &rot.c1);
+      const float sc = cur.sc, gm = cur.gm, dd = cur.dd;
+      const float4 gq = cur.gq, gk = cur.gk;
       const float4 qo = rotate(qh, rot), ko = rotate(kh, rot);   // ko without the scale
       // angle gradients: J (a, b) = (-b, a) applied to the rotated pair
       const float dth0 = (-gq.x * qo.y + gq.y * qo.x) + sc * (-gk.x * ko.y + gk.y * ko.x);
       const float dth1 = (-gq.z * qo.w + gq.w * qo.z) + sc * (-gk.z * ko.w + gk.w * ko.z);
-      if (2 * lane < n_angles) dtheta[hrow * n_angles + 2 * lane] = dth0;
-      if (2 * lane + 1 < n_angles) dtheta[hrow * n_angles + 2 * lane + 1] = dth1;
-      const float dsc = warp_sum(gk.x * ko.x + gk.y * ko.y + gk.z * ko.z + gk.w * ko.w);
-      const float qk = warp_sum(qh.x * kh.x + qh.y * kh.y + qh.z * kh.z + qh.w * kh.w);
+      if ((n_angles & 1) == 0) {   // rows of an even number of angles keep the pair 8-byte aligned
+        if (2 * lane < n_angles) *reinterpret_cast<float2*>(dtheta + hrow * n_angles + 2 * lane) = make_float2(dth0, dth1);
+      } else {
+        if (2 * lane < n_angles) dtheta[hrow * n_angles + 2 * lane] = dth0;
+        if (2 * lane + 1 < n_angles) dtheta[hrow * n_angles + 2 * lane + 1] = dth1;
+      }
+      float dsc = gk.x * ko.x + gk.y * ko.y + gk.z * ko.z + gk.w * ko.w;
+      float qk = qh.x * kh.x + qh.y * kh.y + qh.z * kh.z + qh.w * kh.w;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {   // the two reductions interleaved: independent shuffles issue back to back
+        dsc += __shfl_xor_sync(0xffffffffu, dsc, o);
+        qk += __shfl_xor_sync(0xffffffffu, qk, o);
+      }
       if (lane == 0) {
         dscale[hrow] = dsc;
         dgamma[hrow] = dd * qk;
@@ -161,6 +204,7 @@ __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, c
         atomicAdd(bq, dqh.x); atomicAdd(bq + 1, dqh.y); atomicAdd(bq + 2, dqh.z); atomicAdd(bq + 3, dqh.w);
         atomicAdd(bk, dkh.x); atomicAdd(bk + 1, dkh.y); atomicAdd(bk + 2, dkh.z); atomicAdd(bk + 3, dkh.w);
       }
+      cur = nxt;
     }
     *reinterpret_cast<float4*>(dq + row * N + lane * 4) = dq_sum;
     *reinterpret_cast<float4*>(dk + row * N + lane * 4) = dk_sum;
@@ -172,88 +216,9 @@ __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, c
   }
 }
 
-// The same backward with one warp per head: a block owns one (token, group) row at a time, its `rep` warps (heads of the
-// group) work in parallel and the group sums of dQ / dK go through shared memory.  Used when a group has 2 .. 32 heads: the
-// serial head loop of the kernel above keeps one warp busy with a chain of dependent shuffles per head, this form keeps
-// rep times as many loads in flight.  Shared memory: [2][rep][N] reduce buffers, then [2][heads][N] bias accumulators.
-template <typename T, typename C>
-__global__ void __launch_bounds__(1024) bwd_heads_kernel(const T* __restrict__ q, const T* __restrict__ k,
-                                                         const float* __restrict__ q_bias, const float* __restrict__ k_bias,
-                                                         const float* __restrict__ theta, const float* __restrict__ gamma,
-                                                         const float* __restrict__ scale, const C* __restrict__ dqr,
-                                                         const C* __restrict__ dkr, const float* __restrict__ dqk,
-                                                         float* __restrict__ dq, float* __restrict__ dk, float* __restrict__ dtheta,
-                                                         float* __restrict__ dgamma, float* __restrict__ dscale,
-                                                         float* __restrict__ bias_partials, int64_t rows, int64_t frows, int groups,
-                                                         int heads, int n_angles, int seq_len, int dkr_pad) {
-  extern __shared__ float sm[];
-  const int lane = threadIdx.x & 31, r = threadIdx.x >> 5;
-  const int rep = heads / groups;
-  float* red_q = sm;                          // [rep][N]
-  float* red_k = sm + rep * N;                // [rep][N]
-  float* bias_acc = sm + 2 * rep * N;         // [2][heads][N]
-  const bool want_bias = bias_partials != nullptr;
-  if (want_bias) {
-    for (int i = threadIdx.x; i < 2 * heads * N; i += blockDim.x) bias_acc[i] = 0.f;
-    __syncthreads();
-  }
-  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    const int g = (int)(row % groups);
-    const int64_t tok = row / groups;
-    const int64_t frow = row % frows, ftok = frow / groups;
-    const int h = g * rep + r;
-    const int64_t hrow = tok * heads + h, fhrow = ftok * heads + h;
-    const float4 qg = ld4<T>(q + frow * N + lane * 4), kg = ld4<T>(k + frow * N + lane * 4);
-    const float4 qb = ld4<float>(q_bias + h * N + lane * 4), kb = ld4<float>(k_bias + h * N + lane * 4);
-    const int64_t krow = dkr_pad > 0 ? ((tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len)) * heads + h : hrow;
-    const float4 gq = ld4<C>(dqr + hrow * N + lane * 4), gk = ld4<C>(dkr + krow * N + lane * 4);
-    const Rot rot = load_rot(theta + fhrow * n_angles, lane, n_angles);
-    const float sc = scale[fhrow], gm = gamma[fhrow], dd = dqk[hrow];
-    const float4 qh = make_float4(qg.x + qb.x, qg.y + qb.y, qg.z + qb.z, qg.w + qb.w);
-    const float4 kh = make_float4(kg.x + kb.x, kg.y + kb.y, kg.z + kb.z, kg.w + kb.w);
-    const float4 qo = rotate(qh, rot), ko = rotate(kh, rot);
-    const float dth0 = (-gq.x * qo.y + gq.y * qo.x) + sc * (-gk.x * ko.y + gk.y * ko.x);
-    const float dth1 = (-gq.z * qo.w + gq.w * qo.z) + sc * (-gk.z * ko.w + gk.w * ko.z);
-    if (2 * lane < n_angles) dtheta[hrow * n_angles + 2 * lane] = dth0;
-    if (2 * lane + 1 < n_angles) dtheta[hrow * n_angles + 2 * lane + 1] = dth1;
-    const float dsc = warp_sum(gk.x * ko.x + gk.y * ko.y + gk.z * ko.z + gk.w * ko.w);
-    const float qk = warp_sum(qh.x * kh.x + qh.y * kh.y + qh.z * kh.z + qh.w * kh.w);
-    if (lane == 0) {
-      dscale[hrow] = dsc;
-      dgamma[hrow] = dd * qk;
-    }
-    float4 dqh = rotate_back(gq, rot);
-    float4 dkh = rotate_back(make_float4(gk.x * sc, gk.y * sc, gk.z * sc, gk.w * sc), rot);
-    const float w = dd * gm;
-    dqh = make_float4(dqh.x + w * kh.x, dqh.y + w * kh.y, dqh.z + w * kh.z, dqh.w + w * kh.w);
-    dkh = make_float4(dkh.x + w * qh.x, dkh.y + w * qh.y, dkh.z + w * qh.z, dkh.w + w * qh.w);
-    *reinterpret_cast<float4*>(red_q + r * N + lane * 4) = dqh;
-    *reinterpret_cast<float4*>(red_k + r * N + lane * 4) = dkh;
-    if (want_bias) {   // each (head, element) is owned by one thread of the block: plain adds
-      float4* bq = reinterpret_cast<float4*>(bias_acc + (int64_t)h * N + lane * 4);
-      float4* bk = reinterpret_cast<float4*>(bias_acc + (int64_t)(heads + h) * N + lane * 4);
-      float4 a = *bq, b = *bk;
-      *bq = make_float4(a.x + dqh.x, a.y + dqh.y, a.z + dqh.z, a.w + dqh.w);
-      *bk = make_float4(b.x + dkh.x, b.y + dkh.y, b.z + dkh.z, b.w + dkh.w);
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < 2 * N; i += blockDim.x) {
-      const float* src = i < N ? red_q + i : red_k + (i - N);
-      float acc = 0.f;
-      for (int rr = 0; rr < rep; ++rr) acc += src[rr * N];
-      (i < N ? dq : dk)[row * N + (i < N ? i : i - N)] = acc;
-    }
-    __syncthreads();
-  }
-  if (want_bias) {
-    float* out = bias_partials + (int64_t)blockIdx.x * 2 * heads * N;
-    for (int i = threadIdx.x; i < 2 * heads * N; i += blockDim.x) out[i] = bias_acc[i];
-  }
-}
-
 static int grid_for(int64_t rows) {
   int64_t blocks = (rows + WARPS - 1) / WARPS;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > 148 * 8) blocks = 148 * 8;
   return (int)(blocks < 1 ? 1 : blocks);
 }
 
@@ -287,19 +252,6 @@ static int launch_bwd(const void* q, const void* k, const float* q_bias, const f
                       float* dgamma, float* dscale, float* bias_partials, int64_t rows, int64_t frows, int groups, int heads,
                       int n_angles, int seq_len, int dkr_pad, cudaStream_t st) {
   const int blocks = grid_for(rows);
-  const int rep = heads / groups;
-  if (rep >= 2 && rep <= 32) {
-    const size_t smem2 = (size_t)(2 * rep + 2 * heads) * N * sizeof(float);
-    if (smem2 <= 200 * 1024) {
-      static PerDeviceOnce configured2;
-      cudaError_t e2 = configured2.max_dynamic_smem(bwd_heads_kernel<T, C>, (int)(200 * 1024));
-      if (e2 != cudaSuccess) return (int)e2;
-      bwd_heads_kernel<T, C><<<blocks, rep * 32, smem2, st>>>((const T*)q, (const T*)k, q_bias, k_bias, theta, gamma, scale, (const C*)dqr,
-                                                             (const C*)dkr, dqk, dq, dk, dtheta, dgamma, dscale, bias_partials, rows,
-                                                             frows, groups, heads, n_angles, seq_len, dkr_pad);
-      return (int)cudaGetLastError();
-    }
-  }
   const size_t smem = (size_t)2 * heads * N * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   static PerDeviceOnce configured;

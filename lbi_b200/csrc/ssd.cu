@@ -1126,6 +1126,176 @@ __global__ void rev_state_passing_kernel(const float* __restrict__ chunk_cot, co
   if (d_init) d_init[idx] = st;
 }
 
+// Reversed state passing fused with its chunk products: one CTA owns one head (PH) or two heads of a group of one batch row
+// and walks the chunks from the last to the first.  Per chunk the TMA thread loads the gy and cq tiles (two stages), the
+// compute warps scale the gy rows by e^{c_t} in shared memory, one thread issues the product sum_t e^{c_t} gy_t cq_t^T into
+// one of two TMEM buffers, and each compute thread keeps one row of the running cotangent state in registers:
+//   d_out[c] = state (bf16, written while the product runs),   state = e^{cum_end(c)} state + product(c).
+// Nothing but gy, cq and d_out touches global memory (the per-chunk products and the running state stay on chip).
+template <int N, bool PH>
+struct SmemRev {
+  alignas(1024) uint8_t xs[2][PH ? 1 : 2][PANEL];   // [stage][head]: gy [l][64 p]
+  alignas(1024) uint8_t bt[2][N / 64][PANEL];       // [stage]: cq [l][64 n] per panel
+  uint64_t bar_full[2], bar_scaled[2], bar_done[2], bar_free[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+struct RevParams {
+  int seq_len, heads, groups, chunks, bmod;
+  const float* cum;        // [bmod, H, L_total]
+  const float* d_final;    // [B, H, elems] or null
+  __nv_bfloat16* d_out;    // [B, C, H, elems]
+  float* d_init;           // [B, H, elems] or null
+  int* status;
+};
+
+template <int N, bool PH>
+__global__ void __launch_bounds__(THREADS, PH ? 2 : 1) rev_state_kernel(const __grid_constant__ CUtensorMap map_g,
+                                                                         const __grid_constant__ CUtensorMap map_c,
+                                                                         const RevParams p) {
+  extern __shared__ uint8_t raw_smem[];
+  SmemRev<N, PH>& s = *reinterpret_cast<SmemRev<N, PH>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hp = blockIdx.x, b = blockIdx.y;
+  const int h0 = PH ? hp : 2 * hp;
+  const int g = PH ? h0 : h0 / (p.heads / p.groups);
+  const int fb = b % p.bmod;
+  constexpr uint32_t COLS = PH ? 64 : N;          // TMEM columns of one product
+  constexpr int ROW = PH ? P : N;                 // elements of the state row a compute thread keeps
+  constexpr int ELEMS = P * N;
+
+  if (threadIdx.x == 0) {
+    s.abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.bar_full[i], 1);
+      mbar_init(&s.bar_scaled[i], 4);
+      mbar_init(&s.bar_done[i], 1);
+      mbar_init(&s.bar_free[i], 4);
+    }
+    fence_barrier_init();
+    prefetch_tmap(&map_g);
+    prefetch_tmap(&map_c);
+  }
+  if (warp == 4) tmem_alloc(&s.tmem_base, 2 * COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abortp = &s.abort_flag;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      auto issue_loads = [&](int it) {
+        const int c = p.chunks - 1 - it, st = it & 1;
+        const int row0 = b * p.seq_len + c * L, frow0 = fb * p.seq_len + c * L;
+        mbar_arrive_expect_tx(&s.bar_full[st], ((PH ? 1 : 2) + N / 64) * PANEL);
+        tma_load_2d(s.xs[st][0], &map_g, &s.bar_full[st], h0 * P, row0);
+        if (!PH) tma_load_2d(s.xs[st][PH ? 0 : 1], &map_g, &s.bar_full[st], (h0 + 1) * P, row0);
+        for (int q = 0; q < N / 64; ++q) tma_load_2d(s.bt[st][q], &map_c, &s.bar_full[st], g * N + q * 64, frow0);
+      };
+      issue_loads(0);
+      bool ok = true;
+      for (int it = 0; it < p.chunks && ok; ++it) {
+        const int st = it & 1, k = it >> 1;
+        if (it + 1 < p.chunks) {
+          // the stage of chunk it + 1 was read by the product of chunk it - 1
+          if (it >= 1) ok = mbar_wait(&s.bar_done[(it + 1) & 1], ((it - 1) >> 1) & 1, abortp, p.status, 54);
+          if (!ok) break;
+          issue_loads(it + 1);
+        }
+        ok = mbar_wait(&s.bar_scaled[st], k & 1, abortp, p.status, 55);
+        if (ok && it >= 2) ok = mbar_wait(&s.bar_free[st], (k - 1) & 1, abortp, p.status, 56);
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t idesc = make_idesc_bf16(128, PH ? 64 : N, 1, 1);
+        const uint64_t da = make_smem_desc(smem_u32(PH ? s.bt[st][0] : s.xs[st][0]), PANEL, 1024);
+        const uint64_t db = make_smem_desc(smem_u32(PH ? s.xs[st][0] : s.bt[st][0]), PANEL, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) mma_bf16(tmem + st * COLS, da + 128 * kk, db + 128 * kk, idesc, kk);
+        mma_commit(&s.bar_done[st]);
+      }
+    }
+  } else {
+    const int l = warp * 32 + lane;   // token of the chunk in the scaling pass; row of the state otherwise
+    const int h = PH ? h0 : h0 + (l >> 6), pp = l & 63;
+    const int64_t row_off = PH ? (int64_t)l * P : (int64_t)pp * N;
+    const int64_t bh = (int64_t)b * p.heads + h;
+    float stv[ROW];
+    if (p.d_final) {
+      const float4* src = reinterpret_cast<const float4*>(p.d_final + bh * ELEMS + row_off);
+#pragma unroll
+      for (int e = 0; e < ROW / 4; ++e) {
+        const float4 v = src[e];
+        stv[4 * e] = v.x; stv[4 * e + 1] = v.y; stv[4 * e + 2] = v.z; stv[4 * e + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < ROW; ++e) stv[e] = 0.f;
+    }
+    bool ok = true;
+    for (int it = 0; it < p.chunks && ok; ++it) {
+      const int c = p.chunks - 1 - it, st = it & 1, k = it >> 1;
+      const int64_t base0 = ((int64_t)fb * p.heads + h0) * p.seq_len + c * L;
+      const float f0 = ex2(p.cum[base0 + l] * LOG2E);
+      const float f1 = PH ? 0.f : ex2(p.cum[base0 + p.seq_len + l] * LOG2E);
+      const float decay = ex2(p.cum[((int64_t)fb * p.heads + h) * p.seq_len + c * L + L - 1] * LOG2E);
+      ok = mbar_wait(&s.bar_full[st], k & 1, abortp, p.status, 57);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      scale_row(smem_u32(s.xs[st][0]), l, f0);
+      if (!PH) scale_row(smem_u32(s.xs[st][PH ? 0 : 1]), l, f1);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.bar_scaled[st]);
+      // the state that leaves chunk c, written while the product runs
+      {
+        __nv_bfloat16* dst = p.d_out + (((int64_t)b * p.chunks + c) * p.heads + h) * ELEMS + row_off;
+#pragma unroll
+        for (int e = 0; e < ROW / 8; ++e) {
+          uint4 o;
+          o.x = pack2(stv[8 * e], stv[8 * e + 1]);
+          o.y = pack2(stv[8 * e + 2], stv[8 * e + 3]);
+          o.z = pack2(stv[8 * e + 4], stv[8 * e + 5]);
+          o.w = pack2(stv[8 * e + 6], stv[8 * e + 7]);
+          reinterpret_cast<uint4*>(dst)[e] = o;
+        }
+      }
+      ok = mbar_wait(&s.bar_done[st], k & 1, abortp, p.status, 58);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      fence_after_sync();
+#pragma unroll
+      for (int q = 0; q < ROW / 32; ++q) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem + ((uint32_t)(warp * 32) << 16) + st * COLS + q * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) stv[q * 32 + e] = fmaf(stv[q * 32 + e], decay, __uint_as_float(r[e]));
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.bar_free[st]);
+    }
+    if (ok && p.d_init) {
+      float4* dst = reinterpret_cast<float4*>(p.d_init + bh * ELEMS + row_off);
+#pragma unroll
+      for (int e = 0; e < ROW / 4; ++e) dst[e] = make_float4(stv[4 * e], stv[4 * e + 1], stv[4 * e + 2], stv[4 * e + 3]);
+    }
+  }
+  __syncwarp();
+  if (s.abort_flag) {
+    const unsigned long long t0 = global_ns();
+    while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 4) {
+    fence_after_sync();
+    tmem_dealloc(tmem, 2 * COLS);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ 6. backward glue
 // dx = dt * dX + D * gy,  ddt = da * A + dX . x,  dD[h] += sum gy . x        with dX read in reversed time order.
 // One warp per (batch, token, head) row of 64; dD through one atomic per warp.
@@ -1355,20 +1525,13 @@ static int run_bwd(const void* v, const void* gy, const void* bk, const void* cq
   if (rc) return rc;
   rc = PH ? make_map(&md, d_out, (int64_t)batch * chunks * heads * N, P, N) : make_map(&md, d_out, (int64_t)batch * chunks * heads * P, N, P);
   if (rc) return rc;
-  {   // per-chunk state cotangents: (gy o e^{c})^T cq, the chunk-state product with gy as the v operand and cq as the B operand
-    StateParams p{seq_len, heads, groups, chunks, 1, 1, nullptr, cum, chunk_cot, status, 1, bmod};
-    const size_t smem = sizeof(SmemState<N>) + 1024;
-    rc = set_smem(chunk_state_kernel<N, PH>, smem);
+  {   // cotangents of the chunk-boundary states: chunk products and the reversed passing in one kernel
+    (void)chunk_cot;
+    RevParams rp{seq_len, heads, groups, chunks, bmod, cum, d_final, (__nv_bfloat16*)d_out, d_init, status};
+    const size_t smem = sizeof(SmemRev<N, PH>) + 1024;
+    rc = set_smem(rev_state_kernel<N, PH>, smem);
     if (rc) return rc;
-    chunk_state_kernel<N, PH><<<dim3(chunks, PH ? heads : heads / 2, batch), THREADS, smem, st>>>(mg, mc, p);
-    rc = (int)cudaGetLastError();
-    if (rc) return rc;
-  }
-  {
-    const int elems = P * N;
-    const int64_t total = (int64_t)batch * heads * elems;
-    rev_state_passing_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(chunk_cot, cum, d_final, (__nv_bfloat16*)d_out, d_init,
-                                                                             batch, bmod, heads, chunks, seq_len, elems);
+    rev_state_kernel<N, PH><<<dim3(PH ? heads : heads / 2, batch), THREADS, smem, st>>>(mg, mc, rp);
     rc = (int)cudaGetLastError();
     if (rc) return rc;
   }
