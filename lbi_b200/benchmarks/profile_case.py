@@ -13,6 +13,7 @@
     python -m lbi_b200.benchmarks.profile_case --case chunk_bwd_ssd      # fused chunk backward, Mamba-2 form (grouped B / C, weight dt)
     python -m lbi_b200.benchmarks.profile_case --case mamba_glue         # gate, small-tensor fwd / bwd, conv + SiLU fwd / bwd / wgrad
     python -m lbi_b200.benchmarks.profile_case --case small              # interface / scan / optimizer / embedding / CE kernels
+    python -m lbi_b200.benchmarks.profile_case --case prep_bwd           # SISO preprocessing backward as the pullback runs it (bf16 cotangents, 16 directions, no bias gradients)
 
 Each case holds well under 2 GB on the device, touches more than the 126 MB L2, launches the kernel of interest a
 handful of times and exits.  Typical capture:
@@ -31,7 +32,7 @@ from lbi_b200 import ops
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", required=True, choices=["attn", "gemm", "dgrad", "elementwise", "scan", "attn_fwd", "ssd", "ssd_bwd", "mamba_elementwise", "chunk_bwd",
-                             "chunk_bwd_ssd", "mamba_glue", "small"])
+                             "chunk_bwd_ssd", "mamba_glue", "small", "prep_bwd"])
     ap.add_argument("--repeats", type=int, default=2)
     args = ap.parse_args()
     dev = "cuda"
@@ -126,6 +127,18 @@ def main() -> None:
             torch.autograd.grad(y, (x, z, w), gy)
             _WidePrepFunction.apply(q, k, qb, kb, theta, gamma, scale)
             ops.ext().siso_prep_bwd(q, k, qb, kb, theta, gamma, scale, dqr, dkr, dqk)
+    elif args.case == "prep_bwd":
+        b, reps, l, h, n = 2, 16, 1024, 24, 128
+        q = torch.randn(b, l, 1, n, device=dev).bfloat16()
+        k = torch.randn(b, l, 1, n, device=dev).bfloat16()
+        qb, kb = torch.randn(h, n, device=dev), torch.randn(h, n, device=dev)
+        theta = torch.rand(b, l, h, 32, device=dev) * 6.28
+        gamma, scale = torch.rand(b, l, h, device=dev), torch.rand(b, l, h, device=dev)
+        dqr = torch.randn(reps * b, l, h, n, device=dev).bfloat16()
+        dkr = torch.randn(reps * b, l, h, n, device=dev).bfloat16()
+        dqk = torch.randn(reps * b, l, h, device=dev)
+        for _ in range(args.repeats):
+            ops.ext().siso_prep_bwd(q, k, qb, kb, theta, gamma, scale, dqr, dkr, dqk, False, False)
     elif args.case in ("chunk_bwd", "chunk_bwd_ssd"):
         from lbi_b200.ops import ssd
 

@@ -111,11 +111,13 @@ int lbi_siso_small_fwd(const float* dd_dt, const float* dd_a, const float* trap,
                        cudaStream_t stream);
 // Cotangents dadt, dgamma, dscale [reps * B, L, H] and dtheta [reps * B, L, H, S] -> d_dd_dt, d_dd_a, d_trap [reps * B * L, H]
 // and d_angles [reps * B * L, S] (fp32 or bf16); the forward tensors [B, ...] are shared by the reps directions.
-// H <= 32, S <= 32.
+// H <= 32, S <= 32.  Scratch: seg_sum [reps * B, lbi_siso_small_segments(L), H, 32] fp32 (dtheta summed per segment of the
+// sequence, so that the reversed running sum can start in every segment at once).  Two kernels on `stream`.
+int lbi_siso_small_segments(int seq_len);
 int lbi_siso_small_bwd(const float* dt, const float* a, const float* sig, const float* tanh_a, const float* sp_dt,
                        const float* sp_a, const float* live, const float* dadt, const float* dtheta, const float* dgamma,
-                       const float* dscale, void* d_dd_dt, void* d_dd_a, void* d_trap, void* d_angles, int batch, int reps,
-                       int seq_len, int heads, int n_angles, int out_bf16, cudaStream_t stream);
+                       const float* dscale, float* seg_sum, void* d_dd_dt, void* d_dd_a, void* d_trap, void* d_angles, int batch,
+                       int reps, int seq_len, int heads, int n_angles, int out_bf16, cudaStream_t stream);
 
 // Mamba-2 depthwise causal conv + SiLU over the xBC slice (channels = c0 + c1 + c2, each a multiple of 8; width <= 8).
 // x [tokens, channels] bf16, wt [width, channels] (the weights TRANSPOSED), bias [channels] or null (fp32) -> pre [tokens, channels] bf16 (conv output) and

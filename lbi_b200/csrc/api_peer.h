@@ -23,11 +23,14 @@ int lbi_peer_barrier(uint32_t* const* flag_ptrs, int rank, int world, int slot_b
 //   delta = W2 act(W1 pooled + b1) + b2   (or W1 pooled + b1 when hidden == 0)
 //   pre   = state_in + tanh(alpha) * delta ;  state_out = LayerNorm(pre) * ln_w + ln_b
 // state_out is stored locally and, when peer_state is not null, into the next owner's mailbox, followed by a
-// release-store of `seq` to peer_flag.  One CTA per batch row.  act: 0 = SiLU, 1 = GELU.
+// release-store of `seq` to peer_flag.  act: 0 = SiLU, 1 = GELU.  With a hidden layer, a scratch buffer hidden_buf
+// [batch, hidden] and batch <= 8 the hidden units are spread over the grid (the first weight matrix is read once) and the CTA
+// that finishes last runs the second layer, the LayerNorm and the peer store; otherwise one CTA per batch row does it all.
+// done_counter: a zeroed device word, left zero.
 int lbi_interface_update_handoff(const float* state_in, const float* pooled, const float* w1, const float* b1,
                                  const float* w2, const float* b2, const float* alpha, const float* ln_w,
                                  const float* ln_b, float ln_eps, int act, int batch, int dim, int hidden, int width,
-                                 float* delta_out, float* pre_out, float* state_out, float* peer_state,
+                                 float* hidden_buf, float* delta_out, float* pre_out, float* state_out, float* peer_state,
                                  uint32_t* peer_flag, uint32_t seq, uint32_t* done_counter, cudaStream_t stream);
 
 // Receiver side of the hand-off: wait until flag >= seq, then copy the mailbox into `out`.

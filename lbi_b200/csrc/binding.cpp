@@ -494,9 +494,11 @@ std::vector<Tensor> siso_small_bwd(const Tensor& dt, const Tensor& a, const Tens
   const int64_t rows = reps * batch * seq;
   Tensor d1 = torch::empty({rows, heads}, opt), d2 = torch::empty({rows, heads}, opt), d3 = torch::empty({rows, heads}, opt);
   Tensor d4 = torch::empty({rows, na}, opt);
+  Tensor seg_sum = torch::empty({reps * batch, (int64_t)lbi_siso_small_segments((int)seq), heads, 32}, dt.options());
   check(lbi_siso_small_bwd(dt.data_ptr<float>(), a.data_ptr<float>(), sig.data_ptr<float>(), tanh_a.data_ptr<float>(),
                            sp_dt.data_ptr<float>(), sp_a.data_ptr<float>(), live.data_ptr<float>(), dadt.data_ptr<float>(),
-                           dtheta.data_ptr<float>(), dgamma.data_ptr<float>(), dscale.data_ptr<float>(), d1.data_ptr(), d2.data_ptr(),
+                           dtheta.data_ptr<float>(), dgamma.data_ptr<float>(), dscale.data_ptr<float>(), seg_sum.data_ptr<float>(),
+                           d1.data_ptr(), d2.data_ptr(),
                            d3.data_ptr(), d4.data_ptr(), (int)batch, (int)reps, (int)seq, (int)heads, (int)na, out_bf16 ? 1 : 0,
                            cur_stream()),
         "siso_small_bwd");
@@ -1058,13 +1060,14 @@ std::tuple<Tensor, Tensor, Tensor> interface_update_handoff(
   TORCH_CHECK(w1.size(1) == dim && (two_layer ? (w2->size(0) == width && w2->size(1) == hidden) : w1.size(0) == width),
               "interface map shapes do not match");
   Tensor delta = torch::empty_like(state_in), pre = torch::empty_like(state_in), out = torch::empty_like(state_in);
+  Tensor hidden_buf = torch::empty({batch, std::max(hidden, 1)}, state_in.options());
   auto opt_ptr = [](const c10::optional<Tensor>& t) -> const float* {
     return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr;
   };
   check(lbi_interface_update_handoff(state_in.data_ptr<float>(), pooled.data_ptr<float>(), w1.data_ptr<float>(), opt_ptr(b1),
                                      opt_ptr(w2), opt_ptr(b2), alpha.data_ptr<float>(), ln_w.data_ptr<float>(),
                                      ln_b.data_ptr<float>(), (float)ln_eps, (int)act, batch, dim, hidden, width,
-                                     delta.data_ptr<float>(), pre.data_ptr<float>(), out.data_ptr<float>(),
+                                     hidden_buf.data_ptr<float>(), delta.data_ptr<float>(), pre.data_ptr<float>(), out.data_ptr<float>(),
                                      reinterpret_cast<float*>(peer_state_ptr), reinterpret_cast<uint32_t*>(peer_flag_ptr),
                                      (uint32_t)seq, reinterpret_cast<uint32_t*>(done_counter.data_ptr<int>()), cur_stream()),
         "interface_update_handoff");

@@ -133,8 +133,32 @@ __global__ void siso_small_fwd_kernel(const float* __restrict__ dd_dt, const flo
 }
 
 // ------------------------------------------------------------------------------------------------ siso small, backward
-// grid (P * B), block = heads * 32 (heads <= 32, n_angles <= 32).  Forward tensors are indexed by b = blockIdx.x % batch.
-constexpr int TL = 8;   // tokens per tile
+// grid (P * B, segments), block = heads * 32 (heads <= 32, n_angles <= 32).  Forward tensors are indexed by b = blockIdx.x % batch.
+// The reversed running sum of dtheta is the only dependency along the sequence: the sequence is cut into segments of SEG
+// tokens, a first kernel sums dtheta per (sequence, segment, head, angle), and a block of the second kernel starts its sum
+// from the totals of the later segments.
+constexpr int TL = 8;     // tokens per tile
+constexpr int SEG = 64;   // tokens per segment (a multiple of TL)
+
+// grid (P * B, segments), block = heads * 32: seg_sum[pb][seg][h][32]
+__global__ void __launch_bounds__(1024) dtheta_segment_sums_kernel(const float* __restrict__ dtheta, float* __restrict__ seg_sum,
+                                                                   int seq_len, int heads, int n_angles) {
+  const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pb = blockIdx.x, seg = blockIdx.y;
+  const int t_lo = seg * SEG, t_hi = min(seq_len, t_lo + SEG);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (lane < n_angles) {
+    const float* src = dtheta + (((int64_t)pb * seq_len + t_lo) * heads + h) * n_angles + lane;
+    const int64_t stride = (int64_t)heads * n_angles;
+    int t = t_lo;
+    for (; t + 4 <= t_hi; t += 4) {   // four independent loads in flight
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] += src[(int64_t)(t - t_lo + j) * stride];
+    }
+    for (; t < t_hi; ++t) acc[0] += src[(int64_t)(t - t_lo) * stride];
+  }
+  seg_sum[(((int64_t)pb * gridDim.y + seg) * heads + h) * 32 + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+}
 
 template <typename OutT>
 __device__ __forceinline__ void put(OutT* p, float v);
@@ -148,57 +172,77 @@ __global__ void __launch_bounds__(1024) siso_small_bwd_kernel(
     const float* __restrict__ dt, const float* __restrict__ a, const float* __restrict__ sig, const float* __restrict__ tanh_a,
     const float* __restrict__ sp_dt, const float* __restrict__ sp_a, const float* __restrict__ live,
     const float* __restrict__ dadt, const float* __restrict__ dtheta, const float* __restrict__ dgamma,
-    const float* __restrict__ dscale, OutT* __restrict__ d_dd_dt, OutT* __restrict__ d_dd_a, OutT* __restrict__ d_trap,
-    OutT* __restrict__ d_angles, int batch, int seq_len, int heads, int n_angles) {
-  extern __shared__ float contrib[];   // [TL][heads][32]: pi * (reversed running sum of dtheta) * DT per token, head, angle
+    const float* __restrict__ dscale, const float* __restrict__ seg_sum, OutT* __restrict__ d_dd_dt, OutT* __restrict__ d_dd_a,
+    OutT* __restrict__ d_trap, OutT* __restrict__ d_angles, int batch, int seq_len, int heads, int n_angles) {
+  extern __shared__ float contrib[];   // [TL][heads][32]: pi * (reversed running sum of dtheta) * DT per token, head, angle; then [TL][32]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = warp;
   const int pb = blockIdx.x, b = pb % batch;
   const int64_t frow0 = (int64_t)b * seq_len, crow0 = (int64_t)pb * seq_len;
   const bool has = lane < n_angles;
+  const int seg = blockIdx.y, t_first = seg * SEG;
   float acc = 0.f;
-  for (int t_hi = seq_len - 1; t_hi >= 0; t_hi -= TL) {
+  for (int sg = seg + 1; sg < (int)gridDim.y; ++sg) acc += seg_sum[(((int64_t)pb * gridDim.y + sg) * heads + h) * 32 + lane];
+  float* tanh_tile = contrib + TL * heads * 32;   // [TL][32]: tanh(angle) of the tile's tokens, for the head sum
+  for (int t_hi = min(seq_len, t_first + SEG) - 1; t_hi >= t_first; t_hi -= TL) {
+    // every global load of the tile goes out here, in one round (the tile is bound by load latency, not by bandwidth)
     float dth[TL], tn[TL], dts[TL];
 #pragma unroll
     for (int j = 0; j < TL; ++j) {
       const int t = t_hi - j;
-      const bool ok = t >= 0;
+      const bool ok = t >= t_first;
       dth[j] = (ok && has) ? dtheta[((crow0 + t) * heads + h) * n_angles + lane] : 0.f;
       tn[j] = (ok && has) ? tanh_a[(frow0 + t) * n_angles + lane] : 0.f;
       dts[j] = ok ? dt[(frow0 + t) * heads + h] : 0.f;
     }
+    // lane j < TL finishes the [b, l, h]-sized cotangents of token t_hi - j
+    const int t_mine = t_hi - lane;
+    const bool mine_ok = lane < TL && t_mine >= t_first;
+    const int64_t fi = (frow0 + t_mine) * heads + h, ci = (crow0 + t_mine) * heads + h;
+    float e_dsc = 0.f, e_prev = 0.f, e_dg = 0.f, e_sg = 0.f, e_dt = 0.f, e_da = 0.f, e_a = 0.f, e_spdt = 0.f, e_spa = 0.f, e_live = 0.f;
+    if (mine_ok) {
+      e_dsc = dscale[ci];
+      e_prev = (t_mine > 0 && LBI_IN_RANGE(ci - heads, (int64_t)gridDim.x * seq_len * heads, 94)) ? dscale[ci - heads] : 0.f;
+      e_dg = dgamma[ci];
+      e_sg = sig[fi];
+      e_dt = dt[fi];
+      e_da = dadt[ci];
+      e_a = a[fi];
+      e_spdt = sp_dt[fi];
+      e_spa = sp_a[fi];
+      e_live = live[fi];
+    }
     float mine = 0.f;   // lane j keeps the rotary part of d DT of token t_hi - j
+    float run[TL];
 #pragma unroll
     for (int j = 0; j < TL; ++j) {
       acc += dth[j];
-      const float part = PI_F * warp_sum(acc * tn[j]);
-      if (lane == j) mine = part;
+      run[j] = acc;
       contrib[(j * heads + h) * 32 + lane] = PI_F * acc * dts[j];
+      if (h == 0) tanh_tile[j * 32 + lane] = tn[j];
     }
-    if (lane < TL) {
-      const int t = t_hi - lane;
-      if (t >= 0) {
-        const int64_t fi = (frow0 + t) * heads + h, ci = (crow0 + t) * heads + h;
-        const float dsc = dscale[ci];
-        const float dsc_prev = (t > 0 && LBI_IN_RANGE(ci - heads, (int64_t)gridDim.x * seq_len * heads, 94)) ? dscale[ci - heads] : 0.f;
-        const float dg_all = dgamma[ci] + dsc;
-        const float sg = sig[fi], dtv = dt[fi], da = dadt[ci];
-        const float d_dt = da * a[fi] + mine + dg_all * sg + dsc_prev * (1.f - sg);
-        const float d_sig = dtv * (dg_all - dsc_prev);
-        put(d_dd_dt + ci, d_dt * sp_dt[fi]);
-        put(d_dd_a + ci, -(da * dtv) * sp_a[fi] * live[fi]);
-        put(d_trap + ci, d_sig * sg * (1.f - sg));
-      }
+#pragma unroll
+    for (int j = 0; j < TL; ++j) {   // the TL reductions are independent: their shuffles overlap
+      const float part = PI_F * warp_sum(run[j] * tn[j]);
+      if (lane == j) mine = part;
+    }
+    if (mine_ok) {
+      const float dg_all = e_dg + e_dsc;
+      const float d_dt = e_da * e_a + mine + dg_all * e_sg + e_prev * (1.f - e_sg);
+      const float d_sig = e_dt * (dg_all - e_prev);
+      put(d_dd_dt + ci, d_dt * e_spdt);
+      put(d_dd_a + ci, -(e_da * e_dt) * e_spa * e_live);
+      put(d_trap + ci, d_sig * e_sg * (1.f - e_sg));
     }
     __syncthreads();
     // sum the heads: TL * n_angles outputs
     for (int o = threadIdx.x; o < TL * 32; o += blockDim.x) {
       const int j = o >> 5, s = o & 31;
       const int t = t_hi - j;
-      if (t >= 0 && s < n_angles) {
+      if (t >= t_first && s < n_angles) {
         float sum = 0.f;
         for (int hh = 0; hh < heads; ++hh) sum += contrib[(j * heads + hh) * 32 + s];
-        const float tv = tanh_a[(frow0 + t) * n_angles + s];
+        const float tv = tanh_tile[j * 32 + s];
         put(d_angles + (crow0 + t) * n_angles + s, sum * (1.f - tv * tv));
       }
     }
@@ -245,23 +289,27 @@ extern "C" int lbi_siso_small_fwd(const float* dd_dt, const float* dd_a, const f
   return (int)cudaGetLastError();
 }
 
+extern "C" int lbi_siso_small_segments(int seq_len) { return (seq_len + lbi::msmall::SEG - 1) / lbi::msmall::SEG; }
+
 extern "C" int lbi_siso_small_bwd(const float* dt, const float* a, const float* sig, const float* tanh_a, const float* sp_dt,
                                   const float* sp_a, const float* live, const float* dadt, const float* dtheta,
-                                  const float* dgamma, const float* dscale, void* d_dd_dt, void* d_dd_a, void* d_trap,
-                                  void* d_angles, int batch, int reps, int seq_len, int heads, int n_angles, int out_bf16,
-                                  cudaStream_t st) {
+                                  const float* dgamma, const float* dscale, float* seg_sum, void* d_dd_dt, void* d_dd_a,
+                                  void* d_trap, void* d_angles, int batch, int reps, int seq_len, int heads, int n_angles,
+                                  int out_bf16, cudaStream_t st) {
   using namespace lbi;
   if (batch <= 0 || reps <= 0 || seq_len <= 0) return 0;
-  if (heads > 32 || heads <= 0 || n_angles > 32 || n_angles <= 0) return (int)cudaErrorInvalidValue;
-  const size_t smem = (size_t)msmall::TL * heads * 32 * sizeof(float);
+  if (heads > 32 || heads <= 0 || n_angles > 32 || n_angles <= 0 || !seg_sum) return (int)cudaErrorInvalidValue;
+  const size_t smem = (size_t)msmall::TL * (heads + 1) * 32 * sizeof(float);
+  const dim3 grid(batch * reps, lbi_siso_small_segments(seq_len));
+  msmall::dtheta_segment_sums_kernel<<<grid, heads * 32, 0, st>>>(dtheta, seg_sum, seq_len, heads, n_angles);
   if (out_bf16)
-    msmall::siso_small_bwd_kernel<__nv_bfloat16><<<batch * reps, heads * 32, smem, st>>>(
-        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, (__nv_bfloat16*)d_dd_dt, (__nv_bfloat16*)d_dd_a,
-        (__nv_bfloat16*)d_trap, (__nv_bfloat16*)d_angles, batch, seq_len, heads, n_angles);
+    msmall::siso_small_bwd_kernel<__nv_bfloat16><<<grid, heads * 32, smem, st>>>(
+        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, seg_sum, (__nv_bfloat16*)d_dd_dt,
+        (__nv_bfloat16*)d_dd_a, (__nv_bfloat16*)d_trap, (__nv_bfloat16*)d_angles, batch, seq_len, heads, n_angles);
   else
-    msmall::siso_small_bwd_kernel<float><<<batch * reps, heads * 32, smem, st>>>(
-        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, (float*)d_dd_dt, (float*)d_dd_a, (float*)d_trap,
-        (float*)d_angles, batch, seq_len, heads, n_angles);
+    msmall::siso_small_bwd_kernel<float><<<grid, heads * 32, smem, st>>>(
+        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, seg_sum, (float*)d_dd_dt, (float*)d_dd_a,
+        (float*)d_trap, (float*)d_angles, batch, seq_len, heads, n_angles);
   return (int)cudaGetLastError();
 }
 

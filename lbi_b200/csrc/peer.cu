@@ -148,6 +148,105 @@ __global__ void __launch_bounds__(256) interface_update_handoff_kernel(
   }
 }
 
+// The same update with the hidden layer spread over the grid: one hidden unit per warp, every CTA handles all batch rows, so
+// the first weight matrix is read once (the per-row kernel above reads it once per batch row from a handful of CTAs and is
+// bound by load latency).  The CTA that finishes last (ticket counter) runs the narrow second layer, the LayerNorm, the
+// store into the peer's mailbox and the flag.  batch <= WIDE_MAXB.  Dynamic smem: batch * max(dim, hidden) + batch * width floats.
+constexpr int WIDE_MAXB = 8;
+__global__ void __launch_bounds__(256) interface_update_handoff_wide_kernel(
+    const float* __restrict__ state_in, const float* __restrict__ pooled, const float* __restrict__ w1,
+    const float* __restrict__ b1, const float* __restrict__ w2, const float* __restrict__ b2,
+    const float* __restrict__ alpha, const float* __restrict__ ln_w, const float* __restrict__ ln_b, float ln_eps, int act,
+    int batch, int dim, int hidden, int width, float* hidden_buf, float* __restrict__ delta_out, float* __restrict__ pre_out,
+    float* __restrict__ state_out, float* peer_state, uint32_t* peer_flag, uint32_t seq, uint32_t* ticket) {
+  extern __shared__ float sm[];
+  __shared__ int is_last;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  float* s_in = sm;                                              // [batch][dim], later [batch][hidden]
+  float* s_pre = sm + (size_t)batch * (dim > hidden ? dim : hidden);   // [batch][width]
+  for (int i = threadIdx.x; i < batch * dim; i += blockDim.x) s_in[i] = pooled[i];
+  __syncthreads();
+  const int hcol = blockIdx.x * nwarps + warp;
+  if (hcol < hidden) {
+    const float* wrow = w1 + (size_t)hcol * dim;
+    float acc[WIDE_MAXB];
+#pragma unroll
+    for (int b = 0; b < WIDE_MAXB; ++b) acc[b] = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float wv = wrow[i];
+#pragma unroll
+      for (int b = 0; b < WIDE_MAXB; ++b)
+        if (b < batch) acc[b] = fmaf(wv, s_in[b * dim + i], acc[b]);
+    }
+    const float bias = b1 ? b1[hcol] : 0.f;
+#pragma unroll
+    for (int b = 0; b < WIDE_MAXB; ++b) {
+      if (b < batch) {
+        const float v = warp_sum(acc[b]);
+        if (lane == 0) hidden_buf[(size_t)b * hidden + hcol] = activate(v + bias, act);
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1 ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  if (threadIdx.x == 0) *ticket = 0;
+  __threadfence();
+  for (int i = threadIdx.x; i < batch * hidden; i += blockDim.x) s_in[i] = __ldcg(hidden_buf + i);
+  __syncthreads();
+  const float scale = tanhf(*alpha);
+  for (int rcol = warp; rcol < width; rcol += nwarps) {
+    const float* wrow = w2 + (size_t)rcol * hidden;
+    float acc[WIDE_MAXB];
+#pragma unroll
+    for (int b = 0; b < WIDE_MAXB; ++b) acc[b] = 0.f;
+    for (int i = lane; i < hidden; i += 32) {
+      const float wv = wrow[i];
+#pragma unroll
+      for (int b = 0; b < WIDE_MAXB; ++b)
+        if (b < batch) acc[b] = fmaf(wv, s_in[b * hidden + i], acc[b]);
+    }
+    const float bias = b2 ? b2[rcol] : 0.f;
+#pragma unroll
+    for (int b = 0; b < WIDE_MAXB; ++b) {
+      if (b < batch) {
+        const float d = warp_sum(acc[b]) + bias;
+        if (lane == 0) {
+          const float pre = state_in[(size_t)b * width + rcol] + scale * d;
+          delta_out[(size_t)b * width + rcol] = d;
+          pre_out[(size_t)b * width + rcol] = pre;
+          s_pre[b * width + rcol] = pre;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  // LayerNorm over the interface width: one warp per batch row
+  for (int b = warp; b < batch; b += nwarps) {
+    float part = 0.f;
+    for (int i = lane; i < width; i += 32) part += s_pre[b * width + i];
+    const float mean = warp_sum(part) / (float)width;
+    part = 0.f;
+    for (int i = lane; i < width; i += 32) {
+      const float c = s_pre[b * width + i] - mean;
+      part += c * c;
+    }
+    const float rstd = rsqrtf(warp_sum(part) / (float)width + ln_eps);
+    for (int i = lane; i < width; i += 32) {
+      const float y = (s_pre[b * width + i] - mean) * rstd * ln_w[i] + ln_b[i];
+      state_out[(size_t)b * width + i] = y;
+      if (peer_state) peer_state[(size_t)b * width + i] = y;   // store into the next owner's mailbox over NVLink
+    }
+  }
+  if (peer_state) {
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(peer_flag, seq);
+  }
+}
+
 __global__ void wait_state_kernel(const float* mailbox, const uint32_t* flag, uint32_t seq, float* out, int n, int* status) {
   __shared__ int ok;
   if (threadIdx.x == 0) ok = wait_flag(flag, seq, status, 42) ? 1 : 0;
@@ -243,12 +342,24 @@ __global__ void __launch_bounds__(1024) affine_scan_peer_sum_kernel(const float*
     if (active) {
       float acc = 0.f;
       if (grp == 0)
-        for (int w = 0; w < world; ++w) acc += __ldcv(offs_ptrs[w] + off_base + a);
+        for (int w = 0; w < world; ++w) acc += __ldcg(offs_ptrs[w] + off_base + a);
       if (k < k_total - 1) {
-        for (int j = grp; j < r; j += groups) {
-          float m = 0.f;
-          for (int w = 0; w < world; ++w) m += __ldcv(rows_ptrs[w] + row_base + (size_t)j * r + a);
-          acc += m * cur[j];
+        // sixteen loads in flight per thread: the recursion is bound by load latency, not by bandwidth.  The data was
+        // complete before the flags were seen (acquire), so the loads need not be volatile; they bypass L1 only.
+        for (int j0 = grp; j0 < r; j0 += groups * 16) {
+          float m[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int j = j0 + u * groups;
+            m[u] = 0.f;
+            if (j < r)
+              for (int w = 0; w < world; ++w) m[u] += __ldcg(rows_ptrs[w] + row_base + (size_t)j * r + a);
+          }
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int j = j0 + u * groups;
+            if (j < r) acc = fmaf(m[u], cur[j], acc);
+          }
         }
       }
       part[grp * r + a] = acc;
@@ -405,9 +516,21 @@ int lbi_peer_signal_all(uint32_t* const* flag_ptrs, int rank, int world, int slo
 int lbi_interface_update_handoff(const float* state_in, const float* pooled, const float* w1, const float* b1,
                                  const float* w2, const float* b2, const float* alpha, const float* ln_w,
                                  const float* ln_b, float ln_eps, int act, int batch, int dim, int hidden, int width,
-                                 float* delta_out, float* pre_out, float* state_out, float* peer_state,
+                                 float* hidden_buf, float* delta_out, float* pre_out, float* state_out, float* peer_state,
                                  uint32_t* peer_flag, uint32_t seq, uint32_t* done_counter, cudaStream_t st) {
   if (batch <= 0) return 0;
+  if (hidden > 0 && hidden_buf && batch <= WIDE_MAXB) {
+    const size_t wide = ((size_t)batch * (dim > hidden ? dim : hidden) + (size_t)batch * width) * sizeof(float);
+    if (wide <= 200 * 1024) {
+      static lbi::PerDeviceOnce configured_wide;
+      cudaError_t e = configured_wide.max_dynamic_smem(interface_update_handoff_wide_kernel, (int)(200 * 1024));
+      if (e != cudaSuccess) return (int)e;
+      interface_update_handoff_wide_kernel<<<(hidden + 7) / 8, 256, wide, st>>>(
+          state_in, pooled, w1, b1, w2, b2, alpha, ln_w, ln_b, ln_eps, act, batch, dim, hidden, width, hidden_buf, delta_out,
+          pre_out, state_out, peer_state, peer_flag, seq, done_counter);
+      return (int)cudaGetLastError();
+    }
+  }
   const size_t smem = (size_t)(dim + (hidden > 0 ? hidden : 1) + width) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {

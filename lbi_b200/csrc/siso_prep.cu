@@ -111,11 +111,13 @@ template <typename C>
 __device__ __forceinline__ HeadIn load_head(const float* __restrict__ q_bias, const float* __restrict__ k_bias,
                                             const float* __restrict__ theta, const float* __restrict__ gamma,
                                             const float* __restrict__ scale, const C* __restrict__ dqr, const C* __restrict__ dkr,
-                                            const float* __restrict__ dqk, int64_t tok, int64_t ftok, int h, int heads, int n_angles,
-                                            int seq_len, int dkr_pad, int lane) {
+                                            const float* __restrict__ dqk, int64_t tok, int64_t ftok, int64_t ktok, int h, int heads,
+                                            int n_angles, int lane) {
+  // ktok: the row of dkr that holds token `tok` (the same token, or its place in the reversed, padded layout); computed once
+  // per token by the caller (it takes a 64-bit division)
   HeadIn in;
   const int64_t hrow = tok * heads + h, fhrow = ftok * heads + h;
-  const int64_t krow = dkr_pad > 0 ? ((tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len)) * heads + h : hrow;
+  const int64_t krow = ktok * heads + h;
   in.gq = ld4<C>(dqr + hrow * N + lane * 4);
   in.gk = ld4<C>(dkr + krow * N + lane * 4);
   in.qb = ld4<float>(q_bias + h * N + lane * 4);
@@ -129,7 +131,7 @@ __device__ __forceinline__ HeadIn load_head(const float* __restrict__ q_bias, co
 }
 
 template <typename T, typename C>
-__global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, const T* __restrict__ k,
+__global__ void __launch_bounds__(THREADS, 3) bwd_kernel(const T* __restrict__ q, const T* __restrict__ k,
                                                       const float* __restrict__ q_bias, const float* __restrict__ k_bias,
                                                       const float* __restrict__ theta, const float* __restrict__ gamma,
                                                       const float* __restrict__ scale, const C* __restrict__ dqr,
@@ -149,20 +151,20 @@ __global__ void __launch_bounds__(THREADS) bwd_kernel(const T* __restrict__ q, c
     __syncthreads();
   }
   for (int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * WARPS) {
-    const int g = (int)(row % groups);
-    const int64_t tok = row / groups;
-    const int64_t frow = row % frows, ftok = frow / groups;
+    // 64-bit divisions cost a hundred instructions each: one group and one direction per row are the common cases
+    const int g = groups == 1 ? 0 : (int)(row % groups);
+    const int64_t tok = groups == 1 ? row : row / groups;
+    const int64_t frow = row < frows ? row : row % frows, ftok = groups == 1 ? frow : frow / groups;
     const float4 qg = ld4<T>(q + frow * N + lane * 4), kg = ld4<T>(k + frow * N + lane * 4);
     float4 dq_sum = make_float4(0.f, 0.f, 0.f, 0.f), dk_sum = make_float4(0.f, 0.f, 0.f, 0.f);
-    HeadIn cur = load_head<C>(q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, tok, ftok, g * rep, heads, n_angles, seq_len,
-                              dkr_pad, lane);
+    const int64_t ktok = dkr_pad > 0 ? (tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len) : tok;
+    HeadIn cur = load_head<C>(q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, tok, ftok, ktok, g * rep, heads, n_angles, lane);
     for (int r = 0; r < rep; ++r) {
       const int h = g * rep + r;
       const int64_t hrow = tok * heads + h;
       HeadIn nxt = cur;
       if (r + 1 < rep)
-        nxt = load_head<C>(q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, tok, ftok, h + 1, heads, n_angles, seq_len, dkr_pad,
-                           lane);
+        nxt = load_head<C>(q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, tok, ftok, ktok, h + 1, heads, n_angles, lane);
       const float4 qh = make_float4(qg.x + cur.qb.x, qg.y + cur.qb.y, qg.z + cur.qb.z, qg.w + cur.qb.w);
       const float4 kh = make_float4(kg.x + cur.kb.x, kg.y + cur.kb.y, kg.z + cur.kb.z, kg.w + cur.kb.w);
       Rot rot{1.f, 0.f, 1.f, 0.f};

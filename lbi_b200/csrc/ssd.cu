@@ -690,7 +690,8 @@ template <int N>
 struct SmemBwd {
   alignas(1024) uint8_t ct[N / 64][PANEL];      // cq [t][64 n] per panel
   alignas(1024) uint8_t bt[N / 64][PANEL];      // bk [s][64 n] per panel
-  alignas(1024) uint8_t gyt[PANEL];             // gy [t][64 p]; rows scaled by e^{c_t} once dX has been taken
+  alignas(1024) uint8_t gyt[PANEL];             // gy [t][64 p]
+  alignas(1024) uint8_t gys[PANEL];             // gy rows scaled by e^{c_t} (the A operand of the state term of dcq)
   alignas(1024) uint8_t xt[PANEL];              // v  [s][64 p]; rows scaled by w_s e^{c_end - c_s}
   alignas(1024) uint8_t hin[N / 64][P * 128];   // S_in
   alignas(1024) uint8_t dho[N / 64][P * 128];   // D_out
@@ -703,7 +704,7 @@ struct SmemBwd {
   float r2[L];
   float r3[L];
   float red[BWD_WARPS];
-  uint64_t bar_full, bar_mma, bar_w, bar_x, bar_x2, bar_y, bar_rows;
+  uint64_t bar_full, bar_mma, bar_st, bar_w, bar_y, bar_rows;
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -738,6 +739,19 @@ __device__ __forceinline__ void store_row(float* dst32, __nv_bfloat16* dst16, co
                      pack2(__uint_as_float(r[8 * e + 4]), __uint_as_float(r[8 * e + 5])),
                      pack2(__uint_as_float(r[8 * e + 6]), __uint_as_float(r[8 * e + 7])));
   }
+}
+
+// Columns [32 * half, 32 * half + 32) of row `row` of a 128-byte-row swizzled panel <- 32 fp32 values as bf16 (the layout a
+// TMA store with the 128-byte swizzle reads).
+__device__ __forceinline__ void stage_half_row(uint32_t panel, int row, int half, const uint32_t* r) {
+  const uint32_t base = panel + row * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+    sts128(base + (((half * 4 + c) ^ (row & 7)) << 4),
+           make_uint4(pack2(__uint_as_float(r[8 * c]), __uint_as_float(r[8 * c + 1])),
+                      pack2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3])),
+                      pack2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5])),
+                      pack2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]))));
 }
 
 // Lane j of the warp ends with sum over the 32 lanes of their v[j] (a transposing butterfly: 31 shuffles, no shared memory).
@@ -793,13 +807,81 @@ __device__ __forceinline__ void scale_half_row(uint32_t panel, int row, int half
   }
 }
 
+// One half (16 columns) of a 32 x 32 block of the two Gram tiles: thread = row l.  Reads G1 = cq bk^T and G2 = gy v^T from
+// TMEM, forms W = e^{c_t - c_s} (masked to s + strict <= t when MASKED), writes M = W o G1 and dGw = W o G2 o w_s as bf16
+// into the swizzled operand panels, and leaves E = G1 o dGw (s < t) in ev for the row / column sums.
+template <bool MASKED>
+__device__ __forceinline__ void tile_half(uint32_t trow, int q, int hf, int l, float my_cum2, int strict, const float* cum2,
+                                          const float* wv, uint32_t m_row, uint32_t g_row, float* ev, float& row_sum,
+                                          float& diag_g2) {
+  uint32_t g1[16], g2[16];
+  tmem_ld_32x16(trow + q * 32 + hf * 16, g1);
+  tmem_ld_32x16(trow + 128 + q * 32 + hf * 16, g2);
+  tmem_ld_wait();
+  const float4* c4 = reinterpret_cast<const float4*>(cum2 + q * 32 + hf * 16);   // every lane reads the same words
+  const float4* w4 = reinterpret_cast<const float4*>(wv + q * 32 + hf * 16);
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4) {
+    const float4 cv = c4[j4], wv4 = w4[j4];
+    const float cj[4] = {cv.x, cv.y, cv.z, cv.w}, wj[4] = {wv4.x, wv4.y, wv4.z, wv4.w};
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int j = 4 * j4 + u;
+      const int sidx = q * 32 + hf * 16 + j;
+      float wdec = ex2(my_cum2 - cj[u]);
+      if (MASKED) wdec = sidx + strict <= l ? wdec : 0.f;
+      const float m = __uint_as_float(g1[j]) * wdec;
+      const float dg = __uint_as_float(g2[j]) * wdec * wj[u];
+      float e = __uint_as_float(g1[j]) * dg;
+      if (MASKED) {
+        e = sidx < l ? e : 0.f;
+        if (sidx == l) diag_g2 = __uint_as_float(g2[j]);
+      }
+      row_sum += e;
+      ev[hf * 16 + j] = e;
+      g1[j] = __float_as_uint(m);
+      g2[j] = __float_as_uint(dg);
+    }
+  }
+#pragma unroll
+  for (int c8 = 0; c8 < 2; ++c8) {
+    const int chunk = (q & 1) * 4 + hf * 2 + c8;
+    const uint32_t* a = g1 + c8 * 8;
+    const uint32_t* d = g2 + c8 * 8;
+    sts128(m_row + ((chunk ^ (l & 7)) << 4),
+           make_uint4(pack2(__uint_as_float(a[0]), __uint_as_float(a[1])), pack2(__uint_as_float(a[2]), __uint_as_float(a[3])),
+                      pack2(__uint_as_float(a[4]), __uint_as_float(a[5])), pack2(__uint_as_float(a[6]), __uint_as_float(a[7]))));
+    sts128(g_row + ((chunk ^ (l & 7)) << 4),
+           make_uint4(pack2(__uint_as_float(d[0]), __uint_as_float(d[1])), pack2(__uint_as_float(d[2]), __uint_as_float(d[3])),
+                      pack2(__uint_as_float(d[4]), __uint_as_float(d[5])), pack2(__uint_as_float(d[6]), __uint_as_float(d[7]))));
+  }
+}
+
+// The same into another panel: dst row <- f * src row, columns [32 * half, 32 * half + 32).
+__device__ __forceinline__ void scale_half_row_to(uint32_t src_panel, uint32_t dst_panel, int row, int half, float f) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const uint32_t off = row * 128 + (((half * 4 + c) ^ (row & 7)) << 4);
+    uint4 v = lds128(src_panel + off);
+    float2 a = unpack2(v.x), b = unpack2(v.y), cc = unpack2(v.z), d = unpack2(v.w);
+    v.x = pack2(a.x * f, a.y * f);
+    v.y = pack2(b.x * f, b.y * f);
+    v.z = pack2(cc.x * f, cc.y * f);
+    v.w = pack2(d.x * f, d.y * f);
+    sts128(dst_panel + off, v);
+  }
+}
+
 template <int N, bool PH>
 __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                    const __grid_constant__ CUtensorMap map_gy,
                                                                    const __grid_constant__ CUtensorMap map_b,
                                                                    const __grid_constant__ CUtensorMap map_c,
                                                                    const __grid_constant__ CUtensorMap map_hin,
-                                                                   const __grid_constant__ CUtensorMap map_dho, const BwdParams p) {
+                                                                   const __grid_constant__ CUtensorMap map_dho,
+                                                                   const __grid_constant__ CUtensorMap map_dv,
+                                                                   const __grid_constant__ CUtensorMap map_dcq,
+                                                                   const __grid_constant__ CUtensorMap map_dbk, const BwdParams p) {
   extern __shared__ uint8_t raw_smem[];
   SmemBwd<N>& s = *reinterpret_cast<SmemBwd<N>*>((reinterpret_cast<uintptr_t>(raw_smem) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -811,38 +893,26 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
   constexpr uint32_t PANEL16 = PANEL >> 4, PV16 = (P * 128) >> 4;
   constexpr uint32_t TMEM_COLS = 512;
 
-  if (threadIdx.x == 0) {
-    s.abort_flag = 0;
-    mbar_init(&s.bar_full, 1);
-    mbar_init(&s.bar_mma, 1);
-    mbar_init(&s.bar_w, BWD_WARPS);
-    mbar_init(&s.bar_x, 1);
-    mbar_init(&s.bar_x2, BWD_WARPS / 2);
-    mbar_init(&s.bar_y, 1);
-    mbar_init(&s.bar_rows, BWD_WARPS);
-    fence_barrier_init();
-    prefetch_tmap(&map_x);
-    prefetch_tmap(&map_gy);
-    prefetch_tmap(&map_b);
-    prefetch_tmap(&map_c);
-    prefetch_tmap(&map_hin);
-    prefetch_tmap(&map_dho);
-  }
-  if (warp == BWD_WARPS) tmem_alloc(&s.tmem_base, TMEM_COLS);
-  fence_before_sync();
-  __syncthreads();
-  fence_after_sync();
-  const uint32_t tmem = s.tmem_base;
-  volatile int* abortp = &s.abort_flag;
-
   if (warp == BWD_WARPS) {
-    if (lane == 0) {
+    if (lane == 0) {   // the loads go out before the CTA-wide sync: their latency covers the TMEM allocation and the setup
+      s.abort_flag = 0;
+      mbar_init(&s.bar_full, 1);
+      mbar_init(&s.bar_mma, 1);
+      mbar_init(&s.bar_st, 1);
+      mbar_init(&s.bar_w, BWD_WARPS);
+      mbar_init(&s.bar_y, 1);
+      mbar_init(&s.bar_rows, BWD_WARPS);
+      fence_barrier_init();
       mbar_arrive_expect_tx(&s.bar_full, (2 * (N / 64) + 2) * PANEL + 2 * (N / 64) * P * 128);
       const int st_in = (int)((((int64_t)fb * p.chunks + c) * p.heads + h) * (PH ? N : P));
       const int st_out = (int)((((int64_t)b * p.chunks + c) * p.heads + h) * (PH ? N : P));
       for (int q = 0; q < N / 64; ++q) {
         tma_load_2d(s.ct[q], &map_c, &s.bar_full, g * N + q * 64, frow0);
         tma_load_2d(s.bt[q], &map_b, &s.bar_full, g * N + q * 64, frow0);
+      }
+      tma_load_2d(s.gyt, &map_gy, &s.bar_full, h * P, row0);
+      tma_load_2d(s.xt, &map_x, &s.bar_full, h * P, frow0);
+      for (int q = 0; q < N / 64; ++q) {
         if (!PH) {
           tma_load_2d(s.hin[q], &map_hin, &s.bar_full, q * 64, st_in);
           tma_load_2d(s.dho[q], &map_dho, &s.bar_full, q * 64, st_out);
@@ -852,11 +922,24 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
         tma_load_2d(s.hin[0], &map_hin, &s.bar_full, 0, st_in);
         tma_load_2d(s.dho[0], &map_dho, &s.bar_full, 0, st_out);
       }
-      tma_load_2d(s.gyt, &map_gy, &s.bar_full, h * P, row0);
-      tma_load_2d(s.xt, &map_x, &s.bar_full, h * P, frow0);
+      prefetch_tmap(&map_dv);
+      prefetch_tmap(&map_dcq);
+      prefetch_tmap(&map_dbk);
+    }
+    __syncwarp();
+    tmem_alloc(&s.tmem_base, TMEM_COLS);
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abortp = &s.abort_flag;
+
+  if (warp == BWD_WARPS) {
+    if (lane == 0) {
       const uint64_t kmajor0 = make_smem_desc(0, 16, 1024), mnmajor0 = make_smem_desc(0, PANEL, 1024),
                      mnstate0 = make_smem_desc(0, P * 128, 1024);
-      const uint32_t ct16 = smem_u32(s.ct[0]) >> 4, bt16 = smem_u32(s.bt[0]) >> 4, gy16 = smem_u32(s.gyt) >> 4,
+      const uint32_t ct16 = smem_u32(s.ct[0]) >> 4, bt16 = smem_u32(s.bt[0]) >> 4, gy16 = smem_u32(s.gyt) >> 4, gys16 = smem_u32(s.gys) >> 4,
                      xt16 = smem_u32(s.xt) >> 4, hin16 = smem_u32(s.hin[0]) >> 4, dho16 = smem_u32(s.dho[0]) >> 4,
                      mt16 = smem_u32(s.mt[0]) >> 4, gt16 = smem_u32(s.gt[0]) >> 4;
       bool ok = mbar_wait(&s.bar_full, 0, abortp, p.status, 71);
@@ -869,6 +952,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
                    idesc_g, kk);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) mma_bf16(tmem + 128, kmajor0 + gy16 + kk * 2, kmajor0 + xt16 + kk * 2, idesc_g, kk);
+        mma_commit(&s.bar_mma);   // the compute warps start on the two Gram tiles while the state products run
         const uint32_t idesc_s = make_idesc_bf16(128, 64, 0, PH ? 1 : 0);
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk)
@@ -878,7 +962,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
         for (int kk = 0; kk < KS; ++kk)
           mma_bf16(tmem + 320, kmajor0 + bt16 + (kk >> 2) * PANEL16 + (kk & 3) * 2,
                    PH ? mnmajor0 + dho16 + 128 * kk : kmajor0 + dho16 + (kk >> 2) * PV16 + (kk & 3) * 2, idesc_s, kk);
-        mma_commit(&s.bar_mma);
+        mma_commit(&s.bar_st);
         ok = mbar_wait(&s.bar_w, 0, abortp, p.status, 72);
       }
       if (ok) {
@@ -887,7 +971,6 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
         const uint32_t idesc_x = make_idesc_bf16(128, 64, 1, 1);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) mma_bf16(tmem + 384, mnmajor0 + mt16 + 128 * kk, mnmajor0 + gy16 + 128 * kk, idesc_x, kk);
-        mma_commit(&s.bar_x);
         // dcq[t, n] = sum_s dGw[t, s] bk[s, n]
         const uint32_t idesc_q = make_idesc_bf16(128, N, 0, 1);
 #pragma unroll
@@ -901,15 +984,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
           mma_bf16(tmem + 128, kmajor0 + xt16 + kk * 2, PH ? kmajor0 + dho16 + kk * 2 : mnstate0 + dho16 + 128 * kk, idesc_st, 1);
-        ok = mbar_wait(&s.bar_x2, 0, abortp, p.status, 73);
-        if (ok) {
-          fence_after_sync();
-          // dcq[t, n] += sum_p gy'[t, p] S_in[p, n]
+        // dcq[t, n] += sum_p gy'[t, p] S_in[p, n], gy' = e^{c_t} gy from the scaled copy
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_bf16(tmem, kmajor0 + gy16 + kk * 2, PH ? kmajor0 + hin16 + kk * 2 : mnstate0 + hin16 + 128 * kk, idesc_st, 1);
-          mma_commit(&s.bar_y);
-        }
+        for (int kk = 0; kk < 4; ++kk)
+          mma_bf16(tmem, kmajor0 + gys16 + kk * 2, PH ? kmajor0 + hin16 + kk * 2 : mnstate0 + hin16 + 128 * kk, idesc_st, 1);
+        mma_commit(&s.bar_y);
       }
     }
   } else {
@@ -920,6 +999,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
     const int64_t fbase = ((int64_t)fb * p.heads + h) * p.seq_len + c * L;
     const float my_cum2 = p.cum[fbase + l] * LOG2E;
     const float my_w = p.weight ? p.weight[fbase + l] : 1.f;
+    const float sk = (p.d_skip ? p.d_skip[h] : 0.f) + (p.skip_tok ? p.skip_tok[fbase + l] : 0.f);
     if (q == 0) {
       s.cum2[l] = my_cum2;
       s.wv[l] = my_w;
@@ -944,37 +1024,16 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
         s.colpart[rg][q * 32 + lane] = 0.f;
         s.rowpart[q][l] = 0.f;
       } else {
-        uint32_t g1[32], g2[32];
-        tmem_ld_32x32(trow + q * 32, g1);
-        tmem_ld_32x32(trow + 128 + q * 32, g2);
-        tmem_ld_wait();
+        // two halves of 16 columns: both Gram slices of a half, the decay, the two products, packed and stored; only the
+        // fp32 products E stay live for the column sums.  Blocks strictly below the diagonal take the form without masks.
         float ev[32];
         float row_sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int sidx = q * 32 + j;
-          const bool in_mask = sidx + p.strict <= l;
-          const float wdec = in_mask ? ex2(my_cum2 - s.cum2[sidx]) : 0.f;
-          const float m = __uint_as_float(g1[j]) * wdec;
-          const float dg = __uint_as_float(g2[j]) * wdec * s.wv[sidx];
-          const float e = sidx < l ? __uint_as_float(g1[j]) * dg : 0.f;
-          if (sidx == l) diag_g2 = __uint_as_float(g2[j]);
-          row_sum += e;
-          ev[j] = e;
-          g1[j] = __float_as_uint(m);
-          g2[j] = __float_as_uint(dg);
-        }
-#pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          const int chunk = (q & 1) * 4 + c8;
-          const uint32_t* a = g1 + c8 * 8;
-          const uint32_t* d = g2 + c8 * 8;
-          sts128(m_row + ((chunk ^ (l & 7)) << 4),
-                 make_uint4(pack2(__uint_as_float(a[0]), __uint_as_float(a[1])), pack2(__uint_as_float(a[2]), __uint_as_float(a[3])),
-                            pack2(__uint_as_float(a[4]), __uint_as_float(a[5])), pack2(__uint_as_float(a[6]), __uint_as_float(a[7]))));
-          sts128(g_row + ((chunk ^ (l & 7)) << 4),
-                 make_uint4(pack2(__uint_as_float(d[0]), __uint_as_float(d[1])), pack2(__uint_as_float(d[2]), __uint_as_float(d[3])),
-                            pack2(__uint_as_float(d[4]), __uint_as_float(d[5])), pack2(__uint_as_float(d[6]), __uint_as_float(d[7]))));
+        if (q < rg) {
+          tile_half<false>(trow, q, 0, l, my_cum2, p.strict, s.cum2, s.wv, m_row, g_row, ev, row_sum, diag_g2);
+          tile_half<false>(trow, q, 1, l, my_cum2, p.strict, s.cum2, s.wv, m_row, g_row, ev, row_sum, diag_g2);
+        } else {
+          tile_half<true>(trow, q, 0, l, my_cum2, p.strict, s.cum2, s.wv, m_row, g_row, ev, row_sum, diag_g2);
+          tile_half<true>(trow, q, 1, l, my_cum2, p.strict, s.cum2, s.wv, m_row, g_row, ev, row_sum, diag_g2);
         }
         s.rowpart[q][l] = row_sum;
         s.colpart[rg][q * 32 + lane] = warp_column_sums(ev, lane);
@@ -982,7 +1041,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
       }
       // state terms of the decay gradient (unscaled gy and v rows), split over the column slices:
       //   q = 0, 1: halves of e^{c_t} gy_t . (cq_t S_in^T);  q = 2, 3: halves of w_s e^{c_end - c_s} v_s . (bk_s D_out^T)
-      {
+      ok = mbar_wait(&s.bar_st, 0, abortp, p.status, 79);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        fence_after_sync();
         uint32_t r[32];
         tmem_ld_32x32(trow + (q < 2 ? 256 : 320) + (q & 1) * 32, r);
         tmem_ld_wait();
@@ -1001,8 +1063,12 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
         hd = warp_sum(hd);
         if (lane == 0) s.red[warp] = hd;
       }
-      // v rows scaled for the state term of dbk (slices 2 and 3 own the halves they just read)
-      if (q >= 2) scale_half_row(smem_u32(s.xt), l, q & 1, my_w * f_end);
+      // v rows scaled in place for the state term of dbk (slices 2 and 3 own the halves they just read); gy rows scaled by
+      // e^{c_t} into a copy for the state term of dcq (dX and the skip term need the unscaled rows)
+      if (ok) {
+        if (q >= 2) scale_half_row(smem_u32(s.xt), l, q & 1, my_w * f_end);
+        else scale_half_row_to(smem_u32(s.gyt), smem_u32(s.gys), l, q, ex2(my_cum2));
+      }
     }
     // the two halves of each state term meet in r2 / r3 (shared-memory adds); the barrier is taken by every compute warp,
     // whether or not its waits succeeded, so that a warp that gave up cannot strand the others at it
@@ -1030,35 +1096,34 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
       ok = mbar_wait(&s.bar_rows, 1, abortp, p.status, 76);
       ok = __all_sync(0xffffffffu, ok);
     }
-    uint4 gy_saved[4];
     if (ok) {
-      if (q == 3) {   // one slice finishes the decay gradient of its row
-        float tail2 = 0.f, head3 = 0.f;
-        for (int t = l; t < L; ++t) tail2 += s.r2[t];
-        for (int t = 0; t < l; ++t) head3 += s.r3[t];
+      if (q == 3) {   // one slice finishes the decay gradient of its row: suffix sums of r2, prefix sums of r3
+        float suf = s.r2[l], pre = s.r3[l];
+        float later2 = 0.f, earlier3 = 0.f;
+#pragma unroll
+        for (int gq = 0; gq < 4; ++gq) {   // totals of the other row quarters
+          const float t2 = warp_sum(s.r2[gq * 32 + lane]), t3 = warp_sum(s.r3[gq * 32 + lane]);
+          if (gq > rg) later2 += t2;
+          if (gq < rg) earlier3 += t3;
+        }
+        const float own3 = pre;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const float d2 = __shfl_down_sync(0xffffffffu, suf, o), u3 = __shfl_up_sync(0xffffffffu, pre, o);
+          if (lane + o < 32) suf += d2;
+          if (lane >= o) pre += u3;
+        }
         float through = 0.f;
 #pragma unroll
         for (int w = 0; w < BWD_WARPS; ++w) through += s.red[w];
-        p.da[base + l] = tail2 + head3 + ex2(cum_end2) * through;
-      }
-      // once dX has been taken, gy rows are scaled by e^{c_t} for the state term of dcq (slices 0, 1 own the halves and keep
-      // the unscaled values for the skip term of dX)
-      if (q < 2) {
-        ok = mbar_wait(&s.bar_x, 0, abortp, p.status, 77);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) {
-          const uint32_t gy_row = smem_u32(s.gyt) + l * 128;
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) gy_saved[ch] = lds128(gy_row + (((q * 4 + ch) ^ (l & 7)) << 4));
-          scale_half_row(smem_u32(s.gyt), l, q, ex2(my_cum2));
-          fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s.bar_x2);
-        }
+        p.da[base + l] = (suf + later2) + (pre - own3 + earlier3) + ex2(cum_end2) * through;
       }
       if (ok) ok = mbar_wait(&s.bar_y, 0, abortp, p.status, 78);
       ok = __all_sync(0xffffffffu, ok);
     }
+    // Epilogue.  bf16 results are staged in shared memory (the operand tiles are dead once the last product has completed) in the
+    // swizzled layout and leave with TMA stores: written row by row from the registers, a warp's 32 rows lie kilobytes apart
+    // and every store instruction splits into 32 transactions.  fp32 results (dv of the SSD form) keep the direct stores.
     if (ok) {
       fence_after_sync();
       const int64_t tok = (int64_t)row0 + l;
@@ -1067,29 +1132,43 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) bwd_chunk_kernel(const __grid_
         tmem_ld_32x32(trow + 384 + q * 32, x0);
         tmem_ld_32x32(trow + 320 + q * 32, t0);
         tmem_ld_wait();
-        const float sk = (p.d_skip ? p.d_skip[h] : 0.f) + (p.skip_tok ? p.skip_tok[fbase + l] : 0.f);
+        const uint32_t gy_row = smem_u32(s.gyt) + l * 128;   // the unscaled gy row, for the skip term
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          const uint4 gv = gy_saved[ch];
+          const uint4 gv = lds128(gy_row + (((q * 4 + ch) ^ (l & 7)) << 4));
           const float2 g0 = unpack2(gv.x), g1v = unpack2(gv.y), g2v = unpack2(gv.z), g3 = unpack2(gv.w);
           const float gyv[8] = {g0.x, g0.y, g1v.x, g1v.y, g2v.x, g2v.y, g3.x, g3.y};
 #pragma unroll
           for (int e = 0; e < 8; ++e)
             x0[ch * 8 + e] = __float_as_uint(__uint_as_float(x0[ch * 8 + e]) + f_end * __uint_as_float(t0[ch * 8 + e]) + sk * gyv[e]);
         }
-        const int64_t off = (tok * p.heads + h) * P + q * 32;
-        store_row(p.dv32 ? p.dv32 + off : nullptr, p.dv16 ? p.dv16 + off : nullptr, x0, 32);
+        if (p.dv16) stage_half_row(smem_u32(s.mt[0]), l, q, x0);
+        else store_row(p.dv32 + (tok * p.heads + h) * P + q * 32, nullptr, x0, 32);
       }
-      const int64_t off_n = (tok * p.heads + h) * N + q * 32;
       if (q < N / 32) {
+        const int64_t off_n = (tok * p.heads + h) * N + q * 32;
         uint32_t r[32];
         tmem_ld_32x32(trow + q * 32, r);
         tmem_ld_wait();
-        store_row(p.dcq32 ? p.dcq32 + off_n : nullptr, p.dcq16 ? p.dcq16 + off_n : nullptr, r, 32);
+        if (p.dcq16) stage_half_row(smem_u32(s.ct[q >> 1]), l, q & 1, r);
+        else store_row(p.dcq32 + off_n, nullptr, r, 32);
         tmem_ld_32x32(trow + 128 + q * 32, r);
         tmem_ld_wait();
-        store_row(p.dbk32 ? p.dbk32 + off_n : nullptr, p.dbk16 ? p.dbk16 + off_n : nullptr, r, 32);
+        if (p.dbk16) stage_half_row(smem_u32(s.bt[q >> 1]), l, q & 1, r);
+        else store_row(p.dbk32 + off_n, nullptr, r, 32);
       }
+      fence_proxy_async();
+    }
+    // taken by every compute warp, whether or not its waits succeeded
+    named_barrier_sync(1, BWD_WARPS * 32);
+    if (warp == 0 && lane == 0 && !s.abort_flag) {
+      if (p.dv16) tma_store_2d(&map_dv, s.mt[0], h * P, row0);
+      for (int qq = 0; qq < N / 64; ++qq) {
+        if (p.dcq16) tma_store_2d(&map_dcq, s.ct[qq], h * N + qq * 64, row0);
+        if (p.dbk16) tma_store_2d(&map_dbk, s.bt[qq], h * N + qq * 64, row0);
+      }
+      tma_store_commit();
+      tma_store_wait_read<0>();   // shared memory is released when the CTA exits
     }
   }
   __syncwarp();
@@ -1511,7 +1590,7 @@ static int run_bwd(const void* v, const void* gy, const void* bk, const void* cq
                    cudaStream_t st) {
   const int chunks = seq_len / L;
   const int64_t rows = (int64_t)batch * seq_len, frows = (int64_t)bmod * seq_len;
-  CUtensorMap mx, mg, mb, mc, mh, md;
+  CUtensorMap mx, mg, mb, mc, mh, md, mdv, mdq, mdk;
   int rc = make_map(&mx, v, frows, (int64_t)heads * P, L);
   if (rc) return rc;
   rc = make_map(&mg, gy, rows, (int64_t)heads * P, L);
@@ -1535,12 +1614,19 @@ static int run_bwd(const void* v, const void* gy, const void* bk, const void* cq
     rc = (int)cudaGetLastError();
     if (rc) return rc;
   }
+  // bf16 results leave through TMA stores; a map of an fp32 result is never used and points at gy
+  rc = make_map(&mdv, dv16 ? dv16 : gy, rows, (int64_t)heads * P, L);
+  if (rc) return rc;
+  rc = make_map(&mdq, dcq16 ? dcq16 : gy, rows, (int64_t)heads * (dcq16 ? N : P), L);
+  if (rc) return rc;
+  rc = make_map(&mdk, dbk16 ? dbk16 : gy, rows, (int64_t)heads * (dbk16 ? N : P), L);
+  if (rc) return rc;
   BwdParams p{seq_len, heads, groups, chunks, bmod, strict, weight, cum, skip_tok, d_skip, da, dskip, dv32, (__nv_bfloat16*)dv16,
               dcq32, dbk32, (__nv_bfloat16*)dcq16, (__nv_bfloat16*)dbk16, status};
   const size_t smem = sizeof(SmemBwd<N>) + 1024;
   rc = set_smem(bwd_chunk_kernel<N, PH>, smem);
   if (rc) return rc;
-  bwd_chunk_kernel<N, PH><<<dim3(chunks, heads, batch), BWD_THREADS, smem, st>>>(mx, mg, mb, mc, mh, md, p);
+  bwd_chunk_kernel<N, PH><<<dim3(chunks, heads, batch), BWD_THREADS, smem, st>>>(mx, mg, mb, mc, mh, md, mdv, mdq, mdk, p);
   return (int)cudaGetLastError();
 }
 

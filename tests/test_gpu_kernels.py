@@ -283,6 +283,34 @@ def test_interface_head_forward_and_parameter_vjp_kernels(hidden, act):
         assert torch.allclose(sink[id(p)], want, atol=1e-5, rtol=1e-4)
 
 
+@pytest.mark.parametrize("batch,dim,hidden,width", [(4, 1024, 1024, 128), (2, 256, 64, 16), (12, 256, 64, 16), (3, 256, 0, 16)])
+def test_interface_update_handoff_kernel_matches_the_module(batch, dim, hidden, width):
+    """The fused interface update (hidden units spread over the grid for batch <= 8, one CTA per row otherwise, single-layer
+    maps) without a peer: state, pre-norm state and delta against the PyTorch module."""
+    from lbi_b200.interfaces import VectorMLPInterface
+
+    torch.manual_seed(0)
+    iface = VectorMLPInterface(feature_dim=dim, num_regions=2, interface_width=width, interface_map_hidden_dim=hidden).cuda()
+    with torch.no_grad():
+        iface.update_scale.uniform_(0.2, 0.8)
+    state, pooled = torch.randn(batch, width, device="cuda"), torch.randn(batch, dim, device="cuda")
+    with torch.no_grad():
+        want = iface.update_from_pooled(state, pooled, 1)
+    enc, norm = iface.encoders[1], iface.norms[1]
+    first, second = enc.layers()
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for _ in range(2):   # the ticket counter must come back to zero
+        delta, pre, out = ops.ext().interface_update_handoff(
+            state, pooled, first.weight.detach(), None if first.bias is None else first.bias.detach(),
+            None if second is None else second.weight.detach(), None if (second is None or second.bias is None) else second.bias.detach(),
+            iface.update_scale.detach()[1:2], norm.weight.detach(), norm.bias.detach(), float(norm.eps),
+            0 if iface.activation == "silu" else 1, 0, 0, 0, counter)
+        assert int(counter) == 0
+        torch.testing.assert_close(out, want.state, atol=2e-4, rtol=2e-4)
+        torch.testing.assert_close(pre, want.diagnostics["pre_norm_state"], atol=2e-4, rtol=2e-4)
+        torch.testing.assert_close(delta, want.diagnostics["delta_state"], atol=2e-4, rtol=2e-4)
+
+
 def test_tail_shapes_under_the_bounds_checking_debug_build():
     """The debug extension (-DLBI_BOUNDS_CHECK: index checks that record a site code and skip the access, never trap) on
     shapes that reach the tail paths of the conv / scan-glue kernels: no violation may be recorded.  Runs in a child process
