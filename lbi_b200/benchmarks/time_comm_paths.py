@@ -128,7 +128,23 @@ def bench_scan(symm, coll, iters: int, k: int, r: int, bsz: int, chunk: int = 16
     bytes_in = 4.0 * (k - 1) * bsz * r * r * (world - 1) / world    # rows this rank receives from its peers
     t_fused = _timed(lambda: (fused(), symm.barrier()), iters)
     t_lib = _timed(library, iters)
+    # the parts of the fused path on their own: the barrier, the publish kernel (peer stores + flags; repeating it rewrites
+    # the same values), the recursion over the local, complete copy (its flags are already up)
+    ext = ops.ext()
+    m_buf, o_buf, m_ptrs, o_ptrs, _, _, seg_cache = symm._scan_bufs[("published", tuple(rows.shape))]
+    segs = next(iter(seg_cache.values()))
+    w = symm.world_size
+    slot = symm.scan_slot_base()
+    t_barrier = _timed(symm.barrier, iters)
+    t_publish = _timed(lambda: ext.peer_publish(rows, m_ptrs, segs[0], offs, o_ptrs, segs[1], symm.flag_ptrs, rank, w, slot, symm.seq,
+                                                symm.done_counter), iters)
+    own_m, own_o = m_ptrs[rank : rank + 1], o_ptrs[rank : rank + 1]
+    t_rec = _timed(lambda: ext.affine_scan_peer_sum(own_m, own_o, symm.flags, slot, symm.seq, bsz, 1, k, r, w), iters)
+    t_local = _timed(lambda: ops.affine_suffix_scan(full.permute(1, 0, 3, 2)[:, : k - 1].contiguous(), offs_full.transpose(0, 1)[:, : k - 1].contiguous(),
+                                                    seed=offs_full[k - 1].contiguous()), iters)
     return {f"scan_K{k}_R{r}_B{bsz}": {"fused_us": 1e3 * t_fused, "library_us": 1e3 * t_lib, "max_rel_diff": err,
+                                        "parts_us": {"barrier": 1e3 * t_barrier, "publish": 1e3 * t_publish, "recursion": 1e3 * t_rec,
+                                                     "local_scan_kernel_with_layout_copies": 1e3 * t_local},
                                         "nvlink_bytes_in_per_rank": bytes_in,
                                         "roofline_us": 1e6 * bytes_in / (PEER_COPY_GBS * 1e9)}}
 

@@ -186,6 +186,114 @@ __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __r
   }
 }
 
+// The backward for wide groups (one group of thousands of channels per row, the Mamba-2 form): a block per (row, group), every
+// thread keeps its one or two 16-byte vectors of x, z and dy in registers, so global memory is read once (the warp-per-group
+// kernel above walks a wide group twice with little in flight).  The thread -> channel map is fixed, so the weight gradient
+// accumulates in registers and leaves without atomics.  dw_partials [gridDim.x][dim].
+constexpr int WIDE_THREADS = 256;
+template <typename T>
+__global__ void __launch_bounds__(WIDE_THREADS) gated_rmsnorm_bwd_wide_kernel(
+    const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ z, const float* __restrict__ w,
+    const float* __restrict__ rstd_in, T* __restrict__ dx, T* __restrict__ dz, float* __restrict__ dw_partials, int64_t vrows,
+    int64_t fvrows, int dim, int gs, int gate_first) {
+  constexpr int V = Vec<T>::N;
+  constexpr int NV = 2;
+  __shared__ float red[WIDE_THREADS / 32];
+  const int ngroups = dim / gs, nvec = gs / V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool want_dw = dw_partials != nullptr;
+  float dw_acc[NV][V];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int e = 0; e < V; ++e) dw_acc[i][e] = 0.f;
+  int g_last = 0;
+  for (int64_t vr = blockIdx.x; vr < vrows; vr += gridDim.x) {
+    const int g = ngroups == 1 ? 0 : (int)(vr % ngroups);
+    const int64_t base = (ngroups == 1 ? vr : vr / ngroups) * dim + (int64_t)g * gs;
+    const int64_t fvr = vr < fvrows ? vr : vr % fvrows;
+    const int64_t fbase = (ngroups == 1 ? fvr : fvr / ngroups) * dim + (int64_t)g * gs;
+    const float rstd = rstd_in[fvr];
+    float xv[NV][V], zv[NV][V], gv[NV][V], wv[NV][V];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * WIDE_THREADS + threadIdx.x) * V;
+      if (c < gs) {
+        Vec<T>::load(x + fbase + c, xv[i]);
+        Vec<T>::load(dy + base + c, gv[i]);
+        if (z) Vec<T>::load(z + fbase + c, zv[i]);
+#pragma unroll
+        for (int e = 0; e < V; e += 4) {
+          const float4 t = *reinterpret_cast<const float4*>(w + g * gs + c + e);
+          wv[i][e] = t.x; wv[i][e + 1] = t.y; wv[i][e + 2] = t.z; wv[i][e + 3] = t.w;
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          float u = xv[i][e], dyn = gv[i][e];
+          if (z) {
+            const float gate = zv[i][e] * sigmoidf(zv[i][e]);
+            if (gate_first) u *= gate; else dyn *= gate;
+          }
+          dot = fmaf(dyn * wv[i][e], u * rstd, dot);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    __syncthreads();   // the previous row's readers of red are done
+    if (lane == 0) red[warp] = dot;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int q = 0; q < WIDE_THREADS / 32; ++q) total += red[q];
+    const float mean_gu = total / gs;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * WIDE_THREADS + threadIdx.x) * V;
+      if (c < gs) {
+        float ox[V], oz[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          float u = xv[i][e], dyn = gv[i][e], gate = 1.f, dgate = 0.f;
+          if (z) {
+            const float sg = sigmoidf(zv[i][e]);
+            gate = zv[i][e] * sg;
+            dgate = sg * (1.f + zv[i][e] * (1.f - sg));
+            if (gate_first) u *= gate; else dyn *= gate;
+          }
+          const float uhat = u * rstd;
+          dw_acc[i][e] += dyn * uhat;
+          const float du = rstd * (dyn * wv[i][e] - uhat * mean_gu);
+          if (z && gate_first) {
+            ox[e] = du * gate;
+            oz[e] = du * xv[i][e] * dgate;
+          } else {
+            ox[e] = du;
+            oz[e] = gv[i][e] * uhat * wv[i][e] * dgate;
+          }
+        }
+        Vec<T>::store(dx + base + c, ox);
+        if (z) Vec<T>::store(dz + base + c, oz);
+      }
+    }
+    g_last = g;
+  }
+  (void)g_last;
+  if (want_dw) {
+    // with one group per row (the only shape this kernel is launched for when a weight gradient is wanted) a thread's columns
+    // are the same for every row
+    float* out = dw_partials + (int64_t)blockIdx.x * dim;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * WIDE_THREADS + threadIdx.x) * V;
+      if (c < gs)
+#pragma unroll
+        for (int e = 0; e < V; ++e) out[c + e] = dw_acc[i][e];
+    }
+  }
+}
+
 // lanes per group: the largest power of two <= 32 that divides the number of 16-byte vectors of a group
 static bool plan(int gs, int vec, int* lpg, int* iters) {
   if (gs % vec != 0) return false;
@@ -196,6 +304,9 @@ static bool plan(int gs, int vec, int* lpg, int* iters) {
   *iters = nvec / l;
   return true;
 }
+
+// one group per row, wide enough to occupy a block and narrow enough for two vectors per thread
+static bool wide_shape(int dim, int gs, int vec) { return dim == gs && gs % vec == 0 && gs / vec > 128 && gs / vec <= 2 * WIDE_THREADS; }
 
 static int grid_for(int64_t vrows, int lpg) {
   const int64_t per_block = (int64_t)WARPS * (32 / lpg);
@@ -222,6 +333,11 @@ static int bwd(const void* dy, const void* x, const void* z, const float* w, con
   if (!plan(gs, Vec<T>::N, &lpg, &iters)) return (int)cudaErrorInvalidValue;
   if (frows <= 0 || rows % frows != 0) return (int)cudaErrorInvalidValue;
   const int64_t vrows = rows * (dim / gs), fvrows = frows * (dim / gs);
+  if (wide_shape(dim, gs, Vec<T>::N)) {
+    gated_rmsnorm_bwd_wide_kernel<T><<<grid_for(vrows, 32), WIDE_THREADS, 0, st>>>((const T*)dy, (const T*)x, (const T*)z, w, rstd, (T*)dx,
+                                                                                   (T*)dz, dw_partials, vrows, fvrows, dim, gs, gate_first);
+    return (int)cudaGetLastError();
+  }
   const size_t smem = (size_t)dim * sizeof(float);
   int rc = (int)cudaFuncSetAttribute(gated_rmsnorm_bwd_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (rc) return rc;
@@ -239,6 +355,7 @@ extern "C" int lbi_gated_rmsnorm_slots(int64_t rows, int dim, int group_size, in
   using namespace lbi::gnorm;
   int lpg, iters;
   if (rows <= 0 || dim <= 0 || group_size <= 0 || dim % group_size != 0 || !plan(group_size, is_bf16 ? 8 : 4, &lpg, &iters)) return 0;
+  if (wide_shape(dim, group_size, is_bf16 ? 8 : 4)) lpg = 32;   // the wide backward kernel: one row per block at a time
   return grid_for(rows * (dim / group_size), lpg);
 }
 

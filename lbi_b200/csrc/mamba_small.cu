@@ -402,33 +402,71 @@ __device__ __forceinline__ void dpre8(const D0* d0, const D12* d1, const D12* d2
   for (int e = 0; e < 8; ++e) out[e] = g[e] * dsilu_(pv[e]);
 }
 
-template <typename D0, typename D12>
+// grid (sequences * runs per sequence, ceil(cvecs / 128)), block 128.  A thread owns eight channels and walks the BRUN tokens of
+// its run from the last to the first with a window of the W newest dpre values in registers, so that every cotangent and
+// pre-activation element is read once and its SiLU slope is evaluated once (plus W - 1 tokens of halo per run).
+constexpr int BRUN = 32;
+// WMAX: compile-time bound of the filter width (4 for the usual d_conv = 4, else MAXW): it sizes the register windows.
+template <typename D0, typename D12, int WMAX>
 __global__ void __launch_bounds__(128) conv_silu_bwd_kernel(const D0* __restrict__ d0, const D12* __restrict__ d1,
                                                             const D12* __restrict__ d2, const __nv_bfloat16* __restrict__ pre,
                                                             const float* __restrict__ w, __nv_bfloat16* __restrict__ din, int64_t ld_in,
                                                             Seg seg, int64_t tokens, int64_t ftokens, int seq_len, int width) {
   const int channels = seg.c0 + seg.c1 + seg.c2, cvecs = channels / 8;
-  const int64_t tok = blockIdx.x;
-  const int64_t ftok = tok % ftokens;         // once per block
-  const int t = (int)(ftok % seq_len);
-  const int k_lo = max(0, (width - 1) - (seq_len - 1 - t));   // taps that reach past the last token of the sequence are skipped
-  for (int cv = threadIdx.x; cv < cvecs; cv += blockDim.x) {
-    const int c = cv * 8;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int k = k_lo; k < width; ++k) {
-      const int shift = (width - 1) - k;
-      if (!LBI_IN_RANGE(tok + shift, tokens, 92)) continue;
-      float dp[8];
-      dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tok + shift, ftok + shift, c, dp);
-      {
-        const float4 w0 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c);
-        const float4 w1 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c + 4);
-        acc[0] = fmaf(w0.x, dp[0], acc[0]); acc[1] = fmaf(w0.y, dp[1], acc[1]); acc[2] = fmaf(w0.z, dp[2], acc[2]);
-        acc[3] = fmaf(w0.w, dp[3], acc[3]); acc[4] = fmaf(w1.x, dp[4], acc[4]); acc[5] = fmaf(w1.y, dp[5], acc[5]);
-        acc[6] = fmaf(w1.z, dp[6], acc[6]); acc[7] = fmaf(w1.w, dp[7], acc[7]);
+  const int cv = blockIdx.y * 128 + threadIdx.x;
+  if (cv >= cvecs) return;
+  const int c = cv * 8;
+  const int runs_per_seq = (seq_len + BRUN - 1) / BRUN;
+  const int64_t sq = blockIdx.x / runs_per_seq;
+  const int run = blockIdx.x % runs_per_seq;
+  const int t0 = run * BRUN, t1 = min(seq_len, t0 + BRUN);
+  const int64_t tok_base = sq * seq_len;                                  // first token of the sequence, cotangent rows
+  const int64_t ftok_base = (sq % (ftokens / seq_len)) * seq_len;         // the same in the forward tensors
+  // weights of the eight channels by shift: wk[s][e] = w[W - 1 - s] multiplies dpre[t + s]
+  float wk[WMAX][8];
+#pragma unroll
+  for (int sft = 0; sft < WMAX; ++sft) {
+    if (sft < width) {
+      const int k = width - 1 - sft;
+      const float4 w0 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c);
+      const float4 w1 = *reinterpret_cast<const float4*>(w + (int64_t)k * channels + c + 4);
+      wk[sft][0] = w0.x; wk[sft][1] = w0.y; wk[sft][2] = w0.z; wk[sft][3] = w0.w;
+      wk[sft][4] = w1.x; wk[sft][5] = w1.y; wk[sft][6] = w1.z; wk[sft][7] = w1.w;
+    }
+  }
+  // win[s] = dpre[t + s], s = 0 .. W - 1; starts with the halo after the run (zeros past the end of the sequence)
+  float win[WMAX][8];
+#pragma unroll
+  for (int sft = 1; sft < WMAX; ++sft) {
+    if (sft < width) {
+      const int t = t1 - 1 + sft;
+      if (t < seq_len && LBI_IN_RANGE(tok_base + t, tokens, 92)) {
+        dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tok_base + t, ftok_base + t, c, win[sft]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[sft][e] = 0.f;
       }
     }
-    *reinterpret_cast<bf16x8*>(din + tok * ld_in + c) = pack8(acc);
+  }
+#pragma unroll 4
+  for (int t = t1 - 1; t >= t0; --t) {
+    dpre8<D0, D12>(d0, d1, d2, pre, seg, channels, tok_base + t, ftok_base + t, c, win[0]);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int sft = 0; sft < WMAX; ++sft) {
+      if (sft < width) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(wk[sft][e], win[sft][e], acc[e]);
+      }
+    }
+    *reinterpret_cast<bf16x8*>(din + (tok_base + t) * ld_in + c) = pack8(acc);
+#pragma unroll
+    for (int sft = WMAX - 1; sft >= 1; --sft) {
+      if (sft < width) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[sft][e] = win[sft - 1][e];
+      }
+    }
   }
 }
 
@@ -503,12 +541,19 @@ extern "C" int lbi_conv_silu_bwd(const void* d0, int d0_fp32, const void* d1, co
   if (c0 % 8 || c1 % 8 || c2 % 8 || c0 + c1 + c2 <= 0 || width <= 0 || width > MAXW || seq_len <= 0 || ftokens <= 0 ||
       tokens % ftokens || ftokens % seq_len || ld_in % 8 || ld_in < c0 + c1 + c2)
     return (int)cudaErrorInvalidValue;
-  if (tokens > 2147483647ll) return (int)cudaErrorInvalidValue;
-  const unsigned blocks = (unsigned)tokens;
+  const int64_t runs = (tokens / seq_len) * ((seq_len + BRUN - 1) / BRUN);
+  if (runs > 2147483647ll) return (int)cudaErrorInvalidValue;
+  const dim3 blocks((unsigned)runs, (unsigned)(((c0 + c1 + c2) / 8 + 127) / 128));
   const Seg seg{c0, c1, c2};
-#define LBI_CONV_BWD(A, B)                                                                                                   \
-  conv_silu_bwd_kernel<A, B><<<blocks, 128, 0, st>>>((const A*)d0, (const B*)d1, (const B*)d2, (const __nv_bfloat16*)pre, w, \
-                                                     (__nv_bfloat16*)din, ld_in, seg, tokens, ftokens, seq_len, width)
+#define LBI_CONV_BWD(A, B)                                                                                                          \
+  do {                                                                                                                              \
+    if (width <= 4)                                                                                                                 \
+      conv_silu_bwd_kernel<A, B, 4><<<blocks, 128, 0, st>>>((const A*)d0, (const B*)d1, (const B*)d2, (const __nv_bfloat16*)pre, w, \
+                                                            (__nv_bfloat16*)din, ld_in, seg, tokens, ftokens, seq_len, width);    \
+    else                                                                                                                            \
+      conv_silu_bwd_kernel<A, B, MAXW><<<blocks, 128, 0, st>>>((const A*)d0, (const B*)d1, (const B*)d2, (const __nv_bfloat16*)pre, \
+                                                               w, (__nv_bfloat16*)din, ld_in, seg, tokens, ftokens, seq_len, width); \
+  } while (0)
   if (d0_fp32 && d12_fp32) LBI_CONV_BWD(float, float);
   else if (d0_fp32) LBI_CONV_BWD(float, __nv_bfloat16);
   else if (d12_fp32) LBI_CONV_BWD(__nv_bfloat16, float);

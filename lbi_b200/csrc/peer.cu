@@ -345,20 +345,29 @@ __global__ void __launch_bounds__(1024) affine_scan_peer_sum_kernel(const float*
         for (int w = 0; w < world; ++w) acc += __ldcg(offs_ptrs[w] + off_base + a);
       if (k < k_total - 1) {
         // sixteen loads in flight per thread: the recursion is bound by load latency, not by bandwidth.  The data was
-        // complete before the flags were seen (acquire), so the loads need not be volatile; they bypass L1 only.
-        for (int j0 = grp; j0 < r; j0 += groups * 16) {
-          float m[16];
+        // complete before the flags were seen (acquire), so the loads need not be volatile; they bypass L1 only.  The
+        // single-buffer form (published rows) is spelled out: with the loop over buffers between them, the add that
+        // consumes a load sits before the next load in program order and an in-order warp then waits for each load in turn.
+        if (world == 1) {
+          const float* rows = rows_ptrs[0] + row_base + a;
+          for (int j0 = grp; j0 < r; j0 += groups * 16) {
+            float m[16];
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int j = j0 + u * groups;
-            m[u] = 0.f;
-            if (j < r)
-              for (int w = 0; w < world; ++w) m[u] += __ldcg(rows_ptrs[w] + row_base + (size_t)j * r + a);
+            for (int u = 0; u < 16; ++u) {
+              const int j = j0 + u * groups;
+              m[u] = j < r ? __ldcg(rows + (size_t)j * r) : 0.f;
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+              const int j = j0 + u * groups;
+              if (j < r) acc = fmaf(m[u], cur[j], acc);
+            }
           }
-#pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const int j = j0 + u * groups;
-            if (j < r) acc = fmaf(m[u], cur[j], acc);
+        } else {
+          for (int j = grp; j < r; j += groups) {
+            float m = 0.f;
+            for (int w = 0; w < world; ++w) m += __ldcg(rows_ptrs[w] + row_base + (size_t)j * r + a);
+            acc = fmaf(m, cur[j], acc);
           }
         }
       }

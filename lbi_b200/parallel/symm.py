@@ -115,6 +115,10 @@ class SymmComm(CollectiveComm):
         dist.barrier(group=self.group)
         self.barrier()
 
+    def scan_slot_base(self) -> int:
+        """First flag word of the scan's per-rank flags (for callers that drive the publish / recursion kernels directly)."""
+        return _SLOT_SCAN * self.world_size
+
     def barrier(self) -> None:
         self.seq += 1
         ops.ext().peer_barrier(self.flag_ptrs, self.rank, self.world_size, _SLOT_BARRIER * self.world_size, self.seq)

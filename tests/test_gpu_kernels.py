@@ -226,6 +226,32 @@ def test_gated_rmsnorm_kernels_match_the_pytorch_form(dtype, gated, norm_before_
         assert err <= (1e-2 if dtype == torch.bfloat16 else 1e-5), f"{name}: {err:.2e}"
 
 
+@pytest.mark.parametrize("dim,gate_first", [(3072, True), (3072, False), (1536, True)])
+def test_wide_group_gated_rmsnorm_backward_matches_the_pytorch_form(dim, gate_first):
+    """One group of thousands of channels per row (the Mamba-2 shape) takes the block-per-row backward kernel: stacked
+    directions sharing the forward tensors, with and without the weight gradient, against the fp32 PyTorch statement."""
+    from lbi_b200.ops import mamba as mops
+
+    torch.manual_seed(2)
+    n, reps = 37, 3
+    x = torch.randn(n, dim, device=DEV).bfloat16()
+    z = torch.randn(n, dim, device=DEV).bfloat16()
+    w = torch.rand(dim, device=DEV) + 0.5
+    y, rstd = mops.gated_rmsnorm_fwd(x, z, w, 1e-5, dim, gate_first)
+    for r, want_dw in ((reps, False), (1, True)):
+        dy = torch.randn(r * n, dim, device=DEV).bfloat16()
+        before = ops.dispatch.KERNEL_LAUNCHES["count"]
+        got = mops.gated_rmsnorm_bwd(dy, x, z, w, rstd, dim, gate_first, want_dweight=want_dw)
+        assert ops.dispatch.KERNEL_LAUNCHES["count"] == before + 1
+        want = mops.gated_rmsnorm_bwd(dy.float().cpu(), x.float().cpu(), z.float().cpu(), w.cpu(), rstd.cpu(), dim, gate_first,
+                                      want_dweight=want_dw)
+        for name, a_, w_ in zip(("dx", "dz", "dw"), got, want):
+            if w_ is None:
+                continue
+            err = (a_.float().cpu() - w_.float()).norm().item() / w_.float().norm().item()
+            assert err <= 1e-2, f"{name}: {err:.2e}"
+
+
 def test_mamba2_conv_silu_kernels_match_pytorch():
     """Depthwise causal conv + SiLU over the x | B | C slice: forward (split outputs), input cotangent for stacked directions
     written into a column range of a wider buffer, and the weight / bias gradient."""
