@@ -4,7 +4,8 @@
     python bench.py --gpus N --steps K --warmup W            # this framework
     python bench.py --impl reference --gpus N ...            # the unmodified reference from baseline/_ref
 
-Configs "cfg3" / "cfg5" (--config): LBI Mamba-3 130M / LBI Mamba-2 780M through the scan engine on one GPU.
+Configs "cfg3" / "cfg5" (--config): LBI Mamba-3 130M / LBI Mamba-2 780M, on the same region-parallel engine at 1 - 8 GPUs
+(--engine scan: the autograd scan engine, one GPU).  --variant dense: the dense model of the same size, either --impl.
 Config "cfg4" (default): LBI Transformer, 24 layers, d_model 1024, 16 heads x 64, RoPE, RMSNorm, SwiGLU 2816,
 vocab 32768, sequence 16384 split into 8 regions of 2048 tokens, interface width 128, batch 4, bf16, AdamW,
 uniform-random tokens, random-init weights.  Regions are placed on the GPUs in contiguous blocks (8 regions on N
@@ -32,8 +33,7 @@ CONFIGS = {
                        vocab=32768, seq_len=16384, regions=8, batch=4, message_dim=128, message_hidden=1024, axis="depth"),
     "small": dict(model="lbi-transformer-small", layers=4, dim=512, n_heads=8, d_intermediate=1408, vocab=8192,
                   seq_len=4096, regions=8, batch=2, message_dim=32, message_hidden=512),
-    # Mamba backbones run through the autograd-based scan engine (one GPU): the region-parallel fast engine is the
-    # Transformer's.  cfg3 / cfg5 are the LBI Mamba-3 (~130M) and LBI Mamba-2 (~780M) shapes.
+    # cfg3 / cfg5 are the LBI Mamba-3 (~130M) and LBI Mamba-2 (~780M) shapes (region-parallel engine like cfg4).
     "cfg3": dict(model="lbi-mamba3-130m", backbone="mamba3", layers=24, dim=768, d_state=128, headdim=64, expand=2, chunk=128,
                  vocab=32768, seq_len=8192, regions=8, batch=8, message_dim=64, message_hidden=768),
     "cfg5": dict(model="lbi-mamba2-780m", backbone="mamba2", layers=48, dim=1536, d_state=128, headdim=64, expand=2, chunk=256,
@@ -623,7 +623,11 @@ def run_reference(args) -> dict:
             torch.cuda.empty_cache()
             continue
         except Exception as exc:  # noqa: BLE001
-            return {"impl": "reference", "unavailable": f"reference step failed: {exc!r}"[:300]}
+            # compiler errors quote the whole kernel first and say what went wrong last: keep both ends, on one line
+            text = " ".join(f"{type(exc).__name__}: {exc}".split())
+            if len(text) > 520:
+                text = text[:200] + " ... " + text[-300:]
+            return {"impl": "reference", "unavailable": f"reference step failed: {text}"}
     else:
         return {"impl": "reference", "unavailable": f"reference ran out of GPU memory at the named config for every recompute chunk in {chunks}: {last_oom}"}
     ms = start.elapsed_time(stop) / max(1, n_steps)
