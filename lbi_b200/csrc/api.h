@@ -104,11 +104,14 @@ int lbi_gate_silu_fwd(const void* y, const void* z, void* out, int64_t numel, cu
 int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, void* dy, void* dz, int64_t numel, int reps,
                       cudaStream_t stream);
 // Mamba-3 per-token, per-head scalars.  dd_dt, dd_a, trap [B * L, H], angles [B * L, S], dt_bias [H] (fp32) ->
-// dt, a, sig, adt, gamma, scale, sp_dt, sp_a, live [B, L, H]; tanh_a [B, L, S]; theta [B, L, H, S] in [0, 2 pi).  S <= 64.
+// dt, a, sig, adt, gamma, scale, sp_dt, sp_a, live [B, L, H]; tanh_a [B, L, S]; theta [B, L, H, S] in [0, 2 pi).  S <= 64,
+// H <= 32.  Scratch: seg_inc [B, lbi_siso_small_fwd_segments(L), H, 64] fp32 (phase increments summed per segment of the
+// sequence, so that the running phase can start in every segment at once).  Two kernels on `stream`.
+int lbi_siso_small_fwd_segments(int seq_len);
 int lbi_siso_small_fwd(const float* dd_dt, const float* dd_a, const float* trap, const float* angles, const float* dt_bias,
-                       float a_floor, float* dt, float* a, float* sig, float* adt, float* gamma, float* scale, float* tanh_a,
-                       float* theta, float* sp_dt, float* sp_a, float* live, int batch, int seq_len, int heads, int n_angles,
-                       cudaStream_t stream);
+                       float a_floor, float* seg_inc, float* dt, float* a, float* sig, float* adt, float* gamma, float* scale,
+                       float* tanh_a, float* theta, float* sp_dt, float* sp_a, float* live, int batch, int seq_len, int heads,
+                       int n_angles, cudaStream_t stream);
 // Cotangents dadt, dgamma, dscale [reps * B, L, H] and dtheta [reps * B, L, H, S] -> d_dd_dt, d_dd_a, d_trap [reps * B * L, H]
 // and d_angles [reps * B * L, S] (fp32 or bf16); the forward tensors [B, ...] are shared by the reps directions.
 // H <= 32, S <= 32.  Scratch: seg_sum [reps * B, lbi_siso_small_segments(L), H, 32] fp32 (dtheta summed per segment of the

@@ -458,8 +458,10 @@ std::vector<Tensor> siso_small_fwd(const Tensor& dd_dt, const Tensor& dd_a, cons
   out.push_back(torch::empty({batch, seq_len, na}, f32));
   out.push_back(torch::empty({batch, seq_len, heads, na}, f32));
   for (int i = 0; i < 3; ++i) out.push_back(torch::empty({batch, seq_len, heads}, f32));
+  TORCH_CHECK(heads <= 32, "siso_small_fwd: at most 32 heads");
+  Tensor seg_inc = torch::empty({batch, (int64_t)lbi_siso_small_fwd_segments((int)seq_len), heads, 64}, f32);
   check(lbi_siso_small_fwd(dd_dt.data_ptr<float>(), dd_a.data_ptr<float>(), trap.data_ptr<float>(), angles.data_ptr<float>(),
-                           dt_bias.data_ptr<float>(), (float)a_floor, out[0].data_ptr<float>(), out[1].data_ptr<float>(),
+                           dt_bias.data_ptr<float>(), (float)a_floor, seg_inc.data_ptr<float>(), out[0].data_ptr<float>(), out[1].data_ptr<float>(),
                            out[2].data_ptr<float>(), out[3].data_ptr<float>(), out[4].data_ptr<float>(), out[5].data_ptr<float>(),
                            out[6].data_ptr<float>(), out[7].data_ptr<float>(), out[8].data_ptr<float>(), out[9].data_ptr<float>(),
                            out[10].data_ptr<float>(), (int)batch, (int)seq_len, (int)heads, (int)na, cur_stream()),

@@ -186,111 +186,122 @@ __global__ void __launch_bounds__(THREADS) gated_rmsnorm_bwd_kernel(const T* __r
   }
 }
 
-// The backward for wide groups (one group of thousands of channels per row, the Mamba-2 form): a block per (row, group), every
-// thread keeps its one or two 16-byte vectors of x, z and dy in registers, so global memory is read once (the warp-per-group
-// kernel above walks a wide group twice with little in flight).  The thread -> channel map is fixed, so the weight gradient
-// accumulates in registers and leaves without atomics.  dw_partials [gridDim.x][dim].
+// The backward for wide groups (one group of thousands of channels per row, the Mamba-2 form): a block per row.  The rows of
+// dy, x and z are staged in shared memory with cp.async, two stages deep, so the next row's loads are in flight while the
+// current row is reduced and written (the warp-per-group kernel above walks a wide group twice with little in flight, and
+// a block that keeps its row in registers leaves two rows in flight per SM).  The thread -> channel map is fixed, so the
+// weight gradient accumulates in a shared array without atomics.  dw_partials [gridDim.x][dim].
+// Dynamic smem: 2 stages x 3 rows x gs elements, then dim floats.
 constexpr int WIDE_THREADS = 256;
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 template <typename T>
 __global__ void __launch_bounds__(WIDE_THREADS) gated_rmsnorm_bwd_wide_kernel(
     const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ z, const float* __restrict__ w,
     const float* __restrict__ rstd_in, T* __restrict__ dx, T* __restrict__ dz, float* __restrict__ dw_partials, int64_t vrows,
     int64_t fvrows, int dim, int gs, int gate_first) {
   constexpr int V = Vec<T>::N;
-  constexpr int NV = 2;
+  extern __shared__ __align__(16) uint8_t wide_smem[];
   __shared__ float red[WIDE_THREADS / 32];
-  const int ngroups = dim / gs, nvec = gs / V;
+  T* stage = reinterpret_cast<T*>(wide_smem);                                        // [2][3][gs]
+  float* dw_acc = reinterpret_cast<float*>(wide_smem + (size_t)6 * gs * sizeof(T));   // [gs]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const bool want_dw = dw_partials != nullptr;
-  float dw_acc[NV][V];
-#pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int e = 0; e < V; ++e) dw_acc[i][e] = 0.f;
-  int g_last = 0;
-  for (int64_t vr = blockIdx.x; vr < vrows; vr += gridDim.x) {
-    const int g = ngroups == 1 ? 0 : (int)(vr % ngroups);
-    const int64_t base = (ngroups == 1 ? vr : vr / ngroups) * dim + (int64_t)g * gs;
+  if (want_dw)
+    for (int i = threadIdx.x; i < gs; i += WIDE_THREADS) dw_acc[i] = 0.f;
+  auto prefetch = [&](int64_t vr, int st) {
     const int64_t fvr = vr < fvrows ? vr : vr % fvrows;
-    const int64_t fbase = (ngroups == 1 ? fvr : fvr / ngroups) * dim + (int64_t)g * gs;
+    T* sx = stage + (size_t)st * 3 * gs;
+    for (int c = threadIdx.x * V; c < gs; c += WIDE_THREADS * V) {
+      cp_async16(sx + c, x + fvr * gs + c);
+      cp_async16(sx + gs + c, dy + vr * gs + c);
+      if (z) cp_async16(sx + 2 * gs + c, z + fvr * gs + c);
+    }
+    cp_async_commit();
+  };
+  int st = 0;
+  if ((int64_t)blockIdx.x < vrows) prefetch(blockIdx.x, 0);
+  for (int64_t vr = blockIdx.x; vr < vrows; vr += gridDim.x, st ^= 1) {
+    const int64_t nxt = vr + gridDim.x;
+    if (nxt < vrows) {
+      prefetch(nxt, st ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int64_t fvr = vr < fvrows ? vr : vr % fvrows;
     const float rstd = rstd_in[fvr];
-    float xv[NV][V], zv[NV][V], gv[NV][V], wv[NV][V];
+    const T* sx = stage + (size_t)st * 3 * gs;
     float dot = 0.f;
+    for (int c = threadIdx.x * V; c < gs; c += WIDE_THREADS * V) {
+      float xv[V], zv[V], gv[V], wv[V];
+      Vec<T>::load(sx + c, xv);
+      Vec<T>::load(sx + gs + c, gv);
+      if (z) Vec<T>::load(sx + 2 * gs + c, zv);
+      Vec<float>::load(w + c, wv);
+      if (V == 8) Vec<float>::load(w + c + 4, wv + 4);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = (i * WIDE_THREADS + threadIdx.x) * V;
-      if (c < gs) {
-        Vec<T>::load(x + fbase + c, xv[i]);
-        Vec<T>::load(dy + base + c, gv[i]);
-        if (z) Vec<T>::load(z + fbase + c, zv[i]);
-#pragma unroll
-        for (int e = 0; e < V; e += 4) {
-          const float4 t = *reinterpret_cast<const float4*>(w + g * gs + c + e);
-          wv[i][e] = t.x; wv[i][e + 1] = t.y; wv[i][e + 2] = t.z; wv[i][e + 3] = t.w;
+      for (int e = 0; e < V; ++e) {
+        float u = xv[e], dyn = gv[e];
+        if (z) {
+          const float gate = zv[e] * sigmoidf(zv[e]);
+          if (gate_first) u *= gate; else dyn *= gate;
         }
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          float u = xv[i][e], dyn = gv[i][e];
-          if (z) {
-            const float gate = zv[i][e] * sigmoidf(zv[i][e]);
-            if (gate_first) u *= gate; else dyn *= gate;
-          }
-          dot = fmaf(dyn * wv[i][e], u * rstd, dot);
-        }
+        dot = fmaf(dyn * wv[e], u * rstd, dot);
       }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    __syncthreads();   // the previous row's readers of red are done
     if (lane == 0) red[warp] = dot;
     __syncthreads();
     float total = 0.f;
 #pragma unroll
     for (int q = 0; q < WIDE_THREADS / 32; ++q) total += red[q];
     const float mean_gu = total / gs;
+    for (int c = threadIdx.x * V; c < gs; c += WIDE_THREADS * V) {
+      float xv[V], zv[V], gv[V], ox[V], oz[V], wvec[V];
+      Vec<T>::load(sx + c, xv);
+      Vec<T>::load(sx + gs + c, gv);
+      if (z) Vec<T>::load(sx + 2 * gs + c, zv);
+      Vec<float>::load(w + c, wvec);
+      if (V == 8) Vec<float>::load(w + c + 4, wvec + 4);
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = (i * WIDE_THREADS + threadIdx.x) * V;
-      if (c < gs) {
-        float ox[V], oz[V];
-#pragma unroll
-        for (int e = 0; e < V; ++e) {
-          float u = xv[i][e], dyn = gv[i][e], gate = 1.f, dgate = 0.f;
-          if (z) {
-            const float sg = sigmoidf(zv[i][e]);
-            gate = zv[i][e] * sg;
-            dgate = sg * (1.f + zv[i][e] * (1.f - sg));
-            if (gate_first) u *= gate; else dyn *= gate;
-          }
-          const float uhat = u * rstd;
-          dw_acc[i][e] += dyn * uhat;
-          const float du = rstd * (dyn * wv[i][e] - uhat * mean_gu);
-          if (z && gate_first) {
-            ox[e] = du * gate;
-            oz[e] = du * xv[i][e] * dgate;
-          } else {
-            ox[e] = du;
-            oz[e] = gv[i][e] * uhat * wv[i][e] * dgate;
-          }
+      for (int e = 0; e < V; ++e) {
+        const float wv = wvec[e];
+        float u = xv[e], dyn = gv[e], gate = 1.f, dgate = 0.f;
+        if (z) {
+          const float sg = sigmoidf(zv[e]);
+          gate = zv[e] * sg;
+          dgate = sg * (1.f + zv[e] * (1.f - sg));
+          if (gate_first) u *= gate; else dyn *= gate;
         }
-        Vec<T>::store(dx + base + c, ox);
-        if (z) Vec<T>::store(dz + base + c, oz);
+        const float uhat = u * rstd;
+        if (want_dw) dw_acc[c + e] += dyn * uhat;   // this thread owns column c + e in every row
+        const float du = rstd * (dyn * wv - uhat * mean_gu);
+        if (z && gate_first) {
+          ox[e] = du * gate;
+          oz[e] = du * xv[e] * dgate;
+        } else {
+          ox[e] = du;
+          oz[e] = gv[e] * uhat * wv * dgate;
+        }
       }
+      Vec<T>::store(dx + vr * gs + c, ox);
+      if (z) Vec<T>::store(dz + vr * gs + c, oz);
     }
-    g_last = g;
+    __syncthreads();   // the stage is refilled by the prefetch of the next iteration; red is rewritten
   }
-  (void)g_last;
   if (want_dw) {
-    // with one group per row (the only shape this kernel is launched for when a weight gradient is wanted) a thread's columns
-    // are the same for every row
     float* out = dw_partials + (int64_t)blockIdx.x * dim;
+    for (int c = threadIdx.x * V; c < gs; c += WIDE_THREADS * V)
 #pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = (i * WIDE_THREADS + threadIdx.x) * V;
-      if (c < gs)
-#pragma unroll
-        for (int e = 0; e < V; ++e) out[c + e] = dw_acc[i][e];
-    }
+      for (int e = 0; e < V; ++e) out[c + e] = dw_acc[c + e];
   }
 }
 
@@ -305,8 +316,10 @@ static bool plan(int gs, int vec, int* lpg, int* iters) {
   return true;
 }
 
-// one group per row, wide enough to occupy a block and narrow enough for two vectors per thread
-static bool wide_shape(int dim, int gs, int vec) { return dim == gs && gs % vec == 0 && gs / vec > 128 && gs / vec <= 2 * WIDE_THREADS; }
+// one group per row, wide enough to occupy a block, two staged rows of dy, x, z and the weight-gradient row within 200 KB
+static bool wide_shape(int dim, int gs, int vec) {
+  return dim == gs && gs % vec == 0 && gs / vec > 128 && (size_t)gs * (6 * (vec == 8 ? 2 : 4) + 4) <= 200 * 1024;
+}
 
 static int grid_for(int64_t vrows, int lpg) {
   const int64_t per_block = (int64_t)WARPS * (32 / lpg);
@@ -334,7 +347,11 @@ static int bwd(const void* dy, const void* x, const void* z, const float* w, con
   if (frows <= 0 || rows % frows != 0) return (int)cudaErrorInvalidValue;
   const int64_t vrows = rows * (dim / gs), fvrows = frows * (dim / gs);
   if (wide_shape(dim, gs, Vec<T>::N)) {
-    gated_rmsnorm_bwd_wide_kernel<T><<<grid_for(vrows, 32), WIDE_THREADS, 0, st>>>((const T*)dy, (const T*)x, (const T*)z, w, rstd, (T*)dx,
+    const size_t wide = (size_t)6 * gs * sizeof(T) + (size_t)gs * sizeof(float);
+    static PerDeviceOnce configured_wide;
+    cudaError_t e = configured_wide.max_dynamic_smem(gated_rmsnorm_bwd_wide_kernel<T>, 200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    gated_rmsnorm_bwd_wide_kernel<T><<<grid_for(vrows, 32), WIDE_THREADS, wide, st>>>((const T*)dy, (const T*)x, (const T*)z, w, rstd, (T*)dx,
                                                                                    (T*)dz, dw_partials, vrows, fvrows, dim, gs, gate_first);
     return (int)cudaGetLastError();
   }

@@ -60,26 +60,72 @@ __global__ void gate_silu_bwd_kernel(const bf16x8* __restrict__ dyg, const bf16x
 }
 
 // ------------------------------------------------------------------------------------------------ siso small, forward
-// grid (batch, ceil(heads / warps)), block = warps * 32.  Inputs dd_dt, dd_a, trap [B * L, H], angles [B * L, S] fp32.
+// The running rotary phase is the only dependency along the sequence: the sequence is cut into segments of FSEG tokens, a first
+// kernel sums the phase increments pi tanh(angle) DT per (sequence, segment, head, angle), and a block of the second kernel
+// starts its running phase from the totals of the earlier segments (taken modulo 2 pi like the running value itself).
+constexpr int FSEG = 128;   // tokens per segment (a multiple of 32)
+
+// grid (batch, segments), block = heads * 32: seg_inc[b][seg][h][64]
+__global__ void __launch_bounds__(1024) phase_segment_sums_kernel(const float* __restrict__ dd_dt, const float* __restrict__ angles,
+                                                                  const float* __restrict__ dt_bias, float* __restrict__ seg_inc,
+                                                                  int seq_len, int heads, int n_angles) {
+  const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.x, seg = blockIdx.y;
+  const int t_lo = seg * FSEG, t_hi = min(seq_len, t_lo + FSEG);
+  const float bias = dt_bias[h];
+  const bool has0 = lane < n_angles, has1 = lane + 32 < n_angles;
+  const int64_t row0 = (int64_t)b * seq_len;
+  float acc0 = 0.f, acc1 = 0.f;
+  for (int t0 = t_lo; t0 < t_hi; t0 += 4) {
+    float dts[4], a0[4], a1[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {   // the loads of four tokens go out together
+      const int t = t0 + j;
+      const bool ok = t < t_hi;
+      dts[j] = ok ? dd_dt[(row0 + t) * heads + h] : 0.f;
+      a0[j] = (ok && has0) ? angles[(row0 + t) * n_angles + lane] : 0.f;
+      a1[j] = (ok && has1) ? angles[(row0 + t) * n_angles + lane + 32] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (t0 + j < t_hi) {
+        const float dtv = softplus_(dts[j] + bias);
+        acc0 += PI_F * tanhf(a0[j]) * dtv;
+        acc1 += PI_F * tanhf(a1[j]) * dtv;
+      }
+    }
+  }
+  float* out = seg_inc + (((int64_t)b * gridDim.y + seg) * heads + h) * 64;
+  out[lane] = acc0;
+  out[lane + 32] = acc1;
+}
+
+// grid (batch, ceil(heads / warps), segments), block = warps * 32.  Inputs dd_dt, dd_a, trap [B * L, H], angles [B * L, S] fp32.
 __global__ void siso_small_fwd_kernel(const float* __restrict__ dd_dt, const float* __restrict__ dd_a, const float* __restrict__ trap,
                                       const float* __restrict__ angles, const float* __restrict__ dt_bias, float a_floor,
-                                      float* __restrict__ dt_o, float* __restrict__ a_o, float* __restrict__ sig_o,
-                                      float* __restrict__ adt_o, float* __restrict__ gamma_o, float* __restrict__ scale_o,
-                                      float* __restrict__ tanh_o, float* __restrict__ theta_o, float* __restrict__ spdt_o,
-                                      float* __restrict__ spa_o, float* __restrict__ live_o, int seq_len, int heads, int n_angles) {
+                                      const float* __restrict__ seg_inc, float* __restrict__ dt_o, float* __restrict__ a_o,
+                                      float* __restrict__ sig_o, float* __restrict__ adt_o, float* __restrict__ gamma_o,
+                                      float* __restrict__ scale_o, float* __restrict__ tanh_o, float* __restrict__ theta_o,
+                                      float* __restrict__ spdt_o, float* __restrict__ spa_o, float* __restrict__ live_o, int seq_len,
+                                      int heads, int n_angles) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + warp;
   if (h >= heads) return;
+  const int seg = blockIdx.z, t_lo = seg * FSEG, t_end = min(seq_len, t_lo + FSEG);
   const float bias = dt_bias[h];
   const int64_t row0 = (int64_t)b * seq_len;
   const bool writes_tanh = h == 0;
-  float acc0 = 0.f, acc1 = 0.f;   // running phase of angles lane and lane + 32
-  float carry_next = 0.f;         // DT_{t+1} (1 - sig_{t+1}) seen from token t: filled by walking the elementwise part backwards
-  // elementwise part, tokens spread over the lanes (independent of the running sum)
-  for (int t0 = seq_len - 32; t0 > -32; t0 -= 32) {
+  // DT_{t+1} (1 - sig_{t+1}) seen from the last token of the segment: from the inputs of the next segment's first token
+  float carry_next = 0.f;
+  if (t_end < seq_len) {
+    const int64_t i = (row0 + t_end) * heads + h;
+    carry_next = softplus_(dd_dt[i] + bias) * (1.f - sigmoidf_(trap[i]));
+  }
+  // elementwise part, tokens spread over the lanes, walking backwards so that the carry is known
+  for (int t0 = t_end - 32; t0 > t_lo - 32; t0 -= 32) {
     const int t = t0 + lane;
     float dt = 0.f, sg = 0.f;
-    if (t >= 0) {
+    if (t >= t_lo) {
       const int64_t i = (row0 + t) * heads + h;
       const float pre = dd_dt[i] + bias;
       dt = softplus_(pre);
@@ -98,25 +144,47 @@ __global__ void siso_small_fwd_kernel(const float* __restrict__ dd_dt, const flo
     const float mine = dt * (1.f - sg);
     float next = __shfl_down_sync(0xffffffffu, mine, 1);
     if (lane == 31) next = carry_next;
-    carry_next = __shfl_sync(0xffffffffu, mine, 0);
-    if (t >= 0) scale_o[(row0 + t) * heads + h] = dt * sg + next;
+    carry_next = __shfl_sync(0xffffffffu, mine, 0);   // the first token of this group follows the last of the group before it
+    if (t >= t_lo) scale_o[(row0 + t) * heads + h] = dt * sg + next;
   }
   __syncwarp();
-  // rotary phase: sequential over the tokens, lanes = angles
+  // rotary phase: sequential over the tokens of the segment, lanes = angles
   const bool has0 = lane < n_angles, has1 = lane + 32 < n_angles;
-  for (int t0 = 0; t0 < seq_len; t0 += 8) {
+  float acc0 = 0.f, acc1 = 0.f;   // running phase of angles lane and lane + 32
+  {
+    float p0[4] = {0.f, 0.f, 0.f, 0.f}, p1[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* src = seg_inc + (((int64_t)b * gridDim.z) * heads + h) * 64 + lane;
+    const int64_t stride = (int64_t)heads * 64;
+    int sgi = 0;
+    for (; sgi + 4 <= seg; sgi += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        p0[u] += src[(sgi + u) * stride];
+        p1[u] += src[(sgi + u) * stride + 32];
+      }
+    }
+    for (; sgi < seg; ++sgi) {
+      p0[0] += src[sgi * stride];
+      p1[0] += src[sgi * stride + 32];
+    }
+    acc0 = (p0[0] + p0[1]) + (p0[2] + p0[3]);
+    acc1 = (p1[0] + p1[1]) + (p1[2] + p1[3]);
+    acc0 -= TWO_PI_F * floorf(acc0 * (1.f / TWO_PI_F));
+    acc1 -= TWO_PI_F * floorf(acc1 * (1.f / TWO_PI_F));
+  }
+  for (int t0 = t_lo; t0 < t_end; t0 += 8) {
     float dts[8], t0v[8], t1v[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int t = t0 + j;
-      dts[j] = t < seq_len ? dt_o[(row0 + t) * heads + h] : 0.f;
-      t0v[j] = (t < seq_len && has0) ? tanhf(angles[(row0 + t) * n_angles + lane]) : 0.f;
-      t1v[j] = (t < seq_len && has1) ? tanhf(angles[(row0 + t) * n_angles + lane + 32]) : 0.f;
+      dts[j] = t < t_end ? dt_o[(row0 + t) * heads + h] : 0.f;
+      t0v[j] = (t < t_end && has0) ? tanhf(angles[(row0 + t) * n_angles + lane]) : 0.f;
+      t1v[j] = (t < t_end && has1) ? tanhf(angles[(row0 + t) * n_angles + lane + 32]) : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int t = t0 + j;
-      if (t >= seq_len) break;
+      if (t >= t_end) break;
       acc0 += PI_F * t0v[j] * dts[j];
       acc1 += PI_F * t1v[j] * dts[j];
       acc0 -= TWO_PI_F * floorf(acc0 * (1.f / TWO_PI_F));
@@ -167,8 +235,10 @@ __device__ __forceinline__ void put<float>(float* p, float v) { *p = v; }
 template <>
 __device__ __forceinline__ void put<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16(v); }
 
-template <typename OutT>
-__global__ void __launch_bounds__(1024) siso_small_bwd_kernel(
+// MAXT: the largest block the instantiation is launched with (heads * 32); the smaller bound leaves room for the tile
+// prefetch in registers.
+template <typename OutT, int MAXT>
+__global__ void __launch_bounds__(MAXT) siso_small_bwd_kernel(
     const float* __restrict__ dt, const float* __restrict__ a, const float* __restrict__ sig, const float* __restrict__ tanh_a,
     const float* __restrict__ sp_dt, const float* __restrict__ sp_a, const float* __restrict__ live,
     const float* __restrict__ dadt, const float* __restrict__ dtheta, const float* __restrict__ dgamma,
@@ -182,11 +252,23 @@ __global__ void __launch_bounds__(1024) siso_small_bwd_kernel(
   const bool has = lane < n_angles;
   const int seg = blockIdx.y, t_first = seg * SEG;
   float acc = 0.f;
-  for (int sg = seg + 1; sg < (int)gridDim.y; ++sg) acc += seg_sum[(((int64_t)pb * gridDim.y + sg) * heads + h) * 32 + lane];
+  {   // totals of the later segments: independent partial sums, so that the loads are in flight together
+    float part[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* src = seg_sum + (((int64_t)pb * gridDim.y) * heads + h) * 32 + lane;
+    const int64_t stride = (int64_t)heads * 32;
+    int sg = seg + 1;
+    for (; sg + 4 <= (int)gridDim.y; sg += 4) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) part[u] += src[(sg + u) * stride];
+    }
+    for (; sg < (int)gridDim.y; ++sg) part[0] += src[sg * stride];
+    acc = (part[0] + part[1]) + (part[2] + part[3]);
+  }
   float* tanh_tile = contrib + TL * heads * 32;   // [TL][32]: tanh(angle) of the tile's tokens, for the head sum
-  for (int t_hi = min(seq_len, t_first + SEG) - 1; t_hi >= t_first; t_hi -= TL) {
-    // every global load of the tile goes out here, in one round (the tile is bound by load latency, not by bandwidth)
-    float dth[TL], tn[TL], dts[TL];
+  const int t_last = min(seq_len, t_first + SEG) - 1;
+  // the loads of a tile are issued one tile ahead: a tile is bound by load latency (24 KB in flight per SM otherwise)
+  float dth_n[TL], tn_n[TL], dts_n[TL];
+  auto load_tile = [&](int t_hi, float* dth, float* tn, float* dts) {
 #pragma unroll
     for (int j = 0; j < TL; ++j) {
       const int t = t_hi - j;
@@ -195,6 +277,17 @@ __global__ void __launch_bounds__(1024) siso_small_bwd_kernel(
       tn[j] = (ok && has) ? tanh_a[(frow0 + t) * n_angles + lane] : 0.f;
       dts[j] = ok ? dt[(frow0 + t) * heads + h] : 0.f;
     }
+  };
+  load_tile(t_last, dth_n, tn_n, dts_n);
+  for (int t_hi = t_last; t_hi >= t_first; t_hi -= TL) {
+    float dth[TL], tn[TL], dts[TL];
+#pragma unroll
+    for (int j = 0; j < TL; ++j) {
+      dth[j] = dth_n[j];
+      tn[j] = tn_n[j];
+      dts[j] = dts_n[j];
+    }
+    if (t_hi - TL >= t_first) load_tile(t_hi - TL, dth_n, tn_n, dts_n);
     // lane j < TL finishes the [b, l, h]-sized cotangents of token t_hi - j
     const int t_mine = t_hi - lane;
     const bool mine_ok = lane < TL && t_mine >= t_first;
@@ -275,17 +368,21 @@ extern "C" int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, 
   return (int)cudaGetLastError();
 }
 
+extern "C" int lbi_siso_small_fwd_segments(int seq_len) { return (seq_len + lbi::msmall::FSEG - 1) / lbi::msmall::FSEG; }
+
 extern "C" int lbi_siso_small_fwd(const float* dd_dt, const float* dd_a, const float* trap, const float* angles,
-                                  const float* dt_bias, float a_floor, float* dt, float* a, float* sig, float* adt, float* gamma,
-                                  float* scale, float* tanh_a, float* theta, float* sp_dt, float* sp_a, float* live, int batch,
-                                  int seq_len, int heads, int n_angles, cudaStream_t st) {
+                                  const float* dt_bias, float a_floor, float* seg_inc, float* dt, float* a, float* sig, float* adt,
+                                  float* gamma, float* scale, float* tanh_a, float* theta, float* sp_dt, float* sp_a, float* live,
+                                  int batch, int seq_len, int heads, int n_angles, cudaStream_t st) {
   using namespace lbi;
   if (batch <= 0 || seq_len <= 0) return 0;
-  if (n_angles > 64 || n_angles <= 0) return (int)cudaErrorInvalidValue;
+  if (n_angles > 64 || n_angles <= 0 || heads <= 0 || heads > 32 || !seg_inc) return (int)cudaErrorInvalidValue;
+  const int segs = lbi_siso_small_fwd_segments(seq_len);
+  msmall::phase_segment_sums_kernel<<<dim3(batch, segs), heads * 32, 0, st>>>(dd_dt, angles, dt_bias, seg_inc, seq_len, heads, n_angles);
   const int warps = heads < 8 ? heads : 8;
-  dim3 grid(batch, (heads + warps - 1) / warps);
-  msmall::siso_small_fwd_kernel<<<grid, warps * 32, 0, st>>>(dd_dt, dd_a, trap, angles, dt_bias, a_floor, dt, a, sig, adt, gamma,
-                                                             scale, tanh_a, theta, sp_dt, sp_a, live, seq_len, heads, n_angles);
+  dim3 grid(batch, (heads + warps - 1) / warps, segs);
+  msmall::siso_small_fwd_kernel<<<grid, warps * 32, 0, st>>>(dd_dt, dd_a, trap, angles, dt_bias, a_floor, seg_inc, dt, a, sig, adt,
+                                                             gamma, scale, tanh_a, theta, sp_dt, sp_a, live, seq_len, heads, n_angles);
   return (int)cudaGetLastError();
 }
 
@@ -302,14 +399,19 @@ extern "C" int lbi_siso_small_bwd(const float* dt, const float* a, const float* 
   const size_t smem = (size_t)msmall::TL * (heads + 1) * 32 * sizeof(float);
   const dim3 grid(batch * reps, lbi_siso_small_segments(seq_len));
   msmall::dtheta_segment_sums_kernel<<<grid, heads * 32, 0, st>>>(dtheta, seg_sum, seq_len, heads, n_angles);
-  if (out_bf16)
-    msmall::siso_small_bwd_kernel<__nv_bfloat16><<<grid, heads * 32, smem, st>>>(
-        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, seg_sum, (__nv_bfloat16*)d_dd_dt,
-        (__nv_bfloat16*)d_dd_a, (__nv_bfloat16*)d_trap, (__nv_bfloat16*)d_angles, batch, seq_len, heads, n_angles);
-  else
-    msmall::siso_small_bwd_kernel<float><<<grid, heads * 32, smem, st>>>(
-        dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, dgamma, dscale, seg_sum, (float*)d_dd_dt, (float*)d_dd_a,
-        (float*)d_trap, (float*)d_angles, batch, seq_len, heads, n_angles);
+#define LBI_SMALL_BWD(OutT, MAXT)                                                                                              \
+  msmall::siso_small_bwd_kernel<OutT, MAXT><<<grid, heads * 32, smem, st>>>(dt, a, sig, tanh_a, sp_dt, sp_a, live, dadt, dtheta, \
+                                                                            dgamma, dscale, seg_sum, (OutT*)d_dd_dt,            \
+                                                                            (OutT*)d_dd_a, (OutT*)d_trap, (OutT*)d_angles,      \
+                                                                            batch, seq_len, heads, n_angles)
+  if (out_bf16) {
+    if (heads <= 24) LBI_SMALL_BWD(__nv_bfloat16, 768);
+    else LBI_SMALL_BWD(__nv_bfloat16, 1024);
+  } else {
+    if (heads <= 24) LBI_SMALL_BWD(float, 768);
+    else LBI_SMALL_BWD(float, 1024);
+  }
+#undef LBI_SMALL_BWD
   return (int)cudaGetLastError();
 }
 

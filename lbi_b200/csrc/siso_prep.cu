@@ -218,6 +218,153 @@ __global__ void __launch_bounds__(THREADS, 3) bwd_kernel(const T* __restrict__ q
   }
 }
 
+// The same backward with two heads per warp step: lanes 0 - 15 take head 2i, lanes 16 - 31 head 2i + 1 of the row's group,
+// eight elements per lane.  The per-head bookkeeping (addresses, scalar loads, the shuffle reductions, the scalar stores)
+// is issued once per pair of heads and the reductions are four levels deep; the kernel above is bound by instruction issue
+// (about 290 warp instructions per token and head), not by memory.  Needs an even number of heads per group and
+// n_angles % 4 == 0 (a lane's four rotation pairs are read as one vector); bias gradients go through the kernel above.
+template <typename Cc>
+struct Raw8;
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 v;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { v = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void unpack(float* f) const {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.z));
+    const float2 d = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.w));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+  }
+};
+template <>
+struct Raw8<float> {
+  float4 lo, hi;
+  __device__ __forceinline__ void load(const float* p) {
+    lo = reinterpret_cast<const float4*>(p)[0];
+    hi = reinterpret_cast<const float4*>(p)[1];
+  }
+  __device__ __forceinline__ void unpack(float* f) const {
+    f[0] = lo.x; f[1] = lo.y; f[2] = lo.z; f[3] = lo.w; f[4] = hi.x; f[5] = hi.y; f[6] = hi.z; f[7] = hi.w;
+  }
+};
+
+template <typename C>
+struct PairIn {        // what a lane reads per head of the cotangents and the per-head scalars, loaded one step ahead
+  Raw8<C> gq, gk;
+  float4 th;
+  float sc, gm, dd;
+};
+
+template <typename T, typename C>
+__global__ void __launch_bounds__(THREADS, 2) bwd_pair_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                              const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                                                              const float* __restrict__ theta, const float* __restrict__ gamma,
+                                                              const float* __restrict__ scale, const C* __restrict__ dqr,
+                                                              const C* __restrict__ dkr, const float* __restrict__ dqk,
+                                                              float* __restrict__ dq, float* __restrict__ dk, float* __restrict__ dtheta,
+                                                              float* __restrict__ dgamma, float* __restrict__ dscale, int64_t rows,
+                                                              int64_t frows, int groups, int heads, int n_angles, int seq_len,
+                                                              int dkr_pad) {
+  const int lane = threadIdx.x & 31, half = lane >> 4, li = lane & 15;
+  const int rep = heads / groups;
+  const bool turns = 4 * li < n_angles;   // this lane's four pairs are rotated
+  for (int64_t row = (int64_t)blockIdx.x * WARPS + (threadIdx.x >> 5); row < rows; row += (int64_t)gridDim.x * WARPS) {
+    const int g = groups == 1 ? 0 : (int)(row % groups);
+    const int64_t tok = groups == 1 ? row : row / groups;
+    const int64_t frow = row < frows ? row : row % frows, ftok = groups == 1 ? frow : frow / groups;
+    const int64_t ktok = dkr_pad > 0 ? (tok / seq_len) * dkr_pad + (dkr_pad - 1 - tok % seq_len) : tok;
+    float qg[8], kg[8];
+    {
+      Raw8<T> a, b;
+      a.load(q + frow * N + li * 8);
+      b.load(k + frow * N + li * 8);
+      a.unpack(qg);
+      b.unpack(kg);
+    }
+    float dq_sum[8], dk_sum[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dq_sum[e] = dk_sum[e] = 0.f;
+    auto load_pair = [&](int r2) {
+      PairIn<C> in;
+      const int h = g * rep + 2 * r2 + half;
+      const int64_t hrow = tok * heads + h, fhrow = ftok * heads + h, krow = ktok * heads + h;
+      in.gq.load(dqr + hrow * N + li * 8);
+      in.gk.load(dkr + krow * N + li * 8);
+      in.th = turns ? *reinterpret_cast<const float4*>(theta + fhrow * n_angles + 4 * li) : make_float4(0.f, 0.f, 0.f, 0.f);
+      in.sc = scale[fhrow];
+      in.gm = gamma[fhrow];
+      in.dd = dqk[hrow];
+      return in;
+    };
+    PairIn<C> cur = load_pair(0);
+    for (int r2 = 0; r2 < rep / 2; ++r2) {
+      const int h = g * rep + 2 * r2 + half;
+      const int64_t hrow = tok * heads + h;
+      PairIn<C> nxt = cur;
+      if (r2 + 1 < rep / 2) nxt = load_pair(r2 + 1);
+      float qh[8], kh[8], gq[8], gk[8];
+      {
+        const float4 b0 = *reinterpret_cast<const float4*>(q_bias + h * N + li * 8), b1 = *reinterpret_cast<const float4*>(q_bias + h * N + li * 8 + 4);
+        const float4 c0 = *reinterpret_cast<const float4*>(k_bias + h * N + li * 8), c1 = *reinterpret_cast<const float4*>(k_bias + h * N + li * 8 + 4);
+        qh[0] = qg[0] + b0.x; qh[1] = qg[1] + b0.y; qh[2] = qg[2] + b0.z; qh[3] = qg[3] + b0.w;
+        qh[4] = qg[4] + b1.x; qh[5] = qg[5] + b1.y; qh[6] = qg[6] + b1.z; qh[7] = qg[7] + b1.w;
+        kh[0] = kg[0] + c0.x; kh[1] = kg[1] + c0.y; kh[2] = kg[2] + c0.z; kh[3] = kg[3] + c0.w;
+        kh[4] = kg[4] + c1.x; kh[5] = kg[5] + c1.y; kh[6] = kg[6] + c1.z; kh[7] = kg[7] + c1.w;
+      }
+      cur.gq.unpack(gq);
+      cur.gk.unpack(gk);
+      float cs[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
+      if (turns) {
+        __sincosf(cur.th.x, &sn[0], &cs[0]);
+        __sincosf(cur.th.y, &sn[1], &cs[1]);
+        __sincosf(cur.th.z, &sn[2], &cs[2]);
+        __sincosf(cur.th.w, &sn[3], &cs[3]);
+      }
+      const float sc = cur.sc, w = cur.dd * cur.gm;
+      float dth[4];
+      float dsc = 0.f, qk = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float qa = qh[2 * j], qb2 = qh[2 * j + 1], ka = kh[2 * j], kb2 = kh[2 * j + 1];
+        // rotated pairs (ko without the scale)
+        const float qoa = qa * cs[j] - qb2 * sn[j], qob = qa * sn[j] + qb2 * cs[j];
+        const float koa = ka * cs[j] - kb2 * sn[j], kob = ka * sn[j] + kb2 * cs[j];
+        const float gqa = gq[2 * j], gqb = gq[2 * j + 1], gka = gk[2 * j], gkb = gk[2 * j + 1];
+        dth[j] = (-gqa * qob + gqb * qoa) + sc * (-gka * kob + gkb * koa);   // J (a, b) = (-b, a) applied to the rotated pair
+        dsc = fmaf(gka, koa, fmaf(gkb, kob, dsc));
+        qk = fmaf(qa, ka, fmaf(qb2, kb2, qk));
+        // back through the rotation, plus the q . k term
+        const float dqa = gqa * cs[j] + gqb * sn[j] + w * ka, dqb = -gqa * sn[j] + gqb * cs[j] + w * kb2;
+        const float dka = sc * (gka * cs[j] + gkb * sn[j]) + w * qa, dkb = sc * (-gka * sn[j] + gkb * cs[j]) + w * qb2;
+        dq_sum[2 * j] += dqa; dq_sum[2 * j + 1] += dqb;
+        dk_sum[2 * j] += dka; dk_sum[2 * j + 1] += dkb;
+      }
+      if (turns) *reinterpret_cast<float4*>(dtheta + hrow * n_angles + 4 * li) = make_float4(dth[0], dth[1], dth[2], dth[3]);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) {   // sums over the sixteen lanes of the head, the two reductions interleaved
+        dsc += __shfl_xor_sync(0xffffffffu, dsc, o);
+        qk += __shfl_xor_sync(0xffffffffu, qk, o);
+      }
+      if (li == 0) {
+        dscale[hrow] = dsc;
+        dgamma[hrow] = cur.dd * qk;
+      }
+      cur = nxt;
+    }
+    // the two halves hold the sums of the even and the odd heads
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      dq_sum[e] += __shfl_xor_sync(0xffffffffu, dq_sum[e], 16);
+      dk_sum[e] += __shfl_xor_sync(0xffffffffu, dk_sum[e], 16);
+    }
+    float* dst = (half == 0 ? dq : dk) + row * N + li * 8;
+    const float* src = half == 0 ? dq_sum : dk_sum;
+    reinterpret_cast<float4*>(dst)[0] = make_float4(src[0], src[1], src[2], src[3]);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(src[4], src[5], src[6], src[7]);
+  }
+}
+
 static int grid_for(int64_t rows) {
   int64_t blocks = (rows + WARPS - 1) / WARPS;
   if (blocks > 148 * 8) blocks = 148 * 8;
@@ -254,6 +401,12 @@ static int launch_bwd(const void* q, const void* k, const float* q_bias, const f
                       float* dgamma, float* dscale, float* bias_partials, int64_t rows, int64_t frows, int groups, int heads,
                       int n_angles, int seq_len, int dkr_pad, cudaStream_t st) {
   const int blocks = grid_for(rows);
+  if (!bias_partials && (heads / groups) % 2 == 0 && n_angles % 4 == 0 && n_angles > 0) {
+    bwd_pair_kernel<T, C><<<blocks, THREADS, 0, st>>>((const T*)q, (const T*)k, q_bias, k_bias, theta, gamma, scale, (const C*)dqr,
+                                                      (const C*)dkr, dqk, dq, dk, dtheta, dgamma, dscale, rows, frows, groups, heads,
+                                                      n_angles, seq_len, dkr_pad);
+    return (int)cudaGetLastError();
+  }
   const size_t smem = (size_t)2 * heads * N * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   static PerDeviceOnce configured;

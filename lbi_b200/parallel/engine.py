@@ -127,11 +127,6 @@ class FastLBIEngine:
     def _g(self, p) -> torch.Tensor:
         return self.flat.grad(self.flat.name_of(p))
 
-    def _acc_grads(self, params, grads) -> None:
-        for p, g in zip(params, grads):
-            if g is not None:
-                self._g(p).add_(g.float())
-
     def target(self, name: str):
         """Gradient sink protocol of the structured backward: backbone-relative name -> fp32 accumulator."""
         return self.flat.grad("region_backend.backbone." + name)
