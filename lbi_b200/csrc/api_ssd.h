@@ -57,7 +57,7 @@ int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk, const void
 //   dx = dt * dX + d_skip * gy,  ddt = da * a_param + dX . x,  dd[h] += sum gy . x
 // `reversed`: dx_rev is in reversed time (else natural order); x and dt hold `fbatch` sequences shared by batch / fbatch
 // stacked directions of gy.
-int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void* gy, const float* dt, const float* da,
+int lbi_ssd_bwd_finish(const void* dx_rev, int dx_is_bf16, const void* x, const void* gy, const float* dt, const float* da,
                        const float* a_param, const float* d_skip, void* dx, float* ddt, float* dd, int batch, int seq_len,
                        int seq_pad, int heads, int is_bf16, int reversed, int fbatch, cudaStream_t stream);
 

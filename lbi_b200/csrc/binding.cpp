@@ -974,7 +974,8 @@ std::vector<Tensor> ssd_chunk_bwd(const Tensor& v, const Tensor& gy, const Tenso
 // decay-gradient result), a_param [H], d_skip [H] or none -> (dx like x, ddt [B, L, H], dD [H] or empty).
 std::tuple<Tensor, Tensor, Tensor> ssd_bwd_finish(const Tensor& dx_rev, const Tensor& x, const Tensor& gy, const Tensor& dt, const Tensor& da,
                                                   const Tensor& a_param, const c10::optional<Tensor>& d_skip, bool reversed) {
-  CHECK_F32(dx_rev);
+  TORCH_CHECK(dx_rev.is_cuda() && dx_rev.is_contiguous() && (dx_rev.scalar_type() == at::kFloat || dx_rev.scalar_type() == at::kBFloat16),
+              "ssd_bwd_finish: dx_rev must be a contiguous CUDA fp32 / bf16 tensor");
   CHECK_F32(dt);
   CHECK_F32(a_param);
   c10::cuda::CUDAGuard guard(x.device());
@@ -993,7 +994,7 @@ std::tuple<Tensor, Tensor, Tensor> ssd_bwd_finish(const Tensor& dx_rev, const Te
   Tensor ddt = torch::empty({batch, seq, heads}, dt.options());
   Tensor dd = d_skip ? torch::zeros({heads}, dt.options()) : torch::empty({0}, dt.options());
   if (d_skip) CHECK_F32((*d_skip));
-  check(lbi_ssd_bwd_finish(dx_rev.data_ptr<float>(), x.data_ptr(), gy.data_ptr(), dt.data_ptr<float>(), da_t.data_ptr<float>(),
+  check(lbi_ssd_bwd_finish(dx_rev.data_ptr(), dx_rev.scalar_type() == at::kBFloat16 ? 1 : 0, x.data_ptr(), gy.data_ptr(), dt.data_ptr<float>(), da_t.data_ptr<float>(),
                            a_param.data_ptr<float>(), d_skip ? d_skip->data_ptr<float>() : nullptr, dx.data_ptr(), ddt.data_ptr<float>(),
                            d_skip ? dd.data_ptr<float>() : nullptr, (int)batch, (int)seq, (int)seq_pad, (int)heads,
                            x.scalar_type() == at::kBFloat16 ? 1 : 0, reversed ? 1 : 0, (int)fbatch, cur_stream()),

@@ -1399,8 +1399,9 @@ __device__ __forceinline__ void st2<float>(float* p, float a, float b) {
   *reinterpret_cast<float2*>(p) = make_float2(a, b);
 }
 
-template <typename T>
-__global__ void __launch_bounds__(256) bwd_finish_kernel(const float* __restrict__ dx_rev, const T* __restrict__ x,
+// G: dtype of dx_rev (fp32 from the role-permuted scans, bf16 from the fused chunk backward)
+template <typename T, typename G>
+__global__ void __launch_bounds__(256) bwd_finish_kernel(const G* __restrict__ dx_rev, const T* __restrict__ x,
                                                          const T* __restrict__ gy, const float* __restrict__ dt,
                                                          const float* __restrict__ da, const float* __restrict__ a_param,
                                                          const float* __restrict__ d_skip, T* __restrict__ dx,
@@ -1422,7 +1423,7 @@ __global__ void __launch_bounds__(256) bwd_finish_kernel(const float* __restrict
     const int64_t row = bl * heads + h;
     const int64_t frow = (bl % ftokens) * heads + h;
     const int64_t rrow = (b * seq_pad + (reversed ? seq_pad - 1 - l : l)) * heads + h;
-    const float2 g = *reinterpret_cast<const float2*>(dx_rev + rrow * P + lane * 2);
+    const float2 g = ld2<G>(dx_rev + rrow * P + lane * 2);
     const float2 xv = ld2<T>(x + frow * P + lane * 2);
     const float2 gv = ld2<T>(gy + row * P + lane * 2);
     const float dtv = dt[frow];
@@ -1739,19 +1740,21 @@ extern "C" int lbi_ssd_decay_grad(const void* v, const void* gy, const void* bk,
   return (int)cudaErrorInvalidValue;
 }
 
-extern "C" int lbi_ssd_bwd_finish(const float* dx_rev, const void* x, const void* gy, const float* dt, const float* da,
+extern "C" int lbi_ssd_bwd_finish(const void* dx_rev, int dx_is_bf16, const void* x, const void* gy, const float* dt, const float* da,
                                   const float* a_param, const float* d_skip, void* dx, float* ddt, float* dd, int batch,
                                   int seq_len, int seq_pad, int heads, int is_bf16, int reversed, int fbatch, cudaStream_t st) {
   using namespace lbi::ssd;
   if (batch <= 0 || seq_len <= 0 || seq_pad < seq_len || heads <= 0 || fbatch <= 0 || batch % fbatch != 0) return (int)cudaErrorInvalidValue;
   const int64_t tokens = (int64_t)batch * seq_len, ftokens = (int64_t)fbatch * seq_len;
   const dim3 blocks((unsigned)((tokens + 127) / 128), (unsigned)heads);
-  if (is_bf16)
-    bwd_finish_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(dx_rev, (const __nv_bfloat16*)x, (const __nv_bfloat16*)gy, dt, da, a_param,
-                                                            d_skip, (__nv_bfloat16*)dx, ddt, dd, tokens, seq_len, seq_pad, heads, reversed, ftokens);
-  else
-    bwd_finish_kernel<float><<<blocks, 256, 0, st>>>(dx_rev, (const float*)x, (const float*)gy, dt, da, a_param, d_skip, (float*)dx, ddt,
-                                                    dd, tokens, seq_len, seq_pad, heads, reversed, ftokens);
+#define LBI_FINISH(T, G)                                                                                                       \
+  bwd_finish_kernel<T, G><<<blocks, 256, 0, st>>>((const G*)dx_rev, (const T*)x, (const T*)gy, dt, da, a_param, d_skip, (T*)dx, ddt, \
+                                                  dd, tokens, seq_len, seq_pad, heads, reversed, ftokens)
+  if (is_bf16 && dx_is_bf16) LBI_FINISH(__nv_bfloat16, __nv_bfloat16);
+  else if (is_bf16) LBI_FINISH(__nv_bfloat16, float);
+  else if (dx_is_bf16) LBI_FINISH(float, __nv_bfloat16);
+  else LBI_FINISH(float, float);
+#undef LBI_FINISH
   return (int)cudaGetLastError();
 }
 

@@ -492,8 +492,9 @@ def ssd_backward_fused(x, dt, A, B, C, D, gy, fwd_states):
     g, n = B.shape[2], B.shape[3]
     reps = gy.shape[0] // bsz
     dtf, Af = dt.float(), A.float()
+    # bf16 results leave the chunk kernel through TMA stores; fp32 ones as 128-byte row pieces from registers
     dX, dC_h, dB_h, da, _ = chunk_backward(x, gy, B, C, dtf * Af, dtf, None, fwd_states, per_head=False, strict=False,
-                                           dv_bf16=False, dn_bf16=True)
+                                           dv_bf16=x.dtype == torch.bfloat16, dn_bf16=True)
     xk = x if x.dtype in (torch.bfloat16, torch.float32) else x.float()
     dx, ddt, dD = ext().ssd_bwd_finish(dX.contiguous(), xk.contiguous(), gy.to(xk.dtype).contiguous(), dtf.contiguous(), da,
                                        Af.contiguous(), None if D is None else D.float().contiguous(), False)
