@@ -132,7 +132,8 @@ int lbi_conv_silu_fwd(const void* x, const float* wt, const float* bias, void* p
 int lbi_conv_silu_bwd(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre, const float* wt,
                       void* din, int64_t ld_in, int c0, int c1, int c2, int64_t tokens, int64_t ftokens, int seq_len, int width,
                       cudaStream_t stream);
-// dw [channels, width] += , db [channels] += (fp32; zeroed by the caller).  One direction (tokens = ftokens).
+// dw [channels, width] += , db [channels] += (fp32; zeroed by the caller).  One direction (tokens = ftokens).  pre may be null:
+// the weight gradient of a plain convolution (no SiLU after it), with d0 its output cotangent and c1 = c2 = 0.
 int lbi_conv_silu_wgrad(const void* d0, int d0_fp32, const void* d1, const void* d2, int d12_fp32, const void* pre, const void* x,
                         float* dw, float* db, int c0, int c1, int c2, int64_t tokens, int seq_len, int width, cudaStream_t stream);
 

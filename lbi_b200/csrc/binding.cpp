@@ -613,6 +613,24 @@ std::tuple<Tensor, Tensor> conv_silu_wgrad(const Tensor& d0, const Tensor& d1, c
   return {dw, db};
 }
 
+// Weight / bias gradient of the plain depthwise causal conv (no activation): dy, x [tokens, C] bf16 -> (dw [C, W], db [C]) fp32.
+// The conv + SiLU weight-gradient kernel with a null pre-activation.
+std::tuple<Tensor, Tensor> causal_conv_wgrad(const Tensor& dy, const Tensor& x, int64_t width, int64_t seq_len) {
+  CHECK_BF16(dy);
+  CHECK_BF16(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(dy.dim() == 2 && dy.sizes() == x.sizes() && dy.size(1) % 8 == 0 && width >= 1 && width <= 8 && seq_len > 0 &&
+                  dy.size(0) % seq_len == 0,
+              "causal_conv_wgrad: dy, x [tokens, C] with C % 8 == 0, width <= 8, tokens a multiple of seq_len");
+  const int64_t tokens = dy.size(0), ch = dy.size(1);
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor dw = torch::zeros({ch, width}, f32), db = torch::zeros({ch}, f32);
+  check(lbi_conv_silu_wgrad(dy.data_ptr(), 0, dy.data_ptr(), dy.data_ptr(), 0, nullptr, x.data_ptr(), dw.data_ptr<float>(),
+                            db.data_ptr<float>(), (int)ch, 0, 0, tokens, (int)seq_len, (int)width, cur_stream()),
+        "causal_conv_wgrad");
+  return {dw, db};
+}
+
 // (((in_scale g) @ wa) o d) @ wb over a basis: g [B, P, din] fp32, wa [din, hidden], d [B, hidden] or none, wb [hidden, dout] or none.
 Tensor interface_mlp_jac(const Tensor& g, const Tensor& wa, const c10::optional<Tensor>& d, const c10::optional<Tensor>& wb,
                          double in_scale) {
@@ -1217,6 +1235,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("conv_silu_fwd", &conv_silu_fwd);
   m.def("conv_silu_bwd_", &conv_silu_bwd_);
   m.def("conv_silu_wgrad", &conv_silu_wgrad);
+  m.def("causal_conv_wgrad", &causal_conv_wgrad);
   m.def("gate_silu_fwd", &gate_silu_fwd);
   m.def("gate_silu_bwd", &gate_silu_bwd);
   m.def("siso_small_fwd", &siso_small_fwd);

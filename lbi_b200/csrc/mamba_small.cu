@@ -499,6 +499,11 @@ __device__ __forceinline__ void dpre8(const D0* d0, const D12* d1, const D12* d2
   if (c < seg.c0) load_cot<D0>(d0 + tok * seg.c0 + c, g);
   else if (c < seg.c0 + seg.c1) load_cot<D12>(d1 + tok * seg.c1 + (c - seg.c0), g);
   else load_cot<D12>(d2 + tok * seg.c2 + (c - seg.c0 - seg.c1), g);
+  if (!pre) {   // a plain convolution (no activation after it): the cotangent is the pre-activation cotangent
+#pragma unroll
+    for (int e = 0; e < 8; ++e) out[e] = g[e];
+    return;
+  }
   unpack8(*reinterpret_cast<const bf16x8*>(pre + ftok * channels + c), pv);
 #pragma unroll
   for (int e = 0; e < 8; ++e) out[e] = g[e] * dsilu_(pv[e]);

@@ -273,6 +273,10 @@ def causal_conv_dgrad(dy, weight, batch, seq_len):
 
 
 def causal_conv_wgrad(dy, x, width, batch, seq_len):
+    if (_native(dy, x) and dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and dy.shape == x.shape and dy.shape[-1] % 8 == 0
+            and width <= 8 and hasattr(ext(), "causal_conv_wgrad")):
+        _count()
+        return ext().causal_conv_wgrad(dy.contiguous(), x.contiguous(), int(width), int(seq_len))
     fell_back("causal_conv_wgrad", dy, x, width, batch, seq_len)
     return ref.causal_conv_wgrad(dy, x, width, batch, seq_len)
 

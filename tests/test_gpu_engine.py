@@ -119,13 +119,23 @@ def test_bench_paths_run_on_tiny_configs(config):
     assert out["e2e"]["value"] > 0 and out["e2e"]["h2d_bytes_per_step"] > 0
 
 
-@pytest.mark.parametrize("kind", ["transformer", "mamba3", "mamba2", "hybrid"])
+@pytest.mark.parametrize("kind", ["transformer", "transformer-qkv-conv", "mamba3", "mamba2", "hybrid"])
 def test_engine_step_never_leaves_the_kernels_in_strict_mode(kind):
     """With strict mode on, any route to PyTorch / cuBLAS / flash_attn for a CUDA bf16 tensor raises: a full training step
     of every backbone must pass, and the fallback counters must stay empty."""
     from lbi_b200 import ops
 
-    model = (_model("sequence", 2, True) if kind == "transformer" else _mamba_model(kind)).cuda()
+    if kind == "transformer":
+        model = _model("sequence", 2, True)
+    elif kind == "transformer-qkv-conv":   # the reference's Transformer always has the depthwise conv on qkv (d_conv >= 1)
+        torch.manual_seed(0)
+        spec = BackboneSpec(name="transformer", dim=256, layers=2, n_heads=4, d_conv=4, d_intermediate=512)
+        iface = VectorMLPInterface(feature_dim=256, num_regions=2, interface_width=16, interface_map_hidden_dim=64)
+        model = LBILanguageModel(vocab_size=1024, layers_per_region=1, backbone_spec=spec, interface=iface, region_axis="sequence",
+                                 num_sequence_regions=2, tie_embeddings=True)
+    else:
+        model = _mamba_model(kind)
+    model = model.cuda()
     prev = ops.dispatch.set_strict(True)
     ops.dispatch.FALLBACKS.clear()
     try:

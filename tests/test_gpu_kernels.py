@@ -95,6 +95,13 @@ def test_causal_conv():
     _close(ops.causal_conv_fwd(x, weight, bias, b, t), ref.causal_conv_fwd(x, weight, bias, b, t), 3e-2, 2e-2, "conv fwd")
     dy = torch.randn(3 * b * t, c, device=DEV).bfloat16()
     _close(ops.causal_conv_dgrad(dy, weight, b, t), ref.causal_conv_dgrad(dy, weight, b, t), 3e-2, 2e-2, "conv dgrad")
+    one = dy[: b * t].contiguous()
+    before = ops.dispatch.KERNEL_LAUNCHES["count"]
+    dw, db = ops.causal_conv_wgrad(one, x, w, b, t)
+    assert ops.dispatch.KERNEL_LAUNCHES["count"] == before + 1, "the conv weight-gradient kernel did not run"
+    want_dw, want_db = ref.causal_conv_wgrad(one, x, w, b, t)
+    _close(dw, want_dw, 2e-2 * float(want_dw.abs().max()), 2e-2, "conv wgrad")
+    _close(db, want_db, 2e-2 * float(want_db.abs().max()), 2e-2, "conv bias grad")
 
 
 @pytest.mark.parametrize("b,k,r", [(1, 1, 1), (2, 3, 8), (3, 8, 64), (2, 5, 100), (1, 16, 128), (2, 8, 256)])
