@@ -271,6 +271,7 @@ class _SSDFunction(torch.autograd.Function):
         ctx.save_for_backward(x, dt, A, B, C, D if D is not None else x.new_empty(0),
                               initial_state if initial_state is not None else x.new_empty(0), final, states)
         ctx.has_d, ctx.has_init = D is not None, initial_state is not None
+        ctx.set_materialize_grads(False)   # an unused final state then arrives as None, not as a tensor of zeros
         return y.to(x.dtype), final
 
     @staticmethod
@@ -279,6 +280,13 @@ class _SSDFunction(torch.autograd.Function):
         if BACKWARD_KERNELS and hasattr(ext(), "ssd_decay_grad"):
             if gy is None:
                 gy = torch.zeros_like(x)
+            if (not ctx.has_init and gfinal is None and chunk_backward_supported(x) and x.dtype == torch.bfloat16
+                    and (x.shape[2] // B.shape[2]) % 2 == 0):
+                # no state enters or leaves the sequence: the fused chunk backward (one kernel per chunk and head instead of
+                # three role-permuted scans, the decay-gradient kernel and their glue)
+                dx, ddt, dA, dB, dC, dD = ssd_backward_fused(x, dt, A, B, C, D if ctx.has_d else None, gy, states)
+                return (dx.to(x.dtype), ddt.to(dt.dtype), dA.to(A.dtype), dB.to(B.dtype), dC.to(C.dtype),
+                        None if dD is None else dD.to(D.dtype), None)
             dx, ddt, dA, dB, dC, dD, d_init = ssd_backward(x, dt, A, B, C, D if ctx.has_d else None, init if ctx.has_init else None,
                                                            final, gy, gfinal, fwd_states=states)
             return (dx.to(x.dtype), ddt.to(dt.dtype), dA.to(A.dtype), dB.to(B.dtype), dC.to(C.dtype),

@@ -123,6 +123,25 @@ def test_ssd_backward_kernels_match_autograd_of_the_recurrence(b, l, h, g, n, wi
         assert err <= 2.5e-2, f"{name}: relative error {err:.3e}"
 
 
+@pytest.mark.parametrize("b,l,h,g,n", [(1, 200, 4, 2, 64), (2, 256, 4, 1, 128), (1, 512, 8, 2, 128)])
+def test_ssd_autograd_takes_the_fused_backward_when_no_state_crosses_the_sequence(b, l, h, g, n):
+    """Only y is used (no initial state, final state unused): the autograd Function routes to the fused chunk backward; every
+    gradient against fp64 autograd through the token recurrence."""
+    x, dt, A, B, C, D = _inputs(b, l, h, g, n, seed=5 * l + n)
+    leaves = [t.detach().clone().requires_grad_(True) for t in (x, dt, A, B, C, D)]
+    y = ssd_chunk_scan_cuda(*leaves[:5], D=leaves[5])
+    gy = torch.randn_like(y)
+    got = torch.autograd.grad(y, leaves, gy)
+    torch.cuda.synchronize()
+    assert ops.ext().kernel_status(x) == 0
+    ref_leaves = [t.detach().double().requires_grad_(True) for t in leaves]
+    ry, _ = ssd_recurrent_reference(*ref_leaves[:5], D=ref_leaves[5], initial_state=None)
+    want = torch.autograd.grad(ry, ref_leaves, gy.double())
+    for name, a_, w_ in zip(("dx", "ddt", "dA", "dB", "dC", "dD"), got, want):
+        err = (a_.double() - w_).norm().item() / max(w_.norm().item(), 1e-12)
+        assert err <= 3e-2, f"{name}: relative error {err:.3e}"
+
+
 @pytest.mark.parametrize("b,l,h,g", [(1, 128, 2, 1), (2, 320, 4, 2), (1, 1024, 4, 1)])
 def test_siso_kernels_match_recurrence(b, l, h, g):
     from lbi_b200.backbones.mamba3.siso import mamba3_siso_chunked, mamba3_siso_recurrent_reference
