@@ -419,10 +419,18 @@ class _SISOFunction(torch.autograd.Function):
                     theta.detach().contiguous(), gamma.detach().contiguous(), scale.detach().contiguous())
             Qr, Kr, qk_dot = ext().siso_prep_fwd(*wide)
             skip = qk_dot + D.float()[None, None]
-            dQr, dKr_rev, dadt, dskip, dV = siso_core_backward(Qr, Kr, adt.detach(), skip, V, gy, fwd_states=states,
-                                                               keep_dkr_reversed=True)
-            gQ, gK, gQb, gKb, dtheta, dgamma, dscale = ext().siso_prep_bwd(*wide, dQr.float().contiguous(), dKr_rev.float().contiguous(),
-                                                                            dskip.float().contiguous(), True)
+            if chunk_backward_supported(V) and V.dtype == torch.bfloat16:
+                # the fused chunk backward: every cotangent of the recurrence from one kernel per chunk and head, in natural
+                # time order and bf16, as the preprocessing backward reads them
+                dV, dQr, dKr, dadt, dskip = chunk_backward(V, gy, Kr, Qr, adt.detach(), None, skip, states, per_head=True, strict=True,
+                                                           dv_bf16=True, dn_bf16=True)
+                gQ, gK, gQb, gKb, dtheta, dgamma, dscale = ext().siso_prep_bwd(*wide, dQr.contiguous(), dKr.contiguous(),
+                                                                                dskip.float().contiguous(), False)
+            else:
+                dQr, dKr_rev, dadt, dskip, dV = siso_core_backward(Qr, Kr, adt.detach(), skip, V, gy, fwd_states=states,
+                                                                   keep_dkr_reversed=True)
+                gQ, gK, gQb, gKb, dtheta, dgamma, dscale = ext().siso_prep_bwd(*wide, dQr.float().contiguous(),
+                                                                                dKr_rev.float().contiguous(), dskip.float().contiguous(), True)
             KERNEL_LAUNCHES["count"] += 2
             gADT, gDT, gTrap, gAng = torch.autograd.grad([adt, theta, gamma, scale], small, [dadt, dtheta, dgamma, dscale],
                                                          allow_unused=True)
