@@ -1,14 +1,18 @@
-"""Mamba-2 SSD chunk scan: CUDA forward and backward (csrc/ssd.cu) behind a differentiable wrapper.
+"""Mamba-2 SSD chunk scan and Mamba-3 SISO recurrence: CUDA forward and backward (csrc/ssd.cu) behind differentiable wrappers.
 
-``ssd_chunk_scan_cuda`` runs the four sm_100a kernels (cumsum, chunk state, state passing, fused chunk scan).  The
-backward runs the same kernels three more times with the operand roles permuted (``ssd_backward``): the scan
+``ssd_chunk_scan_cuda`` runs the four sm_100a forward kernels (cumsum, chunk state, state passing, fused chunk scan) of
 
     y_t = sum_{s <= t} exp(c_t - c_s) (cq_t . bk_s) w_s v_s + exp(c_t) cq_t . init
 
-is linear in v, in bk and in cq, and each of the three pullbacks is again a scan of this form, in forward or reversed
-time, so that no separate backward kernels exist.  The gradient of the decay follows from the per-head gradients of B
-and C (``dc_t = C_t . dC_t - B_t . dB_t``).  The reference's counterpart is the Triton pipeline
-``mamba_chunk_scan_combined`` with its ten backward kernels (backbones/mamba2/ops/triton/ssd_combined.py:343-513).
+Two backward forms exist.  ``ssd_backward_fused`` / ``chunk_backward``: one kernel walks the chunks backwards for the
+cotangents of the chunk-boundary states and one kernel per (direction, chunk, head) emits every input cotangent; the forward
+operands may be shared by P stacked cotangent directions.  It is what the region-parallel engine uses and what the autograd
+Functions take when no state enters or leaves the sequence.  ``ssd_backward`` / ``siso_core_backward``: the scan is linear in
+v, in bk and in cq, and each of the three pullbacks is again a scan of this form in forward or reversed time, so the forward
+kernels run three more times with permuted roles, plus a decay-gradient kernel (the identity ``dc_t = C_t . dC_t - B_t . dB_t``
+cancels badly in bf16); it handles an initial state and a cotangent of the final state and serves as a cross-check
+(``LBI_B200_SSD_PERMUTED_BACKWARD=1``).  The reference's counterpart is the Triton pipeline ``mamba_chunk_scan_combined``
+with its ten backward kernels (backbones/mamba2/ops/triton/ssd_combined.py:343-513).
 """
 from __future__ import annotations
 
