@@ -229,7 +229,7 @@ class StructuredMambaRegion:
         proj = ops.linear_fwd(normed, lw.w_in)
         z, xbc_pre, dt_raw = torch.split(proj, [mx.d_inner, mx.d_inner + 2 * gn, h], dim=-1)
         z, xbc_pre = z.contiguous(), xbc_pre.contiguous()
-        dt, dt_slope = mops.softplus_dt_fwd(dt_raw.reshape(bsz, seqlen, h), mx.dt_bias.detach(), *mx.dt_limit)
+        dt, dt_slope = (t.view(bsz, seqlen, h) for t in mops.softplus_dt_fwd(dt_raw, mx.dt_bias.detach(), *mx.dt_limit))
         conv_w = mx.conv1d.weight.detach().squeeze(1).float().contiguous()
         conv_b = None if mx.conv1d.bias is None else mx.conv1d.bias.detach().float()
         xbc_conv, (x, b_, c_) = mops.conv_silu_fwd(xbc_pre, conv_w, conv_b, bsz, seqlen, (mx.d_inner, gn, gn))

@@ -103,6 +103,10 @@ int lbi_gate_silu_fwd(const void* y, const void* z, void* out, int64_t numel, cu
 // dyg, dy, dz [reps * numel] bf16; y, z [numel] shared by the reps stacked directions.
 int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, void* dy, void* dz, int64_t numel, int reps,
                       cudaStream_t stream);
+// Mamba-2 step size: dt = clamp(softplus(dt_raw + bias), lo, hi) and its slope (0 outside the limits), fp32 [rows, heads];
+// dt_raw [rows, heads] bf16 or fp32 with row stride ld (elements).
+int lbi_softplus_dt(const void* dt_raw, int64_t ld, int is_bf16, const float* bias, float lo, float hi, float* dt, float* slope,
+                    int64_t rows, int heads, cudaStream_t stream);
 // Mamba-3 per-token, per-head scalars.  dd_dt, dd_a, trap [B * L, H], angles [B * L, S], dt_bias [H] (fp32) ->
 // dt, a, sig, adt, gamma, scale, sp_dt, sp_a, live [B, L, H]; tanh_a [B, L, S]; theta [B, L, H, S] in [0, 2 pi).  S <= 64,
 // H <= 32.  Scratch: seg_inc [B, lbi_siso_small_fwd_segments(L), H, 64] fp32 (phase increments summed per segment of the

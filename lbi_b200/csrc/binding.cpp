@@ -469,6 +469,22 @@ std::vector<Tensor> siso_small_fwd(const Tensor& dd_dt, const Tensor& dd_a, cons
   return out;
 }
 
+// dt_raw [rows, heads] (bf16 / fp32, unit column stride, any row stride), bias [heads] -> (dt, slope) fp32 [rows, heads]
+std::tuple<Tensor, Tensor> softplus_dt(const Tensor& dt_raw, const Tensor& bias, double lo, double hi) {
+  CHECK_F32(bias);
+  TORCH_CHECK(dt_raw.is_cuda() && dt_raw.dim() == 2 && dt_raw.stride(1) == 1 && dt_raw.stride(0) >= dt_raw.size(1) &&
+                  (dt_raw.scalar_type() == at::kBFloat16 || dt_raw.scalar_type() == at::kFloat) && bias.numel() == dt_raw.size(1),
+              "softplus_dt: dt_raw [rows, heads] bf16 / fp32 with unit column stride, bias [heads]");
+  c10::cuda::CUDAGuard guard(dt_raw.device());
+  auto f32 = dt_raw.options().dtype(at::kFloat);
+  Tensor dt = torch::empty({dt_raw.size(0), dt_raw.size(1)}, f32), slope = torch::empty_like(dt);
+  check(lbi_softplus_dt(dt_raw.data_ptr(), dt_raw.stride(0), dt_raw.scalar_type() == at::kBFloat16 ? 1 : 0, bias.data_ptr<float>(),
+                        (float)lo, (float)hi, dt.data_ptr<float>(), slope.data_ptr<float>(), dt_raw.size(0), (int)dt_raw.size(1),
+                        cur_stream()),
+        "softplus_dt");
+  return {dt, slope};
+}
+
 // -> (d_dd_dt, d_dd_a, d_trap [P * B * L, H], d_angles [P * B * L, S]) in fp32 or bf16
 std::vector<Tensor> siso_small_bwd(const Tensor& dt, const Tensor& a, const Tensor& sig, const Tensor& tanh_a, const Tensor& sp_dt,
                                    const Tensor& sp_a, const Tensor& live, const Tensor& dadt, const Tensor& dtheta,
@@ -1238,6 +1254,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("causal_conv_wgrad", &causal_conv_wgrad);
   m.def("gate_silu_fwd", &gate_silu_fwd);
   m.def("gate_silu_bwd", &gate_silu_bwd);
+  m.def("softplus_dt", &softplus_dt);
   m.def("siso_small_fwd", &siso_small_fwd);
   m.def("siso_small_bwd", &siso_small_bwd);
   m.def("gated_rmsnorm_fwd", &gated_rmsnorm_fwd);

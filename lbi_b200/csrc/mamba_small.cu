@@ -59,6 +59,24 @@ __global__ void gate_silu_bwd_kernel(const bf16x8* __restrict__ dyg, const bf16x
   }
 }
 
+// ------------------------------------------------------------------------------------------------ Mamba-2 step size
+// dt = clamp(softplus(dt_raw + bias), lo, hi), slope = d dt / d dt_raw = sigmoid(dt_raw + bias) inside the limits, 0 outside.
+// dt_raw [rows, heads] with a row stride (a column range of the in_proj output), bf16 or fp32; outputs fp32, contiguous.
+template <typename T>
+__global__ void softplus_dt_kernel(const T* __restrict__ dt_raw, int64_t ld, const float* __restrict__ bias, float lo, float hi,
+                                   float* __restrict__ dt, float* __restrict__ slope, int64_t rows, int heads) {
+  const int64_t total = rows * heads;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / heads;
+    const int h = (int)(i - r * heads);
+    const float pre = (float)dt_raw[r * ld + h] + bias[h];
+    const float v = softplus_(pre);
+    const bool inside = v >= lo && v <= hi;
+    dt[i] = fminf(fmaxf(v, lo), hi);
+    slope[i] = inside ? sigmoidf_(pre) : 0.f;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ siso small, forward
 // The running rotary phase is the only dependency along the sequence: the sequence is cut into segments of FSEG tokens, a first
 // kernel sums the phase increments pi tanh(angle) DT per (sequence, segment, head, angle), and a block of the second kernel
@@ -365,6 +383,20 @@ extern "C" int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, 
   const int blocks = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
   msmall::gate_silu_bwd_kernel<<<blocks, 256, 0, st>>>((const bf16x8*)dyg, (const bf16x8*)y, (const bf16x8*)z, (bf16x8*)dy,
                                                        (bf16x8*)dz, n8, reps);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int lbi_softplus_dt(const void* dt_raw, int64_t ld, int is_bf16, const float* bias, float lo, float hi, float* dt,
+                               float* slope, int64_t rows, int heads, cudaStream_t st) {
+  using namespace lbi;
+  if (rows <= 0 || heads <= 0) return 0;
+  if (ld < heads) return (int)cudaErrorInvalidValue;
+  const int64_t total = rows * heads;
+  const int blocks = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
+  if (is_bf16)
+    msmall::softplus_dt_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)dt_raw, ld, bias, lo, hi, dt, slope, rows, heads);
+  else
+    msmall::softplus_dt_kernel<float><<<blocks, 256, 0, st>>>((const float*)dt_raw, ld, bias, lo, hi, dt, slope, rows, heads);
   return (int)cudaGetLastError();
 }
 

@@ -28,6 +28,13 @@ def _count(n: int = 1) -> None:
     KERNEL_LAUNCHES["count"] += n
 
 
+def _fell_back(op: str, *values) -> None:
+    """Count (strict mode: refuse) a PyTorch route taken by CUDA bf16 operands; see ``ops.dispatch.fell_back``."""
+    from .dispatch import fell_back
+
+    fell_back(op, *values)
+
+
 def _kernel_ok(*tensors, name: str | None = None) -> bool:
     if not native_available() or (name is not None and not hasattr(ext(), name)):
         return False
@@ -46,6 +53,7 @@ def gate_silu_fwd(y: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
     if _kernel_ok(y, z, name="gate_silu_fwd") and y.dtype == torch.bfloat16 and z.dtype == torch.bfloat16 and y.shape[-1] % 8 == 0:
         _count()
         return ext().gate_silu_fwd(y.contiguous(), z.contiguous())
+    _fell_back("gate_silu_fwd", y, z)
     return (y.float() * F.silu(z.float())).to(y.dtype)
 
 
@@ -55,6 +63,7 @@ def gate_silu_bwd(dyg: torch.Tensor, y: torch.Tensor, z: torch.Tensor):
             and z.dtype == torch.bfloat16 and y.shape[-1] % 8 == 0):
         _count()
         return ext().gate_silu_bwd(dyg.contiguous(), y.contiguous(), z.contiguous())
+    _fell_back("gate_silu_bwd", dyg, y, z)
     reps = dyg.shape[0] // y.shape[0]
     g = dyg.float().view(reps, *y.shape)
     zf, yf = z.float(), y.float()
@@ -73,6 +82,7 @@ def gated_rmsnorm_fwd(x, z, weight, eps: float, group: int, gate_first: bool):
         _count()
         return ext().gated_rmsnorm_fwd(x.contiguous(), None if z is None else z.to(x.dtype).contiguous(), weight.float().contiguous(),
                                        float(eps), int(group), bool(gate_first))
+    _fell_back("gated_rmsnorm_fwd", x, z)
     xf = x.float()
     if z is not None and gate_first:
         xf = xf * F.silu(z.float())
@@ -94,6 +104,7 @@ def gated_rmsnorm_bwd(dy, x, z, weight, rstd, group: int, gate_first: bool, want
                                              weight.float().contiguous(), rstd.contiguous(), int(group), bool(gate_first),
                                              bool(want_dweight))
         return dx, (dz if z is not None else None), (dw if want_dweight else None)
+    _fell_back("gated_rmsnorm_bwd", dy, x, z)
     w = weight.float()
     g = dy.float().view(reps, *x.shape)
     xf = x.float()
@@ -142,11 +153,12 @@ def siso_small_fwd(dd_dt, dd_a, trap, angles, dt_bias, a_floor: float, batch: in
     gamma = DT sigmoid(trap), scale_t = gamma_t + DT_{t+1} (1 - sigmoid(trap_{t+1})) (0 past the last token of a sequence),
     theta_t = (sum_{i <= t} pi tanh(angle_i) DT_i) mod 2 pi."""
     h, s = dd_dt.shape[-1], angles.shape[-1]
-    if _kernel_ok(dd_dt, dd_a, trap, angles, dt_bias, name="siso_small_fwd"):
-        _count()
+    if _kernel_ok(dd_dt, dd_a, trap, angles, dt_bias, name="siso_small_fwd") and h <= 32 and s <= 64:
+        _count(2)   # segment totals + the walk over the segments
         out = ext().siso_small_fwd(dd_dt.float().contiguous(), dd_a.float().contiguous(), trap.float().contiguous(),
                                    angles.float().contiguous(), dt_bias.float().contiguous(), float(a_floor), int(batch), int(seq_len))
         return SisoSmall(*out)
+    _fell_back("siso_small_fwd", dd_dt, dd_a, trap, angles)
     pre = dd_dt.float().view(batch, seq_len, h) + dt_bias.float()
     dt = F.softplus(pre)
     raw_a = -F.softplus(dd_a.float().view(batch, seq_len, h))
@@ -169,8 +181,8 @@ def siso_small_bwd(small: SisoSmall, dadt, dtheta, dgamma, dscale, out_dtype=tor
     b, l, h = small.dt.shape
     s = small.tanh_angle.shape[-1]
     reps = dadt.shape[0] // b
-    if _kernel_ok(dadt, dtheta, dgamma, dscale, small.dt, name="siso_small_bwd"):
-        _count()
+    if _kernel_ok(dadt, dtheta, dgamma, dscale, small.dt, name="siso_small_bwd") and h <= 32 and s <= 32:
+        _count(2)   # segment totals + the walk over the segments
         return ext().siso_small_bwd(small.dt, small.a, small.sig, small.tanh_angle, small.sp_dt, small.sp_a, small.a_live,
                                     dadt.float().contiguous(), dtheta.float().contiguous(), dgamma.float().contiguous(),
                                     dscale.float().contiguous(), out_dtype == torch.bfloat16)
@@ -207,6 +219,7 @@ def siso_wide_fwd(q, k, q_bias, k_bias, theta, gamma, scale):
         _count()
         return ext().siso_prep_fwd(q.contiguous(), k.to(q.dtype).contiguous(), q_bias.float().contiguous(), k_bias.float().contiguous(),
                                    theta.float().contiguous(), gamma.float().contiguous(), scale.float().contiguous())
+    _fell_back("siso_wide_fwd", q, k)
     h = q_bias.shape[0]
     rep = h // q.shape[2]
     qh = q.float().repeat_interleave(rep, dim=2) + q_bias.float()
@@ -232,6 +245,7 @@ def siso_wide_bwd(q, k, q_bias, k_bias, theta, gamma, scale, dqr, dkr, dqk, dkr_
         if not want_bias:
             out[2] = out[3] = None
         return tuple(out)
+    _fell_back("siso_wide_bwd", q, k, dqr, dkr)
     if dkr_reversed:
         dkr = dkr.flip(1)[:, :l]
     h, n = q_bias.shape
@@ -279,6 +293,7 @@ def siso_scan_fwd(v, kr, qr, adt, skip, d_skip):
                                                  sk.transpose(1, 2).contiguous(), None)
         _count(4)
         return y[:, :l], states
+    _fell_back("siso_scan_fwd", v, kr, qr)
     y, _ = ssd.scan_generic_torch(v, kr, qr, adt, None, None, strict=True, per_head=True)
     total_skip = skip.float() if d_skip is None else skip.float() + d_skip.float()
     return (y + total_skip.unsqueeze(-1) * v.float()).to(v.dtype), None
@@ -300,12 +315,22 @@ def siso_scan_bwd(qr, kr, adt, skip_total, v, gy, states):
             out = ssd.siso_core_backward(tile(qr), tile(kr), tile(adt), tile(skip_total), tile(v), gy, ops=ssd.KernelScans,
                                          fwd_states=tile(states), keep_dkr_reversed=True)
             return (*out, True)
+    _fell_back("siso_scan_bwd", v, gy, qr, kr)
     return (*ssd.siso_core_backward_dense(qr, kr, adt, skip_total, v, gy), False)
 
 
 # ---------------------------------------------------------------- Mamba-2: softplus of dt, SiLU of the conv output
 def softplus_dt_fwd(dt_raw, dt_bias, lo: float, hi: float):
-    """-> (dt [n, h] fp32, d dt / d dt_raw [n, h] fp32)."""
+    """-> (dt fp32 like dt_raw, d dt / d dt_raw fp32).  dt_raw may be a column range of a wider matrix (last stride 1)."""
+    if _kernel_ok(dt_raw, dt_bias, name="softplus_dt") and dt_raw.dtype in (torch.bfloat16, torch.float32):
+        flat = dt_raw if dt_raw.dim() == 2 else dt_raw.reshape(-1, dt_raw.shape[-1])
+        if flat.stride(-1) == 1:
+            _count()
+            dt, slope = ext().softplus_dt(flat, dt_bias.float().contiguous(), float(lo), float(hi))
+            return dt.view(dt_raw.shape), slope.view(dt_raw.shape)
+    from .dispatch import fell_back
+
+    fell_back("softplus_dt_fwd", dt_raw)
     pre = dt_raw.float() + dt_bias.float()
     dt = F.softplus(pre)
     slope = torch.sigmoid(pre)

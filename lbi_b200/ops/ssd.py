@@ -496,7 +496,7 @@ def chunk_backward(v, gy, bk, cq, a, weight, skip, states_in, *, per_head: bool,
         af = F.pad(af, (0, 0, 0, pad))
         wf = None if wf is None else F.pad(wf, (0, 0, 0, pad))
         sf = None if sf is None else F.pad(sf, (0, 0, 0, pad))
-    KERNEL_LAUNCHES["count"] += 4
+    KERNEL_LAUNCHES["count"] += 3   # cumulative sum, reversed state passing with its chunk products, chunk backward
     dv, dcq, dbk, da, dskip = ext().ssd_chunk_bwd(vb.contiguous(), gyb.contiguous(), bkb.contiguous(), cqb.contiguous(), af.contiguous(),
                                                   None if wf is None else wf.contiguous(), None if sf is None else sf.contiguous(),
                                                   None, states_in, bool(per_head), bool(strict), bool(dv_bf16), bool(dn_bf16))

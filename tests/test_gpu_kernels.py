@@ -259,6 +259,25 @@ def test_wide_group_gated_rmsnorm_backward_matches_the_pytorch_form(dim, gate_fi
             assert err <= 1e-2, f"{name}: {err:.2e}"
 
 
+def test_softplus_dt_kernel_matches_pytorch_on_a_strided_slice():
+    """The Mamba-2 step size from a column range of a wider bf16 matrix (no copy), with and without the limits."""
+    from lbi_b200.ops import mamba as mops
+
+    torch.manual_seed(7)
+    proj = (torch.randn(333, 200, device=DEV) * 2).bfloat16()
+    raw = proj[:, 152:]                                  # 48 heads, row stride 200
+    bias = torch.randn(48, device=DEV)
+    for lo, hi in ((0.0, float("inf")), (0.05, 1.5)):
+        before = ops.dispatch.KERNEL_LAUNCHES["count"]
+        dt, slope = mops.softplus_dt_fwd(raw, bias, lo, hi)
+        assert ops.dispatch.KERNEL_LAUNCHES["count"] == before + 1
+        want_dt, want_slope = mops.softplus_dt_fwd(raw.float().cpu(), bias.cpu(), lo, hi)
+        _close(dt.cpu(), want_dt, 1e-5, 1e-5, "dt")
+        raw_dt = torch.nn.functional.softplus(raw.float().cpu() + bias.cpu())
+        clear = ((raw_dt - lo).abs() > 1e-4) & ((raw_dt - hi).abs() > 1e-4)      # a value on a limit may fall on either side
+        _close(slope.cpu()[clear], want_slope[clear], 1e-5, 1e-5, "slope")
+
+
 def test_mamba2_conv_silu_kernels_match_pytorch():
     """Depthwise causal conv + SiLU over the x | B | C slice: forward (split outputs), input cotangent for stacked directions
     written into a column range of a wider buffer, and the weight / bias gradient."""
