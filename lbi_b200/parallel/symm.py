@@ -197,28 +197,6 @@ class SymmComm(CollectiveComm):
         ops.dispatch.KERNEL_LAUNCHES["count"] += 2
         return g
 
-    def scan_partial_sums(self, rows_all: torch.Tensor, offs_all: torch.Tensor) -> torch.Tensor:
-        """Basis-parallel scan: rows_all [K, B, R, R] and offs_all [K, B, R] hold this rank's share of the work (zeros
-        elsewhere); the sum over ranks happens inside the scan kernel's peer loads.  Returns g [B, K, R] on every rank."""
-        key = ("partial", tuple(rows_all.shape))
-        hit = self._scan_bufs.get(key)
-        if hit is None:
-            m_buf, mh = self._alloc(rows_all.numel(), torch.float32)
-            o_buf, oh = self._alloc(offs_all.numel(), torch.float32)
-            hit = (m_buf, o_buf, self._table(mh), self._table(oh), mh, oh)
-            self._scan_bufs[key] = hit
-            self._setup_barrier()
-        m_buf, o_buf, m_ptrs, o_ptrs, _, _ = hit
-        m_buf.copy_(rows_all.reshape(-1))
-        o_buf.copy_(offs_all.reshape(-1))
-        self.seq += 1
-        w = self.world_size
-        ops.ext().peer_signal_all(self.flag_ptrs, self.rank, w, _SLOT_SCAN * w, self.seq)
-        k_total, bsz, r = rows_all.shape[0], rows_all.shape[1], rows_all.shape[-1]
-        g = ops.ext().affine_scan_peer_sum(m_ptrs, o_ptrs, self.flags, _SLOT_SCAN * w, self.seq, bsz, w, k_total, r)
-        ops.dispatch.KERNEL_LAUNCHES["count"] += 2
-        return g
-
     def scan_published(self, rows_all: torch.Tensor, offs_all: torch.Tensor, row_blocks, off_regions):
         """Basis-parallel scan, gather form.  rows_all [K, B, R, R] / offs_all [K, B, R] hold this rank's results in the
         blocks ``row_blocks`` = [(region, lo, hi)] of basis directions and the offsets of ``off_regions``; one kernel stores
