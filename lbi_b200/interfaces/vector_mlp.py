@@ -73,7 +73,8 @@ def _jac_kernels(*tensors: torch.Tensor) -> bool:
 
 
 def _activation_diagonal(head: VectorMLPHead, first: nn.Linear, x: torch.Tensor) -> torch.Tensor:
-    pre = F.linear(x.float(), first.weight, first.bias)
+    # the pre-activation through the skinny fp32 kernel where it applies (no library GEMM on the engine's path)
+    pre = _linear_forward(x.float(), first, None, False)[0]
     return activation_derivative(pre, head.activation).contiguous()
 
 

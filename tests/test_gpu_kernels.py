@@ -196,7 +196,8 @@ def test_interface_jacobian_kernels_match_the_einsum_forms(hidden, activation):
     with torch.no_grad():
         jt_g, j_t = vm.head_input_jacobian_t(head, x, g), vm.head_input_jacobian(head, x, t)
         ln_t, ln_f = vm.layer_norm_input_jacobian_t(norm, s, g), vm.layer_norm_input_jacobian(norm, s, g)
-    assert ops.dispatch.KERNEL_LAUNCHES["count"] == before + 4, "the Jacobian kernels did not run"
+    # with a hidden layer each head Jacobian also runs the skinny forward kernel for the activation slope
+    assert ops.dispatch.KERNEL_LAUNCHES["count"] == before + 4 + (2 if hidden else 0), "the Jacobian kernels did not run"
     gg, tt = g.clone().requires_grad_(True), t.clone().requires_grad_(True)      # graph attached -> PyTorch forms
     _close(jt_g, vm.head_input_jacobian_t(head, x, gg).detach(), 1e-4, 1e-4, "head J^T")
     _close(j_t, vm.head_input_jacobian(head, x, tt).detach(), 1e-4, 1e-4, "head J")
