@@ -183,15 +183,24 @@ class StructuredMambaRegion:
         if grads is not None:
             _wgrad(grads, prefix + "mixer.out_proj.weight", d_branch, lc.y_in)
         d_yin = ops.linear_dgrad(d_branch, lw.w_out)
+        # the in_proj cotangent [z | x | B | C | dd_dt | dd_A | trap | angles]: the two wide parts are written into their column
+        # ranges by the kernels that produce them, the narrow ones are copied in
+        widths = [mx.d_inner, mx.d_inner, g * ns, g * ns, h, h, h, lc.small.tanh_angle.shape[-1]]
+        offs = [0]
+        for wdt in widths:
+            offs.append(offs[-1] + wdt)
+        d_proj = torch.empty(rows, offs[-1], device=d_branch.device, dtype=dtype)
+        part = lambda i: d_proj[:, offs[i] : offs[i + 1]]  # noqa: E731
         if mx.is_outproj_norm:
             d_y, d_z, dw = mops.gated_rmsnorm_bwd(d_yin, lc.y, lc.z, mx.norm.weight.detach(), lc.norm_rstd, p, False,
                                                   want_dweight=grads is not None)
+            part(0).copy_(d_z)
             if grads is not None:
                 _acc(grads, prefix + "mixer.norm.weight", dw)
         else:
-            d_y, d_z = mops.gate_silu_bwd(d_yin, lc.y, lc.z)
-        d_qr, d_kr, d_adt, d_skip, d_v, reversed_dkr = mops.siso_scan_bwd(lc.qr, lc.kr, lc.small.adt, lc.skip, lc.x.view(bsz, seqlen, h, p),
-                                                                          d_y.view(pb, seqlen, h, p), lc.states)
+            d_y, _ = mops.gate_silu_bwd(d_yin, lc.y, lc.z, dz_out=part(0))
+        d_qr, d_kr, d_adt, d_skip, _, reversed_dkr = mops.siso_scan_bwd(lc.qr, lc.kr, lc.small.adt, lc.skip, lc.x.view(bsz, seqlen, h, p),
+                                                                        d_y.view(pb, seqlen, h, p), lc.states, dv_out=part(1))
         d_c, d_b, d_cb, d_bb, d_theta, d_gamma, d_scale = mops.siso_wide_bwd(
             lc.c_normed, lc.b_normed, mx.C_bias.detach().squeeze(1), mx.B_bias.detach().squeeze(1), lc.small.theta, lc.small.gamma,
             lc.small.scale, d_qr, d_kr, d_skip, dkr_reversed=reversed_dkr, want_bias=grads is not None)
@@ -208,9 +217,8 @@ class StructuredMambaRegion:
             _acc(grads, prefix + "mixer.C_bias", d_cb.unsqueeze(1))
             _acc(grads, prefix + "mixer.D", d_skip.float().sum((0, 1)))
             _acc(grads, prefix + "mixer.dt_bias", d_dd_dt.float().sum(0))
-        d_proj = torch.cat([d_z.to(dtype), d_v.reshape(rows, mx.d_inner).to(dtype), d_braw.reshape(rows, g * ns).to(dtype),
-                            d_craw.reshape(rows, g * ns).to(dtype), d_dd_dt.to(dtype), d_dd_a.to(dtype), d_trap.to(dtype),
-                            d_angles.to(dtype)], dim=-1)
+        for i, t in enumerate((d_braw.reshape(rows, g * ns), d_craw.reshape(rows, g * ns), d_dd_dt, d_dd_a, d_trap, d_angles), start=2):
+            part(i).copy_(t)
         if grads is not None:
             _wgrad(grads, prefix + "mixer.in_proj.weight", d_proj, lc.normed)
         d_normed = ops.linear_dgrad(d_proj, lw.w_in)

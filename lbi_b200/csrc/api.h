@@ -100,9 +100,10 @@ int lbi_siso_prep_bwd(const void* q, const void* k, const float* q_bias, const f
 // ---- Mamba block glue on the small tensors (mamba_small.cu) ------------------------------------------------
 // out = y * silu(z); bf16, numel a multiple of 8.
 int lbi_gate_silu_fwd(const void* y, const void* z, void* out, int64_t numel, cudaStream_t stream);
-// dyg, dy, dz [reps * numel] bf16; y, z [numel] shared by the reps stacked directions.
-int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, void* dy, void* dz, int64_t numel, int reps,
-                      cudaStream_t stream);
+// dyg, dy [reps * numel] bf16; y, z [numel] = [rows, cols] shared by the reps stacked directions; dz [reps * rows, cols] with
+// row stride ld_dz elements (a column range of a wider matrix; ld_dz = cols when contiguous).  cols, ld_dz multiples of 8.
+int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, void* dy, void* dz, int64_t numel, int reps, int cols,
+                      int64_t ld_dz, cudaStream_t stream);
 // Mamba-2 step size: dt = clamp(softplus(dt_raw + bias), lo, hi) and its slope (0 outside the limits), fp32 [rows, heads];
 // dt_raw [rows, heads] bf16 or fp32 with row stride ld (elements).
 int lbi_softplus_dt(const void* dt_raw, int64_t ld, int is_bf16, const float* bias, float lo, float hi, float* dt, float* slope,

@@ -68,12 +68,13 @@ int lbi_ssd_bwd_finish(const void* dx_rev, int dx_is_bf16, const void* x, const 
 // fp32, layout of the states) may be null.  Scratch: d_out [B, L/128, H, 64*N] bf16 (cotangents of the chunk-boundary states);
 // chunk_cot is unused (kept for callers of the earlier three-kernel form) and may be null.
 // Results: d_init (or null), da, dskip (or null) [B, H, L]; dv [B*L, H*64] in dv32 or dv16 (cotangent of w_s v_s, plus
-// (d_skip[h] + skip_tok) * gy when given); dcq, dbk [B*L, H*N] per head in fp32 or bf16.  Two kernels on `stream`.
+// (d_skip[h] + skip_tok) * gy when given); dcq, dbk [B*L, H*N] per head in fp32 or bf16.  dv_ld: row stride of dv16 in elements
+// (a column range of a wider matrix; a multiple of 8; 0 = contiguous).  Two kernels on `stream`.
 int lbi_ssd_chunk_bwd(const void* v, const void* gy, const void* bk, const void* cq, const float* weight, const float* cum,
                       const float* skip_tok, const float* d_skip, const void* state_in, const float* d_final, float* chunk_cot,
                       void* d_out, float* d_init, float* da, float* dskip, float* dv32, void* dv16, float* dcq32, float* dbk32,
                       void* dcq16, void* dbk16, int batch, int bmod, int seq_len, int heads, int groups, int d_state, int per_head,
-                      int strict, int* status, cudaStream_t stream);
+                      int strict, int64_t dv_ld, int* status, cudaStream_t stream);
 // out[b, l, g, :n] = sum over the heads h of group g of w[b, l, h] * y[b, l or seq_pad - 1 - l, h, :n]; y bf16 with rows of
 // `width` columns, w [B, L, H] or null, out bf16 or fp32.
 int lbi_ssd_group_sum(const void* y_bf16, const float* w, void* out, int batch, int seq_len, int seq_pad, int heads, int groups,

@@ -425,16 +425,30 @@ Tensor gate_silu_fwd(const Tensor& y, const Tensor& z) {
   return out;
 }
 
-std::tuple<Tensor, Tensor> gate_silu_bwd(const Tensor& dyg, const Tensor& y, const Tensor& z) {
+// dz_out: optional [reps * rows, cols] bf16 view with unit column stride and any row stride (a column range of a wider
+// cotangent matrix); dz is written there instead of into a fresh tensor.
+std::tuple<Tensor, Tensor> gate_silu_bwd(const Tensor& dyg, const Tensor& y, const Tensor& z, const c10::optional<Tensor>& dz_out) {
   CHECK_BF16(dyg);
   CHECK_BF16(y);
   CHECK_BF16(z);
-  TORCH_CHECK(z.sizes() == y.sizes() && y.numel() % 8 == 0 && y.numel() > 0 && dyg.numel() % y.numel() == 0,
-              "gate_silu_bwd: dyg must hold a whole number of copies of y's shape");
+  TORCH_CHECK(z.sizes() == y.sizes() && y.dim() == 2 && y.size(1) % 8 == 0 && y.numel() > 0 && dyg.numel() % y.numel() == 0,
+              "gate_silu_bwd: y, z [rows, cols] with cols % 8 == 0; dyg must hold a whole number of copies of y's shape");
   c10::cuda::CUDAGuard guard(y.device());
-  Tensor dy = torch::empty_like(dyg), dz = torch::empty_like(dyg);
-  check(lbi_gate_silu_bwd(dyg.data_ptr(), y.data_ptr(), z.data_ptr(), dy.data_ptr(), dz.data_ptr(), y.numel(),
-                          (int)(dyg.numel() / y.numel()), cur_stream()),
+  const int64_t reps = dyg.numel() / y.numel(), cols = y.size(1);
+  Tensor dy = torch::empty_like(dyg);
+  Tensor dz;
+  int64_t ld = cols;
+  if (dz_out.has_value() && dz_out->defined()) {
+    dz = *dz_out;
+    TORCH_CHECK(dz.is_cuda() && dz.scalar_type() == at::kBFloat16 && dz.dim() == 2 && dz.size(0) == reps * y.size(0) && dz.size(1) == cols &&
+                    dz.stride(1) == 1 && dz.stride(0) % 8 == 0 && dz.stride(0) >= cols && dz.storage_offset() % 8 == 0,
+                "gate_silu_bwd: dz_out must be [reps * rows, cols] bf16, unit column stride, row stride and offset multiples of 8");
+    ld = dz.stride(0);
+  } else {
+    dz = torch::empty_like(dyg);
+  }
+  check(lbi_gate_silu_bwd(dyg.data_ptr(), y.data_ptr(), z.data_ptr(), dy.data_ptr(), dz.data_ptr(), y.numel(), (int)reps, (int)cols, ld,
+                          cur_stream()),
         "gate_silu_bwd");
   return {dy, dz};
 }
@@ -953,7 +967,9 @@ Tensor ssd_decay_grad(const Tensor& v, const Tensor& gy, const Tensor& bk, const
 std::vector<Tensor> ssd_chunk_bwd(const Tensor& v, const Tensor& gy, const Tensor& bk, const Tensor& cq, const Tensor& a,
                                   const c10::optional<Tensor>& weight, const c10::optional<Tensor>& skip_tok,
                                   const c10::optional<Tensor>& d_skip, const Tensor& state_in, bool per_head, bool strict,
-                                  bool dv_bf16, bool dn_bf16) {
+                                  bool dv_bf16, bool dn_bf16, const c10::optional<Tensor>& dv_out) {
+  // dv_out: optional [B * L, H * 64] bf16 view with unit column stride and any row stride (a column range of a wider cotangent
+  // matrix); with dv_bf16 the kernel's TMA stores write dv there instead of into a fresh tensor
   CHECK_BF16(v);
   CHECK_BF16(gy);
   CHECK_BF16(bk);
@@ -986,7 +1002,18 @@ std::vector<Tensor> ssd_chunk_bwd(const Tensor& v, const Tensor& gy, const Tenso
   if (d_skip) CHECK_F32((*d_skip));
   Tensor d_out = torch::empty({batch, chunks, heads, hd * n}, v.options());
   Tensor da = torch::empty({batch, heads, seq}, f32), dskip = torch::empty({batch, heads, seq}, f32);
-  Tensor dv = torch::empty({batch, seq, heads, hd}, dv_bf16 ? v.options() : f32);
+  Tensor dv;
+  int64_t dv_ld = 0;
+  if (dv_out.has_value() && dv_out->defined()) {
+    dv = *dv_out;
+    TORCH_CHECK(dv_bf16 && dv.is_cuda() && dv.scalar_type() == at::kBFloat16 && dv.dim() == 2 && dv.size(0) == batch * seq &&
+                    dv.size(1) == heads * hd && dv.stride(1) == 1 && dv.stride(0) % 8 == 0 && dv.stride(0) >= heads * hd &&
+                    dv.storage_offset() % 8 == 0,
+                "chunk_bwd: dv_out must be [B * L, H * 64] bf16, unit column stride, row stride and offset multiples of 8");
+    dv_ld = dv.stride(0);
+  } else {
+    dv = torch::empty({batch, seq, heads, hd}, dv_bf16 ? v.options() : f32);
+  }
   Tensor dcq = torch::empty({batch, seq, heads, n}, dn_bf16 ? v.options() : f32), dbk = torch::empty_like(dcq);
   Tensor st = status_word(v);
   check(lbi_ssd_cumsum(a.data_ptr<float>(), nullptr, ones.data_ptr<float>(), a_t.data_ptr<float>(), cum.data_ptr<float>(), (int)fbatch,
@@ -999,7 +1026,7 @@ std::vector<Tensor> ssd_chunk_bwd(const Tensor& v, const Tensor& gy, const Tenso
                           dv_bf16 ? nullptr : dv.data_ptr<float>(), dv_bf16 ? dv.data_ptr() : nullptr,
                           dn_bf16 ? nullptr : dcq.data_ptr<float>(), dn_bf16 ? nullptr : dbk.data_ptr<float>(),
                           dn_bf16 ? dcq.data_ptr() : nullptr, dn_bf16 ? dbk.data_ptr() : nullptr, (int)batch, (int)fbatch, (int)seq,
-                          (int)heads, (int)groups, (int)n, per_head ? 1 : 0, strict ? 1 : 0, st.data_ptr<int>(), cur_stream()),
+                          (int)heads, (int)groups, (int)n, per_head ? 1 : 0, strict ? 1 : 0, dv_ld, st.data_ptr<int>(), cur_stream()),
         "ssd_chunk_bwd");
   return {dv, dcq, dbk, da.transpose(1, 2), dskip.transpose(1, 2)};
 }
@@ -1253,7 +1280,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("conv_silu_wgrad", &conv_silu_wgrad);
   m.def("causal_conv_wgrad", &causal_conv_wgrad);
   m.def("gate_silu_fwd", &gate_silu_fwd);
-  m.def("gate_silu_bwd", &gate_silu_bwd);
+  m.def("gate_silu_bwd", &gate_silu_bwd, py::arg("dyg"), py::arg("y"), py::arg("z"), py::arg("dz_out") = py::none());
   m.def("softplus_dt", &softplus_dt);
   m.def("siso_small_fwd", &siso_small_fwd);
   m.def("siso_small_bwd", &siso_small_bwd);
@@ -1274,7 +1301,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ssd_decay_grad", &ssd_decay_grad);
   m.def("ssd_bwd_finish", &ssd_bwd_finish, py::arg("dx_rev"), py::arg("x"), py::arg("gy"), py::arg("dt"), py::arg("da"),
         py::arg("a_param"), py::arg("d_skip"), py::arg("reversed") = true);
-  m.def("ssd_chunk_bwd", &ssd_chunk_bwd);
+  m.def("ssd_chunk_bwd", &ssd_chunk_bwd, py::arg("v"), py::arg("gy"), py::arg("bk"), py::arg("cq"), py::arg("a"), py::arg("weight"),
+        py::arg("skip_tok"), py::arg("d_skip"), py::arg("state_in"), py::arg("per_head"), py::arg("strict"), py::arg("dv_bf16"),
+        py::arg("dn_bf16"), py::arg("dv_out") = py::none());
   m.def("ssd_group_sum", &ssd_group_sum);
   m.def("kernel_status", &kernel_status);
   m.def("set_peer_wait_limit_ms", &set_peer_wait_limit_ms);

@@ -34,7 +34,10 @@ __global__ void gate_silu_fwd_kernel(const bf16x8* __restrict__ y, const bf16x8*
 
 // dyg [reps * n8]; y, z [n8] shared by the reps directions.
 __global__ void gate_silu_bwd_kernel(const bf16x8* __restrict__ dyg, const bf16x8* __restrict__ y, const bf16x8* __restrict__ z,
-                                     bf16x8* __restrict__ dy, bf16x8* __restrict__ dz, int64_t n8, int reps) {
+                                     bf16x8* __restrict__ dy, bf16x8* __restrict__ dz, int64_t n8, int reps, int cols8, int64_t ld_dz8) {
+  // dz rows may be strided (a column range of a wider cotangent matrix): row r of direction rep sits at
+  // dz + (rep * rows + r) * ld_dz8 vectors; cols8 = vectors per row; ld_dz8 == cols8 is the contiguous case
+  const int64_t rows = n8 / cols8;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
     float yv[8], zv[8], silu[8], slope[8];
     unpack8(y[i], yv);
@@ -45,6 +48,8 @@ __global__ void gate_silu_bwd_kernel(const bf16x8* __restrict__ dyg, const bf16x
       silu[j] = zv[j] * s;
       slope[j] = yv[j] * s * (1.f + zv[j] * (1.f - s));
     }
+    const int64_t row = i / cols8;
+    const int col = (int)(i - row * cols8);
     for (int r = 0; r < reps; ++r) {
       float g[8], a[8], b[8];
       unpack8(dyg[(int64_t)r * n8 + i], g);
@@ -54,7 +59,7 @@ __global__ void gate_silu_bwd_kernel(const bf16x8* __restrict__ dyg, const bf16x
         b[j] = g[j] * slope[j];
       }
       dy[(int64_t)r * n8 + i] = pack8(a);
-      dz[(int64_t)r * n8 + i] = pack8(b);
+      dz[((int64_t)r * rows + row) * ld_dz8 + col] = pack8(b);
     }
   }
 }
@@ -375,14 +380,14 @@ extern "C" int lbi_gate_silu_fwd(const void* y, const void* z, void* out, int64_
 }
 
 extern "C" int lbi_gate_silu_bwd(const void* dyg, const void* y, const void* z, void* dy, void* dz, int64_t numel, int reps,
-                                 cudaStream_t st) {
+                                 int cols, int64_t ld_dz, cudaStream_t st) {
   using namespace lbi;
   if (numel <= 0 || reps <= 0) return 0;
-  if (numel % 8) return (int)cudaErrorInvalidValue;
+  if (numel % 8 || cols <= 0 || cols % 8 || numel % cols || ld_dz % 8 || ld_dz < cols) return (int)cudaErrorInvalidValue;
   const int64_t n8 = numel / 8;
   const int blocks = (int)((n8 + 255) / 256 < 148 * 16 ? (n8 + 255) / 256 : 148 * 16);
   msmall::gate_silu_bwd_kernel<<<blocks, 256, 0, st>>>((const bf16x8*)dyg, (const bf16x8*)y, (const bf16x8*)z, (bf16x8*)dy,
-                                                       (bf16x8*)dz, n8, reps);
+                                                       (bf16x8*)dz, n8, reps, cols / 8, ld_dz / 8);
   return (int)cudaGetLastError();
 }
 

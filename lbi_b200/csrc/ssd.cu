@@ -1491,11 +1491,12 @@ static EncodeTiledFn encode_fn() {
 }
 
 // [rows, width] bf16 row-major, boxes of box_rows x 64 columns, 128-byte swizzle
-static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t width, int box_rows) {
+// ld: row stride in elements (0: the rows are contiguous, ld = width)
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t width, int box_rows, int64_t ld = 0) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return 801;
   cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)(ld > 0 ? ld : width) * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -1588,7 +1589,7 @@ static int run_bwd(const void* v, const void* gy, const void* bk, const void* cq
                    const float* skip_tok, const float* d_skip, const void* state_in, const float* d_final, float* chunk_cot,
                    void* d_out, float* d_init, float* da, float* dskip, float* dv32, void* dv16, float* dcq32, float* dbk32,
                    void* dcq16, void* dbk16, int batch, int bmod, int seq_len, int heads, int groups, int strict, int* status,
-                   cudaStream_t st) {
+                   cudaStream_t st, int64_t dv_ld = 0) {
   const int chunks = seq_len / L;
   const int64_t rows = (int64_t)batch * seq_len, frows = (int64_t)bmod * seq_len;
   CUtensorMap mx, mg, mb, mc, mh, md, mdv, mdq, mdk;
@@ -1616,7 +1617,7 @@ static int run_bwd(const void* v, const void* gy, const void* bk, const void* cq
     if (rc) return rc;
   }
   // bf16 results leave through TMA stores; a map of an fp32 result is never used and points at gy
-  rc = make_map(&mdv, dv16 ? dv16 : gy, rows, (int64_t)heads * P, L);
+  rc = make_map(&mdv, dv16 ? dv16 : gy, rows, (int64_t)heads * P, L, dv16 ? dv_ld : 0);
   if (rc) return rc;
   rc = make_map(&mdq, dcq16 ? dcq16 : gy, rows, (int64_t)heads * (dcq16 ? N : P), L);
   if (rc) return rc;
@@ -1638,23 +1639,24 @@ extern "C" int lbi_ssd_chunk_bwd(const void* v, const void* gy, const void* bk, 
                                  const float* cum, const float* skip_tok, const float* d_skip, const void* state_in,
                                  const float* d_final, float* chunk_cot, void* d_out, float* d_init, float* da, float* dskip,
                                  float* dv32, void* dv16, float* dcq32, float* dbk32, void* dcq16, void* dbk16, int batch, int bmod,
-                                 int seq_len, int heads, int groups, int d_state, int per_head, int strict, int* status,
-                                 cudaStream_t st) {
+                                 int seq_len, int heads, int groups, int d_state, int per_head, int strict, int64_t dv_ld,
+                                 int* status, cudaStream_t st) {
   using namespace lbi::ssd;
   if (seq_len % L != 0 || batch <= 0 || bmod <= 0 || batch % bmod != 0) return (int)cudaErrorInvalidValue;
+  if (dv_ld != 0 && (!dv16 || dv_ld % 8 != 0 || dv_ld < (int64_t)heads * P)) return (int)cudaErrorInvalidValue;
   if (!!dv32 == !!dv16 || !!dcq32 == !!dcq16 || !!dbk32 == !!dbk16) return (int)cudaErrorInvalidValue;
   if (per_head) {
     if (d_state != 128) return (int)cudaErrorInvalidValue;
     return run_bwd<128, true>(v, gy, bk, cq, weight, cum, skip_tok, d_skip, state_in, d_final, chunk_cot, d_out, d_init, da, dskip,
-                              dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st);
+                              dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st, dv_ld);
   }
   if (groups <= 0 || heads % groups != 0 || (heads / groups) % 2 != 0) return (int)cudaErrorInvalidValue;
   if (d_state == 128)
     return run_bwd<128, false>(v, gy, bk, cq, weight, cum, skip_tok, d_skip, state_in, d_final, chunk_cot, d_out, d_init, da, dskip,
-                               dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st);
+                               dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st, dv_ld);
   if (d_state == 64)
     return run_bwd<64, false>(v, gy, bk, cq, weight, cum, skip_tok, d_skip, state_in, d_final, chunk_cot, d_out, d_init, da, dskip,
-                              dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st);
+                              dv32, dv16, dcq32, dbk32, dcq16, dbk16, batch, bmod, seq_len, heads, groups, strict, status, st, dv_ld);
   return (int)cudaErrorInvalidValue;
 }
 

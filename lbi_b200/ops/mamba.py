@@ -57,20 +57,30 @@ def gate_silu_fwd(y: torch.Tensor, z: torch.Tensor) -> torch.Tensor:
     return (y.float() * F.silu(z.float())).to(y.dtype)
 
 
-def gate_silu_bwd(dyg: torch.Tensor, y: torch.Tensor, z: torch.Tensor):
-    """dyg [P * n, d]; y, z [n, d] -> (dy, dz) [P * n, d] in the dtype of dyg."""
+def gate_silu_bwd(dyg: torch.Tensor, y: torch.Tensor, z: torch.Tensor, dz_out: torch.Tensor | None = None):
+    """dyg [P * n, d]; y, z [n, d] -> (dy, dz) [P * n, d] in the dtype of dyg.  ``dz_out``: a [P * n, d] view (a column range of
+    a wider cotangent matrix) that receives dz in place of a fresh tensor."""
     if (_kernel_ok(dyg, y, z, name="gate_silu_bwd") and dyg.dtype == torch.bfloat16 and y.dtype == torch.bfloat16
-            and z.dtype == torch.bfloat16 and y.shape[-1] % 8 == 0):
+            and z.dtype == torch.bfloat16 and y.dim() == 2 and y.shape[-1] % 8 == 0):
+        direct = (dz_out is not None and dz_out.dtype == torch.bfloat16 and dz_out.stride(-1) == 1 and dz_out.stride(0) % 8 == 0
+                  and dz_out.storage_offset() % 8 == 0)
         _count()
-        return ext().gate_silu_bwd(dyg.contiguous(), y.contiguous(), z.contiguous())
+        dy, dz = ext().gate_silu_bwd(dyg.contiguous(), y.contiguous(), z.contiguous(), dz_out if direct else None)
+        if dz_out is not None and not direct:
+            dz_out.copy_(dz)
+            dz = dz_out
+        return dy, dz
     _fell_back("gate_silu_bwd", dyg, y, z)
     reps = dyg.shape[0] // y.shape[0]
     g = dyg.float().view(reps, *y.shape)
     zf, yf = z.float(), y.float()
     sig = torch.sigmoid(zf)
     dy = g * (zf * sig)
-    dz = g * yf * (sig * (1.0 + zf * (1.0 - sig)))
-    return dy.reshape(dyg.shape).to(dyg.dtype), dz.reshape(dyg.shape).to(dyg.dtype)
+    dz = (g * yf * (sig * (1.0 + zf * (1.0 - sig)))).reshape(dyg.shape).to(dyg.dtype)
+    if dz_out is not None:
+        dz_out.copy_(dz)
+        dz = dz_out
+    return dy.reshape(dyg.shape).to(dyg.dtype), dz
 
 
 # ---------------------------------------------------------------- RMSNorm over groups of the last axis, optional SiLU gate
@@ -299,24 +309,33 @@ def siso_scan_fwd(v, kr, qr, adt, skip, d_skip):
     return (y + total_skip.unsqueeze(-1) * v.float()).to(v.dtype), None
 
 
-def siso_scan_bwd(qr, kr, adt, skip_total, v, gy, states):
+def siso_scan_bwd(qr, kr, adt, skip_total, v, gy, states, dv_out=None):
     """gy [P * b, l, h, p] with the forward operands shared by the P directions ->
-    (dQr, dKr, dadt, dskip, dV, dkr_is_time_reversed)."""
+    (dQr, dKr, dadt, dskip, dV, dkr_is_time_reversed).  ``dv_out``: a [P b l, h p] view that receives dV (a column range of the
+    in_proj cotangent), written by the kernel itself where it can."""
     from . import ssd
 
     reps = gy.shape[0] // v.shape[0]
     if ssd.siso_cuda_supported(v, qr) and gy.dtype == torch.bfloat16 and states is not None:
         if ssd.chunk_backward_supported(v):
             dv, dqr, dkr, dadt, dskip = ssd.chunk_backward(v, gy, kr, qr, adt, None, skip_total, states, per_head=True, strict=True,
-                                                           dv_bf16=True, dn_bf16=True)
+                                                           dv_bf16=True, dn_bf16=True, dv_out=dv_out)
             return dqr, dkr, dadt, dskip, dv, False
         if hasattr(ext(), "ssd_decay_grad"):
             tile = lambda t: None if t is None else _tile_rows(t, reps)  # noqa: E731
             out = ssd.siso_core_backward(tile(qr), tile(kr), tile(adt), tile(skip_total), tile(v), gy, ops=ssd.KernelScans,
                                          fwd_states=tile(states), keep_dkr_reversed=True)
-            return (*out, True)
+            return (*_place_dv(out, dv_out), True)
     _fell_back("siso_scan_bwd", v, gy, qr, kr)
-    return (*ssd.siso_core_backward_dense(qr, kr, adt, skip_total, v, gy), False)
+    return (*_place_dv(ssd.siso_core_backward_dense(qr, kr, adt, skip_total, v, gy), dv_out), False)
+
+
+def _place_dv(out, dv_out):
+    """(dQr, dKr, dadt, dskip, dV) with dV copied into ``dv_out`` when one is given."""
+    if dv_out is None:
+        return out
+    dv_out.copy_(out[4].reshape(dv_out.shape))
+    return (*out[:4], dv_out)
 
 
 # ---------------------------------------------------------------- Mamba-2: softplus of dt, SiLU of the conv output

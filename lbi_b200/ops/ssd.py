@@ -478,11 +478,14 @@ def chunk_backward_supported(v: torch.Tensor) -> bool:
                 and os.environ.get("LBI_B200_SSD_PERMUTED_BACKWARD", "0") != "1")
 
 
-def chunk_backward(v, gy, bk, cq, a, weight, skip, states_in, *, per_head: bool, strict: bool, dv_bf16: bool, dn_bf16: bool):
+def chunk_backward(v, gy, bk, cq, a, weight, skip, states_in, *, per_head: bool, strict: bool, dv_bf16: bool, dn_bf16: bool,
+                   dv_out=None):
     """Every input cotangent of the scan ``y_t = sum_{s <= t} e^{c_t - c_s} (cq_t . bk_s) w_s v_s (+ skip_t v_t)`` from one fused
     kernel per (direction, chunk, head) (csrc/ssd.cu, ``bwd_chunk_kernel``).  The forward operands v [b, l, h, 64], bk, cq
     [b, l, g, n], a, weight, skip [b, l, h] and the forward's incoming chunk states are shared by the P = gy.shape[0] / b stacked
-    directions of gy.  Returns (d(w v) [+ skip gy], dcq, dbk per head [P b, l, h, n], da, gy . v [P b, l, h])."""
+    directions of gy.  Returns (d(w v) [+ skip gy], dcq, dbk per head [P b, l, h, n], da, gy . v [P b, l, h]).  ``dv_out``: a
+    [P b l, h 64] bf16 view (a column range of a wider cotangent matrix) the kernel writes the first result into (needs
+    ``dv_bf16`` and a sequence length that is a multiple of 128; otherwise the result is copied there)."""
     from .dispatch import KERNEL_LAUNCHES
 
     bf = torch.bfloat16
@@ -497,11 +500,17 @@ def chunk_backward(v, gy, bk, cq, a, weight, skip, states_in, *, per_head: bool,
         wf = None if wf is None else F.pad(wf, (0, 0, 0, pad))
         sf = None if sf is None else F.pad(sf, (0, 0, 0, pad))
     KERNEL_LAUNCHES["count"] += 3   # cumulative sum, reversed state passing with its chunk products, chunk backward
+    direct = (dv_out is not None and dv_bf16 and not pad and dv_out.dtype == bf and dv_out.dim() == 2 and dv_out.stride(1) == 1
+              and dv_out.stride(0) % 8 == 0 and dv_out.storage_offset() % 8 == 0)
     dv, dcq, dbk, da, dskip = ext().ssd_chunk_bwd(vb.contiguous(), gyb.contiguous(), bkb.contiguous(), cqb.contiguous(), af.contiguous(),
                                                   None if wf is None else wf.contiguous(), None if sf is None else sf.contiguous(),
-                                                  None, states_in, bool(per_head), bool(strict), bool(dv_bf16), bool(dn_bf16))
+                                                  None, states_in, bool(per_head), bool(strict), bool(dv_bf16), bool(dn_bf16),
+                                                  dv_out if direct else None)
     if pad:
         dv, dcq, dbk, da, dskip = (t[:, :seqlen] for t in (dv, dcq, dbk, da, dskip))
+    if dv_out is not None and not direct:
+        dv_out.copy_(dv.reshape(dv_out.shape))
+        dv = dv_out
     return dv, dcq, dbk, da, dskip
 
 
