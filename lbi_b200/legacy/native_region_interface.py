@@ -41,6 +41,17 @@ class RegionForwardCache:
     message_out: torch.Tensor
 
 
+@dataclass
+class RegionInterfaceCache:
+    """The interface view of a forward cache with the reference's field names (legacy/native_region_interface.py:83-89);
+    ``NativeRegionInterfaceModel.interface_cache`` builds it from the dict ``forward_with_cache`` returns."""
+    boundaries: list[torch.Tensor]
+    region_hidden_inputs: list[torch.Tensor]
+    region_messages: list[torch.Tensor]
+    region_ranges: list[tuple[int, int]]
+    region_caches: list[RegionForwardCache]
+
+
 class NativeRegionInterfaceModel(nn.Module):
     def __init__(self, *, vocab_size: int, region_size: int, message_dim: int, backbone_spec: BackboneSpec,
                  message_hidden_dim: int = 0, message_scale_init: float = 0.5, tie_embeddings: bool = False) -> None:
@@ -139,6 +150,13 @@ class NativeRegionInterfaceModel(nn.Module):
             "states": messages, "state_inputs": state_inputs, "initial_state": initial, "detached_states": cut,
             "region_axis": "depth",
         }
+
+    @staticmethod
+    def interface_cache(cache: dict[str, Any]) -> RegionInterfaceCache:
+        """The interface fields of a ``forward_with_cache`` dict as the reference's dataclass."""
+        return RegionInterfaceCache(boundaries=list(cache["boundaries"]), region_hidden_inputs=list(cache["region_hidden_inputs"]),
+                                    region_messages=list(cache["region_messages"]), region_ranges=[tuple(r) for r in cache["region_ranges"]],
+                                    region_caches=list(cache["region_caches"]))
 
     def forward(self, input_ids: torch.Tensor, **kwargs) -> torch.Tensor:
         return self.forward_with_cache(input_ids, **kwargs)[0]

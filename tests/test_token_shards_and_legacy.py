@@ -92,6 +92,33 @@ def test_lbi1_backward_step_matches_autograd():
             assert torch.allclose(p.grad, want[n], atol=1e-5, rtol=1e-4), n
 
 
+@pytest.mark.parametrize("mode", ["graph", "recompute"])
+def test_lbi1_backward_entry_with_the_reference_keywords(mode):
+    """``_native_backward_step(model, ce_loss=..., cache=..., ...)`` returns named gradients, the scan residual and, on request,
+    the Jacobian statistics with their suffix part; ``.grad`` stays untouched."""
+    from lbi_b200.legacy import NativeBackwardResult, RegionInterfaceCache, _native_backward_step, build_region_slices
+
+    assert build_region_slices(5, 2) == [(0, 2), (2, 4), (4, 5)]
+    torch.manual_seed(2)
+    spec = BackboneSpec(name="transformer", dim=32, layers=3, n_heads=4, d_conv=0)
+    model = NativeRegionInterfaceModel(vocab_size=40, region_size=1, message_dim=8, backbone_spec=spec, message_hidden_dim=16)
+    ids, tgt = torch.randint(0, 40, (2, 10)), torch.randint(0, 40, (2, 10))
+    loss = torch.nn.functional.cross_entropy(model(ids).reshape(-1, 40), tgt.reshape(-1))
+    want = dict(zip([n for n, _ in model.named_parameters()], torch.autograd.grad(loss, list(model.parameters()), allow_unused=True)))
+    logits, cache = model.forward_with_cache(ids, detach_states=True)
+    view = model.interface_cache(cache)
+    assert isinstance(view, RegionInterfaceCache) and len(view.region_caches) == 3 and view.region_ranges == [(0, 1), (1, 2), (2, 3)]
+    loss = torch.nn.functional.cross_entropy(logits.reshape(-1, 40), tgt.reshape(-1))
+    out = _native_backward_step(model, ce_loss=loss, cache=cache, interface_jacobian_mode=mode, jacobian_basis_chunk=4,
+                                compute_interface_jacobian_stats=True, include_interface_jacobian_suffix=True)
+    assert isinstance(out, NativeBackwardResult) and out.interface_scan_rms < 1e-5
+    assert {"jac_local_spec_mean", "jac_local_frob_max", "jac_suffix_spec_max"} <= set(out.interface_jacobian_stats)
+    assert all(p.grad is None for p in model.parameters())
+    for n, g in want.items():
+        if g is not None:
+            assert torch.allclose(out.grad_map[n], g, atol=1e-5, rtol=1e-4), n
+
+
 def test_dense_state_dict_has_both_block_prefixes():
     model = DenseLanguageModel(vocab_size=30, backbone_spec=BackboneSpec(name="transformer", dim=16, layers=1, n_heads=2))
     keys = set(model.state_dict())
