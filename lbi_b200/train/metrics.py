@@ -35,6 +35,24 @@ def _readout_parts(model: nn.Module) -> tuple[int, int, bool]:
     return head, norm, tied
 
 
+# The per-component counts under the names the reference exports (train/metrics.py:20-43).
+def canvas_component_params(model: nn.Module) -> int:
+    canvas = getattr(model, "canvas", None)
+    return count_parameters(canvas) if isinstance(canvas, nn.Module) else 0
+
+
+def readout_lm_head_component_params(model: nn.Module) -> int:
+    return _readout_parts(model)[0]
+
+
+def readout_norm_component_params(model: nn.Module) -> int:
+    return _readout_parts(model)[1]
+
+
+def readout_uses_tied_output_weight(model: nn.Module) -> bool:
+    return _readout_parts(model)[2]
+
+
 def infer_data_info(cfg: Any, *, train_corpus: Any, val_corpus: Any) -> dict[str, Any]:
     from . import data as glue
 

@@ -177,3 +177,27 @@ def test_legacy_model_closed_form_region_pullback_matches_autograd():
                                                        retain_graph=True)[0] for j in range(6)], dim=1)
         total = model.region_outer_message_input_pullback(rc, eye, g_hidden_in)["g_message_input_total"]   # [B, j, i]
         assert torch.allclose(total.transpose(1, 2), mats[ridx], atol=1e-5, rtol=1e-4)
+
+
+def test_first_release_trainer_entry_and_component_counts(tmp_path):
+    from lbi_b200.legacy import train_region_interface as legacy_train
+    from lbi_b200.train.model_builders import build_lbi_language_model
+    from lbi_b200.train import metrics
+    from lbi_b200.train.config import NEW_OUTPUT_NAME_BY_VARIANT, LBITrainingConfig
+
+    cfg = LBITrainingConfig(
+        regime="native_region_interface", variants="", backbone="transformer", device="cpu", dtype="float32",
+        output_dir=str(tmp_path), run_name="first", task="copy", vocab_size=32, seq_len=16, train_sequences=16,
+        val_sequences=4, batch_size=2, steps=2, eval_every=1, eval_batches=1, log_every=1, save_every=2, layers=2, dim=16,
+        n_heads=2, region_size=1, message_dim=4, message_hidden_dim=8, seed=3)
+    out = legacy_train.run_training(cfg)
+    assert cfg.variants == "native_region_interface" and out
+    assert set(NEW_OUTPUT_NAME_BY_VARIANT) == {"dense", "lbi"}
+
+    cfg.variants = "lbi"
+    model = build_lbi_language_model(cfg)
+    total = sum(p.numel() for p in model.parameters())
+    parts = (metrics.canvas_component_params(model), metrics.readout_lm_head_component_params(model),
+             metrics.readout_norm_component_params(model))
+    assert all(0 <= p <= total for p in parts) and parts[0] > 0
+    assert isinstance(metrics.readout_uses_tied_output_weight(model), bool)
