@@ -18,6 +18,9 @@ class Mamba3BlockCache:
     mixer: Mamba3ForwardCache
 
 
+Mamba3BlockForwardCache = Mamba3BlockCache  # the reference's name for the same record (backbones/mamba3/block.py)
+
+
 class Mamba3Block(nn.Module):
     def __init__(
         self,

@@ -7,14 +7,66 @@ cache is built lazily when a lowering needs it.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass, field
 from typing import Protocol
 
 import torch
 from torch import nn
+from torch.nn import functional as F
 
 from ..backbones.general import BackboneSpec, build_backbone_stack, init_transformer_module
+from ..backbones.transformer.rope import apply_rope
 from .base import RegionForwardCache, autocast_as, current_autocast
 from .transformer_structured import StructuredTransformerRegion
+
+
+# Named per-layer activation records with the reference's field names (backends/transformer.py:17-61).  The engine does not
+# keep these (its kernels read the flat ``StructuredRegionCache``); ``TransformerRegionBackend.forward_region_with_layer_caches``
+# fills them from the module code for inspection and for code written against the reference's cache.
+@dataclass
+class TransformerAttentionCache:
+    norm_input: torch.Tensor
+    norm_output: torch.Tensor
+    qkv: torch.Tensor
+    q: torch.Tensor
+    k: torch.Tensor
+    v: torch.Tensor
+    q_rope: torch.Tensor
+    k_rope: torch.Tensor
+    k_expanded: torch.Tensor
+    v_expanded: torch.Tensor
+    attn_output: torch.Tensor
+    out_proj_input: torch.Tensor
+    out_proj_output: torch.Tensor
+
+
+@dataclass
+class TransformerMLPCache:
+    norm_input: torch.Tensor
+    norm_output: torch.Tensor
+    fc1_output: torch.Tensor
+    up: torch.Tensor
+    gate: torch.Tensor
+    activation: torch.Tensor
+    down_input: torch.Tensor
+    down_output: torch.Tensor
+
+
+@dataclass
+class TransformerLayerCache:
+    layer_index: int
+    hidden_input: torch.Tensor
+    residual_input: torch.Tensor | None
+    attention: TransformerAttentionCache
+    mlp: TransformerMLPCache
+    hidden_output: torch.Tensor
+    residual_output: torch.Tensor | None
+
+
+@dataclass
+class TransformerRegionCache(RegionForwardCache):
+    layer_caches: list[TransformerLayerCache] = field(default_factory=list)
+    region_output: torch.Tensor | None = None
 
 
 class TransformerLowering(Protocol):
@@ -68,14 +120,22 @@ class StructuredTransformerLowering:
 
 
 class TransformerRegionBackend(nn.Module):
-    def __init__(self, *, backbone_spec: BackboneSpec, region_ranges: list[tuple[int, int]],
-                 lowering: TransformerLowering | None = None) -> None:
+    name = "transformer"
+
+    def __init__(self, *, backbone_spec: BackboneSpec | None = None, region_ranges: list[tuple[int, int]],
+                 backbone: nn.Module | None = None, lowering: TransformerLowering | None = None) -> None:
         super().__init__()
-        if backbone_spec.name != "transformer":
-            raise ValueError("TransformerRegionBackend requires a transformer backbone spec")
+        if backbone is None:
+            if backbone_spec is None:
+                raise ValueError("backbone_spec is required when backbone is not provided")
+            if backbone_spec.name != "transformer":
+                raise ValueError("TransformerRegionBackend requires a transformer backbone spec")
+            backbone = build_backbone_stack(backbone_spec)
         self.backbone_spec = backbone_spec
         self.region_ranges = [tuple(r) for r in region_ranges]
-        self.backbone = build_backbone_stack(backbone_spec)
+        if not self.region_ranges:
+            raise ValueError("transformer region backend requires at least one region")
+        self.backbone = backbone
         self.lowering: TransformerLowering = lowering or StructuredTransformerLowering()
         object.__setattr__(self, "structured", StructuredTransformerRegion(self.backbone.blocks))
 
@@ -91,6 +151,58 @@ class TransformerRegionBackend(nn.Module):
             return self.backbone.forward_range(region_input, start, end), cache
         out, cache.structured = self.structured.forward(region_input, (start, end))
         return out, cache
+
+    @staticmethod
+    def _attention_with_cache(attn: nn.Module, normed: torch.Tensor, norm_input: torch.Tensor):
+        bsz, seqlen, _ = normed.shape
+        qkv = attn.in_proj(normed)
+        if attn.d_conv > 0:
+            qkv = attn.causal_conv(qkv)
+        q, k, v = attn.split_heads(qkv)
+        q_rope = apply_rope(q, base=attn.rope_base, interleaved=attn.rope_interleaved)
+        k_rope = apply_rope(k, base=attn.rope_base, interleaved=attn.rope_interleaved)
+        k_exp, v_exp = attn.expand_kv(k_rope), attn.expand_kv(v)
+        heads = F.scaled_dot_product_attention(q_rope, k_exp, v_exp, dropout_p=0.0, is_causal=True,
+                                               scale=attn.scale).transpose(1, 2)
+        flat = heads.contiguous().view(bsz, seqlen, attn.out_dim)
+        out = attn.out_proj(flat)
+        return out, TransformerAttentionCache(
+            norm_input=norm_input, norm_output=normed, qkv=qkv, q=q, k=k, v=v, q_rope=q_rope, k_rope=k_rope,
+            k_expanded=k_exp, v_expanded=v_exp, attn_output=heads, out_proj_input=flat, out_proj_output=out)
+
+    @staticmethod
+    def _mlp_with_cache(mlp: nn.Module, normed: torch.Tensor, norm_input: torch.Tensor):
+        fc1 = mlp.fc1(normed)
+        up, gate = fc1.chunk(2, dim=-1)
+        act = F.silu(gate)
+        down_in = up * act
+        out = mlp.fc2(down_in)
+        return out, TransformerMLPCache(norm_input=norm_input, norm_output=normed, fc1_output=fc1, up=up, gate=gate,
+                                        activation=act, down_input=down_in, down_output=out)
+
+    def forward_region_with_layer_caches(self, *, region_input: torch.Tensor,
+                                         region_index: int) -> tuple[torch.Tensor, TransformerRegionCache]:
+        """The region through the module code, every intermediate kept under the reference's names
+        (backends/transformer.py:201-237).  Not on the engine's path: one region of activations is held several times over."""
+        start, end = self.region_ranges[region_index]
+        hidden, residual = region_input, None
+        layers: list[TransformerLayerCache] = []
+        for idx in range(start, end):
+            block = self.backbone.blocks[idx]
+            hidden_in, residual_in = hidden, residual
+            stream1 = hidden if residual is None else hidden + residual
+            normed1, residual = block.add_norm(hidden, residual, block.norm)
+            attn_out, attn_cache = self._attention_with_cache(block.attn, normed1, stream1)
+            stream2 = attn_out + residual
+            normed2, residual = block.add_norm(attn_out, residual, block.norm2)
+            hidden, mlp_cache = self._mlp_with_cache(block.mlp, normed2, stream2)
+            layers.append(TransformerLayerCache(layer_index=idx, hidden_input=hidden_in, residual_input=residual_in,
+                                                attention=attn_cache, mlp=mlp_cache, hidden_output=hidden,
+                                                residual_output=residual))
+        out = hidden if residual is None else hidden + residual
+        return out, TransformerRegionCache(region_index=region_index, layer_range=(start, end), region_input=region_input,
+                                           autocast=current_autocast(region_input.device), layer_caches=layers,
+                                           region_output=out)
 
     def parameters_for_region(self, region_index: int) -> list[nn.Parameter]:
         start, end = self.region_ranges[region_index]

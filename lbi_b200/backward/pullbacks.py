@@ -150,6 +150,20 @@ class ForwardModeInterfacePullbackProvider:
         return out
 
 
+def materialize_interface_state_jacobian_t_graph(*, model: Any, cache: dict) -> list[torch.Tensor]:
+    """Function form of the graph provider (reference backward/pullbacks.py:37-81)."""
+    if len(cache["states"]) != model.num_regions + 1:
+        raise ValueError("cache has invalid states length.")
+    return TorchGraphInterfacePullbackProvider().materialize_state_jacobian_t(model=model, cache=cache)
+
+
+def materialize_interface_state_jacobian_t_recompute(*, model: Any, cache: dict, basis_chunk: int) -> list[torch.Tensor]:
+    """Function form of the recompute provider (reference backward/pullbacks.py:84-149)."""
+    if len(cache["region_caches"]) != model.num_regions:
+        raise ValueError("cache has invalid region_caches length.")
+    return TorchRecomputeInterfacePullbackProvider(basis_chunk=basis_chunk).materialize_state_jacobian_t(model=model, cache=cache)
+
+
 def build_interface_pullback_provider(mode: str, *, basis_chunk: int = 1) -> InterfacePullbackProvider:
     if mode == "graph":
         return TorchGraphInterfacePullbackProvider()

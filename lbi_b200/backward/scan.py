@@ -22,6 +22,7 @@ from torch import nn
 from .base import ADResult, LBIBackwardResult, assign_grad_map, is_scan_backprop_model
 from .local_vjp import LocalVJPProvider, TorchAutogradLocalVJPProvider, surrogate_backward
 from .pullbacks import InterfacePullbackProvider, build_interface_pullback_provider
+from .reference_scan import ReferenceScanEngine  # noqa: F401  (importable from here as in the reference, backward/scan.py:171)
 from .suffix_scan import (
     apply_jacobian_t,
     interface_state_jacobian_t_stats,

@@ -58,6 +58,18 @@ def propagate_state_adjoint_affine(state_jacobian_t: Sequence[torch.Tensor], off
     return list(g.unbind(dim=1))
 
 
+def propagate_state_adjoint_by_autograd_chain(*, states: Sequence[torch.Tensor], top_state_adjoint: torch.Tensor) -> list[torch.Tensor]:
+    """Diagnostic: pull the top state's adjoint down the retained forward graph one region at a time, without any
+    materialised Jacobian (reference backward/suffix_scan.py:82-102).  Entry k is the adjoint of state k."""
+    if len(states) < 2:
+        raise ValueError("at least two interface states are required.")
+    adjoints = [top_state_adjoint]
+    for k in range(len(states) - 2, -1, -1):
+        (g,) = torch.autograd.grad(states[k + 1], states[k], adjoints[0], retain_graph=True)
+        adjoints.insert(0, g)
+    return adjoints
+
+
 def propagate_state_adjoint_by_chain(state_jacobian_t: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor]) -> list[torch.Tensor]:
     """Sequential mat-vec recursion; the oracle for the scans."""
     k = len(offsets)

@@ -201,3 +201,61 @@ def test_first_release_trainer_entry_and_component_counts(tmp_path):
              metrics.readout_norm_component_params(model))
     assert all(0 <= p <= total for p in parts) and parts[0] > 0
     assert isinstance(metrics.readout_uses_tied_output_weight(model), bool)
+
+
+def test_reference_names_import_from_the_same_modules():
+    from lbi_b200.backbones.mamba3.block import Mamba3BlockCache, Mamba3BlockForwardCache
+    from lbi_b200.backbones.transformer.block import RMSNorm  # noqa: F401
+    from lbi_b200.backends.transformer import (TransformerAttentionCache, TransformerLayerCache,  # noqa: F401
+                                               TransformerMLPCache, TransformerRegionCache)
+    from lbi_b200.backward.pullbacks import (materialize_interface_state_jacobian_t_graph,  # noqa: F401
+                                             materialize_interface_state_jacobian_t_recompute)
+    from lbi_b200.backward.scan import ReferenceScanEngine  # noqa: F401
+    from lbi_b200.backward.suffix_scan import propagate_state_adjoint_by_autograd_chain  # noqa: F401
+    from lbi_b200.models.lbi_language_model import build_region_ranges  # noqa: F401
+
+    assert Mamba3BlockForwardCache is Mamba3BlockCache
+
+
+def test_transformer_layer_caches_and_jacobian_function_forms():
+    from lbi_b200.backends.transformer import TransformerRegionBackend
+    from lbi_b200.backward.pullbacks import (materialize_interface_state_jacobian_t_graph,
+                                             materialize_interface_state_jacobian_t_recompute)
+    from lbi_b200.backward.suffix_scan import propagate_state_adjoint_by_autograd_chain
+    from lbi_b200.train.config import LBITrainingConfig
+    from lbi_b200.train.model_builders import build_lbi_language_model
+
+    torch.manual_seed(0)
+    cfg = LBITrainingConfig(variants="lbi", backbone="transformer", device="cpu", dtype="float32", vocab_size=32, seq_len=8,
+                            layers=4, dim=16, n_heads=2, region_size=2, message_dim=4, message_hidden_dim=8, d_conv=3)
+    model = build_lbi_language_model(cfg)
+    backend = model.region_backend
+    x = torch.randn(2, 8, 16)
+    with torch.no_grad():
+        want = backend.backbone.forward_range(x, 2, 4)
+        got, cache = backend.forward_region_with_layer_caches(region_input=x, region_index=1)
+    assert torch.allclose(got, want, atol=1e-6) and [lc.layer_index for lc in cache.layer_caches] == [2, 3]
+    first = cache.layer_caches[0]
+    assert first.residual_input is None and first.attention.norm_input is not None
+    assert first.attention.q_rope.shape == first.attention.k_expanded.shape == (2, 2, 8, 8)
+    assert torch.allclose(first.mlp.down_input, first.mlp.up * first.mlp.activation)
+    assert torch.allclose(cache.layer_caches[1].mlp.down_output + cache.layer_caches[1].residual_output, got, atol=1e-6)
+    shared = TransformerRegionBackend(backbone=backend.backbone, region_ranges=[(0, 4)])
+    assert shared.backbone is backend.backbone and shared.count_parameters() == backend.count_parameters()
+    with pytest.raises(ValueError):
+        TransformerRegionBackend(backbone_spec=None, region_ranges=[(0, 1)])
+
+    tokens = torch.randint(0, 32, (2, 8))
+    _, fcache = model.forward_with_cache(tokens)
+    graph = materialize_interface_state_jacobian_t_graph(model=model, cache=fcache)
+    rec = materialize_interface_state_jacobian_t_recompute(model=model, cache=fcache, basis_chunk=3)
+    assert len(graph) == len(rec) == model.num_regions
+    for a, b in zip(graph, rec):
+        assert torch.allclose(a, b, atol=1e-5)
+    top = torch.randn_like(fcache["states"][-1])
+    by_graph = propagate_state_adjoint_by_autograd_chain(states=fcache["states"], top_state_adjoint=top)
+    assert len(by_graph) == model.num_regions + 1 and torch.equal(by_graph[-1], top)
+    expect = torch.einsum("bij,bj->bi", graph[-1], top)
+    assert torch.allclose(by_graph[-2], expect, atol=1e-5)
+    with pytest.raises(ValueError):
+        propagate_state_adjoint_by_autograd_chain(states=fcache["states"][:1], top_state_adjoint=top)
