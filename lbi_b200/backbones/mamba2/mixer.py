@@ -22,6 +22,7 @@ class Mamba2Simple(nn.Module):
         d_model: int,
         d_state: int = 64,
         d_conv: int = 4,
+        conv_init: float | None = None,
         expand: int = 2,
         headdim: int = 128,
         ngroups: int = 1,
@@ -30,6 +31,8 @@ class Mamba2Simple(nn.Module):
         dt_max: float = 0.1,
         dt_init_floor: float = 1e-4,
         dt_limit=(0.0, float("inf")),
+        learnable_init_states: bool = False,
+        activation: str = "swish",
         bias: bool = False,
         conv_bias: bool = True,
         chunk_size: int = 256,
@@ -47,6 +50,9 @@ class Mamba2Simple(nn.Module):
             raise ValueError("expand * d_model must be divisible by headdim")
         self.nheads = self.d_inner // headdim
         self.dt_limit = dt_limit
+        if activation not in ("silu", "swish"):
+            raise ValueError("the Mamba-2 mixer supports the silu / swish activation only")
+        self.conv_init, self.learnable_init_states, self.activation = conv_init, learnable_init_states, activation
         self.chunk_size = chunk_size
         self.use_mem_eff_path = use_mem_eff_path
         self.layer_idx = layer_idx
@@ -55,6 +61,11 @@ class Mamba2Simple(nn.Module):
         self.in_proj = nn.Linear(d_model, 2 * self.d_inner + 2 * ngroups * d_state + self.nheads, bias=bias, **fk)
         conv_dim = self.d_inner + 2 * ngroups * d_state
         self.conv1d = nn.Conv1d(conv_dim, conv_dim, kernel_size=d_conv, groups=conv_dim, padding=d_conv - 1, bias=conv_bias, **fk)
+        if conv_init is not None:
+            nn.init.uniform_(self.conv1d.weight, -conv_init, conv_init)
+        if learnable_init_states:
+            self.init_states = nn.Parameter(torch.zeros(self.nheads, headdim, d_state, **fk))
+            self.init_states._no_weight_decay = True
 
         dt = torch.exp(torch.rand(self.nheads, **fk) * (math.log(dt_max) - math.log(dt_min)) + math.log(dt_min))
         dt = torch.clamp(dt, min=dt_init_floor)
@@ -69,7 +80,29 @@ class Mamba2Simple(nn.Module):
         self.out_proj = nn.Linear(self.d_inner, d_model, bias=bias, **fk)
 
     def forward(self, u: torch.Tensor, seq_idx=None) -> torch.Tensor:
+        """u [B, L, D] -> [B, L, D].  ``seq_idx`` [B, L] (non-decreasing ids of the sequences packed into each row, as in the
+        reference's kernels: mamba2_simple.py:124-147) makes the convolution window and the state start afresh wherever the id
+        changes; the learnable initial state, when there is one, belongs to the first sequence of each row."""
+        if seq_idx is not None:
+            return self._forward_packed(u, seq_idx)
+        return self._forward_tokens(u, first_segment=True)
+
+    def _forward_packed(self, u: torch.Tensor, seq_idx: torch.Tensor) -> torch.Tensor:
+        if seq_idx.shape != u.shape[:2]:
+            raise ValueError("seq_idx must have shape [B, L]")
+        rows = []
+        for b in range(u.shape[0]):
+            cuts = (torch.nonzero(seq_idx[b, 1:] != seq_idx[b, :-1]).flatten() + 1).tolist()
+            edges = [0, *cuts, u.shape[1]]
+            rows.append(torch.cat([self._forward_tokens(u[b : b + 1, s:e], first_segment=(s == 0))
+                                   for s, e in zip(edges[:-1], edges[1:])], dim=1))
+        return torch.cat(rows, dim=0)
+
+    def _forward_tokens(self, u: torch.Tensor, *, first_segment: bool) -> torch.Tensor:
         bsz, seqlen, _ = u.shape
+        init = None
+        if self.learnable_init_states and first_segment:
+            init = self.init_states.unsqueeze(0).expand(bsz, -1, -1, -1)
         zxbcdt = self.in_proj(u)
         gn = self.ngroups * self.d_state
         z, xBC, dt = torch.split(zxbcdt, [self.d_inner, self.d_inner + 2 * gn, self.nheads], dim=-1)
@@ -84,8 +117,8 @@ class Mamba2Simple(nn.Module):
         A = -torch.exp(self.A_log.float())
         if ops_ssd.ssd_cuda_supported(x4, B4) and x4.dtype == torch.bfloat16:
             # sm_100a kernels (chunk 128 inside); the chunk size does not change the result, only the blocking
-            y = ops_ssd.ssd_chunk_scan_cuda(x4, dt, A, B4, C4, D=self.D)
+            y = ops_ssd.ssd_chunk_scan_cuda(x4, dt, A, B4, C4, D=self.D, initial_state=init)
         else:
-            y = ssd_chunk_scan(x4, dt, A, B4, C4, chunk_size=self.chunk_size, D=self.D)
+            y = ssd_chunk_scan(x4, dt, A, B4, C4, chunk_size=self.chunk_size, D=self.D, initial_state=init)
         y = self.norm(y.reshape(bsz, seqlen, self.d_inner), z)
         return self.out_proj(y.to(self.out_proj.weight.dtype))

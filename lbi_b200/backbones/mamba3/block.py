@@ -16,9 +16,25 @@ class Mamba3BlockCache:
     residual_out: torch.Tensor
     normed: torch.Tensor
     mixer: Mamba3ForwardCache
+    hidden_input: Optional[torch.Tensor] = None
+    residual_input: Optional[torch.Tensor] = None
+    hidden_output: Optional[torch.Tensor] = None
+
+    # the reference's field names for the first three (backbones/mamba3/block.py:12-19)
+    @property
+    def residual_output(self) -> torch.Tensor:
+        return self.residual_out
+
+    @property
+    def norm_input(self) -> torch.Tensor:
+        return self.normed
+
+    @property
+    def mixer_cache(self) -> Mamba3ForwardCache:
+        return self.mixer
 
 
-Mamba3BlockForwardCache = Mamba3BlockCache  # the reference's name for the same record (backbones/mamba3/block.py)
+Mamba3BlockForwardCache = Mamba3BlockCache  # the reference's name for the same record
 
 
 class Mamba3Block(nn.Module):
@@ -41,19 +57,45 @@ class Mamba3Block(nn.Module):
             device=device, dtype=dtype,
         )
 
-    def forward(self, hidden_states: torch.Tensor, residual: Optional[torch.Tensor] = None, seq_idx=None):
+    def forward(self, hidden_states: torch.Tensor, residual: Optional[torch.Tensor] = None, seq_idx=None, **kwargs):
         residual = hidden_states if residual is None else hidden_states + residual
-        hidden_states = self.mixer(self.norm(residual.to(dtype=self.norm.weight.dtype)))
+        hidden_states = self.mixer(self.norm(residual.to(dtype=self.norm.weight.dtype)), seq_idx=seq_idx, **kwargs)
         return hidden_states, residual
 
-    def forward_with_cache(self, hidden_states: torch.Tensor, residual: Optional[torch.Tensor] = None):
-        residual = hidden_states if residual is None else hidden_states + residual
-        normed = self.norm(residual.to(dtype=self.norm.weight.dtype))
-        out, mixer_cache = self.mixer.forward_with_cache(normed)
-        return out, residual, Mamba3BlockCache(residual_out=residual, normed=normed, mixer=mixer_cache)
+    def forward_with_cache(self, hidden_states: torch.Tensor, residual: Optional[torch.Tensor] = None, **kwargs):
+        residual_out = hidden_states if residual is None else hidden_states + residual
+        normed = self.norm(residual_out.to(dtype=self.norm.weight.dtype))
+        out, mixer_cache = self.mixer.forward_with_cache(normed, **kwargs)
+        return out, residual_out, Mamba3BlockCache(residual_out=residual_out, normed=normed, mixer=mixer_cache,
+                                                   hidden_input=hidden_states, residual_input=residual, hidden_output=out)
 
-    def input_pullback_matrix(self, hidden_states: torch.Tensor, output_cotangent_basis: torch.Tensor) -> torch.Tensor:
-        """Pullback of a basis [B, P, L, D] through ``x -> mixer(norm(x)) + x`` (first block of a range)."""
+    def input_pullback_matrix(self, first, output_cotangent_basis: torch.Tensor, g_residual_out: Optional[torch.Tensor] = None):
+        """Two call forms.
+
+        ``(hidden_states [B, L, D], basis [B, P, L, D]) -> [B, P, L, D]``: the pullback through
+        ``x -> mixer(norm(x)) + x`` (a block that opens a range, output = branch + stream).
+
+        ``(cache, g_hidden_out, g_residual_out=None) -> (g_hidden_in, g_residual_in)``: the reference's form
+        (backbones/mamba3/block.py:104-123) on a ``forward_with_cache`` record: the cotangent of the branch output goes
+        through the mixer and the norm, the cotangent of the outgoing stream is added, and both inputs (branch and
+        incoming stream, which are summed on entry) receive the total; ``g_residual_in`` is None for a block that had no
+        incoming stream."""
+        if isinstance(first, Mamba3BlockCache):
+            cache, g_hidden_out = first, output_cotangent_basis
+            if g_hidden_out.dim() != 4:
+                raise ValueError("g_hidden_out must have shape [B, P, L, D].")
+            bsz, nbasis = g_hidden_out.shape[:2]
+            stream = cache.residual_out.detach()
+            rep = stream.repeat_interleave(nbasis, dim=0).requires_grad_(True)
+            with torch.enable_grad():
+                out = self.mixer(self.norm(rep.to(dtype=self.norm.weight.dtype)))
+            (g,) = torch.autograd.grad(out, rep, g_hidden_out.reshape(bsz * nbasis, *stream.shape[1:]).to(out.dtype))
+            total = g.reshape(bsz, nbasis, *stream.shape[1:])
+            if g_residual_out is not None:
+                total = total + g_residual_out.to(device=total.device, dtype=total.dtype)
+            total = total.to(device=g_hidden_out.device, dtype=g_hidden_out.dtype)
+            return total, (None if cache.residual_input is None else total.clone())
+        hidden_states = first
         bsz, nbasis = output_cotangent_basis.shape[:2]
         rep = hidden_states.detach().repeat_interleave(nbasis, dim=0).requires_grad_(True)
         with torch.enable_grad():

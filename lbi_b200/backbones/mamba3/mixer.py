@@ -19,7 +19,7 @@ from torch import nn
 
 from ...ops import ssd as ops_ssd
 from ..norms import RMSNormGated
-from .siso import mamba3_siso_chunked
+from .siso import _rotate_pairs, mamba3_siso_chunked
 
 
 @dataclass
@@ -148,18 +148,97 @@ class Mamba3(nn.Module):
         )
 
     def forward(self, u: torch.Tensor, seq_idx=None, cu_seqlens=None, inference_params=None) -> torch.Tensor:
-        if cu_seqlens is not None or inference_params is not None:
-            raise NotImplementedError("only the full-sequence training path is implemented")
+        self._full_sequence_only(cu_seqlens, inference_params)
         return self._forward_impl(u)
 
-    def forward_with_cache(self, u: torch.Tensor):
+    def forward_with_cache(self, u: torch.Tensor, seq_idx=None, cu_seqlens=None, inference_params=None):
+        self._full_sequence_only(cu_seqlens, inference_params)
         return self._forward_impl(u, return_cache=True)
 
-    def input_pullback_matrix(self, u: torch.Tensor, output_cotangent_basis: torch.Tensor) -> torch.Tensor:
-        """Pull a basis of output cotangents [B, P, L, D] back to the mixer input -> [B, P, L, D]."""
+    @staticmethod
+    def _full_sequence_only(cu_seqlens, inference_params) -> None:
+        if cu_seqlens is not None:
+            raise NotImplementedError("variable-length batches are not supported by the Mamba-3 mixer")
+        if inference_params is not None:
+            raise NotImplementedError("decode with allocate_inference_cache() and step(); forward() is the full-sequence path")
+
+    def input_pullback_matrix(self, first, output_cotangent_basis: torch.Tensor) -> torch.Tensor:
+        """Pull a basis of output cotangents [B, P, L, D] back to the mixer input -> [B, P, L, D].
+
+        ``first`` is the mixer input ``u`` or, as in the reference (backbones/mamba3/mamba3.py:306-325), the
+        ``Mamba3ForwardCache`` of a ``forward_with_cache`` call, whose ``input_u`` is then used.  All directions go through
+        one recomputed forward on a replicated batch instead of one backward pass per direction over a retained graph."""
+        u = first.input_u if isinstance(first, Mamba3ForwardCache) else first
+        if output_cotangent_basis.dim() != 4:
+            raise ValueError("the cotangent basis must have shape [B, P, L, D].")
         bsz, nbasis = output_cotangent_basis.shape[:2]
+        if tuple(output_cotangent_basis.shape[2:]) != tuple(u.shape[1:]) or output_cotangent_basis.shape[0] != u.shape[0]:
+            raise ValueError("the cotangent basis does not match the mixer output shape.")
         rep = u.detach().repeat_interleave(nbasis, dim=0).requires_grad_(True)
         with torch.enable_grad():
             out = self._forward_impl(rep)
         (g,) = torch.autograd.grad(out, rep, output_cotangent_basis.reshape(bsz * nbasis, *u.shape[1:]).to(out.dtype))
-        return g.reshape(bsz, nbasis, *u.shape[1:])
+        return g.reshape(bsz, nbasis, *u.shape[1:]).to(output_cotangent_basis.dtype)
+
+    # ------------------------------------------------------------------ token-by-token decode
+    def allocate_inference_cache(self, batch_size, max_seqlen=None, device=None, dtype=None, inplace_state=None, **_unused):
+        """Zeroed decode state ``(angle_state, ssm_state, k_state, v_state)`` with the reference's shapes
+        (backbones/mamba3/mamba3.py:363-403): cumulative rotary phase [B, H, S] fp32, SSM state [B, H, P, N] fp32, the previous
+        token's rotated key [B, 1, H, N] and value [B, H, P]."""
+        device = self.in_proj.weight.device if device is None else device
+        dtype = self.in_proj.weight.dtype if dtype is None else dtype
+        angle_state = torch.zeros(batch_size, self.nheads, self.num_rope_angles, device=device, dtype=torch.float32)
+        ssm_state = torch.zeros(batch_size, self.nheads, self.headdim, self.d_state, device=device, dtype=torch.float32)
+        k_state = torch.zeros(batch_size, 1, self.nheads, self.d_state, device=device, dtype=dtype)
+        v_state = torch.zeros(batch_size, self.nheads, self.headdim, device=device, dtype=dtype)
+        return angle_state, ssm_state, k_state, v_state
+
+    @torch.no_grad()
+    def step(self, u: torch.Tensor, angle_state, ssm_state, k_state, v_state, **_unused):
+        """One token of the recurrence: u [B, D] (or [B, 1, D]) -> output of the same shape; the four state tensors are
+        updated in place.  Feeding a sequence token by token from a zeroed cache reproduces ``forward`` (the reference declares
+        this method and leaves it unimplemented, backbones/mamba3/mamba3.py:360-361).
+
+        The trapezoid rule gives token t a second weight dt_{t+1} (1 - sigmoid(trap_{t+1})) that is only known one token later,
+        so ``ssm_state`` holds the state without that share of the newest token and ``k_state`` / ``v_state`` keep its rotated key
+        and value; the share is added at the start of the next step, before the decay."""
+        squeeze = u.dim() == 3
+        if squeeze:
+            if u.shape[1] != 1:
+                raise ValueError("step() takes one token per sequence")
+            u = u[:, 0]
+        bsz = u.shape[0]
+        gn = self.d_state * self.num_bc_heads
+        proj = self.in_proj(u)
+        z, x, B, C, dd_dt, dd_A, trap, angles = torch.split(
+            proj, [self.d_inner, self.d_inner, gn, gn, self.nheads, self.nheads, self.nheads, self.num_rope_angles], dim=-1
+        )
+        z = z.reshape(bsz, self.nheads, self.headdim)
+        x = x.reshape(bsz, self.nheads, self.headdim)
+        B = self.B_norm(B.reshape(bsz, self.num_bc_heads, self.d_state)).float()
+        C = self.C_norm(C.reshape(bsz, self.num_bc_heads, self.d_state)).float()
+        rep = self.nheads // self.num_bc_heads
+        A = torch.clamp(-F.softplus(dd_A.float()), max=-self.A_floor)
+        dt = F.softplus(dd_dt.float() + self.dt_bias.float())  # [B, H]
+        sig = torch.sigmoid(trap.float())
+        theta = angle_state + math.pi * torch.tanh(angles.float()).unsqueeze(1) * dt.unsqueeze(-1)
+        theta = theta - (2.0 * math.pi) * torch.floor(theta / (2.0 * math.pi))
+        angle_state.copy_(theta)
+        q = C.repeat_interleave(rep, dim=1) + self.C_bias.float().squeeze(1)[None]
+        k = B.repeat_interleave(rep, dim=1) + self.B_bias.float().squeeze(1)[None]
+        qr, kr = _rotate_pairs(q, theta), _rotate_pairs(k, theta)
+        xf = x.float()
+        carry = (dt * (1.0 - sig))[..., None, None] * v_state.float()[..., None] * k_state.float()[:, 0, :, None, :]
+        h = (ssm_state + carry) * torch.exp(A * dt)[..., None, None]
+        gamma = dt * sig
+        skip = gamma * (q * k).sum(dim=-1) + (self.D.float()[None] if self.D is not None else 0.0)
+        y = torch.einsum("bhpn,bhn->bhp", h, qr) + skip[..., None] * xf
+        ssm_state.copy_(h + gamma[..., None, None] * xf[..., None] * kr[:, :, None, :])
+        k_state.copy_(kr.unsqueeze(1).to(k_state.dtype))
+        v_state.copy_(x.to(v_state.dtype))
+        if self.is_outproj_norm:
+            y = self.norm(y.reshape(bsz, self.d_inner).to(x.dtype), z.reshape(bsz, self.d_inner))
+        else:
+            y = (y * F.silu(z.float())).reshape(bsz, self.d_inner)
+        out = self.out_proj(y.to(self.out_proj.weight.dtype))
+        return out.unsqueeze(1) if squeeze else out

@@ -9,7 +9,8 @@ from torch import nn
 from .base import ADResult, collect_named_grads
 
 
-def autograd_backward_step(model: nn.Module, loss: torch.Tensor) -> dict:
+def autograd_backward_step(model: nn.Module, loss: torch.Tensor | None = None, *, ce_loss: torch.Tensor | None = None) -> dict:
+    loss = ce_loss if loss is None else loss  # ``ce_loss`` is the reference's keyword (backward/autograd.py:27)
     model.zero_grad(set_to_none=True)
     loss.backward()
     return collect_named_grads(model)

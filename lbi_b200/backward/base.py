@@ -32,6 +32,10 @@ class ScanBackpropModel(Protocol):
     interface: Any
     region_backend: Any
 
+    def named_parameters(self, *args: Any, **kwargs: Any) -> Any: ...
+
+    def zero_grad(self, *args: Any, **kwargs: Any) -> None: ...
+
     def output_head_vjp_parameters(self) -> list[nn.Parameter]: ...
 
     def canvas_vjp_parameters(self) -> list[nn.Parameter]: ...

@@ -36,6 +36,9 @@ def _state_in(cache, k):
 class TorchGraphInterfacePullbackProvider:
     name = "graph"
 
+    def __init__(self, basis_chunk: int = 1) -> None:
+        self.basis_chunk = int(basis_chunk)  # unused: one batched VJP covers all directions (kept for the reference's signature)
+
     def materialize_state_jacobian_t(self, *, model, cache, regions=None):
         out = []
         for k in _regions(model, regions):

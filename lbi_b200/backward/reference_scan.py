@@ -12,7 +12,24 @@ from .base import ADResult, LBIBackwardResult, assign_grad_map, is_scan_backprop
 from .local_vjp import TorchAutogradLocalVJPProvider, surrogate_backward
 
 
-def lbi_reference_scan_backward_step(*, model: Any, loss: torch.Tensor, cache: dict) -> LBIBackwardResult:
+def lbi_reference_scan_backward_step(model: Any = None, *, loss: torch.Tensor | None = None, cache: dict,
+                                     ce_loss: torch.Tensor | None = None, state_jacobian_mode: str | None = None,
+                                     state_jacobian_basis_chunk: int = 1, compute_interface_jacobian_stats: bool = False,
+                                     include_interface_jacobian_suffix: bool = False) -> LBIBackwardResult:
+    """With ``state_jacobian_mode`` left at None the state cotangents go down the forward graph one VJP at a time; with a
+    provider name ("graph", "recompute", ...) the call is the Jacobian scan with that provider, which is what the reference's
+    function of this name runs (backward/reference_scan.py:12-34).  ``ce_loss`` is the reference's keyword for ``loss``."""
+    loss = ce_loss if loss is None else loss
+    if model is None or loss is None:
+        raise TypeError("lbi_reference_scan_backward_step needs a model and a loss")
+    if state_jacobian_mode is not None:
+        from .pullbacks import build_interface_pullback_provider
+        from .scan import lbi_scan_backward_step
+
+        provider = build_interface_pullback_provider(state_jacobian_mode, basis_chunk=state_jacobian_basis_chunk)
+        return lbi_scan_backward_step(model, loss=loss, cache=cache, pullback_provider=provider,
+                                      compute_interface_jacobian_stats=compute_interface_jacobian_stats,
+                                      include_interface_jacobian_suffix=include_interface_jacobian_suffix)
     k_regions = model.num_regions
     if cache.get("detached_states", False):
         leaves = cache["state_inputs"]

@@ -14,13 +14,14 @@ between the scanned cotangents and a sequential mat-vec chain over the same Jaco
 """
 from __future__ import annotations
 
+import inspect
 from typing import Any
 
 import torch
 from torch import nn
 
 from .base import ADResult, LBIBackwardResult, assign_grad_map, is_scan_backprop_model
-from .local_vjp import LocalVJPProvider, TorchAutogradLocalVJPProvider, surrogate_backward
+from .local_vjp import LocalVJPProvider, TorchAutogradLocalVJPProvider, adapt_local_vjp_provider, surrogate_backward
 from .pullbacks import InterfacePullbackProvider, build_interface_pullback_provider
 from .reference_scan import ReferenceScanEngine  # noqa: F401  (importable from here as in the reference, backward/scan.py:171)
 from .suffix_scan import (
@@ -32,6 +33,17 @@ from .suffix_scan import (
 )
 
 
+def _materialize(provider, model, cache, regions) -> list:
+    """Jacobians of the listed regions; a provider written to the reference's protocol (no ``regions`` keyword,
+    backward/pullbacks.py:9-18) computes all of them and the list is cut here."""
+    fn = provider.materialize_state_jacobian_t
+    params = inspect.signature(fn).parameters
+    if "regions" in params or any(p.kind is inspect.Parameter.VAR_KEYWORD for p in params.values()):
+        return fn(model=model, cache=cache, regions=regions)
+    every = fn(model=model, cache=cache)
+    return [every[k] for k in regions]
+
+
 def _rms_between(a_list, b_list) -> float:
     num = sum(float((a.detach().float() - b.detach().float()).square().sum()) for a, b in zip(a_list, b_list))
     den = sum(a.numel() for a in a_list)
@@ -39,23 +51,27 @@ def _rms_between(a_list, b_list) -> float:
 
 
 def lbi_scan_backward_step(
+    model: Any = None,
     *,
-    model: Any,
-    loss: torch.Tensor,
+    loss: torch.Tensor | None = None,
     cache: dict,
     pullback_provider: InterfacePullbackProvider,
     local_vjp_provider: LocalVJPProvider | None = None,
     compute_interface_jacobian_stats: bool = False,
     include_interface_jacobian_suffix: bool = False,
     compute_scan_diagnostic: bool = True,
+    ce_loss: torch.Tensor | None = None,
 ) -> LBIBackwardResult:
+    loss = ce_loss if loss is None else loss  # ``ce_loss`` is the reference's keyword (backward/scan.py:18-27)
+    if model is None or loss is None:
+        raise TypeError("lbi_scan_backward_step needs a model and a loss")
     k_regions = model.num_regions
     stats = None
     if cache.get("detached_states", False):
         leaves = cache["state_inputs"]
         direct = torch.autograd.grad(loss, leaves, retain_graph=True, allow_unused=True)
         offsets = [torch.zeros_like(s, dtype=torch.float32) if g is None else g.float() for s, g in zip(leaves, direct)]
-        jacobians = pullback_provider.materialize_state_jacobian_t(model=model, cache=cache, regions=range(k_regions - 1))
+        jacobians = _materialize(pullback_provider, model, cache, range(k_regions - 1))
         if compute_interface_jacobian_stats and jacobians:
             stats = interface_state_jacobian_t_stats(jacobians, include_suffix=include_interface_jacobian_suffix)
         only_last = all(not model.plan.region_has_loss(k) for k in range(k_regions - 1)) if hasattr(model, "plan") else False
@@ -70,7 +86,7 @@ def lbi_scan_backward_step(
     # connected graph: the reference's sequence of local VJPs (loss terms only in the last region)
     if getattr(model, "region_axis", "depth") != "depth":
         raise ValueError("sequence-axis regions need a cache built with detach_states=True")
-    vjp = local_vjp_provider or TorchAutogradLocalVJPProvider()
+    vjp = adapt_local_vjp_provider(local_vjp_provider) or TorchAutogradLocalVJPProvider()
     grad_map = vjp.initialize_grad_map(model)
     vjp.output_head_grads(model=model, loss=loss, grad_map=grad_map)
     states = cache["states"]
@@ -79,7 +95,7 @@ def lbi_scan_backward_step(
         g = [vjp.state_adjoint_from_loss(loss=loss, state=states[0])]
     else:
         g_last = vjp.state_adjoint_from_loss(loss=loss, state=states[k_regions - 1])
-        jacobians = pullback_provider.materialize_state_jacobian_t(model=model, cache=cache, regions=range(k_regions - 1))
+        jacobians = _materialize(pullback_provider, model, cache, range(k_regions - 1))
         if compute_interface_jacobian_stats:
             stats = interface_state_jacobian_t_stats(jacobians, include_suffix=include_interface_jacobian_suffix)
         g = propagate_state_adjoint_from_last_region_input([*jacobians, None], g_last)

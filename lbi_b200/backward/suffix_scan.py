@@ -13,34 +13,45 @@ import torch
 from .. import ops
 
 
-def compose_suffix_jacobian_t(state_jacobian_t: Sequence[torch.Tensor]) -> list[torch.Tensor]:
-    """K matrices [B, R, R] -> K + 1 suffix products (S_k = A_k^T ... A_{K-1}^T, S_K = I), fp32."""
-    if len(state_jacobian_t) == 0:
-        raise ValueError("need at least one Jacobian to infer the state shape; handle K = 0 at the call site")
-    stacked = torch.stack([m for m in state_jacobian_t], dim=1)
+def compose_suffix_jacobian_t(state_jacobians_t: Sequence[torch.Tensor]) -> list[torch.Tensor]:
+    """K matrices [B, R, R] -> K + 1 suffix products (S_k = A_k^T ... A_{K-1}^T, S_K = I), fp32; none for K = 0."""
+    if len(state_jacobians_t) == 0:
+        return []
+    if state_jacobians_t[0].shape[-1] != state_jacobians_t[0].shape[-2]:
+        raise ValueError("interface state Jacobian-transpose tensors must be square.")
+    stacked = torch.stack([m for m in state_jacobians_t], dim=1)
     suffix = ops.suffix_scan_pullbacks(stacked)
     return list(suffix.unbind(dim=1))
 
 
-def apply_jacobian_t(jacobian_t: torch.Tensor, cotangent: torch.Tensor) -> torch.Tensor:
+def apply_jacobian_t(jacobian_t: torch.Tensor, cotangent: torch.Tensor, *, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``J^T g`` per batch row in the wider of the two dtypes; ``out_dtype`` casts the result (default: leave it wide)."""
     dtype = torch.promote_types(jacobian_t.dtype, cotangent.dtype)
-    return torch.einsum("bij,bj->bi", jacobian_t.to(dtype), cotangent.to(dtype))
+    out = torch.einsum("bij,bj->bi", jacobian_t.to(dtype), cotangent.to(device=jacobian_t.device, dtype=dtype))
+    return out if out_dtype is None else out.to(out_dtype)
 
 
-def propagate_state_adjoint_with_jacobian_scan(state_jacobian_t: Sequence[torch.Tensor], top_cotangent: torch.Tensor) -> list[torch.Tensor]:
-    """Seed at s_K: returns [g_0, ..., g_K] with g_K = top_cotangent."""
-    if len(state_jacobian_t) == 0:
-        return [top_cotangent]
-    suffix = compose_suffix_jacobian_t(state_jacobian_t)
-    return [apply_jacobian_t(s, top_cotangent) for s in suffix]
+def propagate_state_adjoint_with_jacobian_scan(state_jacobians_t: Sequence[torch.Tensor], g_top_state: torch.Tensor) -> list[torch.Tensor]:
+    """Seed at s_K: returns [g_0, ..., g_K] with g_K = g_top_state."""
+    if len(state_jacobians_t) == 0:
+        return [g_top_state]
+    suffix = compose_suffix_jacobian_t(state_jacobians_t)
+    return [apply_jacobian_t(s, g_top_state) for s in suffix]
 
 
-def propagate_state_adjoint_from_last_region_input(state_jacobian_t: Sequence[torch.Tensor], last_input_cotangent: torch.Tensor) -> list[torch.Tensor]:
+def propagate_state_adjoint_from_last_region_input(state_jacobians_t: Sequence[torch.Tensor], g_last_input_state: torch.Tensor,
+                                                   *, num_regions: int | None = None) -> list[torch.Tensor]:
     """Seed at s_{K-1} (the input state of the last region): the last Jacobian is not needed.
 
-    Accepts either K matrices (the last one is dropped, as the reference does) or K - 1."""
-    mats = list(state_jacobian_t)
-    return propagate_state_adjoint_with_jacobian_scan(mats[:-1] if mats else mats, last_input_cotangent)
+    Accepts either K matrices (the last one is dropped, as the reference does) or K - 1; with ``num_regions`` given the
+    list must hold exactly that many (reference backward/suffix_scan.py:59-79)."""
+    mats = list(state_jacobians_t)
+    if num_regions is not None:
+        if len(mats) != num_regions:
+            raise ValueError("state_jacobians_t length mismatch.")
+        if num_regions == 0:
+            return []
+    return propagate_state_adjoint_with_jacobian_scan(mats[:-1] if mats else mats, g_last_input_state)
 
 
 def propagate_state_adjoint_affine(state_jacobian_t: Sequence[torch.Tensor], offsets: Sequence[torch.Tensor]) -> list[torch.Tensor]:
@@ -91,11 +102,11 @@ def _matrix_norms(mats: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     return torch.linalg.matrix_norm(mats, ord=2), torch.linalg.matrix_norm(mats, ord="fro")
 
 
-def interface_state_jacobian_t_stats(state_jacobian_t: Sequence[torch.Tensor], *, include_suffix: bool = False) -> dict[str, float]:
+def interface_state_jacobian_t_stats(state_jacobians_t: Sequence[torch.Tensor], *, include_suffix: bool = False) -> dict[str, float]:
     """Frobenius / spectral norms of the local Jacobians (and optionally of the suffix products)."""
-    if len(state_jacobian_t) == 0:
+    if len(state_jacobians_t) == 0:
         return {}
-    mats = torch.stack([m.float() for m in state_jacobian_t], dim=1)  # [B, K, R, R]
+    mats = torch.stack([m.float() for m in state_jacobians_t], dim=1)  # [B, K, R, R]
     r = mats.shape[-1]
     spec, frob = _matrix_norms(mats)
     stats = {
@@ -106,7 +117,7 @@ def interface_state_jacobian_t_stats(state_jacobian_t: Sequence[torch.Tensor], *
         "jac_local_frob_normed_mean": float((frob / (r ** 0.5)).mean()),
     }
     if include_suffix:
-        suffix = torch.stack(compose_suffix_jacobian_t(list(state_jacobian_t))[:-1], dim=1)
+        suffix = torch.stack(compose_suffix_jacobian_t(list(state_jacobians_t))[:-1], dim=1)
         sspec = _matrix_norms(suffix)[0]
         stats["jac_suffix_spec_mean"] = float(sspec.mean())
         stats["jac_suffix_spec_max"] = float(sspec.max())

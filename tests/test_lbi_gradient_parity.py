@@ -98,6 +98,109 @@ def test_connected_graph_scan_follows_reference_hooks():
     assert none_names and all(n.startswith(("interface.encoders.3", "interface.norms.3")) for n in none_names)
 
 
+class _ForeignLocalVJP:
+    """A provider written against the reference's hook names only (backward/local_vjp.py:10-62)."""
+
+    name = "foreign"
+
+    def __init__(self):
+        self.calls = []
+
+    def _store(self, model, grad_map, params, grads):
+        names = {id(p): n for n, p in model.named_parameters()}
+        for p, g in zip(params, grads):
+            if g is not None:
+                n = names[id(p)]
+                grad_map[n] = g if grad_map[n] is None else grad_map[n] + g
+
+    def new_grad_map(self, model):
+        self.calls.append("new")
+        return {n: None for n, p in model.named_parameters() if p.requires_grad}
+
+    def store_output_head_grads(self, *, model, loss, grad_map):
+        self.calls.append("head")
+        params = model.output_head_vjp_parameters()
+        self._store(model, grad_map, params, torch.autograd.grad(loss, params, retain_graph=True, allow_unused=True))
+
+    def state_adjoint_from_loss(self, *, loss, state):
+        return torch.autograd.grad(loss, state, retain_graph=True)[0]
+
+    def store_initial_interface_grads(self, *, model, state0, state0_adjoint, grad_map):
+        self.calls.append("initial")
+        params = model.interface.initial_vjp_parameters()
+        self._store(model, grad_map, params, torch.autograd.grad(state0, params, state0_adjoint, retain_graph=True, allow_unused=True))
+
+    def store_region_grads(self, *, model, loss, states, region_index, num_regions, state_adjoints, grad_map):
+        self.calls.append(f"region{region_index}")
+        params = [*model.region_backend.parameters_for_region(region_index), *model.interface.region_vjp_parameters(region_index)]
+        if region_index < num_regions - 1:
+            grads = torch.autograd.grad(states[region_index + 1], params, state_adjoints[region_index + 1], retain_graph=True,
+                                        allow_unused=True)
+        else:
+            grads = torch.autograd.grad(loss, params, retain_graph=True, allow_unused=True)
+        self._store(model, grad_map, params, grads)
+
+    def store_shared_canvas_grads(self, *, model, loss, grad_map):
+        self.calls.append("shared")
+        params = model.shared_local_vjp_parameters()
+        self._store(model, grad_map, params, torch.autograd.grad(loss, params, allow_unused=True))
+
+
+class _ForeignPullback:
+    """No ``regions`` keyword, as in the reference's protocol (backward/pullbacks.py:9-18)."""
+
+    name = "foreign_graph"
+
+    def materialize_state_jacobian_t(self, *, model, cache):
+        from lbi_b200.backward.pullbacks import materialize_interface_state_jacobian_t_graph
+
+        return materialize_interface_state_jacobian_t_graph(model=model, cache=cache)
+
+
+def test_scan_step_with_providers_and_keywords_of_the_reference():
+    from lbi_b200.backward import TorchAutogradLocalVJPProvider, autograd_backward_step, lbi_scan_backward_step
+    from lbi_b200.backward.reference_scan import lbi_reference_scan_backward_step
+
+    model = build("transformer", "depth", 4)
+    ids, tgt = batch()
+
+    def fresh():
+        logits, cache = model.forward_with_cache(ids)
+        return F.cross_entropy(logits.float().reshape(-1, VOCAB), tgt.reshape(-1)), cache
+
+    loss, _ = fresh()
+    ref = autograd_backward_step(model, ce_loss=loss)
+    loss, cache = fresh()
+    foreign = _ForeignLocalVJP()
+    got = lbi_scan_backward_step(model, ce_loss=loss, cache=cache, pullback_provider=_ForeignPullback(), local_vjp_provider=foreign)
+    assert_parity(ref, got.grad_map)
+    assert foreign.calls == ["new", "head", "initial", "region0", "region1", "region2", "region3", "shared"]
+
+    # this package's provider through the reference's hook names
+    loss, cache = fresh()
+    own = TorchAutogradLocalVJPProvider()
+    gm = own.new_grad_map(model)
+    own.store_output_head_grads(model=model, loss=loss, grad_map=gm)
+    states = cache["states"]
+    adj = [None] * 5
+    adj[3] = own.state_adjoint_from_loss(loss=loss, state=states[3])
+    for k in (2, 1, 0):
+        (adj[k],) = torch.autograd.grad(states[k + 1], states[k], adj[k + 1], retain_graph=True)
+    own.store_initial_interface_grads(model=model, state0=states[0], state0_adjoint=adj[0], grad_map=gm)
+    for k in range(4):
+        own.store_region_grads(model=model, loss=loss, states=states, region_index=k, num_regions=4, state_adjoints=adj, grad_map=gm)
+    own.store_shared_canvas_grads(model=model, loss=loss, grad_map=gm)
+    assert_parity(ref, gm)
+
+    for mode in ("graph", "recompute"):
+        loss, cache = fresh()
+        res = lbi_reference_scan_backward_step(model, ce_loss=loss, cache=cache, state_jacobian_mode=mode,
+                                               state_jacobian_basis_chunk=3, compute_interface_jacobian_stats=True,
+                                               include_interface_jacobian_suffix=True)
+        assert_parity(ref, res.grad_map)
+        assert res.interface_jacobian_stats
+
+
 @pytest.mark.parametrize("axis,regions,tie", [("depth", 2, False), ("depth", 4, True), ("sequence", 4, True), ("sequence", 8, False)])
 def test_fast_engine_matches_autograd(axis, regions, tie):
     model = build("transformer", axis, regions, tie=tie, layers=4 if regions <= 4 else 8)

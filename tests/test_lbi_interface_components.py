@@ -169,6 +169,78 @@ def test_mamba3_siso_matches_recurrence_and_block_pullback():
     assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
 
 
+@pytest.mark.parametrize("outproj_norm", [False, True])
+def test_mamba3_decode_steps_reproduce_the_full_sequence(outproj_norm):
+    from lbi_b200.backbones.mamba3.mixer import Mamba3
+
+    torch.manual_seed(11)
+    mixer = Mamba3(d_model=32, d_state=16, expand=2, headdim=16, chunk_size=8, is_outproj_norm=outproj_norm)
+    u = torch.randn(2, 21, 32)
+    with torch.no_grad():
+        want = mixer(u)
+    states = mixer.allocate_inference_cache(2, 21)
+    assert [tuple(t.shape) for t in states] == [(2, 4, 4), (2, 4, 16, 16), (2, 1, 4, 16), (2, 4, 16)]
+    assert states[0].dtype == states[1].dtype == torch.float32
+    got = torch.stack([mixer.step(u[:, t], *states) for t in range(21)], dim=1)
+    assert torch.allclose(got, want, atol=2e-6, rtol=1e-5)
+    assert mixer.step(u[:, :1], *mixer.allocate_inference_cache(2, 1)).shape == (2, 1, 32)
+    assert float(states[1].abs().sum()) > 0 and float(states[0].max()) < 2 * torch.pi
+    with pytest.raises(NotImplementedError):
+        mixer(u, inference_params=object())
+    with pytest.raises(NotImplementedError):
+        mixer.forward_with_cache(u, cu_seqlens=torch.tensor([0, 21]))
+
+
+def test_mamba3_pullbacks_in_the_cache_form_of_the_reference():
+    torch.manual_seed(12)
+    block = Mamba3Block(32, d_state=16, headdim=16, chunk_size=8)
+    hidden, stream_in = torch.randn(2, 12, 32, requires_grad=True), torch.randn(2, 12, 32, requires_grad=True)
+    basis, basis_stream = torch.randn(2, 3, 12, 32), torch.randn(2, 3, 12, 32)
+    out, stream_out, cache = block.forward_with_cache(hidden, stream_in)
+    assert cache.residual_output is stream_out and cache.norm_input is cache.normed and cache.mixer_cache is cache.mixer
+    assert cache.hidden_input is hidden and cache.residual_input is stream_in and cache.hidden_output is out
+    g_hidden, g_stream = block.input_pullback_matrix(cache, basis, basis_stream)
+    for i in range(3):
+        want_h, want_s = torch.autograd.grad([out, stream_out], [hidden, stream_in], [basis[:, i], basis_stream[:, i]],
+                                             retain_graph=True)
+        assert torch.allclose(g_hidden[:, i], want_h, atol=1e-5, rtol=1e-4)
+        assert torch.allclose(g_stream[:, i], want_s, atol=1e-5, rtol=1e-4)
+    _, _, first = block.forward_with_cache(hidden.detach())
+    g_only, none = block.input_pullback_matrix(first, basis)
+    assert none is None and g_only.shape == basis.shape
+    mixer_in = torch.randn(2, 12, 32, requires_grad=True)
+    mixer_out, mixer_cache = block.mixer.forward_with_cache(mixer_in)
+    got = block.mixer.input_pullback_matrix(mixer_cache, basis)
+    want = torch.stack([torch.autograd.grad(mixer_out, mixer_in, basis[:, i], retain_graph=True)[0] for i in range(3)], dim=1)
+    assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+    with pytest.raises(ValueError):
+        block.mixer.input_pullback_matrix(mixer_cache, basis[:, :, :5])
+
+
+def test_mamba2_packed_sequences_initial_states_and_conv_init():
+    from lbi_b200.backbones.mamba2.mixer import Mamba2Simple
+
+    torch.manual_seed(13)
+    mixer = Mamba2Simple(32, d_state=16, headdim=16, chunk_size=8, conv_init=0.3, learnable_init_states=True)
+    assert float(mixer.conv1d.weight.detach().abs().max()) <= 0.3 and mixer.init_states.shape == (4, 16, 16)
+    with torch.no_grad():
+        mixer.init_states.normal_()
+    u = torch.randn(2, 20, 32)
+    seq_idx = torch.tensor([[0] * 7 + [1] * 13, [0] * 20])
+    packed = mixer(u, seq_idx=seq_idx)
+    assert torch.equal(packed[0, :7], mixer(u[:1, :7])[0]) and torch.equal(packed[1], mixer(u[1:])[0])
+    plain = Mamba2Simple(32, d_state=16, headdim=16, chunk_size=8)
+    plain.load_state_dict({k: v for k, v in mixer.state_dict().items() if k != "init_states"})
+    assert torch.allclose(packed[0, 7:], plain(u[:1, 7:])[0], atol=1e-6)           # later sequences start from a zero state
+    assert not torch.allclose(packed[0, :7], plain(u[:1, :7])[0], atol=1e-4)       # the first one from the learnt state
+    packed.sum().backward()
+    assert float(mixer.init_states.grad.abs().sum()) > 0
+    with pytest.raises(ValueError):
+        Mamba2Simple(32, d_state=16, headdim=16, activation="relu")
+    with pytest.raises(ValueError):
+        mixer(u, seq_idx=seq_idx[:, :5])
+
+
 @pytest.mark.parametrize("d_conv,kv", [(0, 4), (4, 2)])
 def test_structured_transformer_lowering_matches_autograd_lowering(d_conv, kv):
     torch.manual_seed(7)
