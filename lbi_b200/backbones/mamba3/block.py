@@ -69,7 +69,8 @@ class Mamba3Block(nn.Module):
         return out, residual_out, Mamba3BlockCache(residual_out=residual_out, normed=normed, mixer=mixer_cache,
                                                    hidden_input=hidden_states, residual_input=residual, hidden_output=out)
 
-    def input_pullback_matrix(self, first, output_cotangent_basis: torch.Tensor, g_residual_out: Optional[torch.Tensor] = None):
+    def input_pullback_matrix(self, first=None, output_cotangent_basis: Optional[torch.Tensor] = None,
+                              g_residual_out: Optional[torch.Tensor] = None, *, cache=None, g_hidden_out=None, hidden_states=None):
         """Two call forms.
 
         ``(hidden_states [B, L, D], basis [B, P, L, D]) -> [B, P, L, D]``: the pullback through
@@ -80,6 +81,10 @@ class Mamba3Block(nn.Module):
         through the mixer and the norm, the cotangent of the outgoing stream is added, and both inputs (branch and
         incoming stream, which are summed on entry) receive the total; ``g_residual_in`` is None for a block that had no
         incoming stream."""
+        first = next((a for a in (first, cache, hidden_states) if a is not None), None)
+        output_cotangent_basis = g_hidden_out if output_cotangent_basis is None else output_cotangent_basis
+        if first is None or output_cotangent_basis is None:
+            raise TypeError("input_pullback_matrix needs a block input or cache and a cotangent basis")
         if isinstance(first, Mamba3BlockCache):
             cache, g_hidden_out = first, output_cotangent_basis
             if g_hidden_out.dim() != 4:

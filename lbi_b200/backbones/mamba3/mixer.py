@@ -104,7 +104,7 @@ class Mamba3(nn.Module):
             self.norm = RMSNormGated(self.d_inner, eps=1e-5, norm_before_gate=True, group_size=headdim, **fk)
         self.out_proj = nn.Linear(self.d_inner, d_model, bias=False, **fk)
 
-    def _forward_impl(self, u: torch.Tensor, *, return_cache: bool = False):
+    def _forward_impl(self, u: torch.Tensor, *, return_cache: bool = False, decode_states=None):
         bsz, seqlen, _ = u.shape
         proj = self.in_proj(u)
         gn = self.d_state * self.num_bc_heads
@@ -121,8 +121,14 @@ class Mamba3(nn.Module):
         DT = DT.transpose(1, 2)
         trap_t = trap.transpose(1, 2)
         angles_h = angles.unsqueeze(-2).expand(-1, -1, self.nheads, -1)
-        use_kernels = ops_ssd.siso_cuda_supported(x, C) and x.dtype == torch.bfloat16 and self.D is not None
-        siso = ops_ssd.mamba3_siso_cuda if use_kernels else partial(mamba3_siso_chunked, chunk_size=self.chunk_size)
+        use_kernels = (decode_states is None and ops_ssd.siso_cuda_supported(x, C) and x.dtype == torch.bfloat16
+                       and self.D is not None)
+        if decode_states is not None:
+            angle_state, ssm_state, k_state, v_state = decode_states
+            siso = partial(mamba3_siso_chunked, chunk_size=self.chunk_size, return_final_states=True,
+                           initial_states=(angle_state, ssm_state, k_state[:, 0], v_state))
+        else:
+            siso = ops_ssd.mamba3_siso_cuda if use_kernels else partial(mamba3_siso_chunked, chunk_size=self.chunk_size)
         y = siso(
             Q=C,
             K=B,
@@ -136,6 +142,12 @@ class Mamba3(nn.Module):
             D=self.D,
             Z=None if self.is_outproj_norm else z,
         )
+        if decode_states is not None:
+            y, angle_last, ssm_last, k_last, v_last = y
+            angle_state.copy_(angle_last)
+            ssm_state.copy_(ssm_last)
+            k_state.copy_(k_last.unsqueeze(1).to(k_state.dtype))
+            v_state.copy_(v_last.to(v_state.dtype))
         y = y.reshape(bsz, seqlen, self.d_inner)
         if self.is_outproj_norm:
             y = self.norm(y, z.reshape(bsz, seqlen, self.d_inner))
@@ -162,12 +174,17 @@ class Mamba3(nn.Module):
         if inference_params is not None:
             raise NotImplementedError("decode with allocate_inference_cache() and step(); forward() is the full-sequence path")
 
-    def input_pullback_matrix(self, first, output_cotangent_basis: torch.Tensor) -> torch.Tensor:
+    def input_pullback_matrix(self, first=None, output_cotangent_basis: torch.Tensor | None = None, *, cache=None, g_out=None,
+                              u=None) -> torch.Tensor:
         """Pull a basis of output cotangents [B, P, L, D] back to the mixer input -> [B, P, L, D].
 
         ``first`` is the mixer input ``u`` or, as in the reference (backbones/mamba3/mamba3.py:306-325), the
         ``Mamba3ForwardCache`` of a ``forward_with_cache`` call, whose ``input_u`` is then used.  All directions go through
         one recomputed forward on a replicated batch instead of one backward pass per direction over a retained graph."""
+        first = next((a for a in (first, cache, u) if a is not None), None)
+        output_cotangent_basis = g_out if output_cotangent_basis is None else output_cotangent_basis
+        if first is None or output_cotangent_basis is None:
+            raise TypeError("input_pullback_matrix needs a mixer input or cache and a cotangent basis")
         u = first.input_u if isinstance(first, Mamba3ForwardCache) else first
         if output_cotangent_basis.dim() != 4:
             raise ValueError("the cotangent basis must have shape [B, P, L, D].")
@@ -192,6 +209,12 @@ class Mamba3(nn.Module):
         k_state = torch.zeros(batch_size, 1, self.nheads, self.d_state, device=device, dtype=dtype)
         v_state = torch.zeros(batch_size, self.nheads, self.headdim, device=device, dtype=dtype)
         return angle_state, ssm_state, k_state, v_state
+
+    @torch.no_grad()
+    def prefill(self, u: torch.Tensor, angle_state, ssm_state, k_state, v_state) -> torch.Tensor:
+        """A whole prompt (or the next piece of one) u [B, L, D] in one chunked pass that starts from the four decode-state
+        tensors and leaves them at the last token, ready for ``step`` or another ``prefill``."""
+        return self._forward_impl(u, decode_states=(angle_state, ssm_state, k_state, v_state))
 
     @torch.no_grad()
     def step(self, u: torch.Tensor, angle_state, ssm_state, k_state, v_state, **_unused):

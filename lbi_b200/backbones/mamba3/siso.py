@@ -26,11 +26,14 @@ import torch.nn.functional as F
 TWO_PI = 2.0 * math.pi
 
 
-def angle_dt_cumsum(angles: torch.Tensor, dt: torch.Tensor) -> torch.Tensor:
-    """angles [b, l, h or 1, s], dt [b, l, h] -> cumulative rotary phase [b, l, h, s] in [0, 2pi)."""
+def angle_dt_cumsum(angles: torch.Tensor, dt: torch.Tensor, init: torch.Tensor | None = None) -> torch.Tensor:
+    """angles [b, l, h or 1, s], dt [b, l, h] -> cumulative rotary phase [b, l, h, s] in [0, 2pi); ``init`` [b, h, s] is the
+    phase reached before the first token."""
     vals = torch.tanh(angles.float()) * math.pi * dt.float().unsqueeze(-1)
     # the scan runs with the token axis innermost (an outer-axis cumulative sum is several times slower on the GPU)
     theta = torch.cumsum(vals.permute(0, 2, 3, 1).contiguous(), dim=-1).permute(0, 3, 1, 2)
+    if init is not None:
+        theta = theta + init.to(theta.dtype).unsqueeze(1)
     return theta - TWO_PI * torch.floor(theta / TWO_PI)
 
 
@@ -85,7 +88,7 @@ def _wide_kernels_ok(Q: torch.Tensor) -> bool:
     return native_available() and hasattr(ext(), "siso_prep_fwd")
 
 
-def _prepare_small(ADT, DT, Trap, Angles, compute_dtype):
+def _prepare_small(ADT, DT, Trap, Angles, compute_dtype, angle_state=None):
     """The [b, l, h]-sized part: log-decay, trapezoid weights gamma / scale, cumulative rotary phase theta [b, l, h, s]."""
     dt = DT.to(compute_dtype).transpose(1, 2)  # [b, l, h]
     adt = ADT.to(compute_dtype).transpose(1, 2)
@@ -93,11 +96,11 @@ def _prepare_small(ADT, DT, Trap, Angles, compute_dtype):
     gamma = dt * sig
     carry = F.pad((dt * (1.0 - sig))[:, 1:], (0, 0, 0, 1))  # dt_{t+1} (1 - sigma_{t+1}), zero after the last token
     scale = gamma + carry
-    theta = angle_dt_cumsum(Angles, dt).to(compute_dtype)
+    theta = angle_dt_cumsum(Angles, dt, angle_state).to(compute_dtype)
     return adt, gamma, scale, theta
 
 
-def _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, compute_dtype, fused: bool = False):
+def _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, compute_dtype, fused: bool = False, angle_state=None):
     """Shared preprocessing: per-head biased/rotated Q, K, trapezoid weights.
 
     The small tensors ([b, l, h] and [b, l, h, angles]: trapezoid weights, cumulative rotary phase) are PyTorch ops.  With
@@ -105,7 +108,7 @@ def _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, compute_dtype, fuse
     direction and Qr, Kr come back in bf16, the dtype the scan kernels take."""
     bsz, seqlen, nheads, _ = V.shape
     rep = nheads // Q.shape[2]
-    adt, gamma, scale, theta = _prepare_small(ADT, DT, Trap, Angles, compute_dtype)
+    adt, gamma, scale, theta = _prepare_small(ADT, DT, Trap, Angles, compute_dtype, angle_state)
     if fused and compute_dtype == torch.float32 and _wide_kernels_ok(Q):
         Qr, Kr, qk_dot = _WidePrepFunction.apply(Q, K, Q_bias, K_bias, theta, gamma, scale)
         return Qr, Kr, adt, qk_dot
@@ -138,11 +141,23 @@ def mamba3_siso_recurrent_reference(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angl
     return out
 
 
-def mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, Z=None, chunk_size: int = 64):
-    """Chunked evaluation in fp32 with the same argument layout as the recurrent reference."""
+def mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, Z=None, chunk_size: int = 64,
+                        initial_states=None, return_final_states: bool = False):
+    """Chunked evaluation in fp32 with the same argument layout as the recurrent reference.
+
+    ``initial_states`` = (angle_state [b, h, s], ssm_state [b, h, p, n], k_state [b, h, n], v_state [b, h, p]) continues a
+    sequence: the phase starts from ``angle_state``, and the state from ``ssm_state`` plus the look-ahead share
+    dt_0 (1 - sigmoid(trap_0)) v_state k_state^T that the previous token is owed under the trapezoid rule.  With
+    ``return_final_states`` the same four tensors come back for the last token (``ssm_state`` again without that token's
+    look-ahead share), so that calls chain and ``Mamba3.step`` can carry on from them."""
     bsz, seqlen, nheads, headdim = V.shape
     out_dtype = V.dtype
-    Qr, Kr, adt, qk_dot = _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, torch.float32)
+    angle0 = ssm0 = None
+    if initial_states is not None:
+        angle0, ssm0, k0, v0 = initial_states
+        owed = DT[:, :, 0].float() * (1.0 - torch.sigmoid(Trap[:, :, 0].float()))
+        ssm0 = ssm0.float() + owed[..., None, None] * v0.float()[..., None] * k0.float()[:, :, None, :]
+    Qr, Kr, adt, qk_dot = _prepare(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, torch.float32, angle_state=angle0)
     Vf = V.float()
     pad = (-seqlen) % chunk_size
     if pad:
@@ -167,7 +182,7 @@ def mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, 
 
     to_end = torch.exp(total[:, :, None, :] - cum)
     chunk_states = torch.einsum("bcqhp,bcqh,bcqhn->bchpn", Vc, to_end, Kc)
-    state = torch.zeros(bsz, nheads, headdim, dstate, dtype=torch.float32, device=V.device)
+    state = torch.zeros(bsz, nheads, headdim, dstate, dtype=torch.float32, device=V.device) if ssm0 is None else ssm0
     incoming = []
     for c in range(nchunks):
         incoming.append(state)
@@ -182,4 +197,41 @@ def mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, 
     y = y.reshape(bsz, nchunks * chunk_size, nheads, headdim)[:, :seqlen]
     if Z is not None:
         y = y * F.silu(Z.float())
-    return y.to(out_dtype)
+    if not return_final_states:
+        return y.to(out_dtype)
+    # zero decay and zero keys on the padding: ``state`` is the state after the last real token
+    theta_last = _prepare_small(ADT, DT, Trap, Angles, torch.float32, angle0)[3][:, -1]  # [b, h, s]
+    rep = nheads // K.shape[2]
+    k_last = K[:, -1].float().repeat_interleave(rep, dim=1) + K_bias.float()[None]
+    return y.to(out_dtype), theta_last, state, _rotate_pairs(k_last, theta_last), V[:, -1]
+
+
+def mamba3_siso_combined(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, Z=None, Input_States=None,
+                         chunk_size: int = 64, return_final_states: bool = False, cu_seqlens=None):
+    """Entry point with the argument list of the reference's combined op
+    (backbones/mamba3/ops/triton/mamba3/mamba3_siso_combined.py:291-307).  Q, K [b, l, g, n]; V, Z [b, l, h, p];
+    ADT, DT, Trap [b, h, l]; Q_bias, K_bias [h, n]; Angles [b, l, h or 1, s]; D [h].
+
+    Without states the sm_100a kernels run where the shape allows them (``ops.ssd.mamba3_siso_cuda``: bf16, head_dim 64,
+    d_state 128); with ``Input_States`` or ``return_final_states`` the chunked fp32 form runs, which carries the four state
+    tensors (see ``mamba3_siso_chunked``).  Packed variable-length batches (``cu_seqlens``) are not supported."""
+    if cu_seqlens is not None:
+        raise NotImplementedError("cu_seqlens: split the packed batch and call once per sequence")
+    if Input_States is None and not return_final_states:
+        from lbi_b200.ops import ssd as ops_ssd
+
+        if ops_ssd.siso_cuda_supported(V, Q) and V.dtype == torch.bfloat16 and D is not None:
+            return ops_ssd.mamba3_siso_cuda(Q=Q, K=K, V=V, ADT=ADT, DT=DT, Trap=Trap, Q_bias=Q_bias, K_bias=K_bias,
+                                            Angles=Angles, D=D, Z=Z)
+    return mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D, Z, chunk_size=chunk_size,
+                               initial_states=Input_States, return_final_states=return_final_states)
+
+
+def angle_dt(angle: torch.Tensor, dt: torch.Tensor, init_state: torch.Tensor | None = None, chunk_size: int = 64,
+             return_output_state: bool = False, cu_seqlens=None):
+    """Cumulative rotary phase with the argument layout of the reference's op (angle_dt.py:127-152): angle [b, l, h, s] raw
+    rates, dt [b, h, l] -> [b, l, h, s] = (init + cumsum(pi tanh(angle) dt)) mod 2 pi, optionally with the last phase."""
+    if cu_seqlens is not None:
+        raise NotImplementedError("cu_seqlens: split the packed batch and call once per sequence")
+    theta = angle_dt_cumsum(angle, dt.transpose(1, 2), init_state)
+    return (theta, theta[:, -1]) if return_output_state else theta

@@ -85,6 +85,62 @@ def gated_rms_norm(x, weight, *, eps, z=None, norm_before_gate=True, group_size=
     return rms_norm_reference(x, weight, eps=eps, z=z, norm_before_gate=norm_before_gate, group_size=group_size)
 
 
+def rms_norm_ref(x, weight, bias, z=None, eps=1e-6, group_size=None, norm_before_gate=True, upcast=True):
+    """The oracle with the argument list of the reference's function (backbones/mamba2/ops/triton/layernorm_gated.py:18-39);
+    always evaluated in fp32 (``upcast`` is accepted for that signature)."""
+    if bias is None:
+        return rms_norm_reference(x, weight, eps=eps, z=z, norm_before_gate=norm_before_gate, group_size=group_size)
+    gate_first = z is not None and not norm_before_gate
+    xin = (x.float() * F.silu(z.float())) if gate_first else x.float()
+    out = rms_norm_reference(xin, weight, eps=eps, group_size=group_size) + bias.float()
+    if z is not None and norm_before_gate:
+        out = out * F.silu(z.float())
+    return out.to(x.dtype)
+
+
+def rmsnorm_fn(x, weight, bias=None, z=None, eps=1e-6, group_size=None, norm_before_gate=True):
+    """Functional gated / grouped RMSNorm (reference layernorm_gated.py:384-385): the kernels of ``gated_rms_norm`` when there
+    is no bias, the fp32 PyTorch form otherwise."""
+    if bias is None:
+        return gated_rms_norm(x, weight, eps=eps, z=z, norm_before_gate=norm_before_gate, group_size=group_size)
+    return rms_norm_ref(x, weight, bias, z=z, eps=eps, group_size=group_size, norm_before_gate=norm_before_gate)
+
+
+def layernorm_fn(x, weight, bias, z=None, eps=1e-6, group_size=None, norm_before_gate=True, is_rms_norm=False):
+    """Functional gated / grouped LayerNorm (mean removed; reference layernorm_gated.py:380-381), fp32 PyTorch; with
+    ``is_rms_norm`` it is ``rmsnorm_fn``."""
+    if is_rms_norm:
+        return rmsnorm_fn(x, weight, bias, z=z, eps=eps, group_size=group_size, norm_before_gate=norm_before_gate)
+    xf = x.float()
+    zf = None if z is None else z.float()
+    if zf is not None and not norm_before_gate:
+        xf = xf * F.silu(zf)
+    grouped = xf.unflatten(-1, (-1, xf.shape[-1] if group_size is None else group_size))
+    centred = grouped - grouped.mean(dim=-1, keepdim=True)
+    out = (centred * torch.rsqrt(centred.square().mean(dim=-1, keepdim=True) + eps)).flatten(-2) * weight.float()
+    if bias is not None:
+        out = out + bias.float()
+    if zf is not None and norm_before_gate:
+        out = out * F.silu(zf)
+    return out.to(x.dtype)
+
+
+class LayerNormGated(nn.Module):
+    """LayerNorm with weight and bias, optional groups and an optional SiLU gate ``z`` (the ``LayerNorm`` of the reference's
+    layernorm_gated.py:388-412)."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-5, group_size: int | None = None, norm_before_gate: bool = True,
+                 device=None, dtype=None) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(hidden_size, device=device, dtype=dtype))
+        self.bias = nn.Parameter(torch.zeros(hidden_size, device=device, dtype=dtype))
+        self.eps, self.group_size, self.norm_before_gate = float(eps), group_size, bool(norm_before_gate)
+
+    def forward(self, x: torch.Tensor, z: torch.Tensor | None = None) -> torch.Tensor:
+        return layernorm_fn(x, self.weight, self.bias, z=z, eps=self.eps, group_size=self.group_size,
+                            norm_before_gate=self.norm_before_gate)
+
+
 class RMSNorm(nn.Module):
     """``y = x / rms(x) * weight`` computed in fp32 and cast back to the input dtype."""
 

@@ -14,11 +14,20 @@ from .base import RegionForwardCache, autocast_as, current_autocast
 
 
 class BackboneStackRegionBackend(nn.Module):
-    def __init__(self, *, backbone_spec: BackboneSpec, region_ranges: list[tuple[int, int]]) -> None:
+    name = "backbone_stack"
+
+    def __init__(self, *, backbone_spec: BackboneSpec | None = None, region_ranges: list[tuple[int, int]],
+                 backbone: nn.Module | None = None) -> None:
         super().__init__()
+        if backbone is None:
+            if backbone_spec is None:
+                raise ValueError("backbone_spec is required when backbone is not provided")
+            backbone = build_backbone_stack(backbone_spec)
         self.backbone_spec = backbone_spec
         self.region_ranges = [tuple(r) for r in region_ranges]
-        self.backbone = build_backbone_stack(backbone_spec)
+        if not self.region_ranges:
+            raise ValueError("region backend requires at least one region")
+        self.backbone = backbone
         self._structured = None
 
     @property

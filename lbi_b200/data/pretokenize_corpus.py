@@ -88,22 +88,52 @@ def write_shards(split_name: str, src_path: Path, tokenizer: TextTokenizerBacken
     return manifest_path
 
 
-def pretokenize_text_corpus(*, train_path: Path, val_path: Path | None, tokenizer_type: str, tokenizer_path: Path,
-                            vocab_size: int, tokenizer_train_bytes: int, out_dir: Path, shard_tokens: int,
-                            train_tokenizer: bool = False) -> tuple[Path, Path | None]:
-    tokenizer = load_text_tokenizer(tokenizer_type=tokenizer_type, tokenizer_path=tokenizer_path, train_path=train_path,
+def resolve_text_paths(text_corpus: str, train_text_path: str = "", val_text_path: str = "") -> tuple[Path, Path | None, str]:
+    """(train file, validation file or None, corpus name for the default tokenizer / output names): explicit paths win over
+    the bundled corpus of that name."""
+    if train_text_path:
+        return Path(train_text_path), (Path(val_text_path) if val_text_path else None), ""
+    from ..train.config import BUNDLED_TEXT_CORPORA
+
+    if text_corpus not in BUNDLED_TEXT_CORPORA:
+        raise ValueError(f"unknown text corpus {text_corpus!r}; give train_text_path or one of {sorted(BUNDLED_TEXT_CORPORA)}")
+    train_name, val_name = BUNDLED_TEXT_CORPORA[text_corpus]
+    return CORPORA_ROOT / train_name, CORPORA_ROOT / val_name, text_corpus
+
+
+def pretokenize_text_corpus(*, tokenizer_type: str, vocab_size: int, tokenizer_train_bytes: int, shard_tokens: int,
+                            train_tokenizer: bool = False, tokenizer_path: Path | str = "", train_path: Path | None = None,
+                            val_path: Path | None = None, out_dir: Path | None = None, text_corpus: str = "",
+                            train_text_path: str = "", val_text_path: str = "",
+                            output_dir: str = "") -> tuple[Path, Path | None]:
+    """Two call forms.  With ``train_path`` (and optionally ``val_path``, ``out_dir``, a resolved ``tokenizer_path``) the files are
+    taken as given and a missing validation split is skipped.  With the reference's keywords (``text_corpus``, ``train_text_path``,
+    ``val_text_path``, ``output_dir``; data/pretokenize_corpus.py:146-182) the paths, the tokenizer file and the output directory
+    are resolved from the corpus name, and both splits must exist."""
+    if train_path is None:
+        train_path, val_path, corpus_name = resolve_text_paths(text_corpus, train_text_path, val_text_path)
+        if not train_path.exists():
+            raise FileNotFoundError(f"train text not found: {train_path}")
+        if val_path is None or not val_path.exists():
+            raise FileNotFoundError(f"val text not found: {val_path}")
+        tokenizer_path = resolve_tokenizer_path(tokenizer_type, str(tokenizer_path or ""), corpus_name, train_path, vocab_size)
+        out_dir = Path(output_dir) if output_dir else default_output_dir(text_corpus, train_path, vocab_size, tokenizer_type)
+    elif out_dir is None:
+        out_dir = Path(output_dir) if output_dir else default_output_dir(text_corpus, train_path, vocab_size, tokenizer_type)
+    tokenizer = load_text_tokenizer(tokenizer_type=tokenizer_type, tokenizer_path=Path(tokenizer_path), train_path=train_path,
                                     vocab_size=vocab_size, train_bytes=tokenizer_train_bytes, force_train=train_tokenizer)
     train_manifest = write_shards("train", train_path, tokenizer, out_dir, shard_tokens)
     val_manifest = write_shards("val", val_path, tokenizer, out_dir, shard_tokens) if val_path is not None else None
     return train_manifest, val_manifest
 
 
-pretokenize_sentencepiece_corpus = pretokenize_text_corpus
+def pretokenize_sentencepiece_corpus(**kwargs) -> tuple[Path, Path | None]:
+    """``pretokenize_text_corpus`` with the SentencePiece tokenizer (reference data/pretokenize_corpus.py:120-143)."""
+    kwargs.pop("tokenizer_type", None)
+    return pretokenize_text_corpus(tokenizer_type="sentencepiece", **kwargs)
 
 
 def main() -> None:
-    from ..train.config import BUNDLED_TEXT_CORPORA
-
     p = argparse.ArgumentParser(description="Tokenise a text corpus into int32 shards with manifests.")
     p.add_argument("--text-corpus", type=str, default="fineweb_edu")
     p.add_argument("--train-text-path", type=str, default="")
@@ -116,14 +146,7 @@ def main() -> None:
     p.add_argument("--output-dir", type=str, default="")
     p.add_argument("--shard-tokens", type=int, default=50_000_000)
     args = p.parse_args()
-    if args.train_text_path:
-        train_path = Path(args.train_text_path)
-        val_path = Path(args.val_text_path) if args.val_text_path else None
-        corpus_name = ""
-    else:
-        train_name, val_name = BUNDLED_TEXT_CORPORA[args.text_corpus]
-        train_path, val_path = CORPORA_ROOT / train_name, CORPORA_ROOT / val_name
-        corpus_name = args.text_corpus
+    train_path, val_path, corpus_name = resolve_text_paths(args.text_corpus, args.train_text_path, args.val_text_path)
     tok_path = resolve_tokenizer_path(args.tokenizer_type, args.tokenizer_path, corpus_name, train_path, args.vocab_size)
     out_dir = Path(args.output_dir) if args.output_dir else default_output_dir(args.text_corpus, train_path, args.vocab_size,
                                                                               args.tokenizer_type)

@@ -142,8 +142,23 @@ def default_kernel_mode(t, head_dim, n_heads, n_kv_heads, seq_len) -> str:
     return "fa2_loop"
 
 
-def attention_input_pullback_basis(q, k, v, dO_basis, *, scale=None, causal=True, use_cuda=True, kernel_mode=None):
-    """q, k, v [B, H, T, Dh]; dO_basis [B, P, H, T, Dh] -> (dQ, dK, dV) each [B, P, H, T, Dh]."""
+# the reference's kernel-mode names (cuda/transformer/__init__.py:279-356) and the mode of this package that serves each
+REFERENCE_KERNEL_MODES = {
+    "fa2_mma_pblock4": None,   # its tensor-core kernels -> the best kernel for the shape (tcgen05 where supported)
+    "fa2_mma_p1": None,
+    "fa2_p1": None,
+    "fa2_loop": "fa2_loop",
+    "simple": "dense",
+}
+
+
+def attention_input_pullback_basis(q, k, v, dO_basis, *, scale=None, causal=True, use_cuda=True, kernel_mode=None,
+                                   softmax_scale=None):
+    """q, k, v [B, H, T, Dh]; dO_basis [B, P, H, T, Dh] -> (dQ, dK, dV) each [B, P, H, T, Dh].
+
+    ``softmax_scale`` is the reference's keyword for ``scale`` (cuda/transformer/__init__.py:279-289)."""
+    scale = softmax_scale if scale is None else scale
+    kernel_mode = REFERENCE_KERNEL_MODES.get(kernel_mode, kernel_mode)
     if q.dim() != 4 or dO_basis.dim() != 5:
         raise ValueError("expected q,k,v [B,H,T,Dh] and dO_basis [B,P,H,T,Dh]")
     bsz, heads, seqlen, head_dim = q.shape

@@ -19,4 +19,6 @@ class ReadoutCache:
 class ReadoutModule(Protocol):
     def forward(self, features: torch.Tensor, *, canvas) -> torch.Tensor: ...
 
+    def forward_with_cache(self, features: torch.Tensor, *, canvas) -> tuple[torch.Tensor, ReadoutCache]: ...
+
     def vjp_parameters(self) -> list[nn.Parameter]: ...

@@ -86,7 +86,10 @@ def _cdf(path_stem: Path, aggregates: Sequence[gp.CaseAggregate]) -> None:
 
 def generate_report(*, output_dir: Path, case_names: Sequence[str] | None = None, plot: bool = False, preset: str = "report",
                     seeds: Sequence[int] | None = None, batches_per_seed: int | None = None,
-                    interface_jacobian_mode: str = "recompute", jacobian_basis_chunk: int = 32) -> list[dict[str, Any]]:
+                    interface_jacobian_mode: str = "recompute", jacobian_basis_chunk: int = 32,
+                    repo_root: Path | None = None) -> list[dict[str, Any]]:
+    """``repo_root`` is accepted and unused: the reference's function loads its test module from that directory by path
+    (scripts/generate_grad_parity_report.py:211-223), here the cases are an importable module (``utils.grad_parity``)."""
     if interface_jacobian_mode not in {"graph", "recompute", "structured", "forward"}:
         raise ValueError("interface_jacobian_mode must be one of: graph, recompute, structured, forward")
     if jacobian_basis_chunk <= 0:

@@ -53,9 +53,18 @@ def readout_uses_tied_output_weight(model: nn.Module) -> bool:
     return _readout_parts(model)[2]
 
 
-def infer_data_info(cfg: Any, *, train_corpus: Any, val_corpus: Any) -> dict[str, Any]:
+def infer_data_info(cfg: Any, *, train_corpus: Any, val_corpus: Any, corpora_root: Any = None, resolve_text_paths_fn=None,
+                    resolve_tokenizer_path_fn=None, resolve_token_shard_manifests_fn=None,
+                    resolve_token_shards_dir_fn=None) -> dict[str, Any]:
+    """Where the run's data came from.  The five optional arguments are the reference's injection points
+    (train/metrics.py:46-56); left out, the resolvers of ``train.data`` are used."""
     from . import data as glue
 
+    corpora_root = glue.CORPORA_ROOT if corpora_root is None else corpora_root
+    text_paths = resolve_text_paths_fn or glue.resolve_text_paths
+    tokenizer_path = resolve_tokenizer_path_fn or glue.resolve_tokenizer_path
+    shard_manifests = resolve_token_shard_manifests_fn or glue.resolve_token_shard_manifests
+    shards_dir = resolve_token_shards_dir_fn or glue.resolve_token_shards_dir
     info: dict[str, Any] = {
         "data_mode": cfg.data_mode, "text_corpus": cfg.text_corpus, "vocab_size": int(cfg.vocab_size),
         "seq_len": int(cfg.seq_len), "train_stream_length": corpus_numel(train_corpus),
@@ -64,25 +73,25 @@ def infer_data_info(cfg: Any, *, train_corpus: Any, val_corpus: Any) -> dict[str
     if cfg.data_mode == "synthetic":
         info.update(task=cfg.task, train_sequences=int(cfg.train_sequences), val_sequences=int(cfg.val_sequences))
         return info
-    if cfg.data_mode == "text_bpe_sharded":
+    if cfg.data_mode == "text_bpe_sharded" and resolve_text_paths_fn is None:
         train_path, val_path = glue._shard_train_path(cfg), None
     else:
-        train_path, val_path, _ = glue.resolve_text_paths(cfg)
+        train_path, val_path, _ = text_paths(cfg)
     info.update(
-        corpora_root=str(glue.CORPORA_ROOT), train_path=str(train_path), val_path=str(val_path) if val_path else "",
+        corpora_root=str(corpora_root), train_path=str(train_path), val_path=str(val_path) if val_path else "",
         train_file_bytes=int(train_path.stat().st_size) if train_path.exists() else 0,
         val_file_bytes=int(val_path.stat().st_size) if (val_path and val_path.exists()) else 0,
     )
     if cfg.data_mode in {"text_bpe", "text_bpe_sharded"}:
-        tok = glue.resolve_tokenizer_path(cfg, train_path=train_path)
+        tok = tokenizer_path(cfg, train_path=train_path)
         vocab = tok.with_suffix(".vocab") if tok.suffix == ".model" else None
         info.update(tokenizer_path=str(tok), tokenizer_type=cfg.tokenizer_type, tokenizer_exists=tok.exists(),
                     tokenizer_vocab_path=str(vocab) if vocab else "", tokenizer_vocab_exists=bool(vocab and vocab.exists()))
     if cfg.data_mode == "text_bpe":
         info["tokenizer_train_bytes"] = int(cfg.tokenizer_train_bytes)
     if cfg.data_mode == "text_bpe_sharded":
-        tm, vm = glue.resolve_token_shard_manifests(cfg, train_path=train_path)
-        info.update(token_shards_dir=str(glue.resolve_token_shards_dir(cfg, train_path=train_path)), train_manifest=str(tm),
+        tm, vm = shard_manifests(cfg, train_path=train_path)
+        info.update(token_shards_dir=str(shards_dir(cfg, train_path=train_path)), train_manifest=str(tm),
                     train_manifest_exists=tm.exists(), val_manifest=str(vm), val_manifest_exists=vm.exists())
     return info
 

@@ -2,6 +2,7 @@
 cache contents, state ablations, backbone smoke, Mamba scans vs token recurrences, structured Transformer lowering."""
 import pytest
 import torch
+import torch.nn.functional as F
 
 from lbi_b200.backbones import BackboneSpec, build_backbone_stack
 from lbi_b200.backbones.mamba2.ssd import ssd_chunk_scan, ssd_recurrent_reference
@@ -191,6 +192,132 @@ def test_mamba3_decode_steps_reproduce_the_full_sequence(outproj_norm):
         mixer.forward_with_cache(u, cu_seqlens=torch.tensor([0, 21]))
 
 
+def test_mamba3_prefill_then_decode_and_state_carrying_combined_op():
+    from lbi_b200.backbones.mamba3.mamba3 import Mamba3
+    from lbi_b200.backbones.mamba3.siso import angle_dt, mamba3_siso_combined
+
+    torch.manual_seed(14)
+    mixer = Mamba3(d_model=32, d_state=16, expand=2, headdim=16, chunk_size=8)
+    u = torch.randn(2, 30, 32)
+    with torch.no_grad():
+        want = mixer(u)
+    states = mixer.allocate_inference_cache(2, 30)
+    pieces = [mixer.prefill(u[:, :11], *states), mixer.prefill(u[:, 11:19], *states)]
+    pieces.append(torch.stack([mixer.step(u[:, t], *states) for t in range(19, 30)], dim=1))
+    assert torch.allclose(torch.cat(pieces, dim=1), want, atol=3e-6, rtol=1e-5)
+
+    b, l, h, p, n, cut = 2, 37, 4, 8, 16, 15
+    Q, K, V, Z = torch.randn(b, l, 1, n), torch.randn(b, l, 1, n), torch.randn(b, l, h, p), torch.randn(b, l, h, p)
+    DT = torch.rand(b, h, l) * 0.5 + 0.01
+    ADT, Trap = -DT * (torch.rand(b, h, l) + 0.1), torch.randn(b, h, l)
+    qb, kb, ang, D = torch.randn(h, n), torch.randn(h, n), torch.randn(b, l, h, n // 4), torch.randn(h)
+    oracle = mamba3_siso_recurrent_reference(Q, K, V, ADT, DT, Trap, qb, kb, ang, D, Z)
+    cutargs = lambda a, z: (Q[:, a:z], K[:, a:z], V[:, a:z], ADT[..., a:z], DT[..., a:z], Trap[..., a:z], qb, kb, ang[:, a:z], D, Z[:, a:z])  # noqa: E731
+    y1, *carry = mamba3_siso_combined(*cutargs(0, cut), chunk_size=8, return_final_states=True)
+    y2, *end = mamba3_siso_combined(*cutargs(cut, l), Input_States=tuple(carry), chunk_size=8, return_final_states=True)
+    assert torch.allclose(torch.cat([y1, y2], dim=1).double(), oracle, atol=2e-4, rtol=1e-4)
+    _, *whole = mamba3_siso_combined(*cutargs(0, l), chunk_size=16, return_final_states=True)
+    for a, c in zip(whole, end):
+        assert torch.allclose(a, c, atol=1e-5)
+    assert torch.allclose(mamba3_siso_combined(*cutargs(0, l)).double(), oracle, atol=2e-4, rtol=1e-4)
+    theta, last = angle_dt(ang, DT, return_output_state=True)
+    assert theta.shape == (b, l, h, n // 4) and torch.equal(last, whole[0]) and float(theta.min()) >= 0
+    with pytest.raises(NotImplementedError):
+        mamba3_siso_combined(*cutargs(0, l), cu_seqlens=torch.tensor([0, l]))
+
+
+def test_mamba2_op_level_entries_match_the_module_and_the_token_loop():
+    from lbi_b200.backbones.mamba2.mamba2_simple import Mamba2Simple
+    from lbi_b200.backbones.mamba2.ops import mamba_chunk_scan_combined, mamba_split_conv1d_scan_combined, ssd_selective_scan
+
+    torch.manual_seed(15)
+    mixer = Mamba2Simple(32, d_state=16, headdim=16, chunk_size=8, learnable_init_states=True)
+    with torch.no_grad():
+        mixer.init_states.normal_()
+    u = torch.randn(2, 20, 32)
+    packed = torch.tensor([[0] * 7 + [1] * 13, [0] * 20])
+    for seq_idx in (None, packed):
+        got = mamba_split_conv1d_scan_combined(
+            mixer.in_proj(u), mixer.conv1d.weight.squeeze(1), mixer.conv1d.bias, mixer.dt_bias, -torch.exp(mixer.A_log), mixer.D, 8,
+            initial_states=mixer.init_states.unsqueeze(0).expand(2, -1, -1, -1), seq_idx=seq_idx, rmsnorm_weight=mixer.norm.weight,
+            rmsnorm_eps=mixer.norm.eps, outproj_weight=mixer.out_proj.weight, outproj_bias=mixer.out_proj.bias, headdim=16,
+            ngroups=1, norm_before_gate=False)
+        assert torch.allclose(got, mixer(u, seq_idx=seq_idx), atol=1e-6)
+    b, l, h, p, n = 2, 19, 4, 8, 16
+    x, dt, A = torch.randn(b, l, h, p), torch.randn(b, l, h), -torch.rand(h) - 0.1
+    B, C, D2, z, bias = torch.randn(b, l, 2, n), torch.randn(b, l, 2, n), torch.randn(h, p), torch.randn(b, l, h, p), torch.randn(h)
+    kw = dict(D=D2, z=z, dt_bias=bias, dt_softplus=True, dt_limit=(0.01, 0.5))
+    y, final = mamba_chunk_scan_combined(x, dt, A, B, C, 8, return_final_states=True, **kw)
+    assert final.shape == (b, h, p, n) and torch.allclose(y, ssd_selective_scan(x, dt, A, B, C, **kw), atol=1e-4, rtol=1e-4)
+    y_next = mamba_chunk_scan_combined(x, dt, A, B, C, 8, initial_states=final, **kw)
+    both = mamba_chunk_scan_combined(torch.cat([x, x], 1), torch.cat([dt, dt], 1), A, torch.cat([B, B], 1), torch.cat([C, C], 1), 8,
+                                     D=D2, z=torch.cat([z, z], 1), dt_bias=bias, dt_softplus=True, dt_limit=(0.01, 0.5))
+    assert torch.allclose(both[:, l:], y_next, atol=1e-4, rtol=1e-4)
+    with pytest.raises(NotImplementedError):
+        mamba_chunk_scan_combined(x, dt, A, B, C, 8, return_varlen_states=True)
+
+
+def test_functional_norms_against_the_written_out_formula():
+    from lbi_b200.backbones.norms import LayerNormGated, layernorm_fn, rms_norm_ref, rmsnorm_fn
+
+    torch.manual_seed(16)
+    x, z, w, bias = torch.randn(3, 5, 16), torch.randn(3, 5, 16), torch.randn(16), torch.randn(16)
+
+    def written_out(b, gate, group, before, rms):
+        t = x * F.silu(gate) if (gate is not None and not before) else x
+        g = t.unflatten(-1, (-1, group or 16))
+        g = g if rms else g - g.mean(-1, keepdim=True)
+        out = (g * torch.rsqrt(g.square().mean(-1, keepdim=True) + 1e-5)).flatten(-2) * w
+        out = out if b is None else out + b
+        return out * F.silu(gate) if (gate is not None and before) else out
+
+    for group in (None, 8):
+        for before in (True, False):
+            for gate in (None, z):
+                for b in (None, bias):
+                    kw = dict(z=gate, eps=1e-5, group_size=group, norm_before_gate=before)
+                    assert torch.allclose(rms_norm_ref(x, w, b, **kw), written_out(b, gate, group, before, True), atol=1e-5)
+                    assert torch.allclose(rmsnorm_fn(x, w, b, **kw), written_out(b, gate, group, before, True), atol=1e-5)
+                    assert torch.allclose(layernorm_fn(x, w, b, **kw), written_out(b, gate, group, before, False), atol=1e-5)
+                    assert torch.equal(layernorm_fn(x, w, b, is_rms_norm=True, **kw), rmsnorm_fn(x, w, b, **kw))
+    module = LayerNormGated(16, group_size=8)
+    assert torch.allclose(module(x, z), layernorm_fn(x, module.weight, module.bias, z=z, eps=1e-5, group_size=8), atol=1e-6)
+
+
+def test_kernel_entry_points_under_the_module_paths_of_the_reference():
+    from lbi_b200.backends.backbone_stack import BackboneStackRegionBackend
+    from lbi_b200.backends.transformer_cuda import CudaTransformerLowering
+    from lbi_b200.cuda.interface import suffix_scan_pullbacks
+    from lbi_b200.cuda.mamba3 import state_mixer_input_pullback_basis
+    from lbi_b200.cuda.transformer import attention_input_pullback_basis
+
+    torch.manual_seed(17)
+    mats = torch.randn(2, 3, 4, 4)
+    suffix = suffix_scan_pullbacks(mats)
+    assert suffix.shape == (2, 4, 4, 4) and torch.allclose(suffix[:, 0], mats[:, 0] @ mats[:, 1] @ mats[:, 2], atol=1e-5)
+    q, k, v, do = torch.randn(1, 2, 8, 4), torch.randn(1, 2, 8, 4), torch.randn(1, 2, 8, 4), torch.randn(1, 3, 2, 8, 4)
+    ref_style = attention_input_pullback_basis(q, k, v, do, softmax_scale=0.5, causal=True, use_cuda=True, kernel_mode="fa2_mma_pblock4")
+    own_style = attention_input_pullback_basis(q, k, v, do, scale=0.5, kernel_mode="dense")
+    lowered = CudaTransformerLowering().attention_input_pullback_basis(q=q, k=k, v=v, output_cotangent_basis=do, softmax_scale=0.5,
+                                                                       kernel_mode="fa2_mma_pblock4")
+    qg = q.clone().requires_grad_(True)
+    out = F.scaled_dot_product_attention(qg, k, v, is_causal=True, scale=0.5)
+    (want,) = torch.autograd.grad(out, qg, do[:, 1])
+    assert torch.allclose(ref_style[0][:, 1], want, atol=1e-5)
+    assert all(torch.equal(a, c) and torch.equal(a, d) for a, c, d in zip(ref_style, own_style, lowered))
+    block = Mamba3Block(32, d_state=16, headdim=16, chunk_size=8)
+    u, basis = torch.randn(2, 6, 32), torch.randn(2, 2, 6, 32)
+    assert torch.equal(state_mixer_input_pullback_basis(block.mixer, u, basis), block.mixer.input_pullback_matrix(u, basis))
+    spec = BackboneSpec(name="mamba2", dim=32, layers=2, d_state=16, headdim=16, chunk_size=8)
+    first = BackboneStackRegionBackend(backbone_spec=spec, region_ranges=[(0, 1), (1, 2)])
+    shared = BackboneStackRegionBackend(backbone=first.backbone, region_ranges=[(0, 2)])
+    assert shared.backbone is first.backbone and shared.count_parameters() == first.count_parameters()
+    with pytest.raises(ValueError):
+        BackboneStackRegionBackend(region_ranges=[(0, 1)])
+    with pytest.raises(ValueError):
+        BackboneStackRegionBackend(backbone_spec=spec, region_ranges=[])
+
+
 def test_mamba3_pullbacks_in_the_cache_form_of_the_reference():
     torch.manual_seed(12)
     block = Mamba3Block(32, d_state=16, headdim=16, chunk_size=8)
@@ -206,11 +333,11 @@ def test_mamba3_pullbacks_in_the_cache_form_of_the_reference():
         assert torch.allclose(g_hidden[:, i], want_h, atol=1e-5, rtol=1e-4)
         assert torch.allclose(g_stream[:, i], want_s, atol=1e-5, rtol=1e-4)
     _, _, first = block.forward_with_cache(hidden.detach())
-    g_only, none = block.input_pullback_matrix(first, basis)
+    g_only, none = block.input_pullback_matrix(cache=first, g_hidden_out=basis)
     assert none is None and g_only.shape == basis.shape
     mixer_in = torch.randn(2, 12, 32, requires_grad=True)
     mixer_out, mixer_cache = block.mixer.forward_with_cache(mixer_in)
-    got = block.mixer.input_pullback_matrix(mixer_cache, basis)
+    got = block.mixer.input_pullback_matrix(cache=mixer_cache, g_out=basis)
     want = torch.stack([torch.autograd.grad(mixer_out, mixer_in, basis[:, i], retain_graph=True)[0] for i in range(3)], dim=1)
     assert torch.allclose(got, want, atol=1e-5, rtol=1e-4)
     with pytest.raises(ValueError):

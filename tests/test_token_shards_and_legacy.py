@@ -259,3 +259,24 @@ def test_transformer_layer_caches_and_jacobian_function_forms():
     assert torch.allclose(by_graph[-2], expect, atol=1e-5)
     with pytest.raises(ValueError):
         propagate_state_adjoint_by_autograd_chain(states=fcache["states"][:1], top_state_adjoint=top)
+
+
+def test_pretokenize_entry_takes_the_keywords_of_the_reference(tmp_path):
+    from lbi_b200.data.pretokenize_corpus import pretokenize_text_corpus
+
+    train, val = tmp_path / "corpus.txt", tmp_path / "corpus_val.txt"
+    train.write_bytes(b"alpha beta gamma alpha beta delta\n" * 40)
+    val.write_bytes(b"gamma delta alpha\n" * 10)
+    common = dict(tokenizer_type="byte_bpe", vocab_size=270, tokenizer_train_bytes=4096, train_tokenizer=True, shard_tokens=150)
+    tm, vm = pretokenize_text_corpus(text_corpus="", train_text_path=str(train), val_text_path=str(val),
+                                     tokenizer_path=str(tmp_path / "tok.json"), output_dir=str(tmp_path / "out"), **common)
+    assert tm == tmp_path / "out" / "train_manifest.json" and vm == tmp_path / "out" / "val_manifest.json"
+    assert json.loads(tm.read_text())["num_tokens_total"] > json.loads(vm.read_text())["num_tokens_total"] > 0
+    with pytest.raises(FileNotFoundError):
+        pretokenize_text_corpus(text_corpus="", train_text_path=str(train), val_text_path="", output_dir=str(tmp_path / "o2"),
+                                tokenizer_path=str(tmp_path / "tok.json"), **common)
+    with pytest.raises(ValueError):
+        pretokenize_text_corpus(text_corpus="no_such_corpus", **common)
+    tm2, vm2 = pretokenize_text_corpus(train_path=train, val_path=None, out_dir=tmp_path / "o3",
+                                       tokenizer_path=tmp_path / "tok.json", **{**common, "train_tokenizer": False})
+    assert vm2 is None and json.loads(tm2.read_text()) == json.loads(tm.read_text())
