@@ -50,9 +50,11 @@ def discover_run_dirs(family_dir: Path) -> list[Path]:
 
 
 def load_run_config(run_dir: Path, *, eval_batches: int, batch_size: int | None, seq_len: int | None,
-                    device: str) -> LBITrainingConfig:
+                    device: str, tokenizer_path: str = "") -> LBITrainingConfig:
     raw = json.loads((run_dir / "config.json").read_text(encoding="utf-8"))
     raw.update(save_checkpoints=False, resume_from="", init_from="")
+    if tokenizer_path:  # the tokenizer the corpora are rebuilt with, when the run's own path is not on this machine
+        raw["tokenizer_path"] = tokenizer_path
     cfg = LBITrainingConfig.from_dict(raw)
     updates: dict[str, Any] = {"eval_batches": int(eval_batches)}
     if batch_size is not None:
@@ -98,8 +100,9 @@ def _json_or_empty(path: Path) -> dict[str, Any]:
 
 
 def evaluate_run(run_dir: Path, *, checkpoint: str, eval_batches: int, batch_size: int | None, seq_len: int | None,
-                 eval_seed: int, device: str) -> dict[str, Any]:
-    cfg = load_run_config(run_dir, eval_batches=eval_batches, batch_size=batch_size, seq_len=seq_len, device=device)
+                 eval_seed: int, device: str, tokenizer_path: str = "") -> dict[str, Any]:
+    cfg = load_run_config(run_dir, eval_batches=eval_batches, batch_size=batch_size, seq_len=seq_len, device=device,
+                          tokenizer_path=tokenizer_path)
     dev = _resolve_device(cfg)
     ckpt_path = checkpoint_path_from_summary(run_dir / "summary.json", preference=checkpoint)
     if ckpt_path is None or not Path(ckpt_path).exists():
@@ -144,7 +147,12 @@ def write_outputs(rows: list[dict[str, Any]], out_dir: Path) -> None:
 
 def main(argv: list[str] | None = None) -> list[dict[str, Any]]:
     p = argparse.ArgumentParser(description="Evaluate the checkpoints of one run family.")
-    p.add_argument("family_dir", type=Path, help="directory holding <run_name>/<variant>/ run directories")
+    p.add_argument("family_dir", type=Path, nargs="?", default=None,
+                   help="directory holding <run_name>/<variant>/ run directories, or one run directory")
+    p.add_argument("--family", type=Path, default=None, help="the same directory as a flag (the reference's spelling)")
+    p.add_argument("--run-dir", action="append", default=[],
+                   help="a run directory to evaluate; may be repeated, and then the family only names the default output directory")
+    p.add_argument("--tokenizer-path", type=str, default="", help="tokenizer used to rebuild the corpora instead of the run's own")
     p.add_argument("--output-dir", type=str, default="", help="where lm_eval_summary.{csv,json} go (default: <family_dir>/evals)")
     p.add_argument("--checkpoint", choices=("best", "latest"), default="best")
     p.add_argument("--eval-batches", type=int, default=512)
@@ -155,13 +163,26 @@ def main(argv: list[str] | None = None) -> list[dict[str, Any]]:
     p.add_argument("--include-regex", type=str, default="", help="keep only runs whose <run_name> matches")
     p.add_argument("--exclude-regex", type=str, default="", help="drop runs whose <run_name> matches")
     ns = p.parse_args(argv)
-    runs = discover_run_dirs(ns.family_dir)
+    family = ns.family_dir if ns.family_dir is not None else ns.family
+    if family is None and not ns.run_dir:
+        p.error("give the family directory (positional or --family) or at least one --run-dir")
+    if ns.run_dir:
+        runs = [Path(r).expanduser() for r in ns.run_dir]
+        family = Path(ns.run_dir[0]).expanduser().parent.parent if family is None else family
+    elif (family / "config.json").exists() and (family / "summary.json").exists():
+        runs = [family]
+    else:
+        runs = discover_run_dirs(family)
+    if not runs:
+        raise FileNotFoundError(f"no completed runs found under: {family}")
+    ns.family_dir = family
     if ns.include_regex:
         runs = [r for r in runs if re.search(ns.include_regex, r.parent.name)]
     if ns.exclude_regex:
         runs = [r for r in runs if not re.search(ns.exclude_regex, r.parent.name)]
     rows = [evaluate_run(r, checkpoint=ns.checkpoint, eval_batches=ns.eval_batches, batch_size=ns.batch_size,
-                         seq_len=ns.seq_len, eval_seed=ns.eval_seed, device=ns.device) for r in runs]
+                         seq_len=ns.seq_len, eval_seed=ns.eval_seed, device=ns.device, tokenizer_path=ns.tokenizer_path)
+            for r in runs]
     write_outputs(rows, Path(ns.output_dir) if ns.output_dir else ns.family_dir / "evals")
     print("run\tposthoc_ce\tppl\ttrain_best_ce\tckpt_step\teval_tokens")
     for r in rows:

@@ -29,9 +29,10 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
     p.add_argument("--dpi", type=int, default=150)
     p.add_argument("--font-scale", type=float, default=1.0)
     p.add_argument("--include-variant-regex", type=str, default="")
+    p.add_argument("--exclude-variant-regex", type=str, default="", help="applied after the include filter")
     ns = p.parse_args(argv)
     out_dir = ns.output_dir or (ns.run_roots[0] / "ablation_plots")
-    groups = load_groups(ns.run_roots, include=ns.include_variant_regex)
+    groups = load_groups(ns.run_roots, include=ns.include_variant_regex, exclude=ns.exclude_variant_regex)
     by_backbone: dict[str, list[dict]] = defaultdict(list)
     for label, runs in groups.items():
         if label == "dense":

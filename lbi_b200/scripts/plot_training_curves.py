@@ -50,29 +50,63 @@ def read_metrics(run_dir: Path) -> list[dict[str, Any]]:
     return rows
 
 
-def run_label(run_dir: Path, cfg: dict[str, Any], mode: str = "auto") -> str:
+_DENSE_NAMES = {"dense", "backprop_ref"}
+_REGIME_ALIASES = {"backprop_ref": "dense", "native_region_interface": "lbi"}
+LABEL_MODES = ("auto", "full", "variant", "backbone", "regime", "backbone_regime", "region_size", "rank_region")
+
+
+def run_regime(run_dir: Path) -> str:
+    """``dense`` or ``lbi`` from the run directory's name (the first release's names map onto them)."""
+    return _REGIME_ALIASES.get(run_dir.name, run_dir.name)
+
+
+def run_label(run_dir: Path, cfg: dict[str, Any], mode: str = "auto", *, several_region_sizes: bool = True) -> str:
+    """The group a run is averaged into.  ``auto``: dense / lbi r<R>; ``full`` adds the region size; ``variant``: the run
+    name without its seed; ``backbone`` / ``regime`` / ``backbone_regime`` / ``region_size`` / ``rank_region`` as in the
+    reference (scripts/plot_training_curves.py:226-268)."""
     variant = run_dir.name
-    is_dense = variant in {"dense", "backprop_ref"}
+    is_dense = variant in _DENSE_NAMES
+    backbone, regime = str(cfg.get("backbone", "model")), run_regime(run_dir)
     if mode == "variant":
         return re.sub(r"_seed\d+$", "", run_dir.parent.name) or variant
+    if mode == "backbone":
+        return backbone
+    if mode == "regime":
+        return regime
+    if mode == "backbone_regime":
+        return f"{backbone}:{regime}"
     if is_dense:
         return "dense"
+    if mode == "region_size":
+        return f"region={cfg.get('region_size', '?')}"
+    if mode == "rank_region":
+        rank = f"lbi r{cfg.get('message_dim', '?')}"
+        return f"{rank}, region={cfg.get('region_size', '?')}" if several_region_sizes else rank
     label = f"lbi r{cfg.get('message_dim', '?')}"
     if mode == "full":
         label += f" rs{cfg.get('region_size', '?')}"
     return label
 
 
-def load_groups(roots: list[Path], *, include: str = "", exclude: str = "", label_mode: str = "auto") -> dict[str, list[dict]]:
-    groups: dict[str, list[dict]] = defaultdict(list)
+def load_groups(roots: list[Path], *, include: str = "", exclude: str = "", label_mode: str = "auto",
+                regimes: set[str] | None = None) -> dict[str, list[dict]]:
+    """``regimes`` keeps only runs of the named kinds (``dense``, ``lbi``; the first release's names are understood)."""
+    wanted = None if not regimes else {_REGIME_ALIASES.get(r, r) for r in regimes}
+    kept: list[tuple[Path, dict]] = []
     for run in discover_runs(roots):
         name = run.parent.name + "/" + run.name
         if include and not re.search(include, name):
             continue
         if exclude and re.search(exclude, name):
             continue
-        cfg = json.loads((run / "config.json").read_text(encoding="utf-8"))
-        groups[run_label(run, cfg, label_mode)].append({"dir": run, "cfg": cfg, "rows": read_metrics(run)})
+        if wanted is not None and run_regime(run) not in wanted:
+            continue
+        kept.append((run, json.loads((run / "config.json").read_text(encoding="utf-8"))))
+    sizes = {cfg.get("region_size") for run, cfg in kept if run.name not in _DENSE_NAMES}
+    groups: dict[str, list[dict]] = defaultdict(list)
+    for run, cfg in kept:
+        label = run_label(run, cfg, label_mode, several_region_sizes=len(sizes) > 1)
+        groups[label].append({"dir": run, "cfg": cfg, "rows": read_metrics(run)})
     return dict(groups)
 
 
@@ -153,13 +187,15 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
     p.add_argument("--output-dir", type=Path, default=None, help="default: <first root>/plots")
     p.add_argument("--include-variant-regex", type=str, default="")
     p.add_argument("--exclude-variant-regex", type=str, default="")
-    p.add_argument("--label-mode", choices=("auto", "full", "variant"), default="auto")
+    p.add_argument("--label-mode", choices=LABEL_MODES, default="auto")
+    p.add_argument("--regimes", type=str, default="", help="comma-separated filter, e.g. lbi (or native_region_interface)")
     p.add_argument("--smooth-window", type=int, default=1, help="moving-average window for training curves")
     p.add_argument("--dpi", type=int, default=150)
     p.add_argument("--font-scale", type=float, default=1.0)
     ns = p.parse_args(argv)
     out_dir = ns.output_dir or (ns.run_roots[0] / "plots")
-    groups = load_groups(ns.run_roots, include=ns.include_variant_regex, exclude=ns.exclude_variant_regex, label_mode=ns.label_mode)
+    groups = load_groups(ns.run_roots, include=ns.include_variant_regex, exclude=ns.exclude_variant_regex, label_mode=ns.label_mode,
+                         regimes={r.strip() for r in ns.regimes.split(",") if r.strip()} or None)
     if not groups:
         raise SystemExit("no runs with metrics.csv found")
     summary = summarize(groups)

@@ -50,6 +50,19 @@ def test_launcher_commands_parse_with_the_training_cli(monkeypatch, kind, backbo
         assert cfg.lr_model == paper_presets.DENSE_RECIPE[backbone][0]
 
 
+def test_posthoc_evaluation_of_named_run_directories(family, tmp_path):
+    one = family / "lbi_r4_seed8" / "lbi"
+    rows = evaluate_paper_checkpoints.main(["--family", str(family), "--run-dir", str(one), "--run-dir", str(family / "dense_seed7" / "dense"),
+                                            "--output-dir", str(tmp_path / "named"), "--eval-batches", "1", "--checkpoint", "latest",
+                                            "--device", "cpu"])
+    assert [r["label"] for r in rows] == ["lbi_r4_seed8", "dense_seed7"] and (tmp_path / "named" / "lm_eval_summary.csv").exists()
+    single = evaluate_paper_checkpoints.main([str(one), "--output-dir", str(tmp_path / "single"), "--eval-batches", "1",
+                                              "--checkpoint", "latest", "--device", "cpu"])
+    assert len(single) == 1 and single[0]["posthoc_val_ce_loss"] == rows[0]["posthoc_val_ce_loss"]
+    with pytest.raises(SystemExit):
+        evaluate_paper_checkpoints.main(["--eval-batches", "1"])
+
+
 def test_posthoc_evaluation_writes_summary(family, tmp_path):
     rows = evaluate_paper_checkpoints.main([str(family), "--output-dir", str(tmp_path / "ev"), "--eval-batches", "2",
                                             "--checkpoint", "latest", "--device", "cpu"])
@@ -69,6 +82,15 @@ def test_training_curve_outputs(family, tmp_path):
     groups = {g["label"]: g for g in json.loads((tmp_path / "plots" / "group_summary.json").read_text())}
     assert groups["lbi r4"]["num_runs"] == 2 and groups["dense"]["num_runs"] == 1
     assert (tmp_path / "plots" / "group_summary.csv").exists()
+    only_lbi = plot_training_curves.main([str(family), "--output-dir", str(tmp_path / "p2"), "--regimes", "native_region_interface",
+                                          "--label-mode", "rank_region"])
+    assert [g["label"] for g in only_lbi["groups"]] == ["lbi r4"] and only_lbi["groups"][0]["num_runs"] == 2
+    for mode, labels in (("backbone", {"transformer"}), ("regime", {"dense", "lbi"}), ("region_size", {"dense", "region=1"}),
+                         ("backbone_regime", {"transformer:dense", "transformer:lbi"})):
+        got = plot_training_curves.main([str(family), "--output-dir", str(tmp_path / f"p_{mode}"), "--label-mode", mode])
+        assert {g["label"] for g in got["groups"]} == labels
+    none_left = plot_message_ablations.main([str(family), "--output-dir", str(tmp_path / "abl_none"), "--exclude-variant-regex", "lbi_r4"])
+    assert none_left["summary"] == []
 
 
 def test_ablation_and_jacobian_outputs(family, tmp_path):
@@ -95,3 +117,28 @@ def test_grad_parity_report(tmp_path):
         assert (tmp_path / name).exists(), name
     assert "Transformer" in (tmp_path / "paper_table.tex").read_text()
     assert generate_grad_parity_report.latex_number(1.5e-9) == r"$1.50\times 10^{-9}$"
+
+
+def test_attention_benchmark_takes_the_sweep_flags_of_the_reference():
+    import torch
+
+    from lbi_b200.benchmarks import time_attention_pullback as bench
+
+    default = bench.sweep_from_args(bench.build_parser().parse_args([]))
+    assert default == {"batches": (8,), "heads": (16,), "seqs": (128, 512, 2048), "dims": (64, 128), "basis": (4, 16),
+                       "dtypes": (torch.float16, torch.bfloat16)}
+    args = bench.build_parser().parse_args(
+        ["--batches", "1", "--heads", "8", "--seq-lens", "128,512", "--head-dims", "64", "--basis-sizes", "4", "--dtype", "float16",
+         "--causal", "true", "--warmup", "5", "--iters", "20", "--include-autograd", "--include-simple", "--include-fa2-loop",
+         "--include-fa2-mma-pblock4", "--skip-torch-formula", "--check", "--check-max-tokens", "131072", "--no-default-kernel"])
+    assert bench.sweep_from_args(args) == {"batches": (1,), "heads": (8,), "seqs": (128, 512), "dims": (64,), "basis": (4,),
+                                           "dtypes": (torch.float16,)}
+    assert bench.modes_for_cell(args, torch.float16, 64, 8, 128, True) == ["fa2_loop", "reference_wmma_pblock4", "dense", "autograd"]
+    assert bench.modes_for_cell(args, torch.float32, 64, 8, 128, False) == ["dense", "autograd"]
+    row = dict(dtype="float16", seq_len=128, head_dim=64, basis=4, batch=8, heads=16)
+    assert bench.cell_name(row) == "float16_T128_D64_P4" and bench.cell_name({**row, "batch": 1}) == "float16_T128_D64_P4_B1_H16"
+    q, k, v, do = torch.randn(1, 2, 8, 4), torch.randn(1, 2, 8, 4), torch.randn(1, 2, 8, 4), torch.randn(1, 3, 2, 8, 4)
+    from lbi_b200.ops.attention import attention_input_pullback_basis
+
+    for got, want in zip(bench.autograd_mode(q, k, v, do, 0.5), attention_input_pullback_basis(q, k, v, do, scale=0.5, kernel_mode="dense")):
+        assert torch.allclose(got, want, atol=1e-5)
