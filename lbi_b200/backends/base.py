@@ -36,6 +36,8 @@ class RegionForwardCache:
 
 
 class RegionBackend(Protocol):
+    name: str
+
     def forward_region(self, *, region_input: torch.Tensor, region_index: int) -> tuple[torch.Tensor, RegionForwardCache]: ...
 
     def parameters_for_region(self, region_index: int) -> list[nn.Parameter]: ...

@@ -70,6 +70,8 @@ class TransformerRegionCache(RegionForwardCache):
 
 
 class TransformerLowering(Protocol):
+    name: str
+
     def input_pullback_basis(self, *, backend: "TransformerRegionBackend", cache: RegionForwardCache,
                              output_cotangent_basis: torch.Tensor) -> torch.Tensor: ...
 
@@ -79,6 +81,8 @@ class TransformerLowering(Protocol):
 
 class TorchAutogradTransformerLowering:
     """Oracle lowering: recompute the region on a basis-replicated batch and differentiate with autograd."""
+
+    name = "torch_autograd"
 
     def input_pullback_basis(self, *, backend, cache, output_cotangent_basis):
         bsz, nbasis = output_cotangent_basis.shape[:2]
@@ -99,6 +103,8 @@ class TorchAutogradTransformerLowering:
 
 class StructuredTransformerLowering:
     """Closed-form lowering over cached activations (fused sm_100a kernels on CUDA)."""
+
+    name = "structured"
 
     def _structured(self, backend, cache):
         if cache.structured is None:

@@ -34,7 +34,7 @@ def _state_in(cache, k):
 
 
 class TorchGraphInterfacePullbackProvider:
-    name = "graph"
+    name = "torch_graph"  # the reference's provider names (backward/pullbacks.py:153, :169)
 
     def __init__(self, basis_chunk: int = 1) -> None:
         self.basis_chunk = int(basis_chunk)  # unused: one batched VJP covers all directions (kept for the reference's signature)
@@ -57,7 +57,7 @@ class TorchGraphInterfacePullbackProvider:
 
 
 class TorchRecomputeInterfacePullbackProvider:
-    name = "recompute"
+    name = "torch_recompute"
 
     def __init__(self, basis_chunk: int = 1) -> None:
         if basis_chunk <= 0:
@@ -168,12 +168,15 @@ def materialize_interface_state_jacobian_t_recompute(*, model: Any, cache: dict,
 
 
 def build_interface_pullback_provider(mode: str, *, basis_chunk: int = 1) -> InterfacePullbackProvider:
-    if mode == "graph":
-        return TorchGraphInterfacePullbackProvider()
-    if mode == "recompute":
+    """``graph`` / ``recompute`` (also spelled ``torch_graph``, ``pytorch_recompute``, ... as in the reference,
+    backward/pullbacks.py:187-197), ``structured``, ``forward``."""
+    normalized = str(mode).strip().lower().replace("-", "_")
+    if normalized in {"graph", "torch_graph", "pytorch_graph"}:
+        return TorchGraphInterfacePullbackProvider(basis_chunk=basis_chunk)
+    if normalized in {"recompute", "torch_recompute", "pytorch_recompute"}:
         return TorchRecomputeInterfacePullbackProvider(basis_chunk=basis_chunk)
-    if mode == "structured":
+    if normalized == "structured":
         return StructuredInterfacePullbackProvider(basis_chunk=basis_chunk)
-    if mode == "forward":
+    if normalized in {"forward", "forward_mode"}:
         return ForwardModeInterfacePullbackProvider(basis_chunk=basis_chunk)
     raise ValueError("interface Jacobian mode must be one of: graph, recompute, structured, forward")
