@@ -98,6 +98,8 @@ def test_init_from_and_external_checkpoint_root_and_no_checkpoint(tmp_path):
 @pytest.mark.parametrize("kw", [
     dict(backbone="mamba2"), dict(backbone="mamba3"), dict(backbone="hybrid", layer_types="mamba3,transformer"),
     dict(backward_engine="fast", d_conv=0), dict(backward_engine="fast", region_axis="sequence", sequence_regions=4, tie_embeddings=True),
+    dict(backward_engine="fast", backbone="mamba2", region_axis="sequence", sequence_regions=2),
+    dict(backward_engine="fast", backbone="mamba3"), dict(backward_engine="fast", backbone="hybrid", layer_types="mamba2,transformer"),
     dict(backward_engine="reference_scan"), dict(backward_engine="autograd"), dict(interface_jacobian_mode="recompute", jacobian_basis_chunk=3),
     dict(interface_jacobian_mode="structured"), dict(region_axis="sequence", sequence_regions=2, interface_activation="gelu"),
 ])
@@ -125,7 +127,7 @@ def test_fast_engine_checkpoint_round_trips_into_torch_adamw(tmp_path):
     dict(steps=0), dict(lr_schedule="step"), dict(warmup_steps=10, steps=2), dict(min_lr_ratio=2.0), dict(region_size=0),
     dict(interface_jacobian_mode="magic"), dict(eval_message_ablation="drop"), dict(message_mask_keep_prob=0.0),
     dict(backbone="hybrid", layer_types=""), dict(backbone="mamba3", d_state=8), dict(region_axis="sequence", sequence_regions=0),
-    dict(backward_engine="fast", backbone="mamba2"),
+    dict(backward_engine="turbo"),
 ])
 def test_config_validation_rejects(tmp_path, bad):
     with pytest.raises(ValueError):
@@ -144,3 +146,62 @@ def test_text_byte_route(tmp_path):
     text.write_bytes(b"the quick brown fox jumps over the lazy dog. " * 200)
     summary = run_lbi_experiment(make_cfg(tmp_path, data_mode="text_byte", vocab_size=256, train_text_path=str(text)))
     assert summary["runs"][0]["final_val_ce_loss"] < 10.0
+
+
+def _tiny_corpus(tmp_path):
+    train, val = tmp_path / "train.txt", tmp_path / "val.txt"
+    train.write_text("hello world\n" * 128 + "bounded interfaces learn\n" * 128, encoding="utf-8")
+    val.write_text("hello bounded world\n" * 32, encoding="utf-8")
+    return train, val
+
+
+def test_text_bpe_route_trains_its_tokenizer(tmp_path):
+    pytest.importorskip("sentencepiece")
+    train, val = _tiny_corpus(tmp_path)
+    tok = tmp_path / "tok.model"
+    summary = run_lbi_experiment(make_cfg(
+        tmp_path, data_mode="text_bpe", train_text_path=str(train), val_text_path=str(val), tokenizer_path=str(tok), vocab_size=320,
+        tokenizer_train_bytes=4096, train_tokenizer=True, message_dim=8, message_hidden_dim=16))
+    run = summary["runs"][0]
+    assert tok.exists() and run["final_train_ce_loss"] == run["final_train_ce_loss"] and run["final_val_ce_loss"] < 10.0
+    info = json.loads((Path(summary["root_dir"]) / "lbi" / "data_info.json").read_text())
+    assert info["tokenizer_exists"] and info["tokenizer_type"] == "sentencepiece" and info["tokenizer_train_bytes"] == 4096
+
+
+def test_text_bpe_sharded_route_reads_pretokenized_shards(tmp_path):
+    pytest.importorskip("sentencepiece")
+    from lbi_b200.data.pretokenize_corpus import pretokenize_text_corpus
+
+    train, val = _tiny_corpus(tmp_path)
+    tok, shards = tmp_path / "tok.model", tmp_path / "tokens"
+    pretokenize_text_corpus(text_corpus="tiny_shakespeare", train_text_path=str(train), val_text_path=str(val),
+                            tokenizer_type="sentencepiece", tokenizer_path=str(tok), vocab_size=320, tokenizer_train_bytes=4096,
+                            train_tokenizer=True, shard_tokens=128, output_dir=str(shards))
+    assert (shards / "train_manifest.json").exists() and (shards / "val_manifest.json").exists()
+    summary = run_lbi_experiment(make_cfg(
+        tmp_path, data_mode="text_bpe_sharded", train_text_path=str(train), val_text_path=str(val), tokenizer_path=str(tok),
+        token_shards_dir=str(shards), vocab_size=320, save_every=2, message_dim=8, message_hidden_dim=16))
+    run = summary["runs"][0]
+    assert run["final_train_ce_loss"] == run["final_train_ce_loss"] and run["final_val_ce_loss"] < 10.0
+    info = json.loads((Path(summary["root_dir"]) / "lbi" / "data_info.json").read_text())
+    assert info["train_manifest_exists"] and info["val_manifest_exists"] and info["token_shards_dir"] == str(shards)
+
+
+@pytest.mark.parametrize("kind", ["llama", "llama31"])
+def test_pretrained_tokenizer_types_cannot_be_trained(tmp_path, kind):
+    from lbi_b200.data.bpe_tokenizer import load_text_tokenizer
+
+    train, _ = _tiny_corpus(tmp_path)
+    with pytest.raises(ValueError):
+        make_cfg(tmp_path, data_mode="text_bpe", train_text_path=str(train), tokenizer_type=kind, train_tokenizer=True, vocab_size=320)
+    with pytest.raises(ValueError):
+        load_text_tokenizer(tokenizer_type=kind, tokenizer_path=tmp_path / "none", train_path=train, vocab_size=320, train_bytes=1024,
+                            force_train=True)
+    with pytest.raises(FileNotFoundError):
+        load_text_tokenizer(tokenizer_type=kind, tokenizer_path=tmp_path / "none", train_path=train, vocab_size=320, train_bytes=1024)
+
+
+def test_fineweb_edu_needs_the_sharded_route(tmp_path):
+    with pytest.raises(ValueError):
+        make_cfg(tmp_path, text_corpus="fineweb_edu", data_mode="text_bpe", vocab_size=320)
+    assert make_cfg(tmp_path, text_corpus="fineweb_edu", data_mode="text_bpe_sharded", vocab_size=320).data_mode == "text_bpe_sharded"
