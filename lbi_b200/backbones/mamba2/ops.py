@@ -51,28 +51,41 @@ def mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, z=None, dt_bia
                               return_varlen_states=False):
     """x [b, l, h, p]; dt [b, l, h]; A [h]; B, C [b, l, g, n]; D [h] or [h, p]; z [b, l, h, p] (output gate: y silu(z));
     dt_bias [h]; initial_states [b, h, p, n]; seq_idx [b, l] ids of the sequences packed into a row (the state starts from
-    zero at every change; the initial state belongs to the first sequence).  Returns y like x, with the final state
-    [b, h, p, n] when ``return_final_states``."""
-    if return_varlen_states or cu_seqlens is not None:
-        raise NotImplementedError("per-sequence final states of a packed batch: call once per sequence")
+    zero at every change; the initial state belongs to the first sequence).  Returns y like x, followed by the final state
+    [b, h, p, n] when ``return_final_states`` and, when ``return_varlen_states`` (one packed row, boundaries in ``cu_seqlens``
+    [num_sequences + 1]), by the state at the end of every sequence [num_sequences, h, p, n]."""
+    if return_varlen_states:
+        if cu_seqlens is None or x.shape[0] != 1:
+            raise ValueError("return_varlen_states needs cu_seqlens and a single packed row")
     dt = _effective_dt(dt, dt_bias, dt_softplus, dt_limit)
-    if seq_idx is None:
+    varlen = None
+    if seq_idx is None and cu_seqlens is None:
         y, final = _scan(x, dt, A, B, C, chunk_size, D, initial_states)
     else:
-        rows, finals = [], []
+        rows, finals, per_sequence = [], [], []
         for b in range(x.shape[0]):
+            if cu_seqlens is not None and x.shape[0] == 1:
+                edges = [int(v) for v in cu_seqlens.tolist()]
+                segments = [(s, e) for s, e in zip(edges[:-1], edges[1:]) if e > s]
+            else:
+                segments = _segments(seq_idx[b])
             parts = []
-            for s, e in _segments(seq_idx[b]):
+            for s, e in segments:
                 init = initial_states[b : b + 1] if (initial_states is not None and s == 0) else None
                 y_seg, final_seg = _scan(x[b : b + 1, s:e], dt[b : b + 1, s:e], A, B[b : b + 1, s:e], C[b : b + 1, s:e], chunk_size, D,
                                          init)
                 parts.append(y_seg)
+                per_sequence.append(final_seg)
             rows.append(torch.cat(parts, dim=1))
             finals.append(final_seg)
         y, final = torch.cat(rows, dim=0), torch.cat(finals, dim=0)
+        varlen = torch.cat(per_sequence, dim=0)
     if z is not None:
         y = (y.float() * F.silu(z.float())).to(x.dtype)
-    return (y, final) if return_final_states else y
+    out = (y, final) if return_final_states else (y,)
+    if return_varlen_states:
+        out = (*out, varlen)
+    return out if len(out) > 1 else out[0]
 
 
 def ssd_selective_scan(x, dt, A, B, C, D=None, z=None, dt_bias=None, dt_softplus=False, dt_limit=_NO_LIMIT):

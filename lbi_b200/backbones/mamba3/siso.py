@@ -206,6 +206,15 @@ def mamba3_siso_chunked(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, 
     return y.to(out_dtype), theta_last, state, _rotate_pairs(k_last, theta_last), V[:, -1]
 
 
+def _packed_edges(cu_seqlens, batch: int, seqlen: int) -> list[tuple[int, int]]:
+    if batch != 1:
+        raise ValueError("cu_seqlens describes one packed row: the batch size must be 1")
+    edges = [int(v) for v in cu_seqlens.tolist()]
+    if edges[0] != 0 or edges[-1] != seqlen or any(b < a for a, b in zip(edges[:-1], edges[1:])):
+        raise ValueError("cu_seqlens must rise from 0 to the packed length")
+    return list(zip(edges[:-1], edges[1:]))
+
+
 def mamba3_siso_combined(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None, Z=None, Input_States=None,
                          chunk_size: int = 64, return_final_states: bool = False, cu_seqlens=None):
     """Entry point with the argument list of the reference's combined op
@@ -214,9 +223,23 @@ def mamba3_siso_combined(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None,
 
     Without states the sm_100a kernels run where the shape allows them (``ops.ssd.mamba3_siso_cuda``: bf16, head_dim 64,
     d_state 128); with ``Input_States`` or ``return_final_states`` the chunked fp32 form runs, which carries the four state
-    tensors (see ``mamba3_siso_chunked``).  Packed variable-length batches (``cu_seqlens``) are not supported."""
+    tensors (see ``mamba3_siso_chunked``).  With ``cu_seqlens`` [num_sequences + 1] the single row holds several sequences end
+    to end: each is evaluated on its own, the states have one entry per sequence."""
     if cu_seqlens is not None:
-        raise NotImplementedError("cu_seqlens: split the packed batch and call once per sequence")
+        outs, finals = [], []
+        for i, (s, e) in enumerate(_packed_edges(cu_seqlens, V.shape[0], V.shape[1])):
+            if e == s:
+                raise ValueError("cu_seqlens holds an empty sequence")
+            init = None if Input_States is None else tuple(t[i : i + 1] for t in Input_States)
+            res = mamba3_siso_chunked(Q[:, s:e], K[:, s:e], V[:, s:e], ADT[..., s:e], DT[..., s:e], Trap[..., s:e], Q_bias, K_bias,
+                                      Angles[:, s:e], D, None if Z is None else Z[:, s:e], chunk_size=chunk_size,
+                                      initial_states=init, return_final_states=True)
+            outs.append(res[0])
+            finals.append(res[1:])
+        y = torch.cat(outs, dim=1)
+        if not return_final_states:
+            return y
+        return (y, *(torch.cat([f[j] for f in finals], dim=0) for j in range(4)))
     if Input_States is None and not return_final_states:
         from lbi_b200.ops import ssd as ops_ssd
 
@@ -230,8 +253,13 @@ def mamba3_siso_combined(Q, K, V, ADT, DT, Trap, Q_bias, K_bias, Angles, D=None,
 def angle_dt(angle: torch.Tensor, dt: torch.Tensor, init_state: torch.Tensor | None = None, chunk_size: int = 64,
              return_output_state: bool = False, cu_seqlens=None):
     """Cumulative rotary phase with the argument layout of the reference's op (angle_dt.py:127-152): angle [b, l, h, s] raw
-    rates, dt [b, h, l] -> [b, l, h, s] = (init + cumsum(pi tanh(angle) dt)) mod 2 pi, optionally with the last phase."""
-    if cu_seqlens is not None:
-        raise NotImplementedError("cu_seqlens: split the packed batch and call once per sequence")
-    theta = angle_dt_cumsum(angle, dt.transpose(1, 2), init_state)
-    return (theta, theta[:, -1]) if return_output_state else theta
+    rates, dt [b, h, l] -> [b, l, h, s] = (init + cumsum(pi tanh(angle) dt)) mod 2 pi, optionally with the last phase
+    ([b, h, s], or one entry per sequence of a packed row when ``cu_seqlens`` is given; ``init_state`` likewise)."""
+    if cu_seqlens is None:
+        theta = angle_dt_cumsum(angle, dt.transpose(1, 2), init_state)
+        return (theta, theta[:, -1]) if return_output_state else theta
+    parts = []
+    for i, (s, e) in enumerate(_packed_edges(cu_seqlens, angle.shape[0], angle.shape[1])):
+        parts.append(angle_dt_cumsum(angle[:, s:e], dt[..., s:e].transpose(1, 2), None if init_state is None else init_state[i : i + 1]))
+    theta = torch.cat(parts, dim=1)
+    return (theta, torch.cat([p[:, -1] for p in parts], dim=0)) if return_output_state else theta

@@ -222,8 +222,19 @@ def test_mamba3_prefill_then_decode_and_state_carrying_combined_op():
     assert torch.allclose(mamba3_siso_combined(*cutargs(0, l)).double(), oracle, atol=2e-4, rtol=1e-4)
     theta, last = angle_dt(ang, DT, return_output_state=True)
     assert theta.shape == (b, l, h, n // 4) and torch.equal(last, whole[0]) and float(theta.min()) >= 0
-    with pytest.raises(NotImplementedError):
-        mamba3_siso_combined(*cutargs(0, l), cu_seqlens=torch.tensor([0, l]))
+    # one packed row of two sequences: each evaluated on its own, states per sequence
+    cu = torch.tensor([0, cut, l])
+    row = lambda t: t[:1]  # noqa: E731
+    packed_args = (row(Q), row(K), row(V), row(ADT), row(DT), row(Trap), qb, kb, row(ang), D, row(Z))
+    yp, *sp = mamba3_siso_combined(*packed_args, chunk_size=8, return_final_states=True, cu_seqlens=cu)
+    first = mamba3_siso_combined(row(Q)[:, :cut], row(K)[:, :cut], row(V)[:, :cut], row(ADT)[..., :cut], row(DT)[..., :cut],
+                                 row(Trap)[..., :cut], qb, kb, row(ang)[:, :cut], D, row(Z)[:, :cut], chunk_size=8,
+                                 return_final_states=True)
+    assert torch.equal(yp[:, :cut], first[0]) and all(t.shape[0] == 2 for t in sp) and torch.equal(sp[1][0], first[2][0])
+    theta_p, last_p = angle_dt(row(ang), row(DT), return_output_state=True, cu_seqlens=cu)
+    assert torch.equal(last_p, sp[0]) and torch.equal(theta_p[:, :cut], angle_dt(row(ang)[:, :cut], row(DT)[..., :cut]))
+    with pytest.raises(ValueError):
+        mamba3_siso_combined(*cutargs(0, l), cu_seqlens=cu)  # two rows cannot be one packed row
 
 
 def test_mamba2_op_level_entries_match_the_module_and_the_token_loop():
@@ -253,7 +264,13 @@ def test_mamba2_op_level_entries_match_the_module_and_the_token_loop():
     both = mamba_chunk_scan_combined(torch.cat([x, x], 1), torch.cat([dt, dt], 1), A, torch.cat([B, B], 1), torch.cat([C, C], 1), 8,
                                      D=D2, z=torch.cat([z, z], 1), dt_bias=bias, dt_softplus=True, dt_limit=(0.01, 0.5))
     assert torch.allclose(both[:, l:], y_next, atol=1e-4, rtol=1e-4)
-    with pytest.raises(NotImplementedError):
+    cu, ids = torch.tensor([0, 7, l]), torch.cat([torch.zeros(7), torch.ones(l - 7)])[None].long()
+    y_p, final_p, per_seq = mamba_chunk_scan_combined(x[:1], dt[:1], A, B[:1], C[:1], 8, seq_idx=ids, cu_seqlens=cu,
+                                                      return_final_states=True, return_varlen_states=True)
+    y_a, final_a = mamba_chunk_scan_combined(x[:1, :7], dt[:1, :7], A, B[:1, :7], C[:1, :7], 8, return_final_states=True)
+    assert per_seq.shape == (2, h, p, n) and torch.equal(per_seq[0], final_a[0]) and torch.equal(per_seq[1], final_p[0])
+    assert torch.equal(y_p[:, :7], y_a)
+    with pytest.raises(ValueError):
         mamba_chunk_scan_combined(x, dt, A, B, C, 8, return_varlen_states=True)
 
 
