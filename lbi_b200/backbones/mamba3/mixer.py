@@ -19,7 +19,7 @@ from torch import nn
 
 from ...ops import ssd as ops_ssd
 from ..norms import RMSNormGated
-from .siso import _rotate_pairs, mamba3_siso_chunked
+from .siso import _rotate_pairs, mamba3_siso_chunked, mamba3_siso_combined
 
 
 @dataclass
@@ -104,7 +104,7 @@ class Mamba3(nn.Module):
             self.norm = RMSNormGated(self.d_inner, eps=1e-5, norm_before_gate=True, group_size=headdim, **fk)
         self.out_proj = nn.Linear(self.d_inner, d_model, bias=False, **fk)
 
-    def _forward_impl(self, u: torch.Tensor, *, return_cache: bool = False, decode_states=None):
+    def _forward_impl(self, u: torch.Tensor, *, return_cache: bool = False, decode_states=None, cu_seqlens=None):
         bsz, seqlen, _ = u.shape
         proj = self.in_proj(u)
         gn = self.d_state * self.num_bc_heads
@@ -121,9 +121,11 @@ class Mamba3(nn.Module):
         DT = DT.transpose(1, 2)
         trap_t = trap.transpose(1, 2)
         angles_h = angles.unsqueeze(-2).expand(-1, -1, self.nheads, -1)
-        use_kernels = (decode_states is None and ops_ssd.siso_cuda_supported(x, C) and x.dtype == torch.bfloat16
-                       and self.D is not None)
-        if decode_states is not None:
+        use_kernels = (decode_states is None and cu_seqlens is None and ops_ssd.siso_cuda_supported(x, C)
+                       and x.dtype == torch.bfloat16 and self.D is not None)
+        if cu_seqlens is not None:  # one packed row of several sequences: the scan runs per sequence, the rest is per token
+            siso = partial(mamba3_siso_combined, chunk_size=self.chunk_size, cu_seqlens=cu_seqlens)
+        elif decode_states is not None:
             angle_state, ssm_state, k_state, v_state = decode_states
             siso = partial(mamba3_siso_chunked, chunk_size=self.chunk_size, return_final_states=True,
                            initial_states=(angle_state, ssm_state, k_state[:, 0], v_state))
@@ -160,17 +162,17 @@ class Mamba3(nn.Module):
         )
 
     def forward(self, u: torch.Tensor, seq_idx=None, cu_seqlens=None, inference_params=None) -> torch.Tensor:
-        self._full_sequence_only(cu_seqlens, inference_params)
-        return self._forward_impl(u)
+        """u [B, L, D] -> [B, L, D].  ``cu_seqlens`` [num_sequences + 1] marks the sequences laid end to end in a single row
+        (B = 1); each starts from a zero state and a zero rotary phase.  ``seq_idx`` is accepted and unused, as in the reference."""
+        self._full_sequence_only(inference_params)
+        return self._forward_impl(u, cu_seqlens=cu_seqlens)
 
     def forward_with_cache(self, u: torch.Tensor, seq_idx=None, cu_seqlens=None, inference_params=None):
-        self._full_sequence_only(cu_seqlens, inference_params)
-        return self._forward_impl(u, return_cache=True)
+        self._full_sequence_only(inference_params)
+        return self._forward_impl(u, return_cache=True, cu_seqlens=cu_seqlens)
 
     @staticmethod
-    def _full_sequence_only(cu_seqlens, inference_params) -> None:
-        if cu_seqlens is not None:
-            raise NotImplementedError("variable-length batches are not supported by the Mamba-3 mixer")
+    def _full_sequence_only(inference_params) -> None:
         if inference_params is not None:
             raise NotImplementedError("decode with allocate_inference_cache() and step(); forward() is the full-sequence path")
 

@@ -188,8 +188,9 @@ def test_mamba3_decode_steps_reproduce_the_full_sequence(outproj_norm):
     assert float(states[1].abs().sum()) > 0 and float(states[0].max()) < 2 * torch.pi
     with pytest.raises(NotImplementedError):
         mixer(u, inference_params=object())
-    with pytest.raises(NotImplementedError):
-        mixer.forward_with_cache(u, cu_seqlens=torch.tensor([0, 21]))
+    packed, _ = mixer.forward_with_cache(u[:1], cu_seqlens=torch.tensor([0, 8, 21]))
+    with torch.no_grad():
+        assert torch.allclose(packed[:, :8], mixer(u[:1, :8]), atol=2e-6) and torch.allclose(packed[:, 8:], mixer(u[:1, 8:]), atol=2e-6)
 
 
 def test_mamba3_prefill_then_decode_and_state_carrying_combined_op():
