@@ -72,13 +72,13 @@ def test_multi_rank_engine_matches_single_process(tmp_path, axis, regions, world
     assert torch.allclose(got["params"][:n], engine.flat.params[:n], atol=1e-5, rtol=1e-5)
 
 
-def _train_worker(rank, world, port, out_dir):
+def _train_worker(rank, world, port, out_dir, overrides=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
     from lbi_b200.train.lbi import run_lbi_experiment
 
     torch.set_num_threads(1)
     try:
-        run_lbi_experiment(_train_cfg(out_dir))
+        run_lbi_experiment(_train_cfg(out_dir, **(overrides or {})))
     finally:
         if dist.is_initialized():
             dist.destroy_process_group()
@@ -123,6 +123,28 @@ def test_training_program_on_two_ranks_matches_one_process(tmp_path, monkeypatch
     # a single process resumes from the checkpoint the two ranks wrote
     resumed = run_lbi_experiment(_train_cfg(tmp_path / "dist", steps=4, resume_from=str(tmp_path / "dist" / "run")))
     assert resumed["runs"][0]["start_step"] == 3
+
+
+@pytest.mark.parametrize("overrides", [
+    dict(backbone="mamba3", d_state=16, headdim=16, chunk_size=16),
+    dict(backbone="hybrid", layer_types="mamba2,transformer", d_state=16, headdim=16, chunk_size=16, d_conv=4, region_axis="depth",
+         region_size=1),
+])
+def test_training_program_on_two_ranks_with_mamba_backbones(tmp_path, monkeypatch, overrides):
+    """The same program on the Mamba-3 and hybrid stacks: the two-rank run logs the losses of the one-process run."""
+    import json
+
+    from lbi_b200.train.lbi import run_lbi_experiment
+
+    for key in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(key, raising=False)
+    mp.spawn(_train_worker, args=(2, _free_port(), str(tmp_path / "dist"), overrides), nprocs=2, join=True)
+    run_lbi_experiment(_train_cfg(tmp_path / "single", **overrides))
+    rows = {tag: [json.loads(line) for line in (tmp_path / tag / "run" / "lbi" / "metrics.jsonl").read_text().splitlines()]
+            for tag in ("dist", "single")}
+    assert len(rows["dist"]) == len(rows["single"]) >= 4
+    for a, b in zip(rows["dist"], rows["single"]):
+        assert a["split"] == b["split"] and a["ce_loss"] == pytest.approx(b["ce_loss"], rel=1e-4, abs=1e-5), (a, b)
 
 
 def test_basis_plan_is_balanced_and_complete():
