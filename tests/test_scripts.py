@@ -30,24 +30,108 @@ def family(tmp_path_factory):
     return root
 
 
+_LAUNCH_VARS = ("BACKBONE", "MODEL_SCALE", "MESSAGE_DIM", "TOKENIZER_PATH", "OUTPUT_ROOT", "FAMILY_NAME", "FAMILY_DIR", "TARGET_STEPS",
+                "TIE_EMBEDDINGS", "TOKENIZER_TYPE", "VOCAB_SIZE", "SEQ_LEN", "FAMILY_SEQ_LEN", "LR_MODEL", "WEIGHT_DECAY", "WARMUP_STEPS",
+                "VARIANT_NAME", "RUN_NAME", "OUTPUT_DIR", "SEED", "BACKWARD_ENGINE", "MESSAGE_HIDDEN_DIM")
+
+
+@pytest.fixture
+def launch_env(monkeypatch):
+    for var in _LAUNCH_VARS:
+        monkeypatch.delenv(var, raising=False)
+    monkeypatch.setenv("LBI_LAUNCH_QUIET", "1")
+    return monkeypatch
+
+
+def _parse(cmd):
+    assert cmd[1:3] == ["-m", "lbi_b200.train.lbi"]
+    return config_from_args(build_arg_parser().parse_args(cmd[3:]))
+
+
 @pytest.mark.parametrize("kind,backbone,dim", [("lbi", "transformer", 64), ("lbi", "hybrid", 32), ("dense", "mamba2", 16),
                                                ("lbi", "mamba3", 16)])
-def test_launcher_commands_parse_with_the_training_cli(monkeypatch, kind, backbone, dim):
-    monkeypatch.setenv("BACKBONE", backbone)
-    monkeypatch.setenv("MESSAGE_DIM", str(dim))
-    monkeypatch.setenv("TOKENIZER_PATH", "/tmp/tok")
-    cmd = paper_presets.build_command(kind)
-    assert cmd[1:3] == ["-m", "lbi_b200.train.lbi"]
-    cfg = config_from_args(build_arg_parser().parse_args(cmd[3:]))
+def test_launcher_commands_parse_with_the_training_cli(launch_env, kind, backbone, dim):
+    launch_env.setenv("BACKBONE", backbone)
+    launch_env.setenv("MESSAGE_DIM", str(dim))
+    launch_env.setenv("TOKENIZER_PATH", "/tmp/tok")
+    cfg = _parse(paper_presets.build_command(kind))
     arch = paper_presets.ARCHITECTURES[("canonical", backbone)]
     assert (cfg.layers, cfg.dim, cfg.backbone) == (arch.layers, arch.dim, backbone)
     assert cfg.seq_len == 1024 and cfg.batch_size == 1 and cfg.steps == 20000 and cfg.tie_embeddings
+    assert cfg.log_every == 20 and cfg.save_every == 5000 and cfg.eval_every == 200 and cfg.eval_batches == 4
     if kind == "lbi":
         assert cfg.message_dim == dim and cfg.region_size == 2 and cfg.interface_jacobian_mode == "recompute"
-        assert cfg.jacobian_basis_chunk == 32 and cfg.message_hidden_dim == arch.dim
+        assert cfg.jacobian_basis_chunk == 32 and cfg.message_hidden_dim == 0 and cfg.message_scale_init == 0.5
         assert cfg.lr_model == paper_presets.lbi_learning_rate(backbone, dim)
     else:
         assert cfg.lr_model == paper_presets.DENSE_RECIPE[backbone][0]
+    if backbone in ("mamba3", "hybrid"):
+        assert cfg.device == "cuda" and cfg.dtype == "bfloat16" and cfg.ngroups == 1
+
+
+def test_launcher_choices_follow_the_tables_of_the_reference_launchers(launch_env):
+    """Values read off scripts/train_lbi_paper.sh:44-92 / :146-176 and scripts/train_dense_paper.sh:40-83 of the reference."""
+    lr, dense, warm, wd = (paper_presets.lbi_learning_rate, paper_presets.dense_learning_rate, paper_presets.warmup_steps,
+                           paper_presets.weight_decay)
+    assert [lr("mamba2", 64), lr("mamba3", 64), lr("hybrid", 64), lr("hybrid", 32), lr("hybrid", 16), lr("transformer", 64)] == \
+        [8e-4, 3e-4, 3e-4, 3e-4, 6e-4, 6e-4]
+    assert [lr("mamba2", 64, "large"), lr("mamba3", 64, "large"), lr("hybrid", 16, "large"), lr("transformer", 8, "large")] == \
+        [6e-4, 3e-4, 3e-4, 6e-4]
+    assert [dense("mamba2"), dense("mamba3"), dense("hybrid"), dense("transformer"), dense("mamba3", "large"), dense("hybrid", "large")] == \
+        [8e-4, 6e-4, 6e-4, 6e-4, 3e-4, 3e-4]
+    assert [warm("mamba3"), warm("hybrid"), warm("mamba2"), warm("transformer"), warm("mamba3", "large")] == [500, 500, 1000, 1000, 1000]
+    assert [wd("mamba2"), wd("mamba3"), wd("hybrid"), wd("transformer"), wd("mamba3", "large"), wd("mamba2", "large")] == \
+        [0.03, 0.03, 0.03, 0.01, 0.1, 0.01]
+    assert [paper_presets.step_tag(n) for n in (20000, 2_000_000, 1500)] == ["20ksteps", "2msteps", "1500steps"]
+    assert [paper_presets.tokenizer_tag(*a) for a in (("llama", 32000), ("llama31", 128256), ("sentencepiece", 32000), ("llama", 1000))] == \
+        ["llama32k", "llama31", "sentencepiece32000", "llama1000"]
+    name = paper_presets.family_name(backbone="transformer", scale="canonical", seq_len=1024, steps=20000, tokenizer_tag="llama32k", tied=True)
+    assert name == "paper_transformer_12l_512d_llama32k_tied_seq1024_20ksteps"
+    assert paper_presets.family_from_env() == ("paper_mamba3_14l_768d_llama32k_tied_seq1024_20ksteps",
+                                               "out/region_interface/paper_mamba3_14l_768d_llama32k_tied_seq1024_20ksteps")
+
+    # leading positional arguments: output root, then backbone; runs land in <root>/<family>/<run name>/<variant>
+    cmd = paper_presets.build_command("lbi", ["/data/runs", "mamba2", "--eval-every", "7"])
+    cfg = _parse(cmd)
+    assert cfg.backbone == "mamba2" and cfg.eval_every == 7 and cfg.message_dim == 64 and cfg.run_name == "lbi_r64_seed7"
+    assert cfg.output_dir == "/data/runs/paper_mamba2_14l_768d_llama32k_tied_seq1024_20ksteps" and cfg.weight_decay == 0.03
+    launch_env.setenv("MODEL_SCALE", "large")
+    launch_env.setenv("BACKBONE", "mamba3")
+    launch_env.setenv("TIE_EMBEDDINGS", "no")
+    launch_env.setenv("BACKWARD_ENGINE", "fast")
+    cfg = _parse(paper_presets.build_command("dense"))
+    assert (cfg.layers, cfg.lr_model, cfg.weight_decay, cfg.warmup_steps, cfg.tie_embeddings) == (28, 3e-4, 0.1, 1000, False)
+    assert cfg.run_name == "dense_seed7" and cfg.output_dir.endswith("paper_mamba3_28l_768d_llama32k_untied_seq1024_20ksteps")
+    assert _parse(paper_presets.build_command("lbi")).backward_engine == "fast"
+    for var, bad in (("MODEL_SCALE", "huge"), ("BACKBONE", "rnn"), ("TIE_EMBEDDINGS", "maybe"), ("TARGET_STEPS", "0")):
+        launch_env.setenv(var, bad)
+        with pytest.raises(SystemExit):
+            paper_presets.build_command("lbi")
+        launch_env.setenv(var, {"MODEL_SCALE": "large", "BACKBONE": "mamba3", "TIE_EMBEDDINGS": "no", "TARGET_STEPS": "20000"}[var])
+
+
+def test_shell_launchers_share_the_family_name(launch_env, family, tmp_path):
+    """train -> evaluate -> plot through the .sh files: the evaluation and plotting launchers find the runs under the family
+    directory the training launcher would write to."""
+    import shutil
+    import subprocess
+    import sys
+
+    scripts = Path(paper_presets.__file__).parent
+    env = {k: v for k, v in __import__("os").environ.items() if k not in _LAUNCH_VARS}
+    env.update(PYTHON_BIN=sys.executable, BACKBONE="transformer", OUTPUT_ROOT=str(tmp_path / "runs"), LBI_LAUNCH_QUIET="1",
+               PYTHONPATH=str(scripts.parent.parent) + ":" + env.get("PYTHONPATH", ""))
+    dry = subprocess.run(["bash", str(scripts / "train_lbi_paper.sh"), "--dry-run"], env=env, capture_output=True, text=True, check=True)
+    name = "paper_transformer_12l_512d_llama32k_tied_seq1024_20ksteps"
+    assert f"--output-dir {tmp_path / 'runs' / name}" in dry.stdout and "--run-name lbi_r64_seed7" in dry.stdout
+    shutil.copytree(family, tmp_path / "runs" / name)  # stand-in for the trained family
+    env.update(EVAL_OUTPUT_ROOT=str(tmp_path / "evals"), EVAL_BATCHES="1", CHECKPOINT="latest", DEVICE="cpu")
+    subprocess.run(["bash", str(scripts / "evaluate_paper_checkpoints.sh")], env=env, capture_output=True, text=True, check=True)
+    assert len(json.loads((tmp_path / "evals" / name / "lm_eval_summary.json").read_text())) == 3
+    env.update(LABEL_MODE="regime", REGIMES="lbi")
+    subprocess.run(["bash", str(scripts / "plot_paper_results.sh")], env=env, capture_output=True, text=True, check=True)
+    groups = json.loads((tmp_path / "runs" / name / "plots_regime" / "group_summary.json").read_text())
+    assert [g["label"] for g in groups] == ["lbi"] and (tmp_path / "runs" / name / "ablation_plots_regime" / "ablation_summary.csv").exists()
 
 
 def test_posthoc_evaluation_of_named_run_directories(family, tmp_path):
