@@ -20,18 +20,40 @@ from typing import Any
 from ._charts import Chart, Series, mean_std, moving_average, write_csv, write_json
 
 
-def discover_runs(roots: list[Path]) -> list[Path]:
-    found: list[Path] = []
+def discover_runs_with_roots(roots: list[Path]) -> list[tuple[Path, Path]]:
+    """(experiment root, run directory) for every directory with ``metrics.csv`` + ``config.json`` at or below the roots; a
+    root that is itself a run directory counts with its parent as the experiment root."""
+    found: list[tuple[Path, Path]] = []
     for root in roots:
         if (root / "metrics.csv").exists():
-            found.append(root)
-        found.extend(p.parent for p in sorted(root.rglob("metrics.csv")) if p.parent != root)
+            found.append((root.parent, root))
+        found.extend((root, p.parent) for p in sorted(root.rglob("metrics.csv")) if p.parent != root)
     seen, out = set(), []
-    for p in found:
-        if p.resolve() not in seen and (p / "config.json").exists():
-            seen.add(p.resolve())
-            out.append(p)
+    for root, run in found:
+        if run.resolve() not in seen and (run / "config.json").exists():
+            seen.add(run.resolve())
+            out.append((root, run))
     return out
+
+
+def discover_runs(roots: list[Path]) -> list[Path]:
+    return [run for _, run in discover_runs_with_roots(roots)]
+
+
+def run_variant(root: Path, run_dir: Path, cfg: dict[str, Any]) -> str:
+    """The name the include / exclude filters see: the first directory below the experiment root (``lbi_r32_seed7`` for
+    ``<root>/lbi_r32_seed7/lbi``), else the run directory's parent, else a name rebuilt from the config
+    (reference scripts/plot_training_curves.py:164-176)."""
+    try:
+        parts = run_dir.resolve().relative_to(root.resolve()).parts
+    except ValueError:
+        parts = (run_dir.name,)
+    variant = parts[0] if len(parts) > 1 else run_dir.parent.name
+    if variant and variant != "." and variant != run_dir.name:
+        return variant
+    if run_dir.name in {"dense", "backprop_ref"}:
+        return f"dense_seed{cfg.get('seed', 'unknown')}"
+    return f"lbi_r{cfg.get('message_dim', 'unknown')}_seed{cfg.get('seed', 'unknown')}"
 
 
 def read_metrics(run_dir: Path) -> list[dict[str, Any]]:
@@ -93,15 +115,16 @@ def load_groups(roots: list[Path], *, include: str = "", exclude: str = "", labe
     """``regimes`` keeps only runs of the named kinds (``dense``, ``lbi``; the first release's names are understood)."""
     wanted = None if not regimes else {_REGIME_ALIASES.get(r, r) for r in regimes}
     kept: list[tuple[Path, dict]] = []
-    for run in discover_runs(roots):
-        name = run.parent.name + "/" + run.name
+    for root, run in discover_runs_with_roots(roots):
+        cfg = json.loads((run / "config.json").read_text(encoding="utf-8"))
+        name = run_variant(root, run, cfg)
         if include and not re.search(include, name):
             continue
         if exclude and re.search(exclude, name):
             continue
         if wanted is not None and run_regime(run) not in wanted:
             continue
-        kept.append((run, json.loads((run / "config.json").read_text(encoding="utf-8"))))
+        kept.append((run, cfg))
     sizes = {cfg.get("region_size") for run, cfg in kept if run.name not in _DENSE_NAMES}
     groups: dict[str, list[dict]] = defaultdict(list)
     for run, cfg in kept:
@@ -128,10 +151,21 @@ def aggregate(runs: list[dict], split: str, xkey: str, ykey: str, smooth: int = 
     return Series("", xs, moving_average(mean, smooth), band if len(curves) > 1 else None)
 
 
+def _population(values: list[float]) -> tuple[float, float]:
+    vals = [float(v) for v in values if v is not None and math.isfinite(float(v))]
+    if not vals:
+        return float("nan"), float("nan")
+    m = sum(vals) / len(vals)
+    return m, (math.sqrt(sum((v - m) ** 2 for v in vals) / len(vals)) if len(vals) > 1 else 0.0)
+
+
 def summarize(groups: dict[str, list[dict]]) -> list[dict[str, Any]]:
+    """One row per group.  The columns of the reference's table (scripts/plot_training_curves.py:615-647: backbones, regimes,
+    seeds, variants, region_sizes, lr_models, seq_lens, mean / std of total parameters and of the final / best validation CE, the
+    spread being the population standard deviation) plus the sample-deviation columns the figures here use and the throughput."""
     out = []
     for label, runs in sorted(groups.items()):
-        finals, bests, tps = [], [], []
+        finals, bests, tps, params = [], [], [], []
         for r in runs:
             val = [x for x in r["rows"] if x["split"] == "val" and x.get("ce_loss") is not None]
             train = [x for x in r["rows"] if x["split"] == "train" and x.get("tokens_per_s")]
@@ -140,12 +174,30 @@ def summarize(groups: dict[str, list[dict]]) -> list[dict[str, Any]]:
                 bests.append(min(x["ce_loss"] for x in val))
             if train:
                 tps.append(sum(x["tokens_per_s"] for x in train) / len(train))
+            info = r["dir"] / "model_info.json"
+            if info.exists():
+                params.append(json.loads(info.read_text(encoding="utf-8")).get("total_params"))
         fm, fs = mean_std(finals)
         bm, bs = mean_std(bests)
         tm, _ = mean_std(tps)
-        out.append({"label": label, "num_runs": len(runs), "seeds": ",".join(str(r["cfg"].get("seed", "")) for r in runs),
-                    "final_val_ce_mean": fm, "final_val_ce_std": fs, "best_val_ce_mean": bm, "best_val_ce_std": bs,
-                    "mean_tokens_per_s": tm})
+        cfgs = [r["cfg"] for r in runs]
+        lbi_cfgs = [r["cfg"] for r in runs if r["dir"].name not in _DENSE_NAMES]
+        by_seed = sorted(runs, key=lambda r: (r["cfg"].get("seed", 0), str(r["dir"])))
+        out.append({
+            "label": label, "num_runs": len(runs),
+            "backbones": ",".join(sorted({str(c.get("backbone", "")) for c in cfgs})),
+            "regimes": ",".join(sorted({run_regime(r["dir"]) for r in runs})),
+            "seeds": ",".join(str(r["cfg"].get("seed", "")) for r in by_seed),
+            "variants": ",".join(sorted(r["dir"].parent.name for r in runs)),
+            "region_sizes": ",".join(str(v) for v in sorted({c["region_size"] for c in lbi_cfgs if c.get("region_size") is not None})),
+            "lr_models": ",".join(f"{v:g}" for v in sorted({float(c["lr_model"]) for c in cfgs if c.get("lr_model") is not None})),
+            "seq_lens": ",".join(str(v) for v in sorted({c["seq_len"] for c in cfgs if c.get("seq_len") is not None})),
+            "mean_total_params": _population(params)[0], "std_total_params": _population(params)[1],
+            "mean_final_val_ce": _population(finals)[0], "std_final_val_ce": _population(finals)[1],
+            "mean_best_val_ce": _population(bests)[0], "std_best_val_ce": _population(bests)[1],
+            "final_val_ce_mean": fm, "final_val_ce_std": fs, "best_val_ce_mean": bm, "best_val_ce_std": bs,
+            "mean_tokens_per_s": tm,
+        })
     return out
 
 

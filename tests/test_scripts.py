@@ -165,6 +165,11 @@ def test_training_curve_outputs(family, tmp_path):
             "tokens_per_s_vs_step", "message_diagnostics", "val_summary_bar"} <= names
     groups = {g["label"]: g for g in json.loads((tmp_path / "plots" / "group_summary.json").read_text())}
     assert groups["lbi r4"]["num_runs"] == 2 and groups["dense"]["num_runs"] == 1
+    lbi = groups["lbi r4"]
+    assert (lbi["backbones"], lbi["regimes"], lbi["seeds"], lbi["variants"], lbi["region_sizes"], lbi["seq_lens"]) == \
+        ("transformer", "lbi", "7,8", "lbi_r4_seed7,lbi_r4_seed8", "1", "16")
+    assert lbi["mean_total_params"] > 0 and lbi["std_total_params"] == 0.0 and lbi["std_final_val_ce"] >= 0.0
+    assert lbi["mean_final_val_ce"] == pytest.approx(lbi["final_val_ce_mean"]) and groups["dense"]["region_sizes"] == ""
     assert (tmp_path / "plots" / "group_summary.csv").exists()
     only_lbi = plot_training_curves.main([str(family), "--output-dir", str(tmp_path / "p2"), "--regimes", "native_region_interface",
                                           "--label-mode", "rank_region"])
@@ -173,6 +178,12 @@ def test_training_curve_outputs(family, tmp_path):
                          ("backbone_regime", {"transformer:dense", "transformer:lbi"})):
         got = plot_training_curves.main([str(family), "--output-dir", str(tmp_path / f"p_{mode}"), "--label-mode", mode])
         assert {g["label"] for g in got["groups"]} == labels
+    anchored = plot_training_curves.main([str(family), "--output-dir", str(tmp_path / "p_anch"), "--include-variant-regex",
+                                          r"^(dense_seed[789]|lbi_r(4|32|64)_seed[78])$", "--exclude-variant-regex", r"^lbi_r4_seed8$"])
+    assert {g["label"]: g["num_runs"] for g in anchored["groups"]} == {"dense": 1, "lbi r4": 1}
+    assert plot_training_curves.run_variant(family, family / "lbi_r4_seed7" / "lbi", {}) == "lbi_r4_seed7"
+    assert plot_training_curves.run_variant(family.parent, family / "lbi_r4_seed7" / "lbi", {}) == family.name
+    assert plot_training_curves.run_variant(family / "x", family / "x" / "lbi", {"message_dim": 4, "seed": 7}) == "x"
     none_left = plot_message_ablations.main([str(family), "--output-dir", str(tmp_path / "abl_none"), "--exclude-variant-regex", "lbi_r4"])
     assert none_left["summary"] == []
 
