@@ -20,8 +20,10 @@ _FIELDS = ("jac_local_spec_mean", "jac_local_spec_max", "jac_local_frob_mean", "
            "jac_suffix_spec_mean", "jac_suffix_spec_max")
 
 
-def _tex_number(v: float) -> str:
-    return "--" if v != v else f"{v:.3g}"
+def _tex_pm(mean: Any, std: Any) -> str:
+    if mean is None or std is None or mean != mean:
+        return "--"
+    return f"{float(mean):.3f} $\\pm$ {0.0 if std != std else float(std):.3f}"
 
 
 def main(argv: list[str] | None = None) -> dict[str, Any]:
@@ -54,7 +56,9 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
         if s is not None:
             s.label = f"R = {rank}"
             chart.series.append(s)
-        row: dict[str, Any] = {"message_dim": rank, "num_runs": len(runs)}
+        runs = sorted(runs, key=lambda r: (r["cfg"].get("seed", 0), str(r["dir"])))
+        row: dict[str, Any] = {"rank": rank, "num_seeds": len(runs), "seeds": ",".join(str(r["cfg"].get("seed", "")) for r in runs),
+                               "message_dim": rank, "num_runs": len(runs)}
         for f in _FIELDS:
             finals = []
             for run in runs:
@@ -65,10 +69,12 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
         table.append(row)
     files = chart.save(out_dir / "jacobian_spec_mean_vs_tokens", dpi=ns.dpi, font_scale=ns.font_scale, also_pdf=True)
     write_csv(out_dir / "jacobian_final_summary.csv", table)
-    lines = [r"\begin{tabular}{r|c|c|c}", r"$R$ & local $\|J\|_2$ mean & local $\|J\|_2$ max & suffix $\|J\|_2$ max \\", r"\hline"]
+    # the table of the paper: rank | local spectral norm | suffix spectral norm | local Frobenius norm / sqrt(r), mean +- std over seeds
+    lines = [r"\begin{tabular}{c|c|c|c}", r"Rank $r$ & Local $\|J\|_2$ & Suffix $\|J\|_2$ & Local $\|J\|_F/\sqrt{r}$ \\", r"\hline"]
     for row in table:
-        lines.append(f"{row['message_dim']} & {_tex_number(row['jac_local_spec_mean_mean'])} & "
-                     f"{_tex_number(row['jac_local_spec_max_mean'])} & {_tex_number(row['jac_suffix_spec_max_mean'])} \\\\")
+        cells = [_tex_pm(row[f + "_mean"], row[f + "_std"]) for f in ("jac_local_spec_mean", "jac_suffix_spec_mean",
+                                                                      "jac_local_frob_normed_mean")]
+        lines.append(f"{row['rank']} & " + " & ".join(cells) + r" \\")
     lines += [r"\end{tabular}", ""]
     (out_dir / "jacobian_final_summary.tex").write_text("\n".join(lines), encoding="utf-8")
     return {"output_dir": str(out_dir), "figures": [str(f) for f in files], "table": table}

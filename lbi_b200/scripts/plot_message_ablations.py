@@ -53,8 +53,8 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
             curves.series.append(s)
             final, spread = s.y[-1], (s.band[-1] if s.band is not None else 0.0)
             bars.append((name, final, spread if math.isfinite(spread) else 0.0))
-            summary.append({"backbone": backbone, "split": split, "num_runs": len(runs), "final_ce_mean": final,
-                            "final_ce_std": spread, "final_tokens_seen": s.x[-1]})
+            summary.append({"backbone": backbone, "split": split, "num_runs": len(runs), "mean_final_ce": final,
+                            "std_final_ce": spread, "final_ce_mean": final, "final_ce_std": spread, "final_tokens_seen": s.x[-1]})
         if curves.series:
             files += curves.save(out_dir / f"{backbone}_ablation_ce_vs_tokens", dpi=ns.dpi, font_scale=ns.font_scale)
             files += Chart(f"{backbone}: final validation CE", "", "val CE", bars=bars).save(

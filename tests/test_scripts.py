@@ -193,10 +193,16 @@ def test_ablation_and_jacobian_outputs(family, tmp_path):
     stems = {Path(f).stem for f in out["figures"]}
     assert {"transformer_ablation_ce_vs_tokens", "transformer_ablation_final_ce"} <= stems
     with (tmp_path / "abl" / "ablation_summary.csv").open() as fh:
-        splits = {r["split"] for r in csv.DictReader(fh)}
+        abl_rows = list(csv.DictReader(fh))
+        splits = {r["split"] for r in abl_rows}
+    assert {"backbone", "split", "num_runs", "mean_final_ce", "std_final_ce"} <= set(abl_rows[0])
     assert {"val", "val_zero_all", "val_noise", "val_mask"} <= splits
     out = plot_jacobian_diagnostics.main([str(family), "--output-dir", str(tmp_path / "jac"), "--min-step", "1"])
     assert out["table"][0]["message_dim"] == 4 and out["table"][0]["num_runs"] == 2
+    first = out["table"][0]
+    assert (first["rank"], first["num_seeds"], first["seeds"]) == (4, 2, "7,8") and "jac_suffix_spec_mean_std" in first
+    tex = (tmp_path / "jac" / "jacobian_final_summary.tex").read_text()
+    assert tex.count("$\\pm$") == 3 and tex.splitlines()[3].startswith("4 & ")
     assert (tmp_path / "jac" / "jacobian_final_summary.csv").exists() and (tmp_path / "jac" / "jacobian_final_summary.tex").exists()
     assert any(Path(f).stem == "jacobian_spec_mean_vs_tokens" for f in out["figures"])
 
