@@ -213,7 +213,7 @@ def make_figures(groups: dict[str, list[dict]], out_dir: Path, *, dpi: int, font
                     s.label, s.style = f"{label}{suffix}", style
                     chart.series.append(s)
         if chart.series:
-            written.extend(chart.save(out_dir / stem, dpi=dpi, font_scale=font_scale))
+            written.extend(chart.save(out_dir / stem, dpi=dpi, font_scale=font_scale, also_pdf=stem.startswith("paper_")))
 
     both = lambda x: [("train", x, "ce_loss", " train", "--"), ("val", x, "ce_loss", " val", "-")]  # noqa: E731
     figure("ce_vs_tokens", "Cross-entropy vs tokens", "tokens seen", "CE loss", both("tokens_seen"))
