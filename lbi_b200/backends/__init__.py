@@ -3,8 +3,12 @@ from .base import RegionBackend, RegionForwardCache
 from .transformer import (
     StructuredTransformerLowering,
     TorchAutogradTransformerLowering,
+    TransformerAttentionCache,
+    TransformerLayerCache,
     TransformerLowering,
+    TransformerMLPCache,
     TransformerRegionBackend,
+    TransformerRegionCache,
 )
 from .transformer_cuda import CudaTransformerLowering
 from .transformer_structured import LayerCache, StructuredRegionCache, StructuredTransformerRegion
@@ -15,6 +19,10 @@ __all__ = [
     "RegionForwardCache",
     "TransformerLowering",
     "TransformerRegionBackend",
+    "TransformerAttentionCache",
+    "TransformerMLPCache",
+    "TransformerLayerCache",
+    "TransformerRegionCache",
     "TorchAutogradTransformerLowering",
     "StructuredTransformerLowering",
     "CudaTransformerLowering",

@@ -8,6 +8,7 @@ from .base import (
     assign_grad_map,
     collect_named_grads,
     is_scan_backprop_model,
+    store_named_grads,
 )
 from .local_vjp import LocalVJPProvider, TorchAutogradLocalVJPProvider, surrogate_backward
 from .pullbacks import (
@@ -17,6 +18,8 @@ from .pullbacks import (
     TorchGraphInterfacePullbackProvider,
     TorchRecomputeInterfacePullbackProvider,
     build_interface_pullback_provider,
+    materialize_interface_state_jacobian_t_graph,
+    materialize_interface_state_jacobian_t_recompute,
 )
 from .reference_scan import ReferenceScanEngine, lbi_reference_scan_backward_step
 from .scan import ScanADEngine, lbi_scan_backward_step
@@ -25,6 +28,7 @@ from .suffix_scan import (
     compose_suffix_jacobian_t,
     interface_state_jacobian_t_stats,
     propagate_state_adjoint_affine,
+    propagate_state_adjoint_by_autograd_chain,
     propagate_state_adjoint_by_chain,
     propagate_state_adjoint_from_last_region_input,
     propagate_state_adjoint_with_jacobian_scan,

@@ -78,3 +78,17 @@ class ReferenceScanEngine:
         result = lbi_reference_scan_backward_step(model=model, loss=loss, cache=cache)
         assign_grad_map(model, result.grad_map)
         return ADResult(grad_map=result.grad_map, diagnostics={"interface_scan_rms": 0.0})
+
+
+def __getattr__(name: str):
+    """``ScanADEngine``, ``lbi_scan_backward_step`` and ``build_interface_pullback_provider`` are importable from this module as
+    in the reference (backward/reference_scan.py:9, :37-42); resolved on first use because ``scan`` imports this module."""
+    if name in ("ScanADEngine", "lbi_scan_backward_step"):
+        from . import scan
+
+        return getattr(scan, name)
+    if name == "build_interface_pullback_provider":
+        from .pullbacks import build_interface_pullback_provider
+
+        return build_interface_pullback_provider
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -80,5 +80,15 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
     return {"output_dir": str(out_dir), "figures": [str(f) for f in files], "table": table}
 
 
+def generate_jacobian_diagnostic_plots(run_root: Path, *, output_dir: Path | None = None, min_step: int = 200, dpi: int = 150,
+                                       font_scale: float = 1.0, include_rank_regex: str = "") -> Path:
+    """Function form with the reference's argument list (scripts/plot_jacobian_diagnostics.py:271-279); returns the output directory."""
+    argv = [str(run_root), "--min-step", str(min_step), "--dpi", str(dpi), "--font-scale", str(font_scale),
+            "--include-rank-regex", include_rank_regex]
+    if output_dir is not None:
+        argv += ["--output-dir", str(output_dir)]
+    return Path(main(argv)["output_dir"])
+
+
 if __name__ == "__main__":
     main()

@@ -63,5 +63,15 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
     return {"output_dir": str(out_dir), "figures": [str(f) for f in files], "summary": summary}
 
 
+def generate_message_ablation_plots(run_roots, *, output_dir: Path | None = None, dpi: int = 150, include_variant_regex: str = "",
+                                    exclude_variant_regex: str = "") -> Path:
+    """Function form with the reference's argument list (scripts/plot_message_ablations.py:241-248); returns the output directory."""
+    argv = [str(r) for r in run_roots] + ["--dpi", str(dpi), "--include-variant-regex", include_variant_regex,
+                                          "--exclude-variant-regex", exclude_variant_regex]
+    if output_dir is not None:
+        argv += ["--output-dir", str(output_dir)]
+    return Path(main(argv)["output_dir"])
+
+
 if __name__ == "__main__":
     main()

@@ -257,5 +257,19 @@ def main(argv: list[str] | None = None) -> dict[str, Any]:
     return {"output_dir": str(out_dir), "figures": [str(f) for f in files], "groups": summary}
 
 
+def generate_training_plots(run_roots, *, output_dir: Path | None = None, dpi: int = 150, label_mode: str = "auto", regimes=None,
+                            smooth_window: int = 25, font_scale: float = 1.0, include_variant_regex: str = "",
+                            exclude_variant_regex: str = "") -> Path:
+    """Function form with the reference's argument list (scripts/plot_training_curves.py:672-683); returns the output directory."""
+    argv = [str(r) for r in run_roots] + ["--dpi", str(dpi), "--label-mode", label_mode, "--smooth-window", str(smooth_window),
+                                          "--font-scale", str(font_scale), "--include-variant-regex", include_variant_regex,
+                                          "--exclude-variant-regex", exclude_variant_regex]
+    if output_dir is not None:
+        argv += ["--output-dir", str(output_dir)]
+    if regimes:
+        argv += ["--regimes", ",".join(r for r in regimes if r)]
+    return Path(main(argv)["output_dir"])
+
+
 if __name__ == "__main__":
     main()

@@ -184,6 +184,10 @@ def test_training_curve_outputs(family, tmp_path):
     assert plot_training_curves.run_variant(family, family / "lbi_r4_seed7" / "lbi", {}) == "lbi_r4_seed7"
     assert plot_training_curves.run_variant(family.parent, family / "lbi_r4_seed7" / "lbi", {}) == family.name
     assert plot_training_curves.run_variant(family / "x", family / "x" / "lbi", {"message_dim": 4, "seed": 7}) == "x"
+    out_dir = plot_training_curves.generate_training_plots([family], output_dir=tmp_path / "fn", regimes=["native_region_interface"],
+                                                           label_mode="rank_region", smooth_window=1)
+    assert out_dir == tmp_path / "fn" and (out_dir / "group_summary.json").exists()
+    assert plot_message_ablations.generate_message_ablation_plots([family], output_dir=tmp_path / "fn_abl") == tmp_path / "fn_abl"
     none_left = plot_message_ablations.main([str(family), "--output-dir", str(tmp_path / "abl_none"), "--exclude-variant-regex", "lbi_r4"])
     assert none_left["summary"] == []
 

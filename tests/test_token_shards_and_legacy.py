@@ -215,6 +215,18 @@ def test_reference_names_import_from_the_same_modules():
     from lbi_b200.models.lbi_language_model import build_region_ranges  # noqa: F401
 
     assert Mamba3BlockForwardCache is Mamba3BlockCache
+    from lbi_b200.backends import TransformerLayerCache as exported_layer_cache, TransformerRegionCache as exported_region_cache
+    from lbi_b200.backward import (ScanADEngine, materialize_interface_state_jacobian_t_graph as exported_graph,  # noqa: F401
+                                   materialize_interface_state_jacobian_t_recompute as exported_recompute,  # noqa: F401
+                                   propagate_state_adjoint_by_autograd_chain as exported_chain, store_named_grads)  # noqa: F401
+    from lbi_b200.backward.reference_scan import ScanADEngine as via_reference_scan, lbi_scan_backward_step  # noqa: F401
+    from lbi_b200.scripts.plot_jacobian_diagnostics import generate_jacobian_diagnostic_plots  # noqa: F401
+    from lbi_b200.scripts.plot_message_ablations import generate_message_ablation_plots  # noqa: F401
+    from lbi_b200.scripts.plot_training_curves import generate_training_plots  # noqa: F401
+    from lbi_b200.train.config import ALL_REGIME, DENSE_REGIME, LBI_REGIME
+
+    assert exported_layer_cache is TransformerLayerCache and exported_region_cache is TransformerRegionCache
+    assert via_reference_scan is ScanADEngine and (DENSE_REGIME, LBI_REGIME, ALL_REGIME) == ("dense", "lbi", "all")
 
 
 def test_transformer_layer_caches_and_jacobian_function_forms():
