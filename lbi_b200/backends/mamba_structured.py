@@ -19,7 +19,7 @@ fp32 PyTorch statements on CPU).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any
 
 import torch

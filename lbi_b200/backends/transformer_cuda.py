@@ -6,8 +6,6 @@ attention entry point with the reference's argument layout.
 """
 from __future__ import annotations
 
-import torch
-
 from .transformer import StructuredTransformerLowering
 
 

@@ -19,7 +19,7 @@ from ..backends.base import current_autocast
 from ..canvas import TokenEmbeddingCanvas
 from ..interfaces import InterfaceModule, InterfaceStep
 from ..readouts import NormLMHeadReadout
-from .region_plan import RegionPlan, build_region_ranges
+from .region_plan import RegionPlan, build_region_ranges  # noqa: F401  (importable from here as in the reference)
 
 _VALID_STATE_ABLATIONS = {"none", "zero_all", "noise", "mask"}
 
