@@ -440,3 +440,24 @@ def test_recomputes_run_under_the_autocast_state_of_the_forward(backbone):
     assert seen and all(seen)
     _, plain = model.forward_with_cache(ids, detach_states=True)
     assert plain["autocast"] is None
+
+
+def test_backbone_spec_validation_and_reference_lm():
+    from lbi_b200.backbones.general import ReferenceLM, infer_message_hidden_dim
+
+    with pytest.raises(ValueError, match="hybrid layer_types must be drawn from"):
+        BackboneSpec(name="hybrid", dim=32, layers=2, d_state=8, d_conv=4, expand=2, headdim=8, n_heads=4,
+                     layer_types=("unsupported", "transformer")).validate()
+    with pytest.raises(ValueError):
+        BackboneSpec(name="hybrid", dim=32, layers=3, d_state=16, headdim=16, n_heads=4, layer_types=("mamba2", "transformer")).validate()
+    with pytest.raises(ValueError):
+        BackboneSpec(name="transformer", dim=30, layers=2, n_heads=4).validate()
+    spec = BackboneSpec(name="mamba2", dim=16, layers=2, d_state=4, d_conv=4, expand=2, headdim=8, ngroups=1, chunk_size=16,
+                        use_mem_eff_path=True)
+    model = ReferenceLM(vocab_size=64, backbone_spec=spec)
+    assert len(model.blocks) == 2 and type(model.blocks[0]).__name__ == "Mamba2Block"
+    logits = model(torch.randint(0, 64, (2, 12)))
+    assert logits.shape == (2, 12, 64) and torch.isfinite(logits).all()
+    assert infer_message_hidden_dim(spec, 0) == 16 and infer_message_hidden_dim(spec, 24) == 24
+    with pytest.raises(ValueError):
+        infer_message_hidden_dim(spec, -1)
