@@ -103,6 +103,64 @@ class NativeRegionInterfaceModel(nn.Module):
         x_out = self.backbone.forward_range(x_static + self.interface.decode(m_in, ridx).unsqueeze(1), start, end)
         return self.interface.update(x_out, m_in, ridx, self.message_alpha[ridx]).state
 
+    # ---- helpers under the names the first release's tests and tools call (reference legacy/native_region_interface.py:155-157,
+    # :172-200, :312-397); each is the closed-form statement over one piece of the interface
+    def _pool_hidden(self, x: torch.Tensor) -> torch.Tensor:
+        return self.interface.pool_hidden(x)
+
+    def _apply_message_ablation(self, m: torch.Tensor, *, mode: str, next_region_idx: int = 0, noise_std: float = 1.0,
+                                mask_keep_prob: float = 0.5, generator: torch.Generator | None = None) -> torch.Tensor:
+        return self._ablate(m, mode, noise_std, mask_keep_prob, generator)
+
+    def _module_input_pullback_matrix_autograd(self, module: nn.Module, x: torch.Tensor, g_out: torch.Tensor) -> torch.Tensor:
+        """J^T of any module on [B, D] inputs for a basis g_out [B, P, D_out], by one backward pass over a replicated batch."""
+        if x.dim() != 2 or g_out.dim() != 3:
+            raise ValueError("module input pullback expects x [B, D] and g_out [B, P, D_out].")
+        bsz, nbasis = g_out.shape[:2]
+        rep = x.detach().repeat_interleave(nbasis, dim=0).requires_grad_(True)
+        with torch.enable_grad():
+            y = module(rep)
+        (g,) = torch.autograd.grad(y, rep, g_out.to(device=y.device, dtype=y.dtype).reshape_as(y))
+        return g.reshape(bsz, nbasis, x.shape[-1]).to(device=g_out.device, dtype=g_out.dtype)
+
+    def _linear_input_pullback_matrix(self, linear: nn.Linear, g_out: torch.Tensor) -> torch.Tensor:
+        if g_out.dim() != 3:
+            raise ValueError("linear pullback expects g_out shaped [B, P, D_out].")
+        dtype = torch.promote_types(g_out.dtype, linear.weight.dtype)
+        return (g_out.to(device=linear.weight.device, dtype=dtype) @ linear.weight.to(dtype)).to(device=g_out.device, dtype=g_out.dtype)
+
+    def _silu_input_pullback_matrix(self, x: torch.Tensor, g_out: torch.Tensor) -> torch.Tensor:
+        if x.dim() != 2 or g_out.dim() != 3:
+            raise ValueError("SiLU pullback expects x [B, D] and g_out [B, P, D].")
+        from ..interfaces.vector_mlp import activation_derivative
+
+        dtype = torch.promote_types(x.dtype, g_out.dtype)
+        slope = activation_derivative(x.to(device=g_out.device, dtype=dtype), "silu")
+        return (g_out.to(dtype) * slope.unsqueeze(1)).to(g_out.dtype)
+
+    def _region_message_head_input_pullback_matrix(self, head: VectorMLPHead, x: torch.Tensor, g_out: torch.Tensor) -> torch.Tensor:
+        if not isinstance(head, VectorMLPHead):
+            raise TypeError(f"unsupported message head type: {type(head).__name__}")
+        return head_input_jacobian_t(head, x, g_out).to(device=g_out.device, dtype=g_out.dtype)
+
+    def _mean_pool_pullback_matrix(self, g_pooled: torch.Tensor, seq_len: int) -> torch.Tensor:
+        if g_pooled.dim() != 3:
+            raise ValueError("mean-pool pullback expects g_pooled shaped [B, P, D].")
+        if seq_len <= 0:
+            raise ValueError("seq_len must be positive.")
+        return mean_pool_jacobian_t(g_pooled, seq_len)
+
+    def _broadcast_message_pullback_matrix(self, g_hidden_input: torch.Tensor) -> torch.Tensor:
+        if g_hidden_input.dim() != 4:
+            raise ValueError("broadcast pullback expects g_hidden_input shaped [B, P, L, D].")
+        return g_hidden_input.sum(dim=2)
+
+    def _materialize_interface_pullback_mats_graph(self, cache: dict[str, Any]) -> list[torch.Tensor]:
+        return self.materialize_interface_pullback_mats(cache, mode="graph")
+
+    def _materialize_interface_pullback_mats_recompute(self, cache: dict[str, Any], basis_chunk: int) -> list[torch.Tensor]:
+        return self._materialize_recompute(cache, int(basis_chunk))
+
     @staticmethod
     def _ablate(m, mode, noise_std, keep_prob, generator):
         if mode == "none":
@@ -158,8 +216,10 @@ class NativeRegionInterfaceModel(nn.Module):
                                     region_messages=list(cache["region_messages"]), region_ranges=[tuple(r) for r in cache["region_ranges"]],
                                     region_caches=list(cache["region_caches"]))
 
-    def forward(self, input_ids: torch.Tensor, **kwargs) -> torch.Tensor:
-        return self.forward_with_cache(input_ids, **kwargs)[0]
+    def forward(self, input_ids: torch.Tensor, *, message_ablation: str = "none", message_noise_std: float = 1.0,
+                message_mask_keep_prob: float = 0.5, ablation_generator: torch.Generator | None = None) -> torch.Tensor:
+        return self.forward_with_cache(input_ids, message_ablation=message_ablation, message_noise_std=message_noise_std,
+                                       message_mask_keep_prob=message_mask_keep_prob, ablation_generator=ablation_generator)[0]
 
     # ---- closed-form pieces of the region-local pullback (reference legacy/native_region_interface.py:399-457; there the
     # LayerNorm factor is an autograd call on a replicated batch, here every factor is closed-form)
@@ -249,9 +309,10 @@ class NativeRegionInterfaceModel(nn.Module):
         return [suffix[:, k].contiguous() for k in range(len(mats) + 1)]
 
     @staticmethod
-    def _apply_pullback_mat(mat: torch.Tensor, vec: torch.Tensor) -> torch.Tensor:
+    def _apply_pullback_mat(mat: torch.Tensor, vec: torch.Tensor, *, out_dtype: torch.dtype | None = None) -> torch.Tensor:
         dtype = torch.promote_types(mat.dtype, vec.dtype)
-        return torch.einsum("bij,bj->bi", mat.to(dtype), vec.to(dtype)).to(vec.dtype)
+        return torch.einsum("bij,bj->bi", mat.to(dtype), vec.to(device=mat.device, dtype=dtype)).to(
+            device=vec.device, dtype=vec.dtype if out_dtype is None else out_dtype)
 
     def interface_vjp_scan_from_mats(self, interface_pullback_mats, g_top_message: torch.Tensor) -> list[torch.Tensor]:
         """Every message cotangent g_k = S_k g_K from the materialised A_k^T and the cotangent of the last message."""

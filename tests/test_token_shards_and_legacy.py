@@ -179,6 +179,54 @@ def test_legacy_model_closed_form_region_pullback_matches_autograd():
         assert torch.allclose(total.transpose(1, 2), mats[ridx], atol=1e-5, rtol=1e-4)
 
 
+def test_legacy_model_helpers_under_the_names_of_the_first_release():
+    from lbi_b200.legacy.native_region_interface import RegionMessageHead
+
+    model = _legacy_model()
+    torch.manual_seed(11)
+    ids = torch.randint(0, 40, (2, 12))
+    logits, cache = model.forward_with_cache(ids)
+    x_static = cache["boundaries"][0]
+    for ridx in range(model.n_regions):  # a region's hidden input is the embedding plus the decoded incoming message
+        want = x_static + model.message_to_hidden[ridx](cache["region_messages"][ridx]).unsqueeze(1)
+        assert torch.allclose(cache["region_hidden_inputs"][ridx], want, atol=1e-6)
+    assert torch.equal(model(ids, message_ablation="none"), logits)
+    assert not torch.allclose(model(ids, message_ablation="zero_all"), logits)
+    assert torch.equal(model._pool_hidden(x_static), x_static.mean(dim=1))
+    m = cache["region_messages"][1]
+    assert torch.equal(model._apply_message_ablation(m, mode="zero_all", next_region_idx=1, noise_std=1.0, mask_keep_prob=0.5,
+                                                     generator=None), torch.zeros_like(m))
+    with pytest.raises(ValueError):
+        model._apply_message_ablation(m, mode="drop", next_region_idx=1, noise_std=1.0, mask_keep_prob=0.5, generator=None)
+
+    for hidden_dim in (0, 9):
+        head = RegionMessageHead(5, 7, hidden_dim=hidden_dim)
+        x, g_out = torch.randn(3, 5, requires_grad=True), torch.randn(3, 4, 7)
+        y = head(x)
+        want = torch.stack([torch.autograd.grad(y, x, g_out[:, i], retain_graph=True)[0] for i in range(4)], dim=1)
+        assert torch.allclose(model._region_message_head_input_pullback_matrix(head, x.detach(), g_out), want, atol=1e-6)
+        assert torch.allclose(model._module_input_pullback_matrix_autograd(head, x.detach(), g_out), want, atol=1e-6)
+    lin = torch.nn.Linear(5, 7)
+    g_out, x = torch.randn(3, 4, 7), torch.randn(3, 7)
+    assert torch.allclose(model._linear_input_pullback_matrix(lin, g_out), g_out @ lin.weight, atol=1e-6)
+    xg = x.clone().requires_grad_(True)
+    (slope,) = torch.autograd.grad(torch.nn.functional.silu(xg).sum(), xg)
+    assert torch.allclose(model._silu_input_pullback_matrix(x, g_out), g_out * slope.unsqueeze(1), atol=1e-6)
+    pooled = torch.randn(2, 3, 6)
+    assert torch.allclose(model._mean_pool_pullback_matrix(pooled, 4), pooled.unsqueeze(2).expand(-1, -1, 4, -1) / 4.0)
+    g_hidden = torch.randn(2, 3, 4, 6)
+    assert torch.equal(model._broadcast_message_pullback_matrix(g_hidden), g_hidden.sum(dim=2))
+    graph = model._materialize_interface_pullback_mats_graph(cache)
+    recompute = model._materialize_interface_pullback_mats_recompute(cache, 4)
+    assert len(graph) == len(recompute) == model.n_regions and all(torch.allclose(a, b, atol=1e-5) for a, b in zip(graph, recompute))
+    vec = torch.randn(2, 6)
+    assert model._apply_pullback_mat(graph[0], vec, out_dtype=torch.float64).dtype == torch.float64
+    for bad in (lambda: model._mean_pool_pullback_matrix(pooled, 0), lambda: model._broadcast_message_pullback_matrix(pooled),
+                lambda: model._linear_input_pullback_matrix(lin, x)):
+        with pytest.raises(ValueError):
+            bad()
+
+
 def test_first_release_trainer_entry_and_component_counts(tmp_path):
     from lbi_b200.legacy import train_region_interface as legacy_train
     from lbi_b200.train.model_builders import build_lbi_language_model
