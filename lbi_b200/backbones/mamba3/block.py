@@ -69,6 +69,19 @@ class Mamba3Block(nn.Module):
         return out, residual_out, Mamba3BlockCache(residual_out=residual_out, normed=normed, mixer=mixer_cache,
                                                    hidden_input=hidden_states, residual_input=residual, hidden_output=out)
 
+    @staticmethod
+    def _module_input_pullback_matrix_autograd(module: nn.Module, x: torch.Tensor, g_out: torch.Tensor) -> torch.Tensor:
+        """J^T of a module on [B, L, D] inputs for a basis g_out [B, P, L, D]: one backward pass over a replicated batch
+        (reference backbones/mamba3/block.py:50-78)."""
+        if x.dim() != 3 or g_out.dim() != 4:
+            raise ValueError("block pullback expects x [B, L, D] and g_out [B, P, L, D].")
+        bsz, nbasis = g_out.shape[:2]
+        rep = x.detach().repeat_interleave(nbasis, dim=0).requires_grad_(True)
+        with torch.enable_grad():
+            y = module(rep)
+        (g,) = torch.autograd.grad(y, rep, g_out.to(device=y.device, dtype=y.dtype).reshape_as(y))
+        return g.reshape(bsz, nbasis, *x.shape[1:]).to(device=g_out.device, dtype=g_out.dtype)
+
     def input_pullback_matrix(self, first=None, output_cotangent_basis: Optional[torch.Tensor] = None,
                               g_residual_out: Optional[torch.Tensor] = None, *, cache=None, g_hidden_out=None, hidden_states=None):
         """Two call forms.

@@ -70,6 +70,17 @@ class CausalSelfAttention(nn.Module):
             return x
         return x.repeat_interleave(self.n_heads // self.n_kv_heads, dim=1)
 
+    _expand_kv = expand_kv  # the reference's name (backbones/transformer/attention.py:61-65)
+
+    def _can_use_flash_attn(self, x: torch.Tensor) -> bool:
+        """Whether ``forward`` may take a fused attention kernel for this input (16-bit CUDA tensors with ``use_flash_attn``)."""
+        return bool(self.use_flash_attn and x.is_cuda and x.dtype in (torch.float16, torch.bfloat16))
+
+    def _flash_attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+        """Causal attention of [B, H, T, Dh] tensors (kv heads already expanded) -> [B, T, H, Dh], the layout the reference's
+        method of this name returns (attention.py:78-85)."""
+        return F.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=True, scale=self.scale).transpose(1, 2)
+
     def causal_conv(self, qkv: torch.Tensor) -> torch.Tensor:
         seqlen = qkv.shape[1]
         return self.conv1d(qkv.transpose(1, 2))[..., :seqlen].transpose(1, 2).contiguous()

@@ -61,6 +61,8 @@ class TransformerBlock(nn.Module):
             stream = stream.to(torch.float32)
         return normed, stream
 
+    _prenorm = add_norm  # the reference's name for the same step (backbones/transformer/block.py:66-76)
+
     def forward(self, hidden_states: torch.Tensor, residual: torch.Tensor | None = None):
         hidden_states, residual = self.add_norm(hidden_states, residual, self.norm)
         hidden_states = self.attn(hidden_states)

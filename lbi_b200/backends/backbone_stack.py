@@ -30,6 +30,12 @@ class BackboneStackRegionBackend(nn.Module):
         self.backbone = backbone
         self._structured = None
 
+    def _region_range(self, region_index: int) -> tuple[int, int]:
+        try:
+            return self.region_ranges[region_index]
+        except IndexError as exc:
+            raise IndexError(f"region_index {region_index} out of range for {len(self.region_ranges)} regions") from exc
+
     @property
     def structured(self):
         """Closed-form lowering of the stack (forward with caches, basis pullback, parameter VJP without autograd); built
@@ -45,7 +51,7 @@ class BackboneStackRegionBackend(nn.Module):
         return self.backbone.blocks
 
     def forward_region(self, *, region_input: torch.Tensor, region_index: int):
-        start, end = self.region_ranges[region_index]
+        start, end = self._region_range(region_index)
         out = self.backbone.forward_range(region_input, start, end)
         return out, RegionForwardCache(region_index=region_index, layer_range=(start, end), region_input=region_input,
                                        autocast=current_autocast(region_input.device))

@@ -150,13 +150,19 @@ class TransformerRegionBackend(nn.Module):
         return self.backbone.blocks
 
     def forward_region(self, *, region_input: torch.Tensor, region_index: int):
-        start, end = self.region_ranges[region_index]
+        start, end = self._region_range(region_index)
         cache = RegionForwardCache(region_index=region_index, layer_range=(start, end), region_input=region_input,
                                    autocast=current_autocast(region_input.device))
         if torch.is_grad_enabled():
             return self.backbone.forward_range(region_input, start, end), cache
         out, cache.structured = self.structured.forward(region_input, (start, end))
         return out, cache
+
+    def _region_range(self, region_index: int) -> tuple[int, int]:
+        try:
+            return self.region_ranges[region_index]
+        except IndexError as exc:
+            raise IndexError(f"region_index {region_index} out of range for {len(self.region_ranges)} regions") from exc
 
     @staticmethod
     def _attention_with_cache(attn: nn.Module, normed: torch.Tensor, norm_input: torch.Tensor):
@@ -186,22 +192,34 @@ class TransformerRegionBackend(nn.Module):
         return out, TransformerMLPCache(norm_input=norm_input, norm_output=normed, fc1_output=fc1, up=up, gate=gate,
                                         activation=act, down_input=down_in, down_output=out)
 
+    # the three steps under the reference's method names and argument lists (backends/transformer.py:118-200)
+    def _attention_forward_with_cache(self, attn: nn.Module, norm_output: torch.Tensor):
+        return self._attention_with_cache(attn, norm_output, norm_output)
+
+    def _mlp_forward_with_cache(self, mlp: nn.Module, norm_output: torch.Tensor):
+        return self._mlp_with_cache(mlp, norm_output, norm_output)
+
+    def _block_forward_with_cache(self, *, block: nn.Module, hidden_states: torch.Tensor, residual: torch.Tensor | None):
+        """-> (mlp branch output, residual stream, attention cache, mlp cache) of one block."""
+        stream1 = hidden_states if residual is None else hidden_states + residual
+        normed1, residual = block.add_norm(hidden_states, residual, block.norm)
+        attn_out, attn_cache = self._attention_with_cache(block.attn, normed1, stream1)
+        stream2 = attn_out + residual
+        normed2, residual = block.add_norm(attn_out, residual, block.norm2)
+        out, mlp_cache = self._mlp_with_cache(block.mlp, normed2, stream2)
+        return out, residual, attn_cache, mlp_cache
+
     def forward_region_with_layer_caches(self, *, region_input: torch.Tensor,
                                          region_index: int) -> tuple[torch.Tensor, TransformerRegionCache]:
         """The region through the module code, every intermediate kept under the reference's names
         (backends/transformer.py:201-237).  Not on the engine's path: one region of activations is held several times over."""
-        start, end = self.region_ranges[region_index]
+        start, end = self._region_range(region_index)
         hidden, residual = region_input, None
         layers: list[TransformerLayerCache] = []
         for idx in range(start, end):
-            block = self.backbone.blocks[idx]
             hidden_in, residual_in = hidden, residual
-            stream1 = hidden if residual is None else hidden + residual
-            normed1, residual = block.add_norm(hidden, residual, block.norm)
-            attn_out, attn_cache = self._attention_with_cache(block.attn, normed1, stream1)
-            stream2 = attn_out + residual
-            normed2, residual = block.add_norm(attn_out, residual, block.norm2)
-            hidden, mlp_cache = self._mlp_with_cache(block.mlp, normed2, stream2)
+            hidden, residual, attn_cache, mlp_cache = self._block_forward_with_cache(block=self.backbone.blocks[idx],
+                                                                                    hidden_states=hidden, residual=residual)
             layers.append(TransformerLayerCache(layer_index=idx, hidden_input=hidden_in, residual_input=residual_in,
                                                 attention=attn_cache, mlp=mlp_cache, hidden_output=hidden,
                                                 residual_output=residual))

@@ -143,6 +143,12 @@ class TorchAutogradLocalVJPProvider:
         self._ensure_names(model)
         self.shared_grads(model=model, loss=loss, grad_map=grad_map)
 
+    def _param_name_map(self, model) -> dict[int, str]:
+        return parameter_name_map(model)
+
+    def _store_grads(self, *, model, grad_map, params, grads) -> None:
+        store_named_grads(grad_map, self._param_name_map(model), params, grads)
+
     def _ensure_names(self, model) -> None:
         if not self._names:
             self._names = parameter_name_map(model)

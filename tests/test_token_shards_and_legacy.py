@@ -277,6 +277,36 @@ def test_reference_names_import_from_the_same_modules():
     assert via_reference_scan is ScanADEngine and (DENSE_REGIME, LBI_REGIME, ALL_REGIME) == ("dense", "lbi", "all")
 
 
+def test_private_step_names_that_subclasses_of_the_reference_override():
+    from lbi_b200.backbones import BackboneSpec, build_backbone_stack
+    from lbi_b200.backends import BackboneStackRegionBackend, TransformerRegionBackend
+
+    torch.manual_seed(0)
+    spec = BackboneSpec(name="transformer", dim=16, layers=2, n_heads=4, n_kv_heads=2, d_conv=0)
+    backend = TransformerRegionBackend(backbone_spec=spec, region_ranges=[(0, 1), (1, 2)])
+    block = backend.backbone.blocks[0]
+    x = torch.randn(2, 8, 16)
+    normed, stream = block._prenorm(x, None, block.norm)
+    assert torch.equal(normed, block.add_norm(x, None, block.norm)[0]) and torch.equal(stream, x)
+    q, k, v = block.attn.split_heads(block.attn.in_proj(normed))
+    assert block.attn._expand_kv(k).shape == q.shape and not block.attn._can_use_flash_attn(normed)
+    heads = block.attn._flash_attention(q, block.attn._expand_kv(k), block.attn._expand_kv(v))
+    assert heads.shape == (2, 8, 4, 4)
+    out, residual, attn_cache, mlp_cache = backend._block_forward_with_cache(block=block, hidden_states=x, residual=None)
+    want_out, want_res = block(x)
+    assert torch.allclose(out, want_out, atol=1e-6) and torch.equal(residual, want_res)
+    assert torch.equal(attn_cache.norm_input, x) and torch.allclose(mlp_cache.down_output, want_out, atol=1e-6)
+    a_out, a_cache = backend._attention_forward_with_cache(block.attn, normed)
+    assert torch.allclose(a_out, block.attn(normed), atol=1e-6) and a_cache.norm_output is normed
+    m_out, _ = backend._mlp_forward_with_cache(block.mlp, normed)
+    assert torch.allclose(m_out, block.mlp(normed), atol=1e-6)
+    assert backend._region_range(1) == (1, 2)
+    stack = BackboneStackRegionBackend(backbone=build_backbone_stack(spec), region_ranges=[(0, 2)])
+    for b in (backend, stack):
+        with pytest.raises(IndexError):
+            b._region_range(5)
+
+
 def test_transformer_layer_caches_and_jacobian_function_forms():
     from lbi_b200.backends.transformer import TransformerRegionBackend
     from lbi_b200.backward.pullbacks import (materialize_interface_state_jacobian_t_graph,
