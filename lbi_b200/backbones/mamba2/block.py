@@ -48,3 +48,12 @@ class Mamba2Block(nn.Module):
         residual = hidden_states if residual is None else hidden_states + residual
         hidden_states = self.mixer(self.norm(residual.to(dtype=self.norm.weight.dtype)), seq_idx=seq_idx)
         return hidden_states, residual
+
+    def allocate_decode_state(self, batch_size: int, max_len: int, device=None, dtype=None):
+        return self.mixer.allocate_inference_cache(batch_size, max_len, device=device, dtype=dtype)
+
+    @torch.no_grad()
+    def decode_step(self, hidden_states: torch.Tensor, residual: Optional[torch.Tensor], state):
+        """One token: (branch [B, D], stream [B, D] or None) -> (branch, stream), the same contract as ``forward``."""
+        residual = hidden_states if residual is None else hidden_states + residual
+        return self.mixer.step(self.norm(residual.to(dtype=self.norm.weight.dtype)), *state), residual

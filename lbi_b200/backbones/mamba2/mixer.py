@@ -122,3 +122,42 @@ class Mamba2Simple(nn.Module):
             y = ssd_chunk_scan(x4, dt, A, B4, C4, chunk_size=self.chunk_size, D=self.D, initial_state=init)
         y = self.norm(y.reshape(bsz, seqlen, self.d_inner), z)
         return self.out_proj(y.to(self.out_proj.weight.dtype))
+
+    # ------------------------------------------------------------------ token-by-token decoding
+    def allocate_inference_cache(self, batch_size: int, max_seqlen=None, device=None, dtype=None, **_unused):
+        """(conv_state [B, conv_dim, d_conv - 1], ssm_state [B, H, P, N] fp32): the last pre-convolution rows and the scan state,
+        which starts from the learnable initial state when the mixer has one."""
+        device = self.in_proj.weight.device if device is None else device
+        dtype = self.in_proj.weight.dtype if dtype is None else dtype
+        conv_dim = self.d_inner + 2 * self.ngroups * self.d_state
+        conv_state = torch.zeros(batch_size, conv_dim, self.d_conv - 1, device=device, dtype=dtype)
+        ssm_state = torch.zeros(batch_size, self.nheads, self.headdim, self.d_state, device=device, dtype=torch.float32)
+        if self.learnable_init_states:
+            ssm_state += self.init_states.detach().float().unsqueeze(0)
+        return conv_state, ssm_state
+
+    @torch.no_grad()
+    def step(self, u: torch.Tensor, conv_state: torch.Tensor, ssm_state: torch.Tensor) -> torch.Tensor:
+        """One token u [B, D] -> [B, D]; both state tensors are updated in place.  Token-by-token evaluation from a fresh cache
+        reproduces ``forward``."""
+        bsz = u.shape[0]
+        gn = self.ngroups * self.d_state
+        z, xBC, dt = torch.split(self.in_proj(u), [self.d_inner, self.d_inner + 2 * gn, self.nheads], dim=-1)
+        window = torch.cat([conv_state, xBC.unsqueeze(-1).to(conv_state.dtype)], dim=-1)  # oldest ... newest
+        conv_state.copy_(window[..., 1:])
+        xBC = (window * self.conv1d.weight[:, 0].to(window.dtype)).sum(dim=-1)
+        if self.conv1d.bias is not None:
+            xBC = xBC + self.conv1d.bias
+        x, B, C = torch.split(F.silu(xBC), [self.d_inner, gn, gn], dim=-1)
+        dt = F.softplus(dt.float() + self.dt_bias.float())
+        if self.dt_limit != (0.0, float("inf")):
+            dt = dt.clamp(self.dt_limit[0], self.dt_limit[1])
+        rep = self.nheads // self.ngroups
+        xh = x.float().reshape(bsz, self.nheads, self.headdim)
+        Bh = B.float().reshape(bsz, self.ngroups, self.d_state).repeat_interleave(rep, dim=1)
+        Ch = C.float().reshape(bsz, self.ngroups, self.d_state).repeat_interleave(rep, dim=1)
+        decay = torch.exp(dt * (-torch.exp(self.A_log.float())))
+        ssm_state.copy_(ssm_state * decay[..., None, None] + (dt[..., None] * xh)[..., None] * Bh[:, :, None, :])
+        y = torch.einsum("bhpn,bhn->bhp", ssm_state, Ch) + self.D.float()[None, :, None] * xh
+        y = self.norm(y.reshape(bsz, self.d_inner).to(x.dtype), z)
+        return self.out_proj(y.to(self.out_proj.weight.dtype))

@@ -121,3 +121,12 @@ class Mamba3Block(nn.Module):
             out = branch + stream
         (g,) = torch.autograd.grad(out, rep, output_cotangent_basis.reshape(bsz * nbasis, *hidden_states.shape[1:]).to(out.dtype))
         return g.reshape(bsz, nbasis, *hidden_states.shape[1:])
+
+    def allocate_decode_state(self, batch_size: int, max_len: int, device=None, dtype=None):
+        return self.mixer.allocate_inference_cache(batch_size, max_len, device=device, dtype=dtype)
+
+    @torch.no_grad()
+    def decode_step(self, hidden_states: torch.Tensor, residual: Optional[torch.Tensor], state):
+        """One token: (branch [B, D], stream [B, D] or None) -> (branch, stream), the same contract as ``forward``."""
+        residual = hidden_states if residual is None else hidden_states + residual
+        return self.mixer.step(self.norm(residual.to(dtype=self.norm.weight.dtype)), *state), residual

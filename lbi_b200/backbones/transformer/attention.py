@@ -97,3 +97,37 @@ class CausalSelfAttention(nn.Module):
         out = F.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=True, scale=self.scale)
         out = out.transpose(1, 2).contiguous().view(bsz, seqlen, self.out_dim)
         return self.out_proj(out)
+
+    # ------------------------------------------------------------------ token-by-token decoding
+    def allocate_decode_state(self, batch_size: int, max_len: int, device=None, dtype=None) -> dict:
+        """Key / value cache for ``max_len`` positions, the last ``d_conv - 1`` pre-convolution qkv rows, the position counter."""
+        device = self.in_proj.weight.device if device is None else device
+        dtype = self.in_proj.weight.dtype if dtype is None else dtype
+        state = {"k": torch.zeros(batch_size, self.n_kv_heads, max_len, self.head_dim, device=device, dtype=dtype),
+                 "v": torch.zeros(batch_size, self.n_kv_heads, max_len, self.head_dim, device=device, dtype=dtype), "pos": 0}
+        if self.d_conv > 0:
+            state["conv"] = torch.zeros(batch_size, self.qkv_dim, self.d_conv - 1, device=device, dtype=dtype)
+        return state
+
+    @torch.no_grad()
+    def step(self, x: torch.Tensor, state: dict) -> torch.Tensor:
+        """One token x [B, D] at position ``state['pos']`` -> [B, D]; equals row ``pos`` of ``forward`` on the whole sequence."""
+        bsz, pos = x.shape[0], int(state["pos"])
+        if pos >= state["k"].shape[2]:
+            raise ValueError("the key / value cache is full")
+        qkv = self.in_proj(x)
+        if self.d_conv > 0:
+            window = torch.cat([state["conv"], qkv.unsqueeze(-1).to(state["conv"].dtype)], dim=-1)  # oldest ... newest
+            state["conv"].copy_(window[..., 1:])
+            qkv = (window * self.conv1d.weight[:, 0].to(window.dtype)).sum(dim=-1)
+            if self.conv1d.bias is not None:
+                qkv = qkv + self.conv1d.bias
+        q, k, v = self.split_heads(qkv.unsqueeze(1))
+        q = apply_rope(q, base=self.rope_base, interleaved=self.rope_interleaved, offset=pos)
+        k = apply_rope(k, base=self.rope_base, interleaved=self.rope_interleaved, offset=pos)
+        state["k"][:, :, pos] = k[:, :, 0].to(state["k"].dtype)
+        state["v"][:, :, pos] = v[:, :, 0].to(state["v"].dtype)
+        state["pos"] = pos + 1
+        keys, values = self.expand_kv(state["k"][:, :, : pos + 1]), self.expand_kv(state["v"][:, :, : pos + 1])
+        out = F.scaled_dot_product_attention(q, keys.to(q.dtype), values.to(q.dtype), dropout_p=0.0, is_causal=False, scale=self.scale)
+        return self.out_proj(out.transpose(1, 2).reshape(bsz, self.out_dim))

@@ -69,3 +69,14 @@ class TransformerBlock(nn.Module):
         hidden_states, residual = self.add_norm(hidden_states, residual, self.norm2)
         hidden_states = self.mlp(hidden_states)
         return hidden_states, residual
+
+    def allocate_decode_state(self, batch_size: int, max_len: int, device=None, dtype=None) -> dict:
+        return self.attn.allocate_decode_state(batch_size, max_len, device=device, dtype=dtype)
+
+    @torch.no_grad()
+    def decode_step(self, hidden_states: torch.Tensor, residual: torch.Tensor | None, state: dict):
+        """One token: (branch [B, D], stream [B, D] or None) -> (branch, stream), the same contract as ``forward``."""
+        normed, residual = self.add_norm(hidden_states, residual, self.norm)
+        branch = self.attn.step(normed, state)
+        normed, residual = self.add_norm(branch, residual, self.norm2)
+        return self.mlp(normed), residual

@@ -23,20 +23,24 @@ def rope_tables(seq_len: int, head_dim: int, base: float, device: torch.device, 
     inv_freq = float(base) ** (-2.0 * torch.arange(half, device=device, dtype=torch.float32) / float(head_dim))
     freqs = torch.outer(pos, inv_freq)
     tables = (freqs.cos().contiguous(), freqs.sin().contiguous())
+    if offset != 0:  # single positions of a decode loop: cheap to rebuild, not worth a cache entry each
+        return tables
     if len(_TABLE_CACHE) > 64:
         _TABLE_CACHE.clear()
     _TABLE_CACHE[key] = tables
     return tables
 
 
-def apply_rope(x: torch.Tensor, base: float = 10000.0, interleaved: bool = False, inverse: bool = False) -> torch.Tensor:
-    """Rotate ``x`` of shape [B, H, L, D]; ``inverse=True`` applies the transpose rotation (its VJP)."""
+def apply_rope(x: torch.Tensor, base: float = 10000.0, interleaved: bool = False, inverse: bool = False,
+               offset: int = 0) -> torch.Tensor:
+    """Rotate ``x`` of shape [B, H, L, D]; ``inverse=True`` applies the transpose rotation (its VJP); ``offset`` is the position
+    of the first of the L tokens (token-by-token decoding)."""
     if x.dim() != 4:
         raise ValueError("RoPE expects x shaped [B, H, L, D].")
     head_dim = x.shape[-1]
     if head_dim % 2 != 0:
         raise ValueError("RoPE requires an even head dimension.")
-    cos, sin = rope_tables(x.shape[-2], head_dim, base, x.device)
+    cos, sin = rope_tables(x.shape[-2], head_dim, base, x.device, offset)
     if inverse:
         sin = -sin
     xf = x.float()

@@ -1,0 +1,104 @@
+"""Decoding (CPU): token-by-token evaluation equals the training forward for every block type and for sequence-axis LBI models,
+in both the recompute and the cached mode; generation is consistent with the full forward."""
+import pytest
+import torch
+
+from lbi_b200.backbones import BackboneSpec, build_backbone_stack
+from lbi_b200.inference import IncrementalLBIDecoder, generate
+from lbi_b200.interfaces import VectorMLPInterface
+from lbi_b200.models import DenseLanguageModel, LBILanguageModel
+
+STACKS = [
+    ("transformer", dict(n_heads=4, n_kv_heads=2, d_conv=4)),
+    ("transformer", dict(n_heads=4, n_kv_heads=4, d_conv=0, rope_interleaved=True)),
+    ("mamba2", dict(d_state=16, headdim=16, chunk_size=8, d_conv=4)),
+    ("mamba3", dict(d_state=16, headdim=16, chunk_size=8)),
+    ("hybrid", dict(d_state=16, headdim=16, chunk_size=8, d_conv=4, n_heads=4, layer_types=("mamba3", "transformer", "mamba2"))),
+]
+
+
+@pytest.mark.parametrize("name,extra", STACKS)
+def test_block_decode_steps_reproduce_the_stack(name, extra):
+    torch.manual_seed(0)
+    layers = len(extra.get("layer_types", (0, 0)))
+    stack = build_backbone_stack(BackboneSpec(name=name, dim=32, layers=layers, **extra)).eval()
+    x = torch.randn(2, 13, 32)
+    with torch.no_grad():
+        want = stack.forward_range(x, 0, layers)
+    states = [block.allocate_decode_state(2, 13) for block in stack.blocks]
+    rows = []
+    for t in range(13):
+        branch, stream = x[:, t], None
+        for block, state in zip(stack.blocks, states):
+            branch, stream = block.decode_step(branch, stream, state)
+        rows.append(branch + stream)
+    assert torch.allclose(torch.stack(rows, dim=1), want, atol=5e-6, rtol=1e-5)
+
+
+def test_attention_cache_refuses_to_overflow():
+    torch.manual_seed(1)
+    stack = build_backbone_stack(BackboneSpec(name="transformer", dim=32, layers=1, n_heads=4, d_conv=0)).eval()
+    block = stack.blocks[0]
+    state = block.allocate_decode_state(1, 2)
+    for _ in range(2):
+        block.decode_step(torch.randn(1, 32), None, state)
+    with pytest.raises(ValueError):
+        block.decode_step(torch.randn(1, 32), None, state)
+
+
+def _lbi(name, extra, regions=4, layers=2):
+    torch.manual_seed(0)
+    spec = BackboneSpec(name=name, dim=32, layers=len(extra.get("layer_types", (0,) * layers)), **extra)
+    iface = VectorMLPInterface(feature_dim=32, num_regions=regions, interface_width=8, interface_map_hidden_dim=16)
+    return LBILanguageModel(vocab_size=50, layers_per_region=1, backbone_spec=spec, interface=iface, region_axis="sequence",
+                            num_sequence_regions=regions, tie_embeddings=True).eval()
+
+
+@pytest.mark.parametrize("name,extra", [STACKS[0], STACKS[2], STACKS[3], STACKS[4]])
+@pytest.mark.parametrize("use_cache", [True, False])
+def test_incremental_decoder_matches_the_training_forward(name, extra, use_cache):
+    model = _lbi(name, extra)
+    ids = torch.randint(0, 50, (2, 22))
+    with torch.no_grad():
+        want, _ = model.forward_with_cache(ids)
+    decoder = IncrementalLBIDecoder(model, 22, use_cache=use_cache)
+    got = torch.cat([decoder.append(ids[:, :5]), decoder.append(ids[:, 5:13]), decoder.append(ids[:, 13:])], dim=1)
+    assert decoder.position == 22 and decoder.region == 4 and decoder.use_cache is use_cache
+    assert torch.allclose(got, want, atol=5e-6, rtol=1e-5)
+    with pytest.raises(ValueError):
+        decoder.append(ids[:, :1])
+
+
+def test_generation_is_consistent_with_the_full_forward_and_between_modes():
+    model = _lbi(*STACKS[0])
+    prompt = torch.randint(0, 50, (2, 7))
+    cached = generate(model, prompt, 15, use_cache=True)
+    assert cached.shape == (2, 22) and torch.equal(cached[:, :7], prompt)
+    assert torch.equal(cached, generate(model, prompt, 15, use_cache=False))
+    with torch.no_grad():
+        logits, _ = model.forward_with_cache(cached)
+    assert torch.equal(logits[:, 6:-1].argmax(dim=-1), cached[:, 7:])  # every generated token is the arg-max of the full forward
+    # the cut of a longer training length: still self-consistent when the rest is filled in later
+    longer = generate(model, prompt, 5, total_len=32)
+    assert longer.shape == (2, 12)
+    sampled = generate(model, prompt, 6, temperature=0.8, top_k=5, generator=torch.Generator().manual_seed(3))
+    again = generate(model, prompt, 6, temperature=0.8, top_k=5, generator=torch.Generator().manual_seed(3))
+    assert torch.equal(sampled, again) and model.training is False
+    with pytest.raises(ValueError):
+        generate(model, prompt, 30, total_len=16)
+
+
+def test_generation_of_dense_and_depth_axis_models_by_recomputation():
+    torch.manual_seed(0)
+    spec = BackboneSpec(name="transformer", dim=32, layers=2, n_heads=4, d_conv=0)
+    dense = DenseLanguageModel(vocab_size=50, backbone_spec=spec, tie_embeddings=True).train()
+    prompt = torch.randint(0, 50, (1, 5))
+    out = generate(dense, prompt, 4)
+    assert out.shape == (1, 9) and dense.training is True  # the mode is put back
+    with torch.no_grad():
+        assert torch.equal(dense.eval()(out)[:, 4:-1].argmax(dim=-1), out[:, 5:])
+    iface = VectorMLPInterface(feature_dim=32, num_regions=2, interface_width=8, interface_map_hidden_dim=16)
+    depth = LBILanguageModel(vocab_size=50, layers_per_region=1, backbone_spec=spec, interface=iface, tie_embeddings=True)
+    assert generate(depth, prompt, 3).shape == (1, 8)
+    with pytest.raises(ValueError):
+        IncrementalLBIDecoder(depth, 8)
