@@ -95,8 +95,19 @@ class IncrementalLBIDecoder:
         if self.position + tokens.shape[1] > self.total_len:
             raise ValueError(f"the decoder was laid out for {self.total_len} tokens")
         out = []
-        for t in range(tokens.shape[1]):
+        t = 0
+        while t < tokens.shape[1]:
+            start_tok, end_tok = self.spans[self.region]
+            span = end_tok - start_tok
+            if self.position == start_tok and tokens.shape[1] - t >= span:
+                # a whole span at once (prompt processing): one pass as in training, then only the state is kept
+                features = self._region_features(tokens[:, t : t + span])
+                out.append(self.model.readout(features, canvas=self.model.canvas))
+                self.state = self.model.interface.update(self.state, features, self.region).state
+                self.position, self.region, t = end_tok, self.region + 1, t + span
+                continue
             tok = tokens[:, t : t + 1]
+            t += 1
             if self.use_cache:
                 last = self._cached_token_features(tok).unsqueeze(1)
             else:
@@ -105,7 +116,6 @@ class IncrementalLBIDecoder:
                 last = features[:, -1:]
             out.append(self.model.readout(last, canvas=self.model.canvas))
             self.position += 1
-            start_tok, end_tok = self.spans[self.region]
             if self.position == end_tok:  # span complete: take the state update, forget the span
                 if self.use_cache:
                     pooled = (self._feature_sum / float(end_tok - start_tok)).to(last.dtype)

@@ -67,6 +67,11 @@ def test_incremental_decoder_matches_the_training_forward(name, extra, use_cache
     assert torch.allclose(got, want, atol=5e-6, rtol=1e-5)
     with pytest.raises(ValueError):
         decoder.append(ids[:, :1])
+    # a prompt that covers whole spans goes through them in one pass each (spans of 22 tokens in 4 regions: 6, 6, 5, 5)
+    whole = IncrementalLBIDecoder(model, 22, use_cache=use_cache)
+    first = whole.append(ids[:, :14])
+    assert whole.region == 2 and whole.position == 14 and (whole._block_states is not None or not use_cache)
+    assert torch.allclose(torch.cat([first, whole.append(ids[:, 14:])], dim=1), want, atol=5e-6, rtol=1e-5)
 
 
 def test_generation_is_consistent_with_the_full_forward_and_between_modes():
