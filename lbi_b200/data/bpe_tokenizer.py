@@ -173,6 +173,9 @@ class SentencePieceBPETokenizer:
     def encode_bytes(self, raw: bytes) -> list[int]:
         return list(self.processor.encode(raw.decode("utf-8", errors="replace"), out_type=int))
 
+    def decode(self, ids) -> bytes:
+        return self.processor.decode([int(i) for i in ids]).encode("utf-8")
+
 
 class HFAutoTextTokenizer:
     def __init__(self, model_path: str | Path) -> None:
@@ -187,6 +190,9 @@ class HFAutoTextTokenizer:
 
     def encode_bytes(self, raw: bytes) -> list[int]:
         return list(self.tokenizer.encode(raw.decode("utf-8", errors="replace"), add_special_tokens=False))
+
+    def decode(self, ids) -> bytes:
+        return self.tokenizer.decode([int(i) for i in ids], skip_special_tokens=True).encode("utf-8")
 
 
 def train_sentencepiece_bpe_tokenizer(train_path, *, model_prefix, vocab_size: int, train_bytes: int) -> SentencePieceBPETokenizer:

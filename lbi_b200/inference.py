@@ -163,4 +163,88 @@ def generate(model: Any, input_ids: torch.Tensor, max_new_tokens: int, *, total_
         model.train(was_training)
 
 
-__all__ = ["IncrementalLBIDecoder", "generate"]
+def load_run(run_dir, *, checkpoint: str = "latest", device: str = "auto"):
+    """(model in eval mode, config) of a trained run directory (``<output>/<run name>/<dense|lbi>``)."""
+    from dataclasses import replace
+    from pathlib import Path
+
+    from .scripts.evaluate_paper_checkpoints import load_run_config
+    from .train.checkpointing import checkpoint_path_from_summary, load_checkpoint, load_model_state
+    from .train.config import normalize_model_variant
+    from .train.model_builders import build_model_for_regime
+    from .train.runners import _resolve_device
+
+    run_dir = Path(run_dir)
+    cfg = load_run_config(run_dir, eval_batches=1, batch_size=None, seq_len=None, device=device)
+    dev = _resolve_device(cfg)
+    path = checkpoint_path_from_summary(run_dir / "summary.json", preference=checkpoint)
+    if path is None or not Path(path).exists():
+        raise FileNotFoundError(f"no {checkpoint} checkpoint recorded for {run_dir}")
+    payload = load_checkpoint(Path(path), device=dev)
+    variant = normalize_model_variant(cfg.regime if cfg.regime not in ("", "all") else run_dir.name)
+    model = build_model_for_regime(replace(cfg, variants=variant, regime=variant), checkpoint=payload).to(dev)
+    load_model_state(model, payload["model_state_dict"])
+    return model.eval(), cfg
+
+
+def load_run_tokenizer(cfg):
+    """The text tokenizer a run was trained with, or None for the synthetic and byte-level data modes."""
+    if cfg.data_mode not in ("text_bpe", "text_bpe_sharded"):
+        return None
+    from .data.bpe_tokenizer import load_text_tokenizer
+    from .train import data as glue
+
+    train_path = glue._shard_train_path(cfg) if cfg.data_mode == "text_bpe_sharded" else glue.resolve_text_paths(cfg)[0]
+    return load_text_tokenizer(tokenizer_type=cfg.tokenizer_type, tokenizer_path=glue.resolve_tokenizer_path(cfg, train_path=train_path),
+                               train_path=train_path, vocab_size=cfg.vocab_size, train_bytes=cfg.tokenizer_train_bytes)
+
+
+def main(argv: list[str] | None = None) -> dict:
+    """python -m lbi_b200.inference RUN_DIR (--prompt TEXT | --prompt-ids 1,2,3) [--max-new-tokens N] ..."""
+    import argparse
+    import json
+
+    p = argparse.ArgumentParser(description="Continue a prompt with a trained run.")
+    p.add_argument("run_dir", type=str, help="<output dir>/<run name>/<dense|lbi>")
+    p.add_argument("--prompt", type=str, default="", help="text (tokenized with the run's tokenizer; bytes in text_byte mode)")
+    p.add_argument("--prompt-ids", type=str, default="", help="comma-separated token ids instead of text")
+    p.add_argument("--max-new-tokens", type=int, default=32)
+    p.add_argument("--total-len", type=int, default=0, help="sequence length whose region cut is used (default: the run's seq_len)")
+    p.add_argument("--temperature", type=float, default=0.0)
+    p.add_argument("--top-k", type=int, default=0)
+    p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--checkpoint", choices=("best", "latest"), default="latest")
+    p.add_argument("--device", choices=("auto", "cpu", "cuda"), default="auto")
+    ns = p.parse_args(argv)
+    model, cfg = load_run(ns.run_dir, checkpoint=ns.checkpoint, device=ns.device)
+    tokenizer = load_run_tokenizer(cfg)
+    if ns.prompt_ids:
+        ids = [int(x) for x in ns.prompt_ids.split(",") if x.strip()]
+    elif not ns.prompt:
+        p.error("give --prompt or --prompt-ids")
+    elif tokenizer is not None:
+        ids = tokenizer.encode_bytes(ns.prompt.encode("utf-8"))
+    elif cfg.data_mode == "text_byte":
+        ids = list(ns.prompt.encode("utf-8"))
+    else:
+        p.error("a synthetic-data run has no tokenizer: use --prompt-ids")
+    device = next(model.parameters()).device
+    prompt = torch.tensor([ids], dtype=torch.long, device=device)
+    total = ns.total_len or max(int(cfg.seq_len), prompt.shape[1] + ns.max_new_tokens)
+    gen = torch.Generator(device=device).manual_seed(ns.seed) if ns.temperature > 0 else None
+    out = generate(model, prompt, ns.max_new_tokens, total_len=total, temperature=ns.temperature, top_k=ns.top_k or None, generator=gen)
+    new_ids = out[0, prompt.shape[1]:].tolist()
+    result = {"prompt_ids": ids, "new_ids": new_ids}
+    if tokenizer is not None and hasattr(tokenizer, "decode"):
+        result["text"] = tokenizer.decode(new_ids).decode("utf-8", errors="replace")
+    elif cfg.data_mode == "text_byte":
+        result["text"] = bytes(i % 256 for i in new_ids).decode("utf-8", errors="replace")
+    print(json.dumps(result))
+    return result
+
+
+__all__ = ["IncrementalLBIDecoder", "generate", "load_run", "load_run_tokenizer", "main"]
+
+
+if __name__ == "__main__":
+    main()

@@ -107,3 +107,32 @@ def test_generation_of_dense_and_depth_axis_models_by_recomputation():
     assert generate(depth, prompt, 3).shape == (1, 8)
     with pytest.raises(ValueError):
         IncrementalLBIDecoder(depth, 8)
+
+
+def test_generation_command_on_trained_runs(tmp_path):
+    from lbi_b200 import inference
+    from lbi_b200.train.config import LBITrainingConfig
+    from lbi_b200.train.lbi import run_lbi_experiment
+
+    base = dict(variants="lbi", backbone="transformer", device="cpu", dtype="float32", output_dir=str(tmp_path), seq_len=16,
+                batch_size=2, steps=2, eval_every=2, eval_batches=1, log_every=1, save_every=2, layers=2, dim=16, n_heads=2, d_conv=0,
+                region_axis="sequence", sequence_regions=4, message_dim=4, message_hidden_dim=8)
+    run_lbi_experiment(LBITrainingConfig(run_name="syn", task="copy", vocab_size=32, train_sequences=16, val_sequences=4, **base))
+    out = inference.main([str(tmp_path / "syn" / "lbi"), "--prompt-ids", "1,2,3", "--max-new-tokens", "5", "--device", "cpu"])
+    assert out["prompt_ids"] == [1, 2, 3] and len(out["new_ids"]) == 5 and all(0 <= i < 32 for i in out["new_ids"])
+    with pytest.raises(SystemExit):
+        inference.main([str(tmp_path / "syn" / "lbi"), "--prompt", "text needs a tokenizer", "--device", "cpu"])
+
+    text = tmp_path / "corpus.txt"
+    text.write_bytes(b"the quick brown fox jumps over the lazy dog. " * 100)
+    run_lbi_experiment(LBITrainingConfig(run_name="bytes", data_mode="text_byte", vocab_size=256, train_text_path=str(text), **base))
+    out = inference.main([str(tmp_path / "bytes" / "lbi"), "--prompt", "the quick", "--max-new-tokens", "4", "--temperature", "0.7",
+                          "--top-k", "8", "--seed", "1", "--device", "cpu"])
+    assert out["prompt_ids"] == list(b"the quick") and len(out["new_ids"]) == 4 and isinstance(out["text"], str)
+
+    pytest.importorskip("sentencepiece")
+    tok = tmp_path / "tok.model"
+    run_lbi_experiment(LBITrainingConfig(run_name="bpe", data_mode="text_bpe", train_text_path=str(text), tokenizer_path=str(tok),
+                                         vocab_size=300, tokenizer_train_bytes=4096, train_tokenizer=True, **base))
+    out = inference.main([str(tmp_path / "bpe" / "lbi"), "--prompt", "the lazy", "--max-new-tokens", "3", "--device", "cpu"])
+    assert len(out["new_ids"]) == 3 and isinstance(out["text"], str)
