@@ -7,8 +7,9 @@ re-evaluates the current span's prefix through the stack for every new token (co
 sequence) and moves the state forward at span boundaries.  The spans are those of a sequence of ``total_len`` tokens, fixed
 up front, because the cut of the training forward depends on the sequence length.
 
-Depth-axis LBI models and dense models have no such shortcut (the depth-axis initial state pools the whole sequence):
-``generate`` re-runs their forward on the growing sequence.
+Dense models decode with the same per-block caches held for the whole sequence (``IncrementalDenseDecoder``).  Depth-axis LBI
+models have no shortcut (their initial state pools the whole sequence): ``generate`` re-runs their forward on the growing
+sequence.
 """
 from __future__ import annotations
 
@@ -128,14 +129,50 @@ class IncrementalLBIDecoder:
         return torch.cat(out, dim=1)
 
 
+class IncrementalDenseDecoder:
+    """Token-by-token evaluation of a ``DenseLanguageModel`` with per-block decode state for up to ``max_len`` tokens (key / value
+    caches grow with the sequence: there is no interface to bound them); ``append`` returns logits equal to the full forward."""
+
+    def __init__(self, model: Any, max_len: int) -> None:
+        from .backbones.general import ResidualBackboneStack
+
+        blocks = getattr(getattr(model, "backbone", None), "blocks", None)
+        if not isinstance(getattr(model, "backbone", None), ResidualBackboneStack) or not blocks or \
+                not all(hasattr(b, "decode_step") for b in blocks):
+            raise ValueError("cached dense decoding needs a residual stack whose blocks all implement decode_step")
+        self.model, self.max_len, self.position = model, int(max_len), 0
+        self._states: list | None = None
+
+    @torch.no_grad()
+    def append(self, tokens: torch.Tensor) -> torch.Tensor:
+        if tokens.dim() != 2:
+            raise ValueError("tokens must have shape [B, n]")
+        if self.position + tokens.shape[1] > self.max_len:
+            raise ValueError(f"the decoder was laid out for {self.max_len} tokens")
+        model, out = self.model, []
+        for t in range(tokens.shape[1]):
+            canvas = model.canvas(tokens[:, t : t + 1])
+            if self._states is None:
+                self._states = [b.allocate_decode_state(tokens.shape[0], self.max_len, device=canvas.device, dtype=canvas.dtype)
+                                for b in model.backbone.blocks]
+            branch, stream = canvas[:, 0], None
+            for block, state in zip(model.backbone.blocks, self._states):
+                branch, stream = block.decode_step(branch, stream, state)
+            features = branch if stream is None else branch + stream
+            out.append(model.readout(features.unsqueeze(1), canvas=model.canvas))
+            self.position += 1
+        return torch.cat(out, dim=1)
+
+
 @torch.no_grad()
 def generate(model: Any, input_ids: torch.Tensor, max_new_tokens: int, *, total_len: int | None = None, temperature: float = 0.0,
              top_k: int | None = None, generator: torch.Generator | None = None, use_cache: bool | None = None) -> torch.Tensor:
     """Continue ``input_ids`` [B, T0] by ``max_new_tokens`` tokens -> [B, T0 + max_new_tokens].
 
     Sequence-axis LBI models decode incrementally under the region spans of a ``total_len``-token sequence (default: the final
-    length; pass the training sequence length to decode under the cut the model was trained with).  Every other model re-runs
-    its forward on the sequence so far."""
+    length; pass the training sequence length to decode under the cut the model was trained with).  Dense models decode with
+    per-block caches over the whole sequence (``use_cache=False``: by re-running the forward); depth-axis LBI models always
+    re-run their forward on the sequence so far."""
     if input_ids.dim() != 2 or input_ids.shape[1] == 0:
         raise ValueError("input_ids must be a non-empty [B, T] tensor")
     was_training = model.training
@@ -153,6 +190,21 @@ def generate(model: Any, input_ids: torch.Tensor, max_new_tokens: int, *, total_
                 tokens = torch.cat([tokens, nxt], dim=1)
                 if i + 1 < int(max_new_tokens):
                     logits = decoder.append(nxt)[:, -1]
+            return tokens
+        dense = None
+        if use_cache is not False and hasattr(model, "backbone") and hasattr(model, "readout") and not hasattr(model, "interface"):
+            try:
+                dense = IncrementalDenseDecoder(model, final_len)
+            except ValueError:
+                if use_cache:
+                    raise
+        if dense is not None:
+            logits = dense.append(tokens)[:, -1]
+            for i in range(int(max_new_tokens)):
+                nxt = _sample(logits, temperature, top_k, generator).unsqueeze(1)
+                tokens = torch.cat([tokens, nxt], dim=1)
+                if i + 1 < int(max_new_tokens):
+                    logits = dense.append(nxt)[:, -1]
             return tokens
         for _ in range(int(max_new_tokens)):
             out = model(tokens)
@@ -243,7 +295,7 @@ def main(argv: list[str] | None = None) -> dict:
     return result
 
 
-__all__ = ["IncrementalLBIDecoder", "generate", "load_run", "load_run_tokenizer", "main"]
+__all__ = ["IncrementalDenseDecoder", "IncrementalLBIDecoder", "generate", "load_run", "load_run_tokenizer", "main"]
 
 
 if __name__ == "__main__":

@@ -100,6 +100,16 @@ def test_generation_of_dense_and_depth_axis_models_by_recomputation():
     prompt = torch.randint(0, 50, (1, 5))
     out = generate(dense, prompt, 4)
     assert out.shape == (1, 9) and dense.training is True  # the mode is put back
+    assert torch.equal(out, generate(dense, prompt, 4, use_cache=False))
+    from lbi_b200.inference import IncrementalDenseDecoder
+
+    ids = torch.randint(0, 50, (2, 11))
+    decoder = IncrementalDenseDecoder(dense.eval(), 11)
+    with torch.no_grad():
+        assert torch.allclose(torch.cat([decoder.append(ids[:, :4]), decoder.append(ids[:, 4:])], dim=1), dense(ids), atol=5e-6, rtol=1e-5)
+    with pytest.raises(ValueError):
+        decoder.append(ids[:, :1])
+    dense.train()
     with torch.no_grad():
         assert torch.equal(dense.eval()(out)[:, 4:-1].argmax(dim=-1), out[:, 5:])
     iface = VectorMLPInterface(feature_dim=32, num_regions=2, interface_width=8, interface_map_hidden_dim=16)
