@@ -8,7 +8,8 @@ arguments, MODEL_SCALE, TARGET_STEPS, SEQ_LEN, BATCH_SIZE, SEED, MESSAGE_DIM, ME
 LR_MODEL, WARMUP_STEPS, WEIGHT_DECAY, TIE_EMBEDDINGS, TOKENIZER_TYPE / PATH, VOCAB_SIZE, FAMILY_NAME, VARIANT_NAME, RUN_NAME,
 OUTPUT_DIR, CHECKPOINT_ROOT, ...), the learning rate / warm-up / weight decay follow the same scale-and-backbone rules, and runs land
 in ``<OUTPUT_ROOT>/<family>/<run name>/<variant>`` with the same family name, so the evaluation and plotting launchers of either
-code base find them.  Added: BACKWARD_ENGINE (e.g. ``fast``), DATA_MODE, TEXT_CORPUS.
+code base find them.  Added: BACKWARD_ENGINE (e.g. ``fast``), NPROC_PER_NODE (with BACKWARD_ENGINE=fast: one process per GPU
+through ``torch.distributed.run``), MASTER_PORT, DATA_MODE, TEXT_CORPUS.
 """
 from __future__ import annotations
 
@@ -177,8 +178,15 @@ def build_command(kind: str, extra: list[str] | None = None) -> list[str]:
     out_root = _env("OUTPUT_ROOT", "out/region_interface")
     out_dir = _env("OUTPUT_DIR", os.path.join(out_root.rstrip("/"), family))  # runs land in <family>/<run name>/<variant>
 
+    nproc = _env("NPROC_PER_NODE", 1)
+    if nproc > 1 and (kind != "lbi" or _env("BACKWARD_ENGINE", "") != "fast"):
+        raise SystemExit("NPROC_PER_NODE > 1 spreads the regions of an LBI run over GPUs: it needs kind lbi and BACKWARD_ENGINE=fast")
+    launcher = [_env("PYTHON_BIN", sys.executable), "-m"]
+    if nproc > 1:  # one process per GPU on this node; the rendezvous address is numeric on purpose
+        launcher += ["torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+                     "--master-port", str(_env("MASTER_PORT", 29500)), "-m"]
     args = [
-        _env("PYTHON_BIN", sys.executable), "-m", "lbi_b200.train.lbi",
+        *launcher, "lbi_b200.train.lbi",
         "--variants", "dense" if kind == "dense" else "lbi", "--backbone", backbone, "--output-dir", out_dir, "--run-name", run_name,
         "--seed", str(seed), "--data-mode", _env("DATA_MODE", "text_bpe_sharded"), "--text-corpus", _env("TEXT_CORPUS", "fineweb_edu"),
         "--tokenizer-type", tokenizer_type, "--vocab-size", str(vocab), "--seq-len", str(seq_len), "--batch-size", str(batch),

@@ -32,7 +32,7 @@ def family(tmp_path_factory):
 
 _LAUNCH_VARS = ("BACKBONE", "MODEL_SCALE", "MESSAGE_DIM", "TOKENIZER_PATH", "OUTPUT_ROOT", "FAMILY_NAME", "FAMILY_DIR", "TARGET_STEPS",
                 "TIE_EMBEDDINGS", "TOKENIZER_TYPE", "VOCAB_SIZE", "SEQ_LEN", "FAMILY_SEQ_LEN", "LR_MODEL", "WEIGHT_DECAY", "WARMUP_STEPS",
-                "VARIANT_NAME", "RUN_NAME", "OUTPUT_DIR", "SEED", "BACKWARD_ENGINE", "MESSAGE_HIDDEN_DIM")
+                "VARIANT_NAME", "RUN_NAME", "OUTPUT_DIR", "SEED", "BACKWARD_ENGINE", "MESSAGE_HIDDEN_DIM", "NPROC_PER_NODE", "MASTER_PORT")
 
 
 @pytest.fixture
@@ -44,8 +44,9 @@ def launch_env(monkeypatch):
 
 
 def _parse(cmd):
-    assert cmd[1:3] == ["-m", "lbi_b200.train.lbi"]
-    return config_from_args(build_arg_parser().parse_args(cmd[3:]))
+    at = cmd.index("lbi_b200.train.lbi")
+    assert cmd[at - 1] == "-m"
+    return config_from_args(build_arg_parser().parse_args(cmd[at + 1:]))
 
 
 @pytest.mark.parametrize("kind,backbone,dim", [("lbi", "transformer", 64), ("lbi", "hybrid", 32), ("dense", "mamba2", 16),
@@ -103,6 +104,13 @@ def test_launcher_choices_follow_the_tables_of_the_reference_launchers(launch_en
     assert (cfg.layers, cfg.lr_model, cfg.weight_decay, cfg.warmup_steps, cfg.tie_embeddings) == (28, 3e-4, 0.1, 1000, False)
     assert cfg.run_name == "dense_seed7" and cfg.output_dir.endswith("paper_mamba3_28l_768d_llama32k_untied_seq1024_20ksteps")
     assert _parse(paper_presets.build_command("lbi")).backward_engine == "fast"
+    launch_env.setenv("NPROC_PER_NODE", "8")
+    multi = paper_presets.build_command("lbi")
+    assert multi[1:7] == ["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=8", "--master-addr", "127.0.0.1"]
+    assert _parse(multi).backward_engine == "fast"
+    with pytest.raises(SystemExit):
+        paper_presets.build_command("dense")
+    launch_env.delenv("NPROC_PER_NODE")
     for var, bad in (("MODEL_SCALE", "huge"), ("BACKBONE", "rnn"), ("TIE_EMBEDDINGS", "maybe"), ("TARGET_STEPS", "0")):
         launch_env.setenv(var, bad)
         with pytest.raises(SystemExit):
