@@ -9,7 +9,7 @@ LR_MODEL, WARMUP_STEPS, WEIGHT_DECAY, TIE_EMBEDDINGS, TOKENIZER_TYPE / PATH, VOC
 OUTPUT_DIR, CHECKPOINT_ROOT, ...), the learning rate / warm-up / weight decay follow the same scale-and-backbone rules, and runs land
 in ``<OUTPUT_ROOT>/<family>/<run name>/<variant>`` with the same family name, so the evaluation and plotting launchers of either
 code base find them.  Added: BACKWARD_ENGINE (e.g. ``fast``), NPROC_PER_NODE (with BACKWARD_ENGINE=fast: one process per GPU
-through ``torch.distributed.run``), MASTER_PORT, DATA_MODE, TEXT_CORPUS.
+through ``torch.distributed.run``), MASTER_PORT, REGION_AXIS / SEQUENCE_REGIONS, DATA_MODE, TEXT_CORPUS.
 """
 from __future__ import annotations
 
@@ -208,6 +208,9 @@ def build_command(kind: str, extra: list[str] | None = None) -> list[str]:
             "--message-scale-init", str(_env("MESSAGE_SCALE_INIT", 0.5)),
             "--interface-jacobian-mode", mode, "--jacobian-basis-chunk", str(chunk),
         ]
+        axis = _env("REGION_AXIS", "")
+        if axis:  # REGION_AXIS=sequence SEQUENCE_REGIONS=8: cut the tokens instead of the layers (one span per GPU at 8 GPUs)
+            args += ["--region-axis", axis, "--sequence-regions", str(_env("SEQUENCE_REGIONS", 8))]
         engine = _env("BACKWARD_ENGINE", "")
         if engine:  # e.g. BACKWARD_ENGINE=fast for the structured kernels (one process per GPU under torchrun)
             args += ["--backward-engine", engine]

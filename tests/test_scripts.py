@@ -32,7 +32,7 @@ def family(tmp_path_factory):
 
 _LAUNCH_VARS = ("BACKBONE", "MODEL_SCALE", "MESSAGE_DIM", "TOKENIZER_PATH", "OUTPUT_ROOT", "FAMILY_NAME", "FAMILY_DIR", "TARGET_STEPS",
                 "TIE_EMBEDDINGS", "TOKENIZER_TYPE", "VOCAB_SIZE", "SEQ_LEN", "FAMILY_SEQ_LEN", "LR_MODEL", "WEIGHT_DECAY", "WARMUP_STEPS",
-                "VARIANT_NAME", "RUN_NAME", "OUTPUT_DIR", "SEED", "BACKWARD_ENGINE", "MESSAGE_HIDDEN_DIM", "NPROC_PER_NODE", "MASTER_PORT")
+                "VARIANT_NAME", "RUN_NAME", "OUTPUT_DIR", "SEED", "BACKWARD_ENGINE", "MESSAGE_HIDDEN_DIM", "NPROC_PER_NODE", "MASTER_PORT", "REGION_AXIS", "SEQUENCE_REGIONS")
 
 
 @pytest.fixture
@@ -108,6 +108,10 @@ def test_launcher_choices_follow_the_tables_of_the_reference_launchers(launch_en
     multi = paper_presets.build_command("lbi")
     assert multi[1:7] == ["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=8", "--master-addr", "127.0.0.1"]
     assert _parse(multi).backward_engine == "fast"
+    launch_env.setenv("REGION_AXIS", "sequence")
+    cut = _parse(paper_presets.build_command("lbi"))
+    assert (cut.region_axis, cut.sequence_regions) == ("sequence", 8)
+    launch_env.delenv("REGION_AXIS")
     with pytest.raises(SystemExit):
         paper_presets.build_command("dense")
     launch_env.delenv("NPROC_PER_NODE")
