@@ -181,7 +181,9 @@ def generate(model: Any, input_ids: torch.Tensor, max_new_tokens: int, *, total_
         final_len = input_ids.shape[1] + int(max_new_tokens)
         tokens = input_ids
         if getattr(model, "region_axis", None) == "sequence":
-            decoder = IncrementalLBIDecoder(model, final_len if total_len is None else int(total_len), use_cache=use_cache)
+            # a sequence cannot be cut into more spans than it has tokens: short requests use the cut of num_regions tokens
+            layout = max(final_len, int(model.num_regions)) if total_len is None else int(total_len)
+            decoder = IncrementalLBIDecoder(model, layout, use_cache=use_cache)
             if final_len > decoder.total_len:
                 raise ValueError("total_len is shorter than the prompt plus the new tokens")
             logits = decoder.append(tokens)[:, -1]

@@ -91,6 +91,7 @@ def test_generation_is_consistent_with_the_full_forward_and_between_modes():
     assert torch.equal(sampled, again) and model.training is False
     with pytest.raises(ValueError):
         generate(model, prompt, 30, total_len=16)
+    assert generate(model, prompt[:, :1], 2).shape == (2, 3)  # shorter than the number of regions
 
 
 def test_generation_of_dense_and_depth_axis_models_by_recomputation():
