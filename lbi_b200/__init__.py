@@ -15,7 +15,11 @@ data/        synthetic tasks, byte streams, tokenizers, token shards
 ops/         Python entry points of the sm_100a CUDA kernels, each with an fp32 PyTorch oracle
 csrc/        CUDA/C++ sources (tcgen05 GEMM, attention pullback, suffix scan, fused elementwise, peer-memory kernels)
 parallel/    one-process-per-GPU runtime: symmetric peer buffers, region placement, fused optimizer
-utils/       device timing, clocks sampling, NVTX ranges
+cuda/        the kernel entry points under the reference's module paths (cuda.interface, cuda.transformer, cuda.mamba3)
+scripts/     paper launchers and presets, post-hoc evaluation, figures, gradient-parity report
+benchmarks/  microbenchmarks (GEMM, attention, SSD, communication paths) and small profiling cases
+utils/       failure handling (heartbeats, watchdog, host-side fault injection), NVTX ranges, gradient-parity harness
+inference.py token-by-token decoding (bounded memory for sequence-axis models), generate(), generation command
 """
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
