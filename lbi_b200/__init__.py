@@ -20,6 +20,7 @@ scripts/     paper launchers and presets, post-hoc evaluation, figures, gradient
 benchmarks/  microbenchmarks (GEMM, attention, SSD, communication paths) and small profiling cases
 utils/       failure handling (heartbeats, watchdog, host-side fault injection), NVTX ranges, gradient-parity harness
 inference.py token-by-token decoding (bounded memory for sequence-axis models), generate(), generation command
+serve.py     HTTP front end for generation (FastAPI / uvicorn when installed)
 """
 
 __version__ = "0.2.0"

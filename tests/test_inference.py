@@ -147,3 +147,29 @@ def test_generation_command_on_trained_runs(tmp_path):
                                          vocab_size=300, tokenizer_train_bytes=4096, train_tokenizer=True, **base))
     out = inference.main([str(tmp_path / "bpe" / "lbi"), "--prompt", "the lazy", "--max-new-tokens", "3", "--device", "cpu"])
     assert len(out["new_ids"]) == 3 and isinstance(out["text"], str)
+
+
+def test_generation_service_requests(tmp_path):
+    from lbi_b200.serve import GenerationService, build_app
+    from lbi_b200.train.config import LBITrainingConfig
+    from lbi_b200.train.lbi import run_lbi_experiment
+
+    text = tmp_path / "corpus.txt"
+    text.write_bytes(b"the quick brown fox jumps over the lazy dog. " * 100)
+    run_lbi_experiment(LBITrainingConfig(
+        variants="lbi", backbone="mamba3", device="cpu", dtype="float32", output_dir=str(tmp_path), run_name="svc", seq_len=16,
+        batch_size=2, steps=2, eval_every=2, eval_batches=1, log_every=1, save_every=2, layers=2, dim=16, d_state=16, headdim=16,
+        chunk_size=16, region_axis="sequence", sequence_regions=4, message_dim=4, message_hidden_dim=8, data_mode="text_byte",
+        vocab_size=256, train_text_path=str(text)))
+    service = GenerationService.from_run(tmp_path / "svc" / "lbi", device="cpu", max_new_tokens_limit=8)
+    assert service.health()["backbone"] == "mamba3" and service.health()["region_axis"] == "sequence"
+    reply = service.handle({"prompt": "the quick", "max_new_tokens": 4})
+    assert reply["prompt_ids"] == list(b"the quick") and len(reply["new_ids"]) == 4 and isinstance(reply["text"], str)
+    assert service.handle({"prompt_ids": [116, 104, 101], "max_new_tokens": 2, "temperature": 0.5, "top_k": 4, "seed": 3}) == \
+        service.handle({"prompt_ids": [116, 104, 101], "max_new_tokens": 2, "temperature": 0.5, "top_k": 4, "seed": 3})
+    for bad in ({}, {"prompt_ids": [999]}, {"prompt": "x", "max_new_tokens": 0}, {"prompt": "x", "max_new_tokens": 99}):
+        with pytest.raises(ValueError):
+            service.handle(bad)
+    pytest.importorskip("fastapi")
+    app = build_app(service)
+    assert {"/health", "/generate"} <= {route.path for route in app.routes}
