@@ -48,8 +48,27 @@ def run_lbi_experiment(cfg: LBITrainingConfig) -> Dict[str, Any]:
 run_training = run_lbi_experiment
 
 
+def run_with_restarts(cfg: LBITrainingConfig, max_restarts: int) -> Dict[str, Any]:
+    """``run_lbi_experiment`` under ``utils.failure.run_with_recovery``: after a step timeout, a bounded kernel wait that ran out,
+    a peer failure or an injected fault the run restarts from its newest loadable checkpoint, at most ``max_restarts`` times
+    (device errors are never retried in-process).  Single-process runs only: with one process per GPU every rank would have to
+    fail and restart in step, so the launcher's own restart policy (``torch.distributed.run --max-restarts``) plus
+    ``--resume-from`` is the tool there."""
+    import os
+
+    from ..utils.failure import run_with_recovery
+
+    if max_restarts <= 0 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        return run_lbi_experiment(cfg)
+    return run_with_recovery(run_lbi_experiment, cfg, max_restarts=max_restarts)
+
+
 def main() -> None:
-    summary = run_lbi_experiment(config_from_args(build_arg_parser().parse_args()))
+    """``LBI_B200_MAX_RESTARTS=N`` (needs ``--run-name``) restarts a failed single-process run from its newest checkpoint."""
+    import os
+
+    cfg = config_from_args(build_arg_parser().parse_args())
+    summary = run_with_restarts(cfg, int(os.environ.get("LBI_B200_MAX_RESTARTS", "0")))
     print(json.dumps(summary, indent=2, sort_keys=True))
 
 

@@ -159,12 +159,15 @@ class Fault:
     kind: str                 # raise | exit | stall_heartbeat | corrupt_checkpoint
     step: int
     rank: int | None = None
+    once: bool = False        # a transient fault: fires once per process, not again when a restarted run reaches the step
 
 
 class FaultInjector:
-    """Host-side faults at chosen steps.  Spec: ``kind@step=N[,rank=R]`` joined by ``;`` (environment LBI_B200_INJECT)."""
+    """Host-side faults at chosen steps.  Spec: ``kind@step=N[,rank=R][,once=1]`` joined by ``;`` (environment LBI_B200_INJECT).
+    ``once=1`` marks a transient fault: it is remembered for the life of the process, so a run restarted in-process passes it."""
 
     KINDS = {"raise", "exit", "stall_heartbeat", "corrupt_checkpoint"}
+    _fired_in_process: set = set()
 
     def __init__(self, spec: str | None = None, rank: int = 0) -> None:
         self.rank = int(rank)
@@ -179,17 +182,24 @@ class FaultInjector:
             if kind not in cls.KINDS:
                 raise ValueError(f"unknown fault kind {kind!r}; known: {sorted(cls.KINDS)}")
             fields = dict(kv.split("=") for kv in rest.split(",") if kv)
-            out.append(Fault(kind, int(fields.get("step", 0)), int(fields["rank"]) if "rank" in fields else None))
+            out.append(Fault(kind, int(fields.get("step", 0)), int(fields["rank"]) if "rank" in fields else None,
+                             fields.get("once", "0") not in ("0", "", "false")))
         return out
+
+    @classmethod
+    def reset_process_memory(cls) -> None:
+        cls._fired_in_process.clear()
 
     def due(self, step: int, kind: str | None = None) -> list[Fault]:
         return [f for f in self.faults if f.step == step and f not in self.fired and (f.rank is None or f.rank == self.rank)
-                and (kind is None or f.kind == kind)]
+                and (kind is None or f.kind == kind) and not (f.once and (f, self.rank) in self._fired_in_process)]
 
     def at_step(self, step: int, *, heartbeat: Heartbeat | None = None, checkpoint_path: Path | None = None) -> None:
         """Call between steps (no kernels or collectives of this rank in flight)."""
         for f in self.due(step):
             self.fired.add(f)
+            if f.once:
+                self._fired_in_process.add((f, self.rank))
             if f.kind == "stall_heartbeat" and heartbeat is not None:
                 heartbeat.mute()
             elif f.kind == "corrupt_checkpoint" and checkpoint_path is not None and Path(checkpoint_path).exists():

@@ -25,6 +25,7 @@ def _cfg(tmp_path, **kw):
 def test_fault_spec_parsing():
     faults = F.FaultInjector.parse("raise@step=3,rank=1; exit@step=5;stall_heartbeat@step=2")
     assert faults == [F.Fault("raise", 3, 1), F.Fault("exit", 5, None), F.Fault("stall_heartbeat", 2, None)]
+    assert F.FaultInjector.parse("raise@step=3,once=1") == [F.Fault("raise", 3, None, True)]
     with pytest.raises(ValueError):
         F.FaultInjector.parse("explode@step=1")
     inj = F.FaultInjector("raise@step=3,rank=1", rank=0)
@@ -56,6 +57,26 @@ def test_recovery_resumes_from_latest_checkpoint(tmp_path, monkeypatch):
     assert run["start_step"] == 2 and run["steps"] == 4
     rows = [json.loads(line) for line in (Path(run["run_dir"]) / "metrics.jsonl").read_text().splitlines()]
     assert [r["step"] for r in rows if r["split"] == "train"] == [1, 2, 3, 4]
+
+
+def test_training_entry_restarts_under_the_restart_limit(tmp_path, monkeypatch):
+    """The command-line route: ``run_with_restarts`` resumes after a transient injected fault and gives up beyond the limit."""
+    from lbi_b200.train.lbi import run_with_restarts
+
+    F.FaultInjector.reset_process_memory()
+    monkeypatch.setenv("LBI_B200_INJECT", "raise@step=3")
+    with pytest.raises(F.InjectedFault):
+        run_with_restarts(_cfg(tmp_path / "none"), 0)
+    with pytest.raises(F.InjectedFault):           # a fault that comes back at the same step every time exhausts the limit
+        run_with_restarts(_cfg(tmp_path / "always"), 1)
+    monkeypatch.setenv("LBI_B200_INJECT", "raise@step=3,once=1")
+    out = run_with_restarts(_cfg(tmp_path / "one"), 2)
+    assert out["restarts"] == 1 and out["runs"][0]["start_step"] >= 2 and out["runs"][0]["steps"] == 4
+    import lbi_b200.train.lbi as entry
+
+    monkeypatch.setenv("WORLD_SIZE", "2")  # multi-process runs are left to the launcher: the call goes straight through
+    monkeypatch.setattr(entry, "run_lbi_experiment", lambda cfg: {"direct": True})
+    assert run_with_restarts(_cfg(tmp_path / "multi"), 2) == {"direct": True}
 
 
 def test_corrupt_latest_checkpoint_falls_back(tmp_path):
