@@ -137,6 +137,9 @@ class ScanADEngine:
             state_jacobian_mode, basis_chunk=self.state_jacobian_basis_chunk
         )
         self.local_vjp_provider = local_vjp_provider or TorchAutogradLocalVJPProvider()
+        # A caller's own local-VJP provider is driven hook by hook, which needs the connected forward graph (depth-axis
+        # regions, as in the reference); without one the graph is cut at every state and one surrogate backward does the VJPs.
+        self.requires_detached_states = local_vjp_provider is None
 
     @classmethod
     def from_config(cls, cfg: Any, *, compute_interface_jacobian_stats: bool = False) -> "ScanADEngine":

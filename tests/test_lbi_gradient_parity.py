@@ -176,6 +176,13 @@ def test_scan_step_with_providers_and_keywords_of_the_reference():
     assert_parity(ref, got.grad_map)
     assert foreign.calls == ["new", "head", "initial", "region0", "region1", "region2", "region3", "shared"]
 
+    # the engine wrapper: a caller's provider makes it ask for the connected graph and is driven hook by hook
+    engine = ScanADEngine(state_jacobian_mode="graph", pullback_provider=_ForeignPullback(), local_vjp_provider=_ForeignLocalVJP())
+    assert engine.requires_detached_states is False and ScanADEngine().requires_detached_states is True
+    _, via_engine = run(model, engine, ids, tgt, engine.requires_detached_states)
+    assert_parity(ref, via_engine.grad_map)
+    assert engine.local_vjp_provider.calls[0] == "new" and engine.local_vjp_provider.calls[-1] == "shared"
+
     # this package's provider through the reference's hook names
     loss, cache = fresh()
     own = TorchAutogradLocalVJPProvider()
