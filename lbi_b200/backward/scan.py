@@ -171,6 +171,9 @@ class ScanADEngine:
             "interface_scan_rms": result.interface_scan_rms,
             "interface_jacobian_mode": self.state_jacobian_mode,
             "jacobian_basis_chunk": self.state_jacobian_basis_chunk,
+            # the two keys the reference's engine reports (backward/scan.py:161-165)
+            "interface_pullback_provider": getattr(self.pullback_provider, "name", type(self.pullback_provider).__name__),
+            "local_vjp_provider": getattr(self.local_vjp_provider, "name", type(self.local_vjp_provider).__name__),
         }
         if result.interface_jacobian_stats is not None:
             diagnostics["interface_jacobian_stats"] = result.interface_jacobian_stats

@@ -182,6 +182,7 @@ def test_scan_step_with_providers_and_keywords_of_the_reference():
     _, via_engine = run(model, engine, ids, tgt, engine.requires_detached_states)
     assert_parity(ref, via_engine.grad_map)
     assert engine.local_vjp_provider.calls[0] == "new" and engine.local_vjp_provider.calls[-1] == "shared"
+    assert (via_engine.diagnostics["interface_pullback_provider"], via_engine.diagnostics["local_vjp_provider"]) == ("foreign_graph", "foreign")
 
     # this package's provider through the reference's hook names
     loss, cache = fresh()
