@@ -128,6 +128,8 @@ class BackboneStack(nn.Module):
 
 
 class LayerwiseBackboneStack(BackboneStack):
+    """Blocks that map x -> x; a range is their composition."""
+
     def forward_range(self, x: torch.Tensor, start: int = 0, end: Optional[int] = None) -> torch.Tensor:
         stop = len(self.blocks) if end is None else end
         for index in range(start, stop):

@@ -11,6 +11,8 @@ from .mixer import Mamba2Simple
 
 
 class Mamba2Block(nn.Module):
+    """Add -> RMSNorm -> Mamba-2 mixer on the (branch, stream) residual contract of the stacks."""
+
     def __init__(
         self,
         dim: int,

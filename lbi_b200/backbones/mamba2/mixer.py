@@ -17,6 +17,8 @@ from .ssd import ssd_chunk_scan
 
 
 class Mamba2Simple(nn.Module):
+    """The Mamba-2 mixer: in_proj -> [z | x B C | dt], causal depthwise conv + SiLU on x B C, SSD scan, gated RMSNorm, out_proj."""
+
     def __init__(
         self,
         d_model: int,

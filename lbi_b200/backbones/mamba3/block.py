@@ -13,6 +13,8 @@ from .mixer import Mamba3, Mamba3ForwardCache
 
 @dataclass
 class Mamba3BlockCache:
+    """One block forward: the outgoing stream, the normed mixer input, the mixer cache and the block's inputs / output."""
+
     residual_out: torch.Tensor
     normed: torch.Tensor
     mixer: Mamba3ForwardCache
@@ -38,6 +40,8 @@ Mamba3BlockForwardCache = Mamba3BlockCache  # the reference's name for the same 
 
 
 class Mamba3Block(nn.Module):
+    """Add -> RMSNorm -> Mamba-3 mixer on the (branch, stream) residual contract of the stacks."""
+
     def __init__(
         self,
         dim: int,

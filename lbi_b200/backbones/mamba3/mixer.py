@@ -24,6 +24,8 @@ from .siso import _rotate_pairs, mamba3_siso_chunked, mamba3_siso_combined
 
 @dataclass
 class Mamba3ForwardCache:
+    """Intermediates of one mixer forward under the reference's field names."""
+
     input_u: torch.Tensor
     in_proj: torch.Tensor
     z: torch.Tensor
@@ -43,6 +45,8 @@ class Mamba3ForwardCache:
 
 
 class Mamba3(nn.Module):
+    """The Mamba-3 SISO mixer (see the module docstring); ``forward_with_cache`` keeps the intermediates, ``step`` / ``prefill`` decode."""
+
     def __init__(
         self,
         d_model: int,

@@ -16,6 +16,8 @@ from .rope import apply_rope
 
 
 class CausalSelfAttention(nn.Module):
+    """Fused qkv projection, optional depthwise causal conv on qkv, RoPE, grouped-query heads, causal softmax attention, output projection."""
+
     def __init__(
         self,
         dim: int,

@@ -16,6 +16,8 @@ from .mlp import GatedMLP
 
 
 class TransformerBlock(nn.Module):
+    """Pre-norm block on an fp32 residual stream: add -> RMSNorm -> attention, add -> RMSNorm -> SwiGLU MLP."""
+
     def __init__(
         self,
         dim: int,

@@ -17,6 +17,8 @@ def swiglu_hidden(dim: int, hidden_features: int | None, multiple_of: int = 128)
 
 
 class GatedMLP(nn.Module):
+    """SwiGLU: ``fc2(up * silu(gate))`` with ``up | gate = fc1(x)``; the hidden width is rounded up to a multiple of ``multiple_of``."""
+
     def __init__(
         self,
         dim: int,
@@ -38,5 +40,7 @@ class GatedMLP(nn.Module):
 
 
 class SwiGLUMLP(GatedMLP):
+    """``GatedMLP`` with the hidden width given as a ratio of the model width and no rounding."""
+
     def __init__(self, dim: int, mlp_ratio: float = 4.0, bias: bool = False) -> None:
         super().__init__(dim, hidden_features=max(1, int(dim * mlp_ratio)), out_features=dim, bias=bias, multiple_of=1)

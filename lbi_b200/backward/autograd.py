@@ -17,6 +17,8 @@ def autograd_backward_step(model: nn.Module, loss: torch.Tensor | None = None, *
 
 
 class AutogradEngine:
+    """Dense autograd: ``loss.backward()`` and the collected named gradients (the oracle of every other engine)."""
+
     name = "autograd"
     requires_detached_states = False
 

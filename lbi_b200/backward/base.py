@@ -12,12 +12,16 @@ GradMap = dict[str, "torch.Tensor | None"]
 
 @dataclass
 class ADResult:
+    """Named gradients plus engine diagnostics."""
+
     grad_map: GradMap
     diagnostics: dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass
 class LBIBackwardResult:
+    """Named gradients, the scan-vs-chain residual, optional Jacobian statistics and the state cotangents of a scan backward."""
+
     grad_map: GradMap
     interface_scan_rms: float
     interface_jacobian_stats: dict[str, float] | None = None
@@ -59,6 +63,8 @@ def is_scan_backprop_model(model: Any) -> bool:
 
 
 class ADEngine(Protocol):
+    """What the runners call: ``backward(model=, loss=, cache=) -> ADResult``."""
+
     name: str
 
     def backward(self, *, model: nn.Module, loss: torch.Tensor, cache: Any | None = None) -> ADResult: ...

@@ -17,6 +17,8 @@ from .base import GradMap, parameter_name_map, store_named_grads
 
 
 class LocalVJPProvider(Protocol):
+    """The six local steps of the scan backward (see the module docstring)."""
+
     name: str
 
     def initialize_grad_map(self, model: Any) -> GradMap: ...
@@ -85,6 +87,8 @@ def _grad(outputs, inputs: Sequence[nn.Parameter], grad_outputs=None, retain_gra
 
 
 class TorchAutogradLocalVJPProvider:
+    """Every local step as a ``torch.autograd.grad`` call on the retained forward graph."""
+
     name = "torch_autograd"
 
     def __init__(self) -> None:

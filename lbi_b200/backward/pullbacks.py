@@ -20,6 +20,8 @@ from ..backends.base import autocast_as
 
 
 class InterfacePullbackProvider(Protocol):
+    """``materialize_state_jacobian_t(model=, cache=, regions=None) -> [A_k^T [B, R, R]]`` for the listed regions."""
+
     name: str
 
     def materialize_state_jacobian_t(self, *, model: Any, cache: dict, regions: Sequence[int] | None = None) -> list[torch.Tensor]: ...
@@ -34,6 +36,8 @@ def _state_in(cache, k):
 
 
 class TorchGraphInterfacePullbackProvider:
+    """One batched VJP of the identity basis through the retained forward graph per region."""
+
     name = "torch_graph"  # the reference's provider names (backward/pullbacks.py:153, :169)
 
     def __init__(self, basis_chunk: int = 1) -> None:
@@ -57,6 +61,8 @@ class TorchGraphInterfacePullbackProvider:
 
 
 class TorchRecomputeInterfacePullbackProvider:
+    """Re-runs decode -> region -> update on a basis-replicated batch, ``basis_chunk`` directions at a time."""
+
     name = "torch_recompute"
 
     def __init__(self, basis_chunk: int = 1) -> None:
@@ -90,6 +96,8 @@ class TorchRecomputeInterfacePullbackProvider:
 
 
 class StructuredInterfacePullbackProvider:
+    """No autograd: closed-form interface J^T, the backend's basis pullback, token sum, closed-form decode J^T."""
+
     name = "structured"
 
     def __init__(self, basis_chunk: int = 0) -> None:
@@ -121,6 +129,8 @@ class StructuredInterfacePullbackProvider:
 
 
 class ForwardModeInterfacePullbackProvider:
+    """Forward mode: pushes the R tangent directions of the incoming state through the region with ``torch.func.jvp``."""
+
     name = "forward"
 
     def __init__(self, basis_chunk: int = 0) -> None:

@@ -66,6 +66,8 @@ def lbi_reference_scan_backward_step(model: Any = None, *, loss: torch.Tensor | 
 
 
 class ReferenceScanEngine:
+    """The same gradients with the state cotangents pulled through the forward graph one region at a time (no Jacobians)."""
+
     name = "reference_scan"
     requires_detached_states = True
 

@@ -114,6 +114,9 @@ def lbi_scan_backward_step(
 
 
 class ScanADEngine:
+    """Exact region-local backward: per-region interface Jacobians from a pullback provider, suffix scan of the state cotangents,
+    local VJPs per region; assigns ``.grad`` and reports the scan diagnostics."""
+
     name = "scan"
     requires_detached_states = True
 

@@ -8,6 +8,8 @@ from .base import CanvasCache
 
 
 class TokenEmbeddingCanvas(nn.Module):
+    """Token ids -> embedding features; ``output_weight()`` hands the embedding matrix to a tied readout."""
+
     def __init__(self, *, vocab_size: int, feature_dim: int) -> None:
         super().__init__()
         self.vocab_size = int(vocab_size)

@@ -255,6 +255,10 @@ def broadcast_condition_jacobian_t(g_region_input: torch.Tensor) -> torch.Tensor
 
 
 class VectorMLPInterface(InterfaceModule):
+    """The bounded interface state as a vector of width R: the initial state is an MLP of the mean-pooled canvas, ``decode`` maps the
+    state to a per-region condition added to every token, ``update`` is ``LayerNorm_k(s + tanh(scale_k) * MLP_k(mean_t(region output)))``.
+    Per-region decoders / encoders / norms and one ``update_scale`` vector; closed-form Jacobian-transpose hooks for the structured engines."""
+
     def __init__(
         self,
         *,

@@ -14,6 +14,8 @@ from ..readouts import NormLMHeadReadout
 
 
 class DenseLanguageModel(nn.Module):
+    """canvas -> the whole backbone -> readout: the baseline without regions or interface."""
+
     def __init__(self, *, vocab_size: int, backbone_spec: BackboneSpec, tie_embeddings: bool = False) -> None:
         super().__init__()
         backbone_spec.validate()

@@ -26,6 +26,8 @@ _VALID_STATE_ABLATIONS = {"none", "zero_all", "noise", "mask"}
 
 @dataclass
 class LBIRegionCache:
+    """One region of a forward pass: ranges, backend cache, canvas features, incoming state, condition, input, output, interface step."""
+
     region_index: int
     layer_range: tuple[int, int]
     token_range: tuple[int, int]
@@ -50,6 +52,11 @@ class LBICache:
 
 
 class LBILanguageModel(nn.Module):
+    """canvas -> interface.initialize -> for every region: decode the state into a condition, run the region backend on
+    canvas + condition, update the state from the region output -> readout.  Regions are layer ranges (``region_axis="depth"``, the
+    reference's cut) or token spans through the whole stack (``"sequence"``); ``forward_with_cache`` returns the states, region
+    inputs / outputs and per-region caches the backward engines work from."""
+
     def __init__(
         self,
         *,

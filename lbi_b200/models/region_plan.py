@@ -39,6 +39,8 @@ def split_tokens(seq_len: int, num_regions: int) -> list[tuple[int, int]]:
 
 @dataclass(frozen=True)
 class RegionPlan:
+    """How a model is cut into regions: the axis, the number of regions, the layer range of each; ``token_ranges(T)`` gives the spans."""
+
     axis: str
     num_regions: int
     layer_ranges: tuple[tuple[int, int], ...]

@@ -16,6 +16,8 @@ import torch.distributed as dist
 
 
 class LocalComm:
+    """The single-process plane: every exchange is the identity."""
+
     rank = 0
     world_size = 1
     name = "local"
@@ -43,6 +45,9 @@ class LocalComm:
 
 
 class CollectiveComm:
+    """Communication plane on library collectives (NCCL on GPUs, gloo on CPUs): state hand-off by send / recv, Jacobian exchange by
+    all-gather, gradient reduce-scatter and weight all-gather around the sharded AdamW.  The twin of ``SymmComm``, and the baseline it is timed against."""
+
     name = "collective"
 
     def __init__(self, group=None) -> None:

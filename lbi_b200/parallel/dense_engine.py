@@ -16,6 +16,9 @@ from .flat import FlatParams
 
 
 class DenseFastEngine:
+    """The dense model of the same size on the same structured kernels (no regions, no interface): forward with cached activations,
+    closed-form backward, fused clip + AdamW on flat buffers.  Single device."""
+
     def __init__(self, model, *, lr: float = 1e-3, betas: tuple[float, float] = (0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.0, grad_clip: float = 1.0, act_dtype: torch.dtype | None = None) -> None:
         from ..backends.mamba_structured import StructuredMambaRegion

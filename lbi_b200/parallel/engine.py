@@ -33,6 +33,8 @@ from .flat import FlatParams
 
 @dataclass
 class RegionRecord:
+    """Per-region forward record kept between the forward chain and the region's turn in the backward."""
+
     index: int
     token_range: tuple[int, int]
     state_in: torch.Tensor
@@ -51,6 +53,8 @@ class RegionRecord:
 
 @dataclass
 class StepResult:
+    """What ``backward`` returns: the loss, the state cotangents g_k [B, K, R] and the interface Jacobians when they were kept."""
+
     loss: torch.Tensor
     state_cotangents: torch.Tensor | None = None
     jacobians: torch.Tensor | None = None
@@ -58,6 +62,11 @@ class StepResult:
 
 
 class FastLBIEngine:
+    """Autograd-free training step of an ``LBILanguageModel`` on the structured kernels: forward chain over the regions with cached
+    activations, interface Jacobians by batched basis pullbacks (the basis directions are split over the ranks), affine suffix scan of
+    the state cotangents, one local VJP per region into a flat fp32 gradient buffer, fused clip + AdamW.  One process per GPU;
+    regions are placed on ranks in contiguous blocks and states, Jacobians and gradients move through the ``comm`` plane."""
+
     def __init__(
         self,
         model,

@@ -16,6 +16,8 @@ from torch import nn
 
 @dataclass
 class Slot:
+    """Where a parameter lives in the flat buffers: name, element offset, element count, shape."""
+
     name: str
     offset: int
     numel: int
@@ -23,6 +25,9 @@ class Slot:
 
 
 class FlatParams:
+    """All trainable parameters of a model as views into one fp32 buffer (aligned slots, padded so that ``world_size`` equal shards
+    tile it), with a gradient buffer of the same layout, AdamW moments per shard and an optional low-precision shadow of the weights."""
+
     def __init__(self, model: nn.Module, *, world_size: int = 1, shadow_dtype: torch.dtype | None = torch.bfloat16,
                  align: int = 64) -> None:
         named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]

@@ -44,6 +44,10 @@ class _GuardedHandle:
 
 
 class SymmComm(CollectiveComm):
+    """Communication plane on symmetric (peer-mapped) memory: the kernels of ``csrc/peer.cu`` store states into the next rank's
+    mailbox, publish Jacobian pieces into every peer's buffer, reduce-scatter gradients by peer loads and all-gather the updated
+    weights by peer stores.  Every device-side wait is bounded; canaries guard the buffers peers write into."""
+
     name = "symm"
 
     def __init__(self, group=None) -> None:

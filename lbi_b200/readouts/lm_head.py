@@ -12,6 +12,8 @@ from .base import ReadoutCache
 
 
 class NormLMHeadReadout(nn.Module):
+    """Final norm, then the vocabulary projection with the canvas embedding (tied) or an own bias-free ``lm_head``."""
+
     def __init__(self, *, norm: nn.Module, feature_dim: int, vocab_size: int, tie_embeddings: bool = True) -> None:
         super().__init__()
         self.norm = norm

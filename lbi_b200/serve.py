@@ -15,6 +15,8 @@ from .inference import generate, load_run, load_run_tokenizer
 
 
 class GenerationService:
+    """One loaded run (model, config, tokenizer) behind a lock; ``handle(request)`` validates, generates and decodes."""
+
     def __init__(self, model: Any, cfg: Any, tokenizer: Any = None, *, max_new_tokens_limit: int = 1024) -> None:
         self.model, self.cfg, self.tokenizer = model, cfg, tokenizer
         self.limit = int(max_new_tokens_limit)
