@@ -14,6 +14,8 @@ from .base import RegionForwardCache, autocast_as, current_autocast
 
 
 class BackboneStackRegionBackend(nn.Module):
+    """Region backend over any backbone stack (Mamba-2, Mamba-3, hybrid): regions are layer ranges of the stack."""
+
     name = "backbone_stack"
 
     def __init__(self, *, backbone_spec: BackboneSpec | None = None, region_ranges: list[tuple[int, int]],

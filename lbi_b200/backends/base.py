@@ -27,6 +27,8 @@ def autocast_as(state: tuple[str, torch.dtype] | None):
 
 @dataclass
 class RegionForwardCache:
+    """What a backend keeps from a region forward: index, layer range, the input, the structured cache (built lazily), autocast state."""
+
     region_index: int
     layer_range: tuple[int, int]
     region_input: torch.Tensor | None = None
@@ -36,6 +38,9 @@ class RegionForwardCache:
 
 
 class RegionBackend(Protocol):
+    """Runs one region (``forward_region``), lists its parameters, and differentiates it: a basis of output cotangents pulled back to
+    the input (``input_pullback_basis``) and the parameter VJP of one cotangent (``parameter_vjp``)."""
+
     name: str
 
     def forward_region(self, *, region_input: torch.Tensor, region_index: int) -> tuple[torch.Tensor, RegionForwardCache]: ...

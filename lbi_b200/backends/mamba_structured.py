@@ -33,6 +33,8 @@ from .transformer_structured import StructuredRegionCache, StructuredTransformer
 # ------------------------------------------------------------------------------------------------ caches
 @dataclass
 class Mamba3LayerCache:
+    """Flat activations of one Mamba-3 block that the closed-form backward reads."""
+
     stream: torch.Tensor          # fp32 residual stream entering the norm                     [n, D]
     rstd: torch.Tensor            # [n]
     normed: torch.Tensor          # input of in_proj                                            [n, D]
@@ -56,6 +58,8 @@ class Mamba3LayerCache:
 
 @dataclass
 class Mamba2LayerCache:
+    """Flat activations of one Mamba-2 block that the closed-form backward reads."""
+
     stream: torch.Tensor
     rstd: torch.Tensor
     normed: torch.Tensor

@@ -25,6 +25,8 @@ from .transformer_structured import StructuredTransformerRegion
 # fills them from the module code for inspection and for code written against the reference's cache.
 @dataclass
 class TransformerAttentionCache:
+    """Attention intermediates of one layer (inspection view)."""
+
     norm_input: torch.Tensor
     norm_output: torch.Tensor
     qkv: torch.Tensor
@@ -42,6 +44,8 @@ class TransformerAttentionCache:
 
 @dataclass
 class TransformerMLPCache:
+    """MLP intermediates of one layer (inspection view)."""
+
     norm_input: torch.Tensor
     norm_output: torch.Tensor
     fc1_output: torch.Tensor
@@ -54,6 +58,8 @@ class TransformerMLPCache:
 
 @dataclass
 class TransformerLayerCache:
+    """One layer of ``forward_region_with_layer_caches``: inputs, attention and MLP records, outputs."""
+
     layer_index: int
     hidden_input: torch.Tensor
     residual_input: torch.Tensor | None
@@ -65,11 +71,15 @@ class TransformerLayerCache:
 
 @dataclass
 class TransformerRegionCache(RegionForwardCache):
+    """A region forward with the per-layer records attached."""
+
     layer_caches: list[TransformerLayerCache] = field(default_factory=list)
     region_output: torch.Tensor | None = None
 
 
 class TransformerLowering(Protocol):
+    """How a Transformer region is differentiated: ``input_pullback_basis`` and ``parameter_vjp`` given the backend and a cache."""
+
     name: str
 
     def input_pullback_basis(self, *, backend: "TransformerRegionBackend", cache: RegionForwardCache,
@@ -126,6 +136,9 @@ class StructuredTransformerLowering:
 
 
 class TransformerRegionBackend(nn.Module):
+    """Region backend of the Transformer stack: module forward while autograd records, the structured kernels otherwise;
+    derivatives through a pluggable lowering (structured by default, autograd as the oracle)."""
+
     name = "transformer"
 
     def __init__(self, *, backbone_spec: BackboneSpec | None = None, region_ranges: list[tuple[int, int]],

@@ -10,6 +10,8 @@ from .transformer import StructuredTransformerLowering
 
 
 class CudaTransformerLowering(StructuredTransformerLowering):
+    """The structured lowering plus the attention basis-pullback entry point with the reference's argument layout."""
+
     name = "cuda"
 
     def __init__(self, *, allow_reference_fallback: bool = False) -> None:

@@ -26,6 +26,8 @@ from ..backbones.transformer.rope import rope_tables
 
 @dataclass
 class LayerCache:
+    """Flat activations of one Transformer layer that the closed-form backward reads."""
+
     stream1: torch.Tensor  # fp32 residual stream entering norm 1          [n, D]
     rstd1: torch.Tensor  # [n]
     normed1: torch.Tensor  # input of in_proj                              [n, D]
@@ -42,6 +44,8 @@ class LayerCache:
 
 @dataclass
 class StructuredRegionCache:
+    """A region forward of the structured Transformer lowering: shapes, input, per-layer caches, output pieces."""
+
     batch: int
     seq_len: int
     layer_range: tuple[int, int]

@@ -25,6 +25,8 @@ _PRETRAINED_HF_TOKENIZER_TYPES = {"llama", "llama31"}
 
 
 class TextTokenizerBackend(Protocol):
+    """What the data layer needs from a tokenizer: ``vocab_size`` and ``encode_bytes``."""
+
     @property
     def vocab_size(self) -> int: ...
 
@@ -48,6 +50,8 @@ def split_bytes_into_pieces(raw: bytes) -> list[bytes]:
 
 @dataclass
 class ByteBPETokenizer:
+    """Dependency-free byte-level BPE: 256 byte tokens plus learnt merges inside whitespace-delimited pieces; exact round trip."""
+
     merges: list[tuple[int, int, int]]
     token_bytes: dict[int, bytes]
 
@@ -160,6 +164,8 @@ def load_or_train_byte_bpe_tokenizer(*, tokenizer_path, train_path, vocab_size: 
 
 
 class SentencePieceBPETokenizer:
+    """A SentencePiece BPE model file."""
+
     def __init__(self, model_path: str | Path) -> None:
         if spm is None:
             raise ImportError("sentencepiece is required for text_bpe mode")
@@ -178,6 +184,8 @@ class SentencePieceBPETokenizer:
 
 
 class HFAutoTextTokenizer:
+    """A local Hugging Face tokenizer directory (the ``llama`` / ``llama31`` tokenizer types)."""
+
     def __init__(self, model_path: str | Path) -> None:
         from transformers import AutoTokenizer
 

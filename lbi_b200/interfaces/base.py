@@ -16,6 +16,8 @@ from torch import nn
 
 @dataclass(frozen=True)
 class InterfaceSpec:
+    """Name and state width of an interface."""
+
     state_shape: tuple[int, ...]
     state_flat_dim: int
     region_condition_dim: int
@@ -23,12 +25,17 @@ class InterfaceSpec:
 
 @dataclass
 class InterfaceStep:
+    """Result of one state update: the new state plus diagnostics (pooled features, delta, scale, pre-norm state)."""
+
     state: torch.Tensor
     diagnostics: dict[str, torch.Tensor] = field(default_factory=dict)
     cache: Any | None = None
 
 
 class InterfaceModule(nn.Module, ABC):
+    """Base class of interfaces: ``initialize``, ``decode``, ``update``, the parameter groups of the local VJPs and the optional
+    closed-form Jacobian-transpose hooks the structured engines call."""
+
     spec: InterfaceSpec
 
     @abstractmethod

@@ -419,6 +419,8 @@ class VectorMLPInterface(InterfaceModule):
 
 @dataclass
 class LegacyInterfaceUpdate:
+    """Result of an LBI-1 state update under that release's field names."""
+
     state: torch.Tensor
     pooled_region_output: torch.Tensor
     delta_state: torch.Tensor

@@ -27,6 +27,8 @@ build_region_slices = lambda layers, region_size: build_region_ranges(layers, re
 
 @dataclass
 class RegionForwardCache:
+    """One region of an LBI-1 forward under that release's field names."""
+
     region_idx: int
     region_range: tuple[int, int]
     x_static: torch.Tensor
@@ -53,6 +55,8 @@ class RegionInterfaceCache:
 
 
 class NativeRegionInterfaceModel(nn.Module):
+    """The LBI-1 model (see the module docstring): depth regions, messages instead of states, first-release parameter names."""
+
     def __init__(self, *, vocab_size: int, region_size: int, message_dim: int, backbone_spec: BackboneSpec,
                  message_hidden_dim: int = 0, message_scale_init: float = 0.5, tie_embeddings: bool = False) -> None:
         super().__init__()

@@ -43,6 +43,8 @@ class LBIRegionCache:
 
 @dataclass
 class LBICache:
+    """Typed view of the dictionary ``forward_with_cache`` returns."""
+
     canvas_features: torch.Tensor
     states: list[torch.Tensor]
     region_inputs: list[torch.Tensor]

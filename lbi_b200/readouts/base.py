@@ -10,6 +10,8 @@ from torch import nn
 
 @dataclass
 class ReadoutCache:
+    """Input features, normed features and logits of one readout call."""
+
     features: torch.Tensor
     normed_features: torch.Tensor
     logits: torch.Tensor
@@ -17,6 +19,8 @@ class ReadoutCache:
 
 @runtime_checkable
 class ReadoutModule(Protocol):
+    """Region features -> vocabulary logits; ``vjp_parameters`` lists what the head VJP differentiates."""
+
     def forward(self, features: torch.Tensor, *, canvas) -> torch.Tensor: ...
 
     def forward_with_cache(self, features: torch.Tensor, *, canvas) -> tuple[torch.Tensor, ReadoutCache]: ...

@@ -26,6 +26,8 @@ def have_matplotlib() -> bool:
 
 @dataclass
 class Series:
+    """One curve: label, x, y, optional band, line style."""
+
     label: str
     x: Sequence[float]
     y: Sequence[float]
@@ -35,6 +37,8 @@ class Series:
 
 @dataclass
 class Chart:
+    """A figure (curves or bars) that saves through matplotlib when installed and through a built-in SVG writer otherwise."""
+
     title: str
     xlabel: str
     ylabel: str

@@ -22,6 +22,8 @@ from dataclasses import dataclass, field
 
 @dataclass(frozen=True)
 class ArchPreset:
+    """Layers, width and the remaining architecture flags of one (scale, backbone) pair."""
+
     layers: int
     dim: int
     flags: dict = field(default_factory=dict)

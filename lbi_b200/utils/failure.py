@@ -156,6 +156,8 @@ class Heartbeat:
 # ------------------------------------------------------------------------------------------------------ injection
 @dataclass(frozen=True)
 class Fault:
+    """One injected fault: kind, step, optional rank, transient or not."""
+
     kind: str                 # raise | exit | stall_heartbeat | corrupt_checkpoint
     step: int
     rank: int | None = None

@@ -26,6 +26,8 @@ _HYBRID_LAYERS = ("mamba3", "transformer", "mamba2", "transformer")
 
 @dataclass(frozen=True)
 class GradParityCase:
+    """One gradient-parity case: backbone, region layout, device / dtype, tolerances."""
+
     name: str
     backbone_name: str
     region_mode: str                 # single_region | multi_region
@@ -50,6 +52,8 @@ class GradParityCase:
 
 @dataclass
 class ParameterMetrics:
+    """Gradient agreement of one parameter in one trial."""
+
     name: str
     numel: int
     has_ref_grad: bool
@@ -63,6 +67,8 @@ class ParameterMetrics:
 
 @dataclass
 class TrialMetrics:
+    """One (seed, batch) trial of a case: losses, global gradient metrics, per-parameter metrics."""
+
     case_name: str
     seed: int
     batch_index: int
@@ -97,6 +103,8 @@ class TrialMetrics:
 
 @dataclass
 class CaseAggregate:
+    """All trials of a case with the worst-case summary the report tables print."""
+
     case: GradParityCase
     interface_jacobian_mode: str
     jacobian_basis_chunk: int
