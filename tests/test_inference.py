@@ -173,3 +173,15 @@ def test_generation_service_requests(tmp_path):
     pytest.importorskip("fastapi")
     app = build_app(service)
     assert {"/health", "/generate"} <= {route.path for route in app.routes}
+
+
+def test_the_python_api_example_of_the_readme_runs():
+    """The snippet under "Python API" in README.md is executed as written."""
+    from pathlib import Path
+
+    text = (Path(__file__).resolve().parent.parent / "README.md").read_text(encoding="utf-8")
+    section = text.split("## Python API", 1)[1]
+    code = section.split("```python", 1)[1].split("```", 1)[0]
+    scope: dict = {}
+    exec(compile(code, "README.md:python-api", "exec"), scope)  # noqa: S102
+    assert scope["tokens"].shape == (2, 16) and scope["first"] == scope["first"] and scope["second"] == scope["second"]
