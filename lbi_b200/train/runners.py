@@ -161,7 +161,7 @@ class _FlatOptimizerView:
         hyper = {"lr": self.param_groups[0]["lr"], "betas": tuple(e.betas), "eps": e.eps, "weight_decay": e.weight_decay,
                  "amsgrad": False, "maximize": False, "foreach": None, "capturable": False, "differentiable": False,
                  "fused": None}
-        return e.flat.state_dict_like_torch(self._order(), hyper, comm=e.comm)
+        return e.flat.state_dict_like_torch(self._order(), hyper, comm=getattr(e, "comm", None))
 
     def load_state_dict(self, sd: dict) -> None:
         self.engine.flat.load_state_dict_like_torch(sd, self._order())
@@ -205,10 +205,31 @@ class _FastStepper:
         return ""
 
 
+class _DenseFastStepper:
+    """The dense model on the structured kernels without autograd (``--variants dense --backward-engine fast``)."""
+
+    def __init__(self, cfg, model, device) -> None:
+        from ..parallel import DenseFastEngine
+
+        act = torch.bfloat16 if cfg.dtype == "bfloat16" else torch.float32
+        self.engine = DenseFastEngine(model, lr=cfg.lr_model, weight_decay=cfg.weight_decay, grad_clip=cfg.grad_clip, act_dtype=act)
+        self.optimizer = _FlatOptimizerView(self.engine, cfg)
+        self.diagnostics: dict[str, Any] = {}
+
+    def step(self, xb, yb, lr: float, want_jacobian_stats: bool = False) -> torch.Tensor:
+        self.optimizer.param_groups[0]["lr"] = lr
+        return self.engine.step(xb, yb, lr=lr)
+
+    def message_norm(self) -> float | str:
+        return ""
+
+
 def _build_stepper(cfg, model, device, variant: str):
     if _world_size() > 1 and (variant == DENSE_VARIANT or cfg.backward_engine != "fast"):
         raise ValueError("multi-process training is region-parallel: it needs the lbi variant with --backward-engine fast")
     if variant == DENSE_VARIANT:
+        if cfg.backward_engine == "fast":
+            return _DenseFastStepper(cfg, model, device)
         return _AutogradStepper(cfg, model, device, AutogradEngine(), lbi=False)
     if cfg.backward_engine == "fast":
         return _FastStepper(cfg, model, device)
@@ -260,7 +281,7 @@ def _run_training_loop(cfg: LBITrainingConfig, *, run_dir: Path, variant: str, h
         mode="resume" if cfg.resume_from else "init", load_from=cfg.resume_from or cfg.init_from, regime=variant, model=model,
         optimizer=stepper.optimizer, device=device, train_generator=train_gen, eval_generator=eval_gen,
     )
-    if isinstance(stepper, _FastStepper):
+    if isinstance(stepper, (_FastStepper, _DenseFastStepper)):
         stepper.engine.flat.refresh_shadow()  # weights may just have been replaced by a checkpoint
 
     final_train = final_val = float("nan")

@@ -110,6 +110,24 @@ def test_variants_of_the_lbi_run(tmp_path, kw):
     assert run["final_val_ce_loss"] < 10.0
 
 
+def test_dense_variant_on_the_fast_engine_trains_resumes_and_saves_torch_layout(tmp_path):
+    first = run_lbi_experiment(make_cfg(tmp_path, variants="dense", backward_engine="fast", d_conv=0, steps=2))
+    run = first["runs"][0]
+    assert run["final_train_ce_loss"] == run["final_train_ce_loss"] and run["final_val_ce_loss"] < 10.0
+    ckpt = torch.load(Path(first["root_dir"]) / "dense" / "checkpoints" / "latest.pt", weights_only=False)
+    from lbi_b200.train.model_builders import build_dense_model
+
+    model = build_dense_model(LBITrainingConfig.from_dict(ckpt["config"]))
+    model.load_state_dict(ckpt["model_state_dict"])
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    opt.load_state_dict(ckpt["optimizer_state_dict"])
+    resumed = run_lbi_experiment(make_cfg(tmp_path, variants="dense", backward_engine="fast", d_conv=0, steps=3,
+                                          resume_from=str(Path(first["root_dir"]))))
+    assert resumed["runs"][0]["start_step"] == 2 and resumed["runs"][0]["steps"] == 3
+    autograd = run_lbi_experiment(make_cfg(tmp_path, variants="dense", d_conv=0, steps=2, run_name="autograd"))
+    assert autograd["runs"][0]["final_train_ce_loss"] == pytest.approx(run["final_train_ce_loss"], rel=2e-3)
+
+
 def test_fast_engine_checkpoint_round_trips_into_torch_adamw(tmp_path):
     summary = run_lbi_experiment(make_cfg(tmp_path, backward_engine="fast", d_conv=0))
     ckpt = torch.load(Path(summary["root_dir"]) / "lbi" / "checkpoints" / "latest.pt", weights_only=False)
