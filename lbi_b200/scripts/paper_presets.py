@@ -213,9 +213,9 @@ def build_command(kind: str, extra: list[str] | None = None) -> list[str]:
         axis = _env("REGION_AXIS", "")
         if axis:  # REGION_AXIS=sequence SEQUENCE_REGIONS=8: cut the tokens instead of the layers (one span per GPU at 8 GPUs)
             args += ["--region-axis", axis, "--sequence-regions", str(_env("SEQUENCE_REGIONS", 8))]
-        engine = _env("BACKWARD_ENGINE", "")
-        if engine:  # e.g. BACKWARD_ENGINE=fast for the structured kernels (one process per GPU under torchrun)
-            args += ["--backward-engine", engine]
+    engine = _env("BACKWARD_ENGINE", "")
+    if engine:  # BACKWARD_ENGINE=fast: the structured kernels without autograd (LBI: one process per GPU under NPROC_PER_NODE)
+        args += ["--backward-engine", engine]
     args += ["--tie-embeddings" if tied else "--no-tie-embeddings"]
     ckpt_root = _env("CHECKPOINT_ROOT", "")
     if ckpt_root:

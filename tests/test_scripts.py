@@ -104,6 +104,7 @@ def test_launcher_choices_follow_the_tables_of_the_reference_launchers(launch_en
     assert (cfg.layers, cfg.lr_model, cfg.weight_decay, cfg.warmup_steps, cfg.tie_embeddings) == (28, 3e-4, 0.1, 1000, False)
     assert cfg.run_name == "dense_seed7" and cfg.output_dir.endswith("paper_mamba3_28l_768d_llama32k_untied_seq1024_20ksteps")
     assert _parse(paper_presets.build_command("lbi")).backward_engine == "fast"
+    assert _parse(paper_presets.build_command("dense")).backward_engine == "fast"
     launch_env.setenv("NPROC_PER_NODE", "8")
     multi = paper_presets.build_command("lbi")
     assert multi[1:7] == ["-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=8", "--master-addr", "127.0.0.1"]
