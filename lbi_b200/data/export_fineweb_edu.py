@@ -55,23 +55,21 @@ def export(dataset_iter, train_path: Path, val_path: Path, train_bytes: int, val
 def main() -> None:
     args = _parse_args()
     try:
-        try:
-            from datasets import load_dataset
-        except ImportError as exc:
-            raise ImportError("the `datasets` package is required for the FineWeb-Edu export") from exc
-        out_dir = Path(args.output_dir).expanduser() if args.output_dir else CORPORA_ROOT / args.output_subdir
-        cache_dir = Path(args.cache_dir).expanduser()
-        out_dir.mkdir(parents=True, exist_ok=True)
-        cache_dir.mkdir(parents=True, exist_ok=True)
-        ds = load_dataset(args.dataset_name, args.config, split="train", streaming=True, cache_dir=str(cache_dir))
-        train_path, val_path = out_dir / "fineweb_edu_train.txt", out_dir / "fineweb_edu_val.txt"
-        wt, wv = export(ds, train_path, val_path, args.train_bytes, args.val_bytes)
-        print(f"[fineweb_edu] wrote train={train_path} bytes={wt}\n[fineweb_edu] wrote val={val_path} bytes={wv}", flush=True)
-    finally:
-        if args.force_exit_after_export:
-            sys.stdout.flush()
-            sys.stderr.flush()
-            os._exit(0)
+        from datasets import load_dataset
+    except ImportError as exc:
+        raise ImportError("the `datasets` package is required for the FineWeb-Edu export") from exc
+    out_dir = Path(args.output_dir).expanduser() if args.output_dir else CORPORA_ROOT / args.output_subdir
+    cache_dir = Path(args.cache_dir).expanduser()
+    out_dir.mkdir(parents=True, exist_ok=True)
+    cache_dir.mkdir(parents=True, exist_ok=True)
+    ds = load_dataset(args.dataset_name, args.config, split="train", streaming=True, cache_dir=str(cache_dir))
+    train_path, val_path = out_dir / "fineweb_edu_train.txt", out_dir / "fineweb_edu_val.txt"
+    wt, wv = export(ds, train_path, val_path, args.train_bytes, args.val_bytes)
+    print(f"[fineweb_edu] wrote train={train_path} bytes={wt}\n[fineweb_edu] wrote val={val_path} bytes={wv}", flush=True)
+    if args.force_exit_after_export:  # only after a successful export: a failure above must keep its traceback and exit code
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -370,3 +370,17 @@ def test_pretokenize_entry_takes_the_keywords_of_the_reference(tmp_path):
     tm2, vm2 = pretokenize_text_corpus(train_path=train, val_path=None, out_dir=tmp_path / "o3",
                                        tokenizer_path=tmp_path / "tok.json", **{**common, "train_tokenizer": False})
     assert vm2 is None and json.loads(tm2.read_text()) == json.loads(tm.read_text())
+
+
+def test_fineweb_export_fills_the_train_budget_before_the_validation_file(tmp_path):
+    from lbi_b200.data.export_fineweb_edu import export
+
+    docs = [{"text": f"document number {i} " + "x" * 40} for i in range(50)] + [{"text": ""}, {"other": 1}]
+    wt, wv = export(iter(docs), tmp_path / "train.txt", tmp_path / "val.txt", train_bytes=500, val_bytes=200)
+    assert (wt, wv) == (500, 200)
+    train, val = (tmp_path / "train.txt").read_bytes(), (tmp_path / "val.txt").read_bytes()
+    assert len(train) == 500 and len(val) == 200 and train.startswith(b"document number 0 ")
+    first_val_doc = int(val.split(b" ")[2])
+    assert first_val_doc > int(train.rsplit(b"document number ", 1)[1].split(b" ")[0]) - 1  # validation starts after the train budget
+    small = export(iter(docs[:3]), tmp_path / "t2.txt", tmp_path / "v2.txt", train_bytes=10_000, val_bytes=10_000)
+    assert small[0] == sum(len(d["text"].strip()) + 1 for d in docs[:3]) and small[1] == 0
