@@ -384,3 +384,41 @@ def test_fineweb_export_fills_the_train_budget_before_the_validation_file(tmp_pa
     assert first_val_doc > int(train.rsplit(b"document number ", 1)[1].split(b" ")[0]) - 1  # validation starts after the train budget
     small = export(iter(docs[:3]), tmp_path / "t2.txt", tmp_path / "v2.txt", train_bytes=10_000, val_bytes=10_000)
     assert small[0] == sum(len(d["text"].strip()) + 1 for d in docs[:3]) and small[1] == 0
+
+
+def test_every_synthetic_task_has_its_structure():
+    from lbi_b200.data.train_data import SYNTHETIC_TASKS, build_synthetic_corpus, sample_batch
+
+    vocab, seq_len = 32, 20
+    bos, sep, pad = vocab - 1, vocab - 2, vocab - 3
+    for task in SYNTHETIC_TASKS:
+        corpus = build_synthetic_corpus(num_sequences=6, seq_len=seq_len, vocab_size=vocab, seed=4, task=task)
+        again = build_synthetic_corpus(num_sequences=6, seq_len=seq_len, vocab_size=vocab, seed=4, task=task)
+        assert corpus.shape == (6, seq_len + 1) and corpus.dtype == torch.long and torch.equal(corpus, again)
+        assert int(corpus.min()) >= 0 and int(corpus.max()) < vocab
+    arith = build_synthetic_corpus(num_sequences=4, seq_len=seq_len, vocab_size=vocab, seed=1, task="arith")
+    stride = (arith[:, 1] - arith[:, 0]) % vocab
+    assert torch.equal((arith[:, 1:] - arith[:, :-1]) % vocab, stride.unsqueeze(1).expand(-1, seq_len)) and int(stride.min()) >= 1
+    plen = (seq_len + 1 - 2) // 2
+    for task, answer in (("copy", lambda p: p), ("reverse", lambda p: p.flip(dims=(1,))), ("selective_copy", lambda p: p[:, ::2])):
+        seq = build_synthetic_corpus(num_sequences=5, seq_len=seq_len, vocab_size=vocab, seed=2, task=task)
+        payload = seq[:, 1 : 1 + plen]
+        want = answer(payload)
+        width = min(want.shape[1], seq_len + 1 - (2 + plen))
+        assert torch.all(seq[:, 0] == bos) and torch.all(seq[:, 1 + plen] == sep) and int(payload.max()) < pad
+        assert torch.equal(seq[:, 2 + plen : 2 + plen + width], want[:, :width])
+    ind = build_synthetic_corpus(num_sequences=5, seq_len=seq_len, vocab_size=vocab, seed=3, task="induction")
+    pairs = (seq_len + 1 - 6) // 2
+    keys, vals = ind[:, 1 : 1 + 2 * pairs : 2], ind[:, 2 : 2 + 2 * pairs : 2]
+    q_key, q_val = ind[:, 2 + 2 * pairs], ind[:, 4 + 2 * pairs]
+    assert torch.all(ind[:, 1 + 2 * pairs] == sep) and torch.all(ind[:, 3 + 2 * pairs] == sep)
+    for row in range(5):  # the queried key occurs among the keys and its value is (one of) the values stored with it
+        hits = (keys[row] == q_key[row]).nonzero().flatten()
+        assert len(hits) > 0 and any(int(vals[row, h]) == int(q_val[row]) for h in hits)
+    x, y = sample_batch(arith, batch_size=3, generator=torch.Generator().manual_seed(0), device=torch.device("cpu"))
+    assert x.shape == y.shape == (3, seq_len) and torch.equal(x[:, 1:], y[:, :-1])
+    for bad in (dict(task="sort"), dict(num_sequences=0), dict(seq_len=1), dict(vocab_size=4, task="copy")):
+        kw = dict(num_sequences=2, seq_len=8, vocab_size=16, seed=0, task="copy")
+        kw.update(bad)
+        with pytest.raises(ValueError):
+            build_synthetic_corpus(**kw)
