@@ -89,3 +89,40 @@ def test_suffix_products_and_affine_recursion_agree_with_the_chain(k, r, b, seed
     assert len(scanned) == len(chained) == k + 1
     for a, c in zip(scanned, chained):
         assert torch.allclose(a.double(), c.double(), atol=1e-4, rtol=1e-4)
+
+
+@settings(max_examples=25, deadline=None)
+@given(lines=st.lists(st.text(alphabet="abcde é", min_size=1, max_size=30), min_size=1, max_size=12),
+       shard_tokens=st.integers(1, 40), seq_len=st.integers(1, 6))
+def test_shard_writer_and_sampler_round_trip(tmp_path_factory, lines, shard_tokens, seq_len):
+    """Whatever the text and the shard size, the shards concatenate to the token stream and every sampled window is a contiguous
+    piece of one shard."""
+    import json
+
+    import numpy as np
+
+    from lbi_b200.data.bpe_tokenizer import ByteBPETokenizer
+    from lbi_b200.data.pretokenize_corpus import write_shards
+    from lbi_b200.data.token_shards import TokenShardCorpus, sample_batch_token_shards
+
+    root = tmp_path_factory.mktemp("shards")
+    text = root / "t.txt"
+    text.write_text("\n".join(lines) + "\n", encoding="utf-8")
+    tok = ByteBPETokenizer(merges=[], token_bytes={i: bytes([i]) for i in range(256)})  # no merges: one token per byte
+    manifest = write_shards("train", text, tok, root / "out", shard_tokens)
+    meta = json.loads(manifest.read_text())
+    joined = np.concatenate([np.fromfile(root / "out" / s["path"], dtype=np.int32) for s in meta["shards"]])
+    assert meta["num_tokens_total"] == len(joined) and joined.tolist() == list(text.read_bytes())
+    corpus = TokenShardCorpus(manifest)
+    longest = max(s["num_tokens"] for s in meta["shards"])
+    gen = torch.Generator().manual_seed(0)
+    if longest < seq_len + 1:
+        with pytest.raises(ValueError):
+            sample_batch_token_shards(corpus, batch_size=2, seq_len=seq_len, generator=gen, device=torch.device("cpu"))
+        return
+    x, y = sample_batch_token_shards(corpus, batch_size=4, seq_len=seq_len, generator=gen, device=torch.device("cpu"))
+    assert x.shape == y.shape == (4, seq_len) and torch.equal(x[:, 1:], y[:, :-1])
+    shards = [np.fromfile(root / "out" / s["path"], dtype=np.int32).tolist() for s in meta["shards"]]
+    for row_x, row_y in zip(x.tolist(), y.tolist()):
+        window = row_x + row_y[-1:]
+        assert any(window == sh[i : i + seq_len + 1] for sh in shards for i in range(len(sh) - seq_len))
