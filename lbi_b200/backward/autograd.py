@@ -10,6 +10,7 @@ from .base import ADResult, collect_named_grads
 
 
 def autograd_backward_step(model: nn.Module, loss: torch.Tensor | None = None, *, ce_loss: torch.Tensor | None = None) -> dict:
+    """Dense autograd gradients of ``loss`` by parameter name (``.grad`` is cleared first and left set)."""
     loss = ce_loss if loss is None else loss  # ``ce_loss`` is the reference's keyword (backward/autograd.py:27)
     model.zero_grad(set_to_none=True)
     loss.backward()

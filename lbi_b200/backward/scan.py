@@ -62,6 +62,10 @@ def lbi_scan_backward_step(
     compute_scan_diagnostic: bool = True,
     ce_loss: torch.Tensor | None = None,
 ) -> LBIBackwardResult:
+    """Exact region-local backward of one step.  With a cache whose graph was cut at every state (``detach_states=True``): loss
+    cotangents per region, Jacobians of regions 0..K-2 from ``pullback_provider``, affine suffix scan, one surrogate backward for
+    all parameters.  With a connected graph (depth regions): the reference's sequence of local VJPs through ``local_vjp_provider``.
+    Returns the named gradients, the scan-vs-chain residual, optional Jacobian statistics and the state cotangents."""
     loss = ce_loss if loss is None else loss  # ``ce_loss`` is the reference's keyword (backward/scan.py:18-27)
     if model is None or loss is None:
         raise TypeError("lbi_scan_backward_step needs a model and a loss")

@@ -107,6 +107,7 @@ class ByteBPETokenizer:
 
 
 def train_byte_bpe_tokenizer(path: str | Path, *, vocab_size: int, max_bytes: int, min_pair_count: int = 2) -> ByteBPETokenizer:
+    """Learn byte-pair merges on the first ``max_bytes`` of a file until the vocabulary reaches ``vocab_size``."""
     if vocab_size <= 256:
         raise ValueError("byte BPE vocab_size must be > 256")
     raw = Path(path).read_bytes()
@@ -155,6 +156,7 @@ def train_byte_bpe_tokenizer(path: str | Path, *, vocab_size: int, max_bytes: in
 
 def load_or_train_byte_bpe_tokenizer(*, tokenizer_path, train_path, vocab_size: int, train_bytes: int,
                                      force_train: bool = False, min_pair_count: int = 2) -> ByteBPETokenizer:
+    """Load the byte-BPE tokenizer file if present (and not ``force_train``), else train and save it."""
     path = Path(tokenizer_path)
     if path.exists() and not force_train:
         return ByteBPETokenizer.load(path)
@@ -204,6 +206,7 @@ class HFAutoTextTokenizer:
 
 
 def train_sentencepiece_bpe_tokenizer(train_path, *, model_prefix, vocab_size: int, train_bytes: int) -> SentencePieceBPETokenizer:
+    """Train a SentencePiece BPE model (byte fallback, identity normalisation, no bos / eos / pad) on the first ``train_bytes``."""
     if spm is None:
         raise ImportError("sentencepiece is required for text_bpe mode")
     raw = Path(train_path).read_bytes()
@@ -225,6 +228,7 @@ def train_sentencepiece_bpe_tokenizer(train_path, *, model_prefix, vocab_size: i
 
 def load_or_train_sentencepiece_bpe_tokenizer(*, tokenizer_path, train_path, vocab_size: int, train_bytes: int,
                                               force_train: bool = False) -> SentencePieceBPETokenizer:
+    """Load the ``.model`` file if present (and not ``force_train``), else train it."""
     model_path = Path(tokenizer_path)
     if model_path.suffix != ".model":
         model_path = model_path.with_suffix(".model")
@@ -236,6 +240,7 @@ def load_or_train_sentencepiece_bpe_tokenizer(*, tokenizer_path, train_path, voc
 
 def load_text_tokenizer(*, tokenizer_type: str, tokenizer_path, train_path, vocab_size: int, train_bytes: int,
                         force_train: bool = False) -> TextTokenizerBackend:
+    """The tokenizer backend for ``tokenizer_type`` (sentencepiece, llama, llama31, byte_bpe); pretrained types cannot be trained."""
     if tokenizer_type == "sentencepiece":
         tok = load_or_train_sentencepiece_bpe_tokenizer(tokenizer_path=tokenizer_path, train_path=train_path,
                                                         vocab_size=vocab_size, train_bytes=train_bytes, force_train=force_train)
@@ -258,6 +263,7 @@ def load_text_tokenizer(*, tokenizer_type: str, tokenizer_path, train_path, voca
 
 
 def build_token_stream(path, *, tokenizer: TextTokenizerBackend, device: torch.device | None = None) -> torch.Tensor:
+    """A text file encoded into one 1-D int64 token stream."""
     raw = Path(path).read_bytes()
     if not raw:
         raise ValueError(f"text file is empty: {path}")

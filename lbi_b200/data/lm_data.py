@@ -20,6 +20,7 @@ def build_byte_stream(path: str | Path, *, device: torch.device | None = None) -
 
 
 def split_stream_train_val(stream: torch.Tensor, *, val_fraction: float):
+    """The last ``val_fraction`` of a stream as validation, the rest as training."""
     if stream.dim() != 1:
         raise ValueError("stream must be 1D")
     if not (0.0 < val_fraction < 1.0):

@@ -22,6 +22,7 @@ def tokenizer_tag(tokenizer_type: str, vocab_size: int) -> str:
 
 
 def default_output_dir(text_corpus: str, train_path: Path, vocab_size: int, tokenizer_type: str) -> Path:
+    """Where shards go by default: below the corpus directory for bundled corpora, beside the text file otherwise."""
     tag = tokenizer_tag(tokenizer_type, vocab_size)
     try:
         inside = train_path.resolve().is_relative_to(CORPORA_ROOT.resolve())
@@ -34,6 +35,7 @@ def default_output_dir(text_corpus: str, train_path: Path, vocab_size: int, toke
 
 
 def resolve_tokenizer_path(tokenizer_type: str, tokenizer_path: str, text_corpus: str, train_path: Path, vocab_size: int) -> Path:
+    """Explicit path, pretrained root for llama types, else the SentencePiece model named after the corpus or the text file."""
     if tokenizer_path:
         return Path(tokenizer_path)
     if tokenizer_type == "llama":
@@ -46,6 +48,7 @@ def resolve_tokenizer_path(tokenizer_type: str, tokenizer_path: str, text_corpus
 
 
 def write_shards(split_name: str, src_path: Path, tokenizer: TextTokenizerBackend, out_dir: Path, shard_tokens: int) -> Path:
+    """Encode a text file line by line into ``<split>_%04d.bin`` int32 shards of about ``shard_tokens`` tokens plus ``<split>_manifest.json``."""
     out_dir.mkdir(parents=True, exist_ok=True)
     shards: list[dict] = []
     buf = np.empty(max(1, shard_tokens) + 65536, dtype=np.int32)

@@ -24,6 +24,7 @@ def build_region_ranges(layers: int, layers_per_region: int) -> list[tuple[int, 
 
 
 def split_tokens(seq_len: int, num_regions: int) -> list[tuple[int, int]]:
+    """Cut ``seq_len`` tokens into ``num_regions`` contiguous spans whose sizes differ by at most one (longer spans first)."""
     if num_regions <= 0:
         raise ValueError("num_regions must be > 0")
     if seq_len < num_regions:

@@ -51,6 +51,7 @@ def discover_run_dirs(family_dir: Path) -> list[Path]:
 
 def load_run_config(run_dir: Path, *, eval_batches: int, batch_size: int | None, seq_len: int | None,
                     device: str, tokenizer_path: str = "") -> LBITrainingConfig:
+    """The stored config of a run with checkpoint saving off and the evaluation overrides applied."""
     raw = json.loads((run_dir / "config.json").read_text(encoding="utf-8"))
     raw.update(save_checkpoints=False, resume_from="", init_from="")
     if tokenizer_path:  # the tokenizer the corpora are rebuilt with, when the run's own path is not on this machine
@@ -68,6 +69,7 @@ def load_run_config(run_dir: Path, *, eval_batches: int, batch_size: int | None,
 
 def evaluate_model(*, cfg: LBITrainingConfig, model: torch.nn.Module, val_corpus: Any, seed: int,
                    device: torch.device) -> dict[str, float]:
+    """Mean next-token cross-entropy, perplexity and tokens / s over ``cfg.eval_batches`` freshly sampled validation batches."""
     gen = torch.Generator(device=device if cfg.data_mode == "synthetic" else torch.device("cpu"))
     gen.manual_seed(int(seed))
     model.eval()
@@ -101,6 +103,7 @@ def _json_or_empty(path: Path) -> dict[str, Any]:
 
 def evaluate_run(run_dir: Path, *, checkpoint: str, eval_batches: int, batch_size: int | None, seq_len: int | None,
                  eval_seed: int, device: str, tokenizer_path: str = "") -> dict[str, Any]:
+    """Rebuild a run's model, load the chosen checkpoint, evaluate it; one row of the summary table."""
     cfg = load_run_config(run_dir, eval_batches=eval_batches, batch_size=batch_size, seq_len=seq_len, device=device,
                           tokenizer_path=tokenizer_path)
     dev = _resolve_device(cfg)

@@ -138,6 +138,7 @@ def _curve(rows: list[dict], split: str, xkey: str, ykey: str) -> dict[float, fl
 
 
 def aggregate(runs: list[dict], split: str, xkey: str, ykey: str, smooth: int = 1) -> Series | None:
+    """Mean curve (and standard-deviation band when several runs) of one metric of one split over the union of logged x values."""
     curves = [_curve(r["rows"], split, xkey, ykey) for r in runs]
     curves = [c for c in curves if c]
     if not curves:
@@ -202,6 +203,7 @@ def summarize(groups: dict[str, list[dict]]) -> list[dict[str, Any]]:
 
 
 def make_figures(groups: dict[str, list[dict]], out_dir: Path, *, dpi: int, font_scale: float, smooth: int) -> list[Path]:
+    """Write every figure of the training-curve set for the grouped runs; returns the files written."""
     written: list[Path] = []
 
     def figure(stem: str, title: str, xlabel: str, ylabel: str, parts: list[tuple[str, str, str, str, str]], logy=False) -> None:

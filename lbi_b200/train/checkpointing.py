@@ -34,6 +34,7 @@ def checkpoint_dir(run_dir: Path, cfg: Any) -> Path:
 
 
 def checkpoint_path_from_summary(summary_path: Path, *, preference: str) -> Path | None:
+    """The checkpoint file a ``summary.json`` records (latest or best first, by ``preference``), if it still exists."""
     if not summary_path.exists():
         return None
     summary = json.loads(summary_path.read_text(encoding="utf-8"))
@@ -48,6 +49,7 @@ def checkpoint_path_from_summary(summary_path: Path, *, preference: str) -> Path
 def save_checkpoint(*, run_dir: Path, filename: str, model: nn.Module, optimizer, cfg: Any, device: torch.device,
                     train_generator: torch.Generator, eval_generator: torch.Generator, step: int, tokens_seen: int,
                     best_val_ce_loss: float, best_val_step: int, extra: dict[str, Any] | None = None) -> Path:
+    """Write one checkpoint file (payload keys in the module docstring) atomically; returns its path."""
     payload: dict[str, Any] = {
         "step": int(step),
         "tokens_seen": int(tokens_seen),
@@ -99,6 +101,7 @@ def resolve_checkpoint_path(load_from: str, *, regime: str, preference: str) -> 
 
 
 def infer_existing_root_dir(load_from: str) -> Path:
+    """The experiment root (``<output_dir>/<run_name>``) that a resume source (file, run directory or root) belongs to."""
     source = Path(load_from).expanduser().resolve()
     if not source.exists():
         raise FileNotFoundError(f"checkpoint source does not exist: {source}")

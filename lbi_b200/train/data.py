@@ -20,6 +20,7 @@ __all__ = [
 
 
 def resolve_text_paths(cfg: Any) -> tuple[Path, Path | None, Path]:
+    """(train file, validation file or None, corpora root) from explicit paths or the bundled corpus name."""
     if cfg.train_text_path:
         return Path(cfg.train_text_path), (Path(cfg.val_text_path) if cfg.val_text_path else None), CORPORA_ROOT
     train_name, val_name = BUNDLED_TEXT_CORPORA[cfg.text_corpus]
@@ -33,6 +34,7 @@ def resolve_text_paths(cfg: Any) -> tuple[Path, Path | None, Path]:
 
 
 def resolve_tokenizer_path(cfg: Any, *, train_path: Path) -> Path:
+    """The tokenizer file or directory of a run: explicit path, pretrained root for llama types, else the trained SentencePiece model."""
     if cfg.tokenizer_path:
         return Path(cfg.tokenizer_path)
     pretrained = {"llama": (LLAMA_TOKENIZER_ROOT, "llama"), "llama31": (LLAMA31_TOKENIZER_ROOT, "llama31")}
@@ -46,6 +48,7 @@ def resolve_tokenizer_path(cfg: Any, *, train_path: Path) -> Path:
 
 
 def resolve_token_shards_dir(cfg: Any, *, train_path: Path) -> Path:
+    """Where the token shards of a corpus / tokenizer pair live (explicit ``token_shards_dir`` wins)."""
     tag = cfg.tokenizer_type if cfg.tokenizer_type in {"llama", "llama31"} else f"sp_bpe_{cfg.vocab_size}"
     if cfg.token_shards_dir:
         return Path(cfg.token_shards_dir)
@@ -82,6 +85,7 @@ def resolve_runtime_vocab_size(cfg: Any) -> int:
 
 
 def build_corpora(cfg: Any, *, device: torch.device):
+    """(train corpus, validation corpus) for the configured data mode: synthetic tensor, byte / token stream, or memory-mapped shards."""
     if cfg.data_mode == "synthetic":
         make = lambda n, seed: build_synthetic_corpus(num_sequences=n, seq_len=cfg.seq_len, vocab_size=cfg.vocab_size,
                                                       seed=seed, task=cfg.task, device=device)

@@ -25,6 +25,7 @@ def _prepare_run_dir(cfg: LBITrainingConfig, run_root_name: str) -> Path:
 
 
 def run_lbi_experiment(cfg: LBITrainingConfig) -> Dict[str, Any]:
+    """Run the configured variants (dense and / or lbi) into one experiment root and write its ``summary.json``."""
     cfg.vocab_size = resolve_runtime_vocab_size(cfg)
     variants = resolve_model_variants(cfg)
     root_dir = infer_existing_root_dir(cfg.resume_from) if cfg.resume_from else _prepare_run_dir(cfg, "_".join(variants) or "lbi")

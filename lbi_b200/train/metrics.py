@@ -97,6 +97,7 @@ def infer_data_info(cfg: Any, *, train_corpus: Any, val_corpus: Any, corpora_roo
 
 
 def infer_model_info(cfg: Any, *, model: nn.Module) -> dict[str, Any]:
+    """Parameter counts in total and per component, region layout and tying, as written to ``model_info.json``."""
     info: dict[str, Any] = {
         "model_class": type(model).__name__, "total_params": count_parameters(model), "layers": int(cfg.layers),
         "dim": int(cfg.dim), "d_state": int(cfg.d_state), "dt_rank": cfg.dt_rank if cfg.dt_rank is not None else "auto",
@@ -132,6 +133,7 @@ def infer_model_info(cfg: Any, *, model: nn.Module) -> dict[str, Any]:
 
 
 def write_run_metadata(*, cfg: Any, run_dir: Path, model: nn.Module, train_corpus: Any, val_corpus: Any, **_unused) -> None:
+    """Write ``config.json``, ``data_info.json`` and ``model_info.json`` of a run directory."""
     dump = lambda obj: json.dumps(obj, indent=2, sort_keys=True)
     (run_dir / "config.json").write_text(dump(cfg.to_dict()), encoding="utf-8")
     (run_dir / "data_info.json").write_text(dump(infer_data_info(cfg, train_corpus=train_corpus, val_corpus=val_corpus)), encoding="utf-8")

@@ -33,6 +33,7 @@ def build_dense_model(cfg: Any, *, backbone_spec: BackboneSpec | None = None) ->
 
 
 def build_lbi_language_model(cfg: Any, *, backbone_spec: BackboneSpec | None = None) -> LBILanguageModel:
+    """The owned LBI model of a config: backbone spec, vector-MLP interface, region plan on the configured axis, tied or own head."""
     spec = backbone_spec or build_backbone_spec(cfg)
     axis = getattr(cfg, "region_axis", "depth")
     n_regions = int(cfg.sequence_regions) if axis == "sequence" else len(build_region_ranges(spec.layers, int(cfg.region_size)))
@@ -74,6 +75,7 @@ def checkpoint_uses_legacy_lbi(checkpoint: dict[str, Any]) -> bool:
 
 def build_model_for_regime(cfg: Any, *, checkpoint: dict[str, Any] | None = None,
                            use_legacy_lbi_checkpoint: bool | None = None, use_owned_lbi: bool | None = None) -> nn.Module:
+    """The model class a run needs: dense, owned LBI, or the LBI-1 model when ``checkpoint`` carries first-release parameter names."""
     spec = build_backbone_spec(cfg)
     regime = normalize_regime_name(cfg.regime)
     if regime == LEGACY_DENSE_REGIME:

@@ -169,6 +169,7 @@ def grad_parity_skip_reason(case: GradParityCase) -> str | None:
 
 
 def build_case_model(case: GradParityCase, seed: int) -> LBILanguageModel:
+    """The model of a gradient-parity case, initialised from ``seed``."""
     torch.manual_seed(seed)
     spec = BackboneSpec(name=case.backbone_name, dim=case.dim, layers=case.layers, n_heads=4, n_kv_heads=2, d_conv=4, d_state=16,
                         headdim=16, chunk_size=8, layer_types=_HYBRID_LAYERS if case.backbone_name == "hybrid" else ())
@@ -204,6 +205,7 @@ def _parameter_metrics(name: str, ref, got, case: GradParityCase) -> ParameterMe
 
 def compute_grad_parity_trial(case: GradParityCase, seed: int, batch_index: int, *, interface_jacobian_mode: str,
                               jacobian_basis_chunk: int) -> TrialMetrics:
+    """One trial: dense autograd against the scan engine on the same batch; losses, global and per-parameter gradient metrics."""
     model = build_case_model(case, seed)
     g = torch.Generator().manual_seed(seed * 7919 + batch_index)
     ids = torch.randint(0, case.vocab_size, (case.batch_size, case.seq_len), generator=g).to(case.device_type)
