@@ -185,3 +185,11 @@ def test_the_python_api_example_of_the_readme_runs():
     scope: dict = {}
     exec(compile(code, "README.md:python-api", "exec"), scope)  # noqa: S102
     assert scope["tokens"].shape == (2, 16) and scope["first"] == scope["first"] and scope["second"] == scope["second"]
+
+
+def test_decode_benchmark_runs_on_the_cpu():
+    from lbi_b200.benchmarks import time_decode
+
+    out = time_decode.main(["--device", "cpu", "--backbone", "mamba2", "--dim", "64", "--layers", "2", "--regions", "2",
+                            "--total-len", "32", "--prompt-len", "4", "--new-tokens", "8", "--vocab", "64"])
+    assert out["cached_tokens_per_s"] > 0 and out["recompute_tokens_per_s"] > 0 and out["decode_state_bytes"] > 0
