@@ -132,11 +132,18 @@ def infer_model_info(cfg: Any, *, model: nn.Module) -> dict[str, Any]:
     return info
 
 
-def write_run_metadata(*, cfg: Any, run_dir: Path, model: nn.Module, train_corpus: Any, val_corpus: Any, **_unused) -> None:
-    """Write ``config.json``, ``data_info.json`` and ``model_info.json`` of a run directory."""
+def write_run_metadata(*, cfg: Any, run_dir: Path, model: nn.Module, train_corpus: Any, val_corpus: Any, corpora_root: Any = None,
+                       resolve_text_paths_fn=None, resolve_tokenizer_path_fn=None, resolve_token_shard_manifests_fn=None,
+                       resolve_token_shards_dir_fn=None) -> None:
+    """Write ``config.json``, ``data_info.json`` and ``model_info.json`` of a run directory (the optional arguments are passed on
+    to ``infer_data_info``)."""
     dump = lambda obj: json.dumps(obj, indent=2, sort_keys=True)
     (run_dir / "config.json").write_text(dump(cfg.to_dict()), encoding="utf-8")
-    (run_dir / "data_info.json").write_text(dump(infer_data_info(cfg, train_corpus=train_corpus, val_corpus=val_corpus)), encoding="utf-8")
+    data_info = infer_data_info(cfg, train_corpus=train_corpus, val_corpus=val_corpus, corpora_root=corpora_root,
+                                resolve_text_paths_fn=resolve_text_paths_fn, resolve_tokenizer_path_fn=resolve_tokenizer_path_fn,
+                                resolve_token_shard_manifests_fn=resolve_token_shard_manifests_fn,
+                                resolve_token_shards_dir_fn=resolve_token_shards_dir_fn)
+    (run_dir / "data_info.json").write_text(dump(data_info), encoding="utf-8")
     (run_dir / "model_info.json").write_text(dump(infer_model_info(cfg, model=model)), encoding="utf-8")
 
 
