@@ -92,6 +92,11 @@ def build(force: bool = False, verbose_ptxas: bool = False, bounds_check: bool =
     return out
 
 
-if __name__ == "__main__":
+def main() -> None:
+    """python -m lbi_b200.build [--force] [--ptxas] [--bounds-check]"""
     path = build(force="--force" in sys.argv, verbose_ptxas="--ptxas" in sys.argv, bounds_check="--bounds-check" in sys.argv)
     print(path)
+
+
+if __name__ == "__main__":
+    main()

@@ -39,3 +39,17 @@ def test_entry_point_module_has_build_and_smoke():
     entry = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(entry)
     assert callable(entry.build) and callable(entry.smoke)
+
+
+def test_package_front_door_lists_and_dispatches_commands(capsys, monkeypatch):
+    import importlib
+
+    from lbi_b200 import __main__ as front
+
+    assert front.main([]) == 0 and "train" in capsys.readouterr().out
+    assert front.main(["nope"]) == 2
+    for name, (module, _) in front.COMMANDS.items():
+        assert callable(getattr(importlib.import_module(module), "main")), name
+    monkeypatch.setenv("LBI_LAUNCH_QUIET", "1")
+    assert front.main(["launch", "dense", "--dry-run"]) == 0
+    assert "--variants dense" in capsys.readouterr().out
